@@ -1,0 +1,70 @@
+// C launch API of the sm_100a kernels. Every function enqueues on the given stream, allocates nothing and
+// returns 0 on success, a negative value for an unsupported argument, or a positive cudaError_t.
+// The Python bindings (bindings.cpp) and C callers share these symbols.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// ---- elementwise.cu ----
+int fb_embed(void* out, const void* table, const int* ids, int rows, int hidden, int vocab, cudaStream_t s);
+int fb_rmsnorm(void* out, void* x_out, const void* x, const void* res, const void* w, int rows, int hidden, float eps,
+               int centred, cudaStream_t s);
+int fb_silu_mul(void* out, const void* gu, int rows, int inter, float clamp, cudaStream_t s);
+int fb_gated_norm(void* out, const float* y, const void* z, long z_stride, const void* w, int rows, int heads, int dv,
+                  float eps, cudaStream_t s);
+int fb_gather_rows(void* out, const void* in, const int* idx, int rows, int width, cudaStream_t s);
+int fb_add_bf16(void* x, const void* y, long n, cudaStream_t s);
+int fb_bf16_to_f32(float* out, const void* in, long n, cudaStream_t s);
+
+// ---- gemv.cu ----
+int fb_gemv_bf16(void* Y, const void* X, const void* W, const void* norm_w, const void* res, int M, int N, int K,
+                 long ldx, long ldy, float eps, int centred, int out_f32, int mode, int sm_count, cudaStream_t s);
+
+// ---- gemm_tcgen05.cu ----
+// Y[M][N] = X[M][K] * W[N][K]^T (+ res), or SwiGLU over W = [gate rows | up rows] (2N rows). bf16 in/out,
+// fp32 accumulation in TMEM. workspace/counters are needed only when split_k > 1.
+int fb_gemm_bf16(void* Y, const void* X, const void* W, const void* res, int M, int N, int K, long ldx, long ldy,
+                 int mode, int split_k, float* workspace, int* counters, int* status, int sm_count, cudaStream_t s);
+long fb_gemm_workspace_bytes(int M, int N, int split_k);
+
+// ---- attn.cu ----
+int fb_attn_prep(void* q_out, void* k_cache, void* v_cache, const void* proj, long proj_stride, const void* q_norm,
+                 const void* k_norm, const float* inv_freq, const int* row_slot, const int* row_pos,
+                 const int* block_table, int max_blocks, int kv_block, int rows, int nq, int nkv, int hd, int rot,
+                 int gated, float eps, int* status, cudaStream_t s);
+int fb_attn_decode(void* out, float* o_part, float* ml_part, const void* q, const void* k_cache, const void* v_cache,
+                   const void* proj, long proj_stride, const int* row_slot, const int* row_kvlen, const int* row_base,
+                   const unsigned long long* row_mask, const int* block_table, int max_blocks, int kv_block, int rows,
+                   int nq, int nkv, int hd, int nsplit, int gated, cudaStream_t s);
+int fb_attn_prefill(void* out, const void* q, const void* k_cache, const void* v_cache, const void* proj,
+                    long proj_stride, const int* seg_slot, const int* seg_row0, const int* seg_nrows,
+                    const int* seg_pos0, const int* block_table, int max_blocks, int kv_block, int nseg, int max_rows,
+                    int nq, int nkv, int hd, int gated, cudaStream_t s);
+
+// ---- gdn.cu ----
+int fb_gdn_conv(void* out, const void* proj, long proj_stride, const void* conv_w, const void* conv_state,
+                const int* seg_slot, const int* seg_row0, const int* seg_nrows, int nseg, int max_rows, int conv_dim,
+                cudaStream_t s);
+int fb_gdn_rec(float* y, float* rec_state, void* conv_state, const void* qkv, const void* proj, long proj_stride,
+               const float* A_log, const float* dt_bias, const int* seg_slot, const int* seg_row0,
+               const int* seg_nrows, int nseg, int nk, int nv, int dk, int dv, float eps, int commit, cudaStream_t s);
+int fb_gdn_chunk(float* y, float* rec_state, void* conv_state, const void* qkv, const void* proj, long proj_stride,
+                 const float* A_log, const float* dt_bias, const int* seg_slot, const int* seg_row0,
+                 const int* seg_nrows, int nseg, int nk, int nv, int dk, int dv, float eps, int commit,
+                 cudaStream_t s);
+
+// ---- sample.cu ----
+int fb_argmax(int* ids, float* vals, int* finite, const void* logits, long stride, int rows, int vocab, int is_f32,
+              cudaStream_t s);
+int fb_sample(int* ids, const void* logits, long stride, int rows, int vocab, const void* params, const int* counts,
+              float* work, int is_f32, cudaStream_t s);
+int fb_chain_accept(int* n_accept, int* out_tokens, const int* target, const int* draft, const int* seg_row0,
+                    const int* seg_ndraft, int nseg, int max_draft, cudaStream_t s);
+
+#ifdef __cplusplus
+}
+#endif

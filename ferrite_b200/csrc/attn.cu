@@ -1,0 +1,303 @@
+// GQA attention over a paged KV cache: attn-prep (q/k RMSNorm + partial RoPE + KV page write), split-KV
+// decode / verify / tree attention, and the fixed-order merge with the sigmoid output gate.
+//
+// Counterparts in the reference: `fe_attn_prep` (`kernels/k-core/src/attn.rs:17`), `fe_attn_split` +
+// `fe_attn_combine` (`:99`, `:219`) and the tree masks of `fe_attn_vk` (`:331`). Differences: the cache is
+// paged (a block table per slot, so parking a sequence is a table move), heads and head_dim are run-time /
+// template parameters rather than compiled-in dims, and split boundaries depend only on the row's own
+// length so a row's result does not depend on what else is in the batch.
+#include "api.h"
+#include "common.cuh"
+
+namespace fb {
+
+// ---------------------------------------------------------------------------------------------------
+// attn-prep. One CTA per row, one warp per head (q heads first, then kv heads). The fused projection row is
+// [per q head: q(hd) | gate(hd)] [k heads] [v heads].
+template <int HD>
+__global__ void attn_prep_kernel(__nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_cache,
+                                 __nv_bfloat16* __restrict__ v_cache, const __nv_bfloat16* __restrict__ proj,
+                                 long proj_stride, const __nv_bfloat16* __restrict__ q_norm,
+                                 const __nv_bfloat16* __restrict__ k_norm, const float* __restrict__ inv_freq,
+                                 const int* __restrict__ row_slot, const int* __restrict__ row_pos,
+                                 const int* __restrict__ block_table, int max_blocks, int kv_block, int nq, int nkv,
+                                 int rot, int gated, float eps, int* status) {
+  constexpr int EPL = HD / 32;
+  const int row = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (warp >= nq + nkv) return;
+  const bool is_q = warp < nq;
+  const int qw = gated ? 2 * HD : HD;
+  const __nv_bfloat16* src = proj + (size_t)row * proj_stride + (is_q ? (size_t)warp * qw : (size_t)nq * qw + (size_t)(warp - nq) * HD);
+  float v[EPL];
+#pragma unroll
+  for (int j = 0; j < EPL; ++j) v[j] = bf2f(src[lane * EPL + j]);
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < EPL; ++j) ss += v[j] * v[j];
+  ss = warp_sum(ss);
+  const float r = rsqrtf(ss / (float)HD + eps);
+  const __nv_bfloat16* nw = is_q ? q_norm : k_norm;
+#pragma unroll
+  for (int j = 0; j < EPL; ++j) v[j] = v[j] * r * (1.f + bf2f(nw[lane * EPL + j]));
+  // partial RoPE, rotate-half pairing (i, i + rot/2) inside the first `rot` dims
+  const int pos = row_pos[row];
+  const int half = rot / 2;
+  const int partner_lanes = half / EPL;                  // lane distance between the two halves of a pair
+#pragma unroll
+  for (int j = 0; j < EPL; ++j) {
+    float other = __shfl_xor_sync(0xffffffffu, v[j], partner_lanes);
+    int d = lane * EPL + j;
+    if (d < rot) {
+      int i = d < half ? d : d - half;
+      float ang = (float)pos * inv_freq[i];
+      float sn, cs;
+      sincosf(ang, &sn, &cs);
+      v[j] = d < half ? (v[j] * cs - other * sn) : (v[j] * cs + other * sn);
+    }
+  }
+  if (is_q) {
+    __nv_bfloat16* dst = q_out + ((size_t)row * nq + warp) * HD;
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) dst[lane * EPL + j] = f2bf(v[j]);
+  } else {
+    const int kvh = warp - nq;
+    const int slot = row_slot[row];
+    const int blk = block_table[(size_t)slot * max_blocks + pos / kv_block];
+    if (blk < 0) { set_status(status, ST_BOUNDS); return; }
+    const size_t off = (((size_t)blk * kv_block + (pos % kv_block)) * nkv + kvh) * HD;
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) k_cache[off + lane * EPL + j] = f2bf(v[j]);
+    const __nv_bfloat16* vsrc = proj + (size_t)row * proj_stride + (size_t)nq * qw + (size_t)(nkv + kvh) * HD;
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) v_cache[off + lane * EPL + j] = vsrc[lane * EPL + j];
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// Split-KV decode attention. grid = (rows, kv heads, splits), 4 warps per CTA. A lane group of HD/8 lanes
+// owns one key at a time; every lane keeps 8 dims of K, V and of the G query heads of the group.
+constexpr int ATT_WARPS = 4;
+
+template <int HD, int G>
+__global__ void __launch_bounds__(ATT_WARPS * 32)
+attn_decode_kernel(float* __restrict__ o_part, float* __restrict__ ml_part, const __nv_bfloat16* __restrict__ q,
+                   const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
+                   const int* __restrict__ row_slot, const int* __restrict__ row_kvlen,
+                   const int* __restrict__ row_base, const unsigned long long* __restrict__ row_mask,
+                   const int* __restrict__ block_table, int max_blocks, int kv_block, int nq, int nkv, int nsplit,
+                   float scale_log2) {
+  constexpr int LPK = HD / 8;           // lanes per key
+  constexpr int KPI = 32 / LPK;         // keys per warp iteration
+  extern __shared__ float sm[];         // [ATT_WARPS][G][HD] o, then [ATT_WARPS][G][2] m,l
+  const int row = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int sub = lane % LPK, kslot = lane / LPK;
+  const int kvlen = row_kvlen[row];
+  const int base = row_base ? row_base[row] : kvlen;
+  const unsigned long long mask = row_mask ? row_mask[row] : 0ull;
+  const int slot = row_slot[row];
+  // split boundaries depend on the row's own length only
+  int per = (kvlen + nsplit - 1) / nsplit;
+  per = (per + 31) / 32 * 32;
+  const int lo = split * per, hi = min(kvlen, lo + per);
+
+  float qf[G][8];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    uint4 qv = *reinterpret_cast<const uint4*>(q + ((size_t)row * nq + (size_t)kvh * G + g) * HD + sub * 8);
+    uint32_t u[4] = {qv.x, qv.y, qv.z, qv.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) { qf[g][2 * j] = bf_lo(u[j]) * scale_log2; qf[g][2 * j + 1] = bf_hi(u[j]) * scale_log2; }
+  }
+  float m[G], l[G], o[G][8];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    m[g] = -INFINITY; l[g] = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[g][j] = 0.f;
+  }
+  const int* bt = block_table + (size_t)slot * max_blocks;
+  for (int t0 = lo + warp * KPI; t0 < hi; t0 += ATT_WARPS * KPI) {
+    const int t = t0 + kslot;
+    bool vis = t < hi;
+    if (vis && t >= base) vis = ((mask >> (t - base)) & 1ull) != 0ull;
+    uint4 kv = make_uint4(0, 0, 0, 0), vv = make_uint4(0, 0, 0, 0);
+    if (vis) {
+      const int blk = bt[t / kv_block];
+      const size_t off = (((size_t)blk * kv_block + (t % kv_block)) * nkv + kvh) * HD + sub * 8;
+      kv = ldg_stream(k_cache + off);
+      vv = ldg_stream(v_cache + off);
+    }
+    uint32_t ku[4] = {kv.x, kv.y, kv.z, kv.w}, vu[4] = {vv.x, vv.y, vv.z, vv.w};
+    float kf[8], vf[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      kf[2 * j] = bf_lo(ku[j]); kf[2 * j + 1] = bf_hi(ku[j]);
+      vf[2 * j] = bf_lo(vu[j]); vf[2 * j + 1] = bf_hi(vu[j]);
+    }
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      float s = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) s = fmaf(qf[g][j], kf[j], s);
+#pragma unroll
+      for (int off = LPK / 2; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+      if (vis) {
+        float mn = fmaxf(m[g], s);
+        float sc = exp2f(m[g] - mn);
+        float p = exp2f(s - mn);
+        l[g] = l[g] * sc + p;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[g][j] = fmaf(p, vf[j], o[g][j] * sc);
+        m[g] = mn;
+      }
+    }
+  }
+  // merge the lane groups of the warp (keys were interleaved over them)
+#pragma unroll
+  for (int off = LPK; off < 32; off <<= 1) {
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      float mo = __shfl_xor_sync(0xffffffffu, m[g], off);
+      float lo_ = __shfl_xor_sync(0xffffffffu, l[g], off);
+      float mn = fmaxf(m[g], mo);
+      float a = (m[g] == -INFINITY) ? 0.f : exp2f(m[g] - mn);
+      float b = (mo == -INFINITY) ? 0.f : exp2f(mo - mn);
+      l[g] = l[g] * a + lo_ * b;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float oo = __shfl_xor_sync(0xffffffffu, o[g][j], off);
+        o[g][j] = o[g][j] * a + oo * b;
+      }
+      m[g] = mn;
+    }
+  }
+  float* so = sm;                                   // [ATT_WARPS][G][HD]
+  float* sml = sm + ATT_WARPS * G * HD;             // [ATT_WARPS][G][2]
+  if (kslot == 0) {
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) so[((size_t)warp * G + g) * HD + sub * 8 + j] = o[g][j];
+      if (sub == 0) { sml[(warp * G + g) * 2] = m[g]; sml[(warp * G + g) * 2 + 1] = l[g]; }
+    }
+  }
+  __syncthreads();
+  // merge the warps in warp order and write this split's partial (unnormalised o, m, l)
+  for (int idx = threadIdx.x; idx < G * HD; idx += blockDim.x) {
+    int g = idx / HD, d = idx % HD;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < ATT_WARPS; ++w) M = fmaxf(M, sml[(w * G + g) * 2]);
+    float acc = 0.f, L = 0.f;
+#pragma unroll
+    for (int w = 0; w < ATT_WARPS; ++w) {
+      float mw = sml[(w * G + g) * 2];
+      float a = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
+      acc += so[((size_t)w * G + g) * HD + d] * a;
+      L += sml[(w * G + g) * 2 + 1] * a;
+    }
+    size_t qh = (size_t)kvh * G + g;
+    size_t pidx = ((size_t)row * nq + qh) * nsplit + split;
+    o_part[pidx * HD + d] = acc;
+    if (d == 0) { ml_part[pidx * 2] = M; ml_part[pidx * 2 + 1] = L; }
+  }
+}
+
+// Merge the splits in split order, normalise, apply the sigmoid gate, write bf16 [rows][nq*HD].
+template <int HD>
+__global__ void attn_combine_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict__ o_part,
+                                    const float* __restrict__ ml_part, const __nv_bfloat16* __restrict__ proj,
+                                    long proj_stride, int nq, int nsplit, int gated) {
+  const int row = blockIdx.x, qh = blockIdx.y;
+  const size_t pbase = ((size_t)row * nq + qh) * nsplit;
+  float M = -INFINITY;
+  for (int s = 0; s < nsplit; ++s) M = fmaxf(M, ml_part[(pbase + s) * 2]);
+  float L = 0.f;
+  for (int s = 0; s < nsplit; ++s) {
+    float ms = ml_part[(pbase + s) * 2];
+    if (ms != -INFINITY) L += ml_part[(pbase + s) * 2 + 1] * exp2f(ms - M);
+  }
+  const float inv = L > 0.f ? 1.f / L : 0.f;
+  for (int d = threadIdx.x; d < HD; d += blockDim.x) {
+    float acc = 0.f;
+    for (int s = 0; s < nsplit; ++s) {
+      float ms = ml_part[(pbase + s) * 2];
+      if (ms != -INFINITY) acc += o_part[(pbase + s) * HD + d] * exp2f(ms - M);
+    }
+    float v = acc * inv;
+    if (gated) v *= sigmoidf_(bf2f(proj[(size_t)row * proj_stride + (size_t)qh * 2 * HD + HD + d]));
+    out[((size_t)row * nq + qh) * HD + d] = f2bf(v);
+  }
+}
+
+template <int HD>
+static int launch_decode(int G, dim3 grid, size_t smem, cudaStream_t s, float* o_part, float* ml_part, const void* q,
+                         const void* kc, const void* vc, const int* row_slot, const int* row_kvlen,
+                         const int* row_base, const unsigned long long* row_mask, const int* bt, int max_blocks,
+                         int kv_block, int nq, int nkv, int nsplit, float scale_log2) {
+#define FB_LAUNCH_G(GV)                                                                                          \
+  case GV: {                                                                                                     \
+    auto kern = attn_decode_kernel<HD, GV>;                                                                      \
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);    \
+    kern<<<grid, ATT_WARPS * 32, smem, s>>>(o_part, ml_part, (const __nv_bfloat16*)q, (const __nv_bfloat16*)kc,  \
+                                            (const __nv_bfloat16*)vc, row_slot, row_kvlen, row_base, row_mask,   \
+                                            bt, max_blocks, kv_block, nq, nkv, nsplit, scale_log2);              \
+    break;                                                                                                       \
+  }
+  switch (G) {
+    FB_LAUNCH_G(1) FB_LAUNCH_G(2) FB_LAUNCH_G(3) FB_LAUNCH_G(4) FB_LAUNCH_G(6) FB_LAUNCH_G(8)
+    default: return -2;
+  }
+#undef FB_LAUNCH_G
+  return (int)cudaGetLastError();
+}
+
+}  // namespace fb
+
+using namespace fb;
+
+extern "C" int fb_attn_prep(void* q_out, void* k_cache, void* v_cache, const void* proj, long proj_stride,
+                            const void* q_norm, const void* k_norm, const float* inv_freq, const int* row_slot,
+                            const int* row_pos, const int* block_table, int max_blocks, int kv_block, int rows, int nq,
+                            int nkv, int hd, int rot, int gated, float eps, int* status, cudaStream_t s) {
+  if (rows <= 0) return 0;
+  int threads = 32 * (nq + nkv);
+  if (threads > 1024) return -1;
+  int epl = hd / 32;
+  if (rot % 2 || (rot / 2) % epl || ((rot / 2 / epl) & (rot / 2 / epl - 1))) return -3;
+#define FB_PREP(HDV)                                                                                              \
+  attn_prep_kernel<HDV><<<rows, threads, 0, s>>>((__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache,                  \
+      (__nv_bfloat16*)v_cache, (const __nv_bfloat16*)proj, proj_stride, (const __nv_bfloat16*)q_norm,             \
+      (const __nv_bfloat16*)k_norm, inv_freq, row_slot, row_pos, block_table, max_blocks, kv_block, nq, nkv, rot, \
+      gated, eps, status)
+  if (hd == 256) FB_PREP(256); else if (hd == 128) FB_PREP(128); else if (hd == 64) FB_PREP(64); else return -2;
+#undef FB_PREP
+  return (int)cudaGetLastError();
+}
+
+extern "C" int fb_attn_decode(void* out, float* o_part, float* ml_part, const void* q, const void* k_cache,
+                              const void* v_cache, const void* proj, long proj_stride, const int* row_slot,
+                              const int* row_kvlen, const int* row_base, const unsigned long long* row_mask,
+                              const int* block_table, int max_blocks, int kv_block, int rows, int nq, int nkv, int hd,
+                              int nsplit, int gated, cudaStream_t s) {
+  if (rows <= 0) return 0;
+  if (nq % nkv) return -1;
+  int G = nq / nkv;
+  dim3 grid(rows, nkv, nsplit);
+  size_t smem = (size_t)ATT_WARPS * G * (hd + 2) * sizeof(float);
+  float scale_log2 = 1.4426950408889634f / sqrtf((float)hd);
+  int rc;
+  if (hd == 256) rc = launch_decode<256>(G, grid, smem, s, o_part, ml_part, q, k_cache, v_cache, row_slot, row_kvlen, row_base, row_mask, block_table, max_blocks, kv_block, nq, nkv, nsplit, scale_log2);
+  else if (hd == 128) rc = launch_decode<128>(G, grid, smem, s, o_part, ml_part, q, k_cache, v_cache, row_slot, row_kvlen, row_base, row_mask, block_table, max_blocks, kv_block, nq, nkv, nsplit, scale_log2);
+  else if (hd == 64) rc = launch_decode<64>(G, grid, smem, s, o_part, ml_part, q, k_cache, v_cache, row_slot, row_kvlen, row_base, row_mask, block_table, max_blocks, kv_block, nq, nkv, nsplit, scale_log2);
+  else return -2;
+  if (rc) return rc;
+  dim3 cgrid(rows, nq);
+  int cthreads = hd >= 128 ? 128 : 64;
+  if (hd == 256) attn_combine_kernel<256><<<cgrid, cthreads, 0, s>>>((__nv_bfloat16*)out, o_part, ml_part, (const __nv_bfloat16*)proj, proj_stride, nq, nsplit, gated);
+  else if (hd == 128) attn_combine_kernel<128><<<cgrid, cthreads, 0, s>>>((__nv_bfloat16*)out, o_part, ml_part, (const __nv_bfloat16*)proj, proj_stride, nq, nsplit, gated);
+  else attn_combine_kernel<64><<<cgrid, cthreads, 0, s>>>((__nv_bfloat16*)out, o_part, ml_part, (const __nv_bfloat16*)proj, proj_stride, nq, nsplit, gated);
+  return (int)cudaGetLastError();
+}

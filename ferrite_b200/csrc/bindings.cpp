@@ -1,0 +1,178 @@
+// Python bindings: thin glue from torch tensors to the C launch API in api.h. No kernel lives here.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAStream.h>
+#include <torch/extension.h>
+
+#include "api.h"
+#include "api_ext.h"
+
+namespace {
+
+using torch::Tensor;
+
+inline cudaStream_t cur_stream() { return c10::cuda::getCurrentCUDAStream().stream(); }
+
+inline void check(int rc, const char* what) {
+  if (rc == 0) return;
+  if (rc > 0) {
+    TORCH_CHECK(false, what, ": CUDA error ", rc, " (", cudaGetErrorString((cudaError_t)rc), ")");
+  }
+  TORCH_CHECK(false, what, ": unsupported arguments (code ", rc, ")");
+}
+
+inline const void* cptr(const c10::optional<Tensor>& t) { return t.has_value() && t->defined() ? t->data_ptr() : nullptr; }
+inline void* mptr(const c10::optional<Tensor>& t) { return t.has_value() && t->defined() ? t->data_ptr() : nullptr; }
+
+int sm_count() {
+  static int n = 0;
+  if (n == 0) n = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+  return n;
+}
+
+void embed(Tensor out, Tensor table, Tensor ids) {
+  check(fb_embed(out.data_ptr(), table.data_ptr(), ids.data_ptr<int>(), (int)ids.numel(), (int)table.size(1),
+                 (int)table.size(0), cur_stream()), "embed");
+}
+
+void rmsnorm(Tensor out, Tensor x, Tensor w, double eps, bool centred, c10::optional<Tensor> res,
+             c10::optional<Tensor> x_out) {
+  int rows = (int)(x.numel() / x.size(-1));
+  check(fb_rmsnorm(out.data_ptr(), mptr(x_out), x.data_ptr(), cptr(res), w.data_ptr(), rows, (int)x.size(-1),
+                   (float)eps, centred ? 1 : 0, cur_stream()), "rmsnorm");
+}
+
+void silu_mul(Tensor out, Tensor gu, double clamp) {
+  int rows = (int)gu.size(0);
+  check(fb_silu_mul(out.data_ptr(), gu.data_ptr(), rows, (int)(gu.size(1) / 2), (float)clamp, cur_stream()), "silu_mul");
+}
+
+void gated_norm(Tensor out, Tensor y, Tensor z_base, int64_t z_off, int64_t z_stride, Tensor w, int64_t heads,
+                int64_t dv, double eps) {
+  int rows = (int)y.size(0);
+  const char* zp = (const char*)z_base.data_ptr() + z_off * 2;
+  check(fb_gated_norm(out.data_ptr(), y.data_ptr<float>(), zp, (long)z_stride, w.data_ptr(), rows, (int)heads, (int)dv,
+                      (float)eps, cur_stream()), "gated_norm");
+}
+
+void gather_rows(Tensor out, Tensor in, Tensor idx) {
+  check(fb_gather_rows(out.data_ptr(), in.data_ptr(), idx.data_ptr<int>(), (int)idx.numel(), (int)in.size(1),
+                       cur_stream()), "gather_rows");
+}
+
+void add_bf16(Tensor x, Tensor y) { check(fb_add_bf16(x.data_ptr(), y.data_ptr(), (long)x.numel(), cur_stream()), "add_bf16"); }
+
+// Y[M][N] (+)= X W^T, small M. mode 0 plain / 1 swiglu.
+void gemv(Tensor Y, Tensor X, Tensor W, c10::optional<Tensor> norm_w, c10::optional<Tensor> res, double eps,
+          bool centred, int64_t mode) {
+  int M = (int)X.size(0), K = (int)X.size(1);
+  int N = (int)(mode == 1 ? W.size(0) / 2 : W.size(0));
+  check(fb_gemv_bf16(Y.data_ptr(), X.data_ptr(), W.data_ptr(), cptr(norm_w), cptr(res), M, N, K, (long)X.stride(0),
+                     (long)Y.stride(0), (float)eps, centred ? 1 : 0, Y.scalar_type() == torch::kFloat32 ? 1 : 0,
+                     (int)mode, sm_count(), cur_stream()), "gemv");
+}
+
+int64_t gemm_workspace_bytes(int64_t M, int64_t N, int64_t split_k) {
+  return fb_gemm_workspace_bytes((int)M, (int)N, (int)split_k);
+}
+
+void gemm(Tensor Y, Tensor X, Tensor W, c10::optional<Tensor> res, int64_t mode, int64_t split_k,
+          c10::optional<Tensor> workspace, c10::optional<Tensor> counters, c10::optional<Tensor> status) {
+  int M = (int)X.size(0), K = (int)X.size(1);
+  int N = (int)(mode == 1 ? W.size(0) / 2 : W.size(0));
+  check(fb_gemm_bf16(Y.data_ptr(), X.data_ptr(), W.data_ptr(), cptr(res), M, N, K, (long)X.stride(0),
+                     (long)Y.stride(0), (int)mode, (int)split_k, (float*)mptr(workspace), (int*)mptr(counters),
+                     (int*)mptr(status), sm_count(), cur_stream()), "gemm");
+}
+
+void attn_prep(Tensor q_out, Tensor k_cache, Tensor v_cache, Tensor proj, Tensor q_norm, Tensor k_norm,
+               Tensor inv_freq, Tensor row_slot, Tensor row_pos, Tensor block_table, int64_t kv_block, int64_t nq,
+               int64_t nkv, int64_t hd, int64_t rot, bool gated, double eps, c10::optional<Tensor> status) {
+  check(fb_attn_prep(q_out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), proj.data_ptr(), (long)proj.stride(0),
+                     q_norm.data_ptr(), k_norm.data_ptr(), inv_freq.data_ptr<float>(), row_slot.data_ptr<int>(),
+                     row_pos.data_ptr<int>(), block_table.data_ptr<int>(), (int)block_table.size(1), (int)kv_block,
+                     (int)row_slot.numel(), (int)nq, (int)nkv, (int)hd, (int)rot, gated ? 1 : 0, (float)eps,
+                     (int*)mptr(status), cur_stream()), "attn_prep");
+}
+
+void attn_decode(Tensor out, Tensor o_part, Tensor ml_part, Tensor q, Tensor k_cache, Tensor v_cache, Tensor proj,
+                 Tensor row_slot, Tensor row_kvlen, c10::optional<Tensor> row_base, c10::optional<Tensor> row_mask,
+                 Tensor block_table, int64_t kv_block, int64_t nq, int64_t nkv, int64_t hd, int64_t nsplit,
+                 bool gated) {
+  check(fb_attn_decode(out.data_ptr(), o_part.data_ptr<float>(), ml_part.data_ptr<float>(), q.data_ptr(),
+                       k_cache.data_ptr(), v_cache.data_ptr(), proj.data_ptr(), (long)proj.stride(0),
+                       row_slot.data_ptr<int>(), row_kvlen.data_ptr<int>(), (const int*)cptr(row_base),
+                       (const unsigned long long*)cptr(row_mask), block_table.data_ptr<int>(),
+                       (int)block_table.size(1), (int)kv_block, (int)row_slot.numel(), (int)nq, (int)nkv, (int)hd,
+                       (int)nsplit, gated ? 1 : 0, cur_stream()), "attn_decode");
+}
+
+void attn_prefill(Tensor out, Tensor q, Tensor k_cache, Tensor v_cache, Tensor proj, Tensor seg_slot, Tensor seg_row0,
+                  Tensor seg_nrows, Tensor seg_pos0, Tensor block_table, int64_t kv_block, int64_t max_rows,
+                  int64_t nq, int64_t nkv, int64_t hd, bool gated) {
+  check(fb_attn_prefill(out.data_ptr(), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), proj.data_ptr(),
+                        (long)proj.stride(0), seg_slot.data_ptr<int>(), seg_row0.data_ptr<int>(),
+                        seg_nrows.data_ptr<int>(), seg_pos0.data_ptr<int>(), block_table.data_ptr<int>(),
+                        (int)block_table.size(1), (int)kv_block, (int)seg_slot.numel(), (int)max_rows, (int)nq,
+                        (int)nkv, (int)hd, gated ? 1 : 0, cur_stream()), "attn_prefill");
+}
+
+void gdn_conv(Tensor out, Tensor proj, Tensor conv_w, Tensor conv_state, Tensor seg_slot, Tensor seg_row0,
+              Tensor seg_nrows, int64_t max_rows) {
+  check(fb_gdn_conv(out.data_ptr(), proj.data_ptr(), (long)proj.stride(0), conv_w.data_ptr(), conv_state.data_ptr(),
+                    seg_slot.data_ptr<int>(), seg_row0.data_ptr<int>(), seg_nrows.data_ptr<int>(),
+                    (int)seg_slot.numel(), (int)max_rows, (int)out.size(1), cur_stream()), "gdn_conv");
+}
+
+void gdn_rec(Tensor y, Tensor rec_state, Tensor conv_state, Tensor qkv, Tensor proj, Tensor A_log, Tensor dt_bias,
+             Tensor seg_slot, Tensor seg_row0, Tensor seg_nrows, int64_t nk, int64_t nv, int64_t dk, int64_t dv,
+             double eps, bool commit, bool chunked) {
+  auto fn = chunked ? fb_gdn_chunk : fb_gdn_rec;
+  check(fn(y.data_ptr<float>(), rec_state.data_ptr<float>(), conv_state.data_ptr(), qkv.data_ptr(), proj.data_ptr(),
+           (long)proj.stride(0), A_log.data_ptr<float>(), dt_bias.data_ptr<float>(), seg_slot.data_ptr<int>(),
+           seg_row0.data_ptr<int>(), seg_nrows.data_ptr<int>(), (int)seg_slot.numel(), (int)nk, (int)nv, (int)dk,
+           (int)dv, (float)eps, commit ? 1 : 0, cur_stream()), "gdn_rec");
+}
+
+void argmax(Tensor ids, Tensor logits, c10::optional<Tensor> vals, c10::optional<Tensor> finite) {
+  check(fb_argmax(ids.data_ptr<int>(), (float*)mptr(vals), (int*)mptr(finite), logits.data_ptr(),
+                  (long)logits.stride(0), (int)logits.size(0), (int)logits.size(1),
+                  logits.scalar_type() == torch::kFloat32 ? 1 : 0, cur_stream()), "argmax");
+}
+
+void sample(Tensor ids, Tensor logits, Tensor params, c10::optional<Tensor> counts, Tensor work) {
+  check(fb_sample(ids.data_ptr<int>(), logits.data_ptr(), (long)logits.stride(0), (int)logits.size(0),
+                  (int)logits.size(1), params.data_ptr(), (const int*)cptr(counts), work.data_ptr<float>(),
+                  logits.scalar_type() == torch::kFloat32 ? 1 : 0, cur_stream()), "sample");
+}
+
+void chain_accept(Tensor n_accept, Tensor out_tokens, Tensor target, Tensor draft, Tensor seg_row0, Tensor seg_ndraft,
+                  int64_t max_draft) {
+  check(fb_chain_accept(n_accept.data_ptr<int>(), out_tokens.data_ptr<int>(), target.data_ptr<int>(),
+                        draft.data_ptr<int>(), seg_row0.data_ptr<int>(), seg_ndraft.data_ptr<int>(),
+                        (int)seg_row0.numel(), (int)max_draft, cur_stream()), "chain_accept");
+}
+
+}  // namespace
+
+void register_ext(pybind11::module_& m);
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("embed", &embed);
+  m.def("rmsnorm", &rmsnorm);
+  m.def("silu_mul", &silu_mul);
+  m.def("gated_norm", &gated_norm);
+  m.def("gather_rows", &gather_rows);
+  m.def("add_bf16", &add_bf16);
+  m.def("gemv", &gemv);
+  m.def("gemm", &gemm);
+  m.def("gemm_workspace_bytes", &gemm_workspace_bytes);
+  m.def("attn_prep", &attn_prep);
+  m.def("attn_decode", &attn_decode);
+  m.def("attn_prefill", &attn_prefill);
+  m.def("gdn_conv", &gdn_conv);
+  m.def("gdn_rec", &gdn_rec);
+  m.def("argmax", &argmax);
+  m.def("sample", &sample);
+  m.def("chain_accept", &chain_accept);
+  register_ext(m);
+}

@@ -1,0 +1,172 @@
+// Gated DeltaNet: causal depthwise conv1d + SiLU, and the gated delta-rule recurrence
+//   S = S * g;  delta = (v - S^T k) * beta;  S += k (x) delta;  y = S^T q
+// with q, k L2-normalised per head (q also scaled by 1/sqrt(dk)), g = exp(-exp(A_log) * softplus(a + dt_bias)),
+// beta = sigmoid(b). State S is fp32 [slot][head][dk][dv].
+//
+// Counterparts in the reference: `fe_gdn_conv` (`kernels/k-core/src/gdn.rs:30`), `fe_gdn_rec` / `fe_gdn_rec2`
+// (`:117`, `:241`) and, through the `commit` flag and saved projections, `fe_gdn_replay` (`:260`).
+// The conv kernel never writes state; the recurrence kernel (which runs after it on the stream) commits both
+// the recurrent state and the conv tail, so no CTA reads state another CTA of the same launch writes.
+#include "api.h"
+#include "common.cuh"
+
+namespace fb {
+
+// proj row layout: [q (nk*dk) | k (nk*dk) | v (nv*dv) | z (nv*dv) | b (nv) | a (nv)]
+// conv_state: [slot][conv_k-1][conv_dim] bf16, oldest input first.
+// grid = (ceil(conv_dim/256), row chunks of 32, segments)
+__global__ void gdn_conv_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ proj,
+                                long proj_stride, const __nv_bfloat16* __restrict__ conv_w,
+                                const __nv_bfloat16* __restrict__ conv_state, const int* __restrict__ seg_slot,
+                                const int* __restrict__ seg_row0, const int* __restrict__ seg_nrows, int conv_dim) {
+  constexpr int CK = 4, CHUNK = 32;
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int seg = blockIdx.z;
+  const int n = seg_nrows[seg];
+  const int r0 = blockIdx.y * CHUNK;
+  if (c >= conv_dim || r0 >= n) return;
+  const int row0 = seg_row0[seg];
+  const int slot = seg_slot[seg];
+  float w[CK];
+#pragma unroll
+  for (int j = 0; j < CK; ++j) w[j] = bf2f(conv_w[(size_t)c * CK + j]);
+  const __nv_bfloat16* st = conv_state + (size_t)slot * (CK - 1) * conv_dim + c;
+  float win[CK - 1];
+#pragma unroll
+  for (int j = 0; j < CK - 1; ++j) {
+    int r = r0 - (CK - 1) + j;                      // time index relative to the segment start
+    win[j] = r >= 0 ? bf2f(proj[(size_t)(row0 + r) * proj_stride + c]) : bf2f(st[(size_t)(CK - 1 + r) * conv_dim]);
+  }
+  const int rend = min(n, r0 + CHUNK);
+  for (int r = r0; r < rend; ++r) {
+    float x = bf2f(proj[(size_t)(row0 + r) * proj_stride + c]);
+    float acc = w[0] * win[0] + w[1] * win[1] + w[2] * win[2] + w[3] * x;
+    out[(size_t)(row0 + r) * conv_dim + c] = f2bf(siluf_(acc));
+    win[0] = win[1]; win[1] = win[2]; win[2] = x;
+  }
+}
+
+// Recurrence over the rows of one segment for one value head. blockDim = DV * 8; thread (col = tid % DV,
+// part = tid / DV) keeps DK/8 rows of state column `col` in registers across the whole segment.
+template <int DK, int DV>
+__global__ void __launch_bounds__(DV * 8)
+gdn_rec_kernel(float* __restrict__ y, float* __restrict__ rec_state, __nv_bfloat16* __restrict__ conv_state,
+               const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ proj, long proj_stride,
+               const float* __restrict__ A_log, const float* __restrict__ dt_bias, const int* __restrict__ seg_slot,
+               const int* __restrict__ seg_row0, const int* __restrict__ seg_nrows, int nk, int nv, float eps,
+               int commit) {
+  constexpr int PARTS = 8, RP = DK / PARTS, CK = 4;
+  __shared__ float qs[DK], ks[DK], vs[DV];
+  __shared__ float red1[PARTS][DV], red2[PARTS][DV];
+  __shared__ float ssq[2][DK / 32];
+  const int h = blockIdx.x, seg = blockIdx.y;
+  const int tid = threadIdx.x, col = tid % DV, part = tid / DV;
+  const int n = seg_nrows[seg];
+  if (n <= 0) return;
+  const int row0 = seg_row0[seg], slot = seg_slot[seg];
+  const int kh = h / (nv / nk);
+  const int conv_dim = 2 * nk * DK + nv * DV;
+  const int q_off = kh * DK, k_off = nk * DK + kh * DK, v_off = 2 * nk * DK + h * DV;
+  const int b_off = conv_dim + nv * DV + h, a_off = b_off + nv;
+  float* Sg = rec_state + (((size_t)slot * nv + h) * DK) * DV;
+  float S[RP];
+#pragma unroll
+  for (int i = 0; i < RP; ++i) S[i] = Sg[(size_t)(part * RP + i) * DV + col];
+  const float expA = __expf(A_log[h]);
+  const float dtb = dt_bias[h];
+  const float qscale = rsqrtf((float)DK);
+
+  for (int r = 0; r < n; ++r) {
+    const __nv_bfloat16* xr = qkv + (size_t)(row0 + r) * conv_dim;
+    if (tid < DK) {
+      float qv = bf2f(xr[q_off + tid]), kv = bf2f(xr[k_off + tid]);
+      qs[tid] = qv; ks[tid] = kv;
+      float sq = warp_sum(qv * qv), sk = warp_sum(kv * kv);
+      if ((tid & 31) == 0) { ssq[0][tid >> 5] = sq; ssq[1][tid >> 5] = sk; }
+    }
+    if (tid < DV) vs[tid] = bf2f(xr[v_off + tid]);
+    __syncthreads();
+    float sq = 0.f, sk = 0.f;
+#pragma unroll
+    for (int i = 0; i < DK / 32; ++i) { sq += ssq[0][i]; sk += ssq[1][i]; }
+    const float rq = rsqrtf(sq + eps) * qscale, rk = rsqrtf(sk + eps);
+    const __nv_bfloat16* pr = proj + (size_t)(row0 + r) * proj_stride;
+    const float beta = sigmoidf_(bf2f(pr[b_off]));
+    const float g = __expf(-expA * softplusf_(bf2f(pr[a_off]) + dtb));
+    float p = 0.f;
+#pragma unroll
+    for (int i = 0; i < RP; ++i) p = fmaf(S[i], ks[part * RP + i], p);
+    red1[part][col] = p;
+    __syncthreads();
+    float kvv = 0.f;
+#pragma unroll
+    for (int i = 0; i < PARTS; ++i) kvv += red1[i][col];
+    kvv *= g * rk;
+    const float delta = (vs[col] - kvv) * beta;
+    float yp = 0.f;
+#pragma unroll
+    for (int i = 0; i < RP; ++i) {
+      S[i] = fmaf(ks[part * RP + i] * rk, delta, S[i] * g);
+      yp = fmaf(S[i], qs[part * RP + i], yp);
+    }
+    red2[part][col] = yp;
+    __syncthreads();
+    if (part == 0) {
+      float yy = 0.f;
+#pragma unroll
+      for (int i = 0; i < PARTS; ++i) yy += red2[i][col];
+      y[((size_t)(row0 + r) * nv + h) * DV + col] = yy * rq;
+    }
+  }
+  if (commit) {
+#pragma unroll
+    for (int i = 0; i < RP; ++i) Sg[(size_t)(part * RP + i) * DV + col] = S[i];
+    // conv tail: the last CK-1 raw inputs of the channels this head owns (q/k channels: first head of the group)
+    __nv_bfloat16* st = conv_state + (size_t)slot * (CK - 1) * conv_dim;
+    const bool own_qk = (h % (nv / nk)) == 0;
+    const int nch = DV + (own_qk ? 2 * DK : 0);
+    for (int idx = tid; idx < nch; idx += blockDim.x) {
+      int c = idx < DV ? v_off + idx : (idx < DV + DK ? q_off + (idx - DV) : k_off + (idx - DV - DK));
+      __nv_bfloat16 nw[CK - 1];
+#pragma unroll
+      for (int j = 0; j < CK - 1; ++j) {
+        int t = n - (CK - 1) + j;
+        nw[j] = t >= 0 ? proj[(size_t)(row0 + t) * proj_stride + c] : st[(size_t)(CK - 1 + t) * conv_dim + c];
+      }
+#pragma unroll
+      for (int j = 0; j < CK - 1; ++j) st[(size_t)j * conv_dim + c] = nw[j];
+    }
+  }
+}
+
+}  // namespace fb
+
+using namespace fb;
+
+extern "C" int fb_gdn_conv(void* out, const void* proj, long proj_stride, const void* conv_w, const void* conv_state,
+                           const int* seg_slot, const int* seg_row0, const int* seg_nrows, int nseg, int max_rows,
+                           int conv_dim, cudaStream_t s) {
+  if (nseg <= 0 || max_rows <= 0) return 0;
+  dim3 grid((conv_dim + 255) / 256, (max_rows + 31) / 32, nseg);
+  gdn_conv_kernel<<<grid, 256, 0, s>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)proj, proj_stride,
+                                       (const __nv_bfloat16*)conv_w, (const __nv_bfloat16*)conv_state, seg_slot,
+                                       seg_row0, seg_nrows, conv_dim);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int fb_gdn_rec(float* y, float* rec_state, void* conv_state, const void* qkv, const void* proj,
+                          long proj_stride, const float* A_log, const float* dt_bias, const int* seg_slot,
+                          const int* seg_row0, const int* seg_nrows, int nseg, int nk, int nv, int dk, int dv,
+                          float eps, int commit, cudaStream_t s) {
+  if (nseg <= 0) return 0;
+  if (nv % nk) return -1;
+  dim3 grid(nv, nseg);
+  if (dk == 128 && dv == 128)
+    gdn_rec_kernel<128, 128><<<grid, 1024, 0, s>>>(y, rec_state, (__nv_bfloat16*)conv_state, (const __nv_bfloat16*)qkv,
+        (const __nv_bfloat16*)proj, proj_stride, A_log, dt_bias, seg_slot, seg_row0, seg_nrows, nk, nv, eps, commit);
+  else if (dk == 64 && dv == 64)
+    gdn_rec_kernel<64, 64><<<grid, 512, 0, s>>>(y, rec_state, (__nv_bfloat16*)conv_state, (const __nv_bfloat16*)qkv,
+        (const __nv_bfloat16*)proj, proj_stride, A_log, dt_bias, seg_slot, seg_row0, seg_nrows, nk, nv, eps, commit);
+  else return -2;
+  return (int)cudaGetLastError();
+}

@@ -1,0 +1,129 @@
+// Small-M weight-streaming dot-product core shared by the plain GEMV kernels and the fused
+// GEMV + all-reduce kernels. Y[m][n] = sum_k X[m][k] * W[n][k] for M <= 8 activation rows.
+//
+// The reference's decode GEMVs (`fe_gemv_bf16` `kernels/k-core/src/gemm.rs:149`, the EXL3 family
+// `kernels/k-exl3/src/gemv.rs:227`) are bandwidth kernels; on a B200 the same job needs ~35 KB of loads in
+// flight per SM to cover HBM3e latency, so every lane keeps R x U independent 16-byte weight loads in flight
+// and the activations are staged once per CTA in shared memory (normalised on the way in when asked).
+//
+// A lane accumulates its k positions in increasing order whatever M is, so a row's bits do not depend on
+// how many other rows ride in the same launch (the reference's batch-invariance rule, `TP2.md:99-105`).
+#pragma once
+#include "common.cuh"
+
+namespace fb {
+
+constexpr int GEMV_THREADS = 256;
+constexpr int GEMV_WARPS = GEMV_THREADS / 32;
+constexpr int GEMV_U = 4;                 // 16-byte loads in flight per lane per weight row
+constexpr int GEMV_STEP = 256;            // k elements a warp covers per load (32 lanes x 8 bf16)
+constexpr int GEMV_SMEM_BYTES = 96 * 1024;
+
+struct GemvArgs {
+  const __nv_bfloat16* X;       // [M][ldx]
+  const __nv_bfloat16* W;       // [N or 2N][K]
+  const __nv_bfloat16* norm_w;  // [K] or null: RMSNorm prologue on X rows
+  const __nv_bfloat16* res;     // [M][ldy] or null: residual added in the epilogue
+  void* Y;                      // [M][ldy] bf16, or fp32 when out_f32
+  int M, N, K;
+  long ldx, ldy;
+  float eps;
+  int centred;
+  int out_f32;
+  int rows_per_cta;
+  int kc;                       // staged chunk length (multiple of GEMV_STEP)
+};
+
+__host__ __device__ inline int gemv_chunk_len(int M, int K) {
+  int kpad = (K + GEMV_STEP - 1) / GEMV_STEP * GEMV_STEP;
+  int cap = (GEMV_SMEM_BYTES / 2 / M) / (GEMV_STEP * GEMV_U) * (GEMV_STEP * GEMV_U);
+  return kpad < cap ? kpad : cap;
+}
+
+// Stage X[:, k0:k0+kc) into shared memory as bf16, applying the RMSNorm scale when present.
+template <int M>
+__device__ __forceinline__ void gemv_stage_x(const GemvArgs& a, __nv_bfloat16* xs, const float* rscale, int k0,
+                                             int kc) {
+  for (int idx = threadIdx.x; idx < M * (kc / 8); idx += blockDim.x) {
+    int m = idx / (kc / 8), c = idx % (kc / 8);
+    int k = k0 + c * 8;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (m < a.M && k < a.K) {
+      v = *reinterpret_cast<const uint4*>(a.X + (size_t)m * a.ldx + k);
+      if (a.norm_w) {
+        uint4 wv = __ldg(reinterpret_cast<const uint4*>(a.norm_w + k));
+        uint32_t xu[4] = {v.x, v.y, v.z, v.w}, wu[4] = {wv.x, wv.y, wv.z, wv.w}, o[4];
+        float r = rscale[m];
+        float add = a.centred ? 1.f : 0.f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          o[j] = pack_bf2(bf_lo(xu[j]) * r * (bf_lo(wu[j]) + add), bf_hi(xu[j]) * r * (bf_hi(wu[j]) + add));
+        v = make_uint4(o[0], o[1], o[2], o[3]);
+      }
+    }
+    *reinterpret_cast<uint4*>(xs + (size_t)m * kc + c * 8) = v;
+  }
+}
+
+// rscale[m] = rsqrt(mean(x_m^2) + eps) for every row (all threads of the CTA take part)
+template <int M>
+__device__ __forceinline__ void gemv_row_scales(const GemvArgs& a, float* rscale, float* scratch) {
+  for (int m = 0; m < M; ++m) {
+    float ss = 0.f;
+    if (m < a.M) {
+      for (int k = threadIdx.x * 8; k < a.K; k += blockDim.x * 8) {
+        uint4 v = *reinterpret_cast<const uint4*>(a.X + (size_t)m * a.ldx + k);
+        uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { float x0 = bf_lo(u[j]), x1 = bf_hi(u[j]); ss += x0 * x0 + x1 * x1; }
+      }
+    }
+    float tot = block_sum(ss, scratch);
+    if (threadIdx.x == 0) rscale[m] = rsqrtf(tot / (float)a.K + a.eps);
+  }
+  __syncthreads();
+}
+
+// Accumulate R weight rows against the staged chunk. wrow[r] points at W[row_r][k0].
+template <int M, int R>
+__device__ __forceinline__ void gemv_accumulate(float (&acc)[R][M], const __nv_bfloat16* const (&wrow)[R],
+                                                const __nv_bfloat16* xs, int kc, int kvalid) {
+  const int lane = threadIdx.x & 31;
+  for (int base = 0; base < kc; base += GEMV_STEP * GEMV_U) {
+    uint4 wv[R][GEMV_U];
+#pragma unroll
+    for (int u = 0; u < GEMV_U; ++u) {
+      int k = base + u * GEMV_STEP + lane * 8;
+#pragma unroll
+      for (int r = 0; r < R; ++r)
+        wv[r][u] = (k < kvalid) ? ldg_stream(wrow[r] + k) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int u = 0; u < GEMV_U; ++u) {
+      int k = base + u * GEMV_STEP + lane * 8;
+      if (k >= kc) continue;
+      float wf[R][8];
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        uint32_t wu[4] = {wv[r][u].x, wv[r][u].y, wv[r][u].z, wv[r][u].w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { wf[r][2 * j] = bf_lo(wu[j]); wf[r][2 * j + 1] = bf_hi(wu[j]); }
+      }
+#pragma unroll
+      for (int m = 0; m < M; ++m) {
+        uint4 xv = *reinterpret_cast<const uint4*>(xs + (size_t)m * kc + k);
+        uint32_t xu[4] = {xv.x, xv.y, xv.z, xv.w};
+        float xf[8];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { xf[2 * j] = bf_lo(xu[j]); xf[2 * j + 1] = bf_hi(xu[j]); }
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[r][m] = fmaf(wf[r][j], xf[j], acc[r][m]);
+        }
+      }
+    }
+  }
+}
+
+}  // namespace fb

@@ -1,0 +1,107 @@
+"""Engine facade: builds the executor for a device (CUDA kernels on a GPU, PyTorch ops on CPU) and offers the
+row-level calls the scheduler, the CLI and the benchmarks use.
+
+The public surface mirrors the reference's engine API (`crates/fe-model/ENGINE_API.md`): `forward` over rows
+of several slots, `prefill` in chunks cut on a fixed grid, `commit`-style slot bookkeeping, greedy `generate`.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from ..config import EngineConfig, ModelConfig
+from ..models.weights import Weights, init_weights, shard_weights
+from .executor import Executor, Segment, StepBatch
+
+
+def prompt_cuts(n: int, chunk: int, align: int) -> List[int]:
+    """Chunk lengths for an n-token prompt: full chunks of `chunk` rows cut on the `align` grid, and no tail of
+    16 rows or fewer (it is merged into the previous chunk). Cuts depend only on n, so a resumed prompt is cut
+    like a fresh one (reference `prompt_cut`, `crates/fe-model/src/sched.rs:636-719`)."""
+    chunk = max(align, chunk // align * align)
+    out: List[int] = []
+    left = n
+    while left > 0:
+        take = min(chunk, left)
+        if 0 < left - take <= 16:
+            take = left
+        out.append(take)
+        left -= take
+    return out
+
+
+class Engine:
+    def __init__(self, cfg: ModelConfig, weights: Optional[Weights] = None, ecfg: Optional[EngineConfig] = None,
+                 device: Optional[str] = None, seed: int = 0, tp=None):
+        self.full_cfg = cfg
+        self.ecfg = ecfg or EngineConfig()
+        if device is None:
+            device = "cuda" if torch.cuda.is_available() else "cpu"
+        self.device = torch.device(device)
+        on_gpu = self.device.type == "cuda"
+        self.dtype = torch.bfloat16 if on_gpu else torch.float32
+        world = tp.world if tp is not None else 1
+        rank = tp.rank if tp is not None else 0
+        if weights is None:
+            weights = init_weights(cfg, seed=seed, dtype=self.dtype, device=self.device)
+        if world > 1:
+            weights = shard_weights(cfg, weights, rank, world)
+        weights = {k: (v.to(self.device) if v.dtype == torch.float32 and k.endswith(("A_log", "dt_bias", "router_bias"))
+                       else v.to(self.device, self.dtype)) for k, v in weights.items()}
+        self.cfg = cfg.shard(world)
+        if on_gpu:
+            from ..ops.cuda_ops import CudaOps
+            ops = CudaOps(self.device, self.dtype)
+        else:
+            from ..ops.torch_ops import TorchOps
+            ops = TorchOps(self.device, self.dtype)
+        self.ops = ops
+        self.tp = tp
+        self.ex = Executor(self.cfg, weights, self.ecfg, ops, tp=tp, full_cfg=cfg)
+        self.slot_len: List[int] = [0] * self.ecfg.n_slots
+
+    # ---- rows ------------------------------------------------------------------------------------
+    def forward(self, segments: Sequence[Segment], commit: bool = True, greedy: bool = True):
+        out = self.ex.forward(StepBatch(list(segments), commit=commit), greedy=greedy)
+        if commit:
+            for s in segments:
+                self.slot_len[s.slot] = s.pos0 + len(s.tokens)
+        return out
+
+    def check(self) -> None:
+        """Raise when a kernel recorded a bounded-wait timeout or a bounds error in the status word."""
+        code = self.ops.status()
+        if code:
+            raise RuntimeError(f"device status {code}: a kernel wait ran out or an index was out of range")
+
+    def reset_slot(self, slot: int) -> None:
+        self.ex.reset_slot(slot)
+        self.slot_len[slot] = 0
+
+    # ---- prompts ---------------------------------------------------------------------------------
+    def prefill(self, slot: int, tokens: Sequence[int], pos0: Optional[int] = None, greedy: bool = True):
+        """Run a prompt (or the rest of one) through the slot in chunks; returns the output of the last chunk."""
+        pos = self.slot_len[slot] if pos0 is None else pos0
+        out = None
+        i = 0
+        for n in prompt_cuts(len(tokens), self.ecfg.prefill_chunk, self.ecfg.prompt_align):
+            last = i + n == len(tokens)
+            seg = Segment(slot, pos, list(tokens[i:i + n]), "last" if last else "none")
+            out = self.forward([seg], commit=True, greedy=greedy)
+            pos += n
+            i += n
+        return out
+
+    @torch.no_grad()
+    def generate(self, prompt: Sequence[int], n_new: int, slot: int = 0) -> List[int]:
+        """Greedy decode of n_new tokens after the prompt."""
+        self.reset_slot(slot)
+        _, picks, _ = self.prefill(slot, prompt)
+        tok = int(picks[0][0])
+        out: List[int] = []
+        for _ in range(n_new):
+            out.append(tok)
+            _, picks, _ = self.forward([Segment(slot, self.slot_len[slot], [tok], "last")])
+            tok = int(picks[0][0])
+        return out

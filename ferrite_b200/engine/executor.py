@@ -1,0 +1,334 @@
+"""Model executor: weights, per-slot state and the forward pass over a batch of rows.
+
+Mechanism half of the reference's two-layer engine API (`crates/fe-model/ENGINE_API.md`; `Engine::forward_ex`
+`crates/fe-model/src/model.rs:2170`, `enqueue_layer` `:2981-3204`, the CUDA-graph cache `:2648-2684`, cache
+primitives `:1846-2141`): rows in, logits out, commit, slot copy / snapshot. Policy lives in `scheduler.py`.
+
+A row is (token, slot, position). Rows of one slot form a segment (contiguous, increasing positions): a decode
+row, a chain of verify rows, or a prompt chunk. State per slot: paged KV for the attention layers (a block
+table per slot), and for every Gated DeltaNet layer an fp32 recurrent state plus a 3-tap conv tail.
+"""
+from __future__ import annotations
+
+import math
+from collections import OrderedDict
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from ..config import EngineConfig, ModelConfig
+from ..models.weights import Weights
+
+
+@dataclass
+class Segment:
+    slot: int
+    pos0: int
+    tokens: List[int]
+    want_logits: str = "last"       # "last" | "all" | "none"
+
+
+@dataclass
+class StepBatch:
+    segments: List[Segment]
+    commit: bool = True             # False: verify rows (GDN state untouched; KV rows are overwritten later)
+
+    @property
+    def n_rows(self) -> int:
+        return sum(len(s.tokens) for s in self.segments)
+
+
+class BlockPool:
+    """Free list of KV pages shared by all slots (and by parked sequences)."""
+
+    def __init__(self, n_blocks: int):
+        self.free: List[int] = list(range(n_blocks - 1, -1, -1))
+        self.n_blocks = n_blocks
+
+    def alloc(self) -> int:
+        if not self.free:
+            raise MemoryError("KV block pool exhausted")
+        return self.free.pop()
+
+    def release(self, blocks: Sequence[int]) -> None:
+        self.free.extend(int(b) for b in blocks if b >= 0)
+
+    @property
+    def n_free(self) -> int:
+        return len(self.free)
+
+
+def _bucket(n: int) -> int:
+    """Row-count buckets for graph keys: exact up to 8, then powers of two."""
+    if n <= 8:
+        return n
+    return 1 << (n - 1).bit_length()
+
+
+class Executor:
+    def __init__(self, cfg: ModelConfig, weights: Weights, ecfg: EngineConfig, ops, tp=None, full_cfg: Optional[ModelConfig] = None):
+        self.cfg = cfg                       # per-rank shapes
+        self.full_cfg = full_cfg or cfg
+        self.w = weights
+        self.ecfg = ecfg
+        self.ops = ops
+        self.tp = tp
+        self.device = ops.device
+        self.dtype = ops.dtype
+        c = cfg
+        self.kinds = c.layer_kinds
+        self.max_blocks = (ecfg.max_ctx + ecfg.kv_block - 1) // ecfg.kv_block
+        n_blocks = ecfg.n_slots * self.max_blocks + (int(ecfg.park_gb * (1 << 30) / max(1, self.kv_block_bytes())) if ecfg.park_gb > 0 else 0)
+        self.pool = BlockPool(n_blocks)
+        dev, dt = self.device, self.dtype
+        self.k_cache: Dict[int, torch.Tensor] = {}
+        self.v_cache: Dict[int, torch.Tensor] = {}
+        self.rec_state: Dict[int, torch.Tensor] = {}
+        self.conv_state: Dict[int, torch.Tensor] = {}
+        for i, kind in enumerate(self.kinds):
+            if kind == "attn":
+                self.k_cache[i] = torch.zeros(n_blocks, ecfg.kv_block, c.n_kv, c.head_dim, dtype=dt, device=dev)
+                self.v_cache[i] = torch.zeros(n_blocks, ecfg.kv_block, c.n_kv, c.head_dim, dtype=dt, device=dev)
+            elif kind == "gdn":
+                self.rec_state[i] = torch.zeros(ecfg.n_slots, c.lin_v_heads, c.lin_dk, c.lin_dv, dtype=torch.float32, device=dev)
+                self.conv_state[i] = torch.zeros(ecfg.n_slots, c.conv_k - 1, c.conv_dim, dtype=dt, device=dev)
+        self.block_table_host = torch.full((ecfg.n_slots, self.max_blocks), -1, dtype=torch.int32)
+        self.block_table = self.block_table_host.to(dev)
+        self.slot_blocks: List[List[int]] = [[] for _ in range(ecfg.n_slots)]
+        half = c.rotary_dim // 2
+        inv = c.rope_theta ** (-torch.arange(half, dtype=torch.float64) / half)
+        self.inv_freq = inv.float().to(dev)
+        # static step metadata (graph replays read these buffers)
+        R = ecfg.max_step_rows
+        S = max(ecfg.n_slots, 1) * 2
+        self.meta_i32 = torch.zeros(5 * R + 4 * S, dtype=torch.int32, device=dev)
+        self.meta_host = torch.zeros(5 * R + 4 * S, dtype=torch.int32, pin_memory=(dev.type == "cuda"))
+        self._R, self._S = R, S
+        self.graphs: "OrderedDict[tuple, tuple]" = OrderedDict()
+        self.taps: List[torch.Tensor] = []
+        self.profile = None
+
+    # ---- sizes -----------------------------------------------------------------------------------
+    def kv_block_bytes(self) -> int:
+        c, e = self.cfg, self.ecfg
+        per = 2 * e.kv_block * c.n_kv * c.head_dim * 2
+        return per * max(1, self.cfg.n_attn)
+
+    # ---- block tables -----------------------------------------------------------------------------
+    def ensure_capacity(self, slot: int, n_tokens: int) -> None:
+        need = (n_tokens + self.ecfg.kv_block - 1) // self.ecfg.kv_block
+        if need > self.max_blocks:
+            raise ValueError(f"sequence of {n_tokens} tokens exceeds max_ctx {self.ecfg.max_ctx}")
+        blocks = self.slot_blocks[slot]
+        changed = False
+        while len(blocks) < need:
+            b = self.pool.alloc()
+            self.block_table_host[slot, len(blocks)] = b
+            blocks.append(b)
+            changed = True
+        if changed:
+            self.block_table.copy_(self.block_table_host, non_blocking=True)
+
+    def reset_slot(self, slot: int) -> None:
+        """Free the slot's pages and zero its recurrent state (reference `reset_slot` `model.rs:2141`)."""
+        self.pool.release(self.slot_blocks[slot])
+        self.slot_blocks[slot] = []
+        self.block_table_host[slot].fill_(-1)
+        self.block_table.copy_(self.block_table_host, non_blocking=True)
+        for t in self.rec_state.values():
+            t[slot].zero_()
+        for t in self.conv_state.values():
+            t[slot].zero_()
+
+    # ---- snapshots (prompt-cache primitives) ---------------------------------------------------------
+    def state_save(self, slot: int) -> Dict[str, torch.Tensor]:
+        """Copy of the GDN recurrent + conv state of a slot (a `Snap`, reference `pcache.rs`); KV stays in place."""
+        return {
+            "rec": torch.stack([t[slot] for t in self.rec_state.values()]).clone() if self.rec_state else torch.empty(0),
+            "conv": torch.stack([t[slot] for t in self.conv_state.values()]).clone() if self.conv_state else torch.empty(0),
+        }
+
+    def state_restore(self, slot: int, snap: Dict[str, torch.Tensor]) -> None:
+        for j, t in enumerate(self.rec_state.values()):
+            t[slot].copy_(snap["rec"][j])
+        for j, t in enumerate(self.conv_state.values()):
+            t[slot].copy_(snap["conv"][j])
+
+    def detach_blocks(self, slot: int, n_tokens: int) -> List[int]:
+        """Hand the slot's first pages (covering n_tokens) to the caller (parking is a table move, no copy)."""
+        need = (n_tokens + self.ecfg.kv_block - 1) // self.ecfg.kv_block
+        blocks = self.slot_blocks[slot]
+        keep, extra = blocks[:need], blocks[need:]
+        self.pool.release(extra)
+        self.slot_blocks[slot] = []
+        self.block_table_host[slot].fill_(-1)
+        self.block_table.copy_(self.block_table_host, non_blocking=True)
+        return keep
+
+    def attach_blocks(self, slot: int, blocks: List[int]) -> None:
+        assert not self.slot_blocks[slot]
+        self.slot_blocks[slot] = list(blocks)
+        for j, b in enumerate(blocks):
+            self.block_table_host[slot, j] = b
+        self.block_table.copy_(self.block_table_host, non_blocking=True)
+
+    def copy_slot(self, src: int, dst: int, n_tokens: int) -> None:
+        """Fork: copy KV pages covering n_tokens and the GDN state from one slot to another
+        (reference `copy_slot` `model.rs:2121`)."""
+        self.reset_slot(dst)
+        self.ensure_capacity(dst, n_tokens)
+        nb = (n_tokens + self.ecfg.kv_block - 1) // self.ecfg.kv_block
+        if nb:
+            s = torch.tensor(self.slot_blocks[src][:nb], device=self.device, dtype=torch.long)
+            d = torch.tensor(self.slot_blocks[dst][:nb], device=self.device, dtype=torch.long)
+            for i in self.k_cache:
+                self.k_cache[i][d] = self.k_cache[i][s]
+                self.v_cache[i][d] = self.v_cache[i][s]
+        for t in self.rec_state.values():
+            t[dst].copy_(t[src])
+        for t in self.conv_state.values():
+            t[dst].copy_(t[src])
+
+    # ---- metadata upload ----------------------------------------------------------------------------
+    def _upload(self, batch: StepBatch):
+        """Fill the pinned metadata buffer for this step and copy its used prefix to the device. Layout (int32):
+        [tok T | slot T | pos T | kvlen T | lrow T | seg_slot S | seg_row0 S | seg_nrows S | seg_pos0 S]."""
+        T, S = batch.n_rows, len(batch.segments)
+        h = self.meta_host
+        tok, slot, pos, kvl, lrow = (h[i * T:(i + 1) * T] for i in range(5))
+        o = 5 * T
+        sslot, srow0, snrows, spos0 = (h[o + i * S:o + (i + 1) * S] for i in range(4))
+        r = 0
+        logit_rows: List[int] = []
+        for si, sg in enumerate(batch.segments):
+            n = len(sg.tokens)
+            self.ensure_capacity(sg.slot, sg.pos0 + n)
+            tok[r:r + n] = torch.tensor(sg.tokens, dtype=torch.int32)
+            slot[r:r + n] = sg.slot
+            pos[r:r + n] = torch.arange(sg.pos0, sg.pos0 + n, dtype=torch.int32)
+            kvl[r:r + n] = torch.arange(sg.pos0 + 1, sg.pos0 + n + 1, dtype=torch.int32)
+            sslot[si], srow0[si], snrows[si], spos0[si] = sg.slot, r, n, sg.pos0
+            if sg.want_logits == "all":
+                logit_rows.extend(range(r, r + n))
+            elif sg.want_logits == "last":
+                logit_rows.append(r + n - 1)
+            r += n
+        nl = len(logit_rows)
+        lrow[:nl] = torch.tensor(logit_rows, dtype=torch.int32) if nl else lrow[:0]
+        used = 5 * T + 4 * S
+        self.meta_i32[:used].copy_(h[:used], non_blocking=True)
+        self.h2d_bytes = used * 4
+        return logit_rows
+
+    def _meta_views(self, T: int, nseg: int, nlog: int):
+        m = self.meta_i32
+        o = 5 * T
+        S = nseg
+        return dict(
+            tok=m[0:T], slot=m[T:2 * T], pos=m[2 * T:3 * T], kvlen=m[3 * T:4 * T], lrow=m[4 * T:4 * T + nlog],
+            sslot=m[o:o + S], srow0=m[o + S:o + 2 * S], snrows=m[o + 2 * S:o + 3 * S], spos0=m[o + 3 * S:o + 4 * S],
+        )
+
+    # ---- forward -----------------------------------------------------------------------------------
+    def _row_parallel(self, x_in, w, res):
+        """Row-parallel projection (o_proj / out_proj / down): partial product, reduction over TP ranks, residual."""
+        if self.tp is None or self.tp.world == 1:
+            return self.ops.linear(x_in, w, res=res)
+        return self.tp.linear_allreduce(self.ops, x_in, w, res)
+
+    def _layers(self, x, mv, T, nseg, max_seg_rows, nsplit, commit):
+        c, w, ops = self.cfg, self.w, self.ops
+        eps = c.eps
+        self.taps = []
+        for i, kind in enumerate(self.kinds):
+            p = f"l{i}."
+            if kind == "gdn":
+                proj = ops.linear(x, w[p + "in_proj"], norm_w=w[p + "input_norm"], eps=eps)
+                qkv = ops.gdn_conv(proj, w[p + "conv_w"], self.conv_state[i], mv["sslot"], mv["srow0"], mv["snrows"],
+                                   c.conv_dim, **({"max_rows": max_seg_rows} if ops.name == "cuda" else {}))
+                y = ops.gdn_rec(qkv, proj, self.rec_state[i], self.conv_state[i], w[p + "A_log"], w[p + "dt_bias"],
+                                mv["sslot"], mv["srow0"], mv["snrows"], c.lin_k_heads, c.lin_v_heads, c.lin_dk,
+                                c.lin_dv, eps, commit=commit, chunked=False)
+                o = ops.gated_norm(y, proj, c.conv_dim, w[p + "gnorm_w"], c.lin_v_heads, c.lin_dv, eps)
+                x = self._row_parallel(o, w[p + "out_proj"], x)
+            else:
+                proj = ops.linear(x, w[p + "in_proj"], norm_w=w[p + "input_norm"], eps=eps)
+                q = ops.attn_prep(proj, w[p + "q_norm"], w[p + "k_norm"], self.inv_freq, mv["slot"], mv["pos"],
+                                  self.block_table, self.k_cache[i], self.v_cache[i], self.ecfg.kv_block, c.n_q,
+                                  c.n_kv, c.head_dim, c.rotary_dim, c.attn_gate, eps)
+                o = ops.attention(q, proj, self.k_cache[i], self.v_cache[i], mv["slot"], mv["kvlen"], self.block_table,
+                                  self.ecfg.kv_block, c.n_q, c.n_kv, c.head_dim, c.attn_gate, nsplit=nsplit)
+                x = self._row_parallel(o, w[p + "out_proj"], x)
+            act = ops.linear(x, w[p + "gate_up"], norm_w=w[p + "post_norm"], eps=eps, swiglu=True)
+            x = self._row_parallel(act, w[p + "down"], x)
+            if i in c.tap_layers:
+                self.taps.append(x)
+        return x
+
+    def _head(self, x, mv, nlog, greedy):
+        c, w, ops = self.cfg, self.w, self.ops
+        if nlog == 0:
+            return None, None
+        rows = x[mv["lrow"].long()] if nlog != x.shape[0] else x
+        head = w["embed"] if c.tie_embeddings else w["lm_head"]
+        logits = ops.linear(rows, head, norm_w=w["final_norm"], eps=c.eps, out_f32=True)
+        if self.tp is not None and self.tp.world > 1:
+            return self.tp.gather_logits(ops, logits, greedy)
+        if greedy:
+            ids, finite = ops.argmax(logits)
+            return logits, (ids, finite)
+        return logits, None
+
+    def _run(self, T, nseg, nlog, max_seg_rows, nsplit, commit, greedy):
+        mv = self._meta_views(T, nseg, nlog)
+        x = self.ops.embed(self.w["embed"], mv["tok"])
+        x = self._layers(x, mv, T, nseg, max_seg_rows, nsplit, commit)
+        return self._head(x, mv, nlog, greedy)
+
+    def attn_splits(self, max_kvlen: int) -> int:
+        """Split count of the decode attention: one split per 256 keys, rounded up to a power of two, capped."""
+        if self.ecfg.attn_splits > 0:
+            return self.ecfg.attn_splits
+        s = max(1, (max_kvlen + 255) // 256)
+        s = 1 << (s - 1).bit_length()
+        return min(s, 64)
+
+    def forward(self, batch: StepBatch, greedy: bool = True):
+        """Run one step. Returns (logits [n_logit_rows, vocab] fp32, (ids, finite) when greedy, logit_rows)."""
+        T = batch.n_rows
+        assert 0 < T <= self._R, f"{T} rows exceed max_step_rows"
+        nseg = len(batch.segments)
+        max_seg_rows = max(len(s.tokens) for s in batch.segments)
+        max_kvlen = max(s.pos0 + len(s.tokens) for s in batch.segments)
+        nsplit = self.attn_splits(max_kvlen) if max_seg_rows <= 64 else 1
+        use_graph = (self.ecfg.use_graphs and self.device.type == "cuda" and T <= self.ecfg.decode_rows_max
+                     and self.profile is None)
+        logit_rows = self._upload(batch)
+        nlog = len(logit_rows)
+        if not use_graph:
+            logits, picks = self._run(T, nseg, nlog, max_seg_rows, nsplit, batch.commit, greedy)
+            return logits, picks, logit_rows
+        key = (T, nseg, nlog, max_seg_rows, nsplit, batch.commit, greedy)
+        hit = self.graphs.get(key)
+        if hit is None:
+            # warm up eagerly once (lazy module / attribute setup), then capture
+            self._run(T, nseg, nlog, max_seg_rows, nsplit, False, greedy)
+            torch.cuda.synchronize(self.device)
+            g = torch.cuda.CUDAGraph()
+            l0 = self.ops.launches
+            with torch.cuda.graph(g):
+                out = self._run(T, nseg, nlog, max_seg_rows, nsplit, batch.commit, greedy)
+            n_kernels = self.ops.launches - l0
+            self.ops.launches = l0
+            hit = (g, out, n_kernels)
+            self.graphs[key] = hit
+            if len(self.graphs) > self.ecfg.graph_max:
+                self.graphs.popitem(last=False)
+            # capture does not execute: replay below performs the step
+        else:
+            self.graphs.move_to_end(key)
+        g, (logits, picks), n_kernels = hit
+        g.replay()
+        self.ops.launches += n_kernels
+        return logits, picks, logit_rows

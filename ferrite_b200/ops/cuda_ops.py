@@ -1,0 +1,146 @@
+"""Device ops backed by the hand-written sm_100a kernels in `csrc/` (loaded from `ferrite_b200/_C.so`).
+
+Same signatures as `torch_ops.TorchOps`. Row counts pick the kernel: up to `GEMV_MAX_ROWS` rows stream the
+weights through the SIMT GEMV (fused norm / SwiGLU / residual), more rows go to the tcgen05 GEMM (swapped
+orientation with split-K up to 64 rows, normal orientation beyond). There is no PyTorch fallback here: a
+missing extension raises.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+
+from .._ext import load
+
+GEMV_MAX_ROWS = 8
+
+
+class CudaOps:
+    name = "cuda"
+
+    def __init__(self, device, dtype=torch.bfloat16):
+        self.C = load()
+        self.device = torch.device(device)
+        self.dtype = dtype
+        assert dtype == torch.bfloat16, "the sm_100a kernels take bf16 activations"
+        self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
+        self.status_word = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._ws: Optional[torch.Tensor] = None
+        self._counters = torch.zeros(4096, dtype=torch.int32, device=self.device)
+        self.force_gemv_chunks = False      # debug: run any row count through 8-row GEMV passes
+        self.launches = 0                   # kernels launched (or recorded into a graph) through this object
+
+    # ---- workspace ---------------------------------------------------------------------------------
+    def _workspace(self, nbytes: int) -> torch.Tensor:
+        if self._ws is None or self._ws.numel() * 4 < nbytes:
+            self._ws = torch.empty(max(nbytes // 4, 1 << 20), dtype=torch.float32, device=self.device)
+        return self._ws
+
+    def status(self) -> int:
+        return int(self.status_word.item())
+
+    # ---- rows ------------------------------------------------------------------------------------
+    def embed(self, table, ids):
+        out = torch.empty(ids.numel(), table.shape[1], dtype=self.dtype, device=self.device)
+        self.launches += 1
+        self.C.embed(out, table, ids)
+        return out
+
+    def rmsnorm(self, x, w, eps, centred=True, res=None):
+        out = torch.empty_like(x)
+        if res is not None:
+            xo = torch.empty_like(x)
+            self.launches += 1
+            self.C.rmsnorm(out, x, w, eps, centred, res, xo)
+            return out, xo
+        self.launches += 1
+        self.C.rmsnorm(out, x, w, eps, centred, None, None)
+        return out, x
+
+    def _split_k(self, M, N, K):
+        tiles = (N + 127) // 128
+        kblocks = (K + 63) // 64
+        s = max(1, min(kblocks // 4, (self.sm_count + tiles - 1) // tiles))
+        return s
+
+    def linear(self, x, w, norm_w=None, eps=1e-6, res=None, swiglu=False, out_f32=False):
+        M, K = x.shape
+        N = w.shape[0] // 2 if swiglu else w.shape[0]
+        if M <= GEMV_MAX_ROWS or self.force_gemv_chunks or out_f32 and M <= 64:
+            y = torch.empty(M, N, dtype=torch.float32 if out_f32 else self.dtype, device=self.device)
+            for r0 in range(0, M, GEMV_MAX_ROWS):
+                r1 = min(M, r0 + GEMV_MAX_ROWS)
+                self.launches += 1
+                self.C.gemv(y[r0:r1], x[r0:r1], w, norm_w, None if res is None else res[r0:r1], eps, True,
+                            1 if swiglu else 0)
+            return y
+        if norm_w is not None:
+            x, _ = self.rmsnorm(x, norm_w, eps, True)
+        y = torch.empty(M, N, dtype=self.dtype, device=self.device)
+        split = self._split_k(M, N, K) if M <= 64 else 1
+        ws = cnt = None
+        if split > 1:
+            nb = self.C.gemm_workspace_bytes(M, N, split)
+            ws = self._workspace(nb)
+            cnt = self._counters
+        self.launches += 1
+        self.C.gemm(y, x, w, res, 1 if swiglu else 0, split, ws, cnt, self.status_word)
+        return y.float() if out_f32 else y
+
+    def silu_mul(self, gu):
+        out = torch.empty(gu.shape[0], gu.shape[1] // 2, dtype=self.dtype, device=self.device)
+        self.launches += 1
+        self.C.silu_mul(out, gu, 0.0)
+        return out
+
+    def gated_norm(self, y, proj, z_off, w, heads, dv, eps):
+        out = torch.empty(y.shape[0], heads * dv, dtype=self.dtype, device=self.device)
+        self.launches += 1
+        self.C.gated_norm(out, y, proj, z_off, proj.stride(0), w, heads, dv, eps)
+        return out
+
+    # ---- attention ---------------------------------------------------------------------------------
+    def attn_prep(self, proj, q_norm, k_norm, inv_freq, row_slot, row_pos, block_table, k_cache, v_cache, kv_block,
+                  nq, nkv, hd, rot, gated, eps):
+        q = torch.empty(proj.shape[0], nq, hd, dtype=self.dtype, device=self.device)
+        self.launches += 1
+        self.C.attn_prep(q, k_cache, v_cache, proj, q_norm, k_norm, inv_freq, row_slot, row_pos, block_table,
+                         kv_block, nq, nkv, hd, rot, gated, eps, self.status_word)
+        return q
+
+    def attention(self, q, proj, k_cache, v_cache, row_slot, row_kvlen, block_table, kv_block, nq, nkv, hd, gated,
+                  row_base=None, row_mask=None, nsplit=1):
+        T = q.shape[0]
+        out = torch.empty(T, nq * hd, dtype=self.dtype, device=self.device)
+        o_part = torch.empty(T, nq, nsplit, hd, dtype=torch.float32, device=self.device)
+        ml_part = torch.empty(T, nq, nsplit, 2, dtype=torch.float32, device=self.device)
+        self.launches += 2
+        self.C.attn_decode(out, o_part, ml_part, q, k_cache, v_cache, proj, row_slot, row_kvlen, row_base, row_mask,
+                           block_table, kv_block, nq, nkv, hd, nsplit, gated)
+        return out
+
+    # ---- gated delta net ---------------------------------------------------------------------------
+    def gdn_conv(self, proj, conv_w, conv_state, seg_slot, seg_row0, seg_nrows, conv_dim, max_rows=None):
+        out = torch.empty(proj.shape[0], conv_dim, dtype=self.dtype, device=self.device)
+        self.launches += 1
+        self.C.gdn_conv(out, proj, conv_w, conv_state, seg_slot, seg_row0, seg_nrows,
+                        proj.shape[0] if max_rows is None else max_rows)
+        return out
+
+    def gdn_rec(self, qkv, proj, rec_state, conv_state, A_log, dt_bias, seg_slot, seg_row0, seg_nrows, nk, nv, dk, dv,
+                eps, commit=True, chunked=False):
+        y = torch.empty(qkv.shape[0], nv * dv, dtype=torch.float32, device=self.device)
+        self.launches += 1
+        self.C.gdn_rec(y, rec_state, conv_state, qkv, proj, A_log, dt_bias, seg_slot, seg_row0, seg_nrows, nk, nv,
+                       dk, dv, eps, commit, chunked)
+        return y
+
+    # ---- selection ---------------------------------------------------------------------------------
+    def argmax(self, logits):
+        ids = torch.empty(logits.shape[0], dtype=torch.int32, device=self.device)
+        finite = torch.empty(logits.shape[0], dtype=torch.int32, device=self.device)
+        self.launches += 1
+        self.C.argmax(ids, logits, None, finite)
+        return ids, finite

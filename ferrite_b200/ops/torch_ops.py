@@ -1,0 +1,176 @@
+"""Plain PyTorch statement of every device op, with the same signatures as `cuda_ops.CudaOps`.
+
+Two uses: it is the fp32 oracle each CUDA kernel test compares against, and it is the op set the engine runs
+on when it is built on a CPU device (the plumbing configuration). It mutates the same paged KV cache and
+state tensors the CUDA kernels do.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+import torch.nn.functional as F
+
+
+def _softplus(x):
+    return torch.where(x > 20, x, torch.log1p(torch.exp(torch.clamp(x, max=20.0))))
+
+
+class TorchOps:
+    name = "torch"
+
+    def __init__(self, device="cpu", dtype=torch.float32):
+        self.device = torch.device(device)
+        self.dtype = dtype
+        self.launches = 0
+
+    # ---- rows ------------------------------------------------------------------------------------
+    def embed(self, table, ids):
+        return table[ids.long()].to(self.dtype)
+
+    def rmsnorm(self, x, w, eps, centred=True, res=None):
+        """Returns (normed, x') with x' = x + res when res is given (the folded residual add)."""
+        if res is not None:
+            x = (x.float() + res.float()).to(x.dtype)
+        xf = x.float()
+        r = torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
+        wf = w.float() + 1.0 if centred else w.float()
+        return (xf * r * wf).to(self.dtype), x
+
+    def linear(self, x, w, norm_w=None, eps=1e-6, res=None, swiglu=False, out_f32=False):
+        """y = x W^T with optional RMSNorm(1+w) prologue, SwiGLU (W = [gate|up]) or residual epilogue."""
+        xf = x.float()
+        if norm_w is not None:
+            r = torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
+            xf = (xf * r * (1.0 + norm_w.float())).to(x.dtype).float()
+        y = xf @ w.float().t()
+        if swiglu:
+            i = y.shape[-1] // 2
+            y = F.silu(y[:, :i]) * y[:, i:]
+        if res is not None:
+            y = y + res.float()
+        return y if out_f32 else y.to(self.dtype)
+
+    def silu_mul(self, gu):
+        i = gu.shape[-1] // 2
+        return (F.silu(gu[:, :i].float()) * gu[:, i:].float()).to(self.dtype)
+
+    def gated_norm(self, y, proj, z_off, w, heads, dv, eps):
+        yf = y.float().view(-1, heads, dv)
+        z = proj[:, z_off:z_off + heads * dv].float().view(-1, heads, dv)
+        r = torch.rsqrt(yf.pow(2).mean(-1, keepdim=True) + eps)
+        return (yf * r * w.float() * F.silu(z)).reshape(-1, heads * dv).to(self.dtype)
+
+    # ---- attention ---------------------------------------------------------------------------------
+    def attn_prep(self, proj, q_norm, k_norm, inv_freq, row_slot, row_pos, block_table, k_cache, v_cache, kv_block,
+                  nq, nkv, hd, rot, gated, eps):
+        T = proj.shape[0]
+        qw = hd * (2 if gated else 1)
+        qg = proj[:, :nq * qw].float().view(T, nq, qw)
+        q = qg[..., :hd]
+        k = proj[:, nq * qw:nq * qw + nkv * hd].float().view(T, nkv, hd)
+        v = proj[:, nq * qw + nkv * hd:nq * qw + 2 * nkv * hd].view(T, nkv, hd)
+
+        def norm(x, w):
+            return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps) * (1.0 + w.float())
+
+        q, k = norm(q, q_norm), norm(k, k_norm)
+        ang = row_pos.float()[:, None] * inv_freq.float()[None, :]
+        cos, sin = ang.cos()[:, None, :], ang.sin()[:, None, :]
+        half = rot // 2
+
+        def rope(x):
+            a, b = x[..., :half], x[..., half:rot]
+            return torch.cat([a * cos - b * sin, b * cos + a * sin, x[..., rot:]], -1)
+
+        q, k = rope(q), rope(k)
+        pos = row_pos.long()
+        blk = block_table[row_slot.long(), pos // kv_block].long()
+        off = pos % kv_block
+        k_cache[blk, off] = k.to(k_cache.dtype)
+        v_cache[blk, off] = v.to(v_cache.dtype)
+        return q.to(self.dtype)
+
+    def attention(self, q, proj, k_cache, v_cache, row_slot, row_kvlen, block_table, kv_block, nq, nkv, hd, gated,
+                  row_base=None, row_mask=None, nsplit=1):
+        T = q.shape[0]
+        out = torch.zeros(T, nq, hd, dtype=torch.float32, device=q.device)
+        grp = nq // nkv
+        for t in range(T):
+            L = int(row_kvlen[t])
+            slot = int(row_slot[t])
+            pos = torch.arange(L, device=q.device)
+            blk = block_table[slot, pos // kv_block].long()
+            K = k_cache[blk, pos % kv_block].float()            # [L, nkv, hd]
+            V = v_cache[blk, pos % kv_block].float()
+            qh = q[t].float().view(nkv, grp, hd)
+            s = torch.einsum("kgd,tkd->kgt", qh, K) / math.sqrt(hd)
+            if row_base is not None and row_mask is not None:
+                base, mask = int(row_base[t]), int(row_mask[t])
+                vis = torch.tensor([(p < base) or ((mask >> (p - base)) & 1) == 1 for p in range(L)], device=q.device)
+                s = s.masked_fill(~vis[None, None, :], float("-inf"))
+            p = torch.softmax(s, -1)
+            out[t] = torch.einsum("kgt,tkd->kgd", p, V).reshape(nq, hd)
+        if gated:
+            gate = proj[:, :nq * 2 * hd].float().view(T, nq, 2 * hd)[..., hd:]
+            out = out * torch.sigmoid(gate)
+        return out.reshape(T, nq * hd).to(self.dtype)
+
+    # ---- gated delta net ---------------------------------------------------------------------------
+    def gdn_conv(self, proj, conv_w, conv_state, seg_slot, seg_row0, seg_nrows, conv_dim):
+        T = proj.shape[0]
+        out = torch.zeros(T, conv_dim, dtype=self.dtype, device=proj.device)
+        ck = conv_w.shape[1]
+        for s in range(len(seg_slot)):
+            n, r0, slot = int(seg_nrows[s]), int(seg_row0[s]), int(seg_slot[s])
+            if n <= 0:
+                continue
+            x = torch.cat([conv_state[slot].float(), proj[r0:r0 + n, :conv_dim].float()], 0)     # [ck-1+n, C]
+            win = x.unfold(0, ck, 1)                                                              # [n, C, ck]
+            out[r0:r0 + n] = F.silu((win * conv_w.float()[None]).sum(-1)).to(self.dtype)
+        return out
+
+    def gdn_rec(self, qkv, proj, rec_state, conv_state, A_log, dt_bias, seg_slot, seg_row0, seg_nrows, nk, nv, dk, dv,
+                eps, commit=True, chunked=False):
+        T = qkv.shape[0]
+        conv_dim = 2 * nk * dk + nv * dv
+        y = torch.zeros(T, nv * dv, dtype=torch.float32, device=qkv.device)
+        rep = nv // nk
+        ck1 = conv_state.shape[1]
+        for s in range(len(seg_slot)):
+            n, r0, slot = int(seg_nrows[s]), int(seg_row0[s]), int(seg_slot[s])
+            if n <= 0:
+                continue
+            S = rec_state[slot].float().clone()                  # [nv, dk, dv]
+            for r in range(r0, r0 + n):
+                x = qkv[r].float()
+                q = x[:nk * dk].view(nk, dk)
+                k = x[nk * dk:2 * nk * dk].view(nk, dk)
+                v = x[2 * nk * dk:].view(nv, dv)
+                q = q * torch.rsqrt(q.pow(2).sum(-1, keepdim=True) + eps) / math.sqrt(dk)
+                k = k * torch.rsqrt(k.pow(2).sum(-1, keepdim=True) + eps)
+                q, k = q.repeat_interleave(rep, 0), k.repeat_interleave(rep, 0)
+                b = proj[r, conv_dim + nv * dv:conv_dim + nv * dv + nv].float()
+                a = proj[r, conv_dim + nv * dv + nv:conv_dim + nv * dv + 2 * nv].float()
+                g = torch.exp(-torch.exp(A_log.float()) * _softplus(a + dt_bias.float()))
+                beta = torch.sigmoid(b)
+                S = S * g[:, None, None]
+                kv = torch.einsum("hkv,hk->hv", S, k)
+                delta = (v - kv) * beta[:, None]
+                S = S + torch.einsum("hk,hv->hkv", k, delta)
+                y[r] = torch.einsum("hkv,hk->hv", S, q).reshape(-1)
+            if commit:
+                rec_state[slot] = S.to(rec_state.dtype)
+                x = torch.cat([conv_state[slot].float(), proj[r0:r0 + n, :conv_dim].float()], 0)
+                conv_state[slot] = x[-ck1:].to(conv_state.dtype)
+        return y
+
+    # ---- selection ---------------------------------------------------------------------------------
+    def argmax(self, logits):
+        lf = logits.float()
+        finite = torch.isfinite(lf).all(-1)
+        return lf.argmax(-1).to(torch.int32), finite
+
+    def status(self) -> int:
+        return 0

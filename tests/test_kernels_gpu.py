@@ -1,0 +1,183 @@
+"""Numerics of each sm_100a kernel against the plain PyTorch fp32 statement of the same op (`TorchOps`)."""
+import math
+
+import pytest
+import torch
+
+from ferrite_b200.ops.torch_ops import TorchOps
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+@pytest.fixture(scope="module")
+def ops(ext):
+    from ferrite_b200.ops.cuda_ops import CudaOps
+    return CudaOps(DEV)
+
+
+@pytest.fixture(scope="module")
+def tops():
+    return TorchOps(DEV, torch.float32)
+
+
+def rnd(*shape, scale=1.0, seed=0, dtype=torch.bfloat16):
+    g = torch.Generator(device=DEV).manual_seed(seed)
+    return (torch.randn(*shape, generator=g, device=DEV) * scale).to(dtype)
+
+
+def close(got, want, rtol=2e-2, atol=2e-2):
+    got, want = got.float(), want.float()
+    err = (got - want).abs().max().item()
+    ref = want.abs().max().item()
+    assert err <= atol * max(1.0, ref) + rtol * ref * 0 + 1e-6, f"max err {err} vs scale {ref}"
+
+
+@pytest.mark.parametrize("M", [1, 2, 3, 4, 8])
+@pytest.mark.parametrize("N,K", [(512, 256), (1000, 768), (5120, 5120), (640, 17408)])
+def test_gemv_plain(ops, tops, M, N, K):
+    x, w = rnd(M, K, seed=1), rnd(N, K, scale=0.05, seed=2)
+    res = rnd(M, N, seed=3)
+    close(ops.linear(x, w), tops.linear(x, w))
+    close(ops.linear(x, w, res=res), tops.linear(x, w, res=res))
+    close(ops.linear(x, w, out_f32=True), tops.linear(x, w, out_f32=True))
+
+
+@pytest.mark.parametrize("M", [1, 4, 8])
+def test_gemv_norm_swiglu(ops, tops, M):
+    K, I = 5120, 1024
+    x, w, nw = rnd(M, K, seed=1), rnd(2 * I, K, scale=0.03, seed=2), rnd(K, scale=0.1, seed=4)
+    close(ops.linear(x, w, norm_w=nw, eps=1e-6, swiglu=True), tops.linear(x, w, norm_w=nw, eps=1e-6, swiglu=True))
+    close(ops.linear(x, w[:I], norm_w=nw, eps=1e-6), tops.linear(x, w[:I], norm_w=nw, eps=1e-6))
+
+
+def test_gemv_batch_invariance(ops):
+    """A row's bits do not depend on how many rows share the launch."""
+    K, N = 5120, 2048
+    x, w = rnd(8, K, seed=1), rnd(N, K, scale=0.05, seed=2)
+    y8 = ops.linear(x, w)
+    for m in (1, 2, 4):
+        assert torch.equal(ops.linear(x[:m].contiguous(), w), y8[:m])
+
+
+@pytest.mark.parametrize("M,N,K", [(16, 512, 256), (33, 1024, 5120), (64, 5120, 2048), (128, 512, 512),
+                                   (300, 1000 // 8 * 8, 768), (2048, 6144, 5120), (512, 5120, 17408)])
+def test_gemm_tcgen05(ops, tops, M, N, K):
+    x, w = rnd(M, K, seed=1), rnd(N, K, scale=0.05, seed=2)
+    res = rnd(M, N, seed=3)
+    close(ops.linear(x, w), tops.linear(x, w))
+    close(ops.linear(x, w, res=res), tops.linear(x, w, res=res))
+    assert ops.status() == 0
+
+
+@pytest.mark.parametrize("M", [24, 64, 200, 1024])
+def test_gemm_tcgen05_swiglu(ops, tops, M):
+    K, I = 1024, 1536
+    x, w = rnd(M, K, seed=1), rnd(2 * I, K, scale=0.05, seed=2)
+    close(ops.linear(x, w, swiglu=True), tops.linear(x, w, swiglu=True))
+    assert ops.status() == 0
+
+
+def test_gemm_determinism(ops):
+    x, w = rnd(48, 5120, seed=1), rnd(5120, 5120, scale=0.05, seed=2)
+    a = ops.linear(x, w)
+    for _ in range(5):
+        assert torch.equal(ops.linear(x, w), a)
+
+
+def test_rmsnorm_embed_silu(ops, tops):
+    x, w, r = rnd(37, 5120, seed=1), rnd(5120, scale=0.1, seed=2), rnd(37, 5120, seed=3)
+    a, _ = ops.rmsnorm(x, w, 1e-6)
+    b, _ = tops.rmsnorm(x, w, 1e-6)
+    close(a, b)
+    a, xa = ops.rmsnorm(x, w, 1e-6, res=r)
+    b, xb = tops.rmsnorm(x, w, 1e-6, res=r)
+    close(a, b)
+    close(xa, xb)
+    table = rnd(1000, 256, seed=5)
+    ids = torch.randint(0, 1000, (19,), device=DEV, dtype=torch.int32)
+    assert torch.equal(ops.embed(table, ids), table[ids.long()])
+    gu = rnd(9, 2 * 768, seed=6)
+    close(ops.silu_mul(gu), tops.silu_mul(gu))
+
+
+@pytest.mark.parametrize("hd,nq,nkv,rot", [(64, 4, 2, 64), (256, 24, 4, 64), (128, 8, 2, 128), (256, 3, 1, 64)])
+def test_attention_paged(ops, tops, hd, nq, nkv, rot):
+    kv_block, n_slots, max_blocks = 64, 3, 8
+    nb = n_slots * max_blocks
+    gated = True
+    width = nq * hd * 2 + 2 * nkv * hd
+    bt = torch.arange(nb, device=DEV, dtype=torch.int32).view(n_slots, max_blocks).flip(0).contiguous()
+    inv = (1e6 ** (-torch.arange(rot // 2, dtype=torch.float64) / (rot // 2))).float().to(DEV)
+    qn, kn = rnd(hd, scale=0.1, seed=7), rnd(hd, scale=0.1, seed=8)
+    kc = [torch.zeros(nb, kv_block, nkv, hd, dtype=torch.bfloat16, device=DEV) for _ in range(2)]
+    vc = [torch.zeros_like(kc[0]) for _ in range(2)]
+    # a 300-token prompt in slot 1, then rows of two slots in one step
+    proj = rnd(300, width, seed=9)
+    slot = torch.full((300,), 1, device=DEV, dtype=torch.int32)
+    pos = torch.arange(300, device=DEV, dtype=torch.int32)
+    qa = ops.attn_prep(proj, qn, kn, inv, slot, pos, bt, kc[0], vc[0], kv_block, nq, nkv, hd, rot, gated, 1e-6)
+    qb = tops.attn_prep(proj, qn, kn, inv, slot, pos, bt, kc[1], vc[1], kv_block, nq, nkv, hd, rot, gated, 1e-6)
+    close(qa, qb)
+    close(kc[0], kc[1])
+    assert torch.equal(vc[0], vc[1])
+    kvlen = pos + 1
+    for nsplit in (1, 4):
+        oa = ops.attention(qa, proj, kc[0], vc[0], slot, kvlen, bt, kv_block, nq, nkv, hd, gated, nsplit=nsplit)
+        ob = tops.attention(qb, proj, kc[1], vc[1], slot, kvlen, bt, kv_block, nq, nkv, hd, gated)
+        close(oa, ob)
+    # tree mask: rows see the first 290 keys plus chosen later ones
+    base = torch.full((300,), 290, device=DEV, dtype=torch.int32)
+    mask = torch.full((300,), 0b1010010011, device=DEV, dtype=torch.int64)
+    lens = torch.full((300,), 300, device=DEV, dtype=torch.int32)
+    oa = ops.attention(qa[:8], proj[:8], kc[0], vc[0], slot[:8], lens[:8], bt, kv_block, nq, nkv, hd, gated,
+                       row_base=base[:8], row_mask=mask[:8], nsplit=2)
+    ob = tops.attention(qb[:8], proj[:8], kc[1], vc[1], slot[:8], lens[:8], bt, kv_block, nq, nkv, hd, gated,
+                        row_base=base[:8], row_mask=mask[:8])
+    close(oa, ob)
+    assert ops.status() == 0
+
+
+@pytest.mark.parametrize("nk,nv,dk,dv", [(4, 4, 64, 64), (16, 16, 128, 128), (2, 4, 128, 128)])
+def test_gdn_conv_and_recurrence(ops, tops, nk, nv, dk, dv):
+    conv_dim = 2 * nk * dk + nv * dv
+    width = conv_dim + nv * dv + 2 * nv
+    n_slots = 3
+    T = 23
+    proj = rnd(T, width, seed=1)
+    conv_w = rnd(conv_dim, 4, scale=0.5, seed=2)
+    A_log = rnd(nv, scale=0.3, seed=3, dtype=torch.float32)
+    dtb = rnd(nv, scale=0.3, seed=4, dtype=torch.float32)
+    gw = (rnd(dv, scale=0.1, seed=5).float() + 1).to(torch.bfloat16)
+    seg_slot = torch.tensor([2, 0], device=DEV, dtype=torch.int32)
+    seg_row0 = torch.tensor([0, 17], device=DEV, dtype=torch.int32)
+    seg_n = torch.tensor([17, 6], device=DEV, dtype=torch.int32)
+    st = []
+    for _ in range(2):
+        st.append((rnd(n_slots, nv, dk, dv, scale=0.2, seed=6, dtype=torch.float32),
+                   rnd(n_slots, 3, conv_dim, seed=7)))
+    qa = ops.gdn_conv(proj, conv_w, st[0][1], seg_slot, seg_row0, seg_n, conv_dim, max_rows=17)
+    qb = tops.gdn_conv(proj, conv_w, st[1][1], seg_slot, seg_row0, seg_n, conv_dim)
+    close(qa, qb)
+    # feed both recurrences the same conv output so only the recurrence is compared
+    for commit in (False, True):
+        ya = ops.gdn_rec(qa, proj, st[0][0], st[0][1], A_log, dtb, seg_slot, seg_row0, seg_n, nk, nv, dk, dv, 1e-6, commit=commit)
+        yb = tops.gdn_rec(qa, proj, st[1][0], st[1][1], A_log, dtb, seg_slot, seg_row0, seg_n, nk, nv, dk, dv, 1e-6, commit=commit)
+        close(ya, yb, atol=5e-3)
+        close(st[0][0], st[1][0], atol=5e-3)
+        assert torch.equal(st[0][1], st[1][1])
+    oa = ops.gated_norm(ya, proj, conv_dim, gw, nv, dv, 1e-6)
+    ob = tops.gated_norm(ya, proj, conv_dim, gw, nv, dv, 1e-6)
+    close(oa, ob)
+
+
+def test_argmax(ops):
+    lg = rnd(5, 151936, seed=1, dtype=torch.float32)
+    lg[2, 777] = 50.0
+    lg[3, 5] = lg[3, 100] = 60.0
+    ids, finite = ops.argmax(lg)
+    assert ids.tolist() == lg.argmax(-1).tolist()
+    assert ids[3].item() == 5 and finite.tolist() == [1] * 5
+    lg[4, 9] = float("nan")
+    _, finite = ops.argmax(lg.to(torch.bfloat16))
+    assert finite.tolist() == [1, 1, 1, 1, 0]
