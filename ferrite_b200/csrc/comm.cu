@@ -1,0 +1,379 @@
+// Fused compute + collective kernels over NVLink peer memory (one process per GPU, symmetric buffers mapped
+// on every rank). No NCCL call and no TMA load touches peer memory here: peers are reached with plain
+// st/ld (system scope) through the peer-pointer table.
+//
+//  * fb_gemv_allreduce   row-parallel GEMV (o_proj / out_proj / down_proj, <= 8 rows) whose epilogue is a
+//                        one-shot all-reduce: every CTA pushes its fp32 partial tile to all ranks, releases a
+//                        flag per (rank, CTA), waits (bounded) for the same tile from every rank, sums in RANK
+//                        ORDER, adds the residual and rounds to bf16. All ranks therefore hold identical bits.
+//  * fb_allreduce_oneshot the same exchange for a partial that another kernel produced (tcgen05 GEMM for 9..64
+//                        verify rows), bf16 or fp32 partials.
+//  * fb_argmax_gather    vocab-parallel head: per-row (max, index) of the local logits shard pushed to all ranks
+//                        and merged in rank order, so only 8 bytes per row cross NVLink instead of the logits.
+//
+// The reference does this job with a NIC: `fab_gather_sum_bf16[in]` stages the partial, rings a doorbell, a CPU
+// proxy thread posts an RDMA write, and the kernel spins on the peer's sequence flag, giving up after a poll
+// limit and setting a poison word (`kernels/k-fabric/src/lib.rs:82-135`, `crates/fe-fabric/src/roce.rs:375-455`,
+// call site `crates/fe-model/src/model.rs:1761-1797`). Here the wait is bounded the same way and reports
+// ST_PEER_TIMEOUT through the status word; epochs live in device memory so the kernels replay inside CUDA graphs.
+#include "api_ext.h"
+#include "gemv_core.cuh"
+
+namespace fb {
+
+constexpr int COMM_MAX_RANKS = 8;
+constexpr int COMM_MAX_ROWS = 8;
+
+// Layout of the symmetric workspace (identical on every rank):
+//   flags : [2 parity][COMM_MAX_RANKS][max_ctas] u32
+//   data  : [2 parity][COMM_MAX_RANKS][slot_floats] f32
+struct CommBuf {
+  void* peer[COMM_MAX_RANKS];      // base of the workspace on each rank (peer[rank] = local)
+  int rank, world;
+  int max_ctas;
+  long slot_floats;
+  uint32_t* epochs;                // local, [max_ctas]: per-CTA launch counter
+  int* status;
+  unsigned spin_limit;
+};
+
+__device__ __forceinline__ uint32_t* comm_flags(void* base, const CommBuf& cb, int parity, int src, int cta) {
+  return reinterpret_cast<uint32_t*>(base) + ((size_t)parity * COMM_MAX_RANKS + src) * cb.max_ctas + cta;
+}
+__device__ __forceinline__ float* comm_data(void* base, const CommBuf& cb, int parity, int src) {
+  char* p = reinterpret_cast<char*>(base) + (size_t)2 * COMM_MAX_RANKS * cb.max_ctas * sizeof(uint32_t);
+  return reinterpret_cast<float*>(p) + ((size_t)parity * COMM_MAX_RANKS + src) * cb.slot_floats;
+}
+
+// Exchange one CTA's tile. `tile` = fp32 values in shared memory, `count` of them, living at float offset
+// `off` of the slot. After the call `tile` holds the rank-ordered sum. All threads of the CTA call this.
+__device__ __forceinline__ void cta_exchange_sum(const CommBuf& cb, float* tile, int count, long off) {
+  __shared__ uint32_t s_epoch;
+  __shared__ int s_fail;
+  const int cta = blockIdx.x;
+  if (threadIdx.x == 0) { s_epoch = cb.epochs[cta] + 1; s_fail = 0; }
+  __syncthreads();
+  const uint32_t epoch = s_epoch;
+  const int parity = epoch & 1;
+  // push to every rank (self included, so the sum below reads one layout)
+  for (int p = 0; p < cb.world; ++p) {
+    float* dst = comm_data(cb.peer[p], cb, parity, cb.rank) + off;
+    for (int i = threadIdx.x * 4; i < count; i += blockDim.x * 4) {
+      if (i + 4 <= count) {
+        st_relaxed_sys_v4(dst + i, *reinterpret_cast<const uint4*>(tile + i));
+      } else {
+        for (int j = i; j < count; ++j) dst[j] = tile[j];
+      }
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < cb.world) {
+    st_release_sys(comm_flags(cb.peer[threadIdx.x], cb, parity, cb.rank, cta), epoch);
+  }
+  // wait for the same tile from every rank
+  if (threadIdx.x < cb.world) {
+    const uint32_t* f = comm_flags(cb.peer[cb.rank], cb, parity, threadIdx.x, cta);
+    if (!wait_flag_eq(f, epoch, cb.spin_limit)) { s_fail = 1; set_status(cb.status, ST_PEER_TIMEOUT); }
+  }
+  __syncthreads();
+  if (!s_fail) {
+    for (int i = threadIdx.x; i < count; i += blockDim.x) {
+      float acc = 0.f;
+      for (int r = 0; r < cb.world; ++r)
+        acc += __ldcg(comm_data(cb.peer[cb.rank], cb, parity, r) + off + i);     // rank order, L2 (peer-written)
+      tile[i] = acc;
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) cb.epochs[cta] = epoch;
+}
+
+// ---- K1: GEMV + one-shot all-reduce + residual ------------------------------------------------------------
+template <int M, int R>
+__global__ void __launch_bounds__(GEMV_THREADS) gemv_allreduce_kernel(GemvArgs a, CommBuf cb) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(smem_raw);
+  float* tile = reinterpret_cast<float*>(smem_raw + (size_t)M * a.kc * sizeof(__nv_bfloat16));  // [M][rows_per_cta]
+  __shared__ float rscale_dummy[M];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row0 = blockIdx.x * a.rows_per_cta;
+  const int row_end = min(a.N, row0 + a.rows_per_cta);
+  const int nrows = row_end - row0;
+  const int nchunks = (a.K + a.kc - 1) / a.kc;
+  for (int i = threadIdx.x; i < M * a.rows_per_cta; i += blockDim.x) tile[i] = 0.f;
+
+  if (nchunks == 1) {
+    gemv_stage_x<M>(a, xs, rscale_dummy, 0, a.kc);
+    __syncthreads();
+    for (int n = row0 + warp * R; n < row_end; n += GEMV_WARPS * R) {
+      float acc[R][M];
+#pragma unroll
+      for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int m = 0; m < M; ++m) acc[r][m] = 0.f;
+      const __nv_bfloat16* wrow[R];
+#pragma unroll
+      for (int r = 0; r < R; ++r) wrow[r] = a.W + (size_t)min(n + r, a.N - 1) * a.K;
+      gemv_accumulate<M, R>(acc, wrow, xs, a.kc, a.K);
+#pragma unroll
+      for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int m = 0; m < M; ++m) acc[r][m] = warp_sum(acc[r][m]);
+      if (lane == 0) {
+#pragma unroll
+        for (int r = 0; r < R; ++r)
+          if (n + r < row_end)
+#pragma unroll
+            for (int m = 0; m < M; ++m) tile[m * a.rows_per_cta + (n + r - row0)] = acc[r][m];
+      }
+    }
+  } else {
+    int n = row0 + warp * R;
+    bool active = n < row_end;
+    float acc[R][M];
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+      for (int m = 0; m < M; ++m) acc[r][m] = 0.f;
+    for (int c = 0; c < nchunks; ++c) {
+      int k0 = c * a.kc;
+      __syncthreads();
+      gemv_stage_x<M>(a, xs, rscale_dummy, k0, a.kc);
+      __syncthreads();
+      if (active) {
+        const __nv_bfloat16* wrow[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r) wrow[r] = a.W + (size_t)min(n + r, a.N - 1) * a.K + k0;
+        gemv_accumulate<M, R>(acc, wrow, xs, a.kc, a.K - k0);
+      }
+    }
+    if (active) {
+#pragma unroll
+      for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int m = 0; m < M; ++m) acc[r][m] = warp_sum(acc[r][m]);
+      if (lane == 0) {
+#pragma unroll
+        for (int r = 0; r < R; ++r)
+          if (n + r < row_end)
+#pragma unroll
+            for (int m = 0; m < M; ++m) tile[m * a.rows_per_cta + (n + r - row0)] = acc[r][m];
+      }
+    }
+  }
+  __syncthreads();
+  // slot layout: CTA-major, so a CTA's tile is one contiguous run of M * rows_per_cta floats
+  cta_exchange_sum(cb, tile, M * a.rows_per_cta, (long)blockIdx.x * M * a.rows_per_cta);
+  for (int i = threadIdx.x; i < a.M * nrows; i += blockDim.x) {
+    int m = i / nrows, j = i % nrows;
+    float v = tile[m * a.rows_per_cta + j];
+    size_t o = (size_t)m * a.ldy + row0 + j;
+    if (a.res) v += bf2f(a.res[o]);
+    reinterpret_cast<__nv_bfloat16*>(a.Y)[o] = f2bf(v);
+  }
+}
+
+// ---- standalone one-shot all-reduce of [rows][n] partials ---------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) allreduce_oneshot_kernel(__nv_bfloat16* __restrict__ y, const T* __restrict__ part,
+                                                                const __nv_bfloat16* __restrict__ res, long count,
+                                                                int per_cta, CommBuf cb) {
+  extern __shared__ __align__(16) float tile_s[];
+  const long i0 = (long)blockIdx.x * per_cta;
+  const int cnt = (int)min((long)per_cta, count - i0);
+  for (int i = threadIdx.x; i < per_cta; i += blockDim.x) {
+    float v = 0.f;
+    if (i < cnt) {
+      if (sizeof(T) == 2) v = bf2f(reinterpret_cast<const __nv_bfloat16*>(part)[i0 + i]);
+      else v = reinterpret_cast<const float*>(part)[i0 + i];
+    }
+    tile_s[i] = v;
+  }
+  __syncthreads();
+  cta_exchange_sum(cb, tile_s, per_cta, i0);
+  for (int i = threadIdx.x; i < cnt; i += blockDim.x) {
+    float v = tile_s[i];
+    if (res) v += bf2f(res[i0 + i]);
+    y[i0 + i] = f2bf(v);
+  }
+}
+
+// ---- K4: vocab-parallel argmax merged over ranks ------------------------------------------------------------
+// grid = rows. Each CTA finds (max, lowest index) of its rank's logits shard, publishes it to every rank and
+// merges the world's candidates: larger value wins, ties go to the lower global index.
+__global__ void __launch_bounds__(1024) argmax_gather_kernel(int* __restrict__ ids, float* __restrict__ vals,
+                                                             const float* __restrict__ logits, long stride,
+                                                             int n_local, int vocab_offset, CommBuf cb) {
+  __shared__ float sv[32];
+  __shared__ int si[32];
+  __shared__ float cand[2];
+  const int row = blockIdx.x;
+  const float* lp = logits + (size_t)row * stride;
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int i = threadIdx.x; i < n_local; i += blockDim.x) {
+    float v = lp[i];
+    if (v > best) { best = v; bi = i; }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+  }
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  if (lane == 0) { sv[w] = best; si[w] = bi; }
+  __syncthreads();
+  if (w == 0) {
+    const int nw = blockDim.x >> 5;
+    best = lane < nw ? sv[lane] : -INFINITY;
+    bi = lane < nw ? si[lane] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    if (lane == 0) { cand[0] = best; cand[1] = __int_as_float(bi == 0x7fffffff ? 0 : bi + vocab_offset); }
+  }
+  __syncthreads();
+  // reuse the exchange buffers: each rank's pair sits in its own slot; no summing, so do the push/wait by hand
+  __shared__ uint32_t s_epoch;
+  __shared__ int s_fail;
+  const int cta = blockIdx.x;
+  if (threadIdx.x == 0) { s_epoch = cb.epochs[cta] + 1; s_fail = 0; }
+  __syncthreads();
+  const uint32_t epoch = s_epoch;
+  const int parity = epoch & 1;
+  if (threadIdx.x < cb.world) {
+    float* dst = comm_data(cb.peer[threadIdx.x], cb, parity, cb.rank) + (long)cta * 2;
+    st_relaxed_sys_v2(dst, __float_as_uint(cand[0]), __float_as_uint(cand[1]));
+    __threadfence_system();
+    st_release_sys(comm_flags(cb.peer[threadIdx.x], cb, parity, cb.rank, cta), epoch);
+    const uint32_t* f = comm_flags(cb.peer[cb.rank], cb, parity, threadIdx.x, cta);
+    if (!wait_flag_eq(f, epoch, cb.spin_limit)) { s_fail = 1; set_status(cb.status, ST_PEER_TIMEOUT); }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float bv = -INFINITY;
+    int bidx = 0;
+    if (!s_fail) {
+      for (int r = 0; r < cb.world; ++r) {
+        const float* src = comm_data(cb.peer[cb.rank], cb, parity, r) + (long)cta * 2;
+        float v = __ldcg(src);
+        int ix = __float_as_int(__ldcg(src + 1));
+        if (v > bv || (v == bv && ix < bidx)) { bv = v; bidx = ix; }
+      }
+    }
+    ids[row] = bidx;
+    if (vals) vals[row] = bv;
+    cb.epochs[cta] = epoch;
+  }
+}
+
+// A wait that is made to run out on purpose by a flag nobody sets: exercises the timeout path on one GPU
+// without faulting anything. Returns through the status word.
+__global__ void comm_wait_probe_kernel(const uint32_t* flag, uint32_t want, unsigned limit, int* status) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    if (!wait_flag_eq(flag, want, limit)) set_status(status, ST_PEER_TIMEOUT);
+  }
+}
+
+static void fill_comm(CommBuf& cb, const void* const* peers, int rank, int world, int max_ctas, long slot_floats,
+                      uint32_t* epochs, int* status, unsigned spin_limit) {
+  for (int i = 0; i < COMM_MAX_RANKS; ++i) cb.peer[i] = i < world ? const_cast<void*>(peers[i]) : nullptr;
+  cb.rank = rank; cb.world = world; cb.max_ctas = max_ctas; cb.slot_floats = slot_floats; cb.epochs = epochs;
+  cb.status = status; cb.spin_limit = spin_limit ? spin_limit : FB_PEER_SPIN_LIMIT;
+}
+
+template <int M>
+static int launch_gemv_ar(GemvArgs a, CommBuf cb, int max_resident, cudaStream_t s) {
+  constexpr int R = 2;
+  a.kc = gemv_chunk_len(M, a.K);
+  const int group = GEMV_WARPS * R;
+  int nchunks = (a.K + a.kc - 1) / a.kc;
+  int rpc;
+  if (nchunks > 1) rpc = group;
+  else {
+    rpc = (a.N + max_resident - 1) / max_resident;
+    rpc = (rpc + group - 1) / group * group;
+  }
+  a.rows_per_cta = rpc;
+  int grid = (a.N + rpc - 1) / rpc;
+  // every CTA waits on its peers: all of them must be resident at once
+  if (grid > max_resident || grid > cb.max_ctas) return -7;
+  if ((long)grid * M * rpc > cb.slot_floats) return -8;
+  size_t smem = (size_t)M * a.kc * sizeof(__nv_bfloat16) + (size_t)M * rpc * sizeof(float);
+  auto kern = gemv_allreduce_kernel<M, R>;
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMV_SMEM_BYTES + 16 * 1024);
+    if (e != cudaSuccess) return (int)e;
+    attr_done = true;
+  }
+  kern<<<grid, GEMV_THREADS, smem, s>>>(a, cb);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace fb
+
+using namespace fb;
+
+extern "C" long fb_comm_workspace_bytes(int max_ctas, long slot_floats) {
+  return (long)2 * COMM_MAX_RANKS * max_ctas * 4 + (long)2 * COMM_MAX_RANKS * slot_floats * 4;
+}
+
+extern "C" int fb_gemv_allreduce(void* Y, const void* X, const void* W, const void* res, int M, int N, int K, long ldx,
+                                 long ldy, const void* const* peers, int rank, int world, int max_ctas,
+                                 long slot_floats, uint32_t* epochs, int* status, unsigned spin_limit,
+                                 int max_resident, cudaStream_t s) {
+  if (M <= 0 || N <= 0) return 0;
+  if (M > COMM_MAX_ROWS || world > COMM_MAX_RANKS || (K % 8) || (ldx % 8)) return -1;
+  GemvArgs a;
+  a.X = (const __nv_bfloat16*)X; a.W = (const __nv_bfloat16*)W; a.norm_w = nullptr; a.res = (const __nv_bfloat16*)res;
+  a.Y = Y; a.M = M; a.N = N; a.K = K; a.ldx = ldx; a.ldy = ldy; a.eps = 0.f; a.centred = 0; a.out_f32 = 0;
+  a.rows_per_cta = 0; a.kc = 0;
+  CommBuf cb;
+  fill_comm(cb, peers, rank, world, max_ctas, slot_floats, epochs, status, spin_limit);
+  if (M == 1) return launch_gemv_ar<1>(a, cb, max_resident, s);
+  if (M == 2) return launch_gemv_ar<2>(a, cb, max_resident, s);
+  if (M <= 4) return launch_gemv_ar<4>(a, cb, max_resident, s);
+  return launch_gemv_ar<8>(a, cb, max_resident, s);
+}
+
+extern "C" int fb_allreduce_oneshot(void* y, const void* part, const void* res, long count, int part_f32,
+                                    const void* const* peers, int rank, int world, int max_ctas, long slot_floats,
+                                    uint32_t* epochs, int* status, unsigned spin_limit, int max_resident,
+                                    cudaStream_t s) {
+  if (count <= 0) return 0;
+  if (count > slot_floats) return -8;
+  CommBuf cb;
+  fill_comm(cb, peers, rank, world, max_ctas, slot_floats, epochs, status, spin_limit);
+  int grid = max_resident < max_ctas ? max_resident : max_ctas;
+  int per = (int)((count + grid - 1) / grid);
+  per = (per + 3) / 4 * 4;
+  if (per < 256) per = 256;
+  if (per > 8192) return -9;
+  grid = (int)((count + per - 1) / per);
+  size_t smem = (size_t)per * sizeof(float);
+  if (part_f32) allreduce_oneshot_kernel<float><<<grid, 256, smem, s>>>((__nv_bfloat16*)y, (const float*)part, (const __nv_bfloat16*)res, count, per, cb);
+  else allreduce_oneshot_kernel<__nv_bfloat16><<<grid, 256, smem, s>>>((__nv_bfloat16*)y, (const __nv_bfloat16*)part, (const __nv_bfloat16*)res, count, per, cb);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int fb_argmax_gather(int* ids, float* vals, const float* logits, long stride, int rows, int n_local,
+                                int vocab_offset, const void* const* peers, int rank, int world, int max_ctas,
+                                long slot_floats, uint32_t* epochs, int* status, unsigned spin_limit, cudaStream_t s) {
+  if (rows <= 0) return 0;
+  if (rows > max_ctas || (long)rows * 2 > slot_floats) return -8;
+  CommBuf cb;
+  fill_comm(cb, peers, rank, world, max_ctas, slot_floats, epochs, status, spin_limit);
+  argmax_gather_kernel<<<rows, 1024, 0, s>>>(ids, vals, logits, stride, n_local, vocab_offset, cb);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int fb_comm_wait_probe(const uint32_t* flag, uint32_t want, unsigned limit, int* status, cudaStream_t s) {
+  comm_wait_probe_kernel<<<1, 32, 0, s>>>(flag, want, limit, status);
+  return (int)cudaGetLastError();
+}

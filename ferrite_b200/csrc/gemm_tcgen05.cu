@@ -450,7 +450,7 @@ extern "C" int fb_gemm_bf16(void* Y, const void* X, const void* W, const void* r
   if (rc) return rc;
   static bool attr_done = false;
   if (!attr_done) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 216 * 1024);
     if (e != cudaSuccess) return (int)e;
     attr_done = true;
   }

@@ -1,8 +1,5 @@
 // Entry points declared in api.h whose kernels are not built yet return -100 so callers fail loudly.
 #include "api.h"
-extern "C" int fb_attn_prefill(void*, const void*, const void*, const void*, const void*, long, const int*, const int*,
-                               const int*, const int*, const int*, int, int, int, int, int, int, int, int,
-                               cudaStream_t) { return -100; }
 extern "C" int fb_gdn_chunk(float*, float*, void*, const void*, const void*, long, const float*, const float*,
                             const int*, const int*, const int*, int, int, int, int, int, float, int, cudaStream_t) {
   return -100;

@@ -59,6 +59,9 @@ class BlockPool:
         return len(self.free)
 
 
+FLASH_MIN_ROWS = 16      # segments longer than this go to the flash prefill kernel (reference FLASH_MIN 17)
+
+
 def _bucket(n: int) -> int:
     """Row-count buckets for graph keys: exact up to 8, then powers of two."""
     if n <= 8:
@@ -103,7 +106,11 @@ class Executor:
         R = ecfg.max_step_rows
         S = max(ecfg.n_slots, 1) * 2
         self.meta_i32 = torch.zeros(5 * R + 4 * S, dtype=torch.int32, device=dev)
-        self.meta_host = torch.zeros(5 * R + 4 * S, dtype=torch.int32, pin_memory=(dev.type == "cuda"))
+        # pinned staging ring: a buffer is rewritten only after the copy that last read it has completed
+        self._ring = [torch.zeros(5 * R + 4 * S, dtype=torch.int32, pin_memory=(dev.type == "cuda")) for _ in range(4)]
+        self._ring_ev = [None] * 4
+        self._ring_i = 0
+        self.h2d_bytes = 0
         self._R, self._S = R, S
         self.graphs: "OrderedDict[tuple, tuple]" = OrderedDict()
         self.taps: List[torch.Tensor] = []
@@ -195,7 +202,11 @@ class Executor:
         """Fill the pinned metadata buffer for this step and copy its used prefix to the device. Layout (int32):
         [tok T | slot T | pos T | kvlen T | lrow T | seg_slot S | seg_row0 S | seg_nrows S | seg_pos0 S]."""
         T, S = batch.n_rows, len(batch.segments)
-        h = self.meta_host
+        ri = self._ring_i
+        self._ring_i = (ri + 1) % len(self._ring)
+        if self._ring_ev[ri] is not None:
+            self._ring_ev[ri].synchronize()
+        h = self._ring[ri]
         tok, slot, pos, kvl, lrow = (h[i * T:(i + 1) * T] for i in range(5))
         o = 5 * T
         sslot, srow0, snrows, spos0 = (h[o + i * S:o + (i + 1) * S] for i in range(4))
@@ -218,6 +229,10 @@ class Executor:
         lrow[:nl] = torch.tensor(logit_rows, dtype=torch.int32) if nl else lrow[:0]
         used = 5 * T + 4 * S
         self.meta_i32[:used].copy_(h[:used], non_blocking=True)
+        if self.device.type == "cuda":
+            ev = torch.cuda.Event()
+            ev.record()
+            self._ring_ev[ri] = ev
         self.h2d_bytes = used * 4
         return logit_rows
 
@@ -257,8 +272,15 @@ class Executor:
                 q = ops.attn_prep(proj, w[p + "q_norm"], w[p + "k_norm"], self.inv_freq, mv["slot"], mv["pos"],
                                   self.block_table, self.k_cache[i], self.v_cache[i], self.ecfg.kv_block, c.n_q,
                                   c.n_kv, c.head_dim, c.rotary_dim, c.attn_gate, eps)
-                o = ops.attention(q, proj, self.k_cache[i], self.v_cache[i], mv["slot"], mv["kvlen"], self.block_table,
-                                  self.ecfg.kv_block, c.n_q, c.n_kv, c.head_dim, c.attn_gate, nsplit=nsplit)
+                if max_seg_rows > FLASH_MIN_ROWS:
+                    o = ops.attention_prefill(q, proj, self.k_cache[i], self.v_cache[i], mv["sslot"], mv["srow0"],
+                                              mv["snrows"], mv["spos0"], self.block_table, self.ecfg.kv_block, c.n_q,
+                                              c.n_kv, c.head_dim, c.attn_gate, max_seg_rows, row_slot=mv["slot"],
+                                              row_kvlen=mv["kvlen"])
+                else:
+                    o = ops.attention(q, proj, self.k_cache[i], self.v_cache[i], mv["slot"], mv["kvlen"],
+                                      self.block_table, self.ecfg.kv_block, c.n_q, c.n_kv, c.head_dim, c.attn_gate,
+                                      nsplit=nsplit)
                 x = self._row_parallel(o, w[p + "out_proj"], x)
             act = ops.linear(x, w[p + "gate_up"], norm_w=w[p + "post_norm"], eps=eps, swiglu=True)
             x = self._row_parallel(act, w[p + "down"], x)
@@ -301,7 +323,7 @@ class Executor:
         nseg = len(batch.segments)
         max_seg_rows = max(len(s.tokens) for s in batch.segments)
         max_kvlen = max(s.pos0 + len(s.tokens) for s in batch.segments)
-        nsplit = self.attn_splits(max_kvlen) if max_seg_rows <= 64 else 1
+        nsplit = self.attn_splits(max_kvlen) if max_seg_rows <= FLASH_MIN_ROWS else 1
         use_graph = (self.ecfg.use_graphs and self.device.type == "cuda" and T <= self.ecfg.decode_rows_max
                      and self.profile is None)
         logit_rows = self._upload(batch)

@@ -121,6 +121,15 @@ class CudaOps:
                            block_table, kv_block, nq, nkv, hd, nsplit, gated)
         return out
 
+    def attention_prefill(self, q, proj, k_cache, v_cache, seg_slot, seg_row0, seg_nrows, seg_pos0, block_table,
+                          kv_block, nq, nkv, hd, gated, max_rows, row_slot=None, row_kvlen=None):
+        """Causal flash attention over prompt segments (their K/V rows are already in the cache)."""
+        out = torch.empty(q.shape[0], nq * hd, dtype=self.dtype, device=self.device)
+        self.launches += 1
+        self.C.attn_prefill(out, q, k_cache, v_cache, proj, seg_slot, seg_row0, seg_nrows, seg_pos0, block_table,
+                            kv_block, max_rows, nq, nkv, hd, gated)
+        return out
+
     # ---- gated delta net ---------------------------------------------------------------------------
     def gdn_conv(self, proj, conv_w, conv_state, seg_slot, seg_row0, seg_nrows, conv_dim, max_rows=None):
         out = torch.empty(proj.shape[0], conv_dim, dtype=self.dtype, device=self.device)

@@ -117,6 +117,18 @@ class TorchOps:
             out = out * torch.sigmoid(gate)
         return out.reshape(T, nq * hd).to(self.dtype)
 
+    def attention_prefill(self, q, proj, k_cache, v_cache, seg_slot, seg_row0, seg_nrows, seg_pos0, block_table,
+                          kv_block, nq, nkv, hd, gated, max_rows, row_slot=None, row_kvlen=None):
+        if row_slot is None:
+            T = q.shape[0]
+            row_slot = torch.zeros(T, dtype=torch.int32, device=q.device)
+            row_kvlen = torch.zeros(T, dtype=torch.int32, device=q.device)
+            for s in range(len(seg_slot)):
+                n, r0 = int(seg_nrows[s]), int(seg_row0[s])
+                row_slot[r0:r0 + n] = int(seg_slot[s])
+                row_kvlen[r0:r0 + n] = torch.arange(int(seg_pos0[s]) + 1, int(seg_pos0[s]) + n + 1, dtype=torch.int32)
+        return self.attention(q, proj, k_cache, v_cache, row_slot, row_kvlen, block_table, kv_block, nq, nkv, hd, gated)
+
     # ---- gated delta net ---------------------------------------------------------------------------
     def gdn_conv(self, proj, conv_w, conv_state, seg_slot, seg_row0, seg_nrows, conv_dim):
         T = proj.shape[0]

@@ -1,0 +1,165 @@
+"""Kernel micro-benchmarks with roofline fractions (the role of the reference's `exl3-bench`, `fp4-bench`,
+`fabric-bench` and `ferrite gemm-bench` binaries, `crates/fe-exl3/src/bin`, `crates/fe-fp4/src/bin`).
+
+    python -m ferrite_b200.utils.microbench gemv --m 1 --n 34816 --k 5120 --swiglu
+    python -m ferrite_b200.utils.microbench gemm --m 2048 --n 5120 --k 17408
+    python -m ferrite_b200.utils.microbench layer           # every linear of one 27B decode step
+
+Timing: CUDA events on the launching stream, `--warmup` untimed launches (>= 3), an L2 flush (a write larger
+than L2) before every timed launch, median over `--iters`. Fractions are of the measured copy bandwidth / cuBLAS
+bf16 rate in MEASURED_PEAKS.json when that file is present ("of measured"), else of 6.65 TB/s / 1.59 PFLOP/s
+("of fallback").
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import statistics
+from pathlib import Path
+
+import torch
+
+
+def peaks():
+    p = Path(__file__).resolve().parents[2] / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return d["hbm_gbs"], d["bf16_tflops"], "of measured"
+    return 6650.0, 1590.0, "of fallback"
+
+
+class Timer:
+    def __init__(self, dev, warmup=3, iters=20, flush=True):
+        self.dev, self.warmup, self.iters, self.flush = dev, max(3, warmup), iters, flush
+        self.junk = torch.empty(256 << 20, dtype=torch.uint8, device=dev) if flush else None
+
+    def run(self, fn):
+        for _ in range(self.warmup):
+            fn()
+        torch.cuda.synchronize(self.dev)
+        ts = []
+        for _ in range(self.iters):
+            if self.flush:
+                self.junk.fill_(1)
+            e0, e1 = torch.cuda.Event(True), torch.cuda.Event(True)
+            torch.cuda.synchronize(self.dev)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize(self.dev)
+            ts.append(e0.elapsed_time(e1))
+        return statistics.median(ts)
+
+
+def rnd(*shape, scale=1.0, dtype=torch.bfloat16, dev="cuda"):
+    return (torch.randn(*shape, device=dev) * scale).to(dtype)
+
+
+def report(name, ms, nbytes, flops, extra=None):
+    hbm, tf, tag = peaks()
+    gbs = nbytes / ms / 1e6
+    tfl = flops / ms / 1e9
+    out = {"kernel": name, "ms": round(ms, 5), "GB/s": round(gbs, 1), "TFLOP/s": round(tfl, 2),
+           "frac_hbm": round(gbs / hbm, 3), "frac_bf16": round(tfl / tf, 3), "peaks": tag}
+    if extra:
+        out.update(extra)
+    print(json.dumps(out), flush=True)
+    return out
+
+
+def bench_linear(ops, t, m, n, k, swiglu=False, norm=False, res=False, label=None):
+    rows = 2 * n if swiglu else n
+    x, w = rnd(m, k), rnd(rows, k, scale=0.02)
+    nw = rnd(k, scale=0.1) if norm else None
+    r = rnd(m, n) if res else None
+    ms = t.run(lambda: ops.linear(x, w, norm_w=nw, res=r, swiglu=swiglu))
+    nbytes = rows * k * 2 + m * k * 2 + m * n * 2 * (2 if res else 1)
+    return report(label or f"linear m{m} n{n} k{k}{' swiglu' if swiglu else ''}", ms, nbytes, 2.0 * m * rows * k,
+                  {"m": m, "n": n, "k": k})
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("what", choices=["gemv", "gemm", "layer", "attn_decode", "attn_prefill", "gdn"])
+    ap.add_argument("--m", type=int, default=1)
+    ap.add_argument("--n", type=int, default=5120)
+    ap.add_argument("--k", type=int, default=5120)
+    ap.add_argument("--ctx", type=int, default=2048)
+    ap.add_argument("--swiglu", action="store_true")
+    ap.add_argument("--norm", action="store_true")
+    ap.add_argument("--res", action="store_true")
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--no-flush", action="store_true")
+    a = ap.parse_args()
+    from ..ops.cuda_ops import CudaOps
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    ops = CudaOps(dev)
+    t = Timer(dev, a.warmup, a.iters, flush=not a.no_flush)
+    if a.what in ("gemv", "gemm"):
+        bench_linear(ops, t, a.m, a.n, a.k, a.swiglu, a.norm, a.res)
+    elif a.what == "layer":
+        from ..config import hybrid_27b
+        c = hybrid_27b()
+        tot_ms = tot_b = 0.0
+        for m in (a.m,):
+            for label, n, k, sw, nm, rs in (
+                    ("gdn in_proj", c.gdn_in_dim, c.hidden, False, True, False),
+                    ("gdn out_proj", c.hidden, c.lin_v_heads * c.lin_dv, False, False, True),
+                    ("attn in_proj", c.attn_in_dim, c.hidden, False, True, False),
+                    ("attn out_proj", c.hidden, c.n_q * c.head_dim, False, False, True),
+                    ("mlp gate_up", c.inter, c.hidden, True, True, False),
+                    ("mlp down", c.hidden, c.inter, False, False, True),
+                    ("lm_head", c.vocab, c.hidden, False, True, False)):
+                r = bench_linear(ops, t, m, n, k, sw, nm, rs, label=f"{label} m{m}")
+                tot_ms += r["ms"]
+                tot_b += r["GB/s"] * r["ms"]
+        print(json.dumps({"sum_ms": round(tot_ms, 4), "mean_GB/s": round(tot_b / tot_ms, 1)}))
+    elif a.what in ("attn_decode", "attn_prefill"):
+        nq, nkv, hd, kvb = 24, 4, 256, 64
+        nslots = 4 if a.what == "attn_decode" else 1
+        rows = a.m if a.what == "attn_decode" else a.ctx
+        nb = (a.ctx + kvb - 1) // kvb
+        kc = rnd(nslots * nb, kvb, nkv, hd)
+        vc = rnd(nslots * nb, kvb, nkv, hd)
+        bt = torch.arange(nslots * nb, device=dev, dtype=torch.int32).view(nslots, nb)
+        proj = rnd(rows, nq * hd * 2 + 2 * nkv * hd)
+        q = rnd(rows, nq, hd)
+        if a.what == "attn_decode":
+            slot = (torch.arange(rows, device=dev, dtype=torch.int32) % nslots).contiguous()
+            kvlen = torch.full((rows,), a.ctx, device=dev, dtype=torch.int32)
+            ns = max(1, min(64, 1 << ((a.ctx + 255) // 256 - 1).bit_length()))
+            ms = t.run(lambda: ops.attention(q, proj, kc, vc, slot, kvlen, bt, kvb, nq, nkv, hd, True, nsplit=ns))
+            nbytes = rows * a.ctx * nkv * hd * 2 * 2
+            report(f"attn_decode rows{rows} ctx{a.ctx} splits{ns}", ms, nbytes, 4.0 * rows * a.ctx * nq * hd)
+        else:
+            i32 = lambda v: torch.tensor([v], device=dev, dtype=torch.int32)
+            ms = t.run(lambda: ops.attention_prefill(q, proj, kc, vc, i32(0), i32(0), i32(rows), i32(0), bt, kvb, nq,
+                                                     nkv, hd, True, rows))
+            report(f"attn_prefill ctx{a.ctx}", ms, 2 * a.ctx * nkv * hd * 2, 4.0 * a.ctx * a.ctx / 2 * nq * hd)
+    elif a.what == "gdn":
+        nk = nv = 16
+        dk = dv = 128
+        conv_dim = 2 * nk * dk + nv * dv
+        rows = a.m
+        proj = rnd(rows, conv_dim + nv * dv + 2 * nv)
+        conv_w = rnd(conv_dim, 4, scale=0.5)
+        rec = rnd(4, nv, dk, dv, scale=0.1, dtype=torch.float32)
+        cst = rnd(4, 3, conv_dim)
+        A, dtb = rnd(nv, dtype=torch.float32), rnd(nv, dtype=torch.float32)
+        i32 = lambda v: torch.tensor(v, device=dev, dtype=torch.int32)
+        nseg = min(4, rows)
+        per = rows // nseg
+        ss, r0, nr = i32(list(range(nseg))), i32([i * per for i in range(nseg)]), i32([per] * nseg)
+
+        def fn():
+            qkv = ops.gdn_conv(proj, conv_w, cst, ss, r0, nr, conv_dim, max_rows=per)
+            ops.gdn_rec(qkv, proj, rec, cst, A, dtb, ss, r0, nr, nk, nv, dk, dv, 1e-6, commit=True,
+                        chunked=per > 16)
+        ms = t.run(fn)
+        report(f"gdn conv+rec rows{rows} segs{nseg}", ms, nseg * nv * dk * dv * 4 * 2, 0.0)
+
+
+if __name__ == "__main__":
+    main()

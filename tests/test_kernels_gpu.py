@@ -126,6 +126,13 @@ def test_attention_paged(ops, tops, hd, nq, nkv, rot):
         oa = ops.attention(qa, proj, kc[0], vc[0], slot, kvlen, bt, kv_block, nq, nkv, hd, gated, nsplit=nsplit)
         ob = tops.attention(qb, proj, kc[1], vc[1], slot, kvlen, bt, kv_block, nq, nkv, hd, gated)
         close(oa, ob)
+    # flash prefill kernel: the same rows as two segments (a resumed prompt with a 100-key prefix, and a fresh one)
+    seg_slot = torch.tensor([1], device=DEV, dtype=torch.int32)
+    for r0, n, p0 in ((0, 300, 0), (100, 200, 100), (290, 10, 290)):
+        segs = [seg_slot, torch.tensor([r0], device=DEV, dtype=torch.int32),
+                torch.tensor([n], device=DEV, dtype=torch.int32), torch.tensor([p0], device=DEV, dtype=torch.int32)]
+        of = ops.attention_prefill(qa, proj, kc[0], vc[0], *segs, bt, kv_block, nq, nkv, hd, gated, n)
+        close(of[r0:r0 + n], ob[r0:r0 + n])
     # tree mask: rows see the first 290 keys plus chosen later ones
     base = torch.full((300,), 290, device=DEV, dtype=torch.int32)
     mask = torch.full((300,), 0b1010010011, device=DEV, dtype=torch.int64)
