@@ -60,6 +60,8 @@ int fb_gdn_chunk(float* y, float* rec_state, void* conv_state, const void* qkv, 
 // ---- sample.cu ----
 int fb_argmax(int* ids, float* vals, int* finite, const void* logits, long stride, int rows, int vocab, int is_f32,
               cudaStream_t s);
+int fb_argmax2(int* ids, float* vals, int* finite, const void* logits, long stride, int rows, int vocab, int is_f32,
+               void* scratch, cudaStream_t s);
 int fb_sample(int* ids, const void* logits, long stride, int rows, int vocab, const void* params, const int* counts,
               float* work, int is_f32, cudaStream_t s);
 int fb_chain_accept(int* n_accept, int* out_tokens, const int* target, const int* draft, const int* seg_row0,

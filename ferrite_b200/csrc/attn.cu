@@ -22,6 +22,7 @@ __global__ void attn_prep_kernel(__nv_bfloat16* __restrict__ q_out, __nv_bfloat1
                                  const int* __restrict__ row_slot, const int* __restrict__ row_pos,
                                  const int* __restrict__ block_table, int max_blocks, int kv_block, int nq, int nkv,
                                  int rot, int gated, float eps, int* status) {
+  pdl_launch_dependents();
   constexpr int EPL = HD / 32;
   const int row = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -75,9 +76,9 @@ __global__ void attn_prep_kernel(__nv_bfloat16* __restrict__ q_out, __nv_bfloat1
 }
 
 // ---------------------------------------------------------------------------------------------------
-// Split-KV decode attention. grid = (rows, kv heads, splits), 4 warps per CTA. A lane group of HD/8 lanes
+// Split-KV decode attention. grid = (rows, kv heads, splits), 8 warps per CTA. A lane group of HD/8 lanes
 // owns one key at a time; every lane keeps 8 dims of K, V and of the G query heads of the group.
-constexpr int ATT_WARPS = 4;
+constexpr int ATT_WARPS = 8;
 
 template <int HD, int G>
 __global__ void __launch_bounds__(ATT_WARPS * 32)
@@ -87,6 +88,7 @@ attn_decode_kernel(float* __restrict__ o_part, float* __restrict__ ml_part, cons
                    const int* __restrict__ row_base, const unsigned long long* __restrict__ row_mask,
                    const int* __restrict__ block_table, int max_blocks, int kv_block, int nq, int nkv, int nsplit,
                    float scale_log2) {
+  pdl_launch_dependents();
   constexpr int LPK = HD / 8;           // lanes per key
   constexpr int KPI = 32 / LPK;         // keys per warp iteration
   extern __shared__ float sm[];         // [ATT_WARPS][G][HD] o, then [ATT_WARPS][G][2] m,l
@@ -118,39 +120,51 @@ attn_decode_kernel(float* __restrict__ o_part, float* __restrict__ ml_part, cons
     for (int j = 0; j < 8; ++j) o[g][j] = 0.f;
   }
   const int* bt = block_table + (size_t)slot * max_blocks;
-  for (int t0 = lo + warp * KPI; t0 < hi; t0 += ATT_WARPS * KPI) {
-    const int t = t0 + kslot;
-    bool vis = t < hi;
-    if (vis && t >= base) vis = ((mask >> (t - base)) & 1ull) != 0ull;
-    uint4 kv = make_uint4(0, 0, 0, 0), vv = make_uint4(0, 0, 0, 0);
-    if (vis) {
-      const int blk = bt[t / kv_block];
-      const size_t off = (((size_t)blk * kv_block + (t % kv_block)) * nkv + kvh) * HD + sub * 8;
-      kv = ldg_stream(k_cache + off);
-      vv = ldg_stream(v_cache + off);
-    }
-    uint32_t ku[4] = {kv.x, kv.y, kv.z, kv.w}, vu[4] = {vv.x, vv.y, vv.z, vv.w};
-    float kf[8], vf[8];
+  // UN keys per lane group are in flight at once: all their K/V loads are issued before any is consumed
+  constexpr int UN = (G <= 6) ? 4 : 2;
+  for (int t0 = lo + warp * KPI * UN; t0 < hi; t0 += ATT_WARPS * KPI * UN) {
+    uint4 kraw[UN], vraw[UN];
+    bool visb[UN];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      kf[2 * j] = bf_lo(ku[j]); kf[2 * j + 1] = bf_hi(ku[j]);
-      vf[2 * j] = bf_lo(vu[j]); vf[2 * j + 1] = bf_hi(vu[j]);
-    }
-#pragma unroll
-    for (int g = 0; g < G; ++g) {
-      float s = 0.f;
-#pragma unroll
-      for (int j = 0; j < 8; ++j) s = fmaf(qf[g][j], kf[j], s);
-#pragma unroll
-      for (int off = LPK / 2; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+    for (int u = 0; u < UN; ++u) {
+      const int t = t0 + u * KPI + kslot;
+      bool vis = t < hi;
+      if (vis && t >= base) vis = ((mask >> (t - base)) & 1ull) != 0ull;
+      visb[u] = vis;
+      kraw[u] = make_uint4(0, 0, 0, 0); vraw[u] = make_uint4(0, 0, 0, 0);
       if (vis) {
-        float mn = fmaxf(m[g], s);
-        float sc = exp2f(m[g] - mn);
-        float p = exp2f(s - mn);
-        l[g] = l[g] * sc + p;
+        const int blk = bt[t / kv_block];
+        const size_t off = (((size_t)blk * kv_block + (t % kv_block)) * nkv + kvh) * HD + sub * 8;
+        kraw[u] = ldg_stream(k_cache + off);
+        vraw[u] = ldg_stream(v_cache + off);
+      }
+    }
 #pragma unroll
-        for (int j = 0; j < 8; ++j) o[g][j] = fmaf(p, vf[j], o[g][j] * sc);
-        m[g] = mn;
+    for (int u = 0; u < UN; ++u) {
+      const bool vis = visb[u];
+      uint32_t ku[4] = {kraw[u].x, kraw[u].y, kraw[u].z, kraw[u].w}, vu[4] = {vraw[u].x, vraw[u].y, vraw[u].z, vraw[u].w};
+      float kf[8], vf[8];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        kf[2 * j] = bf_lo(ku[j]); kf[2 * j + 1] = bf_hi(ku[j]);
+        vf[2 * j] = bf_lo(vu[j]); vf[2 * j + 1] = bf_hi(vu[j]);
+      }
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        float s = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) s = fmaf(qf[g][j], kf[j], s);
+#pragma unroll
+        for (int off = LPK / 2; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+        if (vis) {
+          float mn = fmaxf(m[g], s);
+          float sc = exp2f(m[g] - mn);
+          float p = exp2f(s - mn);
+          l[g] = l[g] * sc + p;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[g][j] = fmaf(p, vf[j], o[g][j] * sc);
+          m[g] = mn;
+        }
       }
     }
   }
@@ -210,6 +224,7 @@ template <int HD>
 __global__ void attn_combine_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict__ o_part,
                                     const float* __restrict__ ml_part, const __nv_bfloat16* __restrict__ proj,
                                     long proj_stride, int nq, int nsplit, int gated) {
+  pdl_launch_dependents();
   const int row = blockIdx.x, qh = blockIdx.y;
   const size_t pbase = ((size_t)row * nq + qh) * nsplit;
   float M = -INFINITY;

@@ -133,7 +133,15 @@ void gdn_rec(Tensor y, Tensor rec_state, Tensor conv_state, Tensor qkv, Tensor p
            (int)dv, (float)eps, commit ? 1 : 0, cur_stream()), "gdn_rec");
 }
 
-void argmax(Tensor ids, Tensor logits, c10::optional<Tensor> vals, c10::optional<Tensor> finite) {
+void argmax(Tensor ids, Tensor logits, c10::optional<Tensor> vals, c10::optional<Tensor> finite,
+            c10::optional<Tensor> scratch) {
+  if (scratch.has_value() && scratch->defined() && logits.size(1) >= 8192) {
+    TORCH_CHECK(scratch->numel() * scratch->element_size() >= logits.size(0) * 64 * 12, "argmax scratch too small");
+    check(fb_argmax2(ids.data_ptr<int>(), (float*)mptr(vals), (int*)mptr(finite), logits.data_ptr(),
+                     (long)logits.stride(0), (int)logits.size(0), (int)logits.size(1),
+                     logits.scalar_type() == torch::kFloat32 ? 1 : 0, scratch->data_ptr(), cur_stream()), "argmax2");
+    return;
+  }
   check(fb_argmax(ids.data_ptr<int>(), (float*)mptr(vals), (int*)mptr(finite), logits.data_ptr(),
                   (long)logits.stride(0), (int)logits.size(0), (int)logits.size(1),
                   logits.scalar_type() == torch::kFloat32 ? 1 : 0, cur_stream()), "argmax");

@@ -95,73 +95,22 @@ __global__ void __launch_bounds__(GEMV_THREADS) gemv_allreduce_kernel(GemvArgs a
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(smem_raw);
   float* tile = reinterpret_cast<float*>(smem_raw + (size_t)M * a.kc * sizeof(__nv_bfloat16));  // [M][rows_per_cta]
-  __shared__ float rscale_dummy[M];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __shared__ float rscale[M];
+  __shared__ float scratch[32];
   const int row0 = blockIdx.x * a.rows_per_cta;
   const int row_end = min(a.N, row0 + a.rows_per_cta);
   const int nrows = row_end - row0;
-  const int nchunks = (a.K + a.kc - 1) / a.kc;
   for (int i = threadIdx.x; i < M * a.rows_per_cta; i += blockDim.x) tile[i] = 0.f;
-
-  if (nchunks == 1) {
-    gemv_stage_x<M>(a, xs, rscale_dummy, 0, a.kc);
-    __syncthreads();
-    for (int n = row0 + warp * R; n < row_end; n += GEMV_WARPS * R) {
-      float acc[R][M];
-#pragma unroll
-      for (int r = 0; r < R; ++r)
-#pragma unroll
-        for (int m = 0; m < M; ++m) acc[r][m] = 0.f;
-      const __nv_bfloat16* wrow[R];
-#pragma unroll
-      for (int r = 0; r < R; ++r) wrow[r] = a.W + (size_t)min(n + r, a.N - 1) * a.K;
-      gemv_accumulate<M, R>(acc, wrow, xs, a.kc, a.K);
-#pragma unroll
-      for (int r = 0; r < R; ++r)
-#pragma unroll
-        for (int m = 0; m < M; ++m) acc[r][m] = warp_sum(acc[r][m]);
-      if (lane == 0) {
-#pragma unroll
-        for (int r = 0; r < R; ++r)
-          if (n + r < row_end)
-#pragma unroll
-            for (int m = 0; m < M; ++m) tile[m * a.rows_per_cta + (n + r - row0)] = acc[r][m];
-      }
-    }
-  } else {
-    int n = row0 + warp * R;
-    bool active = n < row_end;
-    float acc[R][M];
+  __syncthreads();
+  const int rpc = a.rows_per_cta;
+  gemv_main<M, R, false>(a, xs, rscale, scratch, [&](float (&acc)[R][M], int n) {
+    if ((threadIdx.x & 31) != 0) return;
 #pragma unroll
     for (int r = 0; r < R; ++r)
+      if (n + r < row_end)
 #pragma unroll
-      for (int m = 0; m < M; ++m) acc[r][m] = 0.f;
-    for (int c = 0; c < nchunks; ++c) {
-      int k0 = c * a.kc;
-      __syncthreads();
-      gemv_stage_x<M>(a, xs, rscale_dummy, k0, a.kc);
-      __syncthreads();
-      if (active) {
-        const __nv_bfloat16* wrow[R];
-#pragma unroll
-        for (int r = 0; r < R; ++r) wrow[r] = a.W + (size_t)min(n + r, a.N - 1) * a.K + k0;
-        gemv_accumulate<M, R>(acc, wrow, xs, a.kc, a.K - k0);
-      }
-    }
-    if (active) {
-#pragma unroll
-      for (int r = 0; r < R; ++r)
-#pragma unroll
-        for (int m = 0; m < M; ++m) acc[r][m] = warp_sum(acc[r][m]);
-      if (lane == 0) {
-#pragma unroll
-        for (int r = 0; r < R; ++r)
-          if (n + r < row_end)
-#pragma unroll
-            for (int m = 0; m < M; ++m) tile[m * a.rows_per_cta + (n + r - row0)] = acc[r][m];
-      }
-    }
-  }
+        for (int m = 0; m < M; ++m) tile[m * rpc + (n + r - row0)] = acc[r][m];
+  });
   __syncthreads();
   // slot layout: CTA-major, so a CTA's tile is one contiguous run of M * rows_per_cta floats
   cta_exchange_sum(cb, tile, M * a.rows_per_cta, (long)blockIdx.x * M * a.rows_per_cta);

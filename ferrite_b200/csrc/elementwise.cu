@@ -9,6 +9,7 @@ namespace fb {
 
 __global__ void embed_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ table,
                              const int* __restrict__ ids, int hidden, int vocab) {
+  pdl_launch_dependents();
   int row = blockIdx.x;
   int id = ids[row];
   if (id < 0 || id >= vocab) id = 0;
@@ -22,6 +23,7 @@ __global__ void embed_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat1
 __global__ void rmsnorm_kernel(__nv_bfloat16* __restrict__ out, __nv_bfloat16* __restrict__ x_out,
                                const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
                                const __nv_bfloat16* __restrict__ w, int hidden, float eps, int centred) {
+  pdl_launch_dependents();
   extern __shared__ float xs[];          // hidden floats
   __shared__ float scratch[32];
   int row = blockIdx.x;
@@ -96,6 +98,7 @@ __global__ void silu_mul_kernel(__nv_bfloat16* __restrict__ out, const __nv_bflo
 __global__ void gated_norm_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict__ y,
                                   const __nv_bfloat16* __restrict__ z, long z_stride,
                                   const __nv_bfloat16* __restrict__ w, int heads, int dv, float eps) {
+  pdl_launch_dependents();
   int row = blockIdx.x;
   int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   int nw = blockDim.x >> 5;

@@ -19,6 +19,7 @@ __global__ void gdn_conv_kernel(__nv_bfloat16* __restrict__ out, const __nv_bflo
                                 long proj_stride, const __nv_bfloat16* __restrict__ conv_w,
                                 const __nv_bfloat16* __restrict__ conv_state, const int* __restrict__ seg_slot,
                                 const int* __restrict__ seg_row0, const int* __restrict__ seg_nrows, int conv_dim) {
+  pdl_launch_dependents();
   constexpr int CK = 4, CHUNK = 32;
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   const int seg = blockIdx.z;
@@ -55,6 +56,7 @@ gdn_rec_kernel(float* __restrict__ y, float* __restrict__ rec_state, __nv_bfloat
                const float* __restrict__ A_log, const float* __restrict__ dt_bias, const int* __restrict__ seg_slot,
                const int* __restrict__ seg_row0, const int* __restrict__ seg_nrows, int nk, int nv, float eps,
                int commit) {
+  pdl_launch_dependents();
   constexpr int PARTS = 8, RP = DK / PARTS, CK = 4;
   __shared__ float qs[DK], ks[DK], vs[DV];
   __shared__ float red1[PARTS][DV], red2[PARTS][DV];

@@ -1,118 +1,44 @@
 // bf16 GEMV for 1..8 activation rows with fused prologue (RMSNorm) and epilogue (residual add, SwiGLU).
 // Replaces `fe_gemv_bf16`, `fe_gemv_bf16_kw` (`kernels/k-core/src/gemm.rs:149-194`) and, with its fused forms,
 // the separate `fe_rmsnorm` / `fe_silu_mul` / `fe_add_bf16` launches around them on the decode path.
+//
+// Launched with programmatic stream serialization: the grid may become resident while the previous kernel of
+// the stream drains; it issues its first batch of weight loads (weights never depend on the previous kernel)
+// and only then executes griddepcontrol.wait before touching X. The reference overlaps the same way
+// ("L2 prefetch before griddepcontrol.wait", `crates/fe-exl3/src/gpu/pdl.rs`).
 #include "api.h"
 #include "gemv_core.cuh"
 
 namespace fb {
 
 template <int M, int R, bool SWIGLU>
-__global__ void __launch_bounds__(GEMV_THREADS) gemv_kernel(GemvArgs a) {
+__global__ void __launch_bounds__(GEMV_THREADS, (M <= 2 ? 4 : (M <= 4 ? 3 : 2))) gemv_kernel(GemvArgs a) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(smem_raw);
   __shared__ float scratch[32];
   __shared__ float rscale[M];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-
-  if (a.norm_w) gemv_row_scales<M>(a, rscale, scratch);
-
-  const int row0 = blockIdx.x * a.rows_per_cta;
-  const int row_end = min(a.N, row0 + a.rows_per_cta);
-  const int nchunks = (a.K + a.kc - 1) / a.kc;
-  constexpr int RW = SWIGLU ? 1 : R;     // output rows a warp produces per pass
-
-  if (nchunks == 1) {
-    gemv_stage_x<M>(a, xs, rscale, 0, a.kc);
-    __syncthreads();
-    for (int n = row0 + warp * RW; n < row_end; n += GEMV_WARPS * RW) {
-      float acc[R][M];
+  const int row_end = min(a.N, (int)(blockIdx.x + 1) * a.rows_per_cta);
+  gemv_main<M, R, SWIGLU>(a, xs, rscale, scratch, [&](float (&acc)[R][M], int n) {
+    if ((threadIdx.x & 31) != 0) return;
 #pragma unroll
-      for (int r = 0; r < R; ++r)
-#pragma unroll
-        for (int m = 0; m < M; ++m) acc[r][m] = 0.f;
-      const __nv_bfloat16* wrow[R];
-#pragma unroll
-      for (int r = 0; r < R; ++r) {
-        int rr = SWIGLU ? (n + r * a.N) : min(n + r, a.N - 1);
-        wrow[r] = a.W + (size_t)rr * a.K;
-      }
-      gemv_accumulate<M, R>(acc, wrow, xs, a.kc, a.K);
-#pragma unroll
-      for (int r = 0; r < R; ++r)
-#pragma unroll
-        for (int m = 0; m < M; ++m) acc[r][m] = warp_sum(acc[r][m]);
-      if (lane == 0) {
-#pragma unroll
-        for (int m = 0; m < M; ++m) {
-          if (m >= a.M) break;
-          if (SWIGLU) {
-            float v = siluf_(acc[0][m]) * acc[R - 1][m];
-            reinterpret_cast<__nv_bfloat16*>(a.Y)[(size_t)m * a.ldy + n] = f2bf(v);
-          } else {
-#pragma unroll
-            for (int r = 0; r < R; ++r) {
-              int nn = n + r;
-              if (nn >= row_end) break;
-              float v = acc[r][m];
-              if (a.res) v += bf2f(a.res[(size_t)m * a.ldy + nn]);
-              if (a.out_f32) reinterpret_cast<float*>(a.Y)[(size_t)m * a.ldy + nn] = v;
-              else reinterpret_cast<__nv_bfloat16*>(a.Y)[(size_t)m * a.ldy + nn] = f2bf(v);
-            }
-          }
-        }
-      }
-    }
-  } else {
-    // K does not fit one staged chunk: one row group per warp, chunks in the outer loop
-    int n = row0 + warp * RW;
-    bool active = n < row_end;
-    float acc[R][M];
-#pragma unroll
-    for (int r = 0; r < R; ++r)
-#pragma unroll
-      for (int m = 0; m < M; ++m) acc[r][m] = 0.f;
-    for (int c = 0; c < nchunks; ++c) {
-      int k0 = c * a.kc;
-      __syncthreads();
-      gemv_stage_x<M>(a, xs, rscale, k0, a.kc);
-      __syncthreads();
-      if (active) {
-        const __nv_bfloat16* wrow[R];
+    for (int m = 0; m < M; ++m) {
+      if (m >= a.M) break;
+      if (SWIGLU) {
+        float v = siluf_(acc[0][m]) * acc[R - 1][m];
+        reinterpret_cast<__nv_bfloat16*>(a.Y)[(size_t)m * a.ldy + n] = f2bf(v);
+      } else {
 #pragma unroll
         for (int r = 0; r < R; ++r) {
-          int rr = SWIGLU ? (n + r * a.N) : min(n + r, a.N - 1);
-          wrow[r] = a.W + (size_t)rr * a.K + k0;
-        }
-        gemv_accumulate<M, R>(acc, wrow, xs, a.kc, a.K - k0);
-      }
-    }
-    if (active) {
-#pragma unroll
-      for (int r = 0; r < R; ++r)
-#pragma unroll
-        for (int m = 0; m < M; ++m) acc[r][m] = warp_sum(acc[r][m]);
-      if (lane == 0) {
-#pragma unroll
-        for (int m = 0; m < M; ++m) {
-          if (m >= a.M) break;
-          if (SWIGLU) {
-            float v = siluf_(acc[0][m]) * acc[R - 1][m];
-            reinterpret_cast<__nv_bfloat16*>(a.Y)[(size_t)m * a.ldy + n] = f2bf(v);
-          } else {
-#pragma unroll
-            for (int r = 0; r < R; ++r) {
-              int nn = n + r;
-              if (nn >= row_end) break;
-              float v = acc[r][m];
-              if (a.res) v += bf2f(a.res[(size_t)m * a.ldy + nn]);
-              if (a.out_f32) reinterpret_cast<float*>(a.Y)[(size_t)m * a.ldy + nn] = v;
-              else reinterpret_cast<__nv_bfloat16*>(a.Y)[(size_t)m * a.ldy + nn] = f2bf(v);
-            }
-          }
+          int nn = n + r;
+          if (nn >= row_end) break;
+          float v = acc[r][m];
+          if (a.res) v += bf2f(a.res[(size_t)m * a.ldy + nn]);
+          if (a.out_f32) reinterpret_cast<float*>(a.Y)[(size_t)m * a.ldy + nn] = v;
+          else reinterpret_cast<__nv_bfloat16*>(a.Y)[(size_t)m * a.ldy + nn] = f2bf(v);
         }
       }
     }
-  }
+  });
 }
 
 template <int M, int R, bool SWIGLU>
@@ -137,8 +63,13 @@ static int launch_gemv(GemvArgs a, int sm_count, cudaStream_t s) {
     if (e != cudaSuccess) return (int)e;
     attr_done = true;
   }
-  kern<<<grid, GEMV_THREADS, smem, s>>>(a);
-  return (int)cudaGetLastError();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid); cfg.blockDim = dim3(GEMV_THREADS); cfg.dynamicSmemBytes = smem; cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr; cfg.numAttrs = 1;
+  return (int)cudaLaunchKernelEx(&cfg, kern, a);
 }
 
 }  // namespace fb

@@ -84,44 +84,130 @@ __device__ __forceinline__ void gemv_row_scales(const GemvArgs& a, float* rscale
   __syncthreads();
 }
 
-// Accumulate R weight rows against the staged chunk. wrow[r] points at W[row_r][k0].
-template <int M, int R>
-__device__ __forceinline__ void gemv_accumulate(float (&acc)[R][M], const __nv_bfloat16* const (&wrow)[R],
-                                                const __nv_bfloat16* xs, int kc, int kvalid) {
+// Issue the R x U weight loads of the batch starting at k = base (elements, relative to wrow).
+template <int R>
+__device__ __forceinline__ void gemv_load_batch(uint4 (&wv)[R][GEMV_U], const __nv_bfloat16* const (&wrow)[R], int base,
+                                                int kvalid) {
   const int lane = threadIdx.x & 31;
-  for (int base = 0; base < kc; base += GEMV_STEP * GEMV_U) {
-    uint4 wv[R][GEMV_U];
 #pragma unroll
-    for (int u = 0; u < GEMV_U; ++u) {
-      int k = base + u * GEMV_STEP + lane * 8;
+  for (int u = 0; u < GEMV_U; ++u) {
+    int k = base + u * GEMV_STEP + lane * 8;
 #pragma unroll
-      for (int r = 0; r < R; ++r)
-        wv[r][u] = (k < kvalid) ? ldg_stream(wrow[r] + k) : make_uint4(0, 0, 0, 0);
+    for (int r = 0; r < R; ++r) wv[r][u] = (k < kvalid) ? ldg_stream(wrow[r] + k) : make_uint4(0, 0, 0, 0);
+  }
+}
+
+// acc += W batch (registers) x staged activations. koff = position of the batch inside the staged chunk.
+template <int M, int R>
+__device__ __forceinline__ void gemv_consume_batch(float (&acc)[R][M], const uint4 (&wv)[R][GEMV_U],
+                                                   const __nv_bfloat16* xs, int kc, int koff) {
+  const int lane = threadIdx.x & 31;
+#pragma unroll
+  for (int u = 0; u < GEMV_U; ++u) {
+    const int k = koff + u * GEMV_STEP + lane * 8;
+    if (k >= kc) continue;
+    float wf[R][8];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      uint32_t wu[4] = {wv[r][u].x, wv[r][u].y, wv[r][u].z, wv[r][u].w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { wf[r][2 * j] = bf_lo(wu[j]); wf[r][2 * j + 1] = bf_hi(wu[j]); }
     }
 #pragma unroll
-    for (int u = 0; u < GEMV_U; ++u) {
-      int k = base + u * GEMV_STEP + lane * 8;
-      if (k >= kc) continue;
-      float wf[R][8];
+    for (int m = 0; m < M; ++m) {
+      uint4 xv = *reinterpret_cast<const uint4*>(xs + (size_t)m * kc + k);
+      uint32_t xu[4] = {xv.x, xv.y, xv.z, xv.w};
+      float xf[8];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { xf[2 * j] = bf_lo(xu[j]); xf[2 * j + 1] = bf_hi(xu[j]); }
 #pragma unroll
       for (int r = 0; r < R; ++r) {
-        uint32_t wu[4] = {wv[r][u].x, wv[r][u].y, wv[r][u].z, wv[r][u].w};
 #pragma unroll
-        for (int j = 0; j < 4; ++j) { wf[r][2 * j] = bf_lo(wu[j]); wf[r][2 * j + 1] = bf_hi(wu[j]); }
+        for (int j = 0; j < 8; ++j) acc[r][m] = fmaf(wf[r][j], xf[j], acc[r][m]);
       }
+    }
+  }
+}
+
+template <int R, bool SWIGLU>
+__device__ __forceinline__ void gemv_row_ptrs(const GemvArgs& a, const __nv_bfloat16* (&wrow)[R], int n) {
 #pragma unroll
-      for (int m = 0; m < M; ++m) {
-        uint4 xv = *reinterpret_cast<const uint4*>(xs + (size_t)m * kc + k);
-        uint32_t xu[4] = {xv.x, xv.y, xv.z, xv.w};
-        float xf[8];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) { xf[2 * j] = bf_lo(xu[j]); xf[2 * j + 1] = bf_hi(xu[j]); }
-#pragma unroll
-        for (int r = 0; r < R; ++r) {
-#pragma unroll
-          for (int j = 0; j < 8; ++j) acc[r][m] = fmaf(wf[r][j], xf[j], acc[r][m]);
+  for (int r = 0; r < R; ++r) {
+    int rr = SWIGLU ? (min(n, a.N - 1) + r * a.N) : min(n + r, a.N - 1);
+    wrow[r] = a.W + (size_t)rr * a.K;
+  }
+}
+
+// The whole GEMV main loop of one CTA, shared by the plain and the fused-collective kernels.
+//
+// The weight batch a warp will consume next is always already in flight: the first one is requested before
+// griddepcontrol.wait (weights never depend on the previous kernel of the stream, so under programmatic
+// dependent launch those loads overlap its tail and this kernel's own prologue), and each later one right
+// after the previous batch was consumed, across row-group boundaries too. `store(acc, n)` is called by every
+// lane of the warp with the warp-reduced sums of row group n.
+template <int M, int R, bool SWIGLU, class Store>
+__device__ __forceinline__ void gemv_main(const GemvArgs& a, __nv_bfloat16* xs, float* rscale, float* scratch,
+                                          Store store) {
+  const int warp = threadIdx.x >> 5;
+  const int row0 = blockIdx.x * a.rows_per_cta;
+  const int row_end = min(a.N, row0 + a.rows_per_cta);
+  const int nchunks = (a.K + a.kc - 1) / a.kc;
+  constexpr int RW = SWIGLU ? 1 : R;
+  constexpr int BATCH = GEMV_STEP * GEMV_U;
+  int n = row0 + warp * RW;
+
+  pdl_launch_dependents();
+  uint4 wv[R][GEMV_U];
+  const __nv_bfloat16* wrow[R];
+  gemv_row_ptrs<R, SWIGLU>(a, wrow, n);
+  gemv_load_batch<R>(wv, wrow, 0, a.K);
+  pdl_wait();
+
+  if (a.norm_w) gemv_row_scales<M>(a, rscale, scratch);
+
+  if (nchunks == 1) {
+    gemv_stage_x<M>(a, xs, rscale, 0, a.kc);
+    __syncthreads();
+    for (; n < row_end; n += GEMV_WARPS * RW) {
+      float acc[R][M] = {};
+      for (int base = 0; base < a.kc; base += BATCH) {
+        gemv_consume_batch<M, R>(acc, wv, xs, a.kc, base);
+        if (base + BATCH < a.kc) {
+          gemv_load_batch<R>(wv, wrow, base + BATCH, a.K);
+        } else if (n + GEMV_WARPS * RW < row_end) {
+          gemv_row_ptrs<R, SWIGLU>(a, wrow, n + GEMV_WARPS * RW);
+          gemv_load_batch<R>(wv, wrow, 0, a.K);
         }
       }
+#pragma unroll
+      for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int m = 0; m < M; ++m) acc[r][m] = warp_sum(acc[r][m]);
+      store(acc, n);
+    }
+  } else {
+    // K does not fit one staged chunk: one row group per warp, chunks in the outer loop
+    const bool active = n < row_end;
+    float acc[R][M] = {};
+    for (int c = 0; c < nchunks; ++c) {
+      const int k0 = c * a.kc;
+      __syncthreads();
+      gemv_stage_x<M>(a, xs, rscale, k0, a.kc);
+      __syncthreads();
+      if (active) {
+        for (int base = 0; base < a.kc; base += BATCH) {
+          gemv_consume_batch<M, R>(acc, wv, xs, a.kc, base);
+          const int knext = k0 + base + BATCH;
+          if (knext < a.K) gemv_load_batch<R>(wv, wrow, knext, a.K);
+        }
+      }
+    }
+    if (active) {
+#pragma unroll
+      for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int m = 0; m < M; ++m) acc[r][m] = warp_sum(acc[r][m]);
+      store(acc, n);
     }
   }
 }

@@ -15,6 +15,7 @@ template <> __device__ __forceinline__ float ld_logit<__nv_bfloat16>(const __nv_
 template <typename T>
 __global__ void argmax_kernel(int* __restrict__ ids, float* __restrict__ vals, int* __restrict__ finite,
                               const T* __restrict__ logits, long stride, int vocab) {
+  pdl_launch_dependents();
   __shared__ float sv[32];
   __shared__ int si[32];
   __shared__ int sbad;
@@ -55,6 +56,76 @@ __global__ void argmax_kernel(int* __restrict__ ids, float* __restrict__ vals, i
       if (vals) vals[row] = best;
       if (finite) finite[row] = sbad ? 0 : 1;
     }
+  }
+}
+
+// Two-stage argmax for wide vocabularies: stage 1 scans a slice of the row per CTA, stage 2 merges the slices in
+// slice order (ties to the lower index), so one row is spread over many SMs instead of one.
+constexpr int AM_SLICES = 64;
+template <typename T>
+__global__ void argmax_part_kernel(float* __restrict__ pv, int* __restrict__ pi, int* __restrict__ pbad,
+                                   const T* __restrict__ logits, long stride, int vocab) {
+  pdl_launch_dependents();
+  __shared__ float sv[8];
+  __shared__ int si[8];
+  __shared__ int sbad;
+  const int row = blockIdx.x, slice = blockIdx.y;
+  const int per = (vocab + AM_SLICES - 1) / AM_SLICES;
+  const int lo = slice * per, hi = min(vocab, lo + per);
+  const T* lp = logits + (size_t)row * stride;
+  if (threadIdx.x == 0) sbad = 0;
+  __syncthreads();
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  bool bad = false;
+  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+    float v = ld_logit<T>(lp, i);
+    if (!isfinite(v)) bad = true;
+    if (v > best) { best = v; bi = i; }
+  }
+  if (bad) sbad = 1;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+  }
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  if (lane == 0) { sv[w] = best; si[w] = bi; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int k = 1; k < (int)(blockDim.x >> 5); ++k)
+      if (sv[k] > best || (sv[k] == best && si[k] < bi)) { best = sv[k]; bi = si[k]; }
+    pv[row * AM_SLICES + slice] = best;
+    pi[row * AM_SLICES + slice] = bi;
+    pbad[row * AM_SLICES + slice] = sbad;
+  }
+}
+
+__global__ void argmax_fin_kernel(int* __restrict__ ids, float* __restrict__ vals, int* __restrict__ finite,
+                                  const float* __restrict__ pv, const int* __restrict__ pi,
+                                  const int* __restrict__ pbad) {
+  pdl_launch_dependents();
+  const int row = blockIdx.x, lane = threadIdx.x;
+  float best = -INFINITY;
+  int bi = 0x7fffffff, bad = 0;
+  for (int k = lane; k < AM_SLICES; k += 32) {
+    float v = pv[row * AM_SLICES + k];
+    int ix = pi[row * AM_SLICES + k];
+    bad |= pbad[row * AM_SLICES + k];
+    if (v > best || (v == best && ix < bi)) { best = v; bi = ix; }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    bad |= __shfl_xor_sync(0xffffffffu, bad, o);
+    if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+  }
+  if (lane == 0) {
+    ids[row] = bi == 0x7fffffff ? 0 : bi;
+    if (vals) vals[row] = best;
+    if (finite) finite[row] = bad ? 0 : 1;
   }
 }
 
@@ -193,6 +264,20 @@ __global__ void chain_accept_kernel(int* __restrict__ n_accept, int* __restrict_
 }  // namespace fb
 
 using namespace fb;
+
+// scratch: rows * 64 * 3 words (slice maxima, indices, non-finite flags); when null the one-CTA kernel runs
+extern "C" int fb_argmax2(int* ids, float* vals, int* finite, const void* logits, long stride, int rows, int vocab,
+                          int is_f32, void* scratch, cudaStream_t s) {
+  if (rows <= 0) return 0;
+  float* pv = (float*)scratch;
+  int* pi = (int*)scratch + (size_t)rows * AM_SLICES;
+  int* pbad = (int*)scratch + (size_t)2 * rows * AM_SLICES;
+  dim3 grid(rows, AM_SLICES);
+  if (is_f32) argmax_part_kernel<float><<<grid, 256, 0, s>>>(pv, pi, pbad, (const float*)logits, stride, vocab);
+  else argmax_part_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(pv, pi, pbad, (const __nv_bfloat16*)logits, stride, vocab);
+  argmax_fin_kernel<<<rows, 32, 0, s>>>(ids, vals, finite, pv, pi, pbad);
+  return (int)cudaGetLastError();
+}
 
 extern "C" int fb_argmax(int* ids, float* vals, int* finite, const void* logits, long stride, int rows, int vocab,
                          int is_f32, cudaStream_t s) {

@@ -309,12 +309,13 @@ class Executor:
         return self._head(x, mv, nlog, greedy)
 
     def attn_splits(self, max_kvlen: int) -> int:
-        """Split count of the decode attention: one split per 256 keys, rounded up to a power of two, capped."""
+        """Split count of the decode attention: one split per 64 keys (16 per warp), rounded up to a power of two,
+        capped at 128. Short contexts are latency-bound, so the keys are spread over many CTAs."""
         if self.ecfg.attn_splits > 0:
             return self.ecfg.attn_splits
-        s = max(1, (max_kvlen + 255) // 256)
+        s = max(1, (max_kvlen + 63) // 64)
         s = 1 << (s - 1).bit_length()
-        return min(s, 64)
+        return min(s, 128)
 
     def forward(self, batch: StepBatch, greedy: bool = True):
         """Run one step. Returns (logits [n_logit_rows, vocab] fp32, (ids, finite) when greedy, logit_rows)."""

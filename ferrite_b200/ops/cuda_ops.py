@@ -60,9 +60,12 @@ class CudaOps:
         return out, x
 
     def _split_k(self, M, N, K):
+        # work items = weight tiles x k splits, spread persistently over the SMs: aim at >= 4 items per SM so the
+        # last wave is nearly full, but keep at least 8 k blocks (512 k) per item
         tiles = (N + 127) // 128
         kblocks = (K + 63) // 64
-        s = max(1, min(kblocks // 4, (self.sm_count + tiles - 1) // tiles))
+        want = (self.sm_count + tiles - 1) // tiles
+        s = max(1, min(kblocks // 4, want))
         return s
 
     def linear(self, x, w, norm_w=None, eps=1e-6, res=None, swiglu=False, out_f32=False):
@@ -150,6 +153,7 @@ class CudaOps:
     def argmax(self, logits):
         ids = torch.empty(logits.shape[0], dtype=torch.int32, device=self.device)
         finite = torch.empty(logits.shape[0], dtype=torch.int32, device=self.device)
-        self.launches += 1
-        self.C.argmax(ids, logits, None, finite)
+        scratch = torch.empty(logits.shape[0] * 64 * 3, dtype=torch.int32, device=self.device)
+        self.launches += 2 if logits.shape[1] >= 8192 else 1
+        self.C.argmax(ids, logits, None, finite, scratch)
         return ids, finite

@@ -31,7 +31,10 @@ def peaks():
 class Timer:
     def __init__(self, dev, warmup=3, iters=20, flush=True):
         self.dev, self.warmup, self.iters, self.flush = dev, max(3, warmup), iters, flush
+        # flush = write a buffer larger than L2, then read another one so the cache is left full of CLEAN lines
+        # (dirty lines would be written back during the timed kernel and charged to it)
         self.junk = torch.empty(256 << 20, dtype=torch.uint8, device=dev) if flush else None
+        self.junk2 = torch.zeros(64 << 20, dtype=torch.float32, device=dev) if flush else None
 
     def run(self, fn):
         for _ in range(self.warmup):
@@ -41,6 +44,7 @@ class Timer:
         for _ in range(self.iters):
             if self.flush:
                 self.junk.fill_(1)
+                self.junk2.sum()
             e0, e1 = torch.cuda.Event(True), torch.cuda.Event(True)
             torch.cuda.synchronize(self.dev)
             e0.record()
