@@ -1,4 +1,4 @@
-// C launch API, second part: quantised formats, fused compute+collective kernels, MoE, MLA, drafter ops.
+// C launch API, second part: fused compute+collective kernels, quantised formats, MoE, MLA, drafter ops.
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -6,6 +6,20 @@
 #ifdef __cplusplus
 extern "C" {
 #endif
+
+// ---- comm.cu: kernels over NVLink peer memory. `peers` = base pointer of the symmetric workspace on every rank
+// (host array, peers[rank] is the local mapping); epochs = local device array of max_ctas counters. ----
+long fb_comm_workspace_bytes(int max_ctas, long slot_floats);
+int fb_gemv_allreduce(void* Y, const void* X, const void* W, const void* res, int M, int N, int K, long ldx, long ldy,
+                      const void* const* peers, int rank, int world, int max_ctas, long slot_floats, uint32_t* epochs,
+                      int* status, unsigned spin_limit, int max_resident, cudaStream_t s);
+int fb_allreduce_oneshot(void* y, const void* part, const void* res, long count, int part_f32,
+                         const void* const* peers, int rank, int world, int max_ctas, long slot_floats,
+                         uint32_t* epochs, int* status, unsigned spin_limit, int max_resident, cudaStream_t s);
+int fb_argmax_gather(int* ids, float* vals, const float* logits, long stride, int rows, int n_local, int vocab_offset,
+                     const void* const* peers, int rank, int world, int max_ctas, long slot_floats, uint32_t* epochs,
+                     int* status, unsigned spin_limit, cudaStream_t s);
+int fb_comm_wait_probe(const uint32_t* flag, uint32_t want, unsigned limit, int* status, cudaStream_t s);
 
 #ifdef __cplusplus
 }

@@ -23,6 +23,7 @@ __global__ void attn_prep_kernel(__nv_bfloat16* __restrict__ q_out, __nv_bfloat1
                                  const int* __restrict__ block_table, int max_blocks, int kv_block, int nq, int nkv,
                                  int rot, int gated, float eps, int* status) {
   pdl_launch_dependents();
+  pdl_wait();
   constexpr int EPL = HD / 32;
   const int row = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -89,6 +90,7 @@ attn_decode_kernel(float* __restrict__ o_part, float* __restrict__ ml_part, cons
                    const int* __restrict__ block_table, int max_blocks, int kv_block, int nq, int nkv, int nsplit,
                    float scale_log2) {
   pdl_launch_dependents();
+  pdl_wait();
   constexpr int LPK = HD / 8;           // lanes per key
   constexpr int KPI = 32 / LPK;         // keys per warp iteration
   extern __shared__ float sm[];         // [ATT_WARPS][G][HD] o, then [ATT_WARPS][G][2] m,l
@@ -225,6 +227,7 @@ __global__ void attn_combine_kernel(__nv_bfloat16* __restrict__ out, const float
                                     const float* __restrict__ ml_part, const __nv_bfloat16* __restrict__ proj,
                                     long proj_stride, int nq, int nsplit, int gated) {
   pdl_launch_dependents();
+  pdl_wait();
   const int row = blockIdx.x, qh = blockIdx.y;
   const size_t pbase = ((size_t)row * nq + qh) * nsplit;
   float M = -INFINITY;
@@ -256,7 +259,7 @@ static int launch_decode(int G, dim3 grid, size_t smem, cudaStream_t s, float* o
   case GV: {                                                                                                     \
     auto kern = attn_decode_kernel<HD, GV>;                                                                      \
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);    \
-    kern<<<grid, ATT_WARPS * 32, smem, s>>>(o_part, ml_part, (const __nv_bfloat16*)q, (const __nv_bfloat16*)kc,  \
+    launch_pdl(kern, dim3(grid), dim3(ATT_WARPS * 32), (size_t)(smem), s, o_part, ml_part, (const __nv_bfloat16*)q, (const __nv_bfloat16*)kc,  \
                                             (const __nv_bfloat16*)vc, row_slot, row_kvlen, row_base, row_mask,   \
                                             bt, max_blocks, kv_block, nq, nkv, nsplit, scale_log2);              \
     break;                                                                                                       \
@@ -283,7 +286,7 @@ extern "C" int fb_attn_prep(void* q_out, void* k_cache, void* v_cache, const voi
   int epl = hd / 32;
   if (rot % 2 || (rot / 2) % epl || ((rot / 2 / epl) & (rot / 2 / epl - 1))) return -3;
 #define FB_PREP(HDV)                                                                                              \
-  attn_prep_kernel<HDV><<<rows, threads, 0, s>>>((__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache,                  \
+  launch_pdl(attn_prep_kernel<HDV>, dim3(rows), dim3(threads), (size_t)(0), s, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache,                  \
       (__nv_bfloat16*)v_cache, (const __nv_bfloat16*)proj, proj_stride, (const __nv_bfloat16*)q_norm,             \
       (const __nv_bfloat16*)k_norm, inv_freq, row_slot, row_pos, block_table, max_blocks, kv_block, nq, nkv, rot, \
       gated, eps, status)
@@ -311,8 +314,8 @@ extern "C" int fb_attn_decode(void* out, float* o_part, float* ml_part, const vo
   if (rc) return rc;
   dim3 cgrid(rows, nq);
   int cthreads = hd >= 128 ? 128 : 64;
-  if (hd == 256) attn_combine_kernel<256><<<cgrid, cthreads, 0, s>>>((__nv_bfloat16*)out, o_part, ml_part, (const __nv_bfloat16*)proj, proj_stride, nq, nsplit, gated);
-  else if (hd == 128) attn_combine_kernel<128><<<cgrid, cthreads, 0, s>>>((__nv_bfloat16*)out, o_part, ml_part, (const __nv_bfloat16*)proj, proj_stride, nq, nsplit, gated);
-  else attn_combine_kernel<64><<<cgrid, cthreads, 0, s>>>((__nv_bfloat16*)out, o_part, ml_part, (const __nv_bfloat16*)proj, proj_stride, nq, nsplit, gated);
+  if (hd == 256) launch_pdl(attn_combine_kernel<256>, dim3(cgrid), dim3(cthreads), (size_t)(0), s, (__nv_bfloat16*)out, o_part, ml_part, (const __nv_bfloat16*)proj, proj_stride, nq, nsplit, gated);
+  else if (hd == 128) launch_pdl(attn_combine_kernel<128>, dim3(cgrid), dim3(cthreads), (size_t)(0), s, (__nv_bfloat16*)out, o_part, ml_part, (const __nv_bfloat16*)proj, proj_stride, nq, nsplit, gated);
+  else launch_pdl(attn_combine_kernel<64>, dim3(cgrid), dim3(cthreads), (size_t)(0), s, (__nv_bfloat16*)out, o_part, ml_part, (const __nv_bfloat16*)proj, proj_stride, nq, nsplit, gated);
   return (int)cudaGetLastError();
 }

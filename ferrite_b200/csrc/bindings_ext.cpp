@@ -1,9 +1,80 @@
-// Python bindings, second part (quantised formats, fused collectives, MoE, MLA, drafter ops).
+// Python bindings, second part (fused collectives, quantised formats, MoE, MLA, drafter ops).
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAStream.h>
 #include <torch/extension.h>
 
+#include <vector>
+
 #include "api.h"
 #include "api_ext.h"
 
-void register_ext(pybind11::module_& m) { (void)m; }
+namespace {
+
+using torch::Tensor;
+
+inline cudaStream_t cur_stream() { return c10::cuda::getCurrentCUDAStream().stream(); }
+inline void check(int rc, const char* what) {
+  if (rc == 0) return;
+  if (rc > 0) TORCH_CHECK(false, what, ": CUDA error ", rc, " (", cudaGetErrorString((cudaError_t)rc), ")");
+  TORCH_CHECK(false, what, ": unsupported arguments (code ", rc, ")");
+}
+inline const void* cptr(const c10::optional<Tensor>& t) { return t.has_value() && t->defined() ? t->data_ptr() : nullptr; }
+
+// Handle to the symmetric communication workspace of one rank.
+struct Comm {
+  std::vector<const void*> peers;
+  int rank = 0, world = 1, max_ctas = 0, max_resident = 0;
+  long slot_floats = 0;
+  Tensor epochs, status;
+  unsigned spin_limit = 0;
+};
+
+Comm make_comm(std::vector<int64_t> peer_ptrs, int64_t rank, int64_t max_ctas, int64_t slot_floats, Tensor epochs,
+               Tensor status, int64_t spin_limit, int64_t max_resident) {
+  Comm c;
+  for (auto p : peer_ptrs) c.peers.push_back(reinterpret_cast<const void*>(p));
+  c.rank = (int)rank; c.world = (int)peer_ptrs.size(); c.max_ctas = (int)max_ctas; c.slot_floats = (long)slot_floats;
+  c.epochs = epochs; c.status = status; c.spin_limit = (unsigned)spin_limit; c.max_resident = (int)max_resident;
+  return c;
+}
+
+void gemv_allreduce(const Comm& c, Tensor Y, Tensor X, Tensor W, c10::optional<Tensor> res) {
+  check(fb_gemv_allreduce(Y.data_ptr(), X.data_ptr(), W.data_ptr(), cptr(res), (int)X.size(0), (int)W.size(0),
+                          (int)X.size(1), (long)X.stride(0), (long)Y.stride(0), c.peers.data(), c.rank, c.world,
+                          c.max_ctas, c.slot_floats, (uint32_t*)c.epochs.data_ptr(), c.status.data_ptr<int>(),
+                          c.spin_limit, c.max_resident, cur_stream()), "gemv_allreduce");
+}
+
+void allreduce_oneshot(const Comm& c, Tensor y, Tensor part, c10::optional<Tensor> res) {
+  check(fb_allreduce_oneshot(y.data_ptr(), part.data_ptr(), cptr(res), (long)part.numel(),
+                             part.scalar_type() == torch::kFloat32 ? 1 : 0, c.peers.data(), c.rank, c.world,
+                             c.max_ctas, c.slot_floats, (uint32_t*)c.epochs.data_ptr(), c.status.data_ptr<int>(),
+                             c.spin_limit, c.max_resident, cur_stream()), "allreduce_oneshot");
+}
+
+void argmax_gather(const Comm& c, Tensor ids, Tensor logits, int64_t vocab_offset, c10::optional<Tensor> vals) {
+  check(fb_argmax_gather(ids.data_ptr<int>(), vals.has_value() ? vals->data_ptr<float>() : nullptr,
+                         logits.data_ptr<float>(), (long)logits.stride(0), (int)logits.size(0), (int)logits.size(1),
+                         (int)vocab_offset, c.peers.data(), c.rank, c.world, c.max_ctas, c.slot_floats,
+                         (uint32_t*)c.epochs.data_ptr(), c.status.data_ptr<int>(), c.spin_limit, cur_stream()),
+        "argmax_gather");
+}
+
+void comm_wait_probe(Tensor flag, int64_t want, int64_t limit, Tensor status) {
+  check(fb_comm_wait_probe((const uint32_t*)flag.data_ptr(), (uint32_t)want, (unsigned)limit, status.data_ptr<int>(),
+                           cur_stream()), "comm_wait_probe");
+}
+
+}  // namespace
+
+void register_ext(pybind11::module_& m) {
+  pybind11::class_<Comm>(m, "Comm");
+  m.def("make_comm", &make_comm);
+  m.def("comm_workspace_bytes", [](int64_t max_ctas, int64_t slot_floats) {
+    return (int64_t)fb_comm_workspace_bytes((int)max_ctas, (long)slot_floats);
+  });
+  m.def("gemv_allreduce", &gemv_allreduce);
+  m.def("allreduce_oneshot", &allreduce_oneshot);
+  m.def("argmax_gather", &argmax_gather);
+  m.def("comm_wait_probe", &comm_wait_probe);
+}

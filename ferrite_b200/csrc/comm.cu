@@ -243,11 +243,9 @@ static int launch_gemv_ar(GemvArgs a, CommBuf cb, int max_resident, cudaStream_t
   const int group = GEMV_WARPS * R;
   int nchunks = (a.K + a.kc - 1) / a.kc;
   int rpc;
-  if (nchunks > 1) rpc = group;
-  else {
-    rpc = (a.N + max_resident - 1) / max_resident;
-    rpc = (rpc + group - 1) / group * group;
-  }
+  (void)nchunks;
+  rpc = (a.N + max_resident - 1) / max_resident;
+  rpc = (rpc + group - 1) / group * group;
   a.rows_per_cta = rpc;
   int grid = (a.N + rpc - 1) / rpc;
   // every CTA waits on its peers: all of them must be resident at once
@@ -261,8 +259,13 @@ static int launch_gemv_ar(GemvArgs a, CommBuf cb, int max_resident, cudaStream_t
     if (e != cudaSuccess) return (int)e;
     attr_done = true;
   }
-  kern<<<grid, GEMV_THREADS, smem, s>>>(a, cb);
-  return (int)cudaGetLastError();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid); cfg.blockDim = dim3(GEMV_THREADS); cfg.dynamicSmemBytes = smem; cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr; cfg.numAttrs = 1;
+  return (int)cudaLaunchKernelEx(&cfg, kern, a, cb);
 }
 
 }  // namespace fb

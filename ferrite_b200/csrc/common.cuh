@@ -367,6 +367,21 @@ __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepc
 
 }  // namespace fb
 
+// Host helper: launch with programmatic stream serialization, so the grid may be scheduled while its
+// predecessor drains. Every kernel launched this way executes griddepcontrol.wait before it touches anything
+// the predecessor wrote.
+template <typename... KArgs, typename... Args>
+static inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s,
+                                     Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr; cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
 #define FB_CUDA_CHECK(expr)                                                                      \
   do {                                                                                           \
     cudaError_t _e = (expr);                                                                     \

@@ -10,6 +10,7 @@ namespace fb {
 __global__ void embed_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ table,
                              const int* __restrict__ ids, int hidden, int vocab) {
   pdl_launch_dependents();
+  pdl_wait();
   int row = blockIdx.x;
   int id = ids[row];
   if (id < 0 || id >= vocab) id = 0;
@@ -24,6 +25,7 @@ __global__ void rmsnorm_kernel(__nv_bfloat16* __restrict__ out, __nv_bfloat16* _
                                const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
                                const __nv_bfloat16* __restrict__ w, int hidden, float eps, int centred) {
   pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ float xs[];          // hidden floats
   __shared__ float scratch[32];
   int row = blockIdx.x;
@@ -99,6 +101,7 @@ __global__ void gated_norm_kernel(__nv_bfloat16* __restrict__ out, const float* 
                                   const __nv_bfloat16* __restrict__ z, long z_stride,
                                   const __nv_bfloat16* __restrict__ w, int heads, int dv, float eps) {
   pdl_launch_dependents();
+  pdl_wait();
   int row = blockIdx.x;
   int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   int nw = blockDim.x >> 5;
@@ -146,7 +149,7 @@ using namespace fb;
 extern "C" int fb_embed(void* out, const void* table, const int* ids, int rows, int hidden, int vocab, cudaStream_t s) {
   if (rows <= 0) return 0;
   if (hidden % 8) return -1;
-  embed_kernel<<<rows, 256, 0, s>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)table, ids, hidden, vocab);
+  launch_pdl(embed_kernel, dim3(rows), dim3(256), (size_t)(0), s, (__nv_bfloat16*)out, (const __nv_bfloat16*)table, ids, hidden, vocab);
   return (int)cudaGetLastError();
 }
 
@@ -157,7 +160,7 @@ extern "C" int fb_rmsnorm(void* out, void* x_out, const void* x, const void* res
   size_t smem = (size_t)hidden * sizeof(float);
   if (smem > 48 * 1024) cudaFuncSetAttribute(rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   int threads = hidden >= 4096 ? 512 : 256;
-  rmsnorm_kernel<<<rows, threads, smem, s>>>((__nv_bfloat16*)out, (__nv_bfloat16*)x_out, (const __nv_bfloat16*)x,
+  launch_pdl(rmsnorm_kernel, dim3(rows), dim3(threads), (size_t)(smem), s, (__nv_bfloat16*)out, (__nv_bfloat16*)x_out, (const __nv_bfloat16*)x,
                                              (const __nv_bfloat16*)res, (const __nv_bfloat16*)w, hidden, eps, centred);
   return (int)cudaGetLastError();
 }
@@ -174,7 +177,7 @@ extern "C" int fb_gated_norm(void* out, const float* y, const void* z, long z_st
                              int heads, int dv, float eps, cudaStream_t s) {
   if (rows <= 0) return 0;
   int threads = heads >= 8 ? 256 : 32 * heads;
-  gated_norm_kernel<<<rows, threads, 0, s>>>((__nv_bfloat16*)out, y, (const __nv_bfloat16*)z, z_stride,
+  launch_pdl(gated_norm_kernel, dim3(rows), dim3(threads), (size_t)(0), s, (__nv_bfloat16*)out, y, (const __nv_bfloat16*)z, z_stride,
                                              (const __nv_bfloat16*)w, heads, dv, eps);
   return (int)cudaGetLastError();
 }

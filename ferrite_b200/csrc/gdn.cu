@@ -20,6 +20,7 @@ __global__ void gdn_conv_kernel(__nv_bfloat16* __restrict__ out, const __nv_bflo
                                 const __nv_bfloat16* __restrict__ conv_state, const int* __restrict__ seg_slot,
                                 const int* __restrict__ seg_row0, const int* __restrict__ seg_nrows, int conv_dim) {
   pdl_launch_dependents();
+  pdl_wait();
   constexpr int CK = 4, CHUNK = 32;
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   const int seg = blockIdx.z;
@@ -57,6 +58,7 @@ gdn_rec_kernel(float* __restrict__ y, float* __restrict__ rec_state, __nv_bfloat
                const int* __restrict__ seg_row0, const int* __restrict__ seg_nrows, int nk, int nv, float eps,
                int commit) {
   pdl_launch_dependents();
+  pdl_wait();
   constexpr int PARTS = 8, RP = DK / PARTS, CK = 4;
   __shared__ float qs[DK], ks[DK], vs[DV];
   __shared__ float red1[PARTS][DV], red2[PARTS][DV];
@@ -150,7 +152,7 @@ extern "C" int fb_gdn_conv(void* out, const void* proj, long proj_stride, const 
                            int conv_dim, cudaStream_t s) {
   if (nseg <= 0 || max_rows <= 0) return 0;
   dim3 grid((conv_dim + 255) / 256, (max_rows + 31) / 32, nseg);
-  gdn_conv_kernel<<<grid, 256, 0, s>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)proj, proj_stride,
+  launch_pdl(gdn_conv_kernel, dim3(grid), dim3(256), (size_t)(0), s, (__nv_bfloat16*)out, (const __nv_bfloat16*)proj, proj_stride,
                                        (const __nv_bfloat16*)conv_w, (const __nv_bfloat16*)conv_state, seg_slot,
                                        seg_row0, seg_nrows, conv_dim);
   return (int)cudaGetLastError();
@@ -164,10 +166,10 @@ extern "C" int fb_gdn_rec(float* y, float* rec_state, void* conv_state, const vo
   if (nv % nk) return -1;
   dim3 grid(nv, nseg);
   if (dk == 128 && dv == 128)
-    gdn_rec_kernel<128, 128><<<grid, 1024, 0, s>>>(y, rec_state, (__nv_bfloat16*)conv_state, (const __nv_bfloat16*)qkv,
+    launch_pdl(gdn_rec_kernel<128, 128>, dim3(grid), dim3(1024), (size_t)(0), s, y, rec_state, (__nv_bfloat16*)conv_state, (const __nv_bfloat16*)qkv,
         (const __nv_bfloat16*)proj, proj_stride, A_log, dt_bias, seg_slot, seg_row0, seg_nrows, nk, nv, eps, commit);
   else if (dk == 64 && dv == 64)
-    gdn_rec_kernel<64, 64><<<grid, 512, 0, s>>>(y, rec_state, (__nv_bfloat16*)conv_state, (const __nv_bfloat16*)qkv,
+    launch_pdl(gdn_rec_kernel<64, 64>, dim3(grid), dim3(512), (size_t)(0), s, y, rec_state, (__nv_bfloat16*)conv_state, (const __nv_bfloat16*)qkv,
         (const __nv_bfloat16*)proj, proj_stride, A_log, dt_bias, seg_slot, seg_row0, seg_nrows, nk, nv, eps, commit);
   else return -2;
   return (int)cudaGetLastError();

@@ -186,28 +186,37 @@ __device__ __forceinline__ void gemv_main(const GemvArgs& a, __nv_bfloat16* xs, 
       store(acc, n);
     }
   } else {
-    // K does not fit one staged chunk: one row group per warp, chunks in the outer loop
-    const bool active = n < row_end;
-    float acc[R][M] = {};
-    for (int c = 0; c < nchunks; ++c) {
-      const int k0 = c * a.kc;
-      __syncthreads();
-      gemv_stage_x<M>(a, xs, rscale, k0, a.kc);
-      __syncthreads();
-      if (active) {
-        for (int base = 0; base < a.kc; base += BATCH) {
-          gemv_consume_batch<M, R>(acc, wv, xs, a.kc, base);
-          const int knext = k0 + base + BATCH;
-          if (knext < a.K) gemv_load_batch<R>(wv, wrow, knext, a.K);
+    // K does not fit one staged chunk: per pass one row group per warp, the chunks re-staged inside the pass
+    // (the loop bounds are uniform over the CTA because of the barriers)
+    const int passes = (row_end - row0 + GEMV_WARPS * RW - 1) / (GEMV_WARPS * RW);
+    for (int pass = 0; pass < passes; ++pass, n += GEMV_WARPS * RW) {
+      const bool active = n < row_end;
+      float acc[R][M] = {};
+      for (int c = 0; c < nchunks; ++c) {
+        const int k0 = c * a.kc;
+        __syncthreads();
+        gemv_stage_x<M>(a, xs, rscale, k0, a.kc);
+        __syncthreads();
+        if (active) {
+          for (int base = 0; base < a.kc; base += BATCH) {
+            gemv_consume_batch<M, R>(acc, wv, xs, a.kc, base);
+            const int knext = k0 + base + BATCH;
+            if (knext < a.K) {
+              gemv_load_batch<R>(wv, wrow, knext, a.K);
+            } else if (c == nchunks - 1 && base + BATCH >= a.kc && n + GEMV_WARPS * RW < row_end) {
+              gemv_row_ptrs<R, SWIGLU>(a, wrow, n + GEMV_WARPS * RW);
+              gemv_load_batch<R>(wv, wrow, 0, a.K);
+            }
+          }
         }
       }
-    }
-    if (active) {
+      if (active) {
 #pragma unroll
-      for (int r = 0; r < R; ++r)
+        for (int r = 0; r < R; ++r)
 #pragma unroll
-        for (int m = 0; m < M; ++m) acc[r][m] = warp_sum(acc[r][m]);
-      store(acc, n);
+          for (int m = 0; m < M; ++m) acc[r][m] = warp_sum(acc[r][m]);
+        store(acc, n);
+      }
     }
   }
 }

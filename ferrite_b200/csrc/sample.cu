@@ -16,6 +16,7 @@ template <typename T>
 __global__ void argmax_kernel(int* __restrict__ ids, float* __restrict__ vals, int* __restrict__ finite,
                               const T* __restrict__ logits, long stride, int vocab) {
   pdl_launch_dependents();
+  pdl_wait();
   __shared__ float sv[32];
   __shared__ int si[32];
   __shared__ int sbad;
@@ -66,6 +67,7 @@ template <typename T>
 __global__ void argmax_part_kernel(float* __restrict__ pv, int* __restrict__ pi, int* __restrict__ pbad,
                                    const T* __restrict__ logits, long stride, int vocab) {
   pdl_launch_dependents();
+  pdl_wait();
   __shared__ float sv[8];
   __shared__ int si[8];
   __shared__ int sbad;
@@ -106,6 +108,7 @@ __global__ void argmax_fin_kernel(int* __restrict__ ids, float* __restrict__ val
                                   const float* __restrict__ pv, const int* __restrict__ pi,
                                   const int* __restrict__ pbad) {
   pdl_launch_dependents();
+  pdl_wait();
   const int row = blockIdx.x, lane = threadIdx.x;
   float best = -INFINITY;
   int bi = 0x7fffffff, bad = 0;
@@ -273,17 +276,17 @@ extern "C" int fb_argmax2(int* ids, float* vals, int* finite, const void* logits
   int* pi = (int*)scratch + (size_t)rows * AM_SLICES;
   int* pbad = (int*)scratch + (size_t)2 * rows * AM_SLICES;
   dim3 grid(rows, AM_SLICES);
-  if (is_f32) argmax_part_kernel<float><<<grid, 256, 0, s>>>(pv, pi, pbad, (const float*)logits, stride, vocab);
-  else argmax_part_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(pv, pi, pbad, (const __nv_bfloat16*)logits, stride, vocab);
-  argmax_fin_kernel<<<rows, 32, 0, s>>>(ids, vals, finite, pv, pi, pbad);
+  if (is_f32) launch_pdl(argmax_part_kernel<float>, dim3(grid), dim3(256), (size_t)(0), s, pv, pi, pbad, (const float*)logits, stride, vocab);
+  else launch_pdl(argmax_part_kernel<__nv_bfloat16>, dim3(grid), dim3(256), (size_t)(0), s, pv, pi, pbad, (const __nv_bfloat16*)logits, stride, vocab);
+  launch_pdl(argmax_fin_kernel, dim3(rows), dim3(32), (size_t)(0), s, ids, vals, finite, pv, pi, pbad);
   return (int)cudaGetLastError();
 }
 
 extern "C" int fb_argmax(int* ids, float* vals, int* finite, const void* logits, long stride, int rows, int vocab,
                          int is_f32, cudaStream_t s) {
   if (rows <= 0) return 0;
-  if (is_f32) argmax_kernel<float><<<rows, 1024, 0, s>>>(ids, vals, finite, (const float*)logits, stride, vocab);
-  else argmax_kernel<__nv_bfloat16><<<rows, 1024, 0, s>>>(ids, vals, finite, (const __nv_bfloat16*)logits, stride, vocab);
+  if (is_f32) launch_pdl(argmax_kernel<float>, dim3(rows), dim3(1024), (size_t)(0), s, ids, vals, finite, (const float*)logits, stride, vocab);
+  else launch_pdl(argmax_kernel<__nv_bfloat16>, dim3(rows), dim3(1024), (size_t)(0), s, ids, vals, finite, (const __nv_bfloat16*)logits, stride, vocab);
   return (int)cudaGetLastError();
 }
 

@@ -294,9 +294,14 @@ class Executor:
             return None, None
         rows = x[mv["lrow"].long()] if nlog != x.shape[0] else x
         head = w["embed"] if c.tie_embeddings else w["lm_head"]
-        logits = ops.linear(rows, head, norm_w=w["final_norm"], eps=c.eps, out_f32=True)
         if self.tp is not None and self.tp.world > 1:
-            return self.tp.gather_logits(ops, logits, greedy)
+            per = (c.vocab + self.tp.world - 1) // self.tp.world
+            off = self.tp.rank * per
+            if c.tie_embeddings:
+                head = head[off:min(c.vocab, off + per)]          # tied head: each rank takes its vocabulary rows
+            logits = ops.linear(rows, head, norm_w=w["final_norm"], eps=c.eps, out_f32=True)
+            return self.tp.gather_logits(ops, logits, greedy, off, c.vocab)
+        logits = ops.linear(rows, head, norm_w=w["final_norm"], eps=c.eps, out_f32=True)
         if greedy:
             ids, finite = ops.argmax(logits)
             return logits, (ids, finite)

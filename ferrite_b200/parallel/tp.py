@@ -1,0 +1,126 @@
+"""Tensor parallelism inside one NVSwitch box: one process per GPU, `torch.distributed` for the plumbing, and
+hand-written kernels that reduce over NVLink peer memory for the hot paths.
+
+The reference runs TP=2 over RoCE between two boxes: a TCP bootstrap, NCCL for prompt-sized reductions and a
+custom one-shot exchange for decode-sized ones (`crates/fe-fabric/src/lib.rs:62-203`, `crates/fe-model/src/tp.rs`,
+reduction site `crates/fe-model/src/model.rs:1761-1797`). Here:
+
+* bootstrap / control = the process group the caller built (NCCL on GPUs, gloo on CPU ranks);
+* the symmetric workspace (flags + staging slots, mapped on every rank) comes from
+  `torch.distributed._symmetric_memory`; kernels get the table of peer base pointers;
+* decode-sized reductions (<= 8 rows) are fused into the producing GEMV (`fb_gemv_allreduce`), up to
+  `ONESHOT_MAX` elements go through the one-shot P2P all-reduce kernel, larger ones through NCCL (the baseline);
+* ranks sum in rank order, so every rank holds identical bits (the reference's rule, `TP2.md:58-71`).
+
+`fused=False` (or a CPU device) keeps every collective on the process group: that is the baseline path and the
+one the CPU multi-rank tests run.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+MAX_CTAS = 1024
+SLOT_FLOATS = 512 * 1024
+ONESHOT_MAX = SLOT_FLOATS
+
+
+class TensorParallel:
+    def __init__(self, group, device, fused: bool = True, spin_limit: int = 0):
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.device = torch.device(device)
+        self.fused = bool(fused) and self.device.type == "cuda" and self.world > 1
+        self.comm = None
+        self.stats = {"fused_gemv": 0, "oneshot": 0, "nccl": 0}
+        if self.fused:
+            self._setup_symmetric(spin_limit)
+
+    # ---- symmetric workspace ---------------------------------------------------------------------------
+    def _setup_symmetric(self, spin_limit: int) -> None:
+        import torch.distributed._symmetric_memory as symm_mem
+
+        from .._ext import load
+        C = load()
+        nbytes = int(C.comm_workspace_bytes(MAX_CTAS, SLOT_FLOATS))
+        name = self.group.group_name
+        try:
+            symm_mem.enable_symm_mem_for_group(name)
+        except Exception:
+            pass
+        self.ws = symm_mem.empty(nbytes, dtype=torch.uint8, device=self.device)
+        self.hdl = symm_mem.rendezvous(self.ws, group=name)
+        self.ws.zero_()
+        torch.cuda.synchronize(self.device)
+        dist.barrier(self.group)                       # nobody pushes before every rank has zeroed its flags
+        self.epochs = torch.zeros(MAX_CTAS, dtype=torch.int32, device=self.device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        sm = torch.cuda.get_device_properties(self.device).multi_processor_count
+        self.max_resident = 2 * sm                     # every CTA of a fused kernel must be resident at once
+        ptrs = [int(p) for p in self.hdl.buffer_ptrs]
+        self.comm = C.make_comm(ptrs, self.rank, MAX_CTAS, SLOT_FLOATS, self.epochs, self.status, spin_limit,
+                                self.max_resident)
+        self.C = C
+
+    def check(self) -> None:
+        """Raise when a peer wait ran out (the kernel returned normally and left a status code)."""
+        if self.fused and int(self.status.item()) != 0:
+            raise RuntimeError(f"tensor-parallel rank {self.rank}: peer wait timed out (status {int(self.status.item())})")
+
+    # ---- row-parallel projection + all-reduce + residual --------------------------------------------------
+    def linear_allreduce(self, ops, x, w, res):
+        M, N = x.shape[0], w.shape[0]
+        if self.fused and M <= 8:
+            y = torch.empty(M, N, dtype=x.dtype, device=x.device)
+            self.C.gemv_allreduce(self.comm, y, x, w, res)
+            ops.launches += 1
+            self.stats["fused_gemv"] += 1
+            return y
+        part = ops.linear(x, w)
+        if self.fused and M * N <= ONESHOT_MAX:
+            y = torch.empty_like(part)
+            self.C.allreduce_oneshot(self.comm, y, part, res)
+            ops.launches += 1
+            self.stats["oneshot"] += 1
+            return y
+        self.stats["nccl"] += 1
+        if part.device.type == "cpu":
+            part = part.float()
+        dist.all_reduce(part, group=self.group)
+        if res is not None:
+            part = (part.float() + res.float()).to(res.dtype) if part.device.type == "cpu" else part.add_(res)
+        return part.to(x.dtype)
+
+    # ---- vocabulary-parallel head -----------------------------------------------------------------------------
+    def gather_logits(self, ops, logits, greedy: bool, vocab_offset: int, vocab: int):
+        """logits: this rank's shard [rows, n_local] fp32. greedy: (None, (ids, finite)) with ids merged over ranks
+        (only (max, index) pairs cross the link). Otherwise the full [rows, vocab] logits on every rank."""
+        rows, n_local = logits.shape
+        if greedy and self.fused and rows <= MAX_CTAS:
+            ids = torch.empty(rows, dtype=torch.int32, device=logits.device)
+            vals = torch.empty(rows, dtype=torch.float32, device=logits.device)
+            self.C.argmax_gather(self.comm, ids, logits, vocab_offset, vals)
+            ops.launches += 1
+            finite = torch.isfinite(vals).to(torch.int32)
+            return None, (ids, finite)
+        per = (vocab + self.world - 1) // self.world
+        pad = torch.full((rows, per), float("-inf"), dtype=torch.float32, device=logits.device)
+        pad[:, :n_local] = logits
+        full = torch.empty(self.world, rows, per, dtype=torch.float32, device=logits.device)
+        dist.all_gather_into_tensor(full, pad, group=self.group) if logits.device.type == "cuda" else \
+            dist.all_gather(list(full.unbind(0)), pad, group=self.group)
+        full = full.permute(1, 0, 2).reshape(rows, self.world * per)[:, :vocab].contiguous()
+        if greedy:
+            ids, finite = ops.argmax(full)
+            return full, (ids, finite)
+        return full, None
+
+    def broadcast_object(self, obj, src: int = 0):
+        """Control plane: rank 0's step descriptor to every rank (reference: the follower RPC stream,
+        `crates/fe-model/src/follow.rs`)."""
+        box = [obj]
+        dist.broadcast_object_list(box, src=src, group=self.group)
+        return box[0]

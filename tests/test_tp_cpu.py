@@ -1,0 +1,94 @@
+"""Tensor-parallel plumbing on CPU ranks (gloo): sharded weights + process-group reductions reproduce the
+single-rank logits; a rank that never joins is detected by a short process-group timeout, not by a hang."""
+import datetime
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from ferrite_b200.config import EngineConfig, tiny_hybrid
+from ferrite_b200.engine.engine import Engine
+from ferrite_b200.engine.executor import Segment
+from ferrite_b200.models.weights import init_weights
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, prompt, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=60))
+    from ferrite_b200.parallel.tp import TensorParallel
+    tp = TensorParallel(dist.group.WORLD, "cpu", fused=False)
+    cfg = tiny_hybrid()
+    w = init_weights(cfg, seed=0)
+    eng = Engine(cfg, w, EngineConfig(n_slots=1, max_ctx=128), device="cpu", tp=tp)
+    logits, picks, _ = eng.forward([Segment(0, 0, prompt, "all")])
+    l2, p2, _ = eng.forward([Segment(0, len(prompt), [int(picks[0][-1])], "last")])
+    q.put((rank, logits, picks[0], l2))
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2])
+def test_tp_matches_single_rank(world):
+    cfg = tiny_hybrid()
+    w = init_weights(cfg, seed=0)
+    prompt = torch.randint(0, cfg.vocab, (24,), generator=torch.Generator().manual_seed(5)).tolist()
+    eng = Engine(cfg, w, EngineConfig(n_slots=1, max_ctx=128), device="cpu")
+    want, wp, _ = eng.forward([Segment(0, 0, prompt, "all")])
+    want2, _, _ = eng.forward([Segment(0, len(prompt), [int(wp[0][-1])], "last")])
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, prompt, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    outs = sorted([q.get(timeout=120) for _ in range(world)], key=lambda t: t[0])
+    for p in procs:
+        p.join(timeout=60)
+    for rank, logits, ids, l2 in outs:
+        assert torch.allclose(logits, want, atol=3e-5, rtol=1e-4), rank
+        assert ids.tolist() == wp[0].tolist()
+        assert torch.allclose(l2, want2, atol=3e-5, rtol=1e-4)
+    # every rank holds identical bits
+    assert torch.equal(outs[0][1], outs[1][1])
+
+
+def _lonely(rank, world, port, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=3))
+    if rank == 1:
+        q.put((rank, "left"))            # leaves between steps, nothing in flight
+        return
+    try:
+        t = torch.ones(4)
+        dist.all_reduce(t)
+        q.put((rank, "no error"))
+    except Exception as e:                # the survivor's collective ends with an error instead of hanging
+        q.put((rank, "error:" + type(e).__name__))
+
+
+def test_missing_rank_is_an_error_not_a_hang():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_lonely, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = dict(q.get(timeout=60) for _ in range(2))
+    for p in procs:
+        p.join(timeout=30)
+        if p.is_alive():
+            p.terminate()
+    assert got[1] == "left"
+    assert got[0].startswith("error")
