@@ -21,6 +21,15 @@ int fb_argmax_gather(int* ids, float* vals, const float* logits, long stride, in
                      int* status, unsigned spin_limit, cudaStream_t s);
 int fb_comm_wait_probe(const uint32_t* flag, uint32_t want, unsigned limit, int* status, cudaStream_t s);
 
+// ---- gemv_nvfp4.cu: NVFP4-weight GEMV (W4A16), plain and with the fused one-shot all-reduce ----
+int fb_gemv_nvfp4(void* Y, const void* X, const void* Wq, const void* Sc, float global_scale, const void* norm_w,
+                  const void* res, int M, int N, int K, long ldx, long ldy, long sc_stride, float eps, int out_f32,
+                  int mode, int sm_count, cudaStream_t s);
+int fb_gemv_nvfp4_allreduce(void* Y, const void* X, const void* Wq, const void* Sc, float global_scale,
+                            const void* res, int M, int N, int K, long ldx, long ldy, long sc_stride,
+                            const void* const* peers, int rank, int world, int max_ctas, long slot_floats,
+                            uint32_t* epochs, int* status, unsigned spin_limit, int max_resident, cudaStream_t s);
+
 #ifdef __cplusplus
 }
 #endif

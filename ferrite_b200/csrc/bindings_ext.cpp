@@ -65,6 +65,28 @@ void comm_wait_probe(Tensor flag, int64_t want, int64_t limit, Tensor status) {
                            cur_stream()), "comm_wait_probe");
 }
 
+void gemv_nvfp4(Tensor Y, Tensor X, Tensor packed, Tensor scales, double global_scale, c10::optional<Tensor> norm_w,
+                c10::optional<Tensor> res, double eps, int64_t mode) {
+  int M = (int)X.size(0), K = (int)X.size(1);
+  int N = (int)(mode == 1 ? packed.size(0) / 2 : packed.size(0));
+  TORCH_CHECK(packed.size(1) * 2 == K, "gemv_nvfp4: K mismatch");
+  check(fb_gemv_nvfp4(Y.data_ptr(), X.data_ptr(), packed.data_ptr(), scales.data_ptr(), (float)global_scale,
+                      cptr(norm_w), cptr(res), M, N, K, (long)X.stride(0), (long)Y.stride(0), (long)scales.stride(0),
+                      (float)eps, Y.scalar_type() == torch::kFloat32 ? 1 : 0, (int)mode,
+                      at::cuda::getCurrentDeviceProperties()->multiProcessorCount, cur_stream()), "gemv_nvfp4");
+}
+
+void gemv_nvfp4_allreduce(const Comm& c, Tensor Y, Tensor X, Tensor packed, Tensor scales, double global_scale,
+                          c10::optional<Tensor> res) {
+  int M = (int)X.size(0), K = (int)X.size(1), N = (int)packed.size(0);
+  TORCH_CHECK(packed.size(1) * 2 == K, "gemv_nvfp4_allreduce: K mismatch");
+  check(fb_gemv_nvfp4_allreduce(Y.data_ptr(), X.data_ptr(), packed.data_ptr(), scales.data_ptr(), (float)global_scale,
+                                cptr(res), M, N, K, (long)X.stride(0), (long)Y.stride(0), (long)scales.stride(0),
+                                c.peers.data(), c.rank, c.world, c.max_ctas, c.slot_floats,
+                                (uint32_t*)c.epochs.data_ptr(), c.status.data_ptr<int>(), c.spin_limit, c.max_resident,
+                                cur_stream()), "gemv_nvfp4_allreduce");
+}
+
 }  // namespace
 
 void register_ext(pybind11::module_& m) {
@@ -77,4 +99,6 @@ void register_ext(pybind11::module_& m) {
   m.def("allreduce_oneshot", &allreduce_oneshot);
   m.def("argmax_gather", &argmax_gather);
   m.def("comm_wait_probe", &comm_wait_probe);
+  m.def("gemv_nvfp4", &gemv_nvfp4);
+  m.def("gemv_nvfp4_allreduce", &gemv_nvfp4_allreduce);
 }

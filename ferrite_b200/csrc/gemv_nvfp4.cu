@@ -1,0 +1,371 @@
+// NVFP4-weight GEMV for 1..8 activation rows (W4A16): e2m1 codes are converted to f16x2 with the sm_100a
+// cvt instruction, multiplied against f16 activations with HFMA2 inside each 16-value block, and the block
+// sums are scaled (e4m3 block scale) into fp32 accumulators. 0.5625 bytes per weight cross HBM instead of 2.
+//
+// The decode-side role of the reference's low-bit GEMVs (`exl3_gemv*`, `kernels/k-exl3/src/gemv.rs:227`; NVFP4
+// itself serves only its prompt path, `kernels/k-fp4/src/lib.rs`). Same structure as the bf16 GEMV: the next
+// weight batch is always in flight, the first one requested before griddepcontrol.wait, RMSNorm prologue,
+// residual / SwiGLU epilogue, and an optional one-shot all-reduce over NVLink peers fused into the epilogue for
+// row-parallel projections under tensor parallelism.
+//
+// Layouts: codes [rows][K/2] bytes, element 2i in the low nibble; scales tiled per row as
+// [group of 4 spans][lane 32][span 4][2 blocks] (see formats/nvfp4.py `tile_scales_gemv`).
+#include <cuda_fp4.h>
+#include <cuda_fp8.h>
+
+#include "api_ext.h"
+#include "comm_core.cuh"
+
+namespace fb {
+
+constexpr int G4_THREADS = 256;
+constexpr int G4_WARPS = 8;
+constexpr int G4_R = 2;                       // weight rows per warp
+constexpr int G4_SPAN = 1024;                 // weights per warp load (32 lanes x 32 codes)
+constexpr int G4_GROUP = 4;                   // spans per batch
+constexpr int G4_BATCH = G4_SPAN * G4_GROUP;  // 4096 weights
+constexpr int G4_SMEM = 96 * 1024;
+
+struct Gemv4Args {
+  const __nv_bfloat16* X;       // [M][ldx]
+  const uint8_t* Wq;            // [rows][K/2]
+  const uint8_t* Sc;            // [rows][sc_stride] tiled scales
+  const __nv_bfloat16* norm_w;
+  const __nv_bfloat16* res;
+  void* Y;
+  float global_scale;
+  int M, N, K;
+  long ldx, ldy;
+  long sc_stride;
+  float eps;
+  int out_f32;
+  int rows_per_cta;
+  int kc;
+};
+
+struct Batch4 {
+  uint4 w[G4_R][G4_GROUP];
+  uint2 s[G4_R];
+};
+
+__host__ __device__ inline int gemv4_chunk_len(int M, int K) {
+  int kpad = (K + G4_BATCH - 1) / G4_BATCH * G4_BATCH;
+  int cap = (G4_SMEM / 2 / M) / G4_BATCH * G4_BATCH;
+  if (cap < G4_BATCH) cap = G4_BATCH;
+  return kpad < cap ? kpad : cap;
+}
+
+template <bool SWIGLU>
+__device__ __forceinline__ void g4_rows(const Gemv4Args& a, int (&rows)[G4_R], int n) {
+#pragma unroll
+  for (int r = 0; r < G4_R; ++r) rows[r] = SWIGLU ? (min(n, a.N - 1) + r * a.N) : min(n + r, a.N - 1);
+}
+
+// loads of the batch that starts at absolute k = kb (a multiple of 4096)
+__device__ __forceinline__ void g4_load(Batch4& b, const Gemv4Args& a, const int (&rows)[G4_R], int kb) {
+  const int lane = threadIdx.x & 31;
+#pragma unroll
+  for (int r = 0; r < G4_R; ++r) {
+    const uint8_t* wrow = a.Wq + (size_t)rows[r] * (a.K / 2);
+#pragma unroll
+    for (int u = 0; u < G4_GROUP; ++u) {
+      int k = kb + u * G4_SPAN + lane * 32;
+      b.w[r][u] = (k < a.K) ? ldg_stream(wrow + k / 2) : make_uint4(0, 0, 0, 0);
+    }
+    b.s[r] = ldg_stream8(a.Sc + (size_t)rows[r] * a.sc_stride + (size_t)(kb / G4_BATCH) * 256 + lane * 8);
+  }
+}
+
+__device__ __forceinline__ __half2 e2m1x2_to_half2(uint32_t byte) {
+  __half2_raw h = __nv_cvt_fp4x2_to_halfraw2((__nv_fp4x2_storage_t)(byte & 0xffu), __NV_E2M1);
+  return *reinterpret_cast<__half2*>(&h);
+}
+__device__ __forceinline__ float e4m3_to_float(uint32_t byte) {
+  __half_raw h = __nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)(byte & 0xffu), __NV_E4M3);
+  return __half2float(*reinterpret_cast<__half*>(&h));
+}
+
+template <int M>
+__device__ __forceinline__ void g4_consume(float (&acc)[G4_R][M], const Batch4& b, const __half* xs, int kc, int koff) {
+  const int lane = threadIdx.x & 31;
+#pragma unroll
+  for (int u = 0; u < G4_GROUP; ++u) {
+    const int k = koff + u * G4_SPAN + lane * 32;
+    if (k >= kc) continue;
+    __half2 wh[G4_R][16];
+    float sc[G4_R][2];
+#pragma unroll
+    for (int r = 0; r < G4_R; ++r) {
+      const uint32_t words[4] = {b.w[r][u].x, b.w[r][u].y, b.w[r][u].z, b.w[r][u].w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int t = 0; t < 4; ++t) wh[r][j * 4 + t] = e2m1x2_to_half2(words[j] >> (8 * t));
+      const uint32_t sw = (u < 2) ? b.s[r].x : b.s[r].y;
+      sc[r][0] = e4m3_to_float(sw >> ((u & 1) * 16));
+      sc[r][1] = e4m3_to_float(sw >> ((u & 1) * 16 + 8));
+    }
+#pragma unroll
+    for (int m = 0; m < M; ++m) {
+      const uint4* xp = reinterpret_cast<const uint4*>(xs + (size_t)m * kc + k);
+      __half2 xh[16];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint4 v = xp[j];
+        xh[j * 4 + 0] = *reinterpret_cast<__half2*>(&v.x); xh[j * 4 + 1] = *reinterpret_cast<__half2*>(&v.y);
+        xh[j * 4 + 2] = *reinterpret_cast<__half2*>(&v.z); xh[j * 4 + 3] = *reinterpret_cast<__half2*>(&v.w);
+      }
+#pragma unroll
+      for (int r = 0; r < G4_R; ++r) {
+#pragma unroll
+        for (int blk = 0; blk < 2; ++blk) {
+          __half2 s0 = __float2half2_rn(0.f), s1 = __float2half2_rn(0.f);
+#pragma unroll
+          for (int j = 0; j < 8; j += 2) {
+            s0 = __hfma2(wh[r][blk * 8 + j], xh[blk * 8 + j], s0);
+            s1 = __hfma2(wh[r][blk * 8 + j + 1], xh[blk * 8 + j + 1], s1);
+          }
+          float2 f0 = __half22float2(s0), f1 = __half22float2(s1);
+          acc[r][m] = fmaf((f0.x + f0.y) + (f1.x + f1.y), sc[r][blk], acc[r][m]);
+        }
+      }
+    }
+  }
+}
+
+// Stage X[:, k0:k0+kc) as f16 (normalised when asked); positions past K are zero.
+template <int M>
+__device__ __forceinline__ void g4_stage(const Gemv4Args& a, __half* xs, const float* rscale, int k0, int kc) {
+  for (int idx = threadIdx.x; idx < M * (kc / 8); idx += blockDim.x) {
+    int m = idx / (kc / 8), c = idx % (kc / 8);
+    int k = k0 + c * 8;
+    __half2 o[4] = {__float2half2_rn(0.f), __float2half2_rn(0.f), __float2half2_rn(0.f), __float2half2_rn(0.f)};
+    if (m < a.M && k < a.K) {
+      uint4 v = *reinterpret_cast<const uint4*>(a.X + (size_t)m * a.ldx + k);
+      uint32_t xu[4] = {v.x, v.y, v.z, v.w};
+      if (a.norm_w) {
+        uint4 wv = __ldg(reinterpret_cast<const uint4*>(a.norm_w + k));
+        uint32_t wu[4] = {wv.x, wv.y, wv.z, wv.w};
+        float r = rscale[m];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          // round through bf16 first so this path sees the same normalised activations as the bf16 kernels
+          float a0 = bf2f(f2bf(bf_lo(xu[j]) * r * (bf_lo(wu[j]) + 1.f)));
+          float a1 = bf2f(f2bf(bf_hi(xu[j]) * r * (bf_hi(wu[j]) + 1.f)));
+          o[j] = __floats2half2_rn(a0, a1);
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) o[j] = __floats2half2_rn(bf_lo(xu[j]), bf_hi(xu[j]));
+      }
+    }
+    uint4 ov;
+    ov.x = *reinterpret_cast<uint32_t*>(&o[0]); ov.y = *reinterpret_cast<uint32_t*>(&o[1]);
+    ov.z = *reinterpret_cast<uint32_t*>(&o[2]); ov.w = *reinterpret_cast<uint32_t*>(&o[3]);
+    *reinterpret_cast<uint4*>(xs + (size_t)m * kc + c * 8) = ov;
+  }
+}
+
+template <int M>
+__device__ __forceinline__ void g4_row_scales(const Gemv4Args& a, float* rscale, float* scratch) {
+  for (int m = 0; m < M; ++m) {
+    float ss = 0.f;
+    if (m < a.M) {
+      for (int k = threadIdx.x * 8; k < a.K; k += blockDim.x * 8) {
+        uint4 v = *reinterpret_cast<const uint4*>(a.X + (size_t)m * a.ldx + k);
+        uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { float x0 = bf_lo(u[j]), x1 = bf_hi(u[j]); ss += x0 * x0 + x1 * x1; }
+      }
+    }
+    float tot = block_sum(ss, scratch);
+    if (threadIdx.x == 0) rscale[m] = rsqrtf(tot / (float)a.K + a.eps);
+  }
+  __syncthreads();
+}
+
+template <int M, bool SWIGLU, class Store>
+__device__ __forceinline__ void gemv4_main(const Gemv4Args& a, __half* xs, float* rscale, float* scratch, Store store) {
+  const int warp = threadIdx.x >> 5;
+  const int row0 = blockIdx.x * a.rows_per_cta;
+  const int row_end = min(a.N, row0 + a.rows_per_cta);
+  const int nchunks = (a.K + a.kc - 1) / a.kc;
+  constexpr int RW = SWIGLU ? 1 : G4_R;
+  int n = row0 + warp * RW;
+
+  pdl_launch_dependents();
+  Batch4 b;
+  int rows[G4_R];
+  g4_rows<SWIGLU>(a, rows, n);
+  g4_load(b, a, rows, 0);
+  pdl_wait();
+
+  if (a.norm_w) g4_row_scales<M>(a, rscale, scratch);
+
+  const int passes = (row_end - row0 + G4_WARPS * RW - 1) / (G4_WARPS * RW);
+  for (int pass = 0; pass < passes; ++pass, n += G4_WARPS * RW) {
+    const bool active = n < row_end;
+    float acc[G4_R][M] = {};
+    for (int c = 0; c < nchunks; ++c) {
+      const int k0 = c * a.kc;
+      if (nchunks > 1 || pass == 0) {
+        __syncthreads();
+        g4_stage<M>(a, xs, rscale, k0, a.kc);
+        __syncthreads();
+      }
+      if (active) {
+        for (int base = 0; base < a.kc; base += G4_BATCH) {
+          g4_consume<M>(acc, b, xs, a.kc, base);
+          const int knext = k0 + base + G4_BATCH;
+          if (knext < a.K) {
+            g4_load(b, a, rows, knext);
+          } else if (c == nchunks - 1 && base + G4_BATCH >= a.kc && n + G4_WARPS * RW < row_end) {
+            g4_rows<SWIGLU>(a, rows, n + G4_WARPS * RW);
+            g4_load(b, a, rows, 0);
+          }
+        }
+      }
+    }
+    if (active) {
+#pragma unroll
+      for (int r = 0; r < G4_R; ++r)
+#pragma unroll
+        for (int m = 0; m < M; ++m) acc[r][m] = warp_sum(acc[r][m]) * a.global_scale;
+      store(acc, n);
+    }
+  }
+}
+
+template <int M, bool SWIGLU>
+__global__ void __launch_bounds__(G4_THREADS, (M == 1 ? 3 : 2)) gemv_nvfp4_kernel(Gemv4Args a) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __half* xs = reinterpret_cast<__half*>(smem_raw);
+  __shared__ float scratch[32];
+  __shared__ float rscale[M];
+  const int row_end = min(a.N, (int)(blockIdx.x + 1) * a.rows_per_cta);
+  gemv4_main<M, SWIGLU>(a, xs, rscale, scratch, [&](float (&acc)[G4_R][M], int n) {
+    if ((threadIdx.x & 31) != 0) return;
+#pragma unroll
+    for (int m = 0; m < M; ++m) {
+      if (m >= a.M) break;
+      if (SWIGLU) {
+        float v = siluf_(acc[0][m]) * acc[1][m];
+        reinterpret_cast<__nv_bfloat16*>(a.Y)[(size_t)m * a.ldy + n] = f2bf(v);
+      } else {
+#pragma unroll
+        for (int r = 0; r < G4_R; ++r) {
+          int nn = n + r;
+          if (nn >= row_end) break;
+          float v = acc[r][m];
+          if (a.res) v += bf2f(a.res[(size_t)m * a.ldy + nn]);
+          if (a.out_f32) reinterpret_cast<float*>(a.Y)[(size_t)m * a.ldy + nn] = v;
+          else reinterpret_cast<__nv_bfloat16*>(a.Y)[(size_t)m * a.ldy + nn] = f2bf(v);
+        }
+      }
+    }
+  });
+}
+
+// Row-parallel projection under tensor parallelism: GEMV partial -> one-shot all-reduce over peers -> + residual.
+template <int M>
+__global__ void __launch_bounds__(G4_THREADS, 2) gemv_nvfp4_allreduce_kernel(Gemv4Args a, CommBuf cb) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __half* xs = reinterpret_cast<__half*>(smem_raw);
+  float* tile = reinterpret_cast<float*>(smem_raw + (size_t)M * a.kc * sizeof(__half));      // [M][rows_per_cta]
+  __shared__ float scratch[32];
+  __shared__ float rscale[M];
+  const int row0 = blockIdx.x * a.rows_per_cta;
+  const int row_end = min(a.N, row0 + a.rows_per_cta);
+  const int nrows = row_end - row0;
+  const int rpc = a.rows_per_cta;
+  for (int i = threadIdx.x; i < M * rpc; i += blockDim.x) tile[i] = 0.f;
+  __syncthreads();
+  gemv4_main<M, false>(a, xs, rscale, scratch, [&](float (&acc)[G4_R][M], int n) {
+    if ((threadIdx.x & 31) != 0) return;
+#pragma unroll
+    for (int r = 0; r < G4_R; ++r)
+      if (n + r < row_end)
+#pragma unroll
+        for (int m = 0; m < M; ++m) tile[m * rpc + (n + r - row0)] = acc[r][m];
+  });
+  __syncthreads();
+  cta_exchange_sum(cb, tile, M * rpc, (long)blockIdx.x * M * rpc);
+  for (int i = threadIdx.x; i < a.M * nrows; i += blockDim.x) {
+    int m = i / nrows, j = i % nrows;
+    float v = tile[m * rpc + j];
+    size_t o = (size_t)m * a.ldy + row0 + j;
+    if (a.res) v += bf2f(a.res[o]);
+    reinterpret_cast<__nv_bfloat16*>(a.Y)[o] = f2bf(v);
+  }
+}
+
+template <typename Kern, typename... Args>
+static int g4_launch(Kern kern, int grid, size_t smem, cudaStream_t s, Args... args) {
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, G4_SMEM + 16 * 1024);
+  if (e != cudaSuccess) return (int)e;
+  return (int)launch_pdl(kern, dim3(grid), dim3(G4_THREADS), smem, s, args...);
+}
+
+}  // namespace fb
+
+using namespace fb;
+
+static int fill_args(Gemv4Args& a, void* Y, const void* X, const void* Wq, const void* Sc, float gs,
+                     const void* norm_w, const void* res, int M, int N, int K, long ldx, long ldy, long sc_stride,
+                     float eps, int out_f32) {
+  if (M > 8 || (K % 32) != 0 || (ldx % 8) != 0) return -1;
+  a.X = (const __nv_bfloat16*)X; a.Wq = (const uint8_t*)Wq; a.Sc = (const uint8_t*)Sc; a.global_scale = gs;
+  a.norm_w = (const __nv_bfloat16*)norm_w; a.res = (const __nv_bfloat16*)res; a.Y = Y; a.M = M; a.N = N; a.K = K;
+  a.ldx = ldx; a.ldy = ldy; a.sc_stride = sc_stride; a.eps = eps; a.out_f32 = out_f32; a.rows_per_cta = 0; a.kc = 0;
+  return 0;
+}
+
+// mode: 0 plain (+res), 1 SwiGLU (2N weight rows: gate then up)
+extern "C" int fb_gemv_nvfp4(void* Y, const void* X, const void* Wq, const void* Sc, float global_scale,
+                             const void* norm_w, const void* res, int M, int N, int K, long ldx, long ldy,
+                             long sc_stride, float eps, int out_f32, int mode, int sm_count, cudaStream_t s) {
+  if (M <= 0 || N <= 0) return 0;
+  Gemv4Args a;
+  int rc = fill_args(a, Y, X, Wq, Sc, global_scale, norm_w, res, M, N, K, ldx, ldy, sc_stride, eps, out_f32);
+  if (rc) return rc;
+  if (sm_count <= 0) sm_count = 148;
+  const int Mt = M == 1 ? 1 : (M == 2 ? 2 : (M <= 4 ? 4 : 8));
+  a.kc = gemv4_chunk_len(Mt, K);
+  const int group = G4_WARPS * (mode == 1 ? 1 : G4_R);
+  int rpc = (N + sm_count * 3 - 1) / (sm_count * 3);
+  a.rows_per_cta = (rpc + group - 1) / group * group;
+  const int grid = (N + a.rows_per_cta - 1) / a.rows_per_cta;
+  const size_t smem = (size_t)Mt * a.kc * sizeof(__half);
+#define G4_GO(MV)                                                                                  \
+  return mode == 1 ? g4_launch(gemv_nvfp4_kernel<MV, true>, grid, smem, s, a)                       \
+                   : g4_launch(gemv_nvfp4_kernel<MV, false>, grid, smem, s, a);
+  if (Mt == 1) { G4_GO(1) } else if (Mt == 2) { G4_GO(2) } else if (Mt == 4) { G4_GO(4) } else { G4_GO(8) }
+#undef G4_GO
+}
+
+extern "C" int fb_gemv_nvfp4_allreduce(void* Y, const void* X, const void* Wq, const void* Sc, float global_scale,
+                                       const void* res, int M, int N, int K, long ldx, long ldy, long sc_stride,
+                                       const void* const* peers, int rank, int world, int max_ctas, long slot_floats,
+                                       uint32_t* epochs, int* status, unsigned spin_limit, int max_resident,
+                                       cudaStream_t s) {
+  if (M <= 0 || N <= 0) return 0;
+  Gemv4Args a;
+  int rc = fill_args(a, Y, X, Wq, Sc, global_scale, nullptr, res, M, N, K, ldx, ldy, sc_stride, 0.f, 0);
+  if (rc) return rc;
+  if (world > COMM_MAX_RANKS) return -1;
+  CommBuf cb;
+  fill_comm(cb, peers, rank, world, max_ctas, slot_floats, epochs, status, spin_limit);
+  const int Mt = M == 1 ? 1 : (M == 2 ? 2 : (M <= 4 ? 4 : 8));
+  a.kc = gemv4_chunk_len(Mt, K);
+  const int group = G4_WARPS * G4_R;
+  int rpc = (N + max_resident - 1) / max_resident;
+  a.rows_per_cta = (rpc + group - 1) / group * group;
+  const int grid = (N + a.rows_per_cta - 1) / a.rows_per_cta;
+  if (grid > max_resident || grid > max_ctas) return -7;
+  if ((long)grid * Mt * a.rows_per_cta > slot_floats) return -8;
+  const size_t smem = (size_t)Mt * a.kc * sizeof(__half) + (size_t)Mt * a.rows_per_cta * sizeof(float);
+  if (Mt == 1) return g4_launch(gemv_nvfp4_allreduce_kernel<1>, grid, smem, s, a, cb);
+  if (Mt == 2) return g4_launch(gemv_nvfp4_allreduce_kernel<2>, grid, smem, s, a, cb);
+  if (Mt == 4) return g4_launch(gemv_nvfp4_allreduce_kernel<4>, grid, smem, s, a, cb);
+  return g4_launch(gemv_nvfp4_allreduce_kernel<8>, grid, smem, s, a, cb);
+}

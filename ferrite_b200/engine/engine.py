@@ -49,6 +49,14 @@ class Engine:
             weights = shard_weights(cfg, weights, rank, world)
         weights = {k: (v.to(self.device) if v.dtype == torch.float32 and k.endswith(("A_log", "dt_bias", "router_bias"))
                        else v.to(self.device, self.dtype)) for k, v in weights.items()}
+        if self.ecfg.weight_dtype == "nvfp4":
+            from ..ops.qweight import quantize_weight
+            big = ("in_proj", "out_proj", "gate_up", "down", "lm_head")
+            for k in list(weights.keys()):
+                if k.split(".")[-1] in big and weights[k].dim() == 2 and weights[k].shape[1] % 32 == 0:
+                    weights[k] = quantize_weight(weights[k], "nvfp4", keep_dense=True, dense_dtype=self.dtype)
+        elif self.ecfg.weight_dtype != "bf16":
+            raise ValueError(f"weight_dtype {self.ecfg.weight_dtype!r} is not wired into the engine yet")
         self.cfg = cfg.shard(world)
         if on_gpu:
             from ..ops.cuda_ops import CudaOps

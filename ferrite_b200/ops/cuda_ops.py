@@ -13,6 +13,7 @@ from typing import Optional
 import torch
 
 from .._ext import load
+from .qweight import QWeight
 
 GEMV_MAX_ROWS = 8
 
@@ -69,6 +70,15 @@ class CudaOps:
         return s
 
     def linear(self, x, w, norm_w=None, eps=1e-6, res=None, swiglu=False, out_f32=False):
+        if isinstance(w, QWeight):
+            M = x.shape[0]
+            if M <= GEMV_MAX_ROWS and not self.force_gemv_chunks:
+                N = w.rows // 2 if swiglu else w.rows
+                y = torch.empty(M, N, dtype=torch.float32 if out_f32 else self.dtype, device=self.device)
+                self.launches += 1
+                self.C.gemv_nvfp4(y, x, w.packed, w.gemv_scales, w.global_scale, norm_w, res, eps, 1 if swiglu else 0)
+                return y
+            w = w.dense
         M, K = x.shape
         N = w.shape[0] // 2 if swiglu else w.shape[0]
         if M <= GEMV_MAX_ROWS or self.force_gemv_chunks or out_f32 and M <= 64:

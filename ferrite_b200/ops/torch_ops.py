@@ -40,6 +40,8 @@ class TorchOps:
 
     def linear(self, x, w, norm_w=None, eps=1e-6, res=None, swiglu=False, out_f32=False):
         """y = x W^T with optional RMSNorm(1+w) prologue, SwiGLU (W = [gate|up]) or residual epilogue."""
+        if hasattr(w, "dense"):
+            w = w.dense                      # quantised weight: the oracle multiplies by its dequantised values
         xf = x.float()
         if norm_w is not None:
             r = torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)

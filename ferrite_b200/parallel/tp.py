@@ -75,7 +75,10 @@ class TensorParallel:
         M, N = x.shape[0], w.shape[0]
         if self.fused and M <= 8:
             y = torch.empty(M, N, dtype=x.dtype, device=x.device)
-            self.C.gemv_allreduce(self.comm, y, x, w, res)
+            if hasattr(w, "packed"):
+                self.C.gemv_nvfp4_allreduce(self.comm, y, x, w.packed, w.gemv_scales, w.global_scale, res)
+            else:
+                self.C.gemv_allreduce(self.comm, y, x, w, res)
             ops.launches += 1
             self.stats["fused_gemv"] += 1
             return y

@@ -71,13 +71,18 @@ def report(name, ms, nbytes, flops, extra=None):
     return out
 
 
-def bench_linear(ops, t, m, n, k, swiglu=False, norm=False, res=False, label=None):
+def bench_linear(ops, t, m, n, k, swiglu=False, norm=False, res=False, label=None, fp4=False):
     rows = 2 * n if swiglu else n
     x, w = rnd(m, k), rnd(rows, k, scale=0.02)
+    wbytes = rows * k * 2
+    if fp4:
+        from ..ops.qweight import quantize_weight
+        w = quantize_weight(w)
+        wbytes = rows * k // 2 + rows * k // 16
     nw = rnd(k, scale=0.1) if norm else None
     r = rnd(m, n) if res else None
     ms = t.run(lambda: ops.linear(x, w, norm_w=nw, res=r, swiglu=swiglu))
-    nbytes = rows * k * 2 + m * k * 2 + m * n * 2 * (2 if res else 1)
+    nbytes = wbytes + m * k * 2 + m * n * 2 * (2 if res else 1)
     return report(label or f"linear m{m} n{n} k{k}{' swiglu' if swiglu else ''}", ms, nbytes, 2.0 * m * rows * k,
                   {"m": m, "n": n, "k": k})
 
@@ -95,6 +100,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--no-flush", action="store_true")
+    ap.add_argument("--fp4", action="store_true", help="NVFP4 weights (W4A16 GEMV for <= 8 rows)")
     a = ap.parse_args()
     from ..ops.cuda_ops import CudaOps
     dev = torch.device("cuda", 0)
@@ -102,7 +108,7 @@ def main():
     ops = CudaOps(dev)
     t = Timer(dev, a.warmup, a.iters, flush=not a.no_flush)
     if a.what in ("gemv", "gemm"):
-        bench_linear(ops, t, a.m, a.n, a.k, a.swiglu, a.norm, a.res)
+        bench_linear(ops, t, a.m, a.n, a.k, a.swiglu, a.norm, a.res, fp4=a.fp4)
     elif a.what == "layer":
         from ..config import hybrid_27b
         c = hybrid_27b()
@@ -116,7 +122,7 @@ def main():
                     ("mlp gate_up", c.inter, c.hidden, True, True, False),
                     ("mlp down", c.hidden, c.inter, False, False, True),
                     ("lm_head", c.vocab, c.hidden, False, True, False)):
-                r = bench_linear(ops, t, m, n, k, sw, nm, rs, label=f"{label} m{m}")
+                r = bench_linear(ops, t, m, n, k, sw, nm, rs, label=f"{label} m{m}", fp4=a.fp4)
                 tot_ms += r["ms"]
                 tot_b += r["GB/s"] * r["ms"]
         print(json.dumps({"sum_ms": round(tot_ms, 4), "mean_GB/s": round(tot_b / tot_ms, 1)}))

@@ -47,3 +47,20 @@ def test_27b_width_layers_decode_matches_prefill(ext):
     err = (a - b).abs().max().item()
     assert err < 0.03 * a.abs().max().item() + 0.02, err
     eng.check()
+
+
+def test_nvfp4_engine_matches_dequantised_oracle(ext):
+    """NVFP4 weights: the decode path (fp4 GEMV) and the oracle run on the same dequantised weights."""
+    cfg = tiny_hybrid()
+    w = init_weights(cfg, seed=0)
+    eng = Engine(cfg, w, EngineConfig(n_slots=1, max_ctx=256, weight_dtype="nvfp4"), device="cuda")
+    wq = {k: (v.dense.float().cpu() if hasattr(v, "dense") else v.float().cpu()) for k, v in eng.ex.w.items()}
+    ref = RefModel(cfg, wq)
+    prompt = _prompt(cfg, 20)
+    want = ref.forward(prompt + [3, 4], ref.new_state())
+    eng.forward([Segment(0, 0, prompt, "none")])
+    for i, t in enumerate([3, 4]):
+        lg, _, _ = eng.forward([Segment(0, 20 + i, [t], "last")])
+        err = (lg[0].cpu() - want[20 + i]).abs().max().item()
+        assert err < 0.05 * want.abs().max().item() + 0.02, (i, err)
+    eng.check()

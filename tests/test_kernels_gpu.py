@@ -188,3 +188,28 @@ def test_argmax(ops):
     lg[4, 9] = float("nan")
     _, finite = ops.argmax(lg.to(torch.bfloat16))
     assert finite.tolist() == [1, 1, 1, 1, 0]
+
+
+@pytest.mark.parametrize("M", [1, 2, 4, 8])
+@pytest.mark.parametrize("N,K", [(512, 1024), (5120, 5120), (640, 17408), (1024, 2048)])
+def test_gemv_nvfp4(ops, tops, M, N, K):
+    from ferrite_b200.ops.qweight import quantize_weight
+    x, w = rnd(M, K, seed=1), rnd(N, K, scale=0.05, seed=2)
+    q = quantize_weight(w)
+    # the quantiser itself: dequantised weights stay within fp4 error of the originals
+    assert (q.dense.float() - w.float()).abs().max().item() <= 0.27 * w.float().abs().max().item()
+    res = rnd(M, N, seed=3)
+    nw = rnd(K, scale=0.1, seed=4)
+    close(ops.linear(x, q), tops.linear(x, q))
+    close(ops.linear(x, q, res=res, norm_w=nw), tops.linear(x, q, res=res, norm_w=nw))
+    close(ops.linear(x, q, out_f32=True), tops.linear(x, q, out_f32=True))
+
+
+@pytest.mark.parametrize("M", [1, 4])
+def test_gemv_nvfp4_swiglu(ops, tops, M):
+    from ferrite_b200.ops.qweight import quantize_weight
+    K, I = 5120, 2048
+    x, w = rnd(M, K, seed=1), rnd(2 * I, K, scale=0.03, seed=2)
+    q = quantize_weight(w)
+    nw = rnd(K, scale=0.1, seed=4)
+    close(ops.linear(x, q, norm_w=nw, swiglu=True), tops.linear(x, q, norm_w=nw, swiglu=True))
