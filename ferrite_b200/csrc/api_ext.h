@@ -30,6 +30,15 @@ int fb_gemv_nvfp4_allreduce(void* Y, const void* X, const void* Wq, const void* 
                             const void* const* peers, int rank, int world, int max_ctas, long slot_floats,
                             uint32_t* epochs, int* status, unsigned spin_limit, int max_resident, cudaStream_t s);
 
+// ---- gemm_nvfp4.cu: activation quantiser and block-scaled tcgen05 GEMM (W4A4) ----
+long fb_nvfp4_sf_bytes(int rows, int K);
+int fb_quant_nvfp4(void* codes, void* sf, float* row_scale, const void* x, long ldx, const void* norm_w, int M, int K,
+                   float eps, cudaStream_t s);
+long fb_gemm_nvfp4_workspace_bytes(int M, int N, int split_k);
+int fb_gemm_nvfp4(void* Y, const void* Xq, const void* x_sf, const float* row_scale, const void* Wq, const void* w_sf,
+                  float w_scale, const void* res, int M, int N, int K, long ldy, int mode, int split_k,
+                  float* workspace, int* counters, int* status, int sm_count, cudaStream_t s);
+
 #ifdef __cplusplus
 }
 #endif

@@ -87,6 +87,31 @@ void gemv_nvfp4_allreduce(const Comm& c, Tensor Y, Tensor X, Tensor packed, Tens
                                 cur_stream()), "gemv_nvfp4_allreduce");
 }
 
+int64_t nvfp4_sf_bytes(int64_t rows, int64_t K) { return fb_nvfp4_sf_bytes((int)rows, (int)K); }
+
+void quant_nvfp4(Tensor codes, Tensor sf, Tensor row_scale, Tensor x, c10::optional<Tensor> norm_w, double eps) {
+  check(fb_quant_nvfp4(codes.data_ptr(), sf.data_ptr(), row_scale.data_ptr<float>(), x.data_ptr(), (long)x.stride(0),
+                       cptr(norm_w), (int)x.size(0), (int)x.size(1), (float)eps, cur_stream()), "quant_nvfp4");
+}
+
+int64_t gemm_nvfp4_workspace_bytes(int64_t M, int64_t N, int64_t split_k) {
+  return fb_gemm_nvfp4_workspace_bytes((int)M, (int)N, (int)split_k);
+}
+
+void gemm_nvfp4(Tensor Y, Tensor xq, Tensor x_sf, Tensor row_scale, Tensor wq, Tensor w_sf, double w_scale,
+                c10::optional<Tensor> res, int64_t mode, int64_t split_k, c10::optional<Tensor> workspace,
+                c10::optional<Tensor> counters, c10::optional<Tensor> status) {
+  int M = (int)xq.size(0), K = (int)xq.size(1) * 2;
+  int N = (int)(mode == 1 ? wq.size(0) / 2 : wq.size(0));
+  TORCH_CHECK(wq.size(1) * 2 == K, "gemm_nvfp4: K mismatch");
+  check(fb_gemm_nvfp4(Y.data_ptr(), xq.data_ptr(), x_sf.data_ptr(), row_scale.data_ptr<float>(), wq.data_ptr(),
+                      w_sf.data_ptr(), (float)w_scale, cptr(res), M, N, K, (long)Y.stride(0), (int)mode, (int)split_k,
+                      workspace.has_value() ? (float*)workspace->data_ptr() : nullptr,
+                      counters.has_value() ? (int*)counters->data_ptr() : nullptr,
+                      status.has_value() ? (int*)status->data_ptr() : nullptr,
+                      at::cuda::getCurrentDeviceProperties()->multiProcessorCount, cur_stream()), "gemm_nvfp4");
+}
+
 }  // namespace
 
 void register_ext(pybind11::module_& m) {
@@ -100,5 +125,9 @@ void register_ext(pybind11::module_& m) {
   m.def("argmax_gather", &argmax_gather);
   m.def("comm_wait_probe", &comm_wait_probe);
   m.def("gemv_nvfp4", &gemv_nvfp4);
+  m.def("nvfp4_sf_bytes", &nvfp4_sf_bytes);
+  m.def("quant_nvfp4", &quant_nvfp4);
+  m.def("gemm_nvfp4_workspace_bytes", &gemm_nvfp4_workspace_bytes);
+  m.def("gemm_nvfp4", &gemm_nvfp4);
   m.def("gemv_nvfp4_allreduce", &gemv_nvfp4_allreduce);
 }

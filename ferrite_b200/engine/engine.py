@@ -49,7 +49,7 @@ class Engine:
             weights = shard_weights(cfg, weights, rank, world)
         weights = {k: (v.to(self.device) if v.dtype == torch.float32 and k.endswith(("A_log", "dt_bias", "router_bias"))
                        else v.to(self.device, self.dtype)) for k, v in weights.items()}
-        if self.ecfg.weight_dtype == "nvfp4":
+        if self.ecfg.weight_dtype in ("nvfp4", "nvfp4-a16"):
             from ..ops.qweight import quantize_weight
             big = ("in_proj", "out_proj", "gate_up", "down", "lm_head")
             for k in list(weights.keys()):
@@ -64,6 +64,10 @@ class Engine:
         else:
             from ..ops.torch_ops import TorchOps
             ops = TorchOps(self.device, self.dtype)
+        # "nvfp4": weights and activations in NVFP4 on the block-scaled tcgen05 GEMM for every row count;
+        # "nvfp4-a16": NVFP4 weights against 16-bit activations (SIMT GEMV for decode rows, dense copy for prompts)
+        if on_gpu:
+            ops.fp4_act = self.ecfg.weight_dtype == "nvfp4"
         self.ops = ops
         self.tp = tp
         self.ex = Executor(self.cfg, weights, self.ecfg, ops, tp=tp, full_cfg=cfg)

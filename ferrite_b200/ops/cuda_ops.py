@@ -32,6 +32,8 @@ class CudaOps:
         self._counters = torch.zeros(4096, dtype=torch.int32, device=self.device)
         self.force_gemv_chunks = False      # debug: run any row count through 8-row GEMV passes
         self.launches = 0                   # kernels launched (or recorded into a graph) through this object
+        self.fp4_act = False                # NVFP4 weights: quantise activations too and use the tcgen05 GEMM
+        self._sf_pool = {}
 
     # ---- workspace ---------------------------------------------------------------------------------
     def _workspace(self, nbytes: int) -> torch.Tensor:
@@ -72,6 +74,10 @@ class CudaOps:
     def linear(self, x, w, norm_w=None, eps=1e-6, res=None, swiglu=False, out_f32=False):
         if isinstance(w, QWeight):
             M = x.shape[0]
+            N = w.rows // 2 if swiglu else w.rows
+            if (self.fp4_act and w.mma_scales is not None and w.cols % 256 == 0 and not out_f32
+                    and (not swiglu or N % 128 == 0) and (M <= 64 or N % 8 == 0)):
+                return self._linear_w4a4(x, w, norm_w, eps, res, swiglu, M, N)
             if M <= GEMV_MAX_ROWS and not self.force_gemv_chunks:
                 N = w.rows // 2 if swiglu else w.rows
                 y = torch.empty(M, N, dtype=torch.float32 if out_f32 else self.dtype, device=self.device)
@@ -101,6 +107,35 @@ class CudaOps:
         self.launches += 1
         self.C.gemm(y, x, w, res, 1 if swiglu else 0, split, ws, cnt, self.status_word)
         return y.float() if out_f32 else y
+
+    # ---- NVFP4 weights x NVFP4 activations on the block-scaled tensor-core GEMM -------------------------
+    def quant_nvfp4(self, x, norm_w=None, eps=1e-6):
+        """Quantise activation rows (optionally after RMSNorm) to e2m1 codes + tiled e4m3 scales + per-row scale."""
+        M, K = x.shape
+        codes = torch.empty(M, K // 2, dtype=torch.uint8, device=self.device)
+        key = ((M + 127) // 128, K)
+        sf = self._sf_pool.get(key)
+        if sf is None:
+            # zero-initialised once: rows of the last 128-row tile that no call writes keep a finite (zero) scale
+            sf = torch.zeros(int(self.C.nvfp4_sf_bytes(M, K)), dtype=torch.uint8, device=self.device)
+            self._sf_pool[key] = sf
+        rs = torch.empty(M, dtype=torch.float32, device=self.device)
+        self.launches += 1
+        self.C.quant_nvfp4(codes, sf, rs, x, norm_w, eps)
+        return codes, sf, rs
+
+    def _linear_w4a4(self, x, w, norm_w, eps, res, swiglu, M, N):
+        xq, xsf, rs = self.quant_nvfp4(x, norm_w, eps)
+        y = torch.empty(M, N, dtype=self.dtype, device=self.device)
+        split = self._split_k(M, N, w.cols // 4) if M <= 64 else 1
+        ws = cnt = None
+        if split > 1:
+            ws = self._workspace(int(self.C.gemm_nvfp4_workspace_bytes(M, N, split)))
+            cnt = self._counters
+        self.launches += 1
+        self.C.gemm_nvfp4(y, xq, xsf, rs, w.packed, w.mma_scales, w.global_scale, res, 1 if swiglu else 0, split, ws,
+                          cnt, self.status_word)
+        return y
 
     def silu_mul(self, gu):
         out = torch.empty(gu.shape[0], gu.shape[1] // 2, dtype=self.dtype, device=self.device)

@@ -34,7 +34,8 @@ class QWeight:
         raise TypeError("slice a QWeight before quantising it")
 
 
-def quantize_weight(w: torch.Tensor, kind: str = "nvfp4", keep_dense: bool = True, dense_dtype=None) -> QWeight:
+def quantize_weight(w: torch.Tensor, kind: str = "nvfp4", keep_dense: bool = True, dense_dtype=None,
+                    mma: bool = True) -> QWeight:
     assert kind == "nvfp4"
     rows, cols = w.shape
     # quantise in row slabs to bound the fp32 temporaries
@@ -50,4 +51,5 @@ def quantize_weight(w: torch.Tensor, kind: str = "nvfp4", keep_dense: bool = Tru
             dense.append(q.dequantize(dense_dtype or w.dtype))
     sc = torch.cat(scales, 0)
     return QWeight(kind, rows, cols, torch.cat(packed, 0).contiguous(), nvfp4.tile_scales_gemv(sc), gs,
-                   torch.cat(dense, 0).contiguous() if keep_dense else None)
+                   torch.cat(dense, 0).contiguous() if keep_dense else None,
+                   nvfp4.tile_scales_mma(sc).contiguous() if mma and cols % 64 == 0 else None)

@@ -73,7 +73,7 @@ class TensorParallel:
     # ---- row-parallel projection + all-reduce + residual --------------------------------------------------
     def linear_allreduce(self, ops, x, w, res):
         M, N = x.shape[0], w.shape[0]
-        if self.fused and M <= 8:
+        if self.fused and M <= 8 and not (hasattr(w, "packed") and getattr(ops, "fp4_act", False)):
             y = torch.empty(M, N, dtype=x.dtype, device=x.device)
             if hasattr(w, "packed"):
                 self.C.gemv_nvfp4_allreduce(self.comm, y, x, w.packed, w.gemv_scales, w.global_scale, res)

@@ -100,12 +100,14 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--no-flush", action="store_true")
-    ap.add_argument("--fp4", action="store_true", help="NVFP4 weights (W4A16 GEMV for <= 8 rows)")
+    ap.add_argument("--fp4", action="store_true", help="NVFP4 weights and activations (block-scaled tcgen05 GEMM)")
+    ap.add_argument("--a16", action="store_true", help="with --fp4: keep 16-bit activations (W4A16 GEMV)")
     a = ap.parse_args()
     from ..ops.cuda_ops import CudaOps
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
     ops = CudaOps(dev)
+    ops.fp4_act = a.fp4 and not a.a16
     t = Timer(dev, a.warmup, a.iters, flush=not a.no_flush)
     if a.what in ("gemv", "gemm"):
         bench_linear(ops, t, a.m, a.n, a.k, a.swiglu, a.norm, a.res, fp4=a.fp4)

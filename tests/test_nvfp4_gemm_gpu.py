@@ -1,0 +1,84 @@
+"""Block-scaled NVFP4 tcgen05 GEMM and its activation quantiser against host decodes of the same codes."""
+import pytest
+import torch
+
+from ferrite_b200.formats import nvfp4
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+@pytest.fixture(scope="module")
+def ops(ext):
+    from ferrite_b200.ops.cuda_ops import CudaOps
+    o = CudaOps(DEV)
+    o.fp4_act = True
+    return o
+
+
+def rnd(*shape, scale=1.0, seed=0):
+    g = torch.Generator(device=DEV).manual_seed(seed)
+    return (torch.randn(*shape, generator=g, device=DEV) * scale).to(torch.bfloat16)
+
+
+def untile(sf, rows, K):
+    """Tiled activation scales [rt][K/64][32][4][4] back to [rows][K/16]."""
+    rt, kt = (rows + 127) // 128, K // 64
+    t = sf[:rt * kt * 512].view(rt, kt, 32, 4, 4).permute(0, 3, 2, 1, 4).reshape(rt * 128, kt * 4)
+    return t[:rows]
+
+
+def decode_act(codes, sf, rs, rows, K):
+    lo = nvfp4.e2m1_to_float(codes & 0xF)
+    hi = nvfp4.e2m1_to_float(codes >> 4)
+    v = torch.stack([lo, hi], -1).reshape(rows, K)
+    sc = untile(sf, rows, K).view(torch.float8_e4m3fn).float().repeat_interleave(16, 1)
+    return v * sc * rs[:, None]
+
+
+@pytest.mark.parametrize("M,K", [(1, 256), (5, 5120), (130, 1024)])
+def test_activation_quantiser(ops, M, K):
+    x = rnd(M, K, seed=1)
+    codes, sf, rs = ops.quant_nvfp4(x)
+    got = decode_act(codes, sf, rs, M, K)
+    # same recipe on the host (per-row global scale)
+    want = torch.stack([nvfp4.quantize(x[i:i + 1].float(), global_scale=float(rs[i])).dequantize()[0] for i in range(M)])
+    assert torch.allclose(rs, x.float().abs().amax(1) / (6 * 448), rtol=1e-6)
+    mism = (got != want).float().mean().item()
+    assert mism < 5e-3, mism                      # identical up to rare rounding ties (device multiplies by 1/scale)
+    assert (got - x.float()).abs().max().item() <= 0.3 * x.float().abs().max().item()
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 256, 256), (4, 5120, 5120), (16, 1024, 2048), (48, 5120, 17408),
+                                   (128, 512, 512), (300, 1024, 768), (2048, 6144, 5120)])
+def test_gemm_nvfp4(ops, M, N, K):
+    from ferrite_b200.ops.qweight import quantize_weight
+    x, w = rnd(M, K, seed=1), rnd(N, K, scale=0.05, seed=2)
+    q = quantize_weight(w)
+    res = rnd(M, N, seed=3)
+    codes, sf, rs = ops.quant_nvfp4(x)
+    xdq = decode_act(codes, sf, rs, M, K)
+    want = xdq @ q.dense.float().t()
+    got = ops.linear(x, q)
+    err = (got.float() - want).abs().max().item() / want.abs().max().item()
+    assert err < 1.5e-2, err
+    got = ops.linear(x, q, res=res)
+    err = (got.float() - (want + res.float())).abs().max().item() / want.abs().max().item()
+    assert err < 1.5e-2, err
+    assert ops.status() == 0
+
+
+@pytest.mark.parametrize("M", [2, 24, 200])
+def test_gemm_nvfp4_swiglu_norm(ops, M):
+    from ferrite_b200.ops.qweight import quantize_weight
+    K, I = 1024, 1536
+    x, w, nw = rnd(M, K, seed=1), rnd(2 * I, K, scale=0.05, seed=2), rnd(K, scale=0.1, seed=4)
+    q = quantize_weight(w)
+    codes, sf, rs = ops.quant_nvfp4(x, nw, 1e-6)
+    xdq = decode_act(codes, sf, rs, M, K)
+    y = xdq @ q.dense.float().t()
+    want = torch.nn.functional.silu(y[:, :I]) * y[:, I:]
+    got = ops.linear(x, q, norm_w=nw, eps=1e-6, swiglu=True)
+    err = (got.float() - want).abs().max().item() / want.abs().max().item()
+    assert err < 2e-2, err
+    assert ops.status() == 0
