@@ -39,6 +39,11 @@ int fb_gemm_nvfp4(void* Y, const void* Xq, const void* x_sf, const float* row_sc
                   float w_scale, const void* res, int M, int N, int K, long ldy, int mode, int split_k,
                   float* workspace, int* counters, int* status, int sm_count, cudaStream_t s);
 
+int fb_gemm_nvfp4_fused(void* Y, const void* X, long ldx, const void* norm_w, float eps, const void* Wq,
+                        const void* w_sf, float w_scale, const void* res, int M, int N, int K, long ldy, int mode,
+                        int split_k, int out_f32, float* workspace, int* counters, int* status, int sm_count,
+                        cudaStream_t s);
+
 #ifdef __cplusplus
 }
 #endif

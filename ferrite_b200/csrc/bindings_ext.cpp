@@ -112,6 +112,22 @@ void gemm_nvfp4(Tensor Y, Tensor xq, Tensor x_sf, Tensor row_scale, Tensor wq, T
                       at::cuda::getCurrentDeviceProperties()->multiProcessorCount, cur_stream()), "gemm_nvfp4");
 }
 
+void gemm_nvfp4_fused(Tensor Y, Tensor X, c10::optional<Tensor> norm_w, double eps, Tensor wq, Tensor w_sf,
+                      double w_scale, c10::optional<Tensor> res, int64_t mode, int64_t split_k,
+                      c10::optional<Tensor> workspace, c10::optional<Tensor> counters, c10::optional<Tensor> status) {
+  int M = (int)X.size(0), K = (int)X.size(1);
+  int N = (int)(mode == 1 ? wq.size(0) / 2 : wq.size(0));
+  TORCH_CHECK(wq.size(1) * 2 == K, "gemm_nvfp4_fused: K mismatch");
+  check(fb_gemm_nvfp4_fused(Y.data_ptr(), X.data_ptr(), (long)X.stride(0), cptr(norm_w), (float)eps, wq.data_ptr(),
+                            w_sf.data_ptr(), (float)w_scale, cptr(res), M, N, K, (long)Y.stride(0), (int)mode,
+                            (int)split_k, Y.scalar_type() == torch::kFloat32 ? 1 : 0,
+                            workspace.has_value() ? (float*)workspace->data_ptr() : nullptr,
+                            counters.has_value() ? (int*)counters->data_ptr() : nullptr,
+                            status.has_value() ? (int*)status->data_ptr() : nullptr,
+                            at::cuda::getCurrentDeviceProperties()->multiProcessorCount, cur_stream()),
+        "gemm_nvfp4_fused");
+}
+
 }  // namespace
 
 void register_ext(pybind11::module_& m) {
@@ -129,5 +145,6 @@ void register_ext(pybind11::module_& m) {
   m.def("quant_nvfp4", &quant_nvfp4);
   m.def("gemm_nvfp4_workspace_bytes", &gemm_nvfp4_workspace_bytes);
   m.def("gemm_nvfp4", &gemm_nvfp4);
+  m.def("gemm_nvfp4_fused", &gemm_nvfp4_fused);
   m.def("gemv_nvfp4_allreduce", &gemv_nvfp4_allreduce);
 }

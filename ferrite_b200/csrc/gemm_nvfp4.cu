@@ -47,6 +47,14 @@ struct Q4Args {
   int b_sf_tiles;             // 128-row scale tiles of the B operand per stage
   int n_bm;                   // B boxes that get their own MMA + accumulator (normal SwiGLU: gate, up)
   int n_buf;                  // accumulator buffers in TMEM (2 = epilogue overlaps the next tile)
+  // fused activation quantiser (swapped orientation, <= 8 rows): the epilogue warps read the bf16 rows,
+  // normalise + quantise them stage by stage straight into the B tile and its scale atoms
+  int fuseq;
+  const __nv_bfloat16* X;
+  long ldx;
+  const __nv_bfloat16* norm_w;
+  float eps;
+  int out_f32;
 };
 
 __device__ __forceinline__ bool q4_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
@@ -75,7 +83,10 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_s;
   __shared__ int last_flag_s;
+  __shared__ float rs_s[8], rn_s[8];      // fused quantiser: per-row global scale and RMSNorm factor
+  __shared__ float red_s[4][8];
 
+  pdl_launch_dependents();
   unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int b_bytes = a.n_b * a.b_box_rows * Q4_BKB;
@@ -91,7 +102,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 
   if (threadIdx.x == 0) {
     abort_s = 0;
-    for (int i = 0; i < a.stages; ++i) { mbar_init(&full_bar[i], 1); mbar_init(&empty_bar[i], 1); }
+    for (int i = 0; i < a.stages; ++i) { mbar_init(&full_bar[i], a.fuseq ? 5 : 1); mbar_init(&empty_bar[i], 1); }
     for (int i = 0; i < 2; ++i) { mbar_init(&tfull_bar[i], 1); mbar_init(&tempty_bar[i], 4); }
     fence_mbar_init();
   }
@@ -117,8 +128,11 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       tma_prefetch_desc(&tmA);
       tma_prefetch_desc(&tmB);
       int stage = 0; uint32_t phase = 0;
-      const uint32_t tx = (uint32_t)(a.n_a * Q4_A_BYTES + b_bytes + sfa_bytes + sfb_bytes);
+      const uint32_t tx = (uint32_t)(a.n_a * Q4_A_BYTES + sfa_bytes + (a.fuseq ? 0 : b_bytes + sfb_bytes));
       bool ok = true;
+      // weights never depend on the previous kernel: with the fused quantiser this warp starts streaming them
+      // at once; otherwise it also loads the quantised activations and has to wait for their producer
+      if (!a.fuseq) pdl_wait();
       for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
         int ta, tb, ks;
         decode_work(w, ta, tb, ks);
@@ -137,11 +151,11 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             bulk_load(ssfa + i * Q4_SF_STAGE, a.sf_a + ((size_t)(row / 128) * kt_total + (size_t)kb * 4) * Q4_SF_ATOM,
                       Q4_SF_STAGE, &full_bar[stage]);
           }
-          for (int i = 0; i < a.n_b; ++i) {
+          for (int i = 0; i < (a.fuseq ? 0 : a.n_b); ++i) {
             const int row = tb * a.b_box_rows + i * a.N;
             tma_load_2d(sb + (size_t)i * a.b_box_rows * Q4_BKB, &tmB, &full_bar[stage], kx, row);
           }
-          for (int i = 0; i < a.b_sf_tiles; ++i) {
+          for (int i = 0; i < (a.fuseq ? 0 : a.b_sf_tiles); ++i) {
             // normal SwiGLU: scale tile 0 = gate rows, tile 1 = up rows; otherwise consecutive 128-row tiles
             const int row = a.swap ? 0 : tb * a.b_box_rows + i * a.N;
             bulk_load(ssfb + i * Q4_SF_STAGE, a.sf_b + ((size_t)(row / 128) * kt_total + (size_t)kb * 4) * Q4_SF_ATOM,
@@ -214,9 +228,133 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     int buf = 0; uint32_t tphase[2] = {0, 0};
     bool ok = true;
     __nv_bfloat16* Yb = reinterpret_cast<__nv_bfloat16*>(a.Y);
+    pdl_wait();                                  // everything below reads X or writes Y / the split-K workspace
+    int qstage = 0; uint32_t qphase = 0;
+    if (a.fuseq) {
+      // zero the B tiles and their scale atoms once: rows >= M of the 16-row box stay zero for the whole kernel
+      for (int st = 0; st < a.stages; ++st) {
+        unsigned char* sb = tiles + (size_t)st * stage_bytes + a.n_a * Q4_A_BYTES;
+        for (int i = etid * 16; i < b_bytes_pad; i += 128 * 16) *reinterpret_cast<uint4*>(sb + i) = make_uint4(0, 0, 0, 0);
+        unsigned char* sf = sb + b_bytes_pad + sfa_bytes;
+        for (int i = etid * 16; i < sfb_bytes; i += 128 * 16) *reinterpret_cast<uint4*>(sf + i) = make_uint4(0, 0, 0, 0);
+      }
+      // per-row RMSNorm factor, then per-row amax of the (normalised, bf16-rounded) values -> global scale
+      for (int pass = 0; pass < 2; ++pass) {
+        if (pass == 0 && !a.norm_w) { if (etid < 8) rn_s[etid] = 1.f; asm volatile("bar.sync 1, 128;" ::: "memory"); continue; }
+        float acc[8];
+#pragma unroll
+        for (int m = 0; m < 8; ++m) acc[m] = 0.f;
+        for (int m = 0; m < a.M; ++m) {
+          const __nv_bfloat16* xr = a.X + (size_t)m * a.ldx;
+          const float rn = pass ? rn_s[m] : 0.f;
+          for (int k = etid * 8; k < a.K; k += 128 * 8) {
+            uint4 v = *reinterpret_cast<const uint4*>(xr + k);
+            uint32_t u[4] = {v.x, v.y, v.z, v.w};
+            if (pass == 0) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) { float x0 = bf_lo(u[j]), x1 = bf_hi(u[j]); acc[m] += x0 * x0 + x1 * x1; }
+            } else if (a.norm_w) {
+              uint4 wv = __ldg(reinterpret_cast<const uint4*>(a.norm_w + k));
+              uint32_t wu[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                acc[m] = fmaxf(acc[m], fabsf(bf2f(f2bf(bf_lo(u[j]) * rn * (1.f + bf_lo(wu[j]))))));
+                acc[m] = fmaxf(acc[m], fabsf(bf2f(f2bf(bf_hi(u[j]) * rn * (1.f + bf_hi(wu[j]))))));
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) acc[m] = fmaxf(acc[m], fmaxf(fabsf(bf_lo(u[j])), fabsf(bf_hi(u[j]))));
+            }
+          }
+        }
+#pragma unroll
+        for (int m = 0; m < 8; ++m) {
+          float v = acc[m];
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) {
+            float t = __shfl_xor_sync(0xffffffffu, v, o);
+            v = pass ? fmaxf(v, t) : v + t;
+          }
+          if (lane == 0) red_s[quad][m] = v;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (etid < 8) {
+          float v = pass ? fmaxf(fmaxf(red_s[0][etid], red_s[1][etid]), fmaxf(red_s[2][etid], red_s[3][etid]))
+                         : red_s[0][etid] + red_s[1][etid] + red_s[2][etid] + red_s[3][etid];
+          if (pass == 0) rn_s[etid] = rsqrtf(v / (float)a.K + a.eps);
+          else rs_s[etid] = v > 0.f ? v / (6.f * 448.f) : 1.f;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+      }
+    }
     for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
       int ta, tb, ks;
       decode_work(w, ta, tb, ks);
+      if (a.fuseq) {
+        // quantise this item's k blocks into the B tiles: thread = (row, 16-value block) of the 256-wide stage
+        const int qm = etid >> 4, qb = etid & 15;
+        const int kb0 = ks * kb_per_split, kb1 = min(kblocks_total, kb0 + kb_per_split);
+        // the activation (and norm weight) values of the next k block are requested before this one is
+        // quantised, so their L2 latency overlaps the work instead of adding to every stage
+        const bool qact = qm < a.M;
+        uint4 nx0 = make_uint4(0, 0, 0, 0), nx1 = nx0, nw0 = nx0, nw1 = nx0;
+        if (qact && kb0 < kb1) {
+          const int k = kb0 * Q4_BK + qb * 16;
+          const uint4* xp = reinterpret_cast<const uint4*>(a.X + (size_t)qm * a.ldx + k);
+          nx0 = xp[0]; nx1 = xp[1];
+          if (a.norm_w) { const uint4* wp = reinterpret_cast<const uint4*>(a.norm_w + k); nw0 = __ldg(wp); nw1 = __ldg(wp + 1); }
+        }
+        for (int kb = kb0; kb < kb1 && ok; ++kb) {
+          const uint4 v0 = nx0, v1 = nx1, w0 = nw0, w1 = nw1;
+          if (qact && kb + 1 < kb1) {
+            const int k = (kb + 1) * Q4_BK + qb * 16;
+            const uint4* xp = reinterpret_cast<const uint4*>(a.X + (size_t)qm * a.ldx + k);
+            nx0 = xp[0]; nx1 = xp[1];
+            if (a.norm_w) { const uint4* wp = reinterpret_cast<const uint4*>(a.norm_w + k); nw0 = __ldg(wp); nw1 = __ldg(wp + 1); }
+          }
+          ok = q4_wait(&empty_bar[qstage], qphase ^ 1u, abort_flag);
+          if (ok && qact) {
+            unsigned char* sb = tiles + (size_t)qstage * stage_bytes + a.n_a * Q4_A_BYTES;
+            unsigned char* sf = sb + b_bytes_pad + sfa_bytes;
+            uint32_t u[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+            float xv[16];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) { xv[2 * j] = bf_lo(u[j]); xv[2 * j + 1] = bf_hi(u[j]); }
+            if (a.norm_w) {
+              uint32_t wu[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+              const float rn = rn_s[qm];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                xv[2 * j] = bf2f(f2bf(xv[2 * j] * rn * (1.f + bf_lo(wu[j]))));
+                xv[2 * j + 1] = bf2f(f2bf(xv[2 * j + 1] * rn * (1.f + bf_hi(wu[j]))));
+              }
+            }
+            float bm = 0.f;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) bm = fmaxf(bm, fabsf(xv[j]));
+            const float gs = rs_s[qm];
+            __nv_fp8_storage_t sc8 = __nv_cvt_float_to_fp8(bm * (1.f / gs) * (1.f / 6.f), __NV_SATFINITE, __NV_E4M3);
+            __half_raw hr = __nv_cvt_fp8_to_halfraw(sc8, __NV_E4M3);
+            const float scf = __half2float(*reinterpret_cast<__half*>(&hr));
+            const float inv = scf > 0.f ? 1.f / (scf * gs) : 0.f;
+            uint32_t packed[2] = {0, 0};
+#pragma unroll
+            for (int j = 0; j < 16; j += 2) {
+              __nv_fp4x2_storage_t c2 = __nv_cvt_float2_to_fp4x2(make_float2(xv[j] * inv, xv[j + 1] * inv), __NV_E2M1, cudaRoundNearest);
+              packed[j / 8] |= (uint32_t)c2 << (8 * ((j / 2) % 4));
+            }
+            // 128-byte swizzle of the K-major tile: 16-byte chunk c of row r lives at chunk c ^ (r % 8)
+            const int chunk = (qb >> 1) ^ (qm & 7);
+            *reinterpret_cast<uint2*>(sb + qm * 128 + chunk * 16 + (qb & 1) * 8) = make_uint2(packed[0], packed[1]);
+            sf[(qb >> 2) * Q4_SF_ATOM + qm * 16 + (qb & 3)] = sc8;
+          }
+          fence_proxy_async();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&full_bar[qstage]);
+          if (++qstage == a.stages) { qstage = 0; qphase ^= 1u; }
+        }
+        if (!ok) break;
+      }
       ok = q4_wait(&tfull_bar[buf], tphase[buf], abort_flag);
       if (a.split_k > 1) {
         uint32_t all_ok;
@@ -289,11 +427,12 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
               for (int j = 0; j < 16; ++j) {
                 const int m = m0 + c + j;
                 if (m < a.M) {
-                  const float alpha = a.w_scale * a.row_scale[m];
+                  const float alpha = a.w_scale * (a.fuseq ? rs_s[m] : a.row_scale[m]);
                   float x = __uint_as_float(r0[j]) * alpha;
                   if (a.dual) x = siluf_(x) * (__uint_as_float(r1[j]) * alpha);
                   if (a.res) x += bf2f(a.res[(size_t)m * a.ldy + n]);
-                  Yb[(size_t)m * a.ldy + n] = f2bf(x);
+                  if (a.out_f32) reinterpret_cast<float*>(a.Y)[(size_t)m * a.ldy + n] = x;
+                  else Yb[(size_t)m * a.ldy + n] = f2bf(x);
                 }
               }
             }
@@ -333,10 +472,11 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                 if (a.dual) u += __ldcg(p + (size_t)(a.bn + c) * Q4_BM + etid);
               }
               if (n_ok) {
-                const float alpha = a.w_scale * a.row_scale[m];
+                const float alpha = a.w_scale * (a.fuseq ? rs_s[m] : a.row_scale[m]);
                 float x = a.dual ? siluf_(g * alpha) * (u * alpha) : g * alpha;
                 if (a.res) x += bf2f(a.res[(size_t)m * a.ldy + n]);
-                Yb[(size_t)m * a.ldy + n] = f2bf(x);
+                if (a.out_f32) reinterpret_cast<float*>(a.Y)[(size_t)m * a.ldy + n] = x;
+                else Yb[(size_t)m * a.ldy + n] = f2bf(x);
               }
             }
             if (etid == 0) a.counters[tile_id] = 0;
@@ -483,13 +623,18 @@ extern "C" long fb_gemm_nvfp4_workspace_bytes(int M, int N, int split_k) {
 }
 
 // Xq/x_sf/row_scale: quantised activations from fb_quant_nvfp4. Wq/w_sf: weight codes [rows][K/2] and tiled scales.
-extern "C" int fb_gemm_nvfp4(void* Y, const void* Xq, const void* x_sf, const float* row_scale, const void* Wq,
-                             const void* w_sf, float w_scale, const void* res, int M, int N, int K, long ldy, int mode,
-                             int split_k, float* workspace, int* counters, int* status, int sm_count, cudaStream_t s) {
+static int gemm_nvfp4_impl(void* Y, const void* Xq, const void* x_sf, const float* row_scale, const void* Wq,
+                           const void* w_sf, float w_scale, const void* res, int M, int N, int K, long ldy, int mode,
+                           int split_k, float* workspace, int* counters, int* status, int sm_count, cudaStream_t s,
+                           const void* X16, long ldx, const void* norm_w, float eps, int out_f32) {
   if (M <= 0 || N <= 0) return 0;
   if (K % Q4_BK || (ldy % 8 && M > 64)) return -1;
   if (sm_count <= 0) sm_count = 148;
   Q4Args a;
+  a.fuseq = X16 != nullptr; a.X = (const __nv_bfloat16*)X16; a.ldx = ldx; a.norm_w = (const __nv_bfloat16*)norm_w;
+  a.eps = eps; a.out_f32 = out_f32;
+  if (a.fuseq && (M > 8 || (ldx % 8))) return -1;
+  if (out_f32 && M > 64) return -1;
   a.M = M; a.N = N; a.K = K; a.dual = mode == 1; a.swap = M <= 64;
   const int w_rows = a.dual ? 2 * N : N;
   if (a.dual && (N % 128)) return -2;                 // gate and up scale tiles must start on a 128-row tile
@@ -533,7 +678,9 @@ extern "C" int fb_gemm_nvfp4(void* Y, const void* Xq, const void* x_sf, const fl
     a.sf_a = (const uint8_t*)w_sf; a.sf_b = (const uint8_t*)x_sf;
     rc = make_tmap_u8(&tmA, Wq, (uint64_t)w_rows, (uint64_t)K / 2, Q4_BM);
     if (rc) return rc;
-    rc = make_tmap_u8(&tmB, Xq, (uint64_t)M, (uint64_t)K / 2, (uint32_t)a.b_box_rows);
+    // fused quantiser: the B tile is written by the kernel itself; the map is never used (any valid one will do)
+    rc = a.fuseq ? make_tmap_u8(&tmB, Wq, (uint64_t)w_rows, (uint64_t)K / 2, (uint32_t)a.b_box_rows)
+                 : make_tmap_u8(&tmB, Xq, (uint64_t)M, (uint64_t)K / 2, (uint32_t)a.b_box_rows);
   } else {
     a.sf_a = (const uint8_t*)x_sf; a.sf_b = (const uint8_t*)w_sf;
     rc = make_tmap_u8(&tmA, Xq, (uint64_t)M, (uint64_t)K / 2, Q4_BM);
@@ -551,6 +698,21 @@ extern "C" int fb_gemm_nvfp4(void* Y, const void* Xq, const void* x_sf, const fl
   }
   int total = a.tiles_a * a.tiles_b * a.split_k;
   int grid = total < sm_count ? total : sm_count;
-  gemm_nvfp4_kernel<<<grid, Q4_THREADS, smem, s>>>(tmA, tmB, a);
-  return (int)cudaGetLastError();
+  return (int)launch_pdl(gemm_nvfp4_kernel, dim3(grid), dim3(Q4_THREADS), smem, s, tmA, tmB, a);
+}
+
+extern "C" int fb_gemm_nvfp4(void* Y, const void* Xq, const void* x_sf, const float* row_scale, const void* Wq,
+                             const void* w_sf, float w_scale, const void* res, int M, int N, int K, long ldy, int mode,
+                             int split_k, float* workspace, int* counters, int* status, int sm_count, cudaStream_t s) {
+  return gemm_nvfp4_impl(Y, Xq, x_sf, row_scale, Wq, w_sf, w_scale, res, M, N, K, ldy, mode, split_k, workspace,
+                         counters, status, sm_count, s, nullptr, 0, nullptr, 0.f, 0);
+}
+
+// Decode form (<= 8 rows): bf16 activations in, RMSNorm + NVFP4 quantisation fused into the GEMM kernel.
+extern "C" int fb_gemm_nvfp4_fused(void* Y, const void* X, long ldx, const void* norm_w, float eps, const void* Wq,
+                                   const void* w_sf, float w_scale, const void* res, int M, int N, int K, long ldy,
+                                   int mode, int split_k, int out_f32, float* workspace, int* counters, int* status,
+                                   int sm_count, cudaStream_t s) {
+  return gemm_nvfp4_impl(Y, nullptr, nullptr, nullptr, Wq, w_sf, w_scale, res, M, N, K, ldy, mode, split_k, workspace,
+                         counters, status, sm_count, s, X, ldx, norm_w, eps, out_f32);
 }

@@ -75,9 +75,9 @@ class CudaOps:
         if isinstance(w, QWeight):
             M = x.shape[0]
             N = w.rows // 2 if swiglu else w.rows
-            if (self.fp4_act and w.mma_scales is not None and w.cols % 256 == 0 and not out_f32
+            if (self.fp4_act and w.mma_scales is not None and w.cols % 256 == 0 and (not out_f32 or M <= 8)
                     and (not swiglu or N % 128 == 0) and (M <= 64 or N % 8 == 0)):
-                return self._linear_w4a4(x, w, norm_w, eps, res, swiglu, M, N)
+                return self._linear_w4a4(x, w, norm_w, eps, res, swiglu, M, N, out_f32)
             if M <= GEMV_MAX_ROWS and not self.force_gemv_chunks:
                 N = w.rows // 2 if swiglu else w.rows
                 y = torch.empty(M, N, dtype=torch.float32 if out_f32 else self.dtype, device=self.device)
@@ -124,14 +124,21 @@ class CudaOps:
         self.C.quant_nvfp4(codes, sf, rs, x, norm_w, eps)
         return codes, sf, rs
 
-    def _linear_w4a4(self, x, w, norm_w, eps, res, swiglu, M, N):
-        xq, xsf, rs = self.quant_nvfp4(x, norm_w, eps)
-        y = torch.empty(M, N, dtype=self.dtype, device=self.device)
+    def _linear_w4a4(self, x, w, norm_w, eps, res, swiglu, M, N, out_f32=False):
         split = self._split_k(M, N, w.cols // 4) if M <= 64 else 1
         ws = cnt = None
         if split > 1:
             ws = self._workspace(int(self.C.gemm_nvfp4_workspace_bytes(M, N, split)))
             cnt = self._counters
+        if M <= GEMV_MAX_ROWS:
+            # decode rows: RMSNorm + activation quantisation happen inside the GEMM kernel
+            y = torch.empty(M, N, dtype=torch.float32 if out_f32 else self.dtype, device=self.device)
+            self.launches += 1
+            self.C.gemm_nvfp4_fused(y, x, norm_w, eps, w.packed, w.mma_scales, w.global_scale, res,
+                                    1 if swiglu else 0, split, ws, cnt, self.status_word)
+            return y
+        xq, xsf, rs = self.quant_nvfp4(x, norm_w, eps)
+        y = torch.empty(M, N, dtype=self.dtype, device=self.device)
         self.launches += 1
         self.C.gemm_nvfp4(y, xq, xsf, rs, w.packed, w.mma_scales, w.global_scale, res, 1 if swiglu else 0, split, ws,
                           cnt, self.status_word)

@@ -53,7 +53,7 @@ def test_nvfp4_engine_matches_dequantised_oracle(ext):
     """NVFP4 weights: the decode path (fp4 GEMV) and the oracle run on the same dequantised weights."""
     cfg = tiny_hybrid()
     w = init_weights(cfg, seed=0)
-    eng = Engine(cfg, w, EngineConfig(n_slots=1, max_ctx=256, weight_dtype="nvfp4"), device="cuda")
+    eng = Engine(cfg, w, EngineConfig(n_slots=1, max_ctx=256, weight_dtype="nvfp4-a16"), device="cuda")
     wq = {k: (v.dense.float().cpu() if hasattr(v, "dense") else v.float().cpu()) for k, v in eng.ex.w.items()}
     ref = RefModel(cfg, wq)
     prompt = _prompt(cfg, 20)
@@ -64,3 +64,21 @@ def test_nvfp4_engine_matches_dequantised_oracle(ext):
         err = (lg[0].cpu() - want[20 + i]).abs().max().item()
         assert err < 0.05 * want.abs().max().item() + 0.02, (i, err)
     eng.check()
+
+
+def test_nvfp4_w4a4_engine_tracks_the_16bit_activation_path(ext):
+    """Weights and activations in NVFP4 (block-scaled tcgen05 GEMM): next-token distributions stay close to the
+    NVFP4-weight / 16-bit-activation engine on the same weights (activation quantisation noise only)."""
+    cfg = scaled(hybrid_27b(), 2)
+    a = Engine(cfg, None, EngineConfig(n_slots=1, max_ctx=256, weight_dtype="nvfp4-a16"), device="cuda", seed=5)
+    b = Engine(cfg, None, EngineConfig(n_slots=1, max_ctx=256, weight_dtype="nvfp4"), device="cuda", seed=5)
+    prompt = _prompt(cfg, 40)
+    la, _, _ = a.forward([Segment(0, 0, prompt, "last")])
+    lb, _, _ = b.forward([Segment(0, 0, prompt, "last")])
+    for i in range(3):
+        la, _, _ = a.forward([Segment(0, 40 + i, [11 + i], "last")])
+        lb, _, _ = b.forward([Segment(0, 40 + i, [11 + i], "last")])
+        pa, pb = torch.log_softmax(la[0].float(), -1), torch.log_softmax(lb[0].float(), -1)
+        kl = (pa.exp() * (pa - pb)).sum().item()
+        assert kl < 0.5, kl           # random-init logits are nearly flat: quantisation noise shows up amplified
+    a.check(); b.check()

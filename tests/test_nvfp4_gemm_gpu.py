@@ -82,3 +82,30 @@ def test_gemm_nvfp4_swiglu_norm(ops, M):
     err = (got.float() - want).abs().max().item() / want.abs().max().item()
     assert err < 2e-2, err
     assert ops.status() == 0
+
+
+@pytest.mark.parametrize("M", [1, 3, 8])
+@pytest.mark.parametrize("N,K,swiglu", [(5120, 5120, False), (2048, 17408, False), (1536, 1024, True)])
+def test_gemm_nvfp4_fused_quantiser(ops, M, N, K, swiglu):
+    """Decode form: bf16 rows in, norm + quantisation inside the GEMM kernel; same result as quantise-then-GEMM."""
+    from ferrite_b200.ops.qweight import quantize_weight
+    x, nw = rnd(M, K, seed=1), rnd(K, scale=0.1, seed=4)
+    w = rnd(2 * N if swiglu else N, K, scale=0.05, seed=2)
+    q = quantize_weight(w)
+    res = None if swiglu else rnd(M, N, seed=3)
+    codes, sf, rs = ops.quant_nvfp4(x, nw, 1e-6)
+    xdq = decode_act(codes, sf, rs, M, K)
+    y = xdq @ q.dense.float().t()
+    want = torch.nn.functional.silu(y[:, :N]) * y[:, N:] if swiglu else y + res.float()
+    got = ops.linear(x, q, norm_w=nw, eps=1e-6, res=res, swiglu=swiglu)
+    err = (got.float() - want).abs().max().item() / want.abs().max().item()
+    assert err < 2e-2, err
+    if not swiglu:
+        got32 = ops.linear(x, q, norm_w=nw, eps=1e-6, out_f32=True)
+        assert got32.dtype == torch.float32
+        err = (got32 - y).abs().max().item() / y.abs().max().item()
+        assert err < 2e-2, err
+    # replays give identical bits (split-K partials are summed in split order)
+    again = ops.linear(x, q, norm_w=nw, eps=1e-6, res=res, swiglu=swiglu)
+    assert torch.equal(got, again)
+    assert ops.status() == 0
