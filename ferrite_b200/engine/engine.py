@@ -74,12 +74,24 @@ class Engine:
         self.slot_len: List[int] = [0] * self.ecfg.n_slots
 
     # ---- rows ------------------------------------------------------------------------------------
-    def forward(self, segments: Sequence[Segment], commit: bool = True, greedy: bool = True):
-        out = self.ex.forward(StepBatch(list(segments), commit=commit), greedy=greedy)
+    def forward(self, segments: Sequence[Segment], commit: bool = True, greedy: bool = True, x_add=None):
+        out = self.ex.forward(StepBatch(list(segments), commit=commit), greedy=greedy, x_add=x_add)
+        self._last_segments = list(segments)
         if commit:
             for s in segments:
                 self.slot_len[s.slot] = s.pos0 + len(s.tokens)
         return out
+
+    def commit_verified(self, keep: Sequence[int]) -> None:
+        """Accept the first keep[i] rows of every segment of the last verify step (forward with commit=False)."""
+        self.ex.commit_verified(keep)
+        for s, k in zip(self._last_segments, keep):
+            self.slot_len[s.slot] = s.pos0 + int(k)
+
+    @property
+    def taps(self):
+        """Hidden rows of the tapped layers from the last forward (inputs of the block drafter)."""
+        return self.ex.taps
 
     def check(self) -> None:
         """Raise when a kernel recorded a bounded-wait timeout or a bounds error in the status word."""

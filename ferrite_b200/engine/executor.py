@@ -114,6 +114,9 @@ class Executor:
         self._R, self._S = R, S
         self.graphs: "OrderedDict[tuple, tuple]" = OrderedDict()
         self.taps: List[torch.Tensor] = []
+        self.verify_proj: Dict[int, torch.Tensor] = {}
+        self.reclaim = None                          # callable() -> bool: free some pages (set by the scheduler)
+        self._last_meta = None
         self.profile = None
 
     # ---- sizes -----------------------------------------------------------------------------------
@@ -130,6 +133,8 @@ class Executor:
         blocks = self.slot_blocks[slot]
         changed = False
         while len(blocks) < need:
+            while self.pool.n_free == 0 and self.reclaim is not None and self.reclaim():
+                pass                                  # the scheduler evicts parked sequences to free pages
             b = self.pool.alloc()
             self.block_table_host[slot, len(blocks)] = b
             blocks.append(b)
@@ -179,6 +184,17 @@ class Executor:
         for j, b in enumerate(blocks):
             self.block_table_host[slot, j] = b
         self.block_table.copy_(self.block_table_host, non_blocking=True)
+
+    def copy_blocks(self, src_blocks: Sequence[int], dst_blocks: Sequence[int]) -> None:
+        """Copy KV pages (every attention layer) from one page list to another (shared-prefix restore, slot fork;
+        reference `kv_blocks_copy`, `crates/fe-model/src/model.rs:1846-2138`)."""
+        if not len(src_blocks):
+            return
+        s = torch.tensor(list(src_blocks), device=self.device, dtype=torch.long)
+        d = torch.tensor(list(dst_blocks), device=self.device, dtype=torch.long)
+        for i in self.k_cache:
+            self.k_cache[i][d] = self.k_cache[i][s]
+            self.v_cache[i][d] = self.v_cache[i][s]
 
     def copy_slot(self, src: int, dst: int, n_tokens: int) -> None:
         """Fork: copy KV pages covering n_tokens and the GDN state from one slot to another
@@ -262,6 +278,8 @@ class Executor:
                 proj = ops.linear(x, w[p + "in_proj"], norm_w=w[p + "input_norm"], eps=eps)
                 qkv = ops.gdn_conv(proj, w[p + "conv_w"], self.conv_state[i], mv["sslot"], mv["srow0"], mv["snrows"],
                                    c.conv_dim, **({"max_rows": max_seg_rows} if ops.name == "cuda" else {}))
+                if not commit:
+                    self.verify_proj[i] = proj           # kept so the accepted rows can be replayed into the state
                 y = ops.gdn_rec(qkv, proj, self.rec_state[i], self.conv_state[i], w[p + "A_log"], w[p + "dt_bias"],
                                 mv["sslot"], mv["srow0"], mv["snrows"], c.lin_k_heads, c.lin_v_heads, c.lin_dk,
                                 c.lin_dv, eps, commit=commit, chunked=False)
@@ -307,9 +325,12 @@ class Executor:
             return logits, (ids, finite)
         return logits, None
 
-    def _run(self, T, nseg, nlog, max_seg_rows, nsplit, commit, greedy):
+    def _run(self, T, nseg, nlog, max_seg_rows, nsplit, commit, greedy, x_add=None):
         mv = self._meta_views(T, nseg, nlog)
+        self._last_meta = (mv, max_seg_rows)
         x = self.ops.embed(self.w["embed"], mv["tok"])
+        if x_add is not None:
+            x = (x.float() + x_add.float()).to(x.dtype)      # drafter: target features fused into the input rows
         x = self._layers(x, mv, T, nseg, max_seg_rows, nsplit, commit)
         return self._head(x, mv, nlog, greedy)
 
@@ -322,7 +343,27 @@ class Executor:
         s = 1 << (s - 1).bit_length()
         return min(s, 128)
 
-    def forward(self, batch: StepBatch, greedy: bool = True):
+    def commit_verified(self, keep: Sequence[int]) -> None:
+        """After a verify step (commit=False): advance the Gated DeltaNet state of every segment by its first
+        keep[i] rows, replaying the saved projections (reference `commit_rows` / `fe_gdn_replay`,
+        `crates/fe-model/src/model.rs:2516-2606`, `kernels/k-core/src/gdn.rs:260`). KV rows past the kept ones are
+        simply overwritten by later steps."""
+        mv, max_seg_rows = self._last_meta
+        c, w, ops = self.cfg, self.w, self.ops
+        mv["snrows"].copy_(torch.tensor(list(keep), dtype=torch.int32), non_blocking=False)
+        mr = max(max(keep), 1)
+        for i, kind in enumerate(self.kinds):
+            if kind != "gdn":
+                continue
+            p = f"l{i}."
+            proj = self.verify_proj[i]
+            qkv = ops.gdn_conv(proj, w[p + "conv_w"], self.conv_state[i], mv["sslot"], mv["srow0"], mv["snrows"],
+                               c.conv_dim, **({"max_rows": mr} if ops.name == "cuda" else {}))
+            ops.gdn_rec(qkv, proj, self.rec_state[i], self.conv_state[i], w[p + "A_log"], w[p + "dt_bias"],
+                        mv["sslot"], mv["srow0"], mv["snrows"], c.lin_k_heads, c.lin_v_heads, c.lin_dk, c.lin_dv,
+                        c.eps, commit=True, chunked=False)
+
+    def forward(self, batch: StepBatch, greedy: bool = True, x_add=None):
         """Run one step. Returns (logits [n_logit_rows, vocab] fp32, (ids, finite) when greedy, logit_rows)."""
         T = batch.n_rows
         assert 0 < T <= self._R, f"{T} rows exceed max_step_rows"
@@ -331,11 +372,11 @@ class Executor:
         max_kvlen = max(s.pos0 + len(s.tokens) for s in batch.segments)
         nsplit = self.attn_splits(max_kvlen) if max_seg_rows <= FLASH_MIN_ROWS else 1
         use_graph = (self.ecfg.use_graphs and self.device.type == "cuda" and T <= self.ecfg.decode_rows_max
-                     and self.profile is None)
+                     and self.profile is None and x_add is None)
         logit_rows = self._upload(batch)
         nlog = len(logit_rows)
         if not use_graph:
-            logits, picks = self._run(T, nseg, nlog, max_seg_rows, nsplit, batch.commit, greedy)
+            logits, picks = self._run(T, nseg, nlog, max_seg_rows, nsplit, batch.commit, greedy, x_add)
             return logits, picks, logit_rows
         key = (T, nseg, nlog, max_seg_rows, nsplit, batch.commit, greedy)
         hit = self.graphs.get(key)
@@ -357,6 +398,7 @@ class Executor:
         else:
             self.graphs.move_to_end(key)
         g, (logits, picks), n_kernels = hit
+        self._last_meta = (self._meta_views(T, nseg, nlog), max_seg_rows)
         g.replay()
         self.ops.launches += n_kernels
         return logits, picks, logit_rows

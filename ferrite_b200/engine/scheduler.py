@@ -1,0 +1,496 @@
+"""Continuous-batching scheduler: admission with prompt-cache resume, decode / verify / prompt rows per step,
+token selection, commit, snapshots, guards, failure bookkeeping.
+
+Policy half of the reference's engine API (`crates/fe-model/src/sched.rs`: `Scheduler::start` `:253`, `submit` `:351`,
+`Worker::run` `:802`, `admit_inner` `:952-1097`, `step` `:1099-1839`, `prompt_cut` `:636`, `tree_walk` `:125`,
+`cache_save` `:1888`, `park_slot` `:1963`, `finish` `:2059`). Differences: no fixed cap of 4 requests (any number of
+slots), paged KV so parking moves page ids instead of copying, and drafts are verified as chains.
+
+One engine thread owns the device. `submit()` may be called from any thread; events go to the request's sink.
+"""
+from __future__ import annotations
+
+import itertools
+import os
+import queue
+import threading
+import time
+import traceback
+from dataclasses import dataclass, field
+from typing import Callable, Dict, List, Optional, Sequence
+
+import torch
+
+from .copy import Copier
+from .engine import Engine, prompt_cuts
+from .executor import Segment
+from .pcache import PREFIX_MIN, Park, SlotCache, Snap, common_prefix
+from .sampler import Sampler, Sampling
+
+STEP_FAILS_FATAL = 3      # consecutive failed steps that kill the engine (reference STEP_FAILS_FATAL)
+DECODE_ROWS = 16          # most rows a request contributes to a verify segment (1 + drafts)
+
+
+@dataclass
+class SchedOptions:
+    """Reference `SchedOptions` (`sched.rs:14-48`): FE_SPEC draft depth, FE_POOL park entries, FE_BATCH_ROWS."""
+
+    spec: int = 0                      # draft tokens per step (0 = plain decoding)
+    copy_rows: bool = True             # context-copy proposals
+    pool: int = 64                     # parked entries kept
+    batch_rows: int = 2048             # prompt rows per step
+    finite_check: bool = True
+    step_timeout_s: float = 120.0
+    prof: int = 0                      # 1: one line per step on stderr
+
+    @staticmethod
+    def from_env() -> "SchedOptions":
+        e = os.environ
+        return SchedOptions(spec=int(e.get("FE_SPEC", "0")), pool=int(e.get("FE_POOL", "64")),
+                            batch_rows=int(e.get("FE_BATCH_ROWS", "2048")),
+                            finite_check=e.get("FE_FINITE_CHECK", "1") != "0",
+                            step_timeout_s=float(e.get("FE_STEP_TIMEOUT", "120")), prof=int(e.get("FE_SCHED_PROF", "0")))
+
+
+@dataclass
+class Event:
+    kind: str                          # "tokens" | "finish" | "error"
+    tokens: List[int] = field(default_factory=list)
+    reason: str = ""                   # finish: "stop" | "length" | "cancelled" | "error" | "guard"
+    timings: Dict[str, float] = field(default_factory=dict)
+    message: str = ""
+
+
+@dataclass
+class Request:
+    prompt: List[int]
+    sampling: Sampling = field(default_factory=Sampling)
+    sink: Optional[Callable[[Event], None]] = None
+    snapshots: List[int] = field(default_factory=list)     # prompt positions worth a snapshot (template boundaries)
+    cancel: threading.Event = field(default_factory=threading.Event)
+    guard: Optional[Callable[[List[int]], Optional[str]]] = None   # called with new tokens; returns a finish reason
+    rid: int = 0
+
+
+@dataclass
+class Active:
+    req: Request
+    slot: int
+    pos: int                           # tokens whose state is in the slot
+    pending: List[int]                 # prompt tokens not yet run
+    sampler: Sampler
+    copier: Optional[Copier]
+    out: List[int] = field(default_factory=list)
+    next_token: Optional[int] = None   # token to feed in the next decode row
+    cached: int = 0                    # prompt tokens reused from the cache
+    t_submit: float = 0.0
+    t_first: float = 0.0
+    t_prompt_done: float = 0.0
+    drafts_proposed: int = 0
+    drafts_accepted: int = 0
+    snap_at: List[int] = field(default_factory=list)
+
+
+class Drafter:
+    """Plug-in interface of a draft model (reference trait `Drafter`, `sched.rs:58-116`)."""
+
+    def draft(self, slot: int, last_token: int, pos: int, taps, n: int) -> List[int]:
+        return []
+
+    def absorb(self, slot: int, tokens: Sequence[int], pos0: int, taps) -> None:
+        pass
+
+    def reset(self, slot: int) -> None:
+        pass
+
+    def save_window(self, slot: int):
+        return None
+
+    def restore_window(self, slot: int, blob) -> None:
+        pass
+
+
+class Scheduler:
+    def __init__(self, engine: Engine, opts: Optional[SchedOptions] = None, drafter: Optional[Drafter] = None):
+        self.eng = engine
+        self.opts = opts or SchedOptions()
+        self.drafter = drafter
+        n = engine.ecfg.n_slots
+        self.free: List[int] = list(range(n))
+        self.slot_cache: List[SlotCache] = [SlotCache() for _ in range(n)]
+        self.active: Dict[int, Active] = {}
+        self.waiting: "queue.Queue[Request]" = queue.Queue()
+        self.backlog: List[Request] = []
+        self.park = Park(self.opts.pool)
+        self._ids = itertools.count(1)
+        self._thread: Optional[threading.Thread] = None
+        self._stop = threading.Event()
+        self.dead_reason: Optional[str] = None
+        self.step_no = 0
+        self.fails = 0
+        self.step_started = 0.0
+        self.stats = {"steps": 0, "tokens": 0, "prompt_tokens": 0, "cached_tokens": 0, "drafted": 0, "accepted": 0}
+        self.panic_step = int(os.environ.get("FE_TEST_PANIC_STEP", "0"))     # fault injection (host side only)
+        self.eng.ex.reclaim = self._reclaim
+
+    # ---- public ------------------------------------------------------------------------------------
+    def submit(self, req: Request) -> int:
+        req.rid = next(self._ids)
+        self.waiting.put(req)
+        return req.rid
+
+    def start(self) -> None:
+        self._thread = threading.Thread(target=self._run, name="ferrite-engine", daemon=True)
+        self._thread.start()
+
+    def stop(self) -> None:
+        self._stop.set()
+        if self._thread:
+            self._thread.join(timeout=10)
+
+    def dead(self) -> Optional[str]:
+        """Reason the engine is unusable: an unrecoverable step error, or a step running past the timeout."""
+        if self.dead_reason:
+            return self.dead_reason
+        if self.step_started and time.time() - self.step_started > self.opts.step_timeout_s:
+            return f"step {self.step_no} has been running for more than {self.opts.step_timeout_s:.0f} s"
+        return None
+
+    @property
+    def running(self) -> int:
+        return len(self.active)
+
+    @property
+    def queued(self) -> int:
+        return self.waiting.qsize() + len(self.backlog)
+
+    # ---- engine thread -----------------------------------------------------------------------------
+    def _run(self) -> None:
+        while not self._stop.is_set():
+            try:
+                busy = self.run_once(block=True)
+                if not busy:
+                    continue
+            except Exception as e:                                  # noqa: BLE001
+                self.dead_reason = f"engine thread died: {e!r}"
+                traceback.print_exc()
+                for a in list(self.active.values()):
+                    self._emit(a, Event("error", message=self.dead_reason))
+                return
+
+    def run_once(self, block: bool = False) -> bool:
+        """Drain arrivals, admit, run one step. Returns False when idle. Tests drive the scheduler with this."""
+        self._drain(block and not self.active and not self.backlog)
+        self._admit()
+        if not self.active:
+            return False
+        self.step_no += 1
+        if self.panic_step and self.step_no == self.panic_step:
+            raise RuntimeError("injected panic (FE_TEST_PANIC_STEP)")
+        self.step_started = time.time()
+        try:
+            self._step()
+            self.fails = 0
+        except Exception as e:                                      # noqa: BLE001
+            self.fails += 1
+            if self.fails >= STEP_FAILS_FATAL:
+                self.step_started = 0.0
+                raise
+            for a in list(self.active.values()):                    # fail the requests of this step, keep serving
+                self._finish(a, "error", message=repr(e))
+        self.step_started = 0.0
+        self.stats["steps"] += 1
+        return True
+
+    def _drain(self, block: bool) -> None:
+        try:
+            if block:
+                self.backlog.append(self.waiting.get(timeout=0.05))
+            while True:
+                self.backlog.append(self.waiting.get_nowait())
+        except queue.Empty:
+            pass
+
+    # ---- admission ----------------------------------------------------------------------------------
+    def _pick_slot(self, prompt: Sequence[int]) -> Optional[int]:
+        """Free slot with the longest resumable prefix of this prompt (reference `admit_inner`)."""
+        if not self.free:
+            return None
+        best, best_pos = self.free[0], -1
+        for s in self.free:
+            snap = self.slot_cache[s].best_snap(prompt)
+            p = snap.pos if snap else (0 if self.slot_cache[s].tokens else -1)
+            if p > best_pos:
+                best, best_pos = s, p
+        return best
+
+    def _park_slot(self, slot: int) -> None:
+        """Move a finished slot's pages and snapshots to the parked pool so the slot can take another sequence."""
+        sc = self.slot_cache[slot]
+        if sc.snaps:
+            last = max(s.pos for s in sc.snaps)
+            blocks = self.eng.ex.detach_blocks(slot, last)
+            while len(self.park) >= self.opts.pool and self._reclaim():
+                pass
+            self.park.add(sc.tokens[:last], [s for s in sc.snaps if s.pos <= last], blocks)
+        self.eng.reset_slot(slot)
+        sc.clear()
+
+    def _reclaim(self) -> bool:
+        """Evict the least recently used parked sequence and return its pages to the pool."""
+        ev = self.park.evict_lru()
+        if ev is None:
+            return False
+        self.eng.ex.pool.release(ev.blocks)
+        return True
+
+    def _admit(self) -> None:
+        while self.backlog and self.free:
+            req = self.backlog.pop(0)
+            if req.cancel.is_set():
+                if req.sink:
+                    req.sink(Event("finish", reason="cancelled"))
+                continue
+            slot = self._pick_slot(req.prompt)
+            self.free.remove(slot)
+            sc = self.slot_cache[slot]
+            snap = sc.best_snap(req.prompt)
+            pe, ps = self.park.best(req.prompt)
+            resume = 0
+            if ps is not None and (snap is None or ps.pos > snap.pos):
+                # restore a parked sequence into this slot: move (exclusive) or copy (shared) its pages
+                if not pe.shared:
+                    self.park.take(pe)                 # out of the pool first, so parking this slot cannot evict it
+                self._park_slot(slot) if sc.tokens else self.eng.reset_slot(slot)
+                nb = (ps.pos + self.eng.ecfg.kv_block - 1) // self.eng.ecfg.kv_block
+                if pe.shared:
+                    self.eng.ex.ensure_capacity(slot, ps.pos)
+                    self.eng.ex.copy_blocks(pe.blocks[:nb], self.eng.ex.slot_blocks[slot][:nb])
+                    self.park.touch(pe)
+                else:
+                    self.eng.ex.attach_blocks(slot, pe.blocks[:nb])
+                    self.eng.ex.pool.release(pe.blocks[nb:])
+                self.eng.ex.state_restore(slot, ps.state["gdn"])
+                if self.drafter:
+                    self.drafter.restore_window(slot, ps.state.get("draft"))
+                sc.tokens, sc.snaps = list(pe.tokens[:ps.pos]), [s for s in pe.snaps if s.pos <= ps.pos]
+                resume = ps.pos
+            elif snap is not None:
+                self.eng.ex.state_restore(slot, snap.state["gdn"])
+                if self.drafter:
+                    self.drafter.restore_window(slot, snap.state.get("draft"))
+                sc.truncate(snap.pos)
+                resume = snap.pos
+            else:
+                if sc.tokens:
+                    self._park_slot(slot)
+                else:
+                    self.eng.reset_slot(slot)
+                if self.drafter:
+                    self.drafter.reset(slot)
+            self.eng.slot_len[slot] = resume
+            a = Active(req, slot, resume, list(req.prompt[resume:]), Sampler(req.sampling, request_seed=req.rid),
+                       Copier() if (self.opts.copy_rows and self.opts.spec > 0) else None, cached=resume,
+                       t_submit=time.time(), snap_at=sorted(p for p in req.snapshots if resume < p <= len(req.prompt)))
+            self.active[slot] = a
+            self.stats["cached_tokens"] += resume
+
+    # ---- one step -----------------------------------------------------------------------------------
+    def _step(self) -> None:
+        t0 = time.time()
+        for a in list(self.active.values()):
+            if a.req.cancel.is_set():
+                self._finish(a, "cancelled")
+        decoders = [a for a in self.active.values() if not a.pending and a.next_token is not None]
+        prefills = [a for a in self.active.values() if a.pending]
+        n_dec = n_pre = 0
+        if decoders:
+            n_dec = self._decode_step(decoders)
+        budget = self.opts.batch_rows
+        for a in prefills:                                # short remainders first (reference: short chunks first)
+            if budget <= 0:
+                break
+            n_pre += self._prefill_step(a, budget)
+            budget -= n_pre
+        if self.opts.prof:
+            import sys
+            print(f"step {self.step_no}: dec {n_dec} rows, prompt {n_pre} rows, {1e3 * (time.time() - t0):.2f} ms",
+                  file=sys.stderr)
+
+    def _prefill_step(self, a: Active, budget: int) -> int:
+        """Run the next chunk of a prompt. Chunks end at snapshot positions so the state can be saved there."""
+        cut = prompt_cuts(len(a.pending), min(self.eng.ecfg.prefill_chunk, max(32, budget)), self.eng.ecfg.prompt_align)[0]
+        for sp in a.snap_at:
+            if a.pos < sp < a.pos + cut:
+                cut = sp - a.pos
+                break
+        toks = a.pending[:cut]
+        last = cut == len(a.pending)
+        greedy = a.req.sampling.greedy and not a.req.sampling.banned_first
+        logits, picks, _ = self.eng.forward([Segment(a.slot, a.pos, toks, "last" if last else "none")], greedy=greedy)
+        a.pos += cut
+        a.pending = a.pending[cut:]
+        self.slot_cache[a.slot].tokens = a.req.prompt[:a.pos]
+        self.stats["prompt_tokens"] += cut
+        if a.pos in a.snap_at:
+            self._snapshot(a, pinned=(a.pos == a.snap_at[0]))
+        if self.drafter:
+            self.drafter.absorb(a.slot, toks, a.pos - cut, self.eng.taps)
+        if last:
+            a.t_prompt_done = time.time()
+            tok = int(picks[0][0]) if greedy else a.sampler.sample(logits[0], first=True)
+            if self.opts.finite_check and not bool(torch.isfinite(logits[0]).all()):
+                self._finish(a, "error", message="non-finite logits")
+                return cut
+            self._accept(a, [tok])
+        return cut
+
+    def _decode_step(self, decoders: List[Active]) -> int:
+        """One decode / verify step over all decoding requests: a row per request plus its draft rows."""
+        segs, drafts = [], []
+        for a in decoders:
+            d: List[int] = []
+            if self.opts.spec > 0:
+                room = min(self.opts.spec, DECODE_ROWS - 1, a.req.sampling.max_tokens - len(a.out) - 1,
+                           self.eng.ecfg.max_ctx - a.pos - 2)
+                if room > 0:
+                    if a.copier is not None:
+                        a.copier.sync(a.req.prompt + a.out[:-1] + [a.next_token])
+                        d = a.copier.propose(room)
+                    if not d and self.drafter is not None:
+                        d = self.drafter.draft(a.slot, a.next_token, a.pos, self.eng.taps, room)
+                    d = [int(t) for t in d[:room]]
+            drafts.append(d)
+            segs.append(Segment(a.slot, a.pos, [a.next_token] + d, "all"))
+        spec = any(drafts)
+        all_greedy = all(a.req.sampling.greedy for a in decoders)
+        logits, picks, rows = self.eng.forward(segs, commit=not spec, greedy=all_greedy)
+        ids = picks[0].tolist() if all_greedy else None
+        if self.opts.finite_check:
+            finite = bool(picks[1].all()) if all_greedy else bool(torch.isfinite(logits).all())
+            if not finite:
+                for a in decoders:
+                    self._finish(a, "error", message="non-finite logits")
+                return len(rows)
+        keep, r = [], 0
+        taps = self.eng.taps
+        for a, d in zip(decoders, drafts):
+            n = 1 + len(d)
+            if all_greedy:
+                # accept-while-match walk over the chain (reference `tree_walk` on a path)
+                new = []
+                for i in range(n):
+                    t = int(ids[r + i])
+                    new.append(t)
+                    if i < len(d) and t != d[i]:
+                        break
+            else:
+                new = a.sampler.spec_accept(logits[r:r + n], d)
+            acc = len(new) - 1
+            keep.append(len(new))
+            a.drafts_proposed += len(d)
+            a.drafts_accepted += acc
+            self.stats["drafted"] += len(d)
+            self.stats["accepted"] += acc
+            if a.copier is not None:
+                a.copier.observe(len(d), acc)
+            fed = [a.next_token] + d[:acc]
+            a.pos += len(new)
+            if self.drafter is not None:
+                self.drafter.absorb(a.slot, fed, a.pos - len(new), [t[r:r + len(new)] for t in taps])
+            self._accept(a, new, sampled=not all_greedy)
+            r += n
+        if spec:
+            self.eng.commit_verified(keep)
+        return len(rows)
+
+    # ---- bookkeeping --------------------------------------------------------------------------------
+    def _snapshot(self, a: Active, pinned: bool = False) -> None:
+        state = {"gdn": self.eng.ex.state_save(a.slot)}
+        if self.drafter:
+            state["draft"] = self.drafter.save_window(a.slot)
+        self.slot_cache[a.slot].push(Snap(a.pos, state, pinned))
+
+    def _accept(self, a: Active, toks: List[int], sampled: bool = False) -> None:
+        """Record newly chosen tokens: emit them, detect stop / length / guard, set the next input token."""
+        if a.slot not in self.active:
+            return
+        if not a.t_first:
+            a.t_first = time.time()
+        emit: List[int] = []
+        reason = None
+        for t in toks:
+            if not sampled:
+                a.sampler.observe(t)                  # (speculative sampling already counted its own tokens)
+            if t in a.req.sampling.stop_ids:
+                reason = "stop"
+                break
+            emit.append(t)
+            a.out.append(t)
+            if len(a.out) >= a.req.sampling.max_tokens:
+                reason = "length"
+                break
+        if emit:
+            self.stats["tokens"] += len(emit)
+            self._emit(a, Event("tokens", tokens=emit))
+            if a.req.guard is not None and reason is None:
+                g = a.req.guard(emit)
+                if g:
+                    reason = g
+        if reason:
+            self._finish(a, reason)
+        else:
+            a.next_token = toks[-1]
+            self.slot_cache[a.slot].tokens = a.req.prompt + a.out[:-1]
+
+    def _emit(self, a: Active, ev: Event) -> None:
+        if a.req.sink:
+            try:
+                a.req.sink(ev)
+            except Exception:                                       # a closed stream cancels the request
+                a.req.cancel.set()
+
+    def _finish(self, a: Active, reason: str, message: str = "") -> None:
+        if a.slot not in self.active:
+            return
+        now = time.time()
+        timings = {
+            "prompt_n": len(a.req.prompt) - a.cached, "cache_n": a.cached,
+            "prompt_ms": 1e3 * ((a.t_prompt_done or now) - a.t_submit),
+            "predicted_n": len(a.out), "predicted_ms": 1e3 * (now - (a.t_prompt_done or now)),
+            "draft_n": a.drafts_proposed, "draft_accepted_n": a.drafts_accepted,
+        }
+        # the slot keeps its sequence for a later turn; a snapshot at the end of the reply makes it resumable
+        if reason in ("stop", "length") and a.next_token is not None:
+            sc = self.slot_cache[a.slot]
+            sc.tokens = (a.req.prompt + a.out)[:a.pos]
+            self._snapshot(a)
+        del self.active[a.slot]
+        self.free.append(a.slot)
+        kind = "error" if reason == "error" else "finish"
+        self._emit(a, Event(kind, reason=reason, timings=timings, message=message))
+
+
+def generate(sched: Scheduler, prompts: Sequence[Sequence[int]], sampling: Optional[Sampling] = None,
+             snapshots: Optional[Sequence[Sequence[int]]] = None) -> List[List[int]]:
+    """Synchronous helper: run prompts to completion through the scheduler (single-threaded stepping)."""
+    outs: List[List[int]] = [[] for _ in prompts]
+    done = [False] * len(prompts)
+
+    def sink(i):
+        def f(ev: Event):
+            if ev.kind == "tokens":
+                outs[i].extend(ev.tokens)
+            else:
+                done[i] = True
+        return f
+
+    for i, p in enumerate(prompts):
+        sched.submit(Request(list(p), sampling or Sampling(), sink(i),
+                             snapshots=list(snapshots[i]) if snapshots else []))
+    guard = 0
+    while not all(done):
+        sched.run_once()
+        guard += 1
+        assert guard < 100000, "scheduler made no progress"
+    return outs

@@ -1,0 +1,74 @@
+"""Block drafter for speculative decoding: a small attention-only decoder conditioned on hidden states tapped
+from the target model, drafting a block of tokens in one forward pass.
+
+Shape of the reference's DFlash2 drafter (`crates/fe-dflash/src/lib.rs`: 5 Qwen3-style layers, hidden 5120, 32Q/8KV
+heads of 128, FFN 17408, reads feature taps of the target, block 16, draft window ring). Here it is an `Engine`
+over an attention-only `ModelConfig`, plus one fusion matrix that maps the concatenated taps of the last committed
+row into the drafter's input space. A block is drafted by feeding [last token, MASK x (n-1)] at the next n positions
+(causal inside the block) with the fused features added to every row; row j predicts draft token j+1. Kept rows are
+absorbed into the drafter's own KV cache with the features of the rows they came from.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence
+
+import torch
+
+from ..config import EngineConfig, ModelConfig
+from ..engine.engine import Engine
+from ..engine.executor import Segment
+from ..engine.scheduler import Drafter
+
+
+class BlockDrafter(Drafter):
+    def __init__(self, cfg: ModelConfig, target_hidden: int, n_taps: int, n_slots: int, max_ctx: int,
+                 device: Optional[str] = None, seed: int = 1, block: int = 16, weights=None, mask_token: int = 0):
+        ecfg = EngineConfig(n_slots=n_slots, max_ctx=max_ctx, use_graphs=False)
+        self.eng = Engine(cfg, weights, ecfg, device=device, seed=seed)
+        self.block = block
+        self.mask_token = mask_token
+        g = torch.Generator().manual_seed(seed + 17)
+        self.n_taps = n_taps
+        self.fuse = (torch.randn(cfg.hidden, n_taps * target_hidden, generator=g) * 0.02).to(self.eng.device, self.eng.dtype)
+        self.last_feat = [None] * n_slots            # fused features of the last committed row of each slot
+
+    def _fused(self, taps, rows: slice) -> Optional[torch.Tensor]:
+        if not taps or self.n_taps == 0:
+            return None
+        cat = torch.cat([t[rows].to(self.eng.device, self.eng.dtype) for t in taps[:self.n_taps]], -1)
+        return (cat.float() @ self.fuse.float().t()).to(self.eng.dtype)
+
+    def reset(self, slot: int) -> None:
+        self.eng.reset_slot(slot)
+        self.last_feat[slot] = None
+
+    def absorb(self, slot: int, tokens: Sequence[int], pos0: int, taps) -> None:
+        """Extend the drafter's cache with committed tokens and the target features of their rows."""
+        n = len(tokens)
+        if n == 0:
+            return
+        feat = self._fused(taps, slice(0, n)) if taps and taps[0].shape[0] >= n else None
+        self.eng.forward([Segment(slot, pos0, list(tokens), "none")], commit=True, x_add=feat)
+        if feat is not None:
+            self.last_feat[slot] = feat[-1:].clone()
+
+    def draft(self, slot: int, last_token: int, pos: int, taps, n: int) -> List[int]:
+        n = min(n, self.block)
+        if n <= 0:
+            return []
+        toks = [last_token] + [self.mask_token] * (n - 1)
+        feat = self.last_feat[slot]
+        x_add = feat.expand(n, -1).contiguous() if feat is not None else None
+        _, picks, _ = self.eng.forward([Segment(slot, pos, toks, "all")], commit=False, greedy=True, x_add=x_add)
+        return [int(t) for t in picks[0].tolist()]
+
+    def save_window(self, slot: int):
+        return {"len": self.eng.slot_len[slot], "feat": self.last_feat[slot]}
+
+    def restore_window(self, slot: int, blob) -> None:
+        # the drafter's KV rows up to the snapshot position are still in its slot; only the length rolls back
+        if blob is None:
+            self.reset(slot)
+            return
+        self.eng.slot_len[slot] = min(self.eng.slot_len[slot], blob["len"])
+        self.last_feat[slot] = blob["feat"]

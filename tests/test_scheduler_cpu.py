@@ -1,0 +1,192 @@
+"""Scheduler policy on the CPU engine: continuous batching, prompt-cache resume, parking, speculation, sampling,
+fault bookkeeping. Every comparison is against plain single-request greedy decoding of the same tiny model."""
+import torch
+
+from ferrite_b200.config import EngineConfig, ModelConfig, tiny_hybrid
+from ferrite_b200.engine.copy import Copier
+from ferrite_b200.engine.engine import Engine
+from ferrite_b200.engine.pcache import Park, SlotCache, Snap, common_prefix
+from ferrite_b200.engine.sampler import Sampler, Sampling, SplitMix64, dist
+from ferrite_b200.engine.scheduler import Event, Request, SchedOptions, Scheduler, generate
+from ferrite_b200.models.weights import init_weights
+
+
+def _engine(n_slots=2, max_ctx=256, chunk=32):
+    cfg = tiny_hybrid()
+    w = init_weights(cfg, seed=0)
+    return cfg, w, Engine(cfg, w, EngineConfig(n_slots=n_slots, max_ctx=max_ctx, prefill_chunk=chunk), device="cpu")
+
+
+def _prompt(cfg, n, seed):
+    return torch.randint(0, cfg.vocab, (n,), generator=torch.Generator().manual_seed(seed)).tolist()
+
+
+def _plain(cfg, w, prompt, n):
+    return Engine(cfg, w, EngineConfig(n_slots=1, max_ctx=256), device="cpu").generate(prompt, n)
+
+
+def test_batched_requests_equal_single_greedy():
+    cfg, w, eng = _engine(n_slots=2)
+    prompts = [_prompt(cfg, 20, 1), _prompt(cfg, 45, 2), _prompt(cfg, 7, 3)]       # 3 requests on 2 slots
+    outs = generate(Scheduler(eng), prompts, Sampling(max_tokens=12))
+    for p, o in zip(prompts, outs):
+        assert o == _plain(cfg, w, p, 12)
+
+
+def test_prompt_cache_resume_is_exact_and_counts_cached_tokens():
+    cfg, w, eng = _engine(n_slots=1)
+    sched = Scheduler(eng)
+    system = _prompt(cfg, 40, 5)
+    turn1 = system + _prompt(cfg, 10, 6)
+    o1 = generate(sched, [turn1], Sampling(max_tokens=8), snapshots=[[40, len(turn1)]])[0]
+    turn2 = turn1 + o1 + _prompt(cfg, 9, 7)
+    o2 = generate(sched, [turn2], Sampling(max_tokens=8), snapshots=[[40, len(turn2)]])[0]
+    assert sched.stats["cached_tokens"] >= len(turn1)            # second turn resumed past the first prompt
+    assert o2 == _plain(cfg, w, turn2, 8)
+    # a different conversation sharing only the system prompt resumes at the pinned system snapshot
+    other = system + _prompt(cfg, 12, 8)
+    before = sched.stats["cached_tokens"]
+    o3 = generate(sched, [other], Sampling(max_tokens=6), snapshots=[[40]])[0]
+    assert sched.stats["cached_tokens"] - before == 40
+    assert o3 == _plain(cfg, w, other, 6)
+
+
+def test_parked_sequence_is_restored_into_another_slot():
+    cfg, w, eng = _engine(n_slots=1)
+    sched = Scheduler(eng)
+    a = _prompt(cfg, 70, 11)
+    generate(sched, [a], Sampling(max_tokens=4), snapshots=[[64]])
+    b = _prompt(cfg, 30, 12)
+    generate(sched, [b], Sampling(max_tokens=4))                  # evicts a's sequence to the park pool
+    assert len(sched.park) >= 1
+    before = sched.stats["cached_tokens"]
+    a2 = a + _prompt(cfg, 5, 13)
+    out = generate(sched, [a2], Sampling(max_tokens=6))[0]
+    assert sched.stats["cached_tokens"] - before == 64            # resumed from the parked snapshot (page move)
+    assert out == _plain(cfg, w, a2, 6)
+
+
+def test_copy_speculation_keeps_greedy_output():
+    cfg, w, eng = _engine(n_slots=2)
+    span = _prompt(cfg, 12, 21)
+    prompt = span * 5                                             # repeated spans: the copier has proposals
+    sched = Scheduler(eng, SchedOptions(spec=8))
+    out = generate(sched, [prompt, _prompt(cfg, 18, 22)], Sampling(max_tokens=16))
+    assert out[0] == _plain(cfg, w, prompt, 16)
+    assert out[1] == _plain(cfg, w, _prompt(cfg, 18, 22), 16)
+    assert sched.stats["drafted"] > 0
+
+
+def test_block_drafter_keeps_greedy_output():
+    from ferrite_b200.models.drafter import BlockDrafter
+    cfg, w, eng = _engine(n_slots=1)
+    cfg.tap_layers = [1, 3]
+    eng.cfg.tap_layers = [1, 3]
+    eng.ex.cfg.tap_layers = [1, 3]
+    dcfg = ModelConfig(name="tiny-drafter", hidden=128, inter=256, n_layers=2, full_attn_every=1, head_dim=32, n_q=4,
+                       n_kv=2, rotary_dim=32, attn_gate=False, vocab=cfg.vocab, tie_embeddings=True)
+    dr = BlockDrafter(dcfg, target_hidden=cfg.hidden, n_taps=2, n_slots=1, max_ctx=256, device="cpu", block=6)
+    sched = Scheduler(eng, SchedOptions(spec=6, copy_rows=False), drafter=dr)
+    prompt = _prompt(cfg, 25, 31)
+    out = generate(sched, [prompt], Sampling(max_tokens=14))[0]
+    assert out == _plain(cfg, w, prompt, 14)
+    assert sched.stats["drafted"] > 0
+
+
+def test_sampling_is_seeded_and_respects_filters():
+    cfg, w, eng = _engine(n_slots=1)
+    sched = Scheduler(eng)
+    p = _prompt(cfg, 16, 41)
+    s = Sampling(temperature=0.9, top_k=20, top_p=0.95, seed=123, max_tokens=10)
+    a = generate(sched, [p], s)[0]
+    b = generate(sched, [p], s)[0]
+    assert a == b and len(a) == 10
+    lg = torch.randn(500, generator=torch.Generator().manual_seed(0))
+    pr = dist(lg, Sampling(temperature=1.0, top_k=7))
+    assert int((pr > 0).sum()) == 7 and abs(float(pr.sum()) - 1) < 1e-6
+    pr = dist(lg, Sampling(temperature=1.0, top_p=0.5))
+    sp = torch.sort(torch.softmax(lg, -1), descending=True).values
+    k = int((torch.cumsum(sp, 0) < 0.5).sum()) + 1
+    assert int((pr > 0).sum()) == k
+    pr = dist(lg, Sampling(temperature=1.0, min_p=0.2))
+    sm = torch.softmax(lg, -1)
+    assert int((pr > 0).sum()) == int((sm >= 0.2 * sm.max()).sum())
+
+
+def test_speculative_sampling_preserves_the_distribution():
+    """Point-mass drafts accepted with probability p(draft), replaced from p \\ {draft} otherwise: first-token
+    frequencies match the target distribution."""
+    lg = torch.tensor([[2.0, 1.0, 0.5, 0.0, -1.0]] * 2)
+    want = torch.softmax(lg[0], -1)
+    counts = torch.zeros(5)
+    for seed in range(4000):
+        s = Sampler(Sampling(temperature=1.0, seed=seed))
+        counts[s.spec_accept(lg, [1])[0]] += 1
+    assert torch.allclose(counts / counts.sum(), want, atol=0.03)
+
+
+def test_stop_token_and_cancel_and_guard():
+    cfg, w, eng = _engine(n_slots=1)
+    p = _prompt(cfg, 10, 51)
+    ref = _plain(cfg, w, p, 8)
+    sched = Scheduler(eng)
+    out = generate(sched, [p], Sampling(max_tokens=8, stop_ids=[ref[3]]))[0]
+    assert out == ref[:ref.index(ref[3])]
+    events = []
+    req = Request(p, Sampling(max_tokens=50), events.append, guard=lambda toks: "guard" if len(events) >= 3 else None)
+    sched.submit(req)
+    while not any(e.kind == "finish" for e in events):
+        sched.run_once()
+    assert events[-1].reason == "guard"
+    events2 = []
+    req2 = Request(p, Sampling(max_tokens=50), events2.append)
+    sched.submit(req2)
+    sched.run_once(); sched.run_once()
+    req2.cancel.set()
+    while not any(e.kind == "finish" for e in events2):
+        sched.run_once()
+    assert events2[-1].reason == "cancelled" and sched.running == 0 and len(sched.free) == 1
+
+
+def test_step_failures_kill_the_engine_after_three(monkeypatch):
+    cfg, w, eng = _engine(n_slots=1)
+    sched = Scheduler(eng)
+    calls = {"n": 0}
+
+    def boom(*a, **k):
+        calls["n"] += 1
+        raise RuntimeError("injected step failure")
+
+    monkeypatch.setattr(eng, "forward", boom)
+    died = False
+    for i in range(3):
+        evs = []
+        sched.submit(Request(_prompt(cfg, 5, 60 + i), Sampling(max_tokens=3), evs.append))
+        try:
+            sched.run_once()
+        except RuntimeError:
+            died = True
+            break
+        assert evs and evs[-1].kind == "error"                   # the request fails, the engine keeps serving
+    assert died and calls["n"] == 3
+
+
+def test_pcache_structures():
+    sc = SlotCache(tokens=list(range(50)))
+    for p in (10, 20, 30, 40):
+        sc.push(Snap(p, None, pinned=(p == 10)))
+    assert [s.pos for s in sc.snaps] == [10, 30, 40]              # pinned first + KEEP_LAST 2
+    assert sc.best_snap(list(range(35)) + [99]).pos == 30
+    assert sc.best_snap(list(range(30))).pos == 10                # a snapshot at len(prompt) leaves nothing to run
+    sc.truncate(30)
+    assert [s.pos for s in sc.snaps] == [10, 30] and len(sc.tokens) == 30
+    park = Park(4)
+    park.add(list(range(100)), [Snap(64, None)], [1, 2])
+    e, s = park.best(list(range(80)))
+    assert s.pos == 64 and park.has_prefix(list(range(80)), 64) and not park.has_prefix([5, 6, 7], 1)
+    assert common_prefix([1, 2, 3], [1, 2, 4]) == 2
+    c = Copier()
+    c.sync(list(range(30)) + list(range(10, 17)))
+    assert c.propose(4) == [17, 18, 19, 20]
+    r = SplitMix64(7)
+    assert 0 <= r.uniform() < 1
