@@ -326,11 +326,11 @@ class Scheduler:
                 break
         toks = a.pending[:cut]
         last = cut == len(a.pending)
-        greedy = a.req.sampling.greedy and not a.req.sampling.banned_first
+        greedy = a.req.sampling.greedy and not (a.req.sampling.banned_first and not a.out)
         logits, picks, _ = self.eng.forward([Segment(a.slot, a.pos, toks, "last" if last else "none")], greedy=greedy)
         a.pos += cut
         a.pending = a.pending[cut:]
-        self.slot_cache[a.slot].tokens = a.req.prompt[:a.pos]
+        self.slot_cache[a.slot].tokens = (a.req.prompt + a.out)[:a.pos]
         self.stats["prompt_tokens"] += cut
         if a.pos in a.snap_at:
             self._snapshot(a, pinned=(a.pos == a.snap_at[0]))
@@ -338,7 +338,7 @@ class Scheduler:
             self.drafter.absorb(a.slot, toks, a.pos - cut, self.eng.taps)
         if last:
             a.t_prompt_done = time.time()
-            tok = int(picks[0][0]) if greedy else a.sampler.sample(logits[0], first=True)
+            tok = int(picks[0][0]) if greedy else a.sampler.sample(logits[0], first=not a.out)
             if self.opts.finite_check and not bool(torch.isfinite(logits[0]).all()):
                 self._finish(a, "error", message="non-finite logits")
                 return cut
@@ -435,6 +435,15 @@ class Scheduler:
             self._emit(a, Event("tokens", tokens=emit))
             if a.req.guard is not None and reason is None:
                 g = a.req.guard(emit)
+                if isinstance(g, (list, tuple)) and g:
+                    # forced continuation (e.g. the closing tag of a capped reasoning block): the tokens become part
+                    # of the reply and are run through the slot like prompt rows before sampling resumes
+                    forced = [int(t) for t in g]
+                    a.out.extend(forced)
+                    self._emit(a, Event("tokens", tokens=forced))
+                    a.pending = [toks[-1]] + forced
+                    a.next_token = None
+                    return
                 if g:
                     reason = g
         if reason:

@@ -1,0 +1,95 @@
+"""`python -m ferrite_b200.server`: the serving binary (reference `crates/fe-server/src/main.rs` flags, `scripts/serve.sh`
+environment). Binds the port, builds the engine, serves; exits with code 70 when the engine dies so a supervisor
+restarts the process."""
+from __future__ import annotations
+
+import argparse
+import asyncio
+import os
+import sys
+
+from aiohttp import web
+
+from ..config import PRESETS, EngineConfig, ModelConfig, SiteConfig, scaled
+
+
+def build_engine(args, tok):
+    from .engine_api import MockEngine, SchedulerEngine
+    if args.mock or args.engine == "mock":
+        return MockEngine(tok, args.served_model_name, max_batch=args.slots, max_len=args.max_model_len)
+    import torch
+
+    from ..engine.engine import Engine
+    from ..engine.scheduler import SchedOptions, Scheduler
+    cfg_path = os.path.join(args.model_dir, "config.json") if args.model_dir else ""
+    if cfg_path and os.path.exists(cfg_path):
+        cfg = ModelConfig.from_hf(cfg_path)
+    else:
+        cfg = PRESETS[args.preset]()
+        if args.layers:
+            cfg = scaled(cfg, args.layers)
+    ecfg = EngineConfig.from_env(n_slots=args.slots, max_ctx=args.max_model_len, prefill_chunk=args.prefill_chunk,
+                                 weight_dtype=args.weights)
+    weights = None
+    if args.model_dir and any(f.endswith(".safetensors") for f in os.listdir(args.model_dir)):
+        from ..formats.loader import load_model_weights
+        weights = load_model_weights(args.model_dir, cfg)
+    eng = Engine(cfg, weights, ecfg, device=args.device or None, seed=0)
+    opts = SchedOptions.from_env()
+    return SchedulerEngine(Scheduler(eng, opts), args.served_model_name)
+
+
+def main(argv=None) -> int:
+    site = SiteConfig.from_env()
+    ap = argparse.ArgumentParser(prog="ferrite-server")
+    ap.add_argument("--model-dir", default=os.environ.get("FERRITE_MODEL_DIR", ""))
+    ap.add_argument("--host", default=site.host)
+    ap.add_argument("--port", type=int, default=site.port)
+    ap.add_argument("--served-model-name", default=site.served_model_name)
+    ap.add_argument("--engine", default="ferrite", choices=["ferrite", "mock"])
+    ap.add_argument("--preset", default="tiny", choices=sorted(PRESETS))
+    ap.add_argument("--layers", type=int, default=0)
+    ap.add_argument("--weights", default=os.environ.get("FERRITE_WEIGHTS", "bf16"))
+    ap.add_argument("--device", default="")
+    ap.add_argument("--slots", type=int, default=int(os.environ.get("FERRITE_SLOTS", "4")))
+    ap.add_argument("--prefill-chunk", type=int, default=int(os.environ.get("FERRITE_CHUNK", "2048")))
+    ap.add_argument("--max-concurrent", type=int, default=site.max_concurrent)
+    ap.add_argument("--max-model-len", type=int, default=int(os.environ.get("FERRITE_CTX", "8192")))
+    ap.add_argument("--profile", default=os.environ.get("FERRITE_PROFILE", "default"))
+    ap.add_argument("--mock", action="store_true")
+    args = ap.parse_args(argv)
+
+    from .app import AppState, make_app
+    from .profiles import GenDefaults
+    from .template import ChatTemplate
+    from .tokenizer import load_tokenizer
+
+    vocab = PRESETS[args.preset]().vocab
+    tok = load_tokenizer(args.model_dir or None, vocab)
+    engine_box = {}
+
+    def factory():
+        engine_box["e"] = build_engine(args, tok)
+        return AppState(engine_box["e"], tok, ChatTemplate.from_dir(args.model_dir or None),
+                        GenDefaults.from_dir(args.model_dir or None, args.profile), args.served_model_name,
+                        args.max_concurrent)
+
+    app = make_app(factory)
+
+    async def watch(app):
+        async def loop():
+            while True:
+                await asyncio.sleep(1.0)
+                e = engine_box.get("e")
+                if e is not None and e.dead():
+                    print(f"engine dead: {e.dead()}", file=sys.stderr, flush=True)
+                    os._exit(70)
+        app["watch"] = asyncio.create_task(loop())
+
+    app.on_startup.append(watch)
+    web.run_app(app, host=args.host, port=args.port, print=lambda *a: print(*a, file=sys.stderr))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
