@@ -1,4 +1,5 @@
 """Codecs and tilings of the quantised formats (CPU)."""
+import pytest
 import torch
 
 from ferrite_b200.formats import nvfp4
@@ -43,3 +44,139 @@ def test_mma_scale_tiling_shape():
     sc = torch.ones(200, 40, dtype=torch.uint8).view(torch.float8_e4m3fn)
     t = nvfp4.tile_scales_mma(sc)
     assert t.shape == (2, 10, 512)
+
+
+def _ref_q4k_block(b):
+    """Scalar restatement of ggml's dequantize_row_q4_K for one 144-byte block."""
+    import numpy as np
+    d, dmin = np.frombuffer(b[0:2], np.float16)[0].astype(np.float32), np.frombuffer(b[2:4], np.float16)[0].astype(np.float32)
+    sc, qs = b[4:16], b[16:144]
+
+    def sm(j):
+        if j < 4:
+            return sc[j] & 63, sc[j + 4] & 63
+        return (sc[j + 4] & 0xF) | ((sc[j - 4] >> 6) << 4), (sc[j + 4] >> 4) | ((sc[j] >> 6) << 4)
+    y, is_, q = [], 0, 0
+    for _ in range(4):
+        s1, m1 = sm(is_); s2, m2 = sm(is_ + 1)
+        y += [d * s1 * (qs[q + l] & 0xF) - dmin * m1 for l in range(32)]
+        y += [d * s2 * (qs[q + l] >> 4) - dmin * m2 for l in range(32)]
+        q += 32; is_ += 2
+    return np.array(y, np.float32)
+
+
+def _ref_q6k_block(b):
+    import numpy as np
+    ql, qh, sc = b[0:128].astype(np.int32), b[128:192].astype(np.int32), np.frombuffer(b[192:208], np.int8).astype(np.int32)
+    d = np.frombuffer(b[208:210], np.float16)[0].astype(np.float32)
+    y = np.zeros(256, np.float32)
+    for n in range(2):
+        for l in range(32):
+            i = l // 16
+            L, H, S, Y = ql[64 * n:], qh[32 * n:], sc[8 * n:], 128 * n
+            q1 = ((L[l] & 0xF) | (((H[l] >> 0) & 3) << 4)) - 32
+            q2 = ((L[l + 32] & 0xF) | (((H[l] >> 2) & 3) << 4)) - 32
+            q3 = ((L[l] >> 4) | (((H[l] >> 4) & 3) << 4)) - 32
+            q4 = ((L[l + 32] >> 4) | (((H[l] >> 6) & 3) << 4)) - 32
+            y[Y + l], y[Y + l + 32] = d * S[i] * q1, d * S[i + 2] * q2
+            y[Y + l + 64], y[Y + l + 96] = d * S[i + 4] * q3, d * S[i + 6] * q4
+    return y
+
+
+def test_gguf_reader_and_block_decoders(tmp_path):
+    import numpy as np
+    from ferrite_b200.formats import gguf
+    r = np.random.default_rng(0)
+    x = r.standard_normal((4, 64)).astype(np.float32)
+    p = str(tmp_path / "t.gguf")
+    gguf.write_gguf(p, {"general.architecture": "test", "n": 3, "names": ["a", "b"]},
+                    {"w8": (gguf.quantize_q8_0(x), 8, [4, 64]), "w4": (gguf.quantize_q4_0(x), 2, [4, 64]),
+                     "f": (x.view(np.uint8).reshape(-1), 0, [4, 64])})
+    g = gguf.Gguf(p)
+    assert g.meta["n"] == 3 and g.meta["names"] == ["a", "b"] and g.tensors["w8"].shape == [4, 64]
+    assert torch.equal(g.get("f"), torch.from_numpy(x))
+    assert (g.get("w8") - torch.from_numpy(x)).abs().max() < 0.02
+    assert (g.get("w4") - torch.from_numpy(x)).abs().max() < 0.35
+    # K-quants and friends: random block bytes (valid fp16 scales) against scalar restatements of the ggml decoders
+    for name, ref in (("Q4_K", _ref_q4k_block), ("Q6_K", _ref_q6k_block)):
+        tid = gguf.TYPE_ID[name]
+        bb = gguf.TYPES[tid][2]
+        blk = r.integers(0, 256, size=(3, bb), dtype=np.uint8)
+        if name == "Q4_K":
+            blk[:, 0:4] = np.array([0.01, 0.002], np.float16).view(np.uint8)
+        else:
+            blk[:, 208:210] = np.array([0.01], np.float16).view(np.uint8)
+        got = gguf.dequantize(blk.reshape(-1), tid).reshape(3, 256)
+        want = np.stack([ref(blk[i]) for i in range(3)])
+        assert np.allclose(got, want, rtol=1e-6, atol=1e-7), name
+    # 4-bit codebook types: every code of IQ4_NL / MXFP4 decodes to its table value times the scale
+    blk = np.zeros((1, 18), np.uint8); blk[0, :2] = np.array([0.5], np.float16).view(np.uint8); blk[0, 2:] = np.arange(16) | (np.arange(16)[::-1] << 4)
+    got = gguf.dequantize(blk.reshape(-1), gguf.TYPE_ID["IQ4_NL"])
+    assert np.allclose(got[:16], 0.5 * gguf.KVALUES_IQ4NL) and np.allclose(got[16:], 0.5 * gguf.KVALUES_IQ4NL[::-1])
+    blk = np.zeros((1, 17), np.uint8); blk[0, 0] = 128; blk[0, 1:] = np.arange(16)
+    assert np.allclose(gguf.dequantize(blk.reshape(-1), gguf.TYPE_ID["MXFP4"])[:16], gguf.KVALUES_MXFP4)   # 2^(128-127)/2 = 1
+    with pytest.raises(NotImplementedError):
+        gguf.dequantize(np.zeros(66, np.uint8), gguf.TYPE_ID["IQ2_XXS"])
+
+
+def test_exl3_decode_reconstruct_and_slices():
+    import numpy as np
+    from ferrite_b200.formats.exl3 import Exl3Tensor
+    t = Exl3Tensor.random(256, 384, 4, seed=1)
+    W = t.weight(torch.float64)
+    x = torch.randn(3, 256, dtype=torch.float64, generator=torch.Generator().manual_seed(0))
+    assert (x @ W - t.linear(x)).abs().max() < 1e-12                      # factored form == reconstructed weight
+    assert (t.slice_cols(128, 384).weight(torch.float64) - W[:, 128:]).abs().max() == 0
+    parts = t.slice_rows(0, 128).linear(x[:, :128]) + t.slice_rows(128, 256).linear(x[:, 128:])
+    assert (parts - x @ W).abs().max() < 1e-12                            # row slices sum to the whole (TP split)
+    tr = t.trellis[1, 2].astype(np.uint32)
+    words = tr[0::2] | (tr[1::2] << 16)
+
+    def state(pos, bits=4):                                               # scalar window extraction
+        L, s = 256 * bits, 0
+        st = ((pos + 1) * bits + L - 16) % L
+        for b in range(16):
+            p = (st + b) % L
+            s = (s << 1) | int((words[p // 32] >> (31 - p % 32)) & 1)
+        return s
+    S = t.states()[1, 2]
+    assert all(state(i) == int(S[i]) for i in range(0, 256, 7))
+
+
+def test_safetensors_roundtrip_and_loader(tmp_path):
+    from ferrite_b200.config import tiny_hybrid
+    from ferrite_b200.formats.loader import load_model_weights, save_native
+    from ferrite_b200.formats.safetensors_io import SafeTensors, save_file
+    from ferrite_b200.models.weights import init_weights
+    cfg = tiny_hybrid()
+    w = init_weights(cfg, seed=0)
+    save_native(w, str(tmp_path / "model.safetensors"), cfg)
+    back = load_model_weights(str(tmp_path), cfg, torch.float32)
+    assert set(back) == set(w) and all(torch.equal(back[k], w[k]) for k in w)
+    # the same model written with Hugging Face names (separate projections) loads into the fused layout
+    hf = {"model.embed_tokens.weight": w["embed"], "model.norm.weight": w["final_norm"]}
+    nk, nv, dk, dv = cfg.lin_k_heads, cfg.lin_v_heads, cfg.lin_dk, cfg.lin_dv
+    for i, kind in enumerate(cfg.layer_kinds):
+        q, p = f"model.layers.{i}.", f"l{i}."
+        hf[q + "input_layernorm.weight"], hf[q + "post_attention_layernorm.weight"] = w[p + "input_norm"], w[p + "post_norm"]
+        if kind == "gdn":
+            ip = w[p + "in_proj"]
+            o = cfg.conv_dim
+            hf[q + "linear_attn.in_proj_qkv.weight"], hf[q + "linear_attn.in_proj_z.weight"] = ip[:o], ip[o:o + nv * dv]
+            hf[q + "linear_attn.in_proj_b.weight"], hf[q + "linear_attn.in_proj_a.weight"] = ip[o + nv * dv:o + nv * dv + nv], ip[o + nv * dv + nv:]
+            hf[q + "linear_attn.conv1d.weight"] = w[p + "conv_w"].view(cfg.conv_dim, 1, cfg.conv_k)
+            hf[q + "linear_attn.A_log"], hf[q + "linear_attn.dt_bias"] = w[p + "A_log"], w[p + "dt_bias"]
+            hf[q + "linear_attn.norm.weight"], hf[q + "linear_attn.out_proj.weight"] = w[p + "gnorm_w"], w[p + "out_proj"]
+        else:
+            ip = w[p + "in_proj"]
+            qd = cfg.attn_q_dim
+            hf[q + "self_attn.q_proj.weight"], hf[q + "self_attn.k_proj.weight"] = ip[:qd], ip[qd:qd + cfg.n_kv * cfg.head_dim]
+            hf[q + "self_attn.v_proj.weight"], hf[q + "self_attn.o_proj.weight"] = ip[qd + cfg.n_kv * cfg.head_dim:], w[p + "out_proj"]
+            hf[q + "self_attn.q_norm.weight"], hf[q + "self_attn.k_norm.weight"] = w[p + "q_norm"], w[p + "k_norm"]
+        gu = w[p + "gate_up"]
+        hf[q + "mlp.gate_proj.weight"], hf[q + "mlp.up_proj.weight"], hf[q + "mlp.down_proj.weight"] = gu[:cfg.inter], gu[cfg.inter:], w[p + "down"]
+    d2 = tmp_path / "hf"
+    d2.mkdir()
+    save_file({k: v.contiguous() for k, v in hf.items()}, str(d2 / "model.safetensors"))
+    back = load_model_weights(str(d2), cfg, torch.float32)
+    assert all(torch.equal(back[k], w[k]) for k in w)
