@@ -44,6 +44,16 @@ int fb_gemm_nvfp4_fused(void* Y, const void* X, long ldx, const void* norm_w, fl
                         int split_k, int out_f32, float* workspace, int* counters, int* status, int sm_count,
                         cudaStream_t s);
 
+// ---- moe.cu: router, grouped-expert GEMVs over (token, expert) pairs, fixed-order combine ----
+int fb_moe_route(int* ids, float* wts, const float* logits, const float* bias, int rows, int n_exp, int top_k, int mode,
+                 int n_groups, int topk_groups, float scale, cudaStream_t s);
+int fb_moe_gate_up(void* act, const void* x, const void* w_gu, const int* ids, int pairs, int top_k, int hidden,
+                   int inter, int e_lo, int e_hi, cudaStream_t s);
+int fb_moe_down(float* yp, const void* act, const void* w_down, const int* ids, int pairs, int hidden, int inter,
+                int e_lo, int e_hi, cudaStream_t s);
+int fb_moe_combine(void* out, const float* yp, const float* wts, const void* shared, const float* shared_gate,
+                   const void* res, int rows, int top_k, int hidden, int out_f32, cudaStream_t s);
+
 #ifdef __cplusplus
 }
 #endif

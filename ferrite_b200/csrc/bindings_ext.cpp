@@ -128,6 +128,28 @@ void gemm_nvfp4_fused(Tensor Y, Tensor X, c10::optional<Tensor> norm_w, double e
         "gemm_nvfp4_fused");
 }
 
+void moe_route(Tensor ids, Tensor wts, Tensor logits, c10::optional<Tensor> bias, int64_t mode, int64_t n_groups,
+               int64_t topk_groups, double scale) {
+  check(fb_moe_route(ids.data_ptr<int>(), wts.data_ptr<float>(), logits.data_ptr<float>(),
+                     bias.has_value() ? bias->data_ptr<float>() : nullptr, (int)logits.size(0), (int)logits.size(1),
+                     (int)ids.size(1), (int)mode, (int)n_groups, (int)topk_groups, (float)scale, cur_stream()),
+        "moe_route");
+}
+
+void moe_experts(Tensor out, Tensor act, Tensor yp, Tensor x, Tensor w_gu, Tensor w_down, Tensor ids, Tensor wts,
+                 int64_t e_lo, int64_t e_hi, c10::optional<Tensor> shared, c10::optional<Tensor> shared_gate,
+                 c10::optional<Tensor> res) {
+  int rows = (int)x.size(0), hidden = (int)x.size(1), top_k = (int)ids.size(1), inter = (int)w_down.size(2);
+  int pairs = rows * top_k;
+  check(fb_moe_gate_up(act.data_ptr(), x.data_ptr(), w_gu.data_ptr(), ids.data_ptr<int>(), pairs, top_k, hidden, inter,
+                       (int)e_lo, (int)e_hi, cur_stream()), "moe_gate_up");
+  check(fb_moe_down(yp.data_ptr<float>(), act.data_ptr(), w_down.data_ptr(), ids.data_ptr<int>(), pairs, hidden, inter,
+                    (int)e_lo, (int)e_hi, cur_stream()), "moe_down");
+  check(fb_moe_combine(out.data_ptr(), yp.data_ptr<float>(), wts.data_ptr<float>(), cptr(shared),
+                       shared_gate.has_value() ? shared_gate->data_ptr<float>() : nullptr, cptr(res), rows, top_k,
+                       hidden, out.scalar_type() == torch::kFloat32 ? 1 : 0, cur_stream()), "moe_combine");
+}
+
 }  // namespace
 
 void register_ext(pybind11::module_& m) {
@@ -141,6 +163,8 @@ void register_ext(pybind11::module_& m) {
   m.def("argmax_gather", &argmax_gather);
   m.def("comm_wait_probe", &comm_wait_probe);
   m.def("gemv_nvfp4", &gemv_nvfp4);
+  m.def("moe_route", &moe_route);
+  m.def("moe_experts", &moe_experts);
   m.def("nvfp4_sf_bytes", &nvfp4_sf_bytes);
   m.def("quant_nvfp4", &quant_nvfp4);
   m.def("gemm_nvfp4_workspace_bytes", &gemm_nvfp4_workspace_bytes);

@@ -268,6 +268,30 @@ class Executor:
             return self.ops.linear(x_in, w, res=res)
         return self.tp.linear_allreduce(self.ops, x_in, w, res)
 
+    def _moe_ffn(self, x, i):
+        """Routed experts + shared expert. Under expert parallelism a rank computes the pairs of the experts it owns
+        (and its column slice of the shared expert); the partial sums are reduced over ranks with the residual."""
+        c, w, ops = self.cfg, self.w, self.ops
+        p = f"l{i}."
+        h, _ = ops.rmsnorm(x, w[p + "post_norm"], c.eps, True)
+        logits = ops.linear(h, w[p + "router"], out_f32=True) if h.shape[0] <= 64 else ops.linear(h, w[p + "router"]).float()
+        ids, wts = ops.moe_route(logits.contiguous(), w.get(p + "router_bias"), 0 if c.router == "softmax" else 1, c.top_k,
+                                 c.n_groups, c.topk_groups, c.route_scale)
+        shared = sgate = None
+        if c.n_shared:
+            shared = ops.linear(ops.linear(h, w[p + "shared_gate_up"], swiglu=True), w[p + "shared_down"])
+            if c.router == "softmax":
+                sgate = ops.linear(h, w[p + "shared_gate"], out_f32=True) if h.shape[0] <= 64 else ops.linear(h, w[p + "shared_gate"]).float()
+        world = self.tp.world if self.tp is not None else 1
+        rank = self.tp.rank if self.tp is not None else 0
+        n_exp = self.full_cfg.n_experts
+        per = n_exp // world
+        e_lo, e_hi = rank * per, (rank + 1) * per
+        if world == 1:
+            return ops.moe_experts(h, ids, wts, w[p + "experts_gate_up"], w[p + "experts_down"], e_lo, e_hi, shared, sgate, x)
+        part = ops.moe_experts(h, ids, wts, w[p + "experts_gate_up"], w[p + "experts_down"], e_lo, e_hi, shared, sgate, None)
+        return self.tp.allreduce_rows(ops, part, x)
+
     def _layers(self, x, mv, T, nseg, max_seg_rows, nsplit, commit):
         c, w, ops = self.cfg, self.w, self.ops
         eps = c.eps
@@ -300,8 +324,11 @@ class Executor:
                                       self.block_table, self.ecfg.kv_block, c.n_q, c.n_kv, c.head_dim, c.attn_gate,
                                       nsplit=nsplit)
                 x = self._row_parallel(o, w[p + "out_proj"], x)
-            act = ops.linear(x, w[p + "gate_up"], norm_w=w[p + "post_norm"], eps=eps, swiglu=True)
-            x = self._row_parallel(act, w[p + "down"], x)
+            if c.is_moe(i):
+                x = self._moe_ffn(x, i)
+            else:
+                act = ops.linear(x, w[p + "gate_up"], norm_w=w[p + "post_norm"], eps=eps, swiglu=True)
+                x = self._row_parallel(act, w[p + "down"], x)
             if i in c.tap_layers:
                 self.taps.append(x)
         return x

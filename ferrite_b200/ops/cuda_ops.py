@@ -16,6 +16,7 @@ from .._ext import load
 from .qweight import QWeight
 
 GEMV_MAX_ROWS = 8
+MOE_PAIR_ROWS = 16     # up to this many rows the experts run as per-pair GEMVs, beyond as grouped GEMMs
 
 
 class CudaOps:
@@ -155,6 +156,56 @@ class CudaOps:
         self.launches += 1
         self.C.gated_norm(out, y, proj, z_off, proj.stride(0), w, heads, dv, eps)
         return out
+
+    # ---- mixture of experts ---------------------------------------------------------------------------
+    def moe_route(self, logits, bias, mode, top_k, n_groups, topk_groups, scale):
+        T = logits.shape[0]
+        ids = torch.empty(T, top_k, dtype=torch.int32, device=self.device)
+        wts = torch.empty(T, top_k, dtype=torch.float32, device=self.device)
+        self.launches += 1
+        self.C.moe_route(ids, wts, logits, bias, mode, n_groups, topk_groups, scale)
+        return ids, wts
+
+    def moe_experts(self, h, ids, wts, w_gu, w_down, e_lo, e_hi, shared=None, shared_gate=None, res=None, out_f32=False):
+        T, K = ids.shape
+        H, inter = h.shape[1], w_down.shape[2]
+        if T > MOE_PAIR_ROWS:
+            return self._moe_grouped(h, ids, wts, w_gu, w_down, e_lo, e_hi, shared, shared_gate, res, out_f32)
+        act = torch.empty(T * K, inter, dtype=self.dtype, device=self.device)
+        yp = torch.empty(T * K, H, dtype=torch.float32, device=self.device)
+        out = torch.empty(T, H, dtype=torch.float32 if out_f32 else self.dtype, device=self.device)
+        self.launches += 3
+        self.C.moe_experts(out, act, yp, h, w_gu, w_down, ids, wts, e_lo, e_hi, shared,
+                           None if shared_gate is None else shared_gate.reshape(-1).float().contiguous(), res)
+        return out
+
+    def _moe_grouped(self, h, ids, wts, w_gu, w_down, e_lo, e_hi, shared, shared_gate, res, out_f32):
+        """Prompt-sized batches: sort the (token, expert) pairs by expert and run one tcgen05 GEMM pair per expert that
+        received rows (reference: sorted pair list + segmented GEMM, `kernels/k-gguf/src/sort.rs`, `mmq.rs:522`)."""
+        T, K = ids.shape
+        flat = ids.reshape(-1).long()
+        order = torch.argsort(flat, stable=True)
+        tok = (order // K)
+        counts = torch.bincount(flat, minlength=e_hi)[e_lo:e_hi].tolist()
+        start = int((flat < e_lo).sum())
+        out = torch.zeros(T, h.shape[1], dtype=torch.float32, device=self.device)
+        wflat = wts.reshape(-1)
+        for j, n in enumerate(counts):
+            if n == 0:
+                continue
+            sel = order[start:start + n]
+            rows = tok[start:start + n]
+            xe = h[rows].contiguous()
+            a = self.linear(xe, w_gu[j], swiglu=True)
+            y = self.linear(a, w_down[j])
+            out.index_add_(0, rows, y.float() * wflat[sel][:, None])
+            start += n
+        if shared is not None:
+            g = torch.sigmoid(shared_gate.float()).reshape(-1, 1) if shared_gate is not None else 1.0
+            out += shared.float() * g
+        if res is not None:
+            out += res.float()
+        return out if out_f32 else out.to(self.dtype)
 
     # ---- attention ---------------------------------------------------------------------------------
     def attn_prep(self, proj, q_norm, k_norm, inv_freq, row_slot, row_pos, block_table, k_cache, v_cache, kv_block,

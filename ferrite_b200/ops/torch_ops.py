@@ -180,6 +180,35 @@ class TorchOps:
                 conv_state[slot] = x[-ck1:].to(conv_state.dtype)
         return y
 
+    # ---- mixture of experts ---------------------------------------------------------------------------
+    def moe_route(self, logits, bias, mode, top_k, n_groups, topk_groups, scale):
+        from ..config import ModelConfig
+        from ..models.ref import route
+        c = ModelConfig(router="softmax" if mode == 0 else "sigmoid_group", top_k=top_k, n_groups=n_groups,
+                        topk_groups=topk_groups, route_scale=scale, n_experts=logits.shape[1])
+        idx, w = route(c, logits.float().cpu(), None if bias is None else bias.cpu())
+        return idx.to(torch.int32).to(logits.device), w.float().to(logits.device)
+
+    def moe_experts(self, h, ids, wts, w_gu, w_down, e_lo, e_hi, shared=None, shared_gate=None, res=None, out_f32=False):
+        T, K = ids.shape
+        out = torch.zeros(T, h.shape[1], dtype=torch.float32, device=h.device)
+        hf = h.float()
+        for t in range(T):
+            for k in range(K):
+                e = int(ids[t, k])
+                if e < e_lo or e >= e_hi:
+                    continue
+                gu = w_gu[e - e_lo].float() @ hf[t]
+                i = gu.shape[0] // 2
+                a = (F.silu(gu[:i]) * gu[i:]).to(self.dtype).float()
+                out[t] += float(wts[t, k]) * (w_down[e - e_lo].float() @ a)
+        if shared is not None:
+            g = torch.sigmoid(shared_gate.float()).reshape(-1, 1) if shared_gate is not None else 1.0
+            out = out + shared.float() * g
+        if res is not None:
+            out = out + res.float()
+        return out if out_f32 else out.to(self.dtype)
+
     # ---- selection ---------------------------------------------------------------------------------
     def argmax(self, logits):
         lf = logits.float()

@@ -97,6 +97,23 @@ class TensorParallel:
             part = (part.float() + res.float()).to(res.dtype) if part.device.type == "cpu" else part.add_(res)
         return part.to(x.dtype)
 
+    def allreduce_rows(self, ops, part, res):
+        """Sum [rows, n] partials over the ranks (rank order) and add the residual: the combine step of the expert-
+        parallel MoE block, where every rank holds the partial output of the experts it owns."""
+        if self.fused and part.numel() <= ONESHOT_MAX:
+            part = part.contiguous()
+            y = torch.empty_like(part)
+            self.C.allreduce_oneshot(self.comm, y, part, res)
+            ops.launches += 1
+            self.stats["oneshot"] += 1
+            return y
+        self.stats["nccl"] += 1
+        buf = part.float() if part.device.type == "cpu" else part.clone()
+        dist.all_reduce(buf, group=self.group)
+        if res is not None:
+            buf = buf.float() + res.float()
+        return buf.to(res.dtype if res is not None else part.dtype)
+
     # ---- vocabulary-parallel head -----------------------------------------------------------------------------
     def gather_logits(self, ops, logits, greedy: bool, vocab_offset: int, vocab: int):
         """logits: this rank's shard [rows, n_local] fp32. greedy: (None, (ids, finite)) with ids merged over ranks
