@@ -16,7 +16,8 @@ from .._ext import load
 from .qweight import QWeight
 
 GEMV_MAX_ROWS = 8
-MOE_PAIR_ROWS = 16     # up to this many rows the experts run as per-pair GEMVs, beyond as grouped GEMMs
+MOE_PAIR_ROWS = 64     # up to this many rows (the largest graph-captured step) the experts run as per-pair GEMVs,
+                       # beyond as grouped GEMMs, which read the per-expert row counts on the host
 
 
 class CudaOps:
@@ -33,6 +34,7 @@ class CudaOps:
         self._counters = torch.zeros(4096, dtype=torch.int32, device=self.device)
         self.force_gemv_chunks = False      # debug: run any row count through 8-row GEMV passes
         self.launches = 0                   # kernels launched (or recorded into a graph) through this object
+        self.moe_pair_rows = MOE_PAIR_ROWS
         self.fp4_act = False                # NVFP4 weights: quantise activations too and use the tcgen05 GEMM
         self._sf_pool = {}
 
@@ -98,7 +100,8 @@ class CudaOps:
             return y
         if norm_w is not None:
             x, _ = self.rmsnorm(x, norm_w, eps, True)
-        y = torch.empty(M, N, dtype=self.dtype, device=self.device)
+        # the wide-M epilogue stores 16-byte row pieces: give odd widths a padded leading dimension
+        y = torch.empty(M, (N + 7) // 8 * 8, dtype=self.dtype, device=self.device)[:, :N]
         split = self._split_k(M, N, K) if M <= 64 else 1
         ws = cnt = None
         if split > 1:
@@ -169,7 +172,7 @@ class CudaOps:
     def moe_experts(self, h, ids, wts, w_gu, w_down, e_lo, e_hi, shared=None, shared_gate=None, res=None, out_f32=False):
         T, K = ids.shape
         H, inter = h.shape[1], w_down.shape[2]
-        if T > MOE_PAIR_ROWS:
+        if T > self.moe_pair_rows:
             return self._moe_grouped(h, ids, wts, w_gu, w_down, e_lo, e_hi, shared, shared_gate, res, out_f32)
         act = torch.empty(T * K, inter, dtype=self.dtype, device=self.device)
         yp = torch.empty(T * K, H, dtype=torch.float32, device=self.device)

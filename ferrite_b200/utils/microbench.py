@@ -89,7 +89,7 @@ def bench_linear(ops, t, m, n, k, swiglu=False, norm=False, res=False, label=Non
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemv", "gemm", "layer", "attn_decode", "attn_prefill", "gdn"])
+    ap.add_argument("what", choices=["gemv", "gemm", "layer", "attn_decode", "attn_prefill", "gdn", "moe"])
     ap.add_argument("--m", type=int, default=1)
     ap.add_argument("--n", type=int, default=5120)
     ap.add_argument("--k", type=int, default=5120)
@@ -171,6 +171,23 @@ def main():
                         chunked=per > 16)
         ms = t.run(fn)
         report(f"gdn conv+rec rows{rows} segs{nseg}", ms, nseg * nv * dk * dv * 4 * 2, 0.0)
+    elif a.what == "moe":
+        # routed-expert block of one decode step at the 80B-A3B shapes: 512 experts, top-10, hidden 2048, expert FFN 512
+        E, K, H, I = 512, 10, 2048, 512
+        rows = a.m
+        h = rnd(rows, H)
+        w_gu, w_dn = rnd(E, 2 * I, H, scale=0.02), rnd(E, H, I, scale=0.02)
+        logits = rnd(rows, E, dtype=torch.float32)
+        res = rnd(rows, H)
+
+        def fn():
+            ids, wts = ops.moe_route(logits, None, 0, K, 1, 1, 1.0)
+            ops.moe_experts(h, ids, wts, w_gu, w_dn, 0, E, None, None, res)
+        ms = t.run(fn)
+        ids, _ = ops.moe_route(logits, None, 0, K, 1, 1, 1.0)
+        distinct = int(ids.unique().numel())
+        report(f"moe route+experts rows{rows} (distinct experts {distinct})", ms, distinct * 3 * H * I * 2,
+               2.0 * rows * K * 3 * H * I)
 
 
 if __name__ == "__main__":

@@ -45,7 +45,8 @@ def test_router(ops, mode, E, K, ng, tg, scale, T):
 
 @pytest.mark.parametrize("T", [1, 4, 16, 48])
 @pytest.mark.parametrize("ep", [False, True])
-def test_experts(ops, T, ep):
+def test_experts(ops, T, ep, monkeypatch):
+    monkeypatch.setattr(ops, "moe_pair_rows", 16)
     E, K, H, I = 16, 4, 512, 256
     tops = TorchOps(DEV, torch.float32)
     h = rnd(T, H, seed=1)
@@ -71,11 +72,11 @@ def test_moe_engine_gpu(ext, router):
     cfg = dataclasses.replace(tiny_hybrid(), n_experts=32, top_k=4, expert_inter=64, n_shared=1, router=router, **kw)
     w = init_weights(cfg, seed=0)
     ref = Engine(cfg, w, EngineConfig(n_slots=2, max_ctx=128), device="cpu")
-    p = torch.randint(0, cfg.vocab, (40,), generator=torch.Generator().manual_seed(1)).tolist()
+    p = torch.randint(0, cfg.vocab, (88,), generator=torch.Generator().manual_seed(1)).tolist()
     want, _, _ = ref.forward([Segment(0, 0, p, "all")])
     eng = Engine(cfg, w, EngineConfig(n_slots=2, max_ctx=128), device=DEV)
-    got, _, _ = eng.forward([Segment(0, 0, p[:32], "all")])          # grouped GEMM path
-    tail = [eng.forward([Segment(0, 32 + i, [p[32 + i]], "last")])[0] for i in range(8)]   # pair GEMV path
+    got, _, _ = eng.forward([Segment(0, 0, p[:80], "all")])          # grouped GEMM path
+    tail = [eng.forward([Segment(0, 80 + i, [p[80 + i]], "last")])[0] for i in range(8)]   # pair GEMV path
     got = torch.cat([got] + tail).float().cpu()
     # bf16 weights/activations against the fp32 oracle: compare distributions, not raw logits
     kl = torch.nn.functional.kl_div(torch.log_softmax(got, -1), torch.log_softmax(want, -1), log_target=True,
