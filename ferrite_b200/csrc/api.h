@@ -52,9 +52,11 @@ int fb_gdn_conv(void* out, const void* proj, long proj_stride, const void* conv_
 int fb_gdn_rec(float* y, float* rec_state, void* conv_state, const void* qkv, const void* proj, long proj_stride,
                const float* A_log, const float* dt_bias, const int* seg_slot, const int* seg_row0,
                const int* seg_nrows, int nseg, int nk, int nv, int dk, int dv, float eps, int commit, cudaStream_t s);
-int fb_gdn_chunk(float* y, float* rec_state, void* conv_state, const void* qkv, const void* proj, long proj_stride,
-                 const float* A_log, const float* dt_bias, const int* seg_slot, const int* seg_row0,
-                 const int* seg_nrows, int nseg, int nk, int nv, int dk, int dv, float eps, int commit,
+// chunked scan for prompt-sized segments; `scratch` holds fb_gdn_chunk_scratch_bytes(rows, nseg, nv, dk) bytes
+long fb_gdn_chunk_scratch_bytes(int rows, int nseg, int nv, int dk);
+int fb_gdn_chunk(float* y, float* rec_state, void* conv_state, float* scratch, const void* qkv, const void* proj,
+                 long proj_stride, const float* A_log, const float* dt_bias, const int* seg_slot, const int* seg_row0,
+                 const int* seg_nrows, int nseg, int max_rows, int nk, int nv, int dk, int dv, float eps, int commit,
                  cudaStream_t s);
 
 // ---- sample.cu ----

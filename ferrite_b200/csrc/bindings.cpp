@@ -125,12 +125,28 @@ void gdn_conv(Tensor out, Tensor proj, Tensor conv_w, Tensor conv_state, Tensor 
 
 void gdn_rec(Tensor y, Tensor rec_state, Tensor conv_state, Tensor qkv, Tensor proj, Tensor A_log, Tensor dt_bias,
              Tensor seg_slot, Tensor seg_row0, Tensor seg_nrows, int64_t nk, int64_t nv, int64_t dk, int64_t dv,
-             double eps, bool commit, bool chunked) {
-  auto fn = chunked ? fb_gdn_chunk : fb_gdn_rec;
-  check(fn(y.data_ptr<float>(), rec_state.data_ptr<float>(), conv_state.data_ptr(), qkv.data_ptr(), proj.data_ptr(),
-           (long)proj.stride(0), A_log.data_ptr<float>(), dt_bias.data_ptr<float>(), seg_slot.data_ptr<int>(),
-           seg_row0.data_ptr<int>(), seg_nrows.data_ptr<int>(), (int)seg_slot.numel(), (int)nk, (int)nv, (int)dk,
-           (int)dv, (float)eps, commit ? 1 : 0, cur_stream()), "gdn_rec");
+             double eps, bool commit) {
+  check(fb_gdn_rec(y.data_ptr<float>(), rec_state.data_ptr<float>(), conv_state.data_ptr(), qkv.data_ptr(),
+                   proj.data_ptr(), (long)proj.stride(0), A_log.data_ptr<float>(), dt_bias.data_ptr<float>(),
+                   seg_slot.data_ptr<int>(), seg_row0.data_ptr<int>(), seg_nrows.data_ptr<int>(),
+                   (int)seg_slot.numel(), (int)nk, (int)nv, (int)dk, (int)dv, (float)eps, commit ? 1 : 0, cur_stream()),
+        "gdn_rec");
+}
+
+int64_t gdn_chunk_scratch_bytes(int64_t rows, int64_t nseg, int64_t nv, int64_t dk) {
+  return fb_gdn_chunk_scratch_bytes((int)rows, (int)nseg, (int)nv, (int)dk);
+}
+
+void gdn_chunk(Tensor y, Tensor rec_state, Tensor conv_state, Tensor scratch, Tensor qkv, Tensor proj, Tensor A_log,
+               Tensor dt_bias, Tensor seg_slot, Tensor seg_row0, Tensor seg_nrows, int64_t max_rows, int64_t nk,
+               int64_t nv, int64_t dk, int64_t dv, double eps, bool commit) {
+  TORCH_CHECK((int64_t)(scratch.numel() * scratch.element_size()) >=
+                  gdn_chunk_scratch_bytes(qkv.size(0), seg_slot.numel(), nv, dk), "gdn_chunk: scratch too small");
+  check(fb_gdn_chunk(y.data_ptr<float>(), rec_state.data_ptr<float>(), conv_state.data_ptr(), (float*)scratch.data_ptr(),
+                     qkv.data_ptr(), proj.data_ptr(), (long)proj.stride(0), A_log.data_ptr<float>(),
+                     dt_bias.data_ptr<float>(), seg_slot.data_ptr<int>(), seg_row0.data_ptr<int>(),
+                     seg_nrows.data_ptr<int>(), (int)seg_slot.numel(), (int)max_rows, (int)nk, (int)nv, (int)dk, (int)dv,
+                     (float)eps, commit ? 1 : 0, cur_stream()), "gdn_chunk");
 }
 
 void argmax(Tensor ids, Tensor logits, c10::optional<Tensor> vals, c10::optional<Tensor> finite,
@@ -179,6 +195,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("attn_prefill", &attn_prefill);
   m.def("gdn_conv", &gdn_conv);
   m.def("gdn_rec", &gdn_rec);
+  m.def("gdn_chunk", &gdn_chunk);
+  m.def("gdn_chunk_scratch_bytes", &gdn_chunk_scratch_bytes);
   m.def("argmax", &argmax);
   m.def("sample", &sample);
   m.def("chain_accept", &chain_accept);

@@ -60,6 +60,7 @@ class BlockPool:
 
 
 FLASH_MIN_ROWS = 16      # segments longer than this go to the flash prefill kernel (reference FLASH_MIN 17)
+GDN_CHUNK_MIN_ROWS = 24  # segments this long go through the chunked GDN scan instead of the row-by-row recurrence
 
 
 def _bucket(n: int) -> int:
@@ -306,7 +307,8 @@ class Executor:
                     self.verify_proj[i] = proj           # kept so the accepted rows can be replayed into the state
                 y = ops.gdn_rec(qkv, proj, self.rec_state[i], self.conv_state[i], w[p + "A_log"], w[p + "dt_bias"],
                                 mv["sslot"], mv["srow0"], mv["snrows"], c.lin_k_heads, c.lin_v_heads, c.lin_dk,
-                                c.lin_dv, eps, commit=commit, chunked=False)
+                                c.lin_dv, eps, commit=commit, chunked=commit and max_seg_rows >= GDN_CHUNK_MIN_ROWS,
+                                max_rows=max_seg_rows)
                 o = ops.gated_norm(y, proj, c.conv_dim, w[p + "gnorm_w"], c.lin_v_heads, c.lin_dv, eps)
                 x = self._row_parallel(o, w[p + "out_proj"], x)
             else:

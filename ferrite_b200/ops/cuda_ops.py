@@ -35,6 +35,7 @@ class CudaOps:
         self.force_gemv_chunks = False      # debug: run any row count through 8-row GEMV passes
         self.launches = 0                   # kernels launched (or recorded into a graph) through this object
         self.moe_pair_rows = MOE_PAIR_ROWS
+        self._gdn_scratch = None
         self.fp4_act = False                # NVFP4 weights: quantise activations too and use the tcgen05 GEMM
         self._sf_pool = {}
 
@@ -248,11 +249,19 @@ class CudaOps:
         return out
 
     def gdn_rec(self, qkv, proj, rec_state, conv_state, A_log, dt_bias, seg_slot, seg_row0, seg_nrows, nk, nv, dk, dv,
-                eps, commit=True, chunked=False):
+                eps, commit=True, chunked=False, max_rows=None):
         y = torch.empty(qkv.shape[0], nv * dv, dtype=torch.float32, device=self.device)
+        if chunked and dk == 128 and dv % 16 == 0:
+            nb = int(self.C.gdn_chunk_scratch_bytes(qkv.shape[0], seg_slot.numel(), nv, dk))
+            if self._gdn_scratch is None or self._gdn_scratch.numel() < nb:
+                self._gdn_scratch = torch.empty(nb, dtype=torch.uint8, device=self.device)
+            self.launches += 2
+            self.C.gdn_chunk(y, rec_state, conv_state, self._gdn_scratch, qkv, proj, A_log, dt_bias, seg_slot, seg_row0,
+                             seg_nrows, qkv.shape[0] if max_rows is None else max_rows, nk, nv, dk, dv, eps, commit)
+            return y
         self.launches += 1
         self.C.gdn_rec(y, rec_state, conv_state, qkv, proj, A_log, dt_bias, seg_slot, seg_row0, seg_nrows, nk, nv,
-                       dk, dv, eps, commit, chunked)
+                       dk, dv, eps, commit)
         return y
 
     # ---- selection ---------------------------------------------------------------------------------

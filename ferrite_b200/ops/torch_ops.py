@@ -146,7 +146,7 @@ class TorchOps:
         return out
 
     def gdn_rec(self, qkv, proj, rec_state, conv_state, A_log, dt_bias, seg_slot, seg_row0, seg_nrows, nk, nv, dk, dv,
-                eps, commit=True, chunked=False):
+                eps, commit=True, chunked=False, max_rows=None):
         T = qkv.shape[0]
         conv_dim = 2 * nk * dk + nv * dv
         y = torch.zeros(T, nv * dv, dtype=torch.float32, device=qkv.device)

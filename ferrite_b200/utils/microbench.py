@@ -168,7 +168,7 @@ def main():
         def fn():
             qkv = ops.gdn_conv(proj, conv_w, cst, ss, r0, nr, conv_dim, max_rows=per)
             ops.gdn_rec(qkv, proj, rec, cst, A, dtb, ss, r0, nr, nk, nv, dk, dv, 1e-6, commit=True,
-                        chunked=per > 16)
+                        chunked=per >= 24, max_rows=per)
         ms = t.run(fn)
         report(f"gdn conv+rec rows{rows} segs{nseg}", ms, nseg * nv * dk * dv * 4 * 2, 0.0)
     elif a.what == "moe":

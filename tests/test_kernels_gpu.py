@@ -213,3 +213,33 @@ def test_gemv_nvfp4_swiglu(ops, tops, M):
     q = quantize_weight(w)
     nw = rnd(K, scale=0.1, seed=4)
     close(ops.linear(x, q, norm_w=nw, swiglu=True), tops.linear(x, q, norm_w=nw, swiglu=True))
+
+
+@pytest.mark.parametrize("nk,nv", [(2, 2), (2, 4)])
+def test_gdn_chunked_scan(ops, tops, nk, nv):
+    """Chunked prompt scan against the row-by-row fp32 recurrence: whole chunks, a ragged tail, a one-row segment,
+    non-zero starting state; outputs, committed state and conv tail."""
+    dk = dv = 128
+    conv_dim = 2 * nk * dk + nv * dv
+    width = conv_dim + nv * dv + 2 * nv
+    lens = [130, 64, 1, 37]
+    T = sum(lens)
+    proj = rnd(T, width, seed=11)
+    qkv = rnd(T, conv_dim, seed=12)
+    A_log = rnd(nv, scale=0.3, seed=3, dtype=torch.float32)
+    dtb = rnd(nv, scale=0.3, seed=4, dtype=torch.float32)
+    seg_slot = torch.tensor([3, 0, 2, 1], device=DEV, dtype=torch.int32)
+    row0 = [0, 130, 194, 195]
+    seg_row0 = torch.tensor(row0, device=DEV, dtype=torch.int32)
+    seg_n = torch.tensor(lens, device=DEV, dtype=torch.int32)
+    mk = lambda: (rnd(4, nv, dk, dv, scale=0.2, seed=6, dtype=torch.float32), rnd(4, 3, conv_dim, seed=7))
+    sa, sb, sc = mk(), mk(), mk()
+    ya = ops.gdn_rec(qkv, proj, sa[0], sa[1], A_log, dtb, seg_slot, seg_row0, seg_n, nk, nv, dk, dv, 1e-6, commit=True,
+                     chunked=True, max_rows=max(lens))
+    yb = ops.gdn_rec(qkv, proj, sb[0], sb[1], A_log, dtb, seg_slot, seg_row0, seg_n, nk, nv, dk, dv, 1e-6, commit=True)
+    yc = tops.gdn_rec(qkv, proj, sc[0], sc[1], A_log, dtb, seg_slot, seg_row0, seg_n, nk, nv, dk, dv, 1e-6, commit=True)
+    close(yb, yc, atol=5e-3)
+    close(ya, yc, atol=5e-3, rtol=1e-2)
+    close(sa[0], sc[0], atol=5e-3, rtol=1e-2)
+    assert torch.equal(sa[1], sc[1])
+    assert float((ya - yb).abs().max()) < 2e-3
