@@ -319,3 +319,83 @@ extern "C" int fb_attn_decode(void* out, float* o_part, float* ml_part, const vo
   else launch_pdl(attn_combine_kernel<64>, dim3(cgrid), dim3(cthreads), (size_t)(0), s, (__nv_bfloat16*)out, o_part, ml_part, (const __nv_bfloat16*)proj, proj_stride, nq, nsplit, gated);
   return (int)cudaGetLastError();
 }
+
+// ---- allocation-free variant (declared in api_static.h) -----------------------------------------------------------
+// The per-split partials live in an array that is part of the library image, so a caller that may not allocate device
+// memory can still run split-KV decode attention. In host code the array's name is only a handle for the runtime's
+// symbol table; the address the kernels need is looked up once per device with cudaGetSymbolAddress.
+#include <cstdio>
+#include <mutex>
+
+#include "api_static.h"
+
+namespace fb {
+constexpr long ATT_STATIC_FLOATS = 2l * 1024 * 1024;                       // 8 MiB per GPU
+static __device__ __align__(256) float g_attn_static_scratch[ATT_STATIC_FLOATS];
+constexpr int ATT_STATIC_MAX_DEV = 64;
+static float* g_attn_static_ptr[ATT_STATIC_MAX_DEV] = {};
+static std::mutex g_attn_static_mu;
+static thread_local char g_attn_static_err[256] = "";
+}  // namespace fb
+
+extern "C" long fb_attn_decode_static_scratch_bytes(void) { return fb::ATT_STATIC_FLOATS * (long)sizeof(float); }
+
+extern "C" long fb_attn_decode_static_need_bytes(int rows, int nq, int hd, int nsplit) {
+  return (long)rows * nq * nsplit * (hd + 2) * (long)sizeof(float);
+}
+
+extern "C" const char* fb_attn_decode_static_error(void) { return fb::g_attn_static_err; }
+
+extern "C" int fb_attn_decode_static(void* out, const void* q, const void* k_cache, const void* v_cache,
+                                     const void* proj, long proj_stride, const int* row_slot, const int* row_kvlen,
+                                     const int* row_base, const unsigned long long* row_mask, const int* block_table,
+                                     int max_blocks, int kv_block, int rows, int nq, int nkv, int hd, int nsplit,
+                                     int gated, cudaStream_t s) {
+  using namespace fb;
+  g_attn_static_err[0] = 0;
+  if (rows <= 0) return 0;
+  if (nq <= 0 || nkv <= 0 || hd <= 0 || nsplit <= 0) {
+    snprintf(g_attn_static_err, sizeof g_attn_static_err, "fb_attn_decode_static: non-positive size");
+    return -1;
+  }
+  const long need = fb_attn_decode_static_need_bytes(rows, nq, hd, nsplit);
+  if (need > fb_attn_decode_static_scratch_bytes()) {
+    snprintf(g_attn_static_err, sizeof g_attn_static_err,
+             "fb_attn_decode_static: rows=%d nq=%d hd=%d nsplit=%d need %ld bytes of scratch, the built-in array holds %ld",
+             rows, nq, hd, nsplit, need, fb_attn_decode_static_scratch_bytes());
+    return -20;
+  }
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) {
+    snprintf(g_attn_static_err, sizeof g_attn_static_err, "fb_attn_decode_static: cudaGetDevice: %s", cudaGetErrorString(e));
+    return (int)e;
+  }
+  if (dev < 0 || dev >= ATT_STATIC_MAX_DEV) {
+    snprintf(g_attn_static_err, sizeof g_attn_static_err, "fb_attn_decode_static: device %d beyond the set-up table", dev);
+    return -21;
+  }
+  float* base;
+  {
+    std::lock_guard<std::mutex> lk(g_attn_static_mu);
+    if (!g_attn_static_ptr[dev]) {                    // first call on this device (it is the current one)
+      void* p = nullptr;
+      e = cudaGetSymbolAddress(&p, g_attn_static_scratch);
+      if (e != cudaSuccess || !p) {
+        snprintf(g_attn_static_err, sizeof g_attn_static_err, "fb_attn_decode_static: cudaGetSymbolAddress: %s",
+                 cudaGetErrorString(e));
+        return e != cudaSuccess ? (int)e : -22;
+      }
+      g_attn_static_ptr[dev] = static_cast<float*>(p);
+    }
+    base = g_attn_static_ptr[dev];
+  }
+  float* o_part = base;                                              // [rows][nq][nsplit][hd]
+  float* ml_part = base + (size_t)rows * nq * nsplit * hd;           // [rows][nq][nsplit][2]
+  int rc = fb_attn_decode(out, o_part, ml_part, q, k_cache, v_cache, proj, proj_stride, row_slot, row_kvlen, row_base,
+                          row_mask, block_table, max_blocks, kv_block, rows, nq, nkv, hd, nsplit, gated, s);
+  if (rc)
+    snprintf(g_attn_static_err, sizeof g_attn_static_err, "fb_attn_decode_static: launch failed with code %d%s%s", rc,
+             rc > 0 ? ": " : "", rc > 0 ? cudaGetErrorString((cudaError_t)rc) : "");
+  return rc;
+}
