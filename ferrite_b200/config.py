@@ -242,6 +242,7 @@ class EngineConfig:
     decode_rows_max: int = 64          # rows routed to the small-M (GEMV) kernels
     attn_splits: int = 0               # 0 = pick from context length
     use_graphs: bool = True
+    seq_parallel: bool = True          # TP prompts: row-sharded residual stream, all-gather/reduce-scatter fused into the GEMMs
     graph_max: int = 128               # LRU size of the CUDA-graph cache (reference GRAPH_MAX)
     spec_depth: int = 0
     park_gb: float = 0.0
@@ -269,6 +270,7 @@ class EngineConfig:
             c.park_gb = float(e["FE_PARK_GB"])
         c.park_host = e.get("FE_PARK_HOST", "0") not in ("", "0")
         c.use_graphs = e.get("FE_NO_GRAPHS", "0") in ("", "0")
+        c.seq_parallel = e.get("FE_NO_SEQ_PARALLEL", "0") in ("", "0")
         c.step_timeout_s = float(e.get("FE_STEP_TIMEOUT", c.step_timeout_s))
         for k, v in over.items():
             if v is not None:

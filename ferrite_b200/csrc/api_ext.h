@@ -54,6 +54,16 @@ int fb_moe_down(float* yp, const void* act, const void* w_down, const int* ids, 
 int fb_moe_combine(void* out, const float* yp, const float* wts, const void* shared, const float* shared_gate,
                    const void* res, int rows, int top_k, int hidden, int out_f32, cudaStream_t s);
 
+// ---- gemm_comm.cu: tensor-parallel GEMMs with the collective inside the kernel ----
+long fb_big_workspace_bytes(int world, long max_rows, long max_cols);
+long fb_big_xfull_offset(int world, long max_rows, long max_cols);
+int fb_gemm_rs(void* y_shard, const void* X, const void* W, const void* res_shard, int M, int N, int K, long ldx,
+               const void* const* peers, int rank, int world, long max_rows, long max_cols, uint32_t* ctr, int* status,
+               unsigned spin_limit, int sm_count, cudaStream_t s);
+int fb_ag_gemm(void* Y, const void* W, const void* res, int M, int N, int K, long ldy, int mode,
+               const void* const* peers, int rank, int world, long max_rows, long max_cols, uint32_t* ctr, int* status,
+               unsigned spin_limit, int sm_count, cudaStream_t s);
+
 #ifdef __cplusplus
 }
 #endif

@@ -150,9 +150,53 @@ void moe_experts(Tensor out, Tensor act, Tensor yp, Tensor x, Tensor w_gu, Tenso
                        hidden, out.scalar_type() == torch::kFloat32 ? 1 : 0, cur_stream()), "moe_combine");
 }
 
+// Handle to the large symmetric workspace used by the GEMMs with a fused reduce-scatter / all-gather.
+struct BigComm {
+  std::vector<const void*> peers;
+  int rank = 0, world = 1, sm = 148;
+  long max_rows = 0, max_cols = 0;
+  Tensor ctr, status;
+  unsigned spin_limit = 0;
+};
+
+BigComm make_big_comm(std::vector<int64_t> peer_ptrs, int64_t rank, int64_t max_rows, int64_t max_cols, Tensor ctr,
+                      Tensor status, int64_t spin_limit, int64_t sm) {
+  BigComm c;
+  for (auto p : peer_ptrs) c.peers.push_back(reinterpret_cast<const void*>(p));
+  c.rank = (int)rank; c.world = (int)peer_ptrs.size(); c.max_rows = max_rows; c.max_cols = max_cols;
+  c.ctr = ctr; c.status = status; c.spin_limit = (unsigned)spin_limit; c.sm = (int)sm;
+  TORCH_CHECK(ctr.numel() >= 2 + (max_rows + 127) / 128, "make_big_comm: counter array too small");
+  return c;
+}
+
+void gemm_rs(const BigComm& c, Tensor y_shard, Tensor X, Tensor W, c10::optional<Tensor> res_shard) {
+  check(fb_gemm_rs(y_shard.data_ptr(), X.data_ptr(), W.data_ptr(), cptr(res_shard), (int)X.size(0), (int)W.size(0),
+                   (int)X.size(1), (long)X.stride(0), c.peers.data(), c.rank, c.world, c.max_rows, c.max_cols,
+                   (uint32_t*)c.ctr.data_ptr(), c.status.data_ptr<int>(), c.spin_limit, c.sm, cur_stream()), "gemm_rs");
+}
+
+void ag_gemm(const BigComm& c, Tensor Y, Tensor W, c10::optional<Tensor> res, int64_t K, int64_t mode) {
+  int M = (int)Y.size(0);
+  int N = (int)(mode == 1 ? W.size(0) / 2 : W.size(0));
+  TORCH_CHECK(W.size(1) == K, "ag_gemm: K mismatch");
+  check(fb_ag_gemm(Y.data_ptr(), W.data_ptr(), cptr(res), M, N, (int)K, (long)Y.stride(0), (int)mode, c.peers.data(),
+                   c.rank, c.world, c.max_rows, c.max_cols, (uint32_t*)c.ctr.data_ptr(), c.status.data_ptr<int>(),
+                   c.spin_limit, c.sm, cur_stream()), "ag_gemm");
+}
+
 }  // namespace
 
 void register_ext(pybind11::module_& m) {
+  pybind11::class_<BigComm>(m, "BigComm");
+  m.def("make_big_comm", &make_big_comm);
+  m.def("big_workspace_bytes", [](int64_t world, int64_t max_rows, int64_t max_cols) {
+    return (int64_t)fb_big_workspace_bytes((int)world, (long)max_rows, (long)max_cols);
+  });
+  m.def("big_xfull_offset", [](int64_t world, int64_t max_rows, int64_t max_cols) {
+    return (int64_t)fb_big_xfull_offset((int)world, (long)max_rows, (long)max_cols);
+  });
+  m.def("gemm_rs", &gemm_rs);
+  m.def("ag_gemm", &ag_gemm);
   pybind11::class_<Comm>(m, "Comm");
   m.def("make_comm", &make_comm);
   m.def("comm_workspace_bytes", [](int64_t max_ctas, int64_t slot_floats) {

@@ -70,6 +70,8 @@ class Engine:
             ops.fp4_act = self.ecfg.weight_dtype == "nvfp4"
         self.ops = ops
         self.tp = tp
+        if tp is not None and tp.world > 1 and self.ecfg.seq_parallel and tp.sp_max is None:
+            tp.setup_big(self.ecfg.max_step_rows, cfg.hidden)
         self.ex = Executor(self.cfg, weights, self.ecfg, ops, tp=tp, full_cfg=cfg)
         self.slot_len: List[int] = [0] * self.ecfg.n_slots
 

@@ -19,6 +19,7 @@ import torch
 
 from ..config import EngineConfig, ModelConfig
 from ..models.weights import Weights
+from ..ops.qweight import QWeight
 
 
 @dataclass
@@ -297,10 +298,29 @@ class Executor:
         c, w, ops = self.cfg, self.w, self.ops
         eps = c.eps
         self.taps = []
+        # Sequence-parallel prompt path under tensor parallelism: the residual stream is sharded by rows between
+        # blocks; column-parallel projections gather the rows (all-gather fused into the GEMM), row-parallel ones
+        # reduce-scatter them (fused into the GEMM epilogue). Decode-sized steps keep replicated rows.
+        sp = self.tp is not None and self.tp.sp_ready(T) and c.n_experts == 0 and not isinstance(
+            w["l0.in_proj"], QWeight)
+        if sp:
+            lo, hi = self.tp.shard_rows(T)
+            x = x[lo:hi].contiguous()
+
+            def col(xs, wt, norm_w, swiglu=False):
+                return self.tp.ag_linear(ops, xs, wt, norm_w, eps, T, swiglu)
+
+            def row(act, wt, xs):
+                return self.tp.rs_linear(ops, act, wt, xs, T)
+        else:
+            def col(xs, wt, norm_w, swiglu=False):
+                return ops.linear(xs, wt, norm_w=norm_w, eps=eps, swiglu=swiglu)
+
+            row = self._row_parallel
         for i, kind in enumerate(self.kinds):
             p = f"l{i}."
             if kind == "gdn":
-                proj = ops.linear(x, w[p + "in_proj"], norm_w=w[p + "input_norm"], eps=eps)
+                proj = col(x, w[p + "in_proj"], w[p + "input_norm"])
                 qkv = ops.gdn_conv(proj, w[p + "conv_w"], self.conv_state[i], mv["sslot"], mv["srow0"], mv["snrows"],
                                    c.conv_dim, **({"max_rows": max_seg_rows} if ops.name == "cuda" else {}))
                 if not commit:
@@ -310,9 +330,9 @@ class Executor:
                                 c.lin_dv, eps, commit=commit, chunked=commit and max_seg_rows >= GDN_CHUNK_MIN_ROWS,
                                 max_rows=max_seg_rows)
                 o = ops.gated_norm(y, proj, c.conv_dim, w[p + "gnorm_w"], c.lin_v_heads, c.lin_dv, eps)
-                x = self._row_parallel(o, w[p + "out_proj"], x)
+                x = row(o, w[p + "out_proj"], x)
             else:
-                proj = ops.linear(x, w[p + "in_proj"], norm_w=w[p + "input_norm"], eps=eps)
+                proj = col(x, w[p + "in_proj"], w[p + "input_norm"])
                 q = ops.attn_prep(proj, w[p + "q_norm"], w[p + "k_norm"], self.inv_freq, mv["slot"], mv["pos"],
                                   self.block_table, self.k_cache[i], self.v_cache[i], self.ecfg.kv_block, c.n_q,
                                   c.n_kv, c.head_dim, c.rotary_dim, c.attn_gate, eps)
@@ -325,15 +345,15 @@ class Executor:
                     o = ops.attention(q, proj, self.k_cache[i], self.v_cache[i], mv["slot"], mv["kvlen"],
                                       self.block_table, self.ecfg.kv_block, c.n_q, c.n_kv, c.head_dim, c.attn_gate,
                                       nsplit=nsplit)
-                x = self._row_parallel(o, w[p + "out_proj"], x)
+                x = row(o, w[p + "out_proj"], x)
             if c.is_moe(i):
                 x = self._moe_ffn(x, i)
             else:
-                act = ops.linear(x, w[p + "gate_up"], norm_w=w[p + "post_norm"], eps=eps, swiglu=True)
-                x = self._row_parallel(act, w[p + "down"], x)
+                act = col(x, w[p + "gate_up"], w[p + "post_norm"], swiglu=True)
+                x = row(act, w[p + "down"], x)
             if i in c.tap_layers:
-                self.taps.append(x)
-        return x
+                self.taps.append(self.tp.gather_rows(x, T) if sp else x)
+        return self.tp.gather_rows(x, T) if sp else x
 
     def _head(self, x, mv, nlog, greedy):
         c, w, ops = self.cfg, self.w, self.ops

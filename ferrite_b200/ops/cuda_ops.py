@@ -55,8 +55,8 @@ class CudaOps:
         self.C.embed(out, table, ids)
         return out
 
-    def rmsnorm(self, x, w, eps, centred=True, res=None):
-        out = torch.empty_like(x)
+    def rmsnorm(self, x, w, eps, centred=True, res=None, out=None):
+        out = torch.empty_like(x) if out is None else out
         if res is not None:
             xo = torch.empty_like(x)
             self.launches += 1

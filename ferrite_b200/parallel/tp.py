@@ -36,6 +36,8 @@ class TensorParallel:
         self.fused = bool(fused) and self.device.type == "cuda" and self.world > 1
         self.comm = None
         self.stats = {"fused_gemv": 0, "oneshot": 0, "nccl": 0}
+        self.big = None
+        self.sp_max = None
         if self.fused:
             self._setup_symmetric(spin_limit)
 
@@ -64,6 +66,81 @@ class TensorParallel:
         self.comm = C.make_comm(ptrs, self.rank, MAX_CTAS, SLOT_FLOATS, self.epochs, self.status, spin_limit,
                                 self.max_resident)
         self.C = C
+
+    # ---- sequence-parallel prompt path: all-gather -> GEMM and GEMM -> reduce-scatter ------------------------
+    def setup_big(self, max_rows: int, max_cols: int, spin_limit: int = 0) -> None:
+        """Allocate the large symmetric workspace (staging slots of the reduce-scatter, the gathered-X buffer, flags)
+        for steps of up to `max_rows` rows and row widths up to `max_cols`. Collective: every rank calls it."""
+        self.sp_max = (int(max_rows), int(max_cols))
+        if not self.fused:
+            return
+        import torch.distributed._symmetric_memory as symm_mem
+        C = self.C
+        nbytes = int(C.big_workspace_bytes(self.world, max_rows, max_cols))
+        self.big_ws = symm_mem.empty(nbytes, dtype=torch.uint8, device=self.device)
+        self.big_hdl = symm_mem.rendezvous(self.big_ws, group=self.group.group_name)
+        self.big_ws.zero_()
+        torch.cuda.synchronize(self.device)
+        dist.barrier(self.group)
+        self.big_ctr = torch.zeros(2 + (max_rows + 127) // 128 + 62, dtype=torch.int32, device=self.device)
+        sm = torch.cuda.get_device_properties(self.device).multi_processor_count
+        self.big = C.make_big_comm([int(p) for p in self.big_hdl.buffer_ptrs], self.rank, max_rows, max_cols,
+                                   self.big_ctr, self.status, spin_limit, sm)
+        self.xfull_off = int(C.big_xfull_offset(self.world, max_rows, max_cols))
+
+    def sp_ready(self, T: int) -> bool:
+        return self.world > 1 and T > 64 and self.sp_max is not None and T <= self.sp_max[0]
+
+    def shard_rows(self, T: int):
+        per = (T + self.world - 1) // self.world
+        lo = min(T, self.rank * per)
+        return lo, min(T, lo + per)
+
+    def _xfull(self, T: int, K: int) -> torch.Tensor:
+        return self.big_ws[self.xfull_off:self.xfull_off + T * K * 2].view(torch.bfloat16).view(T, K)
+
+    def ag_linear(self, ops, x_shard, w, norm_w, eps, T: int, swiglu: bool = False):
+        """y[T, N_local] = (all-gather over ranks of norm(x_shard)) W^T, SwiGLU optional."""
+        K = x_shard.shape[1]
+        lo, hi = self.shard_rows(T)
+        if self.fused and self.big is not None and K <= self.sp_max[1]:
+            xf = self._xfull(T, K)
+            if norm_w is not None:
+                ops.rmsnorm(x_shard, norm_w, eps, True, out=xf[lo:hi])
+            else:
+                xf[lo:hi].copy_(x_shard)
+            N = w.shape[0] // 2 if swiglu else w.shape[0]
+            y = torch.empty(T, (N + 7) // 8 * 8, dtype=x_shard.dtype, device=x_shard.device)[:, :N]
+            self.C.ag_gemm(self.big, y, w, None, K, 1 if swiglu else 0)
+            ops.launches += 1
+            self.stats["ag_gemm"] = self.stats.get("ag_gemm", 0) + 1
+            return y
+        h = ops.rmsnorm(x_shard, norm_w, eps, True)[0] if norm_w is not None else x_shard
+        return ops.linear(self.gather_rows(h, T), w, swiglu=swiglu)
+
+    def rs_linear(self, ops, act, w, res_shard, T: int):
+        """y_shard = rows of this rank of (sum over ranks of act W^T) + res_shard."""
+        lo, hi = self.shard_rows(T)
+        N = w.shape[0]
+        if self.fused and self.big is not None and N <= self.sp_max[1]:
+            y = torch.empty(hi - lo, N, dtype=act.dtype, device=act.device)
+            self.C.gemm_rs(self.big, y, act, w, res_shard)
+            ops.launches += 1
+            self.stats["gemm_rs"] = self.stats.get("gemm_rs", 0) + 1
+            return y
+        part = ops.linear(act, w)
+        buf = part.float() if part.device.type == "cpu" else part
+        dist.all_reduce(buf, group=self.group)
+        return (buf[lo:hi].float() + res_shard.float()).to(act.dtype)
+
+    def gather_rows(self, x_shard, T: int):
+        """All-gather of row shards into the full [T, H] tensor (process group; once per step and per tap)."""
+        per = (T + self.world - 1) // self.world
+        pad = torch.zeros(per, x_shard.shape[1], dtype=x_shard.dtype, device=x_shard.device)
+        pad[:x_shard.shape[0]] = x_shard
+        out = torch.empty(self.world * per, x_shard.shape[1], dtype=x_shard.dtype, device=x_shard.device)
+        dist.all_gather_into_tensor(out, pad, group=self.group)
+        return out[:T]
 
     def check(self) -> None:
         """Raise when a peer wait ran out (the kernel returned normally and left a status code)."""

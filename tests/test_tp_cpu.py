@@ -38,11 +38,13 @@ def _worker(rank, world, port, prompt, q):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world", [2])
-def test_tp_matches_single_rank(world):
+@pytest.mark.parametrize("world,plen", [(2, 24), (2, 97)])
+def test_tp_matches_single_rank(world, plen):
+    """24 rows: replicated rows + all-reduce; 97 rows: the sequence-parallel prompt path (row-sharded residual stream,
+    all-gather before column-parallel and reduce-scatter after row-parallel projections) with a ragged last shard."""
     cfg = tiny_hybrid()
     w = init_weights(cfg, seed=0)
-    prompt = torch.randint(0, cfg.vocab, (24,), generator=torch.Generator().manual_seed(5)).tolist()
+    prompt = torch.randint(0, cfg.vocab, (plen,), generator=torch.Generator().manual_seed(5)).tolist()
     eng = Engine(cfg, w, EngineConfig(n_slots=1, max_ctx=128), device="cpu")
     want, wp, _ = eng.forward([Segment(0, 0, prompt, "all")])
     want2, _, _ = eng.forward([Segment(0, len(prompt), [int(wp[0][-1])], "last")])
