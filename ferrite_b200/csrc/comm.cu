@@ -120,7 +120,9 @@ __global__ void __launch_bounds__(1024) argmax_gather_kernel(int* __restrict__ i
     if (lane == 0) { cand[0] = best; cand[1] = __int_as_float(bi == 0x7fffffff ? 0 : bi + vocab_offset); }
   }
   __syncthreads();
-  // reuse the exchange buffers: each rank's pair sits in its own slot; no summing, so do the push/wait by hand
+  // Each rank's candidate travels as one 16-byte store {value, epoch, index, epoch}: both halves carry the epoch,
+  // so a reader that sees two matching epoch words has the whole candidate (8-byte halves are written atomically).
+  // The candidates live in the top COMM_TOP_RESERVE words of the data slots, apart from the all-reduce pairs.
   __shared__ uint32_t s_epoch;
   __shared__ int s_fail;
   const int cta = blockIdx.x;
@@ -128,25 +130,32 @@ __global__ void __launch_bounds__(1024) argmax_gather_kernel(int* __restrict__ i
   __syncthreads();
   const uint32_t epoch = s_epoch;
   const int parity = epoch & 1;
+  const long top = cb.slot_floats - COMM_TOP_RESERVE + (long)cta * 4;
+  __shared__ float rv[COMM_MAX_RANKS];
+  __shared__ int ri[COMM_MAX_RANKS];
   if (threadIdx.x < cb.world) {
-    float* dst = comm_data(cb.peer[threadIdx.x], cb, parity, cb.rank) + (long)cta * 2;
-    st_relaxed_sys_v2(dst, __float_as_uint(cand[0]), __float_as_uint(cand[1]));
-    __threadfence_system();
-    st_release_sys(comm_flags(cb.peer[threadIdx.x], cb, parity, cb.rank, cta), epoch);
-    const uint32_t* f = comm_flags(cb.peer[cb.rank], cb, parity, threadIdx.x, cta);
-    if (!wait_flag_eq(f, epoch, cb.spin_limit)) { s_fail = 1; set_status(cb.status, ST_PEER_TIMEOUT); }
+    const int r = threadIdx.x;
+    if (r != cb.rank) {
+      st_relaxed_sys_v4(comm_data(cb.peer[r], cb, parity, cb.rank) + top,
+                        make_uint4(__float_as_uint(cand[0]), epoch, __float_as_uint(cand[1]), epoch));
+      const float* src = comm_data(cb.peer[cb.rank], cb, parity, r) + top;
+      uint4 v = ld_relaxed_sys_v4(src);
+      for (uint32_t spin = 0; (v.y != epoch || v.w != epoch) && spin < cb.spin_limit; ++spin) v = ld_relaxed_sys_v4(src);
+      if (v.y != epoch || v.w != epoch) { s_fail = 1; set_status(cb.status, ST_PEER_TIMEOUT); }
+      rv[r] = __uint_as_float(v.x);
+      ri[r] = (int)v.z;
+    } else {
+      rv[r] = cand[0];
+      ri[r] = __float_as_int(cand[1]);
+    }
   }
   __syncthreads();
   if (threadIdx.x == 0) {
     float bv = -INFINITY;
     int bidx = 0;
     if (!s_fail) {
-      for (int r = 0; r < cb.world; ++r) {
-        const float* src = comm_data(cb.peer[cb.rank], cb, parity, r) + (long)cta * 2;
-        float v = __ldcg(src);
-        int ix = __float_as_int(__ldcg(src + 1));
-        if (v > bv || (v == bv && ix < bidx)) { bv = v; bidx = ix; }
-      }
+      for (int r = 0; r < cb.world; ++r)
+        if (rv[r] > bv || (rv[r] == bv && ri[r] < bidx)) { bv = rv[r]; bidx = ri[r]; }
     }
     ids[row] = bidx;
     if (vals) vals[row] = bv;
@@ -176,7 +185,7 @@ static int launch_gemv_ar(GemvArgs a, CommBuf cb, int max_resident, cudaStream_t
   int grid = (a.N + rpc - 1) / rpc;
   // every CTA waits on its peers: all of them must be resident at once
   if (grid > max_resident || grid > cb.max_ctas) return -7;
-  if ((long)grid * M * rpc > cb.slot_floats) return -8;
+  if ((long)grid * M * rpc * 2 > cb.slot_floats - COMM_TOP_RESERVE) return -8;
   size_t smem = (size_t)M * a.kc * sizeof(__nv_bfloat16) + (size_t)M * rpc * sizeof(float);
   auto kern = gemv_allreduce_kernel<M, R>;
   static bool attr_done = false;
@@ -225,7 +234,7 @@ extern "C" int fb_allreduce_oneshot(void* y, const void* part, const void* res, 
                                     uint32_t* epochs, int* status, unsigned spin_limit, int max_resident,
                                     cudaStream_t s) {
   if (count <= 0) return 0;
-  if (count > slot_floats) return -8;
+  if (count * 2 > slot_floats - COMM_TOP_RESERVE) return -8;
   CommBuf cb;
   fill_comm(cb, peers, rank, world, max_ctas, slot_floats, epochs, status, spin_limit);
   int grid = max_resident < max_ctas ? max_resident : max_ctas;
@@ -244,7 +253,7 @@ extern "C" int fb_argmax_gather(int* ids, float* vals, const float* logits, long
                                 int vocab_offset, const void* const* peers, int rank, int world, int max_ctas,
                                 long slot_floats, uint32_t* epochs, int* status, unsigned spin_limit, cudaStream_t s) {
   if (rows <= 0) return 0;
-  if (rows > max_ctas || (long)rows * 2 > slot_floats) return -8;
+  if (rows > max_ctas || (long)rows * 4 > COMM_TOP_RESERVE) return -8;
   CommBuf cb;
   fill_comm(cb, peers, rank, world, max_ctas, slot_floats, epochs, status, spin_limit);
   argmax_gather_kernel<<<rows, 1024, 0, s>>>(ids, vals, logits, stride, n_local, vocab_offset, cb);

@@ -362,7 +362,7 @@ extern "C" int fb_gemv_nvfp4_allreduce(void* Y, const void* X, const void* Wq, c
   a.rows_per_cta = (rpc + group - 1) / group * group;
   const int grid = (N + a.rows_per_cta - 1) / a.rows_per_cta;
   if (grid > max_resident || grid > max_ctas) return -7;
-  if ((long)grid * Mt * a.rows_per_cta > slot_floats) return -8;
+  if ((long)grid * Mt * a.rows_per_cta * 2 > slot_floats - COMM_TOP_RESERVE) return -8;
   const size_t smem = (size_t)Mt * a.kc * sizeof(__half) + (size_t)Mt * a.rows_per_cta * sizeof(float);
   if (Mt == 1) return g4_launch(gemv_nvfp4_allreduce_kernel<1>, grid, smem, s, a, cb);
   if (Mt == 2) return g4_launch(gemv_nvfp4_allreduce_kernel<2>, grid, smem, s, a, cb);

@@ -24,7 +24,7 @@ import torch.distributed as dist
 
 MAX_CTAS = 1024
 SLOT_FLOATS = 512 * 1024
-ONESHOT_MAX = SLOT_FLOATS
+ONESHOT_MAX = (SLOT_FLOATS - 1024) // 2     # a slot holds (value, epoch) pairs below the argmax candidates
 
 
 class TensorParallel:
