@@ -64,6 +64,18 @@ int fb_ag_gemm(void* Y, const void* W, const void* res, int M, int N, int K, lon
                const void* const* peers, int rank, int world, long max_rows, long max_cols, uint32_t* ctr, int* status,
                unsigned spin_limit, int sm_count, cudaStream_t s);
 
+int fb_gemm_grouped(void* Y, const void* X, const void* W, const int* tile_start, const int* row_base, int experts,
+                    int max_rows, int N, int K, long ldx, long ldy, int mode, int* status, int sm_count, cudaStream_t s);
+
+// ---- moe_ep.cu: expert-parallel MoE block (dispatch / grouped GEMMs / combine over peer memory) ----
+long fb_ep_workspace_bytes(int n_experts, int hidden, long cap_rows);
+long fb_ep_recv_offset(int n_experts, int hidden, long cap_rows);
+long fb_ep_out_offset(int n_experts, int hidden, long cap_rows);
+int fb_ep_moe(void* out, const void* x, const int* ids, const float* wts, const void* w_gu, const void* w_down,
+              const void* shared, const float* shared_gate, const void* res, void* act, int* plan, int rows, int top_k,
+              int n_experts, int hidden, int inter, long cap_rows, const void* const* peers, int rank, int world,
+              uint32_t* ctr, int* status, unsigned spin_limit, int sm_count, cudaStream_t s);
+
 #ifdef __cplusplus
 }
 #endif

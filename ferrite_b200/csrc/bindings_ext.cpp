@@ -184,9 +184,53 @@ void ag_gemm(const BigComm& c, Tensor Y, Tensor W, c10::optional<Tensor> res, in
                    c.spin_limit, c.sm, cur_stream()), "ag_gemm");
 }
 
+// Handle to the symmetric workspace of the expert-parallel MoE block.
+struct EpHandle {
+  std::vector<const void*> peers;
+  int rank = 0, world = 1, n_experts = 0, hidden = 0, sm = 148;
+  long cap_rows = 0;
+  Tensor ctr, status;
+  unsigned spin_limit = 0;
+};
+
+EpHandle make_ep_comm(std::vector<int64_t> peer_ptrs, int64_t rank, int64_t n_experts, int64_t hidden, int64_t cap_rows,
+                      Tensor ctr, Tensor status, int64_t spin_limit, int64_t sm) {
+  EpHandle c;
+  for (auto p : peer_ptrs) c.peers.push_back(reinterpret_cast<const void*>(p));
+  c.rank = (int)rank; c.world = (int)peer_ptrs.size(); c.n_experts = (int)n_experts; c.hidden = (int)hidden;
+  c.cap_rows = cap_rows; c.ctr = ctr; c.status = status; c.spin_limit = (unsigned)spin_limit; c.sm = (int)sm;
+  return c;
+}
+
+void ep_moe(const EpHandle& c, Tensor out, Tensor x, Tensor ids, Tensor wts, Tensor w_gu, Tensor w_down,
+            c10::optional<Tensor> shared, c10::optional<Tensor> shared_gate, c10::optional<Tensor> res, Tensor act,
+            Tensor plan) {
+  int rows = (int)x.size(0), top_k = (int)ids.size(1), inter = (int)w_down.size(2);
+  TORCH_CHECK(plan.numel() >= (int64_t)rows * top_k + 3 * c.n_experts + 8, "ep_moe: plan scratch too small");
+  TORCH_CHECK(act.numel() >= c.cap_rows * inter, "ep_moe: activation scratch too small");
+  check(fb_ep_moe(out.data_ptr(), x.data_ptr(), ids.data_ptr<int>(), wts.data_ptr<float>(), w_gu.data_ptr(),
+                  w_down.data_ptr(), cptr(shared), shared_gate.has_value() ? shared_gate->data_ptr<float>() : nullptr,
+                  cptr(res), act.data_ptr(), plan.data_ptr<int>(), rows, top_k, c.n_experts, c.hidden, inter, c.cap_rows,
+                  c.peers.data(), c.rank, c.world, (uint32_t*)c.ctr.data_ptr(), c.status.data_ptr<int>(), c.spin_limit,
+                  c.sm, cur_stream()), "ep_moe");
+}
+
+void gemm_grouped(Tensor Y, Tensor X, Tensor W, Tensor tile_start, Tensor row_base, int64_t mode, Tensor status) {
+  int experts = (int)W.size(0);
+  int N = (int)(mode == 1 ? W.size(1) / 2 : W.size(1));
+  check(fb_gemm_grouped(Y.data_ptr(), X.data_ptr(), W.data_ptr(), tile_start.data_ptr<int>(), row_base.data_ptr<int>(),
+                        experts, (int)X.size(0), N, (int)X.size(1), (long)X.stride(0), (long)Y.stride(0), (int)mode,
+                        status.data_ptr<int>(), 0, cur_stream()), "gemm_grouped");
+}
+
 }  // namespace
 
 void register_ext(pybind11::module_& m) {
+  pybind11::class_<EpHandle>(m, "EpHandle");
+  m.def("make_ep_comm", &make_ep_comm);
+  m.def("ep_workspace_bytes", [](int64_t e, int64_t h, int64_t cap) { return (int64_t)fb_ep_workspace_bytes((int)e, (int)h, cap); });
+  m.def("ep_moe", &ep_moe);
+  m.def("gemm_grouped", &gemm_grouped);
   pybind11::class_<BigComm>(m, "BigComm");
   m.def("make_big_comm", &make_big_comm);
   m.def("big_workspace_bytes", [](int64_t world, int64_t max_rows, int64_t max_cols) {

@@ -137,3 +137,31 @@ extern "C" int fb_ag_gemm(void* Y, const void* W, const void* res, int M, int N,
   if (rc) return rc;
   return launch<2>(p, tmA, tmB, s);
 }
+
+// ---- grouped GEMM over expert-sorted rows (mixture of experts, prompt-sized) ------------------------------------
+// Y[r][N] = X[r][K] W[e(r)][N or 2N][K]^T (+ SwiGLU) for the rows r of every expert e: rows are contiguous per
+// expert, `row_base` / `tile_start` are device-side prefix sums (experts + 1 entries) so the call needs no host
+// synchronisation. `max_rows` bounds the rows (the tensor map's extent). Counterpart of the reference's segmented
+// prompt GEMM over sorted (token, expert) pairs (`ggq_mmq_moe*`, `kernels/k-gguf/src/mmq.rs:522`).
+extern "C" int fb_gemm_grouped(void* Y, const void* X, const void* W, const int* tile_start, const int* row_base,
+                               int experts, int max_rows, int N, int K, long ldx, long ldy, int mode, int* status,
+                               int sm_count, cudaStream_t s) {
+  if (experts <= 0 || max_rows <= 0) return 0;
+  if (K % 8 || ldx % 8 || ldy % 8) return -1;
+  if (sm_count <= 0) sm_count = 148;
+  GemmPlan p{};
+  int rc = plan_gemm(p, max_rows > 64 ? max_rows : 65, N, K, mode, 1, sm_count);     // normal orientation
+  if (rc) return rc;
+  GemmArgs& a = p.a;
+  const int w_rows = a.dual ? 2 * N : N;
+  a.gr.tile_start = tile_start; a.gr.row_base = row_base; a.gr.experts = experts; a.gr.w_rows = w_rows;
+  a.Y = Y; a.res = nullptr; a.workspace = nullptr; a.counters = nullptr; a.status = status; a.ldy = ldy;
+  a.M = max_rows;
+  p.grid = sm_count;                               // the real tile count is only known on the device
+  CUtensorMap tmA, tmB;
+  rc = make_tmap_bf16_2d(&tmA, X, (uint64_t)max_rows, (uint64_t)K, (uint64_t)ldx, GM_BM);
+  if (rc) return rc;
+  rc = make_tmap_bf16_2d(&tmB, W, (uint64_t)experts * w_rows, (uint64_t)K, (uint64_t)K, (uint32_t)a.b_box_rows);
+  if (rc) return rc;
+  return launch<3>(p, tmA, tmB, s);
+}

@@ -55,8 +55,18 @@ struct GemmComm {
   const __nv_bfloat16* res_shard;   // mode 1: local residual [Ms][N] or null
 };
 
+//   3  grouped (mixture-of-experts): the rows of X are sorted by expert; row tile -> expert comes from two device
+//      tables (prefix sums of rows and of 128-row tiles per expert), each expert multiplies by its own weight block
+struct GemmGroups {
+  const int* tile_start;    // [experts + 1] prefix sum of 128-row tiles
+  const int* row_base;      // [experts + 1] prefix sum of rows
+  int experts;
+  int w_rows;               // weight rows per expert in the stacked [experts * w_rows][K] matrix
+};
+
 struct GemmArgs {
   GemmComm cm;
+  GemmGroups gr;
   void* Y;
   const __nv_bfloat16* res;
   float* workspace;
@@ -144,7 +154,8 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   // rows FIRST, they need no transfer). The ring is cut into two phases (own / not own) and each phase into groups of
   // `gs` row tiles; inside a group the row tiles vary fastest so the CTAs running together share weight panels.
   int seq0 = 0, n_first = 0, gs = 1, groups_first = 0, total_work = a.tiles_a * a.tiles_b * a.split_k;
-  if constexpr (COMM != 0) {
+  if constexpr (COMM == 3) total_work = a.gr.tile_start[a.gr.experts] * a.tiles_b;
+  if constexpr (COMM == 1 || COMM == 2) {
     epoch = *reinterpret_cast<volatile uint32_t*>(&a.cm.ctr[0]) + 1;
     parity = (int)(epoch & 1u);
     const int my0 = min(a.M, a.cm.rank * a.cm.rows_per_rank), my1 = min(a.M, my0 + a.cm.rows_per_rank);
@@ -161,8 +172,23 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 
   // work item -> (tile along A rows, tile along B rows, k split); A-row tiles vary fastest in the normal
   // orientation so CTAs running together share weight panels through L2.
+  int g_row0 = 0, g_row_end = 0, g_wrow = 0;          // grouped mode: set by decode_work
   auto decode_work = [&](int w, int& ta, int& tb, int& ks) -> bool {
-    if constexpr (COMM != 0) {
+    if constexpr (COMM == 3) {
+      ks = 0;
+      ta = w / a.tiles_b;                              // global row tile; weight panels of one row tile run together
+      tb = w % a.tiles_b;
+      int lo = 0, hi = a.gr.experts;                   // last expert whose first tile is <= ta
+      while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (a.gr.tile_start[mid] <= ta) lo = mid; else hi = mid;
+      }
+      g_row0 = a.gr.row_base[lo] + (ta - a.gr.tile_start[lo]) * GM_BM;
+      g_row_end = min(a.gr.row_base[lo + 1], a.M);     // a.M = capacity of the row buffers
+      g_wrow = lo * a.gr.w_rows;
+      return true;
+    }
+    if constexpr (COMM == 1 || COMM == 2) {
       ks = 0;
       const int pos = w / (gs * a.tiles_b), rem = w % (gs * a.tiles_b);
       int base, sz;
@@ -213,11 +239,11 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           const int kx = kb * GM_BK;
           // A boxes: swapped SwiGLU loads gate rows and up rows (N apart) as two boxes
           for (int i = 0; i < a.n_a; ++i)
-            tma_load_2d(sa + i * GM_A_BYTES, &tmA, &full_bar[stage], kx, ta * GM_BM + i * a.N);
+            tma_load_2d(sa + i * GM_A_BYTES, &tmA, &full_bar[stage], kx, (COMM == 3 ? g_row0 : ta * GM_BM) + i * a.N);
           // B boxes: normal SwiGLU stacks 128 gate rows and 128 up rows into one N = 256 operand
           for (int i = 0; i < a.n_b; ++i)
             tma_load_2d(sb + (size_t)i * a.b_box_rows * GM_BK * 2, &tmB, &full_bar[stage], kx,
-                        tb * a.b_box_rows + i * a.N);
+                        tb * a.b_box_rows + i * a.N + (COMM == 3 ? g_wrow : 0));
           if (++stage == a.stages) { stage = 0; phase ^= 1u; }
         }
       }
@@ -466,7 +492,8 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         if (!ok) break;
       } else if (!a.swap) {
         // lanes = token rows, columns = output features
-        const int m = ta * GM_BM + etid;
+        const int m = (COMM == 3 ? g_row0 : ta * GM_BM) + etid;
+        const int m_end = COMM == 3 ? g_row_end : a.M;
         const int ncols_out = a.dual ? a.bn / 2 : a.bn;
         const int n0 = tb * ncols_out;
         for (int c = 0; c < ncols_out; c += 32) {
@@ -474,7 +501,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           tmem_ld32(tbase + (uint32_t)c, r0);
           if (a.dual) tmem_ld32(tbase + (uint32_t)(c + a.bn / 2), r1);
           tmem_ld_wait();
-          if (m < a.M) {
+          if (m < m_end) {
             const int n = n0 + c;
             float v[32];
 #pragma unroll
@@ -598,7 +625,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     tc_fence_after();
     tmem_dealloc(tmem_base, (uint32_t)a.tmem_cols);
   }
-  if constexpr (COMM != 0) {
+  if constexpr (COMM == 1 || COMM == 2) {
     // the last CTA to finish advances the call counter (and clears the arrival counts for the next call)
     if (threadIdx.x == 0) {
       __threadfence();

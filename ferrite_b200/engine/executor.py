@@ -120,6 +120,7 @@ class Executor:
         self.reclaim = None                          # callable() -> bool: free some pages (set by the scheduler)
         self._last_meta = None
         self.profile = None
+        self.ep = None                        # ExpertParallel, set by the engine for MoE models under TP
 
     # ---- sizes -----------------------------------------------------------------------------------
     def kv_block_bytes(self) -> int:
@@ -270,6 +271,24 @@ class Executor:
             return self.ops.linear(x_in, w, res=res)
         return self.tp.linear_allreduce(self.ops, x_in, w, res)
 
+    def _moe_ffn_sp(self, x, i, col, row):
+        """MoE block on a row shard of the tokens (prompt path under tensor/expert parallelism): route the local
+        tokens, run the column-sharded shared expert through the gather/reduce-scatter GEMMs, and send the routed
+        pairs through the expert-parallel dispatch -> grouped GEMM -> combine kernels."""
+        c, w, ops = self.cfg, self.w, self.ops
+        p = f"l{i}."
+        h, _ = ops.rmsnorm(x, w[p + "post_norm"], c.eps, True)
+        small = h.shape[0] <= 64
+        logits = ops.linear(h, w[p + "router"], out_f32=True) if small else ops.linear(h, w[p + "router"]).float()
+        ids, wts = ops.moe_route(logits.contiguous(), w.get(p + "router_bias"), 0 if c.router == "softmax" else 1, c.top_k,
+                                 c.n_groups, c.topk_groups, c.route_scale)
+        shared = sgate = None
+        if c.n_shared:
+            shared = row(col(x, w[p + "shared_gate_up"], w[p + "post_norm"], swiglu=True), w[p + "shared_down"], None)
+            if c.router == "softmax":
+                sgate = ops.linear(h, w[p + "shared_gate"], out_f32=True) if small else ops.linear(h, w[p + "shared_gate"]).float()
+        return self.ep.moe(ops, h, ids, wts, w[p + "experts_gate_up"], w[p + "experts_down"], shared, sgate, x)
+
     def _moe_ffn(self, x, i):
         """Routed experts + shared expert. Under expert parallelism a rank computes the pairs of the experts it owns
         (and its column slice of the shared expert); the partial sums are reduced over ranks with the residual."""
@@ -301,8 +320,8 @@ class Executor:
         # Sequence-parallel prompt path under tensor parallelism: the residual stream is sharded by rows between
         # blocks; column-parallel projections gather the rows (all-gather fused into the GEMM), row-parallel ones
         # reduce-scatter them (fused into the GEMM epilogue). Decode-sized steps keep replicated rows.
-        sp = self.tp is not None and self.tp.sp_ready(T) and c.n_experts == 0 and not isinstance(
-            w["l0.in_proj"], QWeight)
+        sp = (self.tp is not None and self.tp.sp_ready(T) and (c.n_experts == 0 or self.ep is not None)
+              and not isinstance(w["l0.in_proj"], QWeight))
         if sp:
             lo, hi = self.tp.shard_rows(T)
             x = x[lo:hi].contiguous()
@@ -347,7 +366,7 @@ class Executor:
                                       nsplit=nsplit)
                 x = row(o, w[p + "out_proj"], x)
             if c.is_moe(i):
-                x = self._moe_ffn(x, i)
+                x = self._moe_ffn_sp(x, i, col, row) if sp else self._moe_ffn(x, i)
             else:
                 act = col(x, w[p + "gate_up"], w[p + "post_norm"], swiglu=True)
                 x = row(act, w[p + "down"], x)

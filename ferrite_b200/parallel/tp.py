@@ -131,7 +131,8 @@ class TensorParallel:
         part = ops.linear(act, w)
         buf = part.float() if part.device.type == "cpu" else part
         dist.all_reduce(buf, group=self.group)
-        return (buf[lo:hi].float() + res_shard.float()).to(act.dtype)
+        out = buf[lo:hi].float()
+        return (out + res_shard.float() if res_shard is not None else out).to(act.dtype)
 
     def gather_rows(self, x_shard, T: int):
         """All-gather of row shards into the full [T, H] tensor (process group; once per step and per tap)."""

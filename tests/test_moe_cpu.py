@@ -67,7 +67,7 @@ def _free_port():
     return p
 
 
-def _worker(rank, world, port, q):
+def _worker(rank, world, port, q, plen=20):
     try:
         os.environ["MASTER_ADDR"] = "127.0.0.1"
         os.environ["MASTER_PORT"] = str(port)
@@ -75,22 +75,25 @@ def _worker(rank, world, port, q):
         from ferrite_b200.parallel.tp import TensorParallel
         tp = TensorParallel(dist.group.WORLD, "cpu", fused=False)
         cfg = tiny_moe("softmax")
-        eng = Engine(cfg, weights(cfg), EngineConfig(n_slots=1, max_ctx=64), device="cpu", tp=tp)
-        logits, _, _ = eng.forward([Segment(0, 0, prompt_of(cfg), "all")])
+        eng = Engine(cfg, weights(cfg), EngineConfig(n_slots=1, max_ctx=128), device="cpu", tp=tp)
+        logits, _, _ = eng.forward([Segment(0, 0, prompt_of(cfg, plen), "all")])
         q.put((rank, logits))
         dist.destroy_process_group()
     except Exception as e:  # noqa: BLE001
         q.put((rank, repr(e)))
 
 
-def test_expert_parallel_two_ranks():
+@pytest.mark.parametrize("plen", [20, 75])
+def test_expert_parallel_two_ranks(plen):
+    """20 rows: replicated rows, owners' partial sums reduced. 75 rows: tokens sharded by rows, routed pairs dispatched
+    to the expert owners and combined back (process-group statement of the fused kernels)."""
     cfg = tiny_moe("softmax")
-    eng = Engine(cfg, weights(cfg), EngineConfig(n_slots=1, max_ctx=64), device="cpu")
-    want, _, _ = eng.forward([Segment(0, 0, prompt_of(cfg), "all")])
+    eng = Engine(cfg, weights(cfg), EngineConfig(n_slots=1, max_ctx=128), device="cpu")
+    want, _, _ = eng.forward([Segment(0, 0, prompt_of(cfg, plen), "all")])
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q, plen)) for r in range(2)]
     for p in procs:
         p.start()
     outs = [q.get(timeout=120) for _ in range(2)]

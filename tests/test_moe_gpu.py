@@ -82,3 +82,26 @@ def test_moe_engine_gpu(ext, router):
     kl = torch.nn.functional.kl_div(torch.log_softmax(got, -1), torch.log_softmax(want, -1), log_target=True,
                                     reduction="batchmean").item()
     assert kl < 2e-2, kl
+
+
+@pytest.mark.parametrize("T,E,K", [(300, 16, 4), (1000, 64, 8), (5, 16, 4)])
+def test_ep_pipeline_one_rank(ops, T, E, K):
+    """The expert-parallel kernels with a world of one (dispatch to self): plan, dispatch, grouped tcgen05 GEMMs and
+    pulled combine against the pair-by-pair fp32 statement; run twice so flags and counters advance an epoch."""
+    from ferrite_b200.parallel.ep import ExpertParallel
+    H, I = 512, 256
+    tops = TorchOps(DEV, torch.float32)
+    ep = ExpertParallel(None, DEV, E, H, cap_rows=T * K)
+    h = rnd(T, H, seed=1)
+    w_gu, w_dn = rnd(E, 2 * I, H, scale=0.05, seed=2), rnd(E, H, I, scale=0.05, seed=3)
+    g = torch.Generator().manual_seed(T)
+    ids = torch.stack([torch.randperm(E, generator=g)[:K] for _ in range(T)]).to(torch.int32).to(DEV)
+    wts = torch.rand(T, K, generator=g).to(DEV)
+    shared, sgate, res = rnd(T, H, seed=4), rnd(T, 1, seed=5, dtype=torch.float32), rnd(T, H, seed=6)
+    want = tops.moe_experts(h, ids, wts, w_gu, w_dn, 0, E, shared, sgate, res)
+    for _ in range(2):
+        got = ep.moe(ops, h, ids, wts, w_gu, w_dn, shared, sgate, res)
+        torch.cuda.synchronize()
+        ep.check()
+        err = (got.float() - want.float()).abs().max().item()
+        assert err < 3e-2 * max(1.0, want.abs().max().item()), err

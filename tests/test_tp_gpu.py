@@ -222,6 +222,93 @@ def _sp_worker_body(rank, world, port, q):
     dist.destroy_process_group()
 
 
+def _ep_worker(rank, world, port, q):
+    try:
+        _ep_worker_body(rank, world, port, q)
+    except Exception as e:
+        import traceback
+        q.put((rank, False, {"exception": repr(e), "trace": traceback.format_exc()[-1500:]}))
+
+
+def _ep_worker_body(rank, world, port, q):
+    """Expert-parallel MoE block (dispatch / grouped GEMM / combine over peer memory) on row-sharded tokens against
+    the fp32 statement over all tokens; then a MoE prompt through the engine against the single-rank CPU oracle."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev,
+                            timeout=datetime.timedelta(seconds=120))
+    from ferrite_b200.ops.cuda_ops import CudaOps
+    from ferrite_b200.ops.torch_ops import TorchOps
+    from ferrite_b200.parallel.ep import ExpertParallel
+    from ferrite_b200.parallel.tp import TensorParallel
+    tp = TensorParallel(dist.group.WORLD, dev, fused=True, spin_limit=1 << 22)
+    ops, tops = CudaOps(dev), TorchOps(dev, torch.float32)
+    res, ok = {}, True
+    g = torch.Generator(device=dev).manual_seed(7)
+    T, E, K, H, I = 1024, 64, 8, 2048, 512
+    ep = ExpertParallel(tp, dev, E, H, cap_rows=T * K, spin_limit=1 << 22)
+    r = lambda *s, sc=1.0: (torch.randn(*s, generator=g, device=dev) * sc).to(torch.bfloat16)
+    h, w_gu, w_dn = r(T, H), r(E, 2 * I, H, sc=0.03), r(E, H, I, sc=0.03)
+    ids = torch.stack([torch.randperm(E, generator=g, device=dev)[:K] for _ in range(T)]).to(torch.int32)
+    wts = torch.rand(T, K, generator=g, device=dev)
+    shared, xres = r(T, H), r(T, H)
+    sgate = torch.randn(T, 1, generator=g, device=dev)
+    want = tops.moe_experts(h[:256], ids[:256], wts[:256], w_gu, w_dn, 0, E, shared[:256], sgate[:256], xres[:256])
+    lo, hi = tp.shard_rows(T)
+    per = E // world
+    wg, wd = w_gu[rank * per:(rank + 1) * per].contiguous(), w_dn[rank * per:(rank + 1) * per].contiguous()
+    outs = [ep.moe(ops, h[lo:hi].contiguous(), ids[lo:hi].contiguous(), wts[lo:hi].contiguous(), wg, wd,
+                   shared[lo:hi].contiguous(), sgate[lo:hi].contiguous(), xres[lo:hi].contiguous()) for _ in range(3)]
+    torch.cuda.synchronize()
+    ep.check()
+    full = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+    dist.all_gather_into_tensor(full, outs[-1])
+    err = (full[:256].float() - want.float()).abs().max().item() / want.abs().max().item()
+    res["ep_err"] = err
+    ok = ok and err < 3e-2 and torch.equal(outs[0], outs[-1])
+    e0, e1 = torch.cuda.Event(True), torch.cuda.Event(True)
+    dist.barrier(); torch.cuda.synchronize()
+    e0.record()
+    for _ in range(10):
+        ep.moe(ops, h[lo:hi].contiguous(), ids[lo:hi].contiguous(), wts[lo:hi].contiguous(), wg, wd, None, None, None)
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / 10], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    res["ep_block_us_T1024"] = t.item() * 1e3
+    # engine: MoE prompt on the sequence-parallel + expert-parallel path
+    import dataclasses
+    from ferrite_b200.config import EngineConfig, tiny_hybrid
+    from ferrite_b200.engine.engine import Engine
+    from ferrite_b200.engine.executor import Segment
+    from ferrite_b200.models.weights import init_weights
+    cfg = dataclasses.replace(tiny_hybrid(), n_experts=32, top_k=4, expert_inter=64, n_shared=1, router="softmax")
+    w = init_weights(cfg, seed=0)
+    prompt = torch.randint(0, cfg.vocab, (150,), generator=torch.Generator().manual_seed(5)).tolist()
+    ref = Engine(cfg, w, EngineConfig(n_slots=1, max_ctx=256), device="cpu")
+    want, _, _ = ref.forward([Segment(0, 0, prompt, "all")])
+    tp2 = TensorParallel(dist.group.WORLD, dev, fused=True, spin_limit=1 << 22)
+    eng = Engine(cfg, w, EngineConfig(n_slots=1, max_ctx=256, max_step_rows=512), device=dev, tp=tp2)
+    got, _, _ = eng.forward([Segment(0, 0, prompt, "all")], greedy=False)
+    kl = torch.nn.functional.kl_div(torch.log_softmax(got.float().cpu(), -1), torch.log_softmax(want, -1),
+                                    log_target=True, reduction="batchmean").item()
+    res["engine_ep_kl"] = kl
+    res["ep_calls"] = eng.ex.ep.calls
+    ok = ok and kl < 2e-2 and eng.ex.ep.calls > 0
+    tp2.check()
+    q.put((rank, ok, res))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_expert_parallel_dispatch_combine(ext):
+    world = min(torch.cuda.device_count(), 8)
+    if world < 2:
+        pytest.skip("needs 2+ GPUs")
+    _run_ranks(_ep_worker, world)
+
+
 def _run_ranks(target, world, deadline_s=240):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
