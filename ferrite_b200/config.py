@@ -213,8 +213,18 @@ def mla_671b() -> ModelConfig:
     )
 
 
+def tiny_mla(moe: bool = True) -> ModelConfig:
+    """3-layer MLA model (latent 64 + rope 64) with the grouped-sigmoid MoE and a leading dense layer: the plumbing
+    model of the 671B-class family."""
+    kw = dict(n_experts=16, top_k=4, expert_inter=64, n_shared=1, router="sigmoid_group", n_groups=4, topk_groups=2,
+              route_scale=2.5, first_dense=1, dense_inter=512) if moe else {}
+    return ModelConfig(name="tiny-mla", hidden=256, inter=512, n_layers=3, head_dim=96, n_q=4, n_kv=4, rotary_dim=64,
+                       vocab=1024, tie_embeddings=True, kv_lora=64, q_lora=128, rope_head_dim=64, nope_head_dim=32,
+                       v_head_dim=32, **kw)
+
+
 PRESETS = {
-    "tiny": tiny_hybrid, "27b": hybrid_27b, "drafter": drafter_block, "moe80b": moe_80b, "mla671b": mla_671b,
+    "tiny": tiny_hybrid, "tiny-mla": tiny_mla, "27b": hybrid_27b, "drafter": drafter_block, "moe80b": moe_80b, "mla671b": mla_671b,
 }
 
 

@@ -76,6 +76,26 @@ int fb_ep_moe(void* out, const void* x, const int* ids, const float* wts, const 
               int n_experts, int hidden, int inter, long cap_rows, const void* const* peers, int rank, int world,
               uint32_t* ctr, int* status, unsigned spin_limit, int sm_count, cudaStream_t s);
 
+// ---- gguf_quant.cu: GGUF block formats ----
+int fb_gguf_dequant(void* out_bf16, const void* raw, int type, long n_values, cudaStream_t s);
+int fb_q8_1_quant(void* out, const void* x_bf16, long n_values, cudaStream_t s);
+int fb_gguf_gemv(void* y, const void* x, const void* raw, const void* res, int type, int M, int N, int K, long ldx,
+                 long ldy, cudaStream_t s);
+
+// ---- exl3.cu: EXL3 trellis-quantised linears ----
+int fb_exl3_had(void* out, const void* in, const void* pre_f16, const void* post_f16, const void* res, int rows, int width,
+                float scale, int in_f32, int out_bf16, cudaStream_t s);
+int fb_exl3_gemv(float* z, const float* xh, const void* trellis, int rows, int k, int n, int bits, cudaStream_t s);
+int fb_exl3_decode(void* w_hat_t_bf16, const void* trellis, int k, int n, int bits, cudaStream_t s);
+
+// ---- mla.cu: multi-head latent attention over a paged latent cache ----
+int fb_mla_prep(void* cache, void* qabs, const void* kva, long kva_stride, const void* q, long q_stride, const void* norm_w,
+                const float* inv_freq, const int* row_slot, const int* row_pos, const int* block_table, int max_blocks,
+                int kv_block, int rows, int nq, int dn, int L, int R, float eps, int* status, cudaStream_t s);
+int fb_mla_attn(void* out, float* o_part, float* ml_part, const void* qabs, const void* cache, const int* row_slot,
+                const int* row_kvlen, const int* block_table, int max_blocks, int kv_block, int rows, int nq, int L, int R,
+                int nsplit, float scale, cudaStream_t s);
+
 #ifdef __cplusplus
 }
 #endif

@@ -223,9 +223,65 @@ void gemm_grouped(Tensor Y, Tensor X, Tensor W, Tensor tile_start, Tensor row_ba
                         status.data_ptr<int>(), 0, cur_stream()), "gemm_grouped");
 }
 
+void gguf_dequant(Tensor out, Tensor raw, int64_t type) {
+  check(fb_gguf_dequant(out.data_ptr(), raw.data_ptr(), (int)type, (long)out.numel(), cur_stream()), "gguf_dequant");
+}
+
+void q8_1_quant(Tensor out, Tensor x) {
+  TORCH_CHECK(out.numel() >= x.numel() / 32 * 36, "q8_1_quant: output too small");
+  check(fb_q8_1_quant(out.data_ptr(), x.data_ptr(), (long)x.numel(), cur_stream()), "q8_1_quant");
+}
+
+void gguf_gemv(Tensor y, Tensor x, Tensor raw, int64_t type, int64_t N, c10::optional<Tensor> res) {
+  check(fb_gguf_gemv(y.data_ptr(), x.data_ptr(), raw.data_ptr(), cptr(res), (int)type, (int)x.size(0), (int)N,
+                     (int)x.size(1), (long)x.stride(0), (long)y.stride(0), cur_stream()), "gguf_gemv");
+}
+
+void exl3_had(Tensor out, Tensor in, c10::optional<Tensor> pre, c10::optional<Tensor> post, c10::optional<Tensor> res,
+              double scale) {
+  check(fb_exl3_had(out.data_ptr(), in.data_ptr(), cptr(pre), cptr(post), cptr(res), (int)in.size(0), (int)in.size(1),
+                    (float)scale, in.scalar_type() == torch::kFloat32 ? 1 : 0, out.scalar_type() == torch::kBFloat16 ? 1 : 0,
+                    cur_stream()), "exl3_had");
+}
+
+void exl3_gemv(Tensor z, Tensor xh, Tensor trellis, int64_t bits) {
+  check(fb_exl3_gemv(z.data_ptr<float>(), xh.data_ptr<float>(), trellis.data_ptr(), (int)xh.size(0), (int)xh.size(1),
+                     (int)z.size(1), (int)bits, cur_stream()), "exl3_gemv");
+}
+
+void exl3_decode(Tensor out, Tensor trellis, int64_t bits) {
+  check(fb_exl3_decode(out.data_ptr(), trellis.data_ptr(), (int)out.size(1), (int)out.size(0), (int)bits, cur_stream()),
+        "exl3_decode");
+}
+
+void mla_prep(Tensor cache, Tensor qabs, Tensor kva, Tensor q, Tensor norm_w, Tensor inv_freq, Tensor row_slot,
+              Tensor row_pos, Tensor block_table, int64_t kv_block, int64_t nq, int64_t dn, int64_t L, int64_t R, double eps,
+              Tensor status) {
+  check(fb_mla_prep(cache.data_ptr(), qabs.data_ptr(), kva.data_ptr(), (long)kva.stride(0), q.data_ptr(), (long)q.stride(0),
+                    norm_w.data_ptr(), inv_freq.data_ptr<float>(), row_slot.data_ptr<int>(), row_pos.data_ptr<int>(),
+                    block_table.data_ptr<int>(), (int)block_table.size(1), (int)kv_block, (int)q.size(0), (int)nq, (int)dn,
+                    (int)L, (int)R, (float)eps, status.data_ptr<int>(), cur_stream()), "mla_prep");
+}
+
+void mla_attn(Tensor out, Tensor o_part, Tensor ml_part, Tensor qabs, Tensor cache, Tensor row_slot, Tensor row_kvlen,
+              Tensor block_table, int64_t kv_block, int64_t nq, int64_t L, int64_t R, int64_t nsplit, double scale) {
+  check(fb_mla_attn(out.data_ptr(), o_part.data_ptr<float>(), ml_part.data_ptr<float>(), qabs.data_ptr(), cache.data_ptr(),
+                    row_slot.data_ptr<int>(), row_kvlen.data_ptr<int>(), block_table.data_ptr<int>(),
+                    (int)block_table.size(1), (int)kv_block, (int)qabs.size(0), (int)nq, (int)L, (int)R, (int)nsplit,
+                    (float)scale, cur_stream()), "mla_attn");
+}
+
 }  // namespace
 
 void register_ext(pybind11::module_& m) {
+  m.def("mla_prep", &mla_prep);
+  m.def("mla_attn", &mla_attn);
+  m.def("exl3_had", &exl3_had);
+  m.def("exl3_gemv", &exl3_gemv);
+  m.def("exl3_decode", &exl3_decode);
+  m.def("gguf_dequant", &gguf_dequant);
+  m.def("q8_1_quant", &q8_1_quant);
+  m.def("gguf_gemv", &gguf_gemv);
   pybind11::class_<EpHandle>(m, "EpHandle");
   m.def("make_ep_comm", &make_ep_comm);
   m.def("ep_workspace_bytes", [](int64_t e, int64_t h, int64_t cap) { return (int64_t)fb_ep_workspace_bytes((int)e, (int)h, cap); });

@@ -181,29 +181,44 @@ __global__ void sample_kernel(int* __restrict__ ids, const T* __restrict__ logit
   float sum = 0.f;
   for (int i = threadIdx.x; i < vocab; i += blockDim.x) { float p = __expf(wk[i] - mx); wk[i] = p; sum += p; }
   sum = block_sum(sum, scratch);
-  // threshold on p / sum: start from min-p, then tighten for top-k and top-p by bisection
-  float lo = sp.min_p > 0.f ? sp.min_p : 0.f;      // relative to the max probability (which is 1 before /sum)
-  float thr = lo;
+  // The kept set is the intersection of the three filters, applied in the host sampler's order: top-k first, top-p
+  // over the mass that top-k kept, min-p relative to the largest probability. Each filter is a probability threshold
+  // (wk holds p / p_max, so the largest value is 1) found by bisection; the final threshold is the largest of them.
   const bool need_k = sp.top_k > 0 && sp.top_k < vocab;
   const bool need_p = sp.top_p > 0.f && sp.top_p < 1.f;
-  if (need_k || need_p) {
-    float a = lo, b = 1.0f;                          // invariant: threshold a keeps too many (or ok), b keeps too few
-    for (int it = 0; it < 24; ++it) {
-      float mid = 0.5f * (a + b);
-      float c = 0.f, m = 0.f;
-      for (int i = threadIdx.x; i < vocab; i += blockDim.x) { float p = wk[i]; if (p >= mid) { c += 1.f; m += p; } }
+  float thr_k = 0.f, mass_k = sum;
+  if (need_k) {
+    float a = 0.f, b = 1.0f;                          // a keeps >= k tokens, b (pushed just above 1) keeps fewer
+    for (int it = 0; it < 26; ++it) {
+      const float mid = 0.5f * (a + b);
+      float c = 0.f;
+      for (int i = threadIdx.x; i < vocab; i += blockDim.x) c += wk[i] >= mid ? 1.f : 0.f;
       c = block_sum(c, scratch);
-      m = block_sum(m, scratch);
-      bool too_few = false;
-      if (need_k && c < (float)sp.top_k) too_few = true;          // fewer than k kept: loosen
-      if (need_p && m < sp.top_p * sum) too_few = true;           // mass below top-p: loosen
-      // we want the tightest threshold that still keeps >= k tokens... and mass >= top_p; whichever is looser
-      // of the two constraints may be exceeded by the other, so "too_few" means any constraint unmet when
-      // both are required to be met by the kept set
-      if (too_few) b = mid; else a = mid;
+      if (c >= (float)sp.top_k) a = mid; else b = mid;
     }
-    thr = a;
+    thr_k = a;
+    float m = 0.f;
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) { const float p = wk[i]; if (p >= thr_k) m += p; }
+    mass_k = block_sum(m, scratch);
   }
+  float thr_p = thr_k;
+  if (need_p) {
+    // largest threshold whose kept mass still reaches top_p of the top-k mass: the shortest prefix of the sorted
+    // distribution that covers top_p
+    float a = thr_k, b = 1.0f;
+    const float want = sp.top_p * mass_k;
+    for (int it = 0; it < 26; ++it) {
+      const float mid = 0.5f * (a + b);
+      float m = 0.f;
+      for (int i = threadIdx.x; i < vocab; i += blockDim.x) { const float p = wk[i]; if (p >= mid) m += p; }
+      m = block_sum(m, scratch);
+      if (m >= want) a = mid; else b = mid;
+    }
+    thr_p = a;
+  }
+  float thr = fmaxf(thr_k, thr_p);
+  if (sp.min_p > 0.f) thr = fmaxf(thr, sp.min_p);
+  thr = fminf(thr, 1.0f);                             // the most likely token always survives
   if (threadIdx.x == 0) s_thr = thr;
   __syncthreads();
   thr = s_thr;

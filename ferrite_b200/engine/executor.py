@@ -95,6 +95,10 @@ class Executor:
             if kind == "attn":
                 self.k_cache[i] = torch.zeros(n_blocks, ecfg.kv_block, c.n_kv, c.head_dim, dtype=dt, device=dev)
                 self.v_cache[i] = torch.zeros(n_blocks, ecfg.kv_block, c.n_kv, c.head_dim, dtype=dt, device=dev)
+            elif kind == "mla":
+                # one latent row [kv_lora | rope] per token; the value cache slot stays empty
+                self.k_cache[i] = torch.zeros(n_blocks, ecfg.kv_block, 1, c.kv_lora + c.rope_head_dim, dtype=dt, device=dev)
+                self.v_cache[i] = torch.zeros(n_blocks, 0, dtype=dt, device=dev)
             elif kind == "gdn":
                 self.rec_state[i] = torch.zeros(ecfg.n_slots, c.lin_v_heads, c.lin_dk, c.lin_dv, dtype=torch.float32, device=dev)
                 self.conv_state[i] = torch.zeros(ecfg.n_slots, c.conv_k - 1, c.conv_dim, dtype=dt, device=dev)
@@ -104,6 +108,17 @@ class Executor:
         half = c.rotary_dim // 2
         inv = c.rope_theta ** (-torch.arange(half, dtype=torch.float64) / half)
         self.inv_freq = inv.float().to(dev)
+        # MLA: per-head slices of kv_b with the key part transposed for the absorbed query, W_uk^T [nq, L, dn] and
+        # W_uv [nq, dv, L] (reference: weight absorption in `crates/fe-dsc/src/engine.rs`)
+        self.mla_w: Dict[int, Tuple[torch.Tensor, torch.Tensor]] = {}
+        if c.kv_lora > 0:
+            dn, dvh, L = c.nope_head_dim, c.v_head_dim, c.kv_lora
+            hr = c.rope_head_dim // 2
+            self.inv_freq_mla = (c.rope_theta ** (-torch.arange(hr, dtype=torch.float64) / hr)).float().to(dev)
+            for i, kind in enumerate(self.kinds):
+                if kind == "mla":
+                    kvb = self.w[f"l{i}.kv_b"].view(c.n_q, dn + dvh, L)
+                    self.mla_w[i] = (kvb[:, :dn].transpose(1, 2).contiguous(), kvb[:, dn:].contiguous())
         # static step metadata (graph replays read these buffers)
         R = ecfg.max_step_rows
         S = max(ecfg.n_slots, 1) * 2
@@ -126,6 +141,8 @@ class Executor:
     def kv_block_bytes(self) -> int:
         c, e = self.cfg, self.ecfg
         per = 2 * e.kv_block * c.n_kv * c.head_dim * 2
+        if c.kv_lora > 0:
+            per = e.kv_block * (c.kv_lora + c.rope_head_dim) * 2
         return per * max(1, self.cfg.n_attn)
 
     # ---- block tables -----------------------------------------------------------------------------
@@ -321,7 +338,7 @@ class Executor:
         # blocks; column-parallel projections gather the rows (all-gather fused into the GEMM), row-parallel ones
         # reduce-scatter them (fused into the GEMM epilogue). Decode-sized steps keep replicated rows.
         sp = (self.tp is not None and self.tp.sp_ready(T) and (c.n_experts == 0 or self.ep is not None)
-              and not isinstance(w["l0.in_proj"], QWeight))
+              and c.kv_lora == 0 and not isinstance(w["l0.in_proj"], QWeight))
         if sp:
             lo, hi = self.tp.shard_rows(T)
             x = x[lo:hi].contiguous()
@@ -350,6 +367,20 @@ class Executor:
                                 max_rows=max_seg_rows)
                 o = ops.gated_norm(y, proj, c.conv_dim, w[p + "gnorm_w"], c.lin_v_heads, c.lin_dv, eps)
                 x = row(o, w[p + "out_proj"], x)
+            elif kind == "mla":
+                h, _ = ops.rmsnorm(x, w[p + "input_norm"], eps, True)
+                qa, _ = ops.rmsnorm(ops.linear(h, w[p + "q_a"]), w[p + "q_a_norm"], eps, True)
+                q = ops.linear(qa, w[p + "q_b"])
+                kva = ops.linear(h, w[p + "kv_a"])
+                w_uk_t, w_uv = self.mla_w[i]
+                L, R = c.kv_lora, c.rope_head_dim
+                qabs = ops.mla_prep(q, kva, w[p + "kv_a_norm"], w_uk_t, self.inv_freq_mla, mv["slot"], mv["pos"],
+                                    self.block_table, self.k_cache[i].view(-1, self.ecfg.kv_block, L + R),
+                                    self.ecfg.kv_block, c.n_q, c.nope_head_dim, L, R, eps)
+                ol = ops.mla_attention(qabs, self.k_cache[i].view(-1, self.ecfg.kv_block, L + R), mv["slot"], mv["kvlen"],
+                                       self.block_table, self.ecfg.kv_block, c.n_q, L, R,
+                                       1.0 / math.sqrt(c.nope_head_dim + R), nsplit=nsplit if max_seg_rows <= FLASH_MIN_ROWS else 1)
+                x = row(ops.mla_out(ol, w_uv), w[p + "out_proj"], x)
             else:
                 proj = col(x, w[p + "in_proj"], w[p + "input_norm"])
                 q = ops.attn_prep(proj, w[p + "q_norm"], w[p + "k_norm"], self.inv_freq, mv["slot"], mv["pos"],

@@ -75,7 +75,7 @@ class CudaOps:
         s = max(1, min(kblocks // 4, want))
         return s
 
-    def linear(self, x, w, norm_w=None, eps=1e-6, res=None, swiglu=False, out_f32=False):
+    def linear(self, x, w, norm_w=None, eps=1e-6, res=None, swiglu=False, out_f32=False, out=None):
         if isinstance(w, QWeight):
             M = x.shape[0]
             N = w.rows // 2 if swiglu else w.rows
@@ -92,7 +92,7 @@ class CudaOps:
         M, K = x.shape
         N = w.shape[0] // 2 if swiglu else w.shape[0]
         if M <= GEMV_MAX_ROWS or self.force_gemv_chunks or out_f32 and M <= 64:
-            y = torch.empty(M, N, dtype=torch.float32 if out_f32 else self.dtype, device=self.device)
+            y = out if out is not None else torch.empty(M, N, dtype=torch.float32 if out_f32 else self.dtype, device=self.device)
             for r0 in range(0, M, GEMV_MAX_ROWS):
                 r1 = min(M, r0 + GEMV_MAX_ROWS)
                 self.launches += 1
@@ -102,7 +102,7 @@ class CudaOps:
         if norm_w is not None:
             x, _ = self.rmsnorm(x, norm_w, eps, True)
         # the wide-M epilogue stores 16-byte row pieces: give odd widths a padded leading dimension
-        y = torch.empty(M, (N + 7) // 8 * 8, dtype=self.dtype, device=self.device)[:, :N]
+        y = out if out is not None else torch.empty(M, (N + 7) // 8 * 8, dtype=self.dtype, device=self.device)[:, :N]
         split = self._split_k(M, N, K) if M <= 64 else 1
         ws = cnt = None
         if split > 1:
@@ -264,7 +264,77 @@ class CudaOps:
                        dk, dv, eps, commit)
         return y
 
-    # ---- selection ---------------------------------------------------------------------------------
+    # ---- multi-head latent attention (absorbed form) ----------------------------------------------------
+    def mla_prep(self, q, kva, norm_w, w_uk_t, inv_freq, row_slot, row_pos, block_table, cache, kv_block, nq, dn, L, R, eps):
+        T = q.shape[0]
+        qabs = torch.empty(T, nq, L + R, dtype=self.dtype, device=self.device)
+        self.launches += 1
+        self.C.mla_prep(cache, qabs, kva, q, norm_w, inv_freq, row_slot, row_pos, block_table, kv_block, nq, dn, L, R, eps,
+                        self.status_word)
+        q3 = q.view(T, nq, dn + R)
+        flat = qabs.view(T, nq * (L + R))
+        for h in range(nq):                     # key up-projection folded into the query, one small linear per head
+            self.linear(q3[:, h, :dn], w_uk_t[h], out=flat[:, h * (L + R):h * (L + R) + L])
+        return qabs
+
+    def mla_attention(self, qabs, cache, row_slot, row_kvlen, block_table, kv_block, nq, L, R, scale, nsplit=1):
+        T = qabs.shape[0]
+        out = torch.empty(T, nq, L, dtype=self.dtype, device=self.device)
+        o_part = torch.empty(T * nq * nsplit * L, dtype=torch.float32, device=self.device)
+        ml_part = torch.empty(T * nq * nsplit * 2, dtype=torch.float32, device=self.device)
+        self.launches += 2
+        self.C.mla_attn(out, o_part, ml_part, qabs, cache, row_slot, row_kvlen, block_table, kv_block, nq, L, R, nsplit,
+                        scale)
+        return out
+
+    def mla_out(self, ol, w_uv):
+        T, nq, L = ol.shape
+        dv = w_uv.shape[1]
+        o = torch.empty(T, nq * dv, dtype=self.dtype, device=self.device)
+        for h in range(nq):
+            self.linear(ol[:, h, :], w_uv[h], out=o[:, h * dv:(h + 1) * dv])
+        return o
+
+    # ---- GGUF block formats ------------------------------------------------------------------------
+    def gguf_dequant(self, raw, type_id, shape):
+        """raw: uint8 tensor of GGUF blocks on the device -> bf16 tensor of `shape`."""
+        out = torch.empty(shape, dtype=torch.bfloat16, device=self.device)
+        self.launches += 1
+        self.C.gguf_dequant(out, raw, type_id)
+        return out
+
+    def gguf_gemv(self, x, raw, type_id, N, res=None):
+        """y = x W^T for up to 8 rows with W [N, K] kept in its GGUF blocks."""
+        y = torch.empty(x.shape[0], N, dtype=torch.bfloat16, device=self.device)
+        self.launches += 1
+        self.C.gguf_gemv(y, x, raw, type_id, N, res)
+        return y
+
+    def q8_1_quant(self, x):
+        out = torch.empty(x.numel() // 32 * 36, dtype=torch.uint8, device=self.device)
+        self.launches += 1
+        self.C.q8_1_quant(out, x.contiguous())
+        return out
+
+    def sample(self, logits, samplings, seeds, counts=None):
+        """One draw per row on the device: temperature, penalties (with `counts` [rows, vocab] int32), top-k, top-p
+        inside the top-k set, min-p; `samplings` are `engine.sampler.Sampling` objects, `seeds` one integer per row.
+        Same filter order as the host sampler (`engine/sampler.py::dist`)."""
+        import numpy as np
+        rows, vocab = logits.shape
+        rec = np.zeros(rows, dtype=np.dtype([("temperature", "f4"), ("top_p", "f4"), ("min_p", "f4"), ("presence", "f4"),
+                                             ("frequency", "f4"), ("repetition", "f4"), ("top_k", "i4"), ("pad", "i4"),
+                                             ("seed", "u8")]))
+        for i, (sp, seed) in enumerate(zip(samplings, seeds)):
+            rec[i] = (sp.temperature, sp.top_p, sp.min_p, sp.presence_penalty, sp.frequency_penalty,
+                      sp.repetition_penalty, sp.top_k, 0, int(seed) & 0xFFFFFFFFFFFFFFFF)
+        params = torch.from_numpy(rec.view(np.uint8)).to(self.device)
+        ids = torch.empty(rows, dtype=torch.int32, device=self.device)
+        work = torch.empty(rows, vocab, dtype=torch.float32, device=self.device)
+        self.launches += 1
+        self.C.sample(ids, logits, params, counts, work)
+        return ids
+
     def argmax(self, logits):
         ids = torch.empty(logits.shape[0], dtype=torch.int32, device=self.device)
         finite = torch.empty(logits.shape[0], dtype=torch.int32, device=self.device)

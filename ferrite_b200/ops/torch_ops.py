@@ -180,6 +180,45 @@ class TorchOps:
                 conv_state[slot] = x[-ck1:].to(conv_state.dtype)
         return y
 
+    # ---- multi-head latent attention (absorbed form) ----------------------------------------------------
+    def mla_prep(self, q, kva, norm_w, w_uk_t, inv_freq, row_slot, row_pos, block_table, cache, kv_block, nq, dn, L, R, eps):
+        """Latent RMSNorm + key RoPE into the paged cache [blocks, kv_block, L + R]; returns the absorbed queries
+        [T, nq, L + R] = [q_nope W_uk | rope(q_rope)]."""
+        T = q.shape[0]
+        q3 = q.reshape(T, nq, dn + R).float()
+        kf = kva.float()
+        lat = kf[:, :L] * torch.rsqrt(kf[:, :L].pow(2).mean(-1, keepdim=True) + eps) * (1.0 + norm_w.float())
+        ang = row_pos.float()[:, None] * inv_freq.float()[None, :]
+        cos, sin = ang.cos(), ang.sin()
+        half = R // 2
+
+        def rope(v, c, s):
+            a, b = v[..., :half], v[..., half:]
+            return torch.cat([a * c - b * s, b * c + a * s], -1)
+        kr = rope(kf[:, L:], cos, sin)
+        qr = rope(q3[..., dn:], cos[:, None, :], sin[:, None, :])
+        rows = torch.cat([lat, kr], -1).to(cache.dtype)
+        for t in range(T):
+            slot, pos = int(row_slot[t]), int(row_pos[t])
+            cache[int(block_table[slot, pos // kv_block]), pos % kv_block] = rows[t]
+        qn = torch.einsum("thd,hld->thl", q3[..., :dn], w_uk_t.float())
+        return torch.cat([qn, qr], -1).to(self.dtype)
+
+    def mla_attention(self, qabs, cache, row_slot, row_kvlen, block_table, kv_block, nq, L, R, scale, nsplit=1):
+        T = qabs.shape[0]
+        out = torch.zeros(T, nq, L, dtype=torch.float32, device=qabs.device)
+        for t in range(T):
+            n, slot = int(row_kvlen[t]), int(row_slot[t])
+            nb = (n + kv_block - 1) // kv_block
+            keys = cache[block_table[slot, :nb].long()].reshape(-1, L + R)[:n].float()
+            s = (qabs[t].float() @ keys.t()) * scale
+            out[t] = torch.softmax(s, -1) @ keys[:, :L]
+        return out.to(self.dtype)
+
+    def mla_out(self, ol, w_uv):
+        """ol [T, nq, L] latent-space outputs -> [T, nq * dv] through the per-head value up-projection [nq, dv, L]."""
+        return torch.einsum("thl,hvl->thv", ol.float(), w_uv.float()).reshape(ol.shape[0], -1).to(self.dtype)
+
     # ---- mixture of experts ---------------------------------------------------------------------------
     def moe_route(self, logits, bias, mode, top_k, n_groups, topk_groups, scale):
         from ..config import ModelConfig

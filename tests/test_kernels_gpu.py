@@ -243,3 +243,25 @@ def test_gdn_chunked_scan(ops, tops, nk, nv):
     close(sa[0], sc[0], atol=5e-3, rtol=1e-2)
     assert torch.equal(sa[1], sc[1])
     assert float((ya - yb).abs().max()) < 2e-3
+
+
+def test_device_sampler_filters(ops):
+    """The device sampler keeps exactly the host sampler's candidate set (top-k, then top-p inside it, then min-p) and
+    draws from it with the right frequencies."""
+    from ferrite_b200.engine.sampler import Sampling, dist
+    V = 4096
+    g = torch.Generator(device=DEV).manual_seed(3)
+    logits = (torch.randn(1, V, generator=g, device=DEV) * 3.0)
+    for sp in (Sampling(temperature=0.8, top_k=40, top_p=0.9), Sampling(temperature=1.0, top_k=0, top_p=0.7),
+               Sampling(temperature=1.2, top_k=10, top_p=1.0), Sampling(temperature=1.0, min_p=0.05),
+               Sampling(temperature=0.7, top_k=50, top_p=0.95, min_p=0.02)):
+        p = dist(logits[0].cpu(), sp)
+        support = set(torch.nonzero(p > 0).flatten().tolist())
+        n = 512
+        ids = ops.sample(logits.expand(n, V).contiguous(), [sp] * n, list(range(1000, 1000 + n)))
+        torch.cuda.synchronize()
+        drawn = ids.tolist()
+        assert set(drawn) <= support, (sp, sorted(set(drawn) - support)[:5])
+        top = int(p.argmax())
+        freq = drawn.count(top) / n
+        assert abs(freq - float(p[top])) < 0.08, (sp, freq, float(p[top]))
