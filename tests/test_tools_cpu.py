@@ -1,0 +1,60 @@
+"""The black-box clients against a live server (scripted mock engine) on a local port."""
+import asyncio
+import json
+import socket
+import threading
+import time
+
+from aiohttp import web
+
+from ferrite_b200.server.app import AppState, make_app
+from ferrite_b200.server.engine_api import MockEngine
+from ferrite_b200.server.profiles import GenDefaults
+from ferrite_b200.server.template import ChatTemplate
+from ferrite_b200.server.tokenizer import load_tokenizer
+
+
+def _serve():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    tok = load_tokenizer(None, 4096)
+    app = make_app(lambda: AppState(MockEngine(tok, "mock-model", max_batch=8, max_len=4096), tok, ChatTemplate.from_dir(None),
+                                    GenDefaults.from_dir(None, "default"), "mock-model", 8))
+    loop = asyncio.new_event_loop()
+    started = threading.Event()
+
+    def run():
+        asyncio.set_event_loop(loop)
+        runner = web.AppRunner(app)
+        loop.run_until_complete(runner.setup())
+        loop.run_until_complete(web.TCPSite(runner, "127.0.0.1", port).start())
+        started.set()
+        loop.run_forever()
+    threading.Thread(target=run, daemon=True).start()
+    assert started.wait(20)
+    return f"http://127.0.0.1:{port}", loop
+
+
+def test_conformance_suite_passes_on_the_mock_server(capsys):
+    from ferrite_b200.tools.conformance import main
+    url, loop = _serve()
+    try:
+        rc = main(["--base-url", url, "--mock"])
+    finally:
+        loop.call_soon_threadsafe(loop.stop)
+    out = capsys.readouterr().out
+    assert rc == 0, out
+    assert "FAIL" not in out
+
+
+def test_quickbench_reports_streams(capsys):
+    from ferrite_b200.tools.quickbench import main
+    url, loop = _serve()
+    try:
+        rc = main(["--base-url", url, "--streams", "3", "--prompt-tokens", "16", "--max-tokens", "24"])
+    finally:
+        loop.call_soon_threadsafe(loop.stop)
+    line = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert rc == 0 and line["ok"] == 3 and line["total_tokens"] > 0
