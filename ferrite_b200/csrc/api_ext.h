@@ -96,6 +96,11 @@ int fb_mla_attn(void* out, float* o_part, float* ml_part, const void* qabs, cons
                 const int* row_kvlen, const int* block_table, int max_blocks, int kv_block, int rows, int nq, int L, int R,
                 int nsplit, float scale, cudaStream_t s);
 
+// ---- drafter_ops.cu ----
+int fb_w4_gemv(void* y, const void* x, const void* qweight, const void* scales, const void* biases, const void* res, int M,
+               int N, int K, long ldx, long ldy, cudaStream_t s);
+int fb_topk16(int* ids, float* vals, const void* logits, long stride, int rows, int vocab, int is_f32, cudaStream_t s);
+
 #ifdef __cplusplus
 }
 #endif

@@ -271,9 +271,23 @@ void mla_attn(Tensor out, Tensor o_part, Tensor ml_part, Tensor qabs, Tensor cac
                     (float)scale, cur_stream()), "mla_attn");
 }
 
+void w4_gemv(Tensor y, Tensor x, Tensor qweight, Tensor scales, Tensor biases, c10::optional<Tensor> res) {
+  check(fb_w4_gemv(y.data_ptr(), x.data_ptr(), qweight.data_ptr(), scales.data_ptr(), biases.data_ptr(), cptr(res),
+                   (int)x.size(0), (int)qweight.size(0), (int)x.size(1), (long)x.stride(0), (long)y.stride(0), cur_stream()),
+        "w4_gemv");
+}
+
+void topk16(Tensor ids, c10::optional<Tensor> vals, Tensor logits) {
+  check(fb_topk16(ids.data_ptr<int>(), vals.has_value() ? vals->data_ptr<float>() : nullptr, logits.data_ptr(),
+                  (long)logits.stride(0), (int)logits.size(0), (int)logits.size(1),
+                  logits.scalar_type() == torch::kFloat32 ? 1 : 0, cur_stream()), "topk16");
+}
+
 }  // namespace
 
 void register_ext(pybind11::module_& m) {
+  m.def("w4_gemv", &w4_gemv);
+  m.def("topk16", &topk16);
   m.def("mla_prep", &mla_prep);
   m.def("mla_attn", &mla_attn);
   m.def("exl3_had", &exl3_had);

@@ -295,6 +295,21 @@ class CudaOps:
             self.linear(ol[:, h, :], w_uv[h], out=o[:, h * dv:(h + 1) * dv])
         return o
 
+    # ---- drafter kernels ---------------------------------------------------------------------------
+    def w4_gemv(self, x, qweight, scales, biases, res=None):
+        """y = x W^T, W affine 4-bit in groups of 64: qweight uint32/int32 [N, K/8], scales / biases bf16 [N, K/64]."""
+        y = torch.empty(x.shape[0], qweight.shape[0], dtype=self.dtype, device=self.device)
+        self.launches += 1
+        self.C.w4_gemv(y, x, qweight, scales, biases, res)
+        return y
+
+    def topk16(self, logits):
+        ids = torch.empty(logits.shape[0], 16, dtype=torch.int32, device=self.device)
+        vals = torch.empty(logits.shape[0], 16, dtype=torch.float32, device=self.device)
+        self.launches += 1
+        self.C.topk16(ids, vals, logits)
+        return ids, vals
+
     # ---- GGUF block formats ------------------------------------------------------------------------
     def gguf_dequant(self, raw, type_id, shape):
         """raw: uint8 tensor of GGUF blocks on the device -> bf16 tensor of `shape`."""

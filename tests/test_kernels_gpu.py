@@ -265,3 +265,41 @@ def test_device_sampler_filters(ops):
         top = int(p.argmax())
         freq = drawn.count(top) / n
         assert abs(freq - float(p[top])) < 0.08, (sp, freq, float(p[top]))
+
+
+@pytest.mark.parametrize("M", [1, 4, 8])
+def test_w4_affine_gemv(ops, M):
+    N, K = 320, 1024
+    g = torch.Generator().manual_seed(M)
+    q = torch.randint(0, 16, (N, K), generator=g)
+    scales = (torch.rand(N, K // 64, generator=g) * 0.02 + 0.001).to(torch.bfloat16)
+    biases = (torch.randn(N, K // 64, generator=g) * 0.05).to(torch.bfloat16)
+    packed = torch.zeros(N, K // 8, dtype=torch.int64)
+    for j in range(8):
+        packed |= q[:, j::8] << (4 * j)
+    packed = packed.to(torch.int32) if packed.max() < 2 ** 31 else (packed - (packed >= 2 ** 31) * 2 ** 32).to(torch.int32)
+    w = q.float() * scales.float().repeat_interleave(64, 1) + biases.float().repeat_interleave(64, 1)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    res = torch.randn(M, N, generator=g).to(torch.bfloat16)
+    want = x.float() @ w.t() + res.float()
+    got = ops.w4_gemv(x.to(DEV), packed.to(DEV), scales.to(DEV), biases.to(DEV), res.to(DEV)).float().cpu()
+    assert (got - want).abs().max().item() < 2e-2 * max(1.0, want.abs().max().item())
+
+
+def test_topk16(ops):
+    V = 131072
+    g = torch.Generator(device=DEV).manual_seed(5)
+    logits = torch.randn(3, V, generator=g, device=DEV)
+    logits[1, 1000:1020] = 7.5                       # ties: lower index first
+    ids, vals = ops.topk16(logits)
+    for r in range(3):
+        lr = logits[r].cpu().tolist()
+        order = sorted(range(V), key=lambda i: (-lr[i], i))[:16] if r == 1 else None
+        tv, ti = torch.topk(logits[r], 16)
+        assert torch.allclose(vals[r], tv)
+        if r == 1:
+            assert ids[r].tolist() == order
+        else:
+            assert ids[r].tolist() == ti.tolist()
+    idb, _ = ops.topk16(logits.to(torch.bfloat16))
+    assert idb.shape == (3, 16)
