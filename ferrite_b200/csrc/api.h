@@ -31,6 +31,13 @@ int fb_gemm_bf16(void* Y, const void* X, const void* W, const void* res, int M, 
                  int mode, int split_k, float* workspace, int* counters, int* status, int sm_count, cudaStream_t s);
 long fb_gemm_workspace_bytes(int M, int N, int split_k);
 
+// FP8 (e4m3) GEMM with per-row / per-feature scales, and the activation quantiser (gemm_tcgen05.cu)
+int fb_quant_fp8(void* q, float* scale, const void* x, const void* norm_w, int rows, int K, long ldx, float eps,
+                 cudaStream_t s);
+int fb_gemm_fp8(void* Y, const void* Xq, const void* Wq, const float* scale_m, const float* scale_n, const void* res, int M,
+                int N, int K, long ldy, int mode, int split_k, float* workspace, int* counters, int* status, int sm_count,
+                cudaStream_t s);
+
 // ---- attn.cu ----
 int fb_attn_prep(void* q_out, void* k_cache, void* v_cache, const void* proj, long proj_stride, const void* q_norm,
                  const void* k_norm, const float* inv_freq, const int* row_slot, const int* row_pos,

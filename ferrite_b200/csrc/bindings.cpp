@@ -84,6 +84,21 @@ void gemm(Tensor Y, Tensor X, Tensor W, c10::optional<Tensor> res, int64_t mode,
                      (int*)mptr(status), sm_count(), cur_stream()), "gemm");
 }
 
+void quant_fp8(Tensor q, Tensor scale, Tensor x, c10::optional<Tensor> norm_w, double eps) {
+  check(fb_quant_fp8(q.data_ptr(), scale.data_ptr<float>(), x.data_ptr(), cptr(norm_w), (int)x.size(0), (int)x.size(1),
+                     (long)x.stride(0), (float)eps, cur_stream()), "quant_fp8");
+}
+
+void gemm_fp8(Tensor Y, Tensor Xq, Tensor Wq, c10::optional<Tensor> scale_m, c10::optional<Tensor> scale_n,
+              c10::optional<Tensor> res, int64_t mode, int64_t split_k, c10::optional<Tensor> workspace,
+              c10::optional<Tensor> counters, c10::optional<Tensor> status) {
+  int M = (int)Xq.size(0), K = (int)Xq.size(1);
+  int N = (int)(mode == 1 ? Wq.size(0) / 2 : Wq.size(0));
+  check(fb_gemm_fp8(Y.data_ptr(), Xq.data_ptr(), Wq.data_ptr(), (const float*)cptr(scale_m), (const float*)cptr(scale_n),
+                    cptr(res), M, N, K, (long)Y.stride(0), (int)mode, (int)split_k, (float*)mptr(workspace),
+                    (int*)mptr(counters), (int*)mptr(status), sm_count(), cur_stream()), "gemm_fp8");
+}
+
 void attn_prep(Tensor q_out, Tensor k_cache, Tensor v_cache, Tensor proj, Tensor q_norm, Tensor k_norm,
                Tensor inv_freq, Tensor row_slot, Tensor row_pos, Tensor block_table, int64_t kv_block, int64_t nq,
                int64_t nkv, int64_t hd, int64_t rot, bool gated, double eps, c10::optional<Tensor> status) {
@@ -195,6 +210,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("attn_prefill", &attn_prefill);
   m.def("gdn_conv", &gdn_conv);
   m.def("gdn_rec", &gdn_rec);
+  m.def("quant_fp8", &quant_fp8);
+  m.def("gemm_fp8", &gemm_fp8);
   m.def("gdn_chunk", &gdn_chunk);
   m.def("gdn_chunk_scratch_bytes", &gdn_chunk_scratch_bytes);
   m.def("argmax", &argmax);

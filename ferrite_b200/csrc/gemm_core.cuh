@@ -67,6 +67,12 @@ struct GemmGroups {
 struct GemmArgs {
   GemmComm cm;
   GemmGroups gr;
+  // FP8 (e4m3) operands on kind::f8f6f4: one stage still holds 128 bytes of K per row (128 elements instead of 64),
+  // so the shared-memory layout, the descriptors and their k advance are those of the bf16 path. The epilogue
+  // multiplies by a per-token-row and a per-output-feature scale (either may be null).
+  int fp8;
+  const float* scale_m;     // [M]
+  const float* scale_n;     // [N] (SwiGLU: [2N], gate features then up features)
   void* Y;
   const __nv_bfloat16* res;
   float* workspace;
@@ -128,7 +134,8 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int b_bytes = a.n_b * a.b_box_rows * GM_BK * 2;
   const int stage_bytes = a.n_a * GM_A_BYTES + ((b_bytes + 1023) & ~1023);
-  const int kblocks_total = (a.K + GM_BK - 1) / GM_BK;
+  const int bk_elems = a.fp8 ? 2 * GM_BK : GM_BK;
+  const int kblocks_total = (a.K + bk_elems - 1) / bk_elems;
   const int kb_per_split = (kblocks_total + a.split_k - 1) / a.split_k;
   volatile int* abort_flag = &abort_s;
 
@@ -236,7 +243,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           unsigned char* sa = tiles + (size_t)stage * stage_bytes;
           unsigned char* sb = sa + a.n_a * GM_A_BYTES;
           mbar_expect_tx(&full_bar[stage], tx);
-          const int kx = kb * GM_BK;
+          const int kx = kb * bk_elems;
           // A boxes: swapped SwiGLU loads gate rows and up rows (N apart) as two boxes
           for (int i = 0; i < a.n_a; ++i)
             tma_load_2d(sa + i * GM_A_BYTES, &tmA, &full_bar[stage], kx, (COMM == 3 ? g_row0 : ta * GM_BM) + i * a.N);
@@ -304,7 +311,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (elect_one()) {
-      const uint32_t idesc = umma_idesc(1, 1, GM_BM, (uint32_t)a.bn);
+      const uint32_t idesc = a.fp8 ? umma_idesc(0, 0, GM_BM, (uint32_t)a.bn) : umma_idesc(1, 1, GM_BM, (uint32_t)a.bn);
       int stage = 0; uint32_t phase = 0;
       int buf = 0; uint32_t tphase[2] = {0, 0};
       bool ok = true;
@@ -325,8 +332,12 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             const uint64_t da = umma_desc_k128(sa + i * GM_A_BYTES);
 #pragma unroll
             for (int k = 0; k < GM_BK / 16; ++k)
-              tc_mma_f16(d0 + (uint32_t)(i * a.bn), da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc,
-                         (kb > kb0 || k > 0) ? 1u : 0u);
+              if (a.fp8)
+                tc_mma_f8f6f4(d0 + (uint32_t)(i * a.bn), da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc,
+                              (kb > kb0 || k > 0) ? 1u : 0u);
+              else
+                tc_mma_f16(d0 + (uint32_t)(i * a.bn), da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc,
+                           (kb > kb0 || k > 0) ? 1u : 0u);
           }
           tc_commit(&empty_bar[stage]);               // frees the smem slot once these MMAs have read it
           if (++stage == a.stages) { stage = 0; phase ^= 1u; }
@@ -505,9 +516,16 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             const int n = n0 + c;
             float v[32];
 #pragma unroll
+            const float sm_row = a.scale_m ? a.scale_m[m] : 1.f;
+#pragma unroll
             for (int j = 0; j < 32; ++j) {
-              float x = __uint_as_float(r0[j]);
-              v[j] = a.dual ? siluf_(x) * __uint_as_float(r1[j]) : x;
+              float x = __uint_as_float(r0[j]) * sm_row;
+              float u = a.dual ? __uint_as_float(r1[j]) * sm_row : 0.f;
+              if (a.scale_n && n + j < a.N) {
+                x *= a.scale_n[n + j];
+                if (a.dual) u *= a.scale_n[a.N + n + j];
+              }
+              v[j] = a.dual ? siluf_(x) * u : x;
             }
             if (n + 32 <= a.N) {
               if (a.res) {
@@ -552,8 +570,9 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
               for (int j = 0; j < 16; ++j) {
                 const int m = m0 + c + j;
                 if (m < a.M) {
-                  float x = __uint_as_float(r0[j]);
-                  if (a.dual) x = siluf_(x) * __uint_as_float(r1[j]);
+                  const float sc = (a.scale_m ? a.scale_m[m] : 1.f);
+                  float x = __uint_as_float(r0[j]) * sc * (a.scale_n ? a.scale_n[n] : 1.f);
+                  if (a.dual) x = siluf_(x) * (__uint_as_float(r1[j]) * sc * (a.scale_n ? a.scale_n[a.N + n] : 1.f));
                   if (a.res) x += bf2f(a.res[(size_t)m * a.ldy + n]);
                   Yb[(size_t)m * a.ldy + n] = f2bf(x);
                 }
@@ -596,6 +615,9 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 if (a.dual) u += __ldcg(p + (size_t)(a.bn + c) * GM_BM + etid);
               }
               if (n_ok) {
+                const float sc = (a.scale_m ? a.scale_m[m] : 1.f);
+                g *= sc * (a.scale_n ? a.scale_n[n] : 1.f);
+                if (a.dual) u *= sc * (a.scale_n ? a.scale_n[a.N + n] : 1.f);
                 float x = a.dual ? siluf_(g) * u : g;
                 if (a.res) x += bf2f(a.res[(size_t)m * a.ldy + n]);
                 Yb[(size_t)m * a.ldy + n] = f2bf(x);
@@ -673,12 +695,28 @@ static int make_tmap_bf16_2d(CUtensorMap* out, const void* base, uint64_t rows, 
   return r == CUDA_SUCCESS ? 0 : -12;
 }
 
+// 2-D byte tensor map (FP8 operands): box = {128 bytes, box_rows}, 128-byte swizzle
+static int make_tmap_u8_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return -10;
+  if ((uintptr_t)base % 16 || ld % 16) return -11;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld};
+  cuuint32_t box[2] = {128, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -12;
+}
+
 static int round_up_pow2(int v) { int p = 32; while (p < v) p <<= 1; return p; }
 
 struct GemmPlan { GemmArgs a; int grid; size_t smem; };
 
-static int plan_gemm(GemmPlan& p, int M, int N, int K, int mode, int split_k, int sm_count) {
+static int plan_gemm(GemmPlan& p, int M, int N, int K, int mode, int split_k, int sm_count, int fp8 = 0) {
   GemmArgs& a = p.a;
+  a.fp8 = fp8; a.scale_m = nullptr; a.scale_n = nullptr;
   a.M = M; a.N = N; a.K = K;
   a.dual = mode == 1;
   a.swap = M <= 64;
@@ -700,7 +738,8 @@ static int plan_gemm(GemmPlan& p, int M, int N, int K, int mode, int split_k, in
     a.tiles_b = (N + ncols_out - 1) / ncols_out;
     a.split_k = 1;
   }
-  int kblocks = (K + GM_BK - 1) / GM_BK;
+  const int bk_elems = fp8 ? 2 * GM_BK : GM_BK;
+  int kblocks = (K + bk_elems - 1) / bk_elems;
   if (a.split_k > kblocks) a.split_k = kblocks;
   {
     // every split must own at least one k block (an empty split would publish an unwritten accumulator)

@@ -113,6 +113,33 @@ class CudaOps:
         self.C.gemm(y, x, w, res, 1 if swiglu else 0, split, ws, cnt, self.status_word)
         return y.float() if out_f32 else y
 
+    # ---- FP8 (e4m3) weights and activations -----------------------------------------------------------
+    @staticmethod
+    def quantize_weight_fp8(w):
+        """Per-output-feature e4m3 quantisation of a [N, K] weight: (codes uint8 [N, K], scales fp32 [N])."""
+        wf = w.float()
+        sc = (wf.abs().amax(1) / 448.0).clamp_min(1e-12)
+        q = (wf / sc[:, None]).to(torch.float8_e4m3fn).view(torch.uint8)
+        return q.contiguous(), sc.contiguous()
+
+    def linear_fp8(self, x, wq, w_scale, norm_w=None, eps=1e-6, res=None, swiglu=False):
+        """y = x W^T with both operands in e4m3 on the tcgen05 f8f6f4 path: rows are quantised on the fly (optionally
+        after RMSNorm) with one scale per row; the epilogue applies row scale x feature scale."""
+        M, K = x.shape
+        N = wq.shape[0] // 2 if swiglu else wq.shape[0]
+        xq = torch.empty(M, K, dtype=torch.uint8, device=self.device)
+        xs = torch.empty(M, dtype=torch.float32, device=self.device)
+        self.C.quant_fp8(xq, xs, x, norm_w, eps)
+        y = torch.empty(M, (N + 7) // 8 * 8, dtype=self.dtype, device=self.device)[:, :N]
+        split = self._split_k(M, N, K // 2) if M <= 64 else 1
+        ws = cnt = None
+        if split > 1:
+            ws = self._workspace(self.C.gemm_workspace_bytes(M, N, split))
+            cnt = self._counters
+        self.launches += 2
+        self.C.gemm_fp8(y, xq, wq, xs, w_scale, res, 1 if swiglu else 0, split, ws, cnt, self.status_word)
+        return y
+
     # ---- NVFP4 weights x NVFP4 activations on the block-scaled tensor-core GEMM -------------------------
     def quant_nvfp4(self, x, norm_w=None, eps=1e-6):
         """Quantise activation rows (optionally after RMSNorm) to e2m1 codes + tiled e4m3 scales + per-row scale."""

@@ -220,5 +220,12 @@ class TensorParallel:
         """Control plane: rank 0's step descriptor to every rank (reference: the follower RPC stream,
         `crates/fe-model/src/follow.rs`)."""
         box = [obj]
-        dist.broadcast_object_list(box, src=src, group=self.group)
+        dist.broadcast_object_list(box, src=src, group=self.ctrl_group())
         return box[0]
+
+    def ctrl_group(self):
+        """CPU-side (gloo) group for control records, so they neither touch the GPUs nor wait on their streams. Created
+        on first use: every rank must reach its first `broadcast_object` together."""
+        if getattr(self, "_ctrl", None) is None:
+            self._ctrl = self.group if dist.get_backend(self.group) == "gloo" else dist.new_group(backend="gloo")
+        return self._ctrl

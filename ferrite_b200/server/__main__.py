@@ -34,7 +34,30 @@ def build_engine(args, tok):
     if args.model_dir and any(f.endswith(".safetensors") for f in os.listdir(args.model_dir)):
         from ..formats.loader import load_model_weights
         weights = load_model_weights(args.model_dir, cfg)
-    eng = Engine(cfg, weights, ecfg, device=args.device or None, seed=0)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    tp = None
+    if world > 1:
+        # launched with torch.distributed.run: every rank builds its shard; rank 0 schedules and serves, the others
+        # replay its engine calls (leader / follower control, `engine/follow.py`)
+        import torch.distributed as dist
+
+        from ..parallel.tp import TensorParallel
+        local = int(os.environ.get("LOCAL_RANK", "0"))
+        on_gpu = torch.cuda.is_available() and args.device != "cpu"
+        if on_gpu:
+            torch.cuda.set_device(local)
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl" if on_gpu else "gloo",
+                                **({"device_id": torch.device("cuda", local)} if on_gpu else {}))
+        tp = TensorParallel(dist.group.WORLD, f"cuda:{local}" if on_gpu else "cpu")
+        args.device = f"cuda:{local}" if on_gpu else "cpu"
+    eng = Engine(cfg, weights, ecfg, device=args.device or None, seed=0, tp=tp)
+    if tp is not None:
+        from ..engine.follow import Leader, follow
+        if tp.rank != 0:
+            follow(eng, tp)
+            raise SystemExit(0)
+        eng = Leader(eng, tp)
     opts = SchedOptions.from_env()
     return SchedulerEngine(Scheduler(eng, opts), args.served_model_name)
 
@@ -73,6 +96,10 @@ def main(argv=None) -> int:
         return AppState(engine_box["e"], tok, ChatTemplate.from_dir(args.model_dir or None),
                         GenDefaults.from_dir(args.model_dir or None, args.profile), args.served_model_name,
                         args.max_concurrent)
+
+    if int(os.environ.get("RANK", "0")) > 0:          # tensor-parallel follower: no HTTP side, replay until told to stop
+        build_engine(args, tok)
+        return 0
 
     app = make_app(factory)
 

@@ -303,3 +303,28 @@ def test_topk16(ops):
             assert ids[r].tolist() == ti.tolist()
     idb, _ = ops.topk16(logits.to(torch.bfloat16))
     assert idb.shape == (3, 16)
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 512, 1024), (8, 384, 2048), (48, 1024, 1024), (300, 640, 1536), (2048, 1024, 4096)])
+def test_gemm_fp8(ops, M, N, K):
+    """e4m3 x e4m3 on the tcgen05 f8f6f4 path against the fp32 product of the dequantised operands."""
+    x, w = rnd(M, K, seed=1), rnd(N, K, scale=0.05, seed=2)
+    res = rnd(M, N, seed=3)
+    wq, ws = ops.quantize_weight_fp8(w)
+    got = ops.linear_fp8(x, wq, ws, res=res)
+    xs = (x.float().abs().amax(1) / 448.0).clamp_min(1e-12)
+    xd = (x.float() / xs[:, None]).to(torch.float8_e4m3fn).float() * xs[:, None]
+    wd = wq.view(torch.float8_e4m3fn).float() * ws[:, None]
+    want = xd @ wd.t() + res.float()
+    assert (got.float() - want).abs().max().item() < 2e-2 * max(1.0, want.abs().max().item())
+
+
+@pytest.mark.parametrize("M", [4, 200])
+def test_gemm_fp8_norm_swiglu(ops, tops, M):
+    N, K = 512, 1024
+    x, w, nw = rnd(M, K, seed=1), rnd(2 * N, K, scale=0.05, seed=2), rnd(K, scale=0.1, seed=3)
+    wq, ws = ops.quantize_weight_fp8(w)
+    got = ops.linear_fp8(x, wq, ws, norm_w=nw, swiglu=True)
+    want = tops.linear(x, wq.view(torch.float8_e4m3fn).float() * ws[:, None], norm_w=nw, eps=1e-6, swiglu=True)
+    err = (got.float() - want.float()).abs().max().item()
+    assert err < 6e-2 * max(1.0, want.abs().max().item()), err        # includes the e4m3 rounding of the activations
