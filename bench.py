@@ -197,6 +197,26 @@ def main():
         ms4, _, _, _ = decode_run(4, K, W, e2e=False)
         extras["decode_4streams_tok_s"] = 4 * K / (ms4 / 1e3)
         extras["decode_4streams_vs_baseline"] = extras["decode_4streams_tok_s"] / BASELINE_DECODE_4
+    if not args.no_extras and args.streams == 1:
+        # speculative verification: one step scores 1 + 16 drafted rows of one stream without committing them; with k
+        # accepted drafts per step the stream advances k + 1 tokens in this time
+        p0 = eng.slot_len[0]
+        rows = feed[0][:17]
+
+        def verify():
+            eng.forward([Segment(0, p0, rows, "all")], commit=False, greedy=True)
+        for _ in range(W):
+            verify()
+        barrier()
+        e0, e1 = torch.cuda.Event(True), torch.cuda.Event(True)
+        e0.record()
+        for _ in range(K):
+            verify()
+        e1.record()
+        barrier()
+        vms = max_over_ranks(e0.elapsed_time(e1)) / K
+        extras["verify_17rows_ms"] = vms
+        extras["spec_tok_s_at_8_accepted"] = 9.0 / (vms / 1e3)
     extras["prefill_tok_s"] = args.ctx / (prefill_ms / 1e3)
     extras["prefill_ctx"] = args.ctx
     extras["prefill_vs_baseline"] = extras["prefill_tok_s"] / BASELINE_PREFILL_2K

@@ -59,6 +59,10 @@ int fb_gdn_conv(void* out, const void* proj, long proj_stride, const void* conv_
 int fb_gdn_rec(float* y, float* rec_state, void* conv_state, const void* qkv, const void* proj, long proj_stride,
                const float* A_log, const float* dt_bias, const int* seg_slot, const int* seg_row0,
                const int* seg_nrows, int nseg, int nk, int nv, int dk, int dv, float eps, int commit, cudaStream_t s);
+// decode rows: conv + recurrence + gated norm of a layer in one launch (bf16 out [rows][nv * dv])
+int fb_gdn_step(void* out, float* rec_state, void* conv_state, const void* proj, long proj_stride, const void* conv_w,
+                const float* A_log, const float* dt_bias, const void* gnorm_w, const int* seg_slot, const int* seg_row0,
+                const int* seg_nrows, int nseg, int nk, int nv, int dk, int dv, float eps, int commit, cudaStream_t s);
 // chunked scan for prompt-sized segments; `scratch` holds fb_gdn_chunk_scratch_bytes(rows, nseg, nv, dk) bytes
 long fb_gdn_chunk_scratch_bytes(int rows, int nseg, int nv, int dk);
 int fb_gdn_chunk(float* y, float* rec_state, void* conv_state, float* scratch, const void* qkv, const void* proj,

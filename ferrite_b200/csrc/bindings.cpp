@@ -148,6 +148,16 @@ void gdn_rec(Tensor y, Tensor rec_state, Tensor conv_state, Tensor qkv, Tensor p
         "gdn_rec");
 }
 
+void gdn_step(Tensor out, Tensor rec_state, Tensor conv_state, Tensor proj, Tensor conv_w, Tensor A_log, Tensor dt_bias,
+              Tensor gnorm_w, Tensor seg_slot, Tensor seg_row0, Tensor seg_nrows, int64_t nk, int64_t nv, int64_t dk,
+              int64_t dv, double eps, bool commit) {
+  check(fb_gdn_step(out.data_ptr(), rec_state.data_ptr<float>(), conv_state.data_ptr(), proj.data_ptr(),
+                    (long)proj.stride(0), conv_w.data_ptr(), A_log.data_ptr<float>(), dt_bias.data_ptr<float>(),
+                    gnorm_w.data_ptr(), seg_slot.data_ptr<int>(), seg_row0.data_ptr<int>(), seg_nrows.data_ptr<int>(),
+                    (int)seg_slot.numel(), (int)nk, (int)nv, (int)dk, (int)dv, (float)eps, commit ? 1 : 0, cur_stream()),
+        "gdn_step");
+}
+
 int64_t gdn_chunk_scratch_bytes(int64_t rows, int64_t nseg, int64_t nv, int64_t dk) {
   return fb_gdn_chunk_scratch_bytes((int)rows, (int)nseg, (int)nv, (int)dk);
 }
@@ -210,6 +220,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("attn_prefill", &attn_prefill);
   m.def("gdn_conv", &gdn_conv);
   m.def("gdn_rec", &gdn_rec);
+  m.def("gdn_step", &gdn_step);
   m.def("quant_fp8", &quant_fp8);
   m.def("gemm_fp8", &gemm_fp8);
   m.def("gdn_chunk", &gdn_chunk);

@@ -143,6 +143,136 @@ gdn_rec_kernel(float* __restrict__ y, float* __restrict__ rec_state, __nv_bfloat
   }
 }
 
+// Decode-row fusion of the three kernels above: causal conv + SiLU of this head's q / k / v channels, the delta-rule
+// recurrence, and the gated per-head RMSNorm (y * rsqrt(mean y^2 + eps) * w * silu(z)) in one launch per layer.
+// Same arithmetic as the separate kernels (the conv output is rounded to bf16 as it would be when stored), so both
+// paths agree to fp32 rounding of the norm's sum. blockDim = DV * 8 as in gdn_rec_kernel.
+template <int DK, int DV>
+__global__ void __launch_bounds__(DV * 8)
+gdn_step_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ rec_state, __nv_bfloat16* __restrict__ conv_state,
+                const __nv_bfloat16* __restrict__ proj, long proj_stride, const __nv_bfloat16* __restrict__ conv_w,
+                const float* __restrict__ A_log, const float* __restrict__ dt_bias,
+                const __nv_bfloat16* __restrict__ gnorm_w, const int* __restrict__ seg_slot,
+                const int* __restrict__ seg_row0, const int* __restrict__ seg_nrows, int nk, int nv, float eps,
+                int commit) {
+  pdl_launch_dependents();
+  pdl_wait();
+  constexpr int PARTS = 8, RP = DK / PARTS, CK = 4;
+  __shared__ float qs[DK], ks[DK], vs[DV];
+  __shared__ float red1[PARTS][DV], red2[PARTS][DV];
+  __shared__ float ssq[2][DK / 32], ssn[DV / 32];
+  const int h = blockIdx.x, seg = blockIdx.y;
+  const int tid = threadIdx.x, col = tid % DV, part = tid / DV;
+  const int n = seg_nrows[seg];
+  if (n <= 0) return;
+  const int row0 = seg_row0[seg], slot = seg_slot[seg];
+  const int kh = h / (nv / nk);
+  const int conv_dim = 2 * nk * DK + nv * DV;
+  const int q_off = kh * DK, k_off = nk * DK + kh * DK, v_off = 2 * nk * DK + h * DV;
+  const int z_off = conv_dim + h * DV;
+  const int b_off = conv_dim + nv * DV + h, a_off = b_off + nv;
+  float* Sg = rec_state + (((size_t)slot * nv + h) * DK) * DV;
+  __nv_bfloat16* st = conv_state + (size_t)slot * (CK - 1) * conv_dim;
+  float S[RP];
+#pragma unroll
+  for (int i = 0; i < RP; ++i) S[i] = Sg[(size_t)(part * RP + i) * DV + col];
+  const float expA = __expf(A_log[h]);
+  const float dtb = dt_bias[h];
+  const float qscale = rsqrtf((float)DK);
+  // sliding conv windows of the channels this thread produces: q and k (tid < DK), v (tid < DV)
+  float wq[CK], wk[CK], wv[CK], winq[CK - 1], wink[CK - 1], winv[CK - 1];
+  if (tid < DK) {
+#pragma unroll
+    for (int j = 0; j < CK; ++j) { wq[j] = bf2f(conv_w[(size_t)(q_off + tid) * CK + j]); wk[j] = bf2f(conv_w[(size_t)(k_off + tid) * CK + j]); }
+#pragma unroll
+    for (int j = 0; j < CK - 1; ++j) { winq[j] = bf2f(st[(size_t)j * conv_dim + q_off + tid]); wink[j] = bf2f(st[(size_t)j * conv_dim + k_off + tid]); }
+  }
+  if (tid < DV) {
+#pragma unroll
+    for (int j = 0; j < CK; ++j) wv[j] = bf2f(conv_w[(size_t)(v_off + tid) * CK + j]);
+#pragma unroll
+    for (int j = 0; j < CK - 1; ++j) winv[j] = bf2f(st[(size_t)j * conv_dim + v_off + tid]);
+  }
+  const float gw = bf2f(gnorm_w[col]);
+
+  for (int r = 0; r < n; ++r) {
+    const __nv_bfloat16* pr = proj + (size_t)(row0 + r) * proj_stride;
+    if (tid < DK) {
+      const float xq = bf2f(pr[q_off + tid]), xk = bf2f(pr[k_off + tid]);
+      const float qv = bf2f(f2bf(siluf_(wq[0] * winq[0] + wq[1] * winq[1] + wq[2] * winq[2] + wq[3] * xq)));
+      const float kv = bf2f(f2bf(siluf_(wk[0] * wink[0] + wk[1] * wink[1] + wk[2] * wink[2] + wk[3] * xk)));
+      winq[0] = winq[1]; winq[1] = winq[2]; winq[2] = xq;
+      wink[0] = wink[1]; wink[1] = wink[2]; wink[2] = xk;
+      qs[tid] = qv; ks[tid] = kv;
+      const float sq = warp_sum(qv * qv), sk = warp_sum(kv * kv);
+      if ((tid & 31) == 0) { ssq[0][tid >> 5] = sq; ssq[1][tid >> 5] = sk; }
+    }
+    if (tid < DV) {
+      const float xv = bf2f(pr[v_off + tid]);
+      vs[tid] = bf2f(f2bf(siluf_(wv[0] * winv[0] + wv[1] * winv[1] + wv[2] * winv[2] + wv[3] * xv)));
+      winv[0] = winv[1]; winv[1] = winv[2]; winv[2] = xv;
+    }
+    __syncthreads();
+    float sq = 0.f, sk = 0.f;
+#pragma unroll
+    for (int i = 0; i < DK / 32; ++i) { sq += ssq[0][i]; sk += ssq[1][i]; }
+    const float rq = rsqrtf(sq + eps) * qscale, rk = rsqrtf(sk + eps);
+    const float beta = sigmoidf_(bf2f(pr[b_off]));
+    const float g = __expf(-expA * softplusf_(bf2f(pr[a_off]) + dtb));
+    float p = 0.f;
+#pragma unroll
+    for (int i = 0; i < RP; ++i) p = fmaf(S[i], ks[part * RP + i], p);
+    red1[part][col] = p;
+    __syncthreads();
+    float kvv = 0.f;
+#pragma unroll
+    for (int i = 0; i < PARTS; ++i) kvv += red1[i][col];
+    kvv *= g * rk;
+    const float delta = (vs[col] - kvv) * beta;
+    float yp = 0.f;
+#pragma unroll
+    for (int i = 0; i < RP; ++i) {
+      S[i] = fmaf(ks[part * RP + i] * rk, delta, S[i] * g);
+      yp = fmaf(S[i], qs[part * RP + i], yp);
+    }
+    red2[part][col] = yp;
+    __syncthreads();
+    float yy = 0.f;
+    if (part == 0) {
+#pragma unroll
+      for (int i = 0; i < PARTS; ++i) yy += red2[i][col];
+      yy *= rq;
+      const float s2 = warp_sum(yy * yy);
+      if ((tid & 31) == 0) ssn[tid >> 5] = s2;
+    }
+    __syncthreads();
+    if (part == 0) {
+      float ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < DV / 32; ++i) ss += ssn[i];
+      const float rn = rsqrtf(ss / (float)DV + eps);
+      out[((size_t)(row0 + r) * nv + h) * DV + col] = f2bf(yy * rn * gw * siluf_(bf2f(pr[z_off + col])));
+    }
+  }
+  if (commit) {
+#pragma unroll
+    for (int i = 0; i < RP; ++i) Sg[(size_t)(part * RP + i) * DV + col] = S[i];
+    // conv tail = the windows after the last row (q / k channels: first head of the group writes them)
+    const bool own_qk = (h % (nv / nk)) == 0;
+    if (tid < DK && own_qk) {
+#pragma unroll
+      for (int j = 0; j < CK - 1; ++j) {
+        st[(size_t)j * conv_dim + q_off + tid] = f2bf(winq[j]);
+        st[(size_t)j * conv_dim + k_off + tid] = f2bf(wink[j]);
+      }
+    }
+    if (tid < DV) {
+#pragma unroll
+      for (int j = 0; j < CK - 1; ++j) st[(size_t)j * conv_dim + v_off + tid] = f2bf(winv[j]);
+    }
+  }
+}
+
 }  // namespace fb
 
 using namespace fb;
@@ -171,6 +301,25 @@ extern "C" int fb_gdn_rec(float* y, float* rec_state, void* conv_state, const vo
   else if (dk == 64 && dv == 64)
     launch_pdl(gdn_rec_kernel<64, 64>, dim3(grid), dim3(512), (size_t)(0), s, y, rec_state, (__nv_bfloat16*)conv_state, (const __nv_bfloat16*)qkv,
         (const __nv_bfloat16*)proj, proj_stride, A_log, dt_bias, seg_slot, seg_row0, seg_nrows, nk, nv, eps, commit);
+  else return -2;
+  return (int)cudaGetLastError();
+}
+
+extern "C" int fb_gdn_step(void* out, float* rec_state, void* conv_state, const void* proj, long proj_stride,
+                           const void* conv_w, const float* A_log, const float* dt_bias, const void* gnorm_w,
+                           const int* seg_slot, const int* seg_row0, const int* seg_nrows, int nseg, int nk, int nv, int dk,
+                           int dv, float eps, int commit, cudaStream_t s) {
+  if (nseg <= 0) return 0;
+  if (nv % nk) return -1;
+  dim3 grid(nv, nseg);
+  if (dk == 128 && dv == 128)
+    launch_pdl(gdn_step_kernel<128, 128>, dim3(grid), dim3(1024), (size_t)(0), s, (__nv_bfloat16*)out, rec_state,
+               (__nv_bfloat16*)conv_state, (const __nv_bfloat16*)proj, proj_stride, (const __nv_bfloat16*)conv_w, A_log, dt_bias,
+               (const __nv_bfloat16*)gnorm_w, seg_slot, seg_row0, seg_nrows, nk, nv, eps, commit);
+  else if (dk == 64 && dv == 64)
+    launch_pdl(gdn_step_kernel<64, 64>, dim3(grid), dim3(512), (size_t)(0), s, (__nv_bfloat16*)out, rec_state,
+               (__nv_bfloat16*)conv_state, (const __nv_bfloat16*)proj, proj_stride, (const __nv_bfloat16*)conv_w, A_log, dt_bias,
+               (const __nv_bfloat16*)gnorm_w, seg_slot, seg_row0, seg_nrows, nk, nv, eps, commit);
   else return -2;
   return (int)cudaGetLastError();
 }

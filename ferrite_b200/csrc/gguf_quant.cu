@@ -116,8 +116,8 @@ __global__ void q8_1_quant_kernel(unsigned char* __restrict__ out, const __nv_bf
   unsigned char* o = out + blk * 36;
   o[4 + lane] = (unsigned char)(signed char)q;
   if (lane == 0) {
-    const unsigned short hd = __half_as_ushort(__float2half_rn(d)), hs = __half_as_ushort(__float2half_rn(d * s));
-    o[0] = hd & 0xFF; o[1] = hd >> 8; o[2] = hs & 0xFF; o[3] = hs >> 8;
+    __half2 hh = __floats2half2_rn(d, d * s);                 // blocks are 36 bytes, so `o` is 4-byte aligned
+    *reinterpret_cast<__half2*>(o) = hh;
   }
 }
 

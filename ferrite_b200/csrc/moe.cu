@@ -46,8 +46,9 @@ __global__ void __launch_bounds__(32) route_kernel(int* __restrict__ ids, float*
       sel[j] = e < n_exp ? sc[j] + (bias ? bias[e] : 0.f) : -INFINITY;
     }
     if (n_groups > 1 && topk_groups < n_groups) {
-      // a group spans gl = 32 / n_groups lanes; its score is the sum of its two best biased scores
-      const int gl = 32 / n_groups;
+      // a group spans gl = (experts per group) / (experts per lane) lanes; its score is the sum of its two best
+      // biased scores
+      const int gl = (n_exp / n_groups) / per;
       float b1 = -INFINITY, b2 = -INFINITY;
       for (int j = 0; j < per; ++j) { float v = sel[j]; if (v > b1) { b2 = b1; b1 = v; } else if (v > b2) b2 = v; }
       for (int o = 1; o < gl; o <<= 1) {
@@ -196,7 +197,13 @@ extern "C" int fb_moe_route(int* ids, float* wts, const float* logits, const flo
                             int mode, int n_groups, int topk_groups, float scale, cudaStream_t s) {
   if (rows <= 0) return 0;
   if (n_exp > 32 * RT_MAXPL || top_k > 32 || top_k > n_exp) return -1;
-  if (mode == 1 && n_groups > 1 && (32 % n_groups || n_exp % 32)) return -2;
+  if (mode == 1 && n_groups > 1) {
+    // a group must cover a power-of-two number of whole lanes
+    const int per = (n_exp + 31) / 32;
+    if (n_exp % n_groups || (n_exp / n_groups) % per) return -2;
+    const int gl = (n_exp / n_groups) / per;
+    if (gl < 1 || (gl & (gl - 1)) || n_groups * gl > 32) return -2;
+  }
   return (int)launch_pdl(route_kernel, dim3(rows), dim3(32), 0, s, ids, wts, logits, bias, n_exp, top_k, mode,
                          n_groups, topk_groups, scale);
 }

@@ -61,6 +61,7 @@ class BlockPool:
 
 
 FLASH_MIN_ROWS = 16      # segments longer than this go to the flash prefill kernel (reference FLASH_MIN 17)
+GDN_STEP_MAX_ROWS = 16    # decode / verify rows per segment handled by the fused conv + recurrence + norm kernel
 GDN_CHUNK_MIN_ROWS = 24  # segments this long go through the chunked GDN scan instead of the row-by-row recurrence
 
 
@@ -357,6 +358,21 @@ class Executor:
             p = f"l{i}."
             if kind == "gdn":
                 proj = col(x, w[p + "in_proj"], w[p + "input_norm"])
+                if hasattr(ops, "gdn_step") and max_seg_rows <= GDN_STEP_MAX_ROWS and c.lin_dk == c.lin_dv and c.lin_dk in (64, 128):
+                    if not commit:
+                        self.verify_proj[i] = proj
+                    o = ops.gdn_step(proj, w[p + "conv_w"], self.rec_state[i], self.conv_state[i], w[p + "A_log"],
+                                     w[p + "dt_bias"], w[p + "gnorm_w"], mv["sslot"], mv["srow0"], mv["snrows"],
+                                     c.lin_k_heads, c.lin_v_heads, c.lin_dk, c.lin_dv, eps, commit=commit)
+                    x = row(o, w[p + "out_proj"], x)
+                    if c.is_moe(i):
+                        x = self._moe_ffn_sp(x, i, col, row) if sp else self._moe_ffn(x, i)
+                    else:
+                        act = col(x, w[p + "gate_up"], w[p + "post_norm"], swiglu=True)
+                        x = row(act, w[p + "down"], x)
+                    if i in c.tap_layers:
+                        self.taps.append(self.tp.gather_rows(x, T) if sp else x)
+                    continue
                 qkv = ops.gdn_conv(proj, w[p + "conv_w"], self.conv_state[i], mv["sslot"], mv["srow0"], mv["snrows"],
                                    c.conv_dim, **({"max_rows": max_seg_rows} if ops.name == "cuda" else {}))
                 if not commit:

@@ -275,6 +275,15 @@ class CudaOps:
                         proj.shape[0] if max_rows is None else max_rows)
         return out
 
+    def gdn_step(self, proj, conv_w, rec_state, conv_state, A_log, dt_bias, gnorm_w, seg_slot, seg_row0, seg_nrows, nk, nv,
+                 dk, dv, eps, commit=True):
+        """Decode rows: conv + recurrence + gated norm in one launch; returns bf16 [rows, nv * dv]."""
+        out = torch.empty(proj.shape[0], nv * dv, dtype=self.dtype, device=self.device)
+        self.launches += 1
+        self.C.gdn_step(out, rec_state, conv_state, proj, conv_w, A_log, dt_bias, gnorm_w, seg_slot, seg_row0, seg_nrows, nk,
+                        nv, dk, dv, eps, commit)
+        return out
+
     def gdn_rec(self, qkv, proj, rec_state, conv_state, A_log, dt_bias, seg_slot, seg_row0, seg_nrows, nk, nv, dk, dv,
                 eps, commit=True, chunked=False, max_rows=None):
         y = torch.empty(qkv.shape[0], nv * dv, dtype=torch.float32, device=self.device)
