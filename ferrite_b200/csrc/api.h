@@ -31,6 +31,9 @@ int fb_gemm_bf16(void* Y, const void* X, const void* W, const void* res, int M, 
                  int mode, int split_k, float* workspace, int* counters, int* status, int sm_count, cudaStream_t s);
 long fb_gemm_workspace_bytes(int M, int N, int split_k);
 
+// 2..32 rows: weight-streaming linear on mma.sync with in-register A fragments (gemv_mma.cu)
+int fb_gemv_mma(void* y, const void* x, const void* w, const void* norm_w, const void* res, int M, int N, int K, long ldx,
+                long ldy, float eps, int mode, int out_f32, cudaStream_t s);
 // FP8 (e4m3) GEMM with per-row / per-feature scales, and the activation quantiser (gemm_tcgen05.cu)
 int fb_quant_fp8(void* q, float* scale, const void* x, const void* norm_w, int rows, int K, long ldx, float eps,
                  cudaStream_t s);

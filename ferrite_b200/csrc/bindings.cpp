@@ -84,6 +84,15 @@ void gemm(Tensor Y, Tensor X, Tensor W, c10::optional<Tensor> res, int64_t mode,
                      (int*)mptr(status), sm_count(), cur_stream()), "gemm");
 }
 
+void gemv_mma(Tensor Y, Tensor X, Tensor W, c10::optional<Tensor> norm_w, c10::optional<Tensor> res, double eps,
+              int64_t mode) {
+  int M = (int)X.size(0), K = (int)X.size(1);
+  int N = (int)(mode == 1 ? W.size(0) / 2 : W.size(0));
+  check(fb_gemv_mma(Y.data_ptr(), X.data_ptr(), W.data_ptr(), cptr(norm_w), cptr(res), M, N, K, (long)X.stride(0),
+                    (long)Y.stride(0), (float)eps, (int)mode, Y.scalar_type() == torch::kFloat32 ? 1 : 0, cur_stream()),
+        "gemv_mma");
+}
+
 void quant_fp8(Tensor q, Tensor scale, Tensor x, c10::optional<Tensor> norm_w, double eps) {
   check(fb_quant_fp8(q.data_ptr(), scale.data_ptr<float>(), x.data_ptr(), cptr(norm_w), (int)x.size(0), (int)x.size(1),
                      (long)x.stride(0), (float)eps, cur_stream()), "quant_fp8");
@@ -220,6 +229,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("attn_prefill", &attn_prefill);
   m.def("gdn_conv", &gdn_conv);
   m.def("gdn_rec", &gdn_rec);
+  m.def("gemv_mma", &gemv_mma);
   m.def("gdn_step", &gdn_step);
   m.def("quant_fp8", &quant_fp8);
   m.def("gemm_fp8", &gemm_fp8);

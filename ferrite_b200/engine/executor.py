@@ -60,8 +60,8 @@ class BlockPool:
         return len(self.free)
 
 
-FLASH_MIN_ROWS = 16      # segments longer than this go to the flash prefill kernel (reference FLASH_MIN 17)
-GDN_STEP_MAX_ROWS = 16    # decode / verify rows per segment handled by the fused conv + recurrence + norm kernel
+FLASH_MIN_ROWS = 32      # segments longer than this go to the flash prefill kernel (reference FLASH_MIN 17)
+GDN_STEP_MAX_ROWS = 32    # decode / verify rows per segment handled by the fused conv + recurrence + norm kernel
 GDN_CHUNK_MIN_ROWS = 24  # segments this long go through the chunked GDN scan instead of the row-by-row recurrence
 
 

@@ -42,6 +42,7 @@ class SchedOptions:
     finite_check: bool = True
     step_timeout_s: float = 120.0
     prof: int = 0                      # 1: one line per step on stderr
+    share_min: int = PREFIX_MIN        # shortest common prefix worth waiting for / forking from a running request
 
     @staticmethod
     def from_env() -> "SchedOptions":
@@ -49,7 +50,8 @@ class SchedOptions:
         return SchedOptions(spec=int(e.get("FE_SPEC", "0")), pool=int(e.get("FE_POOL", "64")),
                             batch_rows=int(e.get("FE_BATCH_ROWS", "2048")),
                             finite_check=e.get("FE_FINITE_CHECK", "1") != "0",
-                            step_timeout_s=float(e.get("FE_STEP_TIMEOUT", "120")), prof=int(e.get("FE_SCHED_PROF", "0")))
+                            step_timeout_s=float(e.get("FE_STEP_TIMEOUT", "120")), prof=int(e.get("FE_SCHED_PROF", "0")),
+                            share_min=int(e.get("FE_SHARE_MIN", str(PREFIX_MIN))))
 
 
 @dataclass
@@ -244,9 +246,42 @@ class Scheduler:
         self.eng.ex.pool.release(ev.blocks)
         return True
 
+    # ---- shared prefill: a request whose prompt starts like one that is being prefilled waits for it --------------
+    def _share_point(self, prompt: Sequence[int], a: Active) -> int:
+        """Position (on the prompt alignment grid) up to which `prompt` and the active request's prompt agree."""
+        cp = min(common_prefix(a.req.prompt, prompt), len(prompt) - 1, len(a.req.prompt))
+        align = self.eng.ecfg.prompt_align
+        return cp // align * align
+
+    def _should_wait(self, req: Request) -> bool:
+        """True while an active request is still prefilling a long prefix this request shares: the leader gets a
+        snapshot point there and the waiter is admitted once the leader has passed it, forking its state and pages
+        instead of computing the prefix again (reference `share_point`, leader / waiter, `sched.rs:653`)."""
+        for a in self.active.values():
+            sp = self._share_point(req.prompt, a)
+            if sp < self.opts.share_min or not a.pending or a.pos >= sp:
+                continue
+            if sp not in a.snap_at:
+                a.snap_at = sorted(set(a.snap_at) | {sp})
+            return True
+        return False
+
+    def _fork_source(self, prompt: Sequence[int]):
+        """(active request, snapshot) with the longest snapshot inside the common prefix, or None."""
+        best = None
+        for a in self.active.values():
+            snap = self.slot_cache[a.slot].best_snap(prompt)
+            if snap is not None and snap.pos >= self.opts.share_min and (best is None or snap.pos > best[1].pos):
+                best = (a, snap)
+        return best
+
     def _admit(self) -> None:
-        while self.backlog and self.free:
-            req = self.backlog.pop(0)
+        i = 0
+        while i < len(self.backlog) and self.free:
+            if self._should_wait(self.backlog[i]):
+                i += 1
+                continue
+            req = self.backlog.pop(i)
             if req.cancel.is_set():
                 if req.sink:
                     req.sink(Event("finish", reason="cancelled"))
@@ -257,7 +292,22 @@ class Scheduler:
             snap = sc.best_snap(req.prompt)
             pe, ps = self.park.best(req.prompt)
             resume = 0
-            if ps is not None and (snap is None or ps.pos > snap.pos):
+            fork = self._fork_source(req.prompt)
+            if fork is not None and fork[1].pos > max(ps.pos if ps is not None else 0, snap.pos if snap is not None else 0):
+                # fork from a running sequence: copy its pages up to the snapshot and take the snapshot's state
+                src, fs = fork
+                self._park_slot(slot) if sc.tokens else self.eng.reset_slot(slot)
+                nb = (fs.pos + self.eng.ecfg.kv_block - 1) // self.eng.ecfg.kv_block
+                self.eng.ex.ensure_capacity(slot, fs.pos)
+                self.eng.ex.copy_blocks(self.eng.ex.slot_blocks[src.slot][:nb], self.eng.ex.slot_blocks[slot][:nb])
+                self.eng.ex.state_restore(slot, fs.state["gdn"])
+                if self.drafter:
+                    self.drafter.restore_window(slot, fs.state.get("draft"))
+                sc.tokens = list(self.slot_cache[src.slot].tokens[:fs.pos])
+                sc.snaps = [x for x in self.slot_cache[src.slot].snaps if x.pos <= fs.pos]
+                resume = fs.pos
+                self.stats["forked"] = self.stats.get("forked", 0) + 1
+            elif ps is not None and (snap is None or ps.pos > snap.pos):
                 # restore a parked sequence into this slot: move (exclusive) or copy (shared) its pages
                 if not pe.shared:
                     self.park.take(pe)                 # out of the pool first, so parking this slot cannot evict it

@@ -35,6 +35,7 @@ class CudaOps:
         self.force_gemv_chunks = False      # debug: run any row count through 8-row GEMV passes
         self.launches = 0                   # kernels launched (or recorded into a graph) through this object
         self.moe_pair_rows = MOE_PAIR_ROWS
+        self.mma_gemv_rows = (2, 32)        # row counts routed to the mma.sync weight-streaming kernel
         self._gdn_scratch = None
         self.fp4_act = False                # NVFP4 weights: quantise activations too and use the tcgen05 GEMM
         self._sf_pool = {}
@@ -91,6 +92,13 @@ class CudaOps:
             w = w.dense
         M, K = x.shape
         N = w.shape[0] // 2 if swiglu else w.shape[0]
+        if (self.mma_gemv_rows[0] <= M <= self.mma_gemv_rows[1] and K % 32 == 0 and not self.force_gemv_chunks
+                and w.stride(0) == K):
+            # a few rows (concurrent decode streams, speculative verify): weights streamed once into mma.sync fragments
+            y = out if out is not None else torch.empty(M, N, dtype=torch.float32 if out_f32 else self.dtype, device=self.device)
+            self.launches += 1
+            self.C.gemv_mma(y, x, w, norm_w, res, eps, 1 if swiglu else 0)
+            return y
         if M <= GEMV_MAX_ROWS or self.force_gemv_chunks or out_f32 and M <= 64:
             y = out if out is not None else torch.empty(M, N, dtype=torch.float32 if out_f32 else self.dtype, device=self.device)
             for r0 in range(0, M, GEMV_MAX_ROWS):

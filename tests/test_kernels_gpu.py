@@ -328,3 +328,19 @@ def test_gemm_fp8_norm_swiglu(ops, tops, M):
     want = tops.linear(x, wq.view(torch.float8_e4m3fn).float() * ws[:, None], norm_w=nw, eps=1e-6, swiglu=True)
     err = (got.float() - want.float()).abs().max().item()
     assert err < 6e-2 * max(1.0, want.abs().max().item()), err        # includes the e4m3 rounding of the activations
+
+
+@pytest.mark.parametrize("M", [2, 4, 8, 9, 17, 24, 32])
+@pytest.mark.parametrize("N,K", [(512, 1024), (1000, 4096), (5120, 2176)])
+def test_gemv_mma(ops, tops, M, N, K):
+    """Few-row weight-streaming linear on mma.sync: plain + residual, RMSNorm prologue + SwiGLU, fp32 output."""
+    x, w, r = rnd(M, K, seed=M), rnd(N, K, scale=0.03, seed=2), rnd(M, N, seed=3)
+    assert ops.mma_gemv_rows[0] <= M <= ops.mma_gemv_rows[1]
+    close(ops.linear(x, w, res=r), tops.linear(x, w, res=r))
+    nw = rnd(K, scale=0.1, seed=4)
+    wg = rnd(2 * N, K, scale=0.03, seed=5)
+    close(ops.linear(x, wg, norm_w=nw, eps=1e-6, swiglu=True), tops.linear(x, wg, norm_w=nw, eps=1e-6, swiglu=True), rtol=3e-2, atol=3e-2)
+    y32 = ops.linear(x, w, norm_w=nw, eps=1e-6, out_f32=True)
+    assert y32.dtype == torch.float32
+    close(y32, tops.linear(x, w, norm_w=nw, eps=1e-6, out_f32=True))
+    assert torch.equal(ops.linear(x, w, res=r), ops.linear(x, w, res=r))

@@ -190,3 +190,23 @@ def test_pcache_structures():
     assert c.propose(4) == [17, 18, 19, 20]
     r = SplitMix64(7)
     assert 0 <= r.uniform() < 1
+
+
+def test_shared_prefill_forks_from_the_running_request():
+    """Two requests with a long common prefix arriving together: the second waits until the first has passed the
+    shared point, then forks its pages and state there instead of computing the prefix again; outputs are those of
+    independent runs."""
+    cfg = tiny_hybrid()
+    w = init_weights(cfg, seed=0)
+    g = torch.Generator().manual_seed(21)
+    base = torch.randint(0, cfg.vocab, (160,), generator=g).tolist()
+    p1 = base + torch.randint(0, cfg.vocab, (20,), generator=g).tolist()
+    p2 = base + torch.randint(0, cfg.vocab, (9,), generator=g).tolist()
+    ecfg = EngineConfig(n_slots=2, max_ctx=512, prefill_chunk=64)
+    want = [generate(Scheduler(Engine(cfg, w, ecfg, device="cpu"), SchedOptions()), [p], Sampling(max_tokens=8))[0]
+            for p in (p1, p2)]
+    sched = Scheduler(Engine(cfg, w, ecfg, device="cpu"), SchedOptions(share_min=64))
+    got = generate(sched, [p1, p2], Sampling(max_tokens=8))
+    assert got == want
+    assert sched.stats.get("forked", 0) == 1
+    assert sched.stats["cached_tokens"] >= 128
