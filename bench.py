@@ -120,7 +120,8 @@ def main():
     W = max(3, args.warmup)
     K = args.steps
     n_streams_max = 4
-    ecfg = EngineConfig(n_slots=n_streams_max, max_ctx=args.ctx + 2 * (K + W) + 64, prefill_chunk=2048,
+    long_ctx = 0 if args.no_extras else 32768
+    ecfg = EngineConfig(n_slots=n_streams_max, max_ctx=max(args.ctx + 2 * (K + W) + 64, long_ctx + 64), prefill_chunk=2048,
                         weight_dtype=args.dtype)
     eng = Engine(cfg, None, ecfg, device=str(dev), seed=0, tp=tp)
     gen = torch.Generator().manual_seed(1234)
@@ -217,6 +218,12 @@ def main():
         vms = max_over_ranks(e0.elapsed_time(e1)) / K
         extras["verify_17rows_ms"] = vms
         extras["spec_tok_s_at_8_accepted"] = 9.0 / (vms / 1e3)
+    if long_ctx:
+        # long-context prefill: 32K synthetic tokens through 2048-row chunks on one slot
+        long_prompt = torch.randint(0, cfg.vocab, (long_ctx,), generator=gen).tolist()
+        ms32 = timed_prefill(3, long_prompt)
+        extras["prefill_32k_tok_s"] = long_ctx / (ms32 / 1e3)
+        extras["prefill_32k_vs_baseline"] = extras["prefill_32k_tok_s"] / BASELINE_PREFILL_32K
     extras["prefill_tok_s"] = args.ctx / (prefill_ms / 1e3)
     extras["prefill_ctx"] = args.ctx
     extras["prefill_vs_baseline"] = extras["prefill_tok_s"] / BASELINE_PREFILL_2K

@@ -252,6 +252,7 @@ class EngineConfig:
     decode_rows_max: int = 64          # rows routed to the small-M (GEMV) kernels
     attn_splits: int = 0               # 0 = pick from context length
     use_graphs: bool = True
+    kv_dtype: str = "bf16"             # "bf16" | "fp8": e4m3 KV cache with one scale per (token, kv head)
     seq_parallel: bool = True          # TP prompts: row-sharded residual stream, all-gather/reduce-scatter fused into the GEMMs
     graph_max: int = 128               # LRU size of the CUDA-graph cache (reference GRAPH_MAX)
     spec_depth: int = 0
@@ -281,6 +282,7 @@ class EngineConfig:
         c.park_host = e.get("FE_PARK_HOST", "0") not in ("", "0")
         c.use_graphs = e.get("FE_NO_GRAPHS", "0") in ("", "0")
         c.seq_parallel = e.get("FE_NO_SEQ_PARALLEL", "0") in ("", "0")
+        c.kv_dtype = e.get("FE_KV_DTYPE", c.kv_dtype)
         c.step_timeout_s = float(e.get("FE_STEP_TIMEOUT", c.step_timeout_s))
         for k, v in over.items():
             if v is not None:

@@ -33,7 +33,8 @@ long fb_gemm_workspace_bytes(int M, int N, int split_k);
 
 // 2..32 rows: weight-streaming linear on mma.sync with in-register A fragments (gemv_mma.cu)
 int fb_gemv_mma(void* y, const void* x, const void* w, const void* norm_w, const void* res, int M, int N, int K, long ldx,
-                long ldy, float eps, int mode, int out_f32, cudaStream_t s);
+                long ldy, float eps, int mode, int out_f32, float* ws, long ws_floats, int* counters, int n_counters,
+                int sm_count, cudaStream_t s);
 // FP8 (e4m3) GEMM with per-row / per-feature scales, and the activation quantiser (gemm_tcgen05.cu)
 int fb_quant_fp8(void* q, float* scale, const void* x, const void* norm_w, int rows, int K, long ldx, float eps,
                  cudaStream_t s);
@@ -50,6 +51,19 @@ int fb_attn_decode(void* out, float* o_part, float* ml_part, const void* q, cons
                    const void* proj, long proj_stride, const int* row_slot, const int* row_kvlen, const int* row_base,
                    const unsigned long long* row_mask, const int* block_table, int max_blocks, int kv_block, int rows,
                    int nq, int nkv, int hd, int nsplit, int gated, cudaStream_t s);
+// FP8 (e4m3) KV cache variants: byte codes + one fp32 scale per (token, kv head) for K and V; fb_kv_dequant decodes
+// the rows a prompt step can see into a per-slot bf16 scratch for the prompt attention kernel
+int fb_attn_prep_kv8(void* q_out, void* k_cache8, void* v_cache8, float* kv_scale, const void* proj, long proj_stride,
+                     const void* q_norm, const void* k_norm, const float* inv_freq, const int* row_slot, const int* row_pos,
+                     const int* block_table, int max_blocks, int kv_block, int rows, int nq, int nkv, int hd, int rot,
+                     int gated, float eps, int* status, cudaStream_t s);
+int fb_attn_decode_kv8(void* out, float* o_part, float* ml_part, const void* q, const void* k_cache8, const void* v_cache8,
+                       const float* kv_scale, const void* proj, long proj_stride, const int* row_slot, const int* row_kvlen,
+                       const int* row_base, const unsigned long long* row_mask, const int* block_table, int max_blocks,
+                       int kv_block, int rows, int nq, int nkv, int hd, int nsplit, int gated, cudaStream_t s);
+int fb_kv_dequant(void* k_out, void* v_out, const void* k_cache8, const void* v_cache8, const float* kv_scale,
+                  const int* seg_slot, const int* seg_pos0, const int* seg_nrows, const int* block_table, int max_blocks,
+                  int kv_block, int nseg, int max_kvlen, int nkv, int hd, int scratch_tokens_per_slot, cudaStream_t s);
 int fb_attn_prefill(void* out, const void* q, const void* k_cache, const void* v_cache, const void* proj,
                     long proj_stride, const int* seg_slot, const int* seg_row0, const int* seg_nrows,
                     const int* seg_pos0, const int* block_table, int max_blocks, int kv_block, int nseg, int max_rows,

@@ -6,6 +6,8 @@
 // paged (a block table per slot, so parking a sequence is a table move), heads and head_dim are run-time /
 // template parameters rather than compiled-in dims, and split boundaries depend only on the row's own
 // length so a row's result does not depend on what else is in the batch.
+#include <cuda_fp8.h>
+
 #include "api.h"
 #include "common.cuh"
 
@@ -14,9 +16,10 @@ namespace fb {
 // ---------------------------------------------------------------------------------------------------
 // attn-prep. One CTA per row, one warp per head (q heads first, then kv heads). The fused projection row is
 // [per q head: q(hd) | gate(hd)] [k heads] [v heads].
-template <int HD>
-__global__ void attn_prep_kernel(__nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_cache,
-                                 __nv_bfloat16* __restrict__ v_cache, const __nv_bfloat16* __restrict__ proj,
+template <int HD, bool KV8>
+__global__ void attn_prep_kernel(__nv_bfloat16* __restrict__ q_out, void* __restrict__ k_cache_v,
+                                 void* __restrict__ v_cache_v, float* __restrict__ kv_scale,
+                                 const __nv_bfloat16* __restrict__ proj,
                                  long proj_stride, const __nv_bfloat16* __restrict__ q_norm,
                                  const __nv_bfloat16* __restrict__ k_norm, const float* __restrict__ inv_freq,
                                  const int* __restrict__ row_slot, const int* __restrict__ row_pos,
@@ -67,12 +70,32 @@ __global__ void attn_prep_kernel(__nv_bfloat16* __restrict__ q_out, __nv_bfloat1
     const int slot = row_slot[row];
     const int blk = block_table[(size_t)slot * max_blocks + pos / kv_block];
     if (blk < 0) { set_status(status, ST_BOUNDS); return; }
-    const size_t off = (((size_t)blk * kv_block + (pos % kv_block)) * nkv + kvh) * HD;
-#pragma unroll
-    for (int j = 0; j < EPL; ++j) k_cache[off + lane * EPL + j] = f2bf(v[j]);
+    const size_t tok = ((size_t)blk * kv_block + (pos % kv_block)) * nkv + kvh;
+    const size_t off = tok * HD;
     const __nv_bfloat16* vsrc = proj + (size_t)row * proj_stride + (size_t)nq * qw + (size_t)(nkv + kvh) * HD;
+    if (KV8) {
+      // e4m3 codes with one fp32 scale per (token, kv head) for K and for V
+      unsigned char* kc8 = reinterpret_cast<unsigned char*>(k_cache_v);
+      unsigned char* vc8 = reinterpret_cast<unsigned char*>(v_cache_v);
+      float vv[EPL], ka = 0.f, va = 0.f;
 #pragma unroll
-    for (int j = 0; j < EPL; ++j) v_cache[off + lane * EPL + j] = vsrc[lane * EPL + j];
+      for (int j = 0; j < EPL; ++j) { vv[j] = bf2f(vsrc[lane * EPL + j]); ka = fmaxf(ka, fabsf(v[j])); va = fmaxf(va, fabsf(vv[j])); }
+      ka = warp_max(ka); va = warp_max(va);
+      const float ks = ka > 0.f ? ka / 448.f : 1.f, vs = va > 0.f ? va / 448.f : 1.f;
+#pragma unroll
+      for (int j = 0; j < EPL; ++j) {
+        kc8[off + lane * EPL + j] = (unsigned char)__nv_cvt_float_to_fp8(v[j] / ks, __NV_SATFINITE, __NV_E4M3);
+        vc8[off + lane * EPL + j] = (unsigned char)__nv_cvt_float_to_fp8(vv[j] / vs, __NV_SATFINITE, __NV_E4M3);
+      }
+      if (lane == 0) { kv_scale[tok * 2] = ks; kv_scale[tok * 2 + 1] = vs; }
+    } else {
+      __nv_bfloat16* k_cache = reinterpret_cast<__nv_bfloat16*>(k_cache_v);
+      __nv_bfloat16* v_cache = reinterpret_cast<__nv_bfloat16*>(v_cache_v);
+#pragma unroll
+      for (int j = 0; j < EPL; ++j) k_cache[off + lane * EPL + j] = f2bf(v[j]);
+#pragma unroll
+      for (int j = 0; j < EPL; ++j) v_cache[off + lane * EPL + j] = vsrc[lane * EPL + j];
+    }
   }
 }
 
@@ -81,10 +104,25 @@ __global__ void attn_prep_kernel(__nv_bfloat16* __restrict__ q_out, __nv_bfloat1
 // owns one key at a time; every lane keeps 8 dims of K, V and of the G query heads of the group.
 constexpr int ATT_WARPS = 8;
 
-template <int HD, int G>
+__device__ __forceinline__ void e4m3x8_to_float(uint2 raw, float* f) {
+  const uint32_t w[2] = {raw.x, raw.y};
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const __half2_raw hr = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)((w[i] >> (16 * h)) & 0xFFFFu), __NV_E4M3);
+      const float2 f2 = __half22float2(*reinterpret_cast<const __half2*>(&hr));
+      f[i * 4 + h * 2] = f2.x;
+      f[i * 4 + h * 2 + 1] = f2.y;
+    }
+  }
+}
+
+template <int HD, int G, bool KV8>
 __global__ void __launch_bounds__(ATT_WARPS * 32)
 attn_decode_kernel(float* __restrict__ o_part, float* __restrict__ ml_part, const __nv_bfloat16* __restrict__ q,
-                   const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
+                   const void* __restrict__ k_cache_v, const void* __restrict__ v_cache_v,
+                   const float* __restrict__ kv_scale,
                    const int* __restrict__ row_slot, const int* __restrict__ row_kvlen,
                    const int* __restrict__ row_base, const unsigned long long* __restrict__ row_mask,
                    const int* __restrict__ block_table, int max_blocks, int kv_block, int nq, int nkv, int nsplit,
@@ -126,6 +164,7 @@ attn_decode_kernel(float* __restrict__ o_part, float* __restrict__ ml_part, cons
   constexpr int UN = (G <= 6) ? 4 : 2;
   for (int t0 = lo + warp * KPI * UN; t0 < hi; t0 += ATT_WARPS * KPI * UN) {
     uint4 kraw[UN], vraw[UN];
+    float2 sc2[UN];
     bool visb[UN];
 #pragma unroll
     for (int u = 0; u < UN; ++u) {
@@ -136,9 +175,18 @@ attn_decode_kernel(float* __restrict__ o_part, float* __restrict__ ml_part, cons
       kraw[u] = make_uint4(0, 0, 0, 0); vraw[u] = make_uint4(0, 0, 0, 0);
       if (vis) {
         const int blk = bt[t / kv_block];
-        const size_t off = (((size_t)blk * kv_block + (t % kv_block)) * nkv + kvh) * HD + sub * 8;
-        kraw[u] = ldg_stream(k_cache + off);
-        vraw[u] = ldg_stream(v_cache + off);
+        const size_t tok = ((size_t)blk * kv_block + (t % kv_block)) * nkv + kvh;
+        const size_t off = tok * HD + sub * 8;
+        if (KV8) {
+          const uint2 k8 = ldg_stream8(reinterpret_cast<const unsigned char*>(k_cache_v) + off);
+          const uint2 v8 = ldg_stream8(reinterpret_cast<const unsigned char*>(v_cache_v) + off);
+          kraw[u] = make_uint4(k8.x, k8.y, 0, 0);
+          vraw[u] = make_uint4(v8.x, v8.y, 0, 0);
+          sc2[u] = *reinterpret_cast<const float2*>(kv_scale + tok * 2);
+        } else {
+          kraw[u] = ldg_stream(reinterpret_cast<const __nv_bfloat16*>(k_cache_v) + off);
+          vraw[u] = ldg_stream(reinterpret_cast<const __nv_bfloat16*>(v_cache_v) + off);
+        }
       }
     }
 #pragma unroll
@@ -146,10 +194,19 @@ attn_decode_kernel(float* __restrict__ o_part, float* __restrict__ ml_part, cons
       const bool vis = visb[u];
       uint32_t ku[4] = {kraw[u].x, kraw[u].y, kraw[u].z, kraw[u].w}, vu[4] = {vraw[u].x, vraw[u].y, vraw[u].z, vraw[u].w};
       float kf[8], vf[8];
+      if (KV8) {
+        e4m3x8_to_float(make_uint2(ku[0], ku[1]), kf);
+        e4m3x8_to_float(make_uint2(vu[0], vu[1]), vf);
+        if (vis) {
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        kf[2 * j] = bf_lo(ku[j]); kf[2 * j + 1] = bf_hi(ku[j]);
-        vf[2 * j] = bf_lo(vu[j]); vf[2 * j + 1] = bf_hi(vu[j]);
+          for (int j = 0; j < 8; ++j) { kf[j] *= sc2[u].x; vf[j] *= sc2[u].y; }
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          kf[2 * j] = bf_lo(ku[j]); kf[2 * j + 1] = bf_hi(ku[j]);
+          vf[2 * j] = bf_lo(vu[j]); vf[2 * j + 1] = bf_hi(vu[j]);
+        }
       }
 #pragma unroll
       for (int g = 0; g < G; ++g) {
@@ -250,17 +307,44 @@ __global__ void attn_combine_kernel(__nv_bfloat16* __restrict__ out, const float
   }
 }
 
-template <int HD>
+// bf16 rows of the keys / values a prompt chunk can see, decoded from the e4m3 cache into a scratch laid out per
+// slot ([slot][position][kv head][hd]) so the prompt attention kernel reads it through an identity block table.
+// grid (max kvlen, nkv, segments); blockDim = hd / 8 (8 elements per thread)
+__global__ void kv_dequant_kernel(__nv_bfloat16* __restrict__ k_out, __nv_bfloat16* __restrict__ v_out,
+                                  const unsigned char* __restrict__ k8, const unsigned char* __restrict__ v8,
+                                  const float* __restrict__ kv_scale, const int* __restrict__ seg_slot,
+                                  const int* __restrict__ seg_pos0, const int* __restrict__ seg_nrows,
+                                  const int* __restrict__ block_table, int max_blocks, int kv_block, int nkv, int hd,
+                                  int scratch_tokens_per_slot) {
+  const int t = blockIdx.x, kvh = blockIdx.y, seg = blockIdx.z;
+  const int n = seg_nrows[seg];
+  if (n <= 0 || t >= seg_pos0[seg] + n) return;
+  const int slot = seg_slot[seg];
+  const int blk = block_table[(size_t)slot * max_blocks + t / kv_block];
+  if (blk < 0) return;
+  const size_t tok = ((size_t)blk * kv_block + (t % kv_block)) * nkv + kvh;
+  const float ks = kv_scale[tok * 2], vs = kv_scale[tok * 2 + 1];
+  const size_t dst = (((size_t)slot * scratch_tokens_per_slot + t) * nkv + kvh) * hd + threadIdx.x * 8;
+  float kf[8], vf[8];
+  e4m3x8_to_float(*reinterpret_cast<const uint2*>(k8 + tok * hd + threadIdx.x * 8), kf);
+  e4m3x8_to_float(*reinterpret_cast<const uint2*>(v8 + tok * hd + threadIdx.x * 8), vf);
+  *reinterpret_cast<uint4*>(k_out + dst) = make_uint4(pack_bf2(kf[0] * ks, kf[1] * ks), pack_bf2(kf[2] * ks, kf[3] * ks),
+                                                      pack_bf2(kf[4] * ks, kf[5] * ks), pack_bf2(kf[6] * ks, kf[7] * ks));
+  *reinterpret_cast<uint4*>(v_out + dst) = make_uint4(pack_bf2(vf[0] * vs, vf[1] * vs), pack_bf2(vf[2] * vs, vf[3] * vs),
+                                                      pack_bf2(vf[4] * vs, vf[5] * vs), pack_bf2(vf[6] * vs, vf[7] * vs));
+}
+
+template <int HD, bool KV8>
 static int launch_decode(int G, dim3 grid, size_t smem, cudaStream_t s, float* o_part, float* ml_part, const void* q,
-                         const void* kc, const void* vc, const int* row_slot, const int* row_kvlen,
+                         const void* kc, const void* vc, const float* kv_scale, const int* row_slot, const int* row_kvlen,
                          const int* row_base, const unsigned long long* row_mask, const int* bt, int max_blocks,
                          int kv_block, int nq, int nkv, int nsplit, float scale_log2) {
 #define FB_LAUNCH_G(GV)                                                                                          \
   case GV: {                                                                                                     \
-    auto kern = attn_decode_kernel<HD, GV>;                                                                      \
+    auto kern = attn_decode_kernel<HD, GV, KV8>;                                                                 \
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);    \
-    launch_pdl(kern, dim3(grid), dim3(ATT_WARPS * 32), (size_t)(smem), s, o_part, ml_part, (const __nv_bfloat16*)q, (const __nv_bfloat16*)kc,  \
-                                            (const __nv_bfloat16*)vc, row_slot, row_kvlen, row_base, row_mask,   \
+    launch_pdl(kern, dim3(grid), dim3(ATT_WARPS * 32), (size_t)(smem), s, o_part, ml_part, (const __nv_bfloat16*)q, kc,  \
+                                            vc, kv_scale, row_slot, row_kvlen, row_base, row_mask,               \
                                             bt, max_blocks, kv_block, nq, nkv, nsplit, scale_log2);              \
     break;                                                                                                       \
   }
@@ -276,30 +360,34 @@ static int launch_decode(int G, dim3 grid, size_t smem, cudaStream_t s, float* o
 
 using namespace fb;
 
-extern "C" int fb_attn_prep(void* q_out, void* k_cache, void* v_cache, const void* proj, long proj_stride,
-                            const void* q_norm, const void* k_norm, const float* inv_freq, const int* row_slot,
-                            const int* row_pos, const int* block_table, int max_blocks, int kv_block, int rows, int nq,
-                            int nkv, int hd, int rot, int gated, float eps, int* status, cudaStream_t s) {
+static int attn_prep_impl(void* q_out, void* k_cache, void* v_cache, float* kv_scale, const void* proj, long proj_stride,
+                          const void* q_norm, const void* k_norm, const float* inv_freq, const int* row_slot,
+                          const int* row_pos, const int* block_table, int max_blocks, int kv_block, int rows, int nq,
+                          int nkv, int hd, int rot, int gated, float eps, int* status, cudaStream_t s) {
   if (rows <= 0) return 0;
   int threads = 32 * (nq + nkv);
   if (threads > 1024) return -1;
   int epl = hd / 32;
   if (rot % 2 || (rot / 2) % epl || ((rot / 2 / epl) & (rot / 2 / epl - 1))) return -3;
-#define FB_PREP(HDV)                                                                                              \
-  launch_pdl(attn_prep_kernel<HDV>, dim3(rows), dim3(threads), (size_t)(0), s, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache,                  \
-      (__nv_bfloat16*)v_cache, (const __nv_bfloat16*)proj, proj_stride, (const __nv_bfloat16*)q_norm,             \
+#define FB_PREP(HDV, K8)                                                                                          \
+  launch_pdl(attn_prep_kernel<HDV, K8>, dim3(rows), dim3(threads), (size_t)(0), s, (__nv_bfloat16*)q_out, k_cache, v_cache, \
+      kv_scale, (const __nv_bfloat16*)proj, proj_stride, (const __nv_bfloat16*)q_norm,                            \
       (const __nv_bfloat16*)k_norm, inv_freq, row_slot, row_pos, block_table, max_blocks, kv_block, nq, nkv, rot, \
       gated, eps, status)
-  if (hd == 256) FB_PREP(256); else if (hd == 128) FB_PREP(128); else if (hd == 64) FB_PREP(64); else return -2;
+  if (kv_scale) {
+    if (hd == 256) FB_PREP(256, true); else if (hd == 128) FB_PREP(128, true); else if (hd == 64) FB_PREP(64, true); else return -2;
+  } else {
+    if (hd == 256) FB_PREP(256, false); else if (hd == 128) FB_PREP(128, false); else if (hd == 64) FB_PREP(64, false); else return -2;
+  }
 #undef FB_PREP
   return (int)cudaGetLastError();
 }
 
-extern "C" int fb_attn_decode(void* out, float* o_part, float* ml_part, const void* q, const void* k_cache,
-                              const void* v_cache, const void* proj, long proj_stride, const int* row_slot,
-                              const int* row_kvlen, const int* row_base, const unsigned long long* row_mask,
-                              const int* block_table, int max_blocks, int kv_block, int rows, int nq, int nkv, int hd,
-                              int nsplit, int gated, cudaStream_t s) {
+static int attn_decode_impl(void* out, float* o_part, float* ml_part, const void* q, const void* k_cache,
+                            const void* v_cache, const float* kv_scale, const void* proj, long proj_stride,
+                            const int* row_slot, const int* row_kvlen, const int* row_base,
+                            const unsigned long long* row_mask, const int* block_table, int max_blocks, int kv_block,
+                            int rows, int nq, int nkv, int hd, int nsplit, int gated, cudaStream_t s) {
   if (rows <= 0) return 0;
   if (nq % nkv) return -1;
   int G = nq / nkv;
@@ -307,16 +395,70 @@ extern "C" int fb_attn_decode(void* out, float* o_part, float* ml_part, const vo
   size_t smem = (size_t)ATT_WARPS * G * (hd + 2) * sizeof(float);
   float scale_log2 = 1.4426950408889634f / sqrtf((float)hd);
   int rc;
-  if (hd == 256) rc = launch_decode<256>(G, grid, smem, s, o_part, ml_part, q, k_cache, v_cache, row_slot, row_kvlen, row_base, row_mask, block_table, max_blocks, kv_block, nq, nkv, nsplit, scale_log2);
-  else if (hd == 128) rc = launch_decode<128>(G, grid, smem, s, o_part, ml_part, q, k_cache, v_cache, row_slot, row_kvlen, row_base, row_mask, block_table, max_blocks, kv_block, nq, nkv, nsplit, scale_log2);
-  else if (hd == 64) rc = launch_decode<64>(G, grid, smem, s, o_part, ml_part, q, k_cache, v_cache, row_slot, row_kvlen, row_base, row_mask, block_table, max_blocks, kv_block, nq, nkv, nsplit, scale_log2);
-  else return -2;
+#define FB_DEC(HDV, K8) rc = launch_decode<HDV, K8>(G, grid, smem, s, o_part, ml_part, q, k_cache, v_cache, kv_scale, row_slot, row_kvlen, row_base, row_mask, block_table, max_blocks, kv_block, nq, nkv, nsplit, scale_log2)
+  if (kv_scale) {
+    if (hd == 256) FB_DEC(256, true); else if (hd == 128) FB_DEC(128, true); else if (hd == 64) FB_DEC(64, true); else return -2;
+  } else {
+    if (hd == 256) FB_DEC(256, false); else if (hd == 128) FB_DEC(128, false); else if (hd == 64) FB_DEC(64, false); else return -2;
+  }
+#undef FB_DEC
   if (rc) return rc;
   dim3 cgrid(rows, nq);
   int cthreads = hd >= 128 ? 128 : 64;
   if (hd == 256) launch_pdl(attn_combine_kernel<256>, dim3(cgrid), dim3(cthreads), (size_t)(0), s, (__nv_bfloat16*)out, o_part, ml_part, (const __nv_bfloat16*)proj, proj_stride, nq, nsplit, gated);
   else if (hd == 128) launch_pdl(attn_combine_kernel<128>, dim3(cgrid), dim3(cthreads), (size_t)(0), s, (__nv_bfloat16*)out, o_part, ml_part, (const __nv_bfloat16*)proj, proj_stride, nq, nsplit, gated);
   else launch_pdl(attn_combine_kernel<64>, dim3(cgrid), dim3(cthreads), (size_t)(0), s, (__nv_bfloat16*)out, o_part, ml_part, (const __nv_bfloat16*)proj, proj_stride, nq, nsplit, gated);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int fb_attn_prep(void* q_out, void* k_cache, void* v_cache, const void* proj, long proj_stride,
+                            const void* q_norm, const void* k_norm, const float* inv_freq, const int* row_slot,
+                            const int* row_pos, const int* block_table, int max_blocks, int kv_block, int rows, int nq,
+                            int nkv, int hd, int rot, int gated, float eps, int* status, cudaStream_t s) {
+  return attn_prep_impl(q_out, k_cache, v_cache, nullptr, proj, proj_stride, q_norm, k_norm, inv_freq, row_slot, row_pos,
+                        block_table, max_blocks, kv_block, rows, nq, nkv, hd, rot, gated, eps, status, s);
+}
+
+extern "C" int fb_attn_decode(void* out, float* o_part, float* ml_part, const void* q, const void* k_cache,
+                              const void* v_cache, const void* proj, long proj_stride, const int* row_slot,
+                              const int* row_kvlen, const int* row_base, const unsigned long long* row_mask,
+                              const int* block_table, int max_blocks, int kv_block, int rows, int nq, int nkv, int hd,
+                              int nsplit, int gated, cudaStream_t s) {
+  return attn_decode_impl(out, o_part, ml_part, q, k_cache, v_cache, nullptr, proj, proj_stride, row_slot, row_kvlen,
+                          row_base, row_mask, block_table, max_blocks, kv_block, rows, nq, nkv, hd, nsplit, gated, s);
+}
+
+// FP8 (e4m3) KV cache: codes [blocks][kv_block][nkv][hd] bytes + scales [blocks][kv_block][nkv][2] fp32 (K, V)
+extern "C" int fb_attn_prep_kv8(void* q_out, void* k_cache8, void* v_cache8, float* kv_scale, const void* proj,
+                                long proj_stride, const void* q_norm, const void* k_norm, const float* inv_freq,
+                                const int* row_slot, const int* row_pos, const int* block_table, int max_blocks,
+                                int kv_block, int rows, int nq, int nkv, int hd, int rot, int gated, float eps, int* status,
+                                cudaStream_t s) {
+  if (!kv_scale) return -4;
+  return attn_prep_impl(q_out, k_cache8, v_cache8, kv_scale, proj, proj_stride, q_norm, k_norm, inv_freq, row_slot, row_pos,
+                        block_table, max_blocks, kv_block, rows, nq, nkv, hd, rot, gated, eps, status, s);
+}
+
+extern "C" int fb_attn_decode_kv8(void* out, float* o_part, float* ml_part, const void* q, const void* k_cache8,
+                                  const void* v_cache8, const float* kv_scale, const void* proj, long proj_stride,
+                                  const int* row_slot, const int* row_kvlen, const int* row_base,
+                                  const unsigned long long* row_mask, const int* block_table, int max_blocks,
+                                  int kv_block, int rows, int nq, int nkv, int hd, int nsplit, int gated, cudaStream_t s) {
+  if (!kv_scale) return -4;
+  return attn_decode_impl(out, o_part, ml_part, q, k_cache8, v_cache8, kv_scale, proj, proj_stride, row_slot, row_kvlen,
+                          row_base, row_mask, block_table, max_blocks, kv_block, rows, nq, nkv, hd, nsplit, gated, s);
+}
+
+// decode the e4m3 rows the segments of a prompt step can see into the per-slot bf16 scratch
+extern "C" int fb_kv_dequant(void* k_out, void* v_out, const void* k_cache8, const void* v_cache8, const float* kv_scale,
+                             const int* seg_slot, const int* seg_pos0, const int* seg_nrows, const int* block_table,
+                             int max_blocks, int kv_block, int nseg, int max_kvlen, int nkv, int hd,
+                             int scratch_tokens_per_slot, cudaStream_t s) {
+  if (nseg <= 0 || max_kvlen <= 0) return 0;
+  if (hd % 8 || max_kvlen > scratch_tokens_per_slot) return -1;
+  kv_dequant_kernel<<<dim3(max_kvlen, nkv, nseg), hd / 8, 0, s>>>((__nv_bfloat16*)k_out, (__nv_bfloat16*)v_out,
+      (const unsigned char*)k_cache8, (const unsigned char*)v_cache8, kv_scale, seg_slot, seg_pos0, seg_nrows, block_table,
+      max_blocks, kv_block, nkv, hd, scratch_tokens_per_slot);
   return (int)cudaGetLastError();
 }
 

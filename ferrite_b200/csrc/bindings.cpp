@@ -85,12 +85,14 @@ void gemm(Tensor Y, Tensor X, Tensor W, c10::optional<Tensor> res, int64_t mode,
 }
 
 void gemv_mma(Tensor Y, Tensor X, Tensor W, c10::optional<Tensor> norm_w, c10::optional<Tensor> res, double eps,
-              int64_t mode) {
+              int64_t mode, c10::optional<Tensor> workspace, c10::optional<Tensor> counters) {
   int M = (int)X.size(0), K = (int)X.size(1);
   int N = (int)(mode == 1 ? W.size(0) / 2 : W.size(0));
+  long wsf = workspace.has_value() ? (long)(workspace->numel() * workspace->element_size() / 4) : 0;
+  int nc = counters.has_value() ? (int)counters->numel() : 0;
   check(fb_gemv_mma(Y.data_ptr(), X.data_ptr(), W.data_ptr(), cptr(norm_w), cptr(res), M, N, K, (long)X.stride(0),
-                    (long)Y.stride(0), (float)eps, (int)mode, Y.scalar_type() == torch::kFloat32 ? 1 : 0, cur_stream()),
-        "gemv_mma");
+                    (long)Y.stride(0), (float)eps, (int)mode, Y.scalar_type() == torch::kFloat32 ? 1 : 0,
+                    (float*)mptr(workspace), wsf, (int*)mptr(counters), nc, sm_count(), cur_stream()), "gemv_mma");
 }
 
 void quant_fp8(Tensor q, Tensor scale, Tensor x, c10::optional<Tensor> norm_w, double eps) {
@@ -110,7 +112,17 @@ void gemm_fp8(Tensor Y, Tensor Xq, Tensor Wq, c10::optional<Tensor> scale_m, c10
 
 void attn_prep(Tensor q_out, Tensor k_cache, Tensor v_cache, Tensor proj, Tensor q_norm, Tensor k_norm,
                Tensor inv_freq, Tensor row_slot, Tensor row_pos, Tensor block_table, int64_t kv_block, int64_t nq,
-               int64_t nkv, int64_t hd, int64_t rot, bool gated, double eps, c10::optional<Tensor> status) {
+               int64_t nkv, int64_t hd, int64_t rot, bool gated, double eps, c10::optional<Tensor> status,
+               c10::optional<Tensor> kv_scale) {
+  if (kv_scale.has_value() && kv_scale->defined()) {
+    check(fb_attn_prep_kv8(q_out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), kv_scale->data_ptr<float>(),
+                           proj.data_ptr(), (long)proj.stride(0), q_norm.data_ptr(), k_norm.data_ptr(),
+                           inv_freq.data_ptr<float>(), row_slot.data_ptr<int>(), row_pos.data_ptr<int>(),
+                           block_table.data_ptr<int>(), (int)block_table.size(1), (int)kv_block, (int)row_slot.numel(),
+                           (int)nq, (int)nkv, (int)hd, (int)rot, gated ? 1 : 0, (float)eps, (int*)mptr(status),
+                           cur_stream()), "attn_prep_kv8");
+    return;
+  }
   check(fb_attn_prep(q_out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), proj.data_ptr(), (long)proj.stride(0),
                      q_norm.data_ptr(), k_norm.data_ptr(), inv_freq.data_ptr<float>(), row_slot.data_ptr<int>(),
                      row_pos.data_ptr<int>(), block_table.data_ptr<int>(), (int)block_table.size(1), (int)kv_block,
@@ -121,13 +133,33 @@ void attn_prep(Tensor q_out, Tensor k_cache, Tensor v_cache, Tensor proj, Tensor
 void attn_decode(Tensor out, Tensor o_part, Tensor ml_part, Tensor q, Tensor k_cache, Tensor v_cache, Tensor proj,
                  Tensor row_slot, Tensor row_kvlen, c10::optional<Tensor> row_base, c10::optional<Tensor> row_mask,
                  Tensor block_table, int64_t kv_block, int64_t nq, int64_t nkv, int64_t hd, int64_t nsplit,
-                 bool gated) {
+                 bool gated, c10::optional<Tensor> kv_scale) {
+  if (kv_scale.has_value() && kv_scale->defined()) {
+    check(fb_attn_decode_kv8(out.data_ptr(), o_part.data_ptr<float>(), ml_part.data_ptr<float>(), q.data_ptr(),
+                             k_cache.data_ptr(), v_cache.data_ptr(), kv_scale->data_ptr<float>(), proj.data_ptr(),
+                             (long)proj.stride(0), row_slot.data_ptr<int>(), row_kvlen.data_ptr<int>(),
+                             (const int*)cptr(row_base), (const unsigned long long*)cptr(row_mask),
+                             block_table.data_ptr<int>(), (int)block_table.size(1), (int)kv_block,
+                             (int)row_slot.numel(), (int)nq, (int)nkv, (int)hd, (int)nsplit, gated ? 1 : 0, cur_stream()),
+          "attn_decode_kv8");
+    return;
+  }
   check(fb_attn_decode(out.data_ptr(), o_part.data_ptr<float>(), ml_part.data_ptr<float>(), q.data_ptr(),
                        k_cache.data_ptr(), v_cache.data_ptr(), proj.data_ptr(), (long)proj.stride(0),
                        row_slot.data_ptr<int>(), row_kvlen.data_ptr<int>(), (const int*)cptr(row_base),
                        (const unsigned long long*)cptr(row_mask), block_table.data_ptr<int>(),
                        (int)block_table.size(1), (int)kv_block, (int)row_slot.numel(), (int)nq, (int)nkv, (int)hd,
                        (int)nsplit, gated ? 1 : 0, cur_stream()), "attn_decode");
+}
+
+void kv_dequant(Tensor k_out, Tensor v_out, Tensor k_cache8, Tensor v_cache8, Tensor kv_scale, Tensor seg_slot,
+                Tensor seg_pos0, Tensor seg_nrows, Tensor block_table, int64_t kv_block, int64_t max_kvlen, int64_t nkv,
+                int64_t hd, int64_t scratch_tokens_per_slot) {
+  check(fb_kv_dequant(k_out.data_ptr(), v_out.data_ptr(), k_cache8.data_ptr(), v_cache8.data_ptr(),
+                      kv_scale.data_ptr<float>(), seg_slot.data_ptr<int>(), seg_pos0.data_ptr<int>(),
+                      seg_nrows.data_ptr<int>(), block_table.data_ptr<int>(), (int)block_table.size(1), (int)kv_block,
+                      (int)seg_slot.numel(), (int)max_kvlen, (int)nkv, (int)hd, (int)scratch_tokens_per_slot, cur_stream()),
+        "kv_dequant");
 }
 
 void attn_prefill(Tensor out, Tensor q, Tensor k_cache, Tensor v_cache, Tensor proj, Tensor seg_slot, Tensor seg_row0,
@@ -229,6 +261,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("attn_prefill", &attn_prefill);
   m.def("gdn_conv", &gdn_conv);
   m.def("gdn_rec", &gdn_rec);
+  m.def("kv_dequant", &kv_dequant);
   m.def("gemv_mma", &gemv_mma);
   m.def("gdn_step", &gdn_step);
   m.def("quant_fp8", &quant_fp8);

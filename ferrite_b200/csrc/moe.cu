@@ -115,25 +115,39 @@ moe_gate_up_kernel(__nv_bfloat16* __restrict__ act, const __nv_bfloat16* __restr
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const __nv_bfloat16* we = w_gu + (size_t)(e - e_lo) * 2 * inter * hidden;
-  for (int r = 0; r < 2; ++r) {
-    const int j = blockIdx.x * 16 + warp * 2 + r;
-    if (j >= inter) break;
-    float g = 0.f, u = 0.f;
-    const __nv_bfloat16* wg = we + (size_t)j * hidden;
-    const __nv_bfloat16* wu = we + (size_t)(inter + j) * hidden;
-    for (int k = lane * 8; k < hidden; k += 256) {
-      uint4 a = ldg_stream(wg + k), b = ldg_stream(wu + k);
-      uint4 xv = *reinterpret_cast<const uint4*>(xs_moe + k);
-      uint32_t au[4] = {a.x, a.y, a.z, a.w}, bu[4] = {b.x, b.y, b.z, b.w}, xu[4] = {xv.x, xv.y, xv.z, xv.w};
+  // the warp's two outputs run together: four weight rows stream at once, twice unrolled (8 loads of 16 bytes in flight)
+  const int j0 = blockIdx.x * 16 + warp * 2;
+  if (j0 >= inter) return;
+  const int j1 = min(j0 + 1, inter - 1);
+  const __nv_bfloat16* wg0 = we + (size_t)j0 * hidden;
+  const __nv_bfloat16* wu0 = we + (size_t)(inter + j0) * hidden;
+  const __nv_bfloat16* wg1 = we + (size_t)j1 * hidden;
+  const __nv_bfloat16* wu1 = we + (size_t)(inter + j1) * hidden;
+  float g0 = 0.f, u0 = 0.f, g1 = 0.f, u1 = 0.f;
+  auto dot8 = [](const uint4& a, const uint4& xv, float acc) {
+    const uint32_t au[4] = {a.x, a.y, a.z, a.w}, xu[4] = {xv.x, xv.y, xv.z, xv.w};
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        float x0 = bf_lo(xu[q]), x1 = bf_hi(xu[q]);
-        g = fmaf(bf_lo(au[q]), x0, fmaf(bf_hi(au[q]), x1, g));
-        u = fmaf(bf_lo(bu[q]), x0, fmaf(bf_hi(bu[q]), x1, u));
-      }
-    }
-    g = warp_sum(g); u = warp_sum(u);
-    if (lane == 0) act[(size_t)p * inter + j] = f2bf(siluf_(g) * u);
+    for (int q = 0; q < 4; ++q) acc = fmaf(bf_lo(au[q]), bf_lo(xu[q]), fmaf(bf_hi(au[q]), bf_hi(xu[q]), acc));
+    return acc;
+  };
+  int k = lane * 8;
+  for (; k + 256 < hidden; k += 512) {
+    const uint4 a0 = ldg_stream(wg0 + k), b0 = ldg_stream(wu0 + k), c0 = ldg_stream(wg1 + k), d0 = ldg_stream(wu1 + k);
+    const uint4 a1 = ldg_stream(wg0 + k + 256), b1 = ldg_stream(wu0 + k + 256), c1 = ldg_stream(wg1 + k + 256),
+                d1 = ldg_stream(wu1 + k + 256);
+    const uint4 x0 = *reinterpret_cast<const uint4*>(xs_moe + k), x1 = *reinterpret_cast<const uint4*>(xs_moe + k + 256);
+    g0 = dot8(a1, x1, dot8(a0, x0, g0)); u0 = dot8(b1, x1, dot8(b0, x0, u0));
+    g1 = dot8(c1, x1, dot8(c0, x0, g1)); u1 = dot8(d1, x1, dot8(d0, x0, u1));
+  }
+  for (; k < hidden; k += 256) {
+    const uint4 a0 = ldg_stream(wg0 + k), b0 = ldg_stream(wu0 + k), c0 = ldg_stream(wg1 + k), d0 = ldg_stream(wu1 + k);
+    const uint4 x0 = *reinterpret_cast<const uint4*>(xs_moe + k);
+    g0 = dot8(a0, x0, g0); u0 = dot8(b0, x0, u0); g1 = dot8(c0, x0, g1); u1 = dot8(d0, x0, u1);
+  }
+  g0 = warp_sum(g0); u0 = warp_sum(u0); g1 = warp_sum(g1); u1 = warp_sum(u1);
+  if (lane == 0) {
+    act[(size_t)p * inter + j0] = f2bf(siluf_(g0) * u0);
+    if (j0 + 1 < inter) act[(size_t)p * inter + j0 + 1] = f2bf(siluf_(g1) * u1);
   }
 }
 
@@ -155,20 +169,25 @@ moe_down_kernel(float* __restrict__ yp, const __nv_bfloat16* __restrict__ act, c
     reinterpret_cast<uint4*>(as_moe)[i] = reinterpret_cast<const uint4*>(act + (size_t)p * inter)[i];
   __syncthreads();
   const __nv_bfloat16* we = w_down + (size_t)(e - e_lo) * hidden * inter;
-  for (int r = 0; r < 2; ++r) {
-    const int n = n0 + r;
-    if (n >= hidden) break;
-    float s = 0.f;
-    const __nv_bfloat16* wr = we + (size_t)n * inter;
-    for (int k = lane * 8; k < inter; k += 256) {
-      uint4 a = ldg_stream(wr + k);
-      uint4 xv = *reinterpret_cast<const uint4*>(as_moe + k);
-      uint32_t au[4] = {a.x, a.y, a.z, a.w}, xu[4] = {xv.x, xv.y, xv.z, xv.w};
+  if (n0 >= hidden) return;
+  const int n1 = min(n0 + 1, hidden - 1);
+  const __nv_bfloat16* w0 = we + (size_t)n0 * inter;
+  const __nv_bfloat16* w1 = we + (size_t)n1 * inter;
+  float s0 = 0.f, s1 = 0.f;
+  for (int k = lane * 8; k < inter; k += 256) {               // both rows of the warp stream together
+    const uint4 a = ldg_stream(w0 + k), b = ldg_stream(w1 + k);
+    const uint4 xv = *reinterpret_cast<const uint4*>(as_moe + k);
+    const uint32_t au[4] = {a.x, a.y, a.z, a.w}, bu[4] = {b.x, b.y, b.z, b.w}, xu[4] = {xv.x, xv.y, xv.z, xv.w};
 #pragma unroll
-      for (int q = 0; q < 4; ++q) s = fmaf(bf_lo(au[q]), bf_lo(xu[q]), fmaf(bf_hi(au[q]), bf_hi(xu[q]), s));
+    for (int q = 0; q < 4; ++q) {
+      s0 = fmaf(bf_lo(au[q]), bf_lo(xu[q]), fmaf(bf_hi(au[q]), bf_hi(xu[q]), s0));
+      s1 = fmaf(bf_lo(bu[q]), bf_lo(xu[q]), fmaf(bf_hi(bu[q]), bf_hi(xu[q]), s1));
     }
-    s = warp_sum(s);
-    if (lane == 0) yp[(size_t)p * hidden + n] = s;
+  }
+  s0 = warp_sum(s0); s1 = warp_sum(s1);
+  if (lane == 0) {
+    yp[(size_t)p * hidden + n0] = s0;
+    if (n0 + 1 < hidden) yp[(size_t)p * hidden + n0 + 1] = s1;
   }
 }
 

@@ -73,9 +73,11 @@ class Engine:
         if tp is not None and tp.world > 1 and self.ecfg.seq_parallel and tp.sp_max is None:
             tp.setup_big(self.ecfg.max_step_rows, cfg.hidden)
         self.ex = Executor(self.cfg, weights, self.ecfg, ops, tp=tp, full_cfg=cfg)
-        if tp is not None and tp.world > 1 and cfg.n_experts > 0 and tp.sp_max is not None:
+        if cfg.n_experts > 0 and ((tp is not None and tp.world > 1 and tp.sp_max is not None) or (world == 1 and on_gpu)):
+            # prompt-sized MoE steps go through plan / dispatch / grouped GEMM / combine; with one rank the dispatch
+            # is a local sort of the (token, expert) pairs
             from ..parallel.ep import ExpertParallel
-            self.ex.ep = ExpertParallel(tp, self.device, cfg.n_experts, cfg.hidden,
+            self.ex.ep = ExpertParallel(tp if world > 1 else None, self.device, cfg.n_experts, cfg.hidden,
                                         cap_rows=self.ecfg.max_step_rows * cfg.top_k)
         self.slot_len: List[int] = [0] * self.ecfg.n_slots
 

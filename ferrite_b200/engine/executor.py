@@ -88,14 +88,20 @@ class Executor:
         n_blocks = ecfg.n_slots * self.max_blocks + (int(ecfg.park_gb * (1 << 30) / max(1, self.kv_block_bytes())) if ecfg.park_gb > 0 else 0)
         self.pool = BlockPool(n_blocks)
         dev, dt = self.device, self.dtype
+        self.kv8 = ecfg.kv_dtype == "fp8"
+        self.kv_scale: Dict[int, torch.Tensor] = {}
         self.k_cache: Dict[int, torch.Tensor] = {}
         self.v_cache: Dict[int, torch.Tensor] = {}
         self.rec_state: Dict[int, torch.Tensor] = {}
         self.conv_state: Dict[int, torch.Tensor] = {}
         for i, kind in enumerate(self.kinds):
             if kind == "attn":
-                self.k_cache[i] = torch.zeros(n_blocks, ecfg.kv_block, c.n_kv, c.head_dim, dtype=dt, device=dev)
-                self.v_cache[i] = torch.zeros(n_blocks, ecfg.kv_block, c.n_kv, c.head_dim, dtype=dt, device=dev)
+                # e4m3 cache: byte codes on the GPU (the CPU oracle keeps dequantised values) + K / V scales per row
+                kdt = torch.uint8 if (self.kv8 and dev.type == "cuda") else dt
+                self.k_cache[i] = torch.zeros(n_blocks, ecfg.kv_block, c.n_kv, c.head_dim, dtype=kdt, device=dev)
+                self.v_cache[i] = torch.zeros(n_blocks, ecfg.kv_block, c.n_kv, c.head_dim, dtype=kdt, device=dev)
+                if self.kv8:
+                    self.kv_scale[i] = torch.ones(n_blocks, ecfg.kv_block, c.n_kv, 2, dtype=torch.float32, device=dev)
             elif kind == "mla":
                 # one latent row [kv_lora | rope] per token; the value cache slot stays empty
                 self.k_cache[i] = torch.zeros(n_blocks, ecfg.kv_block, 1, c.kv_lora + c.rope_head_dim, dtype=dt, device=dev)
@@ -136,12 +142,13 @@ class Executor:
         self.reclaim = None                          # callable() -> bool: free some pages (set by the scheduler)
         self._last_meta = None
         self.profile = None
+        self._step_max_kvlen = None
         self.ep = None                        # ExpertParallel, set by the engine for MoE models under TP
 
     # ---- sizes -----------------------------------------------------------------------------------
     def kv_block_bytes(self) -> int:
         c, e = self.cfg, self.ecfg
-        per = 2 * e.kv_block * c.n_kv * c.head_dim * 2
+        per = 2 * e.kv_block * c.n_kv * c.head_dim * (1 if e.kv_dtype == "fp8" else 2)
         if c.kv_lora > 0:
             per = e.kv_block * (c.kv_lora + c.rope_head_dim) * 2
         return per * max(1, self.cfg.n_attn)
@@ -216,6 +223,8 @@ class Executor:
         for i in self.k_cache:
             self.k_cache[i][d] = self.k_cache[i][s]
             self.v_cache[i][d] = self.v_cache[i][s]
+            if i in self.kv_scale:
+                self.kv_scale[i][d] = self.kv_scale[i][s]
 
     def copy_slot(self, src: int, dst: int, n_tokens: int) -> None:
         """Fork: copy KV pages covering n_tokens and the GDN state from one slot to another
@@ -229,6 +238,8 @@ class Executor:
             for i in self.k_cache:
                 self.k_cache[i][d] = self.k_cache[i][s]
                 self.v_cache[i][d] = self.v_cache[i][s]
+                if i in self.kv_scale:
+                    self.kv_scale[i][d] = self.kv_scale[i][s]
         for t in self.rec_state.values():
             t[dst].copy_(t[src])
         for t in self.conv_state.values():
@@ -327,6 +338,8 @@ class Executor:
         per = n_exp // world
         e_lo, e_hi = rank * per, (rank + 1) * per
         if world == 1:
+            if self.ep is not None and h.shape[0] > getattr(ops, "moe_pair_rows", 1 << 30):
+                return self.ep.moe(ops, h, ids, wts, w[p + "experts_gate_up"], w[p + "experts_down"], shared, sgate, x)
             return ops.moe_experts(h, ids, wts, w[p + "experts_gate_up"], w[p + "experts_down"], e_lo, e_hi, shared, sgate, x)
         part = ops.moe_experts(h, ids, wts, w[p + "experts_gate_up"], w[p + "experts_down"], e_lo, e_hi, shared, sgate, None)
         return self.tp.allreduce_rows(ops, part, x)
@@ -399,18 +412,19 @@ class Executor:
                 x = row(ops.mla_out(ol, w_uv), w[p + "out_proj"], x)
             else:
                 proj = col(x, w[p + "in_proj"], w[p + "input_norm"])
+                kvs = {"kv_scale": self.kv_scale[i]} if self.kv8 else {}
                 q = ops.attn_prep(proj, w[p + "q_norm"], w[p + "k_norm"], self.inv_freq, mv["slot"], mv["pos"],
                                   self.block_table, self.k_cache[i], self.v_cache[i], self.ecfg.kv_block, c.n_q,
-                                  c.n_kv, c.head_dim, c.rotary_dim, c.attn_gate, eps)
+                                  c.n_kv, c.head_dim, c.rotary_dim, c.attn_gate, eps, **kvs)
                 if max_seg_rows > FLASH_MIN_ROWS:
                     o = ops.attention_prefill(q, proj, self.k_cache[i], self.v_cache[i], mv["sslot"], mv["srow0"],
                                               mv["snrows"], mv["spos0"], self.block_table, self.ecfg.kv_block, c.n_q,
                                               c.n_kv, c.head_dim, c.attn_gate, max_seg_rows, row_slot=mv["slot"],
-                                              row_kvlen=mv["kvlen"])
+                                              row_kvlen=mv["kvlen"], **kvs, **({"max_kvlen": self._step_max_kvlen} if kvs else {}))
                 else:
                     o = ops.attention(q, proj, self.k_cache[i], self.v_cache[i], mv["slot"], mv["kvlen"],
                                       self.block_table, self.ecfg.kv_block, c.n_q, c.n_kv, c.head_dim, c.attn_gate,
-                                      nsplit=nsplit)
+                                      nsplit=nsplit, **kvs)
                 x = row(o, w[p + "out_proj"], x)
             if c.is_moe(i):
                 x = self._moe_ffn_sp(x, i, col, row) if sp else self._moe_ffn(x, i)
@@ -490,6 +504,9 @@ class Executor:
                      and self.profile is None and x_add is None)
         logit_rows = self._upload(batch)
         nlog = len(logit_rows)
+        # the e4m3 cache decode before prompt attention sizes its grid by the longest visible context, except inside
+        # graphs, whose launches must not depend on the step
+        self._step_max_kvlen = None if use_graph else max_kvlen
         if not use_graph:
             logits, picks = self._run(T, nseg, nlog, max_seg_rows, nsplit, batch.commit, greedy, x_add)
             return logits, picks, logit_rows

@@ -31,19 +31,20 @@ class CudaOps:
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.status_word = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._ws: Optional[torch.Tensor] = None
-        self._counters = torch.zeros(4096, dtype=torch.int32, device=self.device)
+        self._counters = torch.zeros(16384, dtype=torch.int32, device=self.device)
         self.force_gemv_chunks = False      # debug: run any row count through 8-row GEMV passes
         self.launches = 0                   # kernels launched (or recorded into a graph) through this object
         self.moe_pair_rows = MOE_PAIR_ROWS
         self.mma_gemv_rows = (2, 32)        # row counts routed to the mma.sync weight-streaming kernel
         self._gdn_scratch = None
+        self._kv_scratch = None
         self.fp4_act = False                # NVFP4 weights: quantise activations too and use the tcgen05 GEMM
         self._sf_pool = {}
 
     # ---- workspace ---------------------------------------------------------------------------------
     def _workspace(self, nbytes: int) -> torch.Tensor:
         if self._ws is None or self._ws.numel() * 4 < nbytes:
-            self._ws = torch.empty(max(nbytes // 4, 1 << 20), dtype=torch.float32, device=self.device)
+            self._ws = torch.empty(max(nbytes // 4, 16 << 20), dtype=torch.float32, device=self.device)   # 64 MB up front: graphs keep the pointer
         return self._ws
 
     def status(self) -> int:
@@ -92,14 +93,16 @@ class CudaOps:
             w = w.dense
         M, K = x.shape
         N = w.shape[0] // 2 if swiglu else w.shape[0]
+        # 2..8 rows always; 9..32 rows unless the matrix is very wide or very deep, where the swapped tcgen05 GEMM with
+        # its TMA pipeline measured faster (lm_head, down projection)
         if (self.mma_gemv_rows[0] <= M <= self.mma_gemv_rows[1] and K % 32 == 0 and not self.force_gemv_chunks
-                and w.stride(0) == K):
+                and w.stride(0) == K and (M <= 8 or (N < 65536 and K < 8192) or out_f32 and M <= 8)):
             # a few rows (concurrent decode streams, speculative verify): weights streamed once into mma.sync fragments
             y = out if out is not None else torch.empty(M, N, dtype=torch.float32 if out_f32 else self.dtype, device=self.device)
             self.launches += 1
-            self.C.gemv_mma(y, x, w, norm_w, res, eps, 1 if swiglu else 0)
+            self.C.gemv_mma(y, x, w, norm_w, res, eps, 1 if swiglu else 0, self._workspace(8 << 20), self._counters)
             return y
-        if M <= GEMV_MAX_ROWS or self.force_gemv_chunks or out_f32 and M <= 64:
+        if M <= GEMV_MAX_ROWS or self.force_gemv_chunks:
             y = out if out is not None else torch.empty(M, N, dtype=torch.float32 if out_f32 else self.dtype, device=self.device)
             for r0 in range(0, M, GEMV_MAX_ROWS):
                 r1 = min(M, r0 + GEMV_MAX_ROWS)
@@ -248,28 +251,47 @@ class CudaOps:
 
     # ---- attention ---------------------------------------------------------------------------------
     def attn_prep(self, proj, q_norm, k_norm, inv_freq, row_slot, row_pos, block_table, k_cache, v_cache, kv_block,
-                  nq, nkv, hd, rot, gated, eps):
+                  nq, nkv, hd, rot, gated, eps, kv_scale=None):
+        """q/k RMSNorm + partial RoPE, K/V rows into the paged cache (bf16, or e4m3 codes + per-row scales when
+        `kv_scale` is given)."""
         q = torch.empty(proj.shape[0], nq, hd, dtype=self.dtype, device=self.device)
         self.launches += 1
         self.C.attn_prep(q, k_cache, v_cache, proj, q_norm, k_norm, inv_freq, row_slot, row_pos, block_table,
-                         kv_block, nq, nkv, hd, rot, gated, eps, self.status_word)
+                         kv_block, nq, nkv, hd, rot, gated, eps, self.status_word, kv_scale)
         return q
 
     def attention(self, q, proj, k_cache, v_cache, row_slot, row_kvlen, block_table, kv_block, nq, nkv, hd, gated,
-                  row_base=None, row_mask=None, nsplit=1):
+                  row_base=None, row_mask=None, nsplit=1, kv_scale=None):
         T = q.shape[0]
         out = torch.empty(T, nq * hd, dtype=self.dtype, device=self.device)
         o_part = torch.empty(T, nq, nsplit, hd, dtype=torch.float32, device=self.device)
         ml_part = torch.empty(T, nq, nsplit, 2, dtype=torch.float32, device=self.device)
         self.launches += 2
         self.C.attn_decode(out, o_part, ml_part, q, k_cache, v_cache, proj, row_slot, row_kvlen, row_base, row_mask,
-                           block_table, kv_block, nq, nkv, hd, nsplit, gated)
+                           block_table, kv_block, nq, nkv, hd, nsplit, gated, kv_scale)
         return out
 
     def attention_prefill(self, q, proj, k_cache, v_cache, seg_slot, seg_row0, seg_nrows, seg_pos0, block_table,
-                          kv_block, nq, nkv, hd, gated, max_rows, row_slot=None, row_kvlen=None):
-        """Causal flash attention over prompt segments (their K/V rows are already in the cache)."""
+                          kv_block, nq, nkv, hd, gated, max_rows, row_slot=None, row_kvlen=None, kv_scale=None,
+                          max_kvlen=None):
+        """Causal flash attention over prompt segments (their K/V rows are already in the cache). With an e4m3 cache
+        the visible rows are first decoded into a per-slot bf16 scratch that the kernel reads through an identity
+        block table."""
         out = torch.empty(q.shape[0], nq * hd, dtype=self.dtype, device=self.device)
+        if kv_scale is not None:
+            n_slots, max_blocks = block_table.shape
+            toks = max_blocks * kv_block
+            key = (n_slots, toks, nkv, hd)
+            if self._kv_scratch is None or self._kv_scratch[0] != key:
+                ks = torch.empty(n_slots * max_blocks, kv_block, nkv, hd, dtype=self.dtype, device=self.device)
+                vs = torch.empty_like(ks)
+                ident = torch.arange(n_slots * max_blocks, dtype=torch.int32, device=self.device).view(n_slots, max_blocks)
+                self._kv_scratch = (key, ks, vs, ident.contiguous())
+            _, ks, vs, ident = self._kv_scratch
+            self.launches += 1
+            self.C.kv_dequant(ks, vs, k_cache, v_cache, kv_scale, seg_slot, seg_pos0, seg_nrows, block_table, kv_block,
+                              toks if max_kvlen is None else max_kvlen, nkv, hd, toks)
+            k_cache, v_cache, block_table = ks, vs, ident
         self.launches += 1
         self.C.attn_prefill(out, q, k_cache, v_cache, proj, seg_slot, seg_row0, seg_nrows, seg_pos0, block_table,
                             kv_block, max_rows, nq, nkv, hd, gated)

@@ -66,7 +66,9 @@ class TorchOps:
 
     # ---- attention ---------------------------------------------------------------------------------
     def attn_prep(self, proj, q_norm, k_norm, inv_freq, row_slot, row_pos, block_table, k_cache, v_cache, kv_block,
-                  nq, nkv, hd, rot, gated, eps):
+                  nq, nkv, hd, rot, gated, eps, kv_scale=None):
+        """With `kv_scale` the cache rows take the values an e4m3 cache would return: one scale per (token, kv head),
+        amax / 448, codes rounded to e4m3 (the oracle keeps them dequantised in its float cache)."""
         T = proj.shape[0]
         qw = hd * (2 if gated else 1)
         qg = proj[:, :nq * qw].float().view(T, nq, qw)
@@ -90,12 +92,18 @@ class TorchOps:
         pos = row_pos.long()
         blk = block_table[row_slot.long(), pos // kv_block].long()
         off = pos % kv_block
+        if kv_scale is not None:
+            def fq(x):
+                sc = (x.abs().amax(-1, keepdim=True) / 448.0)
+                sc = torch.where(sc > 0, sc, torch.ones_like(sc))
+                return (x / sc).to(torch.float8_e4m3fn).float() * sc
+            k, v = fq(k.float()), fq(v.float())
         k_cache[blk, off] = k.to(k_cache.dtype)
         v_cache[blk, off] = v.to(v_cache.dtype)
         return q.to(self.dtype)
 
     def attention(self, q, proj, k_cache, v_cache, row_slot, row_kvlen, block_table, kv_block, nq, nkv, hd, gated,
-                  row_base=None, row_mask=None, nsplit=1):
+                  row_base=None, row_mask=None, nsplit=1, kv_scale=None):
         T = q.shape[0]
         out = torch.zeros(T, nq, hd, dtype=torch.float32, device=q.device)
         grp = nq // nkv
@@ -120,7 +128,8 @@ class TorchOps:
         return out.reshape(T, nq * hd).to(self.dtype)
 
     def attention_prefill(self, q, proj, k_cache, v_cache, seg_slot, seg_row0, seg_nrows, seg_pos0, block_table,
-                          kv_block, nq, nkv, hd, gated, max_rows, row_slot=None, row_kvlen=None):
+                          kv_block, nq, nkv, hd, gated, max_rows, row_slot=None, row_kvlen=None, kv_scale=None,
+                          max_kvlen=None):
         if row_slot is None:
             T = q.shape[0]
             row_slot = torch.zeros(T, dtype=torch.int32, device=q.device)

@@ -117,3 +117,20 @@ def test_shard_shapes():
                 assert got[k] == shp
             else:
                 assert got[k] == shp, (k, got[k], shp, world)
+
+
+def test_fp8_kv_cache_stays_close_to_bf16():
+    """e4m3 KV cache (one scale per token and kv head): logits stay close to the full-precision cache and decode
+    through the cache agrees with a longer prompt."""
+    cfg, w, _ = _setup()
+    p = _prompt(cfg, 60)
+    base = Engine(cfg, w, EngineConfig(n_slots=1, max_ctx=128), device="cpu")
+    want, _, _ = base.forward([Segment(0, 0, p, "all")])
+    eng = Engine(cfg, w, EngineConfig(n_slots=1, max_ctx=128, kv_dtype="fp8"), device="cpu")
+    got, _, _ = eng.forward([Segment(0, 0, p[:50], "all")])
+    tail = [eng.forward([Segment(0, 50 + i, [p[50 + i]], "last")])[0] for i in range(10)]
+    got = torch.cat([got] + tail)
+    kl = torch.nn.functional.kl_div(torch.log_softmax(got, -1), torch.log_softmax(want, -1), log_target=True,
+                                    reduction="batchmean").item()
+    assert kl < 1e-3, kl
+    assert not torch.equal(got, want)            # the quantisation is really in the path

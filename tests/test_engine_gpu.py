@@ -82,3 +82,26 @@ def test_nvfp4_w4a4_engine_tracks_the_16bit_activation_path(ext):
         kl = (pa.exp() * (pa - pb)).sum().item()
         assert kl < 0.5, kl           # random-init logits are nearly flat: quantisation noise shows up amplified
     a.check(); b.check()
+
+
+def test_fp8_kv_cache_gpu(ext):
+    """e4m3 KV cache on the GPU (quantising attn-prep, decode kernel reading codes + scales, prompt attention over
+    the decoded scratch) against the CPU oracle with the same cache quantisation."""
+    from ferrite_b200.config import EngineConfig, tiny_hybrid
+    from ferrite_b200.engine.engine import Engine
+    from ferrite_b200.engine.executor import Segment
+    from ferrite_b200.models.weights import init_weights
+    cfg = tiny_hybrid()
+    w = init_weights(cfg, seed=0)
+    p = torch.randint(0, cfg.vocab, (120,), generator=torch.Generator().manual_seed(1)).tolist()
+    ref = Engine(cfg, w, EngineConfig(n_slots=2, max_ctx=256, kv_dtype="fp8"), device="cpu")
+    want, _, _ = ref.forward([Segment(1, 0, p, "all")])
+    eng = Engine(cfg, w, EngineConfig(n_slots=2, max_ctx=256, kv_dtype="fp8"), device="cuda")
+    assert eng.ex.k_cache[3].dtype == torch.uint8 if 3 in eng.ex.k_cache else True
+    a, _, _ = eng.forward([Segment(1, 0, p[:64], "all")], greedy=False)          # prompt chunk 1 (flash over scratch)
+    b, _, _ = eng.forward([Segment(1, 64, p[64:110], "all")], greedy=False)      # chunk 2 sees chunk 1 through the cache
+    tail = [eng.forward([Segment(1, 110 + i, [p[110 + i]], "last")], greedy=False)[0] for i in range(10)]
+    got = torch.cat([a, b] + tail).float().cpu()
+    kl = torch.nn.functional.kl_div(torch.log_softmax(got, -1), torch.log_softmax(want, -1), log_target=True,
+                                    reduction="batchmean").item()
+    assert kl < 2e-2, kl

@@ -105,3 +105,24 @@ def test_ep_pipeline_one_rank(ops, T, E, K):
         ep.check()
         err = (got.float() - want.float()).abs().max().item()
         assert err < 3e-2 * max(1.0, want.abs().max().item()), err
+
+
+def test_moe_80b_widths_few_layers(ext):
+    """The 80B-A3B layer shapes (hidden 2048, 512 experts, top-10, expert FFN 512, shared expert) on a 4-layer cut:
+    a 300-token prompt (grouped tcgen05 expert GEMMs) and decode rows (pair GEMVs) agree with each other through
+    the cache: decoding token t after a prompt of t tokens gives the logits of position t in a longer prompt."""
+    from ferrite_b200.config import EngineConfig, moe_80b, scaled
+    from ferrite_b200.engine.engine import Engine
+    from ferrite_b200.engine.executor import Segment
+    cfg = scaled(moe_80b(), 4)
+    eng = Engine(cfg, None, EngineConfig(n_slots=2, max_ctx=512), device=DEV, seed=0)
+    p = torch.randint(0, cfg.vocab, (304,), generator=torch.Generator().manual_seed(1)).tolist()
+    full, _, _ = eng.forward([Segment(0, 0, p, "all")], greedy=False)
+    eng.forward([Segment(1, 0, p[:300], "none")])
+    tail = [eng.forward([Segment(1, 300 + i, [p[300 + i]], "last")], greedy=False)[0] for i in range(4)]
+    got = torch.cat(tail).float()
+    want = full[300:304].float()
+    kl = torch.nn.functional.kl_div(torch.log_softmax(got, -1), torch.log_softmax(want, -1), log_target=True,
+                                    reduction="batchmean").item()
+    assert kl < 2e-2, kl
+    assert eng.ex.ep is not None and eng.ex.ep.calls > 0
