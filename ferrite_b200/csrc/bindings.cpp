@@ -78,7 +78,7 @@ int64_t gemm_workspace_bytes(int64_t M, int64_t N, int64_t split_k) {
 void gemm(Tensor Y, Tensor X, Tensor W, c10::optional<Tensor> res, int64_t mode, int64_t split_k,
           c10::optional<Tensor> workspace, c10::optional<Tensor> counters, c10::optional<Tensor> status) {
   int M = (int)X.size(0), K = (int)X.size(1);
-  int N = (int)(mode == 1 ? W.size(0) / 2 : W.size(0));
+  int N = (int)((mode & 1) ? W.size(0) / 2 : W.size(0));
   check(fb_gemm_bf16(Y.data_ptr(), X.data_ptr(), W.data_ptr(), cptr(res), M, N, K, (long)X.stride(0),
                      (long)Y.stride(0), (int)mode, (int)split_k, (float*)mptr(workspace), (int*)mptr(counters),
                      (int*)mptr(status), sm_count(), cur_stream()), "gemm");

@@ -9,6 +9,7 @@
 // Every wait in this library is bounded. A wait that runs out records a code in a status word in global
 // memory and the kernel returns normally; nothing traps and nothing spins for ever.
 #pragma once
+#include <cstdlib>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -383,7 +384,8 @@ static inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 blo
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr; cfg.numAttrs = 1;
+  static const bool no_pdl = [] { const char* e = getenv("FB_NO_PDL"); return e && e[0] == '1'; }();   // debugging aid
+  cfg.attrs = attr; cfg.numAttrs = no_pdl ? 0 : 1;
   return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
 }
 

@@ -73,6 +73,7 @@ struct GemmArgs {
   int fp8;
   const float* scale_m;     // [M]
   const float* scale_n;     // [N] (SwiGLU: [2N], gate features then up features)
+  int out_f32;              // Y is fp32 [M][ldy] instead of bf16 (router logits, lm_head rows)
   void* Y;
   const __nv_bfloat16* res;
   float* workspace;
@@ -538,16 +539,23 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                   for (int j = 0; j < 4; ++j) { v[q * 8 + 2 * j] += bf_lo(ru[j]); v[q * 8 + 2 * j + 1] += bf_hi(ru[j]); }
                 }
               }
-              uint4* yp = reinterpret_cast<uint4*>(Yb + (size_t)m * a.ldy + n);
+              if (a.out_f32) {
+                float4* yf = reinterpret_cast<float4*>(reinterpret_cast<float*>(a.Y) + (size_t)m * a.ldy + n);
 #pragma unroll
-              for (int q = 0; q < 4; ++q)
-                yp[q] = make_uint4(pack_bf2(v[q * 8], v[q * 8 + 1]), pack_bf2(v[q * 8 + 2], v[q * 8 + 3]),
-                                   pack_bf2(v[q * 8 + 4], v[q * 8 + 5]), pack_bf2(v[q * 8 + 6], v[q * 8 + 7]));
+                for (int q = 0; q < 8; ++q) yf[q] = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+              } else {
+                uint4* yp = reinterpret_cast<uint4*>(Yb + (size_t)m * a.ldy + n);
+#pragma unroll
+                for (int q = 0; q < 4; ++q)
+                  yp[q] = make_uint4(pack_bf2(v[q * 8], v[q * 8 + 1]), pack_bf2(v[q * 8 + 2], v[q * 8 + 3]),
+                                     pack_bf2(v[q * 8 + 4], v[q * 8 + 5]), pack_bf2(v[q * 8 + 6], v[q * 8 + 7]));
+              }
             } else {
               for (int j = 0; j < 32 && n + j < a.N; ++j) {
                 float x = v[j];
                 if (a.res) x += bf2f(a.res[(size_t)m * a.ldy + n + j]);
-                Yb[(size_t)m * a.ldy + n + j] = f2bf(x);
+                if (a.out_f32) reinterpret_cast<float*>(a.Y)[(size_t)m * a.ldy + n + j] = x;
+                else Yb[(size_t)m * a.ldy + n + j] = f2bf(x);
               }
             }
           }
@@ -574,7 +582,8 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                   float x = __uint_as_float(r0[j]) * sc * (a.scale_n ? a.scale_n[n] : 1.f);
                   if (a.dual) x = siluf_(x) * (__uint_as_float(r1[j]) * sc * (a.scale_n ? a.scale_n[a.N + n] : 1.f));
                   if (a.res) x += bf2f(a.res[(size_t)m * a.ldy + n]);
-                  Yb[(size_t)m * a.ldy + n] = f2bf(x);
+                  if (a.out_f32) reinterpret_cast<float*>(a.Y)[(size_t)m * a.ldy + n] = x;
+                  else Yb[(size_t)m * a.ldy + n] = f2bf(x);
                 }
               }
             }
@@ -620,7 +629,8 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 if (a.dual) u *= sc * (a.scale_n ? a.scale_n[a.N + n] : 1.f);
                 float x = a.dual ? siluf_(g) * u : g;
                 if (a.res) x += bf2f(a.res[(size_t)m * a.ldy + n]);
-                Yb[(size_t)m * a.ldy + n] = f2bf(x);
+                if (a.out_f32) reinterpret_cast<float*>(a.Y)[(size_t)m * a.ldy + n] = x;
+                else Yb[(size_t)m * a.ldy + n] = f2bf(x);
               }
             }
             if (etid == 0) a.counters[tile_id] = 0;       // self-cleaning for the next launch
@@ -716,7 +726,7 @@ struct GemmPlan { GemmArgs a; int grid; size_t smem; };
 
 static int plan_gemm(GemmPlan& p, int M, int N, int K, int mode, int split_k, int sm_count, int fp8 = 0) {
   GemmArgs& a = p.a;
-  a.fp8 = fp8; a.scale_m = nullptr; a.scale_n = nullptr;
+  a.fp8 = fp8; a.scale_m = nullptr; a.scale_n = nullptr; a.out_f32 = 0;
   a.M = M; a.N = N; a.K = K;
   a.dual = mode == 1;
   a.swap = M <= 64;

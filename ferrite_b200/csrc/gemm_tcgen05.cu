@@ -10,10 +10,13 @@ extern "C" long fb_gemm_workspace_bytes(int M, int N, int split_k) {
   return tiles * split_k * 2L * bn * GM_BM * (long)sizeof(float);
 }
 
+// mode bit 0: SwiGLU over gate|up rows; bit 1: Y is fp32 (residual stays bf16 with the same leading dimension)
 extern "C" int fb_gemm_bf16(void* Y, const void* X, const void* W, const void* res, int M, int N, int K, long ldx,
                             long ldy, int mode, int split_k, float* workspace, int* counters, int* status,
                             int sm_count, cudaStream_t s) {
   if (M <= 0 || N <= 0) return 0;
+  const int out_f32 = (mode >> 1) & 1;
+  mode &= 1;
   if (K % 8 || ldx % 8 || (ldy % 8 && M > 64)) return -1;
   if (sm_count <= 0) sm_count = 148;
   GemmPlan p{};
@@ -22,7 +25,7 @@ extern "C" int fb_gemm_bf16(void* Y, const void* X, const void* W, const void* r
   GemmArgs& a = p.a;
   if (a.split_k > 1 && (!workspace || !counters)) return -6;
   a.Y = Y; a.res = (const __nv_bfloat16*)res; a.workspace = workspace; a.counters = counters; a.status = status;
-  a.ldy = ldy;
+  a.ldy = ldy; a.out_f32 = out_f32;
   const int w_rows = a.dual ? 2 * N : N;
   CUtensorMap tmA, tmB;
   if (a.swap) {

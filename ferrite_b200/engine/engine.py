@@ -83,6 +83,9 @@ class Engine:
 
     # ---- rows ------------------------------------------------------------------------------------
     def forward(self, segments: Sequence[Segment], commit: bool = True, greedy: bool = True, x_add=None):
+        """One step over the segments: returns (logits [rows wanted, vocab] or None, picks, row indices). On the GPU the
+        returned tensors are the output buffers of the step's CUDA graph: they are overwritten by the next step of
+        the same shape, so a caller that keeps them across steps clones them."""
         out = self.ex.forward(StepBatch(list(segments), commit=commit), greedy=greedy, x_add=x_add)
         self._last_segments = list(segments)
         if commit:

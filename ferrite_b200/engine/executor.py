@@ -307,15 +307,16 @@ class Executor:
         c, w, ops = self.cfg, self.w, self.ops
         p = f"l{i}."
         h, _ = ops.rmsnorm(x, w[p + "post_norm"], c.eps, True)
-        small = h.shape[0] <= 64
-        logits = ops.linear(h, w[p + "router"], out_f32=True) if small else ops.linear(h, w[p + "router"]).float()
+        # router logits in fp32 for every row count: bf16 logits would reorder near-tied experts between the prompt
+        # and the decode path
+        logits = ops.linear(h, w[p + "router"], out_f32=True)
         ids, wts = ops.moe_route(logits.contiguous(), w.get(p + "router_bias"), 0 if c.router == "softmax" else 1, c.top_k,
                                  c.n_groups, c.topk_groups, c.route_scale)
         shared = sgate = None
         if c.n_shared:
             shared = row(col(x, w[p + "shared_gate_up"], w[p + "post_norm"], swiglu=True), w[p + "shared_down"], None)
             if c.router == "softmax":
-                sgate = ops.linear(h, w[p + "shared_gate"], out_f32=True) if small else ops.linear(h, w[p + "shared_gate"]).float()
+                sgate = ops.linear(h, w[p + "shared_gate"], out_f32=True)
         return self.ep.moe(ops, h, ids, wts, w[p + "experts_gate_up"], w[p + "experts_down"], shared, sgate, x)
 
     def _moe_ffn(self, x, i):
@@ -324,14 +325,14 @@ class Executor:
         c, w, ops = self.cfg, self.w, self.ops
         p = f"l{i}."
         h, _ = ops.rmsnorm(x, w[p + "post_norm"], c.eps, True)
-        logits = ops.linear(h, w[p + "router"], out_f32=True) if h.shape[0] <= 64 else ops.linear(h, w[p + "router"]).float()
+        logits = ops.linear(h, w[p + "router"], out_f32=True)
         ids, wts = ops.moe_route(logits.contiguous(), w.get(p + "router_bias"), 0 if c.router == "softmax" else 1, c.top_k,
                                  c.n_groups, c.topk_groups, c.route_scale)
         shared = sgate = None
         if c.n_shared:
             shared = ops.linear(ops.linear(h, w[p + "shared_gate_up"], swiglu=True), w[p + "shared_down"])
             if c.router == "softmax":
-                sgate = ops.linear(h, w[p + "shared_gate"], out_f32=True) if h.shape[0] <= 64 else ops.linear(h, w[p + "shared_gate"]).float()
+                sgate = ops.linear(h, w[p + "shared_gate"], out_f32=True)
         world = self.tp.world if self.tp is not None else 1
         rank = self.tp.rank if self.tp is not None else 0
         n_exp = self.full_cfg.n_experts

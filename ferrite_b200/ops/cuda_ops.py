@@ -113,7 +113,8 @@ class CudaOps:
         if norm_w is not None:
             x, _ = self.rmsnorm(x, norm_w, eps, True)
         # the wide-M epilogue stores 16-byte row pieces: give odd widths a padded leading dimension
-        y = out if out is not None else torch.empty(M, (N + 7) // 8 * 8, dtype=self.dtype, device=self.device)[:, :N]
+        y = out if out is not None else torch.empty(M, (N + 7) // 8 * 8, dtype=torch.float32 if out_f32 else self.dtype,
+                                                    device=self.device)[:, :N]
         split = self._split_k(M, N, K) if M <= 64 else 1
         ws = cnt = None
         if split > 1:
@@ -121,8 +122,8 @@ class CudaOps:
             ws = self._workspace(nb)
             cnt = self._counters
         self.launches += 1
-        self.C.gemm(y, x, w, res, 1 if swiglu else 0, split, ws, cnt, self.status_word)
-        return y.float() if out_f32 else y
+        self.C.gemm(y, x, w, res, (1 if swiglu else 0) | (2 if out_f32 else 0), split, ws, cnt, self.status_word)
+        return y
 
     # ---- FP8 (e4m3) weights and activations -----------------------------------------------------------
     @staticmethod

@@ -346,3 +346,12 @@ def test_gemv_mma(ops, tops, M, N, K):
     assert y32.dtype == torch.float32
     close(y32, tops.linear(x, w, norm_w=nw, eps=1e-6, out_f32=True))
     assert torch.equal(ops.linear(x, w, res=r), ops.linear(x, w, res=r))
+
+
+@pytest.mark.parametrize("M,N,K", [(40, 512, 1024), (300, 512, 2048), (2048, 1000, 512)])
+def test_gemm_tcgen05_fp32_out(ops, tops, M, N, K):
+    x, w = rnd(M, K, seed=1), rnd(N, K, scale=0.05, seed=2)
+    y = ops.linear(x, w, out_f32=True)
+    assert y.dtype == torch.float32
+    want = tops.linear(x, w, out_f32=True)
+    assert (y - want).abs().max().item() < 2e-3 * max(1.0, want.abs().max().item())

@@ -62,4 +62,4 @@ def test_mla_engine_gpu(ext):
     got = torch.cat([got] + tail).float().cpu()
     kl = torch.nn.functional.kl_div(torch.log_softmax(got, -1), torch.log_softmax(want, -1), log_target=True,
                                     reduction="batchmean").item()
-    assert kl < 5e-2, kl      # bf16 against fp32 with discrete expert routing: a flipped pick moves a row visibly
+    assert kl < 2e-2, kl
