@@ -128,7 +128,7 @@ def test_fp8_kv_cache_stays_close_to_bf16():
     want, _, _ = base.forward([Segment(0, 0, p, "all")])
     eng = Engine(cfg, w, EngineConfig(n_slots=1, max_ctx=128, kv_dtype="fp8"), device="cpu")
     got, _, _ = eng.forward([Segment(0, 0, p[:50], "all")])
-    tail = [eng.forward([Segment(0, 50 + i, [p[50 + i]], "last")])[0] for i in range(10)]
+    tail = [eng.forward([Segment(0, 50 + i, [p[50 + i]], "last")])[0].clone() for i in range(10)]
     got = torch.cat([got] + tail)
     kl = torch.nn.functional.kl_div(torch.log_softmax(got, -1), torch.log_softmax(want, -1), log_target=True,
                                     reduction="batchmean").item()

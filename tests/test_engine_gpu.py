@@ -100,7 +100,7 @@ def test_fp8_kv_cache_gpu(ext):
     assert eng.ex.k_cache[3].dtype == torch.uint8 if 3 in eng.ex.k_cache else True
     a, _, _ = eng.forward([Segment(1, 0, p[:64], "all")], greedy=False)          # prompt chunk 1 (flash over scratch)
     b, _, _ = eng.forward([Segment(1, 64, p[64:110], "all")], greedy=False)      # chunk 2 sees chunk 1 through the cache
-    tail = [eng.forward([Segment(1, 110 + i, [p[110 + i]], "last")], greedy=False)[0] for i in range(10)]
+    tail = [eng.forward([Segment(1, 110 + i, [p[110 + i]], "last")], greedy=False)[0].clone() for i in range(10)]
     got = torch.cat([a, b] + tail).float().cpu()
     kl = torch.nn.functional.kl_div(torch.log_softmax(got, -1), torch.log_softmax(want, -1), log_target=True,
                                     reduction="batchmean").item()

@@ -18,7 +18,7 @@ def test_mla_engine_matches_oracle():
     want = ref.forward(prompt, ref.new_state())
     eng = Engine(cfg, w, EngineConfig(n_slots=2, max_ctx=128), device="cpu")
     got, _, _ = eng.forward([Segment(1, 0, prompt[:30], "all")])                      # prompt rows, causal
-    tail = [eng.forward([Segment(1, 30 + i, [prompt[30 + i]], "last")])[0] for i in range(10)]   # decode rows
+    tail = [eng.forward([Segment(1, 30 + i, [prompt[30 + i]], "last")])[0].clone() for i in range(10)]   # decode rows
     got = torch.cat([got] + tail)
     assert torch.allclose(got, want, atol=3e-5, rtol=1e-4)
 

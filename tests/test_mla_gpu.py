@@ -58,7 +58,7 @@ def test_mla_engine_gpu(ext):
     want, _, _ = ref.forward([Segment(0, 0, p, "all")])
     eng = Engine(cfg, w, EngineConfig(n_slots=1, max_ctx=128), device=DEV)
     got, _, _ = eng.forward([Segment(0, 0, p[:30], "all")])
-    tail = [eng.forward([Segment(0, 30 + i, [p[30 + i]], "last")])[0] for i in range(10)]
+    tail = [eng.forward([Segment(0, 30 + i, [p[30 + i]], "last")])[0].clone() for i in range(10)]
     got = torch.cat([got] + tail).float().cpu()
     kl = torch.nn.functional.kl_div(torch.log_softmax(got, -1), torch.log_softmax(want, -1), log_target=True,
                                     reduction="batchmean").item()

@@ -76,7 +76,7 @@ def test_moe_engine_gpu(ext, router):
     want, _, _ = ref.forward([Segment(0, 0, p, "all")])
     eng = Engine(cfg, w, EngineConfig(n_slots=2, max_ctx=128), device=DEV)
     got, _, _ = eng.forward([Segment(0, 0, p[:80], "all")])          # grouped GEMM path
-    tail = [eng.forward([Segment(0, 80 + i, [p[80 + i]], "last")])[0] for i in range(8)]   # pair GEMV path
+    tail = [eng.forward([Segment(0, 80 + i, [p[80 + i]], "last")])[0].clone() for i in range(8)]   # pair GEMV path
     got = torch.cat([got] + tail).float().cpu()
     # bf16 weights/activations against the fp32 oracle: compare distributions, not raw logits
     kl = torch.nn.functional.kl_div(torch.log_softmax(got, -1), torch.log_softmax(want, -1), log_target=True,
@@ -119,7 +119,7 @@ def test_moe_80b_widths_few_layers(ext):
     p = torch.randint(0, cfg.vocab, (304,), generator=torch.Generator().manual_seed(1)).tolist()
     full, _, _ = eng.forward([Segment(0, 0, p, "all")], greedy=False)
     eng.forward([Segment(1, 0, p[:300], "none")])
-    tail = [eng.forward([Segment(1, 300 + i, [p[300 + i]], "last")], greedy=False)[0] for i in range(4)]
+    tail = [eng.forward([Segment(1, 300 + i, [p[300 + i]], "last")], greedy=False)[0].clone() for i in range(4)]
     got = torch.cat(tail).float()
     want = full[300:304].float()
     kl = torch.nn.functional.kl_div(torch.log_softmax(got, -1), torch.log_softmax(want, -1), log_target=True,
