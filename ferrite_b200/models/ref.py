@@ -1,6 +1,6 @@
 """Plain PyTorch fp32 reference of every model family: the oracle for the CUDA kernels and the CPU path.
 
-Numerics follow the reference's written conventions (`crates/fe-xe/DESIGN.md:44-60`): RMSNorm with (1 + w),
+Numerics follow the reference's written conventions (the design notes of `crates/fe-xe`, lines 44-60): RMSNorm with (1 + w),
 per-head q/k norm and partial RoPE with a sigmoid output gate on attention, Gated DeltaNet with a causal
 depthwise conv (tap 0 = oldest), `g = exp(-exp(A_log) * softplus(a + dt_bias))`, `beta = sigmoid(b)`,
 `S = S g; delta = (v - S^T k) beta; S += k (x) delta; y = S^T q`, gated RMSNorm `rmsnorm(y) * w * silu(z)`.

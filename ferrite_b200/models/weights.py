@@ -8,7 +8,7 @@ projections that share an input are stored fused, so a decode step issues one we
 * MLP  `gate_up`  rows = [gate | up]                        (2*inter x hidden)
 
 RMSNorm weights are stored zero-centred (effective weight 1 + w), the GDN gated-norm weight as used
-(reference convention, `crates/fe-xe/DESIGN.md:56-57`).
+(reference convention, the design notes of `crates/fe-xe`, lines 56-57).
 """
 from __future__ import annotations
 
