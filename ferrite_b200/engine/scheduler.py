@@ -43,6 +43,7 @@ class SchedOptions:
     step_timeout_s: float = 120.0
     prof: int = 0                      # 1: one line per step on stderr
     share_min: int = PREFIX_MIN        # shortest common prefix worth waiting for / forking from a running request
+    mixed: bool = True                 # decode rows and a prompt chunk share one forward when both are waiting
 
     @staticmethod
     def from_env() -> "SchedOptions":
@@ -354,9 +355,15 @@ class Scheduler:
         decoders = [a for a in self.active.values() if not a.pending and a.next_token is not None]
         prefills = [a for a in self.active.values() if a.pending]
         n_dec = n_pre = 0
-        if decoders:
-            n_dec = self._decode_step(decoders)
         budget = self.opts.batch_rows
+        if (decoders and prefills and self.opts.mixed and self.opts.spec == 0 and self.drafter is None
+                and all(a.req.sampling.greedy for a in decoders)):
+            # continuous batching: the decode rows ride along with a prompt chunk, one pass over the weights for both
+            n_dec, n_pre = self._mixed_step(decoders, prefills[0], budget)
+            budget -= n_pre
+            prefills = prefills[1:]
+        elif decoders:
+            n_dec = self._decode_step(decoders)
         for a in prefills:                                # short remainders first (reference: short chunks first)
             if budget <= 0:
                 break
@@ -367,17 +374,53 @@ class Scheduler:
             print(f"step {self.step_no}: dec {n_dec} rows, prompt {n_pre} rows, {1e3 * (time.time() - t0):.2f} ms",
                   file=sys.stderr)
 
-    def _prefill_step(self, a: Active, budget: int) -> int:
-        """Run the next chunk of a prompt. Chunks end at snapshot positions so the state can be saved there."""
+    def _prefill_cut(self, a: Active, budget: int):
+        """Next chunk of a prompt: (rows, tokens, is the last chunk, greedy pick usable). Chunks end at snapshot
+        positions so the state can be saved there."""
         cut = prompt_cuts(len(a.pending), min(self.eng.ecfg.prefill_chunk, max(32, budget)), self.eng.ecfg.prompt_align)[0]
         for sp in a.snap_at:
             if a.pos < sp < a.pos + cut:
                 cut = sp - a.pos
                 break
-        toks = a.pending[:cut]
         last = cut == len(a.pending)
         greedy = a.req.sampling.greedy and not (a.req.sampling.banned_first and not a.out)
+        return cut, a.pending[:cut], last, greedy
+
+    def _mixed_step(self, decoders: List[Active], a: Active, budget: int):
+        """One forward over a decode row of every decoding request plus the next prompt chunk of `a`."""
+        cut, toks, last, greedy = self._prefill_cut(a, max(32, budget - len(decoders)))
+        if not greedy:
+            return self._decode_step(decoders), self._prefill_step(a, budget)
+        segs = [Segment(d.slot, d.pos, [d.next_token], "last") for d in decoders]
+        segs.append(Segment(a.slot, a.pos, toks, "last" if last else "none"))
+        logits, picks, rows = self.eng.forward(segs, commit=True, greedy=True)
+        ids = picks[0].tolist()
+        if self.opts.finite_check and not bool(picks[1].all()):
+            for d in decoders + [a]:
+                self._finish(d, "error", message="non-finite logits")
+            return len(decoders), cut
+        for i, d in enumerate(decoders):
+            d.pos += 1
+            self._accept(d, [int(ids[i])])
+        self._prefill_done(a, cut, toks, last, int(ids[len(decoders)]) if last else None)
+        return len(decoders), cut
+
+    def _prefill_step(self, a: Active, budget: int) -> int:
+        """Run the next chunk of a prompt on its own."""
+        cut, toks, last, greedy = self._prefill_cut(a, budget)
         logits, picks, _ = self.eng.forward([Segment(a.slot, a.pos, toks, "last" if last else "none")], greedy=greedy)
+        tok = None
+        if last:
+            tok = int(picks[0][0]) if greedy else a.sampler.sample(logits[0], first=not a.out)
+            if self.opts.finite_check and not bool(torch.isfinite(logits[0]).all()):
+                a.pos += cut
+                a.pending = a.pending[cut:]
+                self._finish(a, "error", message="non-finite logits")
+                return cut
+        self._prefill_done(a, cut, toks, last, tok)
+        return cut
+
+    def _prefill_done(self, a: Active, cut: int, toks: List[int], last: bool, tok) -> None:
         a.pos += cut
         a.pending = a.pending[cut:]
         self.slot_cache[a.slot].tokens = (a.req.prompt + a.out)[:a.pos]
@@ -388,12 +431,7 @@ class Scheduler:
             self.drafter.absorb(a.slot, toks, a.pos - cut, self.eng.taps)
         if last:
             a.t_prompt_done = time.time()
-            tok = int(picks[0][0]) if greedy else a.sampler.sample(logits[0], first=not a.out)
-            if self.opts.finite_check and not bool(torch.isfinite(logits[0]).all()):
-                self._finish(a, "error", message="non-finite logits")
-                return cut
             self._accept(a, [tok])
-        return cut
 
     def _decode_step(self, decoders: List[Active]) -> int:
         """One decode / verify step over all decoding requests: a row per request plus its draft rows."""

@@ -105,3 +105,34 @@ def test_fp8_kv_cache_gpu(ext):
     kl = torch.nn.functional.kl_div(torch.log_softmax(got, -1), torch.log_softmax(want, -1), log_target=True,
                                     reduction="batchmean").item()
     assert kl < 2e-2, kl
+
+
+def test_mixed_decode_and_prompt_rows_in_one_step(ext):
+    """27B layer widths (2 layers): a decode row of one slot and a 100-row prompt chunk of another in ONE forward give
+    the logits of the two separate forwards (chunked GDN scan with a one-row segment, flash attention with a one-row
+    tile, one GEMM for all rows)."""
+    from ferrite_b200.config import EngineConfig, hybrid_27b, scaled
+    from ferrite_b200.engine.engine import Engine
+    from ferrite_b200.engine.executor import Segment
+    cfg = scaled(hybrid_27b(), 4)
+    g = torch.Generator().manual_seed(3)
+    pa = torch.randint(0, cfg.vocab, (70,), generator=g).tolist()
+    pb = torch.randint(0, cfg.vocab, (100,), generator=g).tolist()
+
+    def fresh():
+        e = Engine(cfg, None, EngineConfig(n_slots=2, max_ctx=512), device="cuda", seed=0)
+        e.forward([Segment(0, 0, pa[:69], "none")])
+        return e
+    e1 = fresh()
+    da = e1.forward([Segment(0, 69, [pa[69]], "last")], greedy=False)[0].clone()
+    db = e1.forward([Segment(1, 0, pb, "last")], greedy=False)[0].clone()
+    e2 = fresh()
+    both = e2.forward([Segment(0, 69, [pa[69]], "last"), Segment(1, 0, pb, "last")], greedy=False)[0]
+    assert both.shape[0] == 2
+    scale = max(1.0, da.abs().max().item())
+    assert (both[0] - da[0]).abs().max().item() < 3e-2 * scale
+    assert (both[1] - db[0]).abs().max().item() < 3e-2 * scale
+    # and the states they leave behind continue identically
+    n1 = e1.forward([Segment(0, 70, [5], "last")], greedy=False)[0].clone()
+    n2 = e2.forward([Segment(0, 70, [5], "last")], greedy=False)[0].clone()
+    assert (n1 - n2).abs().max().item() < 3e-2 * scale

@@ -210,3 +210,36 @@ def test_shared_prefill_forks_from_the_running_request():
     assert got == want
     assert sched.stats.get("forked", 0) == 1
     assert sched.stats["cached_tokens"] >= 128
+
+
+def test_mixed_steps_decode_rows_ride_with_prompt_chunks():
+    """A request that is decoding keeps producing tokens while another one prefills: both share forwards, and the
+    tokens are those of separate runs."""
+    cfg = tiny_hybrid()
+    w = init_weights(cfg, seed=0)
+    g = torch.Generator().manual_seed(31)
+    p1 = torch.randint(0, cfg.vocab, (20,), generator=g).tolist()
+    p2 = torch.randint(0, cfg.vocab, (200,), generator=g).tolist()
+    ecfg = EngineConfig(n_slots=2, max_ctx=512, prefill_chunk=64)
+    want = [generate(Scheduler(Engine(cfg, w, ecfg, device="cpu"), SchedOptions(mixed=False)), [p], Sampling(max_tokens=12))[0]
+            for p in (p1, p2)]
+    sched = Scheduler(Engine(cfg, w, ecfg, device="cpu"), SchedOptions(mixed=True))
+    outs, done = [[], []], [False, False]
+
+    def sink(i):
+        def f(ev):
+            if ev.kind == "tokens":
+                outs[i].extend(ev.tokens)
+            else:
+                done[i] = True
+        return f
+    sched.submit(Request(list(p1), Sampling(max_tokens=12), sink(0)))
+    for _ in range(2):                       # the first request reaches decoding
+        sched.run_once()
+    sched.submit(Request(list(p2), Sampling(max_tokens=12), sink(1)))
+    steps_before = sched.stats["steps"]
+    while not all(done):
+        sched.run_once()
+    assert outs == want
+    # 200 prompt tokens in 64-row chunks = 4 chunk steps; without mixing the decode steps of request 1 would add to them
+    assert sched.stats["steps"] - steps_before <= 4 + 12
