@@ -58,3 +58,26 @@ def test_quickbench_reports_streams(capsys):
         loop.call_soon_threadsafe(loop.stop)
     line = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
     assert rc == 0 and line["ok"] == 3 and line["total_tokens"] > 0
+
+
+def test_launch_commands_and_step_summary():
+    from ferrite_b200.tools.launch import command
+    from ferrite_b200.tools.sched_steps import summarise
+    one = command(1, ["--preset", "tiny"])
+    assert one[1:3] == ["-m", "ferrite_b200.server"]
+    tp = command(8, ["--preset", "27b"], master_port=29500)
+    assert "--nproc-per-node=8" in tp and tp[tp.index("--master-addr") + 1] == "127.0.0.1" and tp[-2:] == ["--preset", "27b"]
+    s = summarise(["step 1: dec 0 rows, prompt 64 rows, 3.10 ms", "step 2: dec 2 rows, prompt 64 rows, 3.50 ms",
+                   "noise", "step 3: dec 2 rows, prompt 0 rows, 1.00 ms"])
+    assert s["prompt"]["steps"] == 1 and s["mixed"]["rows"] == 66 and s["decode"]["ms_per_step"] == 1.0
+
+
+def test_sweep_runs_points(capsys):
+    from ferrite_b200.tools.sweep import main
+    url, loop = _serve()
+    try:
+        rc = main(["--base-url", url, "--streams", "1,2", "--prompt-tokens", "8", "--max-tokens", "8"])
+    finally:
+        loop.call_soon_threadsafe(loop.stop)
+    out = capsys.readouterr().out
+    assert rc == 0 and "agg tok/s" in out
