@@ -134,3 +134,17 @@ def test_fp8_kv_cache_stays_close_to_bf16():
                                     reduction="batchmean").item()
     assert kl < 1e-3, kl
     assert not torch.equal(got, want)            # the quantisation is really in the path
+
+
+def test_op_profiler_counts_calls():
+    from ferrite_b200.utils.profiler import OpProfiler
+    cfg, w, _ = _setup()
+    eng = Engine(cfg, w, EngineConfig(n_slots=1, max_ctx=64), device="cpu")
+    prof = OpProfiler(eng)
+    eng.forward([Segment(0, 0, _prompt(cfg, 8), "last")])
+    rep = prof.report()
+    prof.detach()
+    n_layers = cfg.n_layers
+    assert rep["linear"]["calls"] >= 4 * n_layers and rep["linear"]["ms"] > 0
+    assert "attention" in rep or "attention_prefill" in rep
+    assert eng.ex.profile is None
