@@ -136,3 +136,27 @@ def test_mixed_decode_and_prompt_rows_in_one_step(ext):
     n1 = e1.forward([Segment(0, 70, [5], "last")], greedy=False)[0].clone()
     n2 = e2.forward([Segment(0, 70, [5], "last")], greedy=False)[0].clone()
     assert (n1 - n2).abs().max().item() < 3e-2 * scale
+
+
+def test_verify_then_commit_at_27b_widths(ext):
+    """Speculative verification at the 27B layer widths: 1 + 8 rows scored without committing, the first 5 accepted
+    (replay of the GDN state from the saved projections, KV rows kept), then the next decode row must match the plain
+    path that fed the same 5 tokens normally."""
+    cfg = scaled(hybrid_27b(), 4)
+    p = _prompt(cfg, 90)
+    draft = _prompt(cfg, 9, seed=7)
+    eng = Engine(cfg, None, EngineConfig(n_slots=1, max_ctx=512), device="cuda", seed=3)
+    eng.forward([Segment(0, 0, p, "none")])
+    before = eng.ex.state_save(0)
+    eng.forward([Segment(0, 90, draft, "all")], commit=False)
+    after = eng.ex.state_save(0)
+    assert torch.equal(before["rec"], after["rec"]) and torch.equal(before["conv"], after["conv"])
+    eng.commit_verified([5])
+    assert eng.slot_len[0] == 95
+    a = eng.forward([Segment(0, 95, [11], "last")], greedy=False)[0].clone()
+    ref = Engine(cfg, None, EngineConfig(n_slots=1, max_ctx=512), device="cuda", seed=3)
+    ref.forward([Segment(0, 0, p + draft[:5], "none")])
+    b = ref.forward([Segment(0, 95, [11], "last")], greedy=False)[0].clone()
+    err = (a - b).abs().max().item()
+    assert err < 0.03 * b.abs().max().item() + 0.02, err
+    eng.check()
