@@ -138,6 +138,8 @@ class Executor:
         self._R, self._S = R, S
         self.graphs: "OrderedDict[tuple, tuple]" = OrderedDict()
         self.taps: List[torch.Tensor] = []
+        self.last_hidden: Optional[torch.Tensor] = None
+        self.input_rows = False          # True: forward(x_add=...) replaces the embedded rows instead of adding to them
         self.verify_proj: Dict[int, torch.Tensor] = {}
         self.reclaim = None                          # callable() -> bool: free some pages (set by the scheduler)
         self._last_meta = None
@@ -459,9 +461,12 @@ class Executor:
         mv = self._meta_views(T, nseg, nlog)
         self._last_meta = (mv, max_seg_rows)
         x = self.ops.embed(self.w["embed"], mv["tok"])
-        if x_add is not None:
+        if x_add is not None and self.input_rows:
+            x = x_add.to(x.dtype)                            # MTP head: the caller computed the input rows itself
+        elif x_add is not None:
             x = (x.float() + x_add.float()).to(x.dtype)      # drafter: target features fused into the input rows
         x = self._layers(x, mv, T, nseg, max_seg_rows, nsplit, commit)
+        self.last_hidden = x                                 # rows before the final norm (source of the MTP head)
         return self._head(x, mv, nlog, greedy)
 
     def attn_splits(self, max_kvlen: int) -> int:
@@ -523,14 +528,14 @@ class Executor:
                 out = self._run(T, nseg, nlog, max_seg_rows, nsplit, batch.commit, greedy)
             n_kernels = self.ops.launches - l0
             self.ops.launches = l0
-            hit = (g, out, n_kernels)
+            hit = (g, out, n_kernels, self.taps, self.last_hidden)
             self.graphs[key] = hit
             if len(self.graphs) > self.ecfg.graph_max:
                 self.graphs.popitem(last=False)
             # capture does not execute: replay below performs the step
         else:
             self.graphs.move_to_end(key)
-        g, (logits, picks), n_kernels = hit
+        g, (logits, picks), n_kernels, self.taps, self.last_hidden = hit      # taps / hidden: this graph's buffers
         self._last_meta = (self._meta_views(T, nseg, nlog), max_seg_rows)
         g.replay()
         self.ops.launches += n_kernels

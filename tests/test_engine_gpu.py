@@ -160,3 +160,24 @@ def test_verify_then_commit_at_27b_widths(ext):
     err = (a - b).abs().max().item()
     assert err < 0.03 * b.abs().max().item() + 0.02, err
     eng.check()
+
+
+def test_mtp_chain_drafter_on_the_gpu(ext):
+    """The MTP head (one attention layer over [embedding | target hidden] rows) drafting for the scheduler at the 27B
+    layer widths: drafts are produced and verified, the first token equals the plain engine's (later ones may differ at
+    near-ties of random-weight logits between the one-row and the many-row kernels; exact equality is asserted by the
+    CPU test of the same path)."""
+    from ferrite_b200.engine.scheduler import Sampling, SchedOptions, Scheduler, generate
+    from ferrite_b200.models.mtp import MtpDrafter
+    cfg = scaled(hybrid_27b(), 4)
+    cfg.tap_layers = [cfg.n_layers - 1]
+    prompt = _prompt(cfg, 70)
+    plain = Engine(cfg, None, EngineConfig(n_slots=1, max_ctx=512), device="cuda", seed=3)
+    want = generate(Scheduler(plain, SchedOptions(spec=0)), [prompt], Sampling(max_tokens=12))[0]
+    eng = Engine(cfg, None, EngineConfig(n_slots=1, max_ctx=512), device="cuda", seed=3)
+    dr = MtpDrafter(eng, n_slots=1, max_ctx=512, depth=3)
+    sched = Scheduler(eng, SchedOptions(spec=3, copy_rows=False), drafter=dr)
+    got = generate(sched, [prompt], Sampling(max_tokens=12))[0]
+    assert got[0] == want[0] and len(got) == len(want)
+    assert sched.stats["drafted"] > 0
+    eng.check(); dr.eng.check()

@@ -243,3 +243,41 @@ def test_mixed_steps_decode_rows_ride_with_prompt_chunks():
     assert outs == want
     # 200 prompt tokens in 64-row chunks = 4 chunk steps; without mixing the decode steps of request 1 would add to them
     assert sched.stats["steps"] - steps_before <= 4 + 12
+
+
+def _mtp_setup(n_slots=1):
+    from ferrite_b200.models.mtp import MtpDrafter
+    cfg, w, eng = _engine(n_slots=n_slots)
+    last = cfg.n_layers - 1
+    for c in (cfg, eng.cfg, eng.ex.cfg, eng.full_cfg):
+        c.tap_layers = [last]
+    return cfg, w, eng, MtpDrafter(eng, n_slots=n_slots, max_ctx=256, depth=3)
+
+
+def test_mtp_chain_drafter_keeps_greedy_output():
+    cfg, w, eng, dr = _mtp_setup()
+    sched = Scheduler(eng, SchedOptions(spec=3, copy_rows=False), drafter=dr)
+    prompt = _prompt(cfg, 25, 31)
+    out = generate(sched, [prompt], Sampling(max_tokens=14))[0]
+    assert out == _plain(cfg, w, prompt, 14)
+    assert sched.stats["drafted"] > 0
+    assert dr.eng.ex.w["embed"].data_ptr() == eng.ex.w["embed"].data_ptr()       # the head shares the target's table
+
+
+def test_mtp_rows_do_not_depend_on_how_the_prompt_was_cut():
+    """The head's cache after absorbing a prompt in one piece or in two gives the same chain of drafts, and a draft
+    run leaves no trace (drafting twice gives the same tokens)."""
+    from ferrite_b200.engine.executor import Segment
+    cfg, w, eng, dr = _mtp_setup()
+    p = _prompt(cfg, 30, 5)
+    eng.forward([Segment(0, 0, p, "none")])
+    dr.absorb(0, p, 0, eng.taps)
+    a = dr.draft(0, 9, 30, eng.taps, 3)
+    assert len(a) == 3 and dr.draft(0, 9, 30, eng.taps, 3) == a
+    eng.reset_slot(0); dr.reset(0)
+    eng.forward([Segment(0, 0, p[:17], "none")])
+    dr.absorb(0, p[:17], 0, eng.taps)
+    eng.forward([Segment(0, 17, p[17:], "none")])
+    dr.absorb(0, p[17:], 17, eng.taps)
+    assert dr.draft(0, 9, 30, eng.taps, 3) == a
+    assert dr.draft(0, 9, 29, eng.taps, 3) == []          # no hidden kept for that position: nothing to draft from
