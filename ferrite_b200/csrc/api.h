@@ -47,6 +47,11 @@ int fb_attn_prep(void* q_out, void* k_cache, void* v_cache, const void* proj, lo
                  const void* k_norm, const float* inv_freq, const int* row_slot, const int* row_pos,
                  const int* block_table, int max_blocks, int kv_block, int rows, int nq, int nkv, int hd, int rot,
                  int gated, float eps, int* status, cudaStream_t s);
+// verify-tree rows: rotary position `row_pos` (depth) and cache row `row_cpos` differ; kv_scale != null: e4m3 cache
+int fb_attn_prep_tree(void* q_out, void* k_cache, void* v_cache, float* kv_scale, const void* proj, long proj_stride,
+                      const void* q_norm, const void* k_norm, const float* inv_freq, const int* row_slot,
+                      const int* row_pos, const int* row_cpos, const int* block_table, int max_blocks, int kv_block,
+                      int rows, int nq, int nkv, int hd, int rot, int gated, float eps, int* status, cudaStream_t s);
 int fb_attn_decode(void* out, float* o_part, float* ml_part, const void* q, const void* k_cache, const void* v_cache,
                    const void* proj, long proj_stride, const int* row_slot, const int* row_kvlen, const int* row_base,
                    const unsigned long long* row_mask, const int* block_table, int max_blocks, int kv_block, int rows,
@@ -73,6 +78,15 @@ int fb_attn_prefill(void* out, const void* q, const void* k_cache, const void* v
 int fb_gdn_conv(void* out, const void* proj, long proj_stride, const void* conv_w, const void* conv_state,
                 const int* seg_slot, const int* seg_row0, const int* seg_nrows, int nseg, int max_rows, int conv_dim,
                 cudaStream_t s);
+// verify trees: windows / states follow `row_parent` (parent row inside the segment, -1 = root); see gdn.cu
+long fb_gdn_tree_scratch_bytes(int rows, int nv, int dk, int dv);
+int fb_gdn_conv_tree(void* out, const void* proj, long proj_stride, const void* conv_w, const void* conv_state,
+                     const int* seg_slot, const int* seg_row0, const int* seg_nrows, const int* row_parent, int nseg,
+                     int conv_dim, cudaStream_t s);
+int fb_gdn_rec_tree(float* y, float* rec_state, const void* qkv, const void* proj, long proj_stride, const float* A_log,
+                    const float* dt_bias, const int* seg_slot, const int* seg_row0, const int* seg_nrows,
+                    const int* row_parent, const int* row_flags, float* node_state, int nseg, int nk, int nv, int dk,
+                    int dv, float eps, cudaStream_t s);
 int fb_gdn_rec(float* y, float* rec_state, void* conv_state, const void* qkv, const void* proj, long proj_stride,
                const float* A_log, const float* dt_bias, const int* seg_slot, const int* seg_row0,
                const int* seg_nrows, int nseg, int nk, int nv, int dk, int dv, float eps, int commit, cudaStream_t s);

@@ -23,6 +23,7 @@ __global__ void attn_prep_kernel(__nv_bfloat16* __restrict__ q_out, void* __rest
                                  long proj_stride, const __nv_bfloat16* __restrict__ q_norm,
                                  const __nv_bfloat16* __restrict__ k_norm, const float* __restrict__ inv_freq,
                                  const int* __restrict__ row_slot, const int* __restrict__ row_pos,
+                                 const int* __restrict__ row_cpos,
                                  const int* __restrict__ block_table, int max_blocks, int kv_block, int nq, int nkv,
                                  int rot, int gated, float eps, int* status) {
   pdl_launch_dependents();
@@ -68,9 +69,11 @@ __global__ void attn_prep_kernel(__nv_bfloat16* __restrict__ q_out, void* __rest
   } else {
     const int kvh = warp - nq;
     const int slot = row_slot[row];
-    const int blk = block_table[(size_t)slot * max_blocks + pos / kv_block];
+    // rows of a verify tree rotate by their depth but are stored by their row index: siblings share a position
+    const int cpos = row_cpos ? row_cpos[row] : pos;
+    const int blk = block_table[(size_t)slot * max_blocks + cpos / kv_block];
     if (blk < 0) { set_status(status, ST_BOUNDS); return; }
-    const size_t tok = ((size_t)blk * kv_block + (pos % kv_block)) * nkv + kvh;
+    const size_t tok = ((size_t)blk * kv_block + (cpos % kv_block)) * nkv + kvh;
     const size_t off = tok * HD;
     const __nv_bfloat16* vsrc = proj + (size_t)row * proj_stride + (size_t)nq * qw + (size_t)(nkv + kvh) * HD;
     if (KV8) {
@@ -362,8 +365,8 @@ using namespace fb;
 
 static int attn_prep_impl(void* q_out, void* k_cache, void* v_cache, float* kv_scale, const void* proj, long proj_stride,
                           const void* q_norm, const void* k_norm, const float* inv_freq, const int* row_slot,
-                          const int* row_pos, const int* block_table, int max_blocks, int kv_block, int rows, int nq,
-                          int nkv, int hd, int rot, int gated, float eps, int* status, cudaStream_t s) {
+                          const int* row_pos, const int* row_cpos, const int* block_table, int max_blocks, int kv_block,
+                          int rows, int nq, int nkv, int hd, int rot, int gated, float eps, int* status, cudaStream_t s) {
   if (rows <= 0) return 0;
   int threads = 32 * (nq + nkv);
   if (threads > 1024) return -1;
@@ -372,7 +375,7 @@ static int attn_prep_impl(void* q_out, void* k_cache, void* v_cache, float* kv_s
 #define FB_PREP(HDV, K8)                                                                                          \
   launch_pdl(attn_prep_kernel<HDV, K8>, dim3(rows), dim3(threads), (size_t)(0), s, (__nv_bfloat16*)q_out, k_cache, v_cache, \
       kv_scale, (const __nv_bfloat16*)proj, proj_stride, (const __nv_bfloat16*)q_norm,                            \
-      (const __nv_bfloat16*)k_norm, inv_freq, row_slot, row_pos, block_table, max_blocks, kv_block, nq, nkv, rot, \
+      (const __nv_bfloat16*)k_norm, inv_freq, row_slot, row_pos, row_cpos, block_table, max_blocks, kv_block, nq, nkv, rot, \
       gated, eps, status)
   if (kv_scale) {
     if (hd == 256) FB_PREP(256, true); else if (hd == 128) FB_PREP(128, true); else if (hd == 64) FB_PREP(64, true); else return -2;
@@ -416,7 +419,18 @@ extern "C" int fb_attn_prep(void* q_out, void* k_cache, void* v_cache, const voi
                             const int* row_pos, const int* block_table, int max_blocks, int kv_block, int rows, int nq,
                             int nkv, int hd, int rot, int gated, float eps, int* status, cudaStream_t s) {
   return attn_prep_impl(q_out, k_cache, v_cache, nullptr, proj, proj_stride, q_norm, k_norm, inv_freq, row_slot, row_pos,
-                        block_table, max_blocks, kv_block, rows, nq, nkv, hd, rot, gated, eps, status, s);
+                        nullptr, block_table, max_blocks, kv_block, rows, nq, nkv, hd, rot, gated, eps, status, s);
+}
+
+// Verify-tree form: `row_pos` is the rotary position (depth in the tree), `row_cpos` the cache row the K/V go to.
+// `kv_scale` non-null selects the e4m3 cache.
+extern "C" int fb_attn_prep_tree(void* q_out, void* k_cache, void* v_cache, float* kv_scale, const void* proj,
+                                 long proj_stride, const void* q_norm, const void* k_norm, const float* inv_freq,
+                                 const int* row_slot, const int* row_pos, const int* row_cpos, const int* block_table,
+                                 int max_blocks, int kv_block, int rows, int nq, int nkv, int hd, int rot, int gated,
+                                 float eps, int* status, cudaStream_t s) {
+  return attn_prep_impl(q_out, k_cache, v_cache, kv_scale, proj, proj_stride, q_norm, k_norm, inv_freq, row_slot, row_pos,
+                        row_cpos, block_table, max_blocks, kv_block, rows, nq, nkv, hd, rot, gated, eps, status, s);
 }
 
 extern "C" int fb_attn_decode(void* out, float* o_part, float* ml_part, const void* q, const void* k_cache,
@@ -436,7 +450,7 @@ extern "C" int fb_attn_prep_kv8(void* q_out, void* k_cache8, void* v_cache8, flo
                                 cudaStream_t s) {
   if (!kv_scale) return -4;
   return attn_prep_impl(q_out, k_cache8, v_cache8, kv_scale, proj, proj_stride, q_norm, k_norm, inv_freq, row_slot, row_pos,
-                        block_table, max_blocks, kv_block, rows, nq, nkv, hd, rot, gated, eps, status, s);
+                        nullptr, block_table, max_blocks, kv_block, rows, nq, nkv, hd, rot, gated, eps, status, s);
 }
 
 extern "C" int fb_attn_decode_kv8(void* out, float* o_part, float* ml_part, const void* q, const void* k_cache8,

@@ -113,7 +113,17 @@ void gemm_fp8(Tensor Y, Tensor Xq, Tensor Wq, c10::optional<Tensor> scale_m, c10
 void attn_prep(Tensor q_out, Tensor k_cache, Tensor v_cache, Tensor proj, Tensor q_norm, Tensor k_norm,
                Tensor inv_freq, Tensor row_slot, Tensor row_pos, Tensor block_table, int64_t kv_block, int64_t nq,
                int64_t nkv, int64_t hd, int64_t rot, bool gated, double eps, c10::optional<Tensor> status,
-               c10::optional<Tensor> kv_scale) {
+               c10::optional<Tensor> kv_scale, c10::optional<Tensor> row_cpos) {
+  if (row_cpos.has_value() && row_cpos->defined()) {
+    const bool k8 = kv_scale.has_value() && kv_scale->defined();
+    check(fb_attn_prep_tree(q_out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+                            k8 ? kv_scale->data_ptr<float>() : nullptr, proj.data_ptr(), (long)proj.stride(0),
+                            q_norm.data_ptr(), k_norm.data_ptr(), inv_freq.data_ptr<float>(), row_slot.data_ptr<int>(),
+                            row_pos.data_ptr<int>(), row_cpos->data_ptr<int>(), block_table.data_ptr<int>(),
+                            (int)block_table.size(1), (int)kv_block, (int)row_slot.numel(), (int)nq, (int)nkv, (int)hd,
+                            (int)rot, gated ? 1 : 0, (float)eps, (int*)mptr(status), cur_stream()), "attn_prep_tree");
+    return;
+  }
   if (kv_scale.has_value() && kv_scale->defined()) {
     check(fb_attn_prep_kv8(q_out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), kv_scale->data_ptr<float>(),
                            proj.data_ptr(), (long)proj.stride(0), q_norm.data_ptr(), k_norm.data_ptr(),
@@ -189,6 +199,26 @@ void gdn_rec(Tensor y, Tensor rec_state, Tensor conv_state, Tensor qkv, Tensor p
         "gdn_rec");
 }
 
+void gdn_conv_tree(Tensor out, Tensor proj, Tensor conv_w, Tensor conv_state, Tensor seg_slot, Tensor seg_row0,
+                   Tensor seg_nrows, Tensor row_parent) {
+  check(fb_gdn_conv_tree(out.data_ptr(), proj.data_ptr(), (long)proj.stride(0), conv_w.data_ptr(), conv_state.data_ptr(),
+                         seg_slot.data_ptr<int>(), seg_row0.data_ptr<int>(), seg_nrows.data_ptr<int>(),
+                         row_parent.data_ptr<int>(), (int)seg_slot.numel(), (int)out.size(1), cur_stream()),
+        "gdn_conv_tree");
+}
+
+void gdn_rec_tree(Tensor y, Tensor rec_state, Tensor qkv, Tensor proj, Tensor A_log, Tensor dt_bias, Tensor seg_slot,
+                  Tensor seg_row0, Tensor seg_nrows, Tensor row_parent, Tensor row_flags, Tensor node_state, int64_t nk,
+                  int64_t nv, int64_t dk, int64_t dv, double eps) {
+  TORCH_CHECK(node_state.numel() * (int64_t)node_state.element_size() >=
+                  fb_gdn_tree_scratch_bytes((int)qkv.size(0), (int)nv, (int)dk, (int)dv), "gdn_rec_tree: scratch too small");
+  check(fb_gdn_rec_tree(y.data_ptr<float>(), rec_state.data_ptr<float>(), qkv.data_ptr(), proj.data_ptr(),
+                        (long)proj.stride(0), A_log.data_ptr<float>(), dt_bias.data_ptr<float>(), seg_slot.data_ptr<int>(),
+                        seg_row0.data_ptr<int>(), seg_nrows.data_ptr<int>(), row_parent.data_ptr<int>(),
+                        row_flags.data_ptr<int>(), (float*)node_state.data_ptr(), (int)seg_slot.numel(), (int)nk, (int)nv,
+                        (int)dk, (int)dv, (float)eps, cur_stream()), "gdn_rec_tree");
+}
+
 void gdn_step(Tensor out, Tensor rec_state, Tensor conv_state, Tensor proj, Tensor conv_w, Tensor A_log, Tensor dt_bias,
               Tensor gnorm_w, Tensor seg_slot, Tensor seg_row0, Tensor seg_nrows, int64_t nk, int64_t nv, int64_t dk,
               int64_t dv, double eps, bool commit) {
@@ -261,6 +291,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("attn_prefill", &attn_prefill);
   m.def("gdn_conv", &gdn_conv);
   m.def("gdn_rec", &gdn_rec);
+  m.def("gdn_conv_tree", &gdn_conv_tree);
+  m.def("gdn_rec_tree", &gdn_rec_tree);
   m.def("kv_dequant", &kv_dequant);
   m.def("gemv_mma", &gemv_mma);
   m.def("gdn_step", &gdn_step);

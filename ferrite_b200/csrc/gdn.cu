@@ -48,15 +48,57 @@ __global__ void gdn_conv_kernel(__nv_bfloat16* __restrict__ out, const __nv_bflo
   }
 }
 
+// Verify-tree form of the conv: the window of a row is its three nearest ancestors (then the slot's conv tail), found
+// by walking `row_parent` (parent row inside the segment, -1 for the root row). Counterpart of the tree variant of
+// `fe_gdn_conv` (`kernels/k-core/src/gdn.rs:30`). grid = (ceil(conv_dim/256), segments); never writes state.
+__global__ void gdn_conv_tree_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ proj,
+                                     long proj_stride, const __nv_bfloat16* __restrict__ conv_w,
+                                     const __nv_bfloat16* __restrict__ conv_state, const int* __restrict__ seg_slot,
+                                     const int* __restrict__ seg_row0, const int* __restrict__ seg_nrows,
+                                     const int* __restrict__ row_parent, int conv_dim) {
+  pdl_launch_dependents();
+  pdl_wait();
+  constexpr int CK = 4;
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int seg = blockIdx.y;
+  const int n = seg_nrows[seg];
+  if (c >= conv_dim || n <= 0) return;
+  const int row0 = seg_row0[seg];
+  const int slot = seg_slot[seg];
+  float w[CK];
+#pragma unroll
+  for (int j = 0; j < CK; ++j) w[j] = bf2f(conv_w[(size_t)c * CK + j]);
+  const __nv_bfloat16* st = conv_state + (size_t)slot * (CK - 1) * conv_dim + c;
+  for (int r = 0; r < n; ++r) {
+    float acc = w[CK - 1] * bf2f(proj[(size_t)(row0 + r) * proj_stride + c]);
+    int i = r;
+#pragma unroll
+    for (int j = CK - 2; j >= 0; --j) {
+      // one step back in time: the parent row, or (past the root) one entry further into the saved tail
+      i = i >= 0 ? row_parent[row0 + i] : i - 1;
+      if (i >= n) i = -1;                                    // malformed parent: treat as the root's predecessor
+      const float x = i >= 0 ? bf2f(proj[(size_t)(row0 + i) * proj_stride + c]) : bf2f(st[(size_t)(CK - 1 + i) * conv_dim]);
+      acc = fmaf(w[j], x, acc);
+    }
+    out[(size_t)(row0 + r) * conv_dim + c] = f2bf(siluf_(acc));
+  }
+}
+
 // Recurrence over the rows of one segment for one value head. blockDim = DV * 8; thread (col = tid % DV,
 // part = tid / DV) keeps DK/8 rows of state column `col` in registers across the whole segment.
-template <int DK, int DV>
+// TREE: the rows of a segment form a verify tree. A row starts from the state its parent left (`row_parent`, -1 = the
+// slot's committed state); states are parked in `node_state` [row][head][DK][DV] only where `row_flags` asks for it
+// (bit 0: this row's parent is not the previous row, reload; bit 1: a later row branches from this one, store). A
+// thread reloads exactly the elements it stored, so no barrier is needed. Tree launches never commit. Counterpart of
+// the tree variant of `fe_gdn_rec` (`kernels/k-core/src/gdn.rs:117`).
+template <int DK, int DV, bool TREE>
 __global__ void __launch_bounds__(DV * 8)
 gdn_rec_kernel(float* __restrict__ y, float* __restrict__ rec_state, __nv_bfloat16* __restrict__ conv_state,
                const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ proj, long proj_stride,
                const float* __restrict__ A_log, const float* __restrict__ dt_bias, const int* __restrict__ seg_slot,
                const int* __restrict__ seg_row0, const int* __restrict__ seg_nrows, int nk, int nv, float eps,
-               int commit) {
+               int commit, const int* __restrict__ row_parent, const int* __restrict__ row_flags,
+               float* __restrict__ node_state) {
   pdl_launch_dependents();
   pdl_wait();
   constexpr int PARTS = 8, RP = DK / PARTS, CK = 4;
@@ -81,6 +123,16 @@ gdn_rec_kernel(float* __restrict__ y, float* __restrict__ rec_state, __nv_bfloat
   const float qscale = rsqrtf((float)DK);
 
   for (int r = 0; r < n; ++r) {
+    int flags = 0;
+    if (TREE) {
+      flags = row_flags[row0 + r];
+      if (flags & 1) {
+        const int par = row_parent[row0 + r];
+        const float* src = (par < 0 || par >= r) ? Sg : node_state + (((size_t)(row0 + par) * nv + h) * DK) * DV;
+#pragma unroll
+        for (int i = 0; i < RP; ++i) S[i] = src[(size_t)(part * RP + i) * DV + col];
+      }
+    }
     const __nv_bfloat16* xr = qkv + (size_t)(row0 + r) * conv_dim;
     if (tid < DK) {
       float qv = bf2f(xr[q_off + tid]), kv = bf2f(xr[k_off + tid]);
@@ -121,8 +173,13 @@ gdn_rec_kernel(float* __restrict__ y, float* __restrict__ rec_state, __nv_bfloat
       for (int i = 0; i < PARTS; ++i) yy += red2[i][col];
       y[((size_t)(row0 + r) * nv + h) * DV + col] = yy * rq;
     }
+    if (TREE && (flags & 2)) {
+      float* dst = node_state + (((size_t)(row0 + r) * nv + h) * DK) * DV;
+#pragma unroll
+      for (int i = 0; i < RP; ++i) dst[(size_t)(part * RP + i) * DV + col] = S[i];
+    }
   }
-  if (commit) {
+  if (commit && !TREE) {
 #pragma unroll
     for (int i = 0; i < RP; ++i) Sg[(size_t)(part * RP + i) * DV + col] = S[i];
     // conv tail: the last CK-1 raw inputs of the channels this head owns (q/k channels: first head of the group)
@@ -296,11 +353,50 @@ extern "C" int fb_gdn_rec(float* y, float* rec_state, void* conv_state, const vo
   if (nv % nk) return -1;
   dim3 grid(nv, nseg);
   if (dk == 128 && dv == 128)
-    launch_pdl(gdn_rec_kernel<128, 128>, dim3(grid), dim3(1024), (size_t)(0), s, y, rec_state, (__nv_bfloat16*)conv_state, (const __nv_bfloat16*)qkv,
-        (const __nv_bfloat16*)proj, proj_stride, A_log, dt_bias, seg_slot, seg_row0, seg_nrows, nk, nv, eps, commit);
+    launch_pdl(gdn_rec_kernel<128, 128, false>, dim3(grid), dim3(1024), (size_t)(0), s, y, rec_state, (__nv_bfloat16*)conv_state, (const __nv_bfloat16*)qkv,
+        (const __nv_bfloat16*)proj, proj_stride, A_log, dt_bias, seg_slot, seg_row0, seg_nrows, nk, nv, eps, commit,
+        (const int*)nullptr, (const int*)nullptr, (float*)nullptr);
   else if (dk == 64 && dv == 64)
-    launch_pdl(gdn_rec_kernel<64, 64>, dim3(grid), dim3(512), (size_t)(0), s, y, rec_state, (__nv_bfloat16*)conv_state, (const __nv_bfloat16*)qkv,
-        (const __nv_bfloat16*)proj, proj_stride, A_log, dt_bias, seg_slot, seg_row0, seg_nrows, nk, nv, eps, commit);
+    launch_pdl(gdn_rec_kernel<64, 64, false>, dim3(grid), dim3(512), (size_t)(0), s, y, rec_state, (__nv_bfloat16*)conv_state, (const __nv_bfloat16*)qkv,
+        (const __nv_bfloat16*)proj, proj_stride, A_log, dt_bias, seg_slot, seg_row0, seg_nrows, nk, nv, eps, commit,
+        (const int*)nullptr, (const int*)nullptr, (float*)nullptr);
+  else return -2;
+  return (int)cudaGetLastError();
+}
+
+// Verify trees: conv over ancestor windows, then the recurrence from each row's parent state. `node_state` holds
+// rows x nv x dk x dv floats (rows = all rows of the step); nothing is committed.
+extern "C" long fb_gdn_tree_scratch_bytes(int rows, int nv, int dk, int dv) {
+  return (long)rows * nv * dk * dv * (long)sizeof(float);
+}
+
+extern "C" int fb_gdn_conv_tree(void* out, const void* proj, long proj_stride, const void* conv_w, const void* conv_state,
+                                const int* seg_slot, const int* seg_row0, const int* seg_nrows, const int* row_parent,
+                                int nseg, int conv_dim, cudaStream_t s) {
+  if (nseg <= 0) return 0;
+  dim3 grid((conv_dim + 255) / 256, nseg);
+  launch_pdl(gdn_conv_tree_kernel, dim3(grid), dim3(256), (size_t)(0), s, (__nv_bfloat16*)out, (const __nv_bfloat16*)proj,
+             proj_stride, (const __nv_bfloat16*)conv_w, (const __nv_bfloat16*)conv_state, seg_slot, seg_row0, seg_nrows,
+             row_parent, conv_dim);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int fb_gdn_rec_tree(float* y, float* rec_state, const void* qkv, const void* proj, long proj_stride,
+                               const float* A_log, const float* dt_bias, const int* seg_slot, const int* seg_row0,
+                               const int* seg_nrows, const int* row_parent, const int* row_flags, float* node_state,
+                               int nseg, int nk, int nv, int dk, int dv, float eps, cudaStream_t s) {
+  if (nseg <= 0) return 0;
+  if (nv % nk) return -1;
+  if (!row_parent || !row_flags || !node_state) return -3;
+  dim3 grid(nv, nseg);
+  if (dk == 128 && dv == 128)
+    launch_pdl(gdn_rec_kernel<128, 128, true>, dim3(grid), dim3(1024), (size_t)(0), s, y, rec_state, (__nv_bfloat16*)nullptr,
+               (const __nv_bfloat16*)qkv, (const __nv_bfloat16*)proj, proj_stride, A_log, dt_bias, seg_slot, seg_row0, seg_nrows,
+               nk, nv, eps, 0, row_parent, row_flags, node_state);
+  else if (dk == 64 && dv == 64)
+    launch_pdl(gdn_rec_kernel<64, 64, true>, dim3(grid), dim3(512), (size_t)(0), s, y, rec_state, (__nv_bfloat16*)nullptr,
+               (const __nv_bfloat16*)qkv, (const __nv_bfloat16*)proj, proj_stride, A_log, dt_bias, seg_slot, seg_row0, seg_nrows,
+               nk, nv, eps, 0, row_parent, row_flags, node_state);
   else return -2;
   return (int)cudaGetLastError();
 }

@@ -99,6 +99,13 @@ class Engine:
         for s, k in zip(self._last_segments, keep):
             self.slot_len[s.slot] = s.pos0 + int(k)
 
+    def commit_tree(self, paths) -> None:
+        """Accept one root-to-node path per segment of the last verify step with trees (`Segment.parents`): `paths[i]`
+        lists row indices inside segment i starting with 0. The slot then holds pos0 + len(path) tokens."""
+        self.ex.commit_tree(paths)
+        for s, path in zip(self._last_segments, paths):
+            self.slot_len[s.slot] = s.pos0 + len(path)
+
     @property
     def taps(self):
         """Hidden rows of the tapped layers from the last forward (inputs of the block drafter)."""

@@ -28,6 +28,9 @@ class Segment:
     pos0: int
     tokens: List[int]
     want_logits: str = "last"       # "last" | "all" | "none"
+    # verify tree: parent row of every row inside the segment (-1 for row 0, parents before children). A row sits at
+    # position pos0 + depth, sees the committed context plus its own ancestors, and is stored at cache row pos0 + index.
+    parents: Optional[List[int]] = None
 
 
 @dataclass
@@ -38,6 +41,32 @@ class StepBatch:
     @property
     def n_rows(self) -> int:
         return sum(len(s.tokens) for s in self.segments)
+
+    @property
+    def tree(self) -> bool:
+        return any(s.parents is not None for s in self.segments)
+
+
+TREE_MAX_ROWS = 32       # rows of one verify tree (reference TREE_ROWS 32); the ancestor mask has 64 bits
+
+
+def tree_layout(parents: Sequence[int]):
+    """Depth, ancestor-or-self bit mask, and state load/store flags of every row of a verify tree (reference
+    `ancestors` / `tree_steps`, `crates/fe-model/src/model.rs:210-256`). Flag bit 0: the row's parent is not the row
+    before it (its recurrent state must be reloaded); bit 1: a later row that does not directly follow branches from
+    this row (its state must be parked)."""
+    n = len(parents)
+    assert 0 < n <= TREE_MAX_ROWS, f"a verify tree holds 1..{TREE_MAX_ROWS} rows"
+    depth, mask, flags = [0] * n, [0] * n, [0] * n
+    for r, p in enumerate(parents):
+        assert (p == -1 and r == 0) or (0 <= p < r), "parents come before their children; row 0 is the root"
+        depth[r] = 0 if p < 0 else depth[p] + 1
+        mask[r] = (1 << r) | (0 if p < 0 else mask[p])
+        if p != r - 1:
+            flags[r] |= 1
+            if p >= 0:
+                flags[p] |= 2
+    return depth, mask, flags
 
 
 class BlockPool:
@@ -130,6 +159,9 @@ class Executor:
         R = ecfg.max_step_rows
         S = max(ecfg.n_slots, 1) * 2
         self.meta_i32 = torch.zeros(5 * R + 4 * S, dtype=torch.int32, device=dev)
+        # verify-tree metadata, fixed offsets: [ancestor masks (int64 x R) | cache row R | base R | parent R | flags R]
+        self.tree_i32 = torch.zeros(6 * R, dtype=torch.int32, device=dev)
+        self._tring = [torch.zeros(6 * R, dtype=torch.int32, pin_memory=(dev.type == "cuda")) for _ in range(4)]
         # pinned staging ring: a buffer is rewritten only after the copy that last read it has completed
         self._ring = [torch.zeros(5 * R + 4 * S, dtype=torch.int32, pin_memory=(dev.type == "cuda")) for _ in range(4)]
         self._ring_ev = [None] * 4
@@ -262,6 +294,12 @@ class Executor:
         sslot, srow0, snrows, spos0 = (h[o + i * S:o + (i + 1) * S] for i in range(4))
         r = 0
         logit_rows: List[int] = []
+        tree = batch.tree
+        if tree:
+            R = self._R
+            th = self._tring[ri]
+            tmask = th[:2 * R].view(torch.int64)
+            tcpos, tbase, tpar, tflag = (th[(2 + i) * R:(3 + i) * R] for i in range(4))
         for si, sg in enumerate(batch.segments):
             n = len(sg.tokens)
             self.ensure_capacity(sg.slot, sg.pos0 + n)
@@ -269,6 +307,16 @@ class Executor:
             slot[r:r + n] = sg.slot
             pos[r:r + n] = torch.arange(sg.pos0, sg.pos0 + n, dtype=torch.int32)
             kvl[r:r + n] = torch.arange(sg.pos0 + 1, sg.pos0 + n + 1, dtype=torch.int32)
+            if tree:
+                par = list(sg.parents) if sg.parents is not None else list(range(-1, n - 1))
+                assert len(par) == n
+                depth, mask, flags = tree_layout(par)
+                pos[r:r + n] = torch.tensor([sg.pos0 + d for d in depth], dtype=torch.int32)
+                tmask[r:r + n] = torch.tensor(mask, dtype=torch.int64)
+                tcpos[r:r + n] = torch.arange(sg.pos0, sg.pos0 + n, dtype=torch.int32)
+                tbase[r:r + n] = sg.pos0
+                tpar[r:r + n] = torch.tensor(par, dtype=torch.int32)
+                tflag[r:r + n] = torch.tensor(flags, dtype=torch.int32)
             sslot[si], srow0[si], snrows[si], spos0[si] = sg.slot, r, n, sg.pos0
             if sg.want_logits == "all":
                 logit_rows.extend(range(r, r + n))
@@ -279,6 +327,8 @@ class Executor:
         lrow[:nl] = torch.tensor(logit_rows, dtype=torch.int32) if nl else lrow[:0]
         used = 5 * T + 4 * S
         self.meta_i32[:used].copy_(h[:used], non_blocking=True)
+        if tree:
+            self.tree_i32.copy_(th, non_blocking=True)
         if self.device.type == "cuda":
             ev = torch.cuda.Event()
             ev.record()
@@ -294,6 +344,11 @@ class Executor:
             tok=m[0:T], slot=m[T:2 * T], pos=m[2 * T:3 * T], kvlen=m[3 * T:4 * T], lrow=m[4 * T:4 * T + nlog],
             sslot=m[o:o + S], srow0=m[o + S:o + 2 * S], snrows=m[o + 2 * S:o + 3 * S], spos0=m[o + 3 * S:o + 4 * S],
         )
+
+    def _tree_views(self, T: int):
+        m, R = self.tree_i32, self._R
+        return dict(mask=m[:2 * R].view(torch.int64)[:T], cpos=m[2 * R:2 * R + T], base=m[3 * R:3 * R + T],
+                    parent=m[4 * R:4 * R + T], flags=m[5 * R:5 * R + T])
 
     # ---- forward -----------------------------------------------------------------------------------
     def _row_parallel(self, x_in, w, res):
@@ -347,7 +402,7 @@ class Executor:
         part = ops.moe_experts(h, ids, wts, w[p + "experts_gate_up"], w[p + "experts_down"], e_lo, e_hi, shared, sgate, None)
         return self.tp.allreduce_rows(ops, part, x)
 
-    def _layers(self, x, mv, T, nseg, max_seg_rows, nsplit, commit):
+    def _layers(self, x, mv, T, nseg, max_seg_rows, nsplit, commit, tv=None):
         c, w, ops = self.cfg, self.w, self.ops
         eps = c.eps
         self.taps = []
@@ -374,7 +429,24 @@ class Executor:
             p = f"l{i}."
             if kind == "gdn":
                 proj = col(x, w[p + "in_proj"], w[p + "input_norm"])
-                if hasattr(ops, "gdn_step") and max_seg_rows <= GDN_STEP_MAX_ROWS and c.lin_dk == c.lin_dv and c.lin_dk in (64, 128):
+                if tv is not None:
+                    # verify tree: conv windows and recurrent states follow the parent links; nothing is committed
+                    self.verify_proj[i] = proj
+                    qkv = ops.gdn_conv_tree(proj, w[p + "conv_w"], self.conv_state[i], mv["sslot"], mv["srow0"],
+                                            mv["snrows"], c.conv_dim, tv["parent"])
+                    y = ops.gdn_rec_tree(qkv, proj, self.rec_state[i], w[p + "A_log"], w[p + "dt_bias"], mv["sslot"],
+                                         mv["srow0"], mv["snrows"], tv["parent"], tv["flags"], c.lin_k_heads,
+                                         c.lin_v_heads, c.lin_dk, c.lin_dv, eps)
+                    o = ops.gated_norm(y, proj, c.conv_dim, w[p + "gnorm_w"], c.lin_v_heads, c.lin_dv, eps)
+                    x = row(o, w[p + "out_proj"], x)
+                    if c.is_moe(i):
+                        x = self._moe_ffn(x, i)
+                    else:
+                        x = row(col(x, w[p + "gate_up"], w[p + "post_norm"], swiglu=True), w[p + "down"], x)
+                    if i in c.tap_layers:
+                        self.taps.append(x)
+                    continue
+                elif hasattr(ops, "gdn_step") and max_seg_rows <= GDN_STEP_MAX_ROWS and c.lin_dk == c.lin_dv and c.lin_dk in (64, 128):
                     if not commit:
                         self.verify_proj[i] = proj
                     o = ops.gdn_step(proj, w[p + "conv_w"], self.rec_state[i], self.conv_state[i], w[p + "A_log"],
@@ -418,8 +490,14 @@ class Executor:
                 kvs = {"kv_scale": self.kv_scale[i]} if self.kv8 else {}
                 q = ops.attn_prep(proj, w[p + "q_norm"], w[p + "k_norm"], self.inv_freq, mv["slot"], mv["pos"],
                                   self.block_table, self.k_cache[i], self.v_cache[i], self.ecfg.kv_block, c.n_q,
-                                  c.n_kv, c.head_dim, c.rotary_dim, c.attn_gate, eps, **kvs)
-                if max_seg_rows > FLASH_MIN_ROWS:
+                                  c.n_kv, c.head_dim, c.rotary_dim, c.attn_gate, eps,
+                                  **({"row_cpos": tv["cpos"]} if tv is not None else {}), **kvs)
+                if tv is not None:
+                    # tree rows see the committed context plus their own ancestors (bit mask over the segment's rows)
+                    o = ops.attention(q, proj, self.k_cache[i], self.v_cache[i], mv["slot"], mv["kvlen"],
+                                      self.block_table, self.ecfg.kv_block, c.n_q, c.n_kv, c.head_dim, c.attn_gate,
+                                      row_base=tv["base"], row_mask=tv["mask"], nsplit=nsplit, **kvs)
+                elif max_seg_rows > FLASH_MIN_ROWS:
                     o = ops.attention_prefill(q, proj, self.k_cache[i], self.v_cache[i], mv["sslot"], mv["srow0"],
                                               mv["snrows"], mv["spos0"], self.block_table, self.ecfg.kv_block, c.n_q,
                                               c.n_kv, c.head_dim, c.attn_gate, max_seg_rows, row_slot=mv["slot"],
@@ -457,7 +535,7 @@ class Executor:
             return logits, (ids, finite)
         return logits, None
 
-    def _run(self, T, nseg, nlog, max_seg_rows, nsplit, commit, greedy, x_add=None):
+    def _run(self, T, nseg, nlog, max_seg_rows, nsplit, commit, greedy, x_add=None, tree=False):
         mv = self._meta_views(T, nseg, nlog)
         self._last_meta = (mv, max_seg_rows)
         x = self.ops.embed(self.w["embed"], mv["tok"])
@@ -465,7 +543,7 @@ class Executor:
             x = x_add.to(x.dtype)                            # MTP head: the caller computed the input rows itself
         elif x_add is not None:
             x = (x.float() + x_add.float()).to(x.dtype)      # drafter: target features fused into the input rows
-        x = self._layers(x, mv, T, nseg, max_seg_rows, nsplit, commit)
+        x = self._layers(x, mv, T, nseg, max_seg_rows, nsplit, commit, self._tree_views(T) if tree else None)
         self.last_hidden = x                                 # rows before the final norm (source of the MTP head)
         return self._head(x, mv, nlog, greedy)
 
@@ -498,6 +576,57 @@ class Executor:
                         mv["sslot"], mv["srow0"], mv["snrows"], c.lin_k_heads, c.lin_v_heads, c.lin_dk, c.lin_dv,
                         c.eps, commit=True, chunked=False)
 
+    def commit_tree(self, paths: Sequence[Sequence[int]]) -> None:
+        """After a verify step with trees (commit=False): keep, for every segment, the rows of `paths[i]` (row indices
+        inside the segment from the root down, `paths[i][0] == 0`; empty keeps nothing). The Gated DeltaNet state is
+        advanced by replaying the saved projections of the path rows in order, and the path's K/V rows are moved from
+        the cache rows they were stored at (pos0 + row index) to consecutive positions (pos0 + depth). Reference
+        `commit_tree` (`crates/fe-model/src/model.rs:2516-2606`: keep the accepted path, replay GDN, compact KV)."""
+        batch = self._last_batch
+        c, w, ops = self.cfg, self.w, self.ops
+        dev = self.device
+        rows, row0s, ns, slots = [], [], [], []
+        src, dst = [], []
+        kvb = self.ecfg.kv_block
+        r0 = 0
+        for sg, path in zip(batch.segments, paths):
+            path = [int(r) for r in path]
+            assert not path or path[0] == 0
+            row0s.append(len(rows)); ns.append(len(path)); slots.append(sg.slot)
+            rows.extend(r0 + r for r in path)
+            blocks = self.slot_blocks[sg.slot]
+            for j, r in enumerate(path):
+                if r != j:
+                    a, b = sg.pos0 + r, sg.pos0 + j
+                    src.append(blocks[a // kvb] * kvb + a % kvb)
+                    dst.append(blocks[b // kvb] * kvb + b % kvb)
+            r0 += len(sg.tokens)
+        if rows and any(k == "gdn" for k in self.kinds):
+            idx = torch.tensor(rows, dtype=torch.long, device=dev)
+            sslot = torch.tensor(slots, dtype=torch.int32, device=dev)
+            srow0 = torch.tensor(row0s, dtype=torch.int32, device=dev)
+            snrows = torch.tensor(ns, dtype=torch.int32, device=dev)
+            mr = max(max(ns), 1)
+            for i, kind in enumerate(self.kinds):
+                if kind != "gdn":
+                    continue
+                p = f"l{i}."
+                proj = self.verify_proj[i].index_select(0, idx).contiguous()
+                qkv = ops.gdn_conv(proj, w[p + "conv_w"], self.conv_state[i], sslot, srow0, snrows, c.conv_dim,
+                                   **({"max_rows": mr} if ops.name == "cuda" else {}))
+                ops.gdn_rec(qkv, proj, self.rec_state[i], self.conv_state[i], w[p + "A_log"], w[p + "dt_bias"], sslot,
+                            srow0, snrows, c.lin_k_heads, c.lin_v_heads, c.lin_dk, c.lin_dv, c.eps, commit=True,
+                            chunked=False)
+        if src:
+            s_i = torch.tensor(src, dtype=torch.long, device=dev)
+            d_i = torch.tensor(dst, dtype=torch.long, device=dev)
+            for i in self.k_cache:
+                for cache in (self.k_cache[i], self.v_cache[i]) + ((self.kv_scale[i],) if i in self.kv_scale else ()):
+                    if cache.numel() == 0:
+                        continue
+                    flat = cache.view(cache.shape[0] * cache.shape[1], *cache.shape[2:])
+                    flat[d_i] = flat[s_i]            # the gather is materialised first, so overlapping moves are safe
+
     def forward(self, batch: StepBatch, greedy: bool = True, x_add=None):
         """Run one step. Returns (logits [n_logit_rows, vocab] fp32, (ids, finite) when greedy, logit_rows)."""
         T = batch.n_rows
@@ -508,24 +637,30 @@ class Executor:
         nsplit = self.attn_splits(max_kvlen) if max_seg_rows <= FLASH_MIN_ROWS else 1
         use_graph = (self.ecfg.use_graphs and self.device.type == "cuda" and T <= self.ecfg.decode_rows_max
                      and self.profile is None and x_add is None)
+        tree = batch.tree
+        if tree:
+            assert not batch.commit and max_seg_rows <= TREE_MAX_ROWS and "mla" not in self.kinds, \
+                "verify trees: commit=False, at most TREE_MAX_ROWS rows per segment, attention / GDN layers"
+            assert self.tp is None or self.tp.world == 1 or not self.tp.sp_ready(T)
         logit_rows = self._upload(batch)
         nlog = len(logit_rows)
+        self._last_batch = batch
         # the e4m3 cache decode before prompt attention sizes its grid by the longest visible context, except inside
         # graphs, whose launches must not depend on the step
         self._step_max_kvlen = None if use_graph else max_kvlen
         if not use_graph:
-            logits, picks = self._run(T, nseg, nlog, max_seg_rows, nsplit, batch.commit, greedy, x_add)
+            logits, picks = self._run(T, nseg, nlog, max_seg_rows, nsplit, batch.commit, greedy, x_add, tree)
             return logits, picks, logit_rows
-        key = (T, nseg, nlog, max_seg_rows, nsplit, batch.commit, greedy)
+        key = (T, nseg, nlog, max_seg_rows, nsplit, batch.commit, greedy, tree)
         hit = self.graphs.get(key)
         if hit is None:
             # warm up eagerly once (lazy module / attribute setup), then capture
-            self._run(T, nseg, nlog, max_seg_rows, nsplit, False, greedy)
+            self._run(T, nseg, nlog, max_seg_rows, nsplit, False, greedy, None, tree)
             torch.cuda.synchronize(self.device)
             g = torch.cuda.CUDAGraph()
             l0 = self.ops.launches
             with torch.cuda.graph(g):
-                out = self._run(T, nseg, nlog, max_seg_rows, nsplit, batch.commit, greedy)
+                out = self._run(T, nseg, nlog, max_seg_rows, nsplit, batch.commit, greedy, None, tree)
             n_kernels = self.ops.launches - l0
             self.ops.launches = l0
             hit = (g, out, n_kernels, self.taps, self.last_hidden)

@@ -37,6 +37,7 @@ class CudaOps:
         self.moe_pair_rows = MOE_PAIR_ROWS
         self.mma_gemv_rows = (2, 32)        # row counts routed to the mma.sync weight-streaming kernel
         self._gdn_scratch = None
+        self._tree_scratch = None
         self._kv_scratch = None
         self.fp4_act = False                # NVFP4 weights: quantise activations too and use the tcgen05 GEMM
         self._sf_pool = {}
@@ -252,13 +253,13 @@ class CudaOps:
 
     # ---- attention ---------------------------------------------------------------------------------
     def attn_prep(self, proj, q_norm, k_norm, inv_freq, row_slot, row_pos, block_table, k_cache, v_cache, kv_block,
-                  nq, nkv, hd, rot, gated, eps, kv_scale=None):
+                  nq, nkv, hd, rot, gated, eps, kv_scale=None, row_cpos=None):
         """q/k RMSNorm + partial RoPE, K/V rows into the paged cache (bf16, or e4m3 codes + per-row scales when
-        `kv_scale` is given)."""
+        `kv_scale` is given). `row_cpos`: cache row of each row when it differs from its rotary position (trees)."""
         q = torch.empty(proj.shape[0], nq, hd, dtype=self.dtype, device=self.device)
         self.launches += 1
         self.C.attn_prep(q, k_cache, v_cache, proj, q_norm, k_norm, inv_freq, row_slot, row_pos, block_table,
-                         kv_block, nq, nkv, hd, rot, gated, eps, self.status_word, kv_scale)
+                         kv_block, nq, nkv, hd, rot, gated, eps, self.status_word, kv_scale, row_cpos)
         return q
 
     def attention(self, q, proj, k_cache, v_cache, row_slot, row_kvlen, block_table, kv_block, nq, nkv, hd, gated,
@@ -305,6 +306,27 @@ class CudaOps:
         self.C.gdn_conv(out, proj, conv_w, conv_state, seg_slot, seg_row0, seg_nrows,
                         proj.shape[0] if max_rows is None else max_rows)
         return out
+
+    def gdn_conv_tree(self, proj, conv_w, conv_state, seg_slot, seg_row0, seg_nrows, conv_dim, row_parent):
+        """Conv over verify-tree rows: a row's window is its three nearest ancestors, then the slot's saved tail."""
+        out = torch.empty(proj.shape[0], conv_dim, dtype=self.dtype, device=self.device)
+        self.launches += 1
+        self.C.gdn_conv_tree(out, proj, conv_w, conv_state, seg_slot, seg_row0, seg_nrows, row_parent)
+        return out
+
+    def gdn_rec_tree(self, qkv, proj, rec_state, A_log, dt_bias, seg_slot, seg_row0, seg_nrows, row_parent, row_flags, nk,
+                     nv, dk, dv, eps):
+        """Recurrence over verify-tree rows (read-only): every row starts from the state its parent left. Branch-point
+        states are parked in a scratch of rows x heads x dk x dv floats that all layers share."""
+        T = qkv.shape[0]
+        y = torch.empty(T, nv * dv, dtype=torch.float32, device=self.device)
+        need = T * nv * dk * dv
+        if self._tree_scratch is None or self._tree_scratch.numel() < need:
+            self._tree_scratch = torch.empty(need, dtype=torch.float32, device=self.device)
+        self.launches += 1
+        self.C.gdn_rec_tree(y, rec_state, qkv, proj, A_log, dt_bias, seg_slot, seg_row0, seg_nrows, row_parent, row_flags,
+                            self._tree_scratch, nk, nv, dk, dv, eps)
+        return y
 
     def gdn_step(self, proj, conv_w, rec_state, conv_state, A_log, dt_bias, gnorm_w, seg_slot, seg_row0, seg_nrows, nk, nv,
                  dk, dv, eps, commit=True):

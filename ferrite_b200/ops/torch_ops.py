@@ -66,7 +66,7 @@ class TorchOps:
 
     # ---- attention ---------------------------------------------------------------------------------
     def attn_prep(self, proj, q_norm, k_norm, inv_freq, row_slot, row_pos, block_table, k_cache, v_cache, kv_block,
-                  nq, nkv, hd, rot, gated, eps, kv_scale=None):
+                  nq, nkv, hd, rot, gated, eps, kv_scale=None, row_cpos=None):
         """With `kv_scale` the cache rows take the values an e4m3 cache would return: one scale per (token, kv head),
         amax / 448, codes rounded to e4m3 (the oracle keeps them dequantised in its float cache)."""
         T = proj.shape[0]
@@ -89,7 +89,7 @@ class TorchOps:
             return torch.cat([a * cos - b * sin, b * cos + a * sin, x[..., rot:]], -1)
 
         q, k = rope(q), rope(k)
-        pos = row_pos.long()
+        pos = row_pos.long() if row_cpos is None else row_cpos.long()     # trees: stored by row index, rotated by depth
         blk = block_table[row_slot.long(), pos // kv_block].long()
         off = pos % kv_block
         if kv_scale is not None:
@@ -153,6 +153,54 @@ class TorchOps:
             win = x.unfold(0, ck, 1)                                                              # [n, C, ck]
             out[r0:r0 + n] = F.silu((win * conv_w.float()[None]).sum(-1)).to(self.dtype)
         return out
+
+    def gdn_conv_tree(self, proj, conv_w, conv_state, seg_slot, seg_row0, seg_nrows, conv_dim, row_parent):
+        """Verify-tree rows: the conv window of a row is its ancestors (nearest last), then the slot's saved tail."""
+        T = proj.shape[0]
+        out = torch.zeros(T, conv_dim, dtype=self.dtype, device=proj.device)
+        ck = conv_w.shape[1]
+        wf = conv_w.float()
+        for s in range(len(seg_slot)):
+            n, r0, slot = int(seg_nrows[s]), int(seg_row0[s]), int(seg_slot[s])
+            tail = conv_state[slot].float()                                                       # [ck-1, C], oldest first
+            for r in range(n):
+                acc = wf[:, ck - 1] * proj[r0 + r, :conv_dim].float()
+                i = r
+                for j in range(ck - 2, -1, -1):
+                    i = int(row_parent[r0 + i]) if i >= 0 else i - 1
+                    x = proj[r0 + i, :conv_dim].float() if i >= 0 else tail[ck - 1 + i]
+                    acc = acc + wf[:, j] * x
+                out[r0 + r] = F.silu(acc).to(self.dtype)
+        return out
+
+    def gdn_rec_tree(self, qkv, proj, rec_state, A_log, dt_bias, seg_slot, seg_row0, seg_nrows, row_parent, row_flags, nk,
+                     nv, dk, dv, eps):
+        """Verify-tree rows (read-only): each row applies one delta-rule step to the state its parent left."""
+        T = qkv.shape[0]
+        conv_dim = 2 * nk * dk + nv * dv
+        y = torch.zeros(T, nv * dv, dtype=torch.float32, device=qkv.device)
+        rep = nv // nk
+        for s in range(len(seg_slot)):
+            n, r0, slot = int(seg_nrows[s]), int(seg_row0[s]), int(seg_slot[s])
+            states = {-1: rec_state[slot].float().clone()}
+            for r in range(n):
+                S = states[int(row_parent[r0 + r])]
+                x = qkv[r0 + r].float()
+                q = x[:nk * dk].view(nk, dk)
+                k = x[nk * dk:2 * nk * dk].view(nk, dk)
+                v = x[2 * nk * dk:].view(nv, dv)
+                q = q * torch.rsqrt(q.pow(2).sum(-1, keepdim=True) + eps) / math.sqrt(dk)
+                k = k * torch.rsqrt(k.pow(2).sum(-1, keepdim=True) + eps)
+                q, k = q.repeat_interleave(rep, 0), k.repeat_interleave(rep, 0)
+                b = proj[r0 + r, conv_dim + nv * dv:conv_dim + nv * dv + nv].float()
+                a = proj[r0 + r, conv_dim + nv * dv + nv:conv_dim + nv * dv + 2 * nv].float()
+                g = torch.exp(-torch.exp(A_log.float()) * _softplus(a + dt_bias.float()))
+                S = S * g[:, None, None]
+                delta = (v - torch.einsum("hkv,hk->hv", S, k)) * torch.sigmoid(b)[:, None]
+                S = S + torch.einsum("hk,hv->hkv", k, delta)
+                y[r0 + r] = torch.einsum("hkv,hk->hv", S, q).reshape(-1)
+                states[r] = S
+        return y
 
     def gdn_rec(self, qkv, proj, rec_state, conv_state, A_log, dt_bias, seg_slot, seg_row0, seg_nrows, nk, nv, dk, dv,
                 eps, commit=True, chunked=False, max_rows=None):

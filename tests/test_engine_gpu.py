@@ -181,3 +181,13 @@ def test_mtp_chain_drafter_on_the_gpu(ext):
     assert got[0] == want[0] and len(got) == len(want)
     assert sched.stats["drafted"] > 0
     eng.check(); dr.eng.check()
+
+
+def test_verify_tree_on_the_gpu(ext):
+    """A verify tree (ancestor-masked attention, GDN conv / recurrence along parent links) scores every path like the
+    chain verify of that path, and `commit_tree` (GDN replay of the kept path, KV rows moved into place) leaves the
+    slot as if the path had been fed row by row: tiny model, then the 27B layer widths, then an e4m3 KV cache."""
+    from ferrite_b200.utils.selftest import tree_test
+    tree_test("cuda", 3e-2)
+    tree_test("cuda", 3e-2, cfg=scaled(hybrid_27b(), 4), n_prompt=70)
+    tree_test("cuda", 6e-2, kv_dtype="fp8")

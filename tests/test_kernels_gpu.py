@@ -355,3 +355,39 @@ def test_gemm_tcgen05_fp32_out(ops, tops, M, N, K):
     assert y.dtype == torch.float32
     want = tops.linear(x, w, out_f32=True)
     assert (y - want).abs().max().item() < 2e-3 * max(1.0, want.abs().max().item())
+
+
+@pytest.mark.parametrize("nk,nv,dk,dv", [(2, 4, 128, 128), (2, 2, 64, 64)])
+def test_gdn_tree_conv_and_recurrence(ops, tops, nk, nv, dk, dv):
+    """Verify-tree GDN kernels against the host walk over parent links: two trees in one launch (one branching twice,
+    one a plain chain written as a tree), non-zero slot state, and the tree-as-chain equal to the chain kernels."""
+    from ferrite_b200.engine.executor import tree_layout
+    conv_dim = 2 * nk * dk + nv * dv
+    width = conv_dim + nv * dv + 2 * nv
+    pa = [-1, 0, 0, 1, 2, 3, 2, 6, 0]
+    pb = [-1, 0, 1, 2, 3]
+    T = len(pa) + len(pb)
+    proj = rnd(T, width, seed=21)
+    conv_w = rnd(conv_dim, 4, scale=0.5, seed=2)
+    A_log = rnd(nv, scale=0.3, seed=3, dtype=torch.float32)
+    dtb = rnd(nv, scale=0.3, seed=4, dtype=torch.float32)
+    seg_slot = torch.tensor([1, 2], device=DEV, dtype=torch.int32)
+    seg_row0 = torch.tensor([0, len(pa)], device=DEV, dtype=torch.int32)
+    seg_n = torch.tensor([len(pa), len(pb)], device=DEV, dtype=torch.int32)
+    parent = torch.tensor(pa + pb, device=DEV, dtype=torch.int32)
+    flags = torch.tensor(tree_layout(pa)[2] + tree_layout(pb)[2], device=DEV, dtype=torch.int32)
+    rec = rnd(3, nv, dk, dv, scale=0.2, seed=6, dtype=torch.float32)
+    conv = rnd(3, 3, conv_dim, seed=7)
+    rec0, conv0 = rec.clone(), conv.clone()
+    qa = ops.gdn_conv_tree(proj, conv_w, conv, seg_slot, seg_row0, seg_n, conv_dim, parent)
+    qb = tops.gdn_conv_tree(proj, conv_w, conv, seg_slot, seg_row0, seg_n, conv_dim, parent)
+    close(qa, qb)
+    ya = ops.gdn_rec_tree(qa, proj, rec, A_log, dtb, seg_slot, seg_row0, seg_n, parent, flags, nk, nv, dk, dv, 1e-6)
+    yb = tops.gdn_rec_tree(qa, proj, rec, A_log, dtb, seg_slot, seg_row0, seg_n, parent, flags, nk, nv, dk, dv, 1e-6)
+    close(ya, yb, atol=5e-3)
+    assert torch.equal(rec, rec0) and torch.equal(conv, conv0)             # read-only
+    # the chain segment through the tree kernels equals the chain kernels bit for bit
+    qc = ops.gdn_conv(proj, conv_w, conv, seg_slot[1:], seg_row0[1:], seg_n[1:], conv_dim, max_rows=len(pb))
+    assert torch.equal(qc[len(pa):], qa[len(pa):])
+    yc = ops.gdn_rec(qa, proj, rec, conv, A_log, dtb, seg_slot[1:], seg_row0[1:], seg_n[1:], nk, nv, dk, dv, 1e-6, commit=False)
+    assert torch.equal(yc[len(pa):], ya[len(pa):])
