@@ -16,7 +16,7 @@ import weakref
 from typing import Any, Dict, List
 
 MIRRORED = {
-    "forward", "commit_verified", "reset_slot", "prefill",
+    "forward", "commit_verified", "commit_tree", "reset_slot", "prefill",
     "ex.attach_blocks", "ex.copy_blocks", "ex.detach_blocks", "ex.ensure_capacity", "ex.pool.release",
     "ex.state_save", "ex.state_restore", "ex.copy_slot",
 }

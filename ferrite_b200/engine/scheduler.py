@@ -17,13 +17,13 @@ import threading
 import time
 import traceback
 from dataclasses import dataclass, field
-from typing import Callable, Dict, List, Optional, Sequence
+from typing import Callable, Dict, List, Optional, Sequence, Tuple
 
 import torch
 
 from .copy import Copier
 from .engine import Engine, prompt_cuts
-from .executor import Segment
+from .executor import Segment, TREE_MAX_ROWS
 from .pcache import PREFIX_MIN, Park, SlotCache, Snap, common_prefix
 from .sampler import Sampler, Sampling
 
@@ -44,6 +44,7 @@ class SchedOptions:
     prof: int = 0                      # 1: one line per step on stderr
     share_min: int = PREFIX_MIN        # shortest common prefix worth waiting for / forking from a running request
     mixed: bool = True                 # decode rows and a prompt chunk share one forward when both are waiting
+    tree_rows: int = 0                 # draft rows of a verify tree per request (0 = chains only; needs Drafter.draft_tree)
 
     @staticmethod
     def from_env() -> "SchedOptions":
@@ -52,7 +53,7 @@ class SchedOptions:
                             batch_rows=int(e.get("FE_BATCH_ROWS", "2048")),
                             finite_check=e.get("FE_FINITE_CHECK", "1") != "0",
                             step_timeout_s=float(e.get("FE_STEP_TIMEOUT", "120")), prof=int(e.get("FE_SCHED_PROF", "0")),
-                            share_min=int(e.get("FE_SHARE_MIN", str(PREFIX_MIN))))
+                            share_min=int(e.get("FE_SHARE_MIN", str(PREFIX_MIN))), tree_rows=int(e.get("FE_TREE", "0")))
 
 
 @dataclass
@@ -94,11 +95,64 @@ class Active:
     snap_at: List[int] = field(default_factory=list)
 
 
+def grow_tree(cands: Sequence[Sequence[Tuple[int, float]]], rows: int) -> Tuple[List[int], List[int]]:
+    """Best-first verify tree from per-depth candidates. `cands[d]` lists (token, log-probability) for the draft
+    token at depth d + 1 (a block drafter scores all depths in one pass, independently of the path taken). Nodes are
+    added in order of their path's summed log-probability until `rows` draft rows exist. Returns (tokens, parents) of
+    the draft rows in segment numbering: the root (the token being fed) is row 0, draft row i is row i + 1, parents
+    come before children. Reference `grow_tree` (`crates/fe-dflash/src/lib.rs:306`)."""
+    import heapq
+    toks: List[int] = []
+    par: List[int] = []
+    heap: List[Tuple[float, int, int, int, int]] = []       # (-score, tie, parent row, depth, candidate index)
+    tie = 0
+    if cands and cands[0]:
+        heap.append((-float(cands[0][0][1]), tie, 0, 0, 0))
+    while heap and len(toks) < rows:
+        neg, _, prow, d, ci = heapq.heappop(heap)
+        tok, lp = cands[d][ci]
+        toks.append(int(tok))
+        par.append(prow)
+        me = len(toks)                                       # this node's row in the segment
+        if ci + 1 < len(cands[d]):                           # next-best sibling under the same parent
+            tie += 1
+            heapq.heappush(heap, (neg + float(lp) - float(cands[d][ci + 1][1]), tie, prow, d, ci + 1))
+        if d + 1 < len(cands) and cands[d + 1]:              # best child
+            tie += 1
+            heapq.heappush(heap, (neg - float(cands[d + 1][0][1]), tie, me, d + 1, 0))
+    return toks, par
+
+
+def tree_walk(tokens: Sequence[int], parents: Sequence[int], pick) -> Tuple[List[int], List[int]]:
+    """Walk a verified tree from the root: `pick(row)` is the target's token after the row; descend into the child
+    that carries it, stop when none does. Returns (rows of the accepted path, tokens to emit), one token per path
+    row. Reference `tree_walk` (`crates/fe-model/src/sched.rs:125`)."""
+    kids: Dict[int, List[int]] = {}
+    for r, p in enumerate(parents):
+        if p >= 0:
+            kids.setdefault(p, []).append(r)
+    path, new, node = [0], [], 0
+    while True:
+        t = int(pick(node))
+        new.append(t)
+        nxt = next((c for c in kids.get(node, ()) if int(tokens[c]) == t), None)
+        if nxt is None:
+            return path, new
+        path.append(nxt)
+        node = nxt
+
+
 class Drafter:
     """Plug-in interface of a draft model (reference trait `Drafter`, `sched.rs:58-116`)."""
 
     def draft(self, slot: int, last_token: int, pos: int, taps, n: int) -> List[int]:
         return []
+
+    def draft_tree(self, slot: int, last_token: int, pos: int, taps, depth: int, rows: int) -> Tuple[List[int], List[int]]:
+        """Draft rows of a verify tree: (tokens, parents) in segment numbering (row 0 is `last_token`, draft row i is
+        row i + 1). The default is the chain of `draft`."""
+        d = self.draft(slot, last_token, pos, taps, min(depth, rows))
+        return list(d), list(range(len(d)))
 
     def absorb(self, slot: int, tokens: Sequence[int], pos0: int, taps) -> None:
         pass
@@ -435,9 +489,10 @@ class Scheduler:
 
     def _decode_step(self, decoders: List[Active]) -> int:
         """One decode / verify step over all decoding requests: a row per request plus its draft rows."""
-        segs, drafts = [], []
+        segs, drafts, trees = [], [], []
         for a in decoders:
             d: List[int] = []
+            par: Optional[List[int]] = None
             if self.opts.spec > 0:
                 room = min(self.opts.spec, DECODE_ROWS - 1, a.req.sampling.max_tokens - len(a.out) - 1,
                            self.eng.ecfg.max_ctx - a.pos - 2)
@@ -445,11 +500,18 @@ class Scheduler:
                     if a.copier is not None:
                         a.copier.sync(a.req.prompt + a.out[:-1] + [a.next_token])
                         d = a.copier.propose(room)
-                    if not d and self.drafter is not None:
+                    if not d and self.drafter is not None and self.opts.tree_rows > 0:
+                        n_rows = min(self.opts.tree_rows, TREE_MAX_ROWS - 1, self.eng.ecfg.max_ctx - a.pos - 2)
+                        d, dp = self.drafter.draft_tree(a.slot, a.next_token, a.pos, self.eng.taps, room, n_rows)
+                        d, dp = list(d[:n_rows]), list(dp[:n_rows])
+                        if d and dp != list(range(len(d))):
+                            par = [-1] + [int(p) for p in dp]
+                    elif not d and self.drafter is not None:
                         d = self.drafter.draft(a.slot, a.next_token, a.pos, self.eng.taps, room)
-                    d = [int(t) for t in d[:room]]
+                    d = [int(t) for t in (d if par is not None else d[:room])]
             drafts.append(d)
-            segs.append(Segment(a.slot, a.pos, [a.next_token] + d, "all"))
+            trees.append(par)
+            segs.append(Segment(a.slot, a.pos, [a.next_token] + d, "all", parents=par))
         spec = any(drafts)
         all_greedy = all(a.req.sampling.greedy for a in decoders)
         logits, picks, rows = self.eng.forward(segs, commit=not spec, greedy=all_greedy)
@@ -460,10 +522,36 @@ class Scheduler:
                 for a in decoders:
                     self._finish(a, "error", message="non-finite logits")
                 return len(rows)
-        keep, r = [], 0
+        keep, paths, r = [], [], 0
         taps = self.eng.taps
-        for a, d in zip(decoders, drafts):
+        any_tree = any(t is not None for t in trees)
+        for a, d, par in zip(decoders, drafts, trees):
             n = 1 + len(d)
+            if par is not None:
+                # verify tree: follow the target's choices from the root (reference `tree_walk`); sampling from the
+                # target at every node and descending only on a match keeps the output distribution the target's
+                def pick(node, a=a, r=r):
+                    if all_greedy:
+                        return int(ids[r + node])
+                    t = a.sampler.sample(logits[r + node])
+                    a.sampler.observe(t)
+                    return t
+                path, new = tree_walk([a.next_token] + d, par, pick)
+                paths.append(path)
+                keep.append(len(new))
+                acc = len(new) - 1
+                a.drafts_proposed += len(d)
+                a.drafts_accepted += acc
+                self.stats["drafted"] += len(d)
+                self.stats["accepted"] += acc
+                fed = [a.next_token] + [d[i - 1] for i in path[1:]]
+                a.pos += len(new)
+                if self.drafter is not None:
+                    idx = torch.tensor([r + i for i in path], dtype=torch.long, device=taps[0].device) if taps else None
+                    self.drafter.absorb(a.slot, fed, a.pos - len(new), [t.index_select(0, idx) for t in taps])
+                self._accept(a, new, sampled=not all_greedy)
+                r += n
+                continue
             if all_greedy:
                 # accept-while-match walk over the chain (reference `tree_walk` on a path)
                 new = []
@@ -476,6 +564,7 @@ class Scheduler:
                 new = a.sampler.spec_accept(logits[r:r + n], d)
             acc = len(new) - 1
             keep.append(len(new))
+            paths.append(list(range(len(new))))
             a.drafts_proposed += len(d)
             a.drafts_accepted += acc
             self.stats["drafted"] += len(d)
@@ -488,7 +577,9 @@ class Scheduler:
                 self.drafter.absorb(a.slot, fed, a.pos - len(new), [t[r:r + len(new)] for t in taps])
             self._accept(a, new, sampled=not all_greedy)
             r += n
-        if spec:
+        if spec and any_tree:
+            self.eng.commit_tree(paths)
+        elif spec:
             self.eng.commit_verified(keep)
         return len(rows)
 

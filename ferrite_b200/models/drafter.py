@@ -17,7 +17,7 @@ import torch
 from ..config import EngineConfig, ModelConfig
 from ..engine.engine import Engine
 from ..engine.executor import Segment
-from ..engine.scheduler import Drafter
+from ..engine.scheduler import Drafter, grow_tree
 
 
 class BlockDrafter(Drafter):
@@ -26,6 +26,7 @@ class BlockDrafter(Drafter):
         ecfg = EngineConfig(n_slots=n_slots, max_ctx=max_ctx, use_graphs=False)
         self.eng = Engine(cfg, weights, ecfg, device=device, seed=seed)
         self.block = block
+        self.tree_k = 4                              # candidates per depth when growing a verify tree
         self.mask_token = mask_token
         g = torch.Generator().manual_seed(seed + 17)
         self.n_taps = n_taps
@@ -61,6 +62,20 @@ class BlockDrafter(Drafter):
         x_add = feat.expand(n, -1).contiguous() if feat is not None else None
         _, picks, _ = self.eng.forward([Segment(slot, pos, toks, "all")], commit=False, greedy=True, x_add=x_add)
         return [int(t) for t in picks[0].tolist()]
+
+    def draft_tree(self, slot: int, last_token: int, pos: int, taps, depth: int, rows: int):
+        """One block pass scores every depth at once; the `tree_k` best tokens of each depth are grown into a
+        best-first tree of `rows` draft rows (reference `draft_trees`, `crates/fe-dflash/src/lib.rs:841`)."""
+        n = min(depth, self.block)
+        if n <= 0 or rows <= 0:
+            return [], []
+        toks = [last_token] + [self.mask_token] * (n - 1)
+        feat = self.last_feat[slot]
+        x_add = feat.expand(n, -1).contiguous() if feat is not None else None
+        logits, _, _ = self.eng.forward([Segment(slot, pos, toks, "all")], commit=False, greedy=False, x_add=x_add)
+        lp, ids = torch.log_softmax(logits.float(), -1).topk(min(self.tree_k, logits.shape[-1]), -1)
+        lp, ids = lp.tolist(), ids.tolist()
+        return grow_tree([list(zip(ids[d], lp[d])) for d in range(n)], rows)
 
     def save_window(self, slot: int):
         return {"len": self.eng.slot_len[slot], "feat": self.last_feat[slot]}

@@ -57,3 +57,56 @@ def test_two_trees_and_a_chain_in_one_step_cpu():
     a = tree.forward([Segment(0, 22, [6], "last"), Segment(1, 36, [6], "last")], greedy=False)[0].clone()
     b = chain.forward([Segment(0, 22, [6], "last"), Segment(1, 36, [6], "last")], greedy=False)[0].clone()
     assert (a - b).abs().max().item() < 2e-4
+
+
+def test_grow_tree_and_walk():
+    from ferrite_b200.engine.scheduler import grow_tree, tree_walk
+    import math
+    lp = math.log
+    cands = [[(10, lp(0.6)), (11, lp(0.3)), (12, lp(0.1))], [(20, lp(0.5)), (21, lp(0.4))], [(30, lp(0.9))]]
+    toks, par = grow_tree(cands, 6)
+    assert len(toks) == 6 and par[0] == 0 and all(p <= i for i, p in enumerate(par))       # parents precede children
+    # best path first: 10 (0.6), then 10-20 (0.30) ties 11 (0.30): both in, then 10-20-30 (0.27), 10-21 (0.24), 10-21-30 (0.216)
+    paths = set()
+    for i in range(6):
+        seq, r = [], i + 1
+        while r > 0:
+            seq.append(toks[r - 1]); r = par[r - 1]
+        paths.add(tuple(seq[::-1]))
+    assert paths == {(10,), (11,), (10, 20), (10, 20, 30), (10, 21), (10, 21, 30)}
+    # chain budget 1 keeps only the best token
+    assert grow_tree(cands, 1) == ([10], [0])
+    seg_toks, seg_par = [7] + toks, [-1] + par
+    target = {(): 10, (10,): 21, (10, 21): 99}
+    def pick(node):
+        seq, r = [], node
+        while r > 0:
+            seq.append(seg_toks[r]); r = seg_par[r]
+        return target[tuple(seq[::-1])]
+    path, new = tree_walk(seg_toks, seg_par, pick)
+    assert [seg_toks[r] for r in path] == [7, 10, 21] and new == [10, 21, 99]
+
+
+def test_scheduler_tree_speculation_keeps_greedy_output():
+    from ferrite_b200.config import ModelConfig
+    from ferrite_b200.engine.scheduler import Sampling, SchedOptions, Scheduler, generate
+    from ferrite_b200.models.drafter import BlockDrafter
+    cfg = tiny_hybrid()
+    cfg.tap_layers = [1, 3]
+    w = init_weights(cfg, seed=0)
+    prompt = _prompt(cfg, 25, 31)
+    plain = Engine(cfg, w, EngineConfig(n_slots=2, max_ctx=256), device="cpu")
+    want = generate(Scheduler(plain, SchedOptions(spec=0)), [prompt, prompt[:11]], Sampling(max_tokens=14))
+    eng = Engine(cfg, w, EngineConfig(n_slots=2, max_ctx=256), device="cpu")
+    dcfg = ModelConfig(name="tiny-drafter", hidden=128, inter=256, n_layers=2, full_attn_every=1, head_dim=32, n_q=4,
+                       n_kv=2, rotary_dim=32, attn_gate=False, vocab=cfg.vocab, tie_embeddings=True)
+    dr = BlockDrafter(dcfg, target_hidden=cfg.hidden, n_taps=2, n_slots=2, max_ctx=256, device="cpu", block=4)
+    sched = Scheduler(eng, SchedOptions(spec=4, copy_rows=False, tree_rows=10), drafter=dr)
+    got = generate(sched, [prompt, prompt[:11]], Sampling(max_tokens=14))
+    assert got == want
+    assert sched.stats["drafted"] > 0
+    # sampled requests walk the tree by sampling from the target at every node: seeded runs repeat
+    s = Sampling(temperature=0.8, top_k=30, seed=5, max_tokens=10)
+    a = generate(sched, [prompt], s)[0]
+    b = generate(sched, [prompt], s)[0]
+    assert a == b and len(a) == 10
