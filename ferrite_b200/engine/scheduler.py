@@ -418,11 +418,8 @@ class Scheduler:
             prefills = prefills[1:]
         elif decoders:
             n_dec = self._decode_step(decoders)
-        for a in prefills:                                # short remainders first (reference: short chunks first)
-            if budget <= 0:
-                break
-            n_pre += self._prefill_step(a, budget)
-            budget -= n_pre
+        if prefills and budget > 0:
+            n_pre += self._group_prefill(prefills, budget)
         if self.opts.prof:
             import sys
             print(f"step {self.step_no}: dec {n_dec} rows, prompt {n_pre} rows, {1e3 * (time.time() - t0):.2f} ms",
@@ -459,6 +456,47 @@ class Scheduler:
         self._prefill_done(a, cut, toks, last, int(ids[len(decoders)]) if last else None)
         return len(decoders), cut
 
+    def _group_prefill(self, prefills: List[Active], budget: int) -> int:
+        """Prompt chunks of several requests in ONE forward (reference `group_prefill`,
+        `crates/fe-model/src/model.rs:2279`): short remainders first, each request contributes its next chunk until the
+        step's row budget is used, so four 2K prompts arriving together cost one pass over the weights, not four."""
+        budget = min(budget, self.eng.ecfg.max_step_rows)
+        if len(prefills) == 1:
+            return self._prefill_step(prefills[0], budget)
+        group = []
+        for a in sorted(prefills, key=lambda a: len(a.pending)):
+            if budget < 32 and group:
+                break
+            cut, toks, last, greedy = self._prefill_cut(a, budget)
+            if cut > budget and group:
+                continue
+            group.append((a, cut, toks, last, greedy))
+            budget -= cut
+        if len(group) == 1:
+            return self._prefill_step(group[0][0], group[0][1])
+        segs = [Segment(a.slot, a.pos, toks, "last" if last else "none") for a, _, toks, last, _ in group]
+        all_greedy = all(g for _, _, _, last, g in group if last)
+        logits, picks, _ = self.eng.forward(segs, greedy=all_greedy)
+        ids = picks[0].tolist() if (all_greedy and picks is not None) else None
+        taps = list(self.eng.taps)
+        k = r = n = 0
+        for a, cut, toks, last, _ in group:
+            tok = None
+            if last:
+                if self.opts.finite_check and not bool(torch.isfinite(logits[k]).all()):
+                    a.pos += cut
+                    a.pending = a.pending[cut:]
+                    self._finish(a, "error", message="non-finite logits")
+                    k += 1
+                    r += cut
+                    continue
+                tok = int(ids[k]) if ids is not None else a.sampler.sample(logits[k], first=not a.out)
+                k += 1
+            self._prefill_done(a, cut, toks, last, tok, [t[r:r + cut] for t in taps])
+            r += cut
+            n += cut
+        return n
+
     def _prefill_step(self, a: Active, budget: int) -> int:
         """Run the next chunk of a prompt on its own."""
         cut, toks, last, greedy = self._prefill_cut(a, budget)
@@ -474,7 +512,7 @@ class Scheduler:
         self._prefill_done(a, cut, toks, last, tok)
         return cut
 
-    def _prefill_done(self, a: Active, cut: int, toks: List[int], last: bool, tok) -> None:
+    def _prefill_done(self, a: Active, cut: int, toks: List[int], last: bool, tok, taps=None) -> None:
         a.pos += cut
         a.pending = a.pending[cut:]
         self.slot_cache[a.slot].tokens = (a.req.prompt + a.out)[:a.pos]
@@ -482,7 +520,7 @@ class Scheduler:
         if a.pos in a.snap_at:
             self._snapshot(a, pinned=(a.pos == a.snap_at[0]))
         if self.drafter:
-            self.drafter.absorb(a.slot, toks, a.pos - cut, self.eng.taps)
+            self.drafter.absorb(a.slot, toks, a.pos - cut, self.eng.taps if taps is None else taps)
         if last:
             a.t_prompt_done = time.time()
             self._accept(a, [tok])

@@ -281,3 +281,25 @@ def test_mtp_rows_do_not_depend_on_how_the_prompt_was_cut():
     dr.absorb(0, p[17:], 17, eng.taps)
     assert dr.draft(0, 9, 30, eng.taps, 3) == a
     assert dr.draft(0, 9, 29, eng.taps, 3) == []          # no hidden kept for that position: nothing to draft from
+
+
+def test_group_prefill_runs_several_prompts_in_one_forward():
+    cfg, w, eng = _engine(n_slots=4)
+    prompts = [_prompt(cfg, n, 50 + n) for n in (40, 23, 64)]
+    calls = []
+    fwd = eng.forward
+
+    def spy(segs, **kw):
+        calls.append([len(s.tokens) for s in segs])
+        return fwd(segs, **kw)
+    eng.forward = spy
+    sched = Scheduler(eng, SchedOptions(spec=0))
+    out = generate(sched, prompts, Sampling(max_tokens=6))
+    for p, o in zip(prompts, out):
+        assert o == _plain(cfg, w, p, 6)
+    assert len(calls[0]) == 3 and sum(calls[0]) >= 23 + 32 + 32      # all three prompts share the first forward
+    # sampled requests take their first token from the logits of the shared forward
+    s = Sampling(temperature=0.7, top_k=20, seed=3, max_tokens=5)
+    a = generate(sched, prompts[:2], s)
+    b = generate(sched, prompts[:2], s)
+    assert a == b and all(len(x) == 5 for x in a)
