@@ -73,6 +73,11 @@ int fb_attn_prefill(void* out, const void* q, const void* k_cache, const void* v
                     long proj_stride, const int* seg_slot, const int* seg_row0, const int* seg_nrows,
                     const int* seg_pos0, const int* block_table, int max_blocks, int kv_block, int nseg, int max_rows,
                     int nq, int nkv, int hd, int gated, cudaStream_t s);
+// tcgen05 / TMEM form (attn_prefill_tc.cu): hd 64/128/256 and kv_block a multiple of 64, else returns -20
+int fb_attn_prefill_tc(void* out, const void* q, const void* k_cache, const void* v_cache, const void* proj,
+                       long proj_stride, const int* seg_slot, const int* seg_row0, const int* seg_nrows,
+                       const int* seg_pos0, const int* block_table, int max_blocks, int kv_block, int nseg, int max_rows,
+                       long q_rows, long cache_rows, int nq, int nkv, int hd, int gated, int* status, cudaStream_t s);
 
 // ---- gdn.cu ----
 int fb_gdn_conv(void* out, const void* proj, long proj_stride, const void* conv_w, const void* conv_state,

@@ -182,6 +182,21 @@ void attn_prefill(Tensor out, Tensor q, Tensor k_cache, Tensor v_cache, Tensor p
                         (int)nkv, (int)hd, gated ? 1 : 0, cur_stream()), "attn_prefill");
 }
 
+int64_t attn_prefill_tc(Tensor out, Tensor q, Tensor k_cache, Tensor v_cache, Tensor proj, Tensor seg_slot, Tensor seg_row0,
+                        Tensor seg_nrows, Tensor seg_pos0, Tensor block_table, int64_t kv_block, int64_t max_rows,
+                        int64_t nq, int64_t nkv, int64_t hd, bool gated, c10::optional<Tensor> status) {
+  TORCH_CHECK(q.is_contiguous() && k_cache.is_contiguous() && v_cache.is_contiguous(), "attn_prefill_tc: contiguous inputs");
+  int rc = fb_attn_prefill_tc(out.data_ptr(), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), proj.data_ptr(),
+                              (long)proj.stride(0), seg_slot.data_ptr<int>(), seg_row0.data_ptr<int>(),
+                              seg_nrows.data_ptr<int>(), seg_pos0.data_ptr<int>(), block_table.data_ptr<int>(),
+                              (int)block_table.size(1), (int)kv_block, (int)seg_slot.numel(), (int)max_rows,
+                              (long)q.size(0), (long)(k_cache.size(0) * k_cache.size(1)), (int)nq, (int)nkv, (int)hd,
+                              gated ? 1 : 0, (int*)mptr(status), cur_stream());
+  if (rc == -20) return rc;                     // shape outside this kernel: the caller takes the mma.sync kernel
+  check(rc, "attn_prefill_tc");
+  return 0;
+}
+
 void gdn_conv(Tensor out, Tensor proj, Tensor conv_w, Tensor conv_state, Tensor seg_slot, Tensor seg_row0,
               Tensor seg_nrows, int64_t max_rows) {
   check(fb_gdn_conv(out.data_ptr(), proj.data_ptr(), (long)proj.stride(0), conv_w.data_ptr(), conv_state.data_ptr(),
@@ -289,6 +304,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("attn_prep", &attn_prep);
   m.def("attn_decode", &attn_decode);
   m.def("attn_prefill", &attn_prefill);
+  m.def("attn_prefill_tc", &attn_prefill_tc);
   m.def("gdn_conv", &gdn_conv);
   m.def("gdn_rec", &gdn_rec);
   m.def("gdn_conv_tree", &gdn_conv_tree);

@@ -10,6 +10,8 @@ from __future__ import annotations
 import math
 from typing import Optional
 
+import os
+
 import torch
 
 from .._ext import load
@@ -36,6 +38,7 @@ class CudaOps:
         self.launches = 0                   # kernels launched (or recorded into a graph) through this object
         self.moe_pair_rows = MOE_PAIR_ROWS
         self.mma_gemv_rows = (2, 32)        # row counts routed to the mma.sync weight-streaming kernel
+        self.attn_tc = os.environ.get("FB_ATTN_TC", "1") != "0"     # prompt attention on tcgen05 (0: mma.sync kernel)
         self._gdn_scratch = None
         self._tree_scratch = None
         self._kv_scratch = None
@@ -285,8 +288,10 @@ class CudaOps:
             toks = max_blocks * kv_block
             key = (n_slots, toks, nkv, hd)
             if self._kv_scratch is None or self._kv_scratch[0] != key:
-                ks = torch.empty(n_slots * max_blocks, kv_block, nkv, hd, dtype=self.dtype, device=self.device)
-                vs = torch.empty_like(ks)
+                # zeros: rows past the decoded ones are masked by causality but still multiplied (0 x value) by the
+                # tensor-core kernel, so they must hold finite numbers
+                ks = torch.zeros(n_slots * max_blocks, kv_block, nkv, hd, dtype=self.dtype, device=self.device)
+                vs = torch.zeros_like(ks)
                 ident = torch.arange(n_slots * max_blocks, dtype=torch.int32, device=self.device).view(n_slots, max_blocks)
                 self._kv_scratch = (key, ks, vs, ident.contiguous())
             _, ks, vs, ident = self._kv_scratch
@@ -295,6 +300,13 @@ class CudaOps:
                               toks if max_kvlen is None else max_kvlen, nkv, hd, toks)
             k_cache, v_cache, block_table = ks, vs, ident
         self.launches += 1
+        if self.attn_tc and hd in (64, 128, 256) and kv_block % 64 == 0:
+            # tcgen05 / TMEM kernel (TMA-fed, 128 query rows per CTA); other shapes take the mma.sync kernel
+            rc = self.C.attn_prefill_tc(out, q.view(q.shape[0], nq * hd), k_cache, v_cache, proj, seg_slot, seg_row0,
+                                        seg_nrows, seg_pos0, block_table, kv_block, max_rows, nq, nkv, hd, gated,
+                                        self.status_word)
+            if rc == 0:
+                return out
         self.C.attn_prefill(out, q, k_cache, v_cache, proj, seg_slot, seg_row0, seg_nrows, seg_pos0, block_table,
                             kv_block, max_rows, nq, nkv, hd, gated)
         return out

@@ -391,3 +391,41 @@ def test_gdn_tree_conv_and_recurrence(ops, tops, nk, nv, dk, dv):
     close(qc[len(pa):], qa[len(pa):])
     yc = ops.gdn_rec(qa, proj, rec, conv, A_log, dtb, seg_slot[1:], seg_row0[1:], seg_n[1:], nk, nv, dk, dv, 1e-6, commit=False)
     assert torch.equal(yc[len(pa):], ya[len(pa):])
+
+
+@pytest.mark.parametrize("hd,nq,nkv,gated", [(256, 6, 2, True), (128, 8, 2, False), (64, 4, 4, True)])
+def test_attention_prefill_tcgen05_against_mma_sync_and_reference(ops, tops, hd, nq, nkv, gated):
+    """The tcgen05/TMEM prompt-attention kernel against the mma.sync kernel and the fp32 reference: two segments of
+    different slots in one launch (a 520-row chunk behind a 200-key prefix, and a fresh 333-row prompt whose last
+    tiles are ragged), scattered pages."""
+    kv_block, n_slots, max_blocks = 64, 2, 16
+    nb = n_slots * max_blocks
+    width = nq * hd * (2 if gated else 1) + 2 * nkv * hd
+    g = torch.Generator().manual_seed(5)
+    bt = torch.randperm(nb, generator=g).to(torch.int32).view(n_slots, max_blocks).to(DEV).contiguous()
+    rot = 64
+    inv = (1e6 ** (-torch.arange(rot // 2, dtype=torch.float64) / (rot // 2))).float().to(DEV)
+    qn, kn = rnd(hd, scale=0.1, seed=7), rnd(hd, scale=0.1, seed=8)
+    kc = torch.zeros(nb, kv_block, nkv, hd, dtype=torch.bfloat16, device=DEV)
+    vc = torch.zeros_like(kc)
+    # the prefix of slot 0, then the step's rows: slot 0 continues at 200, slot 1 starts at 0
+    pre = rnd(200, width, seed=10)
+    ops.attn_prep(pre, qn, kn, inv, torch.zeros(200, device=DEV, dtype=torch.int32),
+                  torch.arange(200, device=DEV, dtype=torch.int32), bt, kc, vc, kv_block, nq, nkv, hd, rot, gated, 1e-6)
+    T = 520 + 333
+    proj = rnd(T, width, seed=11)
+    slot = torch.cat([torch.zeros(520), torch.ones(333)]).to(DEV, torch.int32)
+    pos = torch.cat([torch.arange(200, 720), torch.arange(333)]).to(DEV, torch.int32)
+    q = ops.attn_prep(proj, qn, kn, inv, slot, pos, bt, kc, vc, kv_block, nq, nkv, hd, rot, gated, 1e-6)
+    segs = [torch.tensor(v, device=DEV, dtype=torch.int32) for v in ([0, 1], [0, 520], [520, 333], [200, 0])]
+    assert ops.attn_tc
+    a = ops.attention_prefill(q, proj, kc, vc, *segs, bt, kv_block, nq, nkv, hd, gated, 520)
+    ops.attn_tc = False
+    try:
+        b = ops.attention_prefill(q, proj, kc, vc, *segs, bt, kv_block, nq, nkv, hd, gated, 520)
+    finally:
+        ops.attn_tc = True
+    c = tops.attention_prefill(q, proj, kc, vc, *segs, bt, kv_block, nq, nkv, hd, gated, 520)
+    close(b, c)
+    close(a, c)
+    assert ops.status() == 0
