@@ -38,6 +38,12 @@ int fb_gemv_mma(void* y, const void* x, const void* w, const void* norm_w, const
 // FP8 (e4m3) GEMM with per-row / per-feature scales, and the activation quantiser (gemm_tcgen05.cu)
 int fb_quant_fp8(void* q, float* scale, const void* x, const void* norm_w, int rows, int K, long ldx, float eps,
                  cudaStream_t s);
+// block-scaled form (gemm_fp8_block.cu): activations scaled per (row, 128 k), weights per (128 features, 128 k);
+// code matrices are padded to whole k blocks: [rows][kblocks * 128]
+long fb_fp8_block_kblocks(int K);
+int fb_quant_fp8_block(void* q, float* scale, const void* x, int rows, int K, long ldx, cudaStream_t s);
+int fb_gemm_fp8_block(void* Y, const void* Xq, const float* sx, const void* Wq, const float* sw, const void* res, int M,
+                      int N, int K, long ldy, int* status, cudaStream_t s);
 int fb_gemm_fp8(void* Y, const void* Xq, const void* Wq, const float* scale_m, const float* scale_n, const void* res, int M,
                 int N, int K, long ldy, int mode, int split_k, float* workspace, int* counters, int* status, int sm_count,
                 cudaStream_t s);

@@ -100,6 +100,22 @@ void quant_fp8(Tensor q, Tensor scale, Tensor x, c10::optional<Tensor> norm_w, d
                      (long)x.stride(0), (float)eps, cur_stream()), "quant_fp8");
 }
 
+void quant_fp8_block(Tensor q, Tensor scale, Tensor x) {
+  check(fb_quant_fp8_block(q.data_ptr(), scale.data_ptr<float>(), x.data_ptr(), (int)x.size(0), (int)x.size(1),
+                           (long)x.stride(0), cur_stream()), "quant_fp8_block");
+}
+
+void gemm_fp8_block(Tensor Y, Tensor Xq, Tensor sx, Tensor Wq, Tensor sw, c10::optional<Tensor> res, int64_t K,
+                    c10::optional<Tensor> status) {
+  const int M = (int)Xq.size(0), N = (int)Wq.size(0);
+  const long kb = fb_fp8_block_kblocks((int)K);
+  TORCH_CHECK(Xq.size(1) == kb * 128 && Wq.size(1) == kb * 128 && Xq.is_contiguous() && Wq.is_contiguous(),
+              "gemm_fp8_block: code matrices are [rows][kblocks * 128], contiguous");
+  TORCH_CHECK(sx.numel() == (int64_t)M * kb && sw.numel() == (int64_t)((N + 127) / 128) * kb, "gemm_fp8_block: scale shapes");
+  check(fb_gemm_fp8_block(Y.data_ptr(), Xq.data_ptr(), sx.data_ptr<float>(), Wq.data_ptr(), sw.data_ptr<float>(), cptr(res),
+                          M, N, (int)K, (long)Y.stride(0), (int*)mptr(status), cur_stream()), "gemm_fp8_block");
+}
+
 void gemm_fp8(Tensor Y, Tensor Xq, Tensor Wq, c10::optional<Tensor> scale_m, c10::optional<Tensor> scale_n,
               c10::optional<Tensor> res, int64_t mode, int64_t split_k, c10::optional<Tensor> workspace,
               c10::optional<Tensor> counters, c10::optional<Tensor> status) {
@@ -314,6 +330,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gdn_step", &gdn_step);
   m.def("quant_fp8", &quant_fp8);
   m.def("gemm_fp8", &gemm_fp8);
+  m.def("quant_fp8_block", &quant_fp8_block);
+  m.def("gemm_fp8_block", &gemm_fp8_block);
   m.def("gdn_chunk", &gdn_chunk);
   m.def("gdn_chunk_scratch_bytes", &gdn_chunk_scratch_bytes);
   m.def("argmax", &argmax);

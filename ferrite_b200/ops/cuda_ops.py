@@ -156,6 +156,43 @@ class CudaOps:
         self.C.gemm_fp8(y, xq, wq, xs, w_scale, res, 1 if swiglu else 0, split, ws, cnt, self.status_word)
         return y
 
+    @staticmethod
+    def quantize_weight_fp8_block(w):
+        """128 x 128 block e4m3 quantisation of a [N, K] weight: (codes uint8 [N, ceil(K/128)*128] zero padded, scales
+        fp32 [ceil(N/128), ceil(K/128)]), scale = block amax / 448."""
+        N, K = w.shape
+        nb, kb = (N + 127) // 128, (K + 127) // 128
+        wf = torch.zeros(nb * 128, kb * 128, dtype=torch.float32, device=w.device)
+        wf[:N, :K] = w.float()
+        blocks = wf.view(nb, 128, kb, 128)
+        sc = (blocks.abs().amax((1, 3)) / 448.0).clamp_min(1e-12)
+        q = (blocks / sc[:, None, :, None]).to(torch.float8_e4m3fn).view(torch.uint8).view(nb * 128, kb * 128)
+        return q[:N].contiguous(), sc.contiguous()
+
+    def quantize_act_fp8_block(self, x):
+        """Rows to e4m3 with one scale per (row, 128 columns): (codes [M, ceil(K/128)*128], scales fp32 [M, ceil(K/128)])."""
+        M, K = x.shape
+        kb = (K + 127) // 128
+        q = torch.empty(M, kb * 128, dtype=torch.uint8, device=self.device)
+        sc = torch.empty(M, kb, dtype=torch.float32, device=self.device)
+        self.launches += 1
+        self.C.quant_fp8_block(q, sc, x)
+        return q, sc
+
+    def linear_fp8_block(self, x, wq, w_scale, res=None):
+        """y = x W^T with block-scaled e4m3 operands (activations 1 x 128, weights 128 x 128): per k block the tensor
+        core's partial product is scaled and added into fp32 registers by the epilogue warps."""
+        M, K = x.shape
+        N = wq.shape[0]
+        xq, xs = self.quantize_act_fp8_block(x)
+        y = torch.empty(M, (N + 7) // 8 * 8, dtype=self.dtype, device=self.device)[:, :N]
+        fused = res is not None and res.stride(0) == y.stride(0)       # the kernel reads res with y's row stride
+        self.launches += 1
+        self.C.gemm_fp8_block(y, xq, xs, wq, w_scale, res if fused else None, K, self.status_word)
+        if res is not None and not fused:
+            y += res
+        return y
+
     # ---- NVFP4 weights x NVFP4 activations on the block-scaled tensor-core GEMM -------------------------
     def quant_nvfp4(self, x, norm_w=None, eps=1e-6):
         """Quantise activation rows (optionally after RMSNorm) to e2m1 codes + tiled e4m3 scales + per-row scale."""

@@ -101,6 +101,7 @@ def main():
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--no-flush", action="store_true")
     ap.add_argument("--fp4", action="store_true", help="NVFP4 weights and activations (block-scaled tcgen05 GEMM)")
+    ap.add_argument("--fp8b", action="store_true", help="gemm: block-scaled e4m3 (1x128 activations, 128x128 weights)")
     ap.add_argument("--a16", action="store_true", help="with --fp4: keep 16-bit activations (W4A16 GEMV)")
     a = ap.parse_args()
     from ..ops.cuda_ops import CudaOps
@@ -109,7 +110,17 @@ def main():
     ops = CudaOps(dev)
     ops.fp4_act = a.fp4 and not a.a16
     t = Timer(dev, a.warmup, a.iters, flush=not a.no_flush)
-    if a.what in ("gemv", "gemm"):
+    if a.what == "gemm" and a.fp8b:
+        x = rnd(a.m, a.k)
+        wq, ws = ops.quantize_weight_fp8_block(rnd(a.n, a.k, scale=0.05))
+        ms = t.run(lambda: ops.linear_fp8_block(x, wq, ws))
+        xq, xs = ops.quantize_act_fp8_block(x)
+        y = torch.empty(a.m, a.n, dtype=torch.bfloat16, device=dev)
+        ms_g = t.run(lambda: ops.C.gemm_fp8_block(y, xq, xs, wq, ws, None, a.k, ops.status_word))
+        report(f"fp8 block-scaled linear (quantise + gemm) m{a.m} n{a.n} k{a.k}", ms, a.n * a.k + a.m * a.k * 3 + a.m * a.n * 2,
+               2.0 * a.m * a.n * a.k)
+        report(f"fp8 block-scaled gemm only m{a.m} n{a.n} k{a.k}", ms_g, a.n * a.k + a.m * a.k + a.m * a.n * 2, 2.0 * a.m * a.n * a.k)
+    elif a.what in ("gemv", "gemm"):
         bench_linear(ops, t, a.m, a.n, a.k, a.swiglu, a.norm, a.res, fp4=a.fp4)
     elif a.what == "layer":
         from ..config import hybrid_27b

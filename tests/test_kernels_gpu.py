@@ -429,3 +429,39 @@ def test_attention_prefill_tcgen05_against_mma_sync_and_reference(ops, tops, hd,
     close(b, c)
     close(a, c)
     assert ops.status() == 0
+
+
+@pytest.mark.parametrize("M,N,K", [(300, 384, 1024), (64, 200, 7168), (1, 128, 512), (513, 2048, 2048 + 64)])
+def test_fp8_block_scaled_gemm(ops, M, N, K):
+    """Block-scaled e4m3 GEMM (1 x 128 activation blocks, 128 x 128 weight blocks; per-k-block promotion out of TMEM)
+    against an fp32 product of the dequantised operands; the quantiser against the torch rounding; ragged M, N and K."""
+    x = rnd(M, K, seed=1)
+    x[:, :K // 2] *= 8.0                                  # blocks with different scales along k
+    w = rnd(N, K, scale=0.05, seed=2)
+    w[: N // 2, K // 3:] *= 6.0
+    wq, ws = ops.quantize_weight_fp8_block(w)
+    xq, xs = ops.quantize_act_fp8_block(x)
+    kb = (K + 127) // 128
+    assert xq.shape == (M, kb * 128) and xs.shape == (M, kb)
+    xp = torch.zeros(M, kb * 128, device=DEV)
+    xp[:, :K] = x.float()
+    want_s = (xp.view(M, kb, 128).abs().amax(-1) / 448.0)
+    want_s = torch.where(want_s > 0, want_s, torch.ones_like(want_s))
+    assert torch.allclose(xs, want_s, rtol=1e-6)
+    xd = xq.view(torch.float8_e4m3fn).float().view(M, kb, 128) * xs[:, :, None]
+    assert (xd.view(M, -1)[:, :K] - x.float()).abs().max().item() <= 0.07 * x.float().abs().max().item()
+    nb = (N + 127) // 128
+    wd = torch.zeros(nb * 128, kb * 128, device=DEV)
+    wd[:N] = wq.view(torch.float8_e4m3fn).float()
+    wd = (wd.view(nb, 128, kb, 128) * ws[:, None, :, None]).view(nb * 128, kb * 128)[:N]
+    want = xd.view(M, -1) @ wd.t()
+    res = rnd(M, N, seed=3)
+    for r in (None, res):
+        got = ops.linear_fp8_block(x, wq, ws, res=r).float()
+        ref = want + (r.float() if r is not None else 0)
+        assert (got - ref).abs().max().item() < 1e-2 * ref.abs().max().item() + 1e-2
+    # and close to the unquantised product (quantisation noise only)
+    full = x.float() @ w.float().t()
+    rel = (want - full).norm() / full.norm()
+    assert rel < 0.06
+    assert ops.status() == 0
