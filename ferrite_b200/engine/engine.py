@@ -55,6 +55,12 @@ class Engine:
             for k in list(weights.keys()):
                 if k.split(".")[-1] in big and weights[k].dim() == 2 and weights[k].shape[1] % 32 == 0:
                     weights[k] = quantize_weight(weights[k], "nvfp4", keep_dense=True, dense_dtype=self.dtype)
+        elif self.ecfg.weight_dtype == "fp8-block":
+            from ..ops.qweight import quantize_weight
+            big = ("in_proj", "out_proj", "gate_up", "down")
+            for k in list(weights.keys()):
+                if k.split(".")[-1] in big and weights[k].dim() == 2:
+                    weights[k] = quantize_weight(weights[k], "fp8b", keep_dense=True, dense_dtype=self.dtype)
         elif self.ecfg.weight_dtype != "bf16":
             raise ValueError(f"weight_dtype {self.ecfg.weight_dtype!r} is not wired into the engine yet")
         self.cfg = cfg.shard(world)

@@ -82,6 +82,16 @@ class CudaOps:
         return s
 
     def linear(self, x, w, norm_w=None, eps=1e-6, res=None, swiglu=False, out_f32=False, out=None):
+        if isinstance(w, QWeight) and w.kind == "fp8b":
+            # block-scaled e4m3: prompt-sized steps multiply the codes on the f8f6f4 tensor path (activations quantised
+            # per 1 x 128 block on the fly); few-row steps stream the dequantised copy through the bf16 row kernels
+            if x.shape[0] > self.mma_gemv_rows[1] and not out_f32 and out is None:
+                if norm_w is not None:
+                    x, _ = self.rmsnorm(x, norm_w, eps, True)
+                if swiglu:
+                    return self.silu_mul(self.linear_fp8_block(x, w.fp8_codes, w.fp8_scales))
+                return self.linear_fp8_block(x, w.fp8_codes, w.fp8_scales, res=res)
+            w = w.dense
         if isinstance(w, QWeight):
             M = x.shape[0]
             N = w.rows // 2 if swiglu else w.rows

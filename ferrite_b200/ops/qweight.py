@@ -17,7 +17,7 @@ from ..formats import nvfp4
 
 @dataclass
 class QWeight:
-    kind: str                      # "nvfp4"
+    kind: str                      # "nvfp4" | "fp8b" (e4m3, 128 x 128 blocks)
     rows: int
     cols: int
     packed: torch.Tensor           # uint8 [rows, cols/2]
@@ -25,6 +25,8 @@ class QWeight:
     global_scale: float
     dense: Optional[torch.Tensor]  # dequantised copy (activation dtype) for the many-row path
     mma_scales: Optional[torch.Tensor] = None
+    fp8_codes: Optional[torch.Tensor] = None     # "fp8b": uint8 [rows, ceil(cols/128)*128]
+    fp8_scales: Optional[torch.Tensor] = None    # "fp8b": fp32 [ceil(rows/128), ceil(cols/128)]
 
     @property
     def shape(self):
@@ -36,8 +38,23 @@ class QWeight:
 
 def quantize_weight(w: torch.Tensor, kind: str = "nvfp4", keep_dense: bool = True, dense_dtype=None,
                     mma: bool = True) -> QWeight:
-    assert kind == "nvfp4"
     rows, cols = w.shape
+    if kind == "fp8b":
+        # e4m3 codes with one scale per 128 x 128 block (the form block-scaled FP8 checkpoints ship); the dense copy
+        # holds the dequantised values for few-row steps and for the oracle
+        nb, kb = (rows + 127) // 128, (cols + 127) // 128
+        wf = torch.zeros(nb * 128, kb * 128, dtype=torch.float32, device=w.device)
+        wf[:rows, :cols] = w.float()
+        blocks = wf.view(nb, 128, kb, 128)
+        sc = (blocks.abs().amax((1, 3)) / 448.0).clamp_min(1e-12)
+        codes = (blocks / sc[:, None, :, None]).to(torch.float8_e4m3fn)
+        dense = None
+        if keep_dense:
+            dense = (codes.float() * sc[:, None, :, None]).view(nb * 128, kb * 128)[:rows, :cols].to(dense_dtype or w.dtype).contiguous()
+        codes = codes.view(torch.uint8).view(nb * 128, kb * 128)[:rows].contiguous()
+        empty = torch.empty(0, dtype=torch.uint8, device=w.device)
+        return QWeight(kind, rows, cols, empty, empty, 1.0, dense, None, codes, sc.contiguous())
+    assert kind == "nvfp4"
     # quantise in row slabs to bound the fp32 temporaries
     slab = max(1, (64 << 20) // max(1, cols))
     amax = float(w.abs().max())

@@ -151,9 +151,12 @@ class TensorParallel:
     # ---- row-parallel projection + all-reduce + residual --------------------------------------------------
     def linear_allreduce(self, ops, x, w, res):
         M, N = x.shape[0], w.shape[0]
-        if self.fused and M <= 8 and not (hasattr(w, "packed") and getattr(ops, "fp4_act", False)):
+        fp4 = getattr(w, "kind", None) == "nvfp4"
+        if getattr(w, "kind", None) == "fp8b" and M <= 8:
+            w = w.dense                                  # few rows: the dequantised copy through the bf16 row kernels
+        if self.fused and M <= 8 and not (fp4 and getattr(ops, "fp4_act", False)):
             y = torch.empty(M, N, dtype=x.dtype, device=x.device)
-            if hasattr(w, "packed"):
+            if fp4:
                 self.C.gemv_nvfp4_allreduce(self.comm, y, x, w.packed, w.gemv_scales, w.global_scale, res)
             else:
                 self.C.gemv_allreduce(self.comm, y, x, w, res)
