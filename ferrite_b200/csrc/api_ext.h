@@ -51,6 +51,12 @@ int fb_moe_gate_up(void* act, const void* x, const void* w_gu, const int* ids, i
                    int inter, int e_lo, int e_hi, cudaStream_t s);
 int fb_moe_down(float* yp, const void* act, const void* w_down, const int* ids, int pairs, int hidden, int inter,
                 int e_lo, int e_hi, cudaStream_t s);
+// NVFP4 expert weights (moe_fp4.cu): codes [experts][rows][K/2], e4m3 block scales [experts][rows][K/16], one tensor scale
+int fb_moe_gate_up_fp4(void* act, const void* x, const void* wq, const void* ws, float gscale, const int* ids, int pairs,
+                       int top_k, int hidden, int inter, int e_lo, int e_hi, cudaStream_t s);
+int fb_moe_down_fp4(float* yp, const void* act, const void* wq, const void* ws, float gscale, const int* ids, int pairs,
+                    int hidden, int inter, int e_lo, int e_hi, cudaStream_t s);
+int fb_nvfp4_dequant(void* out, const void* wq, const void* ws, float gscale, long elements, cudaStream_t s);
 int fb_moe_combine(void* out, const float* yp, const float* wts, const void* shared, const float* shared_gate,
                    const void* res, int rows, int top_k, int hidden, int out_f32, cudaStream_t s);
 

@@ -150,6 +150,28 @@ void moe_experts(Tensor out, Tensor act, Tensor yp, Tensor x, Tensor w_gu, Tenso
                        hidden, out.scalar_type() == torch::kFloat32 ? 1 : 0, cur_stream()), "moe_combine");
 }
 
+void moe_experts_fp4(Tensor out, Tensor act, Tensor yp, Tensor x, Tensor gu_q, Tensor gu_s, double gu_scale, Tensor dn_q,
+                     Tensor dn_s, double dn_scale, Tensor ids, Tensor wts, int64_t e_lo, int64_t e_hi,
+                     c10::optional<Tensor> shared, c10::optional<Tensor> shared_gate, c10::optional<Tensor> res) {
+  int rows = (int)x.size(0), hidden = (int)x.size(1), top_k = (int)ids.size(1), inter = (int)dn_q.size(2) * 2;
+  int pairs = rows * top_k;
+  TORCH_CHECK(gu_q.size(1) == 2 * inter && gu_q.size(2) * 2 == hidden && dn_q.size(1) == hidden, "moe_experts_fp4: shapes");
+  check(fb_moe_gate_up_fp4(act.data_ptr(), x.data_ptr(), gu_q.data_ptr(), gu_s.data_ptr(), (float)gu_scale,
+                           ids.data_ptr<int>(), pairs, top_k, hidden, inter, (int)e_lo, (int)e_hi, cur_stream()),
+        "moe_gate_up_fp4");
+  check(fb_moe_down_fp4(yp.data_ptr<float>(), act.data_ptr(), dn_q.data_ptr(), dn_s.data_ptr(), (float)dn_scale,
+                        ids.data_ptr<int>(), pairs, hidden, inter, (int)e_lo, (int)e_hi, cur_stream()), "moe_down_fp4");
+  check(fb_moe_combine(out.data_ptr(), yp.data_ptr<float>(), wts.data_ptr<float>(), cptr(shared),
+                       shared_gate.has_value() ? shared_gate->data_ptr<float>() : nullptr, cptr(res), rows, top_k,
+                       hidden, out.scalar_type() == torch::kFloat32 ? 1 : 0, cur_stream()), "moe_combine");
+}
+
+void nvfp4_dequant(Tensor out, Tensor wq, Tensor ws, double gscale) {
+  TORCH_CHECK(out.numel() == wq.numel() * 2 && ws.numel() * 16 == out.numel(), "nvfp4_dequant: sizes");
+  check(fb_nvfp4_dequant(out.data_ptr(), wq.data_ptr(), ws.data_ptr(), (float)gscale, (long)out.numel(), cur_stream()),
+        "nvfp4_dequant");
+}
+
 // Handle to the large symmetric workspace used by the GEMMs with a fused reduce-scatter / all-gather.
 struct BigComm {
   std::vector<const void*> peers;
@@ -323,6 +345,8 @@ void register_ext(pybind11::module_& m) {
   m.def("gemv_nvfp4", &gemv_nvfp4);
   m.def("moe_route", &moe_route);
   m.def("moe_experts", &moe_experts);
+  m.def("moe_experts_fp4", &moe_experts_fp4);
+  m.def("nvfp4_dequant", &nvfp4_dequant);
   m.def("nvfp4_sf_bytes", &nvfp4_sf_bytes);
   m.def("quant_nvfp4", &quant_nvfp4);
   m.def("gemm_nvfp4_workspace_bytes", &gemm_nvfp4_workspace_bytes);

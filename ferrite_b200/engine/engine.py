@@ -50,11 +50,15 @@ class Engine:
         weights = {k: (v.to(self.device) if v.dtype == torch.float32 and k.endswith(("A_log", "dt_bias", "router_bias"))
                        else v.to(self.device, self.dtype)) for k, v in weights.items()}
         if self.ecfg.weight_dtype in ("nvfp4", "nvfp4-a16"):
-            from ..ops.qweight import quantize_weight
+            from ..ops.qweight import quantize_experts, quantize_weight
             big = ("in_proj", "out_proj", "gate_up", "down", "lm_head")
             for k in list(weights.keys()):
                 if k.split(".")[-1] in big and weights[k].dim() == 2 and weights[k].shape[1] % 32 == 0:
                     weights[k] = quantize_weight(weights[k], "nvfp4", keep_dense=True, dense_dtype=self.dtype)
+                elif k.split(".")[-1] in ("experts_gate_up", "experts_down") and weights[k].shape[2] % 16 == 0:
+                    # routed experts: 4-bit only (no dense copy: they are most of an MoE model's bytes); decode rows
+                    # stream the codes, prompt-sized steps dequantise one layer's stack at a time into a shared scratch
+                    weights[k] = quantize_experts(weights[k])
         elif self.ecfg.weight_dtype == "fp8-block":
             from ..ops.qweight import quantize_weight
             big = ("in_proj", "out_proj", "gate_up", "down")

@@ -374,7 +374,8 @@ class Executor:
             shared = row(col(x, w[p + "shared_gate_up"], w[p + "post_norm"], swiglu=True), w[p + "shared_down"], None)
             if c.router == "softmax":
                 sgate = ops.linear(h, w[p + "shared_gate"], out_f32=True)
-        return self.ep.moe(ops, h, ids, wts, w[p + "experts_gate_up"], w[p + "experts_down"], shared, sgate, x)
+        return self.ep.moe(ops, h, ids, wts, ops.experts_dense(w[p + "experts_gate_up"], 0),
+                           ops.experts_dense(w[p + "experts_down"], 1), shared, sgate, x)
 
     def _moe_ffn(self, x, i):
         """Routed experts + shared expert. Under expert parallelism a rank computes the pairs of the experts it owns
@@ -397,7 +398,8 @@ class Executor:
         e_lo, e_hi = rank * per, (rank + 1) * per
         if world == 1:
             if self.ep is not None and h.shape[0] > getattr(ops, "moe_pair_rows", 1 << 30):
-                return self.ep.moe(ops, h, ids, wts, w[p + "experts_gate_up"], w[p + "experts_down"], shared, sgate, x)
+                return self.ep.moe(ops, h, ids, wts, ops.experts_dense(w[p + "experts_gate_up"], 0),
+                                   ops.experts_dense(w[p + "experts_down"], 1), shared, sgate, x)
             return ops.moe_experts(h, ids, wts, w[p + "experts_gate_up"], w[p + "experts_down"], e_lo, e_hi, shared, sgate, x)
         part = ops.moe_experts(h, ids, wts, w[p + "experts_gate_up"], w[p + "experts_down"], e_lo, e_hi, shared, sgate, None)
         return self.tp.allreduce_rows(ops, part, x)

@@ -15,7 +15,7 @@ import os
 import torch
 
 from .._ext import load
-from .qweight import QWeight
+from .qweight import ExpertsFP4, QWeight
 
 GEMV_MAX_ROWS = 8
 MOE_PAIR_ROWS = 64     # up to this many rows (the largest graph-captured step) the experts run as per-pair GEMVs,
@@ -41,6 +41,7 @@ class CudaOps:
         self.attn_tc = os.environ.get("FB_ATTN_TC", "1") != "0"     # prompt attention on tcgen05 (0: mma.sync kernel)
         self._gdn_scratch = None
         self._tree_scratch = None
+        self._expert_scratch = {}
         self._kv_scratch = None
         self.fp4_act = False                # NVFP4 weights: quantise activations too and use the tcgen05 GEMM
         self._sf_pool = {}
@@ -263,6 +264,19 @@ class CudaOps:
     def moe_experts(self, h, ids, wts, w_gu, w_down, e_lo, e_hi, shared=None, shared_gate=None, res=None, out_f32=False):
         T, K = ids.shape
         H, inter = h.shape[1], w_down.shape[2]
+        if isinstance(w_gu, ExpertsFP4):
+            if T > self.moe_pair_rows:
+                w_gu, w_down = self.experts_dense(w_gu, 0), self.experts_dense(w_down, 1)
+            else:
+                # decode rows stream the 4-bit expert rows directly
+                act = torch.empty(T * K, inter, dtype=self.dtype, device=self.device)
+                yp = torch.empty(T * K, H, dtype=torch.float32, device=self.device)
+                out = torch.empty(T, H, dtype=torch.float32 if out_f32 else self.dtype, device=self.device)
+                self.launches += 3
+                self.C.moe_experts_fp4(out, act, yp, h, w_gu.packed, w_gu.scales, w_gu.global_scale, w_down.packed,
+                                       w_down.scales, w_down.global_scale, ids, wts, e_lo, e_hi, shared,
+                                       None if shared_gate is None else shared_gate.reshape(-1).float().contiguous(), res)
+                return out
         if T > self.moe_pair_rows:
             return self._moe_grouped(h, ids, wts, w_gu, w_down, e_lo, e_hi, shared, shared_gate, res, out_f32)
         act = torch.empty(T * K, inter, dtype=self.dtype, device=self.device)
@@ -271,6 +285,21 @@ class CudaOps:
         self.launches += 3
         self.C.moe_experts(out, act, yp, h, w_gu, w_down, ids, wts, e_lo, e_hi, shared,
                            None if shared_gate is None else shared_gate.reshape(-1).float().contiguous(), res)
+        return out
+
+    def experts_dense(self, w, which: int):
+        """bf16 copy of an NVFP4 expert stack in a scratch that all layers share (`which`: 0 gate/up, 1 down): the
+        grouped tensor-core GEMM of prompt-sized steps reads it; the next layer's call overwrites it."""
+        if not isinstance(w, ExpertsFP4):
+            return w
+        e, r, k = w.shape
+        buf = self._expert_scratch.get(which)
+        if buf is None or buf.numel() < e * r * k:
+            buf = torch.empty(e * r * k, dtype=self.dtype, device=self.device)
+            self._expert_scratch[which] = buf
+        out = buf[:e * r * k].view(e, r, k)
+        self.launches += 1
+        self.C.nvfp4_dequant(out, w.packed, w.scales, w.global_scale)
         return out
 
     def _moe_grouped(self, h, ids, wts, w_gu, w_down, e_lo, e_hi, shared, shared_gate, res, out_f32):

@@ -70,3 +70,41 @@ def quantize_weight(w: torch.Tensor, kind: str = "nvfp4", keep_dense: bool = Tru
     return QWeight(kind, rows, cols, torch.cat(packed, 0).contiguous(), nvfp4.tile_scales_gemv(sc), gs,
                    torch.cat(dense, 0).contiguous() if keep_dense else None,
                    nvfp4.tile_scales_mma(sc).contiguous() if mma and cols % 64 == 0 else None)
+
+
+@dataclass
+class ExpertsFP4:
+    """Stacked expert matrices [experts, rows, cols] in NVFP4: `packed` uint8 [E, rows, cols/2] (low nibble = even
+    element), `scales` uint8 [E, rows, cols/16] holding e4m3 bits, one `global_scale` for the whole stack. Decode rows
+    stream this form (`csrc/moe_fp4.cu`); prompt-sized steps dequantise it into a bf16 scratch for the grouped GEMM."""
+    packed: torch.Tensor
+    scales: torch.Tensor
+    global_scale: float
+
+    @property
+    def shape(self):
+        e, r, kb = self.packed.shape
+        return (e, r, kb * 2)
+
+    def dequantize(self, dtype=torch.float32) -> torch.Tensor:
+        e, r, k = self.shape
+        lo = nvfp4.e2m1_to_float(self.packed & 0xF)
+        hi = nvfp4.e2m1_to_float(self.packed >> 4)
+        w = torch.stack([lo, hi], -1).reshape(e, r, k)
+        sc = self.scales.view(torch.float8_e4m3fn).float().repeat_interleave(nvfp4.BLOCK, 2)
+        return (w * sc * self.global_scale).to(dtype)
+
+
+def quantize_experts(w: torch.Tensor) -> ExpertsFP4:
+    """[experts, rows, cols] -> NVFP4 with one tensor scale shared by all experts (expert by expert, to bound the
+    fp32 temporaries)."""
+    e, r, k = w.shape
+    amax = float(w.abs().max())
+    gs = amax / (6.0 * 448.0) if amax > 0 else 1.0
+    packed = torch.empty(e, r, k // 2, dtype=torch.uint8, device=w.device)
+    scales = torch.empty(e, r, k // nvfp4.BLOCK, dtype=torch.uint8, device=w.device)
+    for i in range(e):
+        q = nvfp4.quantize(w[i], global_scale=gs)
+        packed[i] = q.packed
+        scales[i] = q.scales.view(torch.uint8)
+    return ExpertsFP4(packed, scales, gs)

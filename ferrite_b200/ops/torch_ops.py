@@ -285,7 +285,12 @@ class TorchOps:
         idx, w = route(c, logits.float().cpu(), None if bias is None else bias.cpu())
         return idx.to(torch.int32).to(logits.device), w.float().to(logits.device)
 
+    def experts_dense(self, w, which: int):
+        from .qweight import ExpertsFP4
+        return w.dequantize(torch.float32) if isinstance(w, ExpertsFP4) else w
+
     def moe_experts(self, h, ids, wts, w_gu, w_down, e_lo, e_hi, shared=None, shared_gate=None, res=None, out_f32=False):
+        w_gu, w_down = self.experts_dense(w_gu, 0), self.experts_dense(w_down, 1)
         T, K = ids.shape
         out = torch.zeros(T, h.shape[1], dtype=torch.float32, device=h.device)
         hf = h.float()

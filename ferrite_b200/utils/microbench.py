@@ -199,6 +199,16 @@ def main():
         distinct = int(ids.unique().numel())
         report(f"moe route+experts rows{rows} (distinct experts {distinct})", ms, distinct * 3 * H * I * 2,
                2.0 * rows * K * 3 * H * I)
+        if a.fp4:
+            from ..ops.qweight import quantize_experts
+            q_gu, q_dn = quantize_experts(w_gu), quantize_experts(w_dn)
+
+            def fn4():
+                ids, wts = ops.moe_route(logits, None, 0, K, 1, 1, 1.0)
+                ops.moe_experts(h, ids, wts, q_gu, q_dn, 0, E, None, None, res)
+            ms4 = t.run(fn4)
+            report(f"moe fp4 route+experts rows{rows} (distinct experts {distinct})", ms4,
+                   distinct * 3 * H * I * 9 // 16, 2.0 * rows * K * 3 * H * I)
 
 
 if __name__ == "__main__":

@@ -126,3 +126,52 @@ def test_moe_80b_widths_few_layers(ext):
                                     reduction="batchmean").item()
     assert kl < 2e-2, kl
     assert eng.ex.ep is not None and eng.ex.ep.calls > 0
+
+
+@pytest.mark.parametrize("T", [1, 4, 16, 48])
+@pytest.mark.parametrize("ep", [False, True])
+def test_experts_nvfp4(ops, T, ep, monkeypatch):
+    """NVFP4 expert stacks: decode rows through the 4-bit pair GEMVs, prompt-sized batches through the dequantiser and
+    the grouped GEMM; both against fp32 math on the dequantised weights. 80B-A3B widths (hidden 2048, expert FFN 512)."""
+    from ferrite_b200.ops.qweight import quantize_experts
+    monkeypatch.setattr(ops, "moe_pair_rows", 16)
+    E, K, H, I = 16, 4, 2048, 512
+    tops = TorchOps(DEV, torch.float32)
+    h = rnd(T, H, seed=1)
+    w_gu, w_dn = rnd(E, 2 * I, H, scale=0.05, seed=2), rnd(E, H, I, scale=0.05, seed=3)
+    g = torch.Generator().manual_seed(T)
+    ids = torch.stack([torch.randperm(E, generator=g)[:K] for _ in range(T)]).to(torch.int32).to(DEV)
+    wts = torch.rand(T, K, generator=g).to(DEV)
+    shared, sgate, res = rnd(T, H, seed=4), rnd(T, 1, seed=5, dtype=torch.float32), rnd(T, H, seed=6)
+    e_lo, e_hi = (8, 16) if ep else (0, 16)
+    q_gu, q_dn = quantize_experts(w_gu[e_lo:e_hi].contiguous()), quantize_experts(w_dn[e_lo:e_hi].contiguous())
+    dense = ops.experts_dense(q_gu, 0)
+    assert torch.equal(dense.float(), q_gu.dequantize(torch.bfloat16).float())          # the GPU dequantiser, bit for bit
+    got = ops.moe_experts(h, ids, wts, q_gu, q_dn, e_lo, e_hi, shared, sgate, res)
+    want = tops.moe_experts(h, ids, wts, q_gu, q_dn, e_lo, e_hi, shared, sgate, res)
+    err = (got.float() - want.float()).abs().max().item()
+    assert err < 3e-2 * max(1.0, want.abs().max().item()), err
+
+
+def test_moe_engine_nvfp4_experts(ext):
+    """The MoE engine with `weight_dtype="nvfp4-a16"`: routed experts are held in NVFP4 only (no dense copy); prompt and
+    decode steps agree with the CPU engine quantised the same way."""
+    from ferrite_b200.engine.engine import Engine
+    from ferrite_b200.engine.executor import Segment
+    from ferrite_b200.models.weights import init_weights
+    from ferrite_b200.ops.qweight import ExpertsFP4
+    cfg = dataclasses.replace(tiny_hybrid(), n_experts=32, top_k=4, expert_inter=64, n_shared=1)
+    w = init_weights(cfg, seed=0)
+    ecfg = EngineConfig(n_slots=2, max_ctx=128, weight_dtype="nvfp4-a16")
+    ref = Engine(cfg, w, ecfg, device="cpu")
+    p = torch.randint(0, cfg.vocab, (88,), generator=torch.Generator().manual_seed(1)).tolist()
+    want, _, _ = ref.forward([Segment(0, 0, p, "all")])
+    eng = Engine(cfg, w, ecfg, device=DEV)
+    assert isinstance(eng.ex.w["l0.experts_down"], ExpertsFP4)
+    got, _, _ = eng.forward([Segment(0, 0, p[:80], "all")], greedy=False)
+    tail = [eng.forward([Segment(0, 80 + i, [p[80 + i]], "last")], greedy=False)[0].clone() for i in range(8)]
+    got = torch.cat([got] + tail).float().cpu()
+    kl = torch.nn.functional.kl_div(torch.log_softmax(got, -1), torch.log_softmax(want.float(), -1), log_target=True,
+                                    reduction="batchmean").item()
+    assert kl < 2e-2, kl
+    eng.check()
