@@ -16,7 +16,7 @@ namespace fb {
 // ---------------------------------------------------------------------------------------------------
 // attn-prep. One CTA per row, one warp per head (q heads first, then kv heads). The fused projection row is
 // [per q head: q(hd) | gate(hd)] [k heads] [v heads].
-template <int HD, bool KV8>
+template <int HD, int KVM>
 __global__ void attn_prep_kernel(__nv_bfloat16* __restrict__ q_out, void* __restrict__ k_cache_v,
                                  void* __restrict__ v_cache_v, float* __restrict__ kv_scale,
                                  const __nv_bfloat16* __restrict__ proj,
@@ -76,7 +76,32 @@ __global__ void attn_prep_kernel(__nv_bfloat16* __restrict__ q_out, void* __rest
     const size_t tok = ((size_t)blk * kv_block + (cpos % kv_block)) * nkv + kvh;
     const size_t off = tok * HD;
     const __nv_bfloat16* vsrc = proj + (size_t)row * proj_stride + (size_t)nq * qw + (size_t)(nkv + kvh) * HD;
-    if (KV8) {
+    if (KVM == 2) {
+      // 4-bit codes (value = (code - 8) * scale) with one fp32 scale per 32 elements: scales of a (token, kv head) row
+      // are [K groups | V groups]
+      constexpr int NG = HD / 32, GL = 32 / EPL;                 // groups per row, lanes per group
+      unsigned char* kc4 = reinterpret_cast<unsigned char*>(k_cache_v);
+      unsigned char* vc4 = reinterpret_cast<unsigned char*>(v_cache_v);
+      float vv[EPL], ka = 0.f, va = 0.f;
+#pragma unroll
+      for (int j = 0; j < EPL; ++j) { vv[j] = bf2f(vsrc[lane * EPL + j]); ka = fmaxf(ka, fabsf(v[j])); va = fmaxf(va, fabsf(vv[j])); }
+#pragma unroll
+      for (int o2 = GL / 2; o2 > 0; o2 >>= 1) {
+        ka = fmaxf(ka, __shfl_xor_sync(0xffffffffu, ka, o2));
+        va = fmaxf(va, __shfl_xor_sync(0xffffffffu, va, o2));
+      }
+      const float ks = ka > 0.f ? ka / 7.f : 1.f, vs = va > 0.f ? va / 7.f : 1.f;
+      auto code = [](float x, float sc) { return (uint32_t)(min(7, max(-8, __float2int_rn(x / sc))) + 8); };
+#pragma unroll
+      for (int j = 0; j < EPL; j += 2) {
+        kc4[(off + lane * EPL + j) / 2] = (unsigned char)(code(v[j], ks) | (code(v[j + 1], ks) << 4));
+        vc4[(off + lane * EPL + j) / 2] = (unsigned char)(code(vv[j], vs) | (code(vv[j + 1], vs) << 4));
+      }
+      if (lane % GL == 0) {
+        kv_scale[tok * 2 * NG + lane / GL] = ks;
+        kv_scale[tok * 2 * NG + NG + lane / GL] = vs;
+      }
+    } else if (KVM == 1) {
       // e4m3 codes with one fp32 scale per (token, kv head) for K and for V
       unsigned char* kc8 = reinterpret_cast<unsigned char*>(k_cache_v);
       unsigned char* vc8 = reinterpret_cast<unsigned char*>(v_cache_v);
@@ -121,7 +146,7 @@ __device__ __forceinline__ void e4m3x8_to_float(uint2 raw, float* f) {
   }
 }
 
-template <int HD, int G, bool KV8>
+template <int HD, int G, int KVM>
 __global__ void __launch_bounds__(ATT_WARPS * 32)
 attn_decode_kernel(float* __restrict__ o_part, float* __restrict__ ml_part, const __nv_bfloat16* __restrict__ q,
                    const void* __restrict__ k_cache_v, const void* __restrict__ v_cache_v,
@@ -180,7 +205,12 @@ attn_decode_kernel(float* __restrict__ o_part, float* __restrict__ ml_part, cons
         const int blk = bt[t / kv_block];
         const size_t tok = ((size_t)blk * kv_block + (t % kv_block)) * nkv + kvh;
         const size_t off = tok * HD + sub * 8;
-        if (KV8) {
+        if (KVM == 2) {
+          constexpr int NG = HD / 32;
+          kraw[u] = make_uint4(__ldg(reinterpret_cast<const unsigned int*>(reinterpret_cast<const unsigned char*>(k_cache_v) + off / 2)), 0, 0, 0);
+          vraw[u] = make_uint4(__ldg(reinterpret_cast<const unsigned int*>(reinterpret_cast<const unsigned char*>(v_cache_v) + off / 2)), 0, 0, 0);
+          sc2[u] = make_float2(kv_scale[tok * 2 * NG + sub / 4], kv_scale[tok * 2 * NG + NG + sub / 4]);
+        } else if (KVM == 1) {
           const uint2 k8 = ldg_stream8(reinterpret_cast<const unsigned char*>(k_cache_v) + off);
           const uint2 v8 = ldg_stream8(reinterpret_cast<const unsigned char*>(v_cache_v) + off);
           kraw[u] = make_uint4(k8.x, k8.y, 0, 0);
@@ -197,7 +227,13 @@ attn_decode_kernel(float* __restrict__ o_part, float* __restrict__ ml_part, cons
       const bool vis = visb[u];
       uint32_t ku[4] = {kraw[u].x, kraw[u].y, kraw[u].z, kraw[u].w}, vu[4] = {vraw[u].x, vraw[u].y, vraw[u].z, vraw[u].w};
       float kf[8], vf[8];
-      if (KV8) {
+      if (KVM == 2) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          kf[j] = vis ? (float)((int)((ku[0] >> (4 * j)) & 15u) - 8) * sc2[u].x : 0.f;
+          vf[j] = vis ? (float)((int)((vu[0] >> (4 * j)) & 15u) - 8) * sc2[u].y : 0.f;
+        }
+      } else if (KVM == 1) {
         e4m3x8_to_float(make_uint2(ku[0], ku[1]), kf);
         e4m3x8_to_float(make_uint2(vu[0], vu[1]), vf);
         if (vis) {
@@ -318,7 +354,7 @@ __global__ void kv_dequant_kernel(__nv_bfloat16* __restrict__ k_out, __nv_bfloat
                                   const float* __restrict__ kv_scale, const int* __restrict__ seg_slot,
                                   const int* __restrict__ seg_pos0, const int* __restrict__ seg_nrows,
                                   const int* __restrict__ block_table, int max_blocks, int kv_block, int nkv, int hd,
-                                  int scratch_tokens_per_slot) {
+                                  int scratch_tokens_per_slot, int bits) {
   const int t = blockIdx.x, kvh = blockIdx.y, seg = blockIdx.z;
   const int n = seg_nrows[seg];
   if (n <= 0 || t >= seg_pos0[seg] + n) return;
@@ -326,25 +362,38 @@ __global__ void kv_dequant_kernel(__nv_bfloat16* __restrict__ k_out, __nv_bfloat
   const int blk = block_table[(size_t)slot * max_blocks + t / kv_block];
   if (blk < 0) return;
   const size_t tok = ((size_t)blk * kv_block + (t % kv_block)) * nkv + kvh;
-  const float ks = kv_scale[tok * 2], vs = kv_scale[tok * 2 + 1];
   const size_t dst = (((size_t)slot * scratch_tokens_per_slot + t) * nkv + kvh) * hd + threadIdx.x * 8;
-  float kf[8], vf[8];
-  e4m3x8_to_float(*reinterpret_cast<const uint2*>(k8 + tok * hd + threadIdx.x * 8), kf);
-  e4m3x8_to_float(*reinterpret_cast<const uint2*>(v8 + tok * hd + threadIdx.x * 8), vf);
+  float kf[8], vf[8], ks, vs;
+  if (bits == 4) {
+    const int ng = hd / 32;
+    ks = kv_scale[tok * 2 * ng + threadIdx.x / 4];
+    vs = kv_scale[tok * 2 * ng + ng + threadIdx.x / 4];
+    const uint32_t kw = *reinterpret_cast<const uint32_t*>(k8 + (tok * hd + threadIdx.x * 8) / 2);
+    const uint32_t vw = *reinterpret_cast<const uint32_t*>(v8 + (tok * hd + threadIdx.x * 8) / 2);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      kf[j] = (float)((int)((kw >> (4 * j)) & 15u) - 8);
+      vf[j] = (float)((int)((vw >> (4 * j)) & 15u) - 8);
+    }
+  } else {
+    ks = kv_scale[tok * 2]; vs = kv_scale[tok * 2 + 1];
+    e4m3x8_to_float(*reinterpret_cast<const uint2*>(k8 + tok * hd + threadIdx.x * 8), kf);
+    e4m3x8_to_float(*reinterpret_cast<const uint2*>(v8 + tok * hd + threadIdx.x * 8), vf);
+  }
   *reinterpret_cast<uint4*>(k_out + dst) = make_uint4(pack_bf2(kf[0] * ks, kf[1] * ks), pack_bf2(kf[2] * ks, kf[3] * ks),
                                                       pack_bf2(kf[4] * ks, kf[5] * ks), pack_bf2(kf[6] * ks, kf[7] * ks));
   *reinterpret_cast<uint4*>(v_out + dst) = make_uint4(pack_bf2(vf[0] * vs, vf[1] * vs), pack_bf2(vf[2] * vs, vf[3] * vs),
                                                       pack_bf2(vf[4] * vs, vf[5] * vs), pack_bf2(vf[6] * vs, vf[7] * vs));
 }
 
-template <int HD, bool KV8>
+template <int HD, int KVM>
 static int launch_decode(int G, dim3 grid, size_t smem, cudaStream_t s, float* o_part, float* ml_part, const void* q,
                          const void* kc, const void* vc, const float* kv_scale, const int* row_slot, const int* row_kvlen,
                          const int* row_base, const unsigned long long* row_mask, const int* bt, int max_blocks,
                          int kv_block, int nq, int nkv, int nsplit, float scale_log2) {
 #define FB_LAUNCH_G(GV)                                                                                          \
   case GV: {                                                                                                     \
-    auto kern = attn_decode_kernel<HD, GV, KV8>;                                                                 \
+    auto kern = attn_decode_kernel<HD, GV, KVM>;                                                                 \
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);    \
     launch_pdl(kern, dim3(grid), dim3(ATT_WARPS * 32), (size_t)(smem), s, o_part, ml_part, (const __nv_bfloat16*)q, kc,  \
                                             vc, kv_scale, row_slot, row_kvlen, row_base, row_mask,               \
@@ -366,7 +415,8 @@ using namespace fb;
 static int attn_prep_impl(void* q_out, void* k_cache, void* v_cache, float* kv_scale, const void* proj, long proj_stride,
                           const void* q_norm, const void* k_norm, const float* inv_freq, const int* row_slot,
                           const int* row_pos, const int* row_cpos, const int* block_table, int max_blocks, int kv_block,
-                          int rows, int nq, int nkv, int hd, int rot, int gated, float eps, int* status, cudaStream_t s) {
+                          int rows, int nq, int nkv, int hd, int rot, int gated, float eps, int* status, cudaStream_t s,
+                          int bits = 8) {
   if (rows <= 0) return 0;
   int threads = 32 * (nq + nkv);
   if (threads > 1024) return -1;
@@ -377,10 +427,12 @@ static int attn_prep_impl(void* q_out, void* k_cache, void* v_cache, float* kv_s
       kv_scale, (const __nv_bfloat16*)proj, proj_stride, (const __nv_bfloat16*)q_norm,                            \
       (const __nv_bfloat16*)k_norm, inv_freq, row_slot, row_pos, row_cpos, block_table, max_blocks, kv_block, nq, nkv, rot, \
       gated, eps, status)
-  if (kv_scale) {
-    if (hd == 256) FB_PREP(256, true); else if (hd == 128) FB_PREP(128, true); else if (hd == 64) FB_PREP(64, true); else return -2;
+  if (kv_scale && bits == 4) {
+    if (hd == 256) FB_PREP(256, 2); else if (hd == 128) FB_PREP(128, 2); else if (hd == 64) FB_PREP(64, 2); else return -2;
+  } else if (kv_scale) {
+    if (hd == 256) FB_PREP(256, 1); else if (hd == 128) FB_PREP(128, 1); else if (hd == 64) FB_PREP(64, 1); else return -2;
   } else {
-    if (hd == 256) FB_PREP(256, false); else if (hd == 128) FB_PREP(128, false); else if (hd == 64) FB_PREP(64, false); else return -2;
+    if (hd == 256) FB_PREP(256, 0); else if (hd == 128) FB_PREP(128, 0); else if (hd == 64) FB_PREP(64, 0); else return -2;
   }
 #undef FB_PREP
   return (int)cudaGetLastError();
@@ -390,7 +442,7 @@ static int attn_decode_impl(void* out, float* o_part, float* ml_part, const void
                             const void* v_cache, const float* kv_scale, const void* proj, long proj_stride,
                             const int* row_slot, const int* row_kvlen, const int* row_base,
                             const unsigned long long* row_mask, const int* block_table, int max_blocks, int kv_block,
-                            int rows, int nq, int nkv, int hd, int nsplit, int gated, cudaStream_t s) {
+                            int rows, int nq, int nkv, int hd, int nsplit, int gated, cudaStream_t s, int bits = 8) {
   if (rows <= 0) return 0;
   if (nq % nkv) return -1;
   int G = nq / nkv;
@@ -399,10 +451,12 @@ static int attn_decode_impl(void* out, float* o_part, float* ml_part, const void
   float scale_log2 = 1.4426950408889634f / sqrtf((float)hd);
   int rc;
 #define FB_DEC(HDV, K8) rc = launch_decode<HDV, K8>(G, grid, smem, s, o_part, ml_part, q, k_cache, v_cache, kv_scale, row_slot, row_kvlen, row_base, row_mask, block_table, max_blocks, kv_block, nq, nkv, nsplit, scale_log2)
-  if (kv_scale) {
-    if (hd == 256) FB_DEC(256, true); else if (hd == 128) FB_DEC(128, true); else if (hd == 64) FB_DEC(64, true); else return -2;
+  if (kv_scale && bits == 4) {
+    if (hd == 256) FB_DEC(256, 2); else if (hd == 128) FB_DEC(128, 2); else if (hd == 64) FB_DEC(64, 2); else return -2;
+  } else if (kv_scale) {
+    if (hd == 256) FB_DEC(256, 1); else if (hd == 128) FB_DEC(128, 1); else if (hd == 64) FB_DEC(64, 1); else return -2;
   } else {
-    if (hd == 256) FB_DEC(256, false); else if (hd == 128) FB_DEC(128, false); else if (hd == 64) FB_DEC(64, false); else return -2;
+    if (hd == 256) FB_DEC(256, 0); else if (hd == 128) FB_DEC(128, 0); else if (hd == 64) FB_DEC(64, 0); else return -2;
   }
 #undef FB_DEC
   if (rc) return rc;
@@ -472,7 +526,42 @@ extern "C" int fb_kv_dequant(void* k_out, void* v_out, const void* k_cache8, con
   if (hd % 8 || max_kvlen > scratch_tokens_per_slot) return -1;
   kv_dequant_kernel<<<dim3(max_kvlen, nkv, nseg), hd / 8, 0, s>>>((__nv_bfloat16*)k_out, (__nv_bfloat16*)v_out,
       (const unsigned char*)k_cache8, (const unsigned char*)v_cache8, kv_scale, seg_slot, seg_pos0, seg_nrows, block_table,
-      max_blocks, kv_block, nkv, hd, scratch_tokens_per_slot);
+      max_blocks, kv_block, nkv, hd, scratch_tokens_per_slot, 8);
+  return (int)cudaGetLastError();
+}
+
+// ---- 4-bit KV cache: codes [blocks][kv_block][nkv][hd/2] bytes (low nibble = even element, value = (code - 8) * scale),
+// scales [blocks][kv_block][nkv][2 * hd/32] fp32 (K groups then V groups, one per 32 elements). Counterparts of the
+// reference's `fe_attn_prep_q4`, `fe_attn_vk_q*` and the q4 flash path (`kernels/k-core/src/kvq.rs`).
+extern "C" int fb_attn_prep_q4(void* q_out, void* k_cache4, void* v_cache4, float* kv_scale, const void* proj,
+                               long proj_stride, const void* q_norm, const void* k_norm, const float* inv_freq,
+                               const int* row_slot, const int* row_pos, const int* row_cpos, const int* block_table,
+                               int max_blocks, int kv_block, int rows, int nq, int nkv, int hd, int rot, int gated,
+                               float eps, int* status, cudaStream_t s) {
+  if (!kv_scale) return -4;
+  return attn_prep_impl(q_out, k_cache4, v_cache4, kv_scale, proj, proj_stride, q_norm, k_norm, inv_freq, row_slot, row_pos,
+                        row_cpos, block_table, max_blocks, kv_block, rows, nq, nkv, hd, rot, gated, eps, status, s, 4);
+}
+
+extern "C" int fb_attn_decode_q4(void* out, float* o_part, float* ml_part, const void* q, const void* k_cache4,
+                                 const void* v_cache4, const float* kv_scale, const void* proj, long proj_stride,
+                                 const int* row_slot, const int* row_kvlen, const int* row_base,
+                                 const unsigned long long* row_mask, const int* block_table, int max_blocks,
+                                 int kv_block, int rows, int nq, int nkv, int hd, int nsplit, int gated, cudaStream_t s) {
+  if (!kv_scale) return -4;
+  return attn_decode_impl(out, o_part, ml_part, q, k_cache4, v_cache4, kv_scale, proj, proj_stride, row_slot, row_kvlen,
+                          row_base, row_mask, block_table, max_blocks, kv_block, rows, nq, nkv, hd, nsplit, gated, s, 4);
+}
+
+extern "C" int fb_kv_dequant_q4(void* k_out, void* v_out, const void* k_cache4, const void* v_cache4, const float* kv_scale,
+                                const int* seg_slot, const int* seg_pos0, const int* seg_nrows, const int* block_table,
+                                int max_blocks, int kv_block, int nseg, int max_kvlen, int nkv, int hd,
+                                int scratch_tokens_per_slot, cudaStream_t s) {
+  if (nseg <= 0 || max_kvlen <= 0) return 0;
+  if (hd % 32 || max_kvlen > scratch_tokens_per_slot) return -1;
+  kv_dequant_kernel<<<dim3(max_kvlen, nkv, nseg), hd / 8, 0, s>>>((__nv_bfloat16*)k_out, (__nv_bfloat16*)v_out,
+      (const unsigned char*)k_cache4, (const unsigned char*)v_cache4, kv_scale, seg_slot, seg_pos0, seg_nrows, block_table,
+      max_blocks, kv_block, nkv, hd, scratch_tokens_per_slot, 4);
   return (int)cudaGetLastError();
 }
 

@@ -117,7 +117,8 @@ class Executor:
         n_blocks = ecfg.n_slots * self.max_blocks + (int(ecfg.park_gb * (1 << 30) / max(1, self.kv_block_bytes())) if ecfg.park_gb > 0 else 0)
         self.pool = BlockPool(n_blocks)
         dev, dt = self.device, self.dtype
-        self.kv8 = ecfg.kv_dtype == "fp8"
+        self.kv8 = ecfg.kv_dtype in ("fp8", "int4")          # quantised cache: byte codes + fp32 scales
+        self.kv4 = ecfg.kv_dtype == "int4"
         self.kv_scale: Dict[int, torch.Tensor] = {}
         self.k_cache: Dict[int, torch.Tensor] = {}
         self.v_cache: Dict[int, torch.Tensor] = {}
@@ -127,10 +128,13 @@ class Executor:
             if kind == "attn":
                 # e4m3 cache: byte codes on the GPU (the CPU oracle keeps dequantised values) + K / V scales per row
                 kdt = torch.uint8 if (self.kv8 and dev.type == "cuda") else dt
-                self.k_cache[i] = torch.zeros(n_blocks, ecfg.kv_block, c.n_kv, c.head_dim, dtype=kdt, device=dev)
-                self.v_cache[i] = torch.zeros(n_blocks, ecfg.kv_block, c.n_kv, c.head_dim, dtype=kdt, device=dev)
+                # int4 on the GPU: two codes per byte, one scale per 32 elements (K groups then V groups)
+                hd_store = c.head_dim // 2 if (self.kv4 and dev.type == "cuda") else c.head_dim
+                self.k_cache[i] = torch.zeros(n_blocks, ecfg.kv_block, c.n_kv, hd_store, dtype=kdt, device=dev)
+                self.v_cache[i] = torch.zeros(n_blocks, ecfg.kv_block, c.n_kv, hd_store, dtype=kdt, device=dev)
                 if self.kv8:
-                    self.kv_scale[i] = torch.ones(n_blocks, ecfg.kv_block, c.n_kv, 2, dtype=torch.float32, device=dev)
+                    ns = 2 * (c.head_dim // 32) if self.kv4 else 2
+                    self.kv_scale[i] = torch.ones(n_blocks, ecfg.kv_block, c.n_kv, ns, dtype=torch.float32, device=dev)
             elif kind == "mla":
                 # one latent row [kv_lora | rope] per token; the value cache slot stays empty
                 self.k_cache[i] = torch.zeros(n_blocks, ecfg.kv_block, 1, c.kv_lora + c.rope_head_dim, dtype=dt, device=dev)
@@ -183,6 +187,8 @@ class Executor:
     def kv_block_bytes(self) -> int:
         c, e = self.cfg, self.ecfg
         per = 2 * e.kv_block * c.n_kv * c.head_dim * (1 if e.kv_dtype == "fp8" else 2)
+        if e.kv_dtype == "int4":
+            per = 2 * e.kv_block * c.n_kv * (c.head_dim // 2 + c.head_dim // 32 * 4)
         if c.kv_lora > 0:
             per = e.kv_block * (c.kv_lora + c.rope_head_dim) * 2
         return per * max(1, self.cfg.n_attn)

@@ -97,6 +97,15 @@ class TorchOps:
                 sc = (x.abs().amax(-1, keepdim=True) / 448.0)
                 sc = torch.where(sc > 0, sc, torch.ones_like(sc))
                 return (x / sc).to(torch.float8_e4m3fn).float() * sc
+
+            def fq4(x):
+                # 4-bit cache: groups of 32 elements, scale = amax / 7, codes in -8..7 (round half to even)
+                g = x.reshape(*x.shape[:-1], hd // 32, 32)
+                sc = g.abs().amax(-1, keepdim=True) / 7.0
+                sc = torch.where(sc > 0, sc, torch.ones_like(sc))
+                return (torch.round(g / sc).clamp(-8, 7) * sc).reshape(x.shape)
+            if kv_scale.shape[-1] != 2:
+                fq = fq4
             k, v = fq(k.float()), fq(v.float())
         k_cache[blk, off] = k.to(k_cache.dtype)
         v_cache[blk, off] = v.to(v_cache.dtype)

@@ -148,3 +148,26 @@ def test_op_profiler_counts_calls():
     assert rep["linear"]["calls"] >= 4 * n_layers and rep["linear"]["ms"] > 0
     assert "attention" in rep or "attention_prefill" in rep
     assert eng.ex.profile is None
+
+
+def test_int4_kv_cache_stays_close_to_the_16bit_cache():
+    """4-bit KV cache (groups of 32, scale = amax / 7): next-token distributions stay close to the 16-bit cache, decode
+    rows read what prompt rows wrote, and the page accounting shrinks."""
+    import torch
+    from ferrite_b200.config import EngineConfig, tiny_hybrid
+    from ferrite_b200.engine.engine import Engine
+    from ferrite_b200.engine.executor import Segment
+    from ferrite_b200.models.weights import init_weights
+    cfg = tiny_hybrid()
+    w = init_weights(cfg, seed=0)
+    p = torch.randint(0, cfg.vocab, (70,), generator=torch.Generator().manual_seed(1)).tolist()
+    ref = Engine(cfg, w, EngineConfig(n_slots=1, max_ctx=128), device="cpu")
+    q4 = Engine(cfg, w, EngineConfig(n_slots=1, max_ctx=128, kv_dtype="int4"), device="cpu")
+    assert q4.ex.kv_block_bytes() < ref.ex.kv_block_bytes() / 3
+    a = ref.forward([Segment(0, 0, p, "all")])[0]
+    b1 = q4.forward([Segment(0, 0, p[:40], "all")])[0]
+    b2 = torch.cat([q4.forward([Segment(0, 40 + i, [p[40 + i]], "last")])[0] for i in range(30)])
+    b = torch.cat([b1, b2])
+    kl = torch.nn.functional.kl_div(torch.log_softmax(b, -1), torch.log_softmax(a, -1), log_target=True,
+                                    reduction="batchmean").item()
+    assert kl < 1e-3, kl

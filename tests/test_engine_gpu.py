@@ -212,3 +212,26 @@ def test_fp8_block_engine_matches_dequantised_oracle(ext):
     pa, pb = torch.log_softmax(a[0].float(), -1), torch.log_softmax(b[0].float(), -1)
     assert (pb.exp() * (pb - pa)).sum().item() < 0.05
     eng.check()
+
+
+def test_int4_kv_cache_gpu(ext):
+    """4-bit KV cache on the GPU (quantising attn-prep, decode kernel reading nibbles + group scales, prompt attention
+    over the decoded scratch, a verify tree on top) against the CPU oracle with the same cache quantisation."""
+    cfg = tiny_hybrid()
+    w = init_weights(cfg, seed=0)
+    p = torch.randint(0, cfg.vocab, (120,), generator=torch.Generator().manual_seed(1)).tolist()
+    ref = Engine(cfg, w, EngineConfig(n_slots=2, max_ctx=256, kv_dtype="int4"), device="cpu")
+    want, _, _ = ref.forward([Segment(1, 0, p, "all")])
+    eng = Engine(cfg, w, EngineConfig(n_slots=2, max_ctx=256, kv_dtype="int4"), device="cuda")
+    kc = next(iter(eng.ex.k_cache.values()))
+    assert kc.dtype == torch.uint8 and kc.shape[-1] == cfg.head_dim // 2
+    a, _, _ = eng.forward([Segment(1, 0, p[:64], "all")], greedy=False)
+    b, _, _ = eng.forward([Segment(1, 64, p[64:110], "all")], greedy=False)
+    tail = [eng.forward([Segment(1, 110 + i, [p[110 + i]], "last")], greedy=False)[0].clone() for i in range(10)]
+    got = torch.cat([a.clone(), b.clone()] + tail).float().cpu()
+    kl = torch.nn.functional.kl_div(torch.log_softmax(got, -1), torch.log_softmax(want, -1), log_target=True,
+                                    reduction="batchmean").item()
+    assert kl < 2e-2, kl
+    from ferrite_b200.utils.selftest import tree_test
+    tree_test("cuda", 8e-2, kv_dtype="int4")
+    eng.check()
