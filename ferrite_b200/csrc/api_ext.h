@@ -105,6 +105,12 @@ int fb_mla_attn(void* out, float* o_part, float* ml_part, const void* qabs, cons
 // ---- drafter_ops.cu ----
 int fb_w4_gemv(void* y, const void* x, const void* qweight, const void* scales, const void* biases, const void* res, int M,
                int N, int K, long ldx, long ldy, cudaStream_t s);
+// block-drafter sublayers: grouped dynamic conv over a block, merge of per-rank top-16 lists, candidate selector walk
+int fb_dynconv(void* out, const void* x, const void* coef, long ldc, const void* base, void* res, int rows, int H, int group,
+               int blk, cudaStream_t s);
+int fb_topk16_merge(float* ovals, int* oids, const float* vals, const int* ids, int rows, int W, cudaStream_t s);
+int fb_draft_select(int* out, const float* vals, const int* ids, const void* gate, const void* a_cb, const void* b_cb,
+                    int anchor, int rows, int R, cudaStream_t s);
 int fb_topk16(int* ids, float* vals, const void* logits, long stride, int rows, int vocab, int is_f32, cudaStream_t s);
 
 #ifdef __cplusplus

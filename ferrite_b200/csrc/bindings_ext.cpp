@@ -299,6 +299,21 @@ void w4_gemv(Tensor y, Tensor x, Tensor qweight, Tensor scales, Tensor biases, c
         "w4_gemv");
 }
 
+void dynconv(Tensor out, Tensor x, Tensor coef, Tensor base, c10::optional<Tensor> res, int64_t group, int64_t blk) {
+  check(fb_dynconv(out.data_ptr(), x.data_ptr(), coef.data_ptr(), (long)coef.stride(0), base.data_ptr(), res.has_value() ? res->data_ptr() : nullptr,
+                   (int)x.size(0), (int)x.size(1), (int)group, (int)blk, cur_stream()), "dynconv");
+}
+
+void topk16_merge(Tensor ovals, Tensor oids, Tensor vals, Tensor ids) {
+  check(fb_topk16_merge(ovals.data_ptr<float>(), oids.data_ptr<int>(), vals.data_ptr<float>(), ids.data_ptr<int>(),
+                        (int)vals.size(1), (int)vals.size(0), cur_stream()), "topk16_merge");
+}
+
+void draft_select(Tensor out, Tensor vals, Tensor ids, Tensor gate, Tensor a_cb, Tensor b_cb, int64_t anchor) {
+  check(fb_draft_select(out.data_ptr<int>(), vals.data_ptr<float>(), ids.data_ptr<int>(), gate.data_ptr(), a_cb.data_ptr(),
+                        b_cb.data_ptr(), (int)anchor, (int)vals.size(0), (int)gate.size(1), cur_stream()), "draft_select");
+}
+
 void topk16(Tensor ids, c10::optional<Tensor> vals, Tensor logits) {
   check(fb_topk16(ids.data_ptr<int>(), vals.has_value() ? vals->data_ptr<float>() : nullptr, logits.data_ptr(),
                   (long)logits.stride(0), (int)logits.size(0), (int)logits.size(1),
@@ -310,6 +325,9 @@ void topk16(Tensor ids, c10::optional<Tensor> vals, Tensor logits) {
 void register_ext(pybind11::module_& m) {
   m.def("w4_gemv", &w4_gemv);
   m.def("topk16", &topk16);
+  m.def("dynconv", &dynconv);
+  m.def("topk16_merge", &topk16_merge);
+  m.def("draft_select", &draft_select);
   m.def("mla_prep", &mla_prep);
   m.def("mla_attn", &mla_attn);
   m.def("exl3_had", &exl3_had);

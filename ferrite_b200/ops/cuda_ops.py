@@ -480,6 +480,31 @@ class CudaOps:
         self.C.w4_gemv(y, x, qweight, scales, biases, res)
         return y
 
+    def dynconv(self, x, coef, base, group, blk, res=None):
+        """Grouped dynamic causal conv over draft blocks of `blk` rows: y[t] = (base[0] + c[t][g]) x[t] + (base[1] +
+        c[t][G + g]) x[t-1] (second term only inside a block). `coef` [rows, 2 * H / group] may be a column slice of a
+        wider projection. With `res` the result is added into it in place and `res` is returned."""
+        out = res if res is not None else torch.empty_like(x)
+        self.launches += 1
+        self.C.dynconv(out, x, coef, base, res, group, blk)
+        return out
+
+    def topk16_merge(self, vals, ids):
+        """[W, rows, 16] per-rank top-16 lists (global ids) -> merged ([rows, 16] vals, ids), ties to the lower id."""
+        W, rows, _ = vals.shape
+        ov = torch.empty(rows, 16, dtype=torch.float32, device=self.device)
+        oi = torch.empty(rows, 16, dtype=torch.int32, device=self.device)
+        self.launches += 1
+        self.C.topk16_merge(ov, oi, vals.contiguous(), ids.contiguous())
+        return ov, oi
+
+    def draft_select(self, vals, ids, gate, a_cb, b_cb, anchor):
+        """Candidate selector walk: per drafted row pick argmax_c vals[c] + <A[pred] * gate, B[ids[c]]>, pred chained."""
+        out = torch.empty(vals.shape[0], dtype=torch.int32, device=self.device)
+        self.launches += 1
+        self.C.draft_select(out, vals, ids, gate, a_cb, b_cb, int(anchor))
+        return out
+
     def topk16(self, logits):
         ids = torch.empty(logits.shape[0], 16, dtype=torch.int32, device=self.device)
         vals = torch.empty(logits.shape[0], 16, dtype=torch.float32, device=self.device)

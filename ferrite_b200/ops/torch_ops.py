@@ -320,6 +320,42 @@ class TorchOps:
         return out if out_f32 else out.to(self.dtype)
 
     # ---- selection ---------------------------------------------------------------------------------
+    def dynconv(self, x, coef, base, group, blk, res=None):
+        T, H = x.shape
+        G = H // group
+        xf, cf, bf = x.float(), coef.float(), base.float().view(2, H)
+        w0 = bf[0][None] + cf[:, :G].repeat_interleave(group, 1)
+        w1 = bf[1][None] + cf[:, G:2 * G].repeat_interleave(group, 1)
+        prev = torch.cat([torch.zeros(1, H), xf[:-1]], 0)
+        inside = (torch.arange(T) % blk != 0).float()[:, None]
+        y = w0 * xf + inside * w1 * prev
+        if res is not None:
+            res.copy_((res.float() + y.to(res.dtype).float()).to(res.dtype))
+            return res
+        return y.to(self.dtype)
+
+    def topk16_merge(self, vals, ids):
+        W, rows, _ = vals.shape
+        v = vals.permute(1, 0, 2).reshape(rows, W * 16)
+        i = ids.permute(1, 0, 2).reshape(rows, W * 16)
+        # descending by value, ties to the lower id
+        order = sorted
+        ov = torch.empty(rows, 16)
+        oi = torch.empty(rows, 16, dtype=torch.int32)
+        for r in range(rows):
+            pairs = order(zip(v[r].tolist(), i[r].tolist()), key=lambda p: (-p[0], p[1]))[:16]
+            ov[r] = torch.tensor([p[0] for p in pairs])
+            oi[r] = torch.tensor([p[1] for p in pairs], dtype=torch.int32)
+        return ov, oi
+
+    def draft_select(self, vals, ids, gate, a_cb, b_cb, anchor):
+        out, pred = [], int(anchor)
+        for r in range(vals.shape[0]):
+            sc = vals[r].float() + ((a_cb[pred].float() * gate[r].float())[None] * b_cb[ids[r].long()].float()).sum(-1)
+            pred = int(ids[r][int(sc.argmax())])
+            out.append(pred)
+        return torch.tensor(out, dtype=torch.int32)
+
     def argmax(self, logits):
         lf = logits.float()
         finite = torch.isfinite(lf).all(-1)

@@ -465,3 +465,42 @@ def test_fp8_block_scaled_gemm(ops, M, N, K):
     rel = (want - full).norm() / full.norm()
     assert rel < 0.06
     assert ops.status() == 0
+
+
+def test_drafter_sublayers(ops):
+    """Block-drafter kernels against the host statements: grouped dynamic conv (plain and into a residual, coefficients
+    as a column slice), merge of per-rank top-16 lists (ties to the lower id), candidate selector walk."""
+    from ferrite_b200.ops.torch_ops import TorchOps
+    tops = TorchOps("cpu", torch.float32)
+    T, H, group, blk = 48, 5120, 16, 16
+    G = H // group
+    x = rnd(T, H, seed=1)
+    wide = rnd(T, 4 * G, scale=0.3, seed=2)
+    coef = wide[:, 2 * G:]                                  # one side's two taps out of a wider projection
+    base = rnd(2, H, scale=0.5, seed=3)
+    got = ops.dynconv(x, coef, base, group, blk)
+    want = tops.dynconv(x.cpu(), coef.cpu(), base.cpu(), group, blk)
+    assert (got.float().cpu() - want.float()).abs().max().item() < 2e-2 * max(1.0, want.abs().max().item())
+    res = rnd(T, H, seed=4)
+    want_r = tops.dynconv(x.cpu(), coef.cpu(), base.cpu(), group, blk, res=res.cpu().clone())
+    got_r = ops.dynconv(x, coef, base, group, blk, res=res)
+    assert got_r.data_ptr() == res.data_ptr()
+    assert (got_r.float().cpu() - want_r.float()).abs().max().item() < 3e-2 * max(1.0, want_r.abs().max().item())
+    # top-16 merge over 8 ranks with ties
+    W, rows = 8, 5
+    g = torch.Generator().manual_seed(0)
+    vals = torch.randint(0, 40, (W, rows, 16), generator=g).float().sort(-1, descending=True).values
+    ids = torch.stack([torch.stack([torch.randperm(1000, generator=g)[:16] + 1000 * w for _ in range(rows)]) for w in range(W)])
+    ids = ids.to(torch.int32)
+    ov, oi = ops.topk16_merge(vals.to(DEV), ids.to(DEV))
+    wv, wi = tops.topk16_merge(vals, ids)
+    assert torch.equal(ov.cpu(), wv) and torch.equal(oi.cpu(), wi)
+    # selector walk
+    V, R, n = 3000, 256, 12
+    a_cb, b_cb = rnd(V, R, scale=0.3, seed=5), rnd(V, R, scale=0.3, seed=6)
+    gate = rnd(n, R, seed=7)
+    cv = torch.randn(n, 16, generator=g).to(DEV)
+    ci = torch.stack([torch.randperm(V, generator=g)[:16] for _ in range(n)]).to(torch.int32).to(DEV)
+    got = ops.draft_select(cv, ci, gate, a_cb, b_cb, 17)
+    want = tops.draft_select(cv.cpu(), ci.cpu(), gate.cpu(), a_cb.cpu(), b_cb.cpu(), 17)
+    assert got.cpu().tolist() == want.tolist()
