@@ -260,7 +260,7 @@ __global__ void __launch_bounds__(GM2_WARPS * 32, 2) gemv_mma_kernel(GemvMmaArgs
 }
 
 template <int MT, int RT, bool DUAL>
-static int launch_g2(GemvMmaArgs a, int sm_count, float* ws, long ws_floats, int* counters, int n_counters, cudaStream_t s) {
+static int launch_g2(GemvMmaArgs a, int split, float* ws, long ws_floats, int* counters, int n_counters, cudaStream_t s) {
   static bool done = false;
   if (!done) {
     cudaError_t e = cudaFuncSetAttribute(gemv_mma_kernel<MT, RT, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Gm2<MT>::SMEM);
@@ -268,13 +268,6 @@ static int launch_g2(GemvMmaArgs a, int sm_count, float* ws, long ws_floats, int
     done = true;
   }
   const int tiles = (a.N + 16 * RT - 1) / (16 * RT);
-  // split K until the grid holds several CTAs per resident slot (two per SM), keeping >= 1024 k values per CTA
-  // Measured on B200: a CTA costs a few microseconds of fixed work (staging, reduction, workspace round trip), so
-  // splitting only pays when one wave of CTAs would leave most of a second wave empty AND each half still streams
-  // several hundred KB.
-  int split = 1;
-  const int slots = 2 * sm_count;
-  if (tiles > slots && tiles < slots + slots / 4 && a.K >= 16384) split = 2;
   constexpr long REC = (long)RT * 16 * 8 * MT * (DUAL ? 2 : 1) + 8 * MT;
   if (split > 1 && (!ws || !counters || (long)tiles * split * REC > ws_floats || tiles > n_counters)) split = 1;
   a.split = split;
@@ -283,13 +276,39 @@ static int launch_g2(GemvMmaArgs a, int sm_count, float* ws, long ws_floats, int
   return (int)launch_pdl(gemv_mma_kernel<MT, RT, DUAL>, dim3(tiles, split), dim3(GM2_WARPS * 32), Gm2<MT>::SMEM, s, a);
 }
 
+// Row tiles per CTA (RT x 16 weight rows) and k split. Two CTAs are resident per SM; a CTA first stages its k range of
+// x (8 * MT rows) and then streams its weight rows, so what a launch costs is roughly
+//   (resident slots / slots actually filled, counting a nearly empty last wave as a whole one)
+//   x (1 + (staged x bytes + a fixed per-CTA cost) / weight bytes per CTA).
+// Measured on B200 at N 5120, K 17408 (the 27B down projection, 4 rows): 16-row tiles split in two (640 CTAs, 278 KB of
+// weights against 139 KB of x each) took 70 us, where one row took 52 us on the SIMT kernel; 64-row tiles split in three
+// (240 CTAs, 745 KB against 93 KB) fill one wave.
 template <int MT, bool DUAL>
 static int pick_rt(const GemvMmaArgs& a, int sm_count, float* ws, long ws_floats, int* counters, int n_counters,
                    cudaStream_t s) {
-  // more row tiles per CTA amortise the staging of x, as long as the grid still covers the SMs about twice
-  if ((a.N + 63) / 64 >= sm_count * 3 / 2) return launch_g2<MT, 4, DUAL>(a, sm_count, ws, ws_floats, counters, n_counters, s);
-  if ((a.N + 31) / 32 >= sm_count * 3 / 2) return launch_g2<MT, 2, DUAL>(a, sm_count, ws, ws_floats, counters, n_counters, s);
-  return launch_g2<MT, 1, DUAL>(a, sm_count, ws, ws_floats, counters, n_counters, s);
+  const int slots = 2 * sm_count;
+  int best_rt = 1, best_split = 1;
+  double best = 1e30;
+  for (int rt = 4; rt >= 1; rt >>= 1) {
+    const int tiles = (a.N + 16 * rt - 1) / (16 * rt);
+    int split = 1;
+    if (tiles < slots) {
+      split = slots / tiles;
+      split = min(split, min(8, a.K / 2048));
+      split = max(split, 1);
+      while (split > 1 && (long)(split - 1) * (((a.K / 32 + split - 1) / split) * 32) >= a.K) --split;
+    }
+    const long ctas = (long)tiles * split;
+    const long waves = (ctas + slots - 1) / slots;
+    const double fill = (double)ctas / (double)(waves * slots);
+    const double klen = (double)a.K / split;
+    const double wbytes = 16.0 * rt * klen * 2.0 * (DUAL ? 2 : 1), xbytes = 8.0 * MT * klen * 2.0;
+    const double cost = (1.0 / fill) * (1.0 + (xbytes + 65536.0 + (split > 1 ? 16384.0 : 0.0)) / wbytes);
+    if (cost < best) { best = cost; best_rt = rt; best_split = split; }
+  }
+  if (best_rt == 4) return launch_g2<MT, 4, DUAL>(a, best_split, ws, ws_floats, counters, n_counters, s);
+  if (best_rt == 2) return launch_g2<MT, 2, DUAL>(a, best_split, ws, ws_floats, counters, n_counters, s);
+  return launch_g2<MT, 1, DUAL>(a, best_split, ws, ws_floats, counters, n_counters, s);
 }
 
 }  // namespace fb

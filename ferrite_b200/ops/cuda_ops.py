@@ -108,10 +108,10 @@ class CudaOps:
             w = w.dense
         M, K = x.shape
         N = w.shape[0] // 2 if swiglu else w.shape[0]
-        # 2..8 rows always; 9..32 rows unless the matrix is very wide or very deep, where the swapped tcgen05 GEMM with
-        # its TMA pipeline measured faster (lm_head, down projection)
+        # 2..8 rows always; 9..32 rows unless the matrix is very wide (lm_head), where the swapped tcgen05 GEMM with its
+        # TMA pipeline measured faster
         if (self.mma_gemv_rows[0] <= M <= self.mma_gemv_rows[1] and K % 32 == 0 and not self.force_gemv_chunks
-                and w.stride(0) == K and (M <= 8 or (N < 65536 and K < 8192) or out_f32 and M <= 8)):
+                and w.stride(0) == K and (M <= 8 or N < 65536)):
             # a few rows (concurrent decode streams, speculative verify): weights streamed once into mma.sync fragments
             y = out if out is not None else torch.empty(M, N, dtype=torch.float32 if out_f32 else self.dtype, device=self.device)
             self.launches += 1
