@@ -20,6 +20,18 @@ from ..engine.executor import Segment
 from ..engine.scheduler import Drafter, grow_tree
 
 
+def drafter_config_for(target: ModelConfig) -> ModelConfig:
+    """The block drafter's shape for a target: the reference's 5-layer drafter (`config.drafter_block`) for
+    production-width targets, a two-layer miniature for the test presets; always the target's vocabulary."""
+    from ..config import drafter_block
+    if target.hidden >= 2048:
+        cfg = drafter_block()
+        cfg.vocab = target.vocab
+        return cfg
+    return ModelConfig(name="mini-drafter", hidden=128, inter=256, n_layers=2, full_attn_every=1, head_dim=32, n_q=4, n_kv=2,
+                       rotary_dim=32, attn_gate=False, vocab=target.vocab, tie_embeddings=True)
+
+
 class BlockDrafter(Drafter):
     def __init__(self, cfg: ModelConfig, target_hidden: int, n_taps: int, n_slots: int, max_ctx: int,
                  device: Optional[str] = None, seed: int = 1, block: int = 16, weights=None, mask_token: int = 0):

@@ -28,13 +28,21 @@ def build_engine(args, tok):
         cfg = PRESETS[args.preset]()
         if args.layers:
             cfg = scaled(cfg, args.layers)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    kind = getattr(args, "drafter", "none")
+    if kind != "none" and world == 1:
+        # the drafters read hidden rows of the target: the MTP head the last layer's, the block drafter three evenly
+        # spaced ones (the preset's own tap list when it has one)
+        if kind == "mtp":
+            cfg.tap_layers = [cfg.n_layers - 1]
+        elif not cfg.tap_layers:
+            cfg.tap_layers = sorted({max(0, cfg.n_layers * (i + 1) // 4 - 1) for i in range(3)})
     ecfg = EngineConfig.from_env(n_slots=args.slots, max_ctx=args.max_model_len, prefill_chunk=args.prefill_chunk,
                                  weight_dtype=args.weights)
     weights = None
     if args.model_dir and any(f.endswith(".safetensors") for f in os.listdir(args.model_dir)):
         from ..formats.loader import load_model_weights
         weights = load_model_weights(args.model_dir, cfg)
-    world = int(os.environ.get("WORLD_SIZE", "1"))
     tp = None
     if world > 1:
         # launched with torch.distributed.run: every rank builds its shard; rank 0 schedules and serves, the others
@@ -59,7 +67,20 @@ def build_engine(args, tok):
             raise SystemExit(0)
         eng = Leader(eng, tp)
     opts = SchedOptions.from_env()
-    return SchedulerEngine(Scheduler(eng, opts), args.served_model_name)
+    drafter = None
+    if kind != "none" and tp is None:
+        # speculative decoding with a draft model (reference: the drafter `factory`, `crates/fe-dflash/src/lib.rs:1381`,
+        # and the MTP head of the checkpoint); single GPU only, the tensor-parallel leader proxies engine calls only
+        if kind == "mtp":
+            from ..models.mtp import MtpDrafter
+            drafter = MtpDrafter(eng, n_slots=args.slots, max_ctx=args.max_model_len, depth=max(1, min(opts.spec or 4, 8)))
+        else:
+            from ..models.drafter import BlockDrafter, drafter_config_for
+            drafter = BlockDrafter(drafter_config_for(cfg), target_hidden=cfg.hidden, n_taps=len(cfg.tap_layers),
+                                   n_slots=args.slots, max_ctx=args.max_model_len, device=str(eng.device), block=16)
+        if opts.spec == 0:
+            opts.spec = 4 if kind == "mtp" else 8
+    return SchedulerEngine(Scheduler(eng, opts, drafter=drafter), args.served_model_name)
 
 
 def main(argv=None) -> int:
@@ -80,6 +101,8 @@ def main(argv=None) -> int:
     ap.add_argument("--max-model-len", type=int, default=int(os.environ.get("FERRITE_CTX", "8192")))
     ap.add_argument("--profile", default=os.environ.get("FERRITE_PROFILE", "default"))
     ap.add_argument("--mock", action="store_true")
+    ap.add_argument("--drafter", default=os.environ.get("FERRITE_DRAFTER", "none"), choices=["none", "block", "mtp"],
+                    help="draft model for speculative decoding (FE_SPEC sets the depth, FE_TREE the rows of a verify tree)")
     args = ap.parse_args(argv)
 
     from .app import AppState, make_app

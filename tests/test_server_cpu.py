@@ -247,3 +247,39 @@ def test_real_cpu_engine_behind_the_server():
         assert h["running"] == 0 and h["engine"] == "ferrite"
         await c.close()
     run(go())
+
+
+@pytest.mark.parametrize("kind", ["mtp", "block"])
+def test_server_builds_an_engine_with_a_drafter(kind):
+    """`--drafter mtp|block`: the server's engine factory taps the target, builds the draft model and hands it to the
+    scheduler; greedy replies equal the replies without speculation and drafts were verified."""
+    import argparse
+
+    from ferrite_b200.server.__main__ import build_engine
+    from ferrite_b200.server.tokenizer import load_tokenizer
+    base = dict(model_dir="", preset="tiny", layers=0, weights="bf16", device="cpu", slots=2, prefill_chunk=64,
+                max_model_len=256, served_model_name="m", mock=False, engine="ferrite")
+    tok = load_tokenizer(None, 4096)
+    plain = build_engine(argparse.Namespace(drafter="none", **base), tok)
+    spec = build_engine(argparse.Namespace(drafter=kind, **base), tok)
+    assert spec.sched.drafter is not None and spec.sched.opts.spec > 0
+    import threading
+
+    from ferrite_b200.engine.scheduler import Request, Sampling
+
+    def ask(se, prompt):
+        # the server's engine runs its scheduler on a worker thread: submit and wait for the finish event
+        out, fin = [], threading.Event()
+
+        def sink(ev):
+            if ev.kind == "tokens":
+                out.extend(ev.tokens)
+            else:
+                fin.set()
+        se.sched.submit(Request(list(prompt), Sampling(max_tokens=12), sink))
+        assert fin.wait(60)
+        return out
+    p = list(range(5, 45))
+    a, b = ask(plain, p), ask(spec, p)
+    assert a == b and len(a) == 12 and spec.sched.stats["drafted"] > 0
+    plain.sched.stop(); spec.sched.stop()
