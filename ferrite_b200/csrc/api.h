@@ -79,6 +79,14 @@ int fb_attn_prefill(void* out, const void* q, const void* k_cache, const void* v
                     long proj_stride, const int* seg_slot, const int* seg_row0, const int* seg_nrows,
                     const int* seg_pos0, const int* block_table, int max_blocks, int kv_block, int nseg, int max_rows,
                     int nq, int nkv, int hd, int gated, cudaStream_t s);
+int fb_attn_combine(void* out, const float* o_part, const float* ml_part, const void* proj, long proj_stride, int rows,
+                    int nq, int hd, int nsplit, int gated, cudaStream_t s);
+// tensor-core (mma.sync) decode / verify / tree attention over bf16 caches, rows addressed through their segments
+int fb_attn_decode_mma(void* out, float* o_part, float* ml_part, const void* q, const void* k_cache, const void* v_cache,
+                       const void* proj, long proj_stride, const int* seg_slot, const int* seg_row0, const int* seg_nrows,
+                       const int* row_kvlen, const int* row_base, const unsigned long long* row_mask,
+                       const int* block_table, int max_blocks, int kv_block, int nseg, int max_rows, int rows, int nq,
+                       int nkv, int hd, int nsplit, int gated, cudaStream_t s);
 // 4-bit KV cache: codes [..][hd/2] bytes, scales [..][2 * hd/32] fp32 per (token, kv head) row (K groups, V groups)
 int fb_attn_prep_q4(void* q_out, void* k_cache4, void* v_cache4, float* kv_scale, const void* proj, long proj_stride,
                     const void* q_norm, const void* k_norm, const float* inv_freq, const int* row_slot, const int* row_pos,

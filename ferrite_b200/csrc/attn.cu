@@ -438,6 +438,19 @@ static int attn_prep_impl(void* q_out, void* k_cache, void* v_cache, float* kv_s
   return (int)cudaGetLastError();
 }
 
+// merge of the per-split partials in split order + sigmoid output gate (shared by the SIMT and the mma decode kernels)
+extern "C" int fb_attn_combine(void* out, const float* o_part, const float* ml_part, const void* proj, long proj_stride,
+                               int rows, int nq, int hd, int nsplit, int gated, cudaStream_t s) {
+  if (rows <= 0) return 0;
+  dim3 cgrid(rows, nq);
+  int cthreads = hd >= 128 ? 128 : 64;
+  if (hd == 256) launch_pdl(attn_combine_kernel<256>, dim3(cgrid), dim3(cthreads), (size_t)(0), s, (__nv_bfloat16*)out, o_part, ml_part, (const __nv_bfloat16*)proj, proj_stride, nq, nsplit, gated);
+  else if (hd == 128) launch_pdl(attn_combine_kernel<128>, dim3(cgrid), dim3(cthreads), (size_t)(0), s, (__nv_bfloat16*)out, o_part, ml_part, (const __nv_bfloat16*)proj, proj_stride, nq, nsplit, gated);
+  else if (hd == 64) launch_pdl(attn_combine_kernel<64>, dim3(cgrid), dim3(cthreads), (size_t)(0), s, (__nv_bfloat16*)out, o_part, ml_part, (const __nv_bfloat16*)proj, proj_stride, nq, nsplit, gated);
+  else return -2;
+  return (int)cudaGetLastError();
+}
+
 static int attn_decode_impl(void* out, float* o_part, float* ml_part, const void* q, const void* k_cache,
                             const void* v_cache, const float* kv_scale, const void* proj, long proj_stride,
                             const int* row_slot, const int* row_kvlen, const int* row_base,
@@ -460,12 +473,7 @@ static int attn_decode_impl(void* out, float* o_part, float* ml_part, const void
   }
 #undef FB_DEC
   if (rc) return rc;
-  dim3 cgrid(rows, nq);
-  int cthreads = hd >= 128 ? 128 : 64;
-  if (hd == 256) launch_pdl(attn_combine_kernel<256>, dim3(cgrid), dim3(cthreads), (size_t)(0), s, (__nv_bfloat16*)out, o_part, ml_part, (const __nv_bfloat16*)proj, proj_stride, nq, nsplit, gated);
-  else if (hd == 128) launch_pdl(attn_combine_kernel<128>, dim3(cgrid), dim3(cthreads), (size_t)(0), s, (__nv_bfloat16*)out, o_part, ml_part, (const __nv_bfloat16*)proj, proj_stride, nq, nsplit, gated);
-  else launch_pdl(attn_combine_kernel<64>, dim3(cgrid), dim3(cthreads), (size_t)(0), s, (__nv_bfloat16*)out, o_part, ml_part, (const __nv_bfloat16*)proj, proj_stride, nq, nsplit, gated);
-  return (int)cudaGetLastError();
+  return fb_attn_combine(out, o_part, ml_part, proj, proj_stride, rows, nq, hd, nsplit, gated, s);
 }
 
 extern "C" int fb_attn_prep(void* q_out, void* k_cache, void* v_cache, const void* proj, long proj_stride,

@@ -198,6 +198,22 @@ void attn_decode(Tensor out, Tensor o_part, Tensor ml_part, Tensor q, Tensor k_c
                        (int)nsplit, gated ? 1 : 0, cur_stream()), "attn_decode");
 }
 
+int64_t attn_decode_mma(Tensor out, Tensor o_part, Tensor ml_part, Tensor q, Tensor k_cache, Tensor v_cache, Tensor proj,
+                        Tensor seg_slot, Tensor seg_row0, Tensor seg_nrows, int64_t max_rows, Tensor row_kvlen,
+                        c10::optional<Tensor> row_base, c10::optional<Tensor> row_mask, Tensor block_table,
+                        int64_t kv_block, int64_t nq, int64_t nkv, int64_t hd, int64_t nsplit, bool gated) {
+  int rc = fb_attn_decode_mma(out.data_ptr(), o_part.data_ptr<float>(), ml_part.data_ptr<float>(), q.data_ptr(),
+                              k_cache.data_ptr(), v_cache.data_ptr(), proj.data_ptr(), (long)proj.stride(0),
+                              seg_slot.data_ptr<int>(), seg_row0.data_ptr<int>(), seg_nrows.data_ptr<int>(),
+                              row_kvlen.data_ptr<int>(), (const int*)cptr(row_base),
+                              (const unsigned long long*)cptr(row_mask), block_table.data_ptr<int>(),
+                              (int)block_table.size(1), (int)kv_block, (int)seg_slot.numel(), (int)max_rows,
+                              (int)row_kvlen.numel(), (int)nq, (int)nkv, (int)hd, (int)nsplit, gated ? 1 : 0, cur_stream());
+  if (rc == -20) return rc;
+  check(rc, "attn_decode_mma");
+  return 0;
+}
+
 void kv_dequant(Tensor k_out, Tensor v_out, Tensor k_cache8, Tensor v_cache8, Tensor kv_scale, Tensor seg_slot,
                 Tensor seg_pos0, Tensor seg_nrows, Tensor block_table, int64_t kv_block, int64_t max_kvlen, int64_t nkv,
                 int64_t hd, int64_t scratch_tokens_per_slot) {
@@ -349,6 +365,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("attn_decode", &attn_decode);
   m.def("attn_prefill", &attn_prefill);
   m.def("attn_prefill_tc", &attn_prefill_tc);
+  m.def("attn_decode_mma", &attn_decode_mma);
   m.def("gdn_conv", &gdn_conv);
   m.def("gdn_rec", &gdn_rec);
   m.def("gdn_conv_tree", &gdn_conv_tree);

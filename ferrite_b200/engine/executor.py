@@ -504,7 +504,8 @@ class Executor:
                     # tree rows see the committed context plus their own ancestors (bit mask over the segment's rows)
                     o = ops.attention(q, proj, self.k_cache[i], self.v_cache[i], mv["slot"], mv["kvlen"],
                                       self.block_table, self.ecfg.kv_block, c.n_q, c.n_kv, c.head_dim, c.attn_gate,
-                                      row_base=tv["base"], row_mask=tv["mask"], nsplit=nsplit, **kvs)
+                                      row_base=tv["base"], row_mask=tv["mask"], nsplit=nsplit,
+                                      segs=(mv["sslot"], mv["srow0"], mv["snrows"], max_seg_rows), **kvs)
                 elif max_seg_rows > FLASH_MIN_ROWS:
                     o = ops.attention_prefill(q, proj, self.k_cache[i], self.v_cache[i], mv["sslot"], mv["srow0"],
                                               mv["snrows"], mv["spos0"], self.block_table, self.ecfg.kv_block, c.n_q,
@@ -513,7 +514,7 @@ class Executor:
                 else:
                     o = ops.attention(q, proj, self.k_cache[i], self.v_cache[i], mv["slot"], mv["kvlen"],
                                       self.block_table, self.ecfg.kv_block, c.n_q, c.n_kv, c.head_dim, c.attn_gate,
-                                      nsplit=nsplit, **kvs)
+                                      nsplit=nsplit, segs=(mv["sslot"], mv["srow0"], mv["snrows"], max_seg_rows), **kvs)
                 x = row(o, w[p + "out_proj"], x)
             if c.is_moe(i):
                 x = self._moe_ffn_sp(x, i, col, row) if sp else self._moe_ffn(x, i)

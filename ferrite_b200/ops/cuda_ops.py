@@ -38,6 +38,7 @@ class CudaOps:
         self.launches = 0                   # kernels launched (or recorded into a graph) through this object
         self.moe_pair_rows = MOE_PAIR_ROWS
         self.mma_gemv_rows = (2, 32)        # row counts routed to the mma.sync weight-streaming kernel
+        self.attn_mma = os.environ.get("FB_ATTN_MMA", "1") != "0"   # decode attention on mma.sync (0: SIMT kernel)
         self.attn_tc = os.environ.get("FB_ATTN_TC", "1") != "0"     # prompt attention on tcgen05 (0: mma.sync kernel)
         self._gdn_scratch = None
         self._tree_scratch = None
@@ -342,12 +343,20 @@ class CudaOps:
         return q
 
     def attention(self, q, proj, k_cache, v_cache, row_slot, row_kvlen, block_table, kv_block, nq, nkv, hd, gated,
-                  row_base=None, row_mask=None, nsplit=1, kv_scale=None):
+                  row_base=None, row_mask=None, nsplit=1, kv_scale=None, segs=None):
+        """Split-KV decode / verify / tree attention. With `segs` = (seg_slot, seg_row0, seg_nrows, max rows per
+        segment) and a bf16 cache the tensor-core kernel runs: the rows of a segment share one pass over the K/V of
+        each kv head. Quantised caches and callers without segment tables take the SIMT kernel."""
         T = q.shape[0]
         out = torch.empty(T, nq * hd, dtype=self.dtype, device=self.device)
         o_part = torch.empty(T, nq, nsplit, hd, dtype=torch.float32, device=self.device)
         ml_part = torch.empty(T, nq, nsplit, 2, dtype=torch.float32, device=self.device)
         self.launches += 2
+        if segs is not None and kv_scale is None and self.attn_mma and nq // nkv <= 64:
+            rc = self.C.attn_decode_mma(out, o_part, ml_part, q, k_cache, v_cache, proj, segs[0], segs[1], segs[2], segs[3],
+                                        row_kvlen, row_base, row_mask, block_table, kv_block, nq, nkv, hd, nsplit, gated)
+            if rc == 0:
+                return out
         self.C.attn_decode(out, o_part, ml_part, q, k_cache, v_cache, proj, row_slot, row_kvlen, row_base, row_mask,
                            block_table, kv_block, nq, nkv, hd, nsplit, gated, kv_scale)
         return out

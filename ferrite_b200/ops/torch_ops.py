@@ -112,7 +112,7 @@ class TorchOps:
         return q.to(self.dtype)
 
     def attention(self, q, proj, k_cache, v_cache, row_slot, row_kvlen, block_table, kv_block, nq, nkv, hd, gated,
-                  row_base=None, row_mask=None, nsplit=1, kv_scale=None):
+                  row_base=None, row_mask=None, nsplit=1, kv_scale=None, segs=None):
         T = q.shape[0]
         out = torch.zeros(T, nq, hd, dtype=torch.float32, device=q.device)
         grp = nq // nkv

@@ -94,6 +94,7 @@ def main():
     ap.add_argument("--n", type=int, default=5120)
     ap.add_argument("--k", type=int, default=5120)
     ap.add_argument("--ctx", type=int, default=2048)
+    ap.add_argument("--splits", type=int, default=0, help="attn_decode: key splits (0 = by context length)")
     ap.add_argument("--swiglu", action="store_true")
     ap.add_argument("--norm", action="store_true")
     ap.add_argument("--res", action="store_true")
@@ -152,10 +153,21 @@ def main():
         if a.what == "attn_decode":
             slot = (torch.arange(rows, device=dev, dtype=torch.int32) % nslots).contiguous()
             kvlen = torch.full((rows,), a.ctx, device=dev, dtype=torch.int32)
-            ns = max(1, min(64, 1 << ((a.ctx + 255) // 256 - 1).bit_length()))
+            ns = a.splits or max(1, min(64, 1 << ((a.ctx + 255) // 256 - 1).bit_length()))
             ms = t.run(lambda: ops.attention(q, proj, kc, vc, slot, kvlen, bt, kvb, nq, nkv, hd, True, nsplit=ns))
             nbytes = rows * a.ctx * nkv * hd * 2 * 2
-            report(f"attn_decode rows{rows} ctx{a.ctx} splits{ns}", ms, nbytes, 4.0 * rows * a.ctx * nq * hd)
+            report(f"attn_decode (SIMT) rows{rows} ctx{a.ctx} splits{ns}", ms, nbytes, 4.0 * rows * a.ctx * nq * hd)
+            i32 = lambda v: torch.tensor(v, device=dev, dtype=torch.int32)
+            # tensor-core kernel: independent streams (one row per segment), then one verify segment of all rows
+            segs = (slot, i32(list(range(rows))), i32([1] * rows), 1)
+            ms = t.run(lambda: ops.attention(q, proj, kc, vc, slot, kvlen, bt, kvb, nq, nkv, hd, True, nsplit=ns, segs=segs))
+            report(f"attn_decode (mma) {rows} streams ctx{a.ctx} splits{ns}", ms, nbytes, 4.0 * rows * a.ctx * nq * hd)
+            if rows > 1:
+                slot0 = torch.zeros(rows, device=dev, dtype=torch.int32)
+                segs = (i32([0]), i32([0]), i32([rows]), rows)
+                ms = t.run(lambda: ops.attention(q, proj, kc, vc, slot0, kvlen, bt, kvb, nq, nkv, hd, True, nsplit=ns, segs=segs))
+                report(f"attn_decode (mma) verify {rows} rows ctx{a.ctx} splits{ns}", ms, a.ctx * nkv * hd * 2 * 2,
+                       4.0 * rows * a.ctx * nq * hd)
         else:
             i32 = lambda v: torch.tensor([v], device=dev, dtype=torch.int32)
             ms = t.run(lambda: ops.attention_prefill(q, proj, kc, vc, i32(0), i32(0), i32(rows), i32(0), bt, kvb, nq,

@@ -504,3 +504,52 @@ def test_drafter_sublayers(ops):
     got = ops.draft_select(cv, ci, gate, a_cb, b_cb, 17)
     want = tops.draft_select(cv.cpu(), ci.cpu(), gate.cpu(), a_cb.cpu(), b_cb.cpu(), 17)
     assert got.cpu().tolist() == want.tolist()
+
+
+@pytest.mark.parametrize("hd,nq,nkv,gated", [(256, 24, 4, True), (128, 8, 2, False), (64, 4, 4, True), (256, 3, 1, True)])
+def test_attention_decode_mma_against_simt_and_reference(ops, tops, hd, nq, nkv, gated):
+    """Tensor-core decode attention (rows of a segment packed with the q heads of a GQA group into the MMA's M) against
+    the SIMT kernel and the fp32 reference: a 17-row verify segment behind 300 keys, single decode rows of two other
+    slots with different lengths, a tree segment with ancestor masks; several split counts."""
+    kv_block, n_slots, max_blocks = 64, 4, 8
+    nb = n_slots * max_blocks
+    width = nq * hd * (2 if gated else 1) + 2 * nkv * hd
+    g = torch.Generator().manual_seed(3)
+    bt = torch.randperm(nb, generator=g).to(torch.int32).view(n_slots, max_blocks).to(DEV).contiguous()
+    rot = 64
+    inv = (1e6 ** (-torch.arange(rot // 2, dtype=torch.float64) / (rot // 2))).float().to(DEV)
+    qn, kn = rnd(hd, scale=0.1, seed=7), rnd(hd, scale=0.1, seed=8)
+    kc = torch.zeros(nb, kv_block, nkv, hd, dtype=torch.bfloat16, device=DEV)
+    vc = torch.zeros_like(kc)
+    lens = {0: 300, 1: 77, 2: 410, 3: 129}
+    for slot, n in lens.items():                               # the committed context of every slot
+        ops.attn_prep(rnd(n, width, seed=10 + slot), qn, kn, inv, torch.full((n,), slot, device=DEV, dtype=torch.int32),
+                      torch.arange(n, device=DEV, dtype=torch.int32), bt, kc, vc, kv_block, nq, nkv, hd, rot, gated, 1e-6)
+    # step rows: 17 verify rows of slot 0, one decode row of slots 1 and 2, a 6-row tree of slot 3
+    par = [-1, 0, 0, 1, 2, 2]
+    depth = [0, 1, 1, 2, 2, 2]
+    amask = [0b1, 0b11, 0b101, 0b1011, 0b10101, 0b100101]
+    slot = torch.tensor([0] * 17 + [1, 2] + [3] * 6, device=DEV, dtype=torch.int32)
+    pos = torch.tensor(list(range(300, 317)) + [77, 410] + [129 + d for d in depth], device=DEV, dtype=torch.int32)
+    cpos = torch.tensor(list(range(300, 317)) + [77, 410] + list(range(129, 135)), device=DEV, dtype=torch.int32)
+    kvlen = cpos + 1
+    base = torch.tensor([300] * 17 + [77, 410] + [129] * 6, device=DEV, dtype=torch.int32)
+    mask = torch.tensor([(1 << (i + 1)) - 1 for i in range(17)] + [1, 1] + amask, device=DEV, dtype=torch.int64)
+    T = slot.numel()
+    proj = rnd(T, width, seed=30)
+    q = ops.attn_prep(proj, qn, kn, inv, slot, pos, bt, kc, vc, kv_block, nq, nkv, hd, rot, gated, 1e-6, row_cpos=cpos)
+    segs = (torch.tensor([0, 1, 2, 3], device=DEV, dtype=torch.int32), torch.tensor([0, 17, 18, 19], device=DEV, dtype=torch.int32),
+            torch.tensor([17, 1, 1, 6], device=DEV, dtype=torch.int32), 17)
+    want = tops.attention(q, proj, kc, vc, slot, kvlen, bt, kv_block, nq, nkv, hd, gated, row_base=base, row_mask=mask)
+    assert ops.attn_mma
+    for nsplit in (1, 4, 16):
+        a = ops.attention(q, proj, kc, vc, slot, kvlen, bt, kv_block, nq, nkv, hd, gated, row_base=base, row_mask=mask,
+                          nsplit=nsplit, segs=segs)
+        b = ops.attention(q, proj, kc, vc, slot, kvlen, bt, kv_block, nq, nkv, hd, gated, row_base=base, row_mask=mask,
+                          nsplit=nsplit)
+        close(b, want)
+        close(a, want)
+    # without masks (plain causal by kvlen)
+    a = ops.attention(q, proj, kc, vc, slot, kvlen, bt, kv_block, nq, nkv, hd, gated, nsplit=8, segs=segs)
+    close(a, tops.attention(q, proj, kc, vc, slot, kvlen, bt, kv_block, nq, nkv, hd, gated))
+    assert ops.status() == 0
