@@ -218,6 +218,26 @@ def main():
         vms = max_over_ranks(e0.elapsed_time(e1)) / K
         extras["verify_17rows_ms"] = vms
         extras["spec_tok_s_at_8_accepted"] = 9.0 / (vms / 1e3)
+        # the same step with what follows an acceptance of 8 drafts: the GDN state replayed over the 9 kept rows
+        st0 = eng.ex.state_save(0)
+
+        def verify_commit():
+            eng.forward([Segment(0, p0, rows, "all")], commit=False, greedy=True)
+            eng.commit_verified([9])
+            eng.slot_len[0] = p0
+        for _ in range(W):
+            verify_commit()
+        barrier()
+        e0, e1 = torch.cuda.Event(True), torch.cuda.Event(True)
+        e0.record()
+        for _ in range(K):
+            verify_commit()
+        e1.record()
+        barrier()
+        vcms = max_over_ranks(e0.elapsed_time(e1)) / K
+        eng.ex.state_restore(0, st0)
+        extras["verify_commit_ms"] = vcms
+        extras["spec_tok_s_at_8_accepted_with_commit"] = 9.0 / (vcms / 1e3)
     if long_ctx:
         # long-context prefill: 32K synthetic tokens through 2048-row chunks on one slot
         long_prompt = torch.randint(0, cfg.vocab, (long_ctx,), generator=gen).tolist()

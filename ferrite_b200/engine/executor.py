@@ -565,6 +565,11 @@ class Executor:
         s = 1 << (s - 1).bit_length()
         return min(s, 128)
 
+    def _replay_fused(self, max_rows: int) -> bool:
+        c = self.cfg
+        return (hasattr(self.ops, "gdn_step") and max_rows <= GDN_STEP_MAX_ROWS and c.lin_dk == c.lin_dv
+                and c.lin_dk in (64, 128))
+
     def commit_verified(self, keep: Sequence[int]) -> None:
         """After a verify step (commit=False): advance the Gated DeltaNet state of every segment by its first
         keep[i] rows, replaying the saved projections (reference `commit_rows` / `fe_gdn_replay`,
@@ -579,6 +584,12 @@ class Executor:
                 continue
             p = f"l{i}."
             proj = self.verify_proj[i]
+            if self._replay_fused(mr):
+                # one launch per layer: the fused step kernel re-runs the kept rows and commits (its outputs are dropped)
+                ops.gdn_step(proj, w[p + "conv_w"], self.rec_state[i], self.conv_state[i], w[p + "A_log"],
+                             w[p + "dt_bias"], w[p + "gnorm_w"], mv["sslot"], mv["srow0"], mv["snrows"],
+                             c.lin_k_heads, c.lin_v_heads, c.lin_dk, c.lin_dv, c.eps, commit=True)
+                continue
             qkv = ops.gdn_conv(proj, w[p + "conv_w"], self.conv_state[i], mv["sslot"], mv["srow0"], mv["snrows"],
                                c.conv_dim, **({"max_rows": mr} if ops.name == "cuda" else {}))
             ops.gdn_rec(qkv, proj, self.rec_state[i], self.conv_state[i], w[p + "A_log"], w[p + "dt_bias"],
@@ -621,6 +632,11 @@ class Executor:
                     continue
                 p = f"l{i}."
                 proj = self.verify_proj[i].index_select(0, idx).contiguous()
+                if self._replay_fused(mr):
+                    ops.gdn_step(proj, w[p + "conv_w"], self.rec_state[i], self.conv_state[i], w[p + "A_log"],
+                                 w[p + "dt_bias"], w[p + "gnorm_w"], sslot, srow0, snrows, c.lin_k_heads, c.lin_v_heads,
+                                 c.lin_dk, c.lin_dv, c.eps, commit=True)
+                    continue
                 qkv = ops.gdn_conv(proj, w[p + "conv_w"], self.conv_state[i], sslot, srow0, snrows, c.conv_dim,
                                    **({"max_rows": mr} if ops.name == "cuda" else {}))
                 ops.gdn_rec(qkv, proj, self.rec_state[i], self.conv_state[i], w[p + "A_log"], w[p + "dt_bias"], sslot,
