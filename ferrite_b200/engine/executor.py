@@ -175,6 +175,8 @@ class Executor:
         self.graphs: "OrderedDict[tuple, tuple]" = OrderedDict()
         self.taps: List[torch.Tensor] = []
         self.last_hidden: Optional[torch.Tensor] = None
+        self.commit_graphs: Dict[tuple, tuple] = {}
+        self._last_graph_key = None
         self.input_rows = False          # True: forward(x_add=...) replaces the embedded rows instead of adding to them
         self.verify_proj: Dict[int, torch.Tensor] = {}
         self.reclaim = None                          # callable() -> bool: free some pages (set by the scheduler)
@@ -579,6 +581,28 @@ class Executor:
         c, w, ops = self.cfg, self.w, self.ops
         mv["snrows"].copy_(torch.tensor(list(keep), dtype=torch.int32), non_blocking=False)
         mr = max(max(keep), 1)
+        if (self._last_graph_key is not None and self.profile is None and self._replay_fused(mr)
+                and any(k == "gdn" for k in self.kinds)):
+            # The verify step ran as a CUDA graph, so the projections it saved sit in that graph's buffers: the replay
+            # (one fused launch per GDN layer, the kept counts are device data) is captured once per forward graph and
+            # replayed with it. Eager verify steps allocate fresh projections every time and replay eagerly.
+            key = self._last_graph_key
+            g = self.commit_graphs.get(key)
+            if g is None:
+                g = torch.cuda.CUDAGraph()
+                l0 = self.ops.launches
+                with torch.cuda.graph(g):
+                    self._replay_layers(mv, mr)
+                self.commit_graphs[key] = (g, self.ops.launches - l0)
+                self.ops.launches = l0
+                g = self.commit_graphs[key]
+            g[0].replay()
+            self.ops.launches += g[1]
+            return
+        self._replay_layers(mv, mr)
+
+    def _replay_layers(self, mv, mr: int) -> None:
+        c, w, ops = self.cfg, self.w, self.ops
         for i, kind in enumerate(self.kinds):
             if kind != "gdn":
                 continue
@@ -673,6 +697,7 @@ class Executor:
         # the e4m3 cache decode before prompt attention sizes its grid by the longest visible context, except inside
         # graphs, whose launches must not depend on the step
         self._step_max_kvlen = None if use_graph else max_kvlen
+        self._last_graph_key = None
         if not use_graph:
             logits, picks = self._run(T, nseg, nlog, max_seg_rows, nsplit, batch.commit, greedy, x_add, tree)
             return logits, picks, logit_rows
@@ -688,14 +713,18 @@ class Executor:
                 out = self._run(T, nseg, nlog, max_seg_rows, nsplit, batch.commit, greedy, None, tree)
             n_kernels = self.ops.launches - l0
             self.ops.launches = l0
-            hit = (g, out, n_kernels, self.taps, self.last_hidden)
+            hit = (g, out, n_kernels, self.taps, self.last_hidden, dict(self.verify_proj))
             self.graphs[key] = hit
             if len(self.graphs) > self.ecfg.graph_max:
-                self.graphs.popitem(last=False)
+                old_key, _ = self.graphs.popitem(last=False)
+                self.commit_graphs.pop(old_key, None)
             # capture does not execute: replay below performs the step
         else:
             self.graphs.move_to_end(key)
-        g, (logits, picks), n_kernels, self.taps, self.last_hidden = hit      # taps / hidden: this graph's buffers
+        # taps / hidden / saved projections: this graph's buffers, not those of whichever graph was captured last
+        g, (logits, picks), n_kernels, self.taps, self.last_hidden, vp = hit
+        self.verify_proj = dict(vp)
+        self._last_graph_key = key
         self._last_meta = (self._meta_views(T, nseg, nlog), max_seg_rows)
         g.replay()
         self.ops.launches += n_kernels

@@ -235,3 +235,29 @@ def test_int4_kv_cache_gpu(ext):
     from ferrite_b200.utils.selftest import tree_test
     tree_test("cuda", 8e-2, kv_dtype="int4")
     eng.check()
+
+
+def test_commit_after_replayed_verify_graphs(ext):
+    """Verify steps of two slots with different context lengths are different CUDA graphs; replaying the first one again
+    and committing must replay THAT graph's saved projections (and its captured commit graph), not those of the graph
+    captured last. Against an engine without graphs."""
+    cfg = tiny_hybrid()
+    w = init_weights(cfg, seed=0)
+    pa, pb = _prompt(cfg, 40, 1), _prompt(cfg, 300, 2)
+    da, db = _prompt(cfg, 6, 3), _prompt(cfg, 6, 4)
+
+    def run(use_graphs):
+        e = Engine(cfg, w, EngineConfig(n_slots=2, max_ctx=512, use_graphs=use_graphs), device="cuda")
+        e.forward([Segment(0, 0, pa, "none")])
+        e.forward([Segment(1, 0, pb, "none")])
+        outs = []
+        for rnd_ in range(2):                                  # second round replays both verify graphs
+            for slot, d in ((0, da), (1, db)):
+                p0 = e.slot_len[slot]
+                e.forward([Segment(slot, p0, d, "all")], commit=False)
+                e.commit_verified([4])
+                outs.append(e.forward([Segment(slot, p0 + 4, [9], "last")], greedy=False)[0].clone())
+        e.check()
+        return torch.cat(outs).float()
+    a, b = run(True), run(False)
+    assert (a - b).abs().max().item() < 2e-2 * max(1.0, b.abs().max().item())
