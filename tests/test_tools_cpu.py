@@ -81,3 +81,21 @@ def test_sweep_runs_points(capsys):
         loop.call_soon_threadsafe(loop.stop)
     out = capsys.readouterr().out
     assert rc == 0 and "agg tok/s" in out
+
+
+def test_chart_writes_an_svg_from_json_lines(tmp_path):
+    """The chart tool reads sweep / bench JSON lines (nested keys too) and writes a self-contained SVG."""
+    import json
+    import xml.etree.ElementTree as ET
+
+    from ferrite_b200.tools import chart
+    a, b = tmp_path / "a.jsonl", tmp_path / "b.jsonl"
+    a.write_text("noise\n" + "\n".join(json.dumps({"streams": n, "aggregate_tok_s": 100.0 * n ** 0.8, "e2e": {"value": n}})
+                                         for n in (1, 2, 4, 8)))
+    b.write_text("\n".join(json.dumps({"streams": n, "aggregate_tok_s": 60.0 * n}) for n in (1, 2, 4)))
+    assert chart.read_points(str(a), "streams", "e2e.value") == [(1.0, 1.0), (2.0, 2.0), (4.0, 4.0), (8.0, 8.0)]
+    out = tmp_path / "c.svg"
+    assert chart.main([str(a), str(b), "--title", "decode", "-o", str(out)]) == 0
+    root = ET.fromstring(out.read_text())
+    tags = [e.tag.split("}")[-1] for e in root.iter()]
+    assert tags.count("polyline") == 2 and tags.count("circle") == 7
