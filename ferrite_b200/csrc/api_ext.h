@@ -105,6 +105,11 @@ int fb_mla_attn(void* out, float* o_part, float* ml_part, const void* qabs, cons
 // ---- drafter_ops.cu ----
 int fb_w4_gemv(void* y, const void* x, const void* qweight, const void* scales, const void* biases, const void* res, int M,
                int N, int K, long ldx, long ldy, cudaStream_t s);
+// hyper-connection streams (hyperconn.cu): per-stream RMSNorm to bf16, gated mix of the streams, output injection
+int fb_hc_norm(void* y, float* rinv, const float* x, const float* w, int groups, int d, int ngw, float eps, cudaStream_t s);
+int fb_hc_mix(float* mixed, const float* res, const float* rinv, const float* w, const float* gate, int rows, int d, int hc,
+              cudaStream_t s);
+int fb_hc_combine(float* res, const float* out, const float* inj, int rows, int d, int hc, long ldi, cudaStream_t s);
 // block-drafter sublayers: grouped dynamic conv over a block, merge of per-rank top-16 lists, candidate selector walk
 int fb_dynconv(void* out, const void* x, const void* coef, long ldc, const void* base, void* res, int rows, int H, int group,
                int blk, cudaStream_t s);

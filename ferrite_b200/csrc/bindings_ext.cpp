@@ -299,6 +299,21 @@ void w4_gemv(Tensor y, Tensor x, Tensor qweight, Tensor scales, Tensor biases, c
         "w4_gemv");
 }
 
+void hc_norm(Tensor y, Tensor rinv, Tensor x, Tensor w, double eps) {
+  check(fb_hc_norm(y.data_ptr(), rinv.data_ptr<float>(), x.data_ptr<float>(), w.data_ptr<float>(), (int)x.size(0),
+                   (int)x.size(1), (int)w.size(0), (float)eps, cur_stream()), "hc_norm");
+}
+
+void hc_mix(Tensor mixed, Tensor res, Tensor rinv, Tensor w, Tensor gate) {
+  check(fb_hc_mix(mixed.data_ptr<float>(), res.data_ptr<float>(), rinv.data_ptr<float>(), w.data_ptr<float>(),
+                  gate.data_ptr<float>(), (int)res.size(0), (int)res.size(2), (int)res.size(1), cur_stream()), "hc_mix");
+}
+
+void hc_combine(Tensor res, Tensor out, Tensor inj) {
+  check(fb_hc_combine(res.data_ptr<float>(), out.data_ptr<float>(), inj.data_ptr<float>(), (int)res.size(0), (int)res.size(2),
+                      (int)res.size(1), (long)inj.stride(0), cur_stream()), "hc_combine");
+}
+
 void dynconv(Tensor out, Tensor x, Tensor coef, Tensor base, c10::optional<Tensor> res, int64_t group, int64_t blk) {
   check(fb_dynconv(out.data_ptr(), x.data_ptr(), coef.data_ptr(), (long)coef.stride(0), base.data_ptr(), res.has_value() ? res->data_ptr() : nullptr,
                    (int)x.size(0), (int)x.size(1), (int)group, (int)blk, cur_stream()), "dynconv");
@@ -326,6 +341,9 @@ void register_ext(pybind11::module_& m) {
   m.def("w4_gemv", &w4_gemv);
   m.def("topk16", &topk16);
   m.def("dynconv", &dynconv);
+  m.def("hc_norm", &hc_norm);
+  m.def("hc_mix", &hc_mix);
+  m.def("hc_combine", &hc_combine);
   m.def("topk16_merge", &topk16_merge);
   m.def("draft_select", &draft_select);
   m.def("mla_prep", &mla_prep);

@@ -489,6 +489,31 @@ class CudaOps:
         self.C.w4_gemv(y, x, qweight, scales, biases, res)
         return y
 
+    # ---- hyper-connection streams: res [rows, hc, d] fp32 ------------------------------------------------
+    def hc_norm(self, res, w, eps):
+        """Per-stream RMSNorm of the residual streams to bf16: returns (y [rows * hc, d], inv [rows * hc]); `w` [ngw, d]
+        fp32, stream g uses row g % ngw."""
+        rows, hc, d = res.shape
+        y = torch.empty(rows * hc, d, dtype=self.dtype, device=self.device)
+        inv = torch.empty(rows * hc, dtype=torch.float32, device=self.device)
+        self.launches += 1
+        self.C.hc_norm(y, inv, res.view(rows * hc, d), w, eps)
+        return y, inv
+
+    def hc_mix(self, res, inv, w, gate):
+        """mixed[r] = mean over streams of (normalised stream * w[s]) * sigmoid(gate[r][s]); fp32 [rows, d]."""
+        rows, hc, d = res.shape
+        mixed = torch.empty(rows, d, dtype=torch.float32, device=self.device)
+        self.launches += 1
+        self.C.hc_mix(mixed, res, inv, w, gate)
+        return mixed
+
+    def hc_combine(self, res, out, inj):
+        """res[r][s] += out[r] * 2 sigmoid(inj[r][s]) in place (`inj` may be a column slice of a wider projection)."""
+        self.launches += 1
+        self.C.hc_combine(res, out, inj)
+        return res
+
     def dynconv(self, x, coef, base, group, blk, res=None):
         """Grouped dynamic causal conv over draft blocks of `blk` rows: y[t] = (base[0] + c[t][g]) x[t] + (base[1] +
         c[t][G + g]) x[t-1] (second term only inside a block). `coef` [rows, 2 * H / group] may be a column slice of a

@@ -320,6 +320,21 @@ class TorchOps:
         return out if out_f32 else out.to(self.dtype)
 
     # ---- selection ---------------------------------------------------------------------------------
+    def hc_norm(self, res, w, eps):
+        rows, hc, d = res.shape
+        x = res.reshape(rows * hc, d).float()
+        inv = torch.rsqrt(x.pow(2).mean(-1) + eps)
+        wg = w.float()[torch.arange(rows * hc) % w.shape[0]]
+        return (x * inv[:, None] * wg).to(self.dtype), inv
+
+    def hc_mix(self, res, inv, w, gate):
+        rows, hc, d = res.shape
+        return (res.float() * inv.view(rows, hc, 1) * w.float()[None, :hc] * torch.sigmoid(gate.float())).mean(1)
+
+    def hc_combine(self, res, out, inj):
+        res += out.float()[:, None, :] * 2.0 * torch.sigmoid(inj.float())[:, :res.shape[1], None]
+        return res
+
     def dynconv(self, x, coef, base, group, blk, res=None):
         T, H = x.shape
         G = H // group

@@ -553,3 +553,25 @@ def test_attention_decode_mma_against_simt_and_reference(ops, tops, hd, nq, nkv,
     a = ops.attention(q, proj, kc, vc, slot, kvlen, bt, kv_block, nq, nkv, hd, gated, nsplit=8, segs=segs)
     close(a, tops.attention(q, proj, kc, vc, slot, kvlen, bt, kv_block, nq, nkv, hd, gated))
     assert ops.status() == 0
+
+
+def test_hyper_connection_ops(ops):
+    """Hyper-connection kernels (per-stream norm, gated mix, injection) against the host statements."""
+    from ferrite_b200.ops.torch_ops import TorchOps
+    tops = TorchOps("cpu", torch.float32)
+    rows, hc, d = 37, 4, 2560
+    res = rnd(rows, hc, d, seed=1, dtype=torch.float32)
+    w = rnd(hc, d, seed=2, dtype=torch.float32) + 1.0
+    gate = rnd(rows, hc, d, seed=3, dtype=torch.float32)
+    y, inv = ops.hc_norm(res, w, 1e-6)
+    wy, winv = tops.hc_norm(res.cpu(), w.cpu(), 1e-6)
+    assert torch.allclose(inv.cpu(), winv, rtol=1e-5)
+    assert (y.float().cpu() - wy).abs().max().item() < 2e-2 * wy.abs().max().item()
+    m = ops.hc_mix(res, inv, w, gate)
+    assert torch.allclose(m.cpu(), tops.hc_mix(res.cpu(), winv, w.cpu(), gate.cpu()), rtol=1e-4, atol=1e-5)
+    out = rnd(rows, d, seed=4, dtype=torch.float32)
+    wide = rnd(rows, 16, seed=5, dtype=torch.float32)
+    inj = wide[:, 8:8 + hc]                                  # a column slice of a wider projection
+    want = tops.hc_combine(res.cpu().clone(), out.cpu(), inj.cpu())
+    got = ops.hc_combine(res, out, inj)
+    assert torch.allclose(got.cpu(), want, rtol=1e-5, atol=1e-6)
