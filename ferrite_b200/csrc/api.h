@@ -81,9 +81,10 @@ int fb_attn_prefill(void* out, const void* q, const void* k_cache, const void* v
                     int nq, int nkv, int hd, int gated, cudaStream_t s);
 int fb_attn_combine(void* out, const float* o_part, const float* ml_part, const void* proj, long proj_stride, int rows,
                     int nq, int hd, int nsplit, int gated, cudaStream_t s);
-// tensor-core (mma.sync) decode / verify / tree attention over bf16 caches, rows addressed through their segments
+// tensor-core (mma.sync) decode / verify / tree attention over bf16 or e4m3 (kv_scale != null) caches, rows addressed
+// through their segments
 int fb_attn_decode_mma(void* out, float* o_part, float* ml_part, const void* q, const void* k_cache, const void* v_cache,
-                       const void* proj, long proj_stride, const int* seg_slot, const int* seg_row0, const int* seg_nrows,
+                       const float* kv_scale, const void* proj, long proj_stride, const int* seg_slot, const int* seg_row0, const int* seg_nrows,
                        const int* row_kvlen, const int* row_base, const unsigned long long* row_mask,
                        const int* block_table, int max_blocks, int kv_block, int nseg, int max_rows, int rows, int nq,
                        int nkv, int hd, int nsplit, int gated, cudaStream_t s);

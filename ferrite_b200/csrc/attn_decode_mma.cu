@@ -11,6 +11,8 @@
 // Visibility of key t for a row: t < kvlen[row], and, with a verify tree, t < base[row] or bit (t - base[row]) of the
 // row's ancestor mask. Counterpart of the reference's `fe_attn_vk` (`kernels/k-core/src/attn.rs:331`: decode / verify /
 // tree attention on mma.sync with 16-key tiles and ancestor masks) and `fe_attn_combine` (`:99`).
+#include <cuda_fp8.h>
+
 #include "api.h"
 #include "common.cuh"
 
@@ -38,11 +40,35 @@ __device__ __forceinline__ void dm_mma(float (&c)[4], const uint32_t (&a)[4], ui
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-template <int HD>
+__device__ __forceinline__ void dm_cp_async8(void* smem, const void* gmem, bool valid) {
+  int sz = valid ? 8 : 0;
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;" ::"r"(smem_u32(smem)), "l"(gmem), "r"(sz) : "memory");
+}
+// 16 e4m3 codes -> 16 bf16 (exact: e4m3 values are representable in bf16)
+__device__ __forceinline__ void dm_e4m3x16_to_bf16(const uint4& c, uint4& lo, uint4& hi) {
+  const uint32_t w[4] = {c.x, c.y, c.z, c.w};
+  uint32_t o[8];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const __half2_raw hr = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)((w[i] >> (16 * h)) & 0xFFFFu), __NV_E4M3);
+      const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&hr));
+      o[i * 2 + h] = pack_bf2(f.x, f.y);
+    }
+  }
+  lo = make_uint4(o[0], o[1], o[2], o[3]);
+  hi = make_uint4(o[4], o[5], o[6], o[7]);
+}
+
+// KV8: e4m3 cache (codes [..][HD] bytes, scales [token * nkv + head][2] fp32 for K and V). The byte tiles stream through
+// a two-stage cp.async ring and are expanded to bf16 tiles in shared memory before the MMAs; the per-key scales are
+// applied to the scores (K) and to P (V) instead of to every element.
+template <int HD, bool KV8>
 __global__ void __launch_bounds__(DM_WARPS * 32)
 attn_decode_mma_kernel(float* __restrict__ o_part, float* __restrict__ ml_part, const __nv_bfloat16* __restrict__ q,
                        const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
-                       const int* __restrict__ seg_slot, const int* __restrict__ seg_row0,
+                       const float* __restrict__ kv_scale, const int* __restrict__ seg_slot, const int* __restrict__ seg_row0,
                        const int* __restrict__ seg_nrows, const int* __restrict__ row_kvlen,
                        const int* __restrict__ row_base, const unsigned long long* __restrict__ row_mask,
                        const int* __restrict__ block_table, int max_blocks, int kv_block, int nq, int nkv, int nsplit,
@@ -51,8 +77,12 @@ attn_decode_mma_kernel(float* __restrict__ o_part, float* __restrict__ ml_part, 
   constexpr int CPR = HD / 8;                   // 16-byte chunks per row
   extern __shared__ __align__(16) unsigned char dm_smem[];
   __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(dm_smem);           // [BM][LD]
-  __nv_bfloat16* sK = sQ + DM_BM * LD;                                      // [2][BKV][LD]
-  __nv_bfloat16* sV = sK + 2 * DM_BKV * LD;                                 // [2][BKV][LD]
+  constexpr int NST = KV8 ? 1 : 2;              // bf16 tile buffers (the e4m3 form double-buffers the byte tiles instead)
+  __nv_bfloat16* sK = sQ + DM_BM * LD;                                      // [NST][BKV][LD]
+  __nv_bfloat16* sV = sK + NST * DM_BKV * LD;                               // [NST][BKV][LD]
+  unsigned char* rK = reinterpret_cast<unsigned char*>(sV + NST * DM_BKV * LD);   // KV8: [2][BKV][HD] codes
+  unsigned char* rV = rK + 2 * DM_BKV * HD;
+  float* ssc = reinterpret_cast<float*>(rV + 2 * DM_BKV * HD);              // KV8: [2][BKV][2] scales (K, V)
   // No early launch of the dependent grid here: measured inside the decode graph, the dependents' CTAs (which only
   // wait) took the shared memory this kernel's 101 KB CTAs needed and a 27B decode step slowed from 8.9 to 10.8 ms.
   pdl_wait();
@@ -104,6 +134,22 @@ attn_decode_mma_kernel(float* __restrict__ o_part, float* __restrict__ ml_part, 
     dm_cp_async16(sQ + m * LD + cc * 8, src, ok);
   }
   auto load_kv = [&](int t0, int stage) {
+    if (KV8) {
+      const unsigned char* k8 = reinterpret_cast<const unsigned char*>(k_cache);
+      const unsigned char* v8 = reinterpret_cast<const unsigned char*>(v_cache);
+      constexpr int CPR8 = HD / 16;
+      for (int c = tid; c < DM_BKV * CPR8; c += blockDim.x) {
+        const int r = c / CPR8, cc = c % CPR8;
+        const int t = t0 + r;
+        const bool ok = t < hi;
+        size_t tok = 0;
+        if (ok) tok = ((size_t)bt[t / kv_block] * kv_block + (t % kv_block)) * nkv + kvh;
+        dm_cp_async16(rK + ((size_t)stage * DM_BKV + r) * HD + cc * 16, k8 + tok * HD + cc * 16, ok);
+        dm_cp_async16(rV + ((size_t)stage * DM_BKV + r) * HD + cc * 16, v8 + tok * HD + cc * 16, ok);
+        if (cc == 0) dm_cp_async8(ssc + ((size_t)stage * DM_BKV + r) * 2, kv_scale + tok * 2, ok);
+      }
+      return;
+    }
     for (int c = tid; c < DM_BKV * CPR; c += blockDim.x) {
       const int r = c / CPR, cc = c % CPR;
       const int t = t0 + r;
@@ -132,9 +178,25 @@ attn_decode_mma_kernel(float* __restrict__ o_part, float* __restrict__ ml_part, 
     if (tile + 1 < ntiles) { load_kv(lo + (tile + 1) * DM_BKV, stage ^ 1); dm_commit(); dm_wait<1>(); }
     else dm_wait<0>();
     __syncthreads();
+    if (KV8) {
+      // expand this tile's codes to bf16 (the MMAs of the previous tile finished before the barrier above)
+      constexpr int CPR8 = HD / 16;
+      for (int c = tid; c < DM_BKV * CPR8; c += blockDim.x) {
+        const int r = c / CPR8, cc = c % CPR8;
+        uint4 lo4, hi4;
+        dm_e4m3x16_to_bf16(*reinterpret_cast<const uint4*>(rK + ((size_t)stage * DM_BKV + r) * HD + cc * 16), lo4, hi4);
+        *reinterpret_cast<uint4*>(sK + r * LD + cc * 16) = lo4;
+        *reinterpret_cast<uint4*>(sK + r * LD + cc * 16 + 8) = hi4;
+        dm_e4m3x16_to_bf16(*reinterpret_cast<const uint4*>(rV + ((size_t)stage * DM_BKV + r) * HD + cc * 16), lo4, hi4);
+        *reinterpret_cast<uint4*>(sV + r * LD + cc * 16) = lo4;
+        *reinterpret_cast<uint4*>(sV + r * LD + cc * 16 + 8) = hi4;
+      }
+      __syncthreads();
+    }
     if (warp_on) {
-      const __nv_bfloat16* K = sK + stage * DM_BKV * LD;
-      const __nv_bfloat16* V = sV + stage * DM_BKV * LD;
+      const __nv_bfloat16* K = sK + (KV8 ? 0 : stage) * DM_BKV * LD;
+      const __nv_bfloat16* V = sV + (KV8 ? 0 : stage) * DM_BKV * LD;
+      const float* tsc = ssc + (size_t)stage * DM_BKV * 2;   // KV8: (K scale, V scale) of the tile's keys
       float s[4][4];
 #pragma unroll
       for (int i = 0; i < 4; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
@@ -159,7 +221,9 @@ attn_decode_mma_kernel(float* __restrict__ o_part, float* __restrict__ ml_part, 
           const int t = kbase + nt * 8 + (e & 1), h = e >> 1;
           bool vis = t < kvl[h] && t < hi;
           if (vis && t >= base[h]) vis = ((msk[h] >> (t - base[h])) & 1ull) != 0ull;
-          const float v = vis ? s[nt][e] * scale_log2 : -INFINITY;
+          float sv = s[nt][e];
+          if (KV8) sv *= tsc[((lane & 3) * 2 + nt * 8 + (e & 1)) * 2];
+          const float v = vis ? sv * scale_log2 : -INFINITY;
           s[nt][e] = v;
           mx[h] = fmaxf(mx[h], v);
         }
@@ -182,8 +246,10 @@ attn_decode_mma_kernel(float* __restrict__ o_part, float* __restrict__ ml_part, 
         const float p2 = (mrow[1] == -INFINITY) ? 0.f : exp2f(s[nt][2] - mrow[1]);
         const float p3 = (mrow[1] == -INFINITY) ? 0.f : exp2f(s[nt][3] - mrow[1]);
         ls[0] += p0 + p1; ls[1] += p2 + p3;
-        pa[nt >> 1][(nt & 1) * 2 + 0] = pack_bf2(p0, p1);
-        pa[nt >> 1][(nt & 1) * 2 + 1] = pack_bf2(p2, p3);
+        float v0 = 1.f, v1 = 1.f;                           // KV8: the V scale of the two keys rides on P
+        if (KV8) { v0 = tsc[((lane & 3) * 2 + nt * 8) * 2 + 1]; v1 = tsc[((lane & 3) * 2 + nt * 8 + 1) * 2 + 1]; }
+        pa[nt >> 1][(nt & 1) * 2 + 0] = pack_bf2(p0 * v0, p1 * v1);
+        pa[nt >> 1][(nt & 1) * 2 + 1] = pack_bf2(p2 * v0, p3 * v1);
       }
 #pragma unroll
       for (int h = 0; h < 2; ++h) lrow[h] = lrow[h] * sc[h] + ls[h];
@@ -226,14 +292,15 @@ attn_decode_mma_kernel(float* __restrict__ o_part, float* __restrict__ ml_part, 
 
 using namespace fb;
 
-// Same outputs as fb_attn_decode for bf16 caches; rows are addressed through their segments (rows of one segment share
-// a slot). Returns -20 for shapes this kernel does not take (the caller uses fb_attn_decode).
+// Same outputs as fb_attn_decode (bf16 cache) / fb_attn_decode_kv8 (kv_scale != null: e4m3 cache); rows are addressed
+// through their segments (rows of one segment share a slot). Returns -20 for shapes this kernel does not take (the
+// caller uses the SIMT kernel).
 extern "C" int fb_attn_decode_mma(void* out, float* o_part, float* ml_part, const void* q, const void* k_cache,
-                                  const void* v_cache, const void* proj, long proj_stride, const int* seg_slot,
-                                  const int* seg_row0, const int* seg_nrows, const int* row_kvlen, const int* row_base,
-                                  const unsigned long long* row_mask, const int* block_table, int max_blocks,
-                                  int kv_block, int nseg, int max_rows, int rows, int nq, int nkv, int hd, int nsplit,
-                                  int gated, cudaStream_t s) {
+                                  const void* v_cache, const float* kv_scale, const void* proj, long proj_stride,
+                                  const int* seg_slot, const int* seg_row0, const int* seg_nrows, const int* row_kvlen,
+                                  const int* row_base, const unsigned long long* row_mask, const int* block_table,
+                                  int max_blocks, int kv_block, int nseg, int max_rows, int rows, int nq, int nkv, int hd,
+                                  int nsplit, int gated, cudaStream_t s) {
   if (nseg <= 0 || rows <= 0) return 0;
   if (nq % nkv) return -1;
   const int G = nq / nkv;
@@ -242,17 +309,22 @@ extern "C" int fb_attn_decode_mma(void* out, float* o_part, float* ml_part, cons
   const int gps = (max_rows + RG - 1) / RG;
   dim3 grid(nseg * gps, nkv, nsplit);
   const float scale_log2 = 1.4426950408889634f / sqrtf((float)hd);
-#define FB_DM(HDV)                                                                                                  \
+#define FB_DM(HDV, K8)                                                                                              \
   {                                                                                                                 \
-    const size_t smem = (size_t)(DM_BM + 4 * DM_BKV) * (HDV + 8) * 2;                                               \
-    auto kern = attn_decode_mma_kernel<HDV>;                                                                        \
+    const size_t smem = K8 ? (size_t)(DM_BM + 2 * DM_BKV) * (HDV + 8) * 2 + (size_t)4 * DM_BKV * HDV + 4 * DM_BKV * 4 * 2 \
+                           : (size_t)(DM_BM + 4 * DM_BKV) * (HDV + 8) * 2;                                          \
+    auto kern = attn_decode_mma_kernel<HDV, K8>;                                                                    \
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);             \
     if (e != cudaSuccess) return (int)e;                                                                            \
     launch_pdl(kern, grid, dim3(DM_WARPS * 32), smem, s, o_part, ml_part, (const __nv_bfloat16*)q,                   \
-               (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, seg_slot, seg_row0, seg_nrows, row_kvlen, \
-               row_base, row_mask, block_table, max_blocks, kv_block, nq, nkv, nsplit, gps, scale_log2);             \
+               (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, kv_scale, seg_slot, seg_row0, seg_nrows, \
+               row_kvlen, row_base, row_mask, block_table, max_blocks, kv_block, nq, nkv, nsplit, gps, scale_log2);  \
   }
-  if (hd == 256) FB_DM(256) else if (hd == 128) FB_DM(128) else FB_DM(64)
+  if (kv_scale) {
+    if (hd == 256) FB_DM(256, true) else if (hd == 128) FB_DM(128, true) else FB_DM(64, true)
+  } else {
+    if (hd == 256) FB_DM(256, false) else if (hd == 128) FB_DM(128, false) else FB_DM(64, false)
+  }
 #undef FB_DM
   int rc = (int)cudaGetLastError();
   if (rc) return rc;

@@ -201,9 +201,11 @@ void attn_decode(Tensor out, Tensor o_part, Tensor ml_part, Tensor q, Tensor k_c
 int64_t attn_decode_mma(Tensor out, Tensor o_part, Tensor ml_part, Tensor q, Tensor k_cache, Tensor v_cache, Tensor proj,
                         Tensor seg_slot, Tensor seg_row0, Tensor seg_nrows, int64_t max_rows, Tensor row_kvlen,
                         c10::optional<Tensor> row_base, c10::optional<Tensor> row_mask, Tensor block_table,
-                        int64_t kv_block, int64_t nq, int64_t nkv, int64_t hd, int64_t nsplit, bool gated) {
+                        int64_t kv_block, int64_t nq, int64_t nkv, int64_t hd, int64_t nsplit, bool gated,
+                        c10::optional<Tensor> kv_scale) {
   int rc = fb_attn_decode_mma(out.data_ptr(), o_part.data_ptr<float>(), ml_part.data_ptr<float>(), q.data_ptr(),
-                              k_cache.data_ptr(), v_cache.data_ptr(), proj.data_ptr(), (long)proj.stride(0),
+                              k_cache.data_ptr(), v_cache.data_ptr(), (const float*)cptr(kv_scale), proj.data_ptr(),
+                              (long)proj.stride(0),
                               seg_slot.data_ptr<int>(), seg_row0.data_ptr<int>(), seg_nrows.data_ptr<int>(),
                               row_kvlen.data_ptr<int>(), (const int*)cptr(row_base),
                               (const unsigned long long*)cptr(row_mask), block_table.data_ptr<int>(),

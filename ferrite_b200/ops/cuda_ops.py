@@ -346,15 +346,17 @@ class CudaOps:
                   row_base=None, row_mask=None, nsplit=1, kv_scale=None, segs=None):
         """Split-KV decode / verify / tree attention. With `segs` = (seg_slot, seg_row0, seg_nrows, max rows per
         segment) and a bf16 cache the tensor-core kernel runs: the rows of a segment share one pass over the K/V of
-        each kv head. Quantised caches and callers without segment tables take the SIMT kernel."""
+        each kv head (bf16 and e4m3 caches). The 4-bit cache and callers without segment tables take the SIMT kernel."""
         T = q.shape[0]
         out = torch.empty(T, nq * hd, dtype=self.dtype, device=self.device)
         o_part = torch.empty(T, nq, nsplit, hd, dtype=torch.float32, device=self.device)
         ml_part = torch.empty(T, nq, nsplit, 2, dtype=torch.float32, device=self.device)
         self.launches += 2
-        if segs is not None and kv_scale is None and self.attn_mma and nq // nkv <= 64:
+        fp8_cache = kv_scale is not None and k_cache.shape[-1] == hd           # (the 4-bit cache has hd / 2 bytes per row)
+        if segs is not None and (kv_scale is None or fp8_cache) and self.attn_mma and nq // nkv <= 64:
             rc = self.C.attn_decode_mma(out, o_part, ml_part, q, k_cache, v_cache, proj, segs[0], segs[1], segs[2], segs[3],
-                                        row_kvlen, row_base, row_mask, block_table, kv_block, nq, nkv, hd, nsplit, gated)
+                                        row_kvlen, row_base, row_mask, block_table, kv_block, nq, nkv, hd, nsplit, gated,
+                                        kv_scale if fp8_cache else None)
             if rc == 0:
                 return out
         self.C.attn_decode(out, o_part, ml_part, q, k_cache, v_cache, proj, row_slot, row_kvlen, row_base, row_mask,

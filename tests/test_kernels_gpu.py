@@ -575,3 +575,37 @@ def test_hyper_connection_ops(ops):
     want = tops.hc_combine(res.cpu().clone(), out.cpu(), inj.cpu())
     got = ops.hc_combine(res, out, inj)
     assert torch.allclose(got.cpu(), want, rtol=1e-5, atol=1e-6)
+
+
+@pytest.mark.parametrize("hd,nq,nkv", [(256, 24, 4), (128, 8, 2)])
+def test_attention_decode_mma_fp8_cache(ops, hd, nq, nkv):
+    """The tensor-core decode kernel over an e4m3 cache (byte tiles expanded in shared memory, per-key scales applied to
+    the scores and to P) against the SIMT kernel on the same cache: a 9-row verify segment and two single rows."""
+    kv_block, n_slots, max_blocks = 64, 3, 8
+    nb = n_slots * max_blocks
+    gated = True
+    width = nq * hd * 2 + 2 * nkv * hd
+    bt = torch.arange(nb, device=DEV, dtype=torch.int32).view(n_slots, max_blocks).flip(0).contiguous()
+    rot = 64
+    inv = (1e6 ** (-torch.arange(rot // 2, dtype=torch.float64) / (rot // 2))).float().to(DEV)
+    qn, kn = rnd(hd, scale=0.1, seed=7), rnd(hd, scale=0.1, seed=8)
+    kc = torch.zeros(nb, kv_block, nkv, hd, dtype=torch.uint8, device=DEV)
+    vc = torch.zeros_like(kc)
+    sc = torch.ones(nb, kv_block, nkv, 2, dtype=torch.float32, device=DEV)
+    lens = {0: 200, 1: 333, 2: 70}
+    for slot, n in lens.items():
+        ops.attn_prep(rnd(n, width, seed=10 + slot), qn, kn, inv, torch.full((n,), slot, device=DEV, dtype=torch.int32),
+                      torch.arange(n, device=DEV, dtype=torch.int32), bt, kc, vc, kv_block, nq, nkv, hd, rot, gated, 1e-6,
+                      kv_scale=sc)
+    slot = torch.tensor([0] * 9 + [1, 2], device=DEV, dtype=torch.int32)
+    pos = torch.tensor(list(range(200, 209)) + [333, 70], device=DEV, dtype=torch.int32)
+    kvlen = pos + 1
+    proj = rnd(11, width, seed=30)
+    q = ops.attn_prep(proj, qn, kn, inv, slot, pos, bt, kc, vc, kv_block, nq, nkv, hd, rot, gated, 1e-6, kv_scale=sc)
+    i32 = lambda v: torch.tensor(v, device=DEV, dtype=torch.int32)
+    segs = (i32([0, 1, 2]), i32([0, 9, 10]), i32([9, 1, 1]), 9)
+    for nsplit in (1, 8):
+        a = ops.attention(q, proj, kc, vc, slot, kvlen, bt, kv_block, nq, nkv, hd, gated, nsplit=nsplit, kv_scale=sc, segs=segs)
+        b = ops.attention(q, proj, kc, vc, slot, kvlen, bt, kv_block, nq, nkv, hd, gated, nsplit=nsplit, kv_scale=sc)
+        close(a, b)
+    assert ops.status() == 0
