@@ -45,6 +45,7 @@ class SchedOptions:
     share_min: int = PREFIX_MIN        # shortest common prefix worth waiting for / forking from a running request
     mixed: bool = True                 # decode rows and a prompt chunk share one forward when both are waiting
     tree_rows: int = 0                 # draft rows of a verify tree per request (0 = chains only; needs Drafter.draft_tree)
+    device_sampling: bool = True       # plain sampled decode rows are drawn by the device sampler (no logits copy to the host)
 
     @staticmethod
     def from_env() -> "SchedOptions":
@@ -563,6 +564,16 @@ class Scheduler:
         keep, paths, r = [], [], 0
         taps = self.eng.taps
         any_tree = any(t is not None for t in trees)
+        dev_ids = None
+        if (not spec and not all_greedy and self.opts.device_sampling and self.eng.device.type == "cuda"
+                and hasattr(self.eng.ops, "sample")
+                and all((not a.req.sampling.greedy) and a.req.sampling.presence_penalty == 0
+                        and a.req.sampling.frequency_penalty == 0 and a.req.sampling.repetition_penalty == 1.0
+                        for a in decoders)):
+            # one draw per row on the device (top-k / top-p / min-p as on the host); the per-step seed comes from the
+            # request's own generator, so a seeded request repeats. Penalties and drafts keep the host sampler.
+            seeds = [a.sampler.rng.next_u64() for a in decoders]
+            dev_ids = self.eng.ops.sample(logits, [a.req.sampling for a in decoders], seeds).tolist()
         for a, d, par in zip(decoders, drafts, trees):
             n = 1 + len(d)
             if par is not None:
@@ -598,6 +609,9 @@ class Scheduler:
                     new.append(t)
                     if i < len(d) and t != d[i]:
                         break
+            elif dev_ids is not None:
+                new = [int(dev_ids[r])]
+                a.sampler.observe(new[0])
             else:
                 new = a.sampler.spec_accept(logits[r:r + n], d)
             acc = len(new) - 1
