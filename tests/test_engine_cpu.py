@@ -171,3 +171,33 @@ def test_int4_kv_cache_stays_close_to_the_16bit_cache():
     kl = torch.nn.functional.kl_div(torch.log_softmax(b, -1), torch.log_softmax(a, -1), log_target=True,
                                     reduction="batchmean").item()
     assert kl < 1e-3, kl
+
+
+def test_host_statements_of_the_small_ops():
+    """The fp32 statements the GPU tests compare the drafter and hyper-connection kernels against, checked on values
+    worked out by hand."""
+    import torch
+    from ferrite_b200.ops.torch_ops import TorchOps
+    t = TorchOps("cpu", torch.float32)
+    g = torch.Generator().manual_seed(0)
+    x, c, b = torch.randn(8, 64, generator=g), torch.randn(8, 16, generator=g), torch.randn(2, 64, generator=g)
+    y = t.dynconv(x, c, b, 8, 4)
+    j, r = 13, 5
+    want = (b[0, j] + c[r, j // 8]) * x[r, j] + (b[1, j] + c[r, 8 + j // 8]) * x[r - 1, j]
+    assert abs(float(y[r, j]) - float(want)) < 1e-5
+    assert abs(float(y[4, j]) - float((b[0, j] + c[4, j // 8]) * x[4, j])) < 1e-5          # first row of a block: one tap
+    vals = torch.tensor([[[5.0] + [0.0] * 15], [[5.0] + [1.0] * 15]])                      # two ranks, one row
+    ids = torch.stack([torch.arange(100, 116)[None], torch.arange(16)[None]]).to(torch.int32)
+    ov, oi = t.topk16_merge(vals, ids)
+    assert oi[0, :2].tolist() == [0, 100] and ov[0, :3].tolist() == [5.0, 5.0, 1.0]         # tie goes to the lower id
+    a_cb, b_cb, gate = torch.eye(4)[:, :4].repeat(1, 64), torch.eye(4).repeat(1, 64), torch.ones(2, 256)
+    cand = torch.tensor([[0, 1, 2, 3] * 4, [3, 2, 1, 0] * 4], dtype=torch.int32)
+    out = t.draft_select(torch.zeros(2, 16), cand, gate, a_cb, b_cb, 2)
+    assert out.tolist() == [2, 2]                      # <A[pred] * gate, B[c]> peaks at c == pred
+    res = torch.ones(3, 4, 8)
+    yn, inv = t.hc_norm(res, torch.ones(4, 8), 0.0)
+    assert torch.allclose(inv, torch.ones(12)) and torch.allclose(yn, torch.ones(12, 8))
+    mixed = t.hc_mix(res, inv, torch.ones(4, 8), torch.zeros(3, 4, 8))
+    assert torch.allclose(mixed, torch.full((3, 8), 0.5))
+    r2 = t.hc_combine(res.clone(), torch.ones(3, 8), torch.zeros(3, 4))
+    assert torch.allclose(r2, torch.full((3, 4, 8), 2.0))
