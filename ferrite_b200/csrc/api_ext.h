@@ -8,8 +8,16 @@ extern "C" {
 #endif
 
 // ---- comm.cu: kernels over NVLink peer memory. `peers` = base pointer of the symmetric workspace on every rank
-// (host array, peers[rank] is the local mapping); epochs = local device array of max_ctas counters. ----
+// (host array, peers[rank] is the local mapping); epochs = local device array of two words: the epoch of the last
+// finished call and the count of CTAs of the running call that have finished. ----
 long fb_comm_workspace_bytes(int max_ctas, long slot_floats);
+// Profiling: a device buffer of fb_comm_trace_recs() x fb_comm_trace_words() u64 that CTA 0 of every fused GEMV +
+// all-reduce fills with device timestamps (null switches it off; set it before capturing a CUDA graph), and the
+// switch that makes the exchange poll its sources one after the other (the earlier protocol, kept for comparison).
+void fb_comm_trace_set(unsigned long long* buf);
+int fb_comm_trace_recs();
+int fb_comm_trace_words();
+void fb_comm_serial_polls_set(int on);
 int fb_gemv_allreduce(void* Y, const void* X, const void* W, const void* res, int M, int N, int K, long ldx, long ldy,
                       const void* const* peers, int rank, int world, int max_ctas, long slot_floats, uint32_t* epochs,
                       int* status, unsigned spin_limit, int max_resident, cudaStream_t s);
@@ -24,11 +32,12 @@ int fb_comm_wait_probe(const uint32_t* flag, uint32_t want, unsigned limit, int*
 // ---- gemv_nvfp4.cu: NVFP4-weight GEMV (W4A16), plain and with the fused one-shot all-reduce ----
 int fb_gemv_nvfp4(void* Y, const void* X, const void* Wq, const void* Sc, float global_scale, const void* norm_w,
                   const void* res, int M, int N, int K, long ldx, long ldy, long sc_stride, float eps, int out_f32,
-                  int mode, int sm_count, cudaStream_t s);
+                  int mode, int sm_count, const float* row_alpha, cudaStream_t s);
 int fb_gemv_nvfp4_allreduce(void* Y, const void* X, const void* Wq, const void* Sc, float global_scale,
                             const void* res, int M, int N, int K, long ldx, long ldy, long sc_stride,
                             const void* const* peers, int rank, int world, int max_ctas, long slot_floats,
-                            uint32_t* epochs, int* status, unsigned spin_limit, int max_resident, cudaStream_t s);
+                            uint32_t* epochs, int* status, unsigned spin_limit, int max_resident,
+                            const float* row_alpha, cudaStream_t s);
 
 // ---- gemm_nvfp4.cu: activation quantiser and block-scaled tcgen05 GEMM (W4A4) ----
 long fb_nvfp4_sf_bytes(int rows, int K);

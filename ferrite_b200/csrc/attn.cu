@@ -594,7 +594,14 @@ static thread_local char g_attn_static_err[256] = "";
 extern "C" long fb_attn_decode_static_scratch_bytes(void) { return fb::ATT_STATIC_FLOATS * (long)sizeof(float); }
 
 extern "C" long fb_attn_decode_static_need_bytes(int rows, int nq, int hd, int nsplit) {
-  return (long)rows * nq * nsplit * (hd + 2) * (long)sizeof(float);
+  if (rows < 0 || nq < 0 || hd < 0 || nsplit < 0) return -1;
+  const long sat = 1l << 52;                       // the answer for sizes whose product would not fit
+  if (hd > (1 << 16)) return sat;
+  long v = (long)rows * (long)nq;                  // < 2^62
+  if (v > (1l << 30)) return sat;
+  v *= (long)nsplit;                               // < 2^61
+  if (v > (1l << 30)) return sat;
+  return v * ((long)hd + 2) * (long)sizeof(float); // < 2^30 * 2^17 * 4
 }
 
 extern "C" const char* fb_attn_decode_static_error(void) { return fb::g_attn_static_err; }
@@ -609,6 +616,13 @@ extern "C" int fb_attn_decode_static(void* out, const void* q, const void* k_cac
   if (rows <= 0) return 0;
   if (nq <= 0 || nkv <= 0 || hd <= 0 || nsplit <= 0) {
     snprintf(g_attn_static_err, sizeof g_attn_static_err, "fb_attn_decode_static: non-positive size");
+    return -1;
+  }
+  // sizes no call can mean: refused before the byte count is formed, so the product below cannot wrap
+  if (rows > (1 << 20) || nq > 4096 || nsplit > 1024 || (hd != 64 && hd != 128 && hd != 256)) {
+    snprintf(g_attn_static_err, sizeof g_attn_static_err,
+             "fb_attn_decode_static: rows=%d nq=%d hd=%d nsplit=%d outside rows<=2^20, nq<=4096, nsplit<=1024, hd in {64,128,256}",
+             rows, nq, hd, nsplit);
     return -1;
   }
   const long need = fb_attn_decode_static_need_bytes(rows, nq, hd, nsplit);

@@ -66,25 +66,28 @@ void comm_wait_probe(Tensor flag, int64_t want, int64_t limit, Tensor status) {
 }
 
 void gemv_nvfp4(Tensor Y, Tensor X, Tensor packed, Tensor scales, double global_scale, c10::optional<Tensor> norm_w,
-                c10::optional<Tensor> res, double eps, int64_t mode) {
+                c10::optional<Tensor> res, double eps, int64_t mode, c10::optional<Tensor> row_alpha) {
   int M = (int)X.size(0), K = (int)X.size(1);
   int N = (int)(mode == 1 ? packed.size(0) / 2 : packed.size(0));
   TORCH_CHECK(packed.size(1) * 2 == K, "gemv_nvfp4: K mismatch");
+  TORCH_CHECK(!row_alpha.has_value() || (row_alpha->scalar_type() == torch::kFloat32 && row_alpha->numel() == packed.size(0)),
+              "gemv_nvfp4: row_alpha is fp32 [weight rows]");
   check(fb_gemv_nvfp4(Y.data_ptr(), X.data_ptr(), packed.data_ptr(), scales.data_ptr(), (float)global_scale,
                       cptr(norm_w), cptr(res), M, N, K, (long)X.stride(0), (long)Y.stride(0), (long)scales.stride(0),
                       (float)eps, Y.scalar_type() == torch::kFloat32 ? 1 : 0, (int)mode,
-                      at::cuda::getCurrentDeviceProperties()->multiProcessorCount, cur_stream()), "gemv_nvfp4");
+                      at::cuda::getCurrentDeviceProperties()->multiProcessorCount, (const float*)cptr(row_alpha),
+                      cur_stream()), "gemv_nvfp4");
 }
 
 void gemv_nvfp4_allreduce(const Comm& c, Tensor Y, Tensor X, Tensor packed, Tensor scales, double global_scale,
-                          c10::optional<Tensor> res) {
+                          c10::optional<Tensor> res, c10::optional<Tensor> row_alpha) {
   int M = (int)X.size(0), K = (int)X.size(1), N = (int)packed.size(0);
   TORCH_CHECK(packed.size(1) * 2 == K, "gemv_nvfp4_allreduce: K mismatch");
   check(fb_gemv_nvfp4_allreduce(Y.data_ptr(), X.data_ptr(), packed.data_ptr(), scales.data_ptr(), (float)global_scale,
                                 cptr(res), M, N, K, (long)X.stride(0), (long)Y.stride(0), (long)scales.stride(0),
                                 c.peers.data(), c.rank, c.world, c.max_ctas, c.slot_floats,
                                 (uint32_t*)c.epochs.data_ptr(), c.status.data_ptr<int>(), c.spin_limit, c.max_resident,
-                                cur_stream()), "gemv_nvfp4_allreduce");
+                                (const float*)cptr(row_alpha), cur_stream()), "gemv_nvfp4_allreduce");
 }
 
 int64_t nvfp4_sf_bytes(int64_t rows, int64_t K) { return fb_nvfp4_sf_bytes((int)rows, (int)K); }
@@ -378,6 +381,17 @@ void register_ext(pybind11::module_& m) {
   m.def("allreduce_oneshot", &allreduce_oneshot);
   m.def("argmax_gather", &argmax_gather);
   m.def("comm_wait_probe", &comm_wait_probe);
+  m.def("comm_trace_set", [](c10::optional<Tensor> buf) {
+    if (buf.has_value() && buf->defined()) {
+      TORCH_CHECK(buf->scalar_type() == torch::kInt64 && buf->is_cuda() && buf->is_contiguous() &&
+                  buf->numel() >= (int64_t)fb_comm_trace_recs() * fb_comm_trace_words(), "comm_trace_set: int64 cuda buffer too small");
+      fb_comm_trace_set(reinterpret_cast<unsigned long long*>(buf->data_ptr()));
+    } else {
+      fb_comm_trace_set(nullptr);
+    }
+  });
+  m.def("comm_trace_shape", []() { return std::make_pair((int64_t)fb_comm_trace_recs(), (int64_t)fb_comm_trace_words()); });
+  m.def("comm_serial_polls_set", [](bool on) { fb_comm_serial_polls_set(on ? 1 : 0); });
   m.def("gemv_nvfp4", &gemv_nvfp4);
   m.def("moe_route", &moe_route);
   m.def("moe_experts", &moe_experts);

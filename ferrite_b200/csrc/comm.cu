@@ -30,6 +30,8 @@ __global__ void __launch_bounds__(GEMV_THREADS) gemv_allreduce_kernel(GemvArgs a
   float* tile = reinterpret_cast<float*>(smem_raw + (size_t)M * a.kc * sizeof(__nv_bfloat16));  // [M][rows_per_cta]
   __shared__ float rscale[M];
   __shared__ float scratch[32];
+  __shared__ unsigned long long stamps[6];
+  const bool traced = cb.trace != nullptr && blockIdx.x == 0;
   const int row0 = blockIdx.x * a.rows_per_cta;
   const int row_end = min(a.N, row0 + a.rows_per_cta);
   const int nrows = row_end - row0;
@@ -43,10 +45,12 @@ __global__ void __launch_bounds__(GEMV_THREADS) gemv_allreduce_kernel(GemvArgs a
       if (n + r < row_end)
 #pragma unroll
         for (int m = 0; m < M; ++m) tile[m * rpc + (n + r - row0)] = acc[r][m];
-  });
+  }, traced ? &stamps[0] : nullptr);
   __syncthreads();
   // slot layout: CTA-major, so a CTA's tile is one contiguous run of M * rows_per_cta floats
-  cta_exchange_sum(cb, tile, M * a.rows_per_cta, (long)blockIdx.x * M * a.rows_per_cta);
+  const uint32_t epoch = comm_epoch_begin(cb);
+  cta_exchange_sum(cb, tile, M * a.rows_per_cta, (long)blockIdx.x * M * a.rows_per_cta, epoch, traced ? stamps : nullptr);
+  __syncthreads();
   for (int i = threadIdx.x; i < a.M * nrows; i += blockDim.x) {
     int m = i / nrows, j = i % nrows;
     float v = tile[m * a.rows_per_cta + j];
@@ -54,6 +58,8 @@ __global__ void __launch_bounds__(GEMV_THREADS) gemv_allreduce_kernel(GemvArgs a
     if (a.res) v += bf2f(a.res[o]);
     reinterpret_cast<__nv_bfloat16*>(a.Y)[o] = f2bf(v);
   }
+  if (traced) comm_trace_flush(cb, stamps, epoch);
+  comm_epoch_end(cb, epoch);
 }
 
 // ---- standalone one-shot all-reduce of [rows][n] partials ---------------------------------------------------
@@ -72,13 +78,14 @@ __global__ void __launch_bounds__(256) allreduce_oneshot_kernel(__nv_bfloat16* _
     }
     tile_s[i] = v;
   }
-  __syncthreads();
-  cta_exchange_sum(cb, tile_s, per_cta, i0);
-  for (int i = threadIdx.x; i < cnt; i += blockDim.x) {
+  const uint32_t epoch = comm_epoch_begin(cb);          // (its barrier also orders the tile fill above)
+  cta_exchange_sum(cb, tile_s, cnt, i0, epoch);          // only the live values travel: nothing is written past `count`
+  for (int i = threadIdx.x; i < cnt; i += blockDim.x) {  // same thread <-> index map as the exchange: no barrier needed
     float v = tile_s[i];
     if (res) v += bf2f(res[i0 + i]);
     y[i0 + i] = f2bf(v);
   }
+  comm_epoch_end(cb, epoch);
 }
 
 // ---- K4: vocab-parallel argmax merged over ranks ------------------------------------------------------------
@@ -123,12 +130,10 @@ __global__ void __launch_bounds__(1024) argmax_gather_kernel(int* __restrict__ i
   // Each rank's candidate travels as one 16-byte store {value, epoch, index, epoch}: both halves carry the epoch,
   // so a reader that sees two matching epoch words has the whole candidate (8-byte halves are written atomically).
   // The candidates live in the top COMM_TOP_RESERVE words of the data slots, apart from the all-reduce pairs.
-  __shared__ uint32_t s_epoch;
   __shared__ int s_fail;
   const int cta = blockIdx.x;
-  if (threadIdx.x == 0) { s_epoch = cb.epochs[cta] + 1; s_fail = 0; }
-  __syncthreads();
-  const uint32_t epoch = s_epoch;
+  if (threadIdx.x == 0) s_fail = 0;
+  const uint32_t epoch = comm_epoch_begin(cb);
   const int parity = epoch & 1;
   const long top = cb.slot_floats - COMM_TOP_RESERVE + (long)cta * 4;
   __shared__ float rv[COMM_MAX_RANKS];
@@ -159,8 +164,8 @@ __global__ void __launch_bounds__(1024) argmax_gather_kernel(int* __restrict__ i
     }
     ids[row] = bidx;
     if (vals) vals[row] = bv;
-    cb.epochs[cta] = epoch;
   }
+  comm_epoch_end(cb, epoch);
 }
 
 // A wait that is made to run out on purpose by a flag nobody sets: exercises the timeout path on one GPU
@@ -207,6 +212,20 @@ static int launch_gemv_ar(GemvArgs a, CommBuf cb, int max_resident, cudaStream_t
 
 using namespace fb;
 
+// Profiling switches shared by every file that fills a CommBuf. The trace buffer must be set before a CUDA
+// graph is captured (kernel arguments are baked into the graph).
+static unsigned long long* g_comm_trace = nullptr;
+static int g_comm_serial = -1;
+extern "C" unsigned long long* fb_comm_trace_get() { return g_comm_trace; }
+extern "C" void fb_comm_trace_set(unsigned long long* buf) { g_comm_trace = buf; }
+extern "C" int fb_comm_serial_polls_get() {
+  if (g_comm_serial < 0) { const char* e = getenv("FB_COMM_SERIAL_POLLS"); g_comm_serial = (e && e[0] == '1') ? 1 : 0; }
+  return g_comm_serial;
+}
+extern "C" void fb_comm_serial_polls_set(int on) { g_comm_serial = on ? 1 : 0; }
+extern "C" int fb_comm_trace_recs() { return COMM_TRACE_RECS; }
+extern "C" int fb_comm_trace_words() { return COMM_TRACE_WORDS; }
+
 extern "C" long fb_comm_workspace_bytes(int max_ctas, long slot_floats) {
   return (long)2 * COMM_MAX_RANKS * max_ctas * 4 + (long)2 * COMM_MAX_RANKS * slot_floats * 4;
 }
@@ -234,7 +253,7 @@ extern "C" int fb_allreduce_oneshot(void* y, const void* part, const void* res, 
                                     uint32_t* epochs, int* status, unsigned spin_limit, int max_resident,
                                     cudaStream_t s) {
   if (count <= 0) return 0;
-  if (count * 2 > slot_floats - COMM_TOP_RESERVE) return -8;
+  if (count * 2 > slot_floats - COMM_TOP_RESERVE) return -8;     // pairs stay below the argmax candidates
   CommBuf cb;
   fill_comm(cb, peers, rank, world, max_ctas, slot_floats, epochs, status, spin_limit);
   int grid = max_resident < max_ctas ? max_resident : max_ctas;

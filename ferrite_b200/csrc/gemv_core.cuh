@@ -147,7 +147,7 @@ __device__ __forceinline__ void gemv_row_ptrs(const GemvArgs& a, const __nv_bflo
 // lane of the warp with the warp-reduced sums of row group n.
 template <int M, int R, bool SWIGLU, class Store>
 __device__ __forceinline__ void gemv_main(const GemvArgs& a, __nv_bfloat16* xs, float* rscale, float* scratch,
-                                          Store store) {
+                                          Store store, unsigned long long* wait_stamp = nullptr) {
   const int warp = threadIdx.x >> 5;
   const int row0 = blockIdx.x * a.rows_per_cta;
   const int row_end = min(a.N, row0 + a.rows_per_cta);
@@ -162,6 +162,8 @@ __device__ __forceinline__ void gemv_main(const GemvArgs& a, __nv_bfloat16* xs, 
   gemv_row_ptrs<R, SWIGLU>(a, wrow, n);
   gemv_load_batch<R>(wv, wrow, 0, a.K);
   pdl_wait();
+  if (wait_stamp != nullptr && threadIdx.x == 0)       // profiling: when the previous kernel of the stream had finished
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(*wait_stamp));
 
   if (a.norm_w) gemv_row_scales<M>(a, rscale, scratch);
 

@@ -34,6 +34,7 @@ struct Gemv4Args {
   const __nv_bfloat16* res;
   void* Y;
   float global_scale;
+  const float* row_alpha;       // null, or one tensor scale per weight row (fused checkpoint parts); replaces global_scale
   int M, N, K;
   long ldx, ldy;
   long sc_stride;
@@ -228,9 +229,12 @@ __device__ __forceinline__ void gemv4_main(const Gemv4Args& a, __half* xs, float
     }
     if (active) {
 #pragma unroll
-      for (int r = 0; r < G4_R; ++r)
+      for (int r = 0; r < G4_R; ++r) {
+        const int wr = SWIGLU ? (min(n, a.N - 1) + r * a.N) : min(n + r, a.N - 1);
+        const float gs = a.row_alpha ? __ldg(a.row_alpha + wr) : a.global_scale;
 #pragma unroll
-        for (int m = 0; m < M; ++m) acc[r][m] = warp_sum(acc[r][m]) * a.global_scale;
+        for (int m = 0; m < M; ++m) acc[r][m] = warp_sum(acc[r][m]) * gs;
+      }
       store(acc, n);
     }
   }
@@ -289,7 +293,9 @@ __global__ void __launch_bounds__(G4_THREADS, 2) gemv_nvfp4_allreduce_kernel(Gem
         for (int m = 0; m < M; ++m) tile[m * rpc + (n + r - row0)] = acc[r][m];
   });
   __syncthreads();
-  cta_exchange_sum(cb, tile, M * rpc, (long)blockIdx.x * M * rpc);
+  const uint32_t epoch = comm_epoch_begin(cb);
+  cta_exchange_sum(cb, tile, M * rpc, (long)blockIdx.x * M * rpc, epoch);
+  __syncthreads();
   for (int i = threadIdx.x; i < a.M * nrows; i += blockDim.x) {
     int m = i / nrows, j = i % nrows;
     float v = tile[m * rpc + j];
@@ -297,6 +303,7 @@ __global__ void __launch_bounds__(G4_THREADS, 2) gemv_nvfp4_allreduce_kernel(Gem
     if (a.res) v += bf2f(a.res[o]);
     reinterpret_cast<__nv_bfloat16*>(a.Y)[o] = f2bf(v);
   }
+  comm_epoch_end(cb, epoch);
 }
 
 template <typename Kern, typename... Args>
@@ -312,9 +319,10 @@ using namespace fb;
 
 static int fill_args(Gemv4Args& a, void* Y, const void* X, const void* Wq, const void* Sc, float gs,
                      const void* norm_w, const void* res, int M, int N, int K, long ldx, long ldy, long sc_stride,
-                     float eps, int out_f32) {
+                     float eps, int out_f32, const float* row_alpha) {
   if (M > 8 || (K % 32) != 0 || (ldx % 8) != 0) return -1;
   a.X = (const __nv_bfloat16*)X; a.Wq = (const uint8_t*)Wq; a.Sc = (const uint8_t*)Sc; a.global_scale = gs;
+  a.row_alpha = row_alpha;
   a.norm_w = (const __nv_bfloat16*)norm_w; a.res = (const __nv_bfloat16*)res; a.Y = Y; a.M = M; a.N = N; a.K = K;
   a.ldx = ldx; a.ldy = ldy; a.sc_stride = sc_stride; a.eps = eps; a.out_f32 = out_f32; a.rows_per_cta = 0; a.kc = 0;
   return 0;
@@ -323,10 +331,11 @@ static int fill_args(Gemv4Args& a, void* Y, const void* X, const void* Wq, const
 // mode: 0 plain (+res), 1 SwiGLU (2N weight rows: gate then up)
 extern "C" int fb_gemv_nvfp4(void* Y, const void* X, const void* Wq, const void* Sc, float global_scale,
                              const void* norm_w, const void* res, int M, int N, int K, long ldx, long ldy,
-                             long sc_stride, float eps, int out_f32, int mode, int sm_count, cudaStream_t s) {
+                             long sc_stride, float eps, int out_f32, int mode, int sm_count, const float* row_alpha,
+                             cudaStream_t s) {
   if (M <= 0 || N <= 0) return 0;
   Gemv4Args a;
-  int rc = fill_args(a, Y, X, Wq, Sc, global_scale, norm_w, res, M, N, K, ldx, ldy, sc_stride, eps, out_f32);
+  int rc = fill_args(a, Y, X, Wq, Sc, global_scale, norm_w, res, M, N, K, ldx, ldy, sc_stride, eps, out_f32, row_alpha);
   if (rc) return rc;
   if (sm_count <= 0) sm_count = 148;
   const int Mt = M == 1 ? 1 : (M == 2 ? 2 : (M <= 4 ? 4 : 8));
@@ -347,10 +356,10 @@ extern "C" int fb_gemv_nvfp4_allreduce(void* Y, const void* X, const void* Wq, c
                                        const void* res, int M, int N, int K, long ldx, long ldy, long sc_stride,
                                        const void* const* peers, int rank, int world, int max_ctas, long slot_floats,
                                        uint32_t* epochs, int* status, unsigned spin_limit, int max_resident,
-                                       cudaStream_t s) {
+                                       const float* row_alpha, cudaStream_t s) {
   if (M <= 0 || N <= 0) return 0;
   Gemv4Args a;
-  int rc = fill_args(a, Y, X, Wq, Sc, global_scale, nullptr, res, M, N, K, ldx, ldy, sc_stride, 0.f, 0);
+  int rc = fill_args(a, Y, X, Wq, Sc, global_scale, nullptr, res, M, N, K, ldx, ldy, sc_stride, 0.f, 0, row_alpha);
   if (rc) return rc;
   if (world > COMM_MAX_RANKS) return -1;
   CommBuf cb;

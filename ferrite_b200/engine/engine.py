@@ -47,12 +47,24 @@ class Engine:
             weights = init_weights(cfg, seed=seed, dtype=self.dtype, device=self.device)
         if world > 1:
             weights = shard_weights(cfg, weights, rank, world)
-        weights = {k: (v.to(self.device) if v.dtype == torch.float32 and k.endswith(("A_log", "dt_bias", "router_bias"))
+        from ..formats.packed import is_packed
+        weights = {k: (v if is_packed(v) else
+                       v.to(self.device) if v.dtype == torch.float32 and k.endswith(("A_log", "dt_bias", "router_bias"))
                        else v.to(self.device, self.dtype)) for k, v in weights.items()}
+        # linears that arrived packed from a quantised checkpoint (ModelOpt NVFP4 / FP8, EXL3) become the kernels' weight
+        # objects here, after the tensor-parallel cut; on the CPU they are dequantised for the fp32 oracle
+        if any(is_packed(v) for v in weights.values()):
+            from ..ops.qweight import from_packed
+            for k in list(weights.keys()):
+                if is_packed(weights[k]):
+                    weights[k] = from_packed(weights[k], self.device, self.dtype, on_gpu)
+        is_t = lambda v: isinstance(v, torch.Tensor)
         if self.ecfg.weight_dtype in ("nvfp4", "nvfp4-a16"):
             from ..ops.qweight import quantize_experts, quantize_weight
             big = ("in_proj", "out_proj", "gate_up", "down", "lm_head")
             for k in list(weights.keys()):
+                if not is_t(weights[k]):
+                    continue
                 if k.split(".")[-1] in big and weights[k].dim() == 2 and weights[k].shape[1] % 32 == 0:
                     weights[k] = quantize_weight(weights[k], "nvfp4", keep_dense=True, dense_dtype=self.dtype)
                 elif k.split(".")[-1] in ("experts_gate_up", "experts_down") and weights[k].shape[2] % 16 == 0:
@@ -63,10 +75,27 @@ class Engine:
             from ..ops.qweight import quantize_weight
             big = ("in_proj", "out_proj", "gate_up", "down")
             for k in list(weights.keys()):
-                if k.split(".")[-1] in big and weights[k].dim() == 2:
+                if is_t(weights[k]) and k.split(".")[-1] in big and weights[k].dim() == 2:
                     weights[k] = quantize_weight(weights[k], "fp8b", keep_dense=True, dense_dtype=self.dtype)
+        elif self.ecfg.weight_dtype in ("exl3", "exl3-4", "exl3-3", "exl3-5"):
+            # synthetic EXL3 weights of the architecture's shapes (random bit streams are valid tensors): what a
+            # benchmark of the trellis kernels needs when no checkpoint is at hand
+            from ..formats.exl3 import Exl3Tensor
+            from ..formats.packed import PackedEXL3
+            from ..ops.qweight import from_packed
+            bits = int(self.ecfg.weight_dtype[-1]) if self.ecfg.weight_dtype[-1].isdigit() else 4
+            big = ("in_proj", "out_proj", "gate_up", "down")
+            for j, k in enumerate(list(weights.keys())):
+                t = weights[k]
+                if is_t(t) and k.split(".")[-1] in big and t.dim() == 2 and t.shape[0] >= 128 and t.shape[1] % 128 == 0:
+                    main = t.shape[0] // 128 * 128       # rows past the last 128-row block (the b | a rows) stay dense
+                    p = PackedEXL3(Exl3Tensor.random(t.shape[1], main, bits, seed=seed * 1000 + j))
+                    if main < t.shape[0]:
+                        from ..formats.packed import PackedStack
+                        p = PackedStack([p, t[main:].cpu()])
+                    weights[k] = from_packed(p, self.device, self.dtype, on_gpu)
         elif self.ecfg.weight_dtype != "bf16":
-            raise ValueError(f"weight_dtype {self.ecfg.weight_dtype!r} is not wired into the engine yet")
+            raise ValueError(f"weight_dtype {self.ecfg.weight_dtype!r}: expected bf16, nvfp4, nvfp4-a16, fp8-block or exl3")
         self.cfg = cfg.shard(world)
         if on_gpu:
             from ..ops.cuda_ops import CudaOps

@@ -45,22 +45,42 @@ class Sampling:
     banned_first: List[int] = field(default_factory=list)     # ids that may not open the reply (first-token stop ban)
 
     @property
-    def greedy(self) -> bool:
+    def argmax(self) -> bool:
+        """Temperature 0: the pick is the arg-max of the (possibly penalised) logits."""
         return self.temperature <= 0.0
 
+    @property
+    def penalised(self) -> bool:
+        return self.presence_penalty != 0 or self.frequency_penalty != 0 or self.repetition_penalty != 1.0
 
-def penalize(logits: torch.Tensor, counts: Dict[int, int], s: Sampling) -> torch.Tensor:
-    """Presence / frequency / repetition penalties over the tokens generated so far (counts: id -> occurrences)."""
-    if not counts or (s.presence_penalty == 0 and s.frequency_penalty == 0 and s.repetition_penalty == 1.0):
+    @property
+    def greedy(self) -> bool:
+        """The device arg-max kernel may pick this request's tokens: temperature 0 and every penalty neutral (the
+        reference's `greedy()`, `crates/fe-model/src/sched.rs:162`). A temperature-0 request with penalties takes the
+        host sampler's arg-max, so its output does not depend on what else is in the batch."""
+        return self.temperature <= 0.0 and not self.penalised
+
+
+def penalize(logits: torch.Tensor, counts: Dict[int, int], s: Sampling, seen: Optional[Sequence[int]] = None) -> torch.Tensor:
+    """Presence and frequency penalties over the tokens generated so far (counts: id -> occurrences); the repetition
+    penalty over the union of the prompt's tokens (`seen`) and the generated ones, as in the reference (`penalize`,
+    `crates/fe-model/src/sched.rs:2158`)."""
+    if not s.penalised:
         return logits
     out = logits.clone()
-    ids = torch.tensor(list(counts.keys()), dtype=torch.long)
-    cnt = torch.tensor(list(counts.values()), dtype=out.dtype)
-    v = out[ids]
     if s.repetition_penalty != 1.0 and s.repetition_penalty > 0:
-        v = torch.where(v > 0, v / s.repetition_penalty, v * s.repetition_penalty)
-    v = v - s.presence_penalty - s.frequency_penalty * cnt
-    out[ids] = v
+        rep = set(counts.keys())
+        if seen:
+            rep.update(int(t) for t in seen)
+        rep = [t for t in rep if 0 <= t < out.numel()]
+        if rep:
+            ids = torch.tensor(sorted(rep), dtype=torch.long)
+            v = out[ids]
+            out[ids] = torch.where(v > 0, v / s.repetition_penalty, v * s.repetition_penalty)
+    if counts and (s.presence_penalty != 0 or s.frequency_penalty != 0):
+        ids = torch.tensor(list(counts.keys()), dtype=torch.long)
+        cnt = torch.tensor(list(counts.values()), dtype=out.dtype)
+        out[ids] = out[ids] - s.presence_penalty - s.frequency_penalty * cnt
     return out
 
 
@@ -104,21 +124,23 @@ def draw_excluding(p: torch.Tensor, rng: SplitMix64, excluded: int) -> int:
 
 
 class Sampler:
-    def __init__(self, s: Sampling, request_seed: int = 0):
+    def __init__(self, s: Sampling, request_seed: int = 0, prompt: Optional[Sequence[int]] = None):
         self.s = s
         self.rng = SplitMix64(s.seed if s.seed is not None else request_seed)
         self.counts: Dict[int, int] = {}
+        # prompt tokens count for the repetition penalty only
+        self.seen = frozenset(int(t) for t in prompt) if (prompt is not None and s.repetition_penalty != 1.0) else None
 
     def observe(self, tok: int) -> None:
         self.counts[tok] = self.counts.get(tok, 0) + 1
 
     def probs(self, logits: torch.Tensor, first: bool = False) -> torch.Tensor:
-        return dist(penalize(logits.float().cpu(), self.counts, self.s), self.s,
+        return dist(penalize(logits.float().cpu(), self.counts, self.s, self.seen), self.s,
                     self.s.banned_first if first else ())
 
     def sample(self, logits: torch.Tensor, first: bool = False) -> int:
-        if self.s.greedy:
-            lf = penalize(logits.float().cpu(), self.counts, self.s)
+        if self.s.argmax:
+            lf = penalize(logits.float().cpu(), self.counts, self.s, self.seen)
             if first and self.s.banned_first:
                 lf = lf.clone()
                 lf[torch.tensor(self.s.banned_first, dtype=torch.long)] = float("-inf")
@@ -137,7 +159,7 @@ class Sampler:
                 out.append(self.sample(row))
                 break
             d = int(drafts[i])
-            if self.s.greedy:
+            if self.s.argmax:
                 t = self.sample(row)
                 out.append(t)
                 if t != d:

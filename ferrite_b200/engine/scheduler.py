@@ -395,7 +395,7 @@ class Scheduler:
                 if self.drafter:
                     self.drafter.reset(slot)
             self.eng.slot_len[slot] = resume
-            a = Active(req, slot, resume, list(req.prompt[resume:]), Sampler(req.sampling, request_seed=req.rid),
+            a = Active(req, slot, resume, list(req.prompt[resume:]), Sampler(req.sampling, request_seed=req.rid, prompt=req.prompt),
                        Copier() if (self.opts.copy_rows and self.opts.spec > 0) else None, cached=resume,
                        t_submit=time.time(), snap_at=sorted(p for p in req.snapshots if resume < p <= len(req.prompt)))
             self.active[slot] = a
@@ -726,7 +726,8 @@ def generate(sched: Scheduler, prompts: Sequence[Sequence[int]], sampling: Optio
         return f
 
     for i, p in enumerate(prompts):
-        sched.submit(Request(list(p), sampling or Sampling(), sink(i),
+        smp = sampling[i] if isinstance(sampling, (list, tuple)) else sampling      # one Sampling, or one per prompt
+        sched.submit(Request(list(p), smp or Sampling(), sink(i),
                              snapshots=list(snapshots[i]) if snapshots else []))
     guard = 0
     while not all(done):

@@ -80,6 +80,9 @@ class SafeTensors:
     def shape(self, name: str) -> List[int]:
         return self.files[self.where[name]].info(name)[1]
 
+    def dtype(self, name: str) -> torch.dtype:
+        return _DTYPES[self.files[self.where[name]].info(name)[0]]
+
     def get(self, name: str) -> torch.Tensor:
         return self.files[self.where[name]].get(name)
 
@@ -100,7 +103,7 @@ def save_file(tensors: Dict[str, torch.Tensor], path: str, metadata: Optional[Di
     blobs = []
     for name, t in tensors.items():
         t = t.detach().cpu().contiguous()
-        raw = t.view(torch.uint8).numpy().tobytes() if t.numel() else b""
+        raw = t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b""
         header[name] = {"dtype": _NAMES[t.dtype], "shape": list(t.shape), "data_offsets": [off, off + len(raw)]}
         off += len(raw)
         blobs.append(raw)

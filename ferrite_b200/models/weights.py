@@ -17,6 +17,7 @@ from typing import Dict, List
 import torch
 
 from ..config import ModelConfig
+from ..formats.packed import cat_rows
 
 Weights = Dict[str, torch.Tensor]
 
@@ -102,7 +103,8 @@ def shard_weights(cfg: ModelConfig, w: Weights, rank: int, world: int) -> Weight
     """Slice whole-model weights for one tensor-parallel rank. Column-parallel projections keep whole heads
     (KV heads are replicated when world > n_kv), row-parallel ones keep the matching input columns; norms,
     embeddings and the router are replicated, `lm_head` is split by vocabulary rows. Split table modelled
-    on the reference's (`TP2.md:36-50`, `crates/fe-exl3/src/tp.rs`)."""
+    on the reference's (`TP2.md:36-50`, `crates/fe-exl3/src/tp.rs`). Packed quantised linears (`formats/packed.py`)
+    are cut the same way as dense ones: row and column slices move code and scale bytes, nothing is re-quantised."""
     if world == 1:
         return dict(w)
     out: Weights = {}
@@ -125,7 +127,7 @@ def shard_weights(cfg: ModelConfig, w: Weights, rank: int, world: int) -> Weight
             for _ in range(2):  # b, a
                 parts.append(t[o + rank * nvr:o + (rank + 1) * nvr])
                 o += nv
-            out[name] = torch.cat(parts, 0).contiguous()
+            out[name] = cat_rows(parts)
         elif base == "conv_w":
             nk, nv, dk, dv = cfg.lin_k_heads, cfg.lin_v_heads, cfg.lin_dk, cfg.lin_dv
             nkr, nvr = nk // world, nv // world
@@ -134,7 +136,7 @@ def shard_weights(cfg: ModelConfig, w: Weights, rank: int, world: int) -> Weight
             for n_heads, per_rank, d in ((nk, nkr, dk), (nk, nkr, dk), (nv, nvr, dv)):
                 parts.append(t[o + rank * per_rank * d:o + (rank + 1) * per_rank * d])
                 o += n_heads * d
-            out[name] = torch.cat(parts, 0).contiguous()
+            out[name] = cat_rows(parts)
         elif base in ("A_log", "dt_bias"):
             nvr = cfg.lin_v_heads // world
             out[name] = t[rank * nvr:(rank + 1) * nvr].contiguous()
@@ -149,7 +151,7 @@ def shard_weights(cfg: ModelConfig, w: Weights, rank: int, world: int) -> Weight
             vo = ko + cfg.n_kv * hd
             k = t[ko + kv_first * hd:ko + (kv_first + nkvr) * hd]
             v = t[vo + kv_first * hd:vo + (kv_first + nkvr) * hd]
-            out[name] = torch.cat([q, k, v], 0).contiguous()
+            out[name] = cat_rows([q, k, v])
         elif base == "out_proj":
             if kind == "gdn":
                 per = cfg.lin_v_heads // world * cfg.lin_dv
@@ -161,7 +163,7 @@ def shard_weights(cfg: ModelConfig, w: Weights, rank: int, world: int) -> Weight
         elif base in ("gate_up", "shared_gate_up"):
             inter = t.shape[0] // 2
             per = inter // world
-            out[name] = torch.cat([t[rank * per:(rank + 1) * per], t[inter + rank * per:inter + (rank + 1) * per]], 0).contiguous()
+            out[name] = cat_rows([t[rank * per:(rank + 1) * per], t[inter + rank * per:inter + (rank + 1) * per]])
         elif base in ("down", "shared_down"):
             per = t.shape[1] // world
             out[name] = t[:, rank * per:(rank + 1) * per].contiguous()

@@ -15,7 +15,7 @@ import os
 import torch
 
 from .._ext import load
-from .qweight import ExpertsFP4, QWeight
+from .qweight import Exl3Weight, ExpertsFP4, QWeight, StackWeight
 
 GEMV_MAX_ROWS = 8
 MOE_PAIR_ROWS = 64     # up to this many rows (the largest graph-captured step) the experts run as per-pair GEMVs,
@@ -46,6 +46,7 @@ class CudaOps:
         self._kv_scratch = None
         self.fp4_act = False                # NVFP4 weights: quantise activations too and use the tcgen05 GEMM
         self._sf_pool = {}
+        self._scratch = {}
 
     # ---- workspace ---------------------------------------------------------------------------------
     def _workspace(self, nbytes: int) -> torch.Tensor:
@@ -55,6 +56,15 @@ class CudaOps:
 
     def status(self) -> int:
         return int(self.status_word.item())
+
+    def scratch(self, name: str, numel: int, dtype=torch.bfloat16) -> torch.Tensor:
+        """A named device buffer that only grows (its pointer is stable across the steps of a CUDA graph as long as no
+        later call asks for more; callers size it by the largest use up front)."""
+        buf = self._scratch.get(name)
+        if buf is None or buf.numel() < numel or buf.dtype != dtype:
+            buf = torch.empty(numel, dtype=dtype, device=self.device)
+            self._scratch[name] = buf
+        return buf[:numel]
 
     # ---- rows ------------------------------------------------------------------------------------
     def embed(self, table, ids):
@@ -84,6 +94,28 @@ class CudaOps:
         return s
 
     def linear(self, x, w, norm_w=None, eps=1e-6, res=None, swiglu=False, out_f32=False, out=None):
+        if isinstance(w, (Exl3Weight, StackWeight)):
+            # EXL3 (and stacks of differently stored parts): the norm runs once, each part fills its column range, the
+            # SwiGLU / residual run on the joined output. The trellis kernels rotate their own input.
+            if norm_w is not None:
+                x, _ = self.rmsnorm(x, norm_w, eps, True)
+            if isinstance(w, Exl3Weight):
+                y = w.lin.forward(self, x, None if swiglu else res)
+            else:
+                y = torch.cat([self.linear(x, p) for p in w.parts], 1)
+                self.launches += 1
+                if res is not None and not swiglu:
+                    y = y + res
+                    self.launches += 1
+            if swiglu:
+                y = self.silu_mul(y)
+            return y.float() if out_f32 else y
+        if isinstance(w, QWeight) and w.kind == "fp8":
+            # ModelOpt FP8 (per-tensor scales, carried per output row): prompt-sized steps multiply the codes on the
+            # f8f6f4 tensor path with rows quantised on the fly; few-row steps stream the dequantised copy
+            if x.shape[0] > self.mma_gemv_rows[1] and not out_f32 and out is None and w.cols % 128 == 0:
+                return self.linear_fp8(x, w.fp8_codes, w.fp8_scales, norm_w, eps, res, swiglu)
+            w = w.dense
         if isinstance(w, QWeight) and w.kind == "fp8b":
             # block-scaled e4m3: prompt-sized steps multiply the codes on the f8f6f4 tensor path (activations quantised
             # per 1 x 128 block on the fly); few-row steps stream the dequantised copy through the bf16 row kernels
@@ -97,14 +129,15 @@ class CudaOps:
         if isinstance(w, QWeight):
             M = x.shape[0]
             N = w.rows // 2 if swiglu else w.rows
-            if (self.fp4_act and w.mma_scales is not None and w.cols % 256 == 0 and (not out_f32 or M <= 8)
+            if (self.fp4_act and w.row_alpha is None and w.mma_scales is not None and w.cols % 256 == 0 and (not out_f32 or M <= 8)
                     and (not swiglu or N % 128 == 0) and (M <= 64 or N % 8 == 0)):
                 return self._linear_w4a4(x, w, norm_w, eps, res, swiglu, M, N, out_f32)
             if M <= GEMV_MAX_ROWS and not self.force_gemv_chunks:
                 N = w.rows // 2 if swiglu else w.rows
                 y = torch.empty(M, N, dtype=torch.float32 if out_f32 else self.dtype, device=self.device)
                 self.launches += 1
-                self.C.gemv_nvfp4(y, x, w.packed, w.gemv_scales, w.global_scale, norm_w, res, eps, 1 if swiglu else 0)
+                self.C.gemv_nvfp4(y, x, w.packed, w.gemv_scales, w.global_scale, norm_w, res, eps, 1 if swiglu else 0,
+                                  w.row_alpha)
                 return y
             w = w.dense
         M, K = x.shape

@@ -25,8 +25,10 @@ class QWeight:
     global_scale: float
     dense: Optional[torch.Tensor]  # dequantised copy (activation dtype) for the many-row path
     mma_scales: Optional[torch.Tensor] = None
-    fp8_codes: Optional[torch.Tensor] = None     # "fp8b": uint8 [rows, ceil(cols/128)*128]
-    fp8_scales: Optional[torch.Tensor] = None    # "fp8b": fp32 [ceil(rows/128), ceil(cols/128)]
+    fp8_codes: Optional[torch.Tensor] = None     # "fp8b": uint8 [rows, ceil(cols/128)*128]; "fp8": uint8 [rows, cols]
+    fp8_scales: Optional[torch.Tensor] = None    # "fp8b": fp32 [ceil(rows/128), ceil(cols/128)]; "fp8": fp32 [rows]
+    row_alpha: Optional[torch.Tensor] = None     # "nvfp4": fp32 [rows] tensor scale per output row (fused checkpoint parts
+                                                 # bring their own `weight_scale_2`); global_scale is 1 when set
 
     @property
     def shape(self):
@@ -108,3 +110,72 @@ def quantize_experts(w: torch.Tensor) -> ExpertsFP4:
         packed[i] = q.packed
         scales[i] = q.scales.view(torch.uint8)
     return ExpertsFP4(packed, scales, gs)
+
+
+class Exl3Weight:
+    """An EXL3 linear ready for the kernels (`ops/exl3_linear.py`), behind the [out, in] weight surface."""
+    kind = "exl3"
+
+    def __init__(self, lin, rows: int, cols: int, host=None):
+        self.lin, self.rows, self.cols = lin, rows, cols
+        self.host = host                  # the checkpoint tensor (`formats.exl3.Exl3Tensor`), for the oracle
+
+    @property
+    def shape(self):
+        return (self.rows, self.cols)
+
+    def dequantize(self, dtype=torch.float32) -> torch.Tensor:
+        return self.host.weight(torch.float32).t().contiguous().to(dtype)
+
+
+class StackWeight:
+    """Weights of different storage sharing one input, concatenated along the output rows (`formats.packed.PackedStack`
+    after conversion): the linear runs part by part into column ranges of one output."""
+    kind = "stack"
+
+    def __init__(self, parts):
+        self.parts = list(parts)
+        self.rows = sum(p.shape[0] for p in self.parts)
+        self.cols = self.parts[0].shape[1]
+
+    @property
+    def shape(self):
+        return (self.rows, self.cols)
+
+    def dequantize(self, dtype=torch.float32) -> torch.Tensor:
+        return torch.cat([(p.dequantize(dtype) if hasattr(p, "dequantize") else
+                           p.dense.to(dtype) if hasattr(p, "dense") else p.to(dtype)).cpu() for p in self.parts], 0)
+
+
+def from_packed(p, device, dtype, on_gpu: bool, keep_dense: bool = True):
+    """A checkpoint's packed linear (`formats/packed.py`) as the object the linear ops accept. On the CPU (fp32 oracle)
+    that is the dequantised matrix; on the GPU the codes and scales go to the device in the kernels' layouts:
+    NVFP4 -> `QWeight` (GEMV tiling + tensor-core tiling of the block scales, per-row tensor scales when fused parts
+    differ), FP8 -> `QWeight` kind "fp8" (codes + per-row scales for the e4m3 GEMM), EXL3 -> `Exl3Weight`."""
+    from ..formats.packed import PackedEXL3, PackedFP8, PackedNVFP4, PackedStack
+    if isinstance(p, torch.Tensor):
+        return p.to(device, dtype)
+    if not on_gpu:
+        return p.dequantize(torch.float32).to(device, dtype)
+    if isinstance(p, PackedNVFP4):
+        rows, cols = p.shape
+        sc = p.scales.contiguous()
+        alpha = p.alpha.float()
+        uniform = bool((alpha == alpha[0]).all())
+        dense = p.dequantize(torch.float32).to(device, dtype) if keep_dense else None
+        return QWeight("nvfp4", rows, cols, p.packed.contiguous().to(device), nvfp4.tile_scales_gemv(sc).to(device),
+                       float(alpha[0]) if uniform else 1.0, dense,
+                       nvfp4.tile_scales_mma(sc).contiguous().to(device) if cols % 64 == 0 else None,
+                       row_alpha=None if uniform else alpha.contiguous().to(device))
+    if isinstance(p, PackedFP8):
+        rows, cols = p.shape
+        dense = p.dequantize(torch.float32).to(device, dtype)
+        empty = torch.empty(0, dtype=torch.uint8, device=device)
+        return QWeight("fp8", rows, cols, empty, empty, 1.0, dense, None, p.codes.contiguous().to(device),
+                       p.alpha.float().contiguous().to(device))
+    if isinstance(p, PackedEXL3):
+        from .exl3_linear import Exl3Linear
+        return Exl3Weight(Exl3Linear(p.t, device), p.shape[0], p.shape[1], host=p.t)
+    if isinstance(p, PackedStack):
+        return StackWeight([from_packed(q, device, dtype, on_gpu, keep_dense) for q in p.parts])
+    raise TypeError(type(p).__name__)

@@ -151,13 +151,14 @@ class TensorParallel:
     # ---- row-parallel projection + all-reduce + residual --------------------------------------------------
     def linear_allreduce(self, ops, x, w, res):
         M, N = x.shape[0], w.shape[0]
-        fp4 = getattr(w, "kind", None) == "nvfp4"
-        if getattr(w, "kind", None) == "fp8b" and M <= 8:
-            w = w.dense                                  # few rows: the dequantised copy through the bf16 row kernels
-        if self.fused and M <= 8 and not (fp4 and getattr(ops, "fp4_act", False)):
+        kind = getattr(w, "kind", None)
+        fp4 = kind == "nvfp4"
+        if kind in ("fp8b", "fp8") and M <= 8:
+            w, kind = w.dense, None                      # few rows: the dequantised copy through the bf16 row kernels
+        if self.fused and M <= 8 and kind in (None, "nvfp4") and not (fp4 and getattr(ops, "fp4_act", False) and w.row_alpha is None):
             y = torch.empty(M, N, dtype=x.dtype, device=x.device)
             if fp4:
-                self.C.gemv_nvfp4_allreduce(self.comm, y, x, w.packed, w.gemv_scales, w.global_scale, res)
+                self.C.gemv_nvfp4_allreduce(self.comm, y, x, w.packed, w.gemv_scales, w.global_scale, res, w.row_alpha)
             else:
                 self.C.gemv_allreduce(self.comm, y, x, w, res)
             ops.launches += 1
@@ -183,7 +184,7 @@ class TensorParallel:
         parallel MoE block, where every rank holds the partial output of the experts it owns."""
         if self.fused and part.numel() <= ONESHOT_MAX:
             part = part.contiguous()
-            y = torch.empty_like(part)
+            y = torch.empty(part.shape, dtype=torch.bfloat16, device=part.device)     # the kernel rounds the sum to bf16
             self.C.allreduce_oneshot(self.comm, y, part, res)
             ops.launches += 1
             self.stats["oneshot"] += 1

@@ -8,6 +8,12 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run with -m gpu on a B200)")
+    # the fp32 oracle's matmuls must stay fp32: no TF32, whatever the environment says
+    import torch
+    torch.backends.cuda.matmul.allow_tf32 = False
+    torch.backends.cudnn.allow_tf32 = False
+    os.environ.pop("NVIDIA_TF32_OVERRIDE", None)
+    os.environ["TORCH_ALLOW_TF32_CUBLAS_OVERRIDE"] = "0"
 
 
 def pytest_collection_modifyitems(config, items):

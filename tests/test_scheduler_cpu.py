@@ -303,3 +303,31 @@ def test_group_prefill_runs_several_prompts_in_one_forward():
     a = generate(sched, prompts[:2], s)
     b = generate(sched, prompts[:2], s)
     assert a == b and all(len(x) == 5 for x in a)
+
+
+def test_temperature_zero_with_penalties_does_not_depend_on_the_batch():
+    """A temperature-0 request with penalties is not "greedy" for the device arg-max path: it gets the host sampler's
+    penalised arg-max whether it runs alone or beside a sampled request (reference `greedy()`, `sched.rs:162`)."""
+    s = Sampling(temperature=0.0, frequency_penalty=1.5, presence_penalty=0.5, max_tokens=14)
+    assert s.argmax and not s.greedy and Sampling(temperature=0.0).greedy
+    cfg, w, eng = _engine(n_slots=2)
+    p = _prompt(cfg, 24, 31)
+    alone = generate(Scheduler(eng), [p], s)[0]
+    cfg, w, eng = _engine(n_slots=2)
+    sched = Scheduler(eng)
+    other = Sampling(temperature=0.9, top_k=20, seed=3, max_tokens=14)
+    outs = generate(sched, [p, _prompt(cfg, 24, 32)], [s, other])
+    assert outs[0] == alone
+    assert alone != _plain(cfg, w, p, 14)                      # the penalties did change the output
+
+
+def test_repetition_penalty_counts_the_prompt():
+    logits = torch.zeros(16)
+    logits[3], logits[5] = 4.0, 3.9
+    s = Sampling(temperature=0.0, repetition_penalty=2.0)
+    assert Sampler(s, prompt=[1, 2]).sample(logits) == 3
+    assert Sampler(s, prompt=[3, 2]).sample(logits) == 5      # token 3 is in the prompt: 4.0 / 2 < 3.9
+    smp = Sampler(Sampling(temperature=0.0, presence_penalty=1.0), prompt=[3])
+    assert smp.sample(logits) == 3                            # presence / frequency look at generated tokens only
+    smp.observe(3)
+    assert smp.sample(logits) == 5

@@ -312,6 +312,121 @@ def _ep_worker_body(rank, world, port, q):
     dist.destroy_process_group()
 
 
+def _alt_worker(rank, world, port, q):
+    try:
+        _alt_worker_body(rank, world, port, q)
+    except Exception as e:
+        import traceback
+        q.put((rank, False, {"exception": repr(e), "trace": traceback.format_exc()[-1500:]}))
+
+
+def _alt_worker_body(rank, world, port, q):
+    """Kernels of different grids and tile layouts share one workspace: from a freshly zeroed one, alternate the fused
+    GEMV + all-reduce (1 and 4 rows), the standalone one-shot all-reduce and the argmax gather a few calls apart, and
+    check every result (the one-shot sums bit for bit against the rank-ordered fp32 sum) and that all ranks agree.
+    Then decode steps of a tiny MoE model through the engine under tensor parallelism against the CPU oracle."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev,
+                            timeout=datetime.timedelta(seconds=120))
+    from ferrite_b200.ops.cuda_ops import CudaOps
+    from ferrite_b200.parallel.tp import TensorParallel
+    tp = TensorParallel(dist.group.WORLD, dev, fused=True, spin_limit=1 << 22)
+    ops = CudaOps(dev)
+    res, ok = {}, True
+    g = torch.Generator(device=dev).manual_seed(11)
+    N, Kr = 2048, 512
+    wfull = (torch.randn(N, Kr * world, generator=g, device=dev) * 0.03).to(torch.bfloat16)
+    ws = wfull[:, rank * Kr:(rank + 1) * Kr].contiguous()
+    V = 4096 * world
+    bad = []
+
+    def same_everywhere(t):
+        gathered = [torch.empty_like(t) for _ in range(world)]
+        dist.all_gather(gathered, t.contiguous())
+        return all(torch.equal(gathered[0], x) for x in gathered)
+
+    def gemv(M):
+        x = torch.randn(M, Kr * world, generator=g, device=dev).to(torch.bfloat16)
+        r = torch.randn(M, N, generator=g, device=dev).to(torch.bfloat16)
+        y = tp.linear_allreduce(ops, x[:, rank * Kr:(rank + 1) * Kr].contiguous(), ws, r)
+        want = x.float() @ wfull.float().t() + r.float()
+        err = (y.float() - want).abs().max().item() / want.abs().max().item()
+        return err < 2e-2 and same_everywhere(y)
+
+    def oneshot(count):
+        gen_r = torch.Generator(device=dev).manual_seed(1000 + rank + 17 * count)
+        part = torch.randn(1, count, generator=gen_r, device=dev)
+        if count % 2:
+            part = part.to(torch.bfloat16)                # both partial types the kernel takes
+        r = torch.randn(1, count, generator=g, device=dev).to(torch.bfloat16)
+        y = tp.allreduce_rows(ops, part, r)
+        parts = [torch.empty_like(part) for _ in range(world)]
+        dist.all_gather(parts, part)
+        acc = torch.zeros(part.shape, dtype=torch.float32, device=dev)
+        for t in parts:                                   # rank order, fp32, then the residual, then one rounding
+            acc = acc + t.float()
+        want = (acc + r.float()).to(torch.bfloat16)
+        return torch.equal(y, want) and same_everywhere(y)
+
+    def argmax(rows):
+        full = torch.randn(rows, V, generator=g, device=dev)
+        per = V // world
+        shard = full[:, rank * per:(rank + 1) * per].contiguous()
+        _, (ids, _) = tp.gather_logits(ops, shard, True, rank * per, V)
+        return ids.tolist() == full.argmax(-1).tolist()
+
+    seq = []
+    for rnd in range(6):
+        M = 1 if rnd % 2 == 0 else 4
+        seq += [("gemv", M), ("oneshot", 2048), ("argmax", 2 + rnd % 3), ("gemv", M), ("gemv", 5 - M), ("oneshot", 301),
+                ("oneshot", 2048 * 8), ("gemv", M)]
+    for name, arg in seq:
+        good = {"gemv": gemv, "oneshot": oneshot, "argmax": argmax}[name](arg)
+        if not good:
+            bad.append((name, arg))
+    tp.check()
+    res["alternating_bad"] = bad
+    ok = ok and not bad
+    if world == 2:
+        import dataclasses
+        from ferrite_b200.config import EngineConfig, tiny_hybrid
+        from ferrite_b200.engine.engine import Engine
+        from ferrite_b200.engine.executor import Segment
+        from ferrite_b200.models.weights import init_weights
+        cfg = dataclasses.replace(tiny_hybrid(), n_experts=32, top_k=4, expert_inter=64, n_shared=1, router="softmax")
+        w = init_weights(cfg, seed=0)
+        toks = torch.randint(0, cfg.vocab, (40,), generator=torch.Generator().manual_seed(5)).tolist()
+        ref = Engine(cfg, w, EngineConfig(n_slots=1, max_ctx=128), device="cpu")
+        want, _, _ = ref.forward([Segment(0, 0, toks, "all")])
+        tp2 = TensorParallel(dist.group.WORLD, dev, fused=True, spin_limit=1 << 22)
+        eng = Engine(cfg, w, EngineConfig(n_slots=1, max_ctx=128, seq_parallel=False), device=dev, tp=tp2)
+        eng.prefill(0, toks[:32])
+        rows = []
+        for i in range(32, 40):                           # teacher-forced decode rows, one per step (graph replays)
+            lg, _, _ = eng.forward([Segment(0, i, [toks[i]], "last")], greedy=False)
+            rows.append(lg.float().cpu().clone())
+        got = torch.cat(rows)
+        kl = torch.nn.functional.kl_div(torch.log_softmax(got, -1), torch.log_softmax(want[32:40], -1),
+                                        log_target=True, reduction="batchmean").item()
+        res["moe_tp_decode_kl"] = kl
+        res["moe_tp_calls"] = dict(tp2.stats)
+        ok = ok and kl < 2e-2 and same_everywhere(got.to(dev))
+        tp2.check()
+    q.put((rank, ok, res))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_alternating_shapes_share_the_workspace(ext):
+    world = min(torch.cuda.device_count(), 8)
+    if world < 2:
+        pytest.skip("needs 2+ GPUs")
+    _run_ranks(_alt_worker, world)
+
+
+
 def test_expert_parallel_dispatch_combine(ext):
     world = min(torch.cuda.device_count(), 8)
     if world < 2:

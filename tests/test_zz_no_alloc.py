@@ -43,12 +43,12 @@ def _case(rows, ctx, nsplit, seed, nq=8, nkv=2, hd=128, kvb=64):
                 hd=hd, nsplit=nsplit)
 
 
-def _run(lib, c, static):
+def _run(lib, c, static, gated=1):
     out = torch.zeros(c["rows"], c["nq"] * c["hd"], dtype=torch.bfloat16, device=DEV)
     s = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
     common = (c["q"].data_ptr(), c["kc"].data_ptr(), c["vc"].data_ptr(), c["proj"].data_ptr(), c["proj"].stride(0),
               c["slot"].data_ptr(), c["kvlen"].data_ptr(), None, None, c["bt"].data_ptr(), c["nb"], c["kvb"], c["rows"],
-              c["nq"], c["nkv"], c["hd"], c["nsplit"], 1, s)
+              c["nq"], c["nkv"], c["hd"], c["nsplit"], gated, s)
     if static:
         rc = lib.fb_attn_decode_static(out.data_ptr(), *common)
         assert rc == 0, lib.fb_attn_decode_static_error().decode()
@@ -73,6 +73,26 @@ def test_static_scratch_matches_regular_entry_point(ext):
         assert torch.isfinite(got.float()).all()
         assert torch.allclose(got.float(), want.float(), rtol=2e-2, atol=2e-2)
         assert torch.equal(got, want)            # same kernels, same order of operations
+
+
+def test_static_scratch_gated_head_dim_256(ext):
+    """The 27B attention shape (head_dim 256, sigmoid output gate read from the projection row) and the ungated form."""
+    lib = _lib()
+    for gated in (1, 0):
+        c = _case(3, 500, 8, 5 + gated, nq=6, nkv=1, hd=256)
+        want = _run(lib, c, static=False, gated=gated)
+        got = _run(lib, c, static=True, gated=gated)
+        assert torch.isfinite(got.float()).all() and torch.equal(got, want)
+
+
+def test_static_scratch_refuses_sizes_that_would_wrap(ext):
+    lib = _lib()
+    big = 2 ** 31 - 1
+    assert lib.fb_attn_decode_static_need_bytes(big, big, 256, big) > lib.fb_attn_decode_static_scratch_bytes()
+    assert lib.fb_attn_decode_static_need_bytes(-1, 1, 128, 1) == -1
+    rc = lib.fb_attn_decode_static(None, None, None, None, None, 0, None, None, None, None, None, 1, 64, big, big, 8, 128,
+                                   big, 1, None)
+    assert rc == -1 and "outside" in lib.fb_attn_decode_static_error().decode()
 
 
 def test_static_scratch_rejects_oversize(ext):
