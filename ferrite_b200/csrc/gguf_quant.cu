@@ -3,31 +3,42 @@
 // reads the checkpoint's own blocks. One device routine decodes a 32-value group of any supported type, so the
 // dequantiser and the GEMV cannot disagree.
 //
-// Types: Q8_0, Q4_0, Q4_1, Q5_0, Q5_1, IQ4_NL, MXFP4 (32-value blocks) and Q4_K, Q5_K, Q6_K, IQ4_XS (256-value
-// super-blocks of eight 32-value groups). The codebook types (IQ1/IQ2/IQ3) and Q2_K/Q3_K are parsed by the reader
-// but not decoded here. Counterparts in the reference: `ggq_deq_*`, `ggq_q8_1`, `ggq_gemv_*`
-// (`kernels/k-gguf/src/{deq,q8,gemv}.rs`), host reference `crates/fe-ggq/src/refq.rs`.
+// Types: Q8_0, Q4_0, Q4_1, Q5_0, Q5_1, IQ4_NL, MXFP4 (32-value blocks) and Q2_K, Q3_K, Q4_K, Q5_K, Q6_K, IQ4_XS and the
+// codebook types IQ1_S, IQ1_M, IQ2_XXS, IQ2_XS, IQ2_S, IQ3_XXS, IQ3_S (256-value super-blocks of eight 32-value
+// groups; grids in `gguf_tables.cuh`). Every product is written with explicit single roundings in the order of the
+// host decoder (`formats/gguf.py`), so device and host agree bit for bit. Counterparts in the reference: `ggq_deq_*`,
+// `ggq_q8_1`, `ggq_gemv_*` (`kernels/k-gguf/src/{deq,q8,gemv}.rs`), block decoders `dec.rs` / `vq.rs` / `tables.rs`,
+// host reference `crates/fe-ggq/src/refq.rs`.
 #include <cuda_fp16.h>
 
 #include "api_ext.h"
 #include "common.cuh"
+#include "gguf_tables.cuh"
 
 namespace fb {
 
-enum GgmlType { GT_Q4_0 = 2, GT_Q4_1 = 3, GT_Q5_0 = 6, GT_Q5_1 = 7, GT_Q8_0 = 8, GT_Q4_K = 12, GT_Q5_K = 13,
-                GT_Q6_K = 14, GT_IQ4_NL = 20, GT_IQ4_XS = 23, GT_MXFP4 = 39 };
+enum GgmlType { GT_Q4_0 = 2, GT_Q4_1 = 3, GT_Q5_0 = 6, GT_Q5_1 = 7, GT_Q8_0 = 8, GT_Q2_K = 10, GT_Q3_K = 11, GT_Q4_K = 12,
+                GT_Q5_K = 13, GT_Q6_K = 14, GT_IQ2_XXS = 16, GT_IQ2_XS = 17, GT_IQ3_XXS = 18, GT_IQ1_S = 19, GT_IQ4_NL = 20,
+                GT_IQ3_S = 21, GT_IQ2_S = 22, GT_IQ4_XS = 23, GT_IQ1_M = 29, GT_MXFP4 = 39 };
 
 __device__ __constant__ float kIq4nl[16] = {-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113};
 __device__ __constant__ float kMxfp4[16] = {0, 1, 2, 3, 4, 6, 8, 12, 0, -1, -2, -3, -4, -6, -8, -12};
 
 __host__ __device__ inline int gg_block_values(int t) {
-  return (t == GT_Q4_K || t == GT_Q5_K || t == GT_Q6_K || t == GT_IQ4_XS) ? 256 : 32;
+  switch (t) {
+    case GT_Q2_K: case GT_Q3_K: case GT_Q4_K: case GT_Q5_K: case GT_Q6_K: case GT_IQ4_XS: case GT_IQ2_XXS: case GT_IQ2_XS:
+    case GT_IQ2_S: case GT_IQ3_XXS: case GT_IQ3_S: case GT_IQ1_S: case GT_IQ1_M: return 256;
+  }
+  return 32;
 }
 __host__ __device__ inline int gg_block_bytes(int t) {
   switch (t) {
     case GT_Q4_0: return 18; case GT_Q4_1: return 20; case GT_Q5_0: return 22; case GT_Q5_1: return 24;
     case GT_Q8_0: return 34; case GT_Q4_K: return 144; case GT_Q5_K: return 176; case GT_Q6_K: return 210;
     case GT_IQ4_NL: return 18; case GT_IQ4_XS: return 136; case GT_MXFP4: return 17;
+    case GT_Q2_K: return 84; case GT_Q3_K: return 110; case GT_IQ2_XXS: return 66; case GT_IQ2_XS: return 74;
+    case GT_IQ2_S: return 82; case GT_IQ3_XXS: return 98; case GT_IQ3_S: return 110; case GT_IQ1_S: return 50;
+    case GT_IQ1_M: return 56;
   }
   return 0;
 }
@@ -36,6 +47,15 @@ __device__ __forceinline__ float ld_half(const unsigned char* p) {
   const unsigned short u = (unsigned short)p[0] | ((unsigned short)p[1] << 8);
   return __half2float(__ushort_as_half(u));
 }
+
+__device__ __forceinline__ unsigned ld_u16(const unsigned char* p) { return (unsigned)p[0] | ((unsigned)p[1] << 8); }
+__device__ __forceinline__ unsigned ld_u32(const unsigned char* p) { return ld_u16(p) | (ld_u16(p + 2) << 16); }
+// value j (int8) of an 8-value / 4-value grid entry, with the sign bit j of `signs` applied
+__device__ __forceinline__ float grid8(uint64_t e, int j, unsigned signs) {
+  const float v = (float)(signed char)((e >> (8 * j)) & 0xFF);
+  return ((signs >> j) & 1) ? -v : v;
+}
+__device__ __forceinline__ float grid4(uint32_t e, int j) { return (float)(signed char)((e >> (8 * j)) & 0xFF); }
 
 // six-bit (scale, min) pair j of a K-quant super-block (12 packed bytes)
 __device__ __forceinline__ void k4_scale_min(const unsigned char* sc, int j, float& s, float& m) {
@@ -87,6 +107,76 @@ __device__ __forceinline__ float gg_value(int type, const unsigned char* b, int 
       const int ls = ((b[4 + (g >> 1)] >> (4 * (g & 1))) & 0xF) | (((sh >> (2 * g)) & 3) << 4);
       const unsigned char q = b[8 + g * 16 + (l & 15)];
       return ld_half(b) * (float)(ls - 32) * kIq4nl[l < 16 ? (q & 0xF) : (q >> 4)];
+    }
+    case GT_Q2_K: {
+      const unsigned char sc = b[g * 2 + (l >> 4)];
+      const float q = (float)((b[16 + (g >> 2) * 32 + l] >> (2 * (g & 3))) & 3);
+      return __fsub_rn(__fmul_rn(__fmul_rn(ld_half(b + 80), (float)(sc & 0xF)), q), __fmul_rn(ld_half(b + 82), (float)(sc >> 4)));
+    }
+    case GT_Q3_K: {
+      const int k = g * 2 + (l >> 4);
+      const unsigned char* sc = b + 96;
+      const int low = k < 8 ? (sc[k] & 0xF) : (sc[k - 8] >> 4);
+      const int scale = (low | (((sc[8 + (k & 3)] >> (2 * (k >> 2))) & 3) << 4)) - 32;
+      const int q = ((b[32 + (g >> 2) * 32 + l] >> (2 * (g & 3))) & 3) - ((b[l] >> g) & 1 ? 0 : 4);
+      return __fmul_rn(__fmul_rn(ld_half(b + 108), (float)scale), (float)q);
+    }
+    case GT_IQ2_XXS: {
+      const unsigned char* q = b + 2 + 8 * g;
+      const unsigned aux = ld_u32(q + 4);
+      const float db = __fmul_rn(__fmul_rn(ld_half(b), 0.5f + (float)(aux >> 28)), 0.25f);
+      const int e = l >> 3;
+      return __fmul_rn(db, grid8(gguf_iq2xxs_grid[q[e]], l & 7, gguf_ksigns[(aux >> (7 * e)) & 127]));
+    }
+    case GT_IQ2_XS: {
+      const int e = l >> 3;
+      const unsigned q = ld_u16(b + 2 + (g * 4 + e) * 2);
+      const unsigned char sc = b[66 + g];
+      const float db = __fmul_rn(__fmul_rn(ld_half(b), 0.5f + (float)(e < 2 ? (sc & 0xF) : (sc >> 4))), 0.25f);
+      return __fmul_rn(db, grid8(gguf_iq2xs_grid[q & 511], l & 7, gguf_ksigns[q >> 9]));
+    }
+    case GT_IQ2_S: {
+      const int e = l >> 3;
+      const unsigned idx = (unsigned)b[2 + g * 4 + e] | (((unsigned)b[66 + g] << (8 - 2 * e)) & 0x300);
+      const unsigned char sc = b[74 + g];
+      const float db = __fmul_rn(__fmul_rn(ld_half(b), 0.5f + (float)(e < 2 ? (sc & 0xF) : (sc >> 4))), 0.25f);
+      return __fmul_rn(db, grid8(gguf_iq2s_grid[idx], l & 7, b[34 + g * 4 + e]));
+    }
+    case GT_IQ3_XXS: {
+      const unsigned aux = ld_u32(b + 66 + 4 * g);
+      const float db = __fmul_rn(__fmul_rn(ld_half(b), 0.5f + (float)(aux >> 28)), 0.5f);
+      const float v = grid4(gguf_iq3xxs_grid[b[2 + g * 8 + (l >> 2)]], l & 3);
+      const unsigned signs = gguf_ksigns[(aux >> (7 * (l >> 3))) & 127];
+      return __fmul_rn(db, ((signs >> (l & 7)) & 1) ? -v : v);
+    }
+    case GT_IQ3_S: {
+      const unsigned char sc = b[106 + (g >> 1)];
+      const float db = __fmul_rn(ld_half(b), 1.f + 2.f * (float)((g & 1) ? (sc >> 4) : (sc & 0xF)));
+      const int e4 = l >> 2;
+      const unsigned idx = (unsigned)b[2 + g * 8 + e4] | ((((unsigned)b[66 + g] >> e4) & 1) << 8);
+      const float v = grid4(gguf_iq3s_grid[idx], l & 3);
+      return __fmul_rn(db, ((b[74 + g * 4 + (l >> 3)] >> (l & 7)) & 1) ? -v : v);
+    }
+    case GT_IQ1_S: {
+      const unsigned qh = ld_u16(b + 34 + 2 * g);
+      const float dl = __fmul_rn(ld_half(b), (float)(2 * ((qh >> 12) & 7) + 1));
+      const int e = l >> 3;
+      const unsigned idx = (unsigned)b[2 + g * 4 + e] | (((qh >> (3 * e)) & 7) << 8);
+      const float v = (float)(signed char)((gguf_iq1s_grid[idx] >> (8 * (l & 7))) & 0xFF);
+      return __fmul_rn(dl, v + ((qh & 0x8000) ? -0.125f : 0.125f));
+    }
+    case GT_IQ1_M: {
+      const unsigned s0 = ld_u16(b + 48), s1 = ld_u16(b + 50), s2 = ld_u16(b + 52), s3 = ld_u16(b + 54);
+      const unsigned short dbits = (unsigned short)((s0 >> 12) | ((s1 >> 8) & 0x00F0) | ((s2 >> 4) & 0x0F00) | (s3 & 0xF000));
+      const float d = __half2float(__ushort_as_half(dbits));
+      const int e = l >> 3;
+      const unsigned w = (g >> 1) == 0 ? s0 : (g >> 1) == 1 ? s1 : (g >> 1) == 2 ? s2 : s3;
+      const float dl = __fmul_rn(d, (float)(2 * ((w >> (6 * (g & 1) + 3 * (e >> 1))) & 7) + 1));
+      const unsigned char qhb = b[32 + g * 2 + (e >> 1)];
+      const unsigned h = (e & 1) ? (qhb >> 4) : (qhb & 0xF);
+      const unsigned idx = (unsigned)b[g * 4 + e] | ((h & 7) << 8);
+      const float v = (float)(signed char)((gguf_iq1s_grid[idx] >> (8 * (l & 7))) & 0xFF);
+      return __fmul_rn(dl, v + ((h & 8) ? -0.125f : 0.125f));
     }
   }
   return 0.f;

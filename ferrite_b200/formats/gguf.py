@@ -2,9 +2,9 @@
 quantisation types, plus simple encoders and a writer used by the tests.
 
 Counterparts in the reference: `crates/fe-gguf/src/lib.rs` (`Gguf`, `TensorInfo`, `GgmlType::block`) and the host
-dequantisers of `crates/fe-ggq/src/refq.rs`. Decoders follow ggml's public `dequantize_row_*` definitions.
-Types whose decoding needs ggml's large codebook grids (IQ1_S/M, IQ2_XXS/XS/S, IQ3_XXS/S) and Q2_K / Q3_K are parsed
-(shapes, offsets, raw bytes) but not decoded here."""
+dequantisers of `crates/fe-ggq/src/refq.rs` (device side `kernels/k-gguf/src/dec.rs`, `vq.rs`, `tables.rs`). Decoders
+follow ggml's public `dequantize_row_*` definitions, the codebook types (IQ1_S/M, IQ2_XXS/XS/S, IQ3_XXS/S) through the
+grids of `gguf_tables.py`; the tests hold every decoder to the `gguf` Python package's own dequantiser, bit for bit."""
 from __future__ import annotations
 
 import mmap
@@ -261,7 +261,112 @@ def dequantize(raw: np.ndarray, type_id: int) -> np.ndarray:
             out[:, ib, :16] = dl[:, None] * KVALUES_IQ4NL[qs[:, ib] & 0xF]
             out[:, ib, 16:] = dl[:, None] * KVALUES_IQ4NL[qs[:, ib] >> 4]
         return out.reshape(-1)
-    raise NotImplementedError(f"ggml type {name}: block decoding needs codebook tables that are not shipped here")
+    if name == "Q2_K":
+        sc, qs = b[:, 0:16], b[:, 16:80].reshape(nb, 2, 32)
+        d, dmin = _f16(b[:, 80:82]), _f16(b[:, 82:84])
+        out = np.empty((nb, 16, 16), np.float32)
+        for n in range(2):
+            for j in range(4):
+                for half in range(2):
+                    i = n * 8 + j * 2 + half
+                    q = ((qs[:, n, 16 * half:16 * half + 16] >> (2 * j)) & 3).astype(np.float32)
+                    out[:, i] = (d[:, 0] * (sc[:, i] & 0xF))[:, None] * q - (dmin[:, 0] * (sc[:, i] >> 4))[:, None]
+        return out.reshape(-1)
+    if name == "Q3_K":
+        hm, qs = b[:, 0:32], b[:, 32:96].reshape(nb, 2, 32)
+        aux = b[:, 96:108].copy().view(np.uint32)                         # [nb, 3]
+        d = _f16(b[:, 108:110])
+        k1, k2 = np.uint32(0x03030303), np.uint32(0x0F0F0F0F)
+        a0, a1, tmp = aux[:, 0], aux[:, 1], aux[:, 2]
+        sc = np.stack([(a0 & k2) | (((tmp >> 0) & k1) << 4), (a1 & k2) | (((tmp >> 2) & k1) << 4),
+                       ((a0 >> 4) & k2) | (((tmp >> 4) & k1) << 4), ((a1 >> 4) & k2) | (((tmp >> 6) & k1) << 4)], 1)
+        sc = np.ascontiguousarray(sc).view(np.int8).astype(np.float32) - 32.0             # [nb, 16]
+        out = np.empty((nb, 16, 16), np.float32)
+        for n in range(2):
+            for j in range(4):
+                bit = np.uint8(1 << (n * 4 + j))
+                for half in range(2):
+                    i = n * 8 + j * 2 + half
+                    q = ((qs[:, n, 16 * half:16 * half + 16] >> (2 * j)) & 3).astype(np.float32)
+                    q = q - np.where(hm[:, 16 * half:16 * half + 16] & bit, 0.0, 4.0).astype(np.float32)
+                    out[:, i] = (d[:, 0] * sc[:, i])[:, None] * q
+        return out.reshape(-1)
+    if name in ("IQ2_XXS", "IQ2_XS", "IQ2_S", "IQ3_XXS", "IQ3_S", "IQ1_S", "IQ1_M"):
+        return _dequantize_iq(b, name)
+    raise NotImplementedError(f"ggml type {name} has no decoder here")
+
+
+def _signs(mask: np.ndarray) -> np.ndarray:
+    """8-bit sign masks [...] -> [..., 8] of +1 / -1 (bit j set = value j negative)."""
+    return np.where((mask[..., None] >> np.arange(8, dtype=np.uint8)) & 1, np.float32(-1), np.float32(1))
+
+
+def _dequantize_iq(b: np.ndarray, name: str) -> np.ndarray:
+    """The codebook ("IQ") super-blocks of 256 values: grid entries picked by index bits, signs, and sub-block scales."""
+    from .gguf_tables import GRID, KSIGNS
+    nb = b.shape[0]
+    d = _f16(b[:, 0:2])[:, 0] if name != "IQ1_M" else None
+    if name == "IQ2_XXS":
+        q32 = b[:, 2:66].copy().view(np.uint32).reshape(nb, 8, 2)
+        idx = b[:, 2:66].reshape(nb, 8, 8)[:, :, :4]                                   # the 4 grid indices of a group
+        db = d[:, None] * (np.float32(0.5) + (q32[:, :, 1] >> 28).astype(np.float32)) * np.float32(0.25)
+        sg = KSIGNS[(q32[:, :, 1, None] >> (7 * np.arange(4, dtype=np.uint32))) & 127]  # [nb, 8, 4]
+        g = GRID["iq2xxs"][idx].astype(np.float32)                                     # [nb, 8, 4, 8]
+        return (db[:, :, None, None] * g * _signs(sg)).reshape(-1)
+    if name == "IQ2_XS":
+        qs = b[:, 2:66].copy().view(np.uint16).reshape(nb, 8, 4)
+        sc = b[:, 66:74]
+        db = np.stack([sc & 0xF, sc >> 4], -1).astype(np.float32)                       # [nb, 8, 2]
+        db = d[:, None, None] * (np.float32(0.5) + db) * np.float32(0.25)
+        g = GRID["iq2xs"][qs & 511].astype(np.float32)
+        return (np.repeat(db, 2, -1)[..., None] * g * _signs(KSIGNS[qs >> 9])).reshape(-1)
+    if name == "IQ2_S":
+        qs, sg = b[:, 2:34].reshape(nb, 8, 4), b[:, 34:66].reshape(nb, 8, 4)
+        qh, sc = b[:, 66:74], b[:, 74:82]
+        db = np.stack([sc & 0xF, sc >> 4], -1).astype(np.float32)
+        db = d[:, None, None] * (np.float32(0.5) + db) * np.float32(0.25)
+        hi = (qh[:, :, None].astype(np.uint16) << (8 - 2 * np.arange(4, dtype=np.uint16))) & 0x300
+        g = GRID["iq2s"][qs.astype(np.uint16) | hi].astype(np.float32)
+        return (np.repeat(db, 2, -1)[..., None] * g * _signs(sg)).reshape(-1)
+    if name == "IQ3_XXS":
+        qs = b[:, 2:66].reshape(nb, 8, 8)
+        aux = b[:, 66:98].copy().view(np.uint32)                                        # [nb, 8]
+        db = d[:, None] * (np.float32(0.5) + (aux >> 28).astype(np.float32)) * np.float32(0.5)
+        sg = _signs(KSIGNS[(aux[:, :, None] >> (7 * np.arange(4, dtype=np.uint32))) & 127])   # [nb, 8, 4, 8]
+        g = GRID["iq3xxs"][qs].astype(np.float32).reshape(nb, 8, 4, 8)                  # two 4-value entries per 8 signs
+        return (db[:, :, None, None] * g * sg).reshape(-1)
+    if name == "IQ3_S":
+        qs, qh = b[:, 2:66].reshape(nb, 8, 8), b[:, 66:74]
+        sg, sc = b[:, 74:106].reshape(nb, 8, 4), b[:, 106:110]
+        db = np.stack([sc & 0xF, sc >> 4], -1).reshape(nb, 8).astype(np.float32)
+        db = d[:, None] * (np.float32(1) + np.float32(2) * db)
+        hi = ((qh[:, :, None].astype(np.uint16) << 8) >> np.arange(8, dtype=np.uint16)) & 256   # bit l of qh -> bit 8
+        g = GRID["iq3s"][qs.astype(np.uint16) | hi].astype(np.float32).reshape(nb, 8, 4, 8)
+        return (db[:, :, None, None] * g * _signs(sg)).reshape(-1)
+    delta = np.float32(0.125)
+    if name == "IQ1_S":
+        qs = b[:, 2:34].reshape(nb, 8, 4)
+        qh = b[:, 34:50].copy().view(np.uint16)                                         # [nb, 8]
+        dl = d[:, None] * (2 * ((qh >> 12) & 7) + 1).astype(np.float32)
+        dlt = np.where(qh & 0x8000, -delta, delta).astype(np.float32)
+        idx = qs.astype(np.uint16) | (((qh[:, :, None] >> (3 * np.arange(4, dtype=np.uint16))) & 7) << 8)
+        g = GRID["iq1s"][idx].astype(np.float32)                                        # [nb, 8, 4, 8]
+        return (dl[:, :, None, None] * (g + dlt[:, :, None, None])).reshape(-1)
+    # IQ1_M: the fp16 super-block scale is spread over the top nibbles of the four 16-bit scale words
+    qs, qh = b[:, 0:32].reshape(nb, 8, 4), b[:, 32:48].reshape(nb, 8, 2)
+    sc = b[:, 48:56].copy().view(np.uint16)                                             # [nb, 4]
+    dbits = (sc[:, 0] >> 12) | ((sc[:, 1] >> 8) & 0x00F0) | ((sc[:, 2] >> 4) & 0x0F00) | (sc[:, 3] & 0xF000)
+    d = dbits.astype(np.uint16).view(np.float16).astype(np.float32)
+    ib = np.arange(8)
+    w = sc[:, ib // 2]                                                                  # [nb, 8]
+    dl1 = d[:, None] * (2 * ((w >> (6 * (ib % 2))) & 7) + 1).astype(np.float32)
+    dl2 = d[:, None] * (2 * ((w >> (6 * (ib % 2) + 3)) & 7) + 1).astype(np.float32)
+    dl = np.stack([dl1, dl1, dl2, dl2], -1)                                             # [nb, 8, 4]
+    h = np.stack([qh[:, :, 0], qh[:, :, 0] >> 4, qh[:, :, 1], qh[:, :, 1] >> 4], -1).astype(np.uint16)   # 4 nibbles
+    idx = qs.astype(np.uint16) | ((h & 7) << 8)
+    dlt = np.where(h & 8, -delta, delta).astype(np.float32)
+    g = GRID["iq1s"][idx].astype(np.float32)
+    return (dl[..., None] * (g + dlt[..., None])).reshape(-1)
 
 
 # ---- encoders (tests, synthetic checkpoints) and writer -------------------------------------------------------

@@ -164,6 +164,41 @@ class PackedEXL3(PackedLinear):
         return self.t.weight(torch.float32).t().contiguous().to(dtype)
 
 
+class PackedGGUF(PackedLinear):
+    """A GGUF tensor in its own block format: `raw` uint8 [out, in / block values * block bytes], every output row a run
+    of whole blocks. Row cuts are free; column cuts fall on block boundaries (256 values for the K and IQ types)."""
+    kind = "gguf"
+
+    def __init__(self, raw: torch.Tensor, type_id: int, cols: int):
+        from .gguf import TYPES
+        self.raw, self.type_id, self._cols = raw, int(type_id), int(cols)
+        self.bv, self.bb = TYPES[self.type_id][1], TYPES[self.type_id][2]
+        assert raw.dim() == 2 and raw.shape[1] == cols // self.bv * self.bb
+
+    @property
+    def rows(self):
+        return self.raw.shape[0]
+
+    @property
+    def cols(self):
+        return self._cols
+
+    def take_rows(self, lo, hi):
+        return PackedGGUF(self.raw[lo:hi], self.type_id, self._cols)
+
+    def take_cols(self, lo, hi):
+        assert lo % self.bv == 0 and hi % self.bv == 0, f"GGUF column cuts fall on {self.bv}-value blocks"
+        return PackedGGUF(self.raw[:, lo // self.bv * self.bb:hi // self.bv * self.bb], self.type_id, hi - lo)
+
+    def take(self, index):
+        return PackedGGUF(self.raw[index], self.type_id, self._cols)
+
+    def dequantize(self, dtype=torch.float32):
+        from .gguf import dequantize
+        flat = self.raw.contiguous().numpy().reshape(-1)
+        return torch.from_numpy(dequantize(flat, self.type_id)).reshape(self.rows, self._cols).to(dtype)
+
+
 class PackedStack(PackedLinear):
     """Parts of different storage (for instance an EXL3 q|k|v|z block and the small dense b|a rows of a Gated DeltaNet
     input projection) concatenated along the output rows. The kernels run part by part into column ranges of the
@@ -223,6 +258,8 @@ def cat_rows(parts: List):
                                    max(q.input_scale, p.input_scale))
         elif isinstance(p, torch.Tensor) and isinstance(q, torch.Tensor):
             merged[-1] = torch.cat([q, p], 0)
+        elif isinstance(p, PackedGGUF) and isinstance(q, PackedGGUF) and p.type_id == q.type_id:
+            merged[-1] = PackedGGUF(torch.cat([q.raw, p.raw]), p.type_id, p.cols)
         elif isinstance(p, PackedEXL3) and isinstance(q, PackedEXL3) and p.t.bits == q.t.bits and (p.t.suh == q.t.suh).all():
             import numpy as np
             merged[-1] = PackedEXL3(Exl3Tensor(q.t.k, q.t.n + p.t.n, q.t.bits, np.concatenate([q.t.trellis, p.t.trellis], 1),

@@ -15,7 +15,7 @@ import os
 import torch
 
 from .._ext import load
-from .qweight import Exl3Weight, ExpertsFP4, QWeight, StackWeight
+from .qweight import Exl3Weight, ExpertsFP4, GgufWeight, QWeight, StackWeight
 
 GEMV_MAX_ROWS = 8
 MOE_PAIR_ROWS = 64     # up to this many rows (the largest graph-captured step) the experts run as per-pair GEMVs,
@@ -94,13 +94,21 @@ class CudaOps:
         return s
 
     def linear(self, x, w, norm_w=None, eps=1e-6, res=None, swiglu=False, out_f32=False, out=None):
-        if isinstance(w, (Exl3Weight, StackWeight)):
-            # EXL3 (and stacks of differently stored parts): the norm runs once, each part fills its column range, the
-            # SwiGLU / residual run on the joined output. The trellis kernels rotate their own input.
+        if isinstance(w, (Exl3Weight, StackWeight, GgufWeight)):
+            # EXL3 / GGUF blocks (and stacks of differently stored parts): the norm runs once, each part fills its column
+            # range, the SwiGLU / residual run on the joined output. The trellis kernels rotate their own input.
             if norm_w is not None:
                 x, _ = self.rmsnorm(x, norm_w, eps, True)
             if isinstance(w, Exl3Weight):
                 y = w.lin.forward(self, x, None if swiglu else res)
+            elif isinstance(w, GgufWeight):
+                if x.shape[0] <= GEMV_MAX_ROWS and w.cols * 4 * 8 <= 200 * 1024:
+                    y = self.gguf_gemv(x, w.raw, w.type_id, w.rows, None if swiglu else res)
+                else:
+                    dense = self.scratch("gguf_dense", w.rows * w.cols).view(w.rows, w.cols)
+                    self.launches += 1
+                    self.C.gguf_dequant(dense, w.raw, w.type_id)
+                    y = self.linear(x, dense, res=None if swiglu else res)
             else:
                 y = torch.cat([self.linear(x, p) for p in w.parts], 1)
                 self.launches += 1

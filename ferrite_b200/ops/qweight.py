@@ -128,6 +128,22 @@ class Exl3Weight:
         return self.host.weight(torch.float32).t().contiguous().to(dtype)
 
 
+class GgufWeight:
+    """A GGUF tensor on the device in its checkpoint block format (`formats.packed.PackedGGUF`): decode rows run the
+    dequantising GEMV on these blocks, prompt-sized steps dequantise into a scratch for the tensor-core GEMM."""
+    kind = "gguf"
+
+    def __init__(self, raw: torch.Tensor, type_id: int, rows: int, cols: int, host=None):
+        self.raw, self.type_id, self.rows, self.cols, self.host = raw, type_id, rows, cols, host
+
+    @property
+    def shape(self):
+        return (self.rows, self.cols)
+
+    def dequantize(self, dtype=torch.float32) -> torch.Tensor:
+        return self.host.dequantize(dtype)
+
+
 class StackWeight:
     """Weights of different storage sharing one input, concatenated along the output rows (`formats.packed.PackedStack`
     after conversion): the linear runs part by part into column ranges of one output."""
@@ -152,7 +168,7 @@ def from_packed(p, device, dtype, on_gpu: bool, keep_dense: bool = True):
     that is the dequantised matrix; on the GPU the codes and scales go to the device in the kernels' layouts:
     NVFP4 -> `QWeight` (GEMV tiling + tensor-core tiling of the block scales, per-row tensor scales when fused parts
     differ), FP8 -> `QWeight` kind "fp8" (codes + per-row scales for the e4m3 GEMM), EXL3 -> `Exl3Weight`."""
-    from ..formats.packed import PackedEXL3, PackedFP8, PackedNVFP4, PackedStack
+    from ..formats.packed import PackedEXL3, PackedFP8, PackedGGUF, PackedNVFP4, PackedStack
     if isinstance(p, torch.Tensor):
         return p.to(device, dtype)
     if not on_gpu:
@@ -176,6 +192,8 @@ def from_packed(p, device, dtype, on_gpu: bool, keep_dense: bool = True):
     if isinstance(p, PackedEXL3):
         from .exl3_linear import Exl3Linear
         return Exl3Weight(Exl3Linear(p.t, device), p.shape[0], p.shape[1], host=p.t)
+    if isinstance(p, PackedGGUF):
+        return GgufWeight(p.raw.contiguous().view(-1).to(device), p.type_id, p.shape[0], p.shape[1], host=p)
     if isinstance(p, PackedStack):
         return StackWeight([from_packed(q, device, dtype, on_gpu, keep_dense) for q in p.parts])
     raise TypeError(type(p).__name__)

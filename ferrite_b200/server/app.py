@@ -23,7 +23,7 @@ from . import pyjson
 from .api import ApiError, ChatRequest, CompletionRequest
 from .engine_api import EngineBase, GenEvent, GenRequest
 from .guard import LoopRules, PhaseGuard
-from .parser import Delta, StreamParser
+from .parser import Delta, StreamParser, merge_tool_calls
 from .profiles import GenDefaults, resolve_sampling
 from .stop import StopMatcher
 from .template import ChatTemplate
@@ -61,10 +61,10 @@ class Pipeline:
     """ids -> UTF-8-safe text -> stop strings -> reasoning / content / tool-call deltas (reference `Pipeline`)."""
 
     def __init__(self, tok, stops: List[str], include_stop: bool, tools: Optional[ToolSet], thinking: bool, prefix: str = "",
-                 raw: bool = False):
+                 raw: bool = False, max_tool_calls: Optional[int] = None, dsml: bool = False):
         self.dec = IncrementalDecoder(tok)
         self.stop = StopMatcher(stops, include_stop)
-        self.parser = None if raw else StreamParser(tools, thinking, prefix)
+        self.parser = None if raw else StreamParser(tools, thinking, prefix, max_tool_calls=max_tool_calls, dsml=dsml)
         self.stopped = False
         self.text = ""
 
@@ -166,12 +166,16 @@ class Prepared:
         self.snapshots: List[int] = []
         self.guard: Optional[PhaseGuard] = None
         self.raw = False
+        self.max_tool_calls: Optional[int] = None     # parallel_tool_calls: false -> 1
+        self.dsml = False                             # the template writes DSML tool calls
 
 
 def prepare_chat(st: AppState, req: ChatRequest) -> Prepared:
     p = Prepared()
     tools = ToolSet(req.tools) if req.tool_choice != "none" else ToolSet([])
-    forced = tools.resolve_choice(req.tool_choice)
+    p.dsml = "DSML" in getattr(st.template, "source", "")
+    p.max_tool_calls = None if req.parallel_tool_calls else 1
+    forced = tools.resolve_choice(req.tool_choice, p.dsml)
     think = req.enable_thinking
     kwargs = {} if think is None else {"enable_thinking": bool(think)}
     text = st.template.render(req.messages, [dict(t) for t in req.tools] if tools else None, True, **kwargs)
@@ -232,7 +236,8 @@ class Driver:
         self.st, self.p = st, p
         self.q: "asyncio.Queue[GenEvent]" = asyncio.Queue()
         self.loop = asyncio.get_running_loop()
-        self.pipe = Pipeline(st.tok, p.stops, p.include_stop, p.tools, p.thinking, p.prefix, raw=p.raw)
+        self.pipe = Pipeline(st.tok, p.stops, p.include_stop, p.tools, p.thinking, p.prefix, raw=p.raw,
+                             max_tool_calls=p.max_tool_calls, dsml=p.dsml)
         self.req = GenRequest(p.ids, p.sampling, p.snapshots)
         self.completion_tokens = 0
         self.finish_reason = "stop"
@@ -397,7 +402,8 @@ async def _run(request: web.Request, chat: bool) -> web.StreamResponse:
             if reasoning:
                 msg["reasoning_content"] = reasoning
             if calls:
-                msg["tool_calls"] = [{k: v for k, v in c.items() if k != "index"} for c in calls]
+                # streamed pieces (name first, then argument text) fold into whole calls
+                msg["tool_calls"] = [{k: v for k, v in c.items() if k != "index"} for c in merge_tool_calls(calls)]
             choice = {"index": 0, "message": msg, "finish_reason": drv.finish_reason}
         else:
             choice = {"index": 0, "text": content, "finish_reason": drv.finish_reason, "logprobs": None}

@@ -41,9 +41,18 @@ def coerce(value: Any, schema: Optional[Dict[str, Any]]) -> Any:
 
 @dataclass
 class ForcedCall:
-    """Text the reply is forced to start with so that it is a call of a given tool."""
+    """Text the generation prompt is made to end with so that the reply is a tool call (reference `ForcedCall`,
+    `crates/fe-server/src/parser.rs:37-70`): any tool -> the reply starts with the function's name; a named tool -> the
+    reply starts with its parameters."""
     opener: str
     name: Optional[str]
+
+    @staticmethod
+    def make(name: Optional[str], dsml: bool = False) -> "ForcedCall":
+        if dsml:
+            head = "\n\n<｜DSML｜ calls>\n<｜DSML｜ invoke name=\""
+            return ForcedCall(head + (f"{name}\">\n" if name else ""), name)
+        return ForcedCall("<tool_call>\n<function=" + (f"{name}>\n" if name else ""), name)
 
 
 class ToolSet:
@@ -67,7 +76,7 @@ class ToolSet:
             return args
         return coerce(args, fn.get("parameters") or {"type": "object"})
 
-    def resolve_choice(self, tool_choice: Any) -> Optional[ForcedCall]:
+    def resolve_choice(self, tool_choice: Any, dsml: bool = False) -> Optional[ForcedCall]:
         """none -> tools are hidden by the caller; auto/None -> free; required -> must open a call;
         {"type":"function","function":{"name":X}} -> must call X."""
         if tool_choice in (None, "auto", "none"):
@@ -75,10 +84,10 @@ class ToolSet:
         if tool_choice == "required":
             if not self.tools:
                 raise ApiError(400, "tool_choice 'required' needs tools", param="tool_choice")
-            return ForcedCall("<tool_call>\n{\"name\": \"", None)
+            return ForcedCall.make(None, dsml)
         if isinstance(tool_choice, dict):
             name = (tool_choice.get("function") or {}).get("name")
             if name not in self.tools:
                 raise ApiError(400, f"tool_choice names an unknown tool {name!r}", param="tool_choice")
-            return ForcedCall("<tool_call>\n{\"name\": \"" + name + "\", \"arguments\": ", name)
+            return ForcedCall.make(name, dsml)
         raise ApiError(400, "unsupported tool_choice", param="tool_choice")

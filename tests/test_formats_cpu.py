@@ -116,7 +116,7 @@ def test_gguf_reader_and_block_decoders(tmp_path):
     blk = np.zeros((1, 17), np.uint8); blk[0, 0] = 128; blk[0, 1:] = np.arange(16)
     assert np.allclose(gguf.dequantize(blk.reshape(-1), gguf.TYPE_ID["MXFP4"])[:16], gguf.KVALUES_MXFP4)   # 2^(128-127)/2 = 1
     with pytest.raises(NotImplementedError):
-        gguf.dequantize(np.zeros(66, np.uint8), gguf.TYPE_ID["IQ2_XXS"])
+        gguf.dequantize(np.zeros(292, np.uint8), gguf.TYPE_ID["Q8_K"])       # an activation-side type: never in a checkpoint
 
 
 def test_exl3_decode_reconstruct_and_slices():
@@ -271,4 +271,69 @@ def test_engine_runs_from_a_modelopt_checkpoint_on_the_oracle(tmp_path):
     prompt = torch.randint(0, cfg.vocab, (24,), generator=torch.Generator().manual_seed(2)).tolist()
     a = Engine(cfg, packed, EngineConfig(n_slots=1, max_ctx=64), device="cpu").generate(prompt, 6)
     b = Engine(cfg, dense, EngineConfig(n_slots=1, max_ctx=64), device="cpu").generate(prompt, 6)
+    assert a == b
+
+
+@pytest.mark.parametrize("name", ["Q2_K", "Q3_K", "Q4_K", "Q5_K", "Q6_K", "IQ4_NL", "IQ4_XS", "IQ2_XXS", "IQ2_XS", "IQ2_S",
+                                  "IQ3_XXS", "IQ3_S", "IQ1_S", "IQ1_M", "Q8_0", "Q4_0", "Q5_1"])
+def test_gguf_block_decoders_equal_the_gguf_package(name):
+    """Every host block decoder against the dequantiser of the `gguf` Python package (llama.cpp's own), bit for bit, on
+    random blocks with finite scale fields."""
+    gq = pytest.importorskip("gguf.quants")
+    from gguf import GGMLQuantizationType as T
+    import numpy as np
+    from ferrite_b200.formats import gguf as fg
+    tid = fg.TYPE_ID[name]
+    _, bv, bb = fg.TYPES[tid]
+    rng = np.random.default_rng(tid)
+    nb = 48
+    raw = rng.integers(0, 256, size=(nb, bb), dtype=np.uint8)
+    half_at = {"Q2_K": [80, 82], "Q3_K": [108], "Q4_K": [0, 2], "Q5_K": [0, 2], "Q6_K": [208], "Q5_1": [0, 2]}.get(name, [0])
+    if name != "IQ1_M":
+        for off in half_at:
+            raw[:, off:off + 2] = (rng.standard_normal(nb) * 0.01).astype(np.float16).view(np.uint8).reshape(nb, 2)
+    else:
+        d = np.full(nb, np.float16(0.0123)).view(np.uint16)
+        sc = raw[:, 48:56].view(np.uint16)
+        for j in range(4):
+            sc[:, j] = (sc[:, j] & 0x0FFF) | (((d >> (4 * j)) & 0xF) << 12)
+    mine = fg.dequantize(raw.reshape(-1), tid)
+    ref = gq.dequantize(raw, getattr(T, name)).reshape(-1)
+    assert np.array_equal(mine, ref)
+
+
+@pytest.mark.parametrize("moe", [False, True])
+def test_gguf_checkpoint_round_trip_into_the_engine(tmp_path, moe):
+    """A GGUF file written under llama.cpp's tensor names (dense hybrid and MoE) loads into engine weights: metadata
+    gives back the configuration, quantised projections stay in their block format, and the CPU engine built from the
+    packed form equals the one built from the dequantised tensors."""
+    import dataclasses
+    from ferrite_b200.config import EngineConfig, tiny_hybrid
+    from ferrite_b200.engine.engine import Engine
+    from ferrite_b200.formats import gguf as G
+    from ferrite_b200.formats.gguf_model import config_from_gguf, export_gguf, load_gguf_weights
+    from ferrite_b200.formats.packed import PackedGGUF
+    from ferrite_b200.models.weights import init_weights
+    cfg = tiny_hybrid()
+    if moe:
+        cfg = dataclasses.replace(cfg, n_experts=8, top_k=2, expert_inter=64, n_shared=1, router="softmax")
+    w = init_weights(cfg, seed=0)
+    path = str(tmp_path / "m.gguf")
+    export_gguf(w, cfg, path, "Q8_0")
+    g = G.Gguf(path)
+    back = config_from_gguf(g, cfg)
+    g.close()
+    assert (back.n_layers, back.hidden, back.n_q, back.n_kv, back.head_dim, back.vocab, back.n_experts, back.top_k) == \
+        (cfg.n_layers, cfg.hidden, cfg.n_q, cfg.n_kv, cfg.head_dim, cfg.vocab, cfg.n_experts, cfg.top_k)
+    packed = load_gguf_weights(path, cfg, torch.float32)
+    dense = load_gguf_weights(path, cfg, torch.float32, dense=True)
+    assert isinstance(packed["l0.out_proj"], PackedGGUF)
+    assert set(packed) == set(w)
+    for k in w:                                      # norms, vectors and Q8_0 projections come back close to the source
+        d = dense[k].float()
+        assert d.shape == w[k].shape, k
+        assert (d - w[k].float()).abs().max() <= 0.02 * max(1e-3, float(w[k].abs().max())) + 1e-6, k
+    prompt = torch.randint(0, cfg.vocab, (20,), generator=torch.Generator().manual_seed(2)).tolist()
+    a = Engine(cfg, packed, EngineConfig(n_slots=1, max_ctx=64), device="cpu").generate(prompt, 5)
+    b = Engine(cfg, dense, EngineConfig(n_slots=1, max_ctx=64), device="cpu").generate(prompt, 5)
     assert a == b

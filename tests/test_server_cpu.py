@@ -99,7 +99,14 @@ def test_tool_calls_parallel_and_choice():
         r = await c.post("/v1/chat/completions", json={**body, "stream": True})
         ev = [json.loads(x) for x in (await sse(r))[:-1]]
         calls = [tc for e in ev for tc in e["choices"][0]["delta"].get("tool_calls", [])]
-        assert [tc["index"] for tc in calls] == [0, 1] and ev[-1]["choices"][0]["finish_reason"] == "tool_calls"
+        # per call: a start delta with id + name, then pieces of the arguments; folded, they are the two calls
+        assert sorted(set(tc["index"] for tc in calls)) == [0, 1] and ev[-1]["choices"][0]["finish_reason"] == "tool_calls"
+        assert [bool(tc.get("id")) for tc in calls if tc["index"] == 0][0] and sum(1 for tc in calls if tc.get("id")) == 2
+        from ferrite_b200.server.parser import merge_tool_calls
+        whole = merge_tool_calls(calls)
+        assert [json.loads(w["function"]["arguments"]) for w in whole] == [{"city": "Oslo", "days": 3}, {"city": "Rome"}]
+        one = await (await c.post("/v1/chat/completions", json={**body, "parallel_tool_calls": False})).json()
+        assert len(one["choices"][0]["message"]["tool_calls"]) == 1
         bad = await c.post("/v1/chat/completions", json={**body, "tool_choice": {"type": "function", "function": {"name": "x"}}})
         assert bad.status == 400 and (await bad.json())["error"]["param"] == "tool_choice"
         none = await (await c.post("/v1/chat/completions", json={**chat("plain"), "tools": TOOLS, "tool_choice": "none"})).json()
@@ -187,7 +194,8 @@ def test_parser_units():
         content += d.content
     d = p.finish()
     calls += d.tool_calls
-    assert content == "Hi" and json.loads(calls[0]["function"]["arguments"]) == {"city": "Paris", "days": 2}
+    from ferrite_b200.server.parser import merge_tool_calls
+    assert content == "Hi" and json.loads(merge_tool_calls(calls)[0]["function"]["arguments"]) == {"city": "Paris", "days": 2}
     assert parse_call_body('{"name": "f", "arguments": {"a": 1}} trailing', None)["name"] == "f"
     assert parse_call_body("garbage", None) is None
     assert coerce("true", {"type": "boolean"}) is True and coerce("x", {"type": "integer"}) == "x"
