@@ -22,7 +22,8 @@ from ..engine.sampler import Sampling
 from . import pyjson
 from .api import ApiError, ChatRequest, CompletionRequest
 from .engine_api import EngineBase, GenEvent, GenRequest
-from .guard import LoopRules, PhaseGuard
+from .guard import PhaseGuard
+from .loopdet import LoopCfg
 from .parser import Delta, StreamParser, merge_tool_calls
 from .profiles import GenDefaults, resolve_sampling
 from .stop import StopMatcher
@@ -205,7 +206,10 @@ def prepare_chat(st: AppState, req: ChatRequest) -> Prepared:
     p.snapshots = snapshot_points(st.tok, p.ids)
     max_r = req.max_reasoning_tokens if req.max_reasoning_tokens is not None else st.defaults.max_reasoning_tokens
     lb = st.defaults.loop_breaker if req.loop_breaker is None else bool(req.loop_breaker)
-    p.guard = PhaseGuard(st.tok.encode("\n</think>\n\n"), p.thinking, max_r, lb, LoopRules())
+    p.guard = PhaseGuard(st.tok.encode("</think>"), p.thinking, max_r, lb, LoopCfg.from_json(getattr(st.defaults, "loop_rules", None)),
+                         close_ids=st.tok.encode("\n</think>\n\n"),
+                         call_marks=[st.tok.encode(m) for m in ("<tool_call>", "<function=")] if tools else (),
+                         detok=lambda ids: st.tok.decode(list(ids)))
     return p
 
 
@@ -249,6 +253,15 @@ class Driver:
 
     def _guard(self, toks: List[int]):
         act = self.p.guard.feed(toks, "")
+        s = self.req.sampling
+        if act.boost_started:
+            # a loop in the answer: sample the next stretch with the recovery values (a greedy request leaves its cycle)
+            self._own_sampling = (s.temperature, s.top_p)
+            rules = self.p.guard.tracker.rules
+            s.temperature, s.top_p = max(s.temperature, rules.recover_temperature), min(s.top_p, rules.recover_top_p)
+        elif act.boost_ended and getattr(self, "_own_sampling", None):
+            s.temperature, s.top_p = self._own_sampling
+            self._own_sampling = None
         if act.finish:
             return act.finish
         return act.force_tokens or None

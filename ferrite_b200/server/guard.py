@@ -1,120 +1,79 @@
-"""Reply guards working on the token / text stream of one request: reasoning cap, exact-cycle loop breaker,
-repeated-sentence rule, and the boost-then-end escalation. Counterparts: `PhaseGuard::feed` (`crates/fe-server/src/
-guard.rs:106`) over `PhaseTracker`, `SentDet` and the cycle detector of `loopdet.rs`."""
+"""Reply guard of one request: adapts the phase tracker (`loopdet.PhaseTracker`: reasoning cap, loop rules,
+repeated-sentence rule) to the scheduler's guard hook. Counterpart of the reference's `PhaseGuard::feed`
+(`crates/fe-server/src/guard.rs:106`) and of the guard built in `crates/fe-server/src/ferrite.rs` (`guard(&params)`):
+
+* the cap, or a loop inside the reasoning block, forces the block's closing tokens so the model answers;
+* the first loop in the answer boosts the sampling (temperature 0.7, top-p 0.95: a greedy request leaves its cycle) for
+  `BOOST_TOKENS` tokens, then the request's own sampling comes back; a loop that returns ends the reply;
+* what fired is kept in `events` (reported with the finish and in the request-capture file).
+"""
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Dict, List, Optional, Sequence
+from typing import Callable, List, Optional, Sequence
 
-BOOST_TOKENS = 96      # tokens of boosted sampling after a loop is seen before the reply is ended
+from .loopdet import BOOST_TOKENS, LoopCfg, PhaseEvents, PhaseTracker, Trig
 
-
-@dataclass
-class LoopRules:
-    min_period: int = 4            # shortest token cycle considered
-    max_period: int = 256
-    repeats: int = 4               # a cycle repeated this many times is a loop
-    sentence_repeats: int = 5      # the same sentence this many times is a loop
-    min_sentence_chars: int = 24
-
-
-class CycleDetector:
-    """Exact repetition at the tail of the token stream: ... P P P P for some period |P| in [min, max]."""
-
-    def __init__(self, rules: LoopRules):
-        self.r = rules
-        self.toks: List[int] = []
-
-    def feed(self, toks: Sequence[int]) -> Optional[int]:
-        self.toks.extend(int(t) for t in toks)
-        t = self.toks
-        n = len(t)
-        for p in range(self.r.min_period, min(self.r.max_period, n // self.r.repeats) + 1):
-            need = p * self.r.repeats
-            if n < need:
-                break
-            tail = t[n - need:]
-            if all(tail[i] == tail[i % p] for i in range(need)):
-                return p
-        if n > 4 * self.r.max_period * self.r.repeats:
-            self.toks = t[-2 * self.r.max_period * self.r.repeats:]
-        return None
-
-
-class SentenceDetector:
-    """Counts repeated sentences (normalised, long enough) in the decoded text."""
-
-    def __init__(self, rules: LoopRules):
-        self.r = rules
-        self.buf = ""
-        self.counts: Dict[str, int] = {}
-
-    def feed(self, text: str) -> Optional[str]:
-        self.buf += text
-        hit = None
-        while True:
-            idx = min((i for i in (self.buf.find(c) for c in ".!?\n") if i >= 0), default=-1)
-            if idx < 0:
-                break
-            sent, self.buf = self.buf[:idx + 1], self.buf[idx + 1:]
-            key = " ".join(sent.lower().split())
-            if len(key) < self.r.min_sentence_chars:
-                continue
-            self.counts[key] = self.counts.get(key, 0) + 1
-            if self.counts[key] >= self.r.sentence_repeats:
-                hit = key
-        return hit
+__all__ = ["BOOST_TOKENS", "GuardAction", "PhaseGuard"]
 
 
 @dataclass
 class GuardAction:
-    force_tokens: List[int] = field(default_factory=list)   # tokens to append to the sequence (e.g. </think>)
+    force_tokens: List[int] = field(default_factory=list)   # tokens to append to the sequence (the block's closing tag)
     finish: Optional[str] = None                            # end the reply with this reason
-    boost: bool = False                                     # raise temperature / penalties for a while
+    boost: bool = False                                     # the boosted stretch is on
+    boost_started: bool = False                             # ... and began with these tokens
+    boost_ended: bool = False                               # the request's own sampling is back
 
 
 class PhaseGuard:
-    """Tracks thinking vs answer phase; caps reasoning length; escalates on loops: first a sampling boost for
-    BOOST_TOKENS tokens, and if the loop is still there, the end of the reply."""
+    """think_end_ids: the tokens of `</think>` as the model writes it (detection); close_ids: what is forced to close a
+    capped or looping block (defaults to think_end_ids). A multi-token `</think>` (byte-level tokenizers) is detected
+    on its last token, with the tokens before it compared."""
 
-    def __init__(self, think_end_ids: Sequence[int], in_thinking: bool, max_reasoning: Optional[int],
-                 loop_breaker: bool = True, rules: Optional[LoopRules] = None):
-        self.think_end = list(think_end_ids)
-        self.in_thinking = in_thinking
-        self.max_reasoning = max_reasoning
-        self.loop_breaker = loop_breaker
-        self.rules = rules or LoopRules()
-        self.cycles = CycleDetector(self.rules)
-        self.sents = SentenceDetector(self.rules)
-        self.n_reasoning = 0
-        self.boost_left = 0
-        self.loops_seen = 0
+    def __init__(self, think_end_ids: Sequence[int], in_thinking: bool, max_reasoning: Optional[int] = None,
+                 loop_breaker: bool = True, rules: Optional[LoopCfg] = None, close_ids: Optional[Sequence[int]] = None,
+                 call_marks: Sequence[Sequence[int]] = (), detok: Optional[Callable[[Sequence[int]], str]] = None):
+        self.think_end = [int(t) for t in think_end_ids]
+        self.close_ids = [int(t) for t in (close_ids if close_ids is not None else think_end_ids)]
+        last = self.think_end[-1] if self.think_end else None
+        self.tracker = PhaseTracker(last, in_thinking, max_reasoning, loop_breaker, rules, call_marks, detok)
+        self.tail: List[int] = []
+        self.was_boosting = False
+
+    @property
+    def in_thinking(self) -> bool:
+        return self.tracker.in_reasoning
+
+    @property
+    def events(self) -> PhaseEvents:
+        return self.tracker.events
 
     def feed(self, toks: Sequence[int], text: str = "") -> GuardAction:
         act = GuardAction()
-        if self.in_thinking:
-            self.n_reasoning += len(toks)
-        if self.in_thinking and self.think_end:
-            joined = self.cycles.toks + [int(t) for t in toks]
+        tr = self.tracker
+        for t in toks:
+            t = int(t)
             k = len(self.think_end)
-            for i in range(max(0, len(joined) - len(toks) - k + 1), len(joined) - k + 1):
-                if joined[i:i + k] == self.think_end:
-                    self.in_thinking = False
-                    break
-        if self.in_thinking and self.max_reasoning is not None and self.n_reasoning >= self.max_reasoning:
-            act.force_tokens = list(self.think_end)           # close the reasoning block for the model
-            self.in_thinking = False
-        period = self.cycles.feed(toks)
-        sent = self.sents.feed(text) if text else None
-        if self.loop_breaker and (period is not None or sent is not None):
-            self.loops_seen += 1
-            if self.boost_left == 0 and self.loops_seen == 1:
-                self.boost_left = BOOST_TOKENS
-                act.boost = True
-                self.cycles.toks = []
-            elif self.boost_left == 0:
+            if tr.in_reasoning and k > 1 and t == self.think_end[-1]:
+                # the last token of the tag only counts when the tokens before it are the tag's
+                if self.tail[-(k - 1):] != self.think_end[:-1]:
+                    tr.think_end, keep = None, tr.think_end
+                    trig = tr.feed([t])
+                    tr.think_end = keep
+                else:
+                    trig = tr.feed([t])
+            else:
+                trig = tr.feed([t])
+            self.tail = (self.tail + [t])[-max(8, k):]
+            if trig == Trig.CLOSE:
+                act.force_tokens = list(self.close_ids)
+            elif trig == Trig.END_LOOP:
                 act.finish = "loop"
-        if self.boost_left > 0:
-            self.boost_left = max(0, self.boost_left - len(toks))
-            act.boost = act.boost or self.boost_left > 0
+                break
+        now = tr.boosting()
+        act.boost = now
+        act.boost_started = now and not self.was_boosting
+        act.boost_ended = self.was_boosting and not now
+        self.was_boosting = now
         return act

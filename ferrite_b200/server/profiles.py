@@ -31,6 +31,7 @@ class GenDefaults:
     no_token_timeout_s: float = 60.0
     reply_wall_limit_s: float = 0.0
     loop_breaker: bool = True
+    loop_rules: Optional[Dict[str, Any]] = None        # thresholds of the loop breaker (`loopdet.LoopCfg.from_json`)
 
     @staticmethod
     def from_dir(model_dir: Optional[str], profile: str = "default") -> "GenDefaults":
@@ -52,7 +53,7 @@ class GenDefaults:
                     for k, v in (d.get(phase) or {}).items():
                         if hasattr(obj, k):
                             setattr(obj, k, v)
-                for k in ("max_reasoning_tokens", "no_token_timeout_s", "reply_wall_limit_s", "loop_breaker"):
+                for k in ("max_reasoning_tokens", "no_token_timeout_s", "reply_wall_limit_s", "loop_breaker", "loop_rules"):
                     if k in d:
                         setattr(g, k, d[k])
                 break

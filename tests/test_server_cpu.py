@@ -9,7 +9,8 @@ from aiohttp.test_utils import TestClient, TestServer
 from ferrite_b200.server.api import ApiError, ChatRequest
 from ferrite_b200.server.app import AppState, make_app, snapshot_points
 from ferrite_b200.server.engine_api import MockEngine
-from ferrite_b200.server.guard import CycleDetector, LoopRules, PhaseGuard, SentenceDetector
+from ferrite_b200.server.guard import PhaseGuard
+from ferrite_b200.server.loopdet import LoopCfg, LoopRule
 from ferrite_b200.server.parser import StreamParser, parse_call_body
 from ferrite_b200.server.profiles import GenDefaults, resolve_sampling
 from ferrite_b200.server.stop import StopMatcher
@@ -206,17 +207,15 @@ def test_parser_units():
 
 
 def test_guards_and_profiles_and_snapshots():
-    cd = CycleDetector(LoopRules(min_period=2, repeats=3))
-    assert cd.feed([1, 2, 3, 4]) is None and cd.feed([5, 6, 5, 6, 5, 6]) == 2
-    sd = SentenceDetector(LoopRules(sentence_repeats=3, min_sentence_chars=10))
-    assert sd.feed("This is a repeated sentence. " * 2) is None
-    assert sd.feed("This is a repeated sentence. ") is not None
     g = PhaseGuard([9, 9], in_thinking=True, max_reasoning=5)
     assert g.feed([1, 2, 3]).force_tokens == [] and g.feed([4, 5]).force_tokens == [9, 9] and not g.in_thinking
-    g = PhaseGuard([9], in_thinking=False, max_reasoning=None, rules=LoopRules(min_period=2, repeats=3))
-    assert g.feed([7, 8] * 3).boost                                  # first sighting: boosted sampling for a while
-    assert g.feed([7, 8] * 60).finish is None                       # still inside the boost window
-    assert g.feed([7, 8] * 4).finish == "loop"                      # the loop survived the boost: end the reply
+    rules = LoopCfg(answer=LoopRule(3, 12))
+    g = PhaseGuard([9], in_thinking=False, max_reasoning=None, rules=rules)
+    a = g.feed([7, 8] * 12)
+    assert a.boost and a.boost_started                               # first sighting: boosted sampling for a while
+    assert g.feed([7, 8] * 40).finish is None                       # still inside the boost window
+    assert g.feed([7, 8] * 30).finish == "loop"                     # the loop survived the boost: end the reply
+    assert g.events.loop_breaks == 2
     from ferrite_b200.server.api import SamplingRequest
     eff = resolve_sampling(SamplingRequest(temperature=0.1), GenDefaults(), thinking=True, ctx_left=100)
     assert eff["temperature"] == 0.1 and eff["top_p"] == 0.95 and eff["max_tokens"] == 100
