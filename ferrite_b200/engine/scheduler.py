@@ -46,6 +46,14 @@ class SchedOptions:
     mixed: bool = True                 # decode rows and a prompt chunk share one forward when both are waiting
     tree_rows: int = 0                 # draft rows of a verify tree per request (0 = chains only; needs Drafter.draft_tree)
     device_sampling: bool = True       # plain sampled decode rows are drawn by the device sampler (no logits copy to the host)
+    # FE_ARRIVAL_MS (0 = off): an idle engine woken by a request waits until no other has arrived for this long (at most
+    # 4x in all, FE_ARRIVAL_MAX_MS while the server says more are coming), so requests sent together prefill in one forward
+    arrival_ms: float = 5.0
+    arrival_max_ms: float = 250.0
+    # FE_DECODE_SHARE (0 = off): least fraction of wall time spent in decode-only steps while prompts are pending and some
+    # stream decodes; FE_PREFILL_CAP: prompt rows a step may carry then (reference `sched.rs:513-528,1380-1392,1808-1818`)
+    decode_share: float = 0.3
+    prefill_cap: int = 2048
 
     @staticmethod
     def from_env() -> "SchedOptions":
@@ -54,7 +62,10 @@ class SchedOptions:
                             batch_rows=int(e.get("FE_BATCH_ROWS", "2048")),
                             finite_check=e.get("FE_FINITE_CHECK", "1") != "0",
                             step_timeout_s=float(e.get("FE_STEP_TIMEOUT", "120")), prof=int(e.get("FE_SCHED_PROF", "0")),
-                            share_min=int(e.get("FE_SHARE_MIN", str(PREFIX_MIN))), tree_rows=int(e.get("FE_TREE", "0")))
+                            share_min=int(e.get("FE_SHARE_MIN", str(PREFIX_MIN))), tree_rows=int(e.get("FE_TREE", "0")),
+                            arrival_ms=float(e.get("FE_ARRIVAL_MS", "5")), arrival_max_ms=float(e.get("FE_ARRIVAL_MAX_MS", "250")),
+                            decode_share=min(0.95, max(0.0, float(e.get("FE_DECODE_SHARE", "0.3")))),
+                            prefill_cap=max(4 * 32, int(e.get("FE_PREFILL_CAP", "2048"))))
 
 
 @dataclass
@@ -187,6 +198,9 @@ class Scheduler:
         self.step_no = 0
         self.fails = 0
         self.step_started = 0.0
+        self.incoming = 0                 # requests the server is still preparing (arrival window; set by the adapter)
+        self.t_pre = self.t_dec = 0.0     # decayed wall time of steps with / without prompt rows while a stream decodes
+        self.clock = None                 # tests: a fake clock for the fairness bookkeeping (callable -> seconds)
         self.stats = {"steps": 0, "tokens": 0, "prompt_tokens": 0, "cached_tokens": 0, "drafted": 0, "accepted": 0}
         self.panic_step = int(os.environ.get("FE_TEST_PANIC_STEP", "0"))     # fault injection (host side only)
         self.eng.ex.reclaim = self._reclaim
@@ -264,10 +278,32 @@ class Scheduler:
         try:
             if block:
                 self.backlog.append(self.waiting.get(timeout=0.05))
+                self._arrival_window()
             while True:
                 self.backlog.append(self.waiting.get_nowait())
         except queue.Empty:
             pass
+
+    def _arrival_window(self) -> None:
+        """Woken from idle: give the requests sent together a moment to arrive, so they start in the same forward
+        (reference `Worker::run` intake, `crates/fe-model/src/sched.rs:810-835`). `self.incoming` is the number of
+        requests the server is still preparing (tokenising, rendering the template)."""
+        w = self.opts.arrival_ms / 1e3
+        if w <= 0:
+            return
+        t0 = time.time()
+        cap, hard = t0 + 4 * w, t0 + self.opts.arrival_max_ms / 1e3
+        while True:
+            now = time.time()
+            coming = self.incoming > 0 and now < hard
+            left = min(w, (hard if coming else cap) - now)
+            if left <= 0:
+                break
+            try:
+                self.backlog.append(self.waiting.get(timeout=left))
+            except queue.Empty:
+                if not coming:
+                    break
 
     # ---- admission ----------------------------------------------------------------------------------
     def _pick_slot(self, prompt: Sequence[int]) -> Optional[int]:
@@ -404,6 +440,7 @@ class Scheduler:
     # ---- one step -----------------------------------------------------------------------------------
     def _step(self) -> None:
         t0 = time.time()
+        self._step_clock0 = self.clock() if self.clock is not None else 0.0
         for a in list(self.active.values()):
             if a.req.cancel.is_set():
                 self._finish(a, "cancelled")
@@ -411,6 +448,15 @@ class Scheduler:
         prefills = [a for a in self.active.values() if a.pending]
         n_dec = n_pre = 0
         budget = self.opts.batch_rows
+        # fairness: while streams decode, prompt chunks are capped and only get (1 - share) of the wall time
+        decoding = bool(decoders)
+        if not decoding:
+            self.t_pre = self.t_dec = 0.0
+        elif self.opts.decode_share > 0 and prefills:
+            budget = min(budget, self.opts.prefill_cap)
+            if self.t_pre * self.opts.decode_share > (1.0 - self.opts.decode_share) * self.t_dec:
+                prefills = []                                       # a decode-only step
+                self.stats["decode_only_steps"] = self.stats.get("decode_only_steps", 0) + 1
         if (decoders and prefills and self.opts.mixed and self.opts.spec == 0 and self.drafter is None
                 and all(a.req.sampling.greedy for a in decoders)):
             # continuous batching: the decode rows ride along with a prompt chunk, one pass over the weights for both
@@ -421,6 +467,14 @@ class Scheduler:
             n_dec = self._decode_step(decoders)
         if prefills and budget > 0:
             n_pre += self._group_prefill(prefills, budget)
+        if decoding and self.opts.decode_share > 0:
+            dt = (self.clock() - self._step_clock0) if self.clock is not None else time.time() - t0
+            self.t_pre *= 0.97                                      # decay: the share tracks the last few seconds
+            self.t_dec *= 0.97
+            if n_pre > 0:
+                self.t_pre += dt
+            else:
+                self.t_dec += dt
         if self.opts.prof:
             import sys
             print(f"step {self.step_no}: dec {n_dec} rows, prompt {n_pre} rows, {1e3 * (time.time() - t0):.2f} ms",

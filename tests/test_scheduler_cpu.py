@@ -213,6 +213,7 @@ def test_shared_prefill_forks_from_the_running_request():
 
 
 def test_mixed_steps_decode_rows_ride_with_prompt_chunks():
+    # (decode_share=0 below: this test counts steps; the fairness rule, which inserts decode-only steps, has its own test)
     """A request that is decoding keeps producing tokens while another one prefills: both share forwards, and the
     tokens are those of separate runs."""
     cfg = tiny_hybrid()
@@ -223,7 +224,7 @@ def test_mixed_steps_decode_rows_ride_with_prompt_chunks():
     ecfg = EngineConfig(n_slots=2, max_ctx=512, prefill_chunk=64)
     want = [generate(Scheduler(Engine(cfg, w, ecfg, device="cpu"), SchedOptions(mixed=False)), [p], Sampling(max_tokens=12))[0]
             for p in (p1, p2)]
-    sched = Scheduler(Engine(cfg, w, ecfg, device="cpu"), SchedOptions(mixed=True))
+    sched = Scheduler(Engine(cfg, w, ecfg, device="cpu"), SchedOptions(mixed=True, decode_share=0.0))
     outs, done = [[], []], [False, False]
 
     def sink(i):
@@ -331,3 +332,73 @@ def test_repetition_penalty_counts_the_prompt():
     assert smp.sample(logits) == 3                            # presence / frequency look at generated tokens only
     smp.observe(3)
     assert smp.sample(logits) == 5
+
+
+def test_decode_share_interleaves_decode_only_steps_with_prompt_chunks():
+    """While a stream decodes and a long prompt is pending, prompt chunks are capped (`prefill_cap`) and decode-only steps
+    are inserted until decoding has had its share of the (fake) wall time; the outputs stay the plain greedy ones."""
+    cfg, w, eng = _engine(n_slots=2, max_ctx=512, chunk=64)
+    sched = Scheduler(eng, SchedOptions(decode_share=0.5, prefill_cap=64, mixed=False, arrival_ms=0))
+    now = [0.0]
+    sched.clock = lambda: now[0]
+    short, long_p = _prompt(cfg, 8, 41), _prompt(cfg, 200, 42)
+    outs, done = [[], []], [False, False]
+
+    def sink(i):
+        def f(ev):
+            if ev.kind == "tokens":
+                outs[i].extend(ev.tokens)
+            else:
+                done[i] = True
+        return f
+    sched.submit(Request(short, Sampling(max_tokens=40), sink(0)))
+    sched.run_once()                                   # the short prompt is in and decoding
+    sched.submit(Request(long_p, Sampling(max_tokens=4), sink(1)))
+    kinds = []
+    orig_prefill = sched._group_prefill
+
+    def prefill(prefills, budget):                     # a step with prompt rows costs 4 time units, a decode-only step 1
+        n = orig_prefill(prefills, budget)
+        now[0] += 3.0
+        kinds.append(n)
+        return n
+    sched._group_prefill = prefill
+    guard = 0
+    while not all(done) and guard < 500:
+        sched.run_once()
+        now[0] += 1.0
+        guard += 1
+    assert all(done)
+    assert outs[0] == _plain(cfg, w, short, 40) and outs[1] == _plain(cfg, w, long_p, 4)
+    assert sched.stats.get("decode_only_steps", 0) >= 3          # decoding got steps of its own between the chunks
+    assert kinds and max(kinds) <= 64 + 16                       # every prompt chunk respected the cap (a tail of <= 16 rows merges)
+
+
+def test_arrival_window_collects_requests_sent_together():
+    import threading
+    import time as _time
+    cfg, w, eng = _engine(n_slots=4)
+    sched = Scheduler(eng, SchedOptions(arrival_ms=40, arrival_max_ms=400))
+    prompts = [_prompt(cfg, 12, 50 + i) for i in range(3)]
+    outs = [[] for _ in prompts]
+    done = [threading.Event() for _ in prompts]
+
+    def sink(i):
+        def f(ev):
+            if ev.kind == "tokens":
+                outs[i].extend(ev.tokens)
+            else:
+                done[i].set()
+        return f
+    sched.start()
+    try:
+        for i, p in enumerate(prompts):              # sent 10 ms apart: inside the window
+            sched.submit(Request(p, Sampling(max_tokens=3), sink(i)))
+            _time.sleep(0.01)
+        assert all(d.wait(30) for d in done)
+    finally:
+        sched.stop()
+    # all three were admitted before the first step ran: one group prefill
+    assert sched.stats["steps"] <= 1 + 3 + 1
+    for p, o in zip(prompts, outs):
+        assert o == _plain(cfg, w, p, 3)
