@@ -329,6 +329,13 @@ def _sse(obj: Any) -> bytes:
 
 async def _run(request: web.Request, chat: bool) -> web.StreamResponse:
     st: AppState = request.app["state"]
+    st.engine.incoming(+1)              # until the request is handed to the engine (or refused)
+    counted = [True]
+
+    def handed_over():
+        if counted[0]:
+            counted[0] = False
+            st.engine.incoming(-1)
     try:
         raw = await request.read()
         if len(raw) > BODY_LIMIT:
@@ -346,17 +353,35 @@ async def _run(request: web.Request, chat: bool) -> web.StreamResponse:
             req = CompletionRequest.parse(body)
             prep = prepare_completion(st, req)
     except ApiError as e:
+        handed_over()
         st.counters["errors"] += 1
         return _err(e)
+    except BaseException:
+        handed_over()
+        raise
     rid = ("chatcmpl-" if chat else "cmpl-") + uuid.uuid4().hex[:24]
     created = int(time.time())
     _capture(st, "request", body, {"id": rid, "path": request.path, "prompt_tokens": len(prep.ids)})
     st.counters["requests"] += 1
     headers = {"x-sampling-effective": pyjson.dumps(prep.effective)}
     obj = "chat.completion" if chat else "text_completion"
-    async with st.sem:
+    try:
+        await st.sem.acquire()
+    except BaseException:
+        handed_over()
+        raise
+    try:
         drv = Driver(st, prep)
         drv.start()
+        handed_over()
+        return await _respond(st, request, req, prep, drv, rid, created, headers, obj, chat)
+    finally:
+        handed_over()
+        st.sem.release()
+
+
+async def _respond(st, request, req, prep, drv, rid, created, headers, obj, chat):
+    if True:
         if req.stream:
             resp = web.StreamResponse(status=200, headers={**headers, "Content-Type": "text/event-stream; charset=utf-8",
                                                            "Cache-Control": "no-cache"})

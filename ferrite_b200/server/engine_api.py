@@ -57,6 +57,10 @@ class EngineBase:
     def metrics(self) -> Dict[str, float]:
         return {}
 
+    def incoming(self, delta: int) -> None:
+        """The server is preparing (+1) / has handed over or dropped (-1) a request: an idle engine that has just been
+        woken waits a little for requests that are still being tokenised (reference `Engine::incoming`)."""
+
     def shutdown(self) -> None:
         pass
 
@@ -82,6 +86,9 @@ class SchedulerEngine(EngineBase):
 
     def dead(self) -> Optional[str]:
         return self.sched.dead()
+
+    def incoming(self, delta: int) -> None:
+        self.sched.incoming = max(0, self.sched.incoming + delta)
 
     def load(self) -> Dict[str, int]:
         return {"running": self.sched.running, "queued": self.sched.queued}
