@@ -159,8 +159,8 @@ class StackWeight:
         return (self.rows, self.cols)
 
     def dequantize(self, dtype=torch.float32) -> torch.Tensor:
-        return torch.cat([(p.dequantize(dtype) if hasattr(p, "dequantize") else
-                           p.dense.to(dtype) if hasattr(p, "dense") else p.to(dtype)).cpu() for p in self.parts], 0)
+        return torch.cat([(p.to(dtype) if isinstance(p, torch.Tensor) else
+                           p.dequantize(dtype) if hasattr(p, "dequantize") else p.dense.to(dtype)).cpu() for p in self.parts], 0)
 
 
 def from_packed(p, device, dtype, on_gpu: bool, keep_dense: bool = True):

@@ -17,6 +17,12 @@ def build_engine(args, tok):
     from .engine_api import MockEngine, SchedulerEngine
     if args.mock or args.engine == "mock":
         return MockEngine(tok, args.served_model_name, max_batch=args.slots, max_len=args.max_model_len)
+    if args.engine == "fake":
+        # the deterministic CPU step model behind the real batching loop (protocol and load tests without weights)
+        from .batch import BatchConfig, BatchEngine, FakeModel
+        return BatchEngine(BatchConfig("fake", args.prefill_chunk),
+                           lambda: FakeModel(args.slots, args.max_model_len, min(args.prefill_chunk, 2048), vocab=tok.vocab_size
+                                             if hasattr(tok, "vocab_size") else 4096), args.served_model_name)
     import torch
 
     from ..engine.engine import Engine
@@ -59,6 +65,22 @@ def build_engine(args, tok):
                                 **({"device_id": torch.device("cuda", local)} if on_gpu else {}))
         tp = TensorParallel(dist.group.WORLD, f"cuda:{local}" if on_gpu else "cpu")
         args.device = f"cuda:{local}" if on_gpu else "cpu"
+    if args.model_dir and weights is None:
+        ggufs = sorted(f for f in os.listdir(args.model_dir) if f.endswith(".gguf"))
+        if ggufs:
+            from ..formats import gguf as G
+            from ..formats.gguf_model import config_from_gguf, load_gguf_weights
+            path = os.path.join(args.model_dir, ggufs[0])
+            g = G.Gguf(path)
+            cfg = config_from_gguf(g, cfg)
+            g.close()
+            weights = load_gguf_weights(path, cfg)
+    if args.engine == "ferrite-batch":
+        # the small engine: plain continuous batching over the step-model surface (no speculation, no parking)
+        from .batch import BatchConfig, BatchEngine, EngineStepModel
+        return BatchEngine(BatchConfig("ferrite-batch", args.prefill_chunk),
+                           lambda: EngineStepModel(Engine(cfg, weights, ecfg, device=args.device or None, seed=0)),
+                           args.served_model_name)
     eng = Engine(cfg, weights, ecfg, device=args.device or None, seed=0, tp=tp)
     if tp is not None:
         from ..engine.follow import Leader, follow
@@ -90,7 +112,7 @@ def main(argv=None) -> int:
     ap.add_argument("--host", default=site.host)
     ap.add_argument("--port", type=int, default=site.port)
     ap.add_argument("--served-model-name", default=site.served_model_name)
-    ap.add_argument("--engine", default="ferrite", choices=["ferrite", "mock"])
+    ap.add_argument("--engine", default="ferrite", choices=["ferrite", "ferrite-batch", "fake", "mock"])
     ap.add_argument("--preset", default="tiny", choices=sorted(PRESETS))
     ap.add_argument("--layers", type=int, default=0)
     ap.add_argument("--weights", default=os.environ.get("FERRITE_WEIGHTS", "bf16"))
