@@ -15,9 +15,9 @@ from . import pyjson
 DEFAULT_TEMPLATE = r"""{%- if tools %}
 {{- '<|im_start|>system\n' }}
 {%- if messages[0].role == 'system' %}{{- messages[0].content + '\n\n' }}{%- endif %}
-{{- "# Tools\n\nYou may call one or more functions to assist with the user query.\n\nYou are provided with function signatures within <tools></tools> XML tags:\n<tools>" }}
+{{- "# Tools\n\nYou have access to the following functions:\n\n<tools>" }}
 {%- for tool in tools %}{{- "\n" }}{{- tool | tojson }}{%- endfor %}
-{{- "\n</tools>\n\nFor each function call, return a json object with function name and arguments within <tool_call></tool_call> XML tags:\n<tool_call>\n{\"name\": <function-name>, \"arguments\": <args-json-object>}\n</tool_call><|im_end|>\n" }}
+{{- "\n</tools>\n\nTo call a function, reply in exactly this format and nothing after it:\n\n<tool_call>\n<function=function_name>\n<parameter=parameter_name>\nvalue\n</parameter>\n</function>\n</tool_call>\n\nGive every required parameter. A value may span several lines. Explain before the call, never after it.<|im_end|>\n" }}
 {%- else %}
 {%- if messages[0].role == 'system' %}{{- '<|im_start|>system\n' + messages[0].content + '<|im_end|>\n' }}{%- endif %}
 {%- endif %}
@@ -28,9 +28,16 @@ DEFAULT_TEMPLATE = r"""{%- if tools %}
 {%- if message.reasoning_content %}{{- '<think>\n' + message.reasoning_content + '\n</think>\n\n' }}{%- endif %}
 {%- if message.content %}{{- message.content }}{%- endif %}
 {%- for tc in message.tool_calls or [] %}
-{{- '\n<tool_call>\n{"name": "' + tc.function.name + '", "arguments": ' }}
-{%- if tc.function.arguments is string %}{{- tc.function.arguments }}{%- else %}{{- tc.function.arguments | tojson }}{%- endif %}
-{{- '}\n</tool_call>' }}
+{%- if message.content or not loop.first %}{{- '\n' }}{%- endif %}
+{{- '<tool_call>\n<function=' + tc.function.name + '>\n' }}
+{%- if tc.function.arguments is mapping %}
+{%- for k, v in tc.function.arguments | items %}
+{{- '<parameter=' + k + '>\n' }}
+{%- if v is string %}{{- v }}{%- else %}{{- v | tojson }}{%- endif %}
+{{- '\n</parameter>\n' }}
+{%- endfor %}
+{%- endif %}
+{{- '</function>\n</tool_call>' }}
 {%- endfor %}
 {{- '<|im_end|>\n' }}
 {%- elif message.role == 'tool' %}
