@@ -27,6 +27,9 @@ int fb_allreduce_oneshot(void* y, const void* part, const void* res, long count,
 int fb_argmax_gather(int* ids, float* vals, const float* logits, long stride, int rows, int n_local, int vocab_offset,
                      const void* const* peers, int rank, int world, int max_ctas, long slot_floats, uint32_t* epochs,
                      int* status, unsigned spin_limit, cudaStream_t s);
+// start-up self-test: this rank's pattern into its lane (parity 0, source = rank) of every rank's workspace
+int fb_p2p_pattern(const void* const* peers, int rank, int world, int max_ctas, long slot_floats, long word_off,
+                   int n_words, uint32_t seed, cudaStream_t s);
 int fb_comm_wait_probe(const uint32_t* flag, uint32_t want, unsigned limit, int* status, cudaStream_t s);
 
 // ---- gemv_nvfp4.cu: NVFP4-weight GEMV (W4A16), plain and with the fused one-shot all-reduce ----

@@ -381,6 +381,10 @@ void register_ext(pybind11::module_& m) {
   m.def("allreduce_oneshot", &allreduce_oneshot);
   m.def("argmax_gather", &argmax_gather);
   m.def("comm_wait_probe", &comm_wait_probe);
+  m.def("p2p_pattern", [](const Comm& c, int64_t word_off, int64_t n_words, int64_t seed) {
+    check(fb_p2p_pattern(c.peers.data(), c.rank, c.world, c.max_ctas, c.slot_floats, (long)word_off, (int)n_words,
+                         (uint32_t)seed, cur_stream()), "p2p_pattern");
+  });
   m.def("comm_trace_set", [](c10::optional<Tensor> buf) {
     if (buf.has_value() && buf->defined()) {
       TORCH_CHECK(buf->scalar_type() == torch::kInt64 && buf->is_cuda() && buf->is_contiguous() &&

@@ -168,6 +168,20 @@ __global__ void __launch_bounds__(1024) argmax_gather_kernel(int* __restrict__ i
   comm_epoch_end(cb, epoch);
 }
 
+// Start-up self-test of every ordered pair of GPUs: this rank stores a pattern that names (source, destination, word)
+// into its own lane of every peer's workspace with the same plain peer stores the fused kernels use. The host then
+// compares what arrived with what each source must have written (`parallel/selftest.py`).
+__global__ void p2p_pattern_kernel(CommBuf cb, long word_off, int n_words, uint32_t seed) {
+  for (int p = 0; p < cb.world; ++p) {
+    uint32_t* dst = reinterpret_cast<uint32_t*>(comm_data(cb.peer[p], cb, 0, cb.rank)) + word_off;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n_words; i += gridDim.x * blockDim.x) {
+      uint32_t v = seed ^ ((uint32_t)cb.rank * 0x9E3779B1u) ^ ((uint32_t)p * 0x85EBCA77u) ^ ((uint32_t)i * 0xC2B2AE3Du);
+      v ^= v >> 15; v *= 0x2C1B3C6Du; v ^= v >> 12;
+      asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(dst + i), "r"(v) : "memory");
+    }
+  }
+}
+
 // A wait that is made to run out on purpose by a flag nobody sets: exercises the timeout path on one GPU
 // without faulting anything. Returns through the status word.
 __global__ void comm_wait_probe_kernel(const uint32_t* flag, uint32_t want, unsigned limit, int* status) {
@@ -276,6 +290,15 @@ extern "C" int fb_argmax_gather(int* ids, float* vals, const float* logits, long
   CommBuf cb;
   fill_comm(cb, peers, rank, world, max_ctas, slot_floats, epochs, status, spin_limit);
   argmax_gather_kernel<<<rows, 1024, 0, s>>>(ids, vals, logits, stride, n_local, vocab_offset, cb);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int fb_p2p_pattern(const void* const* peers, int rank, int world, int max_ctas, long slot_floats, long word_off,
+                              int n_words, uint32_t seed, cudaStream_t s) {
+  if (n_words <= 0 || word_off < 0 || word_off + n_words > slot_floats - COMM_TOP_RESERVE) return -8;
+  CommBuf cb;
+  fill_comm(cb, peers, rank, world, max_ctas, slot_floats, nullptr, nullptr, 0);
+  p2p_pattern_kernel<<<8, 256, 0, s>>>(cb, word_off, n_words, seed);
   return (int)cudaGetLastError();
 }
 

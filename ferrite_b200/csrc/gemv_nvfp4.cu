@@ -1,6 +1,16 @@
-// NVFP4-weight GEMV for 1..8 activation rows (W4A16): e2m1 codes are converted to f16x2 with the sm_100a
-// cvt instruction, multiplied against f16 activations with HFMA2 inside each 16-value block, and the block
-// sums are scaled (e4m3 block scale) into fp32 accumulators. 0.5625 bytes per weight cross HBM instead of 2.
+// NVFP4-weight GEMV for 1..8 activation rows (W4A16): e2m1 codes become f16x2 by bit placement (two shifts and two
+// logic ops per pair of weights, no conversion instruction), are multiplied against f16 activations with HFMA2 inside
+// each 16-value block, and the block sums are scaled (e4m3 block scale) into fp32 accumulators. 0.5625 bytes per
+// weight cross HBM instead of 2.
+//
+// Why no `cvt.rn.f16x2.e2m1x2`: measured on B200 (ncu, gate|up 2 x 17408 x 5120, 1 row) the conversion pipe was 86 %
+// busy and the kernel ran at 2.15 TB/s; the packed-format conversions issue at a fraction of the ALU rate. The bit
+// placement: a nibble S E E M put at f16 bits 15 and 11..9 is the f16 number e2m1 * 2^-14 (exponent field 000EE,
+// mantissa M0..0; EE = 0 is an f16 subnormal, which is exactly M * 0.5 * 2^-14), so the factor 2^14 moves into the
+// activations: every activation row is staged as x * 2^s with s = min(14, floor(log2(32768 / max|x|))), which also
+// keeps the f16 products in the normal range, and the epilogue multiplies by 2^(14 - s). The staged activations are
+// laid out so that a warp's 16-byte reads of them are contiguous (the first version's reads were 64 bytes apart:
+// 4-way bank conflicts, 67 % of the shared-memory pipe).
 //
 // The decode-side role of the reference's low-bit GEMVs (`exl3_gemv*`, `kernels/k-exl3/src/gemv.rs:227`; NVFP4
 // itself serves only its prompt path, `kernels/k-fp4/src/lib.rs`). Same structure as the bf16 GEMV: the next
@@ -77,116 +87,172 @@ __device__ __forceinline__ void g4_load(Batch4& b, const Gemv4Args& a, const int
   }
 }
 
-__device__ __forceinline__ __half2 e2m1x2_to_half2(uint32_t byte) {
-  __half2_raw h = __nv_cvt_fp4x2_to_halfraw2((__nv_fp4x2_storage_t)(byte & 0xffu), __NV_E2M1);
-  return *reinterpret_cast<__half2*>(&h);
-}
 __device__ __forceinline__ float e4m3_to_float(uint32_t byte) {
   __half_raw h = __nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)(byte & 0xffu), __NV_E4M3);
   return __half2float(*reinterpret_cast<__half*>(&h));
 }
+
+// Eight e2m1 codes of one 32-bit word -> four f16x2 holding (code j, code j + 4) * 2^-14, j = 0..3: nibble j sits
+// 16 bits below nibble j + 4, so one shift lines both up with the two halves of the result.
+__device__ __forceinline__ void e2m1x8_to_half2x4(uint32_t w, __half2 (&h)[4]) {
+  constexpr uint32_t SGN = 0x80008000u, MAG = 0x0E000E00u;
+  uint32_t o[4];
+  o[0] = ((w << 12) & SGN) | ((w << 9) & MAG);
+  o[1] = ((w << 8) & SGN) | ((w << 5) & MAG);
+  o[2] = ((w << 4) & SGN) | ((w << 1) & MAG);
+  o[3] = (w & SGN) | ((w >> 3) & MAG);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) h[j] = *reinterpret_cast<__half2*>(&o[j]);
+}
+
+// Position (in halfs, inside a staged row) of the 16-byte chunk that holds the activations of weight word `wi`
+// (8 codes) of lane `lane` in the span that starts at `span0`: chunks of one word index are contiguous over the lanes.
+__device__ __forceinline__ int g4_xpos(int span0, int lane, int wi) { return span0 + (wi * 32 + lane) * 8; }
 
 template <int M>
 __device__ __forceinline__ void g4_consume(float (&acc)[G4_R][M], const Batch4& b, const __half* xs, int kc, int koff) {
   const int lane = threadIdx.x & 31;
 #pragma unroll
   for (int u = 0; u < G4_GROUP; ++u) {
-    const int k = koff + u * G4_SPAN + lane * 32;
-    if (k >= kc) continue;
-    __half2 wh[G4_R][16];
+    const int span0 = koff + u * G4_SPAN;
+    if (span0 >= kc) continue;
     float sc[G4_R][2];
 #pragma unroll
     for (int r = 0; r < G4_R; ++r) {
-      const uint32_t words[4] = {b.w[r][u].x, b.w[r][u].y, b.w[r][u].z, b.w[r][u].w};
-#pragma unroll
-      for (int j = 0; j < 4; ++j)
-#pragma unroll
-        for (int t = 0; t < 4; ++t) wh[r][j * 4 + t] = e2m1x2_to_half2(words[j] >> (8 * t));
       const uint32_t sw = (u < 2) ? b.s[r].x : b.s[r].y;
       sc[r][0] = e4m3_to_float(sw >> ((u & 1) * 16));
       sc[r][1] = e4m3_to_float(sw >> ((u & 1) * 16 + 8));
     }
+    __half2 s0[G4_R][M], s1[G4_R][M];                         // two chains per (row, activation row) inside a block
 #pragma unroll
-    for (int m = 0; m < M; ++m) {
-      const uint4* xp = reinterpret_cast<const uint4*>(xs + (size_t)m * kc + k);
-      __half2 xh[16];
+    for (int wi = 0; wi < 4; ++wi) {
+      if ((wi & 1) == 0) {
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        uint4 v = xp[j];
-        xh[j * 4 + 0] = *reinterpret_cast<__half2*>(&v.x); xh[j * 4 + 1] = *reinterpret_cast<__half2*>(&v.y);
-        xh[j * 4 + 2] = *reinterpret_cast<__half2*>(&v.z); xh[j * 4 + 3] = *reinterpret_cast<__half2*>(&v.w);
+        for (int r = 0; r < G4_R; ++r)
+#pragma unroll
+          for (int m = 0; m < M; ++m) { s0[r][m] = __float2half2_rn(0.f); s1[r][m] = __float2half2_rn(0.f); }
       }
+      __half2 wh[G4_R][4];
 #pragma unroll
       for (int r = 0; r < G4_R; ++r) {
+        const uint32_t word = wi == 0 ? b.w[r][u].x : wi == 1 ? b.w[r][u].y : wi == 2 ? b.w[r][u].z : b.w[r][u].w;
+        e2m1x8_to_half2x4(word, wh[r]);
+      }
 #pragma unroll
-        for (int blk = 0; blk < 2; ++blk) {
-          __half2 s0 = __float2half2_rn(0.f), s1 = __float2half2_rn(0.f);
+      for (int m = 0; m < M; ++m) {
+        const uint4 xv = *reinterpret_cast<const uint4*>(xs + (size_t)m * kc + g4_xpos(span0, lane, wi));
+        const __half2 x0 = *reinterpret_cast<const __half2*>(&xv.x), x1 = *reinterpret_cast<const __half2*>(&xv.y);
+        const __half2 x2 = *reinterpret_cast<const __half2*>(&xv.z), x3 = *reinterpret_cast<const __half2*>(&xv.w);
 #pragma unroll
-          for (int j = 0; j < 8; j += 2) {
-            s0 = __hfma2(wh[r][blk * 8 + j], xh[blk * 8 + j], s0);
-            s1 = __hfma2(wh[r][blk * 8 + j + 1], xh[blk * 8 + j + 1], s1);
-          }
-          float2 f0 = __half22float2(s0), f1 = __half22float2(s1);
-          acc[r][m] = fmaf((f0.x + f0.y) + (f1.x + f1.y), sc[r][blk], acc[r][m]);
+        for (int r = 0; r < G4_R; ++r) {
+          s0[r][m] = __hfma2(wh[r][0], x0, s0[r][m]);
+          s1[r][m] = __hfma2(wh[r][1], x1, s1[r][m]);
+          s0[r][m] = __hfma2(wh[r][2], x2, s0[r][m]);
+          s1[r][m] = __hfma2(wh[r][3], x3, s1[r][m]);
         }
+      }
+      if (wi & 1) {                                           // words 0,1 = block 0 of this lane, words 2,3 = block 1
+#pragma unroll
+        for (int r = 0; r < G4_R; ++r)
+#pragma unroll
+          for (int m = 0; m < M; ++m) {
+            const float2 f = __half22float2(__hadd2(s0[r][m], s1[r][m]));
+            acc[r][m] = fmaf(f.x + f.y, sc[r][wi >> 1], acc[r][m]);
+          }
       }
     }
   }
 }
 
-// Stage X[:, k0:k0+kc) as f16 (normalised when asked); positions past K are zero.
+// Stage X[:, k0:k0+kc) as f16 scaled by 2^s of its row (normalised when asked), in the chunk order `g4_xpos` reads;
+// positions past K are zero. A thread writes one 16-byte chunk: the 8 activations of one weight word as the pairs
+// (j, j + 4).
 template <int M>
-__device__ __forceinline__ void g4_stage(const Gemv4Args& a, __half* xs, const float* rscale, int k0, int kc) {
+__device__ __forceinline__ void g4_stage(const Gemv4Args& a, __half* xs, const float* rscale, const float* xpow, int k0,
+                                         int kc) {
   for (int idx = threadIdx.x; idx < M * (kc / 8); idx += blockDim.x) {
-    int m = idx / (kc / 8), c = idx % (kc / 8);
-    int k = k0 + c * 8;
-    __half2 o[4] = {__float2half2_rn(0.f), __float2half2_rn(0.f), __float2half2_rn(0.f), __float2half2_rn(0.f)};
+    const int m = idx / (kc / 8), c = idx % (kc / 8);
+    const int k = k0 + c * 8;
+    float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     if (m < a.M && k < a.K) {
-      uint4 v = *reinterpret_cast<const uint4*>(a.X + (size_t)m * a.ldx + k);
-      uint32_t xu[4] = {v.x, v.y, v.z, v.w};
+      uint4 xv = *reinterpret_cast<const uint4*>(a.X + (size_t)m * a.ldx + k);
+      uint32_t xu[4] = {xv.x, xv.y, xv.z, xv.w};
+      const float p = xpow[m];
       if (a.norm_w) {
         uint4 wv = __ldg(reinterpret_cast<const uint4*>(a.norm_w + k));
         uint32_t wu[4] = {wv.x, wv.y, wv.z, wv.w};
-        float r = rscale[m];
+        const float r = rscale[m];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           // round through bf16 first so this path sees the same normalised activations as the bf16 kernels
-          float a0 = bf2f(f2bf(bf_lo(xu[j]) * r * (bf_lo(wu[j]) + 1.f)));
-          float a1 = bf2f(f2bf(bf_hi(xu[j]) * r * (bf_hi(wu[j]) + 1.f)));
-          o[j] = __floats2half2_rn(a0, a1);
+          v[2 * j] = bf2f(f2bf(bf_lo(xu[j]) * r * (bf_lo(wu[j]) + 1.f))) * p;
+          v[2 * j + 1] = bf2f(f2bf(bf_hi(xu[j]) * r * (bf_hi(wu[j]) + 1.f))) * p;
         }
       } else {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) o[j] = __floats2half2_rn(bf_lo(xu[j]), bf_hi(xu[j]));
+        for (int j = 0; j < 4; ++j) { v[2 * j] = bf_lo(xu[j]) * p; v[2 * j + 1] = bf_hi(xu[j]) * p; }
       }
     }
+    __half2 o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o[j] = __floats2half2_rn(v[j], v[j + 4]);
     uint4 ov;
     ov.x = *reinterpret_cast<uint32_t*>(&o[0]); ov.y = *reinterpret_cast<uint32_t*>(&o[1]);
     ov.z = *reinterpret_cast<uint32_t*>(&o[2]); ov.w = *reinterpret_cast<uint32_t*>(&o[3]);
-    *reinterpret_cast<uint4*>(xs + (size_t)m * kc + c * 8) = ov;
+    const int rel = c * 8;                                    // position inside the staged chunk
+    const int span0 = rel / G4_SPAN * G4_SPAN, r = rel % G4_SPAN;
+    *reinterpret_cast<uint4*>(xs + (size_t)m * kc + g4_xpos(span0, r / 32, (r % 32) / 8)) = ov;
   }
 }
 
+// Per row: rscale[m] = rsqrt(mean(x_m^2) + eps) (when a norm weight is given, else 1), xpow[m] = 2^s, the power of
+// two the staged row is multiplied by (s = min(14, floor(log2(32768 / max|staged x|)))), and xinv[m] = 2^(14 - s)
+// for the epilogue. All threads of the CTA take part.
 template <int M>
-__device__ __forceinline__ void g4_row_scales(const Gemv4Args& a, float* rscale, float* scratch) {
+__device__ __forceinline__ void g4_row_scales(const Gemv4Args& a, float* rscale, float* xpow, float* xinv, float* scratch) {
   for (int m = 0; m < M; ++m) {
-    float ss = 0.f;
+    float ss = 0.f, am = 0.f;
     if (m < a.M) {
       for (int k = threadIdx.x * 8; k < a.K; k += blockDim.x * 8) {
         uint4 v = *reinterpret_cast<const uint4*>(a.X + (size_t)m * a.ldx + k);
         uint32_t u[4] = {v.x, v.y, v.z, v.w};
+        if (a.norm_w) {
+          uint4 wv = __ldg(reinterpret_cast<const uint4*>(a.norm_w + k));
+          uint32_t wu[4] = {wv.x, wv.y, wv.z, wv.w};
 #pragma unroll
-        for (int j = 0; j < 4; ++j) { float x0 = bf_lo(u[j]), x1 = bf_hi(u[j]); ss += x0 * x0 + x1 * x1; }
+          for (int j = 0; j < 4; ++j) {
+            const float x0 = bf_lo(u[j]), x1 = bf_hi(u[j]);
+            ss += x0 * x0 + x1 * x1;
+            am = fmaxf(am, fmaxf(fabsf(x0 * (bf_lo(wu[j]) + 1.f)), fabsf(x1 * (bf_hi(wu[j]) + 1.f))));
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) am = fmaxf(am, fmaxf(fabsf(bf_lo(u[j])), fabsf(bf_hi(u[j]))));
+        }
       }
     }
-    float tot = block_sum(ss, scratch);
-    if (threadIdx.x == 0) rscale[m] = rsqrtf(tot / (float)a.K + a.eps);
+    const float tot = block_sum(ss, scratch);
+    const float amax = block_max(am, scratch);
+    if (threadIdx.x == 0) {
+      const float r = a.norm_w ? rsqrtf(tot / (float)a.K + a.eps) : 1.f;
+      rscale[m] = r;
+      const float top = amax * r * 1.01f;                      // the staged values are rounded to bf16 first: a margin
+      int s = 14;
+      if (top > 0.f) {
+        int e;
+        frexpf(32768.f / top, &e);                             // 32768 / top = f * 2^e, f in [0.5, 1)
+        s = min(14, max(-14, e - 1));
+      }
+      xpow[m] = ldexpf(1.f, s);
+      xinv[m] = ldexpf(1.f, 14 - s);
+    }
   }
   __syncthreads();
 }
 
 template <int M, bool SWIGLU, class Store>
 __device__ __forceinline__ void gemv4_main(const Gemv4Args& a, __half* xs, float* rscale, float* scratch, Store store) {
+  __shared__ float xpow[M], xinv[M];
   const int warp = threadIdx.x >> 5;
   const int row0 = blockIdx.x * a.rows_per_cta;
   const int row_end = min(a.N, row0 + a.rows_per_cta);
@@ -201,7 +267,7 @@ __device__ __forceinline__ void gemv4_main(const Gemv4Args& a, __half* xs, float
   g4_load(b, a, rows, 0);
   pdl_wait();
 
-  if (a.norm_w) g4_row_scales<M>(a, rscale, scratch);
+  g4_row_scales<M>(a, rscale, xpow, xinv, scratch);
 
   const int passes = (row_end - row0 + G4_WARPS * RW - 1) / (G4_WARPS * RW);
   for (int pass = 0; pass < passes; ++pass, n += G4_WARPS * RW) {
@@ -211,7 +277,7 @@ __device__ __forceinline__ void gemv4_main(const Gemv4Args& a, __half* xs, float
       const int k0 = c * a.kc;
       if (nchunks > 1 || pass == 0) {
         __syncthreads();
-        g4_stage<M>(a, xs, rscale, k0, a.kc);
+        g4_stage<M>(a, xs, rscale, xpow, k0, a.kc);
         __syncthreads();
       }
       if (active) {
@@ -233,7 +299,7 @@ __device__ __forceinline__ void gemv4_main(const Gemv4Args& a, __half* xs, float
         const int wr = SWIGLU ? (min(n, a.N - 1) + r * a.N) : min(n + r, a.N - 1);
         const float gs = a.row_alpha ? __ldg(a.row_alpha + wr) : a.global_scale;
 #pragma unroll
-        for (int m = 0; m < M; ++m) acc[r][m] = warp_sum(acc[r][m]) * gs;
+        for (int m = 0; m < M; ++m) acc[r][m] = warp_sum(acc[r][m]) * (gs * xinv[m]);
       }
       store(acc, n);
     }

@@ -66,6 +66,8 @@ class TensorParallel:
         self.comm = C.make_comm(ptrs, self.rank, MAX_CTAS, SLOT_FLOATS, self.epochs, self.status, spin_limit,
                                 self.max_resident)
         self.C = C
+        self.slot_floats = SLOT_FLOATS
+        self.data_offset = 2 * 8 * MAX_CTAS * 4                    # bytes of the flag area in front of the data slots
 
     # ---- sequence-parallel prompt path: all-gather -> GEMM and GEMM -> reduce-scatter ------------------------
     def setup_big(self, max_rows: int, max_cols: int, spin_limit: int = 0) -> None:
@@ -142,6 +144,11 @@ class TensorParallel:
         out = torch.empty(self.world * per, x_shard.shape[1], dtype=x_shard.dtype, device=x_shard.device)
         dist.all_gather_into_tensor(out, pad, group=self.group)
         return out[:T]
+
+    def selftest(self) -> None:
+        """Start-up check of every ordered pair of ranks (see `parallel/selftest.py`); every rank calls it."""
+        from .selftest import p2p_selftest
+        p2p_selftest(self)
 
     def check(self) -> None:
         """Raise when a peer wait ran out (the kernel returned normally and left a status code)."""

@@ -64,6 +64,7 @@ def build_engine(args, tok):
         dist.init_process_group("nccl" if on_gpu else "gloo",
                                 **({"device_id": torch.device("cuda", local)} if on_gpu else {}))
         tp = TensorParallel(dist.group.WORLD, f"cuda:{local}" if on_gpu else "cpu")
+        tp.selftest()                      # refuse to serve over a peer path that corrupts data
         args.device = f"cuda:{local}" if on_gpu else "cpu"
     if args.model_dir and weights is None:
         ggufs = sorted(f for f in os.listdir(args.model_dir) if f.endswith(".gguf"))

@@ -94,3 +94,44 @@ def test_missing_rank_is_an_error_not_a_hang():
             p.terminate()
     assert got[1] == "left"
     assert got[0].startswith("error")
+
+
+def _selftest_worker(rank, world, port, corrupt, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    if corrupt:
+        os.environ["FE_TEST_P2P_CORRUPT"] = corrupt
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=60))
+    from ferrite_b200.parallel.tp import TensorParallel
+    tp = TensorParallel(dist.group.WORLD, "cpu", fused=False)
+    try:
+        tp.selftest()
+        q.put((rank, "ok"))
+    except RuntimeError as e:
+        q.put((rank, str(e)))
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("corrupt", ["", "2,0"])
+def test_p2p_selftest_checks_every_ordered_pair(corrupt):
+    """Three CPU ranks: the clean run passes on every rank; a word flipped on the receiving side of the pair 2 -> 0
+    (host-side injection) makes EVERY rank refuse, naming the pair."""
+    from ferrite_b200.parallel.selftest import expected_pattern, verify
+    assert verify([expected_pattern(s, 1, 64) for s in range(3)], 1) == []
+    bad = [expected_pattern(s, 1, 64) for s in range(3)]
+    bad[2][5] ^= 1
+    assert verify(bad, 1) == [(2, 1, 5)]
+    world = 3
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_selftest_worker, args=(r, world, port, corrupt, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = dict(q.get(timeout=120) for _ in range(world))
+    for p in procs:
+        p.join(timeout=60)
+    if not corrupt:
+        assert all(v == "ok" for v in got.values()), got
+    else:
+        assert all("2->0" in v and "refusing" in v for v in got.values()), got

@@ -37,6 +37,7 @@ def _worker_body(rank, world, port, q):
     from ferrite_b200.ops.cuda_ops import CudaOps
     from ferrite_b200.parallel.tp import TensorParallel
     tp = TensorParallel(dist.group.WORLD, dev, fused=True)
+    tp.selftest()                                           # every ordered pair moves its pattern through peer stores
     ops = CudaOps(dev)
     res = {}
     g = torch.Generator(device=dev).manual_seed(1)          # same seed: every rank draws the same tensors
