@@ -5,11 +5,20 @@
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
         bench.py --gpus N --steps K --warmup W
 
-The model is BASELINE config 2 (64 layers 3:1 GDN:GQA, hidden 5120, FFN 17408, vocab 151936) with random-init
-weights and synthetic uniform-random prompts. N > 1 runs tensor parallel (strong scaling: the same request
-stream on more GPUs). A step is one decode step of every stream. Timed with CUDA events between barriers +
-synchronizes, max over ranks. Weights (tens of GB) are streamed every step, far larger than the 126 MB L2.
-One JSON line on rank 0. `--impl reference` reports that the Rust/nvptx reference cannot be built here.
+The model is the 27B-class dense hybrid (64 layers 3:1 GDN:GQA, hidden 5120, FFN 17408, vocab 151936) with random-init
+weights and synthetic uniform-random prompts. N > 1 runs tensor parallel (strong scaling: the same request stream on
+more GPUs). A step is one decode step of every stream. Every timed region is exactly K steps between a barrier +
+synchronize on both sides, timed with CUDA events, max over ranks; the region is repeated until at least 2 s have been
+timed and the median region is reported (`config.repeats` says how many). Weights (tens of GB) are streamed every step,
+far larger than the 126 MB L2. Under tensor parallelism the tokens every rank produced are compared: they must be
+identical. One JSON line on rank 0. `--impl reference` reports that the Rust/nvptx reference cannot be built here.
+
+Extras (skipped with --no-extras): 4 streams (device-timed and end to end), a 17-row verify step with and without the
+commit, prefill at 2K and 32K, decode from NVFP4 weights (`--dtype` picks the headline's weights; the extra always
+measures the other of bf16 / nvfp4-a16), and speculative decoding through the scheduler: accepted tokens per step and
+tok/s with the context-copy proposer on a repeated-span prompt, and with an oracle drafter whose acceptance rate is a
+dial (the drafts are the tokens a plain greedy run produced, each corrupted with probability 1 - p; the block drafter's
+own forward pass runs every step so its cost is charged), checked to reproduce the plain run token for token.
 """
 from __future__ import annotations
 
@@ -26,6 +35,9 @@ BASELINE_DECODE_1 = 33.7      # tok/s, plain decode 1 stream at 2K ctx, 2x GB10 
 BASELINE_DECODE_4 = 119.1     # tok/s aggregate, 4 streams (reference TP2.md:117)
 BASELINE_PREFILL_2K = 3669.0  # tok/s (reference TP2.md:114)
 BASELINE_PREFILL_32K = 2880.0
+BASELINE_SPEC_1 = 267.0       # tok/s, block-draft speculation, code, 1 request (reference README.md:55)
+BASELINE_SPEC_4 = 467.0
+MIN_TIMED_S = 2.0
 
 
 class ClockSampler:
@@ -43,7 +55,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200", "-i", str(self.idx)],
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100", "-i", str(self.idx)],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except Exception:
@@ -85,7 +97,8 @@ def main():
     ap.add_argument("--streams", type=int, default=1)
     ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers (the JSON line says so)")
     ap.add_argument("--dtype", default="bf16")
-    ap.add_argument("--no-extras", action="store_true", help="skip the 4-stream and prefill measurements")
+    ap.add_argument("--no-extras", action="store_true", help="only the headline decode measurement and the 2K prefill")
+    ap.add_argument("--min-timed-s", type=float, default=MIN_TIMED_S)
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -112,6 +125,7 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
         from ferrite_b200.parallel.tp import TensorParallel
         tp = TensorParallel(dist.group.WORLD, dev)
+        tp.selftest()
     assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE {world}: launch with torch.distributed.run"
 
     cfg = hybrid_27b()
@@ -121,12 +135,7 @@ def main():
     K = args.steps
     n_streams_max = 4
     long_ctx = 0 if args.no_extras else 32768
-    ecfg = EngineConfig(n_slots=n_streams_max, max_ctx=max(args.ctx + 2 * (K + W) + 64, long_ctx + 64), prefill_chunk=2048,
-                        weight_dtype=args.dtype)
-    eng = Engine(cfg, None, ecfg, device=str(dev), seed=0, tp=tp)
-    gen = torch.Generator().manual_seed(1234)
-    prompts = [torch.randint(0, cfg.vocab, (args.ctx,), generator=gen).tolist() for _ in range(n_streams_max)]
-    feed = torch.randint(0, cfg.vocab, (n_streams_max, 4 * (K + W) + 8), generator=gen).tolist()
+    budget_steps = 64 * (K + W) + 4096          # positions a slot may advance over all repeats of all regions
 
     def barrier():
         if world > 1:
@@ -140,8 +149,16 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    # ---- prefill (timed as an extra) -------------------------------------------------------------------
-    def timed_prefill(slot, prompt):
+    def build(dtype):
+        ecfg = EngineConfig(n_slots=n_streams_max, max_ctx=max(args.ctx + budget_steps + 64, long_ctx + 64), prefill_chunk=2048,
+                            weight_dtype=dtype)
+        return Engine(cfg, None, ecfg, device=str(dev), seed=0, tp=tp)
+
+    gen = torch.Generator().manual_seed(1234)
+    prompts = [torch.randint(0, cfg.vocab, (args.ctx,), generator=gen).tolist() for _ in range(n_streams_max)]
+    feed = torch.randint(0, cfg.vocab, (n_streams_max, budget_steps + 8), generator=gen).tolist()
+
+    def timed_prefill(eng, slot, prompt):
         eng.reset_slot(slot)
         barrier()
         e0, e1 = torch.cuda.Event(True), torch.cuda.Event(True)
@@ -151,103 +168,134 @@ def main():
         barrier()
         return max_over_ranks(e0.elapsed_time(e1))
 
-    timed_prefill(0, prompts[0][:256])            # warm the prompt kernels
-    prefill_ms = timed_prefill(0, prompts[0])
-    for s in range(1, n_streams_max):
-        eng.prefill(s, prompts[s]) if not args.no_extras else None
-    eng.check()
-
-    def decode_run(n_streams: int, steps: int, warm: int, e2e: bool):
-        """K decode steps of n_streams streams. e2e=False: tokens come from a fixed feed, no host sync inside
-        the region. e2e=True: the public call per step, next tokens read back from the device every step."""
+    def decode_regions(eng, n_streams: int, e2e: bool, min_s: float):
+        """Repeats of exactly K timed decode steps of n_streams streams, until min_s seconds have been timed. e2e=False:
+        tokens come from a fixed feed, nothing crosses to the host inside the region. e2e=True: the public call per step
+        with that step's input tokens copied from pinned host memory and the picked tokens read back to the host every
+        step. Returns (median ms per region, launches per region, h2d bytes, d2h bytes, regions, tokens of the last region)."""
         pos = [eng.slot_len[s] for s in range(n_streams)]
         cur = [feed[s][0] for s in range(n_streams)]
-        d2h = 0
+        state = {"i": 0, "d2h": 0, "h2d": 0, "toks": []}
 
-        def step(i):
-            nonlocal cur, d2h
-            segs = [Segment(s, pos[s] + i, [cur[s] if e2e else feed[s][i]], "last") for s in range(n_streams)]
+        def step():
+            i = state["i"]
+            # the public call: token ids go in as host integers; the engine writes the step's rows (tokens, slots,
+            # positions) into a pinned staging ring and copies them to the device (`Executor._upload`, h2d_bytes)
+            toks = list(cur) if e2e else [feed[s][i] for s in range(n_streams)]
+            segs = [Segment(s, pos[s] + i, [toks[s]], "last") for s in range(n_streams)]
             _, picks, _ = eng.forward(segs, commit=True, greedy=True)
             if e2e:
-                ids = picks[0].cpu()               # device -> host read of the step's result
-                d2h = ids.numel() * ids.element_size()
-                cur = ids.tolist()
+                state["h2d"] = eng.ex.h2d_bytes
+                ids = picks[0].cpu()                                             # the step's result: device -> host
+                state["d2h"] = ids.numel() * ids.element_size()
+                for s in range(n_streams):
+                    cur[s] = int(ids[s])
+                state["toks"].append(ids.tolist())
+            state["i"] = i + 1
 
-        for i in range(warm):
-            step(i)
-        barrier()
-        launches0 = eng.ops.launches
-        e0, e1 = torch.cuda.Event(True), torch.cuda.Event(True)
-        e0.record()
-        for i in range(warm, warm + steps):
-            step(i)
-        e1.record()
-        barrier()
-        ms = max_over_ranks(e0.elapsed_time(e1))
-        for s in range(n_streams):
-            pos[s] += warm + steps
-        return ms, eng.ops.launches - launches0, eng.ex.h2d_bytes, d2h
+        for _ in range(W):
+            step()
+        times, launches = [], 0
+        total = 0.0
+        while total < min_s * 1e3 and state["i"] + K + 1 < budget_steps // 2:
+            state["toks"] = []
+            barrier()
+            l0 = eng.ops.launches
+            e0, e1 = torch.cuda.Event(True), torch.cuda.Event(True)
+            e0.record()
+            for _ in range(K):
+                step()
+            e1.record()
+            barrier()
+            ms = max_over_ranks(e0.elapsed_time(e1))
+            launches = eng.ops.launches - l0
+            times.append(ms)
+            total += ms
+        return statistics.median(times), launches, state["h2d"], state["d2h"], len(times), state["toks"]
+
+    def same_on_every_rank(tokens) -> bool:
+        if world == 1:
+            return True
+        t = torch.tensor(tokens, dtype=torch.int64, device=dev).reshape(-1)
+        box = [torch.empty_like(t) for _ in range(world)]
+        dist.all_gather(box, t)
+        return all(torch.equal(box[0], b) for b in box)
+
+    eng = build(args.dtype)
+    timed_prefill(eng, 0, prompts[0][:256])            # warm the prompt kernels
+    prefill_ms = timed_prefill(eng, 0, prompts[0])
+    if not args.no_extras:
+        for s in range(1, n_streams_max):
+            eng.prefill(s, prompts[s])
+    eng.check()
 
     sampler = ClockSampler(local)
     sampler.start()
-    ms1, launches, h2d, _ = decode_run(args.streams, K, W, e2e=False)
+    ms1, launches, _, _, reps, _ = decode_regions(eng, args.streams, False, args.min_timed_s)
     clocks = sampler.stop()
-    ms_e2e, _, h2d_e, d2h_e = decode_run(args.streams, K, W, e2e=True)
-    extras = {}
+    ms_e2e, _, h2d_e, d2h_e, reps_e, toks = decode_regions(eng, args.streams, True, args.min_timed_s)
+    identical = same_on_every_rank(toks)
+    assert identical, "tensor-parallel ranks produced different tokens"
+    extras = {"ranks_produced_identical_tokens": identical}
+
     if not args.no_extras and args.streams == 1:
-        ms4, _, _, _ = decode_run(4, K, W, e2e=False)
+        ms4, _, _, _, _, _ = decode_regions(eng, 4, False, args.min_timed_s / 2)
+        ms4e, _, _, _, _, toks4 = decode_regions(eng, 4, True, args.min_timed_s / 2)
+        assert same_on_every_rank(toks4)
         extras["decode_4streams_tok_s"] = 4 * K / (ms4 / 1e3)
+        extras["decode_4streams_e2e_tok_s"] = 4 * K / (ms4e / 1e3)
         extras["decode_4streams_vs_baseline"] = extras["decode_4streams_tok_s"] / BASELINE_DECODE_4
-    if not args.no_extras and args.streams == 1:
-        # speculative verification: one step scores 1 + 16 drafted rows of one stream without committing them; with k
-        # accepted drafts per step the stream advances k + 1 tokens in this time
+        # speculative verification: one step scores 1 + 16 drafted rows of one stream without committing them
         p0 = eng.slot_len[0]
         rows = feed[0][:17]
 
-        def verify():
-            eng.forward([Segment(0, p0, rows, "all")], commit=False, greedy=True)
-        for _ in range(W):
-            verify()
-        barrier()
-        e0, e1 = torch.cuda.Event(True), torch.cuda.Event(True)
-        e0.record()
-        for _ in range(K):
-            verify()
-        e1.record()
-        barrier()
-        vms = max_over_ranks(e0.elapsed_time(e1)) / K
-        extras["verify_17rows_ms"] = vms
-        extras["spec_tok_s_at_8_accepted"] = 9.0 / (vms / 1e3)
-        # the same step with what follows an acceptance of 8 drafts: the GDN state replayed over the 9 kept rows
+        def timed(fn):
+            for _ in range(W):
+                fn()
+            barrier()
+            e0, e1 = torch.cuda.Event(True), torch.cuda.Event(True)
+            e0.record()
+            for _ in range(K):
+                fn()
+            e1.record()
+            barrier()
+            return max_over_ranks(e0.elapsed_time(e1)) / K
+
+        extras["verify_17rows_ms"] = timed(lambda: eng.forward([Segment(0, p0, rows, "all")], commit=False, greedy=True))
         st0 = eng.ex.state_save(0)
 
         def verify_commit():
             eng.forward([Segment(0, p0, rows, "all")], commit=False, greedy=True)
             eng.commit_verified([9])
             eng.slot_len[0] = p0
-        for _ in range(W):
-            verify_commit()
-        barrier()
-        e0, e1 = torch.cuda.Event(True), torch.cuda.Event(True)
-        e0.record()
-        for _ in range(K):
-            verify_commit()
-        e1.record()
-        barrier()
-        vcms = max_over_ranks(e0.elapsed_time(e1)) / K
+        extras["verify_commit_9kept_ms"] = timed(verify_commit)
         eng.ex.state_restore(0, st0)
-        extras["verify_commit_ms"] = vcms
-        extras["spec_tok_s_at_8_accepted_with_commit"] = 9.0 / (vcms / 1e3)
+        eng.slot_len[0] = p0
+        extras["speculative"] = measure_spec(eng, cfg, dev, world, barrier, max_over_ranks, same_on_every_rank)
     if long_ctx:
-        # long-context prefill: 32K synthetic tokens through 2048-row chunks on one slot
         long_prompt = torch.randint(0, cfg.vocab, (long_ctx,), generator=gen).tolist()
-        ms32 = timed_prefill(3, long_prompt)
+        ms32 = timed_prefill(eng, 3, long_prompt)
         extras["prefill_32k_tok_s"] = long_ctx / (ms32 / 1e3)
         extras["prefill_32k_vs_baseline"] = extras["prefill_32k_tok_s"] / BASELINE_PREFILL_32K
     extras["prefill_tok_s"] = args.ctx / (prefill_ms / 1e3)
     extras["prefill_ctx"] = args.ctx
     extras["prefill_vs_baseline"] = extras["prefill_tok_s"] / BASELINE_PREFILL_2K
     eng.check()
+    if tp is not None:
+        tp.check()
+
+    if not args.no_extras and args.streams == 1:
+        # decode from the other weight format (bf16 <-> NVFP4 weights with 16-bit activations), same measurement
+        other = "nvfp4-a16" if args.dtype == "bf16" else "bf16"
+        del eng
+        torch.cuda.empty_cache()
+        eng2 = build(other)
+        eng2.prefill(0, prompts[0])
+        ms_o, _, _, _, _, _ = decode_regions(eng2, 1, False, args.min_timed_s / 2)
+        ms_oe, _, _, _, _, _ = decode_regions(eng2, 1, True, args.min_timed_s / 2)
+        extras[f"decode_{other.replace('-', '_')}_tok_s"] = K / (ms_o / 1e3)
+        extras[f"decode_{other.replace('-', '_')}_e2e_tok_s"] = K / (ms_oe / 1e3)
+        eng2.check()
 
     value = args.streams * K / (ms1 / 1e3)
     base = BASELINE_DECODE_1 if args.streams == 1 else BASELINE_DECODE_4
@@ -258,11 +306,12 @@ def main():
         "data": "synthetic uniform-random prompts, random-init weights N(0,0.02)",
         "config": {"model": cfg.name + (f"-{args.layers}layers-DEBUG" if args.layers else ""),
                    "global_batch": args.streams, "seq_len": args.ctx,
-                   "parallelism": f"tp{world}", "params": cfg.param_count(),
+                   "parallelism": f"tp{world}", "params": cfg.param_count(), "repeats": reps,
+                   "timing": "median over `repeats` regions of exactly `steps` steps each (>= 2 s timed in all)",
                    "l2": "inputs larger than L2: every step streams all weights (>40 GB)"},
         "clocks": clocks,
         "e2e": {"value": args.streams * K / (ms_e2e / 1e3), "unit": "tok/s", "h2d_bytes_per_step": h2d_e,
-                "d2h_bytes_per_step": d2h_e},
+                "d2h_bytes_per_step": d2h_e, "repeats": reps_e},
         "gpu_launches": launches,
         "extras": extras,
     }
@@ -271,6 +320,86 @@ def main():
     if world > 1:
         dist.destroy_process_group()
     return 0
+
+
+def measure_spec(eng, cfg, dev, world, barrier, max_over_ranks, same_on_every_rank):
+    """Speculative decoding through the scheduler on slot-sized copies of the engine's state: accepted tokens per step
+    and tok/s. Every run must reproduce the plain greedy run token for token."""
+    import torch
+
+    from ferrite_b200.engine.sampler import Sampling
+    from ferrite_b200.engine.scheduler import SchedOptions, Scheduler, generate
+    from ferrite_b200.models.drafter import BlockDrafter, OracleDrafter, drafter_config_for
+
+    n_new, plen = 160, 1024
+    g = torch.Generator().manual_seed(77)
+    sub = torch.randint(0, cfg.vocab, (256,), generator=g)
+
+    def repeated_spans(n):                       # a 256-token vocabulary subset with repeated 8..32-token spans
+        spans = [sub[torch.randint(0, 256, (int(torch.randint(8, 33, (1,), generator=g)),), generator=g)].tolist() for _ in range(12)]
+        out = []
+        while len(out) < n:
+            out += spans[int(torch.randint(0, len(spans), (1,), generator=g))]
+        return out[:n]
+
+    uniform = lambda n: torch.randint(0, cfg.vocab, (n,), generator=g).tolist()
+    span2k = uniform(2048)
+    prompts = {"repeated_spans_1k": repeated_spans(plen), "edit_2k_span": span2k + uniform(16), "uniform_random_1k": uniform(plen)}
+
+    def opts(**kw):
+        # every rank runs its own scheduler in lockstep: nothing in it may depend on the wall clock
+        return SchedOptions(arrival_ms=0, decode_share=0.0, **kw)
+
+    def run(sched, ps, n):
+        for s in range(len(ps)):
+            eng.reset_slot(s)
+            if sched.drafter is not None:
+                sched.drafter.reset(s)
+        barrier()
+        s0 = sched.stats["steps"]
+        e0, e1 = torch.cuda.Event(True), torch.cuda.Event(True)
+        e0.record()
+        outs = generate(sched, ps, Sampling(max_tokens=n))
+        e1.record()
+        barrier()
+        return outs, max_over_ranks(e0.elapsed_time(e1)), sched.stats["steps"] - s0
+
+    res = {"new_tokens": n_new, "note": "tok/s = new tokens / (time of the run - time of the same run with 1 new token)"}
+    cost = None
+    try:
+        cost = BlockDrafter(drafter_config_for(cfg), target_hidden=cfg.hidden, n_taps=len(cfg.tap_layers), n_slots=eng.ecfg.n_slots,
+                            max_ctx=4096, device=str(dev), block=16)
+    except Exception as e:                       # noqa: BLE001  (e.g. not enough memory next to the target)
+        res["drafter_cost_model"] = f"unavailable: {e!r}"[:120]
+    for name, prompt in prompts.items():
+        for streams in (1, 4):
+            ps = [prompt] * streams if streams == 1 else [prompt[i:] + prompt[:i] for i in range(streams)]
+            plain = Scheduler(eng, opts(spec=0))
+            _, ms_pre, steps_pre = run(plain, ps, 1)
+            truth, ms_plain, _ = run(plain, ps, n_new)
+            entry = {"plain_tok_s": streams * n_new / max(1e-6, (ms_plain - ms_pre) / 1e3)}
+            # the context-copy proposer alone (no draft model)
+            sched = Scheduler(eng, opts(spec=15, copy_rows=True))
+            outs, ms, steps = run(sched, ps, n_new)
+            dsteps = max(1, steps - steps_pre + 1)              # decode / verify steps of the run
+            entry["copy_rows"] = {"tok_s": streams * n_new / max(1e-6, (ms - ms_pre) / 1e3),
+                                  "accepted_per_step_per_stream": sched.stats["accepted"] / dsteps / streams,
+                                  "drafted": sched.stats["drafted"], "accepted": sched.stats["accepted"],
+                                  "equals_plain": outs == truth}
+            if name == "repeated_spans_1k":
+                for p in (0.0, 0.6, 0.9):
+                    od = OracleDrafter(p, cfg.vocab, seed=5, cost_model=cost)
+                    sched = Scheduler(eng, opts(spec=15, copy_rows=False), drafter=od)
+                    for s in range(streams):
+                        od.set_truth(s, len(ps[s]), truth[s])
+                    outs, ms, steps = run(sched, ps, n_new)
+                    dsteps = max(1, steps - steps_pre + 1)
+                    entry[f"oracle_p{p}"] = {"tok_s": streams * n_new / max(1e-6, (ms - ms_pre) / 1e3),
+                                             "accepted_per_step_per_stream": sched.stats["accepted"] / dsteps / streams,
+                                             "equals_plain": outs == truth and same_on_every_rank([t for o in outs for t in o])}
+            res[f"{name}_{streams}stream"] = entry
+    res["vs_baseline_spec_1stream_p0.9"] = res["repeated_spans_1k_1stream"].get("oracle_p0.9", {}).get("tok_s", 0.0) / BASELINE_SPEC_1
+    return res
 
 
 if __name__ == "__main__":

@@ -99,3 +99,46 @@ class BlockDrafter(Drafter):
             return
         self.eng.slot_len[slot] = min(self.eng.slot_len[slot], blob["len"])
         self.last_feat[slot] = blob["feat"]
+
+
+class OracleDrafter(Drafter):
+    """A drafter whose acceptance rate is a dial: it proposes the tokens the target is known to produce (`truth`, recorded
+    from a plain greedy run of the same prompt) and corrupts every proposed token with probability 1 - p (the first
+    corrupted token ends what the verify step accepts). For benchmarks and tests of the speculative path: the cost of
+    the step (verify rows, commit, replay) is real, the acceptance rate is chosen, and the output must equal the plain
+    run's. With `cost_model` set (a `BlockDrafter`), its draft pass runs every step too, so the time of a real draft
+    model is charged while the tokens come from the oracle."""
+
+    def __init__(self, p: float, vocab: int, seed: int = 0, cost_model: Optional[Drafter] = None):
+        self.p = float(p)
+        self.vocab = vocab
+        self.truth = {}                              # slot -> (position of truth[0], tokens)
+        self.rng = torch.Generator().manual_seed(seed)
+        self.cost_model = cost_model
+
+    def set_truth(self, slot: int, pos0: int, tokens: Sequence[int]) -> None:
+        self.truth[slot] = (int(pos0), [int(t) for t in tokens])
+
+    def draft(self, slot: int, last_token: int, pos: int, taps, n: int) -> List[int]:
+        if self.cost_model is not None:
+            self.cost_model.draft(slot, last_token, pos, taps, n)
+        if slot not in self.truth or n <= 0:
+            return []
+        pos0, toks = self.truth[slot]
+        i = pos + 1 - pos0                           # the row at `pos` holds last_token; the draft starts one later
+        out = [int(t) for t in toks[max(i, 0):max(i, 0) + n]]
+        if not out:
+            return []
+        keep = torch.rand(len(out), generator=self.rng) < self.p
+        for j in range(len(out)):
+            if not bool(keep[j]):
+                out[j] = (out[j] + 1 + int(torch.randint(0, self.vocab - 1, (1,), generator=self.rng))) % self.vocab
+        return out
+
+    def absorb(self, slot, tokens, pos0, taps):
+        if self.cost_model is not None:
+            self.cost_model.absorb(slot, tokens, pos0, taps)
+
+    def reset(self, slot):
+        if self.cost_model is not None:
+            self.cost_model.reset(slot)
