@@ -56,6 +56,16 @@ int fb_gemm_nvfp4_fused(void* Y, const void* X, long ldx, const void* norm_w, fl
                         int split_k, int out_f32, float* workspace, int* counters, int* status, int sm_count,
                         cudaStream_t s);
 
+// ---- gemv_nvfp4_tc.cu: few-row NVFP4 linear on the block-scaled tensor cores, activations as residual NVFP4 terms ----
+long fb_gemv_nvfp4_tc_workspace_bytes(int M, int N, int K, int dual, int terms, int sm_count, int ctas_per_sm);
+int fb_gemv_nvfp4_tc_terms(int M, int N, int K, int dual, int terms);
+void fb_gemv_nvfp4_tc_trace_set(void* buf);
+int fb_gemv_nvfp4_tc(void* Y, const void* X, long ldx, const void* norm_w, float eps, const void* Wq, const void* w_sf,
+                     float w_scale, const float* row_alpha, const void* res, int M, int N, int K, long ldy, int mode,
+                     int terms, int out_f32, float* workspace, int* counters, int* status, int sm_count,
+                     int ctas_per_sm, const void* next_Wq, const void* next_sf, int next_N, int next_K, int next_mode,
+                     long prefetch_bytes, cudaStream_t s);
+
 // ---- moe.cu: router, grouped-expert GEMVs over (token, expert) pairs, fixed-order combine ----
 int fb_moe_route(int* ids, float* wts, const float* logits, const float* bias, int rows, int n_exp, int top_k, int mode,
                  int n_groups, int topk_groups, float scale, cudaStream_t s);

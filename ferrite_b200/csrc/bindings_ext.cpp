@@ -131,6 +131,44 @@ void gemm_nvfp4_fused(Tensor Y, Tensor X, c10::optional<Tensor> norm_w, double e
         "gemm_nvfp4_fused");
 }
 
+int64_t gemv_nvfp4_tc_workspace_bytes(int64_t M, int64_t N, int64_t K, bool dual, int64_t terms, int64_t ctas_per_sm) {
+  return fb_gemv_nvfp4_tc_workspace_bytes((int)M, (int)N, (int)K, dual ? 1 : 0, (int)terms,
+                                          at::cuda::getCurrentDeviceProperties()->multiProcessorCount, (int)ctas_per_sm);
+}
+
+int64_t gemv_nvfp4_tc_terms(int64_t M, int64_t N, int64_t K, bool dual, int64_t terms) {
+  return fb_gemv_nvfp4_tc_terms((int)M, (int)N, (int)K, dual ? 1 : 0, (int)terms);
+}
+
+void gemv_nvfp4_tc_trace_set(c10::optional<Tensor> buf) {
+  if (buf.has_value()) TORCH_CHECK(buf->scalar_type() == torch::kInt64 && buf->numel() >= 8 * 1024 * 8, "trace: int64[8 * 1024 * 8]");
+  fb_gemv_nvfp4_tc_trace_set(buf.has_value() ? buf->data_ptr() : nullptr);
+}
+
+void gemv_nvfp4_tc(Tensor Y, Tensor X, c10::optional<Tensor> norm_w, double eps, Tensor wq, Tensor w_sf, double w_scale,
+                   c10::optional<Tensor> row_alpha, c10::optional<Tensor> res, int64_t mode, int64_t terms,
+                   c10::optional<Tensor> workspace, c10::optional<Tensor> counters, c10::optional<Tensor> status,
+                   int64_t ctas_per_sm, c10::optional<Tensor> next_wq, c10::optional<Tensor> next_sf, int64_t next_mode,
+                   int64_t prefetch_bytes) {
+  int M = (int)X.size(0), K = (int)X.size(1);
+  int N = (int)(mode == 1 ? wq.size(0) / 2 : wq.size(0));
+  TORCH_CHECK(wq.size(1) * 2 == K, "gemv_nvfp4_tc: K mismatch");
+  const bool pf = next_wq.has_value() && next_sf.has_value() && next_wq->is_contiguous();
+  int next_N = pf ? (int)(next_mode == 1 ? next_wq->size(0) / 2 : next_wq->size(0)) : 0;
+  int next_K = pf ? (int)next_wq->size(1) * 2 : 0;
+  TORCH_CHECK(X.stride(1) == 1 && Y.stride(1) == 1 && wq.is_contiguous(), "gemv_nvfp4_tc: layout");
+  check(fb_gemv_nvfp4_tc(Y.data_ptr(), X.data_ptr(), (long)X.stride(0), cptr(norm_w), (float)eps, wq.data_ptr(),
+                         w_sf.data_ptr(), (float)w_scale, (const float*)cptr(row_alpha), cptr(res), M, N, K,
+                         (long)Y.stride(0), (int)mode, (int)terms, Y.scalar_type() == torch::kFloat32 ? 1 : 0,
+                         workspace.has_value() ? (float*)workspace->data_ptr() : nullptr,
+                         counters.has_value() ? (int*)counters->data_ptr() : nullptr,
+                         status.has_value() ? (int*)status->data_ptr() : nullptr,
+                         at::cuda::getCurrentDeviceProperties()->multiProcessorCount, (int)ctas_per_sm,
+                         pf ? next_wq->data_ptr() : nullptr, pf ? next_sf->data_ptr() : nullptr, next_N, next_K,
+                         (int)next_mode, (long)prefetch_bytes, cur_stream()),
+        "gemv_nvfp4_tc");
+}
+
 void moe_route(Tensor ids, Tensor wts, Tensor logits, c10::optional<Tensor> bias, int64_t mode, int64_t n_groups,
                int64_t topk_groups, double scale) {
   check(fb_moe_route(ids.data_ptr<int>(), wts.data_ptr<float>(), logits.data_ptr<float>(),
@@ -406,5 +444,9 @@ void register_ext(pybind11::module_& m) {
   m.def("gemm_nvfp4_workspace_bytes", &gemm_nvfp4_workspace_bytes);
   m.def("gemm_nvfp4", &gemm_nvfp4);
   m.def("gemm_nvfp4_fused", &gemm_nvfp4_fused);
+  m.def("gemv_nvfp4_tc", &gemv_nvfp4_tc);
+  m.def("gemv_nvfp4_tc_trace_set", &gemv_nvfp4_tc_trace_set);
+  m.def("gemv_nvfp4_tc_workspace_bytes", &gemv_nvfp4_tc_workspace_bytes);
+  m.def("gemv_nvfp4_tc_terms", &gemv_nvfp4_tc_terms);
   m.def("gemv_nvfp4_allreduce", &gemv_nvfp4_allreduce);
 }

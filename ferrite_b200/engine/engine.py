@@ -111,6 +111,18 @@ class Engine:
         self.tp = tp
         if tp is not None and tp.world > 1 and self.ecfg.seq_parallel and tp.sp_max is None:
             tp.setup_big(self.ecfg.max_step_rows, cfg.hidden)
+        if on_gpu and ops.fp4_act and world == 1:
+            # execution order of the NVFP4 linears, so that each few-row call can prefetch the next one's weights
+            from ..ops.qweight import QWeight
+            order = []
+            names = [f"l{i}.{n}" for i in range(cfg.n_layers) for n in ("in_proj", "out_proj", "gate_up", "down")]
+            for k in names + ["lm_head"]:
+                v = weights.get(k)
+                if isinstance(v, QWeight) and v.kind == "nvfp4" and v.mma_scales is not None:
+                    v.pair = k.endswith("gate_up")
+                    order.append(v)
+            for a, b in zip(order, order[1:] + order[:1]):
+                a.next = b
         self.ex = Executor(self.cfg, weights, self.ecfg, ops, tp=tp, full_cfg=cfg)
         if cfg.n_experts > 0 and ((tp is not None and tp.world > 1 and tp.sp_max is not None) or (world == 1 and on_gpu)):
             # prompt-sized MoE steps go through plan / dispatch / grouped GEMM / combine; with one rank the dispatch

@@ -770,6 +770,7 @@ def generate(sched: Scheduler, prompts: Sequence[Sequence[int]], sampling: Optio
     """Synchronous helper: run prompts to completion through the scheduler (single-threaded stepping)."""
     outs: List[List[int]] = [[] for _ in prompts]
     done = [False] * len(prompts)
+    errors: List[str] = []
 
     def sink(i):
         def f(ev: Event):
@@ -777,6 +778,8 @@ def generate(sched: Scheduler, prompts: Sequence[Sequence[int]], sampling: Optio
                 outs[i].extend(ev.tokens)
             else:
                 done[i] = True
+                if ev.kind == "error":
+                    errors.append(f"prompt {i}: {ev.message}")
         return f
 
     for i, p in enumerate(prompts):
@@ -788,4 +791,6 @@ def generate(sched: Scheduler, prompts: Sequence[Sequence[int]], sampling: Optio
         sched.run_once()
         guard += 1
         assert guard < 100000, "scheduler made no progress"
+    if errors:                                       # a helper for tests and benchmarks: a failed request is a failure
+        raise RuntimeError("; ".join(errors))
     return outs

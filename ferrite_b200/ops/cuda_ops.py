@@ -45,6 +45,9 @@ class CudaOps:
         self._expert_scratch = {}
         self._kv_scratch = None
         self.fp4_act = False                # NVFP4 weights: quantise activations too and use the tcgen05 GEMM
+        self.fp4_terms = 3                  # few-row NVFP4 steps: NVFP4 renderings per activation row (0 = older fused kernel)
+        self.fp4_tc_ctas = 1                # ... and CTAs per SM of that kernel
+        self.fp4_prefetch_mb = 48           # ... and how much of the next weight (`QWeight.next`) it asks L2 for as it drains
         self._sf_pool = {}
         self._scratch = {}
 
@@ -137,6 +140,9 @@ class CudaOps:
         if isinstance(w, QWeight):
             M = x.shape[0]
             N = w.rows // 2 if swiglu else w.rows
+            if (self.fp4_act and self.fp4_terms > 0 and M <= 8 and w.mma_scales is not None and w.cols % 256 == 0
+                    and (not swiglu or N % 128 == 0) and out is None):
+                return self._linear_w4_tc(x, w, norm_w, eps, res, swiglu, M, N, out_f32)
             if (self.fp4_act and w.row_alpha is None and w.mma_scales is not None and w.cols % 256 == 0 and (not out_f32 or M <= 8)
                     and (not swiglu or N % 128 == 0) and (M <= 64 or N % 8 == 0)):
                 return self._linear_w4a4(x, w, norm_w, eps, res, swiglu, M, N, out_f32)
@@ -261,6 +267,23 @@ class CudaOps:
         self.launches += 1
         self.C.quant_nvfp4(codes, sf, rs, x, norm_w, eps)
         return codes, sf, rs
+
+    def _linear_w4_tc(self, x, w, norm_w, eps, res, swiglu, M, N, out_f32=False):
+        """Few rows: weights stay packed on the block-scaled tensor cores, every activation row goes in as up to
+        `fp4_terms` NVFP4 renderings (value, residual, residual of the residual) that the epilogue sums."""
+        K = w.cols
+        nb = int(self.C.gemv_nvfp4_tc_workspace_bytes(M, N, K, swiglu, self.fp4_terms, self.fp4_tc_ctas))
+        y = torch.empty(M, N, dtype=torch.float32 if out_f32 else self.dtype, device=self.device)
+        self.launches += 1
+        nxt = getattr(w, "next", None) if self.fp4_prefetch_mb > 0 else None
+        if nxt is not None and (nxt.mma_scales is None or nxt.cols % 256):
+            nxt = None
+        self.C.gemv_nvfp4_tc(y, x, norm_w, eps, w.packed, w.mma_scales, w.global_scale, w.row_alpha, res,
+                             1 if swiglu else 0, self.fp4_terms, self._workspace(max(nb, 16)), self._counters,
+                             self.status_word, self.fp4_tc_ctas, None if nxt is None else nxt.packed,
+                             None if nxt is None else nxt.mma_scales, 1 if (nxt is not None and nxt.pair) else 0,
+                             self.fp4_prefetch_mb << 20)
+        return y
 
     def _linear_w4a4(self, x, w, norm_w, eps, res, swiglu, M, N, out_f32=False):
         split = self._split_k(M, N, w.cols // 4) if M <= 64 else 1

@@ -7,7 +7,7 @@ decode rows, a second copy of the weights for prompt rows (`Linear::forward`, `c
 """
 from __future__ import annotations
 
-from dataclasses import dataclass
+from dataclasses import dataclass, field
 from typing import Optional
 
 import torch
@@ -29,6 +29,10 @@ class QWeight:
     fp8_scales: Optional[torch.Tensor] = None    # "fp8b": fp32 [ceil(rows/128), ceil(cols/128)]; "fp8": fp32 [rows]
     row_alpha: Optional[torch.Tensor] = None     # "nvfp4": fp32 [rows] tensor scale per output row (fused checkpoint parts
                                                  # bring their own `weight_scale_2`); global_scale is 1 when set
+    pair: bool = False                           # rows are gate | up halves consumed with the SwiGLU epilogue
+    # the NVFP4 weight the step multiplies next (set by the engine, in execution order, the last one pointing at the
+    # first): the few-row tensor-core kernel asks L2 for its head while it drains
+    next: Optional["QWeight"] = field(default=None, repr=False, compare=False)
 
     @property
     def shape(self):

@@ -29,8 +29,8 @@ def peaks():
 
 
 class Timer:
-    def __init__(self, dev, warmup=3, iters=20, flush=True):
-        self.dev, self.warmup, self.iters, self.flush = dev, max(3, warmup), iters, flush
+    def __init__(self, dev, warmup=3, iters=20, flush=True, graph=False, trace=False, hot=False):
+        self.dev, self.warmup, self.iters, self.flush, self.graph, self.trace, self.hot = dev, max(3, warmup), iters, flush, graph, trace, hot
         # flush = write a buffer larger than L2, then read another one so the cache is left full of CLEAN lines
         # (dirty lines would be written back during the timed kernel and charged to it)
         self.junk = torch.empty(256 << 20, dtype=torch.uint8, device=dev) if flush else None
@@ -81,7 +81,58 @@ def bench_linear(ops, t, m, n, k, swiglu=False, norm=False, res=False, label=Non
         wbytes = rows * k // 2 + rows * k // 16
     nw = rnd(k, scale=0.1) if norm else None
     r = rnd(m, n) if res else None
-    ms = t.run(lambda: ops.linear(x, w, norm_w=nw, res=r, swiglu=swiglu))
+    if t.graph:
+        # device time inside a stream of such calls, as in a decode step: R calls over R copies of the weight (together
+        # larger than L2, so every call streams from HBM) captured in one CUDA graph; time of a replay / R. A lone
+        # call timed from an idle GPU also measures the host's launch path, which is longer than these kernels.
+        import copy
+        reps = max(2, min(24, -(-(600 << 20) // wbytes)))
+        ws = [w] * reps if t.hot else [w] + [copy.deepcopy(w) if fp4 else w.clone() for _ in range(reps - 1)]
+        if fp4:
+            for i, wi in enumerate(ws):                      # each call prefetches the weight of the one after it
+                wi.pair, wi.next = swiglu, ws[(i + 1) % reps]
+
+        def chain():
+            for wi in ws:
+                ops.linear(x, wi, norm_w=nw, res=r, swiglu=swiglu)
+        chain()
+        trace = None
+        if t.trace and fp4 and ops.fp4_act:
+            trace = torch.zeros(8 * 1024 * 8, dtype=torch.int64, device=x.device)
+            ops.C.gemv_nvfp4_tc_trace_set(trace)
+            reps = 8
+            ws = ws[:8] if len(ws) >= 8 else (ws * 8)[:8]
+            if fp4 and not t.hot:
+                for i, wi in enumerate(ws):
+                    wi.next = ws[(i + 1) % reps]
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            chain()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                chain()
+        torch.cuda.current_stream().wait_stream(side)
+        flush, t.flush = t.flush, False
+        ms = t.run(g.replay) / reps
+        t.flush = flush
+        if trace is not None:
+            # the capture stamped calls 0..7 into regions (0..7 + eager calls before it) % 8: the last two calls of the
+            # graph are the regions with the two latest end times
+            ops.C.gemv_nvfp4_tc_trace_set(None)
+            tr = trace.view(8, 1024, 8).cpu()
+            used = tr[:, :, 0] > 0
+            ends = [int(tr[c, :, 7][used[c]].max()) if used[c].any() else 0 for c in range(8)]
+            order = sorted(range(8), key=lambda c: ends[c])
+            last, prev = order[-1], order[-2]
+            names = ["entry", "set-up done", "dependency met", "row statistics", "quantised", "first stage landed",
+                     "last MMA issued", "epilogue done"]
+            rel = tr[last][used[last]].double() - ends[prev]
+            print(json.dumps({"trace_us_after_previous_kernel_end": {
+                n: {"median": round(float(rel[:, i].median()) / 1e3, 2), "max": round(float(rel[:, i].max()) / 1e3, 2)}
+                for i, n in enumerate(names)}, "ctas": int(used[last].sum())}), flush=True)
+    else:
+        ms = t.run(lambda: ops.linear(x, w, norm_w=nw, res=r, swiglu=swiglu))
     nbytes = wbytes + m * k * 2 + m * n * 2 * (2 if res else 1)
     return report(label or f"linear m{m} n{n} k{k}{' swiglu' if swiglu else ''}", ms, nbytes, 2.0 * m * rows * k,
                   {"m": m, "n": n, "k": k})
@@ -99,10 +150,18 @@ def main():
     ap.add_argument("--norm", action="store_true")
     ap.add_argument("--res", action="store_true")
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--hot", action="store_true", help="with --graph: every call uses the same weight (L2-resident when it fits)")
+    ap.add_argument("--trace", action="store_true",
+                    help="with --graph --fp4: print where the few-row tensor-core kernel's time goes (%%globaltimer stamps)")
+    ap.add_argument("--graph", action="store_true",
+                    help="gemv/gemm: time the call inside a CUDA graph of back-to-back calls over weight copies larger than L2")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--no-flush", action="store_true")
     ap.add_argument("--fp4", action="store_true", help="NVFP4 weights and activations (block-scaled tcgen05 GEMM)")
     ap.add_argument("--fp8b", action="store_true", help="gemm: block-scaled e4m3 (1x128 activations, 128x128 weights)")
+    ap.add_argument("--terms", type=int, default=3, help="with --fp4, few rows: NVFP4 renderings per activation row (0 = older fused kernel)")
+    ap.add_argument("--prefetch", type=int, default=48, help="with --fp4 --graph, few rows: MB of the next call's weight asked into L2")
+    ap.add_argument("--ctas", type=int, default=1, help="with --fp4, few rows: CTAs per SM of the tensor-core kernel")
     ap.add_argument("--a16", action="store_true", help="with --fp4: keep 16-bit activations (W4A16 GEMV)")
     a = ap.parse_args()
     from ..ops.cuda_ops import CudaOps
@@ -110,7 +169,8 @@ def main():
     torch.cuda.set_device(dev)
     ops = CudaOps(dev)
     ops.fp4_act = a.fp4 and not a.a16
-    t = Timer(dev, a.warmup, a.iters, flush=not a.no_flush)
+    ops.fp4_terms, ops.fp4_tc_ctas, ops.fp4_prefetch_mb = a.terms, a.ctas, a.prefetch
+    t = Timer(dev, a.warmup, a.iters, flush=not a.no_flush, graph=a.graph, trace=a.trace, hot=a.hot)
     if a.what == "gemm" and a.fp8b:
         x = rnd(a.m, a.k)
         wq, ws = ops.quantize_weight_fp8_block(rnd(a.n, a.k, scale=0.05))

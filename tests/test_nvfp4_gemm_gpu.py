@@ -13,6 +13,15 @@ def ops(ext):
     from ferrite_b200.ops.cuda_ops import CudaOps
     o = CudaOps(DEV)
     o.fp4_act = True
+    o.fp4_terms = 0          # the tests below pin the single-rendering (W4A4) kernels; the few-row kernel has its own
+    return o
+
+
+@pytest.fixture(scope="module")
+def ops_tc(ext):
+    from ferrite_b200.ops.cuda_ops import CudaOps
+    o = CudaOps(DEV)
+    o.fp4_act = True
     return o
 
 
@@ -108,6 +117,79 @@ def test_gemm_nvfp4_fused_quantiser(ops, M, N, K, swiglu):
     # replays give identical bits (split-K partials are summed in split order)
     again = ops.linear(x, q, norm_w=nw, eps=1e-6, res=res, swiglu=swiglu)
     assert torch.equal(got, again)
+    assert ops.status() == 0
+
+
+def _normed(x, nw, eps=1e-6):
+    xf = x.float()
+    y = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * (1 + nw.float())
+    return y.to(torch.bfloat16).float()
+
+
+@pytest.mark.parametrize("M", [1, 2, 4, 8])
+@pytest.mark.parametrize("N,K,swiglu,norm", [(5120, 5120, False, True), (2048, 17408, False, False), (1536, 1024, True, True),
+                                             (1000, 768, False, False), (17408, 5120, True, True)])
+def test_few_row_tensor_core_kernel(ops_tc, M, N, K, swiglu, norm):
+    """Weights multiplied packed on the block-scaled tensor cores; activations as residual NVFP4 renderings. Against
+    fp32 math on the dequantised weights and the un-quantised (normalised) activations: with three renderings the
+    activation error is at the level of the bf16 output rounding."""
+    from ferrite_b200.ops.qweight import quantize_weight
+    ops = ops_tc
+    x = rnd(M, K, seed=1)
+    x[:, ::7] *= 8.0                                           # outliers, as real hidden states have
+    nw = rnd(K, scale=0.1, seed=4) if norm else None
+    w = rnd(2 * N if swiglu else N, K, scale=0.05, seed=2)
+    q = quantize_weight(w)
+    res = None if swiglu else rnd(M, N, seed=3)
+    xin = _normed(x, nw) if norm else x.float()
+    y = xin @ q.dense.float().t()
+    want = torch.nn.functional.silu(y[:, :N]) * y[:, N:] if swiglu else y
+    errs = {}
+    for terms in (3, 2, 1):
+        ops.fp4_terms = terms
+        eff = int(ops.C.gemv_nvfp4_tc_terms(M, N, K, swiglu, terms))
+        assert eff == min(terms, 8 // M)
+        got = ops.linear(x, q, norm_w=nw, eps=1e-6, swiglu=swiglu, out_f32=not swiglu)
+        errs[eff] = (got.float() - want).abs().max().item() / want.abs().max().item()
+    ops.fp4_terms = 3
+    assert errs[1] < 0.3, errs
+    if 2 in errs:
+        assert errs[2] < 4e-2 and errs[2] < errs[1], errs
+    if 3 in errs:
+        assert errs[3] < 8e-3 and errs[3] < errs[2], errs
+    got = ops.linear(x, q, norm_w=nw, eps=1e-6, res=res, swiglu=swiglu)
+    assert got.dtype == torch.bfloat16
+    ref = want if swiglu else want + res.float()
+    err = (got.float() - ref).abs().max().item() / ref.abs().max().item()
+    tol = {1: 0.3, 2: 4e-2, 3: 1.5e-2}[min(3, 8 // M)]
+    assert err < tol, err
+    # replays give identical bits (partials are summed in CTA order), also with two CTAs per SM
+    again = ops.linear(x, q, norm_w=nw, eps=1e-6, res=res, swiglu=swiglu)
+    assert torch.equal(got, again)
+    ops.fp4_tc_ctas = 2
+    two = ops.linear(x, q, norm_w=nw, eps=1e-6, res=res, swiglu=swiglu)
+    ops.fp4_tc_ctas = 1
+    err = (two.float() - ref).abs().max().item() / ref.abs().max().item()
+    assert err < tol, err
+    assert ops.status() == 0
+    assert int(ops._counters.abs().sum()) == 0                 # every tile's counter went back to zero
+
+
+def test_few_row_kernel_row_scales(ops_tc):
+    """Fused projections of a checkpoint carry one tensor scale per part: per-row alpha in the epilogue."""
+    from ferrite_b200.ops.qweight import quantize_weight
+    ops = ops_tc
+    N, K = 2048, 1024
+    x = rnd(2, K, seed=1)
+    q = quantize_weight(rnd(N, K, scale=0.05, seed=2))
+    alpha = torch.full((N,), float(q.global_scale), device=DEV)
+    alpha[N // 2:] *= 3.0
+    base = ops.linear(x, q, out_f32=True)
+    q.row_alpha = alpha
+    got = ops.linear(x, q, out_f32=True)
+    want = base.clone()
+    want[:, N // 2:] *= 3.0
+    assert torch.allclose(got, want, rtol=1e-5, atol=1e-6)
     assert ops.status() == 0
 
 
