@@ -97,6 +97,8 @@ def main():
     ap.add_argument("--streams", type=int, default=1)
     ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers (the JSON line says so)")
     ap.add_argument("--dtype", default="bf16")
+    ap.add_argument("--fused-layers", default="auto", choices=["auto", "on", "off"],
+                    help="plain decode rows: one persistent kernel per layer (auto = when tensor parallel)")
     ap.add_argument("--no-extras", action="store_true", help="only the headline decode measurement and the 2K prefill")
     ap.add_argument("--min-timed-s", type=float, default=MIN_TIMED_S)
     args = ap.parse_args()
@@ -151,7 +153,7 @@ def main():
 
     def build(dtype):
         ecfg = EngineConfig(n_slots=n_streams_max, max_ctx=max(args.ctx + budget_steps + 64, long_ctx + 64), prefill_chunk=2048,
-                            weight_dtype=dtype)
+                            weight_dtype=dtype, fused_layers={"auto": None, "on": True, "off": False}[args.fused_layers])
         return Engine(cfg, None, ecfg, device=str(dev), seed=0, tp=tp)
 
     gen = torch.Generator().manual_seed(1234)

@@ -252,6 +252,7 @@ class EngineConfig:
     decode_rows_max: int = 64          # rows routed to the small-M (GEMV) kernels
     attn_splits: int = 0               # 0 = pick from context length
     use_graphs: bool = True
+    fused_layers: Optional[bool] = None   # plain decode rows: one persistent kernel per layer (None = when tensor parallel)
     kv_dtype: str = "bf16"             # "bf16" | "fp8": e4m3 KV cache with one scale per (token, kv head)
     seq_parallel: bool = True          # TP prompts: row-sharded residual stream, all-gather/reduce-scatter fused into the GEMMs
     graph_max: int = 128               # LRU size of the CUDA-graph cache (reference GRAPH_MAX)

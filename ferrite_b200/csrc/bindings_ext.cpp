@@ -52,6 +52,41 @@ void allreduce_oneshot(const Comm& c, Tensor y, Tensor part, c10::optional<Tenso
                              c.spin_limit, c.max_resident, cur_stream()), "allreduce_oneshot");
 }
 
+// start_phase 1: a Gated DeltaNet layer from the hidden rows x_in; 3: the rest of a layer whose mixer output o is given.
+// comm: a Comm, or None on one GPU. Returns nothing; x_out holds the layer's output rows.
+void decode_layer(pybind11::object comm, int64_t start_phase, Tensor x_out, Tensor x_mid, Tensor act, Tensor proj, Tensor o,
+                  Tensor x_in, c10::optional<Tensor> w_in, c10::optional<Tensor> input_norm, Tensor w_out, Tensor post_norm,
+                  Tensor w_gu, Tensor w_down, c10::optional<Tensor> rec_state, c10::optional<Tensor> conv_state,
+                  c10::optional<Tensor> conv_w, c10::optional<Tensor> A_log, c10::optional<Tensor> dt_bias,
+                  c10::optional<Tensor> gnorm_w, c10::optional<Tensor> seg_slot, int64_t nk, int64_t nv, int64_t dk,
+                  double eps, Tensor status, Tensor sync_words) {
+  const int M = (int)x_in.size(0), hidden = (int)x_in.size(1);
+  TORCH_CHECK(x_in.is_contiguous() && x_out.is_contiguous() && x_mid.is_contiguous() && act.is_contiguous() &&
+              o.is_contiguous() && proj.is_contiguous() && w_out.is_contiguous() && w_gu.is_contiguous() &&
+              w_down.is_contiguous(), "decode_layer: contiguous tensors");
+  TORCH_CHECK(w_out.size(0) == hidden && w_out.size(1) == o.size(1) && w_gu.size(1) == hidden &&
+              w_gu.size(0) == 2 * act.size(1) && w_down.size(0) == hidden && w_down.size(1) == act.size(1),
+              "decode_layer: shapes");
+  TORCH_CHECK(sync_words.numel() >= 2 && sync_words.scalar_type() == torch::kInt32, "decode_layer: sync words");
+  if (start_phase == 1)
+    TORCH_CHECK(w_in.has_value() && w_in->is_contiguous() && w_in->size(1) == hidden && proj.size(1) == w_in->size(0) &&
+                rec_state.has_value() && conv_state.has_value() && seg_slot.has_value() && seg_slot->numel() >= M &&
+                o.size(1) == nv * dk, "decode_layer: Gated DeltaNet operands");
+  const Comm* c = comm.is_none() ? nullptr : comm.cast<const Comm*>();
+  check(fb_decode_layer((int)start_phase, M, hidden, x_out.data_ptr(), x_mid.data_ptr(), act.data_ptr(), proj.data_ptr(),
+                        o.data_ptr(), x_in.data_ptr(), cptr(w_in), w_in.has_value() ? (int)w_in->size(0) : 0,
+                        cptr(input_norm), w_out.data_ptr(), (int)w_out.size(1), post_norm.data_ptr(), w_gu.data_ptr(),
+                        (int)act.size(1), w_down.data_ptr(), rec_state.has_value() ? rec_state->data_ptr<float>() : nullptr,
+                        conv_state.has_value() ? conv_state->data_ptr() : nullptr, cptr(conv_w),
+                        A_log.has_value() ? A_log->data_ptr<float>() : nullptr,
+                        dt_bias.has_value() ? dt_bias->data_ptr<float>() : nullptr, cptr(gnorm_w),
+                        seg_slot.has_value() ? seg_slot->data_ptr<int>() : nullptr, (int)nk, (int)nv, (int)dk, (float)eps,
+                        c ? c->peers.data() : nullptr, c ? c->rank : 0, c ? c->world : 1, c ? c->max_ctas : 0,
+                        c ? c->slot_floats : 0, c ? (uint32_t*)c->epochs.data_ptr() : nullptr, status.data_ptr<int>(),
+                        c ? c->spin_limit : 0u, (uint32_t*)sync_words.data_ptr(),
+                        at::cuda::getCurrentDeviceProperties()->multiProcessorCount, cur_stream()), "decode_layer");
+}
+
 void argmax_gather(const Comm& c, Tensor ids, Tensor logits, int64_t vocab_offset, c10::optional<Tensor> vals) {
   check(fb_argmax_gather(ids.data_ptr<int>(), vals.has_value() ? vals->data_ptr<float>() : nullptr,
                          logits.data_ptr<float>(), (long)logits.stride(0), (int)logits.size(0), (int)logits.size(1),
@@ -412,6 +447,7 @@ void register_ext(pybind11::module_& m) {
   m.def("ag_gemm", &ag_gemm);
   pybind11::class_<Comm>(m, "Comm");
   m.def("make_comm", &make_comm);
+  m.def("decode_layer", &decode_layer);
   m.def("comm_workspace_bytes", [](int64_t max_ctas, int64_t slot_floats) {
     return (int64_t)fb_comm_workspace_bytes((int)max_ctas, (long)slot_floats);
   });

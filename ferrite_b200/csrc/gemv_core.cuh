@@ -145,9 +145,16 @@ __device__ __forceinline__ void gemv_row_ptrs(const GemvArgs& a, const __nv_bflo
 // dependent launch those loads overlap its tail and this kernel's own prologue), and each later one right
 // after the previous batch was consumed, across row-group boundaries too. `store(acc, n)` is called by every
 // lane of the warp with the warp-reduced sums of row group n.
-template <int M, int R, bool SWIGLU, class Store>
-__device__ __forceinline__ void gemv_main(const GemvArgs& a, __nv_bfloat16* xs, float* rscale, float* scratch,
-                                          Store store, unsigned long long* wait_stamp = nullptr) {
+// How the main loop learns that its activations are ready. As a kernel of its own: programmatic dependent launch.
+struct GemvPdlWait {
+  __device__ __forceinline__ void before_loads() const { pdl_launch_dependents(); }
+  __device__ __forceinline__ void wait() const { pdl_wait(); }
+};
+
+template <int M, int R, bool SWIGLU, int NWARPS, class Store, class Wait>
+__device__ __forceinline__ void gemv_main_w(const GemvArgs& a, __nv_bfloat16* xs, float* rscale, float* scratch,
+                                            Store store, Wait waiter, unsigned long long* wait_stamp = nullptr) {
+  constexpr int GEMV_WARPS = NWARPS;                   // (shadows the default: row groups stride by this CTA's warps)
   const int warp = threadIdx.x >> 5;
   const int row0 = blockIdx.x * a.rows_per_cta;
   const int row_end = min(a.N, row0 + a.rows_per_cta);
@@ -156,12 +163,12 @@ __device__ __forceinline__ void gemv_main(const GemvArgs& a, __nv_bfloat16* xs, 
   constexpr int BATCH = GEMV_STEP * GEMV_U;
   int n = row0 + warp * RW;
 
-  pdl_launch_dependents();
+  waiter.before_loads();
   uint4 wv[R][GEMV_U];
   const __nv_bfloat16* wrow[R];
   gemv_row_ptrs<R, SWIGLU>(a, wrow, n);
   gemv_load_batch<R>(wv, wrow, 0, a.K);
-  pdl_wait();
+  waiter.wait();
   if (wait_stamp != nullptr && threadIdx.x == 0)       // profiling: when the previous kernel of the stream had finished
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(*wait_stamp));
 
@@ -221,6 +228,12 @@ __device__ __forceinline__ void gemv_main(const GemvArgs& a, __nv_bfloat16* xs, 
       }
     }
   }
+}
+
+template <int M, int R, bool SWIGLU, class Store>
+__device__ __forceinline__ void gemv_main(const GemvArgs& a, __nv_bfloat16* xs, float* rscale, float* scratch,
+                                          Store store, unsigned long long* wait_stamp = nullptr) {
+  gemv_main_w<M, R, SWIGLU, GEMV_WARPS>(a, xs, rscale, scratch, store, GemvPdlWait(), wait_stamp);
 }
 
 }  // namespace fb

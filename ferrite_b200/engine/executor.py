@@ -435,8 +435,24 @@ class Executor:
                 return ops.linear(xs, wt, norm_w=norm_w, eps=eps, swiglu=swiglu)
 
             row = self._row_parallel
+        # plain decode rows (one per sequence): the layer, or what follows its attention, as one persistent kernel
+        fuse = self.ecfg.fused_layers
+        if fuse is None:
+            fuse = self.tp is not None and self.tp.world > 1
+        fuse = (fuse and ops.name == "cuda" and commit and tv is None and not sp and max_seg_rows == 1 and nseg == T and T <= 4
+                and c.n_experts == 0 and c.kv_lora == 0 and isinstance(w["l0.out_proj"], torch.Tensor)
+                and w["l0.out_proj"].dtype == torch.bfloat16 and (self.tp is None or self.tp.world == 1 or self.tp.fused))
+        comm = self.tp.comm if (fuse and self.tp is not None and self.tp.world > 1) else None
         for i, kind in enumerate(self.kinds):
             p = f"l{i}."
+            if fuse and kind == "gdn" and c.lin_dk == c.lin_dv and c.lin_dk in (64, 128) and c.lin_v_heads * T <= ops.sm_count:
+                x = ops.decode_layer(comm, x, None, w[p + "in_proj"], w[p + "input_norm"], w[p + "out_proj"], w[p + "post_norm"],
+                                     w[p + "gate_up"], w[p + "down"],
+                                     gdn=(self.rec_state[i], self.conv_state[i], w[p + "conv_w"], w[p + "A_log"], w[p + "dt_bias"],
+                                          w[p + "gnorm_w"], mv["sslot"], c.lin_k_heads, c.lin_v_heads, c.lin_dk), eps=eps)
+                if i in c.tap_layers:
+                    self.taps.append(x)
+                continue
             if kind == "gdn":
                 proj = col(x, w[p + "in_proj"], w[p + "input_norm"])
                 if tv is not None:
@@ -517,6 +533,12 @@ class Executor:
                     o = ops.attention(q, proj, self.k_cache[i], self.v_cache[i], mv["slot"], mv["kvlen"],
                                       self.block_table, self.ecfg.kv_block, c.n_q, c.n_kv, c.head_dim, c.attn_gate,
                                       nsplit=nsplit, segs=(mv["sslot"], mv["srow0"], mv["snrows"], max_seg_rows), **kvs)
+                if fuse:
+                    x = ops.decode_layer(comm, x, o, None, None, w[p + "out_proj"], w[p + "post_norm"], w[p + "gate_up"],
+                                         w[p + "down"], eps=eps)
+                    if i in c.tap_layers:
+                        self.taps.append(x)
+                    continue
                 x = row(o, w[p + "out_proj"], x)
             if c.is_moe(i):
                 x = self._moe_ffn_sp(x, i, col, row) if sp else self._moe_ffn(x, i)

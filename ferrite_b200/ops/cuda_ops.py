@@ -34,6 +34,7 @@ class CudaOps:
         self.status_word = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._ws: Optional[torch.Tensor] = None
         self._counters = torch.zeros(16384, dtype=torch.int32, device=self.device)
+        self._dl_sync = torch.zeros(2, dtype=torch.int32, device=self.device)      # grid-barrier words of the persistent layer kernel
         self.force_gemv_chunks = False      # debug: run any row count through 8-row GEMV passes
         self.launches = 0                   # kernels launched (or recorded into a graph) through this object
         self.moe_pair_rows = MOE_PAIR_ROWS
@@ -490,6 +491,29 @@ class CudaOps:
         self.C.gdn_rec_tree(y, rec_state, qkv, proj, A_log, dt_bias, seg_slot, seg_row0, seg_nrows, row_parent, row_flags,
                             self._tree_scratch, nk, nv, dk, dv, eps)
         return y
+
+    def decode_layer(self, comm, x, o, w_in, input_norm, w_out, post_norm, w_gu, w_down, gdn=None, eps=1e-6):
+        """The rest of a decoder layer for one-row-per-sequence steps as one persistent kernel (`csrc/decode_layer.cu`).
+        `o` given: out projection + residual, then the MLP block. `o` None: a Gated DeltaNet layer from the hidden rows,
+        `gdn` = (rec_state, conv_state, conv_w, A_log, dt_bias, gnorm_w, seg_slot, nk, nv, dk). `comm`: the tensor-
+        parallel workspace handle (sums over ranks happen inside the kernel) or None."""
+        M, H = x.shape
+        inter = w_down.shape[1]
+        x_out = torch.empty(M, H, dtype=self.dtype, device=self.device)
+        x_mid = torch.empty(M, H, dtype=self.dtype, device=self.device)
+        act = torch.empty(M, inter, dtype=self.dtype, device=self.device)
+        self.launches += 1
+        if o is None:
+            rec, conv, conv_w, A_log, dt_bias, gnorm_w, seg_slot, nk, nv, dk = gdn
+            proj = torch.empty(M, w_in.shape[0], dtype=self.dtype, device=self.device)
+            o = torch.empty(M, w_out.shape[1], dtype=self.dtype, device=self.device)
+            self.C.decode_layer(comm, 1, x_out, x_mid, act, proj, o, x, w_in, input_norm, w_out, post_norm, w_gu, w_down,
+                                rec, conv, conv_w, A_log, dt_bias, gnorm_w, seg_slot, nk, nv, dk, eps, self.status_word,
+                                self._dl_sync)
+        else:
+            self.C.decode_layer(comm, 3, x_out, x_mid, act, x_mid, o, x, None, None, w_out, post_norm, w_gu, w_down,
+                                None, None, None, None, None, None, None, 0, 0, 0, eps, self.status_word, self._dl_sync)
+        return x_out
 
     def gdn_step(self, proj, conv_w, rec_state, conv_state, A_log, dt_bias, gnorm_w, seg_slot, seg_row0, seg_nrows, nk, nv,
                  dk, dv, eps, commit=True):

@@ -288,3 +288,32 @@ def test_scheduler_samples_on_the_device(ext):
     host = Scheduler(eng, SchedOptions(spec=0, device_sampling=False))
     h = generate(host, [p], s1)[0]
     assert len(h) == 12 and len(calls) == n
+
+
+@pytest.mark.parametrize("streams", [1, 3])
+def test_persistent_decode_layer_matches_the_separate_kernels(ext, streams):
+    """One cooperative kernel per layer (grid barriers between its phases) against the separate-launch path: same
+    weights, same prompts, decode rows compared step by step (logits to bf16 rounding of the norms' sums, greedy
+    picks equal), eager first and then through the CUDA graph."""
+    cfg = scaled(hybrid_27b(), 8)                              # 6 Gated DeltaNet layers, 2 attention layers
+    engs = [Engine(cfg, None, EngineConfig(n_slots=streams, max_ctx=256, fused_layers=f), device="cuda", seed=3)
+            for f in (False, True)]
+    prompts = [_prompt(cfg, 30 + 5 * s, seed=10 + s) for s in range(streams)]
+    for e in engs:
+        for s, p in enumerate(prompts):
+            e.prefill(s, p)
+    feed = [[int(t) for t in _prompt(cfg, 12, seed=50 + s)] for s in range(streams)]
+    for i in range(12):
+        outs = []
+        for e in engs:
+            segs = [Segment(s, len(prompts[s]) + i, [feed[s][i]], "last") for s in range(streams)]
+            lg, picks, _ = e.forward(segs, commit=True, greedy=True)
+            outs.append((lg.float().cpu(), picks[0].cpu()))
+        err = (outs[0][0] - outs[1][0]).abs().max().item()
+        # (with several rows the separate path multiplies through mma.sync fragments: another summation order)
+        assert err < 0.05 * outs[0][0].abs().max().item() + 1e-3, (i, err)
+        if streams == 1:
+            assert torch.equal(outs[0][1], outs[1][1]), i
+    assert engs[1].ops.launches < engs[0].ops.launches
+    for e in engs:
+        e.check()
