@@ -66,14 +66,18 @@ int fb_gemv_nvfp4_tc(void* Y, const void* X, long ldx, const void* norm_w, float
                      int ctas_per_sm, const void* next_Wq, const void* next_sf, int next_N, int next_K, int next_mode,
                      long prefetch_bytes, cudaStream_t s);
 
-// ---- decode_layer.cu: one decoder layer of a plain decode step as one persistent cooperative kernel ----
-int fb_decode_layer(int start_phase, int M, int hidden, void* x_out, void* x_mid, void* act, void* proj, void* o,
-                    const void* x_in, const void* w_in, int n_in, const void* input_norm, const void* w_out, int k_out,
-                    const void* post_norm, const void* w_gu, int inter, const void* w_down, float* rec_state,
-                    void* conv_state, const void* conv_w, const float* A_log, const float* dt_bias, const void* gnorm_w,
-                    const int* seg_slot, int nk, int nv, int dk, float eps, const void* const* peers, int rank, int world,
-                    int max_ctas, long slot_floats, uint32_t* epochs, int* status, unsigned spin_limit,
-                    uint32_t* sync_words, int sm_count, cudaStream_t s);
+// ---- decode_layer.cu: one decoder layer of a plain decode step as one persistent kernel ----
+int fb_decode_layers_max();
+int fb_decode_layers(int n_layers, const int* start_phase, int M, int hidden, const void* x_in, void* const* x_out,
+                     void* const* x_mid, void* const* act, void* const* proj, void* const* o, const void* const* w_in,
+                     const int* n_in, const void* const* input_norm, const void* const* w_out, const int* k_out,
+                     const void* const* post_norm, const void* const* w_gu, int inter, const void* const* w_down,
+                     float* const* rec_state, void* const* conv_state, const void* const* conv_w,
+                     const float* const* A_log, const float* const* dt_bias, const void* const* gnorm_w,
+                     const int* seg_slot, int nk, int nv, int dk, float eps, const void* const* peers, int rank, int world,
+                     int max_ctas, long slot_floats, uint32_t* epochs, int* status, unsigned spin_limit,
+                     uint32_t* sync_words, int sm_count, cudaStream_t s);
+void fb_decode_layer_trace_set(void* buf);
 
 // ---- moe.cu: router, grouped-expert GEMVs over (token, expert) pairs, fixed-order combine ----
 int fb_moe_route(int* ids, float* wts, const float* logits, const float* bias, int rows, int n_exp, int top_k, int mode,

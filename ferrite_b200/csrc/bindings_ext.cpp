@@ -52,39 +52,75 @@ void allreduce_oneshot(const Comm& c, Tensor y, Tensor part, c10::optional<Tenso
                              c.spin_limit, c.max_resident, cur_stream()), "allreduce_oneshot");
 }
 
-// start_phase 1: a Gated DeltaNet layer from the hidden rows x_in; 3: the rest of a layer whose mixer output o is given.
-// comm: a Comm, or None on one GPU. Returns nothing; x_out holds the layer's output rows.
-void decode_layer(pybind11::object comm, int64_t start_phase, Tensor x_out, Tensor x_mid, Tensor act, Tensor proj, Tensor o,
-                  Tensor x_in, c10::optional<Tensor> w_in, c10::optional<Tensor> input_norm, Tensor w_out, Tensor post_norm,
-                  Tensor w_gu, Tensor w_down, c10::optional<Tensor> rec_state, c10::optional<Tensor> conv_state,
-                  c10::optional<Tensor> conv_w, c10::optional<Tensor> A_log, c10::optional<Tensor> dt_bias,
-                  c10::optional<Tensor> gnorm_w, c10::optional<Tensor> seg_slot, int64_t nk, int64_t nv, int64_t dk,
-                  double eps, Tensor status, Tensor sync_words) {
+// A run of consecutive decoder layers for one-row-per-sequence steps in one persistent launch. Per-layer lists; entries a
+// layer does not use (a layer entered after its attention has no input projection and no recurrent state) are empty tensors.
+// comm: a Comm, or None on one GPU.
+int64_t decode_layers_max() { return fb_decode_layers_max(); }
+
+void decode_layers(pybind11::object comm, std::vector<int64_t> start_phase, Tensor x_in, std::vector<Tensor> x_out,
+                   std::vector<Tensor> x_mid, std::vector<Tensor> act, std::vector<Tensor> proj, std::vector<Tensor> o,
+                   std::vector<Tensor> w_in, std::vector<Tensor> input_norm, std::vector<Tensor> w_out,
+                   std::vector<Tensor> post_norm, std::vector<Tensor> w_gu, std::vector<Tensor> w_down,
+                   std::vector<Tensor> rec_state, std::vector<Tensor> conv_state, std::vector<Tensor> conv_w,
+                   std::vector<Tensor> A_log, std::vector<Tensor> dt_bias, std::vector<Tensor> gnorm_w,
+                   c10::optional<Tensor> seg_slot, int64_t nk, int64_t nv, int64_t dk, double eps, Tensor status,
+                   Tensor sync_words) {
+  const int n = (int)start_phase.size();
   const int M = (int)x_in.size(0), hidden = (int)x_in.size(1);
-  TORCH_CHECK(x_in.is_contiguous() && x_out.is_contiguous() && x_mid.is_contiguous() && act.is_contiguous() &&
-              o.is_contiguous() && proj.is_contiguous() && w_out.is_contiguous() && w_gu.is_contiguous() &&
-              w_down.is_contiguous(), "decode_layer: contiguous tensors");
-  TORCH_CHECK(w_out.size(0) == hidden && w_out.size(1) == o.size(1) && w_gu.size(1) == hidden &&
-              w_gu.size(0) == 2 * act.size(1) && w_down.size(0) == hidden && w_down.size(1) == act.size(1),
-              "decode_layer: shapes");
-  TORCH_CHECK(sync_words.numel() >= 2 && sync_words.scalar_type() == torch::kInt32, "decode_layer: sync words");
-  if (start_phase == 1)
-    TORCH_CHECK(w_in.has_value() && w_in->is_contiguous() && w_in->size(1) == hidden && proj.size(1) == w_in->size(0) &&
-                rec_state.has_value() && conv_state.has_value() && seg_slot.has_value() && seg_slot->numel() >= M &&
-                o.size(1) == nv * dk, "decode_layer: Gated DeltaNet operands");
+  TORCH_CHECK(n >= 1 && n <= fb_decode_layers_max(), "decode_layers: run length");
+  for (auto* v : {&x_out, &x_mid, &act, &proj, &o, &w_in, &input_norm, &w_out, &post_norm, &w_gu, &w_down, &rec_state,
+                  &conv_state, &conv_w, &A_log, &dt_bias, &gnorm_w})
+    TORCH_CHECK((int)v->size() == n, "decode_layers: one entry per layer in every list");
+  TORCH_CHECK(x_in.is_contiguous(), "decode_layers: contiguous rows");
+  TORCH_CHECK(sync_words.numel() >= 2 && sync_words.scalar_type() == torch::kInt32, "decode_layers: sync words");
+  const int inter = (int)w_down[0].size(1);
+  std::vector<int> sp(n), n_in(n), k_outs(n);
+  std::vector<void*> p_xout(n), p_xmid(n), p_act(n), p_proj(n), p_o(n), p_conv(n);
+  std::vector<const void*> p_win(n), p_inorm(n), p_wout(n), p_pnorm(n), p_wgu(n), p_wdown(n), p_convw(n), p_gnorm(n);
+  std::vector<float*> p_rec(n);
+  std::vector<const float*> p_alog(n), p_dtb(n);
+  auto ptr = [](const Tensor& t) -> void* { return (t.defined() && t.numel() > 0) ? t.data_ptr() : nullptr; };
+  for (int i = 0; i < n; ++i) {
+    sp[i] = (int)start_phase[i];
+    const int k_out = (int)w_out[i].size(1);
+    k_outs[i] = k_out;
+    TORCH_CHECK(x_out[i].is_contiguous() && x_mid[i].is_contiguous() && act[i].is_contiguous() && o[i].is_contiguous() &&
+                w_out[i].is_contiguous() && w_gu[i].is_contiguous() && w_down[i].is_contiguous(), "decode_layers: contiguous");
+    TORCH_CHECK(w_out[i].size(0) == hidden && w_out[i].size(1) == k_out && o[i].size(1) == k_out &&
+                w_gu[i].size(1) == hidden && w_gu[i].size(0) == 2 * inter && w_down[i].size(0) == hidden &&
+                w_down[i].size(1) == inter && act[i].size(1) == inter && x_out[i].size(1) == hidden &&
+                x_mid[i].size(1) == hidden, "decode_layers: shapes");
+    if (sp[i] == 1) {
+      TORCH_CHECK(w_in[i].is_contiguous() && w_in[i].size(1) == hidden && proj[i].is_contiguous() &&
+                  proj[i].size(1) == w_in[i].size(0) && rec_state[i].numel() > 0 && conv_state[i].numel() > 0 &&
+                  seg_slot.has_value() && seg_slot->numel() >= M && k_out == nv * dk,
+                  "decode_layers: Gated DeltaNet operands");
+      n_in[i] = (int)w_in[i].size(0);
+    } else {
+      n_in[i] = 0;
+    }
+    p_xout[i] = x_out[i].data_ptr(); p_xmid[i] = x_mid[i].data_ptr(); p_act[i] = act[i].data_ptr();
+    p_proj[i] = ptr(proj[i]) ? ptr(proj[i]) : x_mid[i].data_ptr(); p_o[i] = o[i].data_ptr();
+    p_win[i] = ptr(w_in[i]); p_inorm[i] = ptr(input_norm[i]); p_wout[i] = w_out[i].data_ptr();
+    p_pnorm[i] = post_norm[i].data_ptr(); p_wgu[i] = w_gu[i].data_ptr(); p_wdown[i] = w_down[i].data_ptr();
+    p_rec[i] = (float*)ptr(rec_state[i]); p_conv[i] = ptr(conv_state[i]); p_convw[i] = ptr(conv_w[i]);
+    p_alog[i] = (const float*)ptr(A_log[i]); p_dtb[i] = (const float*)ptr(dt_bias[i]); p_gnorm[i] = ptr(gnorm_w[i]);
+  }
   const Comm* c = comm.is_none() ? nullptr : comm.cast<const Comm*>();
-  check(fb_decode_layer((int)start_phase, M, hidden, x_out.data_ptr(), x_mid.data_ptr(), act.data_ptr(), proj.data_ptr(),
-                        o.data_ptr(), x_in.data_ptr(), cptr(w_in), w_in.has_value() ? (int)w_in->size(0) : 0,
-                        cptr(input_norm), w_out.data_ptr(), (int)w_out.size(1), post_norm.data_ptr(), w_gu.data_ptr(),
-                        (int)act.size(1), w_down.data_ptr(), rec_state.has_value() ? rec_state->data_ptr<float>() : nullptr,
-                        conv_state.has_value() ? conv_state->data_ptr() : nullptr, cptr(conv_w),
-                        A_log.has_value() ? A_log->data_ptr<float>() : nullptr,
-                        dt_bias.has_value() ? dt_bias->data_ptr<float>() : nullptr, cptr(gnorm_w),
-                        seg_slot.has_value() ? seg_slot->data_ptr<int>() : nullptr, (int)nk, (int)nv, (int)dk, (float)eps,
-                        c ? c->peers.data() : nullptr, c ? c->rank : 0, c ? c->world : 1, c ? c->max_ctas : 0,
-                        c ? c->slot_floats : 0, c ? (uint32_t*)c->epochs.data_ptr() : nullptr, status.data_ptr<int>(),
-                        c ? c->spin_limit : 0u, (uint32_t*)sync_words.data_ptr(),
-                        at::cuda::getCurrentDeviceProperties()->multiProcessorCount, cur_stream()), "decode_layer");
+  check(fb_decode_layers(n, sp.data(), M, hidden, x_in.data_ptr(), p_xout.data(), p_xmid.data(), p_act.data(),
+                         p_proj.data(), p_o.data(), p_win.data(), n_in.data(), p_inorm.data(), p_wout.data(), k_outs.data(),
+                         p_pnorm.data(), p_wgu.data(), inter, p_wdown.data(), p_rec.data(), p_conv.data(), p_convw.data(),
+                         p_alog.data(), p_dtb.data(), p_gnorm.data(),
+                         seg_slot.has_value() ? seg_slot->data_ptr<int>() : nullptr, (int)nk, (int)nv, (int)dk, (float)eps,
+                         c ? c->peers.data() : nullptr, c ? c->rank : 0, c ? c->world : 1, c ? c->max_ctas : 0,
+                         c ? c->slot_floats : 0, c ? (uint32_t*)c->epochs.data_ptr() : nullptr, status.data_ptr<int>(),
+                         c ? c->spin_limit : 0u, (uint32_t*)sync_words.data_ptr(),
+                         at::cuda::getCurrentDeviceProperties()->multiProcessorCount, cur_stream()), "decode_layers");
+}
+
+void decode_layer_trace_set(c10::optional<Tensor> buf) {
+  if (buf.has_value()) TORCH_CHECK(buf->scalar_type() == torch::kInt64 && buf->numel() >= 1024 * 16, "trace: int64[1024 * 16]");
+  fb_decode_layer_trace_set(buf.has_value() ? buf->data_ptr() : nullptr);
 }
 
 void argmax_gather(const Comm& c, Tensor ids, Tensor logits, int64_t vocab_offset, c10::optional<Tensor> vals) {
@@ -447,7 +483,9 @@ void register_ext(pybind11::module_& m) {
   m.def("ag_gemm", &ag_gemm);
   pybind11::class_<Comm>(m, "Comm");
   m.def("make_comm", &make_comm);
-  m.def("decode_layer", &decode_layer);
+  m.def("decode_layers", &decode_layers);
+  m.def("decode_layers_max", &decode_layers_max);
+  m.def("decode_layer_trace_set", &decode_layer_trace_set);
   m.def("comm_workspace_bytes", [](int64_t max_ctas, int64_t slot_floats) {
     return (int64_t)fb_comm_workspace_bytes((int)max_ctas, (long)slot_floats);
   });

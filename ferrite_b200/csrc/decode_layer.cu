@@ -9,9 +9,10 @@
 //     3  x_mid = x + sum over ranks (W_out * o)
 //     4  act   = silu(W_gate * rmsnorm(x_mid)) * (W_up * rmsnorm(x_mid))
 //     5  x_out = x_mid + sum over ranks (W_down * act)
-// run inside one cooperative launch of one CTA per SM, separated by grid barriers (an atomic counter in global memory
+// run inside one launch of one CTA per SM, separated by grid barriers (an atomic counter in global memory
 // with a bounded wait) instead of kernel boundaries. Every phase issues its first weight loads BEFORE it waits at the
-// barrier in front of it, so HBM latency hides behind the barrier. The two sums over ranks are the same one-shot
+// barrier in front of it, so HBM latency hides behind the barrier. (Asking L2 for the whole next phase's rows with
+// cp.async.bulk.prefetch.L2 while a phase runs was measured too: the step got 11 % slower at tensor-parallel 8.) The two sums over ranks are the same one-shot
 // (value, epoch)-pair exchange over NVLink peer memory that the stand-alone fused GEMV + all-reduce uses, executed by
 // the CTA that owns the rows. Attention layers enter at phase 3 with o computed by the attention kernels.
 //
@@ -28,6 +29,9 @@ namespace fb {
 constexpr int DL_THREADS = 512;
 constexpr int DL_WARPS = DL_THREADS / 32;
 constexpr int DL_R = 2;
+constexpr int DL_TRACE_RECS = 1024;
+constexpr int DL_TRACE_WORDS = 16;   // 0 start, 1 in_proj done, 2 barrier, 3 heads done, 4 barrier, 5 out_proj done, 6 summed + stored,
+                                     // 7 barrier, 8 gate|up done, 9 barrier, 10 down done, 11 summed + stored, 12 start phase
 
 struct DLSync {
   uint32_t* counter;      // arrivals, monotonic over all launches
@@ -36,7 +40,9 @@ struct DLSync {
   unsigned spin_limit;
 };
 
-struct DLArgs {
+constexpr int DL_MAX_LAYERS = 4;
+
+struct DLLayer {
   GemvArgs g_in, g_out, g_gu, g_down;
   // phase 2
   __nv_bfloat16* o;
@@ -46,13 +52,20 @@ struct DLArgs {
   const float* A_log;
   const float* dt_bias;
   const __nv_bfloat16* gnorm_w;
+  int start_phase;        // 1: Gated DeltaNet layer, 3: enter with o given (attention layers)
+};
+
+// A run of consecutive layers in one launch: only the first may enter at phase 3.
+struct DLArgs {
+  DLLayer L[DL_MAX_LAYERS];
+  int n_layers;
   const int* seg_slot;
   int nk, nv, dk;
   float eps;
-  int start_phase;        // 1: Gated DeltaNet layer, 3: enter with o given (attention layers)
   int M;
   int xs_bytes;           // bytes of the staged-activation area; the exchange tile follows it
-  int rpc_out, rpc_down;  // rows per CTA of the two exchanged phases (tile row stride)
+  int n_barriers;         // grid barriers of the whole launch
+  unsigned long long* trace;   // null, or [DL_TRACE_RECS][DL_TRACE_WORDS] %globaltimer stamps of CTA 0 (profiling)
   CommBuf cb;             // world 1: no exchange
   DLSync sync;
 };
@@ -87,18 +100,30 @@ struct DLBarrier {
   }
 };
 
-struct DLNoWait {
-  __device__ __forceinline__ void before_loads() const {}
-  __device__ __forceinline__ void wait() const {}
-};
-struct DLBarrierWait {
+// What a phase waits for once its first weight loads are in flight. FIRST (first phase of a launch): the previous
+// kernel of the stream (programmatic dependent launch); only then are the words that kernel may have written read, the
+// barrier base and the exchange epoch. BARRIER: the grid barrier in front of the phase.
+struct DLWait {
+  enum Mode { FIRST, BARRIER };
+  Mode mode;
   DLBarrier* b;
-  __device__ __forceinline__ void before_loads() const {}
-  __device__ __forceinline__ void wait() const { b->sync(); }
+  uint32_t* base_s;
+  const CommBuf* cb;
+  uint32_t* epoch;
+  __device__ __forceinline__ void before_loads() const { if (mode == FIRST) pdl_launch_dependents(); }
+  __device__ __forceinline__ void wait() const {
+    if (mode == BARRIER) { b->sync(); return; }
+    pdl_wait();
+    if (threadIdx.x == 0) *base_s = *reinterpret_cast<volatile uint32_t*>(b->s.base);
+    __syncthreads();
+    b->base = *base_s;
+    if (cb->world > 1) *epoch = comm_epoch_begin(*cb);      // the launch uses epoch, epoch + 1, ...
+  }
 };
 
 template <int M, class Wait>
-__device__ __forceinline__ void dl_gemv_store(const GemvArgs& g, __nv_bfloat16* xs, float* rscale, float* scratch, Wait w) {
+__device__ __forceinline__ void dl_gemv_store(const GemvArgs& g, __nv_bfloat16* xs, float* rscale, float* scratch, Wait w,
+                                              unsigned long long* wait_stamp = nullptr) {
   const int row_end = min(g.N, (int)(blockIdx.x + 1) * g.rows_per_cta);
   gemv_main_w<M, DL_R, false, DL_WARPS>(g, xs, rscale, scratch, [&](float (&acc)[DL_R][M], int n) {
     if ((threadIdx.x & 31) != 0) return;
@@ -114,13 +139,18 @@ __device__ __forceinline__ void dl_gemv_store(const GemvArgs& g, __nv_bfloat16* 
         reinterpret_cast<__nv_bfloat16*>(g.Y)[(size_t)m * g.ldy + nn] = f2bf(v);
       }
     }
-  }, w);
+  }, w, wait_stamp);
 }
 
 // W * x into the CTA's tile, the sum over ranks (world > 1), residual, bf16 rows out
+__device__ __forceinline__ void dl_stamp(unsigned long long* st, int i) {
+  if (st != nullptr && threadIdx.x == 0) st[i] = comm_now();
+}
+
 template <int M, class Wait>
-__device__ __forceinline__ void dl_gemv_reduce(const GemvArgs& g, const CommBuf& cb, uint32_t epoch, __nv_bfloat16* xs,
-                                               float* tile, float* rscale, float* scratch, Wait w) {
+__device__ __forceinline__ void dl_gemv_reduce(const GemvArgs& g, const CommBuf& cb, const uint32_t& epoch0,
+                                               uint32_t epoch_add, __nv_bfloat16* xs, float* tile, float* rscale,
+                                               float* scratch, Wait w, unsigned long long* st = nullptr, int st0 = 0) {
   const int rpc = g.rows_per_cta;
   const int row0 = blockIdx.x * rpc;
   const int row_end = min(g.N, row0 + rpc);
@@ -134,9 +164,11 @@ __device__ __forceinline__ void dl_gemv_reduce(const GemvArgs& g, const CommBuf&
       if (n + r < row_end)
 #pragma unroll
         for (int m = 0; m < M; ++m) tile[m * rpc + (n + r - row0)] = acc[r][m];
-  }, w);
+  }, w, st ? st + st0 : nullptr);
   __syncthreads();
-  if (cb.world > 1 && nrows > 0) cta_exchange_sum(cb, tile, M * rpc, (long)blockIdx.x * M * rpc, epoch);
+  dl_stamp(st, st0 + 1);
+  // (epoch0 is set by the launch's first wait, which may be the one inside the loop above)
+  if (cb.world > 1 && nrows > 0) cta_exchange_sum(cb, tile, M * rpc, (long)blockIdx.x * M * rpc, epoch0 + epoch_add);
   __syncthreads();
   for (int i = threadIdx.x; i < g.M * nrows; i += blockDim.x) {
     const int m = i / nrows, j = i % nrows;
@@ -145,10 +177,11 @@ __device__ __forceinline__ void dl_gemv_reduce(const GemvArgs& g, const CommBuf&
     if (g.res) v += bf2f(g.res[o]);
     reinterpret_cast<__nv_bfloat16*>(g.Y)[o] = f2bf(v);
   }
+  dl_stamp(st, st0 + 2);
 }
 
 template <int M>
-__global__ void __launch_bounds__(DL_THREADS, 1) decode_layer_kernel(DLArgs a) {
+__global__ void __launch_bounds__(DL_THREADS, 1) decode_layer_kernel(const __grid_constant__ DLArgs a) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(smem_raw);
   float* tile = reinterpret_cast<float*>(smem_raw + a.xs_bytes);
@@ -156,73 +189,95 @@ __global__ void __launch_bounds__(DL_THREADS, 1) decode_layer_kernel(DLArgs a) {
   __shared__ float scratch[32];
   __shared__ uint32_t base_s;
   __shared__ int abort_s;
-  if (threadIdx.x == 0) {
-    base_s = *reinterpret_cast<volatile uint32_t*>(a.sync.base);
-    abort_s = 0;
-  }
+  __shared__ unsigned long long stamps_s[DL_TRACE_WORDS];
+  unsigned long long* st = (a.trace != nullptr && blockIdx.x == 0) ? stamps_s : nullptr;
+  if (threadIdx.x == 0) abort_s = 0;
   __syncthreads();
-  DLBarrier bar{a.sync, base_s, &abort_s, 0, a.start_phase == 1 ? 3 : 1};
+  DLBarrier bar{a.sync, 0u, &abort_s, 0, a.n_barriers - 1};
   uint32_t epoch = 0;
-  if (a.cb.world > 1) epoch = comm_epoch_begin(a.cb);        // this launch uses epoch and epoch + 1
+  const DLWait first{DLWait::FIRST, &bar, &base_s, &a.cb, &epoch};
+  const DLWait at_barrier{DLWait::BARRIER, &bar, &base_s, &a.cb, &epoch};
 
-  if (a.start_phase == 1) {
-    dl_gemv_store<M>(a.g_in, xs, rscale, scratch, DLNoWait());
-    bar.sync();
-    // every (head, sequence) pair has a CTA of its own (the host checks nv * M <= grid): the heads of a key group read
-    // the conv tail their first head rewrites at the end
-    const int pair = blockIdx.x;
-    if (pair < a.nv * a.M) {
-      const int h = pair % a.nv, seg = pair / a.nv;
-      if (a.dk == 128)
-        gdn_step_body<128, 128, 4>(a.o, a.rec_state, a.conv_state, reinterpret_cast<const __nv_bfloat16*>(a.g_in.Y),
-                                   a.g_in.ldy, a.conv_w, a.A_log, a.dt_bias, a.gnorm_w, 1, seg, a.seg_slot[seg], h, a.nk,
-                                   a.nv, a.eps, 1);
-      else
-        gdn_step_body<64, 64, 8>(a.o, a.rec_state, a.conv_state, reinterpret_cast<const __nv_bfloat16*>(a.g_in.Y),
-                                 a.g_in.ldy, a.conv_w, a.A_log, a.dt_bias, a.gnorm_w, 1, seg, a.seg_slot[seg], h, a.nk,
-                                 a.nv, a.eps, 1);
+  for (int li = 0; li < a.n_layers; ++li) {
+    const DLLayer& L = a.L[li];
+    const DLWait& enter = li == 0 ? first : at_barrier;
+    const int n_at_start = bar.n;
+    if (st != nullptr && threadIdx.x == 0) {
+      for (int i = 0; i < DL_TRACE_WORDS; ++i) st[i] = 0;
+      st[0] = comm_now(); st[12] = (unsigned long long)L.start_phase; st[14] = (unsigned long long)li;
     }
-    dl_gemv_reduce<M>(a.g_out, a.cb, epoch, xs, tile, rscale, scratch, DLBarrierWait{&bar});
-  } else {
-    dl_gemv_reduce<M>(a.g_out, a.cb, epoch, xs, tile, rscale, scratch, DLNoWait());
-  }
-
-  {
-    const GemvArgs& g = a.g_gu;
-    gemv_main_w<M, DL_R, true, DL_WARPS>(g, xs, rscale, scratch, [&](float (&acc)[DL_R][M], int n) {
-      if ((threadIdx.x & 31) != 0) return;
-#pragma unroll
-      for (int m = 0; m < M; ++m) {
-        if (m >= g.M) break;
-        reinterpret_cast<__nv_bfloat16*>(g.Y)[(size_t)m * g.ldy + n] = f2bf(siluf_(acc[0][m]) * acc[DL_R - 1][m]);
+    if (L.start_phase == 1) {
+      dl_gemv_store<M>(L.g_in, xs, rscale, scratch, enter, st ? st + 13 : nullptr);
+      dl_stamp(st, 1);
+      bar.sync();
+      dl_stamp(st, 2);
+      // every (head, sequence) pair has a CTA of its own (the host checks nv * M <= grid): the heads of a key group
+      // read the conv tail their first head rewrites at the end
+      const int pair = blockIdx.x;
+      if (pair < a.nv * a.M) {
+        const int h = pair % a.nv, seg = pair / a.nv;
+        if (a.dk == 128)
+          gdn_step_body<128, 128, 4>(L.o, L.rec_state, L.conv_state, reinterpret_cast<const __nv_bfloat16*>(L.g_in.Y),
+                                     L.g_in.ldy, L.conv_w, L.A_log, L.dt_bias, L.gnorm_w, 1, seg, a.seg_slot[seg], h, a.nk,
+                                     a.nv, a.eps, 1);
+        else
+          gdn_step_body<64, 64, 8>(L.o, L.rec_state, L.conv_state, reinterpret_cast<const __nv_bfloat16*>(L.g_in.Y),
+                                   L.g_in.ldy, L.conv_w, L.A_log, L.dt_bias, L.gnorm_w, 1, seg, a.seg_slot[seg], h, a.nk,
+                                   a.nv, a.eps, 1);
       }
-    }, DLBarrierWait{&bar});
-  }
+      dl_stamp(st, 3);
+      dl_gemv_reduce<M>(L.g_out, a.cb, epoch, 2u * li, xs, tile, rscale, scratch, at_barrier, st, 4);
+    } else {
+      dl_gemv_reduce<M>(L.g_out, a.cb, epoch, 2u * li, xs, tile, rscale, scratch, enter, st, 4);
+      if (st != nullptr && threadIdx.x == 0) st[13] = st[4];
+    }
 
-  dl_gemv_reduce<M>(a.g_down, a.cb, epoch + 1, xs, tile, rscale, scratch, DLBarrierWait{&bar});
-  if (a.cb.world > 1) comm_epoch_end(a.cb, epoch + 1);
+    {
+      const GemvArgs& g = L.g_gu;
+      gemv_main_w<M, DL_R, true, DL_WARPS>(g, xs, rscale, scratch, [&](float (&acc)[DL_R][M], int n) {
+        if ((threadIdx.x & 31) != 0) return;
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+          if (m >= g.M) break;
+          reinterpret_cast<__nv_bfloat16*>(g.Y)[(size_t)m * g.ldy + n] = f2bf(siluf_(acc[0][m]) * acc[DL_R - 1][m]);
+        }
+      }, at_barrier, st ? st + 7 : nullptr);
+      dl_stamp(st, 8);
+    }
+
+    dl_gemv_reduce<M>(L.g_down, a.cb, epoch, 2u * li + 1u, xs, tile, rscale, scratch, at_barrier, st, 9);
+    if (st != nullptr && threadIdx.x == 0) {
+      unsigned long long* rec = a.trace + (size_t)((base_s / gridDim.x + (uint32_t)n_at_start) % DL_TRACE_RECS) * DL_TRACE_WORDS;
+      for (int i = 0; i < DL_TRACE_WORDS; ++i) rec[i] = st[i];
+    }
+  }
+  if (a.cb.world > 1) comm_epoch_end(a.cb, epoch + 2u * a.n_layers - 1u);
 }
 
-struct DLPlan { int grid; size_t smem; };
-
-static void dl_plan_gemv(GemvArgs& g, int M, int grid, bool swiglu) {
+static void dl_plan_gemv(GemvArgs& g, int M, int grid) {
   g.kc = gemv_chunk_len(M, g.K);
-  const int nchunks = (g.K + g.kc - 1) / g.kc;
-  (void)nchunks; (void)swiglu;
   g.rows_per_cta = (g.N + grid - 1) / grid;
 }
 
 template <int M>
 static int dl_launch(DLArgs& a, int grid, cudaStream_t s) {
-  dl_plan_gemv(a.g_in, M, grid, false);
-  dl_plan_gemv(a.g_out, M, grid, false);
-  dl_plan_gemv(a.g_gu, M, grid, true);
-  dl_plan_gemv(a.g_down, M, grid, false);
-  int kc = a.g_out.kc > a.g_gu.kc ? a.g_out.kc : a.g_gu.kc;
-  if (a.g_down.kc > kc) kc = a.g_down.kc;
-  if (a.start_phase == 1 && a.g_in.kc > kc) kc = a.g_in.kc;
+  int kc = 0, rpc = 0;
+  a.n_barriers = a.n_layers - 1;
+  for (int li = 0; li < a.n_layers; ++li) {
+    DLLayer& L = a.L[li];
+    dl_plan_gemv(L.g_in, M, grid);
+    dl_plan_gemv(L.g_out, M, grid);
+    dl_plan_gemv(L.g_gu, M, grid);
+    dl_plan_gemv(L.g_down, M, grid);
+    if (L.start_phase == 1 && L.g_in.kc > kc) kc = L.g_in.kc;
+    if (L.g_out.kc > kc) kc = L.g_out.kc;
+    if (L.g_gu.kc > kc) kc = L.g_gu.kc;
+    if (L.g_down.kc > kc) kc = L.g_down.kc;
+    if (L.g_out.rows_per_cta > rpc) rpc = L.g_out.rows_per_cta;
+    if (L.g_down.rows_per_cta > rpc) rpc = L.g_down.rows_per_cta;
+    a.n_barriers += L.start_phase == 1 ? 4 : 2;
+  }
   a.xs_bytes = (int)((size_t)M * kc * sizeof(__nv_bfloat16));
-  const int rpc = a.g_out.rows_per_cta > a.g_down.rows_per_cta ? a.g_out.rows_per_cta : a.g_down.rows_per_cta;
   const size_t smem = (size_t)a.xs_bytes + (size_t)M * rpc * sizeof(float);
   if (smem > 160 * 1024) return -5;
   if (a.cb.world > 1) {
@@ -236,35 +291,46 @@ static int dl_launch(DLArgs& a, int grid, cudaStream_t s) {
     if (e != cudaSuccess) return (int)e;
     attr_done = true;
   }
-  // every CTA waits for every other: a cooperative launch makes the driver refuse a grid that cannot be resident at once
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(grid); cfg.blockDim = dim3(DL_THREADS); cfg.dynamicSmemBytes = smem; cfg.stream = s;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeCooperative;
-  attr[0].val.cooperative = 1;
-  cfg.attrs = attr; cfg.numAttrs = 1;
-  return (int)cudaLaunchKernelEx(&cfg, kern, a);
+  // Every CTA waits for every other, so all of them must be resident together: one per SM, checked against what the
+  // occupancy calculator allows. (A cooperative launch would have the driver check the same, but measured 15 us from the
+  // end of one such launch to the start of the next inside a CUDA graph; a plain launch with programmatic dependent
+  // launch lets the next launch's CTAs start, and request their first weights, as SMs free up. CTAs of earlier kernels
+  // never wait for this one, so they drain and every CTA of this grid gets its SM; the barrier waits are bounded.)
+  int per_sm = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, DL_THREADS, smem) != cudaSuccess || per_sm < 1) return -9;
+  return (int)launch_pdl(kern, dim3(grid), dim3(DL_THREADS), smem, s, a);
 }
 
 }  // namespace fb
 
 using namespace fb;
 
-// Persistent decode layer. x_in/x_mid/x_out/act/proj/o: bf16 rows [M][...] (contiguous). start_phase 1: Gated DeltaNet
-// layer (w_in, input_norm, states and head parameters used); 3: o is given. sync: two zero-initialised u32 words owned by
-// the caller (counter, base), shared by all launches of a stream. world 1: peers may be null.
-extern "C" int fb_decode_layer(int start_phase, int M, int hidden, void* x_out, void* x_mid, void* act, void* proj, void* o,
-                               const void* x_in, const void* w_in, int n_in, const void* input_norm, const void* w_out,
-                               int k_out, const void* post_norm, const void* w_gu, int inter, const void* w_down,
-                               float* rec_state, void* conv_state, const void* conv_w, const float* A_log,
-                               const float* dt_bias, const void* gnorm_w, const int* seg_slot, int nk, int nv, int dk,
-                               float eps, const void* const* peers, int rank, int world, int max_ctas, long slot_floats,
-                               uint32_t* epochs, int* status, unsigned spin_limit, uint32_t* sync_words, int sm_count,
-                               cudaStream_t s) {
-  if (M <= 0 || M > 4 || world > COMM_MAX_RANKS) return -1;
-  if ((hidden % 8) || (k_out % 8) || (inter % 8)) return -1;
+static unsigned long long* g_dl_trace = nullptr;
+// Profiling: a device buffer of [1024][16] 64-bit words that CTA 0 of every later launch stamps (nullptr: off). Set it
+// before a CUDA graph is captured.
+extern "C" void fb_decode_layer_trace_set(void* buf) { g_dl_trace = (unsigned long long*)buf; }
+
+extern "C" int fb_decode_layers_max() { return DL_MAX_LAYERS; }
+
+// A run of n_layers consecutive decoder layers (<= fb_decode_layers_max()) for M <= 4 one-row sequences. Per layer, in
+// arrays of n_layers entries: start_phase (1: Gated DeltaNet layer from the hidden rows; 3: the rest of a layer whose
+// mixer output o is given, first layer of the run only), the buffers x_out / x_mid / act / proj / o (bf16, contiguous
+// rows) and the weights; layer l reads the rows layer l - 1 wrote (x_in for the first). sync: two zero-initialised
+// u32 words owned by the caller (counter, base), shared by all launches of a stream. world 1: peers may be null.
+extern "C" int fb_decode_layers(int n_layers, const int* start_phase, int M, int hidden, const void* x_in,
+                                void* const* x_out, void* const* x_mid, void* const* act, void* const* proj,
+                                void* const* o, const void* const* w_in, const int* n_in,
+                                const void* const* input_norm, const void* const* w_out, const int* k_out,
+                                const void* const* post_norm, const void* const* w_gu, int inter,
+                                const void* const* w_down, float* const* rec_state, void* const* conv_state,
+                                const void* const* conv_w, const float* const* A_log, const float* const* dt_bias,
+                                const void* const* gnorm_w, const int* seg_slot, int nk, int nv, int dk, float eps,
+                                const void* const* peers, int rank, int world, int max_ctas, long slot_floats,
+                                uint32_t* epochs, int* status, unsigned spin_limit, uint32_t* sync_words, int sm_count,
+                                cudaStream_t s) {
+  if (M <= 0 || M > 4 || world > COMM_MAX_RANKS || n_layers < 1 || n_layers > DL_MAX_LAYERS) return -1;
+  if ((hidden % 8) || (inter % 8)) return -1;
   if (sm_count <= 0) sm_count = 148;
-  if (start_phase == 1 && (nv * M > sm_count || !(dk == 128 || dk == 64))) return -2;
   typedef const __nv_bfloat16* cbf;
   DLArgs a;
   auto fill = [&](GemvArgs& g, const void* X, long ldx, const void* W, const void* norm_w, const void* res, void* Y,
@@ -272,19 +338,36 @@ extern "C" int fb_decode_layer(int start_phase, int M, int hidden, void* x_out, 
     g.X = (cbf)X; g.W = (cbf)W; g.norm_w = (cbf)norm_w; g.res = (cbf)res; g.Y = Y; g.M = M; g.N = N; g.K = K;
     g.ldx = ldx; g.ldy = ldy; g.eps = eps; g.centred = 1; g.out_f32 = 0; g.rows_per_cta = 0; g.kc = 0;
   };
-  fill(a.g_in, x_in, hidden, w_in ? w_in : w_out, input_norm, nullptr, proj, n_in, start_phase == 1 ? n_in : 1, hidden);
-  fill(a.g_out, o, k_out, w_out, nullptr, x_in, x_mid, hidden, hidden, k_out);
-  fill(a.g_gu, x_mid, hidden, w_gu, post_norm, nullptr, act, inter, inter, hidden);
-  fill(a.g_down, act, inter, w_down, nullptr, x_mid, x_out, hidden, hidden, inter);
-  a.o = (__nv_bfloat16*)o; a.rec_state = rec_state; a.conv_state = (__nv_bfloat16*)conv_state; a.conv_w = (cbf)conv_w;
-  a.A_log = A_log; a.dt_bias = dt_bias; a.gnorm_w = (cbf)gnorm_w; a.seg_slot = seg_slot; a.nk = nk; a.nv = nv; a.dk = dk;
-  a.eps = eps; a.start_phase = start_phase; a.M = M; a.xs_bytes = 0; a.rpc_out = a.rpc_down = 0;
+  const void* x_prev = x_in;
+  for (int li = 0; li < n_layers; ++li) {
+    DLLayer& L = a.L[li];
+    const int sp = start_phase[li];
+    if (sp != 1 && !(sp == 3 && li == 0)) return -2;
+    if (sp == 1 && (nv * M > sm_count || !(dk == 128 || dk == 64))) return -2;
+    if (k_out[li] % 8) return -1;
+    fill(L.g_in, x_prev, hidden, sp == 1 ? w_in[li] : w_out[li], sp == 1 ? input_norm[li] : nullptr, nullptr, proj[li],
+         sp == 1 ? n_in[li] : 1, sp == 1 ? n_in[li] : 1, hidden);
+    fill(L.g_out, o[li], k_out[li], w_out[li], nullptr, x_prev, x_mid[li], hidden, hidden, k_out[li]);
+    fill(L.g_gu, x_mid[li], hidden, w_gu[li], post_norm[li], nullptr, act[li], inter, inter, hidden);
+    fill(L.g_down, act[li], inter, w_down[li], nullptr, x_mid[li], x_out[li], hidden, hidden, inter);
+    L.o = (__nv_bfloat16*)o[li];
+    L.rec_state = sp == 1 ? rec_state[li] : nullptr;
+    L.conv_state = sp == 1 ? (__nv_bfloat16*)conv_state[li] : nullptr;
+    L.conv_w = sp == 1 ? (cbf)conv_w[li] : nullptr;
+    L.A_log = sp == 1 ? A_log[li] : nullptr;
+    L.dt_bias = sp == 1 ? dt_bias[li] : nullptr;
+    L.gnorm_w = sp == 1 ? (cbf)gnorm_w[li] : nullptr;
+    L.start_phase = sp;
+    x_prev = x_out[li];
+  }
+  a.n_layers = n_layers; a.seg_slot = seg_slot; a.nk = nk; a.nv = nv; a.dk = dk; a.eps = eps; a.M = M; a.xs_bytes = 0;
+  a.n_barriers = 0; a.trace = g_dl_trace;
   if (world > 1) {
     fill_comm(a.cb, peers, rank, world, max_ctas, slot_floats, epochs, status, spin_limit);
   } else {
     for (int i = 0; i < COMM_MAX_RANKS; ++i) a.cb.peer[i] = nullptr;
     a.cb.rank = 0; a.cb.world = 1; a.cb.max_ctas = 0; a.cb.slot_floats = 0; a.cb.epochs = nullptr; a.cb.status = status;
-    a.cb.spin_limit = 0; a.cb.serial_polls = 0; a.cb.trace = nullptr;
+    a.cb.spin_limit = 0; a.cb.serial_polls = 0;
   }
   a.cb.trace = nullptr;
   a.sync.counter = sync_words; a.sync.base = sync_words + 1; a.sync.status = status;

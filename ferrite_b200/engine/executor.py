@@ -443,16 +443,29 @@ class Executor:
                 and c.n_experts == 0 and c.kv_lora == 0 and isinstance(w["l0.out_proj"], torch.Tensor)
                 and w["l0.out_proj"].dtype == torch.bfloat16 and (self.tp is None or self.tp.world == 1 or self.tp.fused))
         comm = self.tp.comm if (fuse and self.tp is not None and self.tp.world > 1) else None
+        gdn_fusable = fuse and c.lin_dk == c.lin_dv and c.lin_dk in (64, 128) and c.lin_v_heads * T <= ops.sm_count
+        run, run_idx = [], []                 # consecutive layers waiting to go out as one persistent launch
+        run_max = ops.decode_layers_max if fuse else 0
+
+        def flush():
+            nonlocal x, run, run_idx
+            if run:
+                outs = ops.decode_layers(comm, x, run, mv["sslot"], (c.lin_k_heads, c.lin_v_heads, c.lin_dk), eps)
+                self.taps.extend(outs[j] for j, li in enumerate(run_idx) if li in c.tap_layers)
+                x, run, run_idx = outs[-1], [], []
+
+        tail = lambda p: {"w_out": w[p + "out_proj"], "post_norm": w[p + "post_norm"], "w_gu": w[p + "gate_up"], "w_down": w[p + "down"]}
         for i, kind in enumerate(self.kinds):
             p = f"l{i}."
-            if fuse and kind == "gdn" and c.lin_dk == c.lin_dv and c.lin_dk in (64, 128) and c.lin_v_heads * T <= ops.sm_count:
-                x = ops.decode_layer(comm, x, None, w[p + "in_proj"], w[p + "input_norm"], w[p + "out_proj"], w[p + "post_norm"],
-                                     w[p + "gate_up"], w[p + "down"],
-                                     gdn=(self.rec_state[i], self.conv_state[i], w[p + "conv_w"], w[p + "A_log"], w[p + "dt_bias"],
-                                          w[p + "gnorm_w"], mv["sslot"], c.lin_k_heads, c.lin_v_heads, c.lin_dk), eps=eps)
-                if i in c.tap_layers:
-                    self.taps.append(x)
+            if gdn_fusable and kind == "gdn":
+                run.append({"w_in": w[p + "in_proj"], "input_norm": w[p + "input_norm"], "rec": self.rec_state[i],
+                            "conv": self.conv_state[i], "conv_w": w[p + "conv_w"], "A_log": w[p + "A_log"],
+                            "dt_bias": w[p + "dt_bias"], "gnorm_w": w[p + "gnorm_w"], **tail(p)})
+                run_idx.append(i)
+                if len(run) == run_max:
+                    flush()
                 continue
+            flush()                                # everything else reads the rows
             if kind == "gdn":
                 proj = col(x, w[p + "in_proj"], w[p + "input_norm"])
                 if tv is not None:
@@ -533,11 +546,9 @@ class Executor:
                     o = ops.attention(q, proj, self.k_cache[i], self.v_cache[i], mv["slot"], mv["kvlen"],
                                       self.block_table, self.ecfg.kv_block, c.n_q, c.n_kv, c.head_dim, c.attn_gate,
                                       nsplit=nsplit, segs=(mv["sslot"], mv["srow0"], mv["snrows"], max_seg_rows), **kvs)
-                if fuse:
-                    x = ops.decode_layer(comm, x, o, None, None, w[p + "out_proj"], w[p + "post_norm"], w[p + "gate_up"],
-                                         w[p + "down"], eps=eps)
-                    if i in c.tap_layers:
-                        self.taps.append(x)
+                if fuse:                             # the rest of this layer opens the next run
+                    run.append({"o": o, **tail(p)})
+                    run_idx.append(i)
                     continue
                 x = row(o, w[p + "out_proj"], x)
             if c.is_moe(i):
@@ -547,6 +558,7 @@ class Executor:
                 x = row(act, w[p + "down"], x)
             if i in c.tap_layers:
                 self.taps.append(self.tp.gather_rows(x, T) if sp else x)
+        flush()
         return self.tp.gather_rows(x, T) if sp else x
 
     def _head(self, x, mv, nlog, greedy):

@@ -35,6 +35,8 @@ class CudaOps:
         self._ws: Optional[torch.Tensor] = None
         self._counters = torch.zeros(16384, dtype=torch.int32, device=self.device)
         self._dl_sync = torch.zeros(2, dtype=torch.int32, device=self.device)      # grid-barrier words of the persistent layer kernel
+        self._dl_empty = torch.empty(0, dtype=self.dtype, device=self.device)
+        self.decode_layers_max = int(self.C.decode_layers_max())
         self.force_gemv_chunks = False      # debug: run any row count through 8-row GEMV passes
         self.launches = 0                   # kernels launched (or recorded into a graph) through this object
         self.moe_pair_rows = MOE_PAIR_ROWS
@@ -492,28 +494,36 @@ class CudaOps:
                             self._tree_scratch, nk, nv, dk, dv, eps)
         return y
 
-    def decode_layer(self, comm, x, o, w_in, input_norm, w_out, post_norm, w_gu, w_down, gdn=None, eps=1e-6):
-        """The rest of a decoder layer for one-row-per-sequence steps as one persistent kernel (`csrc/decode_layer.cu`).
-        `o` given: out projection + residual, then the MLP block. `o` None: a Gated DeltaNet layer from the hidden rows,
-        `gdn` = (rec_state, conv_state, conv_w, A_log, dt_bias, gnorm_w, seg_slot, nk, nv, dk). `comm`: the tensor-
-        parallel workspace handle (sums over ranks happen inside the kernel) or None."""
+    def decode_layers(self, comm, x, layers, seg_slot=None, heads=(0, 0, 0), eps=1e-6):
+        """A run of consecutive decoder layers for one-row-per-sequence steps as ONE persistent launch
+        (`csrc/decode_layer.cu`). `layers`: dicts with w_out, post_norm, w_gu, w_down and either `o` (the mixer output of a
+        layer whose attention already ran; first layer of the run only) or the Gated DeltaNet operands w_in, input_norm,
+        rec, conv, conv_w, A_log, dt_bias, gnorm_w. `comm`: the tensor-parallel workspace handle (the sums over ranks
+        happen inside the kernel) or None. Returns the output rows of every layer of the run."""
         M, H = x.shape
-        inter = w_down.shape[1]
-        x_out = torch.empty(M, H, dtype=self.dtype, device=self.device)
-        x_mid = torch.empty(M, H, dtype=self.dtype, device=self.device)
-        act = torch.empty(M, inter, dtype=self.dtype, device=self.device)
+        e = self._dl_empty
+        mk = lambda n: torch.empty(M, n, dtype=self.dtype, device=self.device)
+        cols = {k: [] for k in ("sp", "x_out", "x_mid", "act", "proj", "o", "w_in", "inorm", "w_out", "pnorm", "w_gu", "w_down",
+                                "rec", "conv", "conv_w", "A_log", "dt_bias", "gnorm")}
+        for L in layers:
+            gdn = "o" not in L
+            cols["sp"].append(1 if gdn else 3)
+            cols["x_out"].append(mk(H)); cols["x_mid"].append(mk(H)); cols["act"].append(mk(L["w_down"].shape[1]))
+            cols["proj"].append(mk(L["w_in"].shape[0]) if gdn else e)
+            cols["o"].append(mk(L["w_out"].shape[1]) if gdn else L["o"])
+            cols["w_in"].append(L["w_in"] if gdn else e); cols["inorm"].append(L["input_norm"] if gdn else e)
+            cols["w_out"].append(L["w_out"]); cols["pnorm"].append(L["post_norm"]); cols["w_gu"].append(L["w_gu"])
+            cols["w_down"].append(L["w_down"])
+            for k in ("rec", "conv", "conv_w", "A_log", "dt_bias"):
+                cols[k].append(L[k] if gdn else e)
+            cols["gnorm"].append(L["gnorm_w"] if gdn else e)
         self.launches += 1
-        if o is None:
-            rec, conv, conv_w, A_log, dt_bias, gnorm_w, seg_slot, nk, nv, dk = gdn
-            proj = torch.empty(M, w_in.shape[0], dtype=self.dtype, device=self.device)
-            o = torch.empty(M, w_out.shape[1], dtype=self.dtype, device=self.device)
-            self.C.decode_layer(comm, 1, x_out, x_mid, act, proj, o, x, w_in, input_norm, w_out, post_norm, w_gu, w_down,
-                                rec, conv, conv_w, A_log, dt_bias, gnorm_w, seg_slot, nk, nv, dk, eps, self.status_word,
-                                self._dl_sync)
-        else:
-            self.C.decode_layer(comm, 3, x_out, x_mid, act, x_mid, o, x, None, None, w_out, post_norm, w_gu, w_down,
-                                None, None, None, None, None, None, None, 0, 0, 0, eps, self.status_word, self._dl_sync)
-        return x_out
+        nk, nv, dk = heads
+        self.C.decode_layers(comm, cols["sp"], x, cols["x_out"], cols["x_mid"], cols["act"], cols["proj"], cols["o"], cols["w_in"],
+                             cols["inorm"], cols["w_out"], cols["pnorm"], cols["w_gu"], cols["w_down"], cols["rec"], cols["conv"],
+                             cols["conv_w"], cols["A_log"], cols["dt_bias"], cols["gnorm"], seg_slot, nk, nv, dk, eps,
+                             self.status_word, self._dl_sync)
+        return cols["x_out"]
 
     def gdn_step(self, proj, conv_w, rec_state, conv_state, A_log, dt_bias, gnorm_w, seg_slot, seg_row0, seg_nrows, nk, nv,
                  dk, dv, eps, commit=True):

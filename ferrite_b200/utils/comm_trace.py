@@ -50,6 +50,8 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--ctx", type=int, default=512)
     ap.add_argument("--out", default="")
+    ap.add_argument("--fused-layers", default="auto", choices=["auto", "on", "off"],
+                    help="decode rows through the persistent layer kernel (auto = yes under tensor parallelism)")
     args = ap.parse_args()
 
     from .._ext import load
@@ -68,8 +70,9 @@ def main() -> int:
     C = load()
     tp = TensorParallel(dist.group.WORLD, dev)
     cfg = scaled(hybrid_27b(), args.layers)
-    eng = Engine(cfg, None, EngineConfig(n_slots=1, max_ctx=args.ctx + 4 * (args.steps + args.warmup) + 64), device=str(dev),
-                 seed=0, tp=tp)
+    eng = Engine(cfg, None, EngineConfig(n_slots=1, max_ctx=args.ctx + 4 * (args.steps + args.warmup) + 64,
+                                         fused_layers={"auto": None, "on": True, "off": False}[args.fused_layers]),
+                 device=str(dev), seed=0, tp=tp)
     gen = torch.Generator().manual_seed(7)
     prompt = torch.randint(0, cfg.vocab, (args.ctx,), generator=gen).tolist()
     feed = torch.randint(0, cfg.vocab, (8 * (args.steps + args.warmup),), generator=gen).tolist()
@@ -81,8 +84,38 @@ def main() -> int:
     recs, words = C.comm_trace_shape()
     trace = torch.zeros(recs * words, dtype=torch.int64, device=dev)
     C.comm_trace_set(trace)
+    dl = torch.zeros(1024 * 16, dtype=torch.int64, device=dev)
+    C.decode_layer_trace_set(dl)
     ms, pos = _step_ms(eng, feed, pos, args.steps, args.warmup, dev)
     out["step_ms_traced"] = ms
+    C.decode_layer_trace_set(None)
+    d = dl.view(1024, 16).cpu()
+    d = d[d[:, 0] > 0]
+    if d.shape[0] > 8:
+        # phases of the persistent layer kernel (CTA 0), per kind of launch; max over ranks of the per-rank means
+        d = d[torch.argsort(d[:, 0])].double()
+        gap = torch.cat([d[1:, 0] - d[:-1, 11], d[:1, 0] * 0])            # launch start - end of the launch before it
+        gap[gap > 2e5] = float("nan")                                      # (across steps)
+        phases = {}
+        for kind, first, name in ((1, True, "deltanet_layer_first_of_launch"), (1, False, "deltanet_layer_later_in_launch"),
+                                  (3, True, "after_attention")):
+            sel = (d[:, 12] == kind) & ((d[:, 14] == 0) == first)
+            r = d[sel]
+            if r.shape[0] == 0:
+                continue
+            cols = {}
+            if kind == 1:
+                cols.update({"wait_at_entry": r[:, 13] - r[:, 0], "in_proj": r[:, 1] - r[:, 13], "barrier": r[:, 2] - r[:, 1],
+                             "heads": r[:, 3] - r[:, 2], "barrier_2": r[:, 4] - r[:, 3], "out_proj": r[:, 5] - r[:, 4]})
+            else:
+                cols.update({"wait_at_entry": r[:, 13] - r[:, 0], "out_proj": r[:, 5] - r[:, 13]})
+            cols.update({"sum_over_ranks_store": r[:, 6] - r[:, 5], "barrier_3": r[:, 7] - r[:, 6], "gate_up": r[:, 8] - r[:, 7],
+                         "barrier_4": r[:, 9] - r[:, 8], "down": r[:, 10] - r[:, 9], "sum_over_ranks_store_2": r[:, 11] - r[:, 10],
+                         "kernel_total": r[:, 11] - r[:, 0], "gap_before_launch": gap[sel][~torch.isnan(gap[sel])]})
+            means = torch.tensor([float(v.mean()) / 1e3 if v.numel() else 0.0 for v in cols.values()], device=dev)
+            dist.all_reduce(means, op=dist.ReduceOp.MAX)
+            phases[name] = {"launches": int(r.shape[0]), **{k: round(float(v), 2) for k, v in zip(cols, means.tolist())}}
+        out["persistent_layer_kernel_us"] = phases
     t = trace.view(recs, words).cpu()
     t = t[t[:, 6] > 0]
     table = {}

@@ -292,7 +292,7 @@ def test_scheduler_samples_on_the_device(ext):
 
 @pytest.mark.parametrize("streams", [1, 3])
 def test_persistent_decode_layer_matches_the_separate_kernels(ext, streams):
-    """One cooperative kernel per layer (grid barriers between its phases) against the separate-launch path: same
+    """One persistent kernel per layer (grid barriers between its phases) against the separate-launch path: same
     weights, same prompts, decode rows compared step by step (logits to bf16 rounding of the norms' sums, greedy
     picks equal), eager first and then through the CUDA graph."""
     cfg = scaled(hybrid_27b(), 8)                              # 6 Gated DeltaNet layers, 2 attention layers
