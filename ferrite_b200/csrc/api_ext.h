@@ -68,6 +68,7 @@ int fb_gemv_nvfp4_tc(void* Y, const void* X, long ldx, const void* norm_w, float
 
 // ---- decode_layer.cu: one decoder layer of a plain decode step as one persistent kernel ----
 int fb_decode_layers_max();
+int fb_decode_layers_prepare();
 int fb_decode_layers(int n_layers, const int* start_phase, int M, int hidden, const void* x_in, void* const* x_out,
                      void* const* x_mid, void* const* act, void* const* proj, void* const* o, const void* const* w_in,
                      const int* n_in, const void* const* input_norm, const void* const* w_out, const int* k_out,

@@ -30,7 +30,8 @@ __global__ void attn_prep_kernel(__nv_bfloat16* __restrict__ q_out, void* __rest
   pdl_wait();
   constexpr int EPL = HD / 32;
   const int row = blockIdx.x;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // one warp per (q or kv) head; blockIdx.y carries the heads beyond the first 32
+  const int warp = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (warp >= nq + nkv) return;
   const bool is_q = warp < nq;
   const int qw = gated ? 2 * HD : HD;
@@ -418,12 +419,13 @@ static int attn_prep_impl(void* q_out, void* k_cache, void* v_cache, float* kv_s
                           int rows, int nq, int nkv, int hd, int rot, int gated, float eps, int* status, cudaStream_t s,
                           int bits = 8) {
   if (rows <= 0) return 0;
-  int threads = 32 * (nq + nkv);
-  if (threads > 1024) return -1;
+  const int heads = nq + nkv;
+  const int threads = 32 * (heads < 32 ? heads : 32);
+  const int hgroups = (heads + 31) / 32;
   int epl = hd / 32;
   if (rot % 2 || (rot / 2) % epl || ((rot / 2 / epl) & (rot / 2 / epl - 1))) return -3;
 #define FB_PREP(HDV, K8)                                                                                          \
-  launch_pdl(attn_prep_kernel<HDV, K8>, dim3(rows), dim3(threads), (size_t)(0), s, (__nv_bfloat16*)q_out, k_cache, v_cache, \
+  launch_pdl(attn_prep_kernel<HDV, K8>, dim3(rows, hgroups), dim3(threads), (size_t)(0), s, (__nv_bfloat16*)q_out, k_cache, v_cache, \
       kv_scale, (const __nv_bfloat16*)proj, proj_stride, (const __nv_bfloat16*)q_norm,                            \
       (const __nv_bfloat16*)k_norm, inv_freq, row_slot, row_pos, row_cpos, block_table, max_blocks, kv_block, nq, nkv, rot, \
       gated, eps, status)

@@ -56,6 +56,7 @@ void allreduce_oneshot(const Comm& c, Tensor y, Tensor part, c10::optional<Tenso
 // layer does not use (a layer entered after its attention has no input projection and no recurrent state) are empty tensors.
 // comm: a Comm, or None on one GPU.
 int64_t decode_layers_max() { return fb_decode_layers_max(); }
+void decode_layers_prepare() { check(fb_decode_layers_prepare(), "decode_layers_prepare"); }
 
 void decode_layers(pybind11::object comm, std::vector<int64_t> start_phase, Tensor x_in, std::vector<Tensor> x_out,
                    std::vector<Tensor> x_mid, std::vector<Tensor> act, std::vector<Tensor> proj, std::vector<Tensor> o,
@@ -485,6 +486,7 @@ void register_ext(pybind11::module_& m) {
   m.def("make_comm", &make_comm);
   m.def("decode_layers", &decode_layers);
   m.def("decode_layers_max", &decode_layers_max);
+  m.def("decode_layers_prepare", &decode_layers_prepare);
   m.def("decode_layer_trace_set", &decode_layer_trace_set);
   m.def("comm_workspace_bytes", [](int64_t max_ctas, int64_t slot_floats) {
     return (int64_t)fb_comm_workspace_bytes((int)max_ctas, (long)slot_floats);

@@ -12,8 +12,9 @@
 // run inside one launch of one CTA per SM, separated by grid barriers (an atomic counter in global memory
 // with a bounded wait) instead of kernel boundaries. Every phase issues its first weight loads BEFORE it waits at the
 // barrier in front of it, so HBM latency hides behind the barrier. (Asking L2 for the whole next phase's rows with
-// cp.async.bulk.prefetch.L2 while a phase runs was measured too: the step got 11 % slower at tensor-parallel 8.) The two sums over ranks are the same one-shot
-// (value, epoch)-pair exchange over NVLink peer memory that the stand-alone fused GEMV + all-reduce uses, executed by
+// cp.async.bulk.prefetch.L2 while a phase runs was measured too: the step got 11 % slower at tensor-parallel 8.)
+// The two sums over ranks are the same one-shot (value, epoch)-pair exchange over NVLink peer memory that the
+// stand-alone fused GEMV + all-reduce uses, executed by
 // the CTA that owns the rows. Attention layers enter at phase 3 with o computed by the attention kernels.
 //
 // The reference reaches the same end with one CUDA graph per step over separate kernels (`enqueue_layer`,
@@ -259,6 +260,23 @@ static void dl_plan_gemv(GemvArgs& g, int M, int grid) {
   g.rows_per_cta = (g.N + grid - 1) / grid;
 }
 
+constexpr size_t DL_SMEM_MAX = 160 * 1024;
+
+// Attribute set-up and the residency check, once per instantiation and never inside a stream capture (the engine calls
+// fb_decode_layers_prepare when it is built): one CTA of the largest shared-memory size must fit an SM.
+template <int M>
+static int dl_prepare() {
+  static int state = 0;                       // 0: not yet, 1: ready, < 0: error
+  if (state == 0) {
+    auto kern = decode_layer_kernel<M>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DL_SMEM_MAX);
+    int per_sm = 0;
+    if (e == cudaSuccess) e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, DL_THREADS, DL_SMEM_MAX);
+    state = (e == cudaSuccess && per_sm >= 1) ? 1 : -9;
+  }
+  return state == 1 ? 0 : state;
+}
+
 template <int M>
 static int dl_launch(DLArgs& a, int grid, cudaStream_t s) {
   int kc = 0, rpc = 0;
@@ -279,25 +297,18 @@ static int dl_launch(DLArgs& a, int grid, cudaStream_t s) {
   }
   a.xs_bytes = (int)((size_t)M * kc * sizeof(__nv_bfloat16));
   const size_t smem = (size_t)a.xs_bytes + (size_t)M * rpc * sizeof(float);
-  if (smem > 160 * 1024) return -5;
+  if (smem > DL_SMEM_MAX) return -5;
   if (a.cb.world > 1) {
     if (grid > a.cb.max_ctas) return -7;
     if ((long)grid * M * rpc * 2 > a.cb.slot_floats - COMM_TOP_RESERVE) return -8;
   }
   auto kern = decode_layer_kernel<M>;
-  static bool attr_done = false;
-  if (!attr_done) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
-    if (e != cudaSuccess) return (int)e;
-    attr_done = true;
-  }
+  if (int rc = dl_prepare<M>()) return rc;
   // Every CTA waits for every other, so all of them must be resident together: one per SM, checked against what the
   // occupancy calculator allows. (A cooperative launch would have the driver check the same, but measured 15 us from the
   // end of one such launch to the start of the next inside a CUDA graph; a plain launch with programmatic dependent
   // launch lets the next launch's CTAs start, and request their first weights, as SMs free up. CTAs of earlier kernels
   // never wait for this one, so they drain and every CTA of this grid gets its SM; the barrier waits are bounded.)
-  int per_sm = 0;
-  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, DL_THREADS, smem) != cudaSuccess || per_sm < 1) return -9;
   return (int)launch_pdl(kern, dim3(grid), dim3(DL_THREADS), smem, s, a);
 }
 
@@ -311,6 +322,13 @@ static unsigned long long* g_dl_trace = nullptr;
 extern "C" void fb_decode_layer_trace_set(void* buf) { g_dl_trace = (unsigned long long*)buf; }
 
 extern "C" int fb_decode_layers_max() { return DL_MAX_LAYERS; }
+
+// Call once outside any stream capture before the first fb_decode_layers.
+extern "C" int fb_decode_layers_prepare() {
+  if (int rc = dl_prepare<1>()) return rc;
+  if (int rc = dl_prepare<2>()) return rc;
+  return dl_prepare<4>();
+}
 
 // A run of n_layers consecutive decoder layers (<= fb_decode_layers_max()) for M <= 4 one-row sequences. Per layer, in
 // arrays of n_layers entries: start_phase (1: Gated DeltaNet layer from the hidden rows; 3: the rest of a layer whose

@@ -10,6 +10,8 @@ table per slot), and for every Gated DeltaNet layer an fp32 recurrent state plus
 """
 from __future__ import annotations
 
+import contextlib
+import gc
 import math
 from collections import OrderedDict
 from dataclasses import dataclass, field
@@ -20,6 +22,24 @@ import torch
 from ..config import EngineConfig, ModelConfig
 from ..models.weights import Weights
 from ..ops.qweight import QWeight
+
+
+@contextlib.contextmanager
+def capture(g: "torch.cuda.CUDAGraph"):
+    """`torch.cuda.graph(g)` with the garbage collector out of the way. A cycle collection that happens to run while the
+    stream is being captured may free CUDA graphs or memory pools of engines that went out of scope earlier, and those
+    frees are calls the capture forbids: the capture is invalidated and the next launch fails with "operation failed due to
+    a previous error during capture". So unreachable objects are collected before the capture starts and the collector
+    stays off until it ends."""
+    gc.collect()
+    was_on = gc.isenabled()
+    gc.disable()
+    try:
+        with torch.cuda.graph(g):
+            yield
+    finally:
+        if was_on:
+            gc.enable()
 
 
 @dataclass
@@ -627,7 +647,7 @@ class Executor:
             if g is None:
                 g = torch.cuda.CUDAGraph()
                 l0 = self.ops.launches
-                with torch.cuda.graph(g):
+                with capture(g):
                     self._replay_layers(mv, mr)
                 self.commit_graphs[key] = (g, self.ops.launches - l0)
                 self.ops.launches = l0
@@ -745,7 +765,7 @@ class Executor:
             torch.cuda.synchronize(self.device)
             g = torch.cuda.CUDAGraph()
             l0 = self.ops.launches
-            with torch.cuda.graph(g):
+            with capture(g):
                 out = self._run(T, nseg, nlog, max_seg_rows, nsplit, batch.commit, greedy, None, tree)
             n_kernels = self.ops.launches - l0
             self.ops.launches = l0

@@ -37,6 +37,7 @@ class CudaOps:
         self._dl_sync = torch.zeros(2, dtype=torch.int32, device=self.device)      # grid-barrier words of the persistent layer kernel
         self._dl_empty = torch.empty(0, dtype=self.dtype, device=self.device)
         self.decode_layers_max = int(self.C.decode_layers_max())
+        self.C.decode_layers_prepare()      # attributes + residency check now, not inside a graph capture
         self.force_gemv_chunks = False      # debug: run any row count through 8-row GEMV passes
         self.launches = 0                   # kernels launched (or recorded into a graph) through this object
         self.moe_pair_rows = MOE_PAIR_ROWS

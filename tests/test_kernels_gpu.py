@@ -103,7 +103,8 @@ def test_rmsnorm_embed_silu(ops, tops):
     close(ops.silu_mul(gu), tops.silu_mul(gu))
 
 
-@pytest.mark.parametrize("hd,nq,nkv,rot", [(64, 4, 2, 64), (256, 24, 4, 64), (128, 8, 2, 128), (256, 3, 1, 64)])
+@pytest.mark.parametrize("hd,nq,nkv,rot", [(64, 4, 2, 64), (256, 24, 4, 64), (128, 8, 2, 128), (256, 3, 1, 64),
+                                           (128, 32, 8, 128)])          # 40 heads: more than one CTA's 32 warps per row
 def test_attention_paged(ops, tops, hd, nq, nkv, rot):
     kv_block, n_slots, max_blocks = 64, 3, 8
     nb = n_slots * max_blocks
