@@ -19,7 +19,6 @@ from typing import Any, Dict, List, Optional, Tuple
 from aiohttp import web
 
 from ..engine.sampler import Sampling
-from . import pyjson
 from .api import ApiError, ChatRequest, CompletionRequest
 from .engine_api import EngineBase, GenEvent, GenRequest
 from .guard import PhaseGuard
@@ -324,7 +323,7 @@ class Driver:
 
 
 def _sse(obj: Any) -> bytes:
-    return ("data: " + (obj if isinstance(obj, str) else pyjson.dumps(obj)) + "\n\n").encode("utf-8")
+    return ("data: " + (obj if isinstance(obj, str) else json.dumps(obj, ensure_ascii=False)) + "\n\n").encode("utf-8")
 
 
 async def _run(request: web.Request, chat: bool) -> web.StreamResponse:
@@ -363,7 +362,7 @@ async def _run(request: web.Request, chat: bool) -> web.StreamResponse:
     created = int(time.time())
     _capture(st, "request", body, {"id": rid, "path": request.path, "prompt_tokens": len(prep.ids)})
     st.counters["requests"] += 1
-    headers = {"x-sampling-effective": pyjson.dumps(prep.effective)}
+    headers = {"x-sampling-effective": json.dumps(prep.effective, ensure_ascii=False)}
     obj = "chat.completion" if chat else "text_completion"
     try:
         await st.sem.acquire()
@@ -449,7 +448,7 @@ async def _respond(st, request, req, prep, drv, rid, created, headers, obj, chat
                "usage": drv.usage()}
         if drv.timings:
             out["timings"] = drv.timings
-        return web.json_response(out, headers=headers, dumps=pyjson.dumps)
+        return web.json_response(out, headers=headers, dumps=lambda o: json.dumps(o, ensure_ascii=False))
 
 
 def _account(st: AppState, drv: Driver) -> None:

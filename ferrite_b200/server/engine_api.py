@@ -103,8 +103,11 @@ class SchedulerEngine(EngineBase):
 class MockEngine(EngineBase):
     """Scripted replies for protocol tests (reference `MockEngine` / `plan_response`, `crates/fe-server/src/mock.rs`):
     the reply text is planned from the prompt text. Directives inside the last user message:
-      `[[reason:TEXT]]` reasoning block, `[[call:NAME:JSON]]` a tool call, `[[burst:N]]` tokens per event,
-      `[[silent]]` never answers (watchdog test), `[[die]]` reports the engine dead, otherwise echoes the message."""
+      `[[reason:TEXT]]` reasoning block, `[[say:TEXT]]` words before the calls, `[[call:NAME:JSON]]` a tool call in the
+      JSON body form, `[[xcall:NAME:JSON]]` the same call in the XML parameter form, `[[repeat:N:TEXT]]` TEXT N times
+      (long writes, loops), `[[burst:N]]` tokens per event, `[[slow:MS]]` a pause before the first token (slow prefill),
+      `[[silent]]` never answers (watchdog test), `[[die]]` reports the engine dead, otherwise echoes the message.
+      The prompt tokens shared with the previous request's prompt are reported as served from the cache."""
 
     def __init__(self, tokenizer, model_name: str = "mock", max_batch: int = 4, max_len: int = 8192, delay_s: float = 0.0):
         self.tok = tokenizer
@@ -114,6 +117,7 @@ class MockEngine(EngineBase):
         self._running = 0
         self._lock = threading.Lock()
         self.sem = threading.Semaphore(max_batch)
+        self._last_prompt: List[int] = []
 
     def info(self) -> EngineInfo:
         return EngineInfo("mock", self.model_name, self.max_batch, self.max_len, self.tok.vocab_size)
@@ -128,7 +132,7 @@ class MockEngine(EngineBase):
     def plan_response(prompt_text: str) -> Dict[str, Any]:
         import re
         last = prompt_text.rsplit("<|im_start|>user\n", 1)[-1].split("<|im_end|>")[0]
-        plan = {"burst": 1, "silent": "[[silent]]" in last, "die": "[[die]]" in last, "text": ""}
+        plan = {"burst": 1, "silent": "[[silent]]" in last, "die": "[[die]]" in last, "text": "", "slow_ms": 0}
         out = ""
         m = re.search(r"\[\[reason:(.*?)\]\]", last, re.S)
         thinking_open = prompt_text.rstrip().endswith("<think>")
@@ -136,13 +140,29 @@ class MockEngine(EngineBase):
             out += ("" if thinking_open else "<think>\n") + m.group(1) + "\n</think>\n\n"
         elif thinking_open:
             out += "\n</think>\n\n"
-        for name, js in re.findall(r"\[\[call:([^:\]]+):(.*?)\]\]", last, re.S):
-            out += "<tool_call>\n{\"name\": \"" + name + "\", \"arguments\": " + js + "}\n</tool_call>\n"
+        m = re.search(r"\[\[say:(.*?)\]\]", last, re.S)
+        if m:
+            out += m.group(1) + "\n"
+        for kind, name, js in re.findall(r"\[\[(x?call):([^:\]]+):(.*?)\]\]", last, re.S):
+            if kind == "call":
+                out += "<tool_call>\n{\"name\": \"" + name + "\", \"arguments\": " + js + "}\n</tool_call>\n"
+            else:
+                import json as _json
+                out += "<tool_call>\n<function=" + name + ">\n"
+                for k, v in _json.loads(js).items():
+                    out += "<parameter=" + k + ">\n" + (v if isinstance(v, str) else _json.dumps(v, ensure_ascii=False)) + "\n</parameter>\n"
+                out += "</function>\n</tool_call>\n"
+        m = re.search(r"\[\[repeat:(\d+):(.*?)\]\]", last, re.S)
+        if m:
+            out += m.group(2) * int(m.group(1))
         m = re.search(r"\[\[burst:(\d+)\]\]", last)
         if m:
             plan["burst"] = int(m.group(1))
+        m = re.search(r"\[\[slow:(\d+)\]\]", last)
+        if m:
+            plan["slow_ms"] = int(m.group(1))
         plain = re.sub(r"\[\[.*?\]\]", "", last, flags=re.S).strip()
-        if plain and "[[call:" not in last:
+        if plain and "call:" not in last and "[[repeat:" not in last:
             out += "echo: " + plain
         plan["text"] = out
         return plan
@@ -165,6 +185,15 @@ class MockEngine(EngineBase):
                         time.sleep(0.01)
                     sink(GenEvent("finish", reason="cancelled"))
                     return
+                with self._lock:                       # a one-entry prefix cache: what the prompt shares with the last one
+                    cached = 0
+                    for a, b in zip(req.ids, self._last_prompt):
+                        if a != b:
+                            break
+                        cached += 1
+                    self._last_prompt = list(req.ids)
+                if plan["slow_ms"]:
+                    req.cancel.wait(plan["slow_ms"] / 1e3)
                 ids = self.tok.encode(plan["text"])[:req.sampling.max_tokens]
                 t0 = time.time()
                 reason = "stop" if len(ids) < req.sampling.max_tokens else "length"
@@ -183,7 +212,7 @@ class MockEngine(EngineBase):
                     if self.delay:
                         time.sleep(self.delay)
                 sink(GenEvent("finish", reason=reason, timings={
-                    "prompt_n": len(req.ids), "cache_n": 0, "prompt_ms": 0.0, "predicted_n": len(ids),
+                    "prompt_n": len(req.ids), "cache_n": min(cached, max(0, len(req.ids) - 1)), "prompt_ms": 0.0, "predicted_n": len(ids),
                     "predicted_ms": 1e3 * (time.time() - t0)}))
             finally:
                 with self._lock:

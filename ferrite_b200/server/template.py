@@ -10,7 +10,6 @@ from typing import Any, Dict, List, Optional
 import jinja2
 from jinja2.sandbox import ImmutableSandboxedEnvironment
 
-from . import pyjson
 
 DEFAULT_TEMPLATE = r"""{%- if tools %}
 {{- '<|im_start|>system\n' }}
@@ -70,7 +69,7 @@ def _content_text(c: Any) -> str:
 class ChatTemplate:
     def __init__(self, source: Optional[str] = None):
         self.env = ImmutableSandboxedEnvironment(trim_blocks=True, lstrip_blocks=True, extensions=["jinja2.ext.loopcontrols"])
-        self.env.filters["tojson"] = lambda v, indent=None, ensure_ascii=False: pyjson.dumps(v, indent=indent, ensure_ascii=ensure_ascii)
+        self.env.filters["tojson"] = lambda v, indent=None, ensure_ascii=False: json.dumps(v, indent=indent, ensure_ascii=ensure_ascii)
         self.env.globals["raise_exception"] = _raise
         self.env.globals["strftime_now"] = lambda fmt: datetime.datetime.now().strftime(fmt)
         self.source = source or DEFAULT_TEMPLATE

@@ -41,7 +41,7 @@ def test_conformance_suite_passes_on_the_mock_server(capsys):
     from ferrite_b200.tools.conformance import main
     url, loop = _serve()
     try:
-        rc = main(["--base-url", url, "--mock"])
+        rc = main(["--base-url", url, "--mock", "--tier", "all"])
     finally:
         loop.call_soon_threadsafe(loop.stop)
     out = capsys.readouterr().out
