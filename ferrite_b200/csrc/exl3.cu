@@ -87,68 +87,123 @@ __device__ __forceinline__ float exl3_mul1(uint32_t state) {
   return __half2float(v);
 }
 
-constexpr int EXL3_KC = 4096;        // k values of xh staged per pass (fp16, up to 8 rows: 64 KB)
+// ---- few-row GEMV on mma.sync fragments ---------------------------------------------------------------------------
+// The trellis tile layout IS a tensor-core fragment layout: lane l's eight weights of a 16 x 16 tile sit at k rows
+// 2 (l & 3) + {0, 1} + {0, 8} and columns (l >> 2) + {0, 8}, which are the four A registers of mma.m16n8k16 when the tile
+// is read as W^T [16 columns][16 k]. So a lane decodes its eight codes straight into four f16x2 registers and one
+// mma.sync multiplies the tile with up to eight activation rows (the B operand, from shared memory), fp32 accumulation.
+// No weight is converted to fp32 and no conversion instruction is issued at all: 1024 + s as f16 is the bit pattern
+// 0x6400 + s (s <= 1020 keeps the exponent), two of them are packed into one word and one HFMA2 applies the codebook's
+// affine map to both. With 4 bits per weight a tile is 32 words, one per lane; the 16-bit window of a code is a funnel
+// shift over the lane's word and its left neighbour's (one shuffle per tile). Four tiles per warp are in flight.
+__device__ __forceinline__ uint32_t exl3_pair_f16x2(uint32_t st0, uint32_t st1) {
+  // byte sum of the scrambled state, started at 0x6400: the f16 bit pattern of 1024 + s
+  const uint32_t h0 = __dp4a(st0 * 0x83DCD12Du, 0x01010101u, 0x6400u);
+  const uint32_t h1 = __dp4a(st1 * 0x83DCD12Du, 0x01010101u, 0x6400u);
+  const uint32_t packed = __byte_perm(h0, h1, 0x5410);
+  const __half2 v = __hfma2(*reinterpret_cast<const __half2*>(&packed), __half2half2(__ushort_as_half((unsigned short)0x1EEE)),
+                            __half2half2(__ushort_as_half((unsigned short)0xC931)));
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
 
-// grid = n / 16 column tiles; 8 warps split the k tiles of every pass
-template <int M>
-__global__ void __launch_bounds__(256) exl3_gemv_kernel(float* __restrict__ z, const float* __restrict__ xh,
-                                                        const unsigned short* __restrict__ trellis, int rows, int k,
-                                                        int n, int bits) {
-  extern __shared__ __align__(16) unsigned char smem_exl3[];
-  __half* xs = reinterpret_cast<__half*>(smem_exl3);                               // [M][EXL3_KC]
-  uint32_t* wbuf = reinterpret_cast<uint32_t*>(smem_exl3 + (size_t)M * EXL3_KC * 2);   // [8 warps][64 words]
-  float* part = reinterpret_cast<float*>(wbuf + 8 * 64);                            // [8 warps][M][16]
+__device__ __forceinline__ void exl3_mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// the B fragment of k tile kt for this lane: activation row g (zero beyond `rows`), k = 16 kt + 2t + {0, 1} and + {8, 9};
+// the rotated activations are a few KB that every CTA reads: they stay in L1 / L2, no staging pass
+__device__ __forceinline__ void exl3_bfrag(uint32_t& b0, uint32_t& b1, const float* __restrict__ xh, int rows, int k, int kt,
+                                           int g, int t) {
+  b0 = 0u; b1 = 0u;
+  if (g < rows) {
+    const float* xr = xh + (size_t)g * k + kt * 16 + 2 * t;
+    const float2 lo = __ldg(reinterpret_cast<const float2*>(xr));
+    const float2 hi = __ldg(reinterpret_cast<const float2*>(xr + 8));
+    const __half2 hlo = __float22half2_rn(lo), hhi = __float22half2_rn(hi);
+    b0 = *reinterpret_cast<const uint32_t*>(&hlo);
+    b1 = *reinterpret_cast<const uint32_t*>(&hhi);
+  }
+}
+
+// grid = n / 16 column tiles; the 8 warps of a CTA split the k tiles.
+template <bool BITS4>
+__global__ void __launch_bounds__(256) exl3_gemv_mma_kernel(float* __restrict__ z, const float* __restrict__ xh,
+                                                            const unsigned short* __restrict__ trellis, int rows, int k,
+                                                            int n, int bits) {
+  __shared__ float part[8 * 16 * 8];                         // [8 warps][16 columns][8 rows]
+  __shared__ uint32_t wbuf[8 * 64];                          // [8 warps][64 words] (bits != 4)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
   const int nt = blockIdx.x, n_tiles = n / 16;
   const int n_words = 8 * bits;
-  uint32_t* my_words = wbuf + warp * 64;
-  float acc[M][2];
+  float d[4] = {0.f, 0.f, 0.f, 0.f};
+  const int ntile = k / 16;
+  const uint32_t* tiles = reinterpret_cast<const uint32_t*>(trellis) + (size_t)nt * n_words;
+  const size_t tstride = (size_t)n_tiles * n_words;          // words between consecutive k tiles
+  if (BITS4) {
+    constexpr int DEPTH = 4;
+    uint32_t nxt[DEPTH];
 #pragma unroll
-  for (int m = 0; m < M; ++m) { acc[m][0] = 0.f; acc[m][1] = 0.f; }
-  int rr[8];
-#pragma unroll
-  for (int j = 0; j < 8; ++j) rr[j] = 2 * (lane & 3) + (j & 1) + 8 * ((j >> 1) & 1);
-  for (int kc = 0; kc < k; kc += EXL3_KC) {
-    const int kn = min(EXL3_KC, k - kc);
-    __syncthreads();
-    for (int i = threadIdx.x; i < M * kn; i += blockDim.x) {
-      const int m = i / kn, kk = i % kn;
-      xs[m * EXL3_KC + kk] = __float2half_rn(m < rows ? xh[(size_t)m * k + kc + kk] : 0.f);
+    for (int u = 0; u < DEPTH; ++u) {
+      const int kt = warp + 8 * u;
+      nxt[u] = kt < ntile ? __ldg(tiles + (size_t)kt * tstride + lane) : 0u;
     }
-    __syncthreads();
-    for (int kt = warp; kt < kn / 16; kt += 8) {
-      const unsigned short* tile = trellis + ((size_t)((kc >> 4) + kt) * n_tiles + nt) * (16 * bits);
-      __syncwarp();
-      for (int w = lane; w < n_words; w += 32) my_words[w] = (uint32_t)tile[2 * w] | ((uint32_t)tile[2 * w + 1] << 16);
-      __syncwarp();
+    for (int kt0 = warp; kt0 < ntile; kt0 += 8 * DEPTH) {
+      uint32_t cur[DEPTH];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const float wv = exl3_mul1(exl3_window(my_words, n_words, (lane * 8 + j + 1) * bits));
-        const int krow = kt * 16 + rr[j];
+      for (int u = 0; u < DEPTH; ++u) {
+        cur[u] = nxt[u];
+        const int ktn = kt0 + 8 * (u + DEPTH);
+        nxt[u] = ktn < ntile ? __ldg(tiles + (size_t)ktn * tstride + lane) : 0u;
+      }
 #pragma unroll
-        for (int m = 0; m < M; ++m) acc[m][j >> 2] = fmaf(__half2float(xs[m * EXL3_KC + krow]), wv, acc[m][j >> 2]);
+      for (int u = 0; u < DEPTH; ++u) {
+        const int kt = kt0 + 8 * u;
+        if (kt < ntile) {                                    // uniform over the warp
+          const uint32_t prev = __shfl_sync(0xffffffffu, cur[u], (lane + 31) & 31);
+          uint32_t st[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) st[j] = __funnelshift_r(cur[u], prev, 28 - 4 * j) & 0xFFFFu;
+          // A registers: (col g, k 2t..2t+1), (col g + 8, same k), (col g, k + 8), (col g + 8, k + 8)
+          const uint32_t a[4] = {exl3_pair_f16x2(st[0], st[1]), exl3_pair_f16x2(st[4], st[5]),
+                                 exl3_pair_f16x2(st[2], st[3]), exl3_pair_f16x2(st[6], st[7])};
+          uint32_t b0, b1;
+          exl3_bfrag(b0, b1, xh, rows, k, kt, g, t);
+          exl3_mma(d, a, b0, b1);
+        }
       }
     }
-  }
-  // lanes sharing lane>>2 hold the 16 rows of the same two columns
+  } else {
+    uint32_t* my_words = wbuf + warp * 64;
+    for (int kt = warp; kt < ntile; kt += 8) {
+      __syncwarp();
+      for (int w = lane; w < n_words; w += 32) my_words[w] = __ldg(tiles + (size_t)kt * tstride + w);
+      __syncwarp();
+      uint32_t st[8];
 #pragma unroll
-  for (int m = 0; m < M; ++m) {
-#pragma unroll
-    for (int c = 0; c < 2; ++c) {
-      float v = acc[m][c];
-      v += __shfl_xor_sync(0xffffffffu, v, 1);
-      v += __shfl_xor_sync(0xffffffffu, v, 2);
-      if ((lane & 3) == 0) part[(warp * M + m) * 16 + (lane >> 2) + 8 * c] = v;
+      for (int j = 0; j < 8; ++j) st[j] = exl3_window(my_words, n_words, (lane * 8 + j + 1) * bits);
+      const uint32_t a[4] = {exl3_pair_f16x2(st[0], st[1]), exl3_pair_f16x2(st[4], st[5]),
+                             exl3_pair_f16x2(st[2], st[3]), exl3_pair_f16x2(st[6], st[7])};
+      uint32_t b0, b1;
+      exl3_bfrag(b0, b1, xh, rows, k, kt, g, t);
+      exl3_mma(d, a, b0, b1);
     }
   }
+  // D fragment: rows = columns of the tile (g, g + 8), columns = activation rows (2t, 2t + 1)
+  float* mine = part + warp * 128;
+  mine[g * 8 + 2 * t] = d[0]; mine[g * 8 + 2 * t + 1] = d[1];
+  mine[(g + 8) * 8 + 2 * t] = d[2]; mine[(g + 8) * 8 + 2 * t + 1] = d[3];
   __syncthreads();
-  for (int i = threadIdx.x; i < M * 16; i += blockDim.x) {
-    const int m = i / 16, c = i % 16;
+  for (int i = threadIdx.x; i < 128; i += blockDim.x) {
+    const int c = i >> 3, m = i & 7;
     if (m >= rows) continue;
-    float s = 0.f;
+    float sum = 0.f;
 #pragma unroll
-    for (int w = 0; w < 8; ++w) s += part[(w * M + m) * 16 + c];
-    z[(size_t)m * n + nt * 16 + c] = s;
+    for (int w = 0; w < 8; ++w) sum += part[w * 128 + i];
+    z[(size_t)m * n + nt * 16 + c] = sum;
   }
 }
 
@@ -196,20 +251,9 @@ extern "C" int fb_exl3_gemv(float* z, const float* xh, const void* trellis, int 
                             cudaStream_t s) {
   if (rows <= 0) return 0;
   if (rows > 8 || k % 16 || n % 16 || bits < 1 || bits > 8) return -1;
-  const int M = rows <= 1 ? 1 : rows <= 2 ? 2 : rows <= 4 ? 4 : 8;
-  const size_t smem = (size_t)M * EXL3_KC * 2 + 8 * 64 * 4 + (size_t)8 * M * 16 * 4;
-#define FB_EX(MT)                                                                                                   \
-  do {                                                                                                              \
-    static bool done = false;                                                                                       \
-    if (!done) {                                                                                                    \
-      cudaError_t e = cudaFuncSetAttribute(exl3_gemv_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024); \
-      if (e != cudaSuccess) return (int)e;                                                                          \
-      done = true;                                                                                                  \
-    }                                                                                                               \
-    exl3_gemv_kernel<MT><<<n / 16, 256, smem, s>>>(z, xh, (const unsigned short*)trellis, rows, k, n, bits);        \
-  } while (0)
-  if (M == 1) FB_EX(1); else if (M == 2) FB_EX(2); else if (M == 4) FB_EX(4); else FB_EX(8);
-#undef FB_EX
+  if (((uintptr_t)trellis & 3)) return -1;
+  if (bits == 4) exl3_gemv_mma_kernel<true><<<n / 16, 256, 0, s>>>(z, xh, (const unsigned short*)trellis, rows, k, n, bits);
+  else exl3_gemv_mma_kernel<false><<<n / 16, 256, 0, s>>>(z, xh, (const unsigned short*)trellis, rows, k, n, bits);
   return (int)cudaGetLastError();
 }
 

@@ -83,7 +83,7 @@ class Engine:
             from ..formats.exl3 import Exl3Tensor
             from ..formats.packed import PackedEXL3
             from ..ops.qweight import from_packed
-            bits = int(self.ecfg.weight_dtype[-1]) if self.ecfg.weight_dtype[-1].isdigit() else 4
+            bits = int(self.ecfg.weight_dtype.split("-")[1]) if "-" in self.ecfg.weight_dtype else 4
             big = ("in_proj", "out_proj", "gate_up", "down")
             for j, k in enumerate(list(weights.keys())):
                 t = weights[k]

@@ -6,6 +6,8 @@ against a stored bf16 reference).
 
 Prints one JSON line: mean / max per-position KL(bf16 || quantised) in nats over `--tokens` positions of a seeded
 uniform-random prompt, and the top-1 agreement. Both engines are built from the same seeded random-init weights.
+`--ref dequantised` scores against a bf16 engine over the DEQUANTISED weights (kernel + activation error only, the
+quantisation error of the weights themselves taken out); `--rows decode` scores one-row decode steps.
 """
 from __future__ import annotations
 
@@ -27,6 +29,9 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="cut the model to this many layers (0 = all)")
     ap.add_argument("--dtype", default="nvfp4", choices=["nvfp4", "nvfp4-a16", "fp8-block", "bf16"])
     ap.add_argument("--kv", default="bf16", choices=["bf16", "fp8", "int4"], help="KV cache format of the tested engine")
+    ap.add_argument("--ref", default="bf16", choices=["bf16", "dequantised"],
+                    help="reference engine: bf16 on the original weights, or bf16 on the dequantised weights of the tested engine")
+    ap.add_argument("--rows", default="prefill", choices=["prefill", "decode"], help="score prompt chunks or one-row decode steps")
     ap.add_argument("--tokens", type=int, default=512)
     ap.add_argument("--seed", type=int, default=0)
     a = ap.parse_args()
@@ -41,19 +46,38 @@ def main():
     w = init_weights(cfg, seed=a.seed, dtype=torch.bfloat16, device=dev)
     prompt = torch.randint(0, cfg.vocab, (a.tokens,), generator=torch.Generator().manual_seed(99)).tolist()
     outs = {}
-    for name, dt, kv in (("ref", "bf16", "bf16"), ("test", a.dtype, a.kv)):
-        eng = Engine(cfg, dict(w), EngineConfig(n_slots=1, max_ctx=a.tokens + 64, weight_dtype=dt, kv_dtype=kv), device=dev)
+
+    def logits_of(eng):
+        if a.rows == "decode":
+            # one row per step: the few-row kernels (what a decode step runs) instead of the prompt GEMMs
+            rows = []
+            for i, t in enumerate(prompt):
+                lg, _, _ = eng.forward([Segment(0, i, [t], "last")], greedy=False)
+                rows.append(lg.float().cpu())
+            return torch.cat(rows)
         # two chunks, so the second one reads the first through the (possibly quantised) cache
         half = a.tokens // 2
         l1, _, _ = eng.forward([Segment(0, 0, prompt[:half], "all")], greedy=False)
         l1 = l1.float().cpu()
         l2, _, _ = eng.forward([Segment(0, half, prompt[half:], "all")], greedy=False)
-        outs[name] = torch.cat([l1, l2.float().cpu()])
-        del eng
-        torch.cuda.empty_cache()
+        return torch.cat([l1, l2.float().cpu()])
+
+    eng = Engine(cfg, dict(w), EngineConfig(n_slots=1, max_ctx=a.tokens + 64, weight_dtype=a.dtype, kv_dtype=a.kv), device=dev)
+    outs["test"] = logits_of(eng)
+    if a.ref == "dequantised":
+        # the reference multiplies the very values the codes stand for (the dequantised copies the quantised engine keeps),
+        # in bf16 on the 16-bit kernels: what is left is the error of the quantised kernels and of their activation handling
+        from ..ops.qweight import QWeight
+        w = {k: (v.dense if isinstance(v, QWeight) else v) for k, v in eng.ex.w.items() if isinstance(v, (torch.Tensor, QWeight))}
+    del eng
+    torch.cuda.empty_cache()
+    eng = Engine(cfg, dict(w), EngineConfig(n_slots=1, max_ctx=a.tokens + 64), device=dev)
+    outs["ref"] = logits_of(eng)
+    del eng
+    torch.cuda.empty_cache()
     kl = kl_rows(outs["ref"], outs["test"])
     agree = (outs["ref"].argmax(-1) == outs["test"].argmax(-1)).float().mean().item()
-    print(json.dumps({"model": cfg.name, "layers": cfg.n_layers, "dtype": a.dtype, "kv": a.kv, "positions": a.tokens,
+    print(json.dumps({"model": cfg.name, "layers": cfg.n_layers, "dtype": a.dtype, "kv": a.kv, "reference": a.ref, "rows": a.rows, "positions": a.tokens,
                       "kl_mean": kl.mean().item(), "kl_max": kl.max().item(), "top1_agreement": agree,
                       "data": "seeded uniform-random prompt, random-init weights N(0, 0.02)"}))
 

@@ -140,10 +140,11 @@ def bench_linear(ops, t, m, n, k, swiglu=False, norm=False, res=False, label=Non
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemv", "gemm", "layer", "attn_decode", "attn_prefill", "gdn", "moe"])
+    ap.add_argument("what", choices=["gemv", "gemm", "layer", "attn_decode", "attn_prefill", "gdn", "moe", "exl3"])
     ap.add_argument("--m", type=int, default=1)
     ap.add_argument("--n", type=int, default=5120)
     ap.add_argument("--k", type=int, default=5120)
+    ap.add_argument("--bits", type=int, default=4, help="exl3: bits per weight")
     ap.add_argument("--ctx", type=int, default=2048)
     ap.add_argument("--splits", type=int, default=0, help="attn_decode: key splits (0 = by context length)")
     ap.add_argument("--swiglu", action="store_true")
@@ -171,6 +172,28 @@ def main():
     ops.fp4_act = a.fp4 and not a.a16
     ops.fp4_terms, ops.fp4_tc_ctas, ops.fp4_prefetch_mb = a.terms, a.ctas, a.prefetch
     t = Timer(dev, a.warmup, a.iters, flush=not a.no_flush, graph=a.graph, trace=a.trace, hot=a.hot)
+    if a.what == "exl3":
+        # the three kernels of an EXL3 linear for few rows: input rotation, trellis GEMV, output rotation (+ residual)
+        from ..formats.exl3 import Exl3Tensor
+        from ..ops.exl3_linear import HAD, Exl3Linear
+        nbytes = a.k * a.n * a.bits // 8
+        reps = max(2, min(12, -(-(300 << 20) // nbytes)))
+        lins = [Exl3Linear(Exl3Tensor.random(a.k, a.n, a.bits, seed=i), dev) for i in range(reps)]
+        x = rnd(a.m, a.k)
+        xh = torch.empty(a.m, a.k, dtype=torch.float32, device=dev)
+        z = torch.empty(a.m, a.n, dtype=torch.float32, device=dev)
+        y = torch.empty(a.m, a.n, dtype=torch.bfloat16, device=dev)
+        t.flush = False
+        C = ops.C
+        state = [0]
+
+        def gemv():
+            state[0] = (state[0] + 1) % reps                       # weight copies larger than L2 together
+            C.exl3_gemv(z, xh, lins[state[0]].trellis, a.bits)
+        report(f"exl3 input rotation m{a.m} k{a.k}", t.run(lambda: C.exl3_had(xh, x, lins[0].suh, None, None, HAD)), a.m * a.k * 6, 0)
+        report(f"exl3 trellis gemv m{a.m} n{a.n} k{a.k} {a.bits}bpw", t.run(gemv), nbytes, 2.0 * a.m * a.n * a.k)
+        report(f"exl3 output rotation m{a.m} n{a.n}", t.run(lambda: C.exl3_had(y, z, None, lins[0].svh, None, HAD)), a.m * a.n * 6, 0)
+        return
     if a.what == "gemm" and a.fp8b:
         x = rnd(a.m, a.k)
         wq, ws = ops.quantize_weight_fp8_block(rnd(a.n, a.k, scale=0.05))
