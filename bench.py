@@ -289,9 +289,9 @@ def main():
     if not args.no_extras and args.streams == 1:
         # decode from the other weight format (bf16 <-> NVFP4 weights with 16-bit activations), same measurement
         # "nvfp4": packed weights on the block-scaled tensor cores, activations as residual NVFP4 terms;
-        # "nvfp4-a16": the same weights through the SIMT dequantising GEMV
+        # "nvfp4-a16": the same weights through the SIMT dequantising GEMV; "exl3": 4 bpw trellis codes (synthetic tensors)
         del eng
-        for other in [d for d in ("bf16", "nvfp4", "nvfp4-a16") if d != args.dtype]:
+        for other in [d for d in ("bf16", "nvfp4", "nvfp4-a16", "exl3") if d != args.dtype]:
             torch.cuda.empty_cache()
             eng2 = build(other)
             eng2.prefill(0, prompts[0])

@@ -245,7 +245,7 @@ class EngineConfig:
     max_ctx: int = 4096
     kv_block: int = 64                 # tokens per KV page
     kv_dtype: str = "bf16"             # "bf16" | "fp8"
-    weight_dtype: str = "bf16"         # "bf16" | "nvfp4" | "nvfp4-a16" | "fp8-block" (e4m3, 128 x 128 blocks)
+    weight_dtype: str = "bf16"         # "bf16" | "nvfp4" | "nvfp4-w4a4" | "nvfp4-a16" | "fp8-block" (e4m3, 128 x 128 blocks) | "exl3[-bits]"
     prefill_chunk: int = 2048          # rows per prompt forward (reference FERRITE_CHUNK)
     prompt_align: int = 32             # chunk cuts land on this grid (reference PROMPT_ALIGN)
     max_step_rows: int = 4096

@@ -59,7 +59,7 @@ class Engine:
                 if is_packed(weights[k]):
                     weights[k] = from_packed(weights[k], self.device, self.dtype, on_gpu)
         is_t = lambda v: isinstance(v, torch.Tensor)
-        if self.ecfg.weight_dtype in ("nvfp4", "nvfp4-a16"):
+        if self.ecfg.weight_dtype in ("nvfp4", "nvfp4-a16", "nvfp4-w4a4"):
             from ..ops.qweight import quantize_experts, quantize_weight
             big = ("in_proj", "out_proj", "gate_up", "down", "lm_head")
             for k in list(weights.keys()):
@@ -95,7 +95,7 @@ class Engine:
                         p = PackedStack([p, t[main:].cpu()])
                     weights[k] = from_packed(p, self.device, self.dtype, on_gpu)
         elif self.ecfg.weight_dtype != "bf16":
-            raise ValueError(f"weight_dtype {self.ecfg.weight_dtype!r}: expected bf16, nvfp4, nvfp4-a16, fp8-block or exl3")
+            raise ValueError(f"weight_dtype {self.ecfg.weight_dtype!r}: expected bf16, nvfp4, nvfp4-a16, nvfp4-w4a4, fp8-block or exl3[-bits]")
         self.cfg = cfg.shard(world)
         if on_gpu:
             from ..ops.cuda_ops import CudaOps
@@ -103,10 +103,13 @@ class Engine:
         else:
             from ..ops.torch_ops import TorchOps
             ops = TorchOps(self.device, self.dtype)
-        # "nvfp4": weights and activations in NVFP4 on the block-scaled tcgen05 GEMM for every row count;
-        # "nvfp4-a16": NVFP4 weights against 16-bit activations (SIMT GEMV for decode rows, dense copy for prompts)
+        # "nvfp4": few-row steps multiply the packed weights on the block-scaled tensor cores with the activations expanded
+        #   into residual NVFP4 renderings (16-bit-activation accuracy); prompt-sized steps take the dequantised copy;
+        # "nvfp4-w4a4": weights and activations in NVFP4 for every row count (prompt rows: one rendering);
+        # "nvfp4-a16": NVFP4 weights against 16-bit activations on the SIMT GEMV for decode rows, dense copy for prompts
         if on_gpu:
-            ops.fp4_act = self.ecfg.weight_dtype == "nvfp4"
+            ops.fp4_act = self.ecfg.weight_dtype in ("nvfp4", "nvfp4-w4a4")
+            ops.fp4_prompt = self.ecfg.weight_dtype == "nvfp4-w4a4"
         self.ops = ops
         self.tp = tp
         if tp is not None and tp.world > 1 and self.ecfg.seq_parallel and tp.sp_max is None:

@@ -49,6 +49,7 @@ class CudaOps:
         self._expert_scratch = {}
         self._kv_scratch = None
         self.fp4_act = False                # NVFP4 weights: quantise activations too and use the tcgen05 GEMM
+        self.fp4_prompt = False             # ... for prompt-sized steps too (one NVFP4 rendering per activation row)
         self.fp4_terms = 3                  # few-row NVFP4 steps: NVFP4 renderings per activation row (0 = older fused kernel)
         self.fp4_tc_ctas = 1                # ... and CTAs per SM of that kernel
         self.fp4_prefetch_mb = 48           # ... and how much of the next weight (`QWeight.next`) it asks L2 for as it drains
@@ -147,7 +148,8 @@ class CudaOps:
             if (self.fp4_act and self.fp4_terms > 0 and M <= 8 and w.mma_scales is not None and w.cols % 256 == 0
                     and (not swiglu or N % 128 == 0) and out is None):
                 return self._linear_w4_tc(x, w, norm_w, eps, res, swiglu, M, N, out_f32)
-            if (self.fp4_act and w.row_alpha is None and w.mma_scales is not None and w.cols % 256 == 0 and (not out_f32 or M <= 8)
+            if (self.fp4_act and (self.fp4_prompt or (M <= 8 and self.fp4_terms == 0)) and w.row_alpha is None
+                    and w.mma_scales is not None and w.cols % 256 == 0 and (not out_f32 or M <= 8)
                     and (not swiglu or N % 128 == 0) and (M <= 64 or N % 8 == 0)):
                 return self._linear_w4a4(x, w, norm_w, eps, res, swiglu, M, N, out_f32)
             if M <= GEMV_MAX_ROWS and not self.force_gemv_chunks:

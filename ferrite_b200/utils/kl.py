@@ -27,7 +27,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--model", default="27b")
     ap.add_argument("--layers", type=int, default=0, help="cut the model to this many layers (0 = all)")
-    ap.add_argument("--dtype", default="nvfp4", choices=["nvfp4", "nvfp4-a16", "fp8-block", "bf16"])
+    ap.add_argument("--dtype", default="nvfp4", choices=["nvfp4", "nvfp4-w4a4", "nvfp4-a16", "fp8-block", "exl3", "bf16"])
     ap.add_argument("--kv", default="bf16", choices=["bf16", "fp8", "int4"], help="KV cache format of the tested engine")
     ap.add_argument("--ref", default="bf16", choices=["bf16", "dequantised"],
                     help="reference engine: bf16 on the original weights, or bf16 on the dequantised weights of the tested engine")
@@ -68,7 +68,14 @@ def main():
         # the reference multiplies the very values the codes stand for (the dequantised copies the quantised engine keeps),
         # in bf16 on the 16-bit kernels: what is left is the error of the quantised kernels and of their activation handling
         from ..ops.qweight import QWeight
-        w = {k: (v.dense if isinstance(v, QWeight) else v) for k, v in eng.ex.w.items() if isinstance(v, (torch.Tensor, QWeight))}
+
+        def dense_of(v):
+            if isinstance(v, torch.Tensor):
+                return v
+            if isinstance(v, QWeight) and v.dense is not None:
+                return v.dense
+            return v.dequantize(torch.bfloat16).to(dev)          # EXL3 / GGUF / stacked parts: host decode of the codes
+        w = {k: dense_of(v) for k, v in eng.ex.w.items() if isinstance(v, torch.Tensor) or hasattr(v, "dequantize") or isinstance(v, QWeight)}
     del eng
     torch.cuda.empty_cache()
     eng = Engine(cfg, dict(w), EngineConfig(n_slots=1, max_ctx=a.tokens + 64), device=dev)

@@ -71,7 +71,7 @@ def test_nvfp4_w4a4_engine_tracks_the_16bit_activation_path(ext):
     NVFP4-weight / 16-bit-activation engine on the same weights (activation quantisation noise only)."""
     cfg = scaled(hybrid_27b(), 2)
     a = Engine(cfg, None, EngineConfig(n_slots=1, max_ctx=256, weight_dtype="nvfp4-a16"), device="cuda", seed=5)
-    b = Engine(cfg, None, EngineConfig(n_slots=1, max_ctx=256, weight_dtype="nvfp4"), device="cuda", seed=5)
+    b = Engine(cfg, None, EngineConfig(n_slots=1, max_ctx=256, weight_dtype="nvfp4-w4a4"), device="cuda", seed=5)
     prompt = _prompt(cfg, 40)
     la, _, _ = a.forward([Segment(0, 0, prompt, "last")])
     lb, _, _ = b.forward([Segment(0, 0, prompt, "last")])

@@ -13,6 +13,7 @@ def ops(ext):
     from ferrite_b200.ops.cuda_ops import CudaOps
     o = CudaOps(DEV)
     o.fp4_act = True
+    o.fp4_prompt = True      # block-scaled kernels for every row count
     o.fp4_terms = 0          # the tests below pin the single-rendering (W4A4) kernels; the few-row kernel has its own
     return o
 
@@ -193,12 +194,12 @@ def test_few_row_kernel_row_scales(ops_tc):
     assert ops.status() == 0
 
 
-@pytest.mark.parametrize("mode", ["bf16", "nvfp4"])
+@pytest.mark.parametrize("mode", ["bf16", "nvfp4", "nvfp4-w4a4"])
 def test_engine_from_a_modelopt_nvfp4_checkpoint(ext, tmp_path, mode):
     """A ModelOpt NVFP4 checkpoint goes from file to kernels packed: decode rows stream the codes through the NVFP4
     GEMV with one tensor scale per output row (fused q|k|v and gate|up parts bring their own `weight_scale_2`), prompt
-    rows take the dequantised copy (or, with weight_dtype nvfp4, the block-scaled tensor-core GEMM where a single tensor
-    scale allows it). Logits match the fp32 oracle over the dequantised weights."""
+    rows take the dequantised copy (or, with weight_dtype nvfp4-w4a4, the block-scaled tensor-core GEMM where a single
+    tensor scale allows it); with weight_dtype nvfp4 the decode rows run on the few-row tensor-core kernel. Logits match the fp32 oracle over the dequantised weights."""
     import dataclasses
     from ferrite_b200.config import EngineConfig, tiny_hybrid
     from ferrite_b200.engine.engine import Engine
@@ -230,4 +231,4 @@ def test_engine_from_a_modelopt_nvfp4_checkpoint(ext, tmp_path, mode):
     got = torch.cat(rows)
     kl = torch.nn.functional.kl_div(torch.log_softmax(got, -1), torch.log_softmax(want, -1), log_target=True,
                                     reduction="batchmean").item()
-    assert kl < (2e-2 if mode == "bf16" else 0.3), kl       # nvfp4 mode also quantises the activations of prompt rows
+    assert kl < (0.3 if mode == "nvfp4-w4a4" else 2e-2), kl     # w4a4 also quantises the activations of prompt rows (one rendering)
