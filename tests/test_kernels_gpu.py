@@ -26,11 +26,24 @@ def rnd(*shape, scale=1.0, seed=0, dtype=torch.bfloat16):
     return (torch.randn(*shape, generator=g, device=DEV) * scale).to(dtype)
 
 
-def close(got, want, rtol=2e-2, atol=2e-2):
+# Attention outputs are averages of random value rows: their RMS is ~0.1 while the rounding of P (bf16 in the tensor-core
+# kernels) and of V acts on values of order 1, so the absolute term is a tenth of the output RMS there.
+ATT_ATOL = 0.1
+
+
+def close(got, want, rtol=None, atol=None):
+    """Every element within atol * rms(want) + rtol * |want|. Defaults by the kernel's output type: a bf16 result may be
+    two bf16 roundings away (the kernel rounds once, the fp32 oracle's result is rounded for the comparison by the
+    magnitude term); both kinds see the bf16 rounding of intermediates (normalised rows, activations) and the summation
+    order as noise against the output's RMS: measured up to 1.2 % of it."""
+    low = got.dtype in (torch.bfloat16, torch.float16)
+    rtol = (1.6e-2 if low else 4e-3) if rtol is None else rtol
+    atol = 1.5e-2 if atol is None else atol
     got, want = got.float(), want.float()
-    err = (got - want).abs().max().item()
-    ref = want.abs().max().item()
-    assert err <= atol * max(1.0, ref) + rtol * ref * 0 + 1e-6, f"max err {err} vs scale {ref}"
+    rms = want.pow(2).mean().sqrt().item()
+    excess = ((got - want).abs() - (atol * rms + rtol * want.abs())).max().item()
+    assert excess <= 0, (f"worst element exceeds atol {atol} x rms {rms:.4g} + rtol {rtol} x |want| by {excess:.4g} "
+                         f"(max |err| {(got - want).abs().max().item():.4g}, max |want| {want.abs().max().item():.4g})")
 
 
 @pytest.mark.parametrize("M", [1, 2, 3, 4, 8])
@@ -47,7 +60,8 @@ def test_gemv_plain(ops, tops, M, N, K):
 def test_gemv_norm_swiglu(ops, tops, M):
     K, I = 5120, 1024
     x, w, nw = rnd(M, K, seed=1), rnd(2 * I, K, scale=0.03, seed=2), rnd(K, scale=0.1, seed=4)
-    close(ops.linear(x, w, norm_w=nw, eps=1e-6, swiglu=True), tops.linear(x, w, norm_w=nw, eps=1e-6, swiglu=True))
+    # silu(g) * u: the relative errors of the two factors add
+    close(ops.linear(x, w, norm_w=nw, eps=1e-6, swiglu=True), tops.linear(x, w, norm_w=nw, eps=1e-6, swiglu=True), rtol=2.5e-2)
     close(ops.linear(x, w[:I], norm_w=nw, eps=1e-6), tops.linear(x, w[:I], norm_w=nw, eps=1e-6))
 
 
@@ -128,14 +142,14 @@ def test_attention_paged(ops, tops, hd, nq, nkv, rot):
     for nsplit in (1, 4):
         oa = ops.attention(qa, proj, kc[0], vc[0], slot, kvlen, bt, kv_block, nq, nkv, hd, gated, nsplit=nsplit)
         ob = tops.attention(qb, proj, kc[1], vc[1], slot, kvlen, bt, kv_block, nq, nkv, hd, gated)
-        close(oa, ob)
+        close(oa, ob, atol=ATT_ATOL)
     # flash prefill kernel: the same rows as two segments (a resumed prompt with a 100-key prefix, and a fresh one)
     seg_slot = torch.tensor([1], device=DEV, dtype=torch.int32)
     for r0, n, p0 in ((0, 300, 0), (100, 200, 100), (290, 10, 290)):
         segs = [seg_slot, torch.tensor([r0], device=DEV, dtype=torch.int32),
                 torch.tensor([n], device=DEV, dtype=torch.int32), torch.tensor([p0], device=DEV, dtype=torch.int32)]
         of = ops.attention_prefill(qa, proj, kc[0], vc[0], *segs, bt, kv_block, nq, nkv, hd, gated, n)
-        close(of[r0:r0 + n], ob[r0:r0 + n])
+        close(of[r0:r0 + n], ob[r0:r0 + n], atol=ATT_ATOL)
     # tree mask: rows see the first 290 keys plus chosen later ones
     base = torch.full((300,), 290, device=DEV, dtype=torch.int32)
     mask = torch.full((300,), 0b1010010011, device=DEV, dtype=torch.int64)
@@ -144,7 +158,7 @@ def test_attention_paged(ops, tops, hd, nq, nkv, rot):
                        row_base=base[:8], row_mask=mask[:8], nsplit=2)
     ob = tops.attention(qb[:8], proj[:8], kc[1], vc[1], slot[:8], lens[:8], bt, kv_block, nq, nkv, hd, gated,
                         row_base=base[:8], row_mask=mask[:8])
-    close(oa, ob)
+    close(oa, ob, atol=ATT_ATOL)
     assert ops.status() == 0
 
 
@@ -178,7 +192,7 @@ def test_gdn_conv_and_recurrence(ops, tops, nk, nv, dk, dv):
         assert torch.equal(st[0][1], st[1][1])
     oa = ops.gated_norm(ya, proj, conv_dim, gw, nv, dv, 1e-6)
     ob = tops.gated_norm(ya, proj, conv_dim, gw, nv, dv, 1e-6)
-    close(oa, ob)
+    close(oa, ob, atol=ATT_ATOL)
 
 
 def test_argmax(ops):
@@ -427,8 +441,8 @@ def test_attention_prefill_tcgen05_against_mma_sync_and_reference(ops, tops, hd,
     finally:
         ops.attn_tc = True
     c = tops.attention_prefill(q, proj, kc, vc, *segs, bt, kv_block, nq, nkv, hd, gated, 520)
-    close(b, c)
-    close(a, c)
+    close(b, c, atol=ATT_ATOL)
+    close(a, c, atol=ATT_ATOL)
     assert ops.status() == 0
 
 
