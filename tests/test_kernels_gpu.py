@@ -192,7 +192,56 @@ def test_gdn_conv_and_recurrence(ops, tops, nk, nv, dk, dv):
         assert torch.equal(st[0][1], st[1][1])
     oa = ops.gated_norm(ya, proj, conv_dim, gw, nv, dv, 1e-6)
     ob = tops.gated_norm(ya, proj, conv_dim, gw, nv, dv, 1e-6)
-    close(oa, ob, atol=ATT_ATOL)
+    close(oa, ob)
+
+
+def test_verify_rows_carry_the_bits_of_decode_rows(ops):
+    """A row computed inside a multi-row (verify) segment equals, bit for bit, the same row computed as a one-row decode
+    step after its predecessors were committed: the Gated DeltaNet step kernel (conv window, delta rule and gated norm
+    run row after row with the state in registers) and the split-KV decode attention (a row's keys, their order and the
+    split boundaries do not depend on the rows that share its tile)."""
+    nk, nv, dk, dv = 4, 8, 128, 128
+    conv_dim = 2 * nk * dk + nv * dv
+    width = conv_dim + nv * dv + 2 * nv
+    T = 9
+    proj = rnd(T, width, seed=1)
+    conv_w = rnd(conv_dim, 4, scale=0.5, seed=2)
+    A_log = rnd(nv, scale=0.3, seed=3, dtype=torch.float32)
+    dtb = rnd(nv, scale=0.3, seed=4, dtype=torch.float32)
+    gw = (rnd(dv, scale=0.1, seed=5).float() + 1).to(torch.bfloat16)
+    i32 = lambda *v: torch.tensor(list(v), device=DEV, dtype=torch.int32)
+    rec = [rnd(2, nv, dk, dv, scale=0.2, seed=6, dtype=torch.float32) for _ in range(2)]
+    conv = [rnd(2, 3, conv_dim, seed=7) for _ in range(2)]
+    whole = ops.gdn_step(proj, conv_w, rec[0], conv[0], A_log, dtb, gw, i32(1), i32(0), i32(T), nk, nv, dk, dv, 1e-6, commit=True)
+    rows = [ops.gdn_step(proj[r:r + 1].contiguous(), conv_w, rec[1], conv[1], A_log, dtb, gw, i32(1), i32(0), i32(1), nk, nv, dk,
+                         dv, 1e-6, commit=True) for r in range(T)]
+    assert torch.equal(whole, torch.cat(rows))
+    assert torch.equal(rec[0], rec[1]) and torch.equal(conv[0], conv[1])
+
+    hd, nq, nkv, rot, kv_block = 256, 8, 2, 64, 64
+    nb, ctx = 8, 200
+    aw = nq * hd * 2 + 2 * nkv * hd
+    bt = torch.arange(nb, device=DEV, dtype=torch.int32).view(1, nb)
+    inv = (1e6 ** (-torch.arange(rot // 2, dtype=torch.float64) / (rot // 2))).float().to(DEV)
+    qn, kn = rnd(hd, scale=0.1, seed=7), rnd(hd, scale=0.1, seed=8)
+    kc = torch.zeros(nb, kv_block, nkv, hd, dtype=torch.bfloat16, device=DEV)
+    vc = torch.zeros_like(kc)
+    aproj = rnd(ctx + 5, aw, seed=9)
+    slot = torch.zeros(ctx + 5, device=DEV, dtype=torch.int32)
+    pos = torch.arange(ctx + 5, device=DEV, dtype=torch.int32)
+    q = ops.attn_prep(aproj, qn, kn, inv, slot, pos, bt, kc, vc, kv_block, nq, nkv, hd, rot, True, 1e-6)
+    # the last five rows as one verify segment ...
+    r0 = ctx
+    seg = (i32(0), i32(0), i32(5), 5)
+    many = ops.attention(q[r0:].contiguous(), aproj[r0:].contiguous(), kc, vc, slot[r0:].contiguous(), (pos[r0:] + 1).contiguous(), bt,
+                         kv_block, nq, nkv, hd, True, nsplit=2, segs=seg)
+    # ... and one by one
+    for i in range(5):
+        one = ops.attention(q[r0 + i:r0 + i + 1].contiguous(), aproj[r0 + i:r0 + i + 1].contiguous(), kc, vc, slot[:1].contiguous(),
+                            (pos[r0 + i:r0 + i + 1] + 1).contiguous(), bt, kv_block, nq, nkv, hd, True, nsplit=2,
+                            segs=(i32(0), i32(0), i32(1), 1))
+        assert torch.equal(one[0], many[i]), i
+    assert ops.status() == 0
 
 
 def test_argmax(ops):
