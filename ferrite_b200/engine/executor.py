@@ -440,7 +440,7 @@ class Executor:
         # blocks; column-parallel projections gather the rows (all-gather fused into the GEMM), row-parallel ones
         # reduce-scatter them (fused into the GEMM epilogue). Decode-sized steps keep replicated rows.
         sp = (self.tp is not None and self.tp.sp_ready(T) and (c.n_experts == 0 or self.ep is not None)
-              and c.kv_lora == 0 and not isinstance(w["l0.in_proj"], QWeight))
+              and c.kv_lora == 0 and isinstance(w["l0.in_proj"], torch.Tensor))       # packed weights keep replicated rows
         if sp:
             lo, hi = self.tp.shard_rows(T)
             x = x[lo:hi].contiguous()

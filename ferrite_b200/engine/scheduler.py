@@ -538,7 +538,9 @@ class Scheduler:
         for a, cut, toks, last, _ in group:
             tok = None
             if last:
-                if self.opts.finite_check and not bool(torch.isfinite(logits[k]).all()):
+                # (a greedy step under tensor parallelism merges (max, index) pairs over the ranks and has no logits)
+                finite_k = bool(picks[1][k]) if (ids is not None and logits is None) else bool(torch.isfinite(logits[k]).all())
+                if self.opts.finite_check and not finite_k:
                     a.pos += cut
                     a.pending = a.pending[cut:]
                     self._finish(a, "error", message="non-finite logits")
@@ -559,7 +561,8 @@ class Scheduler:
         tok = None
         if last:
             tok = int(picks[0][0]) if greedy else a.sampler.sample(logits[0], first=not a.out)
-            if self.opts.finite_check and not bool(torch.isfinite(logits[0]).all()):
+            finite = bool(picks[1][0]) if (greedy and logits is None) else bool(torch.isfinite(logits[0]).all())
+            if self.opts.finite_check and not finite:
                 a.pos += cut
                 a.pending = a.pending[cut:]
                 self._finish(a, "error", message="non-finite logits")
