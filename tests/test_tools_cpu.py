@@ -60,6 +60,43 @@ def test_quickbench_reports_streams(capsys):
     assert rc == 0 and line["ok"] == 3 and line["total_tokens"] > 0
 
 
+def test_workload_clients_on_the_mock_server(capsys, tmp_path):
+    """edit / lanes (with the gate) / mixed / agents against the scripted mock: each prints one JSON line and succeeds."""
+    from ferrite_b200.tools.workloads import main
+    url, loop = _serve()
+    try:
+        lines = {}
+        for argv in (["edit", "--streams", "2", "--max-tokens", "32", "--max-source-chars", "600", "--out", str(tmp_path / "e")],
+                     ["lanes", "--lanes", "1,3,64", "--prefix-tokens", "120", "--max-tokens", "24", "--runs", "1", "--gate"],
+                     ["mixed", "--decoders", "2", "--prompts", "2", "--prompt-tokens", "200", "--max-tokens", "40", "--lead-s", "0.05"],
+                     ["agents", "--agents", "2", "--turns", "3", "--prefix-tokens", "80", "--max-tokens", "32"]):
+            rc = main(argv[:1] + ["--base-url", url] + argv[1:])
+            line = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+            assert rc == 0, line
+            lines[line["workload"]] = line
+    finally:
+        loop.call_soon_threadsafe(loop.stop)
+    assert lines["edit"]["streams"] == 2 and (tmp_path / "e-1.txt").exists()
+    pts = {p["lanes"]: p for p in lines["lanes"]["points"]}
+    assert pts[3]["gate_lanes_differing_from_alone"] == [] and pts[3]["cached_tokens"] > 0 and "skipped" in pts[64]
+    assert lines["mixed"]["chunk_gap_ms"]["median"] is not None and len(lines["mixed"]["prompt_ttft_s"]) == 2
+    assert lines["agents"]["cached_share_after_first_turn"] > 0.5
+
+
+def test_release_gate_on_the_mock_server(capsys):
+    from ferrite_b200.tools.release_gate import main
+    url, loop = _serve()
+    try:
+        rc = main(["--base-url", url, "--mock", "--lanes", "1,2", "--prefix-tokens", "100", "--streams", "2"])
+        out = capsys.readouterr().out
+        assert rc == 0 and "release gate: PASS" in out, out
+        rc = main(["--base-url", url, "--mock", "--lanes", "1", "--prefix-tokens", "50", "--streams", "2", "--min-tok-s", "1e9"])
+        out = capsys.readouterr().out
+        assert rc == 1 and "FAIL serving rate" in out, out
+    finally:
+        loop.call_soon_threadsafe(loop.stop)
+
+
 def test_launch_commands_and_step_summary():
     from ferrite_b200.tools.launch import command
     from ferrite_b200.tools.sched_steps import summarise
