@@ -17,11 +17,17 @@ SILENCE = 16       # steps to stay quiet
 
 
 class Copier:
-    def __init__(self):
+    """`lo` / `hi`: bounds of the adaptive proposal length. A proposal that lands whole doubles the next one (up to `hi`),
+    one of which less than half lands halves it (down to `lo`); going quiet resets it (reference `Copier::observe`,
+    `crates/fe-model/src/copy.rs:105-125`)."""
+
+    def __init__(self, lo: int = 4, hi: int = MAX_MATCH):
         self.tokens: List[int] = []
         self.index: Dict[Tuple[int, ...], List[int]] = {}
         self.misses = 0
         self.quiet = 0
+        self.lo, self.hi = max(1, lo), max(lo, hi)
+        self.extra = self.lo                 # copy rows to propose next time
 
     def sync(self, tokens: Sequence[int]) -> None:
         """Bring the index up to date with the sequence (prompt + generated so far); handles rollbacks."""
@@ -35,7 +41,10 @@ class Copier:
                 key = tuple(self.tokens[i + 1 - KEY:i + 1])
                 self.index.setdefault(key, []).append(i + 1)      # position right after the n-gram
 
-    def propose(self, max_len: int = MAX_MATCH) -> List[int]:
+    def propose(self, max_len: int = MAX_MATCH, adaptive: bool = False) -> List[int]:
+        """Up to `max_len` tokens (with `adaptive`: up to the current adaptive length) that followed the latest longest
+        earlier occurrence of the sequence's end. A continuation that reaches the end of the sequence goes on with the
+        copy itself, so a loop with a period shorter than the proposal continues."""
         if self.quiet > 0:
             self.quiet -= 1
             return []
@@ -53,17 +62,47 @@ class Copier:
                 m += 1
             if m > best_len:
                 best_len, best_pos = m, pos
+                if m == MAX_MATCH:
+                    break
         if best_len < MIN_MATCH:
             return []
-        return t[best_pos:best_pos + min(max_len, MAX_MATCH)]
+        want = min(max_len, MAX_MATCH, self.extra if adaptive else MAX_MATCH)
+        out: List[int] = []
+        for j in range(want):
+            i = best_pos + j
+            out.append(t[i] if i < n else out[i - n])
+        return out
 
     def observe(self, proposed: int, accepted: int) -> None:
-        """Feedback after verification: a proposal that got nothing accepted counts as a miss."""
+        """Feedback after verification: how many of the proposed copy rows were kept."""
         if proposed == 0:
             return
+        if accepted == proposed:
+            self.extra = min(self.hi, self.extra * 2)
+        elif 2 * accepted < proposed:
+            self.extra = max(self.lo, self.extra // 2)
         if accepted == 0:
             self.misses += 1
             if self.misses >= MISSES:
-                self.quiet, self.misses = SILENCE, 0
+                self.quiet, self.misses, self.extra = SILENCE, 0, self.lo
         else:
             self.misses = 0
+
+
+def graft(toks: List[int], parents: List[int], copy: Sequence[int], room: int) -> Tuple[int, int]:
+    """Put a copy proposal onto a verify tree. `toks[0]` is the segment's root (the token being fed), `parents[r]` the row
+    a row hangs from (-1 for the root), `copy` the tokens proposed after the root. The copy is followed down the rows that
+    already hold it; up to `room` of what is left is appended as a chain below the deepest of them. Returns (tokens of
+    the copy found in the tree, rows added). Reference `graft`, `crates/fe-model/src/copy.rs:128-147`."""
+    r, i = 0, 0
+    while i < len(copy):
+        nxt = next((c for c in range(r + 1, len(toks)) if parents[c] == r and toks[c] == copy[i]), None)
+        if nxt is None:
+            break
+        r, i = nxt, i + 1
+    add = min(len(copy) - i, max(0, room))
+    for t in copy[i:i + add]:
+        parents.append(r)
+        toks.append(int(t))
+        r = len(toks) - 1
+    return i, add

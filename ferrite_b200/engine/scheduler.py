@@ -21,7 +21,7 @@ from typing import Callable, Dict, List, Optional, Sequence, Tuple
 
 import torch
 
-from .copy import Copier
+from .copy import Copier, graft
 from .engine import Engine, prompt_cuts
 from .executor import Segment, TREE_MAX_ROWS
 from .pcache import PREFIX_MIN, Park, SlotCache, Snap, common_prefix
@@ -37,6 +37,7 @@ class SchedOptions:
 
     spec: int = 0                      # draft tokens per step (0 = plain decoding)
     copy_rows: bool = True             # context-copy proposals
+    copy_adaptive: bool = True         # their length follows how many of them land (doubling / halving between 4 and 64)
     pool: int = 64                     # parked entries kept
     batch_rows: int = 2048             # prompt rows per step
     finite_check: bool = True
@@ -585,26 +586,35 @@ class Scheduler:
 
     def _decode_step(self, decoders: List[Active]) -> int:
         """One decode / verify step over all decoding requests: a row per request plus its draft rows."""
-        segs, drafts, trees = [], [], []
+        segs, drafts, trees, copies = [], [], [], []
         for a in decoders:
             d: List[int] = []
             par: Optional[List[int]] = None
+            copy: List[int] = []
             if self.opts.spec > 0:
                 room = min(self.opts.spec, DECODE_ROWS - 1, a.req.sampling.max_tokens - len(a.out) - 1,
                            self.eng.ecfg.max_ctx - a.pos - 2)
                 if room > 0:
                     if a.copier is not None:
                         a.copier.sync(a.req.prompt + a.out[:-1] + [a.next_token])
-                        d = a.copier.propose(room)
-                    if not d and self.drafter is not None and self.opts.tree_rows > 0:
+                        copy = a.copier.propose(room, adaptive=self.opts.copy_adaptive)
+                    if self.drafter is not None and self.opts.tree_rows > 0:
+                        # the draft model's tree, with the copy proposal grafted onto it: rows the tree already holds
+                        # are shared, the rest of the copy hangs below them as a chain (reference `graft`)
                         n_rows = min(self.opts.tree_rows, TREE_MAX_ROWS - 1, self.eng.ecfg.max_ctx - a.pos - 2)
                         d, dp = self.drafter.draft_tree(a.slot, a.next_token, a.pos, self.eng.taps, room, n_rows)
-                        d, dp = list(d[:n_rows]), list(dp[:n_rows])
-                        if d and dp != list(range(len(d))):
-                            par = [-1] + [int(p) for p in dp]
-                    elif not d and self.drafter is not None:
+                        toks, pars = [a.next_token] + [int(t) for t in d[:n_rows]], [-1] + [int(p) for p in dp[:n_rows]]
+                        if copy:
+                            graft(toks, pars, copy, TREE_MAX_ROWS - len(toks))
+                        d = toks[1:]
+                        if d and pars[1:] != list(range(len(d))):
+                            par = pars
+                    elif copy:
+                        d = copy
+                    elif self.drafter is not None:
                         d = self.drafter.draft(a.slot, a.next_token, a.pos, self.eng.taps, room)
                     d = [int(t) for t in (d if par is not None else d[:room])]
+            copies.append(copy if (par is not None or d[:len(copy)] == copy) else [])
             drafts.append(d)
             trees.append(par)
             segs.append(Segment(a.slot, a.pos, [a.next_token] + d, "all", parents=par))
@@ -631,7 +641,7 @@ class Scheduler:
             # request's own generator, so a seeded request repeats. Penalties and drafts keep the host sampler.
             seeds = [a.sampler.rng.next_u64() for a in decoders]
             dev_ids = self.eng.ops.sample(logits, [a.req.sampling for a in decoders], seeds).tolist()
-        for a, d, par in zip(decoders, drafts, trees):
+        for a, d, par, copy in zip(decoders, drafts, trees, copies):
             n = 1 + len(d)
             if par is not None:
                 # verify tree: follow the target's choices from the root (reference `tree_walk`); sampling from the
@@ -651,6 +661,9 @@ class Scheduler:
                 self.stats["drafted"] += len(d)
                 self.stats["accepted"] += acc
                 fed = [a.next_token] + [d[i - 1] for i in path[1:]]
+                if a.copier is not None and copy:
+                    landed = next((j for j, (x, y) in enumerate(zip(fed[1:], copy)) if x != y), min(len(fed) - 1, len(copy)))
+                    a.copier.observe(len(copy), landed)
                 a.pos += len(new)
                 if self.drafter is not None:
                     idx = torch.tensor([r + i for i in path], dtype=torch.long, device=taps[0].device) if taps else None
@@ -678,8 +691,8 @@ class Scheduler:
             a.drafts_accepted += acc
             self.stats["drafted"] += len(d)
             self.stats["accepted"] += acc
-            if a.copier is not None:
-                a.copier.observe(len(d), acc)
+            if a.copier is not None and copy:
+                a.copier.observe(len(copy), min(acc, len(copy)))
             fed = [a.next_token] + d[:acc]
             a.pos += len(new)
             if self.drafter is not None:

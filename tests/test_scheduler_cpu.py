@@ -402,3 +402,31 @@ def test_arrival_window_collects_requests_sent_together():
     assert sched.stats["steps"] <= 1 + 3 + 1
     for p, o in zip(prompts, outs):
         assert o == _plain(cfg, w, p, 3)
+
+
+def test_copier_adapts_its_length_continues_loops_and_grafts_onto_trees():
+    from ferrite_b200.engine.copy import Copier, graft
+    c = Copier(lo=4, hi=32)
+    seq = list(range(100, 120)) + [7, 8, 9] + list(range(100, 110))          # the tail repeats the head
+    c.sync(seq)
+    assert c.propose(64, adaptive=True) == list(range(110, 114))              # starts at `lo` rows
+    c.observe(4, 4)
+    assert len(c.propose(64, adaptive=True)) == 8                             # a proposal that lands whole doubles
+    c.observe(8, 8); c.observe(16, 16); c.observe(32, 32)
+    assert c.extra == 32                                                      # ... up to `hi`
+    c.observe(32, 10)
+    assert c.extra == 16                                                      # less than half landed: halves
+    assert c.propose(6) == list(range(110, 116))                              # the plain form proposes what is asked for
+    for _ in range(4):
+        c.observe(4, 0)
+    assert c.propose(64) == [] and c.extra == 4                               # four misses: quiet, and back to `lo`
+    # a loop of period 3 continues past the end of the history
+    p = Copier()
+    p.sync([1, 2, 3] * 4)
+    assert p.propose(7) == [1, 2, 3, 1, 2, 3, 1]
+    # graft: the copy 5 6 7 8 onto a tree root -> {5 -> {6, 9}, 4}
+    toks, par = [0, 5, 4, 6, 9], [-1, 0, 0, 1, 1]
+    followed, added = graft(toks, par, [5, 6, 7, 8], room=1)
+    assert (followed, added) == (2, 1) and toks == [0, 5, 4, 6, 9, 7] and par == [-1, 0, 0, 1, 1, 3]
+    toks, par = [0], [-1]
+    assert graft(toks, par, [5, 6], room=8) == (0, 2) and par == [-1, 0, 1]

@@ -110,3 +110,25 @@ def test_scheduler_tree_speculation_keeps_greedy_output():
     a = generate(sched, [prompt], s)[0]
     b = generate(sched, [prompt], s)[0]
     assert a == b and len(a) == 10
+
+
+def test_copy_rows_grafted_onto_the_draft_tree_keep_greedy_output():
+    """A prompt made of repeated spans: the copy proposal is grafted onto the draft model's tree (shared rows followed, the
+    rest hung below them); the text stays the plain greedy text and copy rows are among the drafts."""
+    from ferrite_b200.config import ModelConfig
+    from ferrite_b200.engine.scheduler import Sampling, SchedOptions, Scheduler, generate
+    from ferrite_b200.models.drafter import BlockDrafter
+    cfg = tiny_hybrid()
+    cfg.tap_layers = [1, 3]
+    w = init_weights(cfg, seed=0)
+    prompt = _prompt(cfg, 12, 21) * 5
+    plain = Engine(cfg, w, EngineConfig(n_slots=1, max_ctx=256), device="cpu")
+    want = generate(Scheduler(plain, SchedOptions(spec=0)), [prompt], Sampling(max_tokens=16))
+    eng = Engine(cfg, w, EngineConfig(n_slots=1, max_ctx=256), device="cpu")
+    dcfg = ModelConfig(name="tiny-drafter", hidden=128, inter=256, n_layers=2, full_attn_every=1, head_dim=32, n_q=4,
+                       n_kv=2, rotary_dim=32, attn_gate=False, vocab=cfg.vocab, tie_embeddings=True)
+    dr = BlockDrafter(dcfg, target_hidden=cfg.hidden, n_taps=2, n_slots=1, max_ctx=256, device="cpu", block=4)
+    sched = Scheduler(eng, SchedOptions(spec=8, copy_rows=True, tree_rows=8), drafter=dr)
+    got = generate(sched, [prompt], Sampling(max_tokens=16))
+    assert got == want
+    assert sched.stats["drafted"] > 0
