@@ -34,8 +34,10 @@ class CudaOps:
         self.status_word = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._ws: Optional[torch.Tensor] = None
         self._counters = torch.zeros(16384, dtype=torch.int32, device=self.device)
+        self.empty = torch.empty            # every output buffer of the ops comes from here (see enable_canaries)
+        self._guarded = []
         self._dl_sync = torch.zeros(2, dtype=torch.int32, device=self.device)      # grid-barrier words of the persistent layer kernel
-        self._dl_empty = torch.empty(0, dtype=self.dtype, device=self.device)
+        self._dl_empty = self.empty(0, dtype=self.dtype, device=self.device)
         self.decode_layers_max = int(self.C.decode_layers_max())
         self.C.decode_layers_prepare()      # attributes + residency check now, not inside a graph capture
         self.force_gemv_chunks = False      # debug: run any row count through 8-row GEMV passes
@@ -59,8 +61,47 @@ class CudaOps:
     # ---- workspace ---------------------------------------------------------------------------------
     def _workspace(self, nbytes: int) -> torch.Tensor:
         if self._ws is None or self._ws.numel() * 4 < nbytes:
-            self._ws = torch.empty(max(nbytes // 4, 16 << 20), dtype=torch.float32, device=self.device)   # 64 MB up front: graphs keep the pointer
+            self._ws = self.empty(max(nbytes // 4, 16 << 20), dtype=torch.float32, device=self.device)   # 64 MB up front: graphs keep the pointer
         return self._ws
+
+    # ---- debug: canary-padded output buffers --------------------------------------------------------------
+    CANARY_BYTES, CANARY_BYTE = 256, 0xA5
+
+    def enable_canaries(self, on: bool = True) -> None:
+        """Debug aid (reference: canary-padded allocations, `crates/fe-cuda/src/lib.rs:299-343`): every output buffer the
+        ops allocate gets 256 guard bytes in front and behind, filled with a pattern; `check_canaries()` verifies them, so
+        a kernel that writes just past (or before) its output is caught at the step that did it. Eager steps only (the
+        guard zones of a captured graph are checked after replays as long as canaries stay enabled)."""
+        self.empty = self._empty_guarded if on else torch.empty
+        if not on:
+            self._guarded = []
+
+    def _empty_guarded(self, *shape, dtype=None, device=None, **kw):
+        if len(shape) == 1 and isinstance(shape[0], (tuple, list, torch.Size)):
+            shape = tuple(shape[0])
+        dtype = dtype or torch.float32
+        item = torch.empty(0, dtype=dtype).element_size()
+        nbytes = item
+        for d in shape:
+            nbytes *= int(d)
+        body = (nbytes + 255) // 256 * 256
+        g = self.CANARY_BYTES
+        raw = torch.full((g + body + g,), self.CANARY_BYTE, dtype=torch.uint8, device=device or self.device)
+        self._guarded.append((raw, nbytes, tuple(int(d) for d in shape), dtype))
+        return raw[g:g + nbytes].view(dtype).view(*shape) if nbytes else torch.empty(*shape, dtype=dtype, device=device or self.device)
+
+    def check_canaries(self) -> int:
+        """Raises if any guard byte of a buffer handed out since the last check changed; returns how many were checked."""
+        g, n = self.CANARY_BYTES, len(self._guarded)
+        for raw, nbytes, shape, dtype in self._guarded:
+            front = raw[:g]
+            back = raw[g + nbytes:]                      # the round-up slack behind the data is guard too
+            if not (bool((front == self.CANARY_BYTE).all()) and bool((back == self.CANARY_BYTE).all())):
+                where = "before" if not bool((front == self.CANARY_BYTE).all()) else "behind"
+                self._guarded = []
+                raise RuntimeError(f"canary: a kernel wrote {where} its output buffer {shape} {dtype}")
+        self._guarded = []
+        return n
 
     def status(self) -> int:
         return int(self.status_word.item())
@@ -70,13 +111,13 @@ class CudaOps:
         later call asks for more; callers size it by the largest use up front)."""
         buf = self._scratch.get(name)
         if buf is None or buf.numel() < numel or buf.dtype != dtype:
-            buf = torch.empty(numel, dtype=dtype, device=self.device)
+            buf = self.empty(numel, dtype=dtype, device=self.device)
             self._scratch[name] = buf
         return buf[:numel]
 
     # ---- rows ------------------------------------------------------------------------------------
     def embed(self, table, ids):
-        out = torch.empty(ids.numel(), table.shape[1], dtype=self.dtype, device=self.device)
+        out = self.empty(ids.numel(), table.shape[1], dtype=self.dtype, device=self.device)
         self.launches += 1
         self.C.embed(out, table, ids)
         return out
@@ -154,7 +195,7 @@ class CudaOps:
                 return self._linear_w4a4(x, w, norm_w, eps, res, swiglu, M, N, out_f32)
             if M <= GEMV_MAX_ROWS and not self.force_gemv_chunks:
                 N = w.rows // 2 if swiglu else w.rows
-                y = torch.empty(M, N, dtype=torch.float32 if out_f32 else self.dtype, device=self.device)
+                y = self.empty(M, N, dtype=torch.float32 if out_f32 else self.dtype, device=self.device)
                 self.launches += 1
                 self.C.gemv_nvfp4(y, x, w.packed, w.gemv_scales, w.global_scale, norm_w, res, eps, 1 if swiglu else 0,
                                   w.row_alpha)
@@ -167,12 +208,12 @@ class CudaOps:
         if (self.mma_gemv_rows[0] <= M <= self.mma_gemv_rows[1] and K % 32 == 0 and not self.force_gemv_chunks
                 and w.stride(0) == K and (M <= 8 or N < 65536)):
             # a few rows (concurrent decode streams, speculative verify): weights streamed once into mma.sync fragments
-            y = out if out is not None else torch.empty(M, N, dtype=torch.float32 if out_f32 else self.dtype, device=self.device)
+            y = out if out is not None else self.empty(M, N, dtype=torch.float32 if out_f32 else self.dtype, device=self.device)
             self.launches += 1
             self.C.gemv_mma(y, x, w, norm_w, res, eps, 1 if swiglu else 0, self._workspace(8 << 20), self._counters)
             return y
         if M <= GEMV_MAX_ROWS or self.force_gemv_chunks:
-            y = out if out is not None else torch.empty(M, N, dtype=torch.float32 if out_f32 else self.dtype, device=self.device)
+            y = out if out is not None else self.empty(M, N, dtype=torch.float32 if out_f32 else self.dtype, device=self.device)
             for r0 in range(0, M, GEMV_MAX_ROWS):
                 r1 = min(M, r0 + GEMV_MAX_ROWS)
                 self.launches += 1
@@ -182,7 +223,7 @@ class CudaOps:
         if norm_w is not None:
             x, _ = self.rmsnorm(x, norm_w, eps, True)
         # the wide-M epilogue stores 16-byte row pieces: give odd widths a padded leading dimension
-        y = out if out is not None else torch.empty(M, (N + 7) // 8 * 8, dtype=torch.float32 if out_f32 else self.dtype,
+        y = out if out is not None else self.empty(M, (N + 7) // 8 * 8, dtype=torch.float32 if out_f32 else self.dtype,
                                                     device=self.device)[:, :N]
         split = self._split_k(M, N, K) if M <= 64 else 1
         ws = cnt = None
@@ -208,10 +249,10 @@ class CudaOps:
         after RMSNorm) with one scale per row; the epilogue applies row scale x feature scale."""
         M, K = x.shape
         N = wq.shape[0] // 2 if swiglu else wq.shape[0]
-        xq = torch.empty(M, K, dtype=torch.uint8, device=self.device)
-        xs = torch.empty(M, dtype=torch.float32, device=self.device)
+        xq = self.empty(M, K, dtype=torch.uint8, device=self.device)
+        xs = self.empty(M, dtype=torch.float32, device=self.device)
         self.C.quant_fp8(xq, xs, x, norm_w, eps)
-        y = torch.empty(M, (N + 7) // 8 * 8, dtype=self.dtype, device=self.device)[:, :N]
+        y = self.empty(M, (N + 7) // 8 * 8, dtype=self.dtype, device=self.device)[:, :N]
         split = self._split_k(M, N, K // 2) if M <= 64 else 1
         ws = cnt = None
         if split > 1:
@@ -238,8 +279,8 @@ class CudaOps:
         """Rows to e4m3 with one scale per (row, 128 columns): (codes [M, ceil(K/128)*128], scales fp32 [M, ceil(K/128)])."""
         M, K = x.shape
         kb = (K + 127) // 128
-        q = torch.empty(M, kb * 128, dtype=torch.uint8, device=self.device)
-        sc = torch.empty(M, kb, dtype=torch.float32, device=self.device)
+        q = self.empty(M, kb * 128, dtype=torch.uint8, device=self.device)
+        sc = self.empty(M, kb, dtype=torch.float32, device=self.device)
         self.launches += 1
         self.C.quant_fp8_block(q, sc, x)
         return q, sc
@@ -250,7 +291,7 @@ class CudaOps:
         M, K = x.shape
         N = wq.shape[0]
         xq, xs = self.quantize_act_fp8_block(x)
-        y = torch.empty(M, (N + 7) // 8 * 8, dtype=self.dtype, device=self.device)[:, :N]
+        y = self.empty(M, (N + 7) // 8 * 8, dtype=self.dtype, device=self.device)[:, :N]
         fused = res is not None and res.stride(0) == y.stride(0)       # the kernel reads res with y's row stride
         self.launches += 1
         self.C.gemm_fp8_block(y, xq, xs, wq, w_scale, res if fused else None, K, self.status_word)
@@ -262,14 +303,14 @@ class CudaOps:
     def quant_nvfp4(self, x, norm_w=None, eps=1e-6):
         """Quantise activation rows (optionally after RMSNorm) to e2m1 codes + tiled e4m3 scales + per-row scale."""
         M, K = x.shape
-        codes = torch.empty(M, K // 2, dtype=torch.uint8, device=self.device)
+        codes = self.empty(M, K // 2, dtype=torch.uint8, device=self.device)
         key = ((M + 127) // 128, K)
         sf = self._sf_pool.get(key)
         if sf is None:
             # zero-initialised once: rows of the last 128-row tile that no call writes keep a finite (zero) scale
             sf = torch.zeros(int(self.C.nvfp4_sf_bytes(M, K)), dtype=torch.uint8, device=self.device)
             self._sf_pool[key] = sf
-        rs = torch.empty(M, dtype=torch.float32, device=self.device)
+        rs = self.empty(M, dtype=torch.float32, device=self.device)
         self.launches += 1
         self.C.quant_nvfp4(codes, sf, rs, x, norm_w, eps)
         return codes, sf, rs
@@ -279,7 +320,7 @@ class CudaOps:
         `fp4_terms` NVFP4 renderings (value, residual, residual of the residual) that the epilogue sums."""
         K = w.cols
         nb = int(self.C.gemv_nvfp4_tc_workspace_bytes(M, N, K, swiglu, self.fp4_terms, self.fp4_tc_ctas))
-        y = torch.empty(M, N, dtype=torch.float32 if out_f32 else self.dtype, device=self.device)
+        y = self.empty(M, N, dtype=torch.float32 if out_f32 else self.dtype, device=self.device)
         self.launches += 1
         nxt = getattr(w, "next", None) if self.fp4_prefetch_mb > 0 else None
         if nxt is not None and (nxt.mma_scales is None or nxt.cols % 256):
@@ -299,26 +340,26 @@ class CudaOps:
             cnt = self._counters
         if M <= GEMV_MAX_ROWS:
             # decode rows: RMSNorm + activation quantisation happen inside the GEMM kernel
-            y = torch.empty(M, N, dtype=torch.float32 if out_f32 else self.dtype, device=self.device)
+            y = self.empty(M, N, dtype=torch.float32 if out_f32 else self.dtype, device=self.device)
             self.launches += 1
             self.C.gemm_nvfp4_fused(y, x, norm_w, eps, w.packed, w.mma_scales, w.global_scale, res,
                                     1 if swiglu else 0, split, ws, cnt, self.status_word)
             return y
         xq, xsf, rs = self.quant_nvfp4(x, norm_w, eps)
-        y = torch.empty(M, N, dtype=self.dtype, device=self.device)
+        y = self.empty(M, N, dtype=self.dtype, device=self.device)
         self.launches += 1
         self.C.gemm_nvfp4(y, xq, xsf, rs, w.packed, w.mma_scales, w.global_scale, res, 1 if swiglu else 0, split, ws,
                           cnt, self.status_word)
         return y
 
     def silu_mul(self, gu):
-        out = torch.empty(gu.shape[0], gu.shape[1] // 2, dtype=self.dtype, device=self.device)
+        out = self.empty(gu.shape[0], gu.shape[1] // 2, dtype=self.dtype, device=self.device)
         self.launches += 1
         self.C.silu_mul(out, gu, 0.0)
         return out
 
     def gated_norm(self, y, proj, z_off, w, heads, dv, eps):
-        out = torch.empty(y.shape[0], heads * dv, dtype=self.dtype, device=self.device)
+        out = self.empty(y.shape[0], heads * dv, dtype=self.dtype, device=self.device)
         self.launches += 1
         self.C.gated_norm(out, y, proj, z_off, proj.stride(0), w, heads, dv, eps)
         return out
@@ -326,8 +367,8 @@ class CudaOps:
     # ---- mixture of experts ---------------------------------------------------------------------------
     def moe_route(self, logits, bias, mode, top_k, n_groups, topk_groups, scale):
         T = logits.shape[0]
-        ids = torch.empty(T, top_k, dtype=torch.int32, device=self.device)
-        wts = torch.empty(T, top_k, dtype=torch.float32, device=self.device)
+        ids = self.empty(T, top_k, dtype=torch.int32, device=self.device)
+        wts = self.empty(T, top_k, dtype=torch.float32, device=self.device)
         self.launches += 1
         self.C.moe_route(ids, wts, logits, bias, mode, n_groups, topk_groups, scale)
         return ids, wts
@@ -340,9 +381,9 @@ class CudaOps:
                 w_gu, w_down = self.experts_dense(w_gu, 0), self.experts_dense(w_down, 1)
             else:
                 # decode rows stream the 4-bit expert rows directly
-                act = torch.empty(T * K, inter, dtype=self.dtype, device=self.device)
-                yp = torch.empty(T * K, H, dtype=torch.float32, device=self.device)
-                out = torch.empty(T, H, dtype=torch.float32 if out_f32 else self.dtype, device=self.device)
+                act = self.empty(T * K, inter, dtype=self.dtype, device=self.device)
+                yp = self.empty(T * K, H, dtype=torch.float32, device=self.device)
+                out = self.empty(T, H, dtype=torch.float32 if out_f32 else self.dtype, device=self.device)
                 self.launches += 3
                 self.C.moe_experts_fp4(out, act, yp, h, w_gu.packed, w_gu.scales, w_gu.global_scale, w_down.packed,
                                        w_down.scales, w_down.global_scale, ids, wts, e_lo, e_hi, shared,
@@ -350,9 +391,9 @@ class CudaOps:
                 return out
         if T > self.moe_pair_rows:
             return self._moe_grouped(h, ids, wts, w_gu, w_down, e_lo, e_hi, shared, shared_gate, res, out_f32)
-        act = torch.empty(T * K, inter, dtype=self.dtype, device=self.device)
-        yp = torch.empty(T * K, H, dtype=torch.float32, device=self.device)
-        out = torch.empty(T, H, dtype=torch.float32 if out_f32 else self.dtype, device=self.device)
+        act = self.empty(T * K, inter, dtype=self.dtype, device=self.device)
+        yp = self.empty(T * K, H, dtype=torch.float32, device=self.device)
+        out = self.empty(T, H, dtype=torch.float32 if out_f32 else self.dtype, device=self.device)
         self.launches += 3
         self.C.moe_experts(out, act, yp, h, w_gu, w_down, ids, wts, e_lo, e_hi, shared,
                            None if shared_gate is None else shared_gate.reshape(-1).float().contiguous(), res)
@@ -366,7 +407,7 @@ class CudaOps:
         e, r, k = w.shape
         buf = self._expert_scratch.get(which)
         if buf is None or buf.numel() < e * r * k:
-            buf = torch.empty(e * r * k, dtype=self.dtype, device=self.device)
+            buf = self.empty(e * r * k, dtype=self.dtype, device=self.device)
             self._expert_scratch[which] = buf
         out = buf[:e * r * k].view(e, r, k)
         self.launches += 1
@@ -406,7 +447,7 @@ class CudaOps:
                   nq, nkv, hd, rot, gated, eps, kv_scale=None, row_cpos=None):
         """q/k RMSNorm + partial RoPE, K/V rows into the paged cache (bf16, or e4m3 codes + per-row scales when
         `kv_scale` is given). `row_cpos`: cache row of each row when it differs from its rotary position (trees)."""
-        q = torch.empty(proj.shape[0], nq, hd, dtype=self.dtype, device=self.device)
+        q = self.empty(proj.shape[0], nq, hd, dtype=self.dtype, device=self.device)
         self.launches += 1
         self.C.attn_prep(q, k_cache, v_cache, proj, q_norm, k_norm, inv_freq, row_slot, row_pos, block_table,
                          kv_block, nq, nkv, hd, rot, gated, eps, self.status_word, kv_scale, row_cpos)
@@ -418,9 +459,9 @@ class CudaOps:
         segment) and a bf16 cache the tensor-core kernel runs: the rows of a segment share one pass over the K/V of
         each kv head (bf16 and e4m3 caches). The 4-bit cache and callers without segment tables take the SIMT kernel."""
         T = q.shape[0]
-        out = torch.empty(T, nq * hd, dtype=self.dtype, device=self.device)
-        o_part = torch.empty(T, nq, nsplit, hd, dtype=torch.float32, device=self.device)
-        ml_part = torch.empty(T, nq, nsplit, 2, dtype=torch.float32, device=self.device)
+        out = self.empty(T, nq * hd, dtype=self.dtype, device=self.device)
+        o_part = self.empty(T, nq, nsplit, hd, dtype=torch.float32, device=self.device)
+        ml_part = self.empty(T, nq, nsplit, 2, dtype=torch.float32, device=self.device)
         self.launches += 2
         fp8_cache = kv_scale is not None and k_cache.shape[-1] == hd           # (the 4-bit cache has hd / 2 bytes per row)
         if segs is not None and (kv_scale is None or fp8_cache) and self.attn_mma and nq // nkv <= 64:
@@ -439,7 +480,7 @@ class CudaOps:
         """Causal flash attention over prompt segments (their K/V rows are already in the cache). With an e4m3 cache
         the visible rows are first decoded into a per-slot bf16 scratch that the kernel reads through an identity
         block table."""
-        out = torch.empty(q.shape[0], nq * hd, dtype=self.dtype, device=self.device)
+        out = self.empty(q.shape[0], nq * hd, dtype=self.dtype, device=self.device)
         if kv_scale is not None:
             n_slots, max_blocks = block_table.shape
             toks = max_blocks * kv_block
@@ -470,7 +511,7 @@ class CudaOps:
 
     # ---- gated delta net ---------------------------------------------------------------------------
     def gdn_conv(self, proj, conv_w, conv_state, seg_slot, seg_row0, seg_nrows, conv_dim, max_rows=None):
-        out = torch.empty(proj.shape[0], conv_dim, dtype=self.dtype, device=self.device)
+        out = self.empty(proj.shape[0], conv_dim, dtype=self.dtype, device=self.device)
         self.launches += 1
         self.C.gdn_conv(out, proj, conv_w, conv_state, seg_slot, seg_row0, seg_nrows,
                         proj.shape[0] if max_rows is None else max_rows)
@@ -478,7 +519,7 @@ class CudaOps:
 
     def gdn_conv_tree(self, proj, conv_w, conv_state, seg_slot, seg_row0, seg_nrows, conv_dim, row_parent):
         """Conv over verify-tree rows: a row's window is its three nearest ancestors, then the slot's saved tail."""
-        out = torch.empty(proj.shape[0], conv_dim, dtype=self.dtype, device=self.device)
+        out = self.empty(proj.shape[0], conv_dim, dtype=self.dtype, device=self.device)
         self.launches += 1
         self.C.gdn_conv_tree(out, proj, conv_w, conv_state, seg_slot, seg_row0, seg_nrows, row_parent)
         return out
@@ -488,10 +529,10 @@ class CudaOps:
         """Recurrence over verify-tree rows (read-only): every row starts from the state its parent left. Branch-point
         states are parked in a scratch of rows x heads x dk x dv floats that all layers share."""
         T = qkv.shape[0]
-        y = torch.empty(T, nv * dv, dtype=torch.float32, device=self.device)
+        y = self.empty(T, nv * dv, dtype=torch.float32, device=self.device)
         need = T * nv * dk * dv
         if self._tree_scratch is None or self._tree_scratch.numel() < need:
-            self._tree_scratch = torch.empty(need, dtype=torch.float32, device=self.device)
+            self._tree_scratch = self.empty(need, dtype=torch.float32, device=self.device)
         self.launches += 1
         self.C.gdn_rec_tree(y, rec_state, qkv, proj, A_log, dt_bias, seg_slot, seg_row0, seg_nrows, row_parent, row_flags,
                             self._tree_scratch, nk, nv, dk, dv, eps)
@@ -505,7 +546,7 @@ class CudaOps:
         happen inside the kernel) or None. Returns the output rows of every layer of the run."""
         M, H = x.shape
         e = self._dl_empty
-        mk = lambda n: torch.empty(M, n, dtype=self.dtype, device=self.device)
+        mk = lambda n: self.empty(M, n, dtype=self.dtype, device=self.device)
         cols = {k: [] for k in ("sp", "x_out", "x_mid", "act", "proj", "o", "w_in", "inorm", "w_out", "pnorm", "w_gu", "w_down",
                                 "rec", "conv", "conv_w", "A_log", "dt_bias", "gnorm")}
         for L in layers:
@@ -531,7 +572,7 @@ class CudaOps:
     def gdn_step(self, proj, conv_w, rec_state, conv_state, A_log, dt_bias, gnorm_w, seg_slot, seg_row0, seg_nrows, nk, nv,
                  dk, dv, eps, commit=True):
         """Decode rows: conv + recurrence + gated norm in one launch; returns bf16 [rows, nv * dv]."""
-        out = torch.empty(proj.shape[0], nv * dv, dtype=self.dtype, device=self.device)
+        out = self.empty(proj.shape[0], nv * dv, dtype=self.dtype, device=self.device)
         self.launches += 1
         self.C.gdn_step(out, rec_state, conv_state, proj, conv_w, A_log, dt_bias, gnorm_w, seg_slot, seg_row0, seg_nrows, nk,
                         nv, dk, dv, eps, commit)
@@ -539,11 +580,11 @@ class CudaOps:
 
     def gdn_rec(self, qkv, proj, rec_state, conv_state, A_log, dt_bias, seg_slot, seg_row0, seg_nrows, nk, nv, dk, dv,
                 eps, commit=True, chunked=False, max_rows=None):
-        y = torch.empty(qkv.shape[0], nv * dv, dtype=torch.float32, device=self.device)
+        y = self.empty(qkv.shape[0], nv * dv, dtype=torch.float32, device=self.device)
         if chunked and dk == 128 and dv % 16 == 0:
             nb = int(self.C.gdn_chunk_scratch_bytes(qkv.shape[0], seg_slot.numel(), nv, dk))
             if self._gdn_scratch is None or self._gdn_scratch.numel() < nb:
-                self._gdn_scratch = torch.empty(nb, dtype=torch.uint8, device=self.device)
+                self._gdn_scratch = self.empty(nb, dtype=torch.uint8, device=self.device)
             self.launches += 2
             self.C.gdn_chunk(y, rec_state, conv_state, self._gdn_scratch, qkv, proj, A_log, dt_bias, seg_slot, seg_row0,
                              seg_nrows, qkv.shape[0] if max_rows is None else max_rows, nk, nv, dk, dv, eps, commit)
@@ -556,7 +597,7 @@ class CudaOps:
     # ---- multi-head latent attention (absorbed form) ----------------------------------------------------
     def mla_prep(self, q, kva, norm_w, w_uk_t, inv_freq, row_slot, row_pos, block_table, cache, kv_block, nq, dn, L, R, eps):
         T = q.shape[0]
-        qabs = torch.empty(T, nq, L + R, dtype=self.dtype, device=self.device)
+        qabs = self.empty(T, nq, L + R, dtype=self.dtype, device=self.device)
         self.launches += 1
         self.C.mla_prep(cache, qabs, kva, q, norm_w, inv_freq, row_slot, row_pos, block_table, kv_block, nq, dn, L, R, eps,
                         self.status_word)
@@ -568,9 +609,9 @@ class CudaOps:
 
     def mla_attention(self, qabs, cache, row_slot, row_kvlen, block_table, kv_block, nq, L, R, scale, nsplit=1):
         T = qabs.shape[0]
-        out = torch.empty(T, nq, L, dtype=self.dtype, device=self.device)
-        o_part = torch.empty(T * nq * nsplit * L, dtype=torch.float32, device=self.device)
-        ml_part = torch.empty(T * nq * nsplit * 2, dtype=torch.float32, device=self.device)
+        out = self.empty(T, nq, L, dtype=self.dtype, device=self.device)
+        o_part = self.empty(T * nq * nsplit * L, dtype=torch.float32, device=self.device)
+        ml_part = self.empty(T * nq * nsplit * 2, dtype=torch.float32, device=self.device)
         self.launches += 2
         self.C.mla_attn(out, o_part, ml_part, qabs, cache, row_slot, row_kvlen, block_table, kv_block, nq, L, R, nsplit,
                         scale)
@@ -579,7 +620,7 @@ class CudaOps:
     def mla_out(self, ol, w_uv):
         T, nq, L = ol.shape
         dv = w_uv.shape[1]
-        o = torch.empty(T, nq * dv, dtype=self.dtype, device=self.device)
+        o = self.empty(T, nq * dv, dtype=self.dtype, device=self.device)
         for h in range(nq):
             self.linear(ol[:, h, :], w_uv[h], out=o[:, h * dv:(h + 1) * dv])
         return o
@@ -587,7 +628,7 @@ class CudaOps:
     # ---- drafter kernels ---------------------------------------------------------------------------
     def w4_gemv(self, x, qweight, scales, biases, res=None):
         """y = x W^T, W affine 4-bit in groups of 64: qweight uint32/int32 [N, K/8], scales / biases bf16 [N, K/64]."""
-        y = torch.empty(x.shape[0], qweight.shape[0], dtype=self.dtype, device=self.device)
+        y = self.empty(x.shape[0], qweight.shape[0], dtype=self.dtype, device=self.device)
         self.launches += 1
         self.C.w4_gemv(y, x, qweight, scales, biases, res)
         return y
@@ -597,8 +638,8 @@ class CudaOps:
         """Per-stream RMSNorm of the residual streams to bf16: returns (y [rows * hc, d], inv [rows * hc]); `w` [ngw, d]
         fp32, stream g uses row g % ngw."""
         rows, hc, d = res.shape
-        y = torch.empty(rows * hc, d, dtype=self.dtype, device=self.device)
-        inv = torch.empty(rows * hc, dtype=torch.float32, device=self.device)
+        y = self.empty(rows * hc, d, dtype=self.dtype, device=self.device)
+        inv = self.empty(rows * hc, dtype=torch.float32, device=self.device)
         self.launches += 1
         self.C.hc_norm(y, inv, res.view(rows * hc, d), w, eps)
         return y, inv
@@ -606,7 +647,7 @@ class CudaOps:
     def hc_mix(self, res, inv, w, gate):
         """mixed[r] = mean over streams of (normalised stream * w[s]) * sigmoid(gate[r][s]); fp32 [rows, d]."""
         rows, hc, d = res.shape
-        mixed = torch.empty(rows, d, dtype=torch.float32, device=self.device)
+        mixed = self.empty(rows, d, dtype=torch.float32, device=self.device)
         self.launches += 1
         self.C.hc_mix(mixed, res, inv, w, gate)
         return mixed
@@ -629,22 +670,22 @@ class CudaOps:
     def topk16_merge(self, vals, ids):
         """[W, rows, 16] per-rank top-16 lists (global ids) -> merged ([rows, 16] vals, ids), ties to the lower id."""
         W, rows, _ = vals.shape
-        ov = torch.empty(rows, 16, dtype=torch.float32, device=self.device)
-        oi = torch.empty(rows, 16, dtype=torch.int32, device=self.device)
+        ov = self.empty(rows, 16, dtype=torch.float32, device=self.device)
+        oi = self.empty(rows, 16, dtype=torch.int32, device=self.device)
         self.launches += 1
         self.C.topk16_merge(ov, oi, vals.contiguous(), ids.contiguous())
         return ov, oi
 
     def draft_select(self, vals, ids, gate, a_cb, b_cb, anchor):
         """Candidate selector walk: per drafted row pick argmax_c vals[c] + <A[pred] * gate, B[ids[c]]>, pred chained."""
-        out = torch.empty(vals.shape[0], dtype=torch.int32, device=self.device)
+        out = self.empty(vals.shape[0], dtype=torch.int32, device=self.device)
         self.launches += 1
         self.C.draft_select(out, vals, ids, gate, a_cb, b_cb, int(anchor))
         return out
 
     def topk16(self, logits):
-        ids = torch.empty(logits.shape[0], 16, dtype=torch.int32, device=self.device)
-        vals = torch.empty(logits.shape[0], 16, dtype=torch.float32, device=self.device)
+        ids = self.empty(logits.shape[0], 16, dtype=torch.int32, device=self.device)
+        vals = self.empty(logits.shape[0], 16, dtype=torch.float32, device=self.device)
         self.launches += 1
         self.C.topk16(ids, vals, logits)
         return ids, vals
@@ -652,20 +693,20 @@ class CudaOps:
     # ---- GGUF block formats ------------------------------------------------------------------------
     def gguf_dequant(self, raw, type_id, shape):
         """raw: uint8 tensor of GGUF blocks on the device -> bf16 tensor of `shape`."""
-        out = torch.empty(shape, dtype=torch.bfloat16, device=self.device)
+        out = self.empty(shape, dtype=torch.bfloat16, device=self.device)
         self.launches += 1
         self.C.gguf_dequant(out, raw, type_id)
         return out
 
     def gguf_gemv(self, x, raw, type_id, N, res=None):
         """y = x W^T for up to 8 rows with W [N, K] kept in its GGUF blocks."""
-        y = torch.empty(x.shape[0], N, dtype=torch.bfloat16, device=self.device)
+        y = self.empty(x.shape[0], N, dtype=torch.bfloat16, device=self.device)
         self.launches += 1
         self.C.gguf_gemv(y, x, raw, type_id, N, res)
         return y
 
     def q8_1_quant(self, x):
-        out = torch.empty(x.numel() // 32 * 36, dtype=torch.uint8, device=self.device)
+        out = self.empty(x.numel() // 32 * 36, dtype=torch.uint8, device=self.device)
         self.launches += 1
         self.C.q8_1_quant(out, x.contiguous())
         return out
@@ -683,16 +724,16 @@ class CudaOps:
             rec[i] = (sp.temperature, sp.top_p, sp.min_p, sp.presence_penalty, sp.frequency_penalty,
                       sp.repetition_penalty, sp.top_k, 0, int(seed) & 0xFFFFFFFFFFFFFFFF)
         params = torch.from_numpy(rec.view(np.uint8)).to(self.device)
-        ids = torch.empty(rows, dtype=torch.int32, device=self.device)
-        work = torch.empty(rows, vocab, dtype=torch.float32, device=self.device)
+        ids = self.empty(rows, dtype=torch.int32, device=self.device)
+        work = self.empty(rows, vocab, dtype=torch.float32, device=self.device)
         self.launches += 1
         self.C.sample(ids, logits, params, counts, work)
         return ids
 
     def argmax(self, logits):
-        ids = torch.empty(logits.shape[0], dtype=torch.int32, device=self.device)
-        finite = torch.empty(logits.shape[0], dtype=torch.int32, device=self.device)
-        scratch = torch.empty(logits.shape[0] * 64 * 3, dtype=torch.int32, device=self.device)
+        ids = self.empty(logits.shape[0], dtype=torch.int32, device=self.device)
+        finite = self.empty(logits.shape[0], dtype=torch.int32, device=self.device)
+        scratch = self.empty(logits.shape[0] * 64 * 3, dtype=torch.int32, device=self.device)
         self.launches += 2 if logits.shape[1] >= 8192 else 1
         self.C.argmax(ids, logits, None, finite, scratch)
         return ids, finite

@@ -673,3 +673,30 @@ def test_attention_decode_mma_fp8_cache(ops, hd, nq, nkv):
         b = ops.attention(q, proj, kc, vc, slot, kvlen, bt, kv_block, nq, nkv, hd, gated, nsplit=nsplit, kv_scale=sc)
         close(a, b)
     assert ops.status() == 0
+
+
+def test_determinism_over_cross_cta_hand_offs(capsys):
+    """Split-K sums, stream-K slots, split-KV combine and the chunked scan return the same bits run after run."""
+    from ferrite_b200.utils.detcheck import main
+    rc = main(["--reps", "6"])
+    out = capsys.readouterr().out
+    assert rc == 0, out
+
+
+def test_canary_padded_output_buffers_catch_a_stray_write(ops):
+    """Debug allocator: guard bytes around every output buffer; a decode-sized forward leaves them intact, a write one
+    element past a buffer is reported at the next check."""
+    ops.enable_canaries(True)
+    try:
+        x, w = rnd(3, 1024, seed=1), rnd(768, 1024, scale=0.05, seed=2)
+        y = ops.linear(x, w, res=rnd(3, 768, seed=3))
+        ops.silu_mul(rnd(3, 2 * 640, seed=4))
+        assert ops.check_canaries() >= 2
+        y = ops.linear(x, w)
+        flat = y.untyped_storage()
+        raw = torch.empty(0, dtype=torch.uint8, device=DEV).set_(flat)
+        raw[256 + y.numel() * y.element_size()] = 0          # the byte right behind the data
+        with pytest.raises(RuntimeError, match="canary"):
+            ops.check_canaries()
+    finally:
+        ops.enable_canaries(False)
