@@ -110,6 +110,10 @@ class Engine:
         if on_gpu:
             ops.fp4_act = self.ecfg.weight_dtype in ("nvfp4", "nvfp4-w4a4")
             ops.fp4_prompt = self.ecfg.weight_dtype == "nvfp4-w4a4"
+            if world > 1:
+                # a rank's shard of a projection is too small for the tensor-core kernel's fixed cost to pay: few-row
+                # steps take the SIMT GEMV, whose row-parallel form has the sum over ranks fused in
+                ops.fp4_terms = -1
         self.ops = ops
         self.tp = tp
         if tp is not None and tp.world > 1 and self.ecfg.seq_parallel and tp.sp_max is None:

@@ -162,7 +162,7 @@ class TensorParallel:
         fp4 = kind == "nvfp4"
         if kind in ("fp8b", "fp8") and M <= 8:
             w, kind = w.dense, None                      # few rows: the dequantised copy through the bf16 row kernels
-        if self.fused and M <= 8 and kind in (None, "nvfp4") and not (fp4 and getattr(ops, "fp4_act", False) and w.row_alpha is None):
+        if self.fused and M <= 8 and kind in (None, "nvfp4") and not (fp4 and getattr(ops, "fp4_act", False) and getattr(ops, "fp4_terms", 0) >= 0 and w.row_alpha is None):
             y = torch.empty(M, N, dtype=x.dtype, device=x.device)
             if fp4:
                 self.C.gemv_nvfp4_allreduce(self.comm, y, x, w.packed, w.gemv_scales, w.global_scale, res, w.row_alpha)

@@ -317,3 +317,25 @@ def test_persistent_decode_layer_matches_the_separate_kernels(ext, streams):
     assert engs[1].ops.launches < engs[0].ops.launches
     for e in engs:
         e.check()
+
+
+def test_128k_context_prefill_and_decode(ext):
+    """131072 tokens of context on one GPU (27B widths, 4 layers): chunked prefill, then decode rows whose attention
+    reads the whole cache through 64 key splits. The decode row at position 128K must agree with the same row computed
+    as the last row of a prompt chunk, and stay finite."""
+    cfg = scaled(hybrid_27b(), 4)
+    ctx = 131072
+    eng = Engine(cfg, None, EngineConfig(n_slots=2, max_ctx=ctx + 64, prefill_chunk=4096), device="cuda", seed=3)
+    prompt = _prompt(cfg, ctx + 1, seed=9)
+    for s in range(2):
+        eng.prefill(s, prompt[:ctx])
+    a, _, _ = eng.forward([Segment(0, ctx, prompt[ctx:], "last")])                       # one decode row
+    b, _, _ = eng.forward([Segment(1, ctx, prompt[ctx:] + [5, 6, 7, 8, 9, 10, 11, 12, 13], "all")], commit=False)   # first row of a verify segment
+    assert torch.isfinite(a).all() and torch.isfinite(b).all()
+    err = (a[0] - b[0]).abs().max().item()
+    assert err < 0.03 * a.abs().max().item() + 0.02, err
+    for i in range(3):
+        lg, picks, _ = eng.forward([Segment(0, ctx + 1 + i, [int(picks[0][0]) if i else 3], "last")])
+        assert torch.isfinite(lg).all()
+    assert eng.slot_len[0] == ctx + 4
+    eng.check()
