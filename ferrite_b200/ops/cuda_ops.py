@@ -54,8 +54,9 @@ class CudaOps:
         self.fp4_prompt = False             # ... for prompt-sized steps too (one NVFP4 rendering per activation row)
         self.fp4_terms = 3                  # few-row NVFP4 steps: NVFP4 renderings per activation row (0 = older fused kernel,
                                             # -1 = the SIMT GEMV with 16-bit activations)
-        self.fp4_tc_ctas = 1                # ... and CTAs per SM of that kernel
-        self.fp4_prefetch_mb = 48           # ... and how much of the next weight (`QWeight.next`) it asks L2 for as it drains
+        self.fp4_tc_ctas = int(os.environ.get("FB_FP4_CTAS", "2"))             # ... and CTAs per SM of that kernel
+        self.fp4_prefetch_mb = int(os.environ.get("FB_FP4_PREFETCH_MB", "48"))  # ... and how much of the next weight
+                                                                                # (`QWeight.next`) it asks L2 for as it drains
         self._sf_pool = {}
         self._scratch = {}
 
