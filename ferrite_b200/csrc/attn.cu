@@ -318,6 +318,8 @@ attn_decode_kernel(float* __restrict__ o_part, float* __restrict__ ml_part, cons
   }
 }
 
+constexpr int ATT_MAX_SPLITS = 1025;     // most key splits the combine kernel takes (1024), plus one slot for the sum
+
 // Merge the splits in split order, normalise, apply the sigmoid gate, write bf16 [rows][nq*HD].
 template <int HD>
 __global__ void attn_combine_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict__ o_part,
@@ -327,19 +329,33 @@ __global__ void attn_combine_kernel(__nv_bfloat16* __restrict__ out, const float
   pdl_wait();
   const int row = blockIdx.x, qh = blockIdx.y;
   const size_t pbase = ((size_t)row * nq + qh) * nsplit;
-  float M = -INFINITY;
-  for (int s = 0; s < nsplit; ++s) M = fmaxf(M, ml_part[(pbase + s) * 2]);
-  float L = 0.f;
-  for (int s = 0; s < nsplit; ++s) {
-    float ms = ml_part[(pbase + s) * 2];
-    if (ms != -INFINITY) L += ml_part[(pbase + s) * 2 + 1] * exp2f(ms - M);
+  // The first warp turns the splits' (max, sum) pairs into one weight per split (two dependent memory round trips for
+  // the whole kernel instead of three per thread); then every thread sums its dimensions over the splits in split order.
+  __shared__ float wgt[ATT_MAX_SPLITS];
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    float M = -INFINITY;
+    for (int s0 = lane; s0 < nsplit; s0 += 32) M = fmaxf(M, ml_part[(pbase + s0) * 2]);
+    M = warp_max(M);
+    for (int s0 = lane; s0 < nsplit; s0 += 32) {
+      const float ms = ml_part[(pbase + s0) * 2];
+      wgt[s0] = ms != -INFINITY ? exp2f(ms - M) : 0.f;
+    }
+    __syncwarp();
+    if (lane == 0) {                                       // the normaliser, summed in split order
+      float Ls = 0.f;
+      for (int s0 = 0; s0 < nsplit; ++s0) Ls += ml_part[(pbase + s0) * 2 + 1] * wgt[s0];
+      wgt[nsplit] = Ls;                                    // (nsplit < ATT_MAX_SPLITS is checked on the host)
+    }
   }
+  __syncthreads();
+  const float L = wgt[nsplit];
   const float inv = L > 0.f ? 1.f / L : 0.f;
   for (int d = threadIdx.x; d < HD; d += blockDim.x) {
     float acc = 0.f;
-    for (int s = 0; s < nsplit; ++s) {
-      float ms = ml_part[(pbase + s) * 2];
-      if (ms != -INFINITY) acc += o_part[(pbase + s) * HD + d] * exp2f(ms - M);
+    for (int s0 = 0; s0 < nsplit; ++s0) {
+      const float e = wgt[s0];
+      if (e != 0.f) acc += o_part[(pbase + s0) * HD + d] * e;
     }
     float v = acc * inv;
     if (gated) v *= sigmoidf_(bf2f(proj[(size_t)row * proj_stride + (size_t)qh * 2 * HD + HD + d]));
@@ -444,6 +460,7 @@ static int attn_prep_impl(void* q_out, void* k_cache, void* v_cache, float* kv_s
 extern "C" int fb_attn_combine(void* out, const float* o_part, const float* ml_part, const void* proj, long proj_stride,
                                int rows, int nq, int hd, int nsplit, int gated, cudaStream_t s) {
   if (rows <= 0) return 0;
+  if (nsplit < 1 || nsplit >= ATT_MAX_SPLITS) return -1;
   dim3 cgrid(rows, nq);
   int cthreads = hd >= 128 ? 128 : 64;
   if (hd == 256) launch_pdl(attn_combine_kernel<256>, dim3(cgrid), dim3(cthreads), (size_t)(0), s, (__nv_bfloat16*)out, o_part, ml_part, (const __nv_bfloat16*)proj, proj_stride, nq, nsplit, gated);
