@@ -1,0 +1,39 @@
+"""The engine's command line on the CPU engine: generate, logits, sched-test, park-test."""
+import json
+
+import torch
+
+from ferrite_b200 import cli
+from ferrite_b200.config import PRESETS, EngineConfig
+from ferrite_b200.engine.engine import Engine
+
+
+def _run(capsys, *argv):
+    rc = cli.main(list(argv) + ["--device", "cpu"])
+    return rc, json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+
+
+def test_generate_matches_engine_generate(capsys):
+    rc, out = _run(capsys, "generate", "--ids", "5,9,33,70,12", "--max-tokens", "6")
+    assert rc == 0 and out["prompt_tokens"] == 5 and out["new_tokens"] == 6
+    eng = Engine(PRESETS["tiny"](), None, EngineConfig(n_slots=1, max_ctx=256), device="cpu")
+    assert out["ids"] == eng.generate([5, 9, 33, 70, 12], 6)
+
+
+def test_logits_dump_is_chunk_invariant(capsys, tmp_path):
+    ids = tmp_path / "ids.txt"
+    ids.write_text(",".join(str(3 + 7 * i) for i in range(19)))
+    outs = []
+    for chunk in (4, 32):
+        path = tmp_path / f"l{chunk}.pt"
+        rc, out = _run(capsys, "logits", "--ids-file", str(ids), "--out", str(path), "--chunk", str(chunk))
+        assert rc == 0 and out["positions"] == 19 and out["finite"]
+        outs.append(torch.load(path)["logits"])
+    assert outs[0].shape == (19, PRESETS["tiny"]().vocab)
+    assert torch.allclose(outs[0], outs[1], atol=2e-4, rtol=1e-4)
+
+
+def test_sched_test_and_park_test_pass(capsys):
+    for argv in (["sched-test"], ["sched-test", "--spec", "4", "--slots", "2"], ["park-test"]):
+        rc, out = _run(capsys, *argv)
+        assert rc == 0 and out["ok"], out
