@@ -109,6 +109,13 @@ int fb_ag_gemm(void* Y, const void* W, const void* res, int M, int N, int K, lon
 int fb_gemm_grouped(void* Y, const void* X, const void* W, const int* tile_start, const int* row_base, int experts,
                     int max_rows, int N, int K, long ldx, long ldy, int mode, int* status, int sm_count, cudaStream_t s);
 
+// Y[g] = X[g] W[g]^T for `groups` problems of one shape: X [groups * rows][K], W [groups][N][K], Y [groups * rows][N]
+int fb_gemm_batched(void* Y, const void* X, const void* W, int groups, int rows, int N, int K, int* status, int sm_count,
+                    cudaStream_t s);
+// ---- head_linear.cu: one small linear per attention head over a few rows (strided x / y, W [heads][N][K]) ----
+int fb_head_linear(void* y, const void* x, const void* W, int T, int heads, int N, int K, long x_rs, long x_hs, long y_rs,
+                   long y_hs, cudaStream_t s);
+
 // ---- moe_ep.cu: expert-parallel MoE block (dispatch / grouped GEMMs / combine over peer memory) ----
 long fb_ep_workspace_bytes(int n_experts, int hidden, long cap_rows);
 long fb_ep_recv_offset(int n_experts, int hidden, long cap_rows);

@@ -358,6 +358,27 @@ void gemm_grouped(Tensor Y, Tensor X, Tensor W, Tensor tile_start, Tensor row_ba
                         status.data_ptr<int>(), 0, cur_stream()), "gemm_grouped");
 }
 
+void gemm_batched(Tensor Y, Tensor X, Tensor W, Tensor status) {
+  // X [groups, rows, K], W [groups, N, K], Y [groups, rows, N], all contiguous bf16
+  TORCH_CHECK(X.is_contiguous() && W.is_contiguous() && Y.is_contiguous() && X.dim() == 3 && W.dim() == 3 && Y.dim() == 3,
+              "gemm_batched: contiguous [groups, rows, K] x [groups, N, K] -> [groups, rows, N]");
+  TORCH_CHECK(X.size(0) == W.size(0) && X.size(2) == W.size(2) && Y.size(0) == X.size(0) && Y.size(1) == X.size(1) &&
+              Y.size(2) == W.size(1), "gemm_batched: shapes");
+  check(fb_gemm_batched(Y.data_ptr(), X.data_ptr(), W.data_ptr(), (int)X.size(0), (int)X.size(1), (int)W.size(1),
+                        (int)X.size(2), status.data_ptr<int>(), 0, cur_stream()), "gemm_batched");
+}
+
+void head_linear(Tensor y, Tensor x, Tensor W) {
+  // x [T, heads, >= K] and y [T, heads, >= N]: views with unit stride in the last dimension; W [heads, N, K] contiguous
+  TORCH_CHECK(x.dim() == 3 && y.dim() == 3 && W.dim() == 3 && W.is_contiguous() && x.stride(2) == 1 && y.stride(2) == 1,
+              "head_linear: layouts");
+  TORCH_CHECK(x.size(0) == y.size(0) && x.size(1) == W.size(0) && y.size(1) == W.size(0) && x.size(2) == W.size(2) &&
+              y.size(2) == W.size(1), "head_linear: shapes");
+  check(fb_head_linear(y.data_ptr(), x.data_ptr(), W.data_ptr(), (int)x.size(0), (int)W.size(0), (int)W.size(1),
+                       (int)W.size(2), (long)x.stride(0), (long)x.stride(1), (long)y.stride(0), (long)y.stride(1),
+                       cur_stream()), "head_linear");
+}
+
 void gguf_dequant(Tensor out, Tensor raw, int64_t type) {
   check(fb_gguf_dequant(out.data_ptr(), raw.data_ptr(), (int)type, (long)out.numel(), cur_stream()), "gguf_dequant");
 }
@@ -472,6 +493,8 @@ void register_ext(pybind11::module_& m) {
   m.def("ep_workspace_bytes", [](int64_t e, int64_t h, int64_t cap) { return (int64_t)fb_ep_workspace_bytes((int)e, (int)h, cap); });
   m.def("ep_moe", &ep_moe);
   m.def("gemm_grouped", &gemm_grouped);
+  m.def("gemm_batched", &gemm_batched);
+  m.def("head_linear", &head_linear);
   pybind11::class_<BigComm>(m, "BigComm");
   m.def("make_big_comm", &make_big_comm);
   m.def("big_workspace_bytes", [](int64_t world, int64_t max_rows, int64_t max_cols) {

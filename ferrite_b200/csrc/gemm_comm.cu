@@ -155,6 +155,7 @@ extern "C" int fb_gemm_grouped(void* Y, const void* X, const void* W, const int*
   GemmArgs& a = p.a;
   const int w_rows = a.dual ? 2 * N : N;
   a.gr.tile_start = tile_start; a.gr.row_base = row_base; a.gr.experts = experts; a.gr.w_rows = w_rows;
+  a.gr.uniform_rows = 0;
   a.Y = Y; a.res = nullptr; a.workspace = nullptr; a.counters = nullptr; a.status = status; a.ldy = ldy;
   a.M = max_rows;
   p.grid = sm_count;                               // the real tile count is only known on the device
@@ -162,6 +163,34 @@ extern "C" int fb_gemm_grouped(void* Y, const void* X, const void* W, const int*
   rc = make_tmap_bf16_2d(&tmA, X, (uint64_t)max_rows, (uint64_t)K, (uint64_t)ldx, GM_BM);
   if (rc) return rc;
   rc = make_tmap_bf16_2d(&tmB, W, (uint64_t)experts * w_rows, (uint64_t)K, (uint64_t)K, (uint32_t)a.b_box_rows);
+  if (rc) return rc;
+  return launch<3>(p, tmA, tmB, s);
+}
+
+// ---- batched GEMM: Y[g] = X[g] W[g]^T for `groups` problems of the same shape ---------------------------------------
+// X is [groups * rows][K] (group-major), W [groups][N][K], Y [groups * rows][N]: the grouped kernel with every group
+// `rows` long, so no prefix arrays and nothing computed on the device beforehand. Used for the per-head projections of
+// multi-head latent attention on prompt-sized steps (reference: one `mma` launch per head group,
+// `kernels/k-ds/src/attn.rs:151-548`).
+extern "C" int fb_gemm_batched(void* Y, const void* X, const void* W, int groups, int rows, int N, int K, int* status,
+                               int sm_count, cudaStream_t s) {
+  if (groups <= 0 || rows <= 0) return 0;
+  if (K % 8 || N % 8) return -1;
+  if (sm_count <= 0) sm_count = 148;
+  const long total = (long)groups * rows;
+  if (total > 0x7fffffffL) return -1;
+  GemmPlan p{};
+  int rc = plan_gemm(p, total > 64 ? (int)total : 65, N, K, 0, 1, sm_count);
+  if (rc) return rc;
+  GemmArgs& a = p.a;
+  a.gr.tile_start = nullptr; a.gr.row_base = nullptr; a.gr.experts = groups; a.gr.w_rows = N; a.gr.uniform_rows = rows;
+  a.Y = Y; a.res = nullptr; a.workspace = nullptr; a.counters = nullptr; a.status = status; a.ldy = N;
+  a.M = (int)total;
+  p.grid = sm_count;
+  CUtensorMap tmA, tmB;
+  rc = make_tmap_bf16_2d(&tmA, X, (uint64_t)total, (uint64_t)K, (uint64_t)K, GM_BM);
+  if (rc) return rc;
+  rc = make_tmap_bf16_2d(&tmB, W, (uint64_t)groups * N, (uint64_t)K, (uint64_t)K, (uint32_t)a.b_box_rows);
   if (rc) return rc;
   return launch<3>(p, tmA, tmB, s);
 }

@@ -62,6 +62,7 @@ struct GemmGroups {
   const int* row_base;      // [experts + 1] prefix sum of rows
   int experts;
   int w_rows;               // weight rows per expert in the stacked [experts * w_rows][K] matrix
+  int uniform_rows;         // > 0: every group has this many rows (batched GEMM); the two prefix arrays are not read
 };
 
 struct GemmArgs {
@@ -162,7 +163,9 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   // rows FIRST, they need no transfer). The ring is cut into two phases (own / not own) and each phase into groups of
   // `gs` row tiles; inside a group the row tiles vary fastest so the CTAs running together share weight panels.
   int seq0 = 0, n_first = 0, gs = 1, groups_first = 0, total_work = a.tiles_a * a.tiles_b * a.split_k;
-  if constexpr (COMM == 3) total_work = a.gr.tile_start[a.gr.experts] * a.tiles_b;
+  if constexpr (COMM == 3)
+    total_work = (a.gr.uniform_rows > 0 ? a.gr.experts * ((a.gr.uniform_rows + GM_BM - 1) / GM_BM)
+                                        : a.gr.tile_start[a.gr.experts]) * a.tiles_b;
   if constexpr (COMM == 1 || COMM == 2) {
     epoch = *reinterpret_cast<volatile uint32_t*>(&a.cm.ctr[0]) + 1;
     parity = (int)(epoch & 1u);
@@ -186,6 +189,13 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       ks = 0;
       ta = w / a.tiles_b;                              // global row tile; weight panels of one row tile run together
       tb = w % a.tiles_b;
+      if (a.gr.uniform_rows > 0) {
+        const int per = (a.gr.uniform_rows + GM_BM - 1) / GM_BM, g = ta / per;
+        g_row0 = g * a.gr.uniform_rows + (ta - g * per) * GM_BM;
+        g_row_end = min((g + 1) * a.gr.uniform_rows, a.M);
+        g_wrow = g * a.gr.w_rows;
+        return true;
+      }
       int lo = 0, hi = a.gr.experts;                   // last expert whose first tile is <= ta
       while (hi - lo > 1) {
         const int mid = (lo + hi) >> 1;

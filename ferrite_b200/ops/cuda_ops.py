@@ -603,10 +603,8 @@ class CudaOps:
         self.launches += 1
         self.C.mla_prep(cache, qabs, kva, q, norm_w, inv_freq, row_slot, row_pos, block_table, kv_block, nq, dn, L, R, eps,
                         self.status_word)
-        q3 = q.view(T, nq, dn + R)
-        flat = qabs.view(T, nq * (L + R))
-        for h in range(nq):                     # key up-projection folded into the query, one small linear per head
-            self.linear(q3[:, h, :dn], w_uk_t[h], out=flat[:, h * (L + R):h * (L + R) + L])
+        # key up-projection folded into the query: one small linear per head
+        self.head_linear(q.view(T, nq, dn + R)[:, :, :dn], w_uk_t, out=qabs[:, :, :L])
         return qabs
 
     def mla_attention(self, qabs, cache, row_slot, row_kvlen, block_table, kv_block, nq, L, R, scale, nsplit=1):
@@ -622,10 +620,26 @@ class CudaOps:
     def mla_out(self, ol, w_uv):
         T, nq, L = ol.shape
         dv = w_uv.shape[1]
-        o = self.empty(T, nq * dv, dtype=self.dtype, device=self.device)
-        for h in range(nq):
-            self.linear(ol[:, h, :], w_uv[h], out=o[:, h * dv:(h + 1) * dv])
-        return o
+        return self.head_linear(ol, w_uv).view(T, nq * dv)
+
+    def head_linear(self, x, W, out=None):
+        """y[t, h, :] = W[h] x[t, h, :]: x [T, heads, K] (a view with unit inner stride), W [heads, N, K]. Up to 8 rows:
+        one launch of the row kernel streams the stack once; more rows: head-major copies around one batched tcgen05
+        GEMM (every head a group of T rows)."""
+        T, nh, K = x.shape
+        N = W.shape[1]
+        y = out if out is not None else self.empty(T, nh, N, dtype=self.dtype, device=self.device)
+        if T <= 8 or K % 64 or N % 8 or nh * T < 256 or nh * N < 256:      # the GEMM's 128/256-row boxes fit the operands
+            self.launches += 1
+            self.C.head_linear(y, x, W)
+            return y
+        xh = self.empty(nh, T, K, dtype=self.dtype, device=self.device)
+        xh.copy_(x.transpose(0, 1))
+        yh = self.empty(nh, T, N, dtype=self.dtype, device=self.device)
+        self.launches += 3
+        self.C.gemm_batched(yh, xh, W, self.status_word)
+        y.copy_(yh.transpose(0, 1))
+        return y
 
     # ---- drafter kernels ---------------------------------------------------------------------------
     def w4_gemv(self, x, qweight, scales, biases, res=None):

@@ -285,6 +285,14 @@ class TorchOps:
         """ol [T, nq, L] latent-space outputs -> [T, nq * dv] through the per-head value up-projection [nq, dv, L]."""
         return torch.einsum("thl,hvl->thv", ol.float(), w_uv.float()).reshape(ol.shape[0], -1).to(self.dtype)
 
+    def head_linear(self, x, W, out=None):
+        """y[t, h, :] = W[h] x[t, h, :] for x [T, heads, K], W [heads, N, K]."""
+        y = torch.einsum("thk,hnk->thn", x.float(), W.float()).to(self.dtype)
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
+
     # ---- mixture of experts ---------------------------------------------------------------------------
     def moe_route(self, logits, bias, mode, top_k, n_groups, topk_groups, scale):
         from ..config import ModelConfig

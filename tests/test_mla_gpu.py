@@ -46,6 +46,27 @@ def test_mla_prep_and_attention(ops, L, R, nq, nsplit):
     assert (oa.float() - ob.float()).abs().max().item() < 2e-2
 
 
+@pytest.mark.parametrize("T", [1, 6, 8, 19, 300])
+@pytest.mark.parametrize("nh,N,K", [(16, 512, 128), (16, 128, 512), (4, 64, 32), (3, 40, 64)])
+def test_head_linear_row_kernel_and_batched_gemm(ops, T, nh, N, K):
+    """Per-head linears of the latent attention: <= 8 rows (and shapes the tensor-core tiles do not take) run the row
+    kernel, more rows the batched tcgen05 GEMM; x is a strided view (the query's nope part), y a strided slice."""
+    tops = TorchOps(DEV, torch.float32)
+    g = torch.Generator(device=DEV).manual_seed(T * 131 + N)
+    pad = 64
+    xfull = (torch.randn(T, nh, K + pad, generator=g, device=DEV)).to(torch.bfloat16)
+    W = (torch.randn(nh, N, K, generator=g, device=DEV) * K ** -0.5).to(torch.bfloat16)
+    x = xfull[:, :, :K]
+    want = tops.head_linear(x, W)
+    got = ops.head_linear(x, W)
+    err = (got.float() - want).abs().max().item()
+    assert err < 2e-2 * max(1.0, want.abs().max().item()), err
+    yfull = torch.full((T, nh, N + 24), 7.0, device=DEV, dtype=torch.bfloat16)
+    ops.head_linear(x, W, out=yfull[:, :, :N])
+    assert torch.equal(yfull[:, :, :N], got) and bool((yfull[:, :, N:] == 7.0).all())
+    assert ops.status() == 0
+
+
 def test_mla_engine_gpu(ext):
     from ferrite_b200.config import EngineConfig, tiny_mla
     from ferrite_b200.engine.engine import Engine
