@@ -153,6 +153,34 @@ int fb_hc_norm(void* y, float* rinv, const float* x, const float* w, int groups,
 int fb_hc_mix(float* mixed, const float* res, const float* rinv, const float* w, const float* gate, int rows, int d, int hc,
               cudaStream_t s);
 int fb_hc_combine(float* res, const float* out, const float* inj, int rows, int d, int hc, long ldi, cudaStream_t s);
+int fb_engram_gate(void* out, const void* h, const float* kvp, const void* kvb, const float* qk, int rows, int hc, int d,
+                   int world, float eps, cudaStream_t s);
+
+// ---- sparse_index.cu: compressor, indexer scores, exact top-k, candidate masks, selected-block tables ----
+int fb_comp_step(void* out, float* tail, const float* kvc, const float* sc, const int* row_slot, const int* row_pos, int rows,
+                 int ratio, int dim, int ring_len, cudaStream_t s);
+int fb_index_score(float* score, int ld, const void* q, const float* w, float scale, const void* keys, long key_stride,
+                   const int* row_slot, const int* row_len, const uint8_t* mask, int mask_ld, int mask_block, int rows, int nh,
+                   int D, cudaStream_t s);
+int fb_topk_select(int* sel, const float* score, int ld, int n, const int* row_n, int rows, int k, cudaStream_t s);
+int fb_block_max(float* bmax, int mask_ld, const float* score, int ld, const int* row_n, int rows, int bsize, cudaStream_t s);
+int fb_sel_to_mask(uint8_t* mask, int mask_ld, const int* sel, int rows, int k, cudaStream_t s);
+int fb_qsa_pool(void* pooled, const float* raw, const float* w, const int* pos0, const float* inv_freq, int blocks, int kp,
+                int D, int rot, float eps, cudaStream_t s);
+int fb_qsa_table(int* table, int* kvlen, const int* sel, const int* row_slot, const int* row_pos, const int* block_table,
+                 int max_blocks, int rows, int kp, int top, int* status, cudaStream_t s);
+
+// ---- dspark.cu: Markov head loop, confidence head, reductions over residual streams ----
+int fb_markov_bias(void* out, const void* head, const void* emb, const int* tok, const int* slot, int rows, int V, int rank,
+                   cudaStream_t s);
+int fb_markov_score(void* pair, const float* logits, long ld, const void* stage, const void* cache, const int* slot, int rows,
+                    int parts, int n, int col0, cudaStream_t s);
+int fb_markov_pick(int* draft, int* tok, int* slot, const void* pairs, const int* slot_of, int n_pairs, int rows, int stride,
+                   int step, int vocab, int* status, cudaStream_t s);
+int fb_conf_head(float* conf, const void* xc, const void* emb, const int* draft, const float* w, int streams, int steps, int d,
+                 int rank, int block, int stride, cudaStream_t s);
+int fb_stream_mean(void* out, long ld, const void* h, int rows, int hc, int dim, cudaStream_t s);
+int fb_stream_collapse(void* xc, const void* h, const float* pre, long pre_ld, int rows, int hc, int dim, cudaStream_t s);
 // block-drafter sublayers: grouped dynamic conv over a block, merge of per-rank top-16 lists, candidate selector walk
 int fb_dynconv(void* out, const void* x, const void* coef, long ldc, const void* base, void* res, int rows, int H, int group,
                int blk, cudaStream_t s);

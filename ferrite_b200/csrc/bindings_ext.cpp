@@ -379,6 +379,103 @@ void head_linear(Tensor y, Tensor x, Tensor W) {
                        cur_stream()), "head_linear");
 }
 
+// ---- sparse-attention selection, drafting heads, Engram gate -------------------------------------------------------
+using OptT = c10::optional<Tensor>;
+
+void engram_gate(Tensor out, Tensor h, OptT kvp, OptT kvb, Tensor qk, double eps) {
+  // h / out [rows, hc, d] bf16; kvb [rows, (hc + 1) d] bf16 or kvp [world, rows, (hc + 1) d] fp32; qk [hc, d] fp32
+  const int world = kvp.has_value() ? (int)kvp->size(0) : 0;
+  check(fb_engram_gate(out.data_ptr(), h.data_ptr(), world ? kvp->data_ptr<float>() : nullptr, cptr(kvb),
+                       qk.data_ptr<float>(), (int)h.size(0), (int)h.size(1), (int)h.size(2), world, (float)eps, cur_stream()),
+        "engram_gate");
+}
+
+void comp_step(Tensor out, Tensor tail, Tensor kvc, OptT sc, Tensor row_slot, Tensor row_pos, int64_t ratio) {
+  // tail [slots, ring_len, 2 dim] fp32; kvc / sc [rows, dim] fp32; out [rows, dim] bf16
+  check(fb_comp_step(out.data_ptr(), tail.data_ptr<float>(), kvc.data_ptr<float>(),
+                     sc.has_value() ? sc->data_ptr<float>() : nullptr, row_slot.data_ptr<int>(), row_pos.data_ptr<int>(),
+                     (int)kvc.size(0), (int)ratio, (int)kvc.size(1), (int)tail.size(1), cur_stream()), "comp_step");
+}
+
+void index_score(Tensor score, Tensor q, OptT w, double scale, Tensor keys, Tensor row_slot, Tensor row_len, OptT mask,
+                 int64_t mask_block) {
+  // score [rows, ld] fp32; q [rows, nh, D] bf16; w [rows, nh] fp32; keys [slots, entries, D] bf16; mask [rows, mask_ld] u8
+  TORCH_CHECK(q.is_contiguous() && keys.is_contiguous() && score.is_contiguous(), "index_score: contiguous tensors");
+  check(fb_index_score(score.data_ptr<float>(), (int)score.size(1), q.data_ptr(), w.has_value() ? w->data_ptr<float>() : nullptr,
+                       (float)scale, keys.data_ptr(), (long)keys.stride(0), row_slot.data_ptr<int>(), row_len.data_ptr<int>(),
+                       mask.has_value() ? mask->data_ptr<uint8_t>() : nullptr, mask.has_value() ? (int)mask->size(1) : 0,
+                       (int)mask_block, (int)q.size(0), (int)q.size(1), (int)q.size(2), cur_stream()), "index_score");
+}
+
+void topk_select(Tensor sel, Tensor score, OptT row_n) {
+  // sel [rows, k] int32; score [rows, ld] fp32; row_n [rows] int32 (entries that count; all when absent)
+  check(fb_topk_select(sel.data_ptr<int>(), score.data_ptr<float>(), (int)score.stride(0), (int)score.size(1),
+                       row_n.has_value() ? row_n->data_ptr<int>() : nullptr, (int)score.size(0), (int)sel.size(1), cur_stream()),
+        "topk_select");
+}
+
+void block_max(Tensor bmax, Tensor score, Tensor row_n, int64_t bsize) {
+  check(fb_block_max(bmax.data_ptr<float>(), (int)bmax.size(1), score.data_ptr<float>(), (int)score.stride(0),
+                     row_n.data_ptr<int>(), (int)score.size(0), (int)bsize, cur_stream()), "block_max");
+}
+
+void sel_to_mask(Tensor mask, Tensor sel) {
+  check(fb_sel_to_mask(mask.data_ptr<uint8_t>(), (int)mask.size(1), sel.data_ptr<int>(), (int)sel.size(0), (int)sel.size(1),
+                       cur_stream()), "sel_to_mask");
+}
+
+void qsa_pool(Tensor pooled, Tensor raw, Tensor w, Tensor pos0, Tensor inv_freq, double eps) {
+  // raw [blocks, kp, D] fp32 -> pooled [blocks, D] bf16
+  check(fb_qsa_pool(pooled.data_ptr(), raw.data_ptr<float>(), w.data_ptr<float>(), pos0.data_ptr<int>(),
+                    inv_freq.data_ptr<float>(), (int)raw.size(0), (int)raw.size(1), (int)raw.size(2),
+                    2 * (int)inv_freq.size(0), (float)eps, cur_stream()), "qsa_pool");
+}
+
+void qsa_table(Tensor table, Tensor kvlen, Tensor sel, Tensor row_slot, Tensor row_pos, Tensor block_table, int64_t kp,
+               Tensor status) {
+  // table [rows, top + 1], sel [rows, top]
+  TORCH_CHECK(table.size(1) == sel.size(1) + 1, "qsa_table: table holds top + 1 blocks per row");
+  check(fb_qsa_table(table.data_ptr<int>(), kvlen.data_ptr<int>(), sel.data_ptr<int>(), row_slot.data_ptr<int>(),
+                     row_pos.data_ptr<int>(), block_table.data_ptr<int>(), (int)block_table.size(1), (int)sel.size(0),
+                     (int)kp, (int)sel.size(1), status.data_ptr<int>(), cur_stream()), "qsa_table");
+}
+
+void markov_bias(Tensor out, Tensor head, Tensor emb, Tensor tok, Tensor slot) {
+  check(fb_markov_bias(out.data_ptr(), head.data_ptr(), emb.data_ptr(), tok.data_ptr<int>(), slot.data_ptr<int>(),
+                       (int)out.size(0), (int)head.size(0), (int)head.size(1), cur_stream()), "markov_bias");
+}
+
+void markov_score(Tensor pair, Tensor logits, Tensor stage, Tensor cache, Tensor slot, int64_t col0) {
+  // pair [parts, rows, 2] int32; logits [rows, >= n] fp32; stage [rows, n] / cache [slots, n] bf16
+  check(fb_markov_score(pair.data_ptr(), logits.data_ptr<float>(), (long)logits.stride(0), stage.data_ptr(), cache.data_ptr(),
+                        slot.data_ptr<int>(), (int)pair.size(1), (int)pair.size(0), (int)stage.size(1), (int)col0, cur_stream()),
+        "markov_score");
+}
+
+void markov_pick(Tensor draft, Tensor tok, Tensor slot, Tensor pairs, Tensor slot_of, int64_t step, Tensor status) {
+  // pairs [n_pairs, rows, 2]; draft [rows, stride]; step < 0 starts a loop from draft[:, 0]
+  check(fb_markov_pick(draft.data_ptr<int>(), tok.data_ptr<int>(), slot.data_ptr<int>(), pairs.data_ptr(),
+                       slot_of.data_ptr<int>(), (int)pairs.size(0), (int)draft.size(0), (int)draft.stride(0), (int)step,
+                       (int)slot_of.size(0), status.data_ptr<int>(), cur_stream()), "markov_pick");
+}
+
+void conf_head(Tensor conf, Tensor xc, Tensor emb, Tensor draft, Tensor w, int64_t steps, int64_t block) {
+  // conf [streams * steps]; xc [streams * block, d]; emb [vocab, rank]; draft [streams, stride]; w [d + rank] fp32
+  check(fb_conf_head(conf.data_ptr<float>(), xc.data_ptr(), emb.data_ptr(), draft.data_ptr<int>(), w.data_ptr<float>(),
+                     (int)draft.size(0), (int)steps, (int)xc.size(1), (int)emb.size(1), (int)block, (int)draft.stride(0),
+                     cur_stream()), "conf_head");
+}
+
+void stream_mean(Tensor out, Tensor h) {
+  check(fb_stream_mean(out.data_ptr(), (long)out.stride(0), h.data_ptr(), (int)h.size(0), (int)h.size(1), (int)h.size(2),
+                       cur_stream()), "stream_mean");
+}
+
+void stream_collapse(Tensor xc, Tensor h, Tensor pre) {
+  check(fb_stream_collapse(xc.data_ptr(), h.data_ptr(), pre.data_ptr<float>(), (long)pre.stride(0), (int)h.size(0),
+                           (int)h.size(1), (int)h.size(2), cur_stream()), "stream_collapse");
+}
+
 void gguf_dequant(Tensor out, Tensor raw, int64_t type) {
   check(fb_gguf_dequant(out.data_ptr(), raw.data_ptr(), (int)type, (long)out.numel(), cur_stream()), "gguf_dequant");
 }
@@ -478,6 +575,20 @@ void register_ext(pybind11::module_& m) {
   m.def("hc_norm", &hc_norm);
   m.def("hc_mix", &hc_mix);
   m.def("hc_combine", &hc_combine);
+  m.def("engram_gate", &engram_gate);
+  m.def("comp_step", &comp_step);
+  m.def("index_score", &index_score);
+  m.def("topk_select", &topk_select);
+  m.def("block_max", &block_max);
+  m.def("sel_to_mask", &sel_to_mask);
+  m.def("qsa_pool", &qsa_pool);
+  m.def("qsa_table", &qsa_table);
+  m.def("markov_bias", &markov_bias);
+  m.def("markov_score", &markov_score);
+  m.def("markov_pick", &markov_pick);
+  m.def("conf_head", &conf_head);
+  m.def("stream_mean", &stream_mean);
+  m.def("stream_collapse", &stream_collapse);
   m.def("topk16_merge", &topk16_merge);
   m.def("draft_select", &draft_select);
   m.def("mla_prep", &mla_prep);

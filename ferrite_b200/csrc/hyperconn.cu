@@ -4,9 +4,14 @@
 //   hc_norm     y[g][i]      = bf16(x[g][i] * inv_g * w[(g % ngw)][i]),  inv_g = rsqrt(mean_i x[g][i]^2 + eps),  g = row * hc + s
 //   hc_mix      mixed[r][i]  = mean_s( res[r][s][i] * inv[r * hc + s] * w[s][i] * sigmoid(gate[r][s][i]) )
 //   hc_combine  res[r][s][i] += out[r][i] * 2 * sigmoid(inj[r][s])
+//   engram_gate out[r][s][:] = bf16(h[r][s][:] + gate * value[r][:]),  gate = sigmoid(signed_sqrt(max(|dot|, 1e-6))),
+//               dot = <h[r][s] * qk[s], key[r][s]> * rstd(h[r][s]) * rstd(key[r][s]) / sqrt(d); key / value are the
+//               (hc + 1) slices of a memory lookup's projection, given summed (bf16) or as per-rank fp32 partials that
+//               are summed here in rank order and rounded to bf16 first
 //
 // Residual streams are fp32 (they accumulate over every block of the model). Counterparts of the reference's
-// `fx_hc_norm_bf16`, `fx_hc_mix_res` and `fx_hc_combine` (`kernels/k-fnext/src/fast.rs:1010,1039,768`); the models of this
+// `fx_hc_norm_bf16`, `fx_hc_mix_res` and `fx_hc_combine` (`kernels/k-fnext/src/fast.rs:1010,1039,768`) and `engram_gate`
+// (`kernels/k-engram/src/lib.rs:38`); the models of this
 // repo's presets do not use hyper-connections, the ops are provided for checkpoints of that family.
 #include "api_ext.h"
 #include "common.cuh"
@@ -60,9 +65,53 @@ __global__ void hc_combine_kernel(float* __restrict__ res, const float* __restri
   res[idx] += out[r * d + i] * 2.f * sigmoidf_(inj[r * ldi + s]);
 }
 
+// grid = (rows, hc), 256 threads. h / out [rows][hc][d] bf16; kvb bf16 [rows][(hc + 1) d] or kvp fp32 [world][rows][(hc + 1) d].
+__global__ void __launch_bounds__(256) engram_gate_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ h,
+                                                          const float* __restrict__ kvp, const __nv_bfloat16* __restrict__ kvb,
+                                                          const float* __restrict__ qk, int rows, int hc, int d, int world,
+                                                          float eps) {
+  __shared__ float red[3][32];
+  const int r = blockIdx.x, s = blockIdx.y;
+  const size_t wd = (size_t)(hc + 1) * d, part = (size_t)rows * wd;
+  auto kv_at = [&](size_t i) -> float {
+    if (world == 0) return __bfloat162float(kvb[(size_t)r * wd + i]);
+    float acc = kvp[(size_t)r * wd + i];
+    for (int k = 1; k < world; ++k) acc += kvp[(size_t)k * part + (size_t)r * wd + i];
+    return __bfloat162float(__float2bfloat16(acc));
+  };
+  const __nv_bfloat16* hrow = h + ((size_t)r * hc + s) * d;
+  float sh = 0.f, sk = 0.f, sd = 0.f;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    const float x = __bfloat162float(hrow[i]), k = kv_at((size_t)s * d + i);
+    sh = fmaf(x, x, sh);
+    sk = fmaf(k, k, sk);
+    sd = fmaf(x * qk[(size_t)s * d + i], k, sd);
+  }
+  sh = block_sum(sh, red[0]);
+  sk = block_sum(sk, red[1]);
+  sd = block_sum(sd, red[2]);
+  const float df = (float)d;
+  const float dot = sd * rsqrtf(sh / df + eps) * rsqrtf(sk / df + eps) * rsqrtf(df);
+  const float mag = sqrtf(fmaxf(fabsf(dot), 1e-6f));
+  const float gate = sigmoidf_(dot < 0.f ? -mag : mag);
+  __nv_bfloat16* orow = out + ((size_t)r * hc + s) * d;
+  for (int i = threadIdx.x; i < d; i += blockDim.x)
+    orow[i] = __float2bfloat16(__bfloat162float(hrow[i]) + gate * kv_at((size_t)hc * d + i));
+}
+
 }  // namespace fb
 
 using namespace fb;
+
+extern "C" int fb_engram_gate(void* out, const void* h, const float* kvp, const void* kvb, const float* qk, int rows, int hc,
+                              int d, int world, float eps, cudaStream_t s) {
+  if (rows <= 0) return 0;
+  if (hc < 1 || hc > 65535 || (world == 0 ? !kvb : !kvp)) return -1;
+  engram_gate_kernel<<<dim3(rows, hc), 256, 0, s>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)h, kvp,
+                                                    (const __nv_bfloat16*)kvb, qk, rows, hc, d, world, eps);
+  return (int)cudaGetLastError();
+}
+
 
 extern "C" int fb_hc_norm(void* y, float* rinv, const float* x, const float* w, int groups, int d, int ngw, float eps,
                           cudaStream_t s) {

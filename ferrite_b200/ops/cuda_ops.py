@@ -15,6 +15,7 @@ import os
 import torch
 
 from .._ext import load
+from .extras import CudaExtras
 from .qweight import Exl3Weight, ExpertsFP4, GgufWeight, QWeight, StackWeight
 
 GEMV_MAX_ROWS = 8
@@ -22,7 +23,7 @@ MOE_PAIR_ROWS = 64     # up to this many rows (the largest graph-captured step) 
                        # beyond as grouped GEMMs, which read the per-expert row counts on the host
 
 
-class CudaOps:
+class CudaOps(CudaExtras):
     name = "cuda"
 
     def __init__(self, device, dtype=torch.bfloat16):

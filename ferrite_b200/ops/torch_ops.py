@@ -12,12 +12,14 @@ from typing import Optional
 import torch
 import torch.nn.functional as F
 
+from .extras import TorchExtras
+
 
 def _softplus(x):
     return torch.where(x > 20, x, torch.log1p(torch.exp(torch.clamp(x, max=20.0))))
 
 
-class TorchOps:
+class TorchOps(TorchExtras):
     name = "torch"
 
     def __init__(self, device="cpu", dtype=torch.float32):
