@@ -56,6 +56,11 @@ int fb_gemm_nvfp4_fused(void* Y, const void* X, long ldx, const void* norm_w, fl
                         int split_k, int out_f32, float* workspace, int* counters, int* status, int sm_count,
                         cudaStream_t s);
 
+// gate|up GEMM + SwiGLU with the activation written as NVFP4 (codes, tiled scales, row scales) for the next GEMM
+int fb_gemm_nvfp4_swiglu_q(void* q_codes, void* q_sf, float* q_row_scale, float q_gs, const void* Xq, const void* x_sf,
+                           const float* row_scale, const void* Wq, const void* w_sf, float w_scale, int M, int N, int K,
+                           int* status, int sm_count, cudaStream_t s);
+
 // ---- gemv_nvfp4_tc.cu: few-row NVFP4 linear on the block-scaled tensor cores, activations as residual NVFP4 terms ----
 long fb_gemv_nvfp4_tc_workspace_bytes(int M, int N, int K, int dual, int terms, int sm_count, int ctas_per_sm);
 int fb_gemv_nvfp4_tc_terms(int M, int N, int K, int dual, int terms);

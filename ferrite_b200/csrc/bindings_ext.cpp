@@ -187,6 +187,19 @@ void gemm_nvfp4(Tensor Y, Tensor xq, Tensor x_sf, Tensor row_scale, Tensor wq, T
                       at::cuda::getCurrentDeviceProperties()->multiProcessorCount, cur_stream()), "gemm_nvfp4");
 }
 
+void gemm_nvfp4_swiglu_q(Tensor q_codes, Tensor q_sf, Tensor q_row_scale, double q_gs, Tensor xq, Tensor x_sf,
+                         Tensor row_scale, Tensor wq, Tensor w_sf, double w_scale, Tensor status) {
+  int M = (int)xq.size(0), K = (int)xq.size(1) * 2, N = (int)wq.size(0) / 2;
+  TORCH_CHECK(wq.size(1) * 2 == K && q_codes.size(0) == M && q_codes.size(1) * 2 == N && q_row_scale.numel() >= M,
+              "gemm_nvfp4_swiglu_q: shapes");
+  TORCH_CHECK(q_sf.numel() >= fb_nvfp4_sf_bytes(M, N), "gemm_nvfp4_swiglu_q: scale buffer too small");
+  check(fb_gemm_nvfp4_swiglu_q(q_codes.data_ptr(), q_sf.data_ptr(), q_row_scale.data_ptr<float>(), (float)q_gs, xq.data_ptr(),
+                               x_sf.data_ptr(), row_scale.data_ptr<float>(), wq.data_ptr(), w_sf.data_ptr(), (float)w_scale,
+                               M, N, K, status.data_ptr<int>(),
+                               at::cuda::getCurrentDeviceProperties()->multiProcessorCount, cur_stream()),
+        "gemm_nvfp4_swiglu_q");
+}
+
 void gemm_nvfp4_fused(Tensor Y, Tensor X, c10::optional<Tensor> norm_w, double eps, Tensor wq, Tensor w_sf,
                       double w_scale, c10::optional<Tensor> res, int64_t mode, int64_t split_k,
                       c10::optional<Tensor> workspace, c10::optional<Tensor> counters, c10::optional<Tensor> status) {
@@ -654,6 +667,7 @@ void register_ext(pybind11::module_& m) {
   m.def("gemm_nvfp4_workspace_bytes", &gemm_nvfp4_workspace_bytes);
   m.def("gemm_nvfp4", &gemm_nvfp4);
   m.def("gemm_nvfp4_fused", &gemm_nvfp4_fused);
+  m.def("gemm_nvfp4_swiglu_q", &gemm_nvfp4_swiglu_q);
   m.def("gemv_nvfp4_tc", &gemv_nvfp4_tc);
   m.def("gemv_nvfp4_tc_trace_set", &gemv_nvfp4_tc_trace_set);
   m.def("gemv_nvfp4_tc_workspace_bytes", &gemv_nvfp4_tc_workspace_bytes);

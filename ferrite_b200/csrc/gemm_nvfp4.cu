@@ -55,6 +55,12 @@ struct Q4Args {
   const __nv_bfloat16* norm_w;
   float eps;
   int out_f32;
+  // SwiGLU output re-quantised to NVFP4 by the epilogue (normal orientation): codes [M][N / 2], scales in the tiled
+  // layout of an A operand with K = N, one static global scale for every row
+  uint8_t* q_codes;
+  uint8_t* q_sf;
+  float* q_row_scale;
+  float q_gs;
 };
 
 __device__ __forceinline__ bool q4_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
@@ -385,7 +391,34 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
               float x = __uint_as_float(r0[j]) * alpha;
               v[j] = a.dual ? siluf_(x) * (__uint_as_float(r1[j]) * alpha) : x;
             }
-            if (n + 32 <= a.N) {
+            if (a.q_codes) {
+              // the next GEMM's A operand, written here: per 16 columns an e4m3 scale (block amax / 6 / global scale)
+              // and 8 bytes of e2m1 codes; this thread owns row m, so a block never straddles threads
+              const float inv_gs = 1.f / a.q_gs;
+              uint8_t* sf_row = a.q_sf + (size_t)(m / 128) * (a.N / 64) * Q4_SF_ATOM + (size_t)(m % 32) * 16 +
+                                (size_t)((m % 128) / 32) * 4;
+#pragma unroll
+              for (int blk = 0; blk < 2; ++blk) {
+                float bm = 0.f;
+#pragma unroll
+                for (int j = 0; j < 16; ++j) bm = fmaxf(bm, fabsf(v[blk * 16 + j]));
+                const __nv_fp8_storage_t sc8 = __nv_cvt_float_to_fp8(bm * inv_gs * (1.f / 6.f), __NV_SATFINITE, __NV_E4M3);
+                __half_raw hr = __nv_cvt_fp8_to_halfraw(sc8, __NV_E4M3);
+                const float scf = __half2float(*reinterpret_cast<__half*>(&hr));
+                const float inv = scf > 0.f ? 1.f / (scf * a.q_gs) : 0.f;
+                uint32_t packed[2] = {0, 0};
+#pragma unroll
+                for (int j = 0; j < 16; j += 2) {
+                  const float2 pr = make_float2(v[blk * 16 + j] * inv, v[blk * 16 + j + 1] * inv);
+                  const __nv_fp4x2_storage_t c2 = __nv_cvt_float2_to_fp4x2(pr, __NV_E2M1, cudaRoundNearest);
+                  packed[j / 8] |= (uint32_t)c2 << (8 * ((j / 2) % 4));
+                }
+                const int b = (n >> 4) + blk;
+                *reinterpret_cast<uint2*>(a.q_codes + (size_t)m * (a.N / 2) + (size_t)b * 8) = make_uint2(packed[0], packed[1]);
+                sf_row[(size_t)(b / 4) * Q4_SF_ATOM + (b % 4)] = sc8;
+              }
+              if (n == 0) a.q_row_scale[m] = a.q_gs;
+            } else if (n + 32 <= a.N) {
               if (a.res) {
                 const uint4* rp = reinterpret_cast<const uint4*>(a.res + (size_t)m * a.ldy + n);
 #pragma unroll
@@ -626,13 +659,16 @@ extern "C" long fb_gemm_nvfp4_workspace_bytes(int M, int N, int split_k) {
 static int gemm_nvfp4_impl(void* Y, const void* Xq, const void* x_sf, const float* row_scale, const void* Wq,
                            const void* w_sf, float w_scale, const void* res, int M, int N, int K, long ldy, int mode,
                            int split_k, float* workspace, int* counters, int* status, int sm_count, cudaStream_t s,
-                           const void* X16, long ldx, const void* norm_w, float eps, int out_f32) {
+                           const void* X16, long ldx, const void* norm_w, float eps, int out_f32,
+                           void* q_codes = nullptr, void* q_sf = nullptr, float* q_row_scale = nullptr, float q_gs = 0.f) {
   if (M <= 0 || N <= 0) return 0;
+  if (q_codes && (M <= 64 || mode != 1 || res || !q_sf || !q_row_scale || !(q_gs > 0.f))) return -1;
   if (K % Q4_BK || (ldy % 8 && M > 64)) return -1;
   if (sm_count <= 0) sm_count = 148;
   Q4Args a;
   a.fuseq = X16 != nullptr; a.X = (const __nv_bfloat16*)X16; a.ldx = ldx; a.norm_w = (const __nv_bfloat16*)norm_w;
   a.eps = eps; a.out_f32 = out_f32;
+  a.q_codes = (uint8_t*)q_codes; a.q_sf = (uint8_t*)q_sf; a.q_row_scale = q_row_scale; a.q_gs = q_gs;
   if (a.fuseq && (M > 8 || (ldx % 8))) return -1;
   if (out_f32 && M > 64) return -1;
   a.M = M; a.N = N; a.K = K; a.dual = mode == 1; a.swap = M <= 64;
@@ -715,4 +751,16 @@ extern "C" int fb_gemm_nvfp4_fused(void* Y, const void* X, long ldx, const void*
                                    int sm_count, cudaStream_t s) {
   return gemm_nvfp4_impl(Y, nullptr, nullptr, nullptr, Wq, w_sf, w_scale, res, M, N, K, ldy, mode, split_k, workspace,
                          counters, status, sm_count, s, X, ldx, norm_w, eps, out_f32);
+}
+
+// Prompt rows: gate|up GEMM + SwiGLU whose epilogue writes the activation already quantised for the down projection
+// (codes [M][N / 2], tiled scales of fb_nvfp4_sf_bytes(M, N) bytes, row_scale[m] = q_gs), instead of bf16 rows that a
+// second kernel would read back and quantise. `q_gs` is a static global scale (a checkpoint's input scale of the
+// down projection, or a default that puts block maxima of 6e-3 .. 168 on normal e4m3 scales). Counterpart of
+// `fe_gemm_nvfp4_swiglu` with its fp4 output (`kernels/k-fp4/src/lib.rs:747-764`).
+extern "C" int fb_gemm_nvfp4_swiglu_q(void* q_codes, void* q_sf, float* q_row_scale, float q_gs, const void* Xq,
+                                      const void* x_sf, const float* row_scale, const void* Wq, const void* w_sf,
+                                      float w_scale, int M, int N, int K, int* status, int sm_count, cudaStream_t s) {
+  return gemm_nvfp4_impl(q_codes, Xq, x_sf, row_scale, Wq, w_sf, w_scale, nullptr, M, N, K, N, 1, 1, nullptr, nullptr,
+                         status, sm_count, s, nullptr, 0, nullptr, 0.f, 0, q_codes, q_sf, q_row_scale, q_gs);
 }

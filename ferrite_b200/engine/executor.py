@@ -573,6 +573,8 @@ class Executor:
                 x = row(o, w[p + "out_proj"], x)
             if c.is_moe(i):
                 x = self._moe_ffn_sp(x, i, col, row) if sp else self._moe_ffn(x, i)
+            elif not sp and (self.tp is None or self.tp.world == 1):
+                x = ops.ffn(x, w[p + "gate_up"], w[p + "down"], w[p + "post_norm"], eps, x)
             else:
                 act = col(x, w[p + "gate_up"], w[p + "post_norm"], swiglu=True)
                 x = row(act, w[p + "down"], x)

@@ -56,6 +56,10 @@ class CudaOps(CudaExtras):
         self.fp4_terms = 3                  # few-row NVFP4 steps: NVFP4 renderings per activation row (0 = older fused kernel,
                                             # -1 = the SIMT GEMV with 16-bit activations)
         self.fp4_tc_ctas = int(os.environ.get("FB_FP4_CTAS", "2"))             # ... and CTAs per SM of that kernel
+        # prompt-sized FFN blocks: the gate|up GEMM's epilogue re-quantises the SwiGLU output for the down projection;
+        # static global scale of that activation (block maxima of 6e-3 .. 168 land on normal e4m3 scales)
+        self.fp4_fuse_requant = os.environ.get("FB_FP4_FUSE_REQUANT", "1") != "0"
+        self.fp4_act_gscale = 1.0 / 16.0
         self.fp4_prefetch_mb = int(os.environ.get("FB_FP4_PREFETCH_MB", "48"))  # ... and how much of the next weight
                                                                                 # (`QWeight.next`) it asks L2 for as it drains
         self._sf_pool = {}
@@ -354,6 +358,35 @@ class CudaOps(CudaExtras):
         self.C.gemm_nvfp4(y, xq, xsf, rs, w.packed, w.mma_scales, w.global_scale, res, 1 if swiglu else 0, split, ws,
                           cnt, self.status_word)
         return y
+
+    def ffn(self, x, w_gu, w_down, norm_w, eps, res):
+        """Dense FFN block: down(SwiGLU(gate|up(norm(x)))) + res. With NVFP4 weights on the block-scaled GEMMs and a
+        prompt-sized step the gate|up kernel's epilogue writes the activation already quantised for the down
+        projection (one static global scale, `fp4_act_gscale`): the bf16 activation never exists."""
+        M = x.shape[0]
+        if (self.fp4_fuse_requant and self.fp4_act and self.fp4_prompt and M > 64 and isinstance(w_gu, QWeight)
+                and isinstance(w_down, QWeight) and w_gu.kind == w_down.kind == "nvfp4" and w_gu.row_alpha is None
+                and w_down.row_alpha is None and w_gu.mma_scales is not None and w_down.mma_scales is not None
+                and w_gu.cols % 256 == 0 and w_down.cols % 256 == 0 and (w_gu.rows // 2) % 128 == 0
+                and w_down.rows % 8 == 0):
+            inter = w_gu.rows // 2
+            xq, xsf, rs = self.quant_nvfp4(x, norm_w, eps)
+            codes = self.empty(M, inter // 2, dtype=torch.uint8, device=self.device)
+            key = ((M + 127) // 128, inter, "act")
+            sf = self._sf_pool.get(key)
+            if sf is None:
+                sf = torch.zeros(int(self.C.nvfp4_sf_bytes(M, inter)), dtype=torch.uint8, device=self.device)
+                self._sf_pool[key] = sf
+            ars = self.empty(M, dtype=torch.float32, device=self.device)
+            gs = self.fp4_act_gscale
+            self.launches += 2
+            self.C.gemm_nvfp4_swiglu_q(codes, sf, ars, float(gs), xq, xsf, rs, w_gu.packed, w_gu.mma_scales, w_gu.global_scale,
+                                       self.status_word)
+            y = self.empty(M, w_down.rows, dtype=self.dtype, device=self.device)
+            self.C.gemm_nvfp4(y, codes, sf, ars, w_down.packed, w_down.mma_scales, w_down.global_scale, res, 0, 1, None,
+                              None, self.status_word)
+            return y
+        return self.linear(self.linear(x, w_gu, norm_w=norm_w, eps=eps, swiglu=True), w_down, res=res)
 
     def silu_mul(self, gu):
         out = self.empty(gu.shape[0], gu.shape[1] // 2, dtype=self.dtype, device=self.device)

@@ -287,6 +287,10 @@ class TorchOps(TorchExtras):
         """ol [T, nq, L] latent-space outputs -> [T, nq * dv] through the per-head value up-projection [nq, dv, L]."""
         return torch.einsum("thl,hvl->thv", ol.float(), w_uv.float()).reshape(ol.shape[0], -1).to(self.dtype)
 
+    def ffn(self, x, w_gu, w_down, norm_w, eps, res):
+        """Dense FFN block: down(SwiGLU(gate|up(norm(x)))) + res."""
+        return self.linear(self.linear(x, w_gu, norm_w=norm_w, eps=eps, swiglu=True), w_down, res=res)
+
     def head_linear(self, x, W, out=None):
         """y[t, h, :] = W[h] x[t, h, :] for x [T, heads, K], W [heads, N, K]."""
         y = torch.einsum("thk,hnk->thn", x.float(), W.float()).to(self.dtype)

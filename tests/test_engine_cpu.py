@@ -145,7 +145,7 @@ def test_op_profiler_counts_calls():
     rep = prof.report()
     prof.detach()
     n_layers = cfg.n_layers
-    assert rep["linear"]["calls"] >= 4 * n_layers and rep["linear"]["ms"] > 0
+    assert rep["linear"]["calls"] + 2 * rep["ffn"]["calls"] >= 4 * n_layers and rep["linear"]["ms"] > 0       # an ffn is two linears
     assert "attention" in rep or "attention_prefill" in rep
     assert eng.ex.profile is None
 

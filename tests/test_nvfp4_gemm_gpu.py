@@ -232,3 +232,39 @@ def test_engine_from_a_modelopt_nvfp4_checkpoint(ext, tmp_path, mode):
     kl = torch.nn.functional.kl_div(torch.log_softmax(got, -1), torch.log_softmax(want, -1), log_target=True,
                                     reduction="batchmean").item()
     assert kl < (0.3 if mode == "nvfp4-w4a4" else 2e-2), kl     # w4a4 also quantises the activations of prompt rows (one rendering)
+
+
+@pytest.mark.parametrize("M,H,I", [(65, 512, 256), (300, 1024, 1536), (2048, 5120, 17408)])
+def test_ffn_with_requantised_swiglu(ops, M, H, I):
+    """gate|up GEMM whose epilogue writes the SwiGLU output as NVFP4 (static global scale) + down GEMM on those codes:
+    (1) the codes decode to the SwiGLU of the first GEMM within fp4 rounding, (2) the block equals the down projection of
+    the decoded activation, (3) fused and unfused blocks agree within the quantisation noise of the activation."""
+    from ferrite_b200.ops.qweight import quantize_weight
+    x = rnd(M, H, seed=1)
+    norm_w = rnd(H, scale=0.1, seed=5)
+    w_gu, w_down = quantize_weight(rnd(2 * I, H, scale=H ** -0.5, seed=2)), quantize_weight(rnd(H, I, scale=I ** -0.5, seed=3))
+    res = rnd(M, H, seed=4)
+    xq, xsf, rs = ops.quant_nvfp4(x, norm_w, 1e-6)
+    codes = torch.empty(M, I // 2, dtype=torch.uint8, device=DEV)
+    sf = torch.zeros(int(ops.C.nvfp4_sf_bytes(M, I)), dtype=torch.uint8, device=DEV)
+    ars = torch.empty(M, dtype=torch.float32, device=DEV)
+    ops.C.gemm_nvfp4_swiglu_q(codes, sf, ars, ops.fp4_act_gscale, xq, xsf, rs, w_gu.packed, w_gu.mma_scales,
+                              w_gu.global_scale, ops.status_word)
+    act = decode_act(codes, sf, ars, M, I)
+    gu = decode_act(xq, xsf, rs, M, H) @ w_gu.dense.float().t()
+    want_act = torch.nn.functional.silu(gu[:, :I]) * gu[:, I:]
+    assert bool((ars == ops.fp4_act_gscale).all())
+    rel = (act - want_act).norm().item() / want_act.norm().item()
+    assert rel < 0.12, rel                                           # e2m1 with per-16 scales: about 9 % rms
+    y = ops.ffn(x, w_gu, w_down, norm_w, 1e-6, res)
+    want = act @ w_down.dense.float().t() + res.float()
+    err = (y.float() - want).abs().max().item() / want.abs().max().item()
+    assert err < 2e-2, err
+    ops.fp4_fuse_requant = False
+    try:
+        y2 = ops.ffn(x, w_gu, w_down, norm_w, 1e-6, res)
+    finally:
+        ops.fp4_fuse_requant = True
+    d = (y.float() - y2.float() ).norm().item() / (y2.float() - res.float()).norm().item()
+    assert d < 0.2, d
+    assert ops.status() == 0
