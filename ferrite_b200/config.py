@@ -253,7 +253,9 @@ class EngineConfig:
     attn_splits: int = 0               # 0 = pick from context length
     use_graphs: bool = True
     fused_layers: Optional[bool] = None   # plain decode rows: one persistent kernel per layer (None = when tensor parallel)
-    kv_dtype: str = "bf16"             # "bf16" | "fp8": e4m3 KV cache with one scale per (token, kv head)
+    # "bf16" | "fp8" (e4m3, one scale per (token, kv head)) | "int6" | "int4" (integer codes, one scale per 32 elements);
+    # "fp8h" / "int6h" / "int4h": the same with keys stored in a Walsh-Hadamard rotated basis
+    kv_dtype: str = "bf16"
     seq_parallel: bool = True          # TP prompts: row-sharded residual stream, all-gather/reduce-scatter fused into the GEMMs
     graph_max: int = 128               # LRU size of the CUDA-graph cache (reference GRAPH_MAX)
     spec_depth: int = 0

@@ -100,6 +100,19 @@ int fb_attn_decode_q4(void* out, float* o_part, float* ml_part, const void* q, c
 int fb_kv_dequant_q4(void* k_out, void* v_out, const void* k_cache4, const void* v_cache4, const float* kv_scale,
                      const int* seg_slot, const int* seg_pos0, const int* seg_nrows, const int* block_table, int max_blocks,
                      int kv_block, int nseg, int max_kvlen, int nkv, int hd, int scratch_tokens_per_slot, cudaStream_t s);
+// low-bit KV cache, general form (bits 4 or 6; `hrot`: keys stored / queries handed out Walsh-Hadamard rotated)
+int fb_attn_prep_qn(void* q_out, void* k_cache, void* v_cache, float* kv_scale, const void* proj, long proj_stride,
+                    const void* q_norm, const void* k_norm, const float* inv_freq, const int* row_slot, const int* row_pos,
+                    const int* row_cpos, const int* block_table, int max_blocks, int kv_block, int rows, int nq, int nkv,
+                    int hd, int rot, int gated, float eps, int* status, int bits, int hrot, cudaStream_t s);
+int fb_attn_decode_qn(void* out, float* o_part, float* ml_part, const void* q, const void* k_cache, const void* v_cache,
+                      const float* kv_scale, const void* proj, long proj_stride, const int* row_slot, const int* row_kvlen,
+                      const int* row_base, const unsigned long long* row_mask, const int* block_table, int max_blocks,
+                      int kv_block, int rows, int nq, int nkv, int hd, int nsplit, int gated, int bits, cudaStream_t s);
+int fb_kv_dequant_qn(void* k_out, void* v_out, const void* k_cache, const void* v_cache, const float* kv_scale,
+                     const int* seg_slot, const int* seg_pos0, const int* seg_nrows, const int* block_table, int max_blocks,
+                     int kv_block, int nseg, int max_kvlen, int nkv, int hd, int scratch_tokens_per_slot, int bits,
+                     cudaStream_t s);
 // tcgen05 / TMEM form (attn_prefill_tc.cu): hd 64/128/256 and kv_block a multiple of 64, else returns -20
 int fb_attn_prefill_tc(void* out, const void* q, const void* k_cache, const void* v_cache, const void* proj,
                        long proj_stride, const int* seg_slot, const int* seg_row0, const int* seg_nrows,

@@ -25,7 +25,7 @@ __global__ void attn_prep_kernel(__nv_bfloat16* __restrict__ q_out, void* __rest
                                  const int* __restrict__ row_slot, const int* __restrict__ row_pos,
                                  const int* __restrict__ row_cpos,
                                  const int* __restrict__ block_table, int max_blocks, int kv_block, int nq, int nkv,
-                                 int rot, int gated, float eps, int* status) {
+                                 int rot, int gated, float eps, int* status, int hrot) {
   pdl_launch_dependents();
   pdl_wait();
   constexpr int EPL = HD / 32;
@@ -63,6 +63,29 @@ __global__ void attn_prep_kernel(__nv_bfloat16* __restrict__ q_out, void* __rest
       v[j] = d < half ? (v[j] * cs - other * sn) : (v[j] * cs + other * sn);
     }
   }
+  if (hrot) {
+    // Walsh-Hadamard rotation of the head (queries and keys alike, so q . k is unchanged): it spreads a few large
+    // channels over all of them before the keys are quantised. Element d = lane * EPL + j: the low bits of d are
+    // register indices, the high five bits the lane. Values stay unrotated.
+#pragma unroll
+    for (int st = 1; st < EPL; st <<= 1) {
+#pragma unroll
+      for (int j = 0; j < EPL; ++j) {
+        if (!(j & st)) { const float a = v[j], b = v[j | st]; v[j] = a + b; v[j | st] = a - b; }
+      }
+    }
+#pragma unroll
+    for (int o2 = 1; o2 < 32; o2 <<= 1) {
+#pragma unroll
+      for (int j = 0; j < EPL; ++j) {
+        const float other = __shfl_xor_sync(0xffffffffu, v[j], o2);
+        v[j] = (lane & o2) ? other - v[j] : v[j] + other;
+      }
+    }
+    const float hs = rsqrtf((float)HD);
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) v[j] *= hs;
+  }
   if (is_q) {
     __nv_bfloat16* dst = q_out + ((size_t)row * nq + warp) * HD;
 #pragma unroll
@@ -77,7 +100,49 @@ __global__ void attn_prep_kernel(__nv_bfloat16* __restrict__ q_out, void* __rest
     const size_t tok = ((size_t)blk * kv_block + (cpos % kv_block)) * nkv + kvh;
     const size_t off = tok * HD;
     const __nv_bfloat16* vsrc = proj + (size_t)row * proj_stride + (size_t)nq * qw + (size_t)(nkv + kvh) * HD;
-    if (KVM == 2) {
+    if (KVM == 3) {
+      // 6-bit codes (value = (code - 32) * scale, scale = group amax / 31) with one fp32 scale per 32 elements, packed
+      // little-endian: element d of a row owns bits [6 d, 6 d + 6) of its hd * 3 / 4 bytes
+      constexpr int NG = HD / 32, GL = 32 / EPL;
+      unsigned char* kc6 = reinterpret_cast<unsigned char*>(k_cache_v) + tok * (HD * 3 / 4);
+      unsigned char* vc6 = reinterpret_cast<unsigned char*>(v_cache_v) + tok * (HD * 3 / 4);
+      float vv[EPL], ka = 0.f, va = 0.f;
+#pragma unroll
+      for (int j = 0; j < EPL; ++j) { vv[j] = bf2f(vsrc[lane * EPL + j]); ka = fmaxf(ka, fabsf(v[j])); va = fmaxf(va, fabsf(vv[j])); }
+#pragma unroll
+      for (int o2 = GL / 2; o2 > 0; o2 >>= 1) {
+        ka = fmaxf(ka, __shfl_xor_sync(0xffffffffu, ka, o2));
+        va = fmaxf(va, __shfl_xor_sync(0xffffffffu, va, o2));
+      }
+      const float ks = ka > 0.f ? ka / 31.f : 1.f, vs = va > 0.f ? va / 31.f : 1.f;
+      auto code = [](float x, float sc) { return (unsigned long long)(min(31, max(-32, __float2int_rn(x / sc))) + 32); };
+      unsigned long long kb = 0ull, vb = 0ull;
+#pragma unroll
+      for (int j = 0; j < EPL; ++j) { kb |= code(v[j], ks) << (6 * j); vb |= code(vv[j], vs) << (6 * j); }
+      if (EPL == 2) {
+        // 12 bits per lane: an even lane writes its own and its right neighbour's codes as three bytes
+        const unsigned long long ko = __shfl_down_sync(0xffffffffu, kb, 1), vo = __shfl_down_sync(0xffffffffu, vb, 1);
+        kb |= ko << 12; vb |= vo << 12;
+        if (!(lane & 1)) {
+#pragma unroll
+          for (int b = 0; b < 3; ++b) {
+            kc6[lane / 2 * 3 + b] = (unsigned char)(kb >> (8 * b));
+            vc6[lane / 2 * 3 + b] = (unsigned char)(vb >> (8 * b));
+          }
+        }
+      } else {
+        constexpr int NB = EPL * 6 / 8;                     // 3 bytes (4 elements) or 6 bytes (8 elements) per lane
+#pragma unroll
+        for (int b = 0; b < NB; ++b) {
+          kc6[lane * NB + b] = (unsigned char)(kb >> (8 * b));
+          vc6[lane * NB + b] = (unsigned char)(vb >> (8 * b));
+        }
+      }
+      if (lane % GL == 0) {
+        kv_scale[tok * 2 * NG + lane / GL] = ks;
+        kv_scale[tok * 2 * NG + NG + lane / GL] = vs;
+      }
+    } else if (KVM == 2) {
       // 4-bit codes (value = (code - 8) * scale) with one fp32 scale per 32 elements: scales of a (token, kv head) row
       // are [K groups | V groups]
       constexpr int NG = HD / 32, GL = 32 / EPL;                 // groups per row, lanes per group
@@ -206,7 +271,14 @@ attn_decode_kernel(float* __restrict__ o_part, float* __restrict__ ml_part, cons
         const int blk = bt[t / kv_block];
         const size_t tok = ((size_t)blk * kv_block + (t % kv_block)) * nkv + kvh;
         const size_t off = tok * HD + sub * 8;
-        if (KVM == 2) {
+        if (KVM == 3) {
+          constexpr int NG = HD / 32;
+          const unsigned short* kp = reinterpret_cast<const unsigned short*>(reinterpret_cast<const unsigned char*>(k_cache_v) + tok * (HD * 3 / 4) + sub * 6);
+          const unsigned short* vp = reinterpret_cast<const unsigned short*>(reinterpret_cast<const unsigned char*>(v_cache_v) + tok * (HD * 3 / 4) + sub * 6);
+          kraw[u] = make_uint4((uint32_t)__ldg(kp) | ((uint32_t)__ldg(kp + 1) << 16), (uint32_t)__ldg(kp + 2), 0, 0);
+          vraw[u] = make_uint4((uint32_t)__ldg(vp) | ((uint32_t)__ldg(vp + 1) << 16), (uint32_t)__ldg(vp + 2), 0, 0);
+          sc2[u] = make_float2(kv_scale[tok * 2 * NG + sub / 4], kv_scale[tok * 2 * NG + NG + sub / 4]);
+        } else if (KVM == 2) {
           constexpr int NG = HD / 32;
           kraw[u] = make_uint4(__ldg(reinterpret_cast<const unsigned int*>(reinterpret_cast<const unsigned char*>(k_cache_v) + off / 2)), 0, 0, 0);
           vraw[u] = make_uint4(__ldg(reinterpret_cast<const unsigned int*>(reinterpret_cast<const unsigned char*>(v_cache_v) + off / 2)), 0, 0, 0);
@@ -228,7 +300,15 @@ attn_decode_kernel(float* __restrict__ o_part, float* __restrict__ ml_part, cons
       const bool vis = visb[u];
       uint32_t ku[4] = {kraw[u].x, kraw[u].y, kraw[u].z, kraw[u].w}, vu[4] = {vraw[u].x, vraw[u].y, vraw[u].z, vraw[u].w};
       float kf[8], vf[8];
-      if (KVM == 2) {
+      if (KVM == 3) {
+        const unsigned long long kb = (unsigned long long)ku[0] | ((unsigned long long)ku[1] << 32);
+        const unsigned long long vb = (unsigned long long)vu[0] | ((unsigned long long)vu[1] << 32);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          kf[j] = vis ? (float)((int)((kb >> (6 * j)) & 63ull) - 32) * sc2[u].x : 0.f;
+          vf[j] = vis ? (float)((int)((vb >> (6 * j)) & 63ull) - 32) * sc2[u].y : 0.f;
+        }
+      } else if (KVM == 2) {
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           kf[j] = vis ? (float)((int)((ku[0] >> (4 * j)) & 15u) - 8) * sc2[u].x : 0.f;
@@ -381,7 +461,20 @@ __global__ void kv_dequant_kernel(__nv_bfloat16* __restrict__ k_out, __nv_bfloat
   const size_t tok = ((size_t)blk * kv_block + (t % kv_block)) * nkv + kvh;
   const size_t dst = (((size_t)slot * scratch_tokens_per_slot + t) * nkv + kvh) * hd + threadIdx.x * 8;
   float kf[8], vf[8], ks, vs;
-  if (bits == 4) {
+  if (bits == 6) {
+    const int ng = hd / 32;
+    ks = kv_scale[tok * 2 * ng + threadIdx.x / 4];
+    vs = kv_scale[tok * 2 * ng + ng + threadIdx.x / 4];
+    const unsigned short* kp = reinterpret_cast<const unsigned short*>(k8 + tok * (hd * 3 / 4) + threadIdx.x * 6);
+    const unsigned short* vp = reinterpret_cast<const unsigned short*>(v8 + tok * (hd * 3 / 4) + threadIdx.x * 6);
+    const unsigned long long kb = (unsigned long long)kp[0] | ((unsigned long long)kp[1] << 16) | ((unsigned long long)kp[2] << 32);
+    const unsigned long long vb = (unsigned long long)vp[0] | ((unsigned long long)vp[1] << 16) | ((unsigned long long)vp[2] << 32);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      kf[j] = (float)((int)((kb >> (6 * j)) & 63ull) - 32);
+      vf[j] = (float)((int)((vb >> (6 * j)) & 63ull) - 32);
+    }
+  } else if (bits == 4) {
     const int ng = hd / 32;
     ks = kv_scale[tok * 2 * ng + threadIdx.x / 4];
     vs = kv_scale[tok * 2 * ng + ng + threadIdx.x / 4];
@@ -433,7 +526,7 @@ static int attn_prep_impl(void* q_out, void* k_cache, void* v_cache, float* kv_s
                           const void* q_norm, const void* k_norm, const float* inv_freq, const int* row_slot,
                           const int* row_pos, const int* row_cpos, const int* block_table, int max_blocks, int kv_block,
                           int rows, int nq, int nkv, int hd, int rot, int gated, float eps, int* status, cudaStream_t s,
-                          int bits = 8) {
+                          int bits = 8, int hrot = 0) {
   if (rows <= 0) return 0;
   const int heads = nq + nkv;
   const int threads = 32 * (heads < 32 ? heads : 32);
@@ -444,8 +537,10 @@ static int attn_prep_impl(void* q_out, void* k_cache, void* v_cache, float* kv_s
   launch_pdl(attn_prep_kernel<HDV, K8>, dim3(rows, hgroups), dim3(threads), (size_t)(0), s, (__nv_bfloat16*)q_out, k_cache, v_cache, \
       kv_scale, (const __nv_bfloat16*)proj, proj_stride, (const __nv_bfloat16*)q_norm,                            \
       (const __nv_bfloat16*)k_norm, inv_freq, row_slot, row_pos, row_cpos, block_table, max_blocks, kv_block, nq, nkv, rot, \
-      gated, eps, status)
-  if (kv_scale && bits == 4) {
+      gated, eps, status, hrot)
+  if (kv_scale && bits == 6) {
+    if (hd == 256) FB_PREP(256, 3); else if (hd == 128) FB_PREP(128, 3); else if (hd == 64) FB_PREP(64, 3); else return -2;
+  } else if (kv_scale && bits == 4) {
     if (hd == 256) FB_PREP(256, 2); else if (hd == 128) FB_PREP(128, 2); else if (hd == 64) FB_PREP(64, 2); else return -2;
   } else if (kv_scale) {
     if (hd == 256) FB_PREP(256, 1); else if (hd == 128) FB_PREP(128, 1); else if (hd == 64) FB_PREP(64, 1); else return -2;
@@ -483,7 +578,9 @@ static int attn_decode_impl(void* out, float* o_part, float* ml_part, const void
   float scale_log2 = 1.4426950408889634f / sqrtf((float)hd);
   int rc;
 #define FB_DEC(HDV, K8) rc = launch_decode<HDV, K8>(G, grid, smem, s, o_part, ml_part, q, k_cache, v_cache, kv_scale, row_slot, row_kvlen, row_base, row_mask, block_table, max_blocks, kv_block, nq, nkv, nsplit, scale_log2)
-  if (kv_scale && bits == 4) {
+  if (kv_scale && bits == 6) {
+    if (hd == 256) FB_DEC(256, 3); else if (hd == 128) FB_DEC(128, 3); else if (hd == 64) FB_DEC(64, 3); else return -2;
+  } else if (kv_scale && bits == 4) {
     if (hd == 256) FB_DEC(256, 2); else if (hd == 128) FB_DEC(128, 2); else if (hd == 64) FB_DEC(64, 2); else return -2;
   } else if (kv_scale) {
     if (hd == 256) FB_DEC(256, 1); else if (hd == 128) FB_DEC(128, 1); else if (hd == 64) FB_DEC(64, 1); else return -2;
@@ -589,6 +686,44 @@ extern "C" int fb_kv_dequant_q4(void* k_out, void* v_out, const void* k_cache4, 
   kv_dequant_kernel<<<dim3(max_kvlen, nkv, nseg), hd / 8, 0, s>>>((__nv_bfloat16*)k_out, (__nv_bfloat16*)v_out,
       (const unsigned char*)k_cache4, (const unsigned char*)v_cache4, kv_scale, seg_slot, seg_pos0, seg_nrows, block_table,
       max_blocks, kv_block, nkv, hd, scratch_tokens_per_slot, 4);
+  return (int)cudaGetLastError();
+}
+
+// ---- low-bit KV cache, general form: bits = 4 (codes [..][hd / 2]) or 6 (codes [..][hd * 3 / 4], value = (code - 32) *
+// scale), one fp32 scale per 32 elements in both; `hrot` != 0 stores keys (and hands out queries) in a Walsh-Hadamard
+// rotated basis. Counterpart of the reference's 6-bit records and rotated 4-bit records (`kernels/k-core/src/kvq.rs:95,126`).
+extern "C" int fb_attn_prep_qn(void* q_out, void* k_cache, void* v_cache, float* kv_scale, const void* proj,
+                               long proj_stride, const void* q_norm, const void* k_norm, const float* inv_freq,
+                               const int* row_slot, const int* row_pos, const int* row_cpos, const int* block_table,
+                               int max_blocks, int kv_block, int rows, int nq, int nkv, int hd, int rot, int gated,
+                               float eps, int* status, int bits, int hrot, cudaStream_t s) {
+  if ((bits == 4 || bits == 6) && !kv_scale) return -4;
+  if (bits != 4 && bits != 6 && bits != 8 && bits != 16) return -1;
+  return attn_prep_impl(q_out, k_cache, v_cache, bits == 16 ? nullptr : kv_scale, proj, proj_stride, q_norm, k_norm, inv_freq,
+                        row_slot, row_pos, row_cpos, block_table, max_blocks, kv_block, rows, nq, nkv, hd, rot, gated, eps,
+                        status, s, bits, hrot);
+}
+
+extern "C" int fb_attn_decode_qn(void* out, float* o_part, float* ml_part, const void* q, const void* k_cache,
+                                 const void* v_cache, const float* kv_scale, const void* proj, long proj_stride,
+                                 const int* row_slot, const int* row_kvlen, const int* row_base,
+                                 const unsigned long long* row_mask, const int* block_table, int max_blocks,
+                                 int kv_block, int rows, int nq, int nkv, int hd, int nsplit, int gated, int bits,
+                                 cudaStream_t s) {
+  if (!kv_scale || (bits != 4 && bits != 6)) return -4;
+  return attn_decode_impl(out, o_part, ml_part, q, k_cache, v_cache, kv_scale, proj, proj_stride, row_slot, row_kvlen,
+                          row_base, row_mask, block_table, max_blocks, kv_block, rows, nq, nkv, hd, nsplit, gated, s, bits);
+}
+
+extern "C" int fb_kv_dequant_qn(void* k_out, void* v_out, const void* k_cache, const void* v_cache, const float* kv_scale,
+                                const int* seg_slot, const int* seg_pos0, const int* seg_nrows, const int* block_table,
+                                int max_blocks, int kv_block, int nseg, int max_kvlen, int nkv, int hd,
+                                int scratch_tokens_per_slot, int bits, cudaStream_t s) {
+  if (nseg <= 0 || max_kvlen <= 0) return 0;
+  if (hd % 32 || max_kvlen > scratch_tokens_per_slot || (bits != 4 && bits != 6)) return -1;
+  kv_dequant_kernel<<<dim3(max_kvlen, nkv, nseg), hd / 8, 0, s>>>((__nv_bfloat16*)k_out, (__nv_bfloat16*)v_out,
+      (const unsigned char*)k_cache, (const unsigned char*)v_cache, kv_scale, seg_slot, seg_pos0, seg_nrows, block_table,
+      max_blocks, kv_block, nkv, hd, scratch_tokens_per_slot, bits);
   return (int)cudaGetLastError();
 }
 

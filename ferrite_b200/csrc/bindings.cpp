@@ -129,7 +129,22 @@ void gemm_fp8(Tensor Y, Tensor Xq, Tensor Wq, c10::optional<Tensor> scale_m, c10
 void attn_prep(Tensor q_out, Tensor k_cache, Tensor v_cache, Tensor proj, Tensor q_norm, Tensor k_norm,
                Tensor inv_freq, Tensor row_slot, Tensor row_pos, Tensor block_table, int64_t kv_block, int64_t nq,
                int64_t nkv, int64_t hd, int64_t rot, bool gated, double eps, c10::optional<Tensor> status,
-               c10::optional<Tensor> kv_scale, c10::optional<Tensor> row_cpos) {
+               c10::optional<Tensor> kv_scale, c10::optional<Tensor> row_cpos, int64_t hrot) {
+  const bool scaled = kv_scale.has_value() && kv_scale->defined();
+  const bool bytes = k_cache.scalar_type() == torch::kByte;
+  // a byte cache with hd * 3 / 4 bytes per head row is the 6-bit form; any form can keep its keys Hadamard-rotated
+  const bool six = scaled && bytes && k_cache.size(3) * 4 == hd * 3;
+  if (six || hrot) {
+    const int bits = six ? 6 : (scaled && bytes && k_cache.size(3) * 2 == hd) ? 4 : scaled ? 8 : 16;
+    check(fb_attn_prep_qn(q_out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+                          scaled ? kv_scale->data_ptr<float>() : nullptr, proj.data_ptr(), (long)proj.stride(0),
+                          q_norm.data_ptr(), k_norm.data_ptr(), inv_freq.data_ptr<float>(), row_slot.data_ptr<int>(),
+                          row_pos.data_ptr<int>(), (const int*)cptr(row_cpos), block_table.data_ptr<int>(),
+                          (int)block_table.size(1), (int)kv_block, (int)row_slot.numel(), (int)nq, (int)nkv, (int)hd,
+                          (int)rot, gated ? 1 : 0, (float)eps, (int*)mptr(status), bits, (int)hrot, cur_stream()),
+          "attn_prep_qn");
+    return;
+  }
   // a byte cache with hd/2 bytes per head row is the 4-bit form
   if (kv_scale.has_value() && kv_scale->defined() && k_cache.scalar_type() == torch::kByte && k_cache.size(3) * 2 == hd) {
     check(fb_attn_prep_q4(q_out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), kv_scale->data_ptr<float>(),
@@ -170,6 +185,16 @@ void attn_decode(Tensor out, Tensor o_part, Tensor ml_part, Tensor q, Tensor k_c
                  Tensor row_slot, Tensor row_kvlen, c10::optional<Tensor> row_base, c10::optional<Tensor> row_mask,
                  Tensor block_table, int64_t kv_block, int64_t nq, int64_t nkv, int64_t hd, int64_t nsplit,
                  bool gated, c10::optional<Tensor> kv_scale) {
+  if (kv_scale.has_value() && kv_scale->defined() && k_cache.scalar_type() == torch::kByte && k_cache.size(3) * 4 == hd * 3) {
+    check(fb_attn_decode_qn(out.data_ptr(), o_part.data_ptr<float>(), ml_part.data_ptr<float>(), q.data_ptr(),
+                            k_cache.data_ptr(), v_cache.data_ptr(), kv_scale->data_ptr<float>(), proj.data_ptr(),
+                            (long)proj.stride(0), row_slot.data_ptr<int>(), row_kvlen.data_ptr<int>(),
+                            (const int*)cptr(row_base), (const unsigned long long*)cptr(row_mask),
+                            block_table.data_ptr<int>(), (int)block_table.size(1), (int)kv_block,
+                            (int)row_slot.numel(), (int)nq, (int)nkv, (int)hd, (int)nsplit, gated ? 1 : 0, 6, cur_stream()),
+          "attn_decode_q6");
+    return;
+  }
   if (kv_scale.has_value() && kv_scale->defined() && k_cache.scalar_type() == torch::kByte && k_cache.size(3) * 2 == hd) {
     check(fb_attn_decode_q4(out.data_ptr(), o_part.data_ptr<float>(), ml_part.data_ptr<float>(), q.data_ptr(),
                             k_cache.data_ptr(), v_cache.data_ptr(), kv_scale->data_ptr<float>(), proj.data_ptr(),
@@ -219,6 +244,14 @@ int64_t attn_decode_mma(Tensor out, Tensor o_part, Tensor ml_part, Tensor q, Ten
 void kv_dequant(Tensor k_out, Tensor v_out, Tensor k_cache8, Tensor v_cache8, Tensor kv_scale, Tensor seg_slot,
                 Tensor seg_pos0, Tensor seg_nrows, Tensor block_table, int64_t kv_block, int64_t max_kvlen, int64_t nkv,
                 int64_t hd, int64_t scratch_tokens_per_slot) {
+  if (k_cache8.size(3) * 4 == hd * 3) {
+    check(fb_kv_dequant_qn(k_out.data_ptr(), v_out.data_ptr(), k_cache8.data_ptr(), v_cache8.data_ptr(),
+                           kv_scale.data_ptr<float>(), seg_slot.data_ptr<int>(), seg_pos0.data_ptr<int>(),
+                           seg_nrows.data_ptr<int>(), block_table.data_ptr<int>(), (int)block_table.size(1), (int)kv_block,
+                           (int)seg_slot.numel(), (int)max_kvlen, (int)nkv, (int)hd, (int)scratch_tokens_per_slot, 6,
+                           cur_stream()), "kv_dequant_q6");
+    return;
+  }
   if (k_cache8.size(3) * 2 == hd) {
     check(fb_kv_dequant_q4(k_out.data_ptr(), v_out.data_ptr(), k_cache8.data_ptr(), v_cache8.data_ptr(),
                            kv_scale.data_ptr<float>(), seg_slot.data_ptr<int>(), seg_pos0.data_ptr<int>(),

@@ -137,8 +137,16 @@ class Executor:
         n_blocks = ecfg.n_slots * self.max_blocks + (int(ecfg.park_gb * (1 << 30) / max(1, self.kv_block_bytes())) if ecfg.park_gb > 0 else 0)
         self.pool = BlockPool(n_blocks)
         dev, dt = self.device, self.dtype
-        self.kv8 = ecfg.kv_dtype in ("fp8", "int4")          # quantised cache: byte codes + fp32 scales
-        self.kv4 = ecfg.kv_dtype == "int4"
+        # quantised caches: byte codes + fp32 scales. "fp8": e4m3, one scale per (token, kv head); "int4" / "int6": 4- /
+        # 6-bit codes with one scale per 32 elements; a trailing "h" ("int4h", "int6h", "fp8h") keeps the keys (and hands
+        # out the queries) in a Walsh-Hadamard rotated basis, which spreads outlier channels before quantisation
+        kd = ecfg.kv_dtype
+        self.kv_hrot = kd in ("int4h", "int6h", "fp8h")
+        kd = kd[:-1] if self.kv_hrot else kd
+        assert kd in ("bf16", "fp8", "int4", "int6"), f"kv_dtype {ecfg.kv_dtype!r}"
+        self.kv8 = kd in ("fp8", "int4", "int6")
+        self.kv_bits = {"fp8": 8, "int4": 4, "int6": 6}.get(kd, 16)
+        self.kv4 = kd in ("int4", "int6")                   # group scales (one per 32 elements)
         self.kv_scale: Dict[int, torch.Tensor] = {}
         self.k_cache: Dict[int, torch.Tensor] = {}
         self.v_cache: Dict[int, torch.Tensor] = {}
@@ -149,7 +157,7 @@ class Executor:
                 # e4m3 cache: byte codes on the GPU (the CPU oracle keeps dequantised values) + K / V scales per row
                 kdt = torch.uint8 if (self.kv8 and dev.type == "cuda") else dt
                 # int4 on the GPU: two codes per byte, one scale per 32 elements (K groups then V groups)
-                hd_store = c.head_dim // 2 if (self.kv4 and dev.type == "cuda") else c.head_dim
+                hd_store = c.head_dim * self.kv_bits // 8 if (self.kv4 and dev.type == "cuda") else c.head_dim
                 self.k_cache[i] = torch.zeros(n_blocks, ecfg.kv_block, c.n_kv, hd_store, dtype=kdt, device=dev)
                 self.v_cache[i] = torch.zeros(n_blocks, ecfg.kv_block, c.n_kv, hd_store, dtype=kdt, device=dev)
                 if self.kv8:
@@ -208,9 +216,10 @@ class Executor:
     # ---- sizes -----------------------------------------------------------------------------------
     def kv_block_bytes(self) -> int:
         c, e = self.cfg, self.ecfg
-        per = 2 * e.kv_block * c.n_kv * c.head_dim * (1 if e.kv_dtype == "fp8" else 2)
-        if e.kv_dtype == "int4":
-            per = 2 * e.kv_block * c.n_kv * (c.head_dim // 2 + c.head_dim // 32 * 4)
+        kd = e.kv_dtype[:-1] if e.kv_dtype.endswith("h") else e.kv_dtype
+        per = 2 * e.kv_block * c.n_kv * c.head_dim * (1 if kd == "fp8" else 2)
+        if kd in ("int4", "int6"):
+            per = 2 * e.kv_block * c.n_kv * (c.head_dim * int(kd[3]) // 8 + c.head_dim // 32 * 4)
         if c.kv_lora > 0:
             per = e.kv_block * (c.kv_lora + c.rope_head_dim) * 2
         return per * max(1, self.cfg.n_attn)
@@ -550,7 +559,8 @@ class Executor:
                 q = ops.attn_prep(proj, w[p + "q_norm"], w[p + "k_norm"], self.inv_freq, mv["slot"], mv["pos"],
                                   self.block_table, self.k_cache[i], self.v_cache[i], self.ecfg.kv_block, c.n_q,
                                   c.n_kv, c.head_dim, c.rotary_dim, c.attn_gate, eps,
-                                  **({"row_cpos": tv["cpos"]} if tv is not None else {}), **kvs)
+                                  **({"row_cpos": tv["cpos"]} if tv is not None else {}), **kvs,
+                                  **({"hrot": self.kv_hrot, "kv_bits": self.kv_bits} if self.kv8 else {}))
                 if tv is not None:
                     # tree rows see the committed context plus their own ancestors (bit mask over the segment's rows)
                     o = ops.attention(q, proj, self.k_cache[i], self.v_cache[i], mv["slot"], mv["kvlen"],

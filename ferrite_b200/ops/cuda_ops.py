@@ -480,13 +480,14 @@ class CudaOps(CudaExtras):
 
     # ---- attention ---------------------------------------------------------------------------------
     def attn_prep(self, proj, q_norm, k_norm, inv_freq, row_slot, row_pos, block_table, k_cache, v_cache, kv_block,
-                  nq, nkv, hd, rot, gated, eps, kv_scale=None, row_cpos=None):
-        """q/k RMSNorm + partial RoPE, K/V rows into the paged cache (bf16, or e4m3 codes + per-row scales when
-        `kv_scale` is given). `row_cpos`: cache row of each row when it differs from its rotary position (trees)."""
+                  nq, nkv, hd, rot, gated, eps, kv_scale=None, row_cpos=None, hrot=False, kv_bits=None):
+        """q/k RMSNorm + partial RoPE, K/V rows into the paged cache (bf16, or e4m3 / 6-bit / 4-bit codes + scales when
+        `kv_scale` is given; the byte width of the cache rows tells the form). `row_cpos`: cache row of each row when it
+        differs from its rotary position (trees). `hrot`: queries and keys leave in a Walsh-Hadamard rotated basis."""
         q = self.empty(proj.shape[0], nq, hd, dtype=self.dtype, device=self.device)
         self.launches += 1
         self.C.attn_prep(q, k_cache, v_cache, proj, q_norm, k_norm, inv_freq, row_slot, row_pos, block_table,
-                         kv_block, nq, nkv, hd, rot, gated, eps, self.status_word, kv_scale, row_cpos)
+                         kv_block, nq, nkv, hd, rot, gated, eps, self.status_word, kv_scale, row_cpos, 1 if hrot else 0)
         return q
 
     def attention(self, q, proj, k_cache, v_cache, row_slot, row_kvlen, block_table, kv_block, nq, nkv, hd, gated,

@@ -68,9 +68,11 @@ class TorchOps(TorchExtras):
 
     # ---- attention ---------------------------------------------------------------------------------
     def attn_prep(self, proj, q_norm, k_norm, inv_freq, row_slot, row_pos, block_table, k_cache, v_cache, kv_block,
-                  nq, nkv, hd, rot, gated, eps, kv_scale=None, row_cpos=None):
-        """With `kv_scale` the cache rows take the values an e4m3 cache would return: one scale per (token, kv head),
-        amax / 448, codes rounded to e4m3 (the oracle keeps them dequantised in its float cache)."""
+                  nq, nkv, hd, rot, gated, eps, kv_scale=None, row_cpos=None, hrot=False, kv_bits=None):
+        """With `kv_scale` the cache rows take the values a quantised cache would return (the oracle keeps them
+        dequantised in its float cache): e4m3 with one scale per (token, kv head) = amax / 448, or 4- / 6-bit integer
+        codes with one scale per 32 elements (`kv_bits`; 4 when the scale tensor has group scales and nothing is said).
+        `hrot`: queries and keys are rotated by the orthonormal Walsh-Hadamard matrix of the head width first."""
         T = proj.shape[0]
         qw = hd * (2 if gated else 1)
         qg = proj[:, :nq * qw].float().view(T, nq, qw)
@@ -91,6 +93,12 @@ class TorchOps(TorchExtras):
             return torch.cat([a * cos - b * sin, b * cos + a * sin, x[..., rot:]], -1)
 
         q, k = rope(q), rope(k)
+        if hrot:
+            H = torch.ones(1, 1, device=q.device)
+            while H.shape[0] < hd:
+                H = torch.cat([torch.cat([H, H], 1), torch.cat([H, -H], 1)], 0)
+            H = H / math.sqrt(hd)
+            q, k = q @ H, k @ H
         pos = row_pos.long() if row_cpos is None else row_cpos.long()     # trees: stored by row index, rotated by depth
         blk = block_table[row_slot.long(), pos // kv_block].long()
         off = pos % kv_block
@@ -106,8 +114,14 @@ class TorchOps(TorchExtras):
                 sc = g.abs().amax(-1, keepdim=True) / 7.0
                 sc = torch.where(sc > 0, sc, torch.ones_like(sc))
                 return (torch.round(g / sc).clamp(-8, 7) * sc).reshape(x.shape)
+            def fq6(x):
+                # 6-bit cache: groups of 32 elements, scale = amax / 31, codes in -32..31
+                g = x.reshape(*x.shape[:-1], hd // 32, 32)
+                sc = g.abs().amax(-1, keepdim=True) / 31.0
+                sc = torch.where(sc > 0, sc, torch.ones_like(sc))
+                return (torch.round(g / sc).clamp(-32, 31) * sc).reshape(x.shape)
             if kv_scale.shape[-1] != 2:
-                fq = fq4
+                fq = fq6 if kv_bits == 6 else fq4
             k, v = fq(k.float()), fq(v.float())
         k_cache[blk, off] = k.to(k_cache.dtype)
         v_cache[blk, off] = v.to(v_cache.dtype)

@@ -201,3 +201,34 @@ def test_host_statements_of_the_small_ops():
     assert torch.allclose(mixed, torch.full((3, 8), 0.5))
     r2 = t.hc_combine(res.clone(), torch.ones(3, 8), torch.zeros(3, 4))
     assert torch.allclose(r2, torch.full((3, 4, 8), 2.0))
+
+
+def test_6bit_and_rotated_kv_caches_on_the_oracle():
+    """6-bit cache: much closer to the 16-bit cache than the 4-bit one at 1.4x its bytes. Hadamard-rotated keys: q . k is
+    unchanged in exact arithmetic, so the rotated caches stay as close as the plain ones."""
+    import torch
+    from ferrite_b200.config import EngineConfig, tiny_hybrid
+    from ferrite_b200.engine.engine import Engine
+    from ferrite_b200.engine.executor import Segment
+    from ferrite_b200.models.weights import init_weights
+    cfg = tiny_hybrid()
+    w = init_weights(cfg, seed=0)
+    p = torch.randint(0, cfg.vocab, (70,), generator=torch.Generator().manual_seed(1)).tolist()
+
+    def run(kv):
+        e = Engine(cfg, w, EngineConfig(n_slots=1, max_ctx=128, kv_dtype=kv), device="cpu")
+        a = e.forward([Segment(0, 0, p[:40], "all")])[0]
+        b = torch.cat([e.forward([Segment(0, 40 + i, [p[40 + i]], "last")])[0] for i in range(30)])
+        return e, torch.cat([a, b])
+
+    def kl(x, ref):
+        return torch.nn.functional.kl_div(torch.log_softmax(x, -1), torch.log_softmax(ref, -1), log_target=True,
+                                          reduction="batchmean").item()
+    e16, ref = run("bf16")
+    e4, l4 = run("int4")
+    e6, l6 = run("int6")
+    _, l4h = run("int4h")
+    _, l6h = run("int6h")
+    assert e4.ex.kv_block_bytes() < e6.ex.kv_block_bytes() < e16.ex.kv_block_bytes() / 2
+    assert kl(l6, ref) < kl(l4, ref) / 4 and kl(l6, ref) < 1e-4
+    assert kl(l6h, ref) < 1e-4 and kl(l4h, ref) < 1e-3

@@ -237,6 +237,71 @@ def test_int4_kv_cache_gpu(ext):
     eng.check()
 
 
+@pytest.mark.parametrize("kv", ["int6", "int4h", "int6h", "fp8h"])
+def test_6bit_and_rotated_kv_caches_gpu(ext, kv):
+    """6-bit codes (4 per 3 bytes) and Hadamard-rotated keys on the GPU: quantising attn-prep, the decode kernel reading
+    the packed codes, prompt attention over the decoded scratch, a verify tree, against the CPU oracle of the same form."""
+    cfg = tiny_hybrid()
+    w = init_weights(cfg, seed=0)
+    p = torch.randint(0, cfg.vocab, (120,), generator=torch.Generator().manual_seed(1)).tolist()
+    ref = Engine(cfg, w, EngineConfig(n_slots=2, max_ctx=256, kv_dtype=kv), device="cpu")
+    want, _, _ = ref.forward([Segment(1, 0, p, "all")])
+    eng = Engine(cfg, w, EngineConfig(n_slots=2, max_ctx=256, kv_dtype=kv), device="cuda")
+    kc = next(iter(eng.ex.k_cache.values()))
+    bits = {"int6": 6, "int6h": 6, "int4h": 4, "fp8h": 8}[kv]
+    assert kc.dtype == torch.uint8 and kc.shape[-1] == cfg.head_dim * bits // 8
+    a, _, _ = eng.forward([Segment(1, 0, p[:64], "all")], greedy=False)
+    b, _, _ = eng.forward([Segment(1, 64, p[64:110], "all")], greedy=False)
+    tail = [eng.forward([Segment(1, 110 + i, [p[110 + i]], "last")], greedy=False)[0].clone() for i in range(10)]
+    got = torch.cat([a.clone(), b.clone()] + tail).float().cpu()
+    kl = torch.nn.functional.kl_div(torch.log_softmax(got, -1), torch.log_softmax(want, -1), log_target=True,
+                                    reduction="batchmean").item()
+    assert kl < 2e-2, kl
+    from ferrite_b200.utils.selftest import tree_test
+    tree_test("cuda", 8e-2, kv_dtype=kv)
+    eng.check()
+
+
+@pytest.mark.parametrize("hd", [64, 128, 256])
+def test_6bit_kv_kernels_at_every_head_width(ext, hd):
+    """attn-prep writing 6-bit rows and the decode kernel reading them, per head width (2, 4 and 8 codes per lane pack
+    differently), with rotated keys, against the fp32 statement of the same cache."""
+    from ferrite_b200.ops.cuda_ops import CudaOps
+    from ferrite_b200.ops.torch_ops import TorchOps
+    ops, tops = CudaOps("cuda"), TorchOps("cuda", torch.float32)
+    g = torch.Generator(device="cuda").manual_seed(hd)
+    nq, nkv, kvb, nblk, T, rot = 4, 2, 64, 6, 5, 32
+    proj = torch.randn(T, (nq + 2 * nkv) * hd, generator=g, device="cuda").bfloat16()
+    qn = (torch.randn(hd, generator=g, device="cuda") * 0.1).bfloat16()
+    kn = (torch.randn(hd, generator=g, device="cuda") * 0.1).bfloat16()
+    inv = (1e4 ** (-torch.arange(rot // 2, dtype=torch.float64) / (rot // 2))).float().cuda()
+    slot = torch.tensor([0, 0, 1, 1, 1], dtype=torch.int32, device="cuda")
+    pos = torch.tensor([5, 6, 70, 71, 72], dtype=torch.int32, device="cuda")
+    bt = torch.arange(2 * nblk, dtype=torch.int32, device="cuda").view(2, nblk)
+    # fill the caches with earlier rows first so the decode reads more than the five new rows
+    kc = torch.zeros(2 * nblk, kvb, nkv, hd * 3 // 4, dtype=torch.uint8, device="cuda")
+    vc = torch.zeros_like(kc)
+    sc = torch.ones(2 * nblk, kvb, nkv, 2 * (hd // 32), dtype=torch.float32, device="cuda")
+    kf = torch.zeros(2 * nblk, kvb, nkv, hd, dtype=torch.float32, device="cuda")
+    vf = torch.zeros_like(kf)
+    for s0, n in ((0, 5), (1, 70)):
+        pj = torch.randn(n, (nq + 2 * nkv) * hd, generator=g, device="cuda").bfloat16()
+        sl = torch.full((n,), s0, dtype=torch.int32, device="cuda")
+        ps = torch.arange(n, dtype=torch.int32, device="cuda")
+        ops.attn_prep(pj, qn, kn, inv, sl, ps, bt, kc, vc, kvb, nq, nkv, hd, rot, False, 1e-6, kv_scale=sc, hrot=True)
+        tops.attn_prep(pj, qn, kn, inv, sl, ps, bt, kf, vf, kvb, nq, nkv, hd, rot, False, 1e-6, kv_scale=sc, hrot=True, kv_bits=6)
+    qa = ops.attn_prep(proj, qn, kn, inv, slot, pos, bt, kc, vc, kvb, nq, nkv, hd, rot, False, 1e-6, kv_scale=sc, hrot=True)
+    qb = tops.attn_prep(proj, qn, kn, inv, slot, pos, bt, kf, vf, kvb, nq, nkv, hd, rot, False, 1e-6, kv_scale=sc, hrot=True,
+                        kv_bits=6)
+    assert (qa.float() - qb.float()).abs().max().item() < 5e-2
+    kvlen = (pos + 1).contiguous()
+    for nsplit in (1, 3):
+        oa = ops.attention(qa, proj, kc, vc, slot, kvlen, bt, kvb, nq, nkv, hd, False, nsplit=nsplit, kv_scale=sc)
+        ob = tops.attention(qb, proj, kf, vf, slot, kvlen, bt, kvb, nq, nkv, hd, False)
+        assert (oa.float() - ob.float()).abs().max().item() < 6e-2, (hd, nsplit)
+    assert ops.status() == 0
+
+
 def test_commit_after_replayed_verify_graphs(ext):
     """Verify steps of two slots with different context lengths are different CUDA graphs; replaying the first one again
     and committing must replay THAT graph's saved projections (and its captured commit graph), not those of the graph
