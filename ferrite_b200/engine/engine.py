@@ -138,6 +138,11 @@ class Engine:
             self.ex.ep = ExpertParallel(tp if world > 1 else None, self.device, cfg.n_experts, cfg.hidden,
                                         cap_rows=self.ecfg.max_step_rows * cfg.top_k)
         self.slot_len: List[int] = [0] * self.ecfg.n_slots
+        import os
+        if os.environ.get("FB_DEBUG_BOUNDS", "0") not in ("", "0"):
+            # debug mode: index tensors are checked on the host before every op (eager steps, one sync per check)
+            from ..utils.boundscheck import BoundsChecker
+            self.bounds = BoundsChecker(self)
 
     # ---- rows ------------------------------------------------------------------------------------
     def forward(self, segments: Sequence[Segment], commit: bool = True, greedy: bool = True, x_add=None):

@@ -24,23 +24,28 @@ import torch
 
 
 class _TimedOps:
-    def __init__(self, ops, sink: Dict[str, list], on_gpu: bool):
+    def __init__(self, ops, sink: Dict[str, list], on_gpu: bool, nvtx: bool = False):
         object.__setattr__(self, "_ops", ops)
         object.__setattr__(self, "_sink", sink)
         object.__setattr__(self, "_gpu", on_gpu)
+        object.__setattr__(self, "_nvtx", nvtx and on_gpu)
 
     def __getattr__(self, name: str) -> Any:
         attr = getattr(self._ops, name)
         if not callable(attr) or name.startswith("_") or name in ("status",):
             return attr
-        sink, gpu = self._sink, self._gpu
+        sink, gpu, nvtx = self._sink, self._gpu, self._nvtx
 
         def timed(*a, **kw):
             if gpu:
                 e0, e1 = torch.cuda.Event(True), torch.cuda.Event(True)
+                if nvtx:
+                    torch.cuda.nvtx.range_push(name)        # named ranges for a timeline tool attached to the process
                 e0.record()
                 out = attr(*a, **kw)
                 e1.record()
+                if nvtx:
+                    torch.cuda.nvtx.range_pop()
                 sink.setdefault(name, []).append((e0, e1))
             else:
                 t0 = time.perf_counter()
@@ -79,13 +84,14 @@ class _TimedTP(_TimedOps):
 
 
 class OpProfiler:
-    def __init__(self, engine):
+    def __init__(self, engine, nvtx: bool = False):
+        """`nvtx`: also open an NVTX range per op call (the reference's tracing spans), for a timeline tool."""
         self.engine = engine
         self.ex = engine.ex
         self.records: Dict[str, list] = {}
         self._orig = self.ex.ops
         self._gpu = self.ex.device.type == "cuda"
-        self.ex.ops = _TimedOps(self._orig, self.records, self._gpu)
+        self.ex.ops = _TimedOps(self._orig, self.records, self._gpu, nvtx)
         self.ex.profile = self.records            # a set profile makes the executor run eagerly (no graph replay)
         self._orig_tp = self.ex.tp
         if self.ex.tp is not None:

@@ -232,3 +232,32 @@ def test_6bit_and_rotated_kv_caches_on_the_oracle():
     assert e4.ex.kv_block_bytes() < e6.ex.kv_block_bytes() < e16.ex.kv_block_bytes() / 2
     assert kl(l6, ref) < kl(l4, ref) / 4 and kl(l6, ref) < 1e-4
     assert kl(l6h, ref) < 1e-4 and kl(l4h, ref) < 1e-3
+
+
+def test_bounds_checked_debug_mode():
+    """Attached, the checker leaves results alone, counts what it looked at, and stops an out-of-range index before the
+    op runs, naming op, parameter, element and limit."""
+    import pytest
+    import torch
+    from ferrite_b200.config import EngineConfig, tiny_hybrid
+    from ferrite_b200.engine.engine import Engine
+    from ferrite_b200.engine.executor import Segment
+    from ferrite_b200.utils.boundscheck import BoundsChecker
+    cfg = tiny_hybrid()
+    eng = Engine(cfg, None, EngineConfig(n_slots=2, max_ctx=128), device="cpu")
+    want = eng.forward([Segment(0, 0, [1, 2, 3, 4, 5], "last")])[0].clone()
+    eng.reset_slot(0)
+    chk = BoundsChecker(eng)
+    got = eng.forward([Segment(0, 0, [1, 2, 3, 4, 5], "last")])[0]
+    assert torch.equal(want, got) and chk.checked["embed"] == 1 and chk.checked["attn_prep"] >= 1
+    with pytest.raises(IndexError, match=r"embed: ids\[1\] = 4096 is outside \[0, 4096\)"):
+        eng.ex.ops.embed(eng.ex.w["embed"], torch.tensor([1, cfg.vocab], dtype=torch.int32))
+    with pytest.raises(IndexError, match=r"gdn_conv: seg_slot\[0\] = 7 is outside \[0, 2\) \(slots\)"):
+        eng.ex.ops.gdn_conv(None, None, None, torch.tensor([7], dtype=torch.int32), None, None, 0)
+    bad_table = eng.ex.block_table.clone()
+    bad_table[1, 0] = 10 ** 6
+    with pytest.raises(IndexError, match="block_table"):
+        eng.ex.ops.attention(None, None, None, None, torch.tensor([0], dtype=torch.int32),
+                             torch.tensor([1], dtype=torch.int32), bad_table, 64, 1, 1, 64, False)
+    chk.detach()
+    assert type(eng.ex.ops).__name__ == "TorchOps" and eng.ex.profile is None
