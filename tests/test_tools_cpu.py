@@ -109,6 +109,36 @@ def test_launch_commands_and_step_summary():
     assert s["prompt"]["steps"] == 1 and s["mixed"]["rows"] == 66 and s["decode"]["ms_per_step"] == 1.0
 
 
+def test_launcher_presets_and_gpu_locks(tmp_path, capsys, monkeypatch):
+    """Presets expand to server arguments + environment (the caller's arguments come last, so they win); a GPU's lock
+    file is exclusive, names its holder, and is released for the next launcher."""
+    import subprocess
+    import sys
+
+    from ferrite_b200.tools import launch
+    assert launch.main(["--preset", "27b-spec", "--port", "8123", "--dry-run", "--", "--slots", "2"]) == 0
+    line = capsys.readouterr().out.strip()
+    assert "FE_SPEC=16" in line and "--drafter block" in line and line.endswith("--slots 2 --port 8123")
+    assert launch.main(["--preset", "27b-tp8", "--dry-run"]) == 0
+    assert "--nproc-per-node=8" in capsys.readouterr().out
+    assert launch.main(["--gpus", "2", "--gpu-ids", "4,5", "--dry-run"]) == 0
+    assert "CUDA_VISIBLE_DEVICES=4,5" in capsys.readouterr().out
+    assert launch.main(["--preset", "nope", "--dry-run"]) == 2 and launch.main(["--gpus", "2", "--gpu-ids", "1", "--dry-run"]) == 2
+    capsys.readouterr()
+    base = str(tmp_path / "gpu.lock")
+    fds = launch.take_gpu_locks([1, 0], base=base, note="server A")
+    # flock is per open file description: a second process (here: a child) must be refused and told who holds the GPU
+    code = ("import sys; from ferrite_b200.tools import launch\n"
+            "try:\n    launch.take_gpu_locks([2, 1], base=sys.argv[1])\n"
+            "except launch.LockBusy as e:\n    print(e); sys.exit(4)\n")
+    r = subprocess.run([sys.executable, "-c", code, base], capture_output=True, text=True)
+    assert r.returncode == 4 and "GPU 1 is in use" in r.stdout and "server A" in r.stdout and f"pid {__import__('os').getpid()}" in r.stdout
+    launch.release_locks(fds)
+    r = subprocess.run([sys.executable, "-c", code, base], capture_output=True, text=True)
+    assert r.returncode == 0
+    assert launch.port_of(["--x", "--port", "81"]) == 81 and launch.port_of(["--port=82"]) == 82 and launch.port_of([]) == 0
+
+
 def test_sweep_runs_points(capsys):
     from ferrite_b200.tools.sweep import main
     url, loop = _serve()
