@@ -153,6 +153,9 @@ int fb_argmax2(int* ids, float* vals, int* finite, const void* logits, long stri
                void* scratch, cudaStream_t s);
 int fb_sample(int* ids, const void* logits, long stride, int rows, int vocab, const void* params, const int* counts,
               float* work, int is_f32, cudaStream_t s);
+// accepted tree path: cache rows src[i] -> dst[i] (flat row = page * kv_block + offset), moves grouped per segment
+int fb_kv_move_rows(void* k, long k_row_bytes, void* v, long v_row_bytes, void* sc, long sc_row_bytes, const int* src,
+                    const int* dst, const int* seg_off, int nseg, cudaStream_t s);
 int fb_chain_accept(int* n_accept, int* out_tokens, const int* target, const int* draft, const int* seg_row0,
                     const int* seg_ndraft, int nseg, int max_draft, cudaStream_t s);
 

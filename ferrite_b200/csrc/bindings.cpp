@@ -382,6 +382,15 @@ void chain_accept(Tensor n_accept, Tensor out_tokens, Tensor target, Tensor draf
                         (int)seg_row0.numel(), (int)max_draft, cur_stream()), "chain_accept");
 }
 
+void kv_move_rows(Tensor k, c10::optional<Tensor> v, c10::optional<Tensor> sc, Tensor src, Tensor dst, Tensor seg_off) {
+  // caches [pages, kv_block, ...] contiguous: a row is everything behind the first two dimensions
+  auto row_bytes = [](const Tensor& t) { return (long)(t.numel() / (t.size(0) * t.size(1))) * (long)t.element_size(); };
+  const bool hv = v.has_value() && v->defined() && v->numel() > 0, hs = sc.has_value() && sc->defined() && sc->numel() > 0;
+  check(fb_kv_move_rows(k.data_ptr(), row_bytes(k), hv ? v->data_ptr() : nullptr, hv ? row_bytes(*v) : 0,
+                        hs ? sc->data_ptr() : nullptr, hs ? row_bytes(*sc) : 0, src.data_ptr<int>(), dst.data_ptr<int>(),
+                        seg_off.data_ptr<int>(), (int)seg_off.numel() - 1, cur_stream()), "kv_move_rows");
+}
+
 }  // namespace
 
 void register_ext(pybind11::module_& m);
@@ -417,5 +426,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("argmax", &argmax);
   m.def("sample", &sample);
   m.def("chain_accept", &chain_accept);
+  m.def("kv_move_rows", &kv_move_rows);
   register_ext(m);
 }

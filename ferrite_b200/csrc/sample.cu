@@ -279,9 +279,56 @@ __global__ void chain_accept_kernel(int* __restrict__ n_accept, int* __restrict_
   for (int i = 0; i <= acc; ++i) out_tokens[(size_t)seg * (max_draft + 1) + i] = target[r0 + i];
 }
 
+// Compaction of an accepted tree path's K/V rows: move i of a segment copies cache row src[i] onto row dst[i] (flat row
+// = page * kv_block + offset) in up to three tensors at once (K codes, V codes, scales; blockIdx.z picks the tensor).
+// The moves of a segment are listed root first, where dst <= src and both ascend: a thread owns one 16-byte column of
+// the row and walks the moves in order, so it never reads a row it has already overwritten and needs no staging copy.
+// grid = (column chunks, segments, tensors), 128 threads.
+struct KvMoveArgs {
+  unsigned char* base[3];
+  long row_bytes[3];
+  int vec[3];                 // bytes a thread moves per row: 16 when the rows allow it, else 4
+};
+
+__global__ void __launch_bounds__(128) kv_move_rows_kernel(KvMoveArgs a, const int* __restrict__ src,
+                                                           const int* __restrict__ dst, const int* __restrict__ seg_off) {
+  const int z = blockIdx.z, seg = blockIdx.y;
+  if (!a.base[z]) return;
+  const long col = ((long)blockIdx.x * blockDim.x + threadIdx.x) * a.vec[z];
+  if (col >= a.row_bytes[z]) return;
+  for (int i = seg_off[seg]; i < seg_off[seg + 1]; ++i) {
+    const unsigned char* from = a.base[z] + (size_t)src[i] * a.row_bytes[z] + col;
+    unsigned char* to = a.base[z] + (size_t)dst[i] * a.row_bytes[z] + col;
+    if (a.vec[z] == 16) *reinterpret_cast<uint4*>(to) = *reinterpret_cast<const uint4*>(from);
+    else *reinterpret_cast<uint32_t*>(to) = *reinterpret_cast<const uint32_t*>(from);
+  }
+}
+
 }  // namespace fb
 
 using namespace fb;
+
+// rows of every tensor are multiples of 4 bytes; tensors not given are null
+extern "C" int fb_kv_move_rows(void* k, long k_row_bytes, void* v, long v_row_bytes, void* sc, long sc_row_bytes,
+                               const int* src, const int* dst, const int* seg_off, int nseg, cudaStream_t s) {
+  if (nseg <= 0) return 0;
+  KvMoveArgs a;
+  a.base[0] = (unsigned char*)k; a.base[1] = (unsigned char*)v; a.base[2] = (unsigned char*)sc;
+  a.row_bytes[0] = k_row_bytes; a.row_bytes[1] = v_row_bytes; a.row_bytes[2] = sc_row_bytes;
+  long most = 0;               // threads the widest tensor needs per row
+  for (int i = 0; i < 3; ++i) {
+    a.vec[i] = 16;
+    if (!a.base[i]) continue;
+    if (a.row_bytes[i] % 4 || (reinterpret_cast<uintptr_t>(a.base[i]) & 15)) return -1;
+    if (a.row_bytes[i] % 16) a.vec[i] = 4;
+    const long need = a.row_bytes[i] / a.vec[i];
+    if (need > most) most = need;
+  }
+  if (most == 0) return 0;
+  dim3 grid((unsigned)((most + 127) / 128), nseg, 3);
+  kv_move_rows_kernel<<<grid, 128, 0, s>>>(a, src, dst, seg_off);
+  return (int)cudaGetLastError();
+}
 
 // scratch: rows * 64 * 3 words (slice maxima, indices, non-finite flags); when null the one-CTA kernel runs
 extern "C" int fb_argmax2(int* ids, float* vals, int* finite, const void* logits, long stride, int rows, int vocab,

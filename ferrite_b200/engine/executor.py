@@ -698,7 +698,7 @@ class Executor:
         c, w, ops = self.cfg, self.w, self.ops
         dev = self.device
         rows, row0s, ns, slots = [], [], [], []
-        src, dst = [], []
+        src, dst, seg_off = [], [], [0]
         kvb = self.ecfg.kv_block
         r0 = 0
         for sg, path in zip(batch.segments, paths):
@@ -712,6 +712,7 @@ class Executor:
                     a, b = sg.pos0 + r, sg.pos0 + j
                     src.append(blocks[a // kvb] * kvb + a % kvb)
                     dst.append(blocks[b // kvb] * kvb + b % kvb)
+            seg_off.append(len(src))
             r0 += len(sg.tokens)
         if rows and any(k == "gdn" for k in self.kinds):
             idx = torch.tensor(rows, dtype=torch.long, device=dev)
@@ -734,7 +735,14 @@ class Executor:
                 ops.gdn_rec(qkv, proj, self.rec_state[i], self.conv_state[i], w[p + "A_log"], w[p + "dt_bias"], sslot,
                             srow0, snrows, c.lin_k_heads, c.lin_v_heads, c.lin_dk, c.lin_dv, c.eps, commit=True,
                             chunked=False)
-        if src:
+        if src and ops.name == "cuda":
+            # one launch per layer moves the path's K, V and scale rows; a thread walks a segment's moves root first
+            idx = torch.tensor([src, dst], dtype=torch.int32).pin_memory().to(dev, non_blocking=True)
+            off = torch.tensor(seg_off, dtype=torch.int32).pin_memory().to(dev, non_blocking=True)
+            for i in self.k_cache:
+                vc = self.v_cache.get(i)
+                ops.kv_move_rows(self.k_cache[i], vc, self.kv_scale.get(i), idx[0], idx[1], off)
+        elif src:
             s_i = torch.tensor(src, dtype=torch.long, device=dev)
             d_i = torch.tensor(dst, dtype=torch.long, device=dev)
             for i in self.k_cache:

@@ -388,6 +388,11 @@ class CudaOps(CudaExtras):
             return y
         return self.linear(self.linear(x, w_gu, norm_w=norm_w, eps=eps, swiglu=True), w_down, res=res)
 
+    def kv_move_rows(self, k_cache, v_cache, kv_scale, src, dst, seg_off):
+        """Cache rows src[i] -> dst[i] (flat row ids, grouped per segment by `seg_off`) in K, V and the scales."""
+        self.launches += 1
+        self.C.kv_move_rows(k_cache, v_cache, kv_scale, src, dst, seg_off)
+
     def silu_mul(self, gu):
         out = self.empty(gu.shape[0], gu.shape[1] // 2, dtype=self.dtype, device=self.device)
         self.launches += 1
