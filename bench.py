@@ -97,6 +97,9 @@ def main():
     ap.add_argument("--streams", type=int, default=1)
     ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers (the JSON line says so)")
     ap.add_argument("--dtype", default="bf16")
+    ap.add_argument("--model", default="27b", choices=["27b", "moe80b", "mla671b"],
+                    help="27b: the headline model. moe80b (80B-A3B hybrid MoE, fits one GPU with --dtype nvfp4) and mla671b "
+                         "(needs --layers on one GPU) measure the same plain decode + 2K prefill on the MoE families")
     ap.add_argument("--fused-layers", default="auto", choices=["auto", "on", "off"],
                     help="plain decode rows: one persistent kernel per layer (auto = when tensor parallel)")
     ap.add_argument("--no-extras", action="store_true", help="only the headline decode measurement and the 2K prefill")
@@ -112,7 +115,7 @@ def main():
     import torch
     import torch.distributed as dist
 
-    from ferrite_b200.config import EngineConfig, hybrid_27b, scaled
+    from ferrite_b200.config import EngineConfig, hybrid_27b, mla_671b, moe_80b, scaled
     from ferrite_b200.engine.engine import Engine
     from ferrite_b200.engine.executor import Segment
 
@@ -130,7 +133,9 @@ def main():
         tp.selftest()
     assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE {world}: launch with torch.distributed.run"
 
-    cfg = hybrid_27b()
+    cfg = {"27b": hybrid_27b, "moe80b": moe_80b, "mla671b": mla_671b}[args.model]()
+    if args.model != "27b":
+        args.no_extras = True                   # the extra measurements (speculation, other weight formats) are the 27B model's
     if args.layers:
         cfg = scaled(cfg, args.layers)
     W = max(3, args.warmup)
@@ -226,7 +231,8 @@ def main():
     eng = build(args.dtype)
     timed_prefill(eng, 0, prompts[0][:256])            # warm the prompt kernels
     prefill_ms = timed_prefill(eng, 0, prompts[0])
-    if not args.no_extras:
+    four = args.streams == 1 and (not args.no_extras or args.model != "27b")     # also measure 4 streams
+    if not args.no_extras or four:
         for s in range(1, n_streams_max):
             eng.prefill(s, prompts[s])
     eng.check()
@@ -240,13 +246,15 @@ def main():
     assert identical, "tensor-parallel ranks produced different tokens"
     extras = {"ranks_produced_identical_tokens": identical}
 
-    if not args.no_extras and args.streams == 1:
+    if four:
         ms4, _, _, _, _, _ = decode_regions(eng, 4, False, args.min_timed_s / 2)
         ms4e, _, _, _, _, toks4 = decode_regions(eng, 4, True, args.min_timed_s / 2)
         assert same_on_every_rank(toks4)
         extras["decode_4streams_tok_s"] = 4 * K / (ms4 / 1e3)
         extras["decode_4streams_e2e_tok_s"] = 4 * K / (ms4e / 1e3)
-        extras["decode_4streams_vs_baseline"] = extras["decode_4streams_tok_s"] / BASELINE_DECODE_4
+        if args.model == "27b":
+            extras["decode_4streams_vs_baseline"] = extras["decode_4streams_tok_s"] / BASELINE_DECODE_4
+    if not args.no_extras and args.streams == 1:
         # speculative verification: one step scores 1 + 16 drafted rows of one stream without committing them
         p0 = eng.slot_len[0]
         rows = feed[0][:17]
@@ -310,16 +318,26 @@ def main():
 
     value = args.streams * K / (ms1 / 1e3)
     base = BASELINE_DECODE_1 if args.streams == 1 else BASELINE_DECODE_4
+    model_name = {"27b": "27B hybrid", "moe80b": "80B-A3B hybrid MoE", "mla671b": "671B-class MLA MoE"}[args.model]
+    if args.model == "moe80b":
+        # the reference's plain decode of this family on one card: 38-43 tok/s; 153-193 at 4 requests with MTP drafting
+        base = 43.0 if args.streams == 1 else 193.0
+        extras.pop("prefill_vs_baseline", None)
+        extras["prefill_vs_baseline"] = extras["prefill_tok_s"] / 2410.0          # its best prompt rate (16K)
+    elif args.model == "mla671b":
+        base = None
+        extras.pop("prefill_vs_baseline", None)
     out = {
-        "metric": f"decode tok/s, {args.streams} stream(s), plain decode at {args.ctx} ctx, 27B hybrid",
+        "metric": f"decode tok/s, {args.streams} stream(s), plain decode at {args.ctx} ctx, {model_name}",
         "value": value, "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms1 / K,
-        "higher_is_better": True, "scaling": "strong", "vs_baseline": value / base, "dtype": args.dtype,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": (value / base) if base else None, "dtype": args.dtype,
         "data": "synthetic uniform-random prompts, random-init weights N(0,0.02)",
         "config": {"model": cfg.name + (f"-{args.layers}layers-DEBUG" if args.layers else ""),
                    "global_batch": args.streams, "seq_len": args.ctx,
                    "parallelism": f"tp{world}", "params": cfg.param_count(), "repeats": reps,
                    "timing": "median over `repeats` regions of exactly `steps` steps each (>= 2 s timed in all)",
-                   "l2": "inputs larger than L2: every step streams all weights (>40 GB)"},
+                   "l2": ("inputs larger than L2: every step streams all weights (>40 GB)" if args.model == "27b" else
+                          "inputs larger than L2: every step streams the active experts' and the dense weights (> 1 GB)")},
         "clocks": clocks,
         "e2e": {"value": args.streams * K / (ms_e2e / 1e3), "unit": "tok/s", "h2d_bytes_per_step": h2d_e,
                 "d2h_bytes_per_step": d2h_e, "repeats": reps_e},

@@ -149,6 +149,12 @@ int fb_mla_prep(void* cache, void* qabs, const void* kva, long kva_stride, const
 int fb_mla_attn(void* out, float* o_part, float* ml_part, const void* qabs, const void* cache, const int* row_slot,
                 const int* row_kvlen, const int* block_table, int max_blocks, int kv_block, int rows, int nq, int L, int R,
                 int nsplit, float scale, cudaStream_t s);
+// prompt rows of latent attention in the expanded form: per-head K / V rows (padded to the flash kernel's head width)
+// from the kv_b GEMM output `kvx` [rows][nq][dn + dv] and the latent rows `lat` [rows][L + R]; padded, pre-scaled queries
+int fb_mla_expand(void* kp, void* vp, const void* kvx, const void* lat, long rows, int nq, int dn, int dv, int L, int R, int HP,
+                  cudaStream_t s);
+int fb_mla_qpad(void* qp, const void* q, long q_stride, const void* qabs, long rows, int nq, int dn, int L, int R, int HP,
+                float scale, cudaStream_t s);
 
 // ---- drafter_ops.cu ----
 int fb_w4_gemv(void* y, const void* x, const void* qweight, const void* scales, const void* biases, const void* res, int M,

@@ -537,6 +537,18 @@ void mla_attn(Tensor out, Tensor o_part, Tensor ml_part, Tensor qabs, Tensor cac
                     (float)scale, cur_stream()), "mla_attn");
 }
 
+void mla_expand(Tensor kp, Tensor vp, Tensor kvx, Tensor lat, int64_t nq, int64_t dn, int64_t dv, int64_t L, int64_t R) {
+  // kp / vp [rows, nq, HP]; kvx [rows, nq (dn + dv)]; lat [rows, L + R]; all contiguous bf16
+  TORCH_CHECK(kp.is_contiguous() && vp.is_contiguous() && kvx.is_contiguous() && lat.is_contiguous(), "mla_expand: contiguous");
+  check(fb_mla_expand(kp.data_ptr(), vp.data_ptr(), kvx.data_ptr(), lat.data_ptr(), (long)lat.size(0), (int)nq, (int)dn,
+                      (int)dv, (int)L, (int)R, (int)kp.size(-1), cur_stream()), "mla_expand");
+}
+
+void mla_qpad(Tensor qp, Tensor q, Tensor qabs, int64_t nq, int64_t dn, int64_t L, int64_t R, double scale) {
+  check(fb_mla_qpad(qp.data_ptr(), q.data_ptr(), (long)q.stride(0), qabs.data_ptr(), (long)q.size(0), (int)nq, (int)dn,
+                    (int)L, (int)R, (int)qp.size(-1), (float)scale, cur_stream()), "mla_qpad");
+}
+
 void w4_gemv(Tensor y, Tensor x, Tensor qweight, Tensor scales, Tensor biases, c10::optional<Tensor> res) {
   check(fb_w4_gemv(y.data_ptr(), x.data_ptr(), qweight.data_ptr(), scales.data_ptr(), biases.data_ptr(), cptr(res),
                    (int)x.size(0), (int)qweight.size(0), (int)x.size(1), (long)x.stride(0), (long)y.stride(0), cur_stream()),
@@ -585,6 +597,8 @@ void register_ext(pybind11::module_& m) {
   m.def("w4_gemv", &w4_gemv);
   m.def("topk16", &topk16);
   m.def("dynconv", &dynconv);
+  m.def("mla_expand", &mla_expand);
+  m.def("mla_qpad", &mla_qpad);
   m.def("hc_norm", &hc_norm);
   m.def("hc_mix", &hc_mix);
   m.def("hc_combine", &hc_combine);

@@ -161,9 +161,67 @@ __global__ void mla_combine_kernel(__nv_bfloat16* __restrict__ out, const float*
   }
 }
 
+// ---- prompt rows on the tensor-core flash kernel: the expanded (per-head key / value) form -----------------------------
+// The absorbed form above reads 576-wide latent rows per head per key, which is right for a few rows and quadratic SIMT
+// work for a prompt. For prompt chunks the context's latent rows are expanded once per layer by one dense GEMM with
+// kv_b ([nq (dn + dv)] x L), and packed here into ordinary per-head K / V rows padded to the flash kernel's head width
+// HP (64 / 128 / 256): K = [k_nope | k_rope (shared by the heads) | 0], V = [v | 0], Q = [q_nope | q_rope | 0] * s with
+// s = sqrt(HP / (dn + R)) so that the kernel's 1 / sqrt(HP) becomes the model's 1 / sqrt(dn + R). Zero padding changes
+// neither q . k nor the first dv output columns.
+// grid = context rows, 256 threads, 8 elements per thread step.
+__global__ void __launch_bounds__(256) mla_expand_kernel(__nv_bfloat16* __restrict__ kp, __nv_bfloat16* __restrict__ vp,
+                                                         const __nv_bfloat16* __restrict__ kvx, const __nv_bfloat16* __restrict__ lat,
+                                                         int nq, int dn, int dv, int L, int R, int HP) {
+  const size_t t = blockIdx.x;
+  const int per = HP / 8;
+  const uint4 zero = make_uint4(0, 0, 0, 0);
+  for (int i = threadIdx.x; i < nq * per; i += blockDim.x) {
+    const int h = i / per, c = (i % per) * 8;
+    uint4 kv = zero, vv = zero;
+    if (c < dn) kv = *reinterpret_cast<const uint4*>(kvx + (t * nq + h) * (dn + dv) + c);
+    else if (c < dn + R) kv = *reinterpret_cast<const uint4*>(lat + t * (L + R) + L + (c - dn));
+    if (c < dv) vv = *reinterpret_cast<const uint4*>(kvx + (t * nq + h) * (dn + dv) + dn + c);
+    *reinterpret_cast<uint4*>(kp + (t * nq + h) * HP + c) = kv;
+    *reinterpret_cast<uint4*>(vp + (t * nq + h) * HP + c) = vv;
+  }
+}
+
+// q [rows][nq][dn + R] (rope part not yet rotated), qabs [rows][nq][L + R] (rotated rope part in its tail).
+__global__ void __launch_bounds__(256) mla_qpad_kernel(__nv_bfloat16* __restrict__ qp, const __nv_bfloat16* __restrict__ q,
+                                                       long q_stride, const __nv_bfloat16* __restrict__ qabs, int nq, int dn,
+                                                       int L, int R, int HP, float s) {
+  const size_t t = blockIdx.x;
+  for (int i = threadIdx.x; i < nq * HP; i += blockDim.x) {
+    const int h = i / HP, c = i % HP;
+    float v = 0.f;
+    if (c < dn) v = bf2f(q[t * q_stride + (size_t)h * (dn + R) + c]);
+    else if (c < dn + R) v = bf2f(qabs[(t * nq + h) * (L + R) + L + (c - dn)]);
+    qp[(t * nq + h) * HP + c] = f2bf(v * s);
+  }
+}
+
 }  // namespace fb
 
 using namespace fb;
+
+extern "C" int fb_mla_expand(void* kp, void* vp, const void* kvx, const void* lat, long rows, int nq, int dn, int dv, int L,
+                             int R, int HP, cudaStream_t s) {
+  if (rows <= 0) return 0;
+  if (dn % 8 || dv % 8 || R % 8 || L % 8 || HP % 8 || dn + R > HP || dv > HP) return -1;
+  mla_expand_kernel<<<(unsigned)rows, 256, 0, s>>>((__nv_bfloat16*)kp, (__nv_bfloat16*)vp, (const __nv_bfloat16*)kvx,
+                                                   (const __nv_bfloat16*)lat, nq, dn, dv, L, R, HP);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int fb_mla_qpad(void* qp, const void* q, long q_stride, const void* qabs, long rows, int nq, int dn, int L, int R,
+                           int HP, float scale, cudaStream_t s) {
+  if (rows <= 0) return 0;
+  if (dn + R > HP) return -1;
+  mla_qpad_kernel<<<(unsigned)rows, 256, 0, s>>>((__nv_bfloat16*)qp, (const __nv_bfloat16*)q, q_stride,
+                                                 (const __nv_bfloat16*)qabs, nq, dn, L, R, HP, scale);
+  return (int)cudaGetLastError();
+}
+
 
 extern "C" int fb_mla_prep(void* cache, void* qabs, const void* kva, long kva_stride, const void* q, long q_stride,
                            const void* norm_w, const float* inv_freq, const int* row_slot, const int* row_pos,

@@ -44,11 +44,21 @@ class Engine:
         world = tp.world if tp is not None else 1
         rank = tp.rank if tp is not None else 0
         if weights is None:
-            weights = init_weights(cfg, seed=seed, dtype=self.dtype, device=self.device)
+            post = None
+            if on_gpu and world == 1 and cfg.n_experts > 0 and self.ecfg.weight_dtype in ("nvfp4", "nvfp4-a16", "nvfp4-w4a4"):
+                # seeded MoE weights of a 4-bit engine: every expert stack is packed as soon as it is drawn (an
+                # 80B-class model is 160 GB in 16 bits and 45 GB packed)
+                from ..ops.qweight import quantize_experts
+
+                def post(name, t):
+                    if name.split(".")[-1] in ("experts_gate_up", "experts_down") and t.shape[2] % 16 == 0:
+                        return quantize_experts(t)
+                    return t
+            weights = init_weights(cfg, seed=seed, dtype=self.dtype, device=self.device, post=post)
         if world > 1:
             weights = shard_weights(cfg, weights, rank, world)
         from ..formats.packed import is_packed
-        weights = {k: (v if is_packed(v) else
+        weights = {k: (v if (is_packed(v) or not isinstance(v, torch.Tensor)) else
                        v.to(self.device) if v.dtype == torch.float32 and k.endswith(("A_log", "dt_bias", "router_bias"))
                        else v.to(self.device, self.dtype)) for k, v in weights.items()}
         # linears that arrived packed from a quantised checkpoint (ModelOpt NVFP4 / FP8, EXL3) become the kernels' weight

@@ -211,6 +211,7 @@ class Executor:
         self._last_meta = None
         self.profile = None
         self._step_max_kvlen = None
+        self._step_segments = None            # host view of an eager step's segments: (slot, pos0, rows)
         self.ep = None                        # ExpertParallel, set by the engine for MoE models under TP
 
     # ---- sizes -----------------------------------------------------------------------------------
@@ -546,13 +547,25 @@ class Executor:
                 kva = ops.linear(h, w[p + "kv_a"])
                 w_uk_t, w_uv = self.mla_w[i]
                 L, R = c.kv_lora, c.rope_head_dim
+                # prompt segments: per-head keys / values expanded from the latent rows, tcgen05 flash kernel
+                expand = (ops.name == "cuda" and max_seg_rows > FLASH_MIN_ROWS and self._step_segments is not None
+                          and self.ecfg.kv_block % 64 == 0 and max(c.nope_head_dim + R, c.v_head_dim) <= 256
+                          and isinstance(w[p + "kv_b"], torch.Tensor))
                 qabs = ops.mla_prep(q, kva, w[p + "kv_a_norm"], w_uk_t, self.inv_freq_mla, mv["slot"], mv["pos"],
                                     self.block_table, self.k_cache[i].view(-1, self.ecfg.kv_block, L + R),
-                                    self.ecfg.kv_block, c.n_q, c.nope_head_dim, L, R, eps)
-                ol = ops.mla_attention(qabs, self.k_cache[i].view(-1, self.ecfg.kv_block, L + R), mv["slot"], mv["kvlen"],
-                                       self.block_table, self.ecfg.kv_block, c.n_q, L, R,
-                                       1.0 / math.sqrt(c.nope_head_dim + R), nsplit=nsplit if max_seg_rows <= FLASH_MIN_ROWS else 1)
-                x = row(ops.mla_out(ol, w_uv), w[p + "out_proj"], x)
+                                    self.ecfg.kv_block, c.n_q, c.nope_head_dim, L, R, eps,
+                                    **({"absorb": False} if expand else {}))
+                if expand:
+                    o = ops.mla_attention_prefill(q, qabs, self.k_cache[i], w[p + "kv_b"], self._step_segments, mv["srow0"],
+                                                  mv["snrows"], mv["spos0"], self.block_table, self.ecfg.kv_block, c.n_q,
+                                                  c.nope_head_dim, c.v_head_dim, L, R)
+                else:
+                    ol = ops.mla_attention(qabs, self.k_cache[i].view(-1, self.ecfg.kv_block, L + R), mv["slot"], mv["kvlen"],
+                                           self.block_table, self.ecfg.kv_block, c.n_q, L, R,
+                                           1.0 / math.sqrt(c.nope_head_dim + R),
+                                           nsplit=nsplit if max_seg_rows <= FLASH_MIN_ROWS else 1)
+                    o = ops.mla_out(ol, w_uv)
+                x = row(o, w[p + "out_proj"], x)
             else:
                 proj = col(x, w[p + "in_proj"], w[p + "input_norm"])
                 kvs = {"kv_scale": self.kv_scale[i]} if self.kv8 else {}
@@ -773,6 +786,7 @@ class Executor:
         # the e4m3 cache decode before prompt attention sizes its grid by the longest visible context, except inside
         # graphs, whose launches must not depend on the step
         self._step_max_kvlen = None if use_graph else max_kvlen
+        self._step_segments = None if use_graph else [(s.slot, s.pos0, len(s.tokens)) for s in batch.segments]
         self._last_graph_key = None
         if not use_graph:
             logits, picks = self._run(T, nseg, nlog, max_seg_rows, nsplit, batch.commit, greedy, x_add, tree)

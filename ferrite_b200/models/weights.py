@@ -78,9 +78,11 @@ def weight_shapes(cfg: ModelConfig) -> Dict[str, tuple]:
 _F32_NAMES = ("A_log", "dt_bias", "router_bias")
 
 
-def init_weights(cfg: ModelConfig, seed: int = 0, dtype=torch.float32, device="cpu", std: float = 0.02) -> Weights:
+def init_weights(cfg: ModelConfig, seed: int = 0, dtype=torch.float32, device="cpu", std: float = 0.02, post=None) -> Weights:
     """Seeded N(0, std) weights for every tensor of the architecture. The GDN gated-norm weight is drawn
-    around one (it multiplies directly); all other norm weights are zero-centred offsets."""
+    around one (it multiplies directly); all other norm weights are zero-centred offsets. `post(name, tensor)` may
+    replace a tensor as soon as it is drawn (a quantised engine packs the big ones at once, so a model that only fits
+    packed never exists unpacked)."""
     g = torch.Generator(device=device)
     g.manual_seed(seed)
     w: Weights = {}
@@ -89,7 +91,8 @@ def init_weights(cfg: ModelConfig, seed: int = 0, dtype=torch.float32, device="c
         if name.endswith("gnorm_w"):
             t = t + 1.0
         keep32 = name.endswith(_F32_NAMES)
-        w[name] = t if keep32 else t.to(dtype)
+        t = t if keep32 else t.to(dtype)
+        w[name] = post(name, t) if post is not None else t
     return w
 
 

@@ -637,15 +637,49 @@ class CudaOps(CudaExtras):
         return y
 
     # ---- multi-head latent attention (absorbed form) ----------------------------------------------------
-    def mla_prep(self, q, kva, norm_w, w_uk_t, inv_freq, row_slot, row_pos, block_table, cache, kv_block, nq, dn, L, R, eps):
+    def mla_prep(self, q, kva, norm_w, w_uk_t, inv_freq, row_slot, row_pos, block_table, cache, kv_block, nq, dn, L, R, eps,
+                 absorb=True):
+        """Latent rows into the paged cache and the absorbed queries [T, nq, L + R]. `absorb=False` leaves the first L
+        columns of every query unwritten (the expanded prompt path only reads the rotated rope tail)."""
         T = q.shape[0]
         qabs = self.empty(T, nq, L + R, dtype=self.dtype, device=self.device)
         self.launches += 1
         self.C.mla_prep(cache, qabs, kva, q, norm_w, inv_freq, row_slot, row_pos, block_table, kv_block, nq, dn, L, R, eps,
                         self.status_word)
-        # key up-projection folded into the query: one small linear per head
-        self.head_linear(q.view(T, nq, dn + R)[:, :, :dn], w_uk_t, out=qabs[:, :, :L])
+        if absorb:
+            # key up-projection folded into the query: one small linear per head
+            self.head_linear(q.view(T, nq, dn + R)[:, :, :dn], w_uk_t, out=qabs[:, :, :L])
         return qabs
+
+    def mla_attention_prefill(self, q, qabs, cache, kv_b, segs, seg_row0, seg_nrows, seg_pos0, block_table, kv_block,
+                              nq, dn, dv, L, R):
+        """Latent attention of prompt segments in the expanded form on the tcgen05 flash kernel. `segs`: host list of
+        (slot, pos0, rows) per segment; the context's latent rows are gathered through the block table, expanded to
+        per-head keys / values by one GEMM with `kv_b` [nq (dn + dv), L], packed (padded to the kernel's head width) into
+        a scratch laid out segment after segment, and read through a step-local page table. Returns [T, nq * dv]."""
+        T = q.shape[0]
+        HP = 64 if max(dn + R, dv) <= 64 else 128 if max(dn + R, dv) <= 128 else 256
+        starts, tables, tot = [], [], 0
+        for slot, pos0, n in segs:
+            nb = (pos0 + n + kv_block - 1) // kv_block
+            starts.append((slot, tot, nb))
+            tot += nb
+        max_nb = max(nb for _, _, nb in starts)
+        pages = torch.cat([block_table[slot, :nb] for slot, _, nb in starts]).long()
+        lat = cache.view(-1, kv_block, L + R)[pages].view(tot * kv_block, L + R)            # the segments' latent rows
+        kvx = self.linear(lat[:, :L].contiguous(), kv_b)                                     # [rows, nq (dn + dv)]
+        kp = self.empty(tot, kv_block, nq, HP, dtype=self.dtype, device=self.device)
+        vp = self.empty(tot, kv_block, nq, HP, dtype=self.dtype, device=self.device)
+        qp = self.empty(T, nq, HP, dtype=self.dtype, device=self.device)
+        self.launches += 2
+        self.C.mla_expand(kp, vp, kvx, lat, nq, dn, dv, L, R)
+        self.C.mla_qpad(qp, q, qabs, nq, dn, L, R, math.sqrt(HP / (dn + R)))
+        table = torch.tensor([[s0 + min(j, nb - 1) for j in range(max_nb)] for _, s0, nb in starts], dtype=torch.int32)
+        table = table.pin_memory().to(self.device, non_blocking=True)
+        own = torch.arange(len(segs), dtype=torch.int32, device=self.device)
+        o = self.attention_prefill(qp, qp.view(T, nq * HP), kp, vp, own, seg_row0, seg_nrows, seg_pos0, table, kv_block,
+                                   nq, nq, HP, False, max(n for _, _, n in segs))
+        return o.view(T, nq, HP)[:, :, :dv].contiguous().view(T, nq * dv)
 
     def mla_attention(self, qabs, cache, row_slot, row_kvlen, block_table, kv_block, nq, L, R, scale, nsplit=1):
         T = qabs.shape[0]

@@ -138,9 +138,29 @@ def bench_linear(ops, t, m, n, k, swiglu=False, norm=False, res=False, label=Non
                   {"m": m, "n": n, "k": k})
 
 
+def graph_time(t, chain, reps):
+    """ms per call of `chain` (which issues `reps` calls over distinct buffers) replayed as one CUDA graph: device time in
+    a stream of such calls, without the host's launch path."""
+    chain()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        chain()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            chain()
+    torch.cuda.current_stream().wait_stream(side)
+    flush, t.flush = t.flush, False
+    ms = t.run(g.replay) / reps
+    t.flush = flush
+    return ms
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemv", "gemm", "layer", "attn_decode", "attn_prefill", "gdn", "moe", "exl3"])
+    ap.add_argument("what", choices=["gemv", "gemm", "layer", "attn_decode", "attn_prefill", "gdn", "moe", "exl3",
+                                     "head_linear", "ffn_fp4", "select"])
+    ap.add_argument("--kv", default="bf16", help="attn_decode: cache form (bf16 | fp8 | int6 | int4)")
     ap.add_argument("--m", type=int, default=1)
     ap.add_argument("--n", type=int, default=5120)
     ap.add_argument("--k", type=int, default=5120)
@@ -223,6 +243,46 @@ def main():
                 tot_ms += r["ms"]
                 tot_b += r["GB/s"] * r["ms"]
         print(json.dumps({"sum_ms": round(tot_ms, 4), "mean_GB/s": round(tot_b / tot_ms, 1)}))
+    elif a.what == "head_linear":
+        # per-head up-projections of latent attention at the 671B-class shape: 128 heads, latent 512, head width 128
+        nh, L, dn = 128, 512, 128
+        for N, K, label in ((L, dn, "key up-projection into the query"), (dn, L, "value up-projection")):
+            wbytes = nh * N * K * 2
+            reps = max(2, min(24, -(-(400 << 20) // wbytes)))
+            Ws = [rnd(nh, N, K, scale=K ** -0.5) for _ in range(reps)]
+            x = rnd(a.m, nh, K)
+            ms = graph_time(t, lambda: [ops.head_linear(x, W) for W in Ws], reps)
+            report(f"head_linear rows{a.m} {nh} heads N{N} K{K} ({label})", ms, wbytes + a.m * nh * (N + K) * 2,
+                   2.0 * a.m * nh * N * K)
+    elif a.what == "ffn_fp4":
+        # dense FFN block of the 27B model on prompt rows, NVFP4 weights and activations: gate|up + SwiGLU + down with the
+        # activation re-quantised in the first GEMM's epilogue, against the same block through a bf16 activation
+        from ..ops.qweight import quantize_weight
+        H, I, M = 5120, 17408, max(a.m, 65)
+        ops.fp4_act = ops.fp4_prompt = True
+        x, nw, res = rnd(M, H), rnd(H, scale=0.1), rnd(M, H)
+        w_gu, w_dn = quantize_weight(rnd(2 * I, H, scale=H ** -0.5)), quantize_weight(rnd(H, I, scale=I ** -0.5))
+        flops = 2.0 * M * 3 * H * I
+        wbytes = 3 * H * I // 2 + 3 * H * I // 16
+        for fused in (True, False):
+            ops.fp4_fuse_requant = fused
+            ms = t.run(lambda: ops.ffn(x, w_gu, w_dn, nw, 1e-6, res))
+            act_bytes = M * I // 2 + M * I // 16 if fused else M * I * 2 * 2 + M * I // 2 + M * I // 16
+            report(f"ffn nvfp4 rows{M} {'SwiGLU output written as NVFP4' if fused else 'bf16 activation + quantiser'}", ms,
+                   wbytes + M * H * 2 * 3 + act_bytes, flops)
+        ops.fp4_fuse_requant = True
+    elif a.what == "select":
+        # sparse-attention selection of decode rows: indexer scores over --ctx entries (32 heads x 128 dims), exact top-2048
+        rows, n, nh, D, k = a.m, a.ctx, 32, 128, 2048
+        q, w = rnd(rows, nh, D, scale=0.3), torch.rand(rows, nh, device=dev)
+        keys = rnd(1, n, D)
+        slot = torch.zeros(rows, dtype=torch.int32, device=dev)
+        length = torch.full((rows,), n, dtype=torch.int32, device=dev)
+        ms = t.run(lambda: ops.index_score(q, w, 0.0, keys, slot, length, n))
+        report(f"index_score rows{rows} entries{n}", ms, n * D * 2 + rows * n * 4, 2.0 * rows * n * nh * D)
+        score = ops.index_score(q, w, 0.0, keys, slot, length, n)
+        ms = t.run(lambda: ops.topk_select(score, k))
+        report(f"topk_select rows{rows} entries{n} k{k}", ms, rows * n * 4 * 5, 0.0)
     elif a.what in ("attn_decode", "attn_prefill"):
         nq, nkv, hd, kvb = 24, 4, 256, 64
         nslots = 4 if a.what == "attn_decode" else 1
@@ -237,6 +297,18 @@ def main():
             slot = (torch.arange(rows, device=dev, dtype=torch.int32) % nslots).contiguous()
             kvlen = torch.full((rows,), a.ctx, device=dev, dtype=torch.int32)
             ns = a.splits or max(1, min(64, 1 << ((a.ctx + 255) // 256 - 1).bit_length()))
+            if a.kv != "bf16":
+                # quantised caches (random codes, unit-range scales: the timing does not depend on the values)
+                bits = {"fp8": 8, "int6": 6, "int4": 4}[a.kv]
+                kq = torch.randint(0, 255, (nslots * nb, kvb, nkv, hd * bits // 8), device=dev, dtype=torch.uint8)
+                vq = torch.randint(0, 255, (nslots * nb, kvb, nkv, hd * bits // 8), device=dev, dtype=torch.uint8)
+                if bits == 8:
+                    kq, vq = kq.clamp(max=119), vq.clamp(max=119)               # finite e4m3 codes
+                sc = torch.rand(nslots * nb, kvb, nkv, 2 if bits == 8 else 2 * (hd // 32), device=dev) * 0.1
+                ms = t.run(lambda: ops.attention(q, proj, kq, vq, slot, kvlen, bt, kvb, nq, nkv, hd, True, nsplit=ns, kv_scale=sc))
+                qbytes = rows * a.ctx * nkv * 2 * (hd * bits // 8 + sc.shape[-1] * 2)
+                report(f"attn_decode (SIMT, {a.kv} cache) rows{rows} ctx{a.ctx} splits{ns}", ms, qbytes, 4.0 * rows * a.ctx * nq * hd)
+                return 0
             ms = t.run(lambda: ops.attention(q, proj, kc, vc, slot, kvlen, bt, kvb, nq, nkv, hd, True, nsplit=ns))
             nbytes = rows * a.ctx * nkv * hd * 2 * 2
             report(f"attn_decode (SIMT) rows{rows} ctx{a.ctx} splits{ns}", ms, nbytes, 4.0 * rows * a.ctx * nq * hd)
