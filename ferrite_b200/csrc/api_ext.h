@@ -86,8 +86,10 @@ int fb_decode_layers(int n_layers, const int* start_phase, int M, int hidden, co
 void fb_decode_layer_trace_set(void* buf);
 
 // ---- moe.cu: router, grouped-expert GEMVs over (token, expert) pairs, fixed-order combine ----
+// `ld`: logit row stride (>= n_exp); shared_id >= 0 appends the shared expert as pick top_k (weight sigmoid(logit[shared_col])
+// or 1 when shared_col < 0): ids / wts rows are top_k + 1 wide then
 int fb_moe_route(int* ids, float* wts, const float* logits, const float* bias, int rows, int n_exp, int top_k, int mode,
-                 int n_groups, int topk_groups, float scale, cudaStream_t s);
+                 int n_groups, int topk_groups, float scale, int ld, int shared_col, int shared_id, cudaStream_t s);
 int fb_moe_gate_up(void* act, const void* x, const void* w_gu, const int* ids, int pairs, int top_k, int hidden,
                    int inter, int e_lo, int e_hi, cudaStream_t s);
 int fb_moe_down(float* yp, const void* act, const void* w_down, const int* ids, int pairs, int hidden, int inter,

@@ -255,11 +255,14 @@ void gemv_nvfp4_tc(Tensor Y, Tensor X, c10::optional<Tensor> norm_w, double eps,
 }
 
 void moe_route(Tensor ids, Tensor wts, Tensor logits, c10::optional<Tensor> bias, int64_t mode, int64_t n_groups,
-               int64_t topk_groups, double scale) {
+               int64_t topk_groups, double scale, int64_t n_exp, int64_t shared_col, int64_t shared_id) {
+  // logits [rows, >= n_exp] fp32 (n_exp <= 0: every column is an expert); ids / wts [rows, top_k (+ 1 with a shared expert)]
+  const int ne = n_exp > 0 ? (int)n_exp : (int)logits.size(1);
+  const int top_k = (int)ids.size(1) - (shared_id >= 0 ? 1 : 0);
   check(fb_moe_route(ids.data_ptr<int>(), wts.data_ptr<float>(), logits.data_ptr<float>(),
-                     bias.has_value() ? bias->data_ptr<float>() : nullptr, (int)logits.size(0), (int)logits.size(1),
-                     (int)ids.size(1), (int)mode, (int)n_groups, (int)topk_groups, (float)scale, cur_stream()),
-        "moe_route");
+                     bias.has_value() ? bias->data_ptr<float>() : nullptr, (int)logits.size(0), ne, top_k, (int)mode,
+                     (int)n_groups, (int)topk_groups, (float)scale, (int)logits.stride(0), (int)shared_col, (int)shared_id,
+                     cur_stream()), "moe_route");
 }
 
 void moe_experts(Tensor out, Tensor act, Tensor yp, Tensor x, Tensor w_gu, Tensor w_down, Tensor ids, Tensor wts,

@@ -20,11 +20,14 @@ constexpr int RT_MAXPL = 32;      // experts per lane (up to 1024 experts)
 __global__ void __launch_bounds__(32) route_kernel(int* __restrict__ ids, float* __restrict__ wts,
                                                    const float* __restrict__ logits, const float* __restrict__ bias,
                                                    int n_exp, int top_k, int mode, int n_groups, int topk_groups,
-                                                   float scale) {
+                                                   float scale, int ld, int shared_col, int shared_id) {
   pdl_launch_dependents();
   pdl_wait();
   const int row = blockIdx.x, lane = threadIdx.x;
-  const float* lp = logits + (size_t)row * n_exp;
+  const float* lp = logits + (size_t)row * ld;
+  // `shared_id` >= 0: the always-on shared expert rides along as pick number top_k (expert id shared_id of the stack),
+  // weighted by sigmoid(logit[shared_col]) or 1; ids / wts rows are then top_k + 1 wide
+  const int kout = top_k + (shared_id >= 0 ? 1 : 0);
   const int per = (n_exp + 31) / 32;                 // contiguous experts per lane: lane owns [lane*per, +per)
   float sc[RT_MAXPL], sel[RT_MAXPL];
   float mx = -INFINITY;
@@ -92,8 +95,12 @@ __global__ void __launch_bounds__(32) route_kernel(int* __restrict__ ids, float*
     if (lane == k) { myw = w; myid = e; }
   }
   if (lane < top_k) {
-    ids[(size_t)row * top_k + lane] = myid;
-    wts[(size_t)row * top_k + lane] = myw / (wsum + 1e-20f) * scale;
+    ids[(size_t)row * kout + lane] = myid;
+    wts[(size_t)row * kout + lane] = myw / (wsum + 1e-20f) * scale;
+  }
+  if (shared_id >= 0 && lane == 0) {
+    ids[(size_t)row * kout + top_k] = shared_id;
+    wts[(size_t)row * kout + top_k] = shared_col >= 0 ? sigmoidf_(lp[shared_col]) : 1.f;
   }
 }
 
@@ -213,8 +220,10 @@ __global__ void moe_combine_kernel(void* __restrict__ out, const float* __restri
 using namespace fb;
 
 extern "C" int fb_moe_route(int* ids, float* wts, const float* logits, const float* bias, int rows, int n_exp, int top_k,
-                            int mode, int n_groups, int topk_groups, float scale, cudaStream_t s) {
+                            int mode, int n_groups, int topk_groups, float scale, int ld, int shared_col, int shared_id,
+                            cudaStream_t s) {
   if (rows <= 0) return 0;
+  if (ld < n_exp || shared_col >= ld) return -1;
   if (n_exp > 32 * RT_MAXPL || top_k > 32 || top_k > n_exp) return -1;
   if (mode == 1 && n_groups > 1) {
     // a group must cover a power-of-two number of whole lanes
@@ -224,7 +233,7 @@ extern "C" int fb_moe_route(int* ids, float* wts, const float* logits, const flo
     if (gl < 1 || (gl & (gl - 1)) || n_groups * gl > 32) return -2;
   }
   return (int)launch_pdl(route_kernel, dim3(rows), dim3(32), 0, s, ids, wts, logits, bias, n_exp, top_k, mode,
-                         n_groups, topk_groups, scale);
+                         n_groups, topk_groups, scale, ld, shared_col, shared_id);
 }
 
 extern "C" int fb_moe_gate_up(void* act, const void* x, const void* w_gu, const int* ids, int pairs, int top_k,

@@ -406,12 +406,15 @@ class CudaOps(CudaExtras):
         return out
 
     # ---- mixture of experts ---------------------------------------------------------------------------
-    def moe_route(self, logits, bias, mode, top_k, n_groups, topk_groups, scale):
+    def moe_route(self, logits, bias, mode, top_k, n_groups, topk_groups, scale, n_exp=0, shared_col=-1, shared_id=-1):
+        """Top-k routing. `shared_id` >= 0 appends the shared expert (entry shared_id of the expert stacks) as an extra
+        pick weighted by sigmoid(logits[:, shared_col]) (1 when shared_col < 0); `n_exp`: expert columns of `logits`."""
         T = logits.shape[0]
-        ids = self.empty(T, top_k, dtype=torch.int32, device=self.device)
-        wts = self.empty(T, top_k, dtype=torch.float32, device=self.device)
+        kout = top_k + (1 if shared_id >= 0 else 0)
+        ids = self.empty(T, kout, dtype=torch.int32, device=self.device)
+        wts = self.empty(T, kout, dtype=torch.float32, device=self.device)
         self.launches += 1
-        self.C.moe_route(ids, wts, logits, bias, mode, n_groups, topk_groups, scale)
+        self.C.moe_route(ids, wts, logits, bias, mode, n_groups, topk_groups, scale, n_exp, shared_col, shared_id)
         return ids, wts
 
     def moe_experts(self, h, ids, wts, w_gu, w_down, e_lo, e_hi, shared=None, shared_gate=None, res=None, out_f32=False):

@@ -40,7 +40,7 @@ def _special(ex, op: str, param: str, bound: Dict[str, Any]) -> Optional[Tuple[i
     if op == "embed" and param == "ids":
         return 0, int(bound["table"].shape[0]), "rows of the embedding table"
     if op in ("moe_experts",) and param == "ids":
-        return 0, max(1, ex.full_cfg.n_experts), "experts"
+        return 0, max(1, ex.full_cfg.n_experts) + 1, "experts (+ the shared expert's stack entry)"
     if param == "row_parent":
         return -1, 1 << 30, "tree rows"
     return None

@@ -43,6 +43,44 @@ def test_router(ops, mode, E, K, ng, tg, scale, T):
             assert abs(got[e] - want[e]) < 1e-4 * max(1.0, scale)
 
 
+@pytest.mark.parametrize("mode,E,K,ng,tg,scale", [(0, 512, 10, 1, 1, 1.0), (1, 256, 8, 8, 4, 2.5)])
+def test_router_appends_the_shared_expert(ops, mode, E, K, ng, tg, scale):
+    """Merged router | shared-gate logits (one more column): the first K picks equal the plain router's, pick K is the
+    shared expert's stack entry weighted by the sigmoid of the last column (1 without a gate column)."""
+    T = 5
+    full = rnd(T, E + 1, scale=2.0, seed=9, dtype=torch.float32)
+    bias = rnd(E, scale=0.1, seed=3, dtype=torch.float32) if mode == 1 else None
+    ids0, wts0 = ops.moe_route(full[:, :E].contiguous(), bias, mode, K, ng, tg, scale)
+    ids1, wts1 = ops.moe_route(full, bias, mode, K, ng, tg, scale, n_exp=E, shared_col=E, shared_id=E)
+    assert ids1.shape == (T, K + 1) and torch.equal(ids1[:, :K], ids0) and torch.equal(wts1[:, :K], wts0)
+    assert bool((ids1[:, K] == E).all()) and torch.allclose(wts1[:, K], torch.sigmoid(full[:, E]), atol=1e-6)
+    _, wts2 = ops.moe_route(full[:, :E].contiguous(), bias, mode, K, ng, tg, scale, n_exp=E, shared_col=-1, shared_id=E)
+    assert bool((wts2[:, K] == 1.0).all())
+
+
+def test_shared_expert_as_a_pair_matches_separate_linears(ext, monkeypatch):
+    """Decode rows of the tiny MoE models with the shared expert merged into the expert stacks against the same engine
+    with the merge switched off."""
+    from ferrite_b200.config import EngineConfig, tiny_mla
+    from ferrite_b200.engine.engine import Engine
+    from ferrite_b200.engine.executor import Segment
+    from ferrite_b200.models.weights import init_weights
+    cfg = tiny_mla()
+    w = init_weights(cfg, seed=0)
+    p = torch.randint(0, cfg.vocab, (24,), generator=torch.Generator().manual_seed(5)).tolist()
+    outs = []
+    for merge in ("1", "0"):
+        monkeypatch.setenv("FB_MOE_MERGE_SHARED", merge)
+        eng = Engine(cfg, w, EngineConfig(n_slots=1, max_ctx=64), device=DEV)
+        assert bool(eng.ex.moe_merged) == (merge == "1")
+        eng.forward([Segment(0, 0, p[:16], "none")])
+        outs.append(torch.cat([eng.forward([Segment(0, 16 + i, [p[16 + i]], "last")])[0].clone() for i in range(8)]).float())
+        eng.check()
+    kl = torch.nn.functional.kl_div(torch.log_softmax(outs[0], -1), torch.log_softmax(outs[1], -1), log_target=True,
+                                    reduction="batchmean").item()
+    assert kl < 1e-3, kl
+
+
 @pytest.mark.parametrize("T", [1, 4, 16, 48])
 @pytest.mark.parametrize("ep", [False, True])
 def test_experts(ops, T, ep, monkeypatch):
