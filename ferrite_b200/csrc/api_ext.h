@@ -90,14 +90,13 @@ void fb_decode_layer_trace_set(void* buf);
 // or 1 when shared_col < 0): ids / wts rows are top_k + 1 wide then
 int fb_moe_route(int* ids, float* wts, const float* logits, const float* bias, int rows, int n_exp, int top_k, int mode,
                  int n_groups, int topk_groups, float scale, int ld, int shared_col, int shared_id, cudaStream_t s);
-// `norm_w` non-null: x is the raw residual row, RMSNorm(1 + norm_w) is applied while the row is staged
 int fb_moe_gate_up(void* act, const void* x, const void* w_gu, const int* ids, int pairs, int top_k, int hidden,
-                   int inter, int e_lo, int e_hi, const void* norm_w, float eps, cudaStream_t s);
+                   int inter, int e_lo, int e_hi, cudaStream_t s);
 int fb_moe_down(float* yp, const void* act, const void* w_down, const int* ids, int pairs, int hidden, int inter,
                 int e_lo, int e_hi, cudaStream_t s);
 // NVFP4 expert weights (moe_fp4.cu): codes [experts][rows][K/2], e4m3 block scales [experts][rows][K/16], one tensor scale
 int fb_moe_gate_up_fp4(void* act, const void* x, const void* wq, const void* ws, float gscale, const int* ids, int pairs,
-                       int top_k, int hidden, int inter, int e_lo, int e_hi, const void* norm_w, float eps, cudaStream_t s);
+                       int top_k, int hidden, int inter, int e_lo, int e_hi, cudaStream_t s);
 int fb_moe_down_fp4(float* yp, const void* act, const void* wq, const void* ws, float gscale, const int* ids, int pairs,
                     int hidden, int inter, int e_lo, int e_hi, cudaStream_t s);
 int fb_nvfp4_dequant(void* out, const void* wq, const void* ws, float gscale, long elements, cudaStream_t s);

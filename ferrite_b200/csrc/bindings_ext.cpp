@@ -267,11 +267,11 @@ void moe_route(Tensor ids, Tensor wts, Tensor logits, c10::optional<Tensor> bias
 
 void moe_experts(Tensor out, Tensor act, Tensor yp, Tensor x, Tensor w_gu, Tensor w_down, Tensor ids, Tensor wts,
                  int64_t e_lo, int64_t e_hi, c10::optional<Tensor> shared, c10::optional<Tensor> shared_gate,
-                 c10::optional<Tensor> res, c10::optional<Tensor> norm_w, double eps) {
+                 c10::optional<Tensor> res) {
   int rows = (int)x.size(0), hidden = (int)x.size(1), top_k = (int)ids.size(1), inter = (int)w_down.size(2);
   int pairs = rows * top_k;
   check(fb_moe_gate_up(act.data_ptr(), x.data_ptr(), w_gu.data_ptr(), ids.data_ptr<int>(), pairs, top_k, hidden, inter,
-                       (int)e_lo, (int)e_hi, cptr(norm_w), (float)eps, cur_stream()), "moe_gate_up");
+                       (int)e_lo, (int)e_hi, cur_stream()), "moe_gate_up");
   check(fb_moe_down(yp.data_ptr<float>(), act.data_ptr(), w_down.data_ptr(), ids.data_ptr<int>(), pairs, hidden, inter,
                     (int)e_lo, (int)e_hi, cur_stream()), "moe_down");
   check(fb_moe_combine(out.data_ptr(), yp.data_ptr<float>(), wts.data_ptr<float>(), cptr(shared),
@@ -281,14 +281,12 @@ void moe_experts(Tensor out, Tensor act, Tensor yp, Tensor x, Tensor w_gu, Tenso
 
 void moe_experts_fp4(Tensor out, Tensor act, Tensor yp, Tensor x, Tensor gu_q, Tensor gu_s, double gu_scale, Tensor dn_q,
                      Tensor dn_s, double dn_scale, Tensor ids, Tensor wts, int64_t e_lo, int64_t e_hi,
-                     c10::optional<Tensor> shared, c10::optional<Tensor> shared_gate, c10::optional<Tensor> res,
-                     c10::optional<Tensor> norm_w, double eps) {
+                     c10::optional<Tensor> shared, c10::optional<Tensor> shared_gate, c10::optional<Tensor> res) {
   int rows = (int)x.size(0), hidden = (int)x.size(1), top_k = (int)ids.size(1), inter = (int)dn_q.size(2) * 2;
   int pairs = rows * top_k;
   TORCH_CHECK(gu_q.size(1) == 2 * inter && gu_q.size(2) * 2 == hidden && dn_q.size(1) == hidden, "moe_experts_fp4: shapes");
   check(fb_moe_gate_up_fp4(act.data_ptr(), x.data_ptr(), gu_q.data_ptr(), gu_s.data_ptr(), (float)gu_scale,
-                           ids.data_ptr<int>(), pairs, top_k, hidden, inter, (int)e_lo, (int)e_hi, cptr(norm_w), (float)eps,
-                           cur_stream()),
+                           ids.data_ptr<int>(), pairs, top_k, hidden, inter, (int)e_lo, (int)e_hi, cur_stream()),
         "moe_gate_up_fp4");
   check(fb_moe_down_fp4(yp.data_ptr<float>(), act.data_ptr(), dn_q.data_ptr(), dn_s.data_ptr(), (float)dn_scale,
                         ids.data_ptr<int>(), pairs, hidden, inter, (int)e_lo, (int)e_hi, cur_stream()), "moe_down_fp4");

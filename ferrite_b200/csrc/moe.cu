@@ -110,26 +110,15 @@ constexpr int MOE_THREADS = 256;
 // act[p][j] = silu(Wg[e][j] . x[t]) * (Wu[e][j] . x[t]);  W_gu[e] = [2*inter][hidden] (gate rows then up rows)
 __global__ void __launch_bounds__(MOE_THREADS)
 moe_gate_up_kernel(__nv_bfloat16* __restrict__ act, const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w_gu,
-                   const int* __restrict__ ids, int top_k, int hidden, int inter, int e_lo, int e_hi,
-                   const __nv_bfloat16* __restrict__ norm_w, float eps) {
+                   const int* __restrict__ ids, int top_k, int hidden, int inter, int e_lo, int e_hi) {
   pdl_launch_dependents();
   extern __shared__ __align__(16) __nv_bfloat16 xs_moe[];
-  __shared__ float red_moe[32];
   pdl_wait();                                                // ids come from the router kernel before this one
   const int p = blockIdx.y, e = ids[p];
   if (e < e_lo || e >= e_hi) return;                         // another rank owns this expert
   const int t = p / top_k;
-  if (norm_w) {
-    // RMSNorm(1 + w) of the token row while it is staged (same rounding as the stand-alone norm kernel)
-    float ss = 0.f;
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) { const float v = bf2f(x[(size_t)t * hidden + i]); ss = fmaf(v, v, ss); }
-    const float r = rsqrtf(block_sum(ss, red_moe) / (float)hidden + eps);
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x)
-      xs_moe[i] = f2bf(bf2f(x[(size_t)t * hidden + i]) * r * (1.f + bf2f(norm_w[i])));
-  } else {
-    for (int i = threadIdx.x; i < hidden / 8; i += blockDim.x)
-      reinterpret_cast<uint4*>(xs_moe)[i] = reinterpret_cast<const uint4*>(x + (size_t)t * hidden)[i];
-  }
+  for (int i = threadIdx.x; i < hidden / 8; i += blockDim.x)
+    reinterpret_cast<uint4*>(xs_moe)[i] = reinterpret_cast<const uint4*>(x + (size_t)t * hidden)[i];
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const __nv_bfloat16* we = w_gu + (size_t)(e - e_lo) * 2 * inter * hidden;
@@ -248,12 +237,12 @@ extern "C" int fb_moe_route(int* ids, float* wts, const float* logits, const flo
 }
 
 extern "C" int fb_moe_gate_up(void* act, const void* x, const void* w_gu, const int* ids, int pairs, int top_k,
-                              int hidden, int inter, int e_lo, int e_hi, const void* norm_w, float eps, cudaStream_t s) {
+                              int hidden, int inter, int e_lo, int e_hi, cudaStream_t s) {
   if (pairs <= 0) return 0;
   if (hidden % 8) return -1;
   return (int)launch_pdl(moe_gate_up_kernel, dim3((inter + 15) / 16, pairs), dim3(MOE_THREADS), (size_t)hidden * 2, s,
                          (__nv_bfloat16*)act, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w_gu, ids, top_k, hidden,
-                         inter, e_lo, e_hi, (const __nv_bfloat16*)norm_w, eps);
+                         inter, e_lo, e_hi);
 }
 
 extern "C" int fb_moe_down(float* yp, const void* act, const void* w_down, const int* ids, int pairs, int hidden,

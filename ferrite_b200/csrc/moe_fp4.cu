@@ -55,26 +55,14 @@ __device__ __forceinline__ uint2 mf_ld8(const unsigned char* p) {
 __global__ void __launch_bounds__(MF_THREADS)
 moe_gate_up_fp4_kernel(__nv_bfloat16* __restrict__ act, const __nv_bfloat16* __restrict__ x,
                        const unsigned char* __restrict__ wq, const unsigned char* __restrict__ ws, float gscale,
-                       const int* __restrict__ ids, int top_k, int hidden, int inter, int e_lo, int e_hi,
-                       const __nv_bfloat16* __restrict__ norm_w, float eps) {
+                       const int* __restrict__ ids, int top_k, int hidden, int inter, int e_lo, int e_hi) {
   pdl_launch_dependents();
   extern __shared__ __align__(16) __half xs_mf[];
-  __shared__ float red_mf[32];
   pdl_wait();
   const int p = blockIdx.y, e = ids[p];
   if (e < e_lo || e >= e_hi) return;
   const int t = p / top_k;
-  float r = 1.f;
-  if (norm_w) {                                                 // RMSNorm(1 + w) of the token row while it is staged
-    float ss = 0.f;
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) { const float v = bf2f(x[(size_t)t * hidden + i]); ss = fmaf(v, v, ss); }
-    r = rsqrtf(block_sum(ss, red_mf) / (float)hidden + eps);
-  }
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-    float v = bf2f(x[(size_t)t * hidden + i]);
-    if (norm_w) v = bf2f(f2bf(v * r * (1.f + bf2f(norm_w[i]))));      // the stand-alone norm kernel's rounding
-    xs_mf[i] = __float2half(v);
-  }
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) xs_mf[i] = __float2half(bf2f(x[(size_t)t * hidden + i]));
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int j0 = blockIdx.x * 16 + warp * 2;
@@ -182,13 +170,12 @@ __global__ void nvfp4_dequant_kernel(__nv_bfloat16* __restrict__ out, const unsi
 using namespace fb;
 
 extern "C" int fb_moe_gate_up_fp4(void* act, const void* x, const void* wq, const void* ws, float gscale, const int* ids,
-                                  int pairs, int top_k, int hidden, int inter, int e_lo, int e_hi, const void* norm_w,
-                                  float eps, cudaStream_t s) {
+                                  int pairs, int top_k, int hidden, int inter, int e_lo, int e_hi, cudaStream_t s) {
   if (pairs <= 0) return 0;
   if (hidden % 16 || inter <= 0) return -1;
   launch_pdl(moe_gate_up_fp4_kernel, dim3((inter + 15) / 16, pairs), dim3(MF_THREADS), (size_t)hidden * 2, s,
              (__nv_bfloat16*)act, (const __nv_bfloat16*)x, (const unsigned char*)wq, (const unsigned char*)ws, gscale, ids,
-             top_k, hidden, inter, e_lo, e_hi, (const __nv_bfloat16*)norm_w, eps);
+             top_k, hidden, inter, e_lo, e_hi);
   return (int)cudaGetLastError();
 }
 

@@ -462,19 +462,17 @@ class Executor:
         (and its column slice of the shared expert); the partial sums are reduced over ranks with the residual."""
         c, w, ops = self.cfg, self.w, self.ops
         p = f"l{i}."
+        h, _ = ops.rmsnorm(x, w[p + "post_norm"], c.eps, True)
         merged = self.moe_merged.get(i)
-        if merged is not None and x.shape[0] <= getattr(ops, "moe_pair_rows", 0):
+        if merged is not None and h.shape[0] <= getattr(ops, "moe_pair_rows", 0):
             # few rows on one GPU: the shared expert is entry n_experts of the expert stacks and rides along as one more
-            # (token, expert) pair, weighted by the sigmoid of the last column of the merged router | shared-gate product;
-            # the norm is the router product's prologue and part of the pair kernels' row staging: five launches in all
+            # (token, expert) pair, weighted by the sigmoid of the last column of the merged router | shared-gate product
             n_exp = self.full_cfg.n_experts
-            logits = ops.linear(x, merged, norm_w=w[p + "post_norm"], eps=c.eps, out_f32=True)
+            logits = ops.linear(h, merged, out_f32=True)
             ids, wts = ops.moe_route(logits, w.get(p + "router_bias"), 0 if c.router == "softmax" else 1, c.top_k,
                                      c.n_groups, c.topk_groups, c.route_scale, n_exp=n_exp,
                                      shared_col=n_exp if merged.shape[0] > n_exp else -1, shared_id=n_exp)
-            return ops.moe_experts(x, ids, wts, w[p + "experts_gate_up"], w[p + "experts_down"], 0, n_exp + 1, None, None, x,
-                                   norm_w=w[p + "post_norm"], eps=c.eps)
-        h, _ = ops.rmsnorm(x, w[p + "post_norm"], c.eps, True)
+            return ops.moe_experts(h, ids, wts, w[p + "experts_gate_up"], w[p + "experts_down"], 0, n_exp + 1, None, None, x)
         logits = ops.linear(h, w[p + "router"], out_f32=True)
         ids, wts = ops.moe_route(logits.contiguous(), w.get(p + "router_bias"), 0 if c.router == "softmax" else 1, c.top_k,
                                  c.n_groups, c.topk_groups, c.route_scale)

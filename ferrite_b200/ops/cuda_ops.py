@@ -417,14 +417,8 @@ class CudaOps(CudaExtras):
         self.C.moe_route(ids, wts, logits, bias, mode, n_groups, topk_groups, scale, n_exp, shared_col, shared_id)
         return ids, wts
 
-    def moe_experts(self, h, ids, wts, w_gu, w_down, e_lo, e_hi, shared=None, shared_gate=None, res=None, out_f32=False,
-                    norm_w=None, eps=1e-6):
-        """`norm_w`: `h` is the raw residual and the pair kernels apply RMSNorm(1 + norm_w) while staging each row (few
-        rows only)."""
+    def moe_experts(self, h, ids, wts, w_gu, w_down, e_lo, e_hi, shared=None, shared_gate=None, res=None, out_f32=False):
         T, K = ids.shape
-        if norm_w is not None and T > self.moe_pair_rows:
-            h, _ = self.rmsnorm(h, norm_w, eps, True)
-            norm_w = None
         H, inter = h.shape[1], w_down.shape[2]
         if isinstance(w_gu, ExpertsFP4):
             if T > self.moe_pair_rows:
@@ -437,8 +431,7 @@ class CudaOps(CudaExtras):
                 self.launches += 3
                 self.C.moe_experts_fp4(out, act, yp, h, w_gu.packed, w_gu.scales, w_gu.global_scale, w_down.packed,
                                        w_down.scales, w_down.global_scale, ids, wts, e_lo, e_hi, shared,
-                                       None if shared_gate is None else shared_gate.reshape(-1).float().contiguous(), res,
-                                       norm_w, eps)
+                                       None if shared_gate is None else shared_gate.reshape(-1).float().contiguous(), res)
                 return out
         if T > self.moe_pair_rows:
             return self._moe_grouped(h, ids, wts, w_gu, w_down, e_lo, e_hi, shared, shared_gate, res, out_f32)
@@ -447,7 +440,7 @@ class CudaOps(CudaExtras):
         out = self.empty(T, H, dtype=torch.float32 if out_f32 else self.dtype, device=self.device)
         self.launches += 3
         self.C.moe_experts(out, act, yp, h, w_gu, w_down, ids, wts, e_lo, e_hi, shared,
-                           None if shared_gate is None else shared_gate.reshape(-1).float().contiguous(), res, norm_w, eps)
+                           None if shared_gate is None else shared_gate.reshape(-1).float().contiguous(), res)
         return out
 
     def experts_dense(self, w, which: int):
