@@ -6,7 +6,7 @@
 //                             sum_t kvc_t * softmax_t(sc_t) per channel (ratio 1: the value itself), other rows zeros
 //   index_score               score[r][e] = sum_h w[r][h] * relu(q[r][h] . key[slot(r)][e]) for e < len(r), -inf
 //                             elsewhere (and where a candidate mask drops the entry's block): mma.sync m16n8k16 with
-//                             entries as M, heads as N, the key width as K
+//                             entries as M, heads as N, the key width (permuted for 16-byte loads) as K
 //   topk_select               exact top-k of a score row by 4 x 8-bit radix selection on order-preserving keys; ties to
 //                             the lower index; -inf entries never count; output ascending indices, -1 padded
 //   block_max / sel_to_mask   candidate pool of a later layer: block maxima (the block of the last valid entry always
@@ -70,7 +70,14 @@ __device__ __forceinline__ void idx_mma(float (&c)[4], const uint32_t (&a)[4], u
 constexpr int IDX_MAX_HEADS = 64;
 
 // grid = (ceil(ld / 128), rows), 256 threads: a warp takes 16 entries. q [rows][nh][D] bf16, w [rows][nh] fp32 (null:
-// every head weighs `scale`), keys [slots][key_stride] bf16 with entry e at e * D, D a multiple of 16.
+// every head weighs `scale`), keys [slots][key_stride] bf16 with entry e at e * D, D a multiple of 32 and <= 128.
+//
+// A dot product does not care in which order K is walked, so the K dimension is permuted to suit the loads: lane t of a
+// row's four lanes reads 16 contiguous bytes (8 values) per pair of k16 steps, words {0, 1} feed the first step's two
+// A registers and words {2, 3} the second's; the query fragments are read with the same pattern. All of a warp's key
+// loads (two rows x D / 32 uint4 per lane) are in flight before the first MMA.
+constexpr int IDX_MAX_D = 128;
+
 __global__ void __launch_bounds__(256) index_score_kernel(float* __restrict__ score, int ld, const __nv_bfloat16* __restrict__ q,
                                                           const float* __restrict__ w, float scale,
                                                           const __nv_bfloat16* __restrict__ keys, long key_stride,
@@ -86,26 +93,30 @@ __global__ void __launch_bounds__(256) index_score_kernel(float* __restrict__ sc
   const int ea = e0 + g, eb = e0 + g + 8;
   auto kept = [&](int e) { return e < len && (!mask || mask[(size_t)r * mask_ld + e / mask_block] != 0); };
   const bool ka = kept(ea), kb8 = kept(eb);
-  const int ntiles = (nh + 7) / 8;
+  const int ntiles = (nh + 7) / 8, npair = D / 32;      // pairs of k16 steps
+  uint4 ra[IDX_MAX_D / 32], rb[IDX_MAX_D / 32];
+#pragma unroll
+  for (int j = 0; j < IDX_MAX_D / 32; ++j) {
+    ra[j] = (ka && j < npair) ? ldg_stream(reinterpret_cast<const uint4*>(kb + (size_t)ea * D) + j * 4 + t) : make_uint4(0, 0, 0, 0);
+    rb[j] = (kb8 && j < npair) ? ldg_stream(reinterpret_cast<const uint4*>(kb + (size_t)eb * D) + j * 4 + t) : make_uint4(0, 0, 0, 0);
+  }
   float acc[IDX_MAX_HEADS / 8][4];
 #pragma unroll
   for (int n = 0; n < IDX_MAX_HEADS / 8; ++n) { acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f; }
-  for (int k0 = 0; k0 < D; k0 += 16) {
-    uint32_t a[4];
-    a[0] = ka ? *reinterpret_cast<const uint32_t*>(kb + (size_t)ea * D + k0 + 2 * t) : 0u;
-    a[1] = kb8 ? *reinterpret_cast<const uint32_t*>(kb + (size_t)eb * D + k0 + 2 * t) : 0u;
-    a[2] = ka ? *reinterpret_cast<const uint32_t*>(kb + (size_t)ea * D + k0 + 8 + 2 * t) : 0u;
-    a[3] = kb8 ? *reinterpret_cast<const uint32_t*>(kb + (size_t)eb * D + k0 + 8 + 2 * t) : 0u;
 #pragma unroll
-    for (int n = 0; n < IDX_MAX_HEADS / 8; ++n) {
-      if (n < ntiles) {
-        const int h = n * 8 + g;
-        uint32_t b0 = 0u, b1 = 0u;
-        if (h < nh) {
-          b0 = *reinterpret_cast<const uint32_t*>(qr + (size_t)h * D + k0 + 2 * t);
-          b1 = *reinterpret_cast<const uint32_t*>(qr + (size_t)h * D + k0 + 8 + 2 * t);
+  for (int j = 0; j < IDX_MAX_D / 32; ++j) {
+    if (j < npair) {
+      const uint32_t a0[4] = {ra[j].x, rb[j].x, ra[j].y, rb[j].y};      // first k16 step: (row g, row g + 8) x words {0, 1}
+      const uint32_t a1[4] = {ra[j].z, rb[j].z, ra[j].w, rb[j].w};      // second: words {2, 3}
+#pragma unroll
+      for (int n = 0; n < IDX_MAX_HEADS / 8; ++n) {
+        if (n < ntiles) {
+          const int h = n * 8 + g;
+          uint4 bq = make_uint4(0, 0, 0, 0);
+          if (h < nh) bq = __ldg(reinterpret_cast<const uint4*>(qr + (size_t)h * D) + j * 4 + t);
+          idx_mma(acc[n], a0, bq.x, bq.y);
+          idx_mma(acc[n], a1, bq.z, bq.w);
         }
-        idx_mma(acc[n], a, b0, b1);
       }
     }
   }
@@ -339,7 +350,8 @@ extern "C" int fb_index_score(float* score, int ld, const void* q, const float* 
                               long key_stride, const int* row_slot, const int* row_len, const uint8_t* mask, int mask_ld,
                               int mask_block, int rows, int nh, int D, cudaStream_t s) {
   if (rows <= 0 || ld <= 0) return 0;
-  if (nh < 1 || nh > IDX_MAX_HEADS || D % 16 || rows > 65535 || (mask && mask_block < 1)) return -1;
+  if (nh < 1 || nh > IDX_MAX_HEADS || D % 32 || D > IDX_MAX_D || rows > 65535 || (mask && mask_block < 1)) return -1;
+  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(keys)) & 15 || key_stride % 8) return -1;
   dim3 grid((ld + 127) / 128, rows);
   index_score_kernel<<<grid, 256, 0, s>>>(score, ld, (const __nv_bfloat16*)q, w, scale, (const __nv_bfloat16*)keys,
                                           key_stride, row_slot, row_len, mask, mask_ld, mask_block, nh, D);
