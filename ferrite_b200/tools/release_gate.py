@@ -1,4 +1,4 @@
-"""Release gate: the checks a build has to pass before it is handed out, run against a live server, one verdict.
+"""Release gate: the checks a build has to pass before it is handed out, run against a live server, one pass or fail.
 
     python -m ferrite_b200.tools.release_gate --base-url http://127.0.0.1:8000 [--mock] [--min-tok-s 50] [--lanes 1,2,4]
 
