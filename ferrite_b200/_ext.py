@@ -37,3 +37,15 @@ def available() -> bool:
         return True
     except Exception:
         return False
+
+
+def host():
+    """The extension when it is already built (its host-side classes need no GPU), else None: callers fall back to their
+    plain-Python statement of the same behaviour. `FERRITE_NO_NATIVE_HOST=1` forces the fallback."""
+    if os.environ.get("FERRITE_NO_NATIVE_HOST"):
+        return None
+    try:
+        m = load(build_if_missing=False)
+    except Exception:  # noqa: BLE001 - not built, or built for another torch: the Python paths serve
+        return None
+    return m if hasattr(m, "CopyIndex") else None

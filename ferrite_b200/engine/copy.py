@@ -24,6 +24,11 @@ class Copier:
     def __init__(self, lo: int = 4, hi: int = MAX_MATCH):
         self.tokens: List[int] = []
         self.index: Dict[Tuple[int, ...], List[int]] = {}
+        # the index and the suffix match run in C++ when the extension is built (`csrc/host_runtime.cpp`); the Python
+        # statement below is the same algorithm and serves otherwise
+        from .._ext import host
+        h = host()
+        self.native = h.CopyIndex(KEY, MIN_MATCH, MAX_MATCH, SCAN) if h is not None else None
         self.misses = 0
         self.quiet = 0
         self.lo, self.hi = max(1, lo), max(lo, hi)
@@ -31,6 +36,17 @@ class Copier:
 
     def sync(self, tokens: Sequence[int]) -> None:
         """Bring the index up to date with the sequence (prompt + generated so far); handles rollbacks."""
+        if self.native is not None:
+            # per step the sequence only grows: when its length did not shrink and the indexed sequence's last tokens are
+            # still in place, only the new tokens cross into C++; anything else is a full (exact) resync
+            n = self.native.size()
+            k = min(n, 8)
+            if len(tokens) >= n and [int(t) for t in tokens[n - k:n]] == list(self.native.tail(k)):
+                if len(tokens) > n:
+                    self.native.extend([int(t) for t in tokens[n:]])
+            else:
+                self.native.sync([int(t) for t in tokens])
+            return
         n = len(self.tokens)
         if len(tokens) < n or list(tokens[:n]) != self.tokens:
             self.tokens, self.index = [], {}
@@ -48,6 +64,8 @@ class Copier:
         if self.quiet > 0:
             self.quiet -= 1
             return []
+        if self.native is not None:
+            return list(self.native.propose(min(max_len, MAX_MATCH, self.extra if adaptive else MAX_MATCH)))
         t = self.tokens
         n = len(t)
         if n < MIN_MATCH + 1:
@@ -94,6 +112,12 @@ def graft(toks: List[int], parents: List[int], copy: Sequence[int], room: int) -
     a row hangs from (-1 for the root), `copy` the tokens proposed after the root. The copy is followed down the rows that
     already hold it; up to `room` of what is left is appended as a chain below the deepest of them. Returns (tokens of
     the copy found in the tree, rows added). Reference `graft`, `crates/fe-model/src/copy.rs:128-147`."""
+    from .._ext import host
+    h = host()
+    if h is not None:
+        t2, p2, found, added = h.host_graft([int(t) for t in toks], [int(x) for x in parents], [int(t) for t in copy], int(room))
+        toks[:], parents[:] = list(t2), list(p2)
+        return int(found), int(added)
     r, i = 0, 0
     while i < len(copy):
         nxt = next((c for c in range(r + 1, len(toks)) if parents[c] == r and toks[c] == copy[i]), None)

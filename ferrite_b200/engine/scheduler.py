@@ -114,6 +114,11 @@ def grow_tree(cands: Sequence[Sequence[Tuple[int, float]]], rows: int) -> Tuple[
     added in order of their path's summed log-probability until `rows` draft rows exist. Returns (tokens, parents) of
     the draft rows in segment numbering: the root (the token being fed) is row 0, draft row i is row i + 1, parents
     come before children. Reference `grow_tree` (`crates/fe-dflash/src/lib.rs:306`)."""
+    from .._ext import host
+    h = host()
+    if h is not None:                                        # C++ (`csrc/host_runtime.cpp`), the same heap discipline
+        t2, p2 = h.host_grow_tree([[int(t) for t, _ in c] for c in cands], [[float(lp) for _, lp in c] for c in cands], int(rows))
+        return list(t2), list(p2)
     import heapq
     toks: List[int] = []
     par: List[int] = []
@@ -137,9 +142,18 @@ def grow_tree(cands: Sequence[Sequence[Tuple[int, float]]], rows: int) -> Tuple[
 
 
 def tree_walk(tokens: Sequence[int], parents: Sequence[int], pick) -> Tuple[List[int], List[int]]:
-    """Walk a verified tree from the root: `pick(row)` is the target's token after the row; descend into the child
+    """Walk a verified tree from the root: `pick(row)` (a callable, or the list of all rows' picks) is the target's token
+    after the row; descend into the child
     that carries it, stop when none does. Returns (rows of the accepted path, tokens to emit), one token per path
     row. Reference `tree_walk` (`crates/fe-model/src/sched.rs:125`)."""
+    if not callable(pick):                                   # the picks as a list (greedy rows)
+        from .._ext import host
+        h = host()
+        if h is not None:
+            path, new = h.host_tree_walk([int(t) for t in tokens], [int(p) for p in parents], [int(t) for t in pick])
+            return list(path), list(new)
+        seq = pick
+        pick = lambda node: seq[node]                        # noqa: E731
     kids: Dict[int, List[int]] = {}
     for r, p in enumerate(parents):
         if p >= 0:
@@ -652,7 +666,9 @@ class Scheduler:
                     t = a.sampler.sample(logits[r + node])
                     a.sampler.observe(t)
                     return t
-                path, new = tree_walk([a.next_token] + d, par, pick)
+                # greedy: the target's picks of all rows are known, the walk runs in C++ when the extension is built
+                path, new = tree_walk([a.next_token] + d, par,
+                                      [int(t) for t in ids[r:r + 1 + len(d)]] if all_greedy else pick)
                 paths.append(path)
                 keep.append(len(new))
                 acc = len(new) - 1

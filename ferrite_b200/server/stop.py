@@ -11,6 +11,10 @@ class StopMatcher:
         self.include = include
         self.buf = ""
         self.hit: Optional[str] = None
+        # the scan runs in C++ on UTF-8 bytes when the extension is built (`csrc/host_runtime.cpp`)
+        from .._ext import host
+        h = host()
+        self.native = h.StopScanner([s.encode("utf-8") for s in self.stops], include) if (h is not None and self.stops) else None
 
     def push(self, text: str) -> Tuple[str, bool]:
         """Returns (text safe to emit, stopped)."""
@@ -18,6 +22,11 @@ class StopMatcher:
             return "", True
         if not self.stops:
             return text, False
+        if self.native is not None:
+            out, stopped = self.native.push(text.encode("utf-8"))
+            if stopped:
+                self.hit = self.native.hit().decode("utf-8")
+            return out.decode("utf-8"), stopped
         self.buf += text
         best = None
         for s in self.stops:
@@ -41,5 +50,7 @@ class StopMatcher:
         return out, False
 
     def flush(self) -> str:
+        if self.native is not None:
+            return self.native.flush().decode("utf-8")
         out, self.buf = self.buf, ""
         return out
