@@ -5,6 +5,7 @@
 //   grow_tree     best-first verify tree from per-depth candidates
 //   graft         a copy proposal laid onto a draft tree
 //   StopScanner   stop strings on a text stream, holding back text that may still become one
+//   fill_step_meta the int32 staging block of an engine step (tokens, slots, positions, segment tables, verify-tree layout)
 //
 // Each has a plain-Python statement of the same behaviour (`engine/copy.py`, `engine/scheduler.py`, `server/stop.py`) that
 // serves when the extension is not built and that the tests compare against, result for result. Counterparts of the
@@ -229,6 +230,77 @@ class StopScanner {
   std::string buf_, hit_text_;
 };
 
+// ---- step metadata -------------------------------------------------------------------------------------------------
+// Fills the staging buffer of one engine step (int32, usually pinned): [tok T | slot T | pos T | kvlen T | lrow T |
+// seg_slot S | seg_row0 S | seg_nrows S | seg_pos0 S] from the step's segments. `want`: 0 no logits, 1 the last row's,
+// 2 every row's. With `parents` (one list per segment; empty = a chain) the rows are a verify tree: positions become
+// pos0 + depth and the tree block `th` = [ancestor masks (int64 x R) | cache row R | base R | parent R | flags R] is
+// filled too (flag bit 0: the row's parent is not the row before it; bit 1: a later row branches from this one).
+// Returns the rows whose logits the step produces.
+std::vector<int> fill_step_meta(torch::Tensor h, const std::vector<std::vector<int64_t>>& seg_tokens,
+                                const std::vector<int>& seg_slot, const std::vector<int>& seg_pos0,
+                                const std::vector<int>& seg_want, c10::optional<torch::Tensor> th, int64_t R,
+                                const std::vector<std::vector<int>>& parents) {
+  TORCH_CHECK(h.dtype() == torch::kInt32 && h.is_contiguous() && !h.is_cuda(), "fill_step_meta: host int32 buffer");
+  const size_t S = seg_tokens.size();
+  TORCH_CHECK(seg_slot.size() == S && seg_pos0.size() == S && seg_want.size() == S, "fill_step_meta: one entry per segment");
+  size_t T = 0;
+  for (const auto& t : seg_tokens) T += t.size();
+  TORCH_CHECK((size_t)h.numel() >= 5 * T + 4 * S, "fill_step_meta: staging buffer too small");
+  int32_t* p = h.data_ptr<int32_t>();
+  int32_t *tok = p, *slot = p + T, *pos = p + 2 * T, *kvl = p + 3 * T, *lrow = p + 4 * T;
+  int32_t *sslot = p + 5 * T, *srow0 = sslot + S, *snrows = srow0 + S, *spos0 = snrows + S;
+  const bool tree = th.has_value() && th->defined();
+  int64_t* tmask = nullptr;
+  int32_t *tcpos = nullptr, *tbase = nullptr, *tpar = nullptr, *tflag = nullptr;
+  if (tree) {
+    TORCH_CHECK(th->dtype() == torch::kInt32 && th->is_contiguous() && th->numel() >= 6 * R && (int64_t)T <= R &&
+                parents.size() == S, "fill_step_meta: tree block");
+    int32_t* q = th->data_ptr<int32_t>();
+    tmask = reinterpret_cast<int64_t*>(q);
+    tcpos = q + 2 * R; tbase = q + 3 * R; tpar = q + 4 * R; tflag = q + 5 * R;
+  }
+  std::vector<int> logit_rows;
+  size_t r = 0;
+  for (size_t si = 0; si < S; ++si) {
+    const auto& t = seg_tokens[si];
+    const int n = (int)t.size(), p0 = seg_pos0[si];
+    for (int j = 0; j < n; ++j) {
+      tok[r + j] = (int32_t)t[j];
+      slot[r + j] = seg_slot[si];
+      pos[r + j] = p0 + j;
+      kvl[r + j] = p0 + j + 1;
+    }
+    if (tree) {
+      const auto& par = parents[si];
+      TORCH_CHECK(par.empty() || (int)par.size() == n, "fill_step_meta: one parent per row");
+      TORCH_CHECK(n > 0 && n <= 64, "a verify tree holds 1..64 rows");
+      std::vector<int> depth(n, 0);
+      for (int j = 0; j < n; ++j) {
+        const int pj = par.empty() ? j - 1 : par[j];
+        TORCH_CHECK((pj == -1 && j == 0) || (pj >= 0 && pj < j), "parents come before their children; row 0 is the root");
+        depth[j] = pj < 0 ? 0 : depth[pj] + 1;
+        tmask[r + j] = (int64_t)((1ull << j) | (pj < 0 ? 0ull : (uint64_t)tmask[r + pj]));
+        tflag[r + j] = 0;
+        if (pj != j - 1) {
+          tflag[r + j] |= 1;
+          if (pj >= 0) tflag[r + pj] |= 2;
+        }
+        pos[r + j] = p0 + depth[j];
+        tcpos[r + j] = p0 + j;
+        tbase[r + j] = p0;
+        tpar[r + j] = pj;
+      }
+    }
+    sslot[si] = seg_slot[si]; srow0[si] = (int32_t)r; snrows[si] = n; spos0[si] = p0;
+    if (seg_want[si] == 2) for (int j = 0; j < n; ++j) logit_rows.push_back((int)r + j);
+    else if (seg_want[si] == 1 && n > 0) logit_rows.push_back((int)r + n - 1);
+    r += n;
+  }
+  for (size_t i = 0; i < logit_rows.size(); ++i) lrow[i] = logit_rows[i];
+  return logit_rows;
+}
+
 }  // namespace
 
 void register_host(pybind11::module_& m) {
@@ -242,6 +314,7 @@ void register_host(pybind11::module_& m) {
   m.def("host_tree_walk", &tree_walk);
   m.def("host_grow_tree", &grow_tree);
   m.def("host_graft", &graft);
+  m.def("fill_step_meta", &fill_step_meta);
   py::class_<StopScanner>(m, "StopScanner")
       .def(py::init<std::vector<std::string>, bool>(), py::arg("stops"), py::arg("include") = false)
       .def("push", &StopScanner::push)

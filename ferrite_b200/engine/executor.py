@@ -380,7 +380,19 @@ class Executor:
             th = self._tring[ri]
             tmask = th[:2 * R].view(torch.int64)
             tcpos, tbase, tpar, tflag = (th[(2 + i) * R:(3 + i) * R] for i in range(4))
-        for si, sg in enumerate(batch.segments):
+        from .._ext import host
+        hn = host()
+        if hn is not None:
+            # the whole block is written by one C++ call (`csrc/host_runtime.cpp`); the loop below states the same layout
+            for sg in batch.segments:
+                self.ensure_capacity(sg.slot, sg.pos0 + len(sg.tokens))
+            segs = batch.segments
+            logit_rows = list(hn.fill_step_meta(
+                h, [[int(t) for t in sg.tokens] for sg in segs], [int(sg.slot) for sg in segs], [int(sg.pos0) for sg in segs],
+                [2 if sg.want_logits == "all" else 1 if sg.want_logits == "last" else 0 for sg in segs],
+                th if tree else None, self._R,
+                [([int(x) for x in sg.parents] if sg.parents is not None else []) for sg in segs] if tree else []))
+        for si, sg in enumerate(batch.segments if hn is None else ()):
             n = len(sg.tokens)
             self.ensure_capacity(sg.slot, sg.pos0 + n)
             tok[r:r + n] = torch.tensor(sg.tokens, dtype=torch.int32)
@@ -404,7 +416,8 @@ class Executor:
                 logit_rows.append(r + n - 1)
             r += n
         nl = len(logit_rows)
-        lrow[:nl] = torch.tensor(logit_rows, dtype=torch.int32) if nl else lrow[:0]
+        if hn is None:
+            lrow[:nl] = torch.tensor(logit_rows, dtype=torch.int32) if nl else lrow[:0]
         used = 5 * T + 4 * S
         self.meta_i32[:used].copy_(h[:used], non_blocking=True)
         if tree:

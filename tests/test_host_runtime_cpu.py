@@ -89,3 +89,37 @@ def test_stop_scanner_matches_python(monkeypatch):
             assert nat.push(text[i:i + n]) == ref.push(text[i:i + n]), (case, stops, text, i)
             i += n
         assert nat.hit == ref.hit and nat.flush() == ref.flush()
+
+
+def test_step_metadata_block_matches_python(monkeypatch):
+    """`Executor._upload` through the C++ fill and through the Python loop: the staging block, the tree block and the
+    logit rows are identical, for plain segments and for verify trees."""
+    import torch
+    from ferrite_b200.config import EngineConfig, tiny_hybrid
+    from ferrite_b200.engine.engine import Engine
+    from ferrite_b200.engine.executor import Segment, StepBatch
+    eng = Engine(tiny_hybrid(), None, EngineConfig(n_slots=3, max_ctx=256), device="cpu")
+    ex = eng.ex
+    plain = StepBatch([Segment(0, 5, [11, 12, 13], "all"), Segment(2, 0, [7], "last"), Segment(1, 40, [1, 2], "none")], commit=True)
+    tree = StepBatch([Segment(0, 9, [3, 4, 5, 6, 7], "all", parents=[-1, 0, 0, 1, 2]), Segment(1, 2, [8, 9], "all")], commit=False)
+    for batch in (plain, tree):
+        outs = []
+        for native in (True, False):
+            if native:
+                monkeypatch.delenv("FERRITE_NO_NATIVE_HOST", raising=False)
+            else:
+                monkeypatch.setenv("FERRITE_NO_NATIVE_HOST", "1")
+            for buf in ex._ring + ex._tring:
+                buf.zero_()
+            ex._ring_i = 0
+            rows = ex._upload(batch)
+            T, S = batch.n_rows, len(batch.segments)
+            outs.append((rows, ex._ring[0][:5 * T + 4 * S].clone(), ex._tring[0].clone() if batch.tree else None))
+        (r1, h1, t1), (r2, h2, t2) = outs
+        nl = len(r1)
+        T = batch.n_rows
+        assert r1 == r2 and torch.equal(h1[:4 * T + nl], h2[:4 * T + nl]) and torch.equal(h1[5 * T:], h2[5 * T:])
+        if batch.tree:
+            R = ex._R
+            for blk in range(6):
+                assert torch.equal(t1[blk * R:blk * R + (2 * T if blk == 0 else T)], t2[blk * R:blk * R + (2 * T if blk == 0 else T)]), blk
