@@ -5,6 +5,9 @@
     python -m ferrite_b200.tools.workloads mixed  --base-url URL --decoders 2 --prompts 3 --prompt-tokens 4000
     python -m ferrite_b200.tools.workloads agents --base-url URL --agents 4 --turns 5
 
+    python -m ferrite_b200.tools.workloads modes  --base-url URL --save ref.json | --compare ref.json
+    python -m ferrite_b200.tools.workloads turns  --base-url URL --turns 8
+
 Each prints one JSON line.
   edit    a Python standard-library module in the prompt, an instruction that keeps most of it, the whole updated module
           back (greedy): the workload context-copy speculation is built for. Streams start together; tok/s per stream.
@@ -15,8 +18,14 @@ Each prints one JSON line.
           max) show what a prompt costs the streams; time to first token of the prompts shows what the streams cost them.
   agents  sessions of several turns with a tool call per turn, each turn re-sending the conversation so far: turn latency
           and the share of prompt tokens the server took from its cache.
+  modes   the mode gate: a fixed set of greedy requests (with and without a system message, short and long, a follow-up
+          turn, a file edit) sent one by one to a server; a hash per case is saved (`--save`) or compared with the hashes
+          another configuration of the server produced (`--compare`: prompt cache on / off, drafter kinds, weight
+          formats that must not change greedy text); exit code 1 and the first differing characters on a mismatch.
+  turns   one conversation behind a long system prompt grows turn by turn (each turn appends the reply and a tool
+          result): per turn the prompt tokens, the tokens served from the cache, time to first token and a reply hash.
 The clients read GET /health first and never send more requests at once than `max_batch_size` (points beyond are reported
-as skipped). Counterparts of the reference's `tools/bench/edit.py`, `lanes.py`, `mixed.py`, `agents.py`.
+as skipped). Counterparts of the reference's `tools/bench/edit.py`, `lanes.py`, `mixed.py`, `agents.py`, `modes.py`, `agentturns.py`.
 """
 from __future__ import annotations
 
@@ -279,6 +288,96 @@ def cmd_agents(a) -> int:
     return 0 if len(good) == len(recs) and recs else 1
 
 
+# ---- modes ------------------------------------------------------------------------------------------------------------
+def mode_cases(seed: int, long_tokens: int = 3000, source_chars: int = 8000) -> List[Dict[str, Any]]:
+    review = module_source("bisect.py")[:source_chars]
+    sysbig = "You are the coding agent of an inference-engine repository. Project notes follow.\n\n" + filler(long_tokens, seed)
+    edit = module_source("shlex.py")[:source_chars]
+    first = [{"role": "system", "content": sysbig}, {"role": "user", "content": "Which note mentions the cache? One sentence."}]
+    return [
+        {"name": "sys-short-review", "max_tokens": 200, "messages": [
+            {"role": "system", "content": "You are a careful code reviewer."},
+            {"role": "user", "content": "Review this Python file. Name the three most important issues.\n\n" + review}]},
+        {"name": "nosys-review", "max_tokens": 160, "messages": [
+            {"role": "user", "content": "Review this Python file. Name the three most important issues.\n\n" + review}]},
+        {"name": "sys-short-chat", "max_tokens": 120, "messages": [
+            {"role": "system", "content": "You answer in one short paragraph."},
+            {"role": "user", "content": "Why does a recurrent layer make prompt caching harder?"}]},
+        {"name": "code", "max_tokens": 200, "messages": [
+            {"role": "user", "content": "Write a Python function that checks whether a string is a palindrome, with three tests."}]},
+        {"name": "sys-long-turn1", "max_tokens": 120, "messages": first},
+        {"name": "sys-long-turn2", "max_tokens": 120, "follow": "sys-long-turn1", "messages": first, "then": "And which one mentions a queue?"},
+        {"name": "edit", "max_tokens": 400, "messages": [
+            {"role": "user", "content": "Rename every local variable named `s` to `text` in this module and return the whole "
+                                        "module.\n\n" + edit}]},
+    ]
+
+
+def cmd_modes(a) -> int:
+    import hashlib
+    c = Client(a.base_url)
+    model = model_of(c, a.model)
+    replies: Dict[str, str] = {}
+    for case in mode_cases(a.seed, a.long_tokens, a.max_source_chars):
+        msgs = list(case["messages"])
+        if case.get("follow"):
+            msgs = msgs + [{"role": "assistant", "content": replies[case["follow"]]}, {"role": "user", "content": case["then"]}]
+        r = Run()
+        stream_chat(a.base_url, {"model": model, "messages": msgs, "max_tokens": min(case["max_tokens"], a.max_tokens),
+                                 "temperature": 0, "stream": True}, r)
+        if r.error:
+            print(json.dumps({"workload": "modes", "case": case["name"], "error": r.error}))
+            return 2
+        replies[case["name"]] = r.text
+    hashes = {k: hashlib.sha256(v.encode("utf-8")).hexdigest()[:16] for k, v in replies.items()}
+    out: Dict[str, Any] = {"workload": "modes", "cases": len(hashes), "hashes": hashes}
+    rc = 0
+    if a.save:
+        with open(a.save, "w", encoding="utf-8") as f:
+            json.dump({"hashes": hashes, "texts": replies}, f)
+        out["saved"] = a.save
+    if a.compare:
+        with open(a.compare, "r", encoding="utf-8") as f:
+            ref = json.load(f)
+        diff = {}
+        for k, h in hashes.items():
+            if ref["hashes"].get(k) != h:
+                want, got = ref.get("texts", {}).get(k, ""), replies[k]
+                i = next((j for j, (x, y) in enumerate(zip(want, got)) if x != y), min(len(want), len(got)))
+                diff[k] = {"at": i, "want": want[i:i + 40], "got": got[i:i + 40]}
+        out["different"] = diff
+        rc = 1 if diff else 0
+    print(json.dumps(out))
+    return rc
+
+
+# ---- turns ------------------------------------------------------------------------------------------------------------
+def cmd_turns(a) -> int:
+    import hashlib
+    c = Client(a.base_url)
+    model = model_of(c, a.model)
+    msgs: List[Dict[str, Any]] = [{"role": "system", "content": "You are a coding agent. Notes:\n" + filler(a.prefix_tokens, a.seed)},
+                                  {"role": "user", "content": "Start by listing what you would inspect first."}]
+    rows = []
+    for t in range(a.turns):
+        r = Run()
+        t0 = time.time()
+        stream_chat(a.base_url, {"model": model, "messages": msgs, "max_tokens": a.max_tokens, "temperature": 0, "stream": True}, r)
+        if r.error:
+            print(json.dumps({"workload": "turns", "turn": t, "error": r.error}))
+            return 2
+        rows.append({"turn": t, "prompt_tokens": int(r.usage.get("prompt_tokens") or 0), "cached_tokens": r.cached,
+                     "ttft_s": round(r.times[0], 4) if r.times else None, "total_s": round(time.time() - t0, 4),
+                     "hash": hashlib.sha256(r.text.encode("utf-8")).hexdigest()[:12]})
+        msgs += [{"role": "assistant", "content": r.text},
+                 {"role": "user", "content": "Tool result:\n" + filler(a.tool_tokens, a.seed + 100 + t) + "\nContinue."}]
+    sent = sum(x["prompt_tokens"] for x in rows)
+    cached = sum(x["cached_tokens"] for x in rows)
+    print(json.dumps({"workload": "turns", "turns": rows, "prompt_tokens_sent": sent, "served_from_cache": cached,
+                      "cache_share": round(cached / sent, 3) if sent else 0.0}))
+    return 0
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
     sub = ap.add_subparsers(dest="what", required=True)
@@ -307,8 +406,18 @@ def main(argv=None) -> int:
     p.add_argument("--agents", type=int, default=4)
     p.add_argument("--turns", type=int, default=5)
     p.add_argument("--prefix-tokens", type=int, default=1500)
+    p = common(sub.add_parser("modes"))
+    p.add_argument("--save", default="")
+    p.add_argument("--compare", default="")
+    p.add_argument("--long-tokens", type=int, default=3000, help="words of the long system prompt")
+    p.add_argument("--max-source-chars", type=int, default=8000, help="cut of the source files in the prompts")
+    p = common(sub.add_parser("turns"))
+    p.add_argument("--turns", type=int, default=8)
+    p.add_argument("--prefix-tokens", type=int, default=5000)
+    p.add_argument("--tool-tokens", type=int, default=1000)
     a = ap.parse_args(argv)
-    return {"edit": cmd_edit, "lanes": cmd_lanes, "mixed": cmd_mixed, "agents": cmd_agents}[a.what](a)
+    return {"edit": cmd_edit, "lanes": cmd_lanes, "mixed": cmd_mixed, "agents": cmd_agents, "modes": cmd_modes,
+            "turns": cmd_turns}[a.what](a)
 
 
 if __name__ == "__main__":

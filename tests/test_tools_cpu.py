@@ -83,6 +83,32 @@ def test_workload_clients_on_the_mock_server(capsys, tmp_path):
     assert lines["agents"]["cached_share_after_first_turn"] > 0.5
 
 
+def test_mode_gate_and_turns_on_the_mock_server(capsys, tmp_path):
+    """modes: hashes saved by one run compare equal on the next and a changed reference is reported with the first
+    differing characters; turns: the growing conversation is served from the cache after its first turn."""
+    from ferrite_b200.tools.workloads import main
+    url, loop = _serve()
+    ref = str(tmp_path / "ref.json")
+    try:
+        assert main(["modes", "--base-url", url, "--save", ref, "--max-tokens", "24", "--long-tokens", "150", "--max-source-chars", "500"]) == 0
+        first = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+        assert first["cases"] == 7 and first["saved"] == ref
+        assert main(["modes", "--base-url", url, "--compare", ref, "--max-tokens", "24", "--long-tokens", "150", "--max-source-chars", "500"]) == 0
+        assert json.loads(capsys.readouterr().out.strip().splitlines()[-1])["different"] == {}
+        data = json.load(open(ref))
+        data["hashes"]["code"] = "0" * 16
+        data["texts"]["code"] = "X" + data["texts"]["code"][1:]
+        json.dump(data, open(ref, "w"))
+        assert main(["modes", "--base-url", url, "--compare", ref, "--max-tokens", "24", "--long-tokens", "150", "--max-source-chars", "500"]) == 1
+        diff = json.loads(capsys.readouterr().out.strip().splitlines()[-1])["different"]
+        assert list(diff) == ["code"] and diff["code"]["at"] == 0
+        assert main(["turns", "--base-url", url, "--turns", "3", "--prefix-tokens", "200", "--tool-tokens", "50", "--max-tokens", "16"]) == 0
+        t = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+        assert len(t["turns"]) == 3 and t["turns"][2]["cached_tokens"] > 0 and t["turns"][2]["prompt_tokens"] > t["turns"][0]["prompt_tokens"]
+    finally:
+        loop.call_soon_threadsafe(loop.stop)
+
+
 def test_release_gate_on_the_mock_server(capsys):
     from ferrite_b200.tools.release_gate import main
     url, loop = _serve()
