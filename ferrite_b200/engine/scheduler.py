@@ -42,7 +42,7 @@ class SchedOptions:
     batch_rows: int = 2048             # prompt rows per step
     finite_check: bool = True
     step_timeout_s: float = 120.0
-    prof: int = 0                      # 1: one line per step on stderr
+    prof: int = 0                      # 1: one line per step on stderr; 2: verify steps add slots, rows fed and accepted paths
     share_min: int = PREFIX_MIN        # shortest common prefix worth waiting for / forking from a running request
     mixed: bool = True                 # decode rows and a prompt chunk share one forward when both are waiting
     tree_rows: int = 0                 # draft rows of a verify tree per request (0 = chains only; needs Drafter.draft_tree)
@@ -492,7 +492,13 @@ class Scheduler:
                 self.t_dec += dt
         if self.opts.prof:
             import sys
-            print(f"step {self.step_no}: dec {n_dec} rows, prompt {n_pre} rows, {1e3 * (time.time() - t0):.2f} ms",
+            tail = ""
+            lv = getattr(self, "_last_verify", None)
+            if self.opts.prof >= 2 and lv is not None:
+                import json
+                tail = f" | slots {json.dumps(lv['slots'])} rows {json.dumps(lv['rows'])} paths {json.dumps(lv['paths'])}"
+                self._last_verify = None
+            print(f"step {self.step_no}: dec {n_dec} rows, prompt {n_pre} rows, {1e3 * (time.time() - t0):.2f} ms{tail}",
                   file=sys.stderr)
 
     def _prefill_cut(self, a: Active, budget: int):
@@ -719,6 +725,10 @@ class Scheduler:
             self.eng.commit_tree(paths)
         elif spec:
             self.eng.commit_verified(keep)
+        if self.opts.prof >= 2 and spec:
+            # per request of this verify step: slot, rows fed (1 + drafts) and the accepted path's row indices; what
+            # `tools/sched_budget.py` replays under smaller draft budgets
+            self._last_verify = {"slots": [a.slot for a in decoders], "rows": [1 + len(d) for d in drafts], "paths": paths}
         return len(rows)
 
     # ---- bookkeeping --------------------------------------------------------------------------------

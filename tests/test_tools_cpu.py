@@ -165,6 +165,38 @@ def test_launcher_presets_and_gpu_locks(tmp_path, capsys, monkeypatch):
     assert launch.port_of(["--x", "--port", "81"]) == 81 and launch.port_of(["--port=82"]) == 82 and launch.port_of([]) == 0
 
 
+def test_sched_budget_replays_a_verify_trace():
+    """A speculative run with FE_SCHED_PROF=2-style tracing: the tool reads the verify steps and reports what smaller
+    draft budgets would have accepted; the summary tool still reads the longer lines."""
+    import contextlib
+    import io
+
+    import torch
+
+    from ferrite_b200.config import EngineConfig, tiny_hybrid
+    from ferrite_b200.engine.engine import Engine
+    from ferrite_b200.engine.sampler import Sampling
+    from ferrite_b200.engine.scheduler import SchedOptions, Scheduler, generate
+    from ferrite_b200.tools import sched_budget as SB
+    from ferrite_b200.tools.sched_steps import summarise
+    cfg = tiny_hybrid()
+    eng = Engine(cfg, None, EngineConfig(n_slots=2, max_ctx=256), device="cpu")
+    base = torch.randint(1, cfg.vocab, (30,), generator=torch.Generator().manual_seed(0)).tolist()
+    p = base + base + base[:10]                                   # the copier has something to propose
+    err = io.StringIO()
+    with contextlib.redirect_stderr(err):
+        generate(Scheduler(eng, SchedOptions(spec=8, prof=2, arrival_ms=0)), [p, p[5:]], Sampling(max_tokens=24))
+    lines = err.getvalue().splitlines()
+    steps = SB.parse(lines)
+    assert steps and all(len(s[2]) == len(s[3]) == len(s[4]) for s in steps)
+    rep = SB.budgets(steps, [(2, 8.9), (9, 9.4)], 1.5)
+    for slot in rep.values():
+        accs = [c["accepted"] for c in slot["budgets"].values()]
+        assert accs == sorted(accs) and accs[-1] <= slot["mean_accepted"] + 1e-9 and "tok_s" in slot["budgets"][1]
+    assert summarise(lines)["decode"]["steps"] >= len(steps)
+    assert SB.interp([(2, 1.0), (4, 3.0)], 3) == 2.0 and SB.interp([(2, 1.0), (4, 3.0)], 9) == 3.0
+
+
 def test_sweep_runs_points(capsys):
     from ferrite_b200.tools.sweep import main
     url, loop = _serve()
