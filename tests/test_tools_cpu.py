@@ -197,6 +197,33 @@ def test_sched_budget_replays_a_verify_trace():
     assert SB.interp([(2, 1.0), (4, 3.0)], 3) == 2.0 and SB.interp([(2, 1.0), (4, 3.0)], 9) == 3.0
 
 
+def test_control_tool_and_environment_check(tmp_path, monkeypatch, capsys):
+    """ctl: start a mock server in the background (own session, log + pid files), refuse a second start, report status,
+    stop it. check_env: the report names the toolchain and asks for GPUs only when told to."""
+    from ferrite_b200.tools import check_env, ctl
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    monkeypatch.setenv("FERRITE_LOG_DIR", str(tmp_path))
+    monkeypatch.setenv("FERRITE_START_TIMEOUT", "120")
+    assert ctl.main(["start", "--preset", "mock", "--port", str(port)]) == 0
+    try:
+        assert "serving on" in capsys.readouterr().out
+        assert ctl.main(["start", "--preset", "mock", "--port", str(port)]) == 1         # one server a port
+        assert ctl.main(["status", "--port", str(port)]) == 0
+        st = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+        assert st["running"] and st["health"]["engine"] == "mock"
+        assert (tmp_path / f"server-{port}.log").exists() and (tmp_path / f"server-{port}.pid").exists()
+    finally:
+        assert ctl.main(["stop", "--port", str(port)]) == 0
+    assert ctl.main(["status", "--port", str(port)]) == 1
+    capsys.readouterr()
+    rep = check_env.check(build=True)
+    assert rep["torch"] and rep["nvcc_sm_100a"] is True and rep["extension_loads"] and not rep["errors"]
+    assert check_env.check(gpus=2)["errors"]                      # no GPU on the test machine: asking for two is an error
+
+
 def test_sweep_runs_points(capsys):
     from ferrite_b200.tools.sweep import main
     url, loop = _serve()
