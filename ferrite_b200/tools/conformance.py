@@ -1,6 +1,13 @@
 """API conformance suite: black-box checks of an OpenAI-compatible ferrite_b200 server.
 
     python -m ferrite_b200.tools.conformance --base-url http://127.0.0.1:8000 [--mock] [--tier quick|heavy|all] [--only NAME]
+                                              [--profile hybrid-27b | FILE.json] [--replay DIR]
+
+`--profile` names a model profile (`tools/profiles/*.json`, or a file): the served model's name, its context length, the
+least `max_batch_size`, the header that reports the effective sampling, and checks to skip for that model; the `profile`
+check compares them with what the server says. `--replay DIR` re-sends the requests a server captured with
+`FE_DUMP_REQUESTS=DIR` (`<id>.request.json`): every one must be answered with a well-formed reply, and greedy ones
+(temperature 0) twice with the same text.
 
 Every check prints PASS / FAIL; the exit code is 1 on any failure. Tier `quick` (a minute): health and model list, plain
 chat (full and streamed, the two must agree), usage accounting, `max_tokens` -> `finish_reason: "length"`, stop strings,
@@ -60,8 +67,10 @@ def validate(v: Any, sc: dict, path: str = "$") -> None:
 
 
 class Suite:
-    def __init__(self, client: Client, model: str, mock: bool, tier: str = "quick", only: str = ""):
+    def __init__(self, client: Client, model: str, mock: bool, tier: str = "quick", only: str = "", profile=None,
+                 replay: str = ""):
         self.c, self.model, self.mock, self.tier, self.only = client, model, mock, tier, only
+        self.profile, self.replay = profile or {}, replay
         self.results: List[tuple] = []
 
     def check(self, name: str, fn: Callable[[], None]) -> None:
@@ -87,6 +96,44 @@ class Suite:
     def t_health(self):
         status, body = self.c.get("/health")
         assert status == 200 and body.get("status") == "ok", (status, body)
+
+    def t_profile(self):
+        """What the server reports against the model profile."""
+        p = self.profile
+        _, h = self.c.get("/health")
+        if p.get("context"):
+            assert int(h.get("max_model_len", 0)) <= int(p["context"]), (h.get("max_model_len"), p["context"])
+        if p.get("max_batch_size_min"):
+            assert int(h.get("max_batch_size", 0)) >= int(p["max_batch_size_min"]), h
+        _, m = self.c.get("/v1/models")
+        if p.get("model") and not self.model:
+            assert any(d.get("id") == p["model"] for d in m.get("data", [])), (p["model"], m)
+        if p.get("effective_sampling_header"):
+            _, _, headers = self.c.post("/v1/chat/completions", {"model": self.model, "max_tokens": 4,
+                                                                  "messages": [{"role": "user", "content": "hi"}]})
+            assert p["effective_sampling_header"] in headers, sorted(headers)
+
+    def t_replay(self):
+        """Captured requests, sent again: a well-formed reply each, and the same text twice when greedy."""
+        import glob
+        import os
+        files = sorted(glob.glob(os.path.join(self.replay, "*.request.json")))
+        assert files, f"no *.request.json under {self.replay}"
+        for f in files:
+            with open(f, "r", encoding="utf-8") as fh:
+                cap = json.load(fh)
+            body = dict(cap["body"], stream=False)
+            path = cap.get("meta", {}).get("path") or "/v1/chat/completions"
+            texts = []
+            for _ in range(2 if float(body.get("temperature", 1) or 0) == 0 else 1):
+                status, rep, _ = self.c.post(path, body)
+                assert status == 200 and rep.get("choices"), (f, status, str(rep)[:200])
+                ch = rep["choices"][0]
+                assert ch.get("finish_reason") in ("stop", "length", "tool_calls"), (f, ch.get("finish_reason"))
+                msg = ch.get("message") or {}
+                texts.append(json.dumps([msg.get("content"), msg.get("tool_calls"), ch.get("text")], sort_keys=True))
+                assert rep.get("usage", {}).get("prompt_tokens", 0) > 0, (f, rep.get("usage"))
+            assert len(set(texts)) == 1, f"{f}: two greedy replays differ"
 
     def t_models(self):
         status, body = self.c.get("/v1/models")
@@ -317,7 +364,14 @@ class Suite:
             todo += quick + (quick_mock if self.mock else [])
         if self.tier in ("heavy", "all"):
             todo += ([("models", self.t_models)] if self.tier == "heavy" else []) + heavy + (heavy_mock if self.mock else [])
+        if self.profile:
+            todo.append(("profile", self.t_profile))
+        if self.replay:
+            todo.append(("replay", self.t_replay))
+        skip = set(self.profile.get("skip", []))
         for name, fn in todo:
+            if name in skip:
+                continue
             if not self.only or self.only == name or name in ("models",):
                 self.check(name, fn)
         bad = 0
@@ -335,8 +389,16 @@ def main(argv=None) -> int:
     ap.add_argument("--mock", action="store_true", help="the server runs the scripted mock engine")
     ap.add_argument("--tier", choices=["quick", "heavy", "all"], default="quick")
     ap.add_argument("--only", default="", help="run one check by name")
+    ap.add_argument("--profile", default="", help="model profile: a name under tools/profiles/ or a JSON file")
+    ap.add_argument("--replay", default="", help="directory of captured requests (FE_DUMP_REQUESTS) to send again")
     a = ap.parse_args(argv)
-    return Suite(Client(a.base_url), a.model, a.mock, a.tier, a.only).run()
+    profile = None
+    if a.profile:
+        import os
+        path = a.profile if os.path.exists(a.profile) else os.path.join(os.path.dirname(__file__), "profiles", a.profile + ".json")
+        with open(path, "r", encoding="utf-8") as f:
+            profile = json.load(f)
+    return Suite(Client(a.base_url), a.model, a.mock, a.tier, a.only, profile, a.replay).run()
 
 
 if __name__ == "__main__":

@@ -14,14 +14,14 @@ from ferrite_b200.server.template import ChatTemplate
 from ferrite_b200.server.tokenizer import load_tokenizer
 
 
-def _serve():
+def _serve(capture_dir=None):
     s = socket.socket()
     s.bind(("127.0.0.1", 0))
     port = s.getsockname()[1]
     s.close()
     tok = load_tokenizer(None, 4096)
     app = make_app(lambda: AppState(MockEngine(tok, "mock-model", max_batch=8, max_len=4096), tok, ChatTemplate.from_dir(None),
-                                    GenDefaults.from_dir(None, "default"), "mock-model", 8))
+                                    GenDefaults.from_dir(None, "default"), "mock-model", 8, capture_dir=capture_dir))
     loop = asyncio.new_event_loop()
     started = threading.Event()
 
@@ -47,6 +47,34 @@ def test_conformance_suite_passes_on_the_mock_server(capsys):
     out = capsys.readouterr().out
     assert rc == 0, out
     assert "FAIL" not in out
+
+
+def test_conformance_profile_and_replay_of_captured_requests(capsys, tmp_path):
+    """A server that captures its requests; the suite then checks the model profile and sends the captured requests
+    again (greedy ones twice, same text)."""
+    from ferrite_b200.tools.conformance import main
+    from ferrite_b200.tools.httpc import Client
+    cap = tmp_path / "cap"
+    url, loop = _serve(capture_dir=str(cap))
+    try:
+        c = Client(url)
+        for body in ({"messages": [{"role": "user", "content": "say hello twice"}], "max_tokens": 12, "temperature": 0},
+                     {"messages": [{"role": "user", "content": "[[say:alpha beta]]"}], "max_tokens": 8}):
+            assert c.post("/v1/chat/completions", dict(body, model="mock-model"))[0] == 200
+        assert len(list(cap.glob("*.request.json"))) == 2
+        rc = main(["--base-url", url, "--mock", "--only", "replay", "--profile", "mock", "--replay", str(cap)])
+        out = capsys.readouterr().out
+        assert rc == 0 and "PASS replay" in out and "FAIL" not in out, out
+        rc = main(["--base-url", url, "--mock", "--only", "profile", "--profile", "mock"])
+        out = capsys.readouterr().out
+        assert rc == 0 and "PASS profile" in out, out
+        bad = tmp_path / "p.json"
+        bad.write_text(json.dumps({"model": "other-model", "context": 16, "skip": ["health"]}))
+        rc = main(["--base-url", url, "--only", "profile", "--profile", str(bad)])
+        out = capsys.readouterr().out
+        assert rc == 1 and "FAIL profile" in out, out
+    finally:
+        loop.call_soon_threadsafe(loop.stop)
 
 
 def test_quickbench_reports_streams(capsys):
