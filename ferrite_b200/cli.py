@@ -1,7 +1,8 @@
 """Command line of the engine (no server): `python -m ferrite_b200.cli <command> ...`
 
     generate   --preset 27b [--model DIR] --prompt "text" | --ids 1,2,3  [--max-tokens 64]    greedy text and tok/s
-    logits     --preset 27b [--model DIR] --ids-file ids.txt --out logits.pt [--chunk 256]      per-position logits dump
+    logits     --preset 27b [--model DIR] --ids-file ids.txt --out logits.pt [--chunk 256] [--schedule plain|stagger|split|mix]
+    logits-test --preset tiny [--tokens 200] [--chunk 64]     the same logits whatever the step schedule
     sched-test --preset tiny [--requests 6]      every request through the scheduler together == the same request alone
     park-test  --preset tiny                     a parked conversation resumed from the prompt cache == recomputed from scratch
 
@@ -88,21 +89,69 @@ def cmd_generate(a) -> int:
     return 0
 
 
+def scheduled_logits(eng, ids: List[int], chunk: int, schedule: str) -> torch.Tensor:
+    """Per-position logits of `ids` on slot 0 under a step schedule that must not change them:
+    plain    chunks of `chunk` rows
+    stagger  chunks of varying sizes (chunk, 1, chunk / 2 + 1, 3, ...), so cuts land off the 32-row grid
+    split    the same chunks, but a second request's chunk (other tokens, slot 1) rides in every step before them
+    mix      every prompt chunk shares its step with a decode row of a request running on slot 1
+    Reference: `ferrite logits` under `FE_LOG_SCHED=stagger|split|mix` (`crates/fe-cli/src/main.rs`)."""
+    from .engine.executor import Segment
+    sizes: List[int] = []
+    left, k = len(ids), 0
+    pattern = [chunk] if schedule in ("plain", "split", "mix") else [chunk, 1, chunk // 2 + 1, 3]
+    while left > 0:
+        n = max(1, min(left, pattern[k % len(pattern)]))
+        sizes.append(n)
+        left -= n
+        k += 1
+    other = [(t * 7 + 3) % eng.full_cfg.vocab for t in ids]
+    if schedule == "mix":
+        eng.reset_slot(1)
+        eng.prefill(1, other[:5])
+    rows, i = [], 0
+    for step, n in enumerate(sizes):
+        segs = [Segment(0, i, ids[i:i + n], "all")]
+        if schedule == "split":
+            segs = [Segment(1, i, other[i:i + n], "none")] + segs
+        elif schedule == "mix":
+            segs = [Segment(1, eng.slot_len[1], [other[(5 + step) % len(other)]], "last")] + segs
+        lg, _, lrows = eng.forward(segs, greedy=False)
+        first = next(j for j, r in enumerate(lrows) if r >= sum(len(s.tokens) for s in segs[:-1]))
+        rows.append(lg[first:first + n].float().cpu().clone())
+        i += n
+    return torch.cat(rows)
+
+
 def cmd_logits(a) -> int:
-    cfg, eng, tok = build_engine(a, max_ctx=a.max_ctx)
+    cfg, eng, tok = build_engine(a, n_slots=2, max_ctx=a.max_ctx)
     with open(a.ids_file, "r", encoding="utf-8") as f:
         ids = [int(x) for x in f.readline().replace(" ", "").split(",") if x]
-    from .engine.executor import Segment
-    rows = []
-    for i in range(0, len(ids), a.chunk):
-        lg, _, _ = eng.forward([Segment(0, i, ids[i:i + a.chunk], "all")], greedy=False)
-        rows.append(lg.float().cpu())
-    logits = torch.cat(rows)
+    logits = scheduled_logits(eng, ids, a.chunk, a.schedule)
     torch.save({"ids": ids, "logits": logits, "model": cfg.name, "weights": a.weights}, a.out)
     eng.check()
     print(json.dumps({"positions": len(ids), "vocab": int(logits.shape[1]), "out": a.out,
                       "finite": bool(torch.isfinite(logits).all())}))
     return 0
+
+
+def cmd_logits_test(a) -> int:
+    """The logits of a seeded prompt under every step schedule against the plain one: chunk cuts, a neighbour in the step
+    and a decode row sharing the step must leave every row's logits where they were (to the kernels' batch invariance:
+    bit for bit on the fp32 CPU engine, `--tol` elsewhere)."""
+    cfg, eng, _ = build_engine(a, n_slots=2, max_ctx=a.max_ctx)
+    g = torch.Generator().manual_seed(a.seed + 3)
+    ids = torch.randint(1, cfg.vocab, (a.tokens,), generator=g).tolist()
+    ref = scheduled_logits(eng, ids, a.chunk, "plain")
+    out = {}
+    for sched in ("stagger", "split", "mix"):
+        eng.reset_slot(0)
+        got = scheduled_logits(eng, ids, a.chunk, sched)
+        out[sched] = float((got - ref).abs().max())
+    eng.check()
+    ok = all(v <= a.tol for v in out.values())
+    print(json.dumps({"tokens": len(ids), "chunk": a.chunk, "max_abs_diff": out, "tol": a.tol, "ok": ok}))
+    return 0 if ok else 1
 
 
 def _prompts(cfg, n: int, seed: int, lo: int = 9, hi: int = 90) -> List[List[int]]:
@@ -188,7 +237,13 @@ def main(argv: Optional[List[str]] = None) -> int:
     p.add_argument("--ids-file", required=True, help="one line of comma-separated token ids")
     p.add_argument("--out", required=True)
     p.add_argument("--chunk", type=int, default=256)
+    p.add_argument("--schedule", default="plain", choices=["plain", "stagger", "split", "mix"])
     p.set_defaults(fn=cmd_logits)
+    p = common(sub.add_parser("logits-test"), 0)
+    p.add_argument("--tokens", type=int, default=200)
+    p.add_argument("--chunk", type=int, default=64)
+    p.add_argument("--tol", type=float, default=1e-4)
+    p.set_defaults(fn=cmd_logits_test)
     p = common(sub.add_parser("sched-test"), 12)
     p.add_argument("--requests", type=int, default=6)
     p.add_argument("--slots", type=int, default=3)

@@ -212,11 +212,22 @@ class Executor:
         self.reclaim = None                          # callable() -> bool: free some pages (set by the scheduler)
         self._last_meta = None
         self.profile = None
+        # FE_LOG_DUMP=1: one line per layer and step on stderr with a hash of the residual stream after the layer (steps
+        # run eagerly and unfused then): two builds, or two schedules of the same prompt, diverge at the first line that
+        # differs (reference `FE_LOG_DUMP` layer taps, `crates/fe-model/src/model.rs`)
+        self.dump_layers = os.environ.get("FE_LOG_DUMP", "0") not in ("", "0")
         self.moe_merged: Dict[int, torch.Tensor] = {}
         self._merge_shared_experts()
         self._step_max_kvlen = None
         self._step_segments = None            # host view of an eager step's segments: (slot, pos0, rows)
         self.ep = None                        # ExpertParallel, set by the engine for MoE models under TP
+
+    def _dump_layer(self, i: int, x, sp: bool, T: int) -> None:
+        import hashlib
+        import sys
+        xf = (self.tp.gather_rows(x, T) if sp else x).float().cpu().contiguous()
+        print(f"layer {i}: rows {xf.shape[0]} sha1 {hashlib.sha1(xf.numpy().tobytes()).hexdigest()[:12]} "
+              f"mean {float(xf.mean()):.6f} absmax {float(xf.abs().max()):.4f}", file=sys.stderr)
 
     def _merge_shared_experts(self) -> None:
         """One GPU, one shared expert of the routed experts' width: append it to the expert stacks (entry n_experts) and
@@ -534,7 +545,7 @@ class Executor:
         fuse = self.ecfg.fused_layers
         if fuse is None:
             fuse = self.tp is not None and self.tp.world > 1
-        fuse = (fuse and ops.name == "cuda" and commit and tv is None and not sp and max_seg_rows == 1 and nseg == T and T <= 4
+        fuse = (fuse and not self.dump_layers and ops.name == "cuda" and commit and tv is None and not sp and max_seg_rows == 1 and nseg == T and T <= 4
                 and c.n_experts == 0 and c.kv_lora == 0 and isinstance(w["l0.out_proj"], torch.Tensor)
                 and w["l0.out_proj"].dtype == torch.bfloat16 and (self.tp is None or self.tp.world == 1 or self.tp.fused))
         comm = self.tp.comm if (fuse and self.tp is not None and self.tp.world > 1) else None
@@ -579,6 +590,8 @@ class Executor:
                         x = row(col(x, w[p + "gate_up"], w[p + "post_norm"], swiglu=True), w[p + "down"], x)
                     if i in c.tap_layers:
                         self.taps.append(x)
+                    if self.dump_layers:
+                        self._dump_layer(i, x, False, T)
                     continue
                 elif hasattr(ops, "gdn_step") and max_seg_rows <= GDN_STEP_MAX_ROWS and c.lin_dk == c.lin_dv and c.lin_dk in (64, 128):
                     if not commit:
@@ -594,6 +607,8 @@ class Executor:
                         x = row(act, w[p + "down"], x)
                     if i in c.tap_layers:
                         self.taps.append(self.tp.gather_rows(x, T) if sp else x)
+                    if self.dump_layers:
+                        self._dump_layer(i, x, sp, T)
                     continue
                 qkv = ops.gdn_conv(proj, w[p + "conv_w"], self.conv_state[i], mv["sslot"], mv["srow0"], mv["snrows"],
                                    c.conv_dim, **({"max_rows": max_seg_rows} if ops.name == "cuda" else {}))
@@ -668,6 +683,8 @@ class Executor:
                 x = row(act, w[p + "down"], x)
             if i in c.tap_layers:
                 self.taps.append(self.tp.gather_rows(x, T) if sp else x)
+            if self.dump_layers:
+                self._dump_layer(i, x, sp, T)
         flush()
         return self.tp.gather_rows(x, T) if sp else x
 
@@ -839,7 +856,7 @@ class Executor:
         max_kvlen = max(s.pos0 + len(s.tokens) for s in batch.segments)
         nsplit = self.attn_splits(max_kvlen) if max_seg_rows <= FLASH_MIN_ROWS else 1
         use_graph = (self.ecfg.use_graphs and self.device.type == "cuda" and T <= self.ecfg.decode_rows_max
-                     and self.profile is None and x_add is None)
+                     and self.profile is None and x_add is None and not self.dump_layers)
         tree = batch.tree
         if tree:
             assert not batch.commit and max_seg_rows <= TREE_MAX_ROWS and "mla" not in self.kinds, \

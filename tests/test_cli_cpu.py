@@ -37,3 +37,22 @@ def test_sched_test_and_park_test_pass(capsys):
     for argv in (["sched-test"], ["sched-test", "--spec", "4", "--slots", "2"], ["park-test"]):
         rc, out = _run(capsys, *argv)
         assert rc == 0 and out["ok"], out
+
+
+def test_logits_are_schedule_invariant_and_layer_dump(capsys, tmp_path, monkeypatch):
+    rc, out = _run(capsys, "logits-test", "--tokens", "90", "--chunk", "32")
+    assert rc == 0 and out["ok"] and set(out["max_abs_diff"]) == {"stagger", "split", "mix"}
+    ids = tmp_path / "ids.txt"
+    ids.write_text(",".join(str(3 + 5 * i) for i in range(40)))
+    a, b = tmp_path / "a.pt", tmp_path / "b.pt"
+    assert _run(capsys, "logits", "--ids-file", str(ids), "--out", str(a), "--chunk", "16")[0] == 0
+    assert _run(capsys, "logits", "--ids-file", str(ids), "--out", str(b), "--chunk", "16", "--schedule", "mix")[0] == 0
+    assert torch.allclose(torch.load(a)["logits"], torch.load(b)["logits"], atol=1e-4)
+    # FE_LOG_DUMP: one hash line per layer and step; the same input gives the same lines
+    monkeypatch.setenv("FE_LOG_DUMP", "1")
+    runs = []
+    for _ in range(2):
+        cli.main(["generate", "--ids", "5,6,7", "--max-tokens", "1", "--device", "cpu"])
+        runs.append([ln for ln in capsys.readouterr().err.splitlines() if ln.startswith("layer ")])
+    n_layers = PRESETS["tiny"]().n_layers
+    assert len(runs[0]) == 2 * n_layers and runs[0] == runs[1] and "sha1" in runs[0][0]
