@@ -31,6 +31,11 @@ class CudaOps(CudaExtras):
         self.device = torch.device(device)
         self.dtype = dtype
         assert dtype == torch.bfloat16, "the sm_100a kernels take bf16 activations"
+        cap = torch.cuda.get_device_capability(self.device)
+        if cap != (10, 0) and not os.environ.get("FB_SKIP_ARCH_CHECK"):
+            # the extension holds sm_100a code only: on any other GPU every launch would fail with "no kernel image"
+            raise RuntimeError(f"{torch.cuda.get_device_name(self.device)} has compute capability {cap[0]}.{cap[1]}; "
+                               "the kernels of this build are sm_100a (B200, 10.0) only")
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.status_word = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._ws: Optional[torch.Tensor] = None
