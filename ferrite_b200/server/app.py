@@ -109,7 +109,7 @@ def _err(e: ApiError) -> web.Response:
 
 
 async def health(request: web.Request) -> web.Response:
-    st: AppState = request.app["state"]
+    st: AppState = request.app[STATE]
     info = st.engine.info()
     dead = st.engine.dead()
     load = st.engine.load()
@@ -122,7 +122,7 @@ async def health(request: web.Request) -> web.Response:
 
 
 async def models(request: web.Request) -> web.Response:
-    st: AppState = request.app["state"]
+    st: AppState = request.app[STATE]
     info = st.engine.info()
     card = {"id": st.served_name, "object": "model", "created": int(st.started), "owned_by": "ferrite",
             "context_length": info.max_model_len, "max_model_len": info.max_model_len}
@@ -135,13 +135,16 @@ async def models(request: web.Request) -> web.Response:
 
 
 async def metrics(request: web.Request) -> web.Response:
-    st: AppState = request.app["state"]
+    st: AppState = request.app[STATE]
     load = st.engine.load()
     lines = [f"ferrite_{k}_total {v}" for k, v in st.counters.items()]
     lines += [f"ferrite_running {load['running']}", f"ferrite_queued {load['queued']}",
               f"ferrite_uptime_seconds {time.time() - st.started:.1f}"]
     lines += [f"ferrite_engine_{k} {v}" for k, v in st.engine.metrics().items()]
     return web.Response(text="\n".join(lines) + "\n", content_type="text/plain")
+
+
+STATE: "web.AppKey[AppState]" = web.AppKey("state", AppState)
 
 
 def _capture(st: AppState, kind: str, body: Any, meta: Dict[str, Any]) -> None:
@@ -327,7 +330,7 @@ def _sse(obj: Any) -> bytes:
 
 
 async def _run(request: web.Request, chat: bool) -> web.StreamResponse:
-    st: AppState = request.app["state"]
+    st: AppState = request.app[STATE]
     st.engine.incoming(+1)              # until the request is handed to the engine (or refused)
     counted = [True]
 
@@ -472,10 +475,10 @@ def make_app(state_factory) -> web.Application:
     app = web.Application(client_max_size=BODY_LIMIT + 1024)
 
     async def on_start(app):
-        app["state"] = state_factory()
+        app[STATE] = state_factory()
 
     async def on_stop(app):
-        app["state"].engine.shutdown()
+        app[STATE].engine.shutdown()
 
     app.on_startup.append(on_start)
     app.on_cleanup.append(on_stop)

@@ -150,6 +150,33 @@ def test_six_streams_on_four_slots_and_dead_engine():
     run(go())
 
 
+def test_dropped_stream_cancels_the_request_and_frees_its_slot():
+    """A client that goes away in the middle of a stream: the request is cancelled, its slot comes back, the next
+    request runs (reference `dropped_stream_cancels`, `crates/fe-server/tests/e2e_mock.rs`)."""
+    async def go():
+        c = await client_for(lambda tok: MockEngine(tok, "test-model", max_batch=1, delay_s=0.01))
+        long_reply = "[[repeat:400:word ]]"
+        r = await c.post("/v1/chat/completions", json=chat(long_reply, stream=True, max_tokens=4000))
+        assert r.status == 200
+        got = 0
+        async for line in r.content:                        # read a few chunks, then hang up
+            if line.startswith(b"data: "):
+                got += 1
+                if got >= 5:
+                    break
+        r.close()
+        for _ in range(200):                                # the server notices on its next write
+            h = await (await c.get("/health")).json()
+            if h["running"] == 0 and h["queued"] == 0:
+                break
+            await asyncio.sleep(0.02)
+        assert h["running"] == 0 and h["queued"] == 0, h
+        r2 = await c.post("/v1/chat/completions", json=chat("after the drop"))
+        assert r2.status == 200 and (await r2.json())["choices"][0]["message"]["content"] == "echo: after the drop"
+        await c.close()
+    run(go())
+
+
 def test_watchdog_ends_a_silent_request(monkeypatch):
     monkeypatch.setenv("FE_NO_TOKEN_TIMEOUT", "0.05")
     import ferrite_b200.server.app as appmod
