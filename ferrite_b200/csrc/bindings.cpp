@@ -395,6 +395,7 @@ void kv_move_rows(Tensor k, c10::optional<Tensor> v, c10::optional<Tensor> sc, T
 
 void register_ext(pybind11::module_& m);
 void register_host(pybind11::module_& m);
+void register_oracle(pybind11::module_& m);
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("embed", &embed);
@@ -430,4 +431,5 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("kv_move_rows", &kv_move_rows);
   register_ext(m);
   register_host(m);
+  register_oracle(m);
 }
