@@ -252,6 +252,16 @@ def test_control_tool_and_environment_check(tmp_path, monkeypatch, capsys):
     assert check_env.check(gpus=2)["errors"]                      # no GPU on the test machine: asking for two is an error
 
 
+def test_tp_gate_with_two_cpu_ranks(capsys):
+    """The tensor-parallel server gate end to end on two gloo ranks: start, concurrent lanes equal to solo runs, repeat,
+    ranks alive, stop."""
+    from ferrite_b200.tools.tp_gate import main
+    rc = main(["--gpus", "2", "--lanes", "1,2", "--prefix-tokens", "60", "--start-timeout", "180", "--",
+               "--preset", "tiny", "--device", "cpu", "--slots", "2", "--max-model-len", "1024"])
+    out = capsys.readouterr().out
+    assert rc == 0 and out.count("PASS") == 6 and "tp gate: PASS" in out, out
+
+
 def test_sweep_runs_points(capsys):
     from ferrite_b200.tools.sweep import main
     url, loop = _serve()
