@@ -28,7 +28,9 @@ def main():
     ap.add_argument("--model", default="27b")
     ap.add_argument("--layers", type=int, default=0, help="cut the model to this many layers (0 = all)")
     ap.add_argument("--dtype", default="nvfp4", choices=["nvfp4", "nvfp4-w4a4", "nvfp4-a16", "fp8-block", "exl3", "bf16"])
-    ap.add_argument("--kv", default="bf16", choices=["bf16", "fp8", "int4"], help="KV cache format of the tested engine")
+    ap.add_argument("--kv", default="bf16", choices=["bf16", "fp8", "int6", "int4", "fp8h", "int6h", "int4h"],
+                    help="KV cache format of the tested engine")
+    ap.add_argument("--device", default="cuda", help="cuda, or cpu for the fp32 statements (weight formats then decode to dense)")
     ap.add_argument("--ref", default="bf16", choices=["bf16", "dequantised"],
                     help="reference engine: bf16 on the original weights, or bf16 on the dequantised weights of the tested engine")
     ap.add_argument("--rows", default="prefill", choices=["prefill", "decode"], help="score prompt chunks or one-row decode steps")
@@ -42,7 +44,7 @@ def main():
     cfg = PRESETS[a.model]()
     if a.layers:
         cfg = scaled(cfg, a.layers)
-    dev = "cuda"
+    dev = a.device
     w = init_weights(cfg, seed=a.seed, dtype=torch.bfloat16, device=dev)
     prompt = torch.randint(0, cfg.vocab, (a.tokens,), generator=torch.Generator().manual_seed(99)).tolist()
     outs = {}
