@@ -262,6 +262,34 @@ def test_tp_gate_with_two_cpu_ranks(capsys):
     assert rc == 0 and out.count("PASS") == 6 and "tp gate: PASS" in out, out
 
 
+def test_check_model_reports_missing_tensors_and_changed_files(tmp_path, capsys):
+    import torch
+    from ferrite_b200.config import tiny_hybrid
+    from ferrite_b200.formats.loader import save_native
+    from ferrite_b200.models.weights import init_weights
+    from ferrite_b200.tools import check_model
+    cfg = tiny_hybrid()
+    w = init_weights(cfg, seed=0, dtype=torch.bfloat16)
+    good = tmp_path / "good"
+    good.mkdir()
+    save_native(w, str(good / "model.safetensors"), cfg)
+    assert check_model.main([str(good), "--preset", "tiny", "--manifest"]) == 0
+    rep = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert rep["missing"] == [] and rep["storage"]["bfloat16"]["tensors"] > 10 and rep["params"] == cfg.param_count()
+    (tmp_path / "m.json").write_text(json.dumps(rep))
+    assert check_model.main([str(good), "--preset", "tiny", "--verify", str(tmp_path / "m.json")]) == 0
+    capsys.readouterr()
+    bad = tmp_path / "bad"
+    bad.mkdir()
+    w2 = {k: v for k, v in w.items() if k != "l1.down"}
+    w2["l0.down"] = w2["l0.down"][:, :-8].contiguous()
+    save_native(w2, str(bad / "model.safetensors"), cfg)
+    assert check_model.main([str(bad), "--preset", "tiny", "--verify", str(tmp_path / "m.json")]) == 1
+    rep = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert rep["missing"] == ["l1.down"] and "l0.down" in rep["shape_mismatches"]
+    assert any("differs from the manifest" in p for p in rep["problems"])
+
+
 def test_sweep_runs_points(capsys):
     from ferrite_b200.tools.sweep import main
     url, loop = _serve()
