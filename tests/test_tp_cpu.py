@@ -9,7 +9,7 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from ferrite_b200.config import EngineConfig, tiny_hybrid
+from ferrite_b200.config import PRESETS, EngineConfig, tiny_hybrid
 from ferrite_b200.engine.engine import Engine
 from ferrite_b200.engine.executor import Segment
 from ferrite_b200.models.weights import init_weights
@@ -23,13 +23,13 @@ def _free_port():
     return p
 
 
-def _worker(rank, world, port, prompt, q):
+def _worker(rank, world, port, prompt, q, preset="tiny"):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=60))
     from ferrite_b200.parallel.tp import TensorParallel
     tp = TensorParallel(dist.group.WORLD, "cpu", fused=False)
-    cfg = tiny_hybrid()
+    cfg = PRESETS[preset]()
     w = init_weights(cfg, seed=0)
     eng = Engine(cfg, w, EngineConfig(n_slots=1, max_ctx=128), device="cpu", tp=tp)
     logits, picks, _ = eng.forward([Segment(0, 0, prompt, "all")])
@@ -63,6 +63,32 @@ def test_tp_matches_single_rank(world, plen):
         assert torch.allclose(l2, want2, atol=3e-5, rtol=1e-4)
     # every rank holds identical bits
     assert torch.equal(outs[0][1], outs[1][1])
+
+
+@pytest.mark.parametrize("plen", [20, 70])
+def test_moe_latent_attention_model_under_tp2(plen):
+    """The tiny latent-attention + MoE model on two gloo ranks (heads and experts split over the ranks, expert partial
+    sums reduced): prompt logits, picks and a decode step equal the single-rank run, and both ranks hold the same bits."""
+    cfg = PRESETS["tiny-mla"]()
+    w = init_weights(cfg, seed=0)
+    prompt = torch.randint(0, cfg.vocab, (plen,), generator=torch.Generator().manual_seed(6)).tolist()
+    eng = Engine(cfg, w, EngineConfig(n_slots=1, max_ctx=128), device="cpu")
+    want, wp, _ = eng.forward([Segment(0, 0, prompt, "all")])
+    want2, _, _ = eng.forward([Segment(0, len(prompt), [int(wp[0][-1])], "last")])
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, prompt, q, "tiny-mla")) for r in range(2)]
+    for p in procs:
+        p.start()
+    outs = sorted([q.get(timeout=180) for _ in range(2)], key=lambda t: t[0])
+    for p in procs:
+        p.join(timeout=60)
+    for rank, logits, ids, l2 in outs:
+        assert torch.allclose(logits, want, atol=5e-5, rtol=1e-4), (rank, (logits - want).abs().max())
+        assert ids.tolist() == wp[0].tolist()
+        assert torch.allclose(l2, want2, atol=5e-5, rtol=1e-4)
+    assert torch.equal(outs[0][1], outs[1][1]) and torch.equal(outs[0][3], outs[1][3])
 
 
 def _lonely(rank, world, port, q):
