@@ -34,9 +34,22 @@ def drafter_config_for(target: ModelConfig) -> ModelConfig:
 
 class BlockDrafter(Drafter):
     def __init__(self, cfg: ModelConfig, target_hidden: int, n_taps: int, n_slots: int, max_ctx: int,
-                 device: Optional[str] = None, seed: int = 1, block: int = 16, weights=None, mask_token: int = 0):
-        ecfg = EngineConfig(n_slots=n_slots, max_ctx=max_ctx, use_graphs=False)
+                 device: Optional[str] = None, seed: int = 1, block: int = 16, weights=None, mask_token: int = 0,
+                 window: int = 0, ring: int = 0, weight_dtype: str = "bf16"):
+        """`window` > 0 bounds the drafter's own context: its cache holds at most `ring` (default 2 x window) tokens in
+        drafter-local positions; when a commit would run past the ring, the slot is rebuilt from the last `window`
+        committed tokens and their features (one re-absorb of `window` rows per `ring - window` committed tokens) and
+        goes on from there. The drafter then costs the same at 100K tokens of context as at 2K (reference: draft ring 4096 /
+        window 2048, `crates/fe-dflash/src/lib.rs`). `weight_dtype`: the drafter's own weight format (the reference
+        serves its drafter in 4 bits)."""
+        self.window = int(window)
+        self.ring = int(ring) if ring else 2 * self.window
+        assert self.window == 0 or self.ring > self.window + block, "the ring must hold a window and a block"
+        ecfg = EngineConfig(n_slots=n_slots, max_ctx=(self.ring + block + 2) if self.window else max_ctx, use_graphs=False,
+                            weight_dtype=weight_dtype)
         self.eng = Engine(cfg, weights, ecfg, device=device, seed=seed)
+        self.base = [0] * n_slots                    # target position of the drafter's local position 0
+        self.hist = [[] for _ in range(n_slots)]     # windowed mode: (tokens, fused features or None) of recent commits
         self.block = block
         self.tree_k = 4                              # candidates per depth when growing a verify tree
         self.mask_token = mask_token
@@ -54,6 +67,35 @@ class BlockDrafter(Drafter):
     def reset(self, slot: int) -> None:
         self.eng.reset_slot(slot)
         self.last_feat[slot] = None
+        self.base[slot] = 0
+        self.hist[slot] = []
+
+    def _hist_tokens(self, slot: int) -> int:
+        return sum(len(t) for t, _ in self.hist[slot])
+
+    def _hist_trim(self, slot: int, keep: int) -> None:
+        """Keep only the last `keep` tokens of the slot's commit history."""
+        h = self.hist[slot]
+        extra = self._hist_tokens(slot) - keep
+        while extra > 0 and h:
+            t, f = h[0]
+            if len(t) <= extra:
+                h.pop(0)
+                extra -= len(t)
+            else:
+                h[0] = (t[extra:], None if f is None else f[extra:])
+                extra = 0
+
+    def _hist_drop_tail(self, slot: int, k: int) -> None:
+        h = self.hist[slot]
+        while k > 0 and h:
+            t, f = h[-1]
+            if len(t) <= k:
+                h.pop()
+                k -= len(t)
+            else:
+                h[-1] = (t[:-k], None if f is None else f[:-k])
+                k = 0
 
     def absorb(self, slot: int, tokens: Sequence[int], pos0: int, taps) -> None:
         """Extend the drafter's cache with committed tokens and the target features of their rows."""
@@ -61,7 +103,32 @@ class BlockDrafter(Drafter):
         if n == 0:
             return
         feat = self._fused(taps, slice(0, n)) if taps and taps[0].shape[0] >= n else None
-        self.eng.forward([Segment(slot, pos0, list(tokens), "none")], commit=True, x_add=feat)
+        local = pos0
+        if self.window and n > self.window:
+            # a commit longer than the window (a prompt chunk): only its last `window` rows can matter afterwards
+            cut = n - self.window
+            tokens, pos0, n = list(tokens)[cut:], pos0 + cut, self.window
+            feat = None if feat is None else feat[cut:]
+            self.eng.reset_slot(slot)
+            self.hist[slot] = []
+        if self.window:
+            if self.eng.slot_len[slot] == 0 and not self.hist[slot]:
+                self.base[slot] = pos0                       # an empty drafter starts its own positions here
+            local = pos0 - self.base[slot]
+            if local < 0 or local + n > self.ring:
+                # rebuild the slot from the last `window` committed tokens, then go on behind them
+                self._hist_trim(slot, min(self.window, max(0, self.ring - n)))
+                kept = [t for ts, _ in self.hist[slot] for t in ts]
+                feats = [f for _, f in self.hist[slot]]
+                self.eng.reset_slot(slot)
+                self.base[slot] = pos0 - len(kept)
+                if kept:
+                    x_add = torch.cat(feats) if all(f is not None for f in feats) else None
+                    self.eng.forward([Segment(slot, 0, kept, "none")], commit=True, x_add=x_add)
+                local = len(kept)
+            self.hist[slot].append(([int(t) for t in tokens], None if feat is None else feat.clone()))
+            self._hist_trim(slot, self.window)
+        self.eng.forward([Segment(slot, local, list(tokens), "none")], commit=True, x_add=feat)
         if feat is not None:
             self.last_feat[slot] = feat[-1:].clone()
 
@@ -72,7 +139,7 @@ class BlockDrafter(Drafter):
         toks = [last_token] + [self.mask_token] * (n - 1)
         feat = self.last_feat[slot]
         x_add = feat.expand(n, -1).contiguous() if feat is not None else None
-        _, picks, _ = self.eng.forward([Segment(slot, pos, toks, "all")], commit=False, greedy=True, x_add=x_add)
+        _, picks, _ = self.eng.forward([Segment(slot, pos - self.base[slot], toks, "all")], commit=False, greedy=True, x_add=x_add)
         return [int(t) for t in picks[0].tolist()]
 
     def draft_tree(self, slot: int, last_token: int, pos: int, taps, depth: int, rows: int):
@@ -84,20 +151,24 @@ class BlockDrafter(Drafter):
         toks = [last_token] + [self.mask_token] * (n - 1)
         feat = self.last_feat[slot]
         x_add = feat.expand(n, -1).contiguous() if feat is not None else None
-        logits, _, _ = self.eng.forward([Segment(slot, pos, toks, "all")], commit=False, greedy=False, x_add=x_add)
+        logits, _, _ = self.eng.forward([Segment(slot, pos - self.base[slot], toks, "all")], commit=False, greedy=False, x_add=x_add)
         lp, ids = torch.log_softmax(logits.float(), -1).topk(min(self.tree_k, logits.shape[-1]), -1)
         lp, ids = lp.tolist(), ids.tolist()
         return grow_tree([list(zip(ids[d], lp[d])) for d in range(n)], rows)
 
     def save_window(self, slot: int):
-        return {"len": self.eng.slot_len[slot], "feat": self.last_feat[slot]}
+        return {"len": self.eng.slot_len[slot], "feat": self.last_feat[slot], "base": self.base[slot]}
 
     def restore_window(self, slot: int, blob) -> None:
-        # the drafter's KV rows up to the snapshot position are still in its slot; only the length rolls back
-        if blob is None:
+        # the drafter's KV rows up to the snapshot position are still in its slot; only the length rolls back. A slot
+        # that was rebuilt since the snapshot (windowed mode) no longer holds those rows: it starts over, empty.
+        if blob is None or blob.get("base", 0) != self.base[slot]:
             self.reset(slot)
             return
-        self.eng.slot_len[slot] = min(self.eng.slot_len[slot], blob["len"])
+        cur = self.eng.slot_len[slot]
+        self.eng.slot_len[slot] = min(cur, blob["len"])
+        if self.window and cur > blob["len"]:
+            self._hist_drop_tail(slot, cur - blob["len"])
         self.last_feat[slot] = blob["feat"]
 
 

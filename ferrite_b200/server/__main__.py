@@ -99,8 +99,11 @@ def build_engine(args, tok):
             drafter = MtpDrafter(eng, n_slots=args.slots, max_ctx=args.max_model_len, depth=max(1, min(opts.spec or 4, 8)))
         else:
             from ..models.drafter import BlockDrafter, drafter_config_for
+            # the drafter's own context is bounded (window / ring) once the served context is longer than the ring
+            win = args.draft_window if args.max_model_len > 2 * args.draft_window else 0
             drafter = BlockDrafter(drafter_config_for(cfg), target_hidden=cfg.hidden, n_taps=len(cfg.tap_layers),
-                                   n_slots=args.slots, max_ctx=args.max_model_len, device=str(eng.device), block=16)
+                                   n_slots=args.slots, max_ctx=args.max_model_len, device=str(eng.device), block=16,
+                                   window=win, ring=2 * win, weight_dtype=args.draft_weights)
         if opts.spec == 0:
             opts.spec = 4 if kind == "mtp" else 8
     return SchedulerEngine(Scheduler(eng, opts, drafter=drafter), args.served_model_name)
@@ -126,6 +129,10 @@ def main(argv=None) -> int:
     ap.add_argument("--mock", action="store_true")
     ap.add_argument("--drafter", default=os.environ.get("FERRITE_DRAFTER", "none"), choices=["none", "block", "mtp"],
                     help="draft model for speculative decoding (FE_SPEC sets the depth, FE_TREE the rows of a verify tree)")
+    ap.add_argument("--draft-window", type=int, default=int(os.environ.get("FERRITE_DRAFT_WINDOW", "2048")),
+                    help="block drafter: tokens of its own context (its cache ring holds twice as many); 0 = the whole context")
+    ap.add_argument("--draft-weights", default=os.environ.get("FERRITE_DRAFT_WEIGHTS", "bf16"),
+                    help="block drafter: its weight format (bf16, nvfp4, ...)")
     args = ap.parse_args(argv)
 
     from .app import AppState, make_app

@@ -430,3 +430,48 @@ def test_copier_adapts_its_length_continues_loops_and_grafts_onto_trees():
     assert (followed, added) == (2, 1) and toks == [0, 5, 4, 6, 9, 7] and par == [-1, 0, 0, 1, 1, 3]
     toks, par = [0], [-1]
     assert graft(toks, par, [5, 6], room=8) == (0, 2) and par == [-1, 0, 1]
+
+
+def test_block_drafter_window_bounds_its_context():
+    """A drafter with a window keeps at most `ring` tokens in its own cache however long the sequence gets, is rebuilt
+    from the last `window` committed tokens when a commit would run past the ring, and right after a rebuild drafts what
+    a fresh drafter that saw exactly those tokens drafts. Greedy output through the scheduler stays the target's."""
+    from ferrite_b200.models.drafter import BlockDrafter, drafter_config_for
+    cfg, w, eng = _engine(n_slots=1)
+    dcfg = drafter_config_for(cfg)
+    hid = cfg.hidden
+    mk = lambda **kw: BlockDrafter(dcfg, target_hidden=hid, n_taps=1, n_slots=1, max_ctx=512, device="cpu", block=4, **kw)
+    win = mk(window=16, ring=40)
+    g = torch.Generator().manual_seed(3)
+    toks = torch.randint(1, cfg.vocab, (300,), generator=g).tolist()
+    feats = torch.randn(300, hid, generator=g)
+    pos, rebuilt_at = 0, []
+    for n in [37, 5, 1, 1, 9, 1, 1, 30, 1, 1, 1, 60, 1, 1]:                # prompt chunks, decode rows, a long chunk
+        base0 = win.base[0]
+        win.absorb(0, toks[pos:pos + n], pos, [feats[pos:pos + n]])
+        pos += n
+        assert win.eng.slot_len[0] <= 40 and win.eng.slot_len[0] == pos - win.base[0]
+        if win.base[0] != base0:
+            rebuilt_at.append(pos)
+    assert len(rebuilt_at) >= 3
+    d_win = win.draft(0, toks[pos - 1], pos, None, 4)
+    # a fresh, unbounded drafter fed exactly what the windowed one holds (same local positions) drafts the same
+    held = pos - win.base[0]
+    fresh = mk()
+    fresh.absorb(0, toks[pos - held:pos], 0, [feats[pos - held:pos]])
+    assert fresh.draft(0, toks[pos - 1], held, None, 4) == d_win and len(d_win) == 4
+    # snapshot / restore: same base -> length rolls back; after a rebuild -> the slot starts over
+    blob = win.save_window(0)
+    win.absorb(0, toks[pos:pos + 2], pos, [feats[pos:pos + 2]])
+    win.restore_window(0, blob)
+    assert win.eng.slot_len[0] == blob["len"] and win._hist_tokens(0) <= 16
+    win.absorb(0, toks[pos:pos + 30], pos, [feats[pos:pos + 30]])          # forces a rebuild
+    win.restore_window(0, blob)
+    assert win.eng.slot_len[0] == 0 and win.hist[0] == []
+    # through the scheduler: speculation with a windowed drafter keeps the greedy text
+    p = _prompt(cfg, 50, 21)
+    cfg.tap_layers = [cfg.n_layers - 1]
+    eng2 = Engine(cfg, w, EngineConfig(n_slots=1, max_ctx=256), device="cpu")
+    dr = BlockDrafter(dcfg, target_hidden=hid, n_taps=1, n_slots=1, max_ctx=256, device="cpu", block=4, window=16, ring=40)
+    out = generate(Scheduler(eng2, SchedOptions(spec=3, copy_rows=False), drafter=dr), [p], Sampling(max_tokens=40))[0]
+    assert out == _plain(cfg, w, p, 40) and dr.eng.slot_len[0] <= 40
