@@ -100,10 +100,11 @@ def build_engine(args, tok):
         else:
             from ..models.drafter import BlockDrafter, drafter_config_for
             # the drafter's own context is bounded (window / ring) once the served context is longer than the ring
-            win = args.draft_window if args.max_model_len > 2 * args.draft_window else 0
+            dw = int(getattr(args, "draft_window", 2048))
+            win = dw if args.max_model_len > 2 * dw else 0
             drafter = BlockDrafter(drafter_config_for(cfg), target_hidden=cfg.hidden, n_taps=len(cfg.tap_layers),
                                    n_slots=args.slots, max_ctx=args.max_model_len, device=str(eng.device), block=16,
-                                   window=win, ring=2 * win, weight_dtype=args.draft_weights)
+                                   window=win, ring=2 * win, weight_dtype=getattr(args, "draft_weights", "bf16"))
         if opts.spec == 0:
             opts.spec = 4 if kind == "mtp" else 8
     return SchedulerEngine(Scheduler(eng, opts, drafter=drafter), args.served_model_name)
