@@ -475,3 +475,14 @@ def test_block_drafter_window_bounds_its_context():
     dr = BlockDrafter(dcfg, target_hidden=hid, n_taps=1, n_slots=1, max_ctx=256, device="cpu", block=4, window=16, ring=40)
     out = generate(Scheduler(eng2, SchedOptions(spec=3, copy_rows=False), drafter=dr), [p], Sampling(max_tokens=40))[0]
     assert out == _plain(cfg, w, p, 40) and dr.eng.slot_len[0] <= 40
+
+
+def test_common_prefix_matches_the_token_by_token_loop():
+    import random
+    rng = random.Random(0)
+    for _ in range(1500):
+        n = rng.randrange(0, 500)
+        a = [rng.randrange(3) for _ in range(n)]
+        b = a[:rng.randrange(0, n + 1)] + [rng.randrange(3) for _ in range(rng.randrange(0, 40))]
+        want = next((i for i, (x, y) in enumerate(zip(a, b)) if x != y), min(len(a), len(b)))
+        assert common_prefix(a, b) == want and common_prefix(tuple(a), b) == want
