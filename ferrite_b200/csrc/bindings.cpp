@@ -396,6 +396,7 @@ void kv_move_rows(Tensor k, c10::optional<Tensor> v, c10::optional<Tensor> sc, T
 void register_ext(pybind11::module_& m);
 void register_host(pybind11::module_& m);
 void register_oracle(pybind11::module_& m);
+void register_gguf_host(pybind11::module_& m);
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("embed", &embed);
@@ -432,4 +433,5 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   register_ext(m);
   register_host(m);
   register_oracle(m);
+  register_gguf_host(m);
 }

@@ -162,6 +162,9 @@ def _scale_min_k4(sc: np.ndarray):
     return s, m
 
 
+_NATIVE_TYPES = ("Q8_0", "Q4_0", "Q4_K", "Q5_K", "Q6_K")
+
+
 def dequantize(raw: np.ndarray, type_id: int) -> np.ndarray:
     name, bv, bb = TYPES[type_id]
     if name == "F32":
@@ -172,6 +175,14 @@ def dequantize(raw: np.ndarray, type_id: int) -> np.ndarray:
         return (raw.view(np.uint16).astype(np.uint32) << 16).view(np.float32)
     if name in ("I8", "I16", "I32", "I64", "F64"):
         return raw.view({"I8": np.int8, "I16": np.int16, "I32": np.int32, "I64": np.int64, "F64": np.float64}[name]).astype(np.float32)
+    if name in _NATIVE_TYPES:
+        # the common dense formats decode in C++ (`csrc/host_gguf.cpp`) when the extension is built: the same bits as
+        # the statements below, without their temporaries
+        from .._ext import host
+        h = host()
+        if h is not None and hasattr(h, "gguf_dequant_host"):
+            import torch
+            return h.gguf_dequant_host(torch.from_numpy(np.ascontiguousarray(raw).reshape(-1).view(np.uint8).copy()), name).numpy()
     b = raw.reshape(-1, bb)
     nb = b.shape[0]
     if name == "Q8_0":

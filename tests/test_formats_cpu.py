@@ -337,3 +337,31 @@ def test_gguf_checkpoint_round_trip_into_the_engine(tmp_path, moe):
     a = Engine(cfg, packed, EngineConfig(n_slots=1, max_ctx=64), device="cpu").generate(prompt, 5)
     b = Engine(cfg, dense, EngineConfig(n_slots=1, max_ctx=64), device="cpu").generate(prompt, 5)
     assert a == b
+
+
+def test_native_gguf_decoders_are_bit_exact(monkeypatch):
+    """The C++ decoders of the common dense GGUF formats against the NumPy statements: every bit, over random blocks
+    (subnormal and non-finite scales included) and over blocks made by the writers."""
+    import numpy as np
+
+    from ferrite_b200 import _ext
+    from ferrite_b200.formats import gguf as G
+    h = _ext.host()
+    if h is None or not hasattr(h, "gguf_dequant_host"):
+        import pytest
+        pytest.skip("extension not built")
+    ids = {v[0]: k for k, v in G.TYPES.items()}
+    rng = np.random.default_rng(0)
+    cases = {name: rng.integers(0, 256, size=G.TYPES[ids[name]][2] * 500, dtype=np.uint8) for name in G._NATIVE_TYPES}
+    x = rng.standard_normal(64 * 32).astype(np.float32)
+    cases["Q8_0"] = np.concatenate([cases["Q8_0"], G.quantize_q8_0(x).reshape(-1).view(np.uint8)])
+    cases["Q4_0"] = np.concatenate([cases["Q4_0"], G.quantize_q4_0(x).reshape(-1).view(np.uint8)])
+    with np.errstate(all="ignore"):
+        for name, raw in cases.items():
+            monkeypatch.delenv("FERRITE_NO_NATIVE_HOST", raising=False)
+            got = G.dequantize(raw, ids[name])
+            monkeypatch.setenv("FERRITE_NO_NATIVE_HOST", "1")
+            want = G.dequantize(raw, ids[name])
+            assert got.dtype == np.float32 and got.shape == want.shape
+            assert np.array_equal(got.view(np.uint32) & 0x7fffffff < 0x7f800001, want.view(np.uint32) & 0x7fffffff < 0x7f800001)
+            assert np.array_equal(got, want, equal_nan=True), name
