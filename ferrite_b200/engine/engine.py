@@ -148,6 +148,9 @@ class Engine:
             self.ex.ep = ExpertParallel(tp if world > 1 else None, self.device, cfg.n_experts, cfg.hidden,
                                         cap_rows=self.ecfg.max_step_rows * cfg.top_k)
         self.slot_len: List[int] = [0] * self.ecfg.n_slots
+        if self.ex.heat:
+            import atexit
+            atexit.register(self.close)
         import os
         if os.environ.get("FB_DEBUG_BOUNDS", "0") not in ("", "0"):
             # debug mode: index tensors are checked on the host before every op (eager steps, one sync per check)
@@ -189,6 +192,14 @@ class Engine:
         code = self.ops.status()
         if code:
             raise RuntimeError(f"device status {code}: a kernel wait ran out or an index was out of range")
+
+    def expert_heat(self):
+        """Picks per expert and MoE layer (counted when FE_EXPERT_HEAT is set)."""
+        return self.ex.expert_heat()
+
+    def close(self) -> None:
+        """End of the engine's life: write what was asked to be written (expert heat counters)."""
+        self.ex.write_expert_heat()
 
     def reset_slot(self, slot: int) -> None:
         self.ex.reset_slot(slot)

@@ -216,11 +216,38 @@ class Executor:
         # run eagerly and unfused then): two builds, or two schedules of the same prompt, diverge at the first line that
         # differs (reference `FE_LOG_DUMP` layer taps, `crates/fe-model/src/model.rs`)
         self.dump_layers = os.environ.get("FE_LOG_DUMP", "0") not in ("", "0")
+        # FE_EXPERT_HEAT=<file>: count how often every expert of every MoE layer is picked (device-side adds, no host
+        # sync on the step path); `expert_heat()` reads them, the engine writes them to the file when it is closed.
+        # What expert placement and replication decisions are made from (reference `DSC_HEAT_LOG` / `FNEXT_COUNTS`,
+        # `crates/fe-dsc/src/engine.rs:2251-2315`).
+        self.heat_path = os.environ.get("FE_EXPERT_HEAT", "")
+        self.heat: Dict[int, torch.Tensor] = {}
+        if self.heat_path and cfg.n_experts > 0:
+            for i in range(cfg.n_layers):
+                if cfg.is_moe(i):
+                    self.heat[i] = torch.zeros((full_cfg or cfg).n_experts + 1, dtype=torch.int64, device=self.device)
         self.moe_merged: Dict[int, torch.Tensor] = {}
         self._merge_shared_experts()
         self._step_max_kvlen = None
         self._step_segments = None            # host view of an eager step's segments: (slot, pos0, rows)
         self.ep = None                        # ExpertParallel, set by the engine for MoE models under TP
+
+    def _count_experts(self, i: int, ids) -> None:
+        h = self.heat.get(i)
+        if h is not None:
+            flat = ids.reshape(-1).long()
+            h.scatter_add_(0, flat, torch.ones_like(flat))
+
+    def expert_heat(self) -> Dict[int, List[int]]:
+        """Picks per expert and MoE layer since the engine was built (the last entry counts the shared expert when it
+        rides along as a pair)."""
+        return {i: h.tolist() for i, h in self.heat.items()}
+
+    def write_expert_heat(self) -> None:
+        if self.heat_path and self.heat:
+            import json
+            with open(self.heat_path, "w", encoding="utf-8") as f:
+                json.dump({"layers": {str(i): v for i, v in self.expert_heat().items()}}, f)
 
     def _dump_layer(self, i: int, x, sp: bool, T: int) -> None:
         import hashlib
@@ -473,6 +500,7 @@ class Executor:
         logits = ops.linear(h, w[p + "router"], out_f32=True)
         ids, wts = ops.moe_route(logits.contiguous(), w.get(p + "router_bias"), 0 if c.router == "softmax" else 1, c.top_k,
                                  c.n_groups, c.topk_groups, c.route_scale)
+        self._count_experts(i, ids)
         shared = sgate = None
         if c.n_shared:
             shared = row(col(x, w[p + "shared_gate_up"], w[p + "post_norm"], swiglu=True), w[p + "shared_down"], None)
@@ -496,10 +524,12 @@ class Executor:
             ids, wts = ops.moe_route(logits, w.get(p + "router_bias"), 0 if c.router == "softmax" else 1, c.top_k,
                                      c.n_groups, c.topk_groups, c.route_scale, n_exp=n_exp,
                                      shared_col=n_exp if merged.shape[0] > n_exp else -1, shared_id=n_exp)
+            self._count_experts(i, ids)
             return ops.moe_experts(h, ids, wts, w[p + "experts_gate_up"], w[p + "experts_down"], 0, n_exp + 1, None, None, x)
         logits = ops.linear(h, w[p + "router"], out_f32=True)
         ids, wts = ops.moe_route(logits.contiguous(), w.get(p + "router_bias"), 0 if c.router == "softmax" else 1, c.top_k,
                                  c.n_groups, c.topk_groups, c.route_scale)
+        self._count_experts(i, ids)
         shared = sgate = None
         if c.n_shared:
             shared = ops.linear(ops.linear(h, w[p + "shared_gate_up"], swiglu=True), w[p + "shared_down"])

@@ -102,3 +102,31 @@ def test_expert_parallel_two_ranks(plen):
     for rank, logits in outs:
         assert not isinstance(logits, str), logits
         assert torch.allclose(logits, want, atol=5e-5, rtol=1e-4), rank
+
+
+def test_expert_heat_counters(tmp_path, monkeypatch):
+    """FE_EXPERT_HEAT: every routed pick of every MoE layer is counted (top_k per token and layer), read through the
+    engine and written to the file when the engine is closed."""
+    import json
+
+    import torch
+
+    from ferrite_b200.config import EngineConfig, tiny_mla
+    from ferrite_b200.engine.engine import Engine
+    from ferrite_b200.engine.executor import Segment
+    path = tmp_path / "heat.json"
+    monkeypatch.setenv("FE_EXPERT_HEAT", str(path))
+    cfg = tiny_mla()
+    eng = Engine(cfg, None, EngineConfig(n_slots=1, max_ctx=64), device="cpu")
+    toks = torch.randint(0, cfg.vocab, (21,), generator=torch.Generator().manual_seed(0)).tolist()
+    eng.forward([Segment(0, 0, toks[:20], "none")])
+    eng.forward([Segment(0, 20, toks[20:], "last")])
+    heat = eng.expert_heat()
+    moe_layers = [i for i in range(cfg.n_layers) if cfg.is_moe(i)]
+    assert sorted(heat) == moe_layers
+    for i in moe_layers:
+        assert sum(heat[i]) == 21 * cfg.top_k and len(heat[i]) == cfg.n_experts + 1 and max(heat[i]) > 0
+    eng.close()
+    assert json.loads(path.read_text())["layers"][str(moe_layers[0])] == heat[moe_layers[0]]
+    monkeypatch.delenv("FE_EXPERT_HEAT")
+    assert Engine(cfg, None, EngineConfig(n_slots=1, max_ctx=64), device="cpu").expert_heat() == {}
