@@ -169,6 +169,17 @@ def tree_walk(tokens: Sequence[int], parents: Sequence[int], pick) -> Tuple[List
         node = nxt
 
 
+def select_rows(taps, rows):
+    """The rows of a step's tapped hidden states that a drafter is to read: all of them (`rows` None), a range
+    `(start, stop)`, or a list of row indices (the accepted path of a verify tree)."""
+    if rows is None or not taps:
+        return taps
+    if isinstance(rows, tuple):
+        return [t[rows[0]:rows[1]] for t in taps]
+    idx = torch.tensor([int(r) for r in rows], dtype=torch.long, device=taps[0].device)
+    return [t.index_select(0, idx) for t in taps]
+
+
 class Drafter:
     """Plug-in interface of a draft model (reference trait `Drafter`, `sched.rs:58-116`)."""
 
@@ -183,6 +194,11 @@ class Drafter:
 
     def absorb(self, slot: int, tokens: Sequence[int], pos0: int, taps) -> None:
         pass
+
+    def absorb_rows(self, slot: int, tokens: Sequence[int], pos0: int, taps, rows) -> None:
+        """`absorb` over a selection of the step's tap rows (`select_rows`). What the scheduler calls: the selection
+        travels as plain integers, so a mirrored drafter can repeat it on every rank's own taps."""
+        self.absorb(slot, tokens, pos0, select_rows(taps, rows))
 
     def reset(self, slot: int) -> None:
         pass
@@ -554,7 +570,6 @@ class Scheduler:
         all_greedy = all(g for _, _, _, last, g in group if last)
         logits, picks, _ = self.eng.forward(segs, greedy=all_greedy)
         ids = picks[0].tolist() if (all_greedy and picks is not None) else None
-        taps = list(self.eng.taps)
         k = r = n = 0
         for a, cut, toks, last, _ in group:
             tok = None
@@ -570,7 +585,7 @@ class Scheduler:
                     continue
                 tok = int(ids[k]) if ids is not None else a.sampler.sample(logits[k], first=not a.out)
                 k += 1
-            self._prefill_done(a, cut, toks, last, tok, [t[r:r + cut] for t in taps])
+            self._prefill_done(a, cut, toks, last, tok, (r, r + cut))
             r += cut
             n += cut
         return n
@@ -591,7 +606,7 @@ class Scheduler:
         self._prefill_done(a, cut, toks, last, tok)
         return cut
 
-    def _prefill_done(self, a: Active, cut: int, toks: List[int], last: bool, tok, taps=None) -> None:
+    def _prefill_done(self, a: Active, cut: int, toks: List[int], last: bool, tok, tap_rows=None) -> None:
         a.pos += cut
         a.pending = a.pending[cut:]
         self.slot_cache[a.slot].tokens = (a.req.prompt + a.out)[:a.pos]
@@ -599,7 +614,7 @@ class Scheduler:
         if a.pos in a.snap_at:
             self._snapshot(a, pinned=(a.pos == a.snap_at[0]))
         if self.drafter:
-            self.drafter.absorb(a.slot, toks, a.pos - cut, self.eng.taps if taps is None else taps)
+            self.drafter.absorb_rows(a.slot, toks, a.pos - cut, self.eng.taps, tap_rows)
         if last:
             a.t_prompt_done = time.time()
             self._accept(a, [tok])
@@ -688,8 +703,7 @@ class Scheduler:
                     a.copier.observe(len(copy), landed)
                 a.pos += len(new)
                 if self.drafter is not None:
-                    idx = torch.tensor([r + i for i in path], dtype=torch.long, device=taps[0].device) if taps else None
-                    self.drafter.absorb(a.slot, fed, a.pos - len(new), [t.index_select(0, idx) for t in taps])
+                    self.drafter.absorb_rows(a.slot, fed, a.pos - len(new), taps, [r + i for i in path])
                 self._accept(a, new, sampled=not all_greedy)
                 r += n
                 continue
@@ -718,7 +732,7 @@ class Scheduler:
             fed = [a.next_token] + d[:acc]
             a.pos += len(new)
             if self.drafter is not None:
-                self.drafter.absorb(a.slot, fed, a.pos - len(new), [t[r:r + len(new)] for t in taps])
+                self.drafter.absorb_rows(a.slot, fed, a.pos - len(new), taps, (r, r + len(new)))
             self._accept(a, new, sampled=not all_greedy)
             r += n
         if spec and any_tree:

@@ -35,19 +35,21 @@ def drafter_config_for(target: ModelConfig) -> ModelConfig:
 class BlockDrafter(Drafter):
     def __init__(self, cfg: ModelConfig, target_hidden: int, n_taps: int, n_slots: int, max_ctx: int,
                  device: Optional[str] = None, seed: int = 1, block: int = 16, weights=None, mask_token: int = 0,
-                 window: int = 0, ring: int = 0, weight_dtype: str = "bf16"):
+                 window: int = 0, ring: int = 0, weight_dtype: str = "bf16", tp=None):
         """`window` > 0 bounds the drafter's own context: its cache holds at most `ring` (default 2 x window) tokens in
         drafter-local positions; when a commit would run past the ring, the slot is rebuilt from the last `window`
         committed tokens and their features (one re-absorb of `window` rows per `ring - window` committed tokens) and
         goes on from there. The drafter then costs the same at 100K tokens of context as at 2K (reference: draft ring 4096 /
         window 2048, `crates/fe-dflash/src/lib.rs`). `weight_dtype`: the drafter's own weight format (the reference
-        serves its drafter in 4 bits)."""
+        serves its drafter in 4 bits). `tp`: the target's tensor-parallel group; the drafter's engine is then cut over
+        the same ranks (every rank builds one, `engine/follow.py` keeps them in step) while the fusion matrix and the
+        fused features stay whole on every rank, as the tapped rows they are made from are."""
         self.window = int(window)
         self.ring = int(ring) if ring else 2 * self.window
         assert self.window == 0 or self.ring > self.window + block, "the ring must hold a window and a block"
         ecfg = EngineConfig(n_slots=n_slots, max_ctx=(self.ring + block + 2) if self.window else max_ctx, use_graphs=False,
                             weight_dtype=weight_dtype)
-        self.eng = Engine(cfg, weights, ecfg, device=device, seed=seed)
+        self.eng = Engine(cfg, weights, ecfg, device=device, seed=seed, tp=tp)
         self.base = [0] * n_slots                    # target position of the drafter's local position 0
         self.hist = [[] for _ in range(n_slots)]     # windowed mode: (tokens, fused features or None) of recent commits
         self.block = block

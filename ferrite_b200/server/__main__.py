@@ -36,7 +36,10 @@ def build_engine(args, tok):
             cfg = scaled(cfg, args.layers)
     world = int(os.environ.get("WORLD_SIZE", "1"))
     kind = getattr(args, "drafter", "none")
-    if kind != "none" and world == 1:
+    if kind == "mtp" and world > 1:
+        raise SystemExit("--drafter mtp runs on one GPU only (the head shares the target's embedding and output storage); "
+                         "use --drafter block under tensor parallelism")
+    if kind != "none":
         # the drafters read hidden rows of the target: the MTP head the last layer's, the block drafter three evenly
         # spaced ones (the preset's own tap list when it has one)
         if kind == "mtp":
@@ -83,17 +86,12 @@ def build_engine(args, tok):
                            lambda: EngineStepModel(Engine(cfg, weights, ecfg, device=args.device or None, seed=0)),
                            args.served_model_name)
     eng = Engine(cfg, weights, ecfg, device=args.device or None, seed=0, tp=tp)
-    if tp is not None:
-        from ..engine.follow import Leader, follow
-        if tp.rank != 0:
-            follow(eng, tp)
-            raise SystemExit(0)
-        eng = Leader(eng, tp)
     opts = SchedOptions.from_env()
     drafter = None
-    if kind != "none" and tp is None:
+    if kind != "none":
         # speculative decoding with a draft model (reference: the drafter `factory`, `crates/fe-dflash/src/lib.rs:1381`,
-        # and the MTP head of the checkpoint); single GPU only, the tensor-parallel leader proxies engine calls only
+        # and the MTP head of the checkpoint). Under tensor parallelism every rank builds the block drafter over its
+        # shard of the draft engine and the leader mirrors the drafter's calls (reference: DFlash2 at TP2)
         if kind == "mtp":
             from ..models.mtp import MtpDrafter
             drafter = MtpDrafter(eng, n_slots=args.slots, max_ctx=args.max_model_len, depth=max(1, min(opts.spec or 4, 8)))
@@ -104,9 +102,17 @@ def build_engine(args, tok):
             win = dw if args.max_model_len > 2 * dw else 0
             drafter = BlockDrafter(drafter_config_for(cfg), target_hidden=cfg.hidden, n_taps=len(cfg.tap_layers),
                                    n_slots=args.slots, max_ctx=args.max_model_len, device=str(eng.device), block=16,
-                                   window=win, ring=2 * win, weight_dtype=getattr(args, "draft_weights", "bf16"))
+                                   window=win, ring=2 * win, weight_dtype=getattr(args, "draft_weights", "bf16"), tp=tp)
         if opts.spec == 0:
             opts.spec = 4 if kind == "mtp" else 8
+    if tp is not None:
+        from ..engine.follow import Leader, follow
+        if tp.rank != 0:
+            follow(eng, tp, drafter)
+            raise SystemExit(0)
+        eng = Leader(eng, tp)
+        if drafter is not None:
+            drafter = eng.attach_drafter(drafter)
     return SchedulerEngine(Scheduler(eng, opts, drafter=drafter), args.served_model_name)
 
 

@@ -9,6 +9,8 @@ Steps (each PASS / FAIL, exit code 1 on any failure):
   lanes     N chats sent together: every lane's greedy text equals the same request sent alone (a rank that drifted, a
             lost or reordered engine call on a follower, or a stale exchange buffer shows up here)
   repeat    the same request twice in a row gives the same text (the second is served from the prompt cache)
+  spec      only when the server arguments name a draft model (`--drafter block`): /metrics shows drafted tokens, i.e. the
+            mirrored drafter ran on every rank (a follower without one stops the stream with an error)
   ranks     after the requests every rank process is still running and the server's log holds no traceback
   stop      SIGTERM to the launcher ends all ranks within 60 s
 The role of the reference's `tools/gate-serve-tp2.sh` (4 concurrent requests through the TP2 server, both ranks' logs).
@@ -107,6 +109,10 @@ def main(argv=None) -> int:
                 status, rep, _ = c.post("/v1/chat/completions", body)
                 texts.append(json.dumps(rep.get("choices", [{}])[0].get("message")) if status == 200 else f"HTTP {status}")
             steps.append(("repeat", len(set(texts)) == 1 and not texts[0].startswith("HTTP"), str(texts)[:300]))
+            if "--drafter" in rest and rest[rest.index("--drafter") + 1:][:1] not in ([], ["none"]):
+                _, text = c.get("/metrics")
+                n = next((float(ln.split()[1]) for ln in str(text).splitlines() if ln.startswith("ferrite_engine_drafted ")), 0.0)
+                steps.append(("spec", n > 0, f"ferrite_engine_drafted = {n}"))
             ranks = rank_pids(child.pid)
             text = tail(log.name, 10 ** 6)
             ok = child.poll() is None and len(ranks) >= a.gpus - (1 if a.gpus == 1 else 0) and "Traceback" not in text

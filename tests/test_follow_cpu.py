@@ -77,3 +77,80 @@ def test_follower_replays_the_leaders_calls():
     assert not isinstance(outs[1], str), outs[1]
     assert outs[0] == want
     assert outs[1] > 10          # calls replayed by the follower
+
+
+# ---- a draft model under tensor parallelism: mirrored at the Drafter interface ------------------------------------
+def _spec_cfg():
+    cfg = tiny_hybrid()
+    cfg.tap_layers = sorted({max(0, cfg.n_layers * (i + 1) // 4 - 1) for i in range(3)})
+    return cfg
+
+
+def _spec_run(eng, tp=None, tree=False):
+    from ferrite_b200.models.drafter import BlockDrafter, drafter_config_for
+    cfg = eng.full_cfg
+    drafter = BlockDrafter(drafter_config_for(cfg), target_hidden=cfg.hidden, n_taps=len(cfg.tap_layers), n_slots=2,
+                           max_ctx=256, device="cpu", block=8, tp=tp)
+    if tp is not None and tp.rank != 0:
+        from ferrite_b200.engine.follow import follow
+        return follow(eng, tp, drafter)
+    if tp is not None:
+        from ferrite_b200.engine.follow import Leader
+        eng = Leader(eng, tp)
+        drafter = eng.attach_drafter(drafter)
+    sched = Scheduler(eng, SchedOptions(spec=4, tree_rows=6 if tree else 0), drafter=drafter)
+    out = []
+    for p in _prompts(cfg):
+        out.append(generate(sched, [p], Sampling(max_tokens=12))[0])
+    stats = (sched.stats["drafted"], sched.stats["accepted"])
+    if tp is not None:
+        eng.stop_followers()
+    return out, stats
+
+
+def _spec_worker(rank, world, port, q, tree):
+    try:
+        os.environ["MASTER_ADDR"] = "127.0.0.1"
+        os.environ["MASTER_PORT"] = str(port)
+        dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=60))
+        from ferrite_b200.parallel.tp import TensorParallel
+        tp = TensorParallel(dist.group.WORLD, "cpu", fused=False)
+        cfg = _spec_cfg()
+        eng = Engine(cfg, init_weights(cfg, seed=0), EngineConfig(n_slots=2, max_ctx=256, prefill_chunk=64), device="cpu", tp=tp)
+        q.put((rank, _spec_run(eng, tp, tree)))
+        dist.destroy_process_group()
+    except Exception as e:  # noqa: BLE001
+        import traceback
+        q.put((rank, "ERR " + repr(e) + traceback.format_exc()[-1200:]))
+
+
+def _spec_case(tree):
+    cfg = _spec_cfg()
+    mk = lambda: Engine(cfg, init_weights(cfg, seed=0), EngineConfig(n_slots=2, max_ctx=256, prefill_chunk=64), device="cpu")
+    plain = _run(mk())
+    want, want_stats = _spec_run(mk(), None, tree)
+    assert want == plain                      # speculation does not change greedy output
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_spec_worker, args=(r, 2, port, q, tree)) for r in range(2)]
+    for p in procs:
+        p.start()
+    outs = dict(q.get(timeout=240) for _ in range(2))
+    for p in procs:
+        p.join(timeout=60)
+    assert not isinstance(outs[0], str), outs[0]
+    assert not isinstance(outs[1], str), outs[1]
+    got, stats = outs[0]
+    assert got == want
+    # the sharded drafter drafts what the whole one drafts: same proposals, same acceptance
+    assert stats == want_stats and stats[0] > 0
+    assert outs[1] > 20                       # engine and drafter calls replayed by the follower
+
+
+def test_block_drafter_is_mirrored_under_tensor_parallelism():
+    _spec_case(tree=False)
+
+
+def test_block_drafter_tree_is_mirrored_under_tensor_parallelism():
+    _spec_case(tree=True)

@@ -5,6 +5,7 @@ import socket
 import threading
 import time
 
+import pytest
 from aiohttp import web
 
 from ferrite_b200.server.app import AppState, make_app
@@ -252,14 +253,15 @@ def test_control_tool_and_environment_check(tmp_path, monkeypatch, capsys):
     assert check_env.check(gpus=2)["errors"]                      # no GPU on the test machine: asking for two is an error
 
 
-def test_tp_gate_with_two_cpu_ranks(capsys):
+@pytest.mark.parametrize("drafter", ["none", "block"])
+def test_tp_gate_with_two_cpu_ranks(capsys, drafter):
     """The tensor-parallel server gate end to end on two gloo ranks: start, concurrent lanes equal to solo runs, repeat,
-    ranks alive, stop."""
+    ranks alive, stop; with a block drafter, mirrored on both ranks, speculation must have run too."""
     from ferrite_b200.tools.tp_gate import main
     rc = main(["--gpus", "2", "--lanes", "1,2", "--prefix-tokens", "60", "--start-timeout", "180", "--",
-               "--preset", "tiny", "--device", "cpu", "--slots", "2", "--max-model-len", "1024"])
+               "--preset", "tiny", "--device", "cpu", "--slots", "2", "--max-model-len", "2048", "--drafter", drafter])
     out = capsys.readouterr().out
-    assert rc == 0 and out.count("PASS") == 6 and "tp gate: PASS" in out, out
+    assert rc == 0 and out.count("PASS") == (6 if drafter == "none" else 7) and "tp gate: PASS" in out, out
 
 
 def test_check_model_reports_missing_tensors_and_changed_files(tmp_path, capsys):
