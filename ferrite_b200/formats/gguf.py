@@ -162,7 +162,28 @@ def _scale_min_k4(sc: np.ndarray):
     return s, m
 
 
-_NATIVE_TYPES = ("Q8_0", "Q4_0", "Q4_K", "Q5_K", "Q6_K")
+_NATIVE_TYPES = ("Q8_0", "Q4_0", "Q4_1", "Q5_0", "Q5_1", "Q2_K", "Q3_K", "Q4_K", "Q5_K", "Q6_K", "IQ4_NL", "IQ4_XS",
+                 "IQ2_XXS", "IQ2_XS", "IQ2_S", "IQ3_XXS", "IQ3_S", "IQ1_S", "IQ1_M")
+_NATIVE_GRID = {"IQ2_XXS": "iq2xxs", "IQ2_XS": "iq2xs", "IQ2_S": "iq2s", "IQ3_XXS": "iq3xxs", "IQ3_S": "iq3s", "IQ1_S": "iq1s",
+                "IQ1_M": "iq1s"}
+_native_tables: Dict[str, Any] = {}
+
+
+def _native_args(name: str):
+    """The tables a C++ decoder wants beside the bytes (codebook, sign masks, 4-bit levels), as tensors made once."""
+    import torch
+    if name in ("IQ4_NL", "IQ4_XS"):
+        if "kvalues" not in _native_tables:
+            _native_tables["kvalues"] = torch.from_numpy(KVALUES_IQ4NL.copy())
+        return _native_tables["kvalues"], None
+    key = _NATIVE_GRID.get(name)
+    if key is None:
+        return None, None
+    if key not in _native_tables:
+        from .gguf_tables import GRID, KSIGNS
+        _native_tables[key] = torch.from_numpy(np.ascontiguousarray(GRID[key], dtype=np.int8))
+        _native_tables.setdefault("ksigns", torch.from_numpy(np.ascontiguousarray(KSIGNS, dtype=np.uint8)))
+    return _native_tables[key], _native_tables["ksigns"]
 
 
 def dequantize(raw: np.ndarray, type_id: int) -> np.ndarray:
@@ -176,13 +197,17 @@ def dequantize(raw: np.ndarray, type_id: int) -> np.ndarray:
     if name in ("I8", "I16", "I32", "I64", "F64"):
         return raw.view({"I8": np.int8, "I16": np.int16, "I32": np.int32, "I64": np.int64, "F64": np.float64}[name]).astype(np.float32)
     if name in _NATIVE_TYPES:
-        # the common dense formats decode in C++ (`csrc/host_gguf.cpp`) when the extension is built: the same bits as
-        # the statements below, without their temporaries
+        # block formats decode in C++ (`csrc/host_gguf.cpp`) when the extension is built: the same bits as the statements
+        # below, without their temporaries, the blocks spread over the host's cores
         from .._ext import host
         h = host()
         if h is not None and hasattr(h, "gguf_dequant_host"):
             import torch
-            return h.gguf_dequant_host(torch.from_numpy(np.ascontiguousarray(raw).reshape(-1).view(np.uint8).copy()), name).numpy()
+            grid, ksigns = _native_args(name)
+            flat = np.ascontiguousarray(raw).reshape(-1).view(np.uint8)
+            if not flat.flags.writeable:
+                flat = flat.copy()                           # torch wants a writable buffer (a read-only mmap is not one)
+            return h.gguf_dequant_host(torch.from_numpy(flat), name, grid, ksigns).numpy()
     b = raw.reshape(-1, bb)
     nb = b.shape[0]
     if name == "Q8_0":

@@ -340,8 +340,8 @@ def test_gguf_checkpoint_round_trip_into_the_engine(tmp_path, moe):
 
 
 def test_native_gguf_decoders_are_bit_exact(monkeypatch):
-    """The C++ decoders of the common dense GGUF formats against the NumPy statements: every bit, over random blocks
-    (subnormal and non-finite scales included) and over blocks made by the writers."""
+    """The C++ decoders (legacy, K, non-linear 4-bit and codebook formats) against the NumPy statements: every bit, over
+    random blocks (subnormal and non-finite scales included) and over blocks made by the writers."""
     import numpy as np
 
     from ferrite_b200 import _ext
