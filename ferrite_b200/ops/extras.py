@@ -183,6 +183,38 @@ class TorchExtras:
         """xc[r] = sum_j pre[r, j] h[r, j] (bf16)."""
         return (h.float() * pre.float()[:, :h.shape[1], None]).sum(1).to(torch.bfloat16)
 
+    def block_ring_attention(self, q, ring, kvb, meta, sink, scale, rope_tab, window, block, rope_dims=64):
+        """Attention of a block drafter whose keys are their own values (one latent row per position, shared by all
+        heads). Row r, described by meta[r] = (slot, pos, wend, b0), sees
+          * the slot's ring rows of positions max(0, wend - window) .. wend - 1 (position p lives in ring row
+            p % ring.shape[1]), and
+          * the `block` rows kvb[b0 : b0 + block] of its own draft block, all of them (no mask inside the block);
+        the head's sink logit joins the softmax denominator only. The result is rounded to bf16 and its last `rope_dims`
+        elements are rotated back by the row's position (inverse of the interleaved-pair rotation the latent rows
+        carry; rope_tab [positions, rope_dims] holds (cos, sin) pairs). q [rows, heads, D], ring [slots, ring_len, D],
+        kvb [n, D], sink [heads] -> [rows, heads, D] fp32. Statement only: no kernel of this repo's presets needs it
+        (reference `dspark_attn`, `kernels/k-dspark/src/lib.rs:276-402`)."""
+        rows, heads, D = q.shape
+        ring_len = ring.shape[1]
+        out = torch.zeros(rows, heads, D, dtype=torch.float32, device=q.device)
+        for r in range(rows):
+            slot, pos, wend, b0 = (int(v) for v in meta[r].tolist())
+            first = max(0, wend - window)
+            idx = torch.tensor([p % ring_len for p in range(first, wend)], dtype=torch.long, device=q.device)
+            keys = torch.cat([ring[slot].index_select(0, idx), kvb[b0:b0 + block]], 0).float()        # [n, D]
+            s = (q[r].float() @ keys.t()) * scale                                                     # [heads, n]
+            m = torch.maximum(s.max(-1).values, sink.float())
+            p = torch.exp(s - m[:, None])
+            den = p.sum(-1) + torch.exp(sink.float() - m)
+            o = ((p @ keys) / den[:, None]).to(torch.bfloat16).float()
+            cs = rope_tab[pos, 0::2].float()
+            sn = rope_tab[pos, 1::2].float()
+            a, b = o[:, D - rope_dims::2].clone(), o[:, D - rope_dims + 1::2].clone()
+            o[:, D - rope_dims::2] = a * cs + b * sn
+            o[:, D - rope_dims + 1::2] = b * cs - a * sn
+            out[r] = o
+        return out
+
 
 class CudaExtras:
     """Kernel-backed forms; `self.C` is the extension, `self.status_word` the device status word, `self.device` the GPU."""

@@ -117,3 +117,44 @@ def test_engram_gate_partials_match_summed_form():
     assert torch.allclose(sm.float(), h.float().mean(1), atol=2e-2)
     pre = torch.rand(rows, hc, generator=g)
     assert torch.allclose(OPS.stream_collapse(h, pre).float(), (h.float() * pre[..., None]).sum(1), atol=3e-2)
+
+
+def test_block_ring_attention_window_block_sink_and_inverse_rope():
+    """The block drafter's ring attention: the window is read through the ring (positions modulo its length), the block's
+    keys are all visible, the sink only weakens the result, and the tail of the output is rotated back by the position."""
+    from ferrite_b200.ops.torch_ops import TorchOps
+    ops = TorchOps(torch.device("cpu"), torch.float32)
+    g = torch.Generator().manual_seed(5)
+    heads, D, ring_len, window, block, rd = 3, 96, 8, 5, 4, 32
+    ring = torch.randn(2, ring_len, D, generator=g)
+    kvb = torch.randn(2 * block, D, generator=g)
+    q = torch.randn(2, heads, D, generator=g)
+    # row 0: slot 1, 11 tokens absorbed (the ring wrapped once), its block is the second one; row 1: a fresh slot
+    meta = torch.tensor([[1, 11, 11, block], [0, 0, 0, 0]], dtype=torch.int32)
+    inv = 1.0 / (10000.0 ** (torch.arange(rd // 2).float() / (rd // 2)))
+    ang = torch.arange(16).float()[:, None] * inv[None]
+    tab = torch.stack([ang.cos(), ang.sin()], -1).reshape(16, rd)
+    no_sink = torch.full((heads,), -1e30)
+    got = ops.block_ring_attention(q, ring, kvb, meta, no_sink, 0.1, tab, window, block, rope_dims=rd)
+    # by hand, row 0: positions 6..10 live in ring rows 6, 7, 0, 1, 2
+    keys = torch.cat([ring[1, [6, 7, 0, 1, 2]], kvb[block:2 * block]], 0)
+    want = torch.softmax((q[0] @ keys.t()) * 0.1, -1) @ keys
+    want = want.to(torch.bfloat16).float()
+    head, tail = want[:, :D - rd], want[:, D - rd:].reshape(heads, rd // 2, 2)
+    cs, sn = ang[11].cos(), ang[11].sin()
+    back = torch.stack([tail[..., 0] * cs + tail[..., 1] * sn, tail[..., 1] * cs - tail[..., 0] * sn], -1).reshape(heads, rd)
+    assert torch.allclose(got[0], torch.cat([head, back], -1), atol=1e-6)
+    # the inverse rotation undoes the forward one: rotate forward again and the plain attention output is back
+    t = got[0][:, D - rd:].reshape(heads, rd // 2, 2)
+    fwd = torch.stack([t[..., 0] * cs - t[..., 1] * sn, t[..., 0] * sn + t[..., 1] * cs], -1).reshape(heads, rd)
+    assert torch.allclose(fwd, want[:, D - rd:], atol=1e-5)
+    # row 1 has no window at all: only its block's keys, position 0 leaves the tail as it is
+    w1 = (torch.softmax((q[1] @ kvb[:block].t()) * 0.1, -1) @ kvb[:block]).to(torch.bfloat16).float()
+    assert torch.allclose(got[1], w1, atol=1e-6)
+    # a sink as large as the best logit takes its share of the denominator: same direction, smaller norm
+    s0 = ((q[0] @ keys.t()) * 0.1).max(-1).values
+    sunk = ops.block_ring_attention(q, ring, kvb, meta, s0, 0.1, tab, window, block, rope_dims=rd)
+    ratio = sunk[0].norm(dim=-1) / got[0].norm(dim=-1)
+    assert bool((ratio < 0.95).all()) and bool((ratio > 0.05).all())
+    cosine = torch.nn.functional.cosine_similarity(sunk[0], got[0], dim=-1)
+    assert bool((cosine > 0.99).all())
