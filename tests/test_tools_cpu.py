@@ -2,6 +2,7 @@
 import asyncio
 import json
 import socket
+import sys
 import threading
 import time
 
@@ -319,3 +320,39 @@ def test_chart_writes_an_svg_from_json_lines(tmp_path):
     root = ET.fromstring(out.read_text())
     tags = [e.tag.split("}")[-1] for e in root.iter()]
     assert tags.count("polyline") == 2 and tags.count("circle") == 7
+
+
+def test_package_builds_an_archive_and_refuses_machine_traces(tmp_path):
+    """The release packer on a small stand-in tree: archive + checksum + BUILD-INFO with per-file hashes; a private
+    network address in a packed text file stops the release and names the line."""
+    import hashlib
+    import tarfile
+
+    from ferrite_b200.tools import package as P
+    root = tmp_path / "repo"
+    (root / "ferrite_b200" / "csrc").mkdir(parents=True)
+    (root / "ferrite_b200" / "__pycache__").mkdir()
+    (root / "profiles").mkdir()
+    (root / "tests").mkdir()
+    (root / "ferrite_b200" / "__init__.py").write_text('__version__ = "9.9.9"\n')
+    (root / "ferrite_b200" / "_C.so").write_bytes(b"\x7fELF stand-in")
+    (root / "ferrite_b200" / "csrc" / "k.cu").write_text("__global__ void k() {}\n")
+    (root / "ferrite_b200" / "__pycache__" / "x.pyc").write_bytes(b"junk")
+    (root / "bench.py").write_text("print('bench')\n")
+    (root / "README.md").write_text("connect to 127.0.0.1:8000\n")
+    path, info = P.package(str(root), str(tmp_path / "dist"), build=False, allow=[r"127\.0\.0\.1"])
+    name = "ferrite-b200-9.9.9-sm100a"
+    assert path.endswith(name + ".tar.gz")
+    with tarfile.open(path) as tar:
+        names = sorted(tar.getnames())
+        build = json.loads(tar.extractfile(f"{name}/BUILD-INFO").read())
+    assert f"{name}/ferrite_b200/_C.so" in names and f"{name}/ferrite_b200/csrc/k.cu" in names and f"{name}/bench.py" in names
+    assert not any("__pycache__" in n for n in names)
+    assert build["files"]["bench.py"] == hashlib.sha256(b"print('bench')\n").hexdigest()
+    digest, fname = open(path + ".sha256").read().split()
+    assert fname == name + ".tar.gz" and digest == hashlib.sha256(open(path, "rb").read()).hexdigest()
+    (root / "README.md").write_text("line one\nour box is 192.168.7.20, ask there\n")
+    with pytest.raises(SystemExit) as e:
+        P.package(str(root), str(tmp_path / "dist2"), build=False, allow=[r"127\.0\.0\.1"])
+    assert "README.md:2" in str(e.value) and "192.168.7.20" in str(e.value)
+    assert not (tmp_path / "dist2").exists()
