@@ -397,6 +397,7 @@ void register_ext(pybind11::module_& m);
 void register_host(pybind11::module_& m);
 void register_oracle(pybind11::module_& m);
 void register_gguf_host(pybind11::module_& m);
+void register_sampler_host(pybind11::module_& m);
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("embed", &embed);
@@ -434,4 +435,5 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   register_host(m);
   register_oracle(m);
   register_gguf_host(m);
+  register_sampler_host(m);
 }

@@ -84,8 +84,20 @@ def penalize(logits: torch.Tensor, counts: Dict[int, int], s: Sampling, seen: Op
     return out
 
 
+def _native():
+    """The C++ sampler (`csrc/host_sampler.cpp`) when the extension is built, else None."""
+    from .._ext import host
+    h = host()
+    return h if h is not None and hasattr(h, "sample_probs") else None
+
+
 def dist(logits: torch.Tensor, s: Sampling, banned: Sequence[int] = ()) -> torch.Tensor:
-    """Probability vector after temperature, top-k, top-p and min-p (top-p is applied inside the top-k set)."""
+    """Probability vector after temperature, top-k, top-p and min-p (top-p is applied inside the top-k set). Runs in C++
+    when the extension is built (no full sort of the vocabulary); the statements below are its definition."""
+    h = _native()
+    if h is not None and logits.device.type == "cpu":
+        return h.sample_probs(logits.float().contiguous(), float(s.temperature), int(s.top_k or 0), float(s.top_p),
+                              float(s.min_p), [int(b) for b in banned])
     lf = logits.float().clone()
     if len(banned):
         lf[torch.tensor(list(banned), dtype=torch.long)] = float("-inf")
@@ -109,6 +121,9 @@ def dist(logits: torch.Tensor, s: Sampling, banned: Sequence[int] = ()) -> torch
 
 def draw(p: torch.Tensor, rng: SplitMix64) -> int:
     """Inverse-CDF draw in index order (deterministic for a seed)."""
+    h = _native()
+    if h is not None and p.device.type == "cpu" and p.dtype == torch.float32:
+        return int(h.sample_draw(p.contiguous(), rng.uniform(), -1))
     u = rng.uniform() * float(p.sum())
     c = torch.cumsum(p.double(), 0)
     i = int(torch.searchsorted(c, torch.tensor(u, dtype=torch.float64), right=True))
@@ -116,6 +131,12 @@ def draw(p: torch.Tensor, rng: SplitMix64) -> int:
 
 
 def draw_excluding(p: torch.Tensor, rng: SplitMix64, excluded: int) -> int:
+    h = _native()
+    if h is not None and p.device.type == "cpu" and p.dtype == torch.float32:
+        # the generator advances only when there is something else to draw, as below
+        if not (float(p.sum()) - float(p[excluded]) > 0):
+            return excluded
+        return int(h.sample_draw(p.contiguous(), rng.uniform(), int(excluded)))
     q = p.clone()
     q[excluded] = 0
     if float(q.sum()) <= 0:

@@ -3,6 +3,7 @@ proposals, verify-tree walk / growth / grafting and the stop scanner must agree 
 import random
 
 import pytest
+import torch
 
 from ferrite_b200 import _ext
 
@@ -123,3 +124,79 @@ def test_step_metadata_block_matches_python(monkeypatch):
             R = ex._R
             for blk in range(6):
                 assert torch.equal(t1[blk * R:blk * R + (2 * T if blk == 0 else T)], t2[blk * R:blk * R + (2 * T if blk == 0 else T)]), blk
+
+
+def test_native_sampler_matches_the_python_statements(monkeypatch):
+    """The C++ sampler against the PyTorch statements of `engine/sampler.py`: the same support and probabilities over
+    peaked and flat rows under every filter, the same draws for the same uniforms (boundary cases aside), the draft
+    acceptance walk token for token on a seeded run, and a large-vocabulary row several times faster."""
+    import time
+
+    from ferrite_b200 import _ext
+    from ferrite_b200.engine import sampler as S
+    h = _ext.host()
+    if h is None or not hasattr(h, "sample_probs"):
+        pytest.skip("extension not built")
+    g = torch.Generator().manual_seed(0)
+    settings = [S.Sampling(temperature=0.8), S.Sampling(temperature=1.0, top_k=20), S.Sampling(temperature=0.7, top_p=0.9),
+                S.Sampling(temperature=1.3, top_k=50, top_p=0.8, min_p=0.05), S.Sampling(temperature=1.0, min_p=0.2),
+                S.Sampling(temperature=0.6, top_p=0.3)]
+    same_draws = total_draws = 0
+    for scale in (0.5, 3.0, 12.0):                      # flat, ordinary and peaked rows
+        for s in settings:
+            logits = torch.randn(5000, generator=g) * scale
+            banned = [int(logits.argmax())] if s.top_k else []
+            monkeypatch.delenv("FERRITE_NO_NATIVE_HOST", raising=False)
+            got = S.dist(logits, s, banned)
+            monkeypatch.setenv("FERRITE_NO_NATIVE_HOST", "1")
+            want = S.dist(logits, s, banned)
+            assert torch.equal(got > 0, want > 0), (scale, s)
+            assert torch.allclose(got, want, atol=1e-6, rtol=1e-4)
+            assert abs(float(got.sum()) - 1.0) < 1e-5
+            for k in range(50):
+                seed = 1000 * k + 7
+                monkeypatch.delenv("FERRITE_NO_NATIVE_HOST", raising=False)
+                a = S.draw(got, S.SplitMix64(seed))
+                a_ex = S.draw_excluding(got, S.SplitMix64(seed), int(got.argmax()))
+                monkeypatch.setenv("FERRITE_NO_NATIVE_HOST", "1")
+                b = S.draw(want, S.SplitMix64(seed))
+                b_ex = S.draw_excluding(want, S.SplitMix64(seed), int(want.argmax()))
+                assert float(got[a]) > 0 and a_ex != int(got.argmax()) or float(got.max()) == 1.0
+                same_draws += int(a == b) + int(a_ex == b_ex)
+                total_draws += 2
+    assert same_draws >= 0.995 * total_draws, (same_draws, total_draws)
+    # a point mass: nothing else to draw, the excluded token comes back and the generator does not advance
+    one = torch.zeros(100)
+    one[17] = 1.0
+    monkeypatch.delenv("FERRITE_NO_NATIVE_HOST", raising=False)
+    rng = S.SplitMix64(5)
+    assert S.draw_excluding(one, rng, 17) == 17 and rng.s == 5
+    assert S.draw(one, rng) == 17
+    # the acceptance walk over drafts, seeded: native and Python walk the same tokens
+    logits_rows = torch.randn(5, 3000, generator=g) * 4
+    drafts = [int(logits_rows[i].argmax()) for i in range(4)]
+    outs = []
+    for native in (True, False):
+        if native:
+            monkeypatch.delenv("FERRITE_NO_NATIVE_HOST", raising=False)
+        else:
+            monkeypatch.setenv("FERRITE_NO_NATIVE_HOST", "1")
+        smp = S.Sampler(S.Sampling(temperature=0.9, top_p=0.95, seed=11, presence_penalty=0.3))
+        outs.append(smp.spec_accept(logits_rows, drafts))
+    assert outs[0] == outs[1] and len(outs[0]) >= 1
+    # cost on a vocabulary-sized peaked row
+    big = torch.randn(248320, generator=g) * 6
+    s = S.Sampling(temperature=0.8, top_k=0, top_p=0.9)
+    times = []
+    for native in (True, False):
+        if native:
+            monkeypatch.delenv("FERRITE_NO_NATIVE_HOST", raising=False)
+        else:
+            monkeypatch.setenv("FERRITE_NO_NATIVE_HOST", "1")
+        S.draw(S.dist(big, s), S.SplitMix64(1))
+        t0 = time.perf_counter()
+        for k in range(5):
+            S.draw(S.dist(big, s), S.SplitMix64(k))
+        times.append((time.perf_counter() - t0) / 5)
+    print(f"host sampler, 248K row, top-p: native {times[0] * 1e3:.2f} ms, PyTorch statements {times[1] * 1e3:.2f} ms")
+    assert times[0] < times[1]
