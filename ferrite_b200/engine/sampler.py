@@ -61,14 +61,18 @@ class Sampling:
         return self.temperature <= 0.0 and not self.penalised
 
 
-def penalize(logits: torch.Tensor, counts: Dict[int, int], s: Sampling, seen: Optional[Sequence[int]] = None) -> torch.Tensor:
+def penalize(logits: torch.Tensor, counts: Dict[int, int], s: Sampling, seen: Optional[Sequence[int]] = None,
+             rep_mask: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Presence and frequency penalties over the tokens generated so far (counts: id -> occurrences); the repetition
     penalty over the union of the prompt's tokens (`seen`) and the generated ones, as in the reference (`penalize`,
-    `crates/fe-model/src/sched.rs:2158`)."""
+    `crates/fe-model/src/sched.rs:2158`). `rep_mask` (bool [vocab]) is that union kept up to date by the caller: with it
+    a 100K-token prompt costs one vectorised pass per token instead of a set union."""
     if not s.penalised:
         return logits
     out = logits.clone()
-    if s.repetition_penalty != 1.0 and s.repetition_penalty > 0:
+    if s.repetition_penalty != 1.0 and s.repetition_penalty > 0 and rep_mask is not None:
+        out = torch.where(rep_mask, torch.where(out > 0, out / s.repetition_penalty, out * s.repetition_penalty), out)
+    elif s.repetition_penalty != 1.0 and s.repetition_penalty > 0:
         rep = set(counts.keys())
         if seen:
             rep.update(int(t) for t in seen)
@@ -151,17 +155,30 @@ class Sampler:
         self.counts: Dict[int, int] = {}
         # prompt tokens count for the repetition penalty only
         self.seen = frozenset(int(t) for t in prompt) if (prompt is not None and s.repetition_penalty != 1.0) else None
+        self.rep_mask: Optional[torch.Tensor] = None     # prompt and generated ids, built at the first penalised row
 
     def observe(self, tok: int) -> None:
         self.counts[tok] = self.counts.get(tok, 0) + 1
+        if self.rep_mask is not None and 0 <= tok < self.rep_mask.numel():
+            self.rep_mask[tok] = True
+
+    def _penalized(self, logits: torch.Tensor) -> torch.Tensor:
+        lf = logits.float().cpu()
+        if self.s.repetition_penalty != 1.0 and self.s.repetition_penalty > 0:
+            if self.rep_mask is None or self.rep_mask.numel() != lf.numel():
+                ids = set(self.counts.keys()) | (set(self.seen) if self.seen else set())
+                self.rep_mask = torch.zeros(lf.numel(), dtype=torch.bool)
+                ids = [t for t in ids if 0 <= t < lf.numel()]
+                if ids:
+                    self.rep_mask[torch.tensor(ids, dtype=torch.long)] = True
+        return penalize(lf, self.counts, self.s, self.seen, self.rep_mask)
 
     def probs(self, logits: torch.Tensor, first: bool = False) -> torch.Tensor:
-        return dist(penalize(logits.float().cpu(), self.counts, self.s, self.seen), self.s,
-                    self.s.banned_first if first else ())
+        return dist(self._penalized(logits), self.s, self.s.banned_first if first else ())
 
     def sample(self, logits: torch.Tensor, first: bool = False) -> int:
         if self.s.argmax:
-            lf = penalize(logits.float().cpu(), self.counts, self.s, self.seen)
+            lf = self._penalized(logits)
             if first and self.s.banned_first:
                 lf = lf.clone()
                 lf[torch.tensor(self.s.banned_first, dtype=torch.long)] = float("-inf")

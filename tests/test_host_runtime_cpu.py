@@ -200,3 +200,18 @@ def test_native_sampler_matches_the_python_statements(monkeypatch):
         times.append((time.perf_counter() - t0) / 5)
     print(f"host sampler, 248K row, top-p: native {times[0] * 1e3:.2f} ms, PyTorch statements {times[1] * 1e3:.2f} ms")
     assert times[0] < times[1]
+
+
+def test_repetition_mask_equals_the_set_union():
+    """The sampler's incremental mask of prompt and generated ids gives the logits of the set-union statement."""
+    from ferrite_b200.engine import sampler as S
+    g = torch.Generator().manual_seed(4)
+    prompt = torch.randint(0, 500, (300,), generator=g).tolist()
+    s = S.Sampling(temperature=0.0, repetition_penalty=1.3, presence_penalty=0.2, frequency_penalty=0.1)
+    smp = S.Sampler(s, prompt=prompt)
+    for step in range(20):
+        logits = torch.randn(500, generator=g) * 3
+        want = S.penalize(logits.float(), smp.counts, s, smp.seen)
+        got = smp._penalized(logits)
+        assert torch.equal(got, want), step
+        smp.observe(int(torch.randint(0, 500, (1,), generator=g)))
