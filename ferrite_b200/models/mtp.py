@@ -60,15 +60,21 @@ class MtpDrafter(Drafter):
             weights["mtp.pre_h"] = torch.zeros(cfg.hidden, device=dev, dtype=dt)
         weights = dict(weights)
         tw = target.ex.w
-        weights["embed"] = tw["embed"]                       # shared with the target: the same storage
-        if not cfg.tie_embeddings:
+        tp = getattr(target, "tp", None)
+        sharded = tp is not None and tp.world > 1
+        weights["embed"] = tw["embed"]                       # shared with the target: the same storage (replicated)
+        if not cfg.tie_embeddings and not sharded:
             weights["lm_head"] = tw["lm_head"]
         self.fc = weights.pop("mtp.fc")
         self.pre_e = weights.pop("mtp.pre_e")
         self.pre_h = weights.pop("mtp.pre_h")
         self.tnorm = tw["final_norm"]
+        # under tensor parallelism the head's own layer is cut like the target's layers (every rank builds it from the same
+        # full weights); the target's output matrix is already this rank's vocabulary rows, so it goes in after the cut
         self.eng = Engine(cfg, weights, EngineConfig(n_slots=n_slots, max_ctx=max_ctx, use_graphs=False), device=str(dev),
-                          seed=seed)
+                          seed=seed, tp=tp if sharded else None)
+        if not cfg.tie_embeddings and sharded:
+            self.eng.ex.w["lm_head"] = tw["lm_head"]
         self.eng.ex.input_rows = True
         self.cfg = cfg
         self.base: List[Optional[int]] = [None] * n_slots    # target position of the head's cache row 0

@@ -36,9 +36,6 @@ def build_engine(args, tok):
             cfg = scaled(cfg, args.layers)
     world = int(os.environ.get("WORLD_SIZE", "1"))
     kind = getattr(args, "drafter", "none")
-    if kind == "mtp" and world > 1:
-        raise SystemExit("--drafter mtp runs on one GPU only (the head shares the target's embedding and output storage); "
-                         "use --drafter block under tensor parallelism")
     if kind != "none":
         # the drafters read hidden rows of the target: the MTP head the last layer's, the block drafter three evenly
         # spaced ones (the preset's own tap list when it has one)
@@ -90,8 +87,8 @@ def build_engine(args, tok):
     drafter = None
     if kind != "none":
         # speculative decoding with a draft model (reference: the drafter `factory`, `crates/fe-dflash/src/lib.rs:1381`,
-        # and the MTP head of the checkpoint). Under tensor parallelism every rank builds the block drafter over its
-        # shard of the draft engine and the leader mirrors the drafter's calls (reference: DFlash2 at TP2)
+        # and the MTP head of the checkpoint). Under tensor parallelism every rank builds the drafter over its shard of
+        # the draft engine and the leader mirrors the drafter's calls (reference: DFlash2 at TP2)
         if kind == "mtp":
             from ..models.mtp import MtpDrafter
             drafter = MtpDrafter(eng, n_slots=args.slots, max_ctx=args.max_model_len, depth=max(1, min(opts.spec or 4, 8)))

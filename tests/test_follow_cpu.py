@@ -80,17 +80,25 @@ def test_follower_replays_the_leaders_calls():
 
 
 # ---- a draft model under tensor parallelism: mirrored at the Drafter interface ------------------------------------
-def _spec_cfg():
+def _spec_cfg(kind="block"):
     cfg = tiny_hybrid()
-    cfg.tap_layers = sorted({max(0, cfg.n_layers * (i + 1) // 4 - 1) for i in range(3)})
+    if kind == "mtp":
+        cfg.tap_layers = [cfg.n_layers - 1]
+        cfg.tie_embeddings = False            # the head then borrows the target's output matrix: one vocabulary shard per rank
+    else:
+        cfg.tap_layers = sorted({max(0, cfg.n_layers * (i + 1) // 4 - 1) for i in range(3)})
     return cfg
 
 
-def _spec_run(eng, tp=None, tree=False):
+def _spec_run(eng, tp=None, tree=False, kind="block"):
     from ferrite_b200.models.drafter import BlockDrafter, drafter_config_for
     cfg = eng.full_cfg
-    drafter = BlockDrafter(drafter_config_for(cfg), target_hidden=cfg.hidden, n_taps=len(cfg.tap_layers), n_slots=2,
-                           max_ctx=256, device="cpu", block=8, tp=tp)
+    if kind == "mtp":
+        from ferrite_b200.models.mtp import MtpDrafter
+        drafter = MtpDrafter(eng, n_slots=2, max_ctx=256, depth=4)
+    else:
+        drafter = BlockDrafter(drafter_config_for(cfg), target_hidden=cfg.hidden, n_taps=len(cfg.tap_layers), n_slots=2,
+                               max_ctx=256, device="cpu", block=8, tp=tp)
     if tp is not None and tp.rank != 0:
         from ferrite_b200.engine.follow import follow
         return follow(eng, tp, drafter)
@@ -108,32 +116,32 @@ def _spec_run(eng, tp=None, tree=False):
     return out, stats
 
 
-def _spec_worker(rank, world, port, q, tree):
+def _spec_worker(rank, world, port, q, tree, kind="block"):
     try:
         os.environ["MASTER_ADDR"] = "127.0.0.1"
         os.environ["MASTER_PORT"] = str(port)
         dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=60))
         from ferrite_b200.parallel.tp import TensorParallel
         tp = TensorParallel(dist.group.WORLD, "cpu", fused=False)
-        cfg = _spec_cfg()
+        cfg = _spec_cfg(kind)
         eng = Engine(cfg, init_weights(cfg, seed=0), EngineConfig(n_slots=2, max_ctx=256, prefill_chunk=64), device="cpu", tp=tp)
-        q.put((rank, _spec_run(eng, tp, tree)))
+        q.put((rank, _spec_run(eng, tp, tree, kind)))
         dist.destroy_process_group()
     except Exception as e:  # noqa: BLE001
         import traceback
         q.put((rank, "ERR " + repr(e) + traceback.format_exc()[-1200:]))
 
 
-def _spec_case(tree):
-    cfg = _spec_cfg()
+def _spec_case(tree, kind="block"):
+    cfg = _spec_cfg(kind)
     mk = lambda: Engine(cfg, init_weights(cfg, seed=0), EngineConfig(n_slots=2, max_ctx=256, prefill_chunk=64), device="cpu")
     plain = _run(mk())
-    want, want_stats = _spec_run(mk(), None, tree)
+    want, want_stats = _spec_run(mk(), None, tree, kind)
     assert want == plain                      # speculation does not change greedy output
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_spec_worker, args=(r, 2, port, q, tree)) for r in range(2)]
+    procs = [ctx.Process(target=_spec_worker, args=(r, 2, port, q, tree, kind)) for r in range(2)]
     for p in procs:
         p.start()
     outs = dict(q.get(timeout=240) for _ in range(2))
@@ -154,3 +162,7 @@ def test_block_drafter_is_mirrored_under_tensor_parallelism():
 
 def test_block_drafter_tree_is_mirrored_under_tensor_parallelism():
     _spec_case(tree=True)
+
+
+def test_mtp_head_is_mirrored_under_tensor_parallelism():
+    _spec_case(tree=False, kind="mtp")
