@@ -128,6 +128,23 @@ class DrafterLeader:
         self._l._send("drafter.draft_tree", (int(slot), int(last_token), int(pos), int(depth), int(rows)), {})
         return self._d.draft_tree(slot, last_token, pos, taps, depth, rows)
 
+    def draft_many(self, reqs, taps):
+        reqs = [tuple(int(v) for v in r) for r in reqs]
+        self._l._send("drafter.draft_many", (reqs,), {})
+        return self._d.draft_many(reqs, taps)
+
+    def draft_tree_many(self, reqs, taps):
+        reqs = [tuple(int(v) for v in r) for r in reqs]
+        self._l._send("drafter.draft_tree_many", (reqs,), {})
+        return self._d.draft_tree_many(reqs, taps)
+
+    def absorb_rows_many(self, items, taps) -> None:
+        items = [(int(slot), [int(t) for t in tokens], int(pos0),
+                  rows if rows is None or isinstance(rows, tuple) else [int(r) for r in rows])
+                 for slot, tokens, pos0, rows in items]
+        self._l._send("drafter.absorb_rows_many", (items,), {})
+        self._d.absorb_rows_many(items, taps)
+
     def save_window(self, slot):
         sid = self._l.new_sid()
         self._l._send("drafter.save_window", (int(slot),), {"_sid": sid})
@@ -152,6 +169,8 @@ def _replay_drafter(drafter, engine, name: str, args, kwargs, snaps) -> None:
     elif name == "draft_tree":
         slot, tok, pos, depth, rows = args
         drafter.draft_tree(slot, tok, pos, engine.taps, depth, rows)
+    elif name in ("draft_many", "draft_tree_many", "absorb_rows_many"):
+        getattr(drafter, name)(args[0], engine.taps)
     elif name == "save_window":
         snaps[kwargs["_sid"]] = drafter.save_window(args[0])
     elif name == "restore_window":

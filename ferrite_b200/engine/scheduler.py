@@ -192,6 +192,20 @@ class Drafter:
         d = self.draft(slot, last_token, pos, taps, min(depth, rows))
         return list(d), list(range(len(d)))
 
+    def draft_many(self, reqs: Sequence[Tuple[int, int, int, int]], taps) -> List[List[int]]:
+        """`draft` for several requests of one step, reqs[i] = (slot, last_token, pos, n). A draft model overrides this
+        to run one pass for all of them; the default asks one by one."""
+        return [self.draft(slot, tok, pos, taps, n) for slot, tok, pos, n in reqs]
+
+    def draft_tree_many(self, reqs: Sequence[Tuple[int, int, int, int, int]], taps) -> List[Tuple[List[int], List[int]]]:
+        """`draft_tree` for several requests, reqs[i] = (slot, last_token, pos, depth, rows)."""
+        return [self.draft_tree(slot, tok, pos, taps, depth, rows) for slot, tok, pos, depth, rows in reqs]
+
+    def absorb_rows_many(self, items: Sequence[Tuple[int, Sequence[int], int, object]], taps) -> None:
+        """`absorb_rows` for several requests, items[i] = (slot, tokens, pos0, rows)."""
+        for slot, tokens, pos0, rows in items:
+            self.absorb_rows(slot, tokens, pos0, taps, rows)
+
     def absorb(self, slot: int, tokens: Sequence[int], pos0: int, taps) -> None:
         pass
 
@@ -622,10 +636,14 @@ class Scheduler:
     def _decode_step(self, decoders: List[Active]) -> int:
         """One decode / verify step over all decoding requests: a row per request plus its draft rows."""
         segs, drafts, trees, copies = [], [], [], []
+        # pass 1: every request's room and copy proposal; what the draft model is asked for is collected, so that it
+        # drafts for all requests in one pass of its own (reference `draft_many` / `draft_trees`, `sched.rs:58-116`)
+        rooms: List[int] = []
+        want_tree: List[Tuple[int, int, int, int, int]] = []          # (slot, last token, position, depth, rows)
+        want_chain: List[Tuple[int, int, int, int]] = []              # (slot, last token, position, n)
+        ask: List[Optional[Tuple[str, int]]] = []                     # per request: ("tree" | "chain", index into its list)
         for a in decoders:
-            d: List[int] = []
-            par: Optional[List[int]] = None
-            copy: List[int] = []
+            room, copy, what = 0, [], None
             if self.opts.spec > 0:
                 room = min(self.opts.spec, DECODE_ROWS - 1, a.req.sampling.max_tokens - len(a.out) - 1,
                            self.eng.ecfg.max_ctx - a.pos - 2)
@@ -634,22 +652,38 @@ class Scheduler:
                         a.copier.sync(a.req.prompt + a.out[:-1] + [a.next_token])
                         copy = a.copier.propose(room, adaptive=self.opts.copy_adaptive)
                     if self.drafter is not None and self.opts.tree_rows > 0:
-                        # the draft model's tree, with the copy proposal grafted onto it: rows the tree already holds
-                        # are shared, the rest of the copy hangs below them as a chain (reference `graft`)
                         n_rows = min(self.opts.tree_rows, TREE_MAX_ROWS - 1, self.eng.ecfg.max_ctx - a.pos - 2)
-                        d, dp = self.drafter.draft_tree(a.slot, a.next_token, a.pos, self.eng.taps, room, n_rows)
-                        toks, pars = [a.next_token] + [int(t) for t in d[:n_rows]], [-1] + [int(p) for p in dp[:n_rows]]
-                        if copy:
-                            graft(toks, pars, copy, TREE_MAX_ROWS - len(toks))
-                        d = toks[1:]
-                        if d and pars[1:] != list(range(len(d))):
-                            par = pars
-                    elif copy:
-                        d = copy
-                    elif self.drafter is not None:
-                        d = self.drafter.draft(a.slot, a.next_token, a.pos, self.eng.taps, room)
-                    d = [int(t) for t in (d if par is not None else d[:room])]
-            copies.append(copy if (par is not None or d[:len(copy)] == copy) else [])
+                        what = ("tree", len(want_tree))
+                        want_tree.append((a.slot, a.next_token, a.pos, room, n_rows))
+                    elif not copy and self.drafter is not None:
+                        what = ("chain", len(want_chain))
+                        want_chain.append((a.slot, a.next_token, a.pos, room))
+            rooms.append(room)
+            copies.append(copy)
+            ask.append(what)
+        got_tree = self.drafter.draft_tree_many(want_tree, self.eng.taps) if want_tree else []
+        got_chain = self.drafter.draft_many(want_chain, self.eng.taps) if want_chain else []
+        # pass 2: the rows of every request
+        for a, room, copy, what in zip(decoders, rooms, list(copies), ask):
+            d: List[int] = []
+            par: Optional[List[int]] = None
+            if what is not None and what[0] == "tree":
+                # the draft model's tree, with the copy proposal grafted onto it: rows the tree already holds are
+                # shared, the rest of the copy hangs below them as a chain (reference `graft`)
+                n_rows = want_tree[what[1]][4]
+                d, dp = got_tree[what[1]]
+                toks, pars = [a.next_token] + [int(t) for t in d[:n_rows]], [-1] + [int(p) for p in dp[:n_rows]]
+                if copy:
+                    graft(toks, pars, copy, TREE_MAX_ROWS - len(toks))
+                d = toks[1:]
+                if d and pars[1:] != list(range(len(d))):
+                    par = pars
+            elif copy:
+                d = copy
+            elif what is not None:
+                d = got_chain[what[1]]
+            d = [int(t) for t in (d if par is not None else d[:room])]
+            copies[len(drafts)] = copy if (par is not None or d[:len(copy)] == copy) else []
             drafts.append(d)
             trees.append(par)
             segs.append(Segment(a.slot, a.pos, [a.next_token] + d, "all", parents=par))
@@ -664,6 +698,8 @@ class Scheduler:
                     self._finish(a, "error", message="non-finite logits")
                 return len(rows)
         keep, paths, r = [], [], 0
+        absorbs: List[Tuple[int, List[int], int, object]] = []        # (slot, tokens fed, first position, tap rows)
+        accepts: List[Tuple[Active, List[int]]] = []
         taps = self.eng.taps
         any_tree = any(t is not None for t in trees)
         dev_ids = None
@@ -702,9 +738,8 @@ class Scheduler:
                     landed = next((j for j, (x, y) in enumerate(zip(fed[1:], copy)) if x != y), min(len(fed) - 1, len(copy)))
                     a.copier.observe(len(copy), landed)
                 a.pos += len(new)
-                if self.drafter is not None:
-                    self.drafter.absorb_rows(a.slot, fed, a.pos - len(new), taps, [r + i for i in path])
-                self._accept(a, new, sampled=not all_greedy)
+                absorbs.append((a.slot, fed, a.pos - len(new), [r + i for i in path]))
+                accepts.append((a, new))
                 r += n
                 continue
             if all_greedy:
@@ -731,14 +766,20 @@ class Scheduler:
                 a.copier.observe(len(copy), min(acc, len(copy)))
             fed = [a.next_token] + d[:acc]
             a.pos += len(new)
-            if self.drafter is not None:
-                self.drafter.absorb_rows(a.slot, fed, a.pos - len(new), taps, (r, r + len(new)))
-            self._accept(a, new, sampled=not all_greedy)
+            absorbs.append((a.slot, fed, a.pos - len(new), (r, r + len(new))))
+            accepts.append((a, new))
             r += n
+        # the draft model takes the kept rows of all requests in one pass; the target's state advances along the kept
+        # rows; only then are the tokens handed out: a request that ends here snapshots its slot for the next turn,
+        # and that snapshot must hold the committed state and the drafter's absorbed rows
+        if self.drafter is not None:
+            self.drafter.absorb_rows_many(absorbs, taps)
         if spec and any_tree:
             self.eng.commit_tree(paths)
         elif spec:
             self.eng.commit_verified(keep)
+        for a, new in accepts:
+            self._accept(a, new, sampled=not all_greedy)
         if self.opts.prof >= 2 and spec:
             # per request of this verify step: slot, rows fed (1 + drafts) and the accepted path's row indices; what
             # `tools/sched_budget.py` replays under smaller draft budgets

@@ -158,6 +158,75 @@ class BlockDrafter(Drafter):
         lp, ids = lp.tolist(), ids.tolist()
         return grow_tree([list(zip(ids[d], lp[d])) for d in range(n)], rows)
 
+    # ---- several requests of one step in one pass of the drafter --------------------------------------------------
+    def _block_pass(self, reqs, greedy: bool):
+        """One forward over [last token, MASK ...] blocks of several slots. reqs: (slot, last_token, pos, n) with n > 0.
+        Returns the forward's (logits, picks) with the requests' rows back to back."""
+        segs, adds = [], []
+        any_feat = any(self.last_feat[slot] is not None for slot, _, _, _ in reqs)
+        for slot, tok, pos, n in reqs:
+            segs.append(Segment(slot, pos - self.base[slot], [tok] + [self.mask_token] * (n - 1), "all"))
+            if any_feat:
+                f = self.last_feat[slot]
+                adds.append(f.expand(n, -1) if f is not None else
+                            torch.zeros(n, self.eng.full_cfg.hidden, device=self.eng.device, dtype=self.eng.dtype))
+        x_add = torch.cat(adds).contiguous() if any_feat else None
+        logits, picks, _ = self.eng.forward(segs, commit=False, greedy=greedy, x_add=x_add)
+        return logits, picks
+
+    def draft_many(self, reqs, taps) -> List[List[int]]:
+        live = [(i, slot, tok, pos, min(n, self.block)) for i, (slot, tok, pos, n) in enumerate(reqs) if min(n, self.block) > 0]
+        out: List[List[int]] = [[] for _ in reqs]
+        if len(live) == 1:
+            i, slot, tok, pos, n = live[0]
+            out[i] = self.draft(slot, tok, pos, taps, n)
+        elif live:
+            _, picks = self._block_pass([x[1:] for x in live], greedy=True)
+            ids, r = picks[0].tolist(), 0
+            for i, _, _, _, n in live:
+                out[i] = [int(t) for t in ids[r:r + n]]
+                r += n
+        return out
+
+    def draft_tree_many(self, reqs, taps):
+        live = [(i, slot, tok, pos, min(depth, self.block), rows) for i, (slot, tok, pos, depth, rows) in enumerate(reqs)
+                if min(depth, self.block) > 0 and rows > 0]
+        out = [([], []) for _ in reqs]
+        if len(live) == 1:
+            i, slot, tok, pos, n, rows = live[0]
+            out[i] = self.draft_tree(slot, tok, pos, taps, n, rows)
+        elif live:
+            logits, _ = self._block_pass([x[1:5] for x in live], greedy=False)
+            lp, ids = torch.log_softmax(logits.float(), -1).topk(min(self.tree_k, logits.shape[-1]), -1)
+            lp, ids, r = lp.tolist(), ids.tolist(), 0
+            for i, _, _, _, n, rows in live:
+                out[i] = grow_tree([list(zip(ids[r + d], lp[r + d])) for d in range(n)], rows)
+                r += n
+        return out
+
+    def absorb_rows_many(self, items, taps) -> None:
+        """Kept rows of several requests into the drafter's cache in one forward (whole-context mode; a bounded window
+        keeps its per-slot path, whose rebuilds do not batch)."""
+        from ..engine.scheduler import select_rows
+        items = [it for it in items if len(it[1]) > 0]
+        if self.window or len(items) <= 1 or not taps or self.n_taps == 0:
+            for slot, tokens, pos0, rows in items:
+                self.absorb_rows(slot, tokens, pos0, taps, rows)
+            return
+        segs, feats = [], []
+        for slot, tokens, pos0, rows in items:
+            sel = select_rows(taps, rows)
+            n = len(tokens)
+            if sel[0].shape[0] < n:                          # fewer tap rows than tokens: the per-slot path decides
+                for it in items:
+                    self.absorb_rows(it[0], it[1], it[2], taps, it[3])
+                return
+            feats.append(self._fused(sel, slice(0, n)))
+            segs.append(Segment(slot, pos0, [int(t) for t in tokens], "none"))
+        self.eng.forward(segs, commit=True, x_add=torch.cat(feats).contiguous())
+        for (slot, _, _, _), f in zip(items, feats):
+            self.last_feat[slot] = f[-1:].clone()
+
     def save_window(self, slot: int):
         return {"len": self.eng.slot_len[slot], "feat": self.last_feat[slot], "base": self.base[slot]}
 

@@ -486,3 +486,76 @@ def test_common_prefix_matches_the_token_by_token_loop():
         b = a[:rng.randrange(0, n + 1)] + [rng.randrange(3) for _ in range(rng.randrange(0, 40))]
         want = next((i for i, (x, y) in enumerate(zip(a, b)) if x != y), min(len(a), len(b)))
         assert common_prefix(a, b) == want and common_prefix(tuple(a), b) == want
+
+
+def test_end_of_reply_snapshot_in_a_verify_step_holds_the_committed_state():
+    """A request that ends inside a speculative step snapshots its slot for the next turn: the snapshot must hold the
+    recurrent state after the accepted rows were committed (it is labelled with that position), not the state the step
+    started from."""
+    import torch
+
+    from ferrite_b200.config import EngineConfig, tiny_hybrid
+    from ferrite_b200.engine.engine import Engine
+    from ferrite_b200.engine.sampler import Sampling
+    from ferrite_b200.engine.scheduler import SchedOptions, Scheduler, generate
+    from ferrite_b200.models.drafter import OracleDrafter
+    cfg = tiny_hybrid()
+    g = torch.Generator().manual_seed(1)
+    p1 = torch.randint(1, cfg.vocab, (40,), generator=g).tolist()
+    mk = lambda: Engine(cfg, None, EngineConfig(n_slots=1, max_ctx=256, prefill_chunk=64), device="cpu")
+    for n_out in (9, 12):
+        out1 = mk().generate(p1, n_out)
+        eng = mk()
+        dr = OracleDrafter(1.0, cfg.vocab)
+        dr.set_truth(0, len(p1), out1)
+        sched = Scheduler(eng, SchedOptions(spec=4, arrival_ms=0), drafter=dr)
+        assert generate(sched, [p1], Sampling(max_tokens=n_out))[0] == out1
+        assert sched.stats["accepted"] > 0
+        snap = sched.slot_cache[0].snaps[-1]
+        assert snap.pos == len(p1) + n_out - 1
+        ref = mk()
+        ref.prefill(0, (p1 + out1)[:snap.pos])
+        want = ref.ex.state_save(0)
+        assert float((want["rec"] - snap.state["gdn"]["rec"]).abs().max()) < 1e-5
+        assert float((want["conv"] - snap.state["gdn"]["conv"]).abs().max()) < 1e-5
+
+
+def test_drafter_passes_are_batched_over_the_requests_of_a_step():
+    """Three requests decoding together with a block drafter: the drafter runs one draft pass and one absorb pass per
+    step for all of them (not one per request), drafts what the one-by-one path drafts, and the text stays the plain one.
+    Chains and trees."""
+    import torch
+
+    from ferrite_b200.config import EngineConfig, tiny_hybrid
+    from ferrite_b200.engine.engine import Engine
+    from ferrite_b200.engine.sampler import Sampling
+    from ferrite_b200.engine.scheduler import Drafter, SchedOptions, Scheduler, generate
+    from ferrite_b200.models.drafter import BlockDrafter, drafter_config_for
+    cfg = tiny_hybrid()
+    cfg.tap_layers = [0, 2]
+    g = torch.Generator().manual_seed(6)
+    prompts = [torch.randint(1, cfg.vocab, (n,), generator=g).tolist() for n in (20, 33, 27)]
+    mk = lambda: Engine(cfg, None, EngineConfig(n_slots=3, max_ctx=256, prefill_chunk=64), device="cpu")
+    plain = generate(Scheduler(mk(), SchedOptions(spec=0, arrival_ms=0)), prompts, Sampling(max_tokens=14))
+    for tree_rows in (0, 6):
+        stats = []
+        for batched in (True, False):
+            dr = BlockDrafter(drafter_config_for(cfg), target_hidden=cfg.hidden, n_taps=2, n_slots=3, max_ctx=256,
+                              device="cpu", block=6)
+            if not batched:                           # the interface's defaults: one request at a time
+                dr.draft_many = lambda reqs, taps, dr=dr: Drafter.draft_many(dr, reqs, taps)
+                dr.draft_tree_many = lambda reqs, taps, dr=dr: Drafter.draft_tree_many(dr, reqs, taps)
+                dr.absorb_rows_many = lambda items, taps, dr=dr: Drafter.absorb_rows_many(dr, items, taps)
+            calls = {"n": 0}
+            fwd = dr.eng.forward
+
+            def counted(*a, _fwd=fwd, _c=calls, **kw):
+                _c["n"] += 1
+                return _fwd(*a, **kw)
+            dr.eng.forward = counted
+            sched = Scheduler(mk(), SchedOptions(spec=4, tree_rows=tree_rows, arrival_ms=0), drafter=dr)
+            assert generate(sched, prompts, Sampling(max_tokens=14)) == plain
+            stats.append((sched.stats["drafted"], sched.stats["accepted"], calls["n"]))
+        (d1, a1, n1), (d0, a0, n0) = stats
+        assert (d1, a1) == (d0, a0) and d1 > 0          # the same drafts either way
+        assert n1 < 0.6 * n0, (n1, n0)                  # and far fewer passes of the draft model
