@@ -134,6 +134,38 @@ class MtpDrafter(Drafter):
             hidden, norm = self.eng.ex.last_hidden[-1:].clone(), self.eng.ex.w["final_norm"]
         return out
 
+    def draft_many(self, reqs, taps) -> List[List[int]]:
+        """The chains of several requests, one head pass per depth for all of them (reqs[i] = (slot, last_token, pos, n))."""
+        out: List[List[int]] = [[] for _ in reqs]
+        live = []
+        for i, (slot, tok, pos, n) in enumerate(reqs):
+            kept = self.kept[slot]
+            n = min(n, self.depth)
+            if n > 0 and kept is not None and kept[0] == pos - 1:
+                live.append({"i": i, "slot": slot, "pos": pos, "n": n, "hidden": kept[1], "tok": int(tok)})
+        if len(live) <= 1:
+            for x in live:
+                out[x["i"]] = self.draft(x["slot"], x["tok"], x["pos"], taps, x["n"])
+            return out
+        norm = self.tnorm
+        for j in range(max(x["n"] for x in live)):
+            act = [x for x in live if j < x["n"]]
+            rows = self._rows([x["tok"] for x in act], torch.cat([x["hidden"] for x in act], 0), norm)
+            segs = []
+            for x in act:
+                if self.base[x["slot"]] is None:
+                    self.base[x["slot"]] = x["pos"] - 1
+                segs.append(Segment(x["slot"], x["pos"] - 1 + j - self.base[x["slot"]], [0], "last"))
+            _, picks, _ = self.eng.forward(segs, commit=False, greedy=True, x_add=rows)
+            ids = picks[0].tolist()
+            hid = self.eng.ex.last_hidden
+            for k, x in enumerate(act):
+                x["tok"] = int(ids[k])
+                x["hidden"] = hid[k:k + 1].clone()
+                out[x["i"]].append(x["tok"])
+            norm = self.eng.ex.w["final_norm"]
+        return out
+
     def save_window(self, slot: int):
         return {"len": self.eng.slot_len[slot], "base": self.base[slot], "kept": self.kept[slot]}
 

@@ -559,3 +559,27 @@ def test_drafter_passes_are_batched_over_the_requests_of_a_step():
         (d1, a1, n1), (d0, a0, n0) = stats
         assert (d1, a1) == (d0, a0) and d1 > 0          # the same drafts either way
         assert n1 < 0.6 * n0, (n1, n0)                  # and far fewer passes of the draft model
+
+
+def test_mtp_head_drafts_for_all_requests_of_a_step_in_one_pass_per_depth():
+    from ferrite_b200.engine.scheduler import Drafter
+    stats = []
+    for batched in (True, False):
+        cfg, w, eng, dr = _mtp_setup(n_slots=3)
+        if not batched:
+            dr.draft_many = lambda reqs, taps, dr=dr: Drafter.draft_many(dr, reqs, taps)
+        calls = {"n": 0}
+        fwd = dr.eng.forward
+
+        def counted(*a, _fwd=fwd, _c=calls, **kw):
+            _c["n"] += 1
+            return _fwd(*a, **kw)
+        dr.eng.forward = counted
+        sched = Scheduler(eng, SchedOptions(spec=3, copy_rows=False, arrival_ms=0), drafter=dr)
+        prompts = [_prompt(cfg, n, 70 + n) for n in (25, 31, 19)]
+        out = generate(sched, prompts, Sampling(max_tokens=12))
+        for p, o in zip(prompts, out):
+            assert o == _plain(cfg, w, p, 12)
+        stats.append((sched.stats["drafted"], sched.stats["accepted"], calls["n"]))
+    assert stats[0][:2] == stats[1][:2] and stats[0][0] > 0
+    assert stats[0][2] < stats[1][2]
