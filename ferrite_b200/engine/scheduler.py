@@ -726,6 +726,8 @@ class Scheduler:
                 # greedy: the target's picks of all rows are known, the walk runs in C++ when the extension is built
                 path, new = tree_walk([a.next_token] + d, par,
                                       [int(t) for t in ids[r:r + 1 + len(d)]] if all_greedy else pick)
+                cut = self._stop_cut(a, new)
+                path, new = path[:cut], new[:cut]
                 paths.append(path)
                 keep.append(len(new))
                 acc = len(new) - 1
@@ -755,6 +757,7 @@ class Scheduler:
                 a.sampler.observe(new[0])
             else:
                 new = a.sampler.spec_accept(logits[r:r + n], d)
+            new = new[:self._stop_cut(a, new)]
             acc = len(new) - 1
             keep.append(len(new))
             paths.append(list(range(len(new))))
@@ -785,6 +788,17 @@ class Scheduler:
             # `tools/sched_budget.py` replays under smaller draft budgets
             self._last_verify = {"slots": [a.slot for a in decoders], "rows": [1 + len(d) for d in drafts], "paths": paths}
         return len(rows)
+
+    @staticmethod
+    def _stop_cut(a: Active, new: List[int]) -> int:
+        """How many of a verify step's accepted tokens count: up to and including the first stop token. Rows behind it
+        are not committed, so the slot ends where the reply ends and its end-of-reply snapshot serves the next turn."""
+        stops = a.req.sampling.stop_ids
+        if stops:
+            for i, t in enumerate(new):
+                if t in stops:
+                    return i + 1
+        return len(new)
 
     # ---- bookkeeping --------------------------------------------------------------------------------
     def _snapshot(self, a: Active, pinned: bool = False) -> None:

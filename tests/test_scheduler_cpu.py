@@ -639,3 +639,49 @@ def test_every_snapshot_holds_the_state_of_its_prefix(seed, kind):
         for key, e in sched.park.entries.items():
             check(e, e.tokens, f"park {key} turn {turn}")
     assert sched.stats["cached_tokens"] > 0 and sched.stats["accepted"] > 0
+
+
+def test_stop_token_inside_a_verify_step_leaves_a_resumable_slot():
+    """The stop token is accepted in the middle of a verify step: the rows behind it are not committed, the reply ends
+    there, and the next turn (reply + stop token + new text) resumes from the end-of-reply snapshot with the true state."""
+    import torch
+
+    from ferrite_b200.config import EngineConfig, tiny_hybrid
+    from ferrite_b200.engine.engine import Engine
+    from ferrite_b200.models.drafter import OracleDrafter
+    cfg = tiny_hybrid()
+    mk = lambda: Engine(cfg, None, EngineConfig(n_slots=1, max_ctx=512, prefill_chunk=64), device="cpu")
+    ref = mk()
+    hits = 0
+    for seed in range(40):
+        g = torch.Generator().manual_seed(300 + seed)
+        p = torch.randint(1, cfg.vocab, (30,), generator=g).tolist()
+        ref.reset_slot(0)
+        plain = ref.generate(p, 12, slot=0)
+        j = next((i for i in range(2, 9) if plain[i] not in plain[:i]), None)   # a stop token first seen mid-reply
+        if j is None:
+            continue
+        hits += 1
+        eng = mk()
+        dr = OracleDrafter(1.0, cfg.vocab)
+        dr.set_truth(0, len(p), plain)
+        sched = Scheduler(eng, SchedOptions(spec=6, arrival_ms=0), drafter=dr)
+        out = generate(sched, [p], Sampling(max_tokens=12, stop_ids=[plain[j]]))[0]
+        assert out == plain[:j]
+        assert eng.slot_len[0] == len(p) + j                  # nothing behind the reply was committed
+        snap = sched.slot_cache[0].snaps[-1]
+        assert snap.pos == len(p) + j
+        ref.reset_slot(0)
+        ref.prefill(0, (p + plain)[:snap.pos])
+        want = ref.ex.state_save(0)
+        assert float((want["rec"] - snap.state["gdn"]["rec"]).abs().max()) < 1e-5
+        p2 = p + out + [plain[j]] + torch.randint(1, cfg.vocab, (5,), generator=g).tolist()
+        ref.reset_slot(0)
+        want2 = ref.generate(p2, 5, slot=0)
+        dr.truth.clear()
+        before = sched.stats["cached_tokens"]
+        assert generate(sched, [p2], Sampling(max_tokens=5))[0] == want2
+        assert sched.stats["cached_tokens"] - before == len(p) + j
+        if hits >= 3:
+            break
+    assert hits >= 1
