@@ -685,3 +685,33 @@ def test_stop_token_inside_a_verify_step_leaves_a_resumable_slot():
         if hits >= 3:
             break
     assert hits >= 1
+
+
+@pytest.mark.parametrize("seed", [3, 4])
+def test_kv_pages_are_never_lost_or_held_twice(seed):
+    """Random multi-turn traffic over few slots and a small page pool (conversations are parked, resumed, evicted): after
+    every round each KV page is in exactly one place: a slot's table, a parked entry, or the free list."""
+    import random
+
+    import torch
+
+    from ferrite_b200.config import EngineConfig, tiny_hybrid
+    from ferrite_b200.engine.engine import Engine
+    cfg = tiny_hybrid()
+    rnd = random.Random(seed)
+    g = torch.Generator().manual_seed(900 + seed)
+    eng = Engine(cfg, None, EngineConfig(n_slots=rnd.choice([1, 2, 3]), max_ctx=1024, prefill_chunk=64,
+                                         kv_block=rnd.choice([16, 64])), device="cpu")
+    sched = Scheduler(eng, SchedOptions(spec=rnd.choice([0, 4]), arrival_ms=0))
+    convs = [torch.randint(1, cfg.vocab, (rnd.randint(20, 200),), generator=g).tolist() for _ in range(5)]
+    for turn in range(6):
+        ks = rnd.sample(range(5), rnd.choice([1, 2, 3]))
+        outs = generate(sched, [convs[i] for i in ks], Sampling(max_tokens=rnd.randint(2, 10)))
+        for i, o in zip(ks, outs):
+            convs[i] = convs[i] + o + torch.randint(1, cfg.vocab, (rnd.randint(1, 30),), generator=g).tolist()
+            if len(convs[i]) > 800:
+                convs[i] = convs[i][:100]
+        pool = eng.ex.pool
+        held = [b for s in eng.ex.slot_blocks for b in s] + [b for e in sched.park.entries.values() for b in e.blocks]
+        pages = held + list(pool.free)
+        assert len(pages) == len(set(pages)) == pool.n_blocks, (turn, len(pages), len(set(pages)), pool.n_blocks)
