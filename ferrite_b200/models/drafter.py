@@ -264,6 +264,18 @@ class OracleDrafter(Drafter):
     def draft(self, slot: int, last_token: int, pos: int, taps, n: int) -> List[int]:
         if self.cost_model is not None:
             self.cost_model.draft(slot, last_token, pos, taps, n)
+        return self._pick(slot, pos, n)
+
+    def draft_many(self, reqs, taps) -> List[List[int]]:
+        if self.cost_model is not None:
+            self.cost_model.draft_many(reqs, taps)           # one pass of the real drafter for all requests, as in serving
+        return [self._pick(slot, pos, n) for slot, _, pos, n in reqs]
+
+    def absorb_rows_many(self, items, taps) -> None:
+        if self.cost_model is not None:
+            self.cost_model.absorb_rows_many(items, taps)
+
+    def _pick(self, slot: int, pos: int, n: int) -> List[int]:
         if slot not in self.truth or n <= 0:
             return []
         pos0, toks = self.truth[slot]
