@@ -625,10 +625,11 @@ class Scheduler:
         a.pending = a.pending[cut:]
         self.slot_cache[a.slot].tokens = (a.req.prompt + a.out)[:a.pos]
         self.stats["prompt_tokens"] += cut
+        if self.drafter:
+            # before the snapshot: the drafter window saved with it must end at the snapshot's position
+            self.drafter.absorb_rows(a.slot, toks, a.pos - cut, self.eng.taps, tap_rows)
         if a.pos in a.snap_at:
             self._snapshot(a, pinned=(a.pos == a.snap_at[0]))
-        if self.drafter:
-            self.drafter.absorb_rows(a.slot, toks, a.pos - cut, self.eng.taps, tap_rows)
         if last:
             a.t_prompt_done = time.time()
             self._accept(a, [tok])

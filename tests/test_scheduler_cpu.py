@@ -629,7 +629,8 @@ def test_every_snapshot_holds_the_state_of_its_prefix(seed, kind):
     for turn in range(4):
         ks = rnd.sample(range(3), rnd.choice([1, 2]))
         n_out = rnd.randint(3, 12)
-        outs = generate(sched, [convs[i] for i in ks], Sampling(max_tokens=n_out))
+        hints = [[64 * rnd.randint(1, max(1, len(convs[i]) // 64))] if len(convs[i]) > 64 else [] for i in ks]
+        outs = generate(sched, [convs[i] for i in ks], Sampling(max_tokens=n_out), snapshots=hints)
         for i, o in zip(ks, outs):
             ref.reset_slot(0)
             assert o == ref.generate(convs[i], n_out, slot=0), (turn, i)
