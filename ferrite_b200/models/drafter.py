@@ -59,6 +59,10 @@ class BlockDrafter(Drafter):
         self.n_taps = n_taps
         self.fuse = (torch.randn(cfg.hidden, n_taps * target_hidden, generator=g) * 0.02).to(self.eng.device, self.eng.dtype)
         self.last_feat = [None] * n_slots            # fused features of the last committed row of each slot
+        # rolling signature of the tokens held at the drafter's local positions 0 .. len - 1 of each slot: sig[i] covers
+        # the first i tokens. A window snapshot is only rolled back to when the slot still holds the snapshot's tokens
+        # (a snapshot restored into a slot that another conversation has used since finds other rows there)
+        self.sigs = [[0] for _ in range(n_slots)]
 
     def _fused(self, taps, rows: slice) -> Optional[torch.Tensor]:
         if not taps or self.n_taps == 0:
@@ -71,6 +75,31 @@ class BlockDrafter(Drafter):
         self.last_feat[slot] = None
         self.base[slot] = 0
         self.hist[slot] = []
+        self.sigs[slot] = [0]
+
+    _SIG_P, _SIG_M = 1000003, (1 << 61) - 1
+
+    def _note(self, slot: int, local: int, tokens: Sequence[int]) -> None:
+        """Tokens were written at the slot's local positions local .. local + n - 1."""
+        sg = self.sigs[slot]
+        del sg[local + 1:]
+        if len(sg) != local + 1:                     # rows below `local` that this drafter never wrote: no valid signature
+            sg[:] = [0] + [-1] * local
+        for t in tokens:
+            sg.append((sg[-1] * self._SIG_P + int(t) + 1) % self._SIG_M if sg[-1] >= 0 else -1)
+
+    def _place(self, slot: int, pos0: int) -> int:
+        """Local position of target position pos0 in the slot's cache (whole-context mode). An empty slot starts its own
+        positions at pos0; a gap behind the rows it holds (a restore the drafter could not follow) starts it over."""
+        if self.eng.slot_len[slot] == 0:
+            self.base[slot] = pos0
+        local = pos0 - self.base[slot]
+        if local < 0 or local > self.eng.slot_len[slot]:
+            self.eng.reset_slot(slot)
+            self.sigs[slot] = [0]
+            self.base[slot] = pos0
+            local = 0
+        return local
 
     def _hist_tokens(self, slot: int) -> int:
         return sum(len(t) for t, _ in self.hist[slot])
@@ -105,7 +134,7 @@ class BlockDrafter(Drafter):
         if n == 0:
             return
         feat = self._fused(taps, slice(0, n)) if taps and taps[0].shape[0] >= n else None
-        local = pos0
+        local = pos0 if self.window else self._place(slot, pos0)
         if self.window and n > self.window:
             # a commit longer than the window (a prompt chunk): only its last `window` rows can matter afterwards
             cut = n - self.window
@@ -124,13 +153,16 @@ class BlockDrafter(Drafter):
                 feats = [f for _, f in self.hist[slot]]
                 self.eng.reset_slot(slot)
                 self.base[slot] = pos0 - len(kept)
+                self.sigs[slot] = [0]
                 if kept:
                     x_add = torch.cat(feats) if all(f is not None for f in feats) else None
                     self.eng.forward([Segment(slot, 0, kept, "none")], commit=True, x_add=x_add)
+                    self._note(slot, 0, kept)
                 local = len(kept)
             self.hist[slot].append(([int(t) for t in tokens], None if feat is None else feat.clone()))
             self._hist_trim(slot, self.window)
         self.eng.forward([Segment(slot, local, list(tokens), "none")], commit=True, x_add=feat)
+        self._note(slot, local, tokens)
         if feat is not None:
             self.last_feat[slot] = feat[-1:].clone()
 
@@ -222,24 +254,33 @@ class BlockDrafter(Drafter):
                     self.absorb_rows(it[0], it[1], it[2], taps, it[3])
                 return
             feats.append(self._fused(sel, slice(0, n)))
-            segs.append(Segment(slot, pos0, [int(t) for t in tokens], "none"))
+            segs.append(Segment(slot, self._place(slot, pos0), [int(t) for t in tokens], "none"))
         self.eng.forward(segs, commit=True, x_add=torch.cat(feats).contiguous())
-        for (slot, _, _, _), f in zip(items, feats):
+        for (slot, tokens, _, _), seg, f in zip(items, segs, feats):
+            self._note(slot, seg.pos0, tokens)
             self.last_feat[slot] = f[-1:].clone()
 
     def save_window(self, slot: int):
-        return {"len": self.eng.slot_len[slot], "feat": self.last_feat[slot], "base": self.base[slot]}
+        n = self.eng.slot_len[slot]
+        sg = self.sigs[slot]
+        return {"len": n, "feat": self.last_feat[slot], "base": self.base[slot], "sig": sg[n] if n < len(sg) else -1}
 
     def restore_window(self, slot: int, blob) -> None:
-        # the drafter's KV rows up to the snapshot position are still in its slot; only the length rolls back. A slot
-        # that was rebuilt since the snapshot (windowed mode) no longer holds those rows: it starts over, empty.
-        if blob is None or blob.get("base", 0) != self.base[slot]:
+        # When the slot still holds the snapshot's rows (same local positions, same tokens: the signature tells), only
+        # the length rolls back. A slot that was rebuilt since (windowed mode), or that another conversation has used
+        # (a snapshot restored into another slot), does not hold them: the drafter starts over, empty, from the next
+        # absorbed row.
+        sg = self.sigs[slot]
+        n = -1 if blob is None else int(blob["len"])
+        if (blob is None or blob.get("base", 0) != self.base[slot] or n > self.eng.slot_len[slot] or n >= len(sg)
+                or sg[n] < 0 or sg[n] != blob.get("sig", -1)):
             self.reset(slot)
             return
         cur = self.eng.slot_len[slot]
-        self.eng.slot_len[slot] = min(cur, blob["len"])
-        if self.window and cur > blob["len"]:
-            self._hist_drop_tail(slot, cur - blob["len"])
+        self.eng.slot_len[slot] = n
+        del sg[n + 1:]
+        if self.window and cur > n:
+            self._hist_drop_tail(slot, cur - n)
         self.last_feat[slot] = blob["feat"]
 
 

@@ -79,6 +79,7 @@ class MtpDrafter(Drafter):
         self.cfg = cfg
         self.base: List[Optional[int]] = [None] * n_slots    # target position of the head's cache row 0
         self.kept: List[Optional[tuple]] = [None] * n_slots  # (position, target hidden row) awaiting its next token
+        self.gen = [0] * n_slots                             # bumped when a slot's cache starts over: dates window snapshots
 
     # ---- the head's input rows -------------------------------------------------------------------------
     def _rows(self, tokens: Sequence[int], hidden: torch.Tensor, src_norm: torch.Tensor) -> torch.Tensor:
@@ -102,6 +103,7 @@ class MtpDrafter(Drafter):
         self.eng.reset_slot(slot)
         self.base[slot] = None
         self.kept[slot] = None
+        self.gen[slot] += 1
 
     def absorb(self, slot: int, tokens: Sequence[int], pos0: int, taps) -> None:
         n = len(tokens)
@@ -167,11 +169,15 @@ class MtpDrafter(Drafter):
         return out
 
     def save_window(self, slot: int):
-        return {"len": self.eng.slot_len[slot], "base": self.base[slot], "kept": self.kept[slot]}
+        return {"len": self.eng.slot_len[slot], "base": self.base[slot], "kept": self.kept[slot], "slot": slot,
+                "gen": self.gen[slot]}
 
     def restore_window(self, slot: int, blob) -> None:
-        # the head's KV rows up to the snapshot position are still in its slot; only the length rolls back
-        if blob is None or blob["base"] != self.base[slot]:
+        # the head's KV rows up to the snapshot position are still in its slot when nothing started the slot over since
+        # (same slot, same generation): only the length rolls back. Otherwise (another conversation used the slot, or the
+        # snapshot comes back into another slot) the head starts over
+        if (blob is None or blob["base"] != self.base[slot] or blob.get("slot") != slot or blob.get("gen") != self.gen[slot]
+                or blob["len"] > self.eng.slot_len[slot]):
             self.reset(slot)
             return
         self.eng.slot_len[slot] = min(self.eng.slot_len[slot], blob["len"])

@@ -617,7 +617,8 @@ def test_every_snapshot_holds_the_state_of_its_prefix(seed, kind):
             for k in ("rec", "conv"):
                 assert float((w[k] - sn.state["gdn"][k]).abs().max()) < 1e-4, (where, sn.pos, k)
             blob = sn.state.get("draft")
-            assert blob is None or blob["len"] == sn.pos, (where, sn.pos, blob["len"])
+            # (a drafter that started over after a restore it could not follow counts its rows from `base`)
+            assert blob is None or blob["base"] + blob["len"] == sn.pos, (where, sn.pos, blob["base"], blob["len"])
 
     rnd = random.Random(seed)
     g = torch.Generator().manual_seed(seed)
@@ -716,3 +717,48 @@ def test_kv_pages_are_never_lost_or_held_twice(seed):
         held = [b for s in eng.ex.slot_blocks for b in s] + [b for e in sched.park.entries.values() for b in e.blocks]
         pages = held + list(pool.free)
         assert len(pages) == len(set(pages)) == pool.n_blocks, (turn, len(pages), len(set(pages)), pool.n_blocks)
+
+
+def test_drafter_window_is_not_rolled_back_onto_another_conversations_rows():
+    """A window snapshot names rows of the drafter's cache. Restored into a slot that holds other tokens at those rows
+    (another conversation used it, or it is another slot), the drafter must start over instead of drafting from foreign
+    rows; restored into the slot that still holds them, only the length rolls back."""
+    import torch
+
+    from ferrite_b200.config import EngineConfig, tiny_hybrid
+    from ferrite_b200.engine.engine import Engine
+    from ferrite_b200.engine.executor import Segment
+    from ferrite_b200.models.drafter import BlockDrafter, drafter_config_for
+    cfg = tiny_hybrid()
+    cfg.tap_layers = [0, 2]
+    eng = Engine(cfg, None, EngineConfig(n_slots=2, max_ctx=256, prefill_chunk=64), device="cpu")
+    dr = BlockDrafter(drafter_config_for(cfg), target_hidden=cfg.hidden, n_taps=2, n_slots=2, max_ctx=256, device="cpu", block=6)
+    g = torch.Generator().manual_seed(8)
+    a = torch.randint(1, cfg.vocab, (60,), generator=g).tolist()
+    b = torch.randint(1, cfg.vocab, (60,), generator=g).tolist()
+
+    def feed(slot, toks, lo, hi):
+        eng.forward([Segment(slot, lo, toks[lo:hi], "none")], commit=True)
+        dr.absorb(slot, toks[lo:hi], lo, eng.taps)
+    feed(0, a, 0, 40)
+    blob = dr.save_window(0)
+    want = dr.draft(0, a[40], 40, eng.taps, 6)
+    feed(0, a, 40, 60)
+    dr.restore_window(0, blob)                                  # same slot, same rows: a rollback
+    assert dr.eng.slot_len[0] == 40 and dr.draft(0, a[40], 40, eng.taps, 6) == want
+    # another conversation takes the slot, then the first one's snapshot comes back
+    eng.reset_slot(0)
+    dr.reset(0)
+    feed(0, b, 0, 50)
+    dr.restore_window(0, blob)
+    assert dr.eng.slot_len[0] == 0 and dr.last_feat[0] is None      # started over: conversation b's rows are not a's
+    # and into the other slot, which never held them
+    feed(1, b, 0, 45)
+    dr.restore_window(1, blob)
+    assert dr.eng.slot_len[1] == 0
+    # a drafter that started over works from the next absorbed row on, in its own positions
+    eng.reset_slot(1)
+    eng.forward([Segment(1, 0, a[:40], "none")], commit=True)
+    feed(1, a, 40, 52)
+    assert dr.base[1] == 40 and dr.eng.slot_len[1] == 12
+    assert len(dr.draft(1, a[52], 52, eng.taps, 6)) == 6
