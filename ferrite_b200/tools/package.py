@@ -6,7 +6,7 @@ bench and entry scripts, the docs and profiles.
 Output: DIR/ferrite-b200-<version>-sm100a.tar.gz and its .sha256 (DIR defaults to dist/); <version> is the package's
 `__version__`, `--dev` adds `git describe` to the name. Inside the archive, under one top folder of the same name:
   ferrite_b200/          the package: Python, `csrc/` (every kernel's source), `_C.so` (built for sm_100a)
-  bench.py, __graft_entry__.py, README.md, DESIGN.md, profiles/, tests/
+  bench.py, __graft_entry__.py, README.md, profiles/, tests/
   BUILD-INFO             commit, describe, build time, Python / PyTorch / CUDA versions, the nvcc arch flags, and the
                          SHA-256 of every file in the archive
 Unpacked, the release runs from its own folder (`python -m ferrite_b200.server ...`); `python -m
@@ -34,7 +34,7 @@ import tarfile
 import time
 from typing import Dict, List, Tuple
 
-ROOT_FILES = ["bench.py", "__graft_entry__.py", "README.md", "DESIGN.md"]
+ROOT_FILES = ["bench.py", "__graft_entry__.py", "README.md"]
 ROOT_DIRS = ["ferrite_b200", "profiles", "tests"]
 SKIP_DIRS = {"__pycache__", "build", ".pytest_cache", ".hypothesis"}
 SKIP_SUFFIXES = (".pyc", ".o", ".a", ".ncu-rep")
